@@ -1,0 +1,169 @@
+"""ctypes binding of libsplash_b200.so. There is no fallback: if the library is missing or a call
+fails, an exception says so."""
+import ctypes
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_PATH = os.path.join(_HERE, "libsplash_b200.so")
+
+FMT_Q4K, FMT_Q6K, FMT_Q80, FMT_NVFP4, FMT_BF16, FMT_F16, FMT_F32 = 0, 4, 6, 37, 41, 42, 64
+EP_NONE, EP_RESIDUAL, EP_UP_WITH_GATE, EP_GATE_UP = 0, 1, 2, 3
+LINEAR_PDL = 1
+
+
+class SbError(RuntimeError):
+    pass
+
+
+class SbLinearArgs(ctypes.Structure):
+    _fields_ = [
+        ("weights", ctypes.c_void_p), ("weights2", ctypes.c_void_p), ("x", ctypes.c_void_p),
+        ("aux", ctypes.c_void_p), ("out", ctypes.c_void_p), ("norm_weight", ctypes.c_void_p),
+        ("format", ctypes.c_uint32), ("n", ctypes.c_uint32), ("k", ctypes.c_uint32), ("rows", ctypes.c_uint32),
+        ("x_stride", ctypes.c_uint32), ("aux_stride", ctypes.c_uint32), ("out_stride", ctypes.c_uint32),
+        ("epilogue", ctypes.c_uint32), ("out_f32", ctypes.c_uint32), ("flags", ctypes.c_uint32),
+    ]
+
+
+class SbLinearPlan(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_uint32) for n in
+                ("slices", "ctas", "tile_rows", "stages", "smem_bytes", "stage_blocks", "slice_blocks_max", "tiles")]
+
+
+_lib = None
+
+
+def load():
+    """The shared library; raises if it has not been built (python -c 'import __graft_entry__ as g; g.build()')."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(_PATH):
+            raise SbError(f"{_PATH} is missing: build it with `make -C splash_b200/csrc`; there is no CPU fallback")
+        _lib = ctypes.CDLL(_PATH)
+        _lib.sb_last_error.restype = ctypes.c_char_p
+        _lib.sb_row_bytes.restype = ctypes.c_uint64
+        _lib.sb_row_bytes.argtypes = [ctypes.c_uint32, ctypes.c_uint32]
+        for name in ("sb_alloc", "sb_host_alloc"):
+            getattr(_lib, name).argtypes = [ctypes.c_size_t, ctypes.POINTER(ctypes.c_void_p)]
+        _lib.sb_free.argtypes = [ctypes.c_void_p]
+        _lib.sb_host_free.argtypes = [ctypes.c_void_p]
+        _lib.sb_memset.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_void_p]
+        _lib.sb_upload.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+        _lib.sb_download.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
+        _lib.sb_stream_sync.argtypes = [ctypes.c_void_p]
+        _lib.sb_stream_destroy.argtypes = [ctypes.c_void_p]
+        _lib.sb_event_record.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        _lib.sb_event_sync.argtypes = [ctypes.c_void_p]
+        _lib.sb_event_destroy.argtypes = [ctypes.c_void_p]
+        _lib.sb_event_elapsed_ms.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_float)]
+        _lib.sb_graph_begin.argtypes = [ctypes.c_void_p]
+        _lib.sb_graph_end.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p)]
+        _lib.sb_graph_launch.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        _lib.sb_graph_destroy.argtypes = [ctypes.c_void_p]
+        _lib.sb_linear.argtypes = [ctypes.c_void_p, ctypes.POINTER(SbLinearArgs)]
+        _lib.sb_dequant.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32,
+                                    ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32]
+    return _lib
+
+
+def check(status):
+    if status != 0:
+        raise SbError(f"splash_b200 status {status}: {load().sb_last_error().decode()}")
+
+
+def device_count():
+    return load().sb_device_count()
+
+
+def init(device=0):
+    check(load().sb_init(device))
+
+
+def device_status():
+    s = ctypes.c_uint32(0)
+    check(load().sb_device_status(ctypes.byref(s)))
+    return s.value
+
+
+class DeviceBuffer:
+    """Owns one device allocation (sb_alloc / sb_free)."""
+
+    def __init__(self, nbytes):
+        self.nbytes = int(nbytes)
+        p = ctypes.c_void_p()
+        check(load().sb_alloc(self.nbytes, ctypes.byref(p)))
+        self.ptr = p.value
+
+    @classmethod
+    def from_numpy(cls, a, slack=256):
+        a = np.ascontiguousarray(a)
+        b = cls(a.nbytes + slack)
+        check(load().sb_upload(b.ptr, a.ctypes.data_as(ctypes.c_void_p), a.nbytes, None))
+        check(load().sb_stream_sync(None))
+        return b
+
+    def upload(self, a, stream=None, offset=0):
+        a = np.ascontiguousarray(a)
+        assert offset + a.nbytes <= self.nbytes
+        check(load().sb_upload(self.ptr + offset, a.ctypes.data_as(ctypes.c_void_p), a.nbytes, stream))
+        if stream is None:
+            check(load().sb_stream_sync(None))
+
+    def to_numpy(self, dtype, shape, offset=0):
+        out = np.empty(shape, dtype)
+        assert offset + out.nbytes <= self.nbytes
+        check(load().sb_download(out.ctypes.data_as(ctypes.c_void_p), self.ptr + offset, out.nbytes, None))
+        check(load().sb_stream_sync(None))
+        return out
+
+    def fill(self, byte):
+        check(load().sb_memset(self.ptr, byte, self.nbytes, None))
+
+    def free(self):
+        if self.ptr:
+            load().sb_free(self.ptr)
+            self.ptr = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+class Event:
+    def __init__(self):
+        p = ctypes.c_void_p()
+        check(load().sb_event_create(ctypes.byref(p)))
+        self.ptr = p.value
+
+    def record(self, stream=None):
+        check(load().sb_event_record(self.ptr, stream))
+
+    def sync(self):
+        check(load().sb_event_sync(self.ptr))
+
+    def elapsed_ms(self, stop):
+        ms = ctypes.c_float()
+        check(load().sb_event_elapsed_ms(self.ptr, stop.ptr, ctypes.byref(ms)))
+        return ms.value
+
+
+def stream_create():
+    p = ctypes.c_void_p()
+    check(load().sb_stream_create(ctypes.byref(p)))
+    return p.value
+
+
+def stream_sync(stream=None):
+    check(load().sb_stream_sync(stream))
+
+
+def linear(weights, x, out, fmt, n, k, rows, *, weights2=None, aux=None, norm_weight=None, epilogue=EP_NONE,
+           out_f32=False, x_stride=None, aux_stride=None, out_stride=None, flags=0, stream=None):
+    """sb_linear over device pointers (ints)."""
+    a = SbLinearArgs(weights, weights2, x, aux, out, norm_weight, fmt, n, k, rows,
+                     x_stride or k, (aux_stride or n) if aux else 0, out_stride or n, epilogue, int(out_f32), flags)
+    check(load().sb_linear(stream, ctypes.byref(a)))

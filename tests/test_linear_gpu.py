@@ -1,0 +1,166 @@
+"""Parity of sb_linear (CUDA, through the C ABI) with the oracle on seeded inputs.
+
+Gate, as in the reference's projection test (dev/tests/engine/gguf_projection_test.mm:226-245): every
+output must lie in [round(v - e), round(v + e)] where v is the fp64 dot product of the oracle and e
+its projectionBound; Q4_K uses the bound of exactly represented weights, Q6_K / Q8_0 the bound that
+admits one rounding of each weight to half."""
+import ctypes
+
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+import quant_fixtures as qf
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup():
+    from splash_b200 import lib
+    lib.init(0)
+    return lib
+
+
+def oracle_f64(fmt, W, n, k, X, rows):
+    o = ol.load()
+    val = np.empty((rows, n), np.float64)
+    be = np.empty_like(val)
+    bs = np.empty_like(val)
+    assert o.so_linear_f64(fmt, ol.ptr(W), n, k, ol.ptr(X), rows, ol.ptr(val), ol.ptr(be), ol.ptr(bs)) == 0
+    return val, be, bs
+
+
+def check_interval(got_bits, lo_val, hi_val):
+    lo = ol.bf2f(ol.f2bf(lo_val.astype(np.float32)))
+    hi = ol.bf2f(ol.f2bf(hi_val.astype(np.float32)))
+    got = ol.bf2f(got_bits)
+    bad = ~((got >= lo) & (got <= hi))
+    assert not bad.any(), f"{bad.sum()} of {bad.size} outputs outside the bound; worst |got-v|={np.abs(got - (lo_val+hi_val)/2)[bad].max()}"
+
+
+def run_linear(lib, fmt, W, n, k, X, rows, **kw):
+    wd = lib.DeviceBuffer.from_numpy(W)
+    xd = lib.DeviceBuffer.from_numpy(X)
+    f32 = kw.get("out_f32", False)
+    od = lib.DeviceBuffer(rows * n * (4 if f32 else 2) + 512)
+    od.fill(0xFF)
+    lib.linear(wd.ptr, xd.ptr, od.ptr, fmt, n, k, rows, **kw)
+    lib.stream_sync()
+    assert lib.device_status() == 0
+    return od.to_numpy(np.float32 if f32 else np.uint16, (rows, n))
+
+
+@pytest.mark.parametrize("fmt,n,k,rows", [
+    (0, 512, 1024, 16), (0, 320, 5120, 16), (0, 192, 6144, 5), (0, 64, 17408, 16), (0, 100, 2816, 16),
+    (4, 256, 1024, 16), (4, 128, 17408, 16), (4, 192, 5120, 3),
+    (6, 256, 1024, 16), (6, 128, 5120, 7),
+])
+def test_linear_plain(fmt, n, k, rows):
+    lib = _setup()
+    W = qf.realistic(fmt, n, k, seed=n + k)
+    X = qf.activations(rows, k, seed=rows)
+    got = run_linear(lib, fmt, W, n, k, X, rows)
+    v, be, bs = oracle_f64(fmt, W, n, k, X, rows)
+    e = be if fmt == 0 else bs
+    check_interval(got, v - e, v + e)
+
+
+def test_linear_config0_q4k():
+    """The benchmark's single-projection configuration: X bf16 [16, 5120] ~ N(0,1), W [17408, 5120] Q4_K."""
+    lib = _setup()
+    n, k, rows = 17408, 5120, 16
+    W = qf.config0_q4k(n, k, seed=0)
+    X = qf.activations(rows, k, seed=0)
+    got = run_linear(lib, 0, W, n, k, X, rows)
+    v, be, _ = oracle_f64(0, W, n, k, X, rows)
+    check_interval(got, v - be, v + be)
+    # north-star tolerance as well: 2e-3 relative to the output's scale
+    rel = np.abs(ol.bf2f(got) - v) / np.maximum(np.abs(v), np.abs(v).mean())
+    assert rel.max() < 4e-3  # bf16 rounding alone is 2^-9 = 1.95e-3
+
+
+def test_linear_f32_destination_rounds_to_bf16_destination():
+    lib = _setup()
+    n, k, rows = 256, 5120, 16
+    W = qf.realistic(0, n, k)
+    X = qf.activations(rows, k)
+    a = run_linear(lib, 0, W, n, k, X, rows)
+    b = run_linear(lib, 0, W, n, k, X, rows, out_f32=True)
+    assert np.array_equal(a, ol.f2bf(b))
+
+
+def test_linear_rows_independent_of_batch():
+    """A row's output does not depend on how many other rows share the launch, nor on NaN in them."""
+    lib = _setup()
+    n, k = 256, 5120
+    W = qf.realistic(0, n, k)
+    X = qf.activations(16, k)
+    full = run_linear(lib, 0, W, n, k, X, 16)
+    one = run_linear(lib, 0, W, n, k, X[:1].copy(), 1)
+    assert np.array_equal(full[:1], one)
+    Xn = X.copy()
+    Xn[5:] = 0x7FC0
+    part = run_linear(lib, 0, W, n, k, Xn, 16)
+    assert np.array_equal(full[:5], part[:5])
+
+
+@pytest.mark.parametrize("fmt", [0, 4])
+def test_linear_residual_and_gate(fmt):
+    lib = _setup()
+    n, k, rows = 256, 5120, 16
+    W = qf.realistic(fmt, n, k)
+    X = qf.activations(rows, k)
+    rng = np.random.default_rng(3)
+    aux = ol.f2bf(rng.standard_normal((rows, n)).astype(np.float32) * 4)
+    auxd = lib.DeviceBuffer.from_numpy(aux)
+    plain = run_linear(lib, fmt, W, n, k, X, rows, out_f32=True)
+    res = run_linear(lib, fmt, W, n, k, X, rows, aux=auxd.ptr, epilogue=lib.EP_RESIDUAL)
+    assert np.array_equal(res, ol.f2bf(plain + ol.bf2f(aux)))
+    up = run_linear(lib, fmt, W, n, k, X, rows, aux=auxd.ptr, epilogue=lib.EP_UP_WITH_GATE)
+    g = ol.bf2f(aux)
+    want = ol.bf2f(ol.f2bf(plain)) * (g / (1.0 + np.exp2(-1.44269504089 * g).astype(np.float32)))
+    # the device's exp2 differs from numpy's in the last ulp: allow one bf16 ulp
+    d = np.abs(ol.bf2f(up).astype(np.float64) - want)
+    assert (d <= np.abs(want) * 2.0 ** -7 + 1e-30).all()
+
+
+def test_linear_one_pass_gate_up_equals_two_passes():
+    lib = _setup()
+    n, k, rows = 256, 5120, 16
+    Wg = qf.realistic(0, n, k, seed=1)
+    Wu = qf.realistic(0, n, k, seed=2)
+    X = qf.activations(rows, k)
+    gate = run_linear(lib, 0, Wg, n, k, X, rows)
+    gd = lib.DeviceBuffer.from_numpy(gate)
+    two = run_linear(lib, 0, Wu, n, k, X, rows, aux=gd.ptr, epilogue=lib.EP_UP_WITH_GATE)
+    wud = lib.DeviceBuffer.from_numpy(Wu)
+    one = run_linear(lib, 0, Wg, n, k, X, rows, weights2=wud.ptr, epilogue=lib.EP_GATE_UP)
+    assert np.array_equal(one, two)
+
+
+def test_linear_fused_rmsnorm_matches_oracle_norm():
+    lib = _setup()
+    n, k, rows = 256, 5120, 16
+    W = qf.realistic(0, n, k)
+    X = qf.activations(rows, k)
+    rng = np.random.default_rng(9)
+    wn = (1.0 + 0.1 * rng.standard_normal(k)).astype(np.float32)
+    x = ol.bf2f(X).astype(np.float64)
+    inv = 1.0 / np.sqrt((x * x).mean(axis=1, keepdims=True) + 1e-6)
+    Xn = ol.f2bf(((x * inv).astype(np.float32) * wn).astype(np.float32))
+    wnd = lib.DeviceBuffer.from_numpy(wn)
+    fused = run_linear(lib, 0, W, n, k, X, rows, norm_weight=wnd.ptr, out_f32=True)
+    separate = run_linear(lib, 0, W, n, k, Xn, rows, out_f32=True)
+    # the normalized inputs may differ by one bf16 ulp where fp32 and fp64 inverse RMS round apart
+    assert np.abs(fused - separate).max() <= 2e-2 * np.abs(separate).max()
+    assert np.median(np.abs(fused - separate)) <= 1e-3 * np.abs(separate).max()
+
+
+def test_linear_rejects_bad_arguments():
+    lib = _setup()
+    with pytest.raises(lib.SbError):
+        lib.linear(1 << 20, 1 << 20, 1 << 20, 0, 64, 1000, 16)  # k not whole super-blocks
+    with pytest.raises(lib.SbError):
+        lib.linear(1 << 20, 1 << 20, 1 << 20, 0, 64, 1024, 17)  # too many rows
+    with pytest.raises(lib.SbError):
+        lib.linear(1 << 20, 1 << 20, 1 << 20, 3, 64, 1024, 16)  # unsupported format
