@@ -108,7 +108,9 @@ SB_API int sb_dequant(void *stream, uint32_t format, const void *weights_dev, ui
 typedef struct SbLinearArgs {
   const void *weights;  /* [n] native rows of k weights (gate rows for SB_EPILOGUE_GATE_UP) */
   const void *weights2; /* SB_EPILOGUE_GATE_UP: the up tensor's [n] rows; else NULL */
-  const void *x;        /* bf16 [rows, x_stride] */
+  const void *x;        /* bf16 [rows, x_stride]; may be NULL when `prepared` is given */
+  const void *prepared; /* optional: the input already converted by sb_linear_prepare for this format's
+                           layout (one conversion can feed several projections of the same input) */
   const void *aux;      /* bf16 [rows, aux_stride]: residual or gate, by epilogue; else NULL */
   void *out;            /* bf16 or fp32 [rows, out_stride] */
   const void *norm_weight; /* optional fused RMSNorm of x before the product: fp32 [k] weights, or NULL.
@@ -127,6 +129,14 @@ enum {
   SB_LINEAR_PDL = 1 /* launch with programmatic stream serialization: the weight stream starts while the
                        producer of x drains */
 };
+
+/* Converts a projection input once into the fragment-ordered fp16 form the product reads
+ * (the reference's prepared input: ops::LinearBuffers::prepared / PreparedInput,
+ * runtime/ops/Linear.hpp:265-347; kernel decode_linear_gguf_prepare). `format` selects the layout
+ * (Q4_K's differs from Q6_K / Q8_0's). An RMSNorm is fused in front when norm_weight is given. */
+SB_API uint64_t sb_linear_prepared_bytes(uint32_t k);
+SB_API int sb_linear_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride,
+                             const void *norm_weight, uint32_t format, void *prepared_out, uint32_t flags);
 
 /* Scratch (split-K partials and arrival counters) the context keeps for sb_linear; sized by
  * sb_init for the largest projection of the supported shapes and reused serially within a stream,

@@ -16,6 +16,8 @@ struct Context {
   float *linear_partials = nullptr;      // split-K partials [slice][16][columns]
   uint32_t *linear_counters = nullptr;   // one arrival counter per tile, zero between launches
   size_t linear_partials_bytes = 0;
+  uint8_t *prepared = nullptr;           // sb_linear's own prepared-input scratch
+  size_t prepared_bytes = 0;
   uint32_t linear_counter_count = 0;
 };
 Context &ctx();

@@ -10,12 +10,13 @@
 // d*sc*q - dmin*mn.
 //
 // Layout of one launch
-//   grid      one persistent CTA per SM (a multiple of the k-slice count), 288 threads:
-//             warps 0..7 consume, warp 8 produces
+//   prepare   a small kernel converts the 16 x K activations once (optionally through a fused
+//             RMSNorm) to fp16 with a per-row power-of-two scale, in MMA fragment order
+//   grid      one persistent CTA per SM (a multiple of the k-slice count), 320 threads:
+//             warps 0..7 consume, warp 8 produces, warp 9 finishes tiles
 //   k-slices  K's super-blocks are cut into S contiguous slices; a CTA owns one slice for the whole
-//             launch and keeps its 16 x slice activations resident in shared memory, converted
-//             once to fp16 with a per-row power-of-two scale (exact for bf16 inputs within 2^-27
-//             of the row's largest magnitude) in the order the MMA fragments read them
+//             launch and keeps its slice of the prepared activations resident in shared memory
+//             (one bulk copy)
 //   tiles     64 weight rows x slice; the producer warp streams each tile's rows into a ring of
 //             stages (64 rows x 4 super-blocks) with 1-D bulk async copies completing on
 //             mbarriers; consumer warp (rg, kg) multiplies rows 32 rg..32 rg+31 of super-block kg
@@ -25,10 +26,15 @@
 //             one more MMA of the 6-bit mins against the sub-block sums of x (split hi + lo fp16)
 //   Q6_K      operand = fp16(sc*(q-32)) (one rounding when |.| > 2048); y += d*Aq per super-block
 //   Q8_0      operand = fp16(d*q), the value the reference's staged tile rounds to
-//   reduce    the 4 k-group warps of a tile add their sums in order through shared memory; with
-//             S > 1 the slices publish fp32 partials and the last arriver adds them in slice order
+//   reduce    the epilogue warp adds the 4 k-group warps' sums in order from shared memory while the
+//             consumers start the next tile; with S > 1 the slices publish fp32 partials and the
+//             last arriver adds them in slice order
 //             (runtime/metal/kernels/common/split_reduce.h:24-55), then applies the epilogue
 //             (runtime/metal/kernels/common/gguf_tile.h:8-14, gguf_linear.metal:38)
+#include <algorithm>
+
+#include <cuda.h>
+
 #include "sb_internal.h"
 #include "sb_ptx.cuh"
 
@@ -36,7 +42,7 @@ namespace sb {
 
 constexpr int kTokens = 16;         // rows of X one launch multiplies
 constexpr int kConsumerWarps = 8;
-constexpr int kThreads = 32 * (kConsumerWarps + 1);
+constexpr int kThreads = 32 * (kConsumerWarps + 3);  // + producer warp + two epilogue warps
 constexpr int kRG = 2, kKG = 4, kMT = 2;  // row groups x k groups of consumer warps; m-tiles per warp
 constexpr int kTileRows = kRG * kMT * 16; // 64
 constexpr int kStageSb = kKG;             // super-blocks per ring stage
@@ -46,16 +52,25 @@ constexpr int kRedPitch = 17;
 constexpr uint32_t kXsbBytes = kTokens * 256 * 2;  // fp16 activations of one super-block
 constexpr uint32_t kSxSbBytes = 512;               // hi/lo sub-block sums of one super-block
 
+struct LinearMaps {
+  CUtensorMap m[2][8];  // [tensor: weights / weights2][row residue]
+};
+
 struct LinearParams {
-  const uint8_t *w, *w2;
-  const uint16_t *x, *aux;
+  const uint8_t *w, *w2, *prepared;
+  const uint16_t *aux;
   void *out;
-  const float *norm_w;
   float *partials;
   uint32_t *counters, *status;
-  uint32_t n, k, rows, x_stride, aux_stride, out_stride, epilogue, out_f32;
+  uint32_t n, k, rows, aux_stride, out_stride, epilogue, out_f32;
   uint32_t nsb, slices, tiles, stages, row_bytes, pitch, stage_bytes;
-  uint32_t x_off, sx_off, red_off, ring_off;  // shared memory offsets
+  // Tiled-TMA geometry. A tensor's rows are served by `period` maps, map j holding rows = j (mod
+  // period) so that every map's row stride is a multiple of 16 bytes; a stage is `pieces` column
+  // pieces of `piece_sb` super-blocks, each piece one box per (tensor, map): box_rows x pitch bytes.
+  uint32_t period, pieces, piece_sb, box_rows, box_bytes, tensors;
+  uint32_t lead[2][8];  // bytes between map j's 16-byte aligned base and its first row's first byte
+  uint32_t x_off, red_off, ring_off;  // shared memory offsets
+  uint32_t debug;
 };
 
 template <int FMT> struct WFmt;
@@ -68,112 +83,139 @@ __device__ __forceinline__ void slice_range(uint32_t nsb, uint32_t slices, uint3
   b1 = (s + 1) * nsb / slices;
 }
 
-// ---- activations: bf16 global -> scaled fp16 fragments in shared memory ----
-// Each consumer warp converts tokens 2w and 2w+1 of the CTA's slice. A unit is the 16 bytes one
-// lane of an MMA reads: 8 consecutive inputs in the order [0,2,1,3,4,6,5,7].
-template <bool PAIR>
-__device__ void stage_activations(const LinearParams &p, uint8_t *smem, uint32_t sb0, uint32_t sb1, float *scale_back,
-                                  uint32_t warp, uint32_t lane) {
-  uint8_t *xs = smem + p.x_off;
-  __half *sx = reinterpret_cast<__half *>(smem + p.sx_off);
-  const uint32_t k0 = sb0 * 256, k1 = sb1 * 256;
-  for (uint32_t tok = 2 * warp; tok < 2 * warp + 2; ++tok) {
-    const bool live = tok < p.rows;
-    const uint16_t *row = p.x + size_t(tok) * p.x_stride;
-    float inv = 1.0f;
-    if (live && p.norm_w) {
-      // Sum of squares over the whole row in a fixed order: lane-strided 8-element groups, then a
-      // butterfly over the lanes.
-      float ss = 0.0f;
-      for (uint32_t k = 8 * lane; k < p.k; k += 256) {
-        const uint4 v = *reinterpret_cast<const uint4 *>(row + k);
-        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+// ---- prepared activations ----
+// The product reads its activations as fp16 MMA fragments, so they are converted once per
+// projection input, not once per CTA: sb_linear_prepare writes, for all 16 row slots,
+//   header   64 bytes: scale_back[16] floats, 2^e of each row's power-of-two scale
+//   per super-block of 256 inputs, 8704 bytes:
+//     8192 bytes of 16-byte units, one per (MMA step, token half, lane): 8 consecutive inputs of
+//                one token in the order [0,2,1,3,4,6,5,7], scaled by 2^-e and rounded to fp16
+//                (exact for bf16 inputs down to 2^-27 of the row's largest magnitude)
+//      512 bytes of sub-block sums (32 inputs), each split into hi + lo halves, for the mins' MMA
+// Unit order within a super-block, for lane L = 4 g + t holding token 8 h + g:
+//   pair layout  (Q4_K: lane t multiplies sub-blocks 2t, 2t+1):   (((i2*2 + p)*2 + h)*32 + L), inputs
+//                32 (2t + p) + 8 i2 .. + 7
+//   range layout (Q6_K, Q8_0: lane t multiplies inputs 8t..8t+7 of every group j): ((j*2 + h)*32 + L)
+// This mirrors the reference's prepared input (ops::LinearBuffers::prepared, PreparedInput of
+// runtime/ops/Linear.hpp:265-347; kernel decode_linear_gguf_prepare of
+// runtime/metal/kernels/decode/linear_gguf_sgmatrix.metal). An optional RMSNorm is fused in front:
+// y = bf16((x * rsqrt(mean x^2 + 1e-6)) * w) (runtime/metal/kernels/shared/normalization.metal:60-94).
+constexpr uint32_t kPrepHeader = 64;
+constexpr uint32_t kPrepSbBytes = kXsbBytes + kSxSbBytes;  // 8704
+constexpr int kPrepThreads = 256;
+constexpr int kPrepMaxChunks = 9;  // 8-element chunks a thread keeps in registers: k <= 18432
+
+struct PrepareParams {
+  const uint16_t *x;
+  const float *norm_w;
+  uint8_t *out;
+  uint32_t rows, k, x_stride, pair_layout;
+};
+
+__device__ __forceinline__ float block_reduce(float v, float *scratch, bool is_max) {
+  // Fixed order: butterfly within each warp, then the warps' values in index order.
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float a = bf16_bits_to_float(u[i] & 0xffffu), b = bf16_bits_to_float(u[i] >> 16);
-          ss = fmaf(a, a, ss);
-          ss = fmaf(b, b, ss);
-        }
-      }
+  for (int o = 16; o; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, v, o);
+    v = is_max ? fmaxf(v, other) : v + other;
+  }
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = scratch[0];
+  for (int w = 1; w < kPrepThreads / 32; ++w) r = is_max ? fmaxf(r, scratch[w]) : r + scratch[w];
+  return r;
+}
+
+__global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PrepareParams p) {
+  __shared__ float scratch[kPrepThreads / 32];
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t tok = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
+  const bool live = tok < p.rows;
+  const uint32_t chunks = p.k / 8;
+  float v[kPrepMaxChunks][8];
+  const uint16_t *row = p.x + size_t(tok) * p.x_stride;
 #pragma unroll
-      for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      inv = rsqrtf(ss / float(p.k) + 1e-6f);
+  for (int i = 0; i < kPrepMaxChunks; ++i) {
+    const uint32_t c = tid + kPrepThreads * i;
+    uint4 raw = make_uint4(0, 0, 0, 0);
+    if (live && c < chunks) raw = *reinterpret_cast<const uint4 *>(row + 8 * c);
+    const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      v[i][2 * j] = bf16_bits_to_float(u[j] & 0xffffu);
+      v[i][2 * j + 1] = bf16_bits_to_float(u[j] >> 16);
     }
-    auto load8 = [&](uint32_t k, float (&f)[8]) {
-      if (!live) {
+  }
+  if (p.norm_w) {
+    float ss = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = 0.0f;
-        return;
-      }
-      const uint4 v = *reinterpret_cast<const uint4 *>(row + k);
-      const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    for (int i = 0; i < kPrepMaxChunks; ++i)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        f[2 * i] = bf16_bits_to_float(u[i] & 0xffffu);
-        f[2 * i + 1] = bf16_bits_to_float(u[i] >> 16);
-      }
-      if (p.norm_w) {
-        const float4 w0 = *reinterpret_cast<const float4 *>(p.norm_w + k);
-        const float4 w1 = *reinterpret_cast<const float4 *>(p.norm_w + k + 4);
+      for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
+    ss = block_reduce(ss, scratch, false);
+    const float inv = rsqrtf(ss / float(p.k) + 1e-6f);
+#pragma unroll
+    for (int i = 0; i < kPrepMaxChunks; ++i) {
+      const uint32_t c = tid + kPrepThreads * i;
+      if (live && c < chunks) {
+        const float4 w0 = *reinterpret_cast<const float4 *>(p.norm_w + 8 * c);
+        const float4 w1 = *reinterpret_cast<const float4 *>(p.norm_w + 8 * c + 4);
         const float wn[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-        for (int i = 0; i < 8; ++i) f[i] = round_bf16((f[i] * inv) * wn[i]);
+        for (int j = 0; j < 8; ++j) v[i][j] = round_bf16((v[i][j] * inv) * wn[j]);
       }
-    };
-    // Pass 1: the slice's largest magnitude -> power-of-two scale keeping every value below 2^10.
-    float mx = 0.0f;
-    for (uint32_t k = k0 + 8 * lane; k < k1; k += 256) {
-      float f[8];
-      load8(k, f);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) mx = fmaxf(mx, fabsf(f[i]));  // NaN is ignored here; it survives in the values
     }
+  }
+  float mx = 0.0f;
 #pragma unroll
-    for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-    int e = 0;
-    if (mx > 0.0f && mx <= 3.0e38f) {
-      (void)frexpf(mx, &e);  // mx = f * 2^e, f in [0.5, 1)
-      e -= 10;
+  for (int i = 0; i < kPrepMaxChunks; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(v[i][j]));  // NaN does not win a max; it stays in the values
+  mx = block_reduce(mx, scratch, true);
+  int e = 0;
+  if (mx > 0.0f && mx <= 3.0e38f) {
+    (void)frexpf(mx, &e);  // mx = f * 2^e with f in [0.5, 1): scaled values stay below 2^10
+    e -= 10;
+  }
+  const float down = ldexpf(1.0f, -e);
+  if (tid == 0) reinterpret_cast<float *>(p.out)[tok] = ldexpf(1.0f, e);
+  const uint32_t h = tok >> 3, g = tok & 7;
+#pragma unroll
+  for (int i = 0; i < kPrepMaxChunks; ++i) {
+    const uint32_t c = tid + kPrepThreads * i;  // chunk c = inputs 8c..8c+7; 32 consecutive chunks = one super-block
+    if (c >= chunks) continue;                  // uniform per warp: chunks is a multiple of 32
+    const uint32_t sb = c >> 5, j = lane >> 2, q = lane & 3;
+    __half hv[8];
+    float sum = 0.0f;
+#pragma unroll
+    for (int jj = 0; jj < 8; ++jj) {
+      hv[jj] = __float2half_rn(v[i][jj] * down);
+      sum += __half2float(hv[jj]);
     }
-    const float down = ldexpf(1.0f, -e);
-    if (lane == 0) scale_back[tok] = ldexpf(1.0f, e);
-    // Pass 2: convert and store in fragment order; lane L of an iteration holds inputs 8L..8L+7 of
-    // one super-block.
-    const uint32_t h = tok >> 3, g = tok & 7;
-    for (uint32_t sb = sb0; sb < sb1; ++sb) {
-      float f[8];
-      load8(sb * 256 + 8 * lane, f);
-      __half hv[8];
-      float sum = 0.0f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        hv[i] = __float2half_rn(f[i] * down);
-        sum += __half2float(hv[i]);
-      }
-      const uint32_t j = lane >> 2, q = lane & 3, lsb = sb - sb0;
-      uint32_t unit;
-      if (PAIR) unit = ((((lsb * 4 + q) * 2 + (j & 1)) * 2 + h) * 8 + g) * 4 + (j >> 1);
-      else unit = (((lsb * 8 + j) * 2 + h) * 8 + g) * 4 + q;
-      const __half2 p0 = __halves2half2(hv[0], hv[2]), p1 = __halves2half2(hv[1], hv[3]);
-      const __half2 p2 = __halves2half2(hv[4], hv[6]), p3 = __halves2half2(hv[5], hv[7]);
-      uint4 o;
-      o.x = *reinterpret_cast<const uint32_t *>(&p0);
-      o.y = *reinterpret_cast<const uint32_t *>(&p1);
-      o.z = *reinterpret_cast<const uint32_t *>(&p2);
-      o.w = *reinterpret_cast<const uint32_t *>(&p3);
-      *reinterpret_cast<uint4 *>(xs + size_t(unit) * 16) = o;
-      if (PAIR) {
-        // Sub-block sums (32 inputs = 4 lanes), split into hi + lo halves for the mins' MMA.
-        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-        if (q == 0) {
-          const __half hi = __float2half_rn(sum);
-          const __half lo = __float2half_rn(sum - __half2float(hi));
-          const uint32_t at = (((lsb * 2 + h) * 8 + g) * 4 + (j >> 1)) * 4 + (j & 1) * 2;
-          sx[at] = hi;
-          sx[at + 1] = lo;
-        }
-      }
+    uint32_t unit;
+    if (p.pair_layout) unit = (((q * 2 + (j & 1)) * 2 + h) * 8 + g) * 4 + (j >> 1);
+    else unit = ((j * 2 + h) * 8 + g) * 4 + q;
+    const __half2 p0 = __halves2half2(hv[0], hv[2]), p1 = __halves2half2(hv[1], hv[3]);
+    const __half2 p2 = __halves2half2(hv[4], hv[6]), p3 = __halves2half2(hv[5], hv[7]);
+    uint4 o;
+    o.x = *reinterpret_cast<const uint32_t *>(&p0);
+    o.y = *reinterpret_cast<const uint32_t *>(&p1);
+    o.z = *reinterpret_cast<const uint32_t *>(&p2);
+    o.w = *reinterpret_cast<const uint32_t *>(&p3);
+    uint8_t *sbp = p.out + kPrepHeader + size_t(sb) * kPrepSbBytes;
+    *reinterpret_cast<uint4 *>(sbp + size_t(unit) * 16) = o;
+    // Sub-block sums: 32 inputs = 4 consecutive lanes.
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    if (q == 0) {
+      const __half hi = __float2half_rn(sum);
+      const __half lo = __float2half_rn(sum - __half2float(hi));
+      const uint32_t at = ((h * 8 + g) * 4 + (j >> 1)) * 4 + (j & 1) * 2;
+      __half *sx = reinterpret_cast<__half *>(sbp + kXsbBytes);
+      sx[at] = hi;
+      sx[at + 1] = lo;
     }
   }
 }
@@ -427,13 +469,17 @@ __device__ __forceinline__ void multiply_super_block<SB_FMT_Q80>(const uint8_t *
 }
 
 // ---- the kernel ----
+// Barriers in shared memory: full[s] / empty[s] per ring stage, xfull (activations landed),
+// red_full / red_empty (the tile's partial sums handed to the epilogue warp).
 template <int FMT>
-__global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams p) {
+__global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams p, const __grid_constant__ LinearMaps maps) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
   uint64_t *empty = full + kMaxStages;
-  float *scale_back = reinterpret_cast<float *>(smem + 128);      // 16 floats
-  uint32_t *flags = reinterpret_cast<uint32_t *>(smem + 192);     // [0] arrival, [1] failed
+  uint64_t *xfull = empty + kMaxStages;
+  uint64_t *red_full = xfull + 1;   // [2], one per epilogue warp
+  uint64_t *red_empty = xfull + 3;  // [2]
+  float *scale_back = reinterpret_cast<float *>(smem + 192);  // 16 floats, copied from the prepared header
   constexpr uint32_t kSb = WFmt<FMT>::kSbBytes;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t slice = blockIdx.x % p.slices;
@@ -448,81 +494,206 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams 
       mbar_init(&full[s], 1);
       mbar_init(&empty[s], kConsumerWarps);
     }
-    flags[0] = 0;
-    flags[1] = 0;
+    mbar_init(xfull, 1);
+    for (int e = 0; e < 2; ++e) {
+      mbar_init(&red_full[e], kConsumerWarps);
+      mbar_init(&red_empty[e], 1);
+    }
     fence_mbar_init();
   }
   __syncthreads();
   pdl_launch_dependents();
 
   if (warp == kConsumerWarps) {
-    // ---- producer: weights do not depend on the previous kernel, so no dependency wait here ----
+    // ---- producer ----
+    // Weights do not depend on the previous kernel: the ring fills before the dependency wait; the
+    // prepared activations are fetched after it.
     const uint64_t policy = policy_evict_first();
     uint32_t fill = 0;  // stages issued so far
-    bool ok = true;
+    bool ok = true, x_issued = false;
+    auto issue_x = [&] {
+      pdl_wait();
+      if (lane == 0) {
+        const uint32_t bytes = slice_sb * kPrepSbBytes;
+        mbar_arrive_expect_tx(xfull, bytes + kPrepHeader);
+        bulk_g2s(scale_back, p.prepared, kPrepHeader, xfull);
+        bulk_g2s(smem + p.x_off, p.prepared + kPrepHeader + size_t(sb0) * kPrepSbBytes, bytes, xfull);
+      }
+      x_issued = true;
+    };
     for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
       const uint32_t tile = item / p.slices;
       for (uint32_t c = 0; c < chunks && ok; ++c, ++fill) {
         const uint32_t slot = fill % p.stages, round = fill / p.stages;
-        if (round > 0) ok = mbar_wait(&empty[slot], (round - 1) & 1);
+        if (round > 0) {
+          if (!x_issued) issue_x();
+          ok = mbar_wait_backoff(&empty[slot], (round - 1) & 1);
+        }
         if (!ok) break;
         const uint32_t csb0 = sb0 + c * kStageSb, nsb_c = min(uint32_t(kStageSb), sb1 - csb0);
-        // Per row: [src, src + nsb_c * kSb) widened to 16-byte boundaries.
-        uint32_t bytes[2];
-        const uint8_t *src[2];
-        uint32_t total = 0;
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          const uint32_t r = lane + 32 * i;
-          uint32_t wrow;
-          const uint8_t *wb;
-          if (gate_up) {
-            wrow = min(tile * 32 + (r & 31), p.n - 1);
-            wb = r < 32 ? p.w : p.w2;
-          } else {
-            wrow = min(tile * kTileRows + r, p.n - 1);
-            wb = p.w;
-          }
-          const uint8_t *s = wb + size_t(wrow) * p.row_bytes + size_t(csb0) * kSb;
-          const uint32_t lead = uint32_t(reinterpret_cast<uintptr_t>(s) & 15u);
-          src[i] = s - lead;
-          bytes[i] = (lead + nsb_c * kSb + 15u) & ~15u;
-          total += bytes[i];
-        }
-#pragma unroll
-        for (int o = 16; o; o >>= 1) total += __shfl_xor_sync(0xffffffffu, total, o);
-        if (lane == 0) mbar_arrive_expect_tx(&full[slot], total);
+        // One box per (piece, tensor, row residue): lane = box index.
+        const uint32_t pieces_c = (nsb_c + p.piece_sb - 1) / p.piece_sb;
+        const uint32_t per_piece = p.tensors * p.period, boxes = pieces_c * per_piece;
+        if (lane == 0) mbar_arrive_expect_tx(&full[slot], boxes * p.box_bytes);
         __syncwarp();
-        uint8_t *dst = smem + p.ring_off + slot * p.stage_bytes;
-#pragma unroll
-        for (int i = 0; i < 2; ++i)
-          bulk_g2s_stream(dst + (lane + 32 * i) * p.pitch, src[i], bytes[i], &full[slot], policy);
+        if (lane < boxes) {
+          const uint32_t piece = lane / per_piece, tj = lane % per_piece, tn = tj / p.period, j = tj % p.period;
+          const uint32_t row0 = gate_up ? tile * 32 : tile * kTileRows;
+          const uint32_t byte0 = p.lead[tn][j] + (csb0 + piece * p.piece_sb) * kSb;
+          uint8_t *dst = smem + p.ring_off + slot * p.stage_bytes + lane * p.box_bytes;
+          tma_load_2d(dst, &maps.m[tn][j], int(byte0 >> 4) * 4, int(row0 / p.period), &full[slot], policy, (p.debug & 2) == 0);
+        }
       }
     }
-    if (!ok && lane == 0) {
-      atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
-      flags[1] = 1;
-    }
+    if (!x_issued) issue_x();
+    if (!ok && lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
     // Do not leave while copies are in flight: wait (bounded) until the consumers have released the
     // last fill of every stage, which they do only after its bytes have landed.
     for (uint32_t f = fill > p.stages ? fill - p.stages : 0; f < fill; ++f)
-      if (!mbar_wait(&empty[f % p.stages], (f / p.stages) & 1)) break;
+      if (!mbar_wait_backoff(&empty[f % p.stages], (f / p.stages) & 1)) break;
+    return;
+  }
+
+  float *red = reinterpret_cast<float *>(smem + p.red_off);
+
+  if (warp > kConsumerWarps) {
+    // ---- epilogue warps: tile i of this CTA belongs to epilogue warp i % 2. Each adds the k-group
+    // warps' sums in order, exchanges split-K partials and stores. Lane l owns token l / 2 and tile
+    // rows 32 (l % 2) .. + 31, so every global access of a lane is 64 or 128 contiguous bytes. ----
+    const uint32_t ew = warp - kConsumerWarps - 1;
+    pdl_wait();  // aux / out / partials belong to the stream's earlier kernels until they finish
+    const uint32_t pcols = gate_up ? 2 * p.n : p.n;
+    const uint32_t tok = lane >> 1, half = lane & 1;
+    if (!mbar_wait_backoff(xfull, 0)) { if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED); return; }
+    const float sback = scale_back[tok];
+    uint32_t done = 0;
+    for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++done) {
+      if ((done & 1) != ew) continue;
+      const uint32_t tile = item / p.slices;
+      if (!mbar_wait_backoff(&red_full[ew], (done >> 1) & 1)) { if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED); return; }
+      float v[32];
+#pragma unroll
+      for (int r = 0; r < 32; ++r) {
+        float s = 0.0f;
+#pragma unroll
+        for (int k = 0; k < kKG; ++k) s += red[((half * kKG + k) * 32 + r) * kRedPitch + tok];
+        v[r] = s * sback;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&red_empty[ew]);
+      // First column of the lane's 32 values in the partials; gate/up tiles hold 32 gate rows then the
+      // 32 up rows of the same 32 columns.
+      const uint32_t c0 = gate_up ? tile * 32 : tile * kTileRows + 32 * half;
+      const uint32_t pc0 = gate_up ? c0 + half * p.n : c0;
+      const bool col_ok = c0 < p.n;  // n is a multiple of 32: a 32-column run is inside or outside
+      bool finish = true;
+      if (p.slices > 1) {
+        if (col_ok) {
+          float4 *pp = reinterpret_cast<float4 *>(p.partials + (size_t(slice) * kTokens + tok) * pcols + pc0);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) pp[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        }
+        __threadfence();
+        __syncwarp();
+        uint32_t arrived = 0;
+        if (lane == 0) arrived = atomicAdd(&p.counters[tile], 1u);
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        finish = arrived == p.slices - 1;
+        if (finish) {
+          __threadfence();
+          if (col_ok) {
+#pragma unroll
+            for (int r = 0; r < 32; ++r) v[r] = 0.0f;
+            for (uint32_t sl = 0; sl < p.slices; ++sl) {
+              const float4 *pp = reinterpret_cast<const float4 *>(p.partials + (size_t(sl) * kTokens + tok) * pcols + pc0);
+              float4 q[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) q[i] = __ldcg(pp + i);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                v[4 * i] += q[i].x, v[4 * i + 1] += q[i].y, v[4 * i + 2] += q[i].z, v[4 * i + 3] += q[i].w;
+              }
+            }
+          }
+          if (lane == 0) p.counters[tile] = 0;
+        }
+      }
+      if (!finish) continue;
+      if (gate_up) {
+        // Lane (tok, 0) holds the gate sums, lane (tok, 1) the up sums of the same 32 columns: swap
+        // halves so each lane finishes 16 columns.
+        float gsum[16], usum[16];
+#pragma unroll
+        for (int r = 0; r < 16; ++r) {
+          const float mine_lo = v[r], mine_hi = v[16 + r];
+          const float send = half ? mine_lo : mine_hi;       // what the partner needs
+          const float got = __shfl_xor_sync(0xffffffffu, send, 1);
+          gsum[r] = half ? got : mine_lo;                      // gate of column 16*half + r
+          usum[r] = half ? mine_hi : got;                      // up of column 16*half + r
+        }
+        if (col_ok && tok < p.rows) {
+          uint32_t pk[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const float o0 = round_bf16(usum[2 * r]) * silu_f(round_bf16(gsum[2 * r]));
+            const float o1 = round_bf16(usum[2 * r + 1]) * silu_f(round_bf16(gsum[2 * r + 1]));
+            pk[r] = uint32_t(float_to_bf16_bits(o0)) | (uint32_t(float_to_bf16_bits(o1)) << 16);
+          }
+          uint4 *op = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.out) + size_t(tok) * p.out_stride + c0 + 16 * half);
+          op[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          op[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
+        }
+        continue;
+      }
+      if (!col_ok || tok >= p.rows) continue;
+      if (p.epilogue == SB_EPILOGUE_RESIDUAL || p.epilogue == SB_EPILOGUE_UP_WITH_GATE) {
+        const uint4 *ap = reinterpret_cast<const uint4 *>(p.aux + size_t(tok) * p.aux_stride + c0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint4 a4 = ap[q];
+          const uint32_t u[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float xa = bf16_bits_to_float(u[i] & 0xffffu), xb = bf16_bits_to_float(u[i] >> 16);
+            float &a = v[8 * q + 2 * i], &b = v[8 * q + 2 * i + 1];
+            if (p.epilogue == SB_EPILOGUE_RESIDUAL) {
+              a += xa;
+              b += xb;
+            } else {
+              a = round_bf16(a) * silu_f(xa);
+              b = round_bf16(b) * silu_f(xb);
+            }
+          }
+        }
+      }
+      if (p.out_f32) {
+        float4 *op = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + size_t(tok) * p.out_stride + c0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) op[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      } else {
+        uint4 *op = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.out) + size_t(tok) * p.out_stride + c0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            pk[i] = uint32_t(float_to_bf16_bits(v[8 * q + 2 * i])) | (uint32_t(float_to_bf16_bits(v[8 * q + 2 * i + 1])) << 16);
+          op[q] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+      }
+    }
     return;
   }
 
   // ---- consumers ----
-  pdl_wait();
-  if (WFmt<FMT>::kPairLayout) stage_activations<true>(p, smem, sb0, sb1, scale_back, warp, lane);
-  else stage_activations<false>(p, smem, sb0, sb1, scale_back, warp, lane);
-  named_bar_sync(1, 32 * kConsumerWarps);
-
   const uint32_t rg = warp / kKG, kg = warp % kKG;
   const uint32_t g = lane >> 2, t = lane & 3;
-  (void)t;
-  float *red = reinterpret_cast<float *>(smem + p.red_off);
-  const uint32_t ctid = threadIdx.x;  // 0..255
-  uint32_t drained = 0;
-  for (uint32_t item = blockIdx.x; item < items; item += gridDim.x) {
+  if (!mbar_wait(xfull, 0)) {
+    if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
+    return;
+  }
+  uint32_t drained = 0, done = 0;
+  for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++done) {
     const uint32_t tile = item / p.slices;
     float y[kMT][2][4];
 #pragma unroll
@@ -538,33 +709,34 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams 
         return;  // the launch has failed; the status word says so
       }
       const uint32_t csb0 = sb0 + c * kStageSb, nsb_c = min(uint32_t(kStageSb), sb1 - csb0);
-      if (kg < nsb_c) {
+      if (kg < nsb_c && !(p.debug & 1)) {
         const uint8_t *stage = smem + p.ring_off + slot * p.stage_bytes;
-        // Row r of the stage starts `lead` bytes into its slot: its global address modulo 16 (always 0
-        // for Q4_K, whose rows are 16-byte multiples).
+        // A row sits in the box of its (piece, tensor, residue) at `lead` bytes past a 16-byte boundary
+        // (always 0 for Q4_K, whose rows are 16-byte multiples).
         const uint32_t lsb = csb0 + kg - sb0;
         uint32_t roff[kMT][2];
+        const uint32_t piece = kg / p.piece_sb, within = kg % p.piece_sb;
 #pragma unroll
         for (int mt = 0; mt < kMT; ++mt)
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
-            const uint32_t tr = rg * 32 + mt * 16 + r * 8 + g;
-            uint32_t lead = 0;
-            if (FMT != SB_FMT_Q4K) {
-              const uint32_t wrow = gate_up ? min(tile * 32 + (tr & 31), p.n - 1) : min(tile * kTileRows + tr, p.n - 1);
-              const uint8_t *wb = (gate_up && tr >= 32) ? p.w2 : p.w;
-              lead = uint32_t((reinterpret_cast<uintptr_t>(wb) + size_t(wrow) * p.row_bytes + size_t(csb0) * kSb) & 15u);
-            }
-            roff[mt][r] = tr * p.pitch + lead + kg * kSb;
+            const uint32_t tr = rg * 32 + mt * 16 + r * 8 + g;          // tile row
+            const uint32_t tn = gate_up ? tr >> 5 : 0, rl = gate_up ? tr & 31 : tr;
+            const uint32_t j = rl % p.period, i = rl / p.period;          // map and row within its box
+            const uint32_t lead = (p.lead[tn][j] + (csb0 + piece * p.piece_sb) * kSb) & 15u;
+            roff[mt][r] = ((piece * p.tensors + tn) * p.period + j) * p.box_bytes + i * p.pitch + lead + within * kSb;
           }
-        multiply_super_block<FMT>(stage, roff, smem + p.x_off + lsb * kXsbBytes, smem + p.sx_off + lsb * kSxSbBytes,
-                                  lane, y);
+        const uint8_t *xs_sb = smem + p.x_off + lsb * kPrepSbBytes;
+        multiply_super_block<FMT>(stage, roff, xs_sb, xs_sb + kXsbBytes, lane, y);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[slot]);
     }
-    // ---- tile reduce over the k-group warps, in order ----
-    named_bar_sync(2, 32 * kConsumerWarps);  // the previous tile's readers are done with `red`
+    // Hand the tile's sums to the epilogue warp once it has read the previous tile's.
+    if (done > 0 && !mbar_wait(&red_empty[(done - 1) & 1], ((done - 1) >> 1) & 1)) {
+      if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
+      return;
+    }
     float *mine = red + warp * (32 * kRedPitch);
 #pragma unroll
     for (int mt = 0; mt < kMT; ++mt)
@@ -575,143 +747,109 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams 
         mine[(mt * 16 + g + 8) * kRedPitch + h * 8 + 2 * t] = y[mt][h][2];
         mine[(mt * 16 + g + 8) * kRedPitch + h * 8 + 2 * t + 1] = y[mt][h][3];
       }
-    named_bar_sync(1, 32 * kConsumerWarps);
-    // Thread -> (token, 4 consecutive tile rows).
-    const uint32_t tok = ctid >> 4, r4 = (ctid & 15) * 4;
-    float v[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t r = r4 + i, wrg = r >> 5, rl = r & 31;
-      float s = 0.0f;
-#pragma unroll
-      for (int k = 0; k < kKG; ++k) s += red[((wrg * kKG + k) * 32 + rl) * kRedPitch + tok];
-      v[i] = s * scale_back[tok];
-    }
-    const uint32_t pcols = gate_up ? 2 * p.n : p.n;
-    // Partial / output column of tile row r: plain tiles map rows to columns; a gate/up tile holds
-    // 32 gate rows then 32 up rows of the same 32 columns.
-    const uint32_t col0 = gate_up ? (r4 < 32 ? tile * 32 + r4 : p.n + tile * 32 + (r4 - 32)) : tile * kTileRows + r4;
-    const bool col_ok = gate_up ? (tile * 32 + (r4 & 31) < p.n) : (col0 < p.n);  // n is a multiple of 4
-    bool finish = true;
-    if (p.slices > 1) {
-      if (col_ok)
-        *reinterpret_cast<float4 *>(p.partials + (size_t(slice) * kTokens + tok) * pcols + col0) =
-            make_float4(v[0], v[1], v[2], v[3]);
-      __threadfence();
-      named_bar_sync(2, 32 * kConsumerWarps);
-      if (ctid == 0) flags[0] = atomicAdd(&p.counters[tile], 1u);
-      named_bar_sync(1, 32 * kConsumerWarps);
-      finish = flags[0] == p.slices - 1;
-      if (finish) {
-        __threadfence();
-        if (col_ok) {
-          float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-          for (uint32_t sl = 0; sl < p.slices; ++sl) {
-            const float4 q = __ldcg(reinterpret_cast<const float4 *>(p.partials + (size_t(sl) * kTokens + tok) * pcols + col0));
-            s.x += q.x, s.y += q.y, s.z += q.z, s.w += q.w;
-          }
-          v[0] = s.x, v[1] = s.y, v[2] = s.z, v[3] = s.w;
-        }
-        if (ctid == 0) p.counters[tile] = 0;
-      }
-    }
-    if (finish && tok < p.rows && col_ok) {
-      if (!gate_up) {
-        float o[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float a = v[i];
-          if (p.epilogue == SB_EPILOGUE_RESIDUAL)
-            a += bf16_bits_to_float(p.aux[size_t(tok) * p.aux_stride + col0 + i]);
-          else if (p.epilogue == SB_EPILOGUE_UP_WITH_GATE)
-            a = round_bf16(a) * silu_f(bf16_bits_to_float(p.aux[size_t(tok) * p.aux_stride + col0 + i]));
-          o[i] = a;
-        }
-        if (p.out_f32) {
-          *reinterpret_cast<float4 *>(static_cast<float *>(p.out) + size_t(tok) * p.out_stride + col0) =
-              make_float4(o[0], o[1], o[2], o[3]);
-        } else {
-          uint2 pk;
-          pk.x = uint32_t(float_to_bf16_bits(o[0])) | (uint32_t(float_to_bf16_bits(o[1])) << 16);
-          pk.y = uint32_t(float_to_bf16_bits(o[2])) | (uint32_t(float_to_bf16_bits(o[3])) << 16);
-          *reinterpret_cast<uint2 *>(static_cast<uint16_t *>(p.out) + size_t(tok) * p.out_stride + col0) = pk;
-        }
-      } else {
-        // The up rows' threads (r4 >= 32) hold `up`; the gate sums sit 32 rows earlier in `red` or in
-        // the partials: fetch them again so one thread owns both.
-        if (r4 >= 32) {
-          float gsum[4];
-          if (p.slices > 1) {
-            float4 s = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (uint32_t sl = 0; sl < p.slices; ++sl) {
-              const float4 q = __ldcg(reinterpret_cast<const float4 *>(p.partials + (size_t(sl) * kTokens + tok) * pcols + (col0 - p.n)));
-              s.x += q.x, s.y += q.y, s.z += q.z, s.w += q.w;
-            }
-            gsum[0] = s.x, gsum[1] = s.y, gsum[2] = s.z, gsum[3] = s.w;
-          } else {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const uint32_t rl = (r4 - 32) + i;
-              float s = 0.0f;
-#pragma unroll
-              for (int k = 0; k < kKG; ++k) s += red[((0 * kKG + k) * 32 + rl) * kRedPitch + tok];
-              gsum[i] = s * scale_back[tok];
-            }
-          }
-          const uint32_t oc = col0 - p.n;
-          uint32_t ob[4];
-#pragma unroll
-          for (int i = 0; i < 4; ++i) ob[i] = float_to_bf16_bits(round_bf16(v[i]) * silu_f(round_bf16(gsum[i])));
-          uint2 pk;
-          pk.x = ob[0] | (ob[1] << 16);
-          pk.y = ob[2] | (ob[3] << 16);
-          *reinterpret_cast<uint2 *>(static_cast<uint16_t *>(p.out) + size_t(tok) * p.out_stride + oc) = pk;
-        }
-      }
-    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&red_full[done & 1]);
   }
 }
 
 // ---- host side ----
-static uint32_t pick_slices(uint32_t nsb, int sms) {
-  uint32_t s = (nsb + kMaxSliceSb - 1) / kMaxSliceSb;
+static uint32_t pick_slices(uint32_t nsb, uint32_t sb_bytes) {
+  // Activations of a slice stay resident: at most kMaxSliceSb super-blocks, fewer where a format's
+  // wider stages need the room.
+  const uint32_t cap = sb_bytes > 250 ? 6 : sb_bytes > 160 ? 8 : kMaxSliceSb;
+  const uint32_t s = (nsb + cap - 1) / cap;
   return s < 1 ? 1 : s;
 }
 
 static int make_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t epilogue, LinearParams &p, SbLinearPlan &plan) {
-  FmtInfo fi;
   SB_REQUIRE(format == SB_FMT_Q4K || format == SB_FMT_Q6K || format == SB_FMT_Q80,
              "sb_linear: format %u is not a quantized block format of this kernel", format);
-  fmt_info(format, fi);
   SB_REQUIRE(k && k % 256 == 0, "sb_linear: k = %u is not a multiple of 256", k);
-  SB_REQUIRE(n && n % 4 == 0, "sb_linear: n = %u is not a multiple of 4", n);
+  SB_REQUIRE(n && n % 32 == 0, "sb_linear: n = %u is not a multiple of 32", n);
   const bool gate_up = epilogue == SB_EPILOGUE_GATE_UP;
   const uint32_t sb_bytes = format == SB_FMT_Q4K ? 144 : format == SB_FMT_Q6K ? 210 : 272;
   p.nsb = k / 256;
-  p.slices = pick_slices(p.nsb, ctx().sm_count);
+  p.slices = pick_slices(p.nsb, sb_bytes);
   p.tiles = gate_up ? (n + 31) / 32 : (n + kTileRows - 1) / kTileRows;
   p.row_bytes = uint32_t(sb_row_bytes(format, k));
-  // Row pitch of a stage: the widened copy of kStageSb super-blocks, with the pitch congruent to 16
-  // modulo 32 so the 16-byte reads of 8 rows x 4 lanes spread over all banks.
-  uint32_t pitch = (kStageSb * sb_bytes + 15 + 15) & ~15u;
-  if (format == SB_FMT_Q4K) pitch = kStageSb * sb_bytes;
-  if (pitch % 32 != 16) pitch += 16;
-  p.pitch = pitch;
-  p.stage_bytes = (kTileRows * pitch + 127) & ~127u;
+  // Stage geometry. Q4_K rows are 16-byte multiples: one map, one box of 64 x 144 bytes per
+  // super-block (pitch 144 = 16 mod 32: the 16-byte reads of 8 rows x 4 lanes hit distinct banks).
+  // Q6_K / Q8_0 rows are only 2-byte aligned: `period` maps of every period-th row, boxes wide
+  // enough for piece_sb super-blocks at any 2-byte lead.
+  p.tensors = gate_up ? 2 : 1;
+  const uint32_t tile_rows_per_tensor = gate_up ? 32 : kTileRows;
+  if (format == SB_FMT_Q4K) {
+    p.period = 1, p.pieces = kStageSb, p.piece_sb = 1, p.pitch = 144;
+  } else {
+    uint32_t gcd = 16;
+    while (p.row_bytes % gcd) gcd >>= 1;
+    p.period = 16 / gcd;
+    p.piece_sb = format == SB_FMT_Q6K ? kStageSb : 2;
+    p.pieces = kStageSb / p.piece_sb;
+    p.pitch = (p.piece_sb * sb_bytes + 14 + 15) & ~15u;
+  }
+  p.box_rows = tile_rows_per_tensor / p.period;
+  p.box_bytes = p.box_rows * p.pitch;
+  SB_REQUIRE(p.box_bytes % 128 == 0 && p.pitch <= 1024, "sb_linear: unsupported stage geometry (k = %u)", k);
+  p.stage_bytes = p.pieces * p.tensors * p.period * p.box_bytes;
   const uint32_t slice_max = (p.nsb + p.slices - 1) / p.slices;
   p.x_off = 256;
-  p.sx_off = p.x_off + slice_max * kXsbBytes;
-  p.red_off = p.sx_off + slice_max * kSxSbBytes;
+  p.red_off = p.x_off + slice_max * kPrepSbBytes;
   p.ring_off = (p.red_off + kConsumerWarps * 32 * kRedPitch * 4 + 127) & ~127u;
   const uint32_t budget = 227 * 1024;
   SB_REQUIRE(p.ring_off + 2 * p.stage_bytes <= budget, "sb_linear: shared memory plan does not fit (k = %u)", k);
-  p.stages = min(uint32_t(kMaxStages), (budget - p.ring_off) / p.stage_bytes);
+  p.stages = std::min(uint32_t(kMaxStages), (budget - p.ring_off) / p.stage_bytes);
   const uint32_t sms = uint32_t(ctx().sm_count ? ctx().sm_count : 148);
   uint32_t ctas = sms / p.slices * p.slices;
   const uint32_t items = p.tiles * p.slices;
   if (ctas > items) ctas = items;
   plan = {p.slices, ctas, uint32_t(kTileRows), p.stages, p.ring_off + p.stages * p.stage_bytes, uint32_t(kStageSb),
           slice_max, p.tiles};
+  return SB_OK;
+}
+
+// A 2-D map over `rows` rows of `stride` bytes starting at the 16-byte aligned `base`: u32 elements,
+// box = box_rows x box_bytes. Rows past the end and bytes past a row read as zero.
+static int encode_weight_map(CUtensorMap *map, uintptr_t base, uint32_t stride, uint32_t rows, uint32_t box_bytes,
+                             uint32_t box_rows) {
+  using Encode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  static Encode encode = nullptr;
+  if (!encode) {
+    cudaDriverEntryPointQueryResult qr;
+    void *fn = nullptr;
+    SB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qr));
+    if (!fn || qr != cudaDriverEntryPointSuccess) return fail(SB_ERR_CUDA, "cuTensorMapEncodeTiled is unavailable");
+    encode = reinterpret_cast<Encode>(fn);
+  }
+  SB_REQUIRE(stride % 16 == 0 && box_bytes % 16 == 0 && box_bytes / 4 <= 256 && box_rows <= 256 && box_rows >= 1,
+             "sb_linear: tensor map geometry (stride %u, box %u x %u)", stride, box_rows, box_bytes);
+  const cuuint64_t dims[2] = {stride / 4, rows};
+  const cuuint64_t strides[1] = {stride};
+  const cuuint32_t box[2] = {box_bytes / 4, box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, reinterpret_cast<void *>(base), dims, strides, box,
+                            elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(SB_ERR_CUDA, "cuTensorMapEncodeTiled failed with %d", int(r));
+  return SB_OK;
+}
+
+static int launch_prepare(cudaStream_t stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride,
+                          const void *norm_w, bool pair_layout, void *out, bool pdl) {
+  PrepareParams pp{static_cast<const uint16_t *>(x), static_cast<const float *>(norm_w), static_cast<uint8_t *>(out),
+                   rows, k, x_stride, pair_layout ? 1u : 0u};
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(kTokens);
+  cfg.blockDim = dim3(kPrepThreads);
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  SB_CUDA(cudaLaunchKernelEx(&cfg, prepare_kernel, pp));
   return SB_OK;
 }
 
@@ -727,26 +865,44 @@ extern "C" int sb_linear_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t 
   return make_plan(format, n, k, epilogue, p, *out_plan);
 }
 
+extern "C" uint64_t sb_linear_prepared_bytes(uint32_t k) { return k % 256 ? 0 : kPrepHeader + uint64_t(k / 256) * kPrepSbBytes; }
+
+extern "C" int sb_linear_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride,
+                                 const void *norm_weight, uint32_t format, void *prepared_out, uint32_t flags) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(x && prepared_out, "sb_linear_prepare: null x or destination");
+  SB_REQUIRE(rows >= 1 && rows <= kTokens, "sb_linear_prepare: rows = %u outside 1..%d", rows, kTokens);
+  SB_REQUIRE(k && k % 256 == 0 && k <= 8 * kPrepThreads * kPrepMaxChunks, "sb_linear_prepare: k = %u is not a multiple of 256 up to %d",
+             k, 8 * kPrepThreads * kPrepMaxChunks);
+  SB_REQUIRE(x_stride >= k && x_stride % 8 == 0, "sb_linear_prepare: x_stride %u < k or not a multiple of 8", x_stride);
+  SB_REQUIRE(format == SB_FMT_Q4K || format == SB_FMT_Q6K || format == SB_FMT_Q80, "sb_linear_prepare: format %u", format);
+  SB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(prepared_out) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(norm_weight) & 15) == 0,
+             "sb_linear_prepare: x, norm_weight and the destination must be 16-byte aligned");
+  return launch_prepare(as_stream(stream), x, rows, k, x_stride, norm_weight, format == SB_FMT_Q4K, prepared_out,
+                        (flags & SB_LINEAR_PDL) != 0);
+}
+
 extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
   SB_NEED_DEVICE();
   SB_REQUIRE(a, "sb_linear: null arguments");
-  SB_REQUIRE(a->weights && a->x && a->out, "sb_linear: null weights, x or out");
+  SB_REQUIRE(a->weights && a->out && (a->x || a->prepared), "sb_linear: null weights, out, or neither x nor prepared");
   SB_REQUIRE(a->rows >= 1 && a->rows <= kTokens, "sb_linear: rows = %u outside 1..%d", a->rows, kTokens);
   SB_REQUIRE(a->epilogue <= SB_EPILOGUE_GATE_UP, "sb_linear: unknown epilogue %u", a->epilogue);
   SB_REQUIRE((a->epilogue == SB_EPILOGUE_GATE_UP) == (a->weights2 != nullptr),
              "sb_linear: weights2 is given exactly with SB_EPILOGUE_GATE_UP");
   SB_REQUIRE((a->epilogue == SB_EPILOGUE_RESIDUAL || a->epilogue == SB_EPILOGUE_UP_WITH_GATE) == (a->aux != nullptr),
              "sb_linear: aux is given exactly with the residual and up-with-gate epilogues");
-  SB_REQUIRE(a->x_stride >= a->k && a->x_stride % 8 == 0, "sb_linear: x_stride %u < k or not a multiple of 8", a->x_stride);
-  SB_REQUIRE(a->out_stride >= a->n && a->out_stride % 4 == 0, "sb_linear: out_stride %u < n or not a multiple of 4", a->out_stride);
-  SB_REQUIRE(!a->aux || a->aux_stride >= a->n, "sb_linear: aux_stride %u < n", a->aux_stride);
+  SB_REQUIRE(a->out_stride >= a->n && a->out_stride % 8 == 0, "sb_linear: out_stride %u < n or not a multiple of 8", a->out_stride);
+  SB_REQUIRE(!a->aux || (a->aux_stride >= a->n && a->aux_stride % 8 == 0), "sb_linear: aux_stride %u < n or not a multiple of 8", a->aux_stride);
   SB_REQUIRE(!(a->out_f32 && a->epilogue != SB_EPILOGUE_NONE), "sb_linear: an fp32 destination takes no epilogue");
-  SB_REQUIRE((reinterpret_cast<uintptr_t>(a->x) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->out) & 15) == 0,
-             "sb_linear: x and out must be 16-byte aligned");
-  SB_REQUIRE((reinterpret_cast<uintptr_t>(a->weights) & 1) == 0, "sb_linear: weights must be 2-byte aligned");
+  SB_REQUIRE((reinterpret_cast<uintptr_t>(a->out) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->aux) & 15) == 0,
+             "sb_linear: out and aux must be 16-byte aligned");
+  SB_REQUIRE((reinterpret_cast<uintptr_t>(a->weights) & 1) == 0 && (reinterpret_cast<uintptr_t>(a->weights2) & 1) == 0,
+             "sb_linear: weights must be 2-byte aligned");
   LinearParams p{};
   SbLinearPlan plan;
-  const int st = make_plan(a->format, a->n, a->k, a->epilogue, p, plan);
+  int st = make_plan(a->format, a->n, a->k, a->epilogue, p, plan);
   if (st != SB_OK) return st;
   if (a->format == SB_FMT_Q4K)
     SB_REQUIRE((reinterpret_cast<uintptr_t>(a->weights) & 15) == 0 &&
@@ -757,20 +913,30 @@ extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
   SB_REQUIRE(p.slices == 1 || size_t(p.slices) * kTokens * pcols * 4 <= c.linear_partials_bytes,
              "sb_linear: split-K scratch too small for n = %u with %u slices", a->n, p.slices);
   SB_REQUIRE(p.tiles <= c.linear_counter_count, "sb_linear: too many tiles (%u)", p.tiles);
+  const bool pdl = (a->flags & SB_LINEAR_PDL) != 0;
+  const void *prepared = a->prepared;
+  if (!prepared) {
+    SB_REQUIRE(sb_linear_prepared_bytes(a->k) <= c.prepared_bytes, "sb_linear: k = %u exceeds the context's prepared-input scratch", a->k);
+    st = sb_linear_prepare(stream, a->x, a->rows, a->k, a->x_stride, a->norm_weight, a->format, c.prepared, a->flags);
+    if (st != SB_OK) return st;
+    prepared = c.prepared;
+  } else {
+    SB_REQUIRE((reinterpret_cast<uintptr_t>(prepared) & 15) == 0, "sb_linear: prepared must be 16-byte aligned");
+  }
   p.w = static_cast<const uint8_t *>(a->weights);
   p.w2 = static_cast<const uint8_t *>(a->weights2);
-  p.x = static_cast<const uint16_t *>(a->x);
+  p.prepared = static_cast<const uint8_t *>(prepared);
   p.aux = static_cast<const uint16_t *>(a->aux);
   p.out = a->out;
-  p.norm_w = static_cast<const float *>(a->norm_weight);
   p.partials = c.linear_partials;
   p.counters = c.linear_counters;
   p.status = c.status_dev;
   p.n = a->n, p.k = a->k, p.rows = a->rows;
-  p.x_stride = a->x_stride, p.aux_stride = a->aux_stride, p.out_stride = a->out_stride;
+  p.aux_stride = a->aux_stride, p.out_stride = a->out_stride;
   p.epilogue = a->epilogue, p.out_f32 = a->out_f32;
+  p.debug = a->flags >> 8;
 
-  void (*kernel)(const LinearParams) = a->format == SB_FMT_Q4K   ? linear_kernel<SB_FMT_Q4K>
+  void (*kernel)(const LinearParams, const LinearMaps) = a->format == SB_FMT_Q4K   ? linear_kernel<SB_FMT_Q4K>
                                        : a->format == SB_FMT_Q6K ? linear_kernel<SB_FMT_Q6K>
                                                                  : linear_kernel<SB_FMT_Q80>;
   static bool attr_set[3] = {false, false, false};
@@ -779,6 +945,15 @@ extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
     SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr_set[ki] = true;
   }
+  LinearMaps maps;
+  for (uint32_t tn = 0; tn < p.tensors; ++tn)
+    for (uint32_t j = 0; j < p.period; ++j) {
+      const uintptr_t first = reinterpret_cast<uintptr_t>(tn ? a->weights2 : a->weights) + size_t(j) * p.row_bytes;
+      p.lead[tn][j] = uint32_t(first & 15u);
+      st = encode_weight_map(&maps.m[tn][j], first & ~uintptr_t(15), p.row_bytes * p.period,
+                             (a->n - j + p.period - 1) / p.period, p.pitch, p.box_rows);
+      if (st != SB_OK) return st;
+    }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(plan.ctas);
   cfg.blockDim = dim3(kThreads);
@@ -788,7 +963,7 @@ extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = (a->flags & SB_LINEAR_PDL) ? 1 : 0;
-  SB_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+  cfg.numAttrs = pdl ? 1 : 0;
+  SB_CUDA(cudaLaunchKernelEx(&cfg, kernel, p, maps));
   return SB_OK;
 }

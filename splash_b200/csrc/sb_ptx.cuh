@@ -48,6 +48,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   return false;
 }
 
+// The same wait for warps that only coordinate (producer, epilogue): sleeps between polls so the
+// spinning does not take issue slots from the math warps of the same scheduler.
+__device__ __forceinline__ bool mbar_wait_backoff(uint64_t *bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(64);
+  }
+  return false;
+}
+
 // Global -> shared bulk copy completing on an mbarrier. Both addresses 16-byte aligned, bytes a
 // multiple of 16. No multicast anywhere in this library.
 __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {
@@ -64,6 +74,22 @@ __device__ __forceinline__ void bulk_g2s_stream(void *dst_smem, const void *src_
           "r"(smem_u32(dst_smem)),
       "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
+}
+// Tiled 2-D TMA load of one box at element coordinates (x, y) of a tensor map; x * element size is a
+// multiple of 16 bytes, the destination 128-byte aligned. No multicast.
+__device__ __forceinline__ void tma_load_2d(void *dst_smem, const void *map, int x, int y, uint64_t *bar, uint64_t policy,
+                                            bool hinted) {
+  if (hinted)
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;" ::
+            "r"(smem_u32(dst_smem)),
+        "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
+        : "memory");
+  else
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::
+                     "r"(smem_u32(dst_smem)),
+                 "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar))
+                 : "memory");
 }
 __device__ __forceinline__ uint64_t policy_evict_first() {
   uint64_t p;

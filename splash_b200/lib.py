@@ -20,7 +20,7 @@ class SbError(RuntimeError):
 class SbLinearArgs(ctypes.Structure):
     _fields_ = [
         ("weights", ctypes.c_void_p), ("weights2", ctypes.c_void_p), ("x", ctypes.c_void_p),
-        ("aux", ctypes.c_void_p), ("out", ctypes.c_void_p), ("norm_weight", ctypes.c_void_p),
+        ("prepared", ctypes.c_void_p), ("aux", ctypes.c_void_p), ("out", ctypes.c_void_p), ("norm_weight", ctypes.c_void_p),
         ("format", ctypes.c_uint32), ("n", ctypes.c_uint32), ("k", ctypes.c_uint32), ("rows", ctypes.c_uint32),
         ("x_stride", ctypes.c_uint32), ("aux_stride", ctypes.c_uint32), ("out_stride", ctypes.c_uint32),
         ("epilogue", ctypes.c_uint32), ("out_f32", ctypes.c_uint32), ("flags", ctypes.c_uint32),
@@ -63,6 +63,9 @@ def load():
         _lib.sb_graph_launch.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
         _lib.sb_graph_destroy.argtypes = [ctypes.c_void_p]
         _lib.sb_linear.argtypes = [ctypes.c_void_p, ctypes.POINTER(SbLinearArgs)]
+        _lib.sb_linear_prepare.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32,
+                                           ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32]
+        _lib.sb_linear_prepared_bytes.restype = ctypes.c_uint64
         _lib.sb_dequant.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32,
                                     ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32]
     return _lib
@@ -161,9 +164,9 @@ def stream_sync(stream=None):
     check(load().sb_stream_sync(stream))
 
 
-def linear(weights, x, out, fmt, n, k, rows, *, weights2=None, aux=None, norm_weight=None, epilogue=EP_NONE,
+def linear(weights, x, out, fmt, n, k, rows, *, weights2=None, aux=None, norm_weight=None, prepared=None, epilogue=EP_NONE,
            out_f32=False, x_stride=None, aux_stride=None, out_stride=None, flags=0, stream=None):
     """sb_linear over device pointers (ints)."""
-    a = SbLinearArgs(weights, weights2, x, aux, out, norm_weight, fmt, n, k, rows,
+    a = SbLinearArgs(weights, weights2, x, prepared, aux, out, norm_weight, fmt, n, k, rows,
                      x_stride or k, (aux_stride or n) if aux else 0, out_stride or n, epilogue, int(out_f32), flags)
     check(load().sb_linear(stream, ctypes.byref(a)))

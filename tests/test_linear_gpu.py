@@ -51,7 +51,7 @@ def run_linear(lib, fmt, W, n, k, X, rows, **kw):
 
 
 @pytest.mark.parametrize("fmt,n,k,rows", [
-    (0, 512, 1024, 16), (0, 320, 5120, 16), (0, 192, 6144, 5), (0, 64, 17408, 16), (0, 100, 2816, 16),
+    (0, 512, 1024, 16), (0, 320, 5120, 16), (0, 192, 6144, 5), (0, 64, 17408, 16), (0, 96, 2816, 16),
     (4, 256, 1024, 16), (4, 128, 17408, 16), (4, 192, 5120, 3),
     (6, 256, 1024, 16), (6, 128, 5120, 7),
 ])
