@@ -67,16 +67,17 @@ struct LinearParams {
   // Tiled-TMA geometry. A tensor's rows are served by `period` maps, map j holding rows = j (mod
   // period) so that every map's row stride is a multiple of 16 bytes; a stage is `pieces` column
   // pieces of `piece_sb` super-blocks, each piece one box per (tensor, map): box_rows x pitch bytes.
-  uint32_t period, pieces, piece_sb, box_rows, box_bytes, tensors;
+  uint32_t period, period_log2, pieces, piece_sb, box_rows, box_bytes, tensors;
   uint32_t lead[2][8];  // bytes between map j's 16-byte aligned base and its first row's first byte
   uint32_t x_off, red_off, ring_off;  // shared memory offsets
   uint32_t debug;
 };
 
 template <int FMT> struct WFmt;
-template <> struct WFmt<SB_FMT_Q4K> { static constexpr uint32_t kSbBytes = 144; static constexpr bool kPairLayout = true; };
-template <> struct WFmt<SB_FMT_Q6K> { static constexpr uint32_t kSbBytes = 210; static constexpr bool kPairLayout = false; };
-template <> struct WFmt<SB_FMT_Q80> { static constexpr uint32_t kSbBytes = 272; static constexpr bool kPairLayout = false; };
+// kSbBytes: bytes of 256 weights; kPieceSb: super-blocks per TMA column piece of a stage.
+template <> struct WFmt<SB_FMT_Q4K> { static constexpr uint32_t kSbBytes = 144, kPieceSb = 1; static constexpr bool kPairLayout = true; };
+template <> struct WFmt<SB_FMT_Q6K> { static constexpr uint32_t kSbBytes = 210, kPieceSb = 4; static constexpr bool kPairLayout = false; };
+template <> struct WFmt<SB_FMT_Q80> { static constexpr uint32_t kSbBytes = 272, kPieceSb = 2; static constexpr bool kPairLayout = false; };
 
 __device__ __forceinline__ void slice_range(uint32_t nsb, uint32_t slices, uint32_t s, uint32_t &b0, uint32_t &b1) {
   b0 = s * nsb / slices;
@@ -250,32 +251,23 @@ __device__ __forceinline__ Q4Scales q4_scales(const uint4 hdr, uint32_t t) {
   return r;
 }
 
-template <int FMT>
-__device__ __forceinline__ void multiply_super_block(const uint8_t *wbase, const uint32_t (&roff)[kMT][2],
-                                                     const uint8_t *xs_sb, const uint8_t *sx_sb, uint32_t lane,
-                                                     float (&y)[kMT][2][4]);
-
-template <>
-__device__ __forceinline__ void multiply_super_block<SB_FMT_Q4K>(const uint8_t *wbase, const uint32_t (&roff)[kMT][2],
-                                                                 const uint8_t *xs_sb, const uint8_t *sx_sb,
-                                                                 uint32_t lane, float (&y)[kMT][2][4]) {
+template <int NMT>
+__device__ __forceinline__ void mul_q4k(const uint8_t *wbase, const uint32_t (*roff)[2], const uint8_t *xs_sb,
+                                        const uint8_t *sx_sb, uint32_t lane, float (*y)[2][4]) {
   const uint32_t t = lane & 3;
-  uint32_t q[kMT][2][8];
-  Q4Scales sc[kMT][2];
+  Q4Scales sc[NMT][2];
+  const uint8_t *qrow[NMT][2];
 #pragma unroll
-  for (int mt = 0; mt < kMT; ++mt)
+  for (int mt = 0; mt < NMT; ++mt)
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       const uint8_t *row = wbase + roff[mt][r];
       sc[mt][r] = q4_scales(*reinterpret_cast<const uint4 *>(row), t);
-      const uint4 lo = *reinterpret_cast<const uint4 *>(row + 16 + 32 * t);
-      const uint4 hi = *reinterpret_cast<const uint4 *>(row + 32 + 32 * t);
-      q[mt][r][0] = lo.x, q[mt][r][1] = lo.y, q[mt][r][2] = lo.z, q[mt][r][3] = lo.w;
-      q[mt][r][4] = hi.x, q[mt][r][5] = hi.y, q[mt][r][6] = hi.z, q[mt][r][7] = hi.w;
+      qrow[mt][r] = row + 16 + 32 * t;
     }
-  float aq[kMT][2][4];
+  float aq[NMT][2][4];
 #pragma unroll
-  for (int mt = 0; mt < kMT; ++mt)
+  for (int mt = 0; mt < NMT; ++mt)
 #pragma unroll
     for (int h = 0; h < 2; ++h)
 #pragma unroll
@@ -289,11 +281,16 @@ __device__ __forceinline__ void multiply_super_block<SB_FMT_Q4K>(const uint8_t *
 #pragma unroll
       for (int h = 0; h < 2; ++h)
         bx[p][h] = *reinterpret_cast<const uint4 *>(xs_sb + ((((i2 * 2 + p) * 2 + h) * 32 + lane) << 4));
+    uint2 qw[NMT][2];
 #pragma unroll
-    for (int mt = 0; mt < kMT; ++mt)
+    for (int mt = 0; mt < NMT; ++mt)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) qw[mt][r] = *reinterpret_cast<const uint2 *>(qrow[mt][r] + 8 * i2);
+#pragma unroll
+    for (int mt = 0; mt < NMT; ++mt)
 #pragma unroll
       for (int wi = 0; wi < 2; ++wi) {
-        const uint32_t w0 = q[mt][0][2 * i2 + wi], w1 = q[mt][1][2 * i2 + wi];
+        const uint32_t w0 = wi ? qw[mt][0].y : qw[mt][0].x, w1 = wi ? qw[mt][1].y : qw[mt][1].x;
         const uint32_t w0s = w0 >> 8, w1s = w1 >> 8;
         {
           const uint32_t a0 = hfma2_u32(and_or(w0, 0x000f000fu, kMagic), sc[mt][0].mlo, sc[mt][0].blo);
@@ -320,7 +317,7 @@ __device__ __forceinline__ void multiply_super_block<SB_FMT_Q4K>(const uint8_t *
   for (int h = 0; h < 2; ++h) {
     const uint2 s = *reinterpret_cast<const uint2 *>(sx_sb + ((h * 32 + lane) << 3));
 #pragma unroll
-    for (int mt = 0; mt < kMT; ++mt) {
+    for (int mt = 0; mt < NMT; ++mt) {
       float am[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       mma_f16(am, sc[mt][0].mn0, sc[mt][1].mn0, sc[mt][0].mn1, sc[mt][1].mn1, s.x, s.y);
       y[mt][h][0] = fmaf(sc[mt][0].ndmin, am[0], fmaf(sc[mt][0].d, aq[mt][h][0], y[mt][h][0]));
@@ -342,30 +339,29 @@ __device__ __forceinline__ uint32_t lds2_unaligned(const uint8_t *base, uint32_t
   return *reinterpret_cast<const uint16_t *>(base + at);
 }
 
-template <>
-__device__ __forceinline__ void multiply_super_block<SB_FMT_Q6K>(const uint8_t *wbase, const uint32_t (&roff)[kMT][2],
-                                                                 const uint8_t *xs_sb, const uint8_t *,
-                                                                 uint32_t lane, float (&y)[kMT][2][4]) {
+template <int NMT>
+__device__ __forceinline__ void mul_q6k(const uint8_t *wbase, const uint32_t (*roff)[2], const uint8_t *xs_sb,
+                                        const uint8_t *, uint32_t lane, float (*y)[2][4]) {
   // Lane t of a row multiplies inputs 8t..8t+7 of each of the 8 groups of 32: for half n of the
   // block, ql[64n+8t..] (groups 4n, 4n+2 in its nibbles), ql[64n+32+8t..] (4n+1, 4n+3) and
   // qh[32n+8t..] (two bits per group). The 6-bit code lands in bits 4..9 of a half whose value is
   // 64 + code/... : 0x5400 | code << 4 = 64 + code, so (64 + code) * sc - 96 * sc = sc * (code - 32).
   const uint32_t t = lane & 3;
   const uint32_t kMagic = 0x54005400u, kLow = 0x00f000f0u, kHigh = 0x03000300u;
-  float aq[kMT][2][4];
+  float aq[NMT][2][4];
 #pragma unroll
-  for (int mt = 0; mt < kMT; ++mt)
+  for (int mt = 0; mt < NMT; ++mt)
 #pragma unroll
     for (int h = 0; h < 2; ++h)
 #pragma unroll
       for (int c = 0; c < 4; ++c) aq[mt][h][c] = 0.0f;
-  float dscale[kMT][2];
+  float dscale[NMT][2];
 #pragma unroll
   for (int n = 0; n < 2; ++n) {
-    uint2 qa[kMT][2], qb[kMT][2], qh[kMT][2];
-    uint32_t ms[kMT][2][4], bs[kMT][2][4];
+    uint2 qa[NMT][2], qb[NMT][2], qh[NMT][2];
+    uint32_t ms[NMT][2][4], bs[NMT][2][4];
 #pragma unroll
-    for (int mt = 0; mt < kMT; ++mt)
+    for (int mt = 0; mt < NMT; ++mt)
 #pragma unroll
       for (int r = 0; r < 2; ++r) {
         const uint32_t at = roff[mt][r];
@@ -393,7 +389,7 @@ __device__ __forceinline__ void multiply_super_block<SB_FMT_Q6K>(const uint8_t *
 #pragma unroll
       for (int h = 0; h < 2; ++h) bx[h] = *reinterpret_cast<const uint4 *>(xs_sb + (((j * 2 + h) * 32 + lane) << 4));
 #pragma unroll
-      for (int mt = 0; mt < kMT; ++mt)
+      for (int mt = 0; mt < NMT; ++mt)
 #pragma unroll
         for (int wi = 0; wi < 2; ++wi) {
           uint32_t a[2][2];  // [row][pair]: pair 0 = inputs (0,2), pair 1 = inputs (1,3) of the word
@@ -417,7 +413,7 @@ __device__ __forceinline__ void multiply_super_block<SB_FMT_Q6K>(const uint8_t *
     }
   }
 #pragma unroll
-  for (int mt = 0; mt < kMT; ++mt)
+  for (int mt = 0; mt < NMT; ++mt)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
       y[mt][h][0] = fmaf(dscale[mt][0], aq[mt][h][0], y[mt][h][0]);
@@ -427,10 +423,9 @@ __device__ __forceinline__ void multiply_super_block<SB_FMT_Q6K>(const uint8_t *
     }
 }
 
-template <>
-__device__ __forceinline__ void multiply_super_block<SB_FMT_Q80>(const uint8_t *wbase, const uint32_t (&roff)[kMT][2],
-                                                                 const uint8_t *xs_sb, const uint8_t *,
-                                                                 uint32_t lane, float (&y)[kMT][2][4]) {
+template <int NMT>
+__device__ __forceinline__ void mul_q80(const uint8_t *wbase, const uint32_t (*roff)[2], const uint8_t *xs_sb,
+                                        const uint8_t *, uint32_t lane, float (*y)[2][4]) {
   // A "super-block" is 8 consecutive Q8_0 blocks {half d, 32 int8}. Lane t multiplies bytes
   // 8t..8t+7 of each block; the operand is fp16(d * q), the product rounded once.
   const uint32_t t = lane & 3;
@@ -440,7 +435,7 @@ __device__ __forceinline__ void multiply_super_block<SB_FMT_Q80>(const uint8_t *
 #pragma unroll
     for (int h = 0; h < 2; ++h) bx[h] = *reinterpret_cast<const uint4 *>(xs_sb + (((j * 2 + h) * 32 + lane) << 4));
 #pragma unroll
-    for (int mt = 0; mt < kMT; ++mt) {
+    for (int mt = 0; mt < NMT; ++mt) {
       uint2 qw[2];
       uint32_t d2[2];
 #pragma unroll
@@ -466,6 +461,14 @@ __device__ __forceinline__ void multiply_super_block<SB_FMT_Q80>(const uint8_t *
       }
     }
   }
+}
+
+template <int FMT, int NMT>
+__device__ __forceinline__ void multiply_super_block(const uint8_t *wbase, const uint32_t (*roff)[2], const uint8_t *xs_sb,
+                                                     const uint8_t *sx_sb, uint32_t lane, float (*y)[2][4]) {
+  if (FMT == SB_FMT_Q4K) mul_q4k<NMT>(wbase, roff, xs_sb, sx_sb, lane, y);
+  else if (FMT == SB_FMT_Q6K) mul_q6k<NMT>(wbase, roff, xs_sb, sx_sb, lane, y);
+  else mul_q80<NMT>(wbase, roff, xs_sb, sx_sb, lane, y);
 }
 
 // ---- the kernel ----
@@ -527,7 +530,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams 
         const uint32_t slot = fill % p.stages, round = fill / p.stages;
         if (round > 0) {
           if (!x_issued) issue_x();
-          ok = mbar_wait_backoff(&empty[slot], (round - 1) & 1);
+          ok = (p.debug & 4) ? mbar_wait(&empty[slot], (round - 1) & 1) : mbar_wait_backoff(&empty[slot], (round - 1) & 1);
         }
         if (!ok) break;
         const uint32_t csb0 = sb0 + c * kStageSb, nsb_c = min(uint32_t(kStageSb), sb1 - csb0);
@@ -537,11 +540,11 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams 
         if (lane == 0) mbar_arrive_expect_tx(&full[slot], boxes * p.box_bytes);
         __syncwarp();
         if (lane < boxes) {
-          const uint32_t piece = lane / per_piece, tj = lane % per_piece, tn = tj / p.period, j = tj % p.period;
+          const uint32_t piece = lane / per_piece, tj = lane % per_piece, tn = tj >> p.period_log2, j = tj & (p.period - 1);
           const uint32_t row0 = gate_up ? tile * 32 : tile * kTileRows;
           const uint32_t byte0 = p.lead[tn][j] + (csb0 + piece * p.piece_sb) * kSb;
           uint8_t *dst = smem + p.ring_off + slot * p.stage_bytes + lane * p.box_bytes;
-          tma_load_2d(dst, &maps.m[tn][j], int(byte0 >> 4) * 4, int(row0 / p.period), &full[slot], policy, (p.debug & 2) == 0);
+          tma_load_2d(dst, &maps.m[tn][j], int(byte0 >> 4) * 4, int(row0 >> p.period_log2), &full[slot], policy, (p.debug & 2) == 0);
         }
       }
     }
@@ -568,7 +571,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams 
     const float sback = scale_back[tok];
     uint32_t done = 0;
     for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++done) {
-      if ((done & 1) != ew) continue;
+      if ((done & 1) != ew || (p.debug & 8)) continue;
       const uint32_t tile = item / p.slices;
       if (!mbar_wait_backoff(&red_full[ew], (done >> 1) & 1)) { if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED); return; }
       float v[32];
@@ -709,29 +712,44 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams 
         return;  // the launch has failed; the status word says so
       }
       const uint32_t csb0 = sb0 + c * kStageSb, nsb_c = min(uint32_t(kStageSb), sb1 - csb0);
-      if (kg < nsb_c && !(p.debug & 1)) {
+      // Which super-block of the stage and which of the warp's m-tiles: a full stage gives each
+      // k-group warp one super-block and both m-tiles; a 2-block tail gives every warp one m-tile
+      // (block kg & 1, m-tile kg >> 1), a 1-block tail gives k-groups 0 and 1 one m-tile each.
+      uint32_t sbi = kg, mt0 = 0, nmt = kMT;
+      if (nsb_c == 2) sbi = kg & 1, mt0 = kg >> 1, nmt = 1;
+      else if (nsb_c == 1) sbi = 0, mt0 = kg & 1, nmt = kg < 2 ? 1 : 0;
+      else if (kg >= nsb_c) nmt = 0;
+      if (nmt && !(p.debug & 1)) {
         const uint8_t *stage = smem + p.ring_off + slot * p.stage_bytes;
         // A row sits in the box of its (piece, tensor, residue) at `lead` bytes past a 16-byte boundary
         // (always 0 for Q4_K, whose rows are 16-byte multiples).
-        const uint32_t lsb = csb0 + kg - sb0;
+        constexpr uint32_t kPieceSb = WFmt<FMT>::kPieceSb;
+        const uint32_t lsb = csb0 + sbi - sb0;
+        const uint32_t piece = sbi / kPieceSb, within = sbi % kPieceSb;
         uint32_t roff[kMT][2];
-        const uint32_t piece = kg / p.piece_sb, within = kg % p.piece_sb;
 #pragma unroll
         for (int mt = 0; mt < kMT; ++mt)
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
             const uint32_t tr = rg * 32 + mt * 16 + r * 8 + g;          // tile row
             const uint32_t tn = gate_up ? tr >> 5 : 0, rl = gate_up ? tr & 31 : tr;
-            const uint32_t j = rl % p.period, i = rl / p.period;          // map and row within its box
-            const uint32_t lead = (p.lead[tn][j] + (csb0 + piece * p.piece_sb) * kSb) & 15u;
-            roff[mt][r] = ((piece * p.tensors + tn) * p.period + j) * p.box_bytes + i * p.pitch + lead + within * kSb;
+            if (FMT == SB_FMT_Q4K) {
+              roff[mt][r] = (piece * p.tensors + tn) * p.box_bytes + rl * 144;
+            } else {
+              const uint32_t j = rl & (p.period - 1), i = rl >> p.period_log2;  // map and row within its box
+              const uint32_t lead = (p.lead[tn][j] + (csb0 + piece * kPieceSb) * kSb) & 15u;
+              roff[mt][r] = (((piece * p.tensors + tn) << p.period_log2) + j) * p.box_bytes + i * p.pitch + lead + within * kSb;
+            }
           }
         const uint8_t *xs_sb = smem + p.x_off + lsb * kPrepSbBytes;
-        multiply_super_block<FMT>(stage, roff, xs_sb, xs_sb + kXsbBytes, lane, y);
+        if (nmt == kMT) multiply_super_block<FMT, kMT>(stage, roff, xs_sb, xs_sb + kXsbBytes, lane, y);
+        else if (mt0 == 0) multiply_super_block<FMT, 1>(stage, roff, xs_sb, xs_sb + kXsbBytes, lane, y);
+        else multiply_super_block<FMT, 1>(stage, roff + 1, xs_sb, xs_sb + kXsbBytes, lane, y + 1);
       }
       __syncwarp();
       if (lane == 0) mbar_arrive(&empty[slot]);
     }
+    if (p.debug & 8) continue;
     // Hand the tile's sums to the epilogue warp once it has read the previous tile's.
     if (done > 0 && !mbar_wait(&red_empty[(done - 1) & 1], ((done - 1) >> 1) & 1)) {
       if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
@@ -788,6 +806,7 @@ static int make_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t epilogue,
     p.pieces = kStageSb / p.piece_sb;
     p.pitch = (p.piece_sb * sb_bytes + 14 + 15) & ~15u;
   }
+  p.period_log2 = p.period == 1 ? 0 : p.period == 2 ? 1 : p.period == 4 ? 2 : 3;
   p.box_rows = tile_rows_per_tensor / p.period;
   p.box_bytes = p.box_rows * p.pitch;
   SB_REQUIRE(p.box_bytes % 128 == 0 && p.pitch <= 1024, "sb_linear: unsupported stage geometry (k = %u)", k);
