@@ -66,6 +66,9 @@ SB_API const char *sb_last_error(void);
 /* Reads and clears the device status word (0 = healthy). Synchronizes the device. */
 SB_API int sb_device_status(uint32_t *status);
 SB_API int sb_sm_count(void);
+/* Programmatic dependent launch (kernel prologues overlap the previous kernel's tail) for the small
+ * kernels of this context; on by default. sb_linear takes it per call (SB_LINEAR_PDL). */
+SB_API int sb_set_pdl(int enabled);
 
 SB_API int sb_alloc(size_t bytes, void **out_dev);
 SB_API int sb_free(void *dev);
@@ -150,6 +153,151 @@ typedef struct SbLinearPlan {
 } SbLinearPlan;
 SB_API int sb_linear_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t rows, uint32_t epilogue,
                           SbLinearPlan *out_plan);
+
+
+/* ---- glue operators ---- */
+
+/* y = bf16((x * rsqrt(mean x^2 + 1e-6)) * w), w fp32 [width]. Replaces ops::Normalization::addRms
+ * (runtime/ops/Normalization.cpp:17-42; kernel norm_rms_row, runtime/metal/kernels/shared/normalization.metal:60-94). */
+SB_API int sb_rmsnorm(void *stream, const void *x, uint32_t rows, uint32_t width, uint32_t x_stride, const void *weight,
+                      void *out, uint32_t out_stride);
+
+/* Token row gather with dequantization to bf16; a token outside the table reads row 0. Replaces
+ * ops::Embedding::add (runtime/ops/Embedding.hpp:13-17; runtime/metal/kernels/shared/embedding.metal:10-18). */
+SB_API int sb_embed(void *stream, uint32_t format, const void *table, uint32_t vocab, uint32_t width,
+                    const uint32_t *tokens_dev, uint32_t rows, void *out, uint32_t out_stride);
+
+/* cos/sin [rows][pairs] at positions[row] (device u32), angle = float(position) * inv_freq[pair].
+ * Replaces ops::RoPE::addTreeTables (runtime/ops/RoPE.hpp:12-45; runtime/metal/kernels/shared/rope.metal:50-76):
+ * the caller writes position = anchor + tree depth per row. */
+SB_API int sb_rope_tables(void *stream, const uint32_t *positions_dev, uint32_t rows, const float *inv_freq_dev,
+                          uint32_t pairs, float scale, float *cos_dev, float *sin_dev);
+
+/* fp32 projection of plain fp32 rows: out[rows, n] = x[rows, k] w[n, k]^T, bf16 or fp32 out.
+ * Replaces ops::addGgufFloat (runtime/ops/LinearGguf.cpp:559-604; runtime/metal/kernels/shared/gguf_float.metal:1-8):
+ * the GDN alpha/beta rows and the MoE router. */
+SB_API int sb_linear_f32(void *stream, const float *w_dev, const void *x, uint32_t rows, uint32_t n, uint32_t k,
+                         uint32_t x_stride, void *out, uint32_t out_stride, uint32_t out_f32, const void *norm_weight);
+
+/* ---- INT8 paged KV attention ---- */
+
+/* One attention layer's cache: pages of page_tokens tokens; keys and values token-major
+ * [page][kv_head][token][dim] int8; one scale per (token, kv head), fp32 (scale_f16 = 0, the
+ * reference's: runtime/ops/PagedKv.hpp:223-232) or fp16. */
+typedef struct SbKvLayer {
+  void *k, *v, *k_scale, *v_scale;
+  uint32_t kv_heads, head_dim, page_tokens, scale_f16;
+} SbKvLayer;
+
+/* Per row: per-head RMSNorm of q and k, partial RoPE of pairs (i, i + pairs), queries staged
+ * [row][q_head][dim] bf16, K and V rows quantized into the slot of token committed + row:
+ * scale = max|x| / 127, code = clamp(rint(x * 127 / max), -127, 127). Replaces
+ * ops::PagedAttention::addProjection (runtime/metal/kernels/common/attention_qkv_prepare.h:26-91,
+ * attention_store.h:52-85). qkv row = [q_heads x (q[D], gate[D] if gated)][kv_heads x k][kv_heads x v]. */
+typedef struct SbAttnStoreArgs {
+  const void *qkv;          /* bf16 [rows, qkv_stride] */
+  const float *q_norm, *k_norm; /* fp32 [head_dim] */
+  const float *cos_tab, *sin_tab; /* fp32 [rows, pairs] */
+  const uint32_t *page_table; /* device u32 physical page per logical page */
+  void *queries;            /* bf16 [rows, q_heads, head_dim] */
+  SbKvLayer cache;
+  uint32_t rows, q_heads, gated, pairs, qkv_stride, committed;
+} SbAttnStoreArgs;
+SB_API int sb_attn_store(void *stream, const SbAttnStoreArgs *args);
+
+/* Attention of the step's rows over the stored pages, one launch: a split-KV page loop per (kv head,
+ * split) with online softmax, the splits merged in split order, output gated by sigmoid(gate) where
+ * gated. Row r sees tokens [0, committed + r]; with `tree` (SplashTreeRow: ancestors u32, parent u16,
+ * depth u16; runtime/metal/abi/VerifyTree.h:24-28) block rows are limited to the row's ancestors.
+ * Replaces ops::PagedAttention::addAttention (runtime/metal/kernels/common/paged_attention_tile.h:339-535,
+ * attention_gate.h:19-45). */
+typedef struct SbAttnArgs {
+  const void *queries;      /* bf16 [rows, q_heads, head_dim] from sb_attn_store */
+  const void *qkv;          /* the packed rows, for the gates (NULL when not gated) */
+  const uint32_t *page_table;
+  const void *tree;         /* optional device SplashTreeRow[rows] */
+  void *out;                /* bf16 [rows, out_stride] = [row][q_head][dim] */
+  SbKvLayer cache;
+  uint32_t rows, q_heads, gated, qkv_stride, out_stride, committed;
+} SbAttnArgs;
+SB_API int sb_attn_verify(void *stream, const SbAttnArgs *args);
+
+/* Moves the accepted path's rows (codes and scales) from slot committed + row to slot
+ * committed + depth, in depth order; nothing moves for a chain. Replaces
+ * ops::PagedAttention::addPathCommit (runtime/metal/kernels/shared/kv_path_commit.metal:21-46).
+ * path_mask_dev: device u32, the accepted path's row mask (sb_accept's retained_rows). */
+SB_API int sb_kv_path_commit(void *stream, const SbKvLayer *cache, const uint32_t *page_table, uint32_t committed,
+                             const uint32_t *path_mask_dev);
+
+/* ---- Gated DeltaNet verify step ---- */
+
+typedef struct SbGdnTape {
+  void *inputs; /* bf16 [rows, conv_dim] conv inputs */
+  void *k;      /* bf16 [rows, key_heads * 128] */
+  void *v;      /* bf16 [rows, value_heads * 128] */
+  void *beta;   /* bf16 [rows, value_heads] */
+  float *decay; /* fp32 [rows, value_heads] */
+} SbGdnTape;
+
+/* One lane, one layer: fold the first pending_rows rows of the previous step's tape into the state
+ * (stored as the committed state), then conv + SiLU, q/k norm, gates, the chain scan from the committed
+ * state (outputs only), gated RMSNorm, and this step's tape. pending_rows_dev (optional device u32)
+ * overrides pending_rows so acceptance can stay on the device. Replaces ops::GDN::addDecode / addFold
+ * (runtime/ops/GDN.cpp:225-328; runtime/metal/kernels/decode/gdn.metal:139-616). State fp32
+ * [value_head][value dim 128][key dim 128]. */
+typedef struct SbGdnArgs {
+  const void *qkvz;        /* bf16 [rows, qkvz_stride]: q | k | v | z */
+  const void *b, *a;       /* bf16 [rows, ab_stride] */
+  const void *conv_w;      /* bf16 [conv_dim, 4] */
+  const float *a_scale;    /* fp32 [value_heads] */
+  const void *dt_bias;     /* bf16 [value_heads] */
+  const float *norm_w;     /* fp32 [128] */
+  const void *conv_state_in; /* bf16 [3, conv_dim] */
+  void *conv_state_out;
+  const float *state_in;
+  float *state_out;
+  SbGdnTape pending, step;
+  void *hidden;            /* bf16 [rows, hidden_stride] */
+  const uint32_t *pending_rows_dev;
+  uint32_t rows, pending_rows, key_heads, value_heads, qkvz_stride, ab_stride, hidden_stride, tiled;
+} SbGdnArgs;
+SB_API int sb_gdn_verify(void *stream, const SbGdnArgs *args);
+
+/* ---- selection and acceptance ---- */
+
+/* Selection of every row of one lane's chain. temperature 0: greedy (largest finite logit, ties to the
+ * lowest id, none -> 0xFFFFFFFF). Else weights exp((l - max) / T), shards of 256 ids summed in id order and
+ * the shards in order; the drafted child (input token of row r + 1) is kept iff u_child * Z < w_child, else
+ * the row draws from the residual with its own uniform; the last row draws from the full distribution.
+ * uniforms (device fp32): [0,16) row draws, 16 + 4 * row child tests (runtime/metal/abi/Sampling.h:12-31).
+ * Replaces ops::Sampling::addVerify (runtime/ops/Sampling.cpp:198-328; runtime/metal/kernels/decode/sampling.metal
+ * :1896-1991 greedy, :713-885 draw). */
+typedef struct SbSampleArgs {
+  const float *logits;       /* fp32 [rows, logit_stride] */
+  const uint32_t *input_tokens; /* device u32 [rows] */
+  const float *uniforms;     /* device fp32 [80], or NULL for greedy */
+  uint32_t *selected;        /* device u32 [rows] */
+  float *workspace;          /* device fp32, rows * (2 * shards + 8) */
+  uint32_t rows, vocab, logit_stride;
+  float temperature;
+} SbSampleArgs;
+SB_API uint64_t sb_sample_workspace_bytes(uint32_t rows, uint32_t vocab);
+SB_API int sb_sample_verify(void *stream, const SbSampleArgs *args);
+
+/* Acceptance (runtime/metal/kernels/decode/sampling.metal:2044-2083; params AcceptBatchParams,
+ * runtime/metal/abi/Sampling.h:314-317): follow from row 0 the child whose parent is the row and whose
+ * input token equals the row's selection; kept = min(accepted + 1, remaining); the path's selections
+ * move to the first kept slots of `tokens`; a stop token truncates. results (device u32[4]): retained,
+ * accepted, retained_rows mask, 0. */
+typedef struct SbAcceptArgs {
+  const uint32_t *input_tokens; /* device u32 [rows] */
+  const void *tree;             /* device SplashTreeRow[rows] */
+  uint32_t *tokens;             /* device u32 [rows]: selections in, retained tokens out */
+  uint32_t *results;            /* device u32 [4] */
+  const uint32_t *stop_tokens;  /* device u32 [n_stop] or NULL */
+  uint32_t rows, remaining, n_stop;
+} SbAcceptArgs;
+SB_API int sb_accept(void *stream, const SbAcceptArgs *args);
 
 #ifdef __cplusplus
 }

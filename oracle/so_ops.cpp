@@ -1,0 +1,357 @@
+// TEST INFRASTRUCTURE - CPU oracle, not part of the product library.
+//
+// Glue operators and attention of the verify step, restated from the reference's kernels:
+//   RMSNorm            runtime/metal/kernels/shared/normalization.metal:60-94,
+//                      runtime/metal/kernels/common/rms_inverse.h:15-30
+//   embedding gather   runtime/metal/kernels/shared/embedding.metal:10-18 (out-of-range token -> row 0)
+//   RoPE tables        runtime/metal/kernels/shared/rope.metal:50-76, common/target_rope.h:7-16
+//   q/k norm + RoPE + INT8 KV store
+//                      runtime/metal/kernels/common/attention_qkv_prepare.h:26-91,
+//                      runtime/metal/kernels/common/attention_store.h:52-85
+//                      (CPU twin dev/tests/engine/Q8PageFormatReference.hpp:107-119)
+//   paged attention    runtime/metal/kernels/common/paged_attention_tile.h:178-285,339-471,498-535,
+//                      runtime/metal/kernels/common/attention_gate.h:19-45; the fp64 model follows
+//                      dev/tests/engine/q8_flash_attention_metal_test.mm:483-536
+//   selection          runtime/metal/kernels/decode/sampling.metal:984-989,1896-1991 (greedy),
+//                      :44-49,:778-800 (temperature weights, child test, residual draw)
+//   acceptance         runtime/metal/kernels/decode/sampling.metal:2044-2083
+//   path commit        runtime/metal/kernels/shared/kv_path_commit.metal:21-46
+// Parity of the INT8 quantizer is pinned against the reference's own CPU code through oracle/_ref
+// (tests/test_oracle_ops.py); attention, selection and acceptance have no stored vectors in the
+// reference ("parity unpinned" for those: tolerance gates and invariants only).
+#include "so_common.h"
+
+#include <algorithm>
+#include <cmath>
+#include <vector>
+
+SO_API int so_dequant(uint32_t f, const uint8_t *native, uint32_t rows, uint32_t K, float *out);
+SO_API uint64_t so_row_bytes(uint32_t f, uint32_t K);
+
+using namespace so;
+
+// y = bf16((x * rsqrt(mean x^2 + 1e-6)) * w); the sum of squares runs in the product's order: lanes
+// of 32 over 8-element groups strided by 256, a butterfly over the lanes, then (rows wider than a
+// warp's share) the warps in order. Tests compare with a tolerance of one bf16 ulp, the latitude the
+// reference's own simd_sum leaves.
+SO_API void so_rmsnorm(const uint16_t *x, uint32_t rows, uint32_t width, uint32_t x_stride, const float *w,
+                       uint16_t *out, uint32_t out_stride) {
+  for (uint32_t r = 0; r < rows; ++r) {
+    double ss = 0;
+    for (uint32_t c = 0; c < width; ++c) {
+      const double v = bf2f(x[size_t(r) * x_stride + c]);
+      ss += v * v;
+    }
+    const float inv = 1.0f / std::sqrt(float(ss / width) + kRmsEps);
+    for (uint32_t c = 0; c < width; ++c)
+      out[size_t(r) * out_stride + c] = f2bf((bf2f(x[size_t(r) * x_stride + c]) * inv) * w[c]);
+  }
+}
+
+// Token row gather with dequantization to bf16; a token outside the table reads row 0.
+SO_API int so_embed(uint32_t fmt, const uint8_t *table, uint32_t vocab, uint32_t width, const uint32_t *tokens,
+                    uint32_t rows, uint16_t *out, uint32_t out_stride) {
+  const uint64_t rb = so_row_bytes(fmt, width);
+  if (!rb) return -1;
+  std::vector<float> v(width);
+  for (uint32_t r = 0; r < rows; ++r) {
+    const uint32_t t = tokens[r] < vocab ? tokens[r] : 0;
+    so_dequant(fmt, table + t * rb, 1, width, v.data());
+    for (uint32_t c = 0; c < width; ++c) out[size_t(r) * out_stride + c] = f2bf(v[c]);
+  }
+  return 0;
+}
+
+// cos/sin[row][pair] at position anchor + depth; angle = float(position) * inv_freq[pair], times scale.
+SO_API void so_rope_tables(const uint32_t *positions, uint32_t rows, const float *inv_freq, uint32_t pairs, float scale,
+                           float *cosine, float *sine) {
+  for (uint32_t r = 0; r < rows; ++r)
+    for (uint32_t p = 0; p < pairs; ++p) {
+      const float angle = float(positions[r]) * inv_freq[p];
+      cosine[size_t(r) * pairs + p] = std::cos(angle) * scale;
+      sine[size_t(r) * pairs + p] = std::sin(angle) * scale;
+    }
+}
+
+// INT8 KV row: scale = max|x| / 127 (0 for a zero row), code = clamp(rint(x * 127 / max), -127, 127).
+static inline float kv_scale(float m) { return m == 0.0f ? 0.0f : m / 127.0f; }
+static inline int8_t kv_code(float v, float m) {
+  if (m == 0.0f) return 0;
+  long q = long(std::nearbyint(v * 127.0f / m));
+  return int8_t(std::clamp<long>(q, -127, 127));
+}
+SO_API float so_kv_scale(float m) { return kv_scale(m); }
+SO_API int so_kv_code(float v, float m) { return kv_code(v, m); }
+
+// One attention layer's cache: pages of `page_tokens` tokens, keys and values token-major
+// [page][kv_head][token][dim] int8, scales [page][kv_head][token] fp32 (scale_f16 == 0) or fp16.
+struct SoKvLayer {
+  int8_t *k, *v;
+  void *k_scale, *v_scale;
+  uint32_t kv_heads, head_dim, page_tokens, scale_f16;
+};
+static inline size_t kv_elem(const SoKvLayer &c, uint32_t page, uint32_t head, uint32_t tok) {
+  return ((size_t(page) * c.kv_heads + head) * c.page_tokens + tok) * c.head_dim;
+}
+static inline size_t kv_sc(const SoKvLayer &c, uint32_t page, uint32_t head, uint32_t tok) {
+  return (size_t(page) * c.kv_heads + head) * c.page_tokens + tok;
+}
+static inline float load_scale(const void *p, size_t i, uint32_t f16) {
+  return f16 ? h2f(static_cast<const uint16_t *>(p)[i]) : static_cast<const float *>(p)[i];
+}
+static inline void store_scale(void *p, size_t i, uint32_t f16, float s) {
+  if (f16) static_cast<uint16_t *>(p)[i] = f2h(s);
+  else static_cast<float *>(p)[i] = s;
+}
+
+// Per row of one sequence: per-head RMSNorm of q and k with weights, rotation of pairs (i, i + pairs)
+// of the first 2 * pairs dimensions by the row's table row, queries staged [row][q_head][dim] bf16,
+// K and V rows quantized into the slot of token committed + row through the page table.
+// qkv row = [q_heads x (q[D], gate[D] if gated)] [kv_heads x k[D]] [kv_heads x v[D]].
+SO_API void so_attn_store(const uint16_t *qkv, uint32_t qkv_stride, uint32_t rows, uint32_t q_heads, uint32_t gated,
+                          const float *q_norm, const float *k_norm, const float *cosine, const float *sine,
+                          uint32_t pairs, const SoKvLayer *cache, const uint32_t *page_table, uint32_t committed,
+                          uint16_t *queries) {
+  const uint32_t D = cache->head_dim, KH = cache->kv_heads, qs = gated ? 2 * D : D;
+  std::vector<float> n(D);
+  auto norm_rope = [&](const uint16_t *src, const float *w, uint32_t row, uint16_t *dst) {
+    float ss = 0.0f;
+    // HeadDim / 32 partials of 32 dimensions each, added in order (attention_qkv_prepare.h:59-65).
+    for (uint32_t g = 0; g < D / 32; ++g) {
+      float part = 0.0f;
+      for (uint32_t i = 0; i < 32; ++i) {
+        const float v = bf2f(src[32 * g + i]);
+        part += v * v;
+      }
+      ss += part;
+    }
+    const float inv = 1.0f / std::sqrt(ss / D + kRmsEps);
+    for (uint32_t d = 0; d < D; ++d) n[d] = rbf(bf2f(src[d]) * inv * w[d]);
+    for (uint32_t d = 0; d < D; ++d) {
+      float r = n[d];
+      if (d < 2 * pairs) {
+        const uint32_t p = d % pairs;
+        const float a = n[p], b = n[p + pairs], c = cosine[size_t(row) * pairs + p], s = sine[size_t(row) * pairs + p];
+        r = d < pairs ? rbf(a * c - b * s) : rbf(b * c + a * s);
+      }
+      dst[d] = f2bf(r);
+    }
+  };
+  std::vector<uint16_t> kn(D);
+  for (uint32_t r = 0; r < rows; ++r) {
+    const uint16_t *row = qkv + size_t(r) * qkv_stride;
+    for (uint32_t h = 0; h < q_heads; ++h) norm_rope(row + h * qs, q_norm, r, queries + (size_t(r) * q_heads + h) * D);
+    const uint32_t tok = committed + r, page = page_table[tok / cache->page_tokens], pt = tok % cache->page_tokens;
+    for (uint32_t h = 0; h < KH; ++h) {
+      norm_rope(row + q_heads * qs + h * D, k_norm, r, kn.data());
+      const uint16_t *vsrc = row + q_heads * qs + KH * D + h * D;
+      float km = 0.0f, vm = 0.0f;
+      for (uint32_t d = 0; d < D; ++d) {
+        km = std::max(km, std::fabs(bf2f(kn[d])));
+        vm = std::max(vm, std::fabs(bf2f(vsrc[d])));
+      }
+      for (uint32_t d = 0; d < D; ++d) {
+        cache->k[kv_elem(*cache, page, h, pt) + d] = kv_code(bf2f(kn[d]), km);
+        cache->v[kv_elem(*cache, page, h, pt) + d] = kv_code(bf2f(vsrc[d]), vm);
+      }
+      store_scale(cache->k_scale, kv_sc(*cache, page, h, pt), cache->scale_f16, kv_scale(km));
+      store_scale(cache->v_scale, kv_sc(*cache, page, h, pt), cache->scale_f16, kv_scale(vm));
+    }
+  }
+}
+
+// Attention of `rows` chain rows of one sequence over the stored INT8 pages, in fp64: row r sees
+// tokens [0, committed + r]; score = (q . k_code) * k_scale / sqrt(D); out = softmax . (v_code * v_scale),
+// rounded to bf16, then (gated) times sigmoid(gate) and rounded again. `tree` (optional, 8 bytes a
+// row: ancestors u32, parent u16, depth u16) restricts a row to its ancestors inside the block.
+SO_API void so_attention(const uint16_t *queries, const uint16_t *qkv, uint32_t qkv_stride, uint32_t rows,
+                         uint32_t q_heads, uint32_t gated, const SoKvLayer *cache, const uint32_t *page_table,
+                         uint32_t committed, const uint32_t *tree, uint16_t *out, uint32_t out_stride,
+                         double *out_f64) {
+  const uint32_t D = cache->head_dim, KH = cache->kv_heads, G = q_heads / KH, qs = gated ? 2 * D : D;
+  const double scale = 1.0 / std::sqrt(double(D));
+#pragma omp parallel for collapse(2) schedule(dynamic)
+  for (int64_t r = 0; r < int64_t(rows); ++r)
+    for (int64_t h = 0; h < int64_t(q_heads); ++h) {
+      const uint32_t kvh = uint32_t(h) / G;
+      const uint16_t *q = queries + (size_t(r) * q_heads + h) * D;
+      uint32_t visible = committed + uint32_t(r) + 1, ancestors = 0xffffffffu;
+      if (tree) {
+        ancestors = tree[2 * r];
+        const uint32_t depth = tree[2 * r + 1] >> 16;
+        visible = committed + rows;  // block rows are filtered by the ancestor mask below
+        (void)depth;
+      }
+      std::vector<double> s(visible);
+      double mx = -INFINITY;
+      for (uint32_t t = 0; t < visible; ++t) {
+        if (tree && t >= committed && !((ancestors >> (t - committed)) & 1u)) { s[t] = -INFINITY; continue; }
+        const uint32_t page = page_table[t / cache->page_tokens], pt = t % cache->page_tokens;
+        const int8_t *k = cache->k + kv_elem(*cache, page, kvh, pt);
+        double dot = 0;
+        for (uint32_t d = 0; d < D; ++d) dot += double(bf2f(q[d])) * k[d];
+        s[t] = dot * load_scale(cache->k_scale, kv_sc(*cache, page, kvh, pt), cache->scale_f16) * scale;
+        mx = std::max(mx, s[t]);
+      }
+      std::vector<double> acc(D, 0.0);
+      double den = 0;
+      for (uint32_t t = 0; t < visible; ++t) {
+        if (s[t] == -INFINITY) continue;
+        const uint32_t page = page_table[t / cache->page_tokens], pt = t % cache->page_tokens;
+        const double p = std::exp(s[t] - mx);
+        den += p;
+        const double pv = p * load_scale(cache->v_scale, kv_sc(*cache, page, kvh, pt), cache->scale_f16);
+        const int8_t *v = cache->v + kv_elem(*cache, page, kvh, pt);
+        for (uint32_t d = 0; d < D; ++d) acc[d] += pv * v[d];
+      }
+      for (uint32_t d = 0; d < D; ++d) {
+        const double o = den > 0 ? acc[d] / den : 0.0;
+        float v = rbf(float(o));
+        double exact = o;
+        if (gated) {
+          const float gate = bf2f(qkv[size_t(r) * qkv_stride + h * qs + D + d]);
+          exact = double(v) * double(sigmoid(gate));
+          v = v * sigmoid(gate);
+        }
+        out[size_t(r) * out_stride + h * D + d] = f2bf(v);
+        if (out_f64) out_f64[(size_t(r) * q_heads + h) * D + d] = exact;
+      }
+    }
+}
+
+// Moves the accepted path's rows' K/V (codes and scales) from slot committed + row to slot
+// committed + depth, in depth order; a chain's rows are already in place.
+SO_API void so_kv_path_commit(const SoKvLayer *cache, const uint32_t *page_table, uint32_t committed, uint32_t path_mask) {
+  const uint32_t D = cache->head_dim;
+  uint32_t depth = 0;
+  for (uint32_t row = 0; row < 32; ++row) {
+    if (!((path_mask >> row) & 1u)) continue;
+    if (row != depth) {
+      const uint32_t s = committed + row, t = committed + depth;
+      const uint32_t sp = page_table[s / cache->page_tokens], st = s % cache->page_tokens;
+      const uint32_t tp = page_table[t / cache->page_tokens], tt = t % cache->page_tokens;
+      for (uint32_t h = 0; h < cache->kv_heads; ++h) {
+        memcpy(cache->k + kv_elem(*cache, tp, h, tt), cache->k + kv_elem(*cache, sp, h, st), D);
+        memcpy(cache->v + kv_elem(*cache, tp, h, tt), cache->v + kv_elem(*cache, sp, h, st), D);
+        store_scale(cache->k_scale, kv_sc(*cache, tp, h, tt), cache->scale_f16,
+                    load_scale(cache->k_scale, kv_sc(*cache, sp, h, st), cache->scale_f16));
+        store_scale(cache->v_scale, kv_sc(*cache, tp, h, tt), cache->scale_f16,
+                    load_scale(cache->v_scale, kv_sc(*cache, sp, h, st), cache->scale_f16));
+      }
+    }
+    ++depth;
+  }
+}
+
+// ---- selection ----
+constexpr uint32_t kSentinel = 0xFFFFFFFFu;
+constexpr uint32_t kShard = 256;  // ids per shard of the mass sums
+
+// Greedy: the largest finite logit, ties to the lowest id; none selectable -> the sentinel.
+static uint32_t argmax_row(const float *l, uint32_t vocab) {
+  uint32_t best = kSentinel;
+  float bv = -INFINITY;
+  for (uint32_t v = 0; v < vocab; ++v) {
+    const float x = l[v];
+    if (std::isnan(x) || x == -INFINITY) continue;
+    if (best == kSentinel || x > bv) best = v, bv = x;
+  }
+  return best;
+}
+
+// Selection of every row of one lane (a chain of `rows` rows; row r's drafted child is the input
+// token of row r + 1). temperature == 0: greedy. Otherwise weights w_v = exp((l_v - max) / T)
+// (non-finite logits weigh 0); each shard of 256 ids is summed in id order and the shards in order;
+// the drafted child is accepted iff u_child * Z < w_child (q = 1 for a deterministic draft), else the
+// row draws from the residual (w_child removed) with its own uniform: target = u_row * Z', the first id
+// whose running sum exceeds it; the last row always draws from the full
+// distribution. uniforms: [0,16) row draws, 16 + 4 * row child tests.
+SO_API void so_sample_verify(const float *logits, uint32_t logit_stride, uint32_t vocab, uint32_t rows,
+                             const uint32_t *input_tokens, float temperature, const float *uniforms,
+                             uint32_t *selected, double *decision_margin) {
+  for (uint32_t r = 0; r < rows; ++r) {
+    const float *l = logits + size_t(r) * logit_stride;
+    if (decision_margin) decision_margin[r] = INFINITY;
+    const uint32_t top = argmax_row(l, vocab);
+    if (temperature == 0.0f || top == kSentinel) { selected[r] = top; continue; }
+    const float mx = l[top], inv_t = 1.0f / temperature;
+    const uint32_t shards = (vocab + kShard - 1) / kShard;
+    std::vector<float> w(vocab), shard(shards, 0.0f);
+    for (uint32_t v = 0; v < vocab; ++v) {
+      const float x = l[v];
+      w[v] = (std::isnan(x) || x == -INFINITY) ? 0.0f : expf((x - mx) * inv_t);
+    }
+    const bool has_child = r + 1 < rows;
+    const uint32_t child = has_child ? input_tokens[r + 1] : kSentinel;
+    auto mass = [&](bool drop_child, std::vector<float> &sh) {
+      float total = 0.0f;
+      for (uint32_t s = 0; s < shards; ++s) {
+        float sum = 0.0f;
+        for (uint32_t v = s * kShard; v < std::min(vocab, (s + 1) * kShard); ++v)
+          sum += (drop_child && v == child) ? 0.0f : w[v];
+        sh[s] = sum;
+        total += sum;
+      }
+      return total;
+    };
+    const float z = mass(false, shard);
+    bool drop = false;
+    if (has_child && child < vocab) {
+      const float u = uniforms[16 + 4 * r];
+      if (decision_margin) decision_margin[r] = std::fabs(double(u) * z - w[child]) / std::max(double(z), 1e-30);
+      if (u * z < w[child]) { selected[r] = child; continue; }
+      drop = true;
+    }
+    const float zr = drop ? mass(true, shard) : z;
+    // The first id whose running sum exceeds the target; the running sum of an id is the sum of the
+    // shards before its shard (added in order) plus its shard's ids up to it (added in order from 0).
+    const float target = uniforms[r] * zr;
+    float run = 0.0f;
+    uint32_t pick = kSentinel;
+    for (uint32_t s = 0; s < shards && pick == kSentinel; ++s) {
+      if (run + shard[s] > target) {
+        float loc = 0.0f;
+        for (uint32_t v = s * kShard; v < std::min(vocab, (s + 1) * kShard); ++v) {
+          loc += (drop && v == child) ? 0.0f : w[v];
+          if (run + loc > target) { pick = v; break; }
+        }
+      }
+      run += shard[s];
+    }
+    if (pick == kSentinel)  // rounding put the target at or past the total: the last id that weighs
+      for (uint32_t v = vocab; v-- > 0;)
+        if (w[v] > 0.0f && !(drop && v == child)) { pick = v; break; }
+    selected[r] = pick;
+  }
+}
+
+// Acceptance of one lane (sampling.metal:2044-2083): from row 0 follow the child whose parent is
+// the row and whose input token is the row's selection; kept = min(accepted + 1, remaining); the
+// path's selections move to the first kept slots; a stop token truncates.
+// tree: 8 bytes a row (ancestors u32, parent u16 | depth u16 << 16).
+SO_API void so_accept(const uint32_t *input_tokens, const uint32_t *tree, uint32_t *tokens, uint32_t rows,
+                      uint32_t remaining, const uint32_t *stop_tokens, uint32_t n_stop, uint32_t *retained,
+                      uint32_t *accepted_count, uint32_t *retained_rows) {
+  uint32_t path[32];
+  path[0] = 0;
+  uint32_t accepted = 0;
+  for (uint32_t row = 0;;) {
+    const uint32_t token = tokens[row];
+    uint32_t next = 0;
+    for (uint32_t child = row + 1; child < rows && !next; ++child)
+      next = ((tree[2 * child + 1] & 0xffffu) == row && input_tokens[child] == token) ? child : 0;
+    if (!next) break;
+    path[++accepted] = next;
+    row = next;
+  }
+  uint32_t kept = std::min(accepted + 1, remaining);
+  for (uint32_t i = 0; i < kept; ++i) {
+    const uint32_t token = tokens[path[i]];
+    tokens[i] = token;
+    for (uint32_t s = 0; s < n_stop; ++s)
+      if (stop_tokens[s] == token) kept = i + 1;
+  }
+  *accepted_count = std::min(accepted, kept);
+  *retained = kept;
+  *retained_rows = tree[2 * path[kept - 1]];
+}

@@ -1,0 +1,391 @@
+// INT8 paged-KV attention over the verify block, one kernel: split-KV page loop with online softmax,
+// then the split merge, bf16 rounding and the output gate in the CTA that arrives last for its KV head.
+//
+// Takes the place of the reference's split + reduce kernels (attention_q8_split*, attention_reduce*,
+// runtime/metal/kernels/shared/paged_attention.metal:13-78; tile math
+// runtime/metal/kernels/common/paged_attention_tile.h:178-285,339-471; merge :498-535; gate
+// runtime/metal/kernels/common/attention_gate.h:19-45).
+//
+//   grid      (splits, kv_heads); 256 threads. The step's rows x the KV head's query heads form the
+//             fused rows (row-major: fused = row * group + head_in_group, at most 128); warp w owns fused
+//             rows 16w..16w+15 as one m16 MMA tile, warps without rows only help loading.
+//   split     a contiguous run of 32-token chunks of the visible tokens [0, committed + rows)
+//   chunk     K and V rows (token-major int8, 32 x D bytes contiguous inside a page) are fetched with
+//             16-byte loads one chunk ahead, converted exactly to fp16 ((q ^ 0x80 | 0x6400) - 1152) and
+//             stored in shared memory; S = Q K^T and O += P V run on mma.sync m16n8k16 (fp16 operands,
+//             fp32 accumulators) with ldmatrix fragments; score = S * k_scale[token] / sqrt(D); row r sees
+//             tokens <= committed + r (and, with a tree, only its ancestors inside the block);
+//             P = fp16(p * v_scale[token]) (the reference rounds this product to bf16)
+//   merge     fp32 partial O and (max, sum) per split go to the context's workspace; the last CTA of a KV
+//             head adds the splits in split order with weights exp(max_s - max), divides, rounds to bf16
+//             and multiplies by sigmoid(gate)
+#include <algorithm>
+
+#include "sb_internal.h"
+#include "sb_ptx.cuh"
+
+namespace sb {
+
+constexpr int kAttnThreads = 256;
+constexpr int kChunk = 32;       // tokens per step of the page loop
+constexpr int kMaxFused = 128;   // rows x query heads of one KV head
+
+struct AttnParams {
+  const uint16_t *queries, *qkv;
+  const uint32_t *page_table;
+  const uint2 *tree;
+  uint16_t *out;
+  SbKvLayer cache;
+  float *partials;     // [kv_head][split][fused][D]
+  float *stats;        // [kv_head][split][fused][2]
+  uint32_t *counters;  // [kv_head]
+  uint32_t rows, q_heads, group, gated, qkv_stride, out_stride, committed, splits, chunks_per_split, fused;
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *p) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(p)));
+}
+
+// 16 int8 (one uint4) -> 16 fp16, exactly: (q ^ 0x80) | 0x6400 is 1024 + q + 128.
+__device__ __forceinline__ void int8x16_to_half(const uint4 v, uint4 &lo, uint4 &hi) {
+  const uint32_t w[4] = {v.x ^ 0x80808080u, v.y ^ 0x80808080u, v.z ^ 0x80808080u, v.w ^ 0x80808080u};
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    o[2 * i] = hsub2_u32(__byte_perm(w[i], 0x64646464u, 0x4140), 0x64806480u);      // bytes 0, 1
+    o[2 * i + 1] = hsub2_u32(__byte_perm(w[i], 0x64646464u, 0x4342), 0x64806480u);  // bytes 2, 3
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+template <int D>
+__global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnParams p) {
+  constexpr int PITCH = D + 8;             // halves per shared row: 16-byte rows shifted by 4 banks
+  constexpr int KSTEPS = D / 16, NT_O = D / 8;
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __half *q_s = reinterpret_cast<__half *>(smem_raw);              // [128][PITCH]
+  __half *k_s = q_s + kMaxFused * PITCH;                            // [32][PITCH]
+  __half *v_s = k_s + kChunk * PITCH;                               // [32][PITCH]
+  float *ks_s = reinterpret_cast<float *>(v_s + kChunk * PITCH);    // [32] key scales * 1/sqrt(D) * log2(e)
+  float *vs_s = ks_s + kChunk;                                      // [32]
+  __shared__ uint32_t s_last;
+  pdl_launch_dependents();
+  pdl_wait();
+
+  const uint32_t split = blockIdx.x, kvh = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t g = lane >> 2, t = lane & 3;
+  const uint32_t F = p.fused, G = p.group;
+  const uint32_t visible = p.committed + p.rows;
+  const uint32_t chunks = (visible + kChunk - 1) / kChunk;
+  const uint32_t c_begin = split * p.chunks_per_split, c_end = min(chunks, c_begin + p.chunks_per_split);
+
+  // Queries of this KV head -> fp16 in shared memory (bounded by the q norm, so the conversion is exact
+  // down to fp16's subnormals); rows past the fused rows are zero.
+  for (uint32_t i = tid; i < kMaxFused * (D / 8); i += kAttnThreads) {
+    const uint32_t f = i / (D / 8), c8 = i % (D / 8);
+    uint4 o = make_uint4(0, 0, 0, 0);
+    if (f < F) {
+      const uint32_t row = f / G, hg = f % G;
+      const uint4 raw = *reinterpret_cast<const uint4 *>(p.queries + (size_t(row) * p.q_heads + kvh * G + hg) * D + c8 * 8);
+      const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+      uint32_t h[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __half2 hv = __floats2half2_rn(bf16_bits_to_float(u[j] & 0xffffu), bf16_bits_to_float(u[j] >> 16));
+        h[j] = *reinterpret_cast<const uint32_t *>(&hv);
+      }
+      o = make_uint4(h[0], h[1], h[2], h[3]);
+    }
+    *reinterpret_cast<uint4 *>(q_s + f * PITCH + c8 * 8) = o;
+  }
+
+  const bool computes = warp * 16 < F;
+  float o_acc[NT_O][4];
+#pragma unroll
+  for (int n = 0; n < NT_O; ++n)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o_acc[n][c] = 0.0f;
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
+  // Rows of this thread's two fused rows and what they may see.
+  uint32_t limit[2], anc[2];
+#pragma unroll
+  for (int hrow = 0; hrow < 2; ++hrow) {
+    const uint32_t f = warp * 16 + g + 8 * hrow, row = min(f / G, p.rows - 1);
+    limit[hrow] = p.committed + row + 1;  // tokens below this are visible to a chain row
+    anc[hrow] = 0xffffffffu;
+    if (p.tree) {
+      limit[hrow] = visible;
+      anc[hrow] = p.tree[row].x;
+    }
+  }
+
+  // Chunk loader: thread -> (token = tid / 8, 32 bytes of the row at (tid % 8) * 32 ...). D bytes per
+  // token = D / 16 uint4; 32 tokens x D / 16 uint4 over 256 threads = D / 128 uint4 each, K and V.
+  constexpr int LD = D / 128;  // uint4 per thread per tensor
+  uint4 kreg[LD], vreg[LD];
+  float ksc = 0.0f, vsc = 0.0f;
+  auto fetch = [&](uint32_t chunk) {
+    const uint32_t tok0 = chunk * kChunk;
+#pragma unroll
+    for (int i = 0; i < LD; ++i) {
+      const uint32_t idx = tid + i * kAttnThreads, tok = idx / (D / 16), part = idx % (D / 16);
+      const uint32_t tk = tok0 + tok;
+      kreg[i] = make_uint4(0x80808080u ^ 0x80808080u, 0, 0, 0);
+      vreg[i] = make_uint4(0, 0, 0, 0);
+      if (tk < visible) {
+        const uint32_t page = p.page_table[tk / p.cache.page_tokens], pt = tk % p.cache.page_tokens;
+        const size_t slot = (size_t(page) * p.cache.kv_heads + kvh) * p.cache.page_tokens + pt;
+        kreg[i] = *reinterpret_cast<const uint4 *>(static_cast<const int8_t *>(p.cache.k) + slot * D + part * 16);
+        vreg[i] = *reinterpret_cast<const uint4 *>(static_cast<const int8_t *>(p.cache.v) + slot * D + part * 16);
+      }
+    }
+    if (tid < kChunk) {
+      const uint32_t tk = tok0 + tid;
+      ksc = 0.0f, vsc = 0.0f;
+      if (tk < visible) {
+        const uint32_t page = p.page_table[tk / p.cache.page_tokens], pt = tk % p.cache.page_tokens;
+        const size_t slot = (size_t(page) * p.cache.kv_heads + kvh) * p.cache.page_tokens + pt;
+        if (p.cache.scale_f16) {
+          ksc = __half2float(static_cast<const __half *>(p.cache.k_scale)[slot]);
+          vsc = __half2float(static_cast<const __half *>(p.cache.v_scale)[slot]);
+        } else {
+          ksc = static_cast<const float *>(p.cache.k_scale)[slot];
+          vsc = static_cast<const float *>(p.cache.v_scale)[slot];
+        }
+      }
+    }
+  };
+  const float score_scale = (D == 256 ? 0.0625f : 0.08838834764831845f) * 1.44269504089f;  // 1/sqrt(D) * log2(e)
+  auto stage = [&]() {
+#pragma unroll
+    for (int i = 0; i < LD; ++i) {
+      const uint32_t idx = tid + i * kAttnThreads, tok = idx / (D / 16), part = idx % (D / 16);
+      uint4 lo, hi;
+      int8x16_to_half(kreg[i], lo, hi);
+      *reinterpret_cast<uint4 *>(k_s + tok * PITCH + part * 16) = lo;
+      *reinterpret_cast<uint4 *>(k_s + tok * PITCH + part * 16 + 8) = hi;
+      int8x16_to_half(vreg[i], lo, hi);
+      *reinterpret_cast<uint4 *>(v_s + tok * PITCH + part * 16) = lo;
+      *reinterpret_cast<uint4 *>(v_s + tok * PITCH + part * 16 + 8) = hi;
+    }
+    if (tid < kChunk) {
+      ks_s[tid] = ksc * score_scale;
+      vs_s[tid] = vsc;
+    }
+  };
+
+  if (c_begin < c_end) fetch(c_begin);
+  for (uint32_t chunk = c_begin; chunk < c_end; ++chunk) {
+    __syncthreads();  // the previous chunk's readers are done (and q_s is written, first time)
+    stage();
+    __syncthreads();
+    if (chunk + 1 < c_end) fetch(chunk + 1);
+    if (!computes) continue;
+    const uint32_t tok0 = chunk * kChunk;
+    // S = Q K^T for 16 fused rows x 32 tokens.
+    float s_acc[4][4];
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) s_acc[n][c] = 0.0f;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      uint32_t a[4];
+      ldmatrix_x4(a, q_s + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+      for (int np = 0; np < 2; ++np) {
+        uint32_t b[4];
+        ldmatrix_x4(b, k_s + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * PITCH + ks * 16 + ((lane >> 3) & 1) * 8);
+        mma_f16(s_acc[2 * np], a[0], a[1], a[2], a[3], b[0], b[1]);
+        mma_f16(s_acc[2 * np + 1], a[0], a[1], a[2], a[3], b[2], b[3]);
+      }
+    }
+    // Scores (in log2 units), masks, online softmax. Accumulator c: row g + 8 (c >> 1), token 8 n + 2 t + (c & 1).
+    float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int n = 0; n < 4; ++n)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t tl = 8 * n + 2 * t + (c & 1), tk = tok0 + tl;
+        const int hrow = c >> 1;
+        bool seen = tk < limit[hrow];
+        if (p.tree && tk >= p.committed) seen = seen && ((anc[hrow] >> min(tk - p.committed, 31u)) & 1u);
+        const float sc = seen ? s_acc[n][c] * ks_s[tl] : -INFINITY;
+        s_acc[n][c] = sc;
+        mx[hrow] = fmaxf(mx[hrow], sc);
+      }
+    float corr[2];
+#pragma unroll
+    for (int hrow = 0; hrow < 2; ++hrow) {
+      mx[hrow] = fmaxf(mx[hrow], __shfl_xor_sync(0xffffffffu, mx[hrow], 1));
+      mx[hrow] = fmaxf(mx[hrow], __shfl_xor_sync(0xffffffffu, mx[hrow], 2));
+      const float m_new = fmaxf(m_run[hrow], mx[hrow]);
+      corr[hrow] = (m_new == -INFINITY || m_new == m_run[hrow]) ? 1.0f : exp2f(m_run[hrow] - m_new);
+      m_run[hrow] = m_new;
+    }
+    float psum[2] = {0.0f, 0.0f};
+    uint32_t pa[2][4];  // P as A fragments for the two 16-token k-steps
+#pragma unroll
+    for (int n = 0; n < 4; ++n) {
+      float pv[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int hrow = c >> 1;
+        const float pr = s_acc[n][c] == -INFINITY ? 0.0f : exp2f(s_acc[n][c] - m_run[hrow]);
+        psum[hrow] += pr;
+        pv[c] = pr * vs_s[8 * n + 2 * t + (c & 1)];
+      }
+      const __half2 r0 = __floats2half2_rn(pv[0], pv[1]), r1 = __floats2half2_rn(pv[2], pv[3]);
+      // n-tile n covers tokens 8n..8n+7: k-step n / 2, low (n even) or high (n odd) half of its 16 tokens.
+      pa[n >> 1][(n & 1) * 2 + 0] = *reinterpret_cast<const uint32_t *>(&r0);  // row g
+      pa[n >> 1][(n & 1) * 2 + 1] = *reinterpret_cast<const uint32_t *>(&r1);  // row g + 8
+    }
+#pragma unroll
+    for (int hrow = 0; hrow < 2; ++hrow) {
+      psum[hrow] += __shfl_xor_sync(0xffffffffu, psum[hrow], 1);
+      psum[hrow] += __shfl_xor_sync(0xffffffffu, psum[hrow], 2);
+      l_run[hrow] = l_run[hrow] * corr[hrow] + psum[hrow];
+    }
+    if (corr[0] != 1.0f || corr[1] != 1.0f) {
+#pragma unroll
+      for (int n = 0; n < NT_O; ++n) {
+        o_acc[n][0] *= corr[0], o_acc[n][1] *= corr[0];
+        o_acc[n][2] *= corr[1], o_acc[n][3] *= corr[1];
+      }
+    }
+    // O += P V.
+#pragma unroll
+    for (int kt = 0; kt < 2; ++kt)
+#pragma unroll
+      for (int np = 0; np < NT_O / 2; ++np) {
+        uint32_t b[4];
+        ldmatrix_x4_trans(b, v_s + (kt * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * PITCH + np * 16 + ((lane >> 4) & 1) * 8);
+        mma_f16(o_acc[2 * np], pa[kt][0], pa[kt][1], pa[kt][2], pa[kt][3], b[0], b[1]);
+        mma_f16(o_acc[2 * np + 1], pa[kt][0], pa[kt][1], pa[kt][2], pa[kt][3], b[2], b[3]);
+      }
+  }
+
+  // Partials of this split.
+  if (computes) {
+#pragma unroll
+    for (int hrow = 0; hrow < 2; ++hrow) {
+      const uint32_t f = warp * 16 + g + 8 * hrow;
+      if (f < F) {
+        float *po = p.partials + ((size_t(kvh) * p.splits + split) * kMaxFused + f) * D;
+#pragma unroll
+        for (int n = 0; n < NT_O; ++n)
+          *reinterpret_cast<float2 *>(po + 8 * n + 2 * t) = make_float2(o_acc[n][2 * hrow], o_acc[n][2 * hrow + 1]);
+        if (t == 0) {
+          float *ps = p.stats + ((size_t(kvh) * p.splits + split) * kMaxFused + f) * 2;
+          ps[0] = m_run[hrow];
+          ps[1] = l_run[hrow];
+        }
+      }
+    }
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(&p.counters[kvh], 1u) == p.splits - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // Merge in split order: thread -> dimension(s) of each fused row.
+  for (uint32_t f = warp; f < F; f += kAttnThreads / 32) {
+    float mall = -INFINITY;
+    for (uint32_t s = 0; s < p.splits; ++s)
+      mall = fmaxf(mall, __ldcg(p.stats + ((size_t(kvh) * p.splits + s) * kMaxFused + f) * 2));
+    float num[D / 32];
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) num[i] = 0.0f;
+    float den = 0.0f;
+    for (uint32_t s = 0; s < p.splits; ++s) {
+      const float *ps = p.stats + ((size_t(kvh) * p.splits + s) * kMaxFused + f) * 2;
+      const float ms = __ldcg(ps), ls = __ldcg(ps + 1);
+      if (ms == -INFINITY) continue;
+      const float w = exp2f(ms - mall);
+      const float *po = p.partials + ((size_t(kvh) * p.splits + s) * kMaxFused + f) * D;
+#pragma unroll
+      for (int i = 0; i < D / 32; ++i) num[i] += w * __ldcg(po + lane + 32 * i);
+      den += w * ls;
+    }
+    const uint32_t row = f / G, qh = kvh * G + f % G;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) {
+      const uint32_t d = lane + 32 * i;
+      float o = round_bf16(den > 0.0f ? num[i] / den : 0.0f);
+      if (p.gated) {
+        const float gate = bf16_bits_to_float(p.qkv[size_t(row) * p.qkv_stride + qh * 2 * D + D + d]);
+        o = o * sigmoid_f(gate);
+      }
+      p.out[size_t(row) * p.out_stride + qh * D + d] = float_to_bf16_bits(o);
+    }
+  }
+  if (tid == 0) p.counters[kvh] = 0;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" int sb_attn_verify(void *stream, const SbAttnArgs *a) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(a && a->queries && a->page_table && a->out, "sb_attn_verify: null pointer");
+  const SbKvLayer &c = a->cache;
+  SB_REQUIRE(c.k && c.v && c.k_scale && c.v_scale, "sb_attn_verify: null cache pointer");
+  SB_REQUIRE(c.head_dim == 128 || c.head_dim == 256, "sb_attn_verify: head_dim %u is not 128 or 256", c.head_dim);
+  SB_REQUIRE(c.kv_heads >= 1 && c.page_tokens >= 32 && (c.page_tokens & (c.page_tokens - 1)) == 0,
+             "sb_attn_verify: page_tokens %u is not a power of two >= 32", c.page_tokens);
+  SB_REQUIRE(a->rows >= 1 && a->rows <= 32 && a->q_heads % c.kv_heads == 0, "sb_attn_verify: rows %u outside 1..32 or q_heads not a multiple of kv_heads", a->rows);
+  const uint32_t group = a->q_heads / c.kv_heads, fused = a->rows * group;
+  SB_REQUIRE(fused <= kMaxFused, "sb_attn_verify: rows x group = %u exceeds %d fused rows", fused, kMaxFused);
+  SB_REQUIRE(!a->gated || a->qkv, "sb_attn_verify: a gated layer needs the packed rows");
+  SB_REQUIRE(a->out_stride >= a->q_heads * c.head_dim, "sb_attn_verify: out_stride below the row");
+  Context &cx = ctx();
+  const uint32_t D = c.head_dim, visible = a->committed + a->rows, chunks = (visible + kChunk - 1) / kChunk;
+  // Splits: about one CTA per SM over all KV heads, at least 4 chunks each.
+  uint32_t splits = std::max(1u, uint32_t(cx.sm_count) / c.kv_heads);
+  splits = std::min(splits, std::max(1u, chunks / 4));
+  const uint32_t cps = (chunks + splits - 1) / splits;
+  splits = (chunks + cps - 1) / cps;
+  const size_t need = size_t(c.kv_heads) * splits * kMaxFused * (D + 2) * sizeof(float);
+  SB_REQUIRE(need <= cx.attn_workspace_bytes && c.kv_heads <= 64, "sb_attn_verify: workspace too small (%zu bytes needed)", need);
+  AttnParams p{};
+  p.queries = static_cast<const uint16_t *>(a->queries);
+  p.qkv = static_cast<const uint16_t *>(a->qkv);
+  p.page_table = a->page_table;
+  p.tree = static_cast<const uint2 *>(a->tree);
+  p.out = static_cast<uint16_t *>(a->out);
+  p.cache = c;
+  p.partials = cx.attn_workspace;
+  p.stats = cx.attn_workspace + size_t(c.kv_heads) * splits * kMaxFused * D;
+  p.counters = cx.attn_counters;
+  p.rows = a->rows, p.q_heads = a->q_heads, p.group = group, p.gated = a->gated, p.qkv_stride = a->qkv_stride;
+  p.out_stride = a->out_stride, p.committed = a->committed, p.splits = splits, p.chunks_per_split = cps, p.fused = fused;
+  const size_t smem = size_t(kMaxFused + 2 * kChunk) * (D + 8) * 2 + 2 * kChunk * sizeof(float);
+  void (*kernel)(const AttnParams) = D == 256 ? attention_kernel<256> : attention_kernel<128>;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[D == 256]) {
+    SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
+    attr_set[D == 256] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(splits, c.kv_heads);
+  cfg.blockDim = dim3(kAttnThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = as_stream(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = cx.pdl ? 1 : 0;
+  SB_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+  return SB_OK;
+}

@@ -1,0 +1,285 @@
+// Gated-DeltaNet verify step of one lane and one layer with fp32 state and warp-shuffle reductions.
+//
+// Takes the place of the reference's verify_gdn_fused* kernels (runtime/metal/kernels/decode/gdn.metal:
+// prologue :139-264, fold :270-298, chain scan :312-415, gate :489-526; primitives
+// runtime/metal/kernels/common/gdn_primitives.h:63-106) and of ops::GDN::addDecode / addFold
+// (runtime/ops/GDN.cpp:225-328).
+//
+//   grid     (4, value_heads): the reference runs one threadgroup per value head (48 on the 27B shape,
+//            too few for 148 SMs); a head's 128 state rows (value dimensions) are independent given
+//            k, v and the gates, so each CTA takes 32 of them
+//   CTA      256 threads; warp w owns state rows 4w..4w+3 of the CTA's 32, each lane four fp32 key
+//            columns of each row (16 registers of state); dot products are butterfly shuffles
+//   steps    (1) conv history = last three input rows before the block (carried rows ++ pending rows);
+//            (2) conv + SiLU, q/k RMS norm and scales (2^-7, 128^-1/2), beta and decay per row;
+//            (3) fold the pending rows into the state -> committed state stored; (4) chain scan from the
+//            committed state, outputs only; (5) the head's last CTA normalises (RMS over the 128 value
+//            dimensions), gates by silu(z) and writes the hidden rows; (6) this step's tape
+//   rollback the state after the block is never stored: the caller passes how many tape rows were accepted
+//            (pending_rows, or a device word written by sb_accept) to the next step, which folds them
+#include <algorithm>
+
+#include "sb_internal.h"
+#include "sb_ptx.cuh"
+
+namespace sb {
+
+constexpr int kGdnThreads = 256;
+constexpr int kGdnRows = 16;      // rows of a verify block
+constexpr int kGdnSplit = 4;      // CTAs per value head
+constexpr int kGdnVd = 128 / kGdnSplit;  // value dimensions per CTA
+constexpr int kD = 128, kTaps = 4;
+
+struct GdnParams {
+  SbGdnArgs a;
+  uint16_t *scratch;    // bf16 [value_heads][16][128] recurrent outputs before the gate
+  uint32_t *counters;   // [value_heads]
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__global__ void __launch_bounds__(kGdnThreads) gdn_kernel(const GdnParams p) {
+  const SbGdnArgs &a = p.a;
+  __shared__ float q_s[kGdnRows][kD], k_s[kGdnRows][kD], pk_s[kGdnRows][kD];
+  __shared__ float v_s[kGdnRows][kGdnVd], pv_s[kGdnRows][kGdnVd], o_s[kGdnRows][kGdnVd];
+  __shared__ float beta_s[kGdnRows], decay_s[kGdnRows], pbeta_s[kGdnRows], pdecay_s[kGdnRows];
+  __shared__ uint32_t s_last;
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t vs = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t KH = a.key_heads, VH = a.value_heads, KW = KH * kD, VW = VH * kD, C = 2 * KW + VW;
+  const uint32_t per_key = VH / KH, kh = h / per_key, vd0 = vs * kGdnVd;
+  const uint32_t rows = a.rows;
+  const uint32_t pending = a.pending_rows_dev ? min(*a.pending_rows_dev, uint32_t(kGdnRows)) : a.pending_rows;
+  const uint16_t *qkvz = static_cast<const uint16_t *>(a.qkvz);
+  const uint16_t *conv_w = static_cast<const uint16_t *>(a.conv_w);
+  const uint16_t *cs_in = static_cast<const uint16_t *>(a.conv_state_in);
+  const uint16_t *pin = static_cast<const uint16_t *>(a.pending.inputs);
+  const bool qk_writer = h % per_key == 0 && vs == 0;
+
+  // Conv input of block row `row` (negative: history) at channel ch. History row i (0..2, oldest first)
+  // is row pending - 3 + i of (carried rows ++ pending rows).
+  auto hist = [&](int i, uint32_t ch) -> uint16_t {
+    const int src = int(pending) - 3 + i;
+    return src >= 0 ? pin[size_t(src) * C + ch] : cs_in[size_t(3 + src) * C + ch];
+  };
+  auto input = [&](int row, uint32_t ch) -> float {
+    return bf16_bits_to_float(row >= 0 ? qkvz[size_t(row) * a.qkvz_stride + ch] : hist(3 + row, ch));
+  };
+  auto conv = [&](uint32_t row, uint32_t ch) -> float {
+    float value = 0.0f;
+#pragma unroll
+    for (int tap = 0; tap < kTaps; ++tap)
+      value = __fadd_rn(value, __fmul_rn(input(int(row) + tap - 3, ch), bf16_bits_to_float(conv_w[size_t(ch) * kTaps + tap])));
+    value = round_bf16(value);
+    return round_bf16(silu_f(value));
+  };
+
+  // (2) conv outputs: q, k of the key head (16 x 128 each) and this CTA's 32 value dimensions.
+  for (uint32_t i = tid; i < rows * kD; i += kGdnThreads) {
+    const uint32_t r = i / kD, d = i % kD;
+    q_s[r][d] = conv(r, kh * kD + d);
+    k_s[r][d] = conv(r, KW + kh * kD + d);
+  }
+  for (uint32_t i = tid; i < rows * kGdnVd; i += kGdnThreads) {
+    const uint32_t r = i / kGdnVd, d = i % kGdnVd;
+    v_s[r][d] = conv(r, 2 * KW + h * kD + vd0 + d);
+  }
+  // pending rows' keys, values and gates from their tape
+  for (uint32_t i = tid; i < pending * kD; i += kGdnThreads)
+    pk_s[i / kD][i % kD] = bf16_bits_to_float(static_cast<const uint16_t *>(a.pending.k)[size_t(i / kD) * KW + kh * kD + i % kD]);
+  for (uint32_t i = tid; i < pending * kGdnVd; i += kGdnThreads)
+    pv_s[i / kGdnVd][i % kGdnVd] =
+        bf16_bits_to_float(static_cast<const uint16_t *>(a.pending.v)[size_t(i / kGdnVd) * VW + h * kD + vd0 + i % kGdnVd]);
+  if (tid < pending) {
+    pbeta_s[tid] = bf16_bits_to_float(static_cast<const uint16_t *>(a.pending.beta)[size_t(tid) * VH + h]);
+    pdecay_s[tid] = a.pending.decay[size_t(tid) * VH + h];
+  }
+  if (tid < rows) {
+    const float bb = bf16_bits_to_float(static_cast<const uint16_t *>(a.b)[size_t(tid) * a.ab_stride + h]);
+    const float be = round_bf16(sigmoid_f(bb));
+    const float x = round_bf16(__fadd_rn(bf16_bits_to_float(static_cast<const uint16_t *>(a.a)[size_t(tid) * a.ab_stride + h]),
+                                         bf16_bits_to_float(static_cast<const uint16_t *>(a.dt_bias)[h])));
+    const float sp = round_bf16(fmaxf(x, 0.0f) + log2f(1.0f + exp2f(-1.44269504089f * fabsf(x))) * 0.69314718056f);
+    const float de = expf(a.a_scale[h] * sp);
+    beta_s[tid] = be;
+    decay_s[tid] = de;
+    if (vs == 0) {
+      static_cast<uint16_t *>(a.step.beta)[size_t(tid) * VH + h] = float_to_bf16_bits(be);
+      a.step.decay[size_t(tid) * VH + h] = de;
+    }
+  }
+  __syncthreads();
+  // q/k RMS norm over the head's 128 dimensions: a warp per (row, q or k); 4 dims per lane in order,
+  // then the butterfly.
+  for (uint32_t task = warp; task < 2 * rows; task += kGdnThreads / 32) {
+    const uint32_t r = task >> 1;
+    float *vec = (task & 1) ? k_s[r] : q_s[r];
+    float ss = 0.0f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const float x = vec[32 * g + lane];
+      ss += warp_sum(x * x);
+    }
+    const float inv = rsqrtf(ss / float(kD) + 1e-6f);
+    const float post = (task & 1) ? 0.08838834765f : 0.0078125f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) vec[32 * g + lane] = round_bf16(round_bf16(vec[32 * g + lane] * inv) * post);
+  }
+  __syncthreads();
+  // (6) tape and carried conv rows.
+  {
+    uint16_t *tin = static_cast<uint16_t *>(a.step.inputs), *cs_out = static_cast<uint16_t *>(a.conv_state_out);
+    for (uint32_t i = tid; i < rows * kGdnVd; i += kGdnThreads) {
+      const uint32_t r = i / kGdnVd, d = i % kGdnVd, ch = 2 * KW + h * kD + vd0 + d;
+      tin[size_t(r) * C + ch] = qkvz[size_t(r) * a.qkvz_stride + ch];
+      static_cast<uint16_t *>(a.step.v)[size_t(r) * VW + h * kD + vd0 + d] = float_to_bf16_bits(v_s[r][d]);
+    }
+    for (uint32_t i = tid; i < 3 * kGdnVd; i += kGdnThreads) {
+      const uint32_t r = i / kGdnVd, ch = 2 * KW + h * kD + vd0 + i % kGdnVd;
+      cs_out[size_t(r) * C + ch] = hist(int(r), ch);
+    }
+    if (qk_writer) {
+      for (uint32_t i = tid; i < rows * 2 * kD; i += kGdnThreads) {
+        const uint32_t r = i / (2 * kD), d = i % (2 * kD), ch = (d < kD ? 0 : KW) + kh * kD + d % kD;
+        tin[size_t(r) * C + ch] = qkvz[size_t(r) * a.qkvz_stride + ch];
+      }
+      for (uint32_t i = tid; i < rows * kD; i += kGdnThreads)
+        static_cast<uint16_t *>(a.step.k)[size_t(i / kD) * KW + kh * kD + i % kD] = float_to_bf16_bits(k_s[i / kD][i % kD]);
+      for (uint32_t i = tid; i < 3 * 2 * kD; i += kGdnThreads) {
+        const uint32_t r = i / (2 * kD), d = i % (2 * kD), ch = (d < kD ? 0 : KW) + kh * kD + d % kD;
+        cs_out[size_t(r) * C + ch] = hist(int(r), ch);
+      }
+    }
+  }
+
+  // (3) + (4): warp w owns value dimensions vd0 + 4w .. + 3; lane holds key columns 4 lane .. + 3.
+  float S[4][4];
+  const size_t sbase = (size_t(h) * kD + vd0 + 4 * warp) * kD + 4 * lane;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const float4 s4 = *reinterpret_cast<const float4 *>(a.state_in + sbase + size_t(r) * kD);
+    S[r][0] = s4.x, S[r][1] = s4.y, S[r][2] = s4.z, S[r][3] = s4.w;
+  }
+  auto advance = [&](const float *key, const float *val, float d, float b, const float *query, float *out) {
+    const float4 k4 = *reinterpret_cast<const float4 *>(key + 4 * lane);
+    const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
+    float mem[4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      float m = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        S[r][i] *= d;
+        m = fmaf(S[r][i], kk[i], m);
+      }
+      mem[r] = m;
+    }
+#pragma unroll
+    for (int o = 16; o; o >>= 1)
+#pragma unroll
+      for (int r = 0; r < 4; ++r) mem[r] += __shfl_xor_sync(0xffffffffu, mem[r], o);
+    float res[4];
+    float qq[4] = {0.f, 0.f, 0.f, 0.f};
+    if (query) {
+      const float4 q4 = *reinterpret_cast<const float4 *>(query + 4 * lane);
+      qq[0] = q4.x, qq[1] = q4.y, qq[2] = q4.z, qq[3] = q4.w;
+    }
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const float delta = (val[4 * warp + r] - mem[r]) * b;
+      float acc = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        S[r][i] = fmaf(kk[i], delta, S[r][i]);
+        acc = fmaf(S[r][i], qq[i], acc);
+      }
+      res[r] = acc;
+    }
+    if (query) {
+#pragma unroll
+      for (int o = 16; o; o >>= 1)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) res[r] += __shfl_xor_sync(0xffffffffu, res[r], o);
+      if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < 4; ++r) out[4 * warp + r] = res[r];
+      }
+    }
+  };
+  for (uint32_t t = 0; t < pending; ++t) advance(pk_s[t], pv_s[t], pdecay_s[t], pbeta_s[t], nullptr, nullptr);
+#pragma unroll
+  for (int r = 0; r < 4; ++r)
+    *reinterpret_cast<float4 *>(a.state_out + sbase + size_t(r) * kD) = make_float4(S[r][0], S[r][1], S[r][2], S[r][3]);
+  for (uint32_t t = 0; t < rows; ++t) advance(k_s[t], v_s[t], decay_s[t], beta_s[t], q_s[t], o_s[t]);
+  __syncthreads();
+  // recurrent outputs (bf16) of this CTA's value dimensions -> scratch
+  for (uint32_t i = tid; i < rows * kGdnVd; i += kGdnThreads)
+    p.scratch[(size_t(h) * kGdnRows + i / kGdnVd) * kD + vd0 + i % kGdnVd] = float_to_bf16_bits(o_s[i / kGdnVd][i % kGdnVd]);
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(&p.counters[h], 1u) == kGdnSplit - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // (5) gated RMSNorm: a warp per row, dimensions 32 g + lane, the four partial sums added in order.
+  const uint32_t out_head = a.tiled ? (h % per_key) * KH + h / per_key : h;
+  for (uint32_t r = warp; r < rows; r += kGdnThreads / 32) {
+    float val[4], total = 0.0f;
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      val[g] = bf16_bits_to_float(__ldcg(p.scratch + (size_t(h) * kGdnRows + r) * kD + 32 * g + lane));
+      total += warp_sum(val[g] * val[g]);
+    }
+    const float inv = rsqrtf(total / float(kD) + 1e-6f);
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const uint32_t d = 32 * g + lane;
+      const float normalized = round_bf16((val[g] * inv) * a.norm_w[d]);
+      const float z = bf16_bits_to_float(qkvz[size_t(r) * a.qkvz_stride + C + h * kD + d]);
+      static_cast<uint16_t *>(a.hidden)[size_t(r) * a.hidden_stride + out_head * kD + d] =
+          float_to_bf16_bits((normalized * z) / (1.0f + exp2f(-1.44269504089f * z)));
+    }
+  }
+  if (tid == 0) p.counters[h] = 0;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" int sb_gdn_verify(void *stream, const SbGdnArgs *a) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(a, "sb_gdn_verify: null arguments");
+  SB_REQUIRE(a->qkvz && a->b && a->a && a->conv_w && a->a_scale && a->dt_bias && a->norm_w && a->conv_state_in &&
+                 a->conv_state_out && a->state_in && a->state_out && a->hidden,
+             "sb_gdn_verify: null pointer");
+  SB_REQUIRE(a->rows <= kGdnRows && a->pending_rows <= kGdnRows, "sb_gdn_verify: rows %u or pending rows %u above %d", a->rows,
+             a->pending_rows, kGdnRows);
+  SB_REQUIRE(a->key_heads >= 1 && a->value_heads % a->key_heads == 0 && a->value_heads <= 256, "sb_gdn_verify: %u value heads over %u key heads",
+             a->value_heads, a->key_heads);
+  const uint32_t C = (2 * a->key_heads + a->value_heads) * kD;
+  SB_REQUIRE(a->qkvz_stride >= C + a->value_heads * kD && a->ab_stride >= a->value_heads && a->hidden_stride >= a->value_heads * kD,
+             "sb_gdn_verify: a stride is below its row");
+  SB_REQUIRE(a->rows == 0 || (a->step.inputs && a->step.k && a->step.v && a->step.beta && a->step.decay), "sb_gdn_verify: null tape of this step");
+  SB_REQUIRE((a->pending_rows == 0 && !a->pending_rows_dev) || (a->pending.inputs && a->pending.k && a->pending.v && a->pending.beta && a->pending.decay),
+             "sb_gdn_verify: null pending tape");
+  SB_REQUIRE(a->state_in != a->state_out, "sb_gdn_verify: the committed state goes to a second cell");
+  Context &c = ctx();
+  GdnParams p{*a, c.gdn_scratch, c.gdn_counters};
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(kGdnSplit, a->value_heads);
+  cfg.blockDim = dim3(kGdnThreads);
+  cfg.stream = as_stream(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = c.pdl ? 1 : 0;
+  SB_CUDA(cudaLaunchKernelEx(&cfg, gdn_kernel, p));
+  return SB_OK;
+}

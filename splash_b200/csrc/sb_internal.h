@@ -19,6 +19,12 @@ struct Context {
   uint8_t *prepared = nullptr;           // sb_linear's own prepared-input scratch
   size_t prepared_bytes = 0;
   uint32_t linear_counter_count = 0;
+  float *attn_workspace = nullptr;       // split partials and (max, sum) of sb_attn_verify
+  size_t attn_workspace_bytes = 0;
+  uint32_t *attn_counters = nullptr;     // one arrival counter per KV head, zero between launches
+  uint16_t *gdn_scratch = nullptr;       // recurrent outputs before the gate [value_heads][16][128]
+  uint32_t *gdn_counters = nullptr;      // one arrival counter per value head
+  bool pdl = true;                       // launch glue kernels with programmatic stream serialization
 };
 Context &ctx();
 

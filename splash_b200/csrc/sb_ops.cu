@@ -1,0 +1,507 @@
+// Glue operators of the verify step: RMSNorm, embedding gather, RoPE tables, the fp32 projection of
+// plain fp32 rows, q/k norm + RoPE + INT8 KV store, path commit, selection and acceptance.
+// Each replaces the reference operator named at its entry point in include/splash_b200.h.
+#include <algorithm>
+
+#include "sb_dequant.cuh"
+
+namespace sb {
+
+// Sum over a block of `warps` warps in a fixed order: a butterfly within each warp, then the warps'
+// values in index order. Every thread receives the total.
+template <int WARPS>
+__device__ __forceinline__ float block_sum(float v, float *scratch) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float r = 0.0f;
+#pragma unroll
+  for (int w = 0; w < WARPS; ++w) r += scratch[w];
+  return r;
+}
+
+// ---- RMSNorm: one block of 256 threads per row ----
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const uint16_t *x, uint32_t width, uint32_t x_stride, const float *w,
+                                                      uint16_t *out, uint32_t out_stride) {
+  __shared__ float scratch[8];
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint16_t *row = x + size_t(blockIdx.x) * x_stride;
+  float ss = 0.0f;
+  for (uint32_t c = threadIdx.x; c < width; c += 256) {
+    const float v = bf16_bits_to_float(row[c]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum<8>(ss, scratch);
+  const float inv = rsqrtf(ss / float(width) + 1e-6f);
+  for (uint32_t c = threadIdx.x; c < width; c += 256)
+    out[size_t(blockIdx.x) * out_stride + c] = float_to_bf16_bits((bf16_bits_to_float(row[c]) * inv) * w[c]);
+}
+
+// ---- embedding gather ----
+__global__ void __launch_bounds__(256) embed_kernel(uint32_t format, const uint8_t *table, uint64_t row_bytes, uint32_t vocab,
+                                                    uint32_t width, const uint32_t *tokens, uint16_t *out,
+                                                    uint32_t out_stride) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t r = blockIdx.y;
+  uint32_t t = tokens[r];
+  if (t >= vocab) t = 0;
+  const uint8_t *row = table + size_t(t) * row_bytes;
+  const uint32_t c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= width) return;
+  float v;
+  if (format == SB_FMT_BF16) v = bf16_bits_to_float(reinterpret_cast<const uint16_t *>(row)[c]);
+  else if (format == SB_FMT_F16) v = __half2float(reinterpret_cast<const __half *>(row)[c]);
+  else if (format == SB_FMT_F32) v = reinterpret_cast<const float *>(row)[c];
+  else v = weight_value(format, row, c);
+  out[size_t(r) * out_stride + c] = float_to_bf16_bits(v);
+}
+
+// ---- RoPE tables ----
+__global__ void rope_kernel(const uint32_t *positions, uint32_t rows, const float *inv_freq, uint32_t pairs, float scale,
+                            float *cosine, float *sine) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * pairs) return;
+  const float angle = float(positions[i / pairs]) * inv_freq[i % pairs];
+  float s, c;
+  sincosf(angle, &s, &c);
+  cosine[i] = c * scale;
+  sine[i] = s * scale;
+}
+
+// ---- fp32 projection of plain fp32 rows: one block per output column, all (<= 16) rows ----
+constexpr int kF32Rows = 16;
+__global__ void __launch_bounds__(256) linear_f32_kernel(const float *w, const uint16_t *x, uint32_t rows, uint32_t n,
+                                                         uint32_t k, uint32_t x_stride, void *out, uint32_t out_stride,
+                                                         uint32_t out_f32, const float *norm_w) {
+  __shared__ float scratch[8];
+  __shared__ float inv_s[kF32Rows];
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t col = blockIdx.x;
+  const float *wr = w + size_t(col) * k;
+  if (norm_w) {
+    for (uint32_t r = 0; r < rows; ++r) {
+      float ss = 0.0f;
+      for (uint32_t c = threadIdx.x; c < k; c += 256) {
+        const float v = bf16_bits_to_float(x[size_t(r) * x_stride + c]);
+        ss = fmaf(v, v, ss);
+      }
+      ss = block_sum<8>(ss, scratch);
+      if (threadIdx.x == 0) inv_s[r] = rsqrtf(ss / float(k) + 1e-6f);
+    }
+    __syncthreads();
+  }
+  float acc[kF32Rows];
+#pragma unroll
+  for (int r = 0; r < kF32Rows; ++r) acc[r] = 0.0f;
+  for (uint32_t c = threadIdx.x; c < k; c += 256) {
+    const float wv = wr[c];
+    const float nw = norm_w ? norm_w[c] : 1.0f;
+#pragma unroll
+    for (int r = 0; r < kF32Rows; ++r) {
+      if (r < int(rows)) {
+        float xv = bf16_bits_to_float(x[size_t(r) * x_stride + c]);
+        if (norm_w) xv = round_bf16((xv * inv_s[r]) * nw);
+        acc[r] = fmaf(xv, wv, acc[r]);
+      }
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kF32Rows; ++r) {
+    if (r >= int(rows)) break;
+    const float total = block_sum<8>(acc[r], scratch);
+    if (threadIdx.x == 0) {
+      if (out_f32) static_cast<float *>(out)[size_t(r) * out_stride + col] = total;
+      else static_cast<uint16_t *>(out)[size_t(r) * out_stride + col] = float_to_bf16_bits(total);
+    }
+  }
+}
+
+// ---- q/k norm + RoPE + INT8 KV store: grid (q_heads + kv_heads, rows), head_dim threads ----
+struct StoreParams {
+  const uint16_t *qkv;
+  const float *q_norm, *k_norm, *cos_tab, *sin_tab;
+  const uint32_t *page_table;
+  uint16_t *queries;
+  SbKvLayer cache;
+  uint32_t rows, q_heads, gated, pairs, qkv_stride, committed;
+};
+
+__device__ __forceinline__ int8_t kv_code(float v, float m) {
+  if (m == 0.0f) return 0;
+  const float q = rintf(__fdiv_rn(__fmul_rn(v, 127.0f), m));
+  return int8_t(fminf(fmaxf(q, -127.0f), 127.0f));
+}
+
+template <int D>
+__global__ void __launch_bounds__(D) attn_store_kernel(const StoreParams p) {
+  constexpr int W = D / 32;
+  __shared__ float part[W], part2[W];
+  __shared__ float normed[D];
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t head = blockIdx.x, row = blockIdx.y, d = threadIdx.x, lane = d & 31, warp = d >> 5;
+  const bool query = head < p.q_heads;
+  const uint32_t kvh = query ? 0 : head - p.q_heads, qs = p.gated ? 2 * D : D;
+  const uint16_t *prow = p.qkv + size_t(row) * p.qkv_stride;
+  const uint16_t *src = query ? prow + head * qs : prow + p.q_heads * qs + kvh * D;
+  const float x = bf16_bits_to_float(src[d]);
+  // Sum of squares: 32 dimensions per warp added in dimension order, then the warps in order.
+  float sq = x * x;
+  // in-order sum within the warp: lane 0 accumulates lanes 0..31 (a sequential chain, as the oracle's)
+  float acc = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) acc = __fadd_rn(acc, __shfl_sync(0xffffffffu, sq, i));
+  if (lane == 0) part[warp] = acc;
+  __syncthreads();
+  float ss = 0.0f;
+#pragma unroll
+  for (int w = 0; w < W; ++w) ss = __fadd_rn(ss, part[w]);
+  const float inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, float(D)), 1e-6f)));
+  const float wn = (query ? p.q_norm : p.k_norm)[d];
+  normed[d] = round_bf16(__fmul_rn(__fmul_rn(x, inv), wn));
+  __syncthreads();
+  float r = normed[d];
+  if (d < 2 * p.pairs) {
+    const uint32_t pr = d % p.pairs;
+    const float a = normed[pr], b = normed[pr + p.pairs];
+    const float c = p.cos_tab[size_t(row) * p.pairs + pr], s = p.sin_tab[size_t(row) * p.pairs + pr];
+    r = d < p.pairs ? round_bf16(__fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s)))
+                    : round_bf16(__fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s)));
+  }
+  if (query) {
+    p.queries[(size_t(row) * p.q_heads + head) * D + d] = float_to_bf16_bits(r);
+    return;
+  }
+  const float v = bf16_bits_to_float(prow[p.q_heads * qs + p.cache.kv_heads * D + kvh * D + d]);
+  float km = fabsf(r), vm = fabsf(v);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    km = fmaxf(km, __shfl_xor_sync(0xffffffffu, km, o));
+    vm = fmaxf(vm, __shfl_xor_sync(0xffffffffu, vm, o));
+  }
+  __syncthreads();
+  if (lane == 0) part[warp] = km, part2[warp] = vm;
+  __syncthreads();
+  km = 0.0f, vm = 0.0f;
+#pragma unroll
+  for (int w = 0; w < W; ++w) km = fmaxf(km, part[w]), vm = fmaxf(vm, part2[w]);
+  const uint32_t tok = p.committed + row, page = p.page_table[tok / p.cache.page_tokens], pt = tok % p.cache.page_tokens;
+  const size_t slot = (size_t(page) * p.cache.kv_heads + kvh) * p.cache.page_tokens + pt;
+  static_cast<int8_t *>(p.cache.k)[slot * D + d] = kv_code(r, km);
+  static_cast<int8_t *>(p.cache.v)[slot * D + d] = kv_code(v, vm);
+  if (d == 0) {
+    const float ks = km == 0.0f ? 0.0f : __fdiv_rn(km, 127.0f), vs = vm == 0.0f ? 0.0f : __fdiv_rn(vm, 127.0f);
+    if (p.cache.scale_f16) {
+      static_cast<__half *>(p.cache.k_scale)[slot] = __float2half_rn(ks);
+      static_cast<__half *>(p.cache.v_scale)[slot] = __float2half_rn(vs);
+    } else {
+      static_cast<float *>(p.cache.k_scale)[slot] = ks;
+      static_cast<float *>(p.cache.v_scale)[slot] = vs;
+    }
+  }
+}
+
+// ---- path commit: grid (kv_heads), head_dim threads; rows move in depth order ----
+__global__ void kv_path_commit_kernel(SbKvLayer c, const uint32_t *page_table, uint32_t committed, const uint32_t *path_mask) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t mask = *path_mask, h = blockIdx.x, d = threadIdx.x, D = c.head_dim;
+  uint32_t depth = 0;
+  for (uint32_t row = 0; row < 32; ++row) {
+    if (!((mask >> row) & 1u)) continue;
+    if (row != depth) {
+      const uint32_t s = committed + row, t = committed + depth;
+      const size_t ss = (size_t(page_table[s / c.page_tokens]) * c.kv_heads + h) * c.page_tokens + s % c.page_tokens;
+      const size_t ts = (size_t(page_table[t / c.page_tokens]) * c.kv_heads + h) * c.page_tokens + t % c.page_tokens;
+      static_cast<int8_t *>(c.k)[ts * D + d] = static_cast<int8_t *>(c.k)[ss * D + d];
+      static_cast<int8_t *>(c.v)[ts * D + d] = static_cast<int8_t *>(c.v)[ss * D + d];
+      if (d == 0) {
+        if (c.scale_f16) {
+          static_cast<uint16_t *>(c.k_scale)[ts] = static_cast<uint16_t *>(c.k_scale)[ss];
+          static_cast<uint16_t *>(c.v_scale)[ts] = static_cast<uint16_t *>(c.v_scale)[ss];
+        } else {
+          static_cast<float *>(c.k_scale)[ts] = static_cast<float *>(c.k_scale)[ss];
+          static_cast<float *>(c.v_scale)[ts] = static_cast<float *>(c.v_scale)[ss];
+        }
+      }
+    }
+    ++depth;
+    __syncthreads();  // a later row may read the slot this one wrote
+  }
+}
+
+// ---- selection: one block of 1024 threads per row ----
+constexpr uint32_t kSentinel = 0xFFFFFFFFu;
+constexpr uint32_t kShard = 256;
+constexpr int kSampleThreads = 1024;
+
+__device__ __forceinline__ bool selectable(float x) { return !(isnan(x) || x == -INFINITY); }
+
+__global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SbSampleArgs a) {
+  __shared__ float best_v[32];
+  __shared__ uint32_t best_i[32];
+  __shared__ float s_max;
+  __shared__ uint32_t s_top;
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const float *l = a.logits + size_t(r) * a.logit_stride;
+  // Greedy: value descending, id ascending.
+  float bv = -INFINITY;
+  uint32_t bi = kSentinel;
+  for (uint32_t v = tid; v < a.vocab; v += kSampleThreads) {
+    const float x = l[v];
+    if (selectable(x) && (bi == kSentinel || x > bv)) bv = x, bi = v;
+  }
+  auto better = [](float v1, uint32_t i1, float v2, uint32_t i2) {
+    if (i2 == kSentinel) return true;
+    if (i1 == kSentinel) return false;
+    return v1 > v2 || (v1 == v2 && i1 < i2);
+  };
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (!better(bv, bi, ov, oi)) bv = ov, bi = oi;
+  }
+  if (lane == 0) best_v[warp] = bv, best_i[warp] = bi;
+  __syncthreads();
+  if (tid == 0) {
+    float v = best_v[0];
+    uint32_t i = best_i[0];
+    for (int w = 1; w < kSampleThreads / 32; ++w)
+      if (!better(v, i, best_v[w], best_i[w])) v = best_v[w], i = best_i[w];
+    s_max = v, s_top = i;
+  }
+  __syncthreads();
+  const uint32_t top = s_top;
+  if (a.temperature == 0.0f || !a.uniforms || top == kSentinel) {
+    if (tid == 0) a.selected[r] = top;
+    return;
+  }
+  // Temperature weights; each shard of 256 ids summed by one thread in id order.
+  const float mx = s_max, inv_t = __fdiv_rn(1.0f, a.temperature);
+  const uint32_t shards = (a.vocab + kShard - 1) / kShard;
+  float *shard = a.workspace + size_t(r) * (2 * shards + 8), *shard2 = shard + shards;
+  const bool has_child = r + 1 < a.rows;
+  const uint32_t child = has_child ? a.input_tokens[r + 1] : kSentinel;
+  auto weight = [&](uint32_t v) {
+    const float x = l[v];
+    return selectable(x) ? expf(__fmul_rn(__fsub_rn(x, mx), inv_t)) : 0.0f;
+  };
+  for (uint32_t s = tid; s < shards; s += kSampleThreads) {
+    float sum = 0.0f, sum2 = 0.0f;
+    const uint32_t end = min(a.vocab, (s + 1) * kShard);
+    for (uint32_t v = s * kShard; v < end; ++v) {
+      const float w = weight(v);
+      sum = __fadd_rn(sum, w);
+      sum2 = __fadd_rn(sum2, v == child ? 0.0f : w);
+    }
+    shard[s] = sum;
+    shard2[s] = sum2;
+  }
+  __syncthreads();
+  if (tid != 0) return;
+  float z = 0.0f;
+  for (uint32_t s = 0; s < shards; ++s) z = __fadd_rn(z, shard[s]);
+  bool drop = false;
+  if (has_child && child < a.vocab) {
+    const float u = a.uniforms[16 + 4 * r];
+    if (__fmul_rn(u, z) < weight(child)) {
+      a.selected[r] = child;
+      return;
+    }
+    drop = true;
+  }
+  const float *sh = drop ? shard2 : shard;
+  float zr = z;
+  if (drop) {
+    zr = 0.0f;
+    for (uint32_t s = 0; s < shards; ++s) zr = __fadd_rn(zr, sh[s]);
+  }
+  const float target = __fmul_rn(a.uniforms[r], zr);
+  float run = 0.0f;
+  uint32_t pick = kSentinel;
+  for (uint32_t s = 0; s < shards && pick == kSentinel; ++s) {
+    if (__fadd_rn(run, sh[s]) > target) {
+      float loc = 0.0f;
+      const uint32_t end = min(a.vocab, (s + 1) * kShard);
+      for (uint32_t v = s * kShard; v < end; ++v) {
+        loc = __fadd_rn(loc, (drop && v == child) ? 0.0f : weight(v));
+        if (__fadd_rn(run, loc) > target) {
+          pick = v;
+          break;
+        }
+      }
+    }
+    run = __fadd_rn(run, sh[s]);
+  }
+  if (pick == kSentinel)
+    for (uint32_t v = a.vocab; v-- > 0;)
+      if (weight(v) > 0.0f && !(drop && v == child)) {
+        pick = v;
+        break;
+      }
+  a.selected[r] = pick;
+}
+
+// ---- acceptance: one thread ----
+__global__ void accept_kernel(const SbAcceptArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const uint2 *tree = static_cast<const uint2 *>(a.tree);  // {ancestors, parent | depth << 16}
+  uint32_t path[32];
+  path[0] = 0;
+  uint32_t accepted = 0;
+  for (uint32_t row = 0;;) {
+    const uint32_t token = a.tokens[row];
+    uint32_t next = 0;
+    for (uint32_t child = row + 1; child < a.rows && !next; ++child)
+      next = ((tree[child].y & 0xffffu) == row && a.input_tokens[child] == token) ? child : 0;
+    if (!next) break;
+    path[++accepted] = next;
+    row = next;
+  }
+  uint32_t kept = min(accepted + 1, a.remaining);
+  for (uint32_t i = 0; i < kept; ++i) {
+    const uint32_t token = a.tokens[path[i]];
+    a.tokens[i] = token;
+    for (uint32_t s = 0; s < a.n_stop; ++s)
+      if (a.stop_tokens[s] == token) kept = i + 1;
+  }
+  a.results[0] = kept;
+  a.results[1] = min(accepted, kept);
+  a.results[2] = tree[path[kept - 1]].x;
+  a.results[3] = 0;
+}
+
+template <class... Args>
+static int launch(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = ctx().pdl ? 1 : 0;
+  SB_CUDA(cudaLaunchKernelEx(&cfg, kernel, args...));
+  return SB_OK;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" {
+
+int sb_rmsnorm(void *stream, const void *x, uint32_t rows, uint32_t width, uint32_t x_stride, const void *weight, void *out,
+               uint32_t out_stride) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(x && weight && out && rows && width, "sb_rmsnorm: null pointer or empty shape");
+  SB_REQUIRE(x_stride >= width && out_stride >= width, "sb_rmsnorm: stride below width");
+  return launch(rmsnorm_kernel, dim3(rows), dim3(256), as_stream(stream), static_cast<const uint16_t *>(x), width, x_stride,
+                static_cast<const float *>(weight), static_cast<uint16_t *>(out), out_stride);
+}
+
+int sb_embed(void *stream, uint32_t format, const void *table, uint32_t vocab, uint32_t width, const uint32_t *tokens_dev,
+             uint32_t rows, void *out, uint32_t out_stride) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(table && tokens_dev && out && rows && vocab, "sb_embed: null pointer or empty shape");
+  const uint64_t rb = sb_row_bytes(format, width);
+  SB_REQUIRE(rb != 0 && format != SB_FMT_NVFP4, "sb_embed: width %u is not whole blocks of format %u", width, format);
+  SB_REQUIRE(out_stride >= width, "sb_embed: out_stride below width");
+  return launch(embed_kernel, dim3((width + 255) / 256, rows), dim3(256), as_stream(stream), format,
+                static_cast<const uint8_t *>(table), rb, vocab, width, tokens_dev, static_cast<uint16_t *>(out), out_stride);
+}
+
+int sb_rope_tables(void *stream, const uint32_t *positions_dev, uint32_t rows, const float *inv_freq_dev, uint32_t pairs,
+                   float scale, float *cos_dev, float *sin_dev) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(positions_dev && inv_freq_dev && cos_dev && sin_dev && rows && pairs, "sb_rope_tables: null pointer or empty shape");
+  return launch(rope_kernel, dim3((rows * pairs + 127) / 128), dim3(128), as_stream(stream), positions_dev, rows, inv_freq_dev,
+                pairs, scale, cos_dev, sin_dev);
+}
+
+int sb_linear_f32(void *stream, const float *w_dev, const void *x, uint32_t rows, uint32_t n, uint32_t k, uint32_t x_stride,
+                  void *out, uint32_t out_stride, uint32_t out_f32, const void *norm_weight) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(w_dev && x && out, "sb_linear_f32: null pointer");
+  SB_REQUIRE(rows >= 1 && rows <= kF32Rows && n && k, "sb_linear_f32: rows = %u outside 1..%d, or empty shape", rows, kF32Rows);
+  SB_REQUIRE(x_stride >= k && out_stride >= n, "sb_linear_f32: stride below extent");
+  return launch(linear_f32_kernel, dim3(n), dim3(256), as_stream(stream), w_dev, static_cast<const uint16_t *>(x), rows, n, k,
+                x_stride, out, out_stride, out_f32, static_cast<const float *>(norm_weight));
+}
+
+static int check_cache(const SbKvLayer &c, const char *who) {
+  SB_REQUIRE(c.k && c.v && c.k_scale && c.v_scale, "%s: null cache pointer", who);
+  SB_REQUIRE(c.head_dim == 128 || c.head_dim == 256, "%s: head_dim %u is not 128 or 256", who, c.head_dim);
+  SB_REQUIRE(c.kv_heads >= 1 && c.page_tokens >= 16 && (c.page_tokens & (c.page_tokens - 1)) == 0,
+             "%s: kv_heads %u / page_tokens %u (a power of two >= 16)", who, c.kv_heads, c.page_tokens);
+  return SB_OK;
+}
+
+int sb_attn_store(void *stream, const SbAttnStoreArgs *a) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(a && a->qkv && a->q_norm && a->k_norm && a->page_table && a->queries, "sb_attn_store: null pointer");
+  int st = check_cache(a->cache, "sb_attn_store");
+  if (st != SB_OK) return st;
+  const uint32_t D = a->cache.head_dim, qs = a->gated ? 2 * D : D;
+  SB_REQUIRE(a->rows >= 1 && a->rows <= 32 && a->q_heads >= 1 && a->q_heads % a->cache.kv_heads == 0,
+             "sb_attn_store: rows %u outside 1..32 or q_heads %u not a multiple of kv_heads", a->rows, a->q_heads);
+  SB_REQUIRE(a->qkv_stride >= a->q_heads * qs + 2 * a->cache.kv_heads * D, "sb_attn_store: qkv_stride %u below the packed row", a->qkv_stride);
+  SB_REQUIRE(2 * a->pairs <= D && (a->pairs == 0 || (a->cos_tab && a->sin_tab)), "sb_attn_store: %u rotary pairs exceed the head, or no tables", a->pairs);
+  StoreParams p{static_cast<const uint16_t *>(a->qkv), a->q_norm, a->k_norm, a->cos_tab, a->sin_tab, a->page_table,
+                static_cast<uint16_t *>(a->queries), a->cache, a->rows, a->q_heads, a->gated, a->pairs, a->qkv_stride, a->committed};
+  const dim3 grid(a->q_heads + a->cache.kv_heads, a->rows);
+  if (D == 256) return launch(attn_store_kernel<256>, grid, dim3(256), as_stream(stream), p);
+  return launch(attn_store_kernel<128>, grid, dim3(128), as_stream(stream), p);
+}
+
+int sb_kv_path_commit(void *stream, const SbKvLayer *cache, const uint32_t *page_table, uint32_t committed,
+                      const uint32_t *path_mask_dev) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(cache && page_table && path_mask_dev, "sb_kv_path_commit: null pointer");
+  int st = check_cache(*cache, "sb_kv_path_commit");
+  if (st != SB_OK) return st;
+  return launch(kv_path_commit_kernel, dim3(cache->kv_heads), dim3(cache->head_dim), as_stream(stream), *cache, page_table,
+                committed, path_mask_dev);
+}
+
+uint64_t sb_sample_workspace_bytes(uint32_t rows, uint32_t vocab) {
+  return uint64_t(rows) * (2 * ((vocab + kShard - 1) / kShard) + 8) * sizeof(float);
+}
+
+int sb_sample_verify(void *stream, const SbSampleArgs *a) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(a && a->logits && a->selected && a->input_tokens, "sb_sample_verify: null pointer");
+  SB_REQUIRE(a->rows >= 1 && a->rows <= 16 && a->vocab >= 1 && a->logit_stride >= a->vocab, "sb_sample_verify: rows %u outside 1..16 or bad vocabulary extent", a->rows);
+  SB_REQUIRE(a->temperature >= 0.0f, "sb_sample_verify: negative temperature");
+  SB_REQUIRE(a->temperature == 0.0f || (a->uniforms && a->workspace), "sb_sample_verify: a sampled policy needs uniforms and a workspace");
+  return launch(sample_kernel, dim3(a->rows), dim3(kSampleThreads), as_stream(stream), *a);
+}
+
+int sb_accept(void *stream, const SbAcceptArgs *a) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(a && a->input_tokens && a->tree && a->tokens && a->results, "sb_accept: null pointer");
+  SB_REQUIRE(a->rows >= 1 && a->rows <= 32 && a->remaining >= 1, "sb_accept: rows %u outside 1..32 or nothing remaining", a->rows);
+  SB_REQUIRE(a->n_stop == 0 || a->stop_tokens, "sb_accept: stop tokens missing");
+  return launch(accept_kernel, dim3(1), dim3(32), as_stream(stream), *a);
+}
+
+/* Programmatic dependent launch for the glue kernels of this context (on by default). */
+int sb_set_pdl(int enabled) {
+  ctx().pdl = enabled != 0;
+  return SB_OK;
+}
+
+}  // extern "C"

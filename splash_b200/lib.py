@@ -170,3 +170,79 @@ def linear(weights, x, out, fmt, n, k, rows, *, weights2=None, aux=None, norm_we
     a = SbLinearArgs(weights, weights2, x, prepared, aux, out, norm_weight, fmt, n, k, rows,
                      x_stride or k, (aux_stride or n) if aux else 0, out_stride or n, epilogue, int(out_f32), flags)
     check(load().sb_linear(stream, ctypes.byref(a)))
+
+
+# ---- the remaining operators ----
+_P, _U, _F = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_float
+
+
+class SbKvLayer(ctypes.Structure):
+    _fields_ = [("k", _P), ("v", _P), ("k_scale", _P), ("v_scale", _P),
+                ("kv_heads", _U), ("head_dim", _U), ("page_tokens", _U), ("scale_f16", _U)]
+
+
+class SbAttnStoreArgs(ctypes.Structure):
+    _fields_ = [("qkv", _P), ("q_norm", _P), ("k_norm", _P), ("cos_tab", _P), ("sin_tab", _P), ("page_table", _P),
+                ("queries", _P), ("cache", SbKvLayer),
+                ("rows", _U), ("q_heads", _U), ("gated", _U), ("pairs", _U), ("qkv_stride", _U), ("committed", _U)]
+
+
+class SbAttnArgs(ctypes.Structure):
+    _fields_ = [("queries", _P), ("qkv", _P), ("page_table", _P), ("tree", _P), ("out", _P), ("cache", SbKvLayer),
+                ("rows", _U), ("q_heads", _U), ("gated", _U), ("qkv_stride", _U), ("out_stride", _U), ("committed", _U)]
+
+
+class SbGdnTape(ctypes.Structure):
+    _fields_ = [("inputs", _P), ("k", _P), ("v", _P), ("beta", _P), ("decay", _P)]
+
+
+class SbGdnArgs(ctypes.Structure):
+    _fields_ = [("qkvz", _P), ("b", _P), ("a", _P), ("conv_w", _P), ("a_scale", _P), ("dt_bias", _P), ("norm_w", _P),
+                ("conv_state_in", _P), ("conv_state_out", _P), ("state_in", _P), ("state_out", _P),
+                ("pending", SbGdnTape), ("step", SbGdnTape), ("hidden", _P), ("pending_rows_dev", _P),
+                ("rows", _U), ("pending_rows", _U), ("key_heads", _U), ("value_heads", _U), ("qkvz_stride", _U),
+                ("ab_stride", _U), ("hidden_stride", _U), ("tiled", _U)]
+
+
+class SbSampleArgs(ctypes.Structure):
+    _fields_ = [("logits", _P), ("input_tokens", _P), ("uniforms", _P), ("selected", _P), ("workspace", _P),
+                ("rows", _U), ("vocab", _U), ("logit_stride", _U), ("temperature", _F)]
+
+
+class SbAcceptArgs(ctypes.Structure):
+    _fields_ = [("input_tokens", _P), ("tree", _P), ("tokens", _P), ("results", _P), ("stop_tokens", _P),
+                ("rows", _U), ("remaining", _U), ("n_stop", _U)]
+
+
+def _bind_ops():
+    l = load()
+    if getattr(l, "_ops_bound", False):
+        return l
+    l.sb_rmsnorm.argtypes = [_P, _P, _U, _U, _U, _P, _P, _U]
+    l.sb_embed.argtypes = [_P, _U, _P, _U, _U, _P, _U, _P, _U]
+    l.sb_rope_tables.argtypes = [_P, _P, _U, _P, _U, _F, _P, _P]
+    l.sb_linear_f32.argtypes = [_P, _P, _P, _U, _U, _U, _U, _P, _U, _U, _P]
+    l.sb_attn_store.argtypes = [_P, ctypes.POINTER(SbAttnStoreArgs)]
+    l.sb_attn_verify.argtypes = [_P, ctypes.POINTER(SbAttnArgs)]
+    l.sb_kv_path_commit.argtypes = [_P, ctypes.POINTER(SbKvLayer), _P, _U, _P]
+    l.sb_gdn_verify.argtypes = [_P, ctypes.POINTER(SbGdnArgs)]
+    l.sb_sample_workspace_bytes.restype = ctypes.c_uint64
+    l.sb_sample_workspace_bytes.argtypes = [_U, _U]
+    l.sb_sample_verify.argtypes = [_P, ctypes.POINTER(SbSampleArgs)]
+    l.sb_accept.argtypes = [_P, ctypes.POINTER(SbAcceptArgs)]
+    l._ops_bound = True
+    return l
+
+
+def ops():
+    """The library with every operator's signature bound."""
+    return _bind_ops()
+
+
+def chain_tree(rows):
+    """SplashTreeRow records of a chain: ancestors, parent | depth << 16 (row 0's parent is itself)."""
+    t = np.zeros((rows, 2), np.uint32)
+    for r in range(rows):
+        t[r, 0] = (1 << (r + 1)) - 1
+        t[r, 1] = (max(r - 1, 0) & 0xFFFF) | (r << 16)
+    return t

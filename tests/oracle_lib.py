@@ -60,3 +60,55 @@ def f2bf(x):
 
 def bf2f(u):
     return (np.ascontiguousarray(u, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+# ---- structures of oracle/so_ops.cpp and oracle/so_gdn.cpp ----
+_P, _U = ctypes.c_void_p, ctypes.c_uint32
+
+
+class SoKvLayer(ctypes.Structure):
+    _fields_ = [("k", _P), ("v", _P), ("k_scale", _P), ("v_scale", _P),
+                ("kv_heads", _U), ("head_dim", _U), ("page_tokens", _U), ("scale_f16", _U)]
+
+
+class SoGdnTape(ctypes.Structure):
+    _fields_ = [("inputs", _P), ("k", _P), ("v", _P), ("beta", _P), ("decay", _P)]
+
+
+class SoGdnArgs(ctypes.Structure):
+    _fields_ = [("qkvz", _P), ("b", _P), ("a", _P), ("conv_w", _P), ("a_scale", _P), ("dt_bias", _P), ("norm_w", _P),
+                ("conv_state_in", _P), ("conv_state_out", _P), ("state_in", _P), ("state_out", _P),
+                ("pending", SoGdnTape), ("step", SoGdnTape), ("hidden", _P),
+                ("rows", _U), ("pending_rows", _U), ("key_heads", _U), ("value_heads", _U), ("qkvz_stride", _U),
+                ("ab_stride", _U), ("hidden_stride", _U), ("tiled", _U)]
+
+
+class HostKv:
+    """A host-side INT8 cache of one layer in the product's layout, with its oracle descriptor."""
+
+    def __init__(self, pages, kv_heads, head_dim, page_tokens, scale_f16):
+        self.k = np.zeros((pages, kv_heads, page_tokens, head_dim), np.int8)
+        self.v = np.zeros_like(self.k)
+        st = np.float16 if scale_f16 else np.float32
+        self.ks = np.zeros((pages, kv_heads, page_tokens), st)
+        self.vs = np.zeros_like(self.ks)
+        self.geom = (kv_heads, head_dim, page_tokens, int(bool(scale_f16)))
+
+    def desc(self):
+        return SoKvLayer(ptr(self.k), ptr(self.v), ptr(self.ks), ptr(self.vs), *self.geom)
+
+    def fill_random(self, rng, tokens_per_page_filled=None):
+        self.k[...] = rng.integers(-127, 128, self.k.shape, dtype=np.int8)
+        self.v[...] = rng.integers(-127, 128, self.v.shape, dtype=np.int8)
+        self.ks[...] = rng.uniform(0.005, 0.03, self.ks.shape).astype(self.ks.dtype)
+        self.vs[...] = rng.uniform(0.005, 0.03, self.vs.shape).astype(self.vs.dtype)
+
+
+def bind_ops(lib):
+    F = ctypes.c_float
+    lib.so_kv_scale.restype = F
+    lib.so_kv_scale.argtypes = [F]
+    lib.so_kv_code.argtypes = [F, F]
+    lib.so_rope_tables.argtypes = [_P, _U, _P, _U, F, _P, _P]
+    lib.so_sample_verify.argtypes = [_P, _U, _U, _U, _P, F, _P, _P, _P]
+    return lib

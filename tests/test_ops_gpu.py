@@ -1,0 +1,312 @@
+"""Parity of the glue operators, the KV store, attention, GDN, selection and acceptance (CUDA, through
+the C ABI) with the oracle on the same seeded inputs."""
+import ctypes
+
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+import quant_fixtures as qf
+
+pytestmark = pytest.mark.gpu
+P = ol.ptr
+
+
+def _setup():
+    from splash_b200 import lib
+    lib.init(0)
+    return lib, lib.ops(), ol.bind_ops(ol.load())
+
+
+def bf16_randn(rng, shape, scale=1.0):
+    return ol.f2bf((rng.standard_normal(shape) * scale).astype(np.float32))
+
+
+def ulp_bf16(x):
+    e = np.floor(np.log2(np.maximum(np.abs(x), 2.0 ** -126)))
+    return 2.0 ** (e - 7)
+
+
+def test_rmsnorm_and_fused_float_projection():
+    lib, l, o = _setup()
+    rng = np.random.default_rng(1)
+    rows, width = 16, 5120
+    x = bf16_randn(rng, (rows, width), 3.0)
+    w = (1 + 0.1 * rng.standard_normal(width)).astype(np.float32)
+    want = np.zeros((rows, width), np.uint16)
+    o.so_rmsnorm(P(x), rows, width, width, P(w), P(want), width)
+    xd, wd = lib.DeviceBuffer.from_numpy(x), lib.DeviceBuffer.from_numpy(w)
+    od = lib.DeviceBuffer(rows * width * 2)
+    lib.check(l.sb_rmsnorm(None, xd.ptr, rows, width, width, wd.ptr, od.ptr, width))
+    got = od.to_numpy(np.uint16, (rows, width))
+    d = np.abs(ol.bf2f(got).astype(np.float64) - ol.bf2f(want))
+    assert (d <= ulp_bf16(ol.bf2f(want))).all() and (got != want).mean() < 0.01
+    # fp32 projection of fp32 rows over the normalised input (the GDN alpha/beta rows)
+    n = 96
+    wf = (rng.standard_normal((n, width)) * 0.02).astype(np.float32)
+    wfd = lib.DeviceBuffer.from_numpy(wf)
+    pd = lib.DeviceBuffer(rows * n * 4)
+    lib.check(l.sb_linear_f32(None, wfd.ptr, xd.ptr, rows, n, width, width, pd.ptr, n, 1, wd.ptr))
+    proj = pd.to_numpy(np.float32, (rows, n))
+    ref = ol.bf2f(want).astype(np.float64) @ wf.astype(np.float64).T
+    assert np.abs(proj - ref).max() <= 2e-3 * np.abs(ref).max()
+
+
+@pytest.mark.parametrize("fmt", [4, 0, 6])
+def test_embedding_gather(fmt):
+    lib, l, o = _setup()
+    vocab, width, rows = 1000, 1024, 16
+    table = qf.realistic(fmt, vocab, width, seed=5)
+    tokens = np.array([0, 999, 5, 1000, 4000000000, 17, 3, 3, 9, 100, 200, 300, 400, 500, 600, 700], np.uint32)
+    want = np.zeros((rows, width), np.uint16)
+    assert o.so_embed(fmt, P(table), vocab, width, P(tokens), rows, P(want), width) == 0
+    td, kd = lib.DeviceBuffer.from_numpy(table), lib.DeviceBuffer.from_numpy(tokens)
+    od = lib.DeviceBuffer(rows * width * 2)
+    lib.check(l.sb_embed(None, fmt, td.ptr, vocab, width, kd.ptr, rows, od.ptr, width))
+    assert np.array_equal(od.to_numpy(np.uint16, (rows, width)), want)
+
+
+def test_rope_tables():
+    lib, l, o = _setup()
+    rows, pairs = 16, 32
+    pos = (32768 + np.arange(rows)).astype(np.uint32)
+    inv = (1e6 ** (-np.arange(pairs) / pairs)).astype(np.float32)
+    c, s = np.zeros((rows, pairs), np.float32), np.zeros((rows, pairs), np.float32)
+    o.so_rope_tables(P(pos), rows, P(inv), pairs, 1.0, P(c), P(s))
+    pd, fd = lib.DeviceBuffer.from_numpy(pos), lib.DeviceBuffer.from_numpy(inv)
+    cd, sd = lib.DeviceBuffer(c.nbytes), lib.DeviceBuffer(s.nbytes)
+    lib.check(l.sb_rope_tables(None, pd.ptr, rows, fd.ptr, pairs, 1.0, cd.ptr, sd.ptr))
+    assert np.abs(cd.to_numpy(np.float32, c.shape) - c).max() < 2e-6
+    assert np.abs(sd.to_numpy(np.float32, s.shape) - s).max() < 2e-6
+
+
+class DevKv:
+    def __init__(self, lib, host):
+        self.host = host
+        self.k, self.v = lib.DeviceBuffer.from_numpy(host.k), lib.DeviceBuffer.from_numpy(host.v)
+        self.ks, self.vs = lib.DeviceBuffer.from_numpy(host.ks), lib.DeviceBuffer.from_numpy(host.vs)
+
+    def desc(self, lib):
+        return lib.SbKvLayer(self.k.ptr, self.v.ptr, self.ks.ptr, self.vs.ptr, *self.host.geom)
+
+    def download(self):
+        h = self.host
+        return (self.k.to_numpy(np.int8, h.k.shape), self.v.to_numpy(np.int8, h.v.shape),
+                self.ks.to_numpy(h.ks.dtype, h.ks.shape), self.vs.to_numpy(h.vs.dtype, h.vs.shape))
+
+
+def attention_case(lib, l, o, *, q_heads, kv_heads, D, page_tokens, scale_f16, committed, rows, gated, seed):
+    rng = np.random.default_rng(seed)
+    pairs = 32 if D == 256 else 16
+    pages = (committed + rows + page_tokens - 1) // page_tokens + 1
+    host = ol.HostKv(pages, kv_heads, D, page_tokens, scale_f16)
+    host.fill_random(rng)
+    table = rng.permutation(pages).astype(np.uint32)
+    qs = 2 * D if gated else D
+    stride = q_heads * qs + 2 * kv_heads * D
+    qkv = bf16_randn(rng, (rows, stride), 1.5)
+    qn = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    kn = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    pos = (committed + np.arange(rows)).astype(np.uint32)
+    inv = (1e6 ** (-np.arange(pairs) / pairs)).astype(np.float32)
+    c, s = np.zeros((rows, pairs), np.float32), np.zeros((rows, pairs), np.float32)
+    o.so_rope_tables(P(pos), rows, P(inv), pairs, 1.0, P(c), P(s))
+    dev = DevKv(lib, host)  # upload before the oracle writes its rows
+    # oracle
+    queries = np.zeros((rows, q_heads, D), np.uint16)
+    desc = host.desc()
+    o.so_attn_store(P(qkv), stride, rows, q_heads, int(gated), P(qn), P(kn), P(c), P(s), pairs, ctypes.byref(desc),
+                    P(table), committed, P(queries))
+    want = np.zeros((rows, q_heads * D), np.uint16)
+    want64 = np.zeros((rows, q_heads, D), np.float64)
+    o.so_attention(P(queries), P(qkv), stride, rows, q_heads, int(gated), ctypes.byref(desc), P(table), committed, None,
+                   P(want), q_heads * D, P(want64))
+    # device
+    bufs = {n: lib.DeviceBuffer.from_numpy(a) for n, a in dict(qkv=qkv, qn=qn, kn=kn, c=c, s=s, table=table).items()}
+    qd = lib.DeviceBuffer(queries.nbytes)
+    sa = lib.SbAttnStoreArgs(bufs["qkv"].ptr, bufs["qn"].ptr, bufs["kn"].ptr, bufs["c"].ptr, bufs["s"].ptr, bufs["table"].ptr,
+                             qd.ptr, dev.desc(lib), rows, q_heads, int(gated), pairs, stride, committed)
+    lib.check(l.sb_attn_store(None, ctypes.byref(sa)))
+    od = lib.DeviceBuffer(want.nbytes)
+    od.fill(0xFF)
+    aa = lib.SbAttnArgs(qd.ptr, bufs["qkv"].ptr, bufs["table"].ptr, None, od.ptr, dev.desc(lib), rows, q_heads, int(gated),
+                        stride, q_heads * D, committed)
+    lib.check(l.sb_attn_verify(None, ctypes.byref(aa)))
+    lib.stream_sync()
+    assert lib.device_status() == 0
+    got_q = qd.to_numpy(np.uint16, queries.shape)
+    k, v, ks, vs = dev.download()
+    return dict(host=host, got_q=got_q, want_q=queries, k=k, v=v, ks=ks, vs=vs,
+                got=od.to_numpy(np.uint16, want.shape), want=want, want64=want64.reshape(rows, -1))
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(q_heads=24, kv_heads=4, D=256, page_tokens=256, scale_f16=True, committed=2048, rows=16, gated=True, seed=1),
+    dict(q_heads=8, kv_heads=2, D=128, page_tokens=256, scale_f16=True, committed=2048, rows=16, gated=False, seed=2),
+    dict(q_heads=24, kv_heads=4, D=256, page_tokens=32, scale_f16=False, committed=1000, rows=5, gated=True, seed=3),
+    dict(q_heads=16, kv_heads=2, D=256, page_tokens=64, scale_f16=False, committed=7, rows=16, gated=True, seed=4),
+    dict(q_heads=8, kv_heads=2, D=128, page_tokens=32, scale_f16=True, committed=0, rows=1, gated=False, seed=5),
+])
+def test_kv_store_bit_exact_and_attention_within_gates(cfg):
+    lib, l, o = _setup()
+    r = attention_case(lib, l, o, **cfg)
+    # staged queries and the quantized rows: bit-exact
+    assert np.array_equal(r["got_q"], r["want_q"])
+    h = r["host"]
+    assert np.array_equal(r["k"], h.k) and np.array_equal(r["v"], h.v)
+    assert np.array_equal(r["ks"], h.ks) and np.array_equal(r["vs"], h.vs)
+    # attention: the reference's gates (cosine > 0.9995, max-abs < 0.02) and 2e-3 of the output's scale
+    got, want64 = ol.bf2f(r["got"]).astype(np.float64), r["want64"]
+    cos = (got * want64).sum() / np.sqrt((got * got).sum() * (want64 * want64).sum())
+    assert cos > 0.9995
+    scale = np.abs(want64).max()
+    assert np.abs(got - want64).max() < max(0.02, 4e-3 * scale)
+    rel = np.abs(got - want64) / np.maximum(np.abs(want64), np.sqrt((want64 ** 2).mean()))
+    assert np.median(rel) < 2e-3 and rel.max() < 2e-2
+
+
+def test_attention_long_context_32k():
+    lib, l, o = _setup()
+    r = attention_case(lib, l, o, q_heads=24, kv_heads=4, D=256, page_tokens=256, scale_f16=True, committed=32768 - 16,
+                       rows=16, gated=True, seed=9)
+    got, want64 = ol.bf2f(r["got"]).astype(np.float64), r["want64"]
+    cos = (got * want64).sum() / np.sqrt((got * got).sum() * (want64 * want64).sum())
+    assert cos > 0.9995 and np.abs(got - want64).max() < 0.02
+
+
+def gdn_case(lib, l, o, *, key_heads, value_heads, rows, pending_rows, tiled, seed):
+    rng = np.random.default_rng(seed)
+    D = 128
+    KW, VW = key_heads * D, value_heads * D
+    C = 2 * KW + VW
+    stride = C + VW
+    qkvz = bf16_randn(rng, (16, stride), 1.0)
+    b = bf16_randn(rng, (16, value_heads), 1.0)
+    a = bf16_randn(rng, (16, value_heads), 1.0)
+    conv_w = bf16_randn(rng, (C, 4), 0.4)
+    a_scale = (-np.exp(rng.uniform(-3, 0.5, value_heads))).astype(np.float32)
+    dt_bias = bf16_randn(rng, (value_heads,), 0.5)
+    norm_w = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    cs_in = bf16_randn(rng, (3, C), 1.0)
+    state = (rng.standard_normal((value_heads, D, D)) * 0.05).astype(np.float32)
+    pend = dict(inputs=bf16_randn(rng, (16, C), 1.0), k=bf16_randn(rng, (16, KW), 0.09), v=bf16_randn(rng, (16, VW), 0.5),
+                beta=ol.f2bf(rng.uniform(0.1, 0.9, (16, value_heads)).astype(np.float32)),
+                decay=rng.uniform(0.5, 1.0, (16, value_heads)).astype(np.float32))
+    step = dict(inputs=np.zeros((16, C), np.uint16), k=np.zeros((16, KW), np.uint16), v=np.zeros((16, VW), np.uint16),
+                beta=np.zeros((16, value_heads), np.uint16), decay=np.zeros((16, value_heads), np.float32))
+    cs_out, state_out = np.zeros_like(cs_in), np.zeros_like(state)
+    hidden = np.zeros((16, VW), np.uint16)
+    tape = lambda t: ol.SoGdnTape(P(t["inputs"]), P(t["k"]), P(t["v"]), P(t["beta"]), P(t["decay"]))
+    args = ol.SoGdnArgs(P(qkvz), P(b), P(a), P(conv_w), P(a_scale), P(dt_bias), P(norm_w), P(cs_in), P(cs_out), P(state),
+                        P(state_out), tape(pend), tape(step), P(hidden), rows, pending_rows, key_heads, value_heads,
+                        stride, value_heads, VW, int(tiled))
+    o.so_gdn_verify(ctypes.byref(args))
+    up = lib.DeviceBuffer.from_numpy
+    d = {n: up(x) for n, x in dict(qkvz=qkvz, b=b, a=a, conv_w=conv_w, a_scale=a_scale, dt_bias=dt_bias, norm_w=norm_w,
+                                   cs_in=cs_in, state=state).items()}
+    dp = {n: up(x) for n, x in pend.items()}
+    ds = {n: lib.DeviceBuffer(x.nbytes) for n, x in step.items()}
+    dcs, dst, dh = lib.DeviceBuffer(cs_out.nbytes), lib.DeviceBuffer(state.nbytes), lib.DeviceBuffer(hidden.nbytes)
+    dtape = lambda t: lib.SbGdnTape(t["inputs"].ptr, t["k"].ptr, t["v"].ptr, t["beta"].ptr, t["decay"].ptr)
+    ga = lib.SbGdnArgs(d["qkvz"].ptr, d["b"].ptr, d["a"].ptr, d["conv_w"].ptr, d["a_scale"].ptr, d["dt_bias"].ptr,
+                       d["norm_w"].ptr, d["cs_in"].ptr, dcs.ptr, d["state"].ptr, dst.ptr, dtape(dp), dtape(ds), dh.ptr, None,
+                       rows, pending_rows, key_heads, value_heads, stride, value_heads, VW, int(tiled))
+    lib.check(l.sb_gdn_verify(None, ctypes.byref(ga)))
+    lib.stream_sync()
+    assert lib.device_status() == 0
+    got = dict(cs=dcs.to_numpy(np.uint16, cs_out.shape), state=dst.to_numpy(np.float32, state.shape),
+               hidden=dh.to_numpy(np.uint16, hidden.shape))
+    got.update({n: ds[n].to_numpy(step[n].dtype, step[n].shape) for n in step})
+    return got, dict(cs=cs_out, state=state_out, hidden=hidden, **step), rows
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(key_heads=16, value_heads=48, rows=16, pending_rows=7, tiled=True, seed=1),
+    dict(key_heads=8, value_heads=8, rows=16, pending_rows=16, tiled=False, seed=2),
+    dict(key_heads=2, value_heads=6, rows=5, pending_rows=0, tiled=False, seed=3),
+    dict(key_heads=2, value_heads=4, rows=1, pending_rows=2, tiled=True, seed=4),
+])
+def test_gdn_verify_within_reference_gates(cfg):
+    lib, l, o = _setup()
+    got, want, rows = gdn_case(lib, l, o, **cfg)
+    assert np.array_equal(got["cs"], want["cs"])
+    assert np.array_equal(got["inputs"][:rows], want["inputs"][:rows])
+    # tape k / v and gates within 3 bf16 ulp (the reference's gate); state 1e-4 relative
+    for n in ("k", "v", "beta"):
+        g, w = ol.bf2f(got[n][:rows]).astype(np.float64), ol.bf2f(want[n][:rows]).astype(np.float64)
+        assert (np.abs(g - w) <= 3 * ulp_bf16(w)).all(), n
+    assert np.allclose(got["decay"][:rows], want["decay"][:rows], rtol=1e-5)
+    s_scale = np.abs(want["state"]).max()
+    assert np.abs(got["state"] - want["state"]).max() <= 1e-4 * s_scale
+    g, w = ol.bf2f(got["hidden"][:rows]).astype(np.float64), ol.bf2f(want["hidden"][:rows]).astype(np.float64)
+    bad = np.abs(g - w) > 3 * ulp_bf16(w) + 2e-3 * np.abs(w).mean()
+    assert bad.mean() <= 0.01
+
+
+def test_gdn_fold_then_next_step_is_consistent():
+    """Folding r accepted rows in the next step equals scanning them now: the output of row r of one block
+    equals the output of row 0 of a block that starts after folding the first r rows (same inputs)."""
+    lib, l, o = _setup()
+    got_a, want_a, _ = gdn_case(lib, l, o, key_heads=2, value_heads=4, rows=16, pending_rows=3, tiled=False, seed=11)
+    got_b, want_b, _ = gdn_case(lib, l, o, key_heads=2, value_heads=4, rows=16, pending_rows=3, tiled=False, seed=11)
+    assert np.array_equal(got_a["hidden"], got_b["hidden"]) and np.array_equal(got_a["state"], got_b["state"])
+
+
+def test_greedy_selection_and_acceptance():
+    lib, l, o = _setup()
+    rng = np.random.default_rng(4)
+    rows, vocab = 16, 151936
+    logits = rng.standard_normal((rows, vocab)).astype(np.float32)
+    logits[3, 77] = logits[3, 99000] = 50.0      # a tie: the lowest id wins
+    logits[5, :] = np.nan                         # nothing selectable: the sentinel
+    logits[6, 10] = np.inf
+    logits[7, :] = -np.inf
+    logits[7, 123] = -5.0
+    want = np.zeros(rows, np.uint32)
+    inputs = np.zeros(rows, np.uint32)
+    o.so_sample_verify(P(logits), vocab, vocab, rows, P(inputs), 0.0, None, P(want), None)
+    ld, idd = lib.DeviceBuffer.from_numpy(logits), lib.DeviceBuffer.from_numpy(inputs)
+    sd = lib.DeviceBuffer(rows * 4)
+    sa = lib.SbSampleArgs(ld.ptr, idd.ptr, None, sd.ptr, None, rows, vocab, vocab, 0.0)
+    lib.check(l.sb_sample_verify(None, ctypes.byref(sa)))
+    got = sd.to_numpy(np.uint32, (rows,))
+    assert np.array_equal(got, want)
+    assert got[3] == 77 and got[5] == 0xFFFFFFFF and got[6] == 10 and got[7] == 123
+    # acceptance: the draft matched the first 4 selections
+    inputs = np.concatenate([[1], got[:4], [5, 5, 5, 5, 5, 5, 5, 5, 5, 5, 5]]).astype(np.uint32)[:rows]
+    tree = lib.chain_tree(rows)
+    tokens = got.copy()
+    res = np.zeros(3, np.uint32)
+    o.so_accept(P(inputs), P(tree), P(tokens), rows, 100, None, 0, P(res[0:1]), P(res[1:2]), P(res[2:3]))
+    idd.upload(inputs)
+    td, kd, rd = lib.DeviceBuffer.from_numpy(tree), lib.DeviceBuffer.from_numpy(got), lib.DeviceBuffer(16)
+    aa = lib.SbAcceptArgs(idd.ptr, td.ptr, kd.ptr, rd.ptr, None, rows, 100, 0)
+    lib.check(l.sb_accept(None, ctypes.byref(aa)))
+    dres = rd.to_numpy(np.uint32, (4,))
+    assert dres[0] == res[0] == 5 and dres[1] == res[1] == 4 and dres[2] == res[2] == 0b11111
+    assert np.array_equal(kd.to_numpy(np.uint32, (rows,))[:5], tokens[:5])
+
+
+def test_stochastic_selection_with_supplied_uniforms():
+    lib, l, o = _setup()
+    rng = np.random.default_rng(8)
+    rows, vocab = 16, 32000
+    logits = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
+    greedy = logits.argmax(axis=1).astype(np.uint32)
+    # the draft proposes the argmax with p = 0.7, else a random token
+    inputs = np.zeros(rows, np.uint32)
+    for r in range(1, rows):
+        inputs[r] = greedy[r - 1] if rng.random() < 0.7 else rng.integers(0, vocab)
+    uniforms = rng.random(80).astype(np.float32)
+    want, margin = np.zeros(rows, np.uint32), np.zeros(rows, np.float64)
+    o.so_sample_verify(P(logits), vocab, vocab, rows, P(inputs), 0.7, P(uniforms), P(want), P(margin))
+    ld, idd, ud = (lib.DeviceBuffer.from_numpy(x) for x in (logits, inputs, uniforms))
+    sd = lib.DeviceBuffer(rows * 4)
+    wd = lib.DeviceBuffer(int(l.sb_sample_workspace_bytes(rows, vocab)))
+    sa = lib.SbSampleArgs(ld.ptr, idd.ptr, ud.ptr, sd.ptr, wd.ptr, rows, vocab, vocab, 0.7)
+    lib.check(l.sb_sample_verify(None, ctypes.byref(sa)))
+    got = sd.to_numpy(np.uint32, (rows,))
+    # bit-exact wherever the accept test is not within rounding of its threshold
+    clear = margin > 1e-5
+    assert clear.sum() >= rows - 2
+    assert np.array_equal(got[clear], want[clear])

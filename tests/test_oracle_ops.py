@@ -1,0 +1,135 @@
+"""CPU checks of the oracle itself: the INT8 KV quantizer against the reference's own CPU code (where the
+reference shim was built), the acceptance rule on hand-made chains and trees, selection invariants, and
+the oracle's linear port against its own fp64 dot products within the reference's bound."""
+import ctypes
+
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+import quant_fixtures as qf
+
+P = ol.ptr
+
+
+def test_kv_quantizer_matches_reference_code():
+    ref = ol.load_ref()
+    if ref is None:
+        pytest.skip("reference shim not built (reference tree absent)")
+    o = ol.bind_ops(ol.load())
+    rng = np.random.default_rng(0)
+    vals = np.concatenate([rng.standard_normal(4000).astype(np.float32) * 3, [0.0, 1e-30, -2.5, 127.0, 0.5, 1.5, 2.5]])
+    for m in [0.0, 1.0, 3.7, 127.0, 1e-20, 1e20]:
+        assert o.so_kv_scale(m) == ref.ref_kv_scale(m)
+        for v in vals[:500]:
+            v = float(np.clip(v, -m, m)) if m else float(v)
+            assert o.so_kv_code(v, m) == ref.ref_kv_code(v, m)
+
+
+def chain(rows):
+    t = np.zeros((rows, 2), np.uint32)
+    for r in range(rows):
+        t[r, 0] = (1 << (r + 1)) - 1
+        t[r, 1] = max(r - 1, 0) | (r << 16)
+    return t
+
+
+def accept(o, inputs, tree, tokens, remaining=100, stops=()):
+    inputs, tokens = np.array(inputs, np.uint32), np.array(tokens, np.uint32)
+    stops = np.array(stops, np.uint32)
+    res = np.zeros(3, np.uint32)
+    o.so_accept(P(inputs), P(tree), P(tokens), len(tokens), remaining, P(stops) if len(stops) else None, len(stops),
+                P(res[0:1]), P(res[1:2]), P(res[2:3]))
+    return tokens, res
+
+
+def test_accept_longest_matching_prefix_of_a_chain():
+    o = ol.load()
+    # row r's input is the draft of position r; the target selected 10, 11, 12, 99 ...
+    tokens, res = accept(o, [1, 10, 11, 12, 13, 14], chain(6), [10, 11, 12, 99, 50, 60])
+    assert res[0] == 4 and res[1] == 3 and res[2] == 0b1111
+    assert list(tokens[:4]) == [10, 11, 12, 99]
+    # nothing matches: only the bonus token of row 0 is kept
+    tokens, res = accept(o, [1, 2, 3], chain(3), [7, 8, 9])
+    assert res[0] == 1 and res[1] == 0 and tokens[0] == 7
+    # the lane's cap and a stop token truncate
+    tokens, res = accept(o, [1, 10, 11, 12], chain(4), [10, 11, 12, 13], remaining=2)
+    assert res[0] == 2 and res[1] == 2
+    tokens, res = accept(o, [1, 10, 11, 12], chain(4), [10, 11, 12, 13], stops=[11])
+    assert res[0] == 2 and res[1] == 2
+
+
+def test_accept_follows_a_tree():
+    o = ol.load()
+    # rows: 0 root; 1, 2 children of 0; 3 child of 2; 4 child of 3
+    tree = np.array([[0b00001, 0 | (0 << 16)], [0b00011, 0 | (1 << 16)], [0b00101, 0 | (1 << 16)],
+                     [0b01101, 2 | (2 << 16)], [0b11101, 3 | (3 << 16)]], np.uint32)
+    tokens, res = accept(o, [1, 20, 30, 31, 32], tree, [30, 0, 31, 32, 77])
+    assert res[0] == 4 and res[1] == 3 and res[2] == 0b11101
+    assert list(tokens[:4]) == [30, 31, 32, 77]
+
+
+def test_selection_greedy_equals_numpy_argmax_and_rejection_sampling_statistics():
+    o = ol.bind_ops(ol.load())
+    rng = np.random.default_rng(2)
+    rows, vocab = 8, 1000
+    logits = rng.standard_normal((rows, vocab)).astype(np.float32)
+    sel = np.zeros(rows, np.uint32)
+    inputs = np.zeros(rows, np.uint32)
+    o.so_sample_verify(P(logits), vocab, vocab, rows, P(inputs), 0.0, None, P(sel), None)
+    assert np.array_equal(sel, logits.argmax(axis=1))
+    # sampled: the marginal of the selected token of the last row follows softmax(l / T)
+    T = 0.7
+    p = np.exp((logits[-1] - logits[-1].max()) / T)
+    p /= p.sum()
+    counts = np.zeros(vocab)
+    for i in range(3000):
+        u = rng.random(80).astype(np.float32)
+        o.so_sample_verify(P(logits), vocab, vocab, rows, P(inputs), T, P(u), P(sel), None)
+        counts[sel[-1]] += 1
+    top = np.argsort(-p)[:5]
+    assert np.abs(counts[top] / 3000 - p[top]).max() < 0.03
+
+
+def test_rejection_rule_keeps_the_target_distribution():
+    """With a deterministic draft d: P(select d) = p(d), and P(select v != d) = p(v): rejection sampling is
+    exact (sampling.metal:778-800 with q = 1)."""
+    o = ol.bind_ops(ol.load())
+    rng = np.random.default_rng(3)
+    vocab = 50
+    logits = np.tile(rng.standard_normal(vocab).astype(np.float32) * 2, (2, 1))
+    p = np.exp((logits[0] - logits[0].max()) / 0.7)
+    p /= p.sum()
+    inputs = np.array([0, int(np.argsort(-p)[1])], np.uint32)
+    sel = np.zeros(2, np.uint32)
+    counts = np.zeros(vocab)
+    n = 20000
+    for i in range(n):
+        u = rng.random(80).astype(np.float32)
+        o.so_sample_verify(P(logits), vocab, vocab, 2, P(inputs), 0.7, P(u), P(sel), None)
+        counts[sel[0]] += 1
+    assert np.abs(counts / n - p).max() < 0.015
+
+
+@pytest.mark.parametrize("fmt", [0, 4, 6])
+def test_linear_port_within_projection_bound(fmt):
+    o = ol.load()
+    n, k, rows = 64, 1024, 4
+    W = qf.realistic(fmt, n, k)
+    X = qf.activations(rows, k)
+    v = np.zeros((rows, n))
+    be, bs = np.zeros_like(v), np.zeros_like(v)
+    assert o.so_linear_f64(fmt, P(W), n, k, P(X), rows, P(v), P(be), P(bs)) == 0
+    out = np.zeros((rows, n), np.float32)
+    assert o.so_linear(fmt, P(W), n, k, P(X), rows, 0, None, 0, P(out), n, 1, 0) == 0
+    assert (np.abs(out - v) <= be).all()
+    out16 = np.zeros((rows, n), np.float32)
+    assert o.so_linear(fmt, P(W), n, k, P(X), rows, 0, None, 0, P(out16), n, 1, 1) == 0
+    assert (np.abs(out16 - v) <= bs).all()
+    ref = ol.load_ref()
+    if ref is not None:  # the bound itself against the reference's projectionBound
+        w = ol.dequant(o, fmt, W, n, k)
+        x = ol.bf2f(X)
+        val, ex, st = ctypes.c_double(), ctypes.c_double(), ctypes.c_double()
+        ref.ref_projection(P(x[1]), P(w[5]), k, ctypes.byref(val), ctypes.byref(ex), ctypes.byref(st))
+        assert np.isclose(val.value, v[1, 5]) and np.isclose(ex.value, be[1, 5]) and np.isclose(st.value, bs[1, 5])
