@@ -201,6 +201,7 @@ typedef struct SbAttnStoreArgs {
   const uint32_t *page_table; /* device u32 physical page per logical page */
   void *queries;            /* bf16 [rows, q_heads, head_dim] */
   SbKvLayer cache;
+  const uint32_t *committed_dev; /* optional device word overriding `committed`, so a captured graph follows the lane */
   uint32_t rows, q_heads, gated, pairs, qkv_stride, committed;
 } SbAttnStoreArgs;
 SB_API int sb_attn_store(void *stream, const SbAttnStoreArgs *args);
@@ -218,6 +219,7 @@ typedef struct SbAttnArgs {
   const void *tree;         /* optional device SplashTreeRow[rows] */
   void *out;                /* bf16 [rows, out_stride] = [row][q_head][dim] */
   SbKvLayer cache;
+  const uint32_t *committed_dev; /* optional device word; `committed` is then the bound the split plan is made for */
   uint32_t rows, q_heads, gated, qkv_stride, out_stride, committed;
 } SbAttnArgs;
 SB_API int sb_attn_verify(void *stream, const SbAttnArgs *args);
@@ -298,6 +300,52 @@ typedef struct SbAcceptArgs {
   uint32_t rows, remaining, n_stop;
 } SbAcceptArgs;
 SB_API int sb_accept(void *stream, const SbAcceptArgs *args);
+
+/* ---- the target model's verify step ----
+ * The layer loop and the step's commit, as the reference's QwenTarget::addPrefillLayers /
+ * encodeTargetDecodeForward / encodeVerifyCommit build them (runtime/model/QwenTarget.hpp:618-652,
+ * runtime/model/QwenTarget.cpp:206-496, runtime/model/Runtime.cpp:2677-2717,2883-2892): pre-norm residual blocks,
+ * layer l a full-attention layer iff (l + 1) % attention_interval == 0 (runtime/model/QwenHybridLayout.hpp:132-135),
+ * else Gated DeltaNet; dense SwiGLU FFN; final norm and the vocabulary projection into fp32 logits of every row;
+ * selection, acceptance, and the lane's commit (committed tokens and the GDN tape's accepted rows stay on the device).
+ * One lane (batch 1) per target. */
+typedef struct SbTargetConfig {
+  uint32_t layers, hidden, vocab, intermediate;
+  uint32_t q_heads, kv_heads, head_dim, rotary_pairs;
+  float rope_theta;
+  uint32_t gdn_key_heads, gdn_value_heads;
+  uint32_t attention_interval;  /* 4 */
+  uint32_t page_tokens, kv_scale_f16, max_context;
+  uint32_t fmt_proj, fmt_down, fmt_head, fmt_embed; /* SB_FMT_* */
+  uint32_t gated_attention, tiled_heads;
+} SbTargetConfig;
+
+enum {
+  SB_TARGET_ADVANCE = 1, /* the step commits: committed += retained, the next step folds the accepted rows */
+  SB_TARGET_GRAPH = 2    /* replay the step as a captured CUDA graph (captured on first use per parity) */
+};
+
+SB_API int sb_target_create(const SbTargetConfig *config, void **out_target);
+SB_API int sb_target_destroy(void *target);
+/* Device pointer and byte size of a tensor or buffer by name. Per layer (layer >= 0): attn_norm, ffn_norm,
+ * in_proj, out_proj, ffn_gate, ffn_up, ffn_down, and for GDN layers ssm_ab, ssm_conv, ssm_a, ssm_dt_bias, ssm_norm,
+ * state0/1, conv0/1, for attention layers q_norm, k_norm, kv_k, kv_v, kv_ks, kv_vs. Global (layer = -1):
+ * token_embd, output_norm, output, logits, selected, results, hidden, tokens, uniforms, committed. */
+SB_API int sb_target_tensor(void *target, int layer, const char *name, void **out_dev, uint64_t *out_bytes);
+/* Seeded synthetic weights, a prefilled INT8 cache of `committed` tokens and random GDN state, written on the device. */
+SB_API int sb_target_randomize(void *target, uint64_t seed, uint32_t committed);
+/* Sets the lane's position and clears the pending GDN rows. */
+SB_API int sb_target_reset(void *target, uint32_t committed);
+/* One verify step over inputs already on the device (`tokens`, `uniforms` buffers of the target). */
+SB_API int sb_target_step(void *target, void *stream, uint32_t rows, float temperature, uint32_t flags);
+/* One verify step from host buffers: uploads the block's input tokens (row 0 the last accepted token, rows 1.. the
+ * draft) and the uniforms, runs the step, downloads {retained, accepted, retained_rows, 0} and the retained tokens,
+ * and waits. */
+SB_API int sb_target_verify(void *target, void *stream, const uint32_t *tokens_host, const float *uniforms_host, uint32_t rows,
+                            float temperature, uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host);
+/* Kernels one step launches, and the bytes its weights, cache and state stream (the roofline's numerator). */
+SB_API int sb_target_stats(void *target, uint32_t rows, uint32_t *out_launches, uint64_t *out_weight_bytes, uint64_t *out_kv_bytes,
+                           uint64_t *out_state_bytes);
 
 #ifdef __cplusplus
 }

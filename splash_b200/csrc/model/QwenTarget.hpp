@@ -1,0 +1,267 @@
+// The target model's verify step on the host operator layer: the layer loop of the reference's
+// Qwen3_5Target::addPrefillLayer run on a decode chunk (runtime/model/QwenTarget.cpp:206-255 GDN mixer,
+// :263-347 attention mixer, :351-368 dense FFN, :384-395 and :490-496 final norm and vocabulary projection;
+// layer order runtime/model/QwenHybridLayout.hpp:132-135), followed by the step's commit
+// (runtime/model/Runtime.cpp:2883-2892: selection, acceptance, path commit).
+//
+// State kept on the device between steps, so a step replays as a CUDA graph: the lane's committed token
+// count, the accepted rows of the previous step's GDN tape, the double-buffered GDN cells (current / next
+// alternate by step parity, as do the tapes: runtime/model/Runtime.cpp:2701-2707).
+#pragma once
+#include <array>
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../ops/GDN.hpp"
+#include "../ops/Glue.hpp"
+#include "../ops/Linear.hpp"
+#include "../ops/PagedAttention.hpp"
+#include "../ops/Sampling.hpp"
+
+namespace splash::b200::model {
+
+constexpr uint32_t kVerifyRows = 16;
+
+struct LayerWeights {
+  bool attention = false;
+  ops::NormWeights attnNorm, ffnNorm;
+  ops::QuantizedSegment inProj, outProj, ffnGate, ffnUp, ffnDown;
+  // GDN
+  Buffer ssmAb, ssmConv, ssmA, ssmDtBias, ssmNorm;
+  std::array<ops::GdnCell, 2> cells;
+  std::array<ops::GdnTape, 2> tapes;
+  // attention
+  Buffer qNorm, kNorm;
+  ops::kv::LayerPages pages;
+};
+
+class QwenTarget {
+ public:
+  explicit QwenTarget(const SbTargetConfig &c);
+
+  // Appends one verify step of `rows` rows to the graph. `parity` selects which GDN cell is current.
+  void encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance);
+
+  const SbTargetConfig &config() const { return cfg_; }
+  bool find(int layer, const std::string &name, Buffer &out) const;
+  std::vector<LayerWeights> &layers() { return layers_; }
+
+  // Bytes one step streams: weights once, the visible INT8 cache, the GDN state in and out.
+  uint64_t weightBytes() const { return weightBytes_; }
+  uint64_t kvBytes(uint32_t visible) const;
+  uint64_t stateBytes() const;
+
+  Buffer tokens, uniforms, committed, pendingRows, results, selected, logits, hidden[2], tree, positions, invFreq, cosine, sine;
+  uint32_t committedHost = 0;  // bound of the device's committed word, for extents and the attention plan
+  uint32_t step = 0;
+
+ private:
+  ops::QuantizedSegment segment(uint32_t n, uint32_t k, uint32_t format);
+  Buffer floats(size_t count) { return Buffer::allocate(count * 4); }
+
+  SbTargetConfig cfg_;
+  ops::GdnShape gdn_;
+  ops::kv::Layout kv_;
+  std::vector<LayerWeights> layers_;
+  ops::EmbeddingWeights embedding_;
+  ops::NormWeights outputNorm_;
+  ops::QuantizedSegment output_;
+  Buffer packed_, gates_, mixed_, queries_, act_, prepared_[2], pageTable_, sampleWorkspace_;
+  uint32_t packedStride_ = 0;
+  uint64_t weightBytes_ = 0;
+};
+
+inline ops::QuantizedSegment QwenTarget::segment(uint32_t n, uint32_t k, uint32_t format) {
+  ops::QuantizedSegment s;
+  s.outputSize = n, s.inputSize = k, s.format = format, s.columnOffset = 0;
+  const size_t bytes = size_t(n) * sb_row_bytes(format, k);
+  if (!bytes) throw std::invalid_argument("QwenTarget: a projection's width is not whole blocks of its format");
+  s.rows = Buffer::allocate(bytes);
+  weightBytes_ += bytes;
+  return s;
+}
+
+inline QwenTarget::QwenTarget(const SbTargetConfig &c) : cfg_(c) {
+  if (!c.layers || !c.hidden || !c.vocab || !c.intermediate || !c.attention_interval)
+    throw std::invalid_argument("QwenTarget: empty configuration");
+  if (c.hidden % 256 || c.intermediate % 256) throw std::invalid_argument("QwenTarget: hidden and intermediate sizes are multiples of 256");
+  gdn_.keyHeads = c.gdn_key_heads, gdn_.valueHeads = c.gdn_value_heads;
+  kv_.kvHeads = c.kv_heads, kv_.headDimension = c.head_dim, kv_.pageTokens = c.page_tokens, kv_.halfScales = c.kv_scale_f16 != 0;
+  const uint32_t H = c.hidden, D = c.head_dim;
+  const uint32_t attnIn = c.q_heads * (c.gated_attention ? 2 * D : D) + 2 * c.kv_heads * D;
+  const uint32_t gdnIn = gdn_.convolutionWidth() + gdn_.valueWidth();
+  const uint32_t pages = (c.max_context + kVerifyRows + c.page_tokens - 1) / c.page_tokens;
+  layers_.resize(c.layers);
+  for (uint32_t l = 0; l < c.layers; ++l) {
+    LayerWeights &w = layers_[l];
+    w.attention = (l + 1) % c.attention_interval == 0;
+    w.attnNorm.buffer = floats(H), w.ffnNorm.buffer = floats(H);
+    weightBytes_ += 2 * size_t(H) * 4;
+    if (w.attention) {
+      ++kv_.attentionLayers;
+      w.inProj = segment(attnIn, H, c.fmt_proj);
+      w.outProj = segment(H, c.q_heads * D, c.fmt_proj);
+      w.qNorm = floats(D), w.kNorm = floats(D);
+      w.pages.pages = pages;
+      w.pages.keys = Buffer::allocate(pages * kv_.dataBytesPerLayerPage());
+      w.pages.values = Buffer::allocate(pages * kv_.dataBytesPerLayerPage());
+      w.pages.keyScales = Buffer::allocate(pages * kv_.scaleBytesPerLayerPage());
+      w.pages.valueScales = Buffer::allocate(pages * kv_.scaleBytesPerLayerPage());
+    } else {
+      w.inProj = segment(gdnIn, H, c.fmt_proj);
+      w.outProj = segment(H, gdn_.valueWidth(), c.fmt_proj);
+      w.ssmAb = floats(size_t(2) * gdn_.valueHeads * H);
+      weightBytes_ += size_t(2) * gdn_.valueHeads * H * 4;
+      w.ssmConv = Buffer::allocate(size_t(gdn_.convolutionWidth()) * 4 * 2);
+      w.ssmA = floats(gdn_.valueHeads), w.ssmDtBias = Buffer::allocate(gdn_.valueHeads * 2), w.ssmNorm = floats(128);
+      for (int i = 0; i < 2; ++i) {
+        w.cells[i].state = Buffer::allocate(gdn_.stateBytes());
+        w.cells[i].convolution = Buffer::allocate(gdn_.convolutionStateBytes());
+        w.tapes[i] = ops::GdnTape::allocate(gdn_, kVerifyRows);
+      }
+    }
+    w.ffnGate = segment(c.intermediate, H, c.fmt_proj);
+    w.ffnUp = segment(c.intermediate, H, c.fmt_proj);
+    w.ffnDown = segment(H, c.intermediate, c.fmt_down);
+  }
+  embedding_.rows = Buffer::allocate(size_t(c.vocab) * sb_row_bytes(c.fmt_embed, H));
+  embedding_.vocabulary = c.vocab, embedding_.width = H, embedding_.format = c.fmt_embed;
+  outputNorm_.buffer = floats(H);
+  output_ = segment(c.vocab, H, c.fmt_head);
+
+  packedStride_ = std::max(attnIn, gdnIn);
+  packed_ = Buffer::allocate(size_t(kVerifyRows) * packedStride_ * 2);
+  gates_ = Buffer::allocate(size_t(kVerifyRows) * 2 * std::max(1u, gdn_.valueHeads) * 2);
+  mixed_ = Buffer::allocate(size_t(kVerifyRows) * std::max(gdn_.valueWidth(), c.q_heads * D) * 2);
+  queries_ = Buffer::allocate(size_t(kVerifyRows) * c.q_heads * D * 2);
+  act_ = Buffer::allocate(size_t(kVerifyRows) * c.intermediate * 2);
+  const uint32_t widest = std::max(std::max(H, c.intermediate), std::max(gdn_.valueWidth(), c.q_heads * D));
+  for (auto &p : prepared_) p = Buffer::allocate(ops::Linear::preparedBytes((widest + 255) / 256 * 256));
+  for (auto &h : hidden) h = Buffer::allocate(size_t(kVerifyRows) * H * 2);
+  logits = Buffer::allocate(size_t(kVerifyRows) * c.vocab * 4);
+  tokens = Buffer::allocate(kVerifyRows * 4), selected = Buffer::allocate(kVerifyRows * 4), results = Buffer::allocate(16);
+  uniforms = Buffer::allocate(80 * 4), committed = Buffer::allocate(4), pendingRows = Buffer::allocate(4);
+  tree = Buffer::allocate(kVerifyRows * 8), positions = Buffer::allocate(kVerifyRows * 4);
+  invFreq = Buffer::allocate(std::max(1u, c.rotary_pairs) * 4);
+  cosine = Buffer::allocate(size_t(kVerifyRows) * std::max(1u, c.rotary_pairs) * 4);
+  sine = Buffer::allocate(size_t(kVerifyRows) * std::max(1u, c.rotary_pairs) * 4);
+  pageTable_ = Buffer::allocate(size_t(pages) * 4);
+  sampleWorkspace_ = Buffer::allocate(ops::Sampling::workspace(kVerifyRows, c.vocab));
+}
+
+inline uint64_t QwenTarget::kvBytes(uint32_t visible) const {
+  return uint64_t(kv_.attentionLayers) * 2 * visible * kv_.kvHeads * (kv_.headDimension + (kv_.halfScales ? 2 : 4));
+}
+inline uint64_t QwenTarget::stateBytes() const {
+  uint64_t gdnLayers = 0;
+  for (const LayerWeights &w : layers_) gdnLayers += !w.attention;
+  return gdnLayers * 2 * gdn_.stateBytes();
+}
+
+inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) const {
+  if (layer < 0) {
+    const std::map<std::string, Buffer> g = {{"token_embd", embedding_.rows}, {"output_norm", outputNorm_.buffer}, {"output", output_.rows},
+                                             {"logits", logits}, {"selected", selected}, {"results", results}, {"hidden", hidden[0]},
+                                             {"hidden1", hidden[1]}, {"tokens", tokens}, {"uniforms", uniforms}, {"committed", committed},
+                                             {"pending_rows", pendingRows}, {"tree", tree}, {"page_table", pageTable_}, {"inv_freq", invFreq},
+                                             {"positions", positions}, {"packed", packed_}, {"mixed", mixed_}, {"act", act_}};
+    auto it = g.find(name);
+    if (it == g.end()) return false;
+    out = it->second;
+    return true;
+  }
+  if (size_t(layer) >= layers_.size()) return false;
+  const LayerWeights &w = layers_[layer];
+  std::map<std::string, Buffer> m = {{"attn_norm", w.attnNorm.buffer}, {"ffn_norm", w.ffnNorm.buffer}, {"in_proj", w.inProj.rows},
+                                     {"out_proj", w.outProj.rows}, {"ffn_gate", w.ffnGate.rows}, {"ffn_up", w.ffnUp.rows},
+                                     {"ffn_down", w.ffnDown.rows}};
+  if (w.attention) {
+    m.insert({{"q_norm", w.qNorm}, {"k_norm", w.kNorm}, {"kv_k", w.pages.keys}, {"kv_v", w.pages.values},
+              {"kv_ks", w.pages.keyScales}, {"kv_vs", w.pages.valueScales}});
+  } else {
+    m.insert({{"ssm_ab", w.ssmAb}, {"ssm_conv", w.ssmConv}, {"ssm_a", w.ssmA}, {"ssm_dt_bias", w.ssmDtBias}, {"ssm_norm", w.ssmNorm},
+              {"state0", w.cells[0].state}, {"state1", w.cells[1].state}, {"conv0", w.cells[0].convolution},
+              {"conv1", w.cells[1].convolution}});
+    for (int i = 0; i < 2; ++i) {
+      const std::string s = std::to_string(i);
+      m.insert({{"tape_inputs" + s, w.tapes[i].inputs}, {"tape_k" + s, w.tapes[i].keys}, {"tape_v" + s, w.tapes[i].values},
+                {"tape_beta" + s, w.tapes[i].beta}, {"tape_decay" + s, w.tapes[i].decay}});
+    }
+  }
+  auto it = m.find(name);
+  if (it == m.end()) return false;
+  out = it->second;
+  return true;
+}
+
+// Launched before and after the operator sequence (sb_target.cu).
+void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer &tree, const Buffer &positions, uint32_t rows);
+void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, bool advance);
+
+inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance) {
+  using namespace ops;
+  if (rows < 1 || rows > kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: 1 to 16 rows");
+  if (committedHost + rows > cfg_.max_context + kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: past the context bound");
+  const SbTargetConfig &c = cfg_;
+  const uint32_t H = c.hidden, D = c.head_dim;
+  launchStepBegin(graph, committed, tree, positions, rows);
+  if (c.rotary_pairs) RoPE::addTreeTables(graph, positions, invFreq, cosine, sine, rows, 1.0f, c.rotary_pairs);
+  Embedding::add(graph, tokens, embedding_, hidden[0], rows, H);
+  uint32_t cur = 0;
+  for (LayerWeights &w : layers_) {
+    // mixer: h += mixer(norm(h))
+    PreparedInput in = Linear::prepare(graph, hidden[cur], rows, H, H, &w.attnNorm.buffer, w.inProj.format, prepared_[0]);
+    Projection inProj{w.inProj.outputSize, H, Destination::BFloat16, {w.inProj}};
+    LinearBuffers inB{Buffer(), packed_, Buffer(), H, packedStride_};
+    Linear::add(graph, inB, inProj, Linear::plan(inProj, rows, Epilogue::None), in);
+    uint32_t mixedWidth;
+    if (w.attention) {
+      PagedAttention::addProjection(graph, kv_, w.pages, packed_, packedStride_, w.qNorm, w.kNorm, cosine, sine, pageTable_, queries_, rows,
+                                    c.q_heads, c.gated_attention != 0, c.rotary_pairs, committedHost, &committed);
+      mixedWidth = c.q_heads * D;
+      PagedAttention::addAttention(graph, kv_, w.pages, queries_, packed_, packedStride_, pageTable_, nullptr, mixed_, mixedWidth, rows,
+                                   c.q_heads, c.gated_attention != 0, committedHost, &committed);
+    } else {
+      Linear::addFloat(graph, w.ssmAb, hidden[cur], H, rows, 2 * gdn_.valueHeads, H, gates_, 2 * gdn_.valueHeads, Destination::BFloat16,
+                       &w.attnNorm.buffer);
+      GdnDecodeBuffers g;
+      g.packed = packed_, g.gates = gates_, g.convolutionWeights = w.ssmConv, g.decayWeights = w.ssmA, g.timeBias = w.ssmDtBias;
+      g.mixerNorm = w.ssmNorm, g.current = w.cells[parity], g.next = w.cells[parity ^ 1];
+      g.pendingTape = &w.tapes[parity ^ 1], g.stepTape = &w.tapes[parity];
+      mixedWidth = gdn_.valueWidth();
+      g.hidden = mixed_, g.pendingRowsDevice = &pendingRows, g.packedStride = packedStride_, g.hiddenStride = mixedWidth;
+      g.tiledHeads = c.tiled_heads != 0;
+      GDN::addDecode(graph, g, gdn_, rows);
+    }
+    PreparedInput mixedIn = Linear::prepare(graph, mixed_, rows, mixedWidth, mixedWidth, nullptr, w.outProj.format, prepared_[1]);
+    Projection outProj{H, mixedWidth, Destination::BFloat16, {w.outProj}};
+    LinearBuffers outB{Buffer(), hidden[cur ^ 1], hidden[cur], mixedWidth, H};
+    Linear::add(graph, outB, outProj, Linear::plan(outProj, rows, Epilogue::Residual), mixedIn);
+    cur ^= 1;
+    // FFN: h += down(silu(gate(norm(h))) * up(norm(h)))
+    PreparedInput ffnIn = Linear::prepare(graph, hidden[cur], rows, H, H, &w.ffnNorm.buffer, w.ffnGate.format, prepared_[0]);
+    Linear::addGateUp(graph, act_, c.intermediate, w.ffnGate, w.ffnUp, rows, ffnIn);
+    PreparedInput actIn = Linear::prepare(graph, act_, rows, c.intermediate, c.intermediate, nullptr, w.ffnDown.format, prepared_[1]);
+    Projection down{H, c.intermediate, Destination::BFloat16, {w.ffnDown}};
+    LinearBuffers downB{Buffer(), hidden[cur ^ 1], hidden[cur], c.intermediate, H};
+    Linear::add(graph, downB, down, Linear::plan(down, rows, Epilogue::Residual), actIn);
+    cur ^= 1;
+  }
+  // logits of every row
+  PreparedInput headIn = Linear::prepare(graph, hidden[cur], rows, H, H, &outputNorm_.buffer, output_.format, prepared_[0]);
+  Projection head{c.vocab, H, Destination::Float32, {output_}};
+  LinearBuffers headB{Buffer(), logits, Buffer(), H, c.vocab};
+  Linear::add(graph, headB, head, Linear::plan(head, rows, Epilogue::None), headIn);
+  // selection, acceptance, commit
+  SamplingBuffers sb;
+  sb.logits = logits, sb.inputTokens = tokens, sb.uniforms = uniforms, sb.selected = selected, sb.workspace = sampleWorkspace_;
+  sb.logitStride = c.vocab;
+  Sampling::addVerify(graph, SamplingPolicy{temperature}, sb, rows, c.vocab);
+  AcceptanceBuffers ab;
+  ab.inputTokens = tokens, ab.treeRows = tree, ab.outputTokens = selected, ab.results = results;
+  Sampling::addAcceptance(graph, ab, rows, kVerifyRows);
+  launchStepEnd(graph, results, committed, pendingRows, advance);
+}
+
+}  // namespace splash::b200::model

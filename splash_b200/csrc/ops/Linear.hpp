@@ -1,0 +1,133 @@
+// ops::Linear of the reference (runtime/ops/Linear.hpp:73-347, runtime/ops/LinearGguf.cpp:212-362) on
+// the B200 kernels: a projection's plan (k-slices, CTAs, ring), its prepared input, and the dispatch
+// with an epilogue. A projection is one or more column segments of native GGUF rows
+// (runtime/ops/Weights.hpp:108-225); segments of quantized rows run sb_linear, F32 rows sb_linear_f32.
+#pragma once
+#include <vector>
+
+#include "Backend.hpp"
+
+namespace splash::b200::ops {
+
+enum class Epilogue { None = SB_EPILOGUE_NONE, Residual = SB_EPILOGUE_RESIDUAL, UpWithGate = SB_EPILOGUE_UP_WITH_GATE,
+                      GateUp = SB_EPILOGUE_GATE_UP };
+enum class Destination { BFloat16, Float32 };
+
+// One tensor's rows: `outputSize` rows of `inputSize` weights in `format`, written at `columnOffset`.
+struct QuantizedSegment {
+  Buffer rows;
+  uint32_t outputSize = 0, inputSize = 0, columnOffset = 0, format = SB_FMT_Q4K;
+};
+
+struct Projection {
+  uint32_t outputSize = 0, inputSize = 0;
+  Destination destination = Destination::BFloat16;
+  std::vector<QuantizedSegment> segments;
+};
+
+// The input of a projection converted once for a format's fragment layout; several projections of the
+// same input share it (PreparedInput, runtime/ops/Linear.hpp:287-347).
+struct PreparedInput {
+  Buffer buffer;
+  uint32_t format = SB_FMT_Q4K;  // layout family: Q4_K's, or Q6_K / Q8_0's
+  uint32_t inputSize = 0;
+};
+
+struct LinearBuffers {
+  Buffer input;     // bf16 [rows, inputStride]
+  Buffer output;    // bf16 or fp32 [rows, outputStride]
+  Buffer residual;  // bf16 [rows, outputStride]: Residual's addend or UpWithGate's gate
+  uint32_t inputStride = 0, outputStride = 0;
+};
+
+struct LinearPlan {
+  SbLinearPlan kernel{};
+  uint32_t rows = 0;
+  Epilogue epilogue = Epilogue::None;
+};
+
+class Linear {
+ public:
+  static LinearPlan plan(const Projection &p, uint32_t rows, Epilogue epilogue) {
+    if (p.segments.empty()) throw std::invalid_argument("Linear::plan: a projection without segments");
+    LinearPlan plan;
+    plan.rows = rows;
+    plan.epilogue = epilogue;
+    const QuantizedSegment &s = p.segments.front();
+    if (s.format != SB_FMT_F32) check(sb_linear_plan(s.format, s.outputSize, s.inputSize, rows, uint32_t(epilogue), &plan.kernel));
+    return plan;
+  }
+
+  static uint64_t preparedBytes(uint32_t inputSize) { return sb_linear_prepared_bytes(inputSize); }
+
+  // Converts `input` (optionally through an RMSNorm with fp32 weights) for projections of `format`.
+  static PreparedInput prepare(CommandGraph &graph, const Buffer &input, uint32_t rows, uint32_t inputSize,
+                               uint32_t inputStride, const Buffer *normWeight, uint32_t format, const Buffer &scratch) {
+    requireBytes(input, size_t(rows - 1) * inputStride * 2 + size_t(inputSize) * 2, "Linear::prepare input");
+    requireBytes(scratch, preparedBytes(inputSize), "Linear::prepare scratch");
+    if (normWeight) requireBytes(*normWeight, size_t(inputSize) * 4, "Linear::prepare norm weight");
+    check(sb_linear_prepare(graph.stream, input.as(), rows, inputSize, inputStride, normWeight ? normWeight->as() : nullptr,
+                            format, scratch.as(), graph.pdl ? SB_LINEAR_PDL : 0));
+    ++graph.launches;
+    return {scratch, format == SB_FMT_Q4K ? uint32_t(SB_FMT_Q4K) : uint32_t(SB_FMT_Q6K), inputSize};
+  }
+
+  // One projection over a prepared input; every segment writes its columns of the output.
+  static void add(CommandGraph &graph, const LinearBuffers &b, const Projection &p, const LinearPlan &plan,
+                  const PreparedInput &prepared) {
+    const uint32_t esize = p.destination == Destination::Float32 ? 4 : 2;
+    requireBytes(b.output, (size_t(plan.rows - 1) * b.outputStride + p.outputSize) * esize, "Linear::add output");
+    if (plan.epilogue == Epilogue::Residual || plan.epilogue == Epilogue::UpWithGate)
+      requireBytes(b.residual, (size_t(plan.rows - 1) * b.outputStride + p.outputSize) * 2, "Linear::add residual");
+    if (prepared.inputSize != p.inputSize) throw std::invalid_argument("Linear::add: prepared input of another width");
+    for (const QuantizedSegment &s : p.segments) {
+      if (s.inputSize != p.inputSize || s.columnOffset + s.outputSize > p.outputSize)
+        throw std::invalid_argument("Linear::add: a segment outside its projection");
+      requireBytes(s.rows, size_t(s.outputSize) * sb_row_bytes(s.format, s.inputSize), "Linear::add segment rows");
+      const bool q4 = s.format == SB_FMT_Q4K;
+      if (q4 != (prepared.format == SB_FMT_Q4K)) throw std::invalid_argument("Linear::add: prepared input of another layout");
+      SbLinearArgs a{};
+      a.weights = s.rows.as();
+      a.prepared = prepared.buffer.as();
+      a.aux = b.residual ? b.residual.as<uint8_t>() + size_t(s.columnOffset) * 2 : nullptr;
+      a.out = b.output.as<uint8_t>() + size_t(s.columnOffset) * esize;
+      a.format = s.format, a.n = s.outputSize, a.k = s.inputSize, a.rows = plan.rows;
+      a.aux_stride = a.aux ? b.outputStride : 0, a.out_stride = b.outputStride;
+      a.epilogue = uint32_t(plan.epilogue), a.out_f32 = p.destination == Destination::Float32;
+      a.flags = graph.pdl ? SB_LINEAR_PDL : 0;
+      check(sb_linear(graph.stream, &a));
+      ++graph.launches;
+    }
+  }
+
+  // SwiGLU's first half in one pass over the gate and up tensors: bf16(bf16(up) * silu(bf16(gate)))
+  // (Linear::addSwiGlu, runtime/ops/Linear.cpp:290-308).
+  static void addGateUp(CommandGraph &graph, const Buffer &output, uint32_t outputStride, const QuantizedSegment &gate,
+                        const QuantizedSegment &up, uint32_t rows, const PreparedInput &prepared) {
+    if (gate.format != up.format || gate.outputSize != up.outputSize || gate.inputSize != up.inputSize)
+      throw std::invalid_argument("Linear::addGateUp: gate and up tensors differ in shape or format");
+    requireBytes(output, (size_t(rows - 1) * outputStride + gate.outputSize) * 2, "Linear::addGateUp output");
+    requireBytes(gate.rows, size_t(gate.outputSize) * sb_row_bytes(gate.format, gate.inputSize), "Linear::addGateUp gate");
+    requireBytes(up.rows, size_t(up.outputSize) * sb_row_bytes(up.format, up.inputSize), "Linear::addGateUp up");
+    SbLinearArgs a{};
+    a.weights = gate.rows.as(), a.weights2 = up.rows.as(), a.prepared = prepared.buffer.as(), a.out = output.as();
+    a.format = gate.format, a.n = gate.outputSize, a.k = gate.inputSize, a.rows = rows, a.out_stride = outputStride;
+    a.epilogue = SB_EPILOGUE_GATE_UP, a.flags = graph.pdl ? SB_LINEAR_PDL : 0;
+    check(sb_linear(graph.stream, &a));
+    ++graph.launches;
+  }
+
+  // fp32 rows (GDN alpha/beta, MoE router) over the bf16 input, optionally through the same RMSNorm.
+  static void addFloat(CommandGraph &graph, const Buffer &weights, const Buffer &input, uint32_t inputStride, uint32_t rows,
+                       uint32_t outputSize, uint32_t inputSize, const Buffer &output, uint32_t outputStride, Destination d,
+                       const Buffer *normWeight) {
+    requireBytes(weights, size_t(outputSize) * inputSize * 4, "Linear::addFloat weights");
+    requireBytes(input, size_t(rows - 1) * inputStride * 2 + size_t(inputSize) * 2, "Linear::addFloat input");
+    requireBytes(output, (size_t(rows - 1) * outputStride + outputSize) * (d == Destination::Float32 ? 4 : 2), "Linear::addFloat output");
+    check(sb_linear_f32(graph.stream, weights.as<float>(), input.as(), rows, outputSize, inputSize, inputStride, output.as(),
+                        outputStride, d == Destination::Float32, normWeight ? normWeight->as() : nullptr));
+    ++graph.launches;
+  }
+};
+
+}  // namespace splash::b200::ops

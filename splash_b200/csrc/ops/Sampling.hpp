@@ -1,0 +1,57 @@
+// ops::Sampling of the reference (runtime/ops/Sampling.hpp:58-216, runtime/ops/Sampling.cpp:198-356) on
+// the B200 kernels: the verify rows' selection and the lane's acceptance.
+#pragma once
+#include "Backend.hpp"
+
+namespace splash::b200::ops {
+
+struct SamplingPolicy {
+  float temperature = 0.0f;  // 0: greedy
+};
+
+struct SamplingBuffers {
+  Buffer logits;       // fp32 [rows, logitStride]
+  Buffer inputTokens;  // u32 [rows]
+  Buffer uniforms;     // fp32 [80]: row draws then child tests (runtime/metal/abi/Sampling.h:12-31)
+  Buffer selected;     // u32 [rows]
+  Buffer workspace;
+  uint32_t logitStride = 0;
+};
+
+struct AcceptanceBuffers {
+  Buffer inputTokens, treeRows, outputTokens, results, stopTokens;
+  uint32_t stopTokenCount = 0;
+};
+
+class Sampling {
+ public:
+  static size_t workspace(uint32_t rows, uint32_t vocabulary) { return sb_sample_workspace_bytes(rows, vocabulary); }
+
+  static void addVerify(CommandGraph &graph, const SamplingPolicy &policy, const SamplingBuffers &b, uint32_t rows, uint32_t vocabulary) {
+    requireBytes(b.logits, (size_t(rows - 1) * b.logitStride + vocabulary) * 4, "Sampling::addVerify logits");
+    requireBytes(b.inputTokens, size_t(rows) * 4, "Sampling::addVerify input tokens");
+    requireBytes(b.selected, size_t(rows) * 4, "Sampling::addVerify selected");
+    if (policy.temperature > 0.0f) {
+      requireBytes(b.uniforms, 80 * 4, "Sampling::addVerify uniforms");
+      requireBytes(b.workspace, workspace(rows, vocabulary), "Sampling::addVerify workspace");
+    }
+    SbSampleArgs a{b.logits.as<float>(), b.inputTokens.as<uint32_t>(), policy.temperature > 0.0f ? b.uniforms.as<float>() : nullptr,
+                   b.selected.as<uint32_t>(), b.workspace ? b.workspace.as<float>() : nullptr, rows, vocabulary, b.logitStride,
+                   policy.temperature};
+    check(sb_sample_verify(graph.stream, &a));
+    ++graph.launches;
+  }
+
+  static void addAcceptance(CommandGraph &graph, const AcceptanceBuffers &b, uint32_t rows, uint32_t maximumRetained) {
+    requireBytes(b.inputTokens, size_t(rows) * 4, "Sampling::addAcceptance input tokens");
+    requireBytes(b.treeRows, size_t(rows) * 8, "Sampling::addAcceptance tree rows");
+    requireBytes(b.outputTokens, size_t(rows) * 4, "Sampling::addAcceptance output tokens");
+    requireBytes(b.results, 16, "Sampling::addAcceptance results");
+    SbAcceptArgs a{b.inputTokens.as<uint32_t>(), b.treeRows.as(), b.outputTokens.as<uint32_t>(), b.results.as<uint32_t>(),
+                   b.stopTokenCount ? b.stopTokens.as<uint32_t>() : nullptr, rows, maximumRetained, b.stopTokenCount};
+    check(sb_accept(graph.stream, &a));
+    ++graph.launches;
+  }
+};
+
+}  // namespace splash::b200::ops

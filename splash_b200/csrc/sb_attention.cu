@@ -39,6 +39,7 @@ struct AttnParams {
   float *partials;     // [kv_head][split][fused][D]
   float *stats;        // [kv_head][split][fused][2]
   uint32_t *counters;  // [kv_head]
+  const uint32_t *committed_dev;
   uint32_t rows, q_heads, group, gated, qkv_stride, out_stride, committed, splits, chunks_per_split, fused;
 };
 
@@ -83,7 +84,8 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnPa
   const uint32_t split = blockIdx.x, kvh = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t g = lane >> 2, t = lane & 3;
   const uint32_t F = p.fused, G = p.group;
-  const uint32_t visible = p.committed + p.rows;
+  const uint32_t committed = p.committed_dev ? min(*p.committed_dev, p.committed) : p.committed;
+  const uint32_t visible = committed + p.rows;
   const uint32_t chunks = (visible + kChunk - 1) / kChunk;
   const uint32_t c_begin = split * p.chunks_per_split, c_end = min(chunks, c_begin + p.chunks_per_split);
 
@@ -119,7 +121,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnPa
 #pragma unroll
   for (int hrow = 0; hrow < 2; ++hrow) {
     const uint32_t f = warp * 16 + g + 8 * hrow, row = min(f / G, p.rows - 1);
-    limit[hrow] = p.committed + row + 1;  // tokens below this are visible to a chain row
+    limit[hrow] = committed + row + 1;  // tokens below this are visible to a chain row
     anc[hrow] = 0xffffffffu;
     if (p.tree) {
       limit[hrow] = visible;
@@ -217,7 +219,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnPa
         const uint32_t tl = 8 * n + 2 * t + (c & 1), tk = tok0 + tl;
         const int hrow = c >> 1;
         bool seen = tk < limit[hrow];
-        if (p.tree && tk >= p.committed) seen = seen && ((anc[hrow] >> min(tk - p.committed, 31u)) & 1u);
+        if (p.tree && tk >= committed) seen = seen && ((anc[hrow] >> min(tk - committed, 31u)) & 1u);
         const float sc = seen ? s_acc[n][c] * ks_s[tl] : -INFINITY;
         s_acc[n][c] = sc;
         mx[hrow] = fmaxf(mx[hrow], sc);
@@ -367,6 +369,7 @@ extern "C" int sb_attn_verify(void *stream, const SbAttnArgs *a) {
   p.partials = cx.attn_workspace;
   p.stats = cx.attn_workspace + size_t(c.kv_heads) * splits * kMaxFused * D;
   p.counters = cx.attn_counters;
+  p.committed_dev = a->committed_dev;
   p.rows = a->rows, p.q_heads = a->q_heads, p.group = group, p.gated = a->gated, p.qkv_stride = a->qkv_stride;
   p.out_stride = a->out_stride, p.committed = a->committed, p.splits = splits, p.chunks_per_split = cps, p.fused = fused;
   const size_t smem = size_t(kMaxFused + 2 * kChunk) * (D + 8) * 2 + 2 * kChunk * sizeof(float);

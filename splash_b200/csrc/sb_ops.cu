@@ -130,6 +130,7 @@ struct StoreParams {
   const uint32_t *page_table;
   uint16_t *queries;
   SbKvLayer cache;
+  const uint32_t *committed_dev;
   uint32_t rows, q_heads, gated, pairs, qkv_stride, committed;
 };
 
@@ -192,7 +193,7 @@ __global__ void __launch_bounds__(D) attn_store_kernel(const StoreParams p) {
   km = 0.0f, vm = 0.0f;
 #pragma unroll
   for (int w = 0; w < W; ++w) km = fmaxf(km, part[w]), vm = fmaxf(vm, part2[w]);
-  const uint32_t tok = p.committed + row, page = p.page_table[tok / p.cache.page_tokens], pt = tok % p.cache.page_tokens;
+  const uint32_t tok = (p.committed_dev ? *p.committed_dev : p.committed) + row, page = p.page_table[tok / p.cache.page_tokens], pt = tok % p.cache.page_tokens;
   const size_t slot = (size_t(page) * p.cache.kv_heads + kvh) * p.cache.page_tokens + pt;
   static_cast<int8_t *>(p.cache.k)[slot * D + d] = kv_code(r, km);
   static_cast<int8_t *>(p.cache.v)[slot * D + d] = kv_code(v, vm);
@@ -461,7 +462,7 @@ int sb_attn_store(void *stream, const SbAttnStoreArgs *a) {
   SB_REQUIRE(a->qkv_stride >= a->q_heads * qs + 2 * a->cache.kv_heads * D, "sb_attn_store: qkv_stride %u below the packed row", a->qkv_stride);
   SB_REQUIRE(2 * a->pairs <= D && (a->pairs == 0 || (a->cos_tab && a->sin_tab)), "sb_attn_store: %u rotary pairs exceed the head, or no tables", a->pairs);
   StoreParams p{static_cast<const uint16_t *>(a->qkv), a->q_norm, a->k_norm, a->cos_tab, a->sin_tab, a->page_table,
-                static_cast<uint16_t *>(a->queries), a->cache, a->rows, a->q_heads, a->gated, a->pairs, a->qkv_stride, a->committed};
+                static_cast<uint16_t *>(a->queries), a->cache, a->committed_dev, a->rows, a->q_heads, a->gated, a->pairs, a->qkv_stride, a->committed};
   const dim3 grid(a->q_heads + a->cache.kv_heads, a->rows);
   if (D == 256) return launch(attn_store_kernel<256>, grid, dim3(256), as_stream(stream), p);
   return launch(attn_store_kernel<128>, grid, dim3(128), as_stream(stream), p);

@@ -1,0 +1,366 @@
+// C ABI of the target model's verify step (include/splash_b200.h, "the target model's verify step"):
+// creation, tensor access, seeded synthetic weights written on the device, and the step itself, eager
+// or replayed as a CUDA graph per step parity.
+#include <map>
+#include <memory>
+#include <tuple>
+
+#include "model/QwenTarget.hpp"
+#include "sb_internal.h"
+#include "sb_ptx.cuh"
+
+namespace sb {
+
+// ---- step bookkeeping kernels ----
+// positions[row] = committed + depth(row) and the chain's tree rows (parent = row - 1).
+__global__ void step_begin_kernel(const uint32_t *committed, uint2 *tree, uint32_t *positions, uint32_t rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t r = threadIdx.x;
+  if (r >= rows) return;
+  tree[r] = make_uint2((2u << r) - 1u, (r ? r - 1 : 0) | (r << 16));
+  positions[r] = *committed + r;
+}
+// The lane's commit: the retained rows become history; the next step folds them into the GDN state.
+__global__ void step_end_kernel(const uint32_t *results, uint32_t *committed, uint32_t *pending_rows, uint32_t advance) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x != 0) return;
+  if (advance) {
+    *committed += results[0];
+    *pending_rows = results[0];
+  } else {
+    *pending_rows = 0;
+  }
+}
+
+// ---- seeded synthetic data ----
+__device__ __forceinline__ uint64_t mix64(uint64_t x) {
+  x += 0x9E3779B97F4A7C15ull;
+  x = (x ^ (x >> 30)) * 0xBF58476D1CE4E5B9ull;
+  x = (x ^ (x >> 27)) * 0x94D049BB133111EBull;
+  return x ^ (x >> 31);
+}
+__device__ __forceinline__ float uniform01(uint64_t seed, uint64_t i) { return float(mix64(seed ^ mix64(i)) >> 40) * (1.0f / 16777216.0f); }
+__device__ __forceinline__ float normal01(uint64_t seed, uint64_t i) {
+  const float u1 = fmaxf(uniform01(seed, 2 * i), 1e-7f), u2 = uniform01(seed, 2 * i + 1);
+  return sqrtf(-2.0f * logf(u1)) * cospif(2.0f * u2);
+}
+enum FillKind { kBytes, kF32Normal, kF32Uniform, kBf16Normal, kF16Uniform, kF32NegExp, kInt8 };
+__global__ void fill_kernel(int kind, void *p, uint64_t count, uint64_t seed, float a, float b) {
+  for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < count; i += uint64_t(gridDim.x) * blockDim.x) {
+    switch (kind) {
+      case kBytes: static_cast<uint32_t *>(p)[i] = uint32_t(mix64(seed ^ mix64(i))); break;  // count in words
+      case kF32Normal: static_cast<float *>(p)[i] = a + b * normal01(seed, i); break;
+      case kF32Uniform: static_cast<float *>(p)[i] = a + (b - a) * uniform01(seed, i); break;
+      case kBf16Normal: static_cast<uint16_t *>(p)[i] = float_to_bf16_bits(a + b * normal01(seed, i)); break;
+      case kF16Uniform: static_cast<__half *>(p)[i] = __float2half_rn(a + (b - a) * uniform01(seed, i)); break;
+      case kF32NegExp: static_cast<float *>(p)[i] = -expf(a + (b - a) * uniform01(seed, i)); break;
+      case kInt8: static_cast<int8_t *>(p)[i] = int8_t(int(mix64(seed ^ mix64(i)) % 255) - 127); break;
+    }
+  }
+}
+// The half scale fields of native blocks whose other bytes are already random: Q4_K d and dmin =
+// |N(0,1)| * 1e-3 (the benchmark configuration's recipe); Q6_K d in U(2e-5, 1e-4) and Q8_0 d in
+// U(5e-4, 4e-3) (the ranges of the reference's kernel tests, dev/tests/engine/GgufFormatReference.hpp:292-324).
+__global__ void scale_fields_kernel(uint32_t format, uint8_t *p, uint64_t blocks, uint64_t seed) {
+  for (uint64_t i = blockIdx.x * uint64_t(blockDim.x) + threadIdx.x; i < blocks; i += uint64_t(gridDim.x) * blockDim.x) {
+    if (format == SB_FMT_Q4K) {
+      __half *h = reinterpret_cast<__half *>(p + i * 144);
+      h[0] = __float2half_rn(fabsf(normal01(seed, 2 * i)) * 1e-3f);
+      h[1] = __float2half_rn(fabsf(normal01(seed, 2 * i + 1)) * 1e-3f);
+    } else if (format == SB_FMT_Q6K) {
+      *reinterpret_cast<__half *>(p + i * 210 + 208) = __float2half_rn(2e-5f + 8e-5f * uniform01(seed, i));
+    } else if (format == SB_FMT_Q80) {
+      *reinterpret_cast<__half *>(p + i * 34) = __float2half_rn(5e-4f + 3.5e-3f * uniform01(seed, i));
+    }
+  }
+}
+__global__ void iota_kernel(uint32_t *p, uint32_t n) {
+  const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) p[i] = i;
+}
+__global__ void inv_freq_kernel(float *p, uint32_t pairs, float theta) {
+  const uint32_t i = threadIdx.x;
+  if (i < pairs) p[i] = powf(theta, -float(i) / float(pairs));
+}
+
+static int fill(int kind, const splash::b200::Buffer &b, uint64_t count, uint64_t seed, float a0, float a1) {
+  if (!b || !count) return SB_OK;
+  const uint32_t blocks = uint32_t(std::min<uint64_t>((count + 255) / 256, 148 * 32));
+  fill_kernel<<<blocks, 256>>>(kind, b.as(), count, seed, a0, a1);
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+static int fill_rows(const splash::b200::ops::QuantizedSegment &s, uint64_t seed) {
+  const uint64_t bytes = uint64_t(s.outputSize) * sb_row_bytes(s.format, s.inputSize);
+  int st = fill(kBytes, s.rows, (bytes + 3) / 4, seed, 0, 0);
+  if (st != SB_OK) return st;
+  FmtInfo fi;
+  fmt_info(s.format, fi);
+  const uint64_t blocks = bytes / fi.block_bytes;
+  scale_fields_kernel<<<uint32_t(std::min<uint64_t>((blocks + 255) / 256, 148 * 32)), 256>>>(s.format, s.rows.as<uint8_t>(), blocks, seed ^ 0x5ca1eull);
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
+
+struct Target {
+  std::unique_ptr<splash::b200::model::QwenTarget> model;
+  std::map<std::tuple<uint32_t, uint32_t, uint32_t, uint32_t, uint32_t>, cudaGraphExec_t> graphs;  // rows, temperature bits, parity, advance, bound
+  uint32_t launches = 0;
+  uint32_t *results_pinned = nullptr;  // 4 + 16 words
+};
+
+}  // namespace sb
+
+namespace splash::b200::model {
+void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer &tree, const Buffer &positions, uint32_t rows) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1), cfg.blockDim = dim3(32), cfg.stream = sb::as_stream(graph.stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = graph.pdl ? 1 : 0;
+  if (cudaLaunchKernelEx(&cfg, sb::step_begin_kernel, static_cast<const uint32_t *>(committed.as<uint32_t>()), tree.as<uint2>(),
+                         positions.as<uint32_t>(), rows) != cudaSuccess)
+    throw BackendError(SB_ERR_CUDA, "step_begin launch failed");
+  ++graph.launches;
+}
+void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, bool advance) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1), cfg.blockDim = dim3(32), cfg.stream = sb::as_stream(graph.stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = graph.pdl ? 1 : 0;
+  if (cudaLaunchKernelEx(&cfg, sb::step_end_kernel, static_cast<const uint32_t *>(results.as<uint32_t>()), committed.as<uint32_t>(),
+                         pendingRows.as<uint32_t>(), advance ? 1u : 0u) != cudaSuccess)
+    throw BackendError(SB_ERR_CUDA, "step_end launch failed");
+  ++graph.launches;
+}
+}  // namespace splash::b200::model
+
+using namespace sb;
+using splash::b200::Buffer;
+using splash::b200::CommandGraph;
+using splash::b200::model::QwenTarget;
+
+// Runs `body`, mapping the operator layer's exceptions to status codes.
+template <class F> static int guarded(F body) {
+  try {
+    return body();
+  } catch (const std::invalid_argument &e) {
+    return fail(SB_ERR_INVALID, "%s", e.what());
+  } catch (const splash::b200::BackendError &e) {
+    return fail(e.status(), "%s", e.what());
+  } catch (const std::exception &e) {
+    return fail(SB_ERR_CUDA, "%s", e.what());
+  }
+}
+
+extern "C" {
+
+int sb_target_create(const SbTargetConfig *config, void **out_target) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(config && out_target, "sb_target_create: null pointer");
+  return guarded([&] {
+    auto t = std::make_unique<Target>();
+    t->model = std::make_unique<QwenTarget>(*config);
+    SB_CUDA(cudaMallocHost(&t->results_pinned, 20 * sizeof(uint32_t)));
+    QwenTarget &m = *t->model;
+    Buffer table;
+    m.find(-1, "page_table", table);
+    const uint32_t pages = uint32_t(table.bytes() / 4);
+    iota_kernel<<<(pages + 255) / 256, 256>>>(table.as<uint32_t>(), pages);
+    if (config->rotary_pairs) inv_freq_kernel<<<1, 256>>>(m.invFreq.as<float>(), config->rotary_pairs, config->rope_theta);
+    SB_CUDA(cudaMemset(m.committed.as(), 0, 4));
+    SB_CUDA(cudaMemset(m.pendingRows.as(), 0, 4));
+    SB_CUDA(cudaMemset(m.uniforms.as(), 0, 80 * 4));
+    SB_CUDA(cudaMemset(m.tokens.as(), 0, 64));
+    SB_CUDA(cudaDeviceSynchronize());
+    *out_target = t.release();
+    return int(SB_OK);
+  });
+}
+
+int sb_target_destroy(void *target) {
+  SB_NEED_DEVICE();
+  Target *t = static_cast<Target *>(target);
+  if (!t) return SB_OK;
+  cudaDeviceSynchronize();
+  for (auto &g : t->graphs) cudaGraphExecDestroy(g.second);
+  if (t->results_pinned) cudaFreeHost(t->results_pinned);
+  delete t;
+  return SB_OK;
+}
+
+int sb_target_tensor(void *target, int layer, const char *name, void **out_dev, uint64_t *out_bytes) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target && name && out_dev && out_bytes, "sb_target_tensor: null pointer");
+  Buffer b;
+  SB_REQUIRE(static_cast<Target *>(target)->model->find(layer, name, b), "sb_target_tensor: no tensor '%s' in layer %d", name, layer);
+  *out_dev = b.as();
+  *out_bytes = b.bytes();
+  return SB_OK;
+}
+
+int sb_target_reset(void *target, uint32_t committed) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target, "sb_target_reset: null target");
+  QwenTarget &m = *static_cast<Target *>(target)->model;
+  SB_REQUIRE(committed <= m.config().max_context, "sb_target_reset: %u tokens exceed the context bound %u", committed, m.config().max_context);
+  SB_CUDA(cudaDeviceSynchronize());
+  SB_CUDA(cudaMemcpy(m.committed.as(), &committed, 4, cudaMemcpyHostToDevice));
+  SB_CUDA(cudaMemset(m.pendingRows.as(), 0, 4));
+  m.committedHost = committed;
+  m.step = 0;
+  return SB_OK;
+}
+
+int sb_target_randomize(void *target, uint64_t seed, uint32_t committed) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target, "sb_target_randomize: null target");
+  QwenTarget &m = *static_cast<Target *>(target)->model;
+  const SbTargetConfig &c = m.config();
+  return guarded([&] {
+    uint64_t s = seed * 1000003ull;
+    auto next = [&] { return s += 0x632BE59BD9B4E019ull; };
+    int st;
+#define SB_TRY(x) if ((st = (x)) != SB_OK) return st
+    for (auto &w : m.layers()) {
+      SB_TRY(fill(kF32Normal, w.attnNorm.buffer, c.hidden, next(), 1.0f, 0.1f));
+      SB_TRY(fill(kF32Normal, w.ffnNorm.buffer, c.hidden, next(), 1.0f, 0.1f));
+      SB_TRY(fill_rows(w.inProj, next()));
+      SB_TRY(fill_rows(w.outProj, next()));
+      SB_TRY(fill_rows(w.ffnGate, next()));
+      SB_TRY(fill_rows(w.ffnUp, next()));
+      SB_TRY(fill_rows(w.ffnDown, next()));
+      if (w.attention) {
+        SB_TRY(fill(kF32Normal, w.qNorm, c.head_dim, next(), 1.0f, 0.1f));
+        SB_TRY(fill(kF32Normal, w.kNorm, c.head_dim, next(), 1.0f, 0.1f));
+        SB_TRY(fill(kInt8, w.pages.keys, w.pages.keys.bytes(), next(), 0, 0));
+        SB_TRY(fill(kInt8, w.pages.values, w.pages.values.bytes(), next(), 0, 0));
+        const uint64_t scales = w.pages.keyScales.bytes() / (c.kv_scale_f16 ? 2 : 4);
+        SB_TRY(fill(c.kv_scale_f16 ? kF16Uniform : kF32Uniform, w.pages.keyScales, scales, next(), 0.005f, 0.03f));
+        SB_TRY(fill(c.kv_scale_f16 ? kF16Uniform : kF32Uniform, w.pages.valueScales, scales, next(), 0.005f, 0.03f));
+      } else {
+        SB_TRY(fill(kF32Normal, w.ssmAb, w.ssmAb.bytes() / 4, next(), 0.0f, 0.02f));
+        SB_TRY(fill(kBf16Normal, w.ssmConv, w.ssmConv.bytes() / 2, next(), 0.0f, 0.4f));
+        SB_TRY(fill(kF32NegExp, w.ssmA, c.gdn_value_heads, next(), -3.0f, 0.5f));
+        SB_TRY(fill(kBf16Normal, w.ssmDtBias, c.gdn_value_heads, next(), 0.0f, 0.5f));
+        SB_TRY(fill(kF32Normal, w.ssmNorm, 128, next(), 1.0f, 0.1f));
+        for (int i = 0; i < 2; ++i) {
+          SB_TRY(fill(kF32Normal, w.cells[i].state, w.cells[i].state.bytes() / 4, next(), 0.0f, 0.05f));
+          SB_TRY(fill(kBf16Normal, w.cells[i].convolution, w.cells[i].convolution.bytes() / 2, next(), 0.0f, 1.0f));
+        }
+      }
+    }
+    Buffer b;
+    m.find(-1, "output_norm", b);
+    SB_TRY(fill(kF32Normal, b, c.hidden, next(), 1.0f, 0.1f));
+    splash::b200::ops::QuantizedSegment seg;
+    m.find(-1, "token_embd", seg.rows);
+    seg.outputSize = c.vocab, seg.inputSize = c.hidden, seg.format = c.fmt_embed;
+    SB_TRY(fill_rows(seg, next()));
+    m.find(-1, "output", seg.rows);
+    seg.format = c.fmt_head;
+    SB_TRY(fill_rows(seg, next()));
+#undef SB_TRY
+    SB_CUDA(cudaDeviceSynchronize());
+    return sb_target_reset(target, committed);
+  });
+}
+
+static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float temperature, uint32_t flags) {
+  QwenTarget &m = *t->model;
+  const bool advance = (flags & SB_TARGET_ADVANCE) != 0;
+  const uint32_t parity = m.step & 1;
+  return guarded([&] {
+    if (flags & SB_TARGET_GRAPH) {
+      // The attention plan and the page-table extents are made for a bound of the lane's position; a graph
+      // serves until the lane passes its bound.
+      const uint32_t bound = std::min(m.config().max_context, (m.committedHost / 1024 + 2) * 1024);
+      uint32_t tbits;
+      memcpy(&tbits, &temperature, 4);
+      const auto key = std::make_tuple(rows, tbits, parity, uint32_t(advance), bound);
+      auto it = t->graphs.find(key);
+      if (it == t->graphs.end()) {
+        const uint32_t saved = m.committedHost;
+        m.committedHost = bound;
+        CommandGraph g{stream, true, 0};
+        SB_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+        int status = SB_OK;
+        try {
+          m.encodeVerify(g, rows, temperature, parity, advance);
+        } catch (...) {
+          cudaGraph_t dead = nullptr;
+          cudaStreamEndCapture(stream, &dead);
+          if (dead) cudaGraphDestroy(dead);
+          m.committedHost = saved;
+          throw;
+        }
+        m.committedHost = saved;
+        cudaGraph_t graph = nullptr;
+        SB_CUDA(cudaStreamEndCapture(stream, &graph));
+        cudaGraphExec_t exec = nullptr;
+        const cudaError_t e = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate");
+        t->launches = g.launches;
+        it = t->graphs.emplace(key, exec).first;
+        (void)status;
+      }
+      SB_CUDA(cudaGraphLaunch(it->second, stream));
+    } else {
+      CommandGraph g{stream, ctx().pdl, 0};
+      m.encodeVerify(g, rows, temperature, parity, advance);
+      t->launches = g.launches;
+    }
+    ++m.step;
+    if (advance) m.committedHost = std::min(m.config().max_context, m.committedHost + rows);
+    return int(SB_OK);
+  });
+}
+
+int sb_target_step(void *target, void *stream, uint32_t rows, float temperature, uint32_t flags) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target, "sb_target_step: null target");
+  return run_step(static_cast<Target *>(target), as_stream(stream), rows, temperature, flags);
+}
+
+int sb_target_verify(void *target, void *stream, const uint32_t *tokens_host, const float *uniforms_host, uint32_t rows, float temperature,
+                     uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target && tokens_host && out_tokens_host && out_results_host, "sb_target_verify: null pointer");
+  SB_REQUIRE(rows >= 1 && rows <= splash::b200::model::kVerifyRows, "sb_target_verify: rows = %u outside 1..16", rows);
+  SB_REQUIRE(temperature == 0.0f || uniforms_host, "sb_target_verify: a sampled policy needs uniforms");
+  Target *t = static_cast<Target *>(target);
+  QwenTarget &m = *t->model;
+  cudaStream_t s = as_stream(stream);
+  const uint32_t before = m.committedHost;
+  SB_CUDA(cudaMemcpyAsync(m.tokens.as(), tokens_host, rows * 4, cudaMemcpyHostToDevice, s));
+  if (uniforms_host) SB_CUDA(cudaMemcpyAsync(m.uniforms.as(), uniforms_host, 80 * 4, cudaMemcpyHostToDevice, s));
+  const int st = run_step(t, s, rows, temperature, flags);
+  if (st != SB_OK) return st;
+  SB_CUDA(cudaMemcpyAsync(t->results_pinned, m.results.as(), 16, cudaMemcpyDeviceToHost, s));
+  SB_CUDA(cudaMemcpyAsync(t->results_pinned + 4, m.selected.as(), rows * 4, cudaMemcpyDeviceToHost, s));
+  SB_CUDA(cudaStreamSynchronize(s));
+  memcpy(out_results_host, t->results_pinned, 16);
+  memcpy(out_tokens_host, t->results_pinned + 4, rows * 4);
+  if (flags & SB_TARGET_ADVANCE) m.committedHost = before + t->results_pinned[0];  // the exact position again
+  return SB_OK;
+}
+
+int sb_target_stats(void *target, uint32_t rows, uint32_t *out_launches, uint64_t *out_weight_bytes, uint64_t *out_kv_bytes,
+                    uint64_t *out_state_bytes) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target, "sb_target_stats: null target");
+  Target *t = static_cast<Target *>(target);
+  if (out_launches) *out_launches = t->launches;
+  if (out_weight_bytes) *out_weight_bytes = t->model->weightBytes();
+  if (out_kv_bytes) *out_kv_bytes = t->model->kvBytes(t->model->committedHost + rows);
+  if (out_state_bytes) *out_state_bytes = t->model->stateBytes();
+  return SB_OK;
+}
+
+}  // extern "C"

@@ -183,12 +183,12 @@ class SbKvLayer(ctypes.Structure):
 
 class SbAttnStoreArgs(ctypes.Structure):
     _fields_ = [("qkv", _P), ("q_norm", _P), ("k_norm", _P), ("cos_tab", _P), ("sin_tab", _P), ("page_table", _P),
-                ("queries", _P), ("cache", SbKvLayer),
+                ("queries", _P), ("cache", SbKvLayer), ("committed_dev", _P),
                 ("rows", _U), ("q_heads", _U), ("gated", _U), ("pairs", _U), ("qkv_stride", _U), ("committed", _U)]
 
 
 class SbAttnArgs(ctypes.Structure):
-    _fields_ = [("queries", _P), ("qkv", _P), ("page_table", _P), ("tree", _P), ("out", _P), ("cache", SbKvLayer),
+    _fields_ = [("queries", _P), ("qkv", _P), ("page_table", _P), ("tree", _P), ("out", _P), ("cache", SbKvLayer), ("committed_dev", _P),
                 ("rows", _U), ("q_heads", _U), ("gated", _U), ("qkv_stride", _U), ("out_stride", _U), ("committed", _U)]
 
 

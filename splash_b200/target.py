@@ -1,0 +1,111 @@
+"""ctypes harness of the target model's verify step (sb_target_* of include/splash_b200.h)."""
+import ctypes
+
+import numpy as np
+
+from . import lib
+
+_P, _U, _F = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_float
+ADVANCE, GRAPH = 1, 2
+
+
+class SbTargetConfig(ctypes.Structure):
+    _fields_ = [("layers", _U), ("hidden", _U), ("vocab", _U), ("intermediate", _U),
+                ("q_heads", _U), ("kv_heads", _U), ("head_dim", _U), ("rotary_pairs", _U), ("rope_theta", _F),
+                ("gdn_key_heads", _U), ("gdn_value_heads", _U), ("attention_interval", _U),
+                ("page_tokens", _U), ("kv_scale_f16", _U), ("max_context", _U),
+                ("fmt_proj", _U), ("fmt_down", _U), ("fmt_head", _U), ("fmt_embed", _U),
+                ("gated_attention", _U), ("tiled_heads", _U)]
+
+
+# The benchmark configurations' shapes (weights are synthetic; see quant fixtures and sb_target_randomize).
+TINY = dict(layers=4, hidden=1024, vocab=32000, intermediate=2816, q_heads=8, kv_heads=2, head_dim=128, rotary_pairs=16,
+            rope_theta=1e6, gdn_key_heads=8, gdn_value_heads=8, attention_interval=4, page_tokens=256, kv_scale_f16=1,
+            max_context=4096, fmt_proj=lib.FMT_Q4K, fmt_down=lib.FMT_Q4K, fmt_head=lib.FMT_Q6K, fmt_embed=lib.FMT_Q6K,
+            gated_attention=1, tiled_heads=0)
+QWEN27B = dict(layers=64, hidden=5120, vocab=151936, intermediate=17408, q_heads=24, kv_heads=4, head_dim=256,
+               rotary_pairs=32, rope_theta=1e7, gdn_key_heads=16, gdn_value_heads=48, attention_interval=4, page_tokens=256,
+               kv_scale_f16=1, max_context=32768 + 1024, fmt_proj=lib.FMT_Q4K, fmt_down=lib.FMT_Q6K, fmt_head=lib.FMT_Q6K,
+               fmt_embed=lib.FMT_Q6K, gated_attention=1, tiled_heads=1)
+
+
+def _bind():
+    l = lib.ops()
+    if getattr(l, "_target_bound", False):
+        return l
+    l.sb_target_create.argtypes = [ctypes.POINTER(SbTargetConfig), ctypes.POINTER(_P)]
+    l.sb_target_destroy.argtypes = [_P]
+    l.sb_target_tensor.argtypes = [_P, ctypes.c_int, ctypes.c_char_p, ctypes.POINTER(_P), ctypes.POINTER(ctypes.c_uint64)]
+    l.sb_target_randomize.argtypes = [_P, ctypes.c_uint64, _U]
+    l.sb_target_reset.argtypes = [_P, _U]
+    l.sb_target_step.argtypes = [_P, _P, _U, _F, _U]
+    l.sb_target_verify.argtypes = [_P, _P, _P, _P, _U, _F, _U, _P, _P]
+    l.sb_target_stats.argtypes = [_P, _U, ctypes.POINTER(_U), ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64),
+                                  ctypes.POINTER(ctypes.c_uint64)]
+    l._target_bound = True
+    return l
+
+
+class Target:
+    def __init__(self, **config):
+        self.l = _bind()
+        self.config = dict(config)
+        self.cfg = SbTargetConfig(**config)
+        h = _P()
+        lib.check(self.l.sb_target_create(ctypes.byref(self.cfg), ctypes.byref(h)))
+        self.handle = h.value
+
+    def close(self):
+        if self.handle:
+            self.l.sb_target_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def tensor(self, layer, name):
+        p, n = _P(), ctypes.c_uint64()
+        lib.check(self.l.sb_target_tensor(self.handle, layer, name.encode(), ctypes.byref(p), ctypes.byref(n)))
+        return p.value, n.value
+
+    def upload(self, layer, name, array):
+        a = np.ascontiguousarray(array)
+        p, n = self.tensor(layer, name)
+        assert a.nbytes <= n, (name, a.nbytes, n)
+        lib.check(self.l.sb_upload(p, a.ctypes.data_as(_P), a.nbytes, None))
+        lib.stream_sync()
+
+    def download(self, layer, name, dtype, shape):
+        out = np.empty(shape, dtype)
+        p, n = self.tensor(layer, name)
+        assert out.nbytes <= n, (name, out.nbytes, n)
+        lib.check(self.l.sb_download(out.ctypes.data_as(_P), p, out.nbytes, None))
+        lib.stream_sync()
+        return out
+
+    def randomize(self, seed, committed):
+        lib.check(self.l.sb_target_randomize(self.handle, seed, committed))
+
+    def reset(self, committed):
+        lib.check(self.l.sb_target_reset(self.handle, committed))
+
+    def step(self, rows=16, temperature=0.0, flags=GRAPH, stream=None):
+        lib.check(self.l.sb_target_step(self.handle, stream, rows, temperature, flags))
+
+    def verify(self, tokens, uniforms=None, temperature=0.0, flags=0, stream=None):
+        """One step from host buffers. Returns (retained tokens, retained, accepted, retained_rows mask)."""
+        tokens = np.ascontiguousarray(tokens, np.uint32)
+        rows = len(tokens)
+        out_t, out_r = np.zeros(16, np.uint32), np.zeros(4, np.uint32)
+        u = None if uniforms is None else np.ascontiguousarray(uniforms, np.float32)
+        lib.check(self.l.sb_target_verify(self.handle, stream, tokens.ctypes.data_as(_P), None if u is None else u.ctypes.data_as(_P),
+                                          rows, temperature, flags, out_t.ctypes.data_as(_P), out_r.ctypes.data_as(_P)))
+        return out_t[:out_r[0]].copy(), int(out_r[0]), int(out_r[1]), int(out_r[2])
+
+    def stats(self, rows=16):
+        n, w, k, s = _U(), ctypes.c_uint64(), ctypes.c_uint64(), ctypes.c_uint64()
+        lib.check(self.l.sb_target_stats(self.handle, rows, ctypes.byref(n), ctypes.byref(w), ctypes.byref(k), ctypes.byref(s)))
+        return dict(launches=n.value, weight_bytes=w.value, kv_bytes=k.value, state_bytes=s.value)

@@ -1,0 +1,172 @@
+"""The tiny hybrid model's verify step on the CPU oracle (test infrastructure): the same layer loop as
+splash_b200/csrc/model/QwenTarget.hpp, every operator an oracle call, for parity of whole steps."""
+import ctypes
+
+import numpy as np
+
+import oracle_lib as ol
+import quant_fixtures as qf
+
+P = ol.ptr
+
+
+def make_weights(cfg, seed=0):
+    """Seeded synthetic tensors of the tiny configuration, keyed (layer, name) like sb_target_tensor."""
+    rng = np.random.default_rng(seed)
+    H, D, I = cfg["hidden"], cfg["head_dim"], cfg["intermediate"]
+    KH, VH = cfg["gdn_key_heads"], cfg["gdn_value_heads"]
+    conv = (2 * KH + VH) * 128
+    attn_in = cfg["q_heads"] * (2 * D if cfg["gated_attention"] else D) + 2 * cfg["kv_heads"] * D
+    gdn_in = conv + VH * 128
+    w = {}
+    norm = lambda n: (1 + 0.1 * rng.standard_normal(n)).astype(np.float32)
+    rows = lambda fmt, n, k: qf.realistic(fmt, n, k, seed=int(rng.integers(1 << 30)))
+    for l in range(cfg["layers"]):
+        attention = (l + 1) % cfg["attention_interval"] == 0
+        w[l, "attn_norm"], w[l, "ffn_norm"] = norm(H), norm(H)
+        if attention:
+            w[l, "in_proj"] = rows(cfg["fmt_proj"], attn_in, H)
+            w[l, "out_proj"] = rows(cfg["fmt_proj"], H, cfg["q_heads"] * D)
+            w[l, "q_norm"], w[l, "k_norm"] = norm(D), norm(D)
+        else:
+            w[l, "in_proj"] = rows(cfg["fmt_proj"], gdn_in, H)
+            w[l, "out_proj"] = rows(cfg["fmt_proj"], H, VH * 128)
+            w[l, "ssm_ab"] = (rng.standard_normal((2 * VH, H)) * 0.02).astype(np.float32)
+            w[l, "ssm_conv"] = ol.f2bf((rng.standard_normal((conv, 4)) * 0.4).astype(np.float32))
+            w[l, "ssm_a"] = (-np.exp(rng.uniform(-3, 0.5, VH))).astype(np.float32)
+            w[l, "ssm_dt_bias"] = ol.f2bf((rng.standard_normal(VH) * 0.5).astype(np.float32))
+            w[l, "ssm_norm"] = norm(128)
+        w[l, "ffn_gate"] = rows(cfg["fmt_proj"], I, H)
+        w[l, "ffn_up"] = rows(cfg["fmt_proj"], I, H)
+        w[l, "ffn_down"] = rows(cfg["fmt_down"], H, I)
+    w[-1, "token_embd"] = rows(cfg["fmt_embed"], cfg["vocab"], H)
+    w[-1, "output_norm"] = norm(H)
+    w[-1, "output"] = rows(cfg["fmt_head"], cfg["vocab"], H)
+    return w
+
+
+def make_state(cfg, committed, seed=1):
+    """A prefilled INT8 cache of `committed` random tokens per attention layer and random GDN cells."""
+    rng = np.random.default_rng(seed)
+    KH, VH = cfg["gdn_key_heads"], cfg["gdn_value_heads"]
+    conv = (2 * KH + VH) * 128
+    pages = (cfg["max_context"] + 16 + cfg["page_tokens"] - 1) // cfg["page_tokens"]
+    s = {"committed": committed, "pending_rows": 0, "step": 0}
+    for l in range(cfg["layers"]):
+        if (l + 1) % cfg["attention_interval"] == 0:
+            kv = ol.HostKv(pages, cfg["kv_heads"], cfg["head_dim"], cfg["page_tokens"], cfg["kv_scale_f16"])
+            kv.fill_random(rng)
+            s[l, "kv"] = kv
+        else:
+            for i in range(2):
+                s[l, f"state{i}"] = (rng.standard_normal((VH, 128, 128)) * 0.05).astype(np.float32)
+                s[l, f"conv{i}"] = ol.f2bf(rng.standard_normal((3, conv)).astype(np.float32))
+                s[l, f"tape{i}"] = dict(inputs=np.zeros((16, conv), np.uint16), k=np.zeros((16, KH * 128), np.uint16),
+                                        v=np.zeros((16, VH * 128), np.uint16), beta=np.zeros((16, VH), np.uint16),
+                                        decay=np.zeros((16, VH), np.float32))
+    return s
+
+
+def linear(o, fmt, W, n, k, X, rows, epilogue=0, aux=None, out_f32=False, W2=None):
+    out = np.zeros((rows, n), np.float32 if out_f32 else np.uint16)
+    Wfull = W if W2 is None else np.concatenate([W, W2], axis=0)
+    assert o.so_linear(fmt, P(np.ascontiguousarray(Wfull)), n, k, P(X), rows, epilogue, P(aux) if aux is not None else None, n,
+                       P(out), n, int(out_f32), 0) == 0
+    return out
+
+
+def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True, mutate=True):
+    """One verify step of a chain. Returns dict(logits, selected, retained, accepted, mask, tokens)."""
+    o = ol.bind_ops(ol.load())
+    rows = len(tokens)
+    H, D, I, V = cfg["hidden"], cfg["head_dim"], cfg["intermediate"], cfg["vocab"]
+    KH, VH, QH, KVH = cfg["gdn_key_heads"], cfg["gdn_value_heads"], cfg["q_heads"], cfg["kv_heads"]
+    conv = (2 * KH + VH) * 128
+    pairs = cfg["rotary_pairs"]
+    committed, parity = s["committed"], s["step"] & 1
+    tokens = np.ascontiguousarray(tokens, np.uint32)
+    pos = (committed + np.arange(rows)).astype(np.uint32)
+    inv = (np.float32(cfg["rope_theta"]) ** (-np.arange(pairs, dtype=np.float32) / np.float32(pairs))).astype(np.float32)
+    cos, sin = np.zeros((rows, pairs), np.float32), np.zeros((rows, pairs), np.float32)
+    o.so_rope_tables(P(pos), rows, P(inv), pairs, 1.0, P(cos), P(sin))
+    h = np.zeros((rows, H), np.uint16)
+    assert o.so_embed(cfg["fmt_embed"], P(w[-1, "token_embd"]), V, H, P(tokens), rows, P(h), H) == 0
+    page_table = np.arange((cfg["max_context"] + 16 + cfg["page_tokens"] - 1) // cfg["page_tokens"], dtype=np.uint32)
+    new_state = {}
+    for l in range(cfg["layers"]):
+        attention = (l + 1) % cfg["attention_interval"] == 0
+        n1 = np.zeros_like(h)
+        o.so_rmsnorm(P(h), rows, H, H, P(w[l, "attn_norm"]), P(n1), H)
+        if attention:
+            attn_in = QH * (2 * D if cfg["gated_attention"] else D) + 2 * KVH * D
+            packed = linear(o, cfg["fmt_proj"], w[l, "in_proj"], attn_in, H, n1, rows)
+            kv = s[l, "kv"]
+            if not mutate:
+                import copy
+                kv = copy.deepcopy(kv)
+            desc = kv.desc()
+            queries = np.zeros((rows, QH, D), np.uint16)
+            o.so_attn_store(P(packed), attn_in, rows, QH, cfg["gated_attention"], P(w[l, "q_norm"]), P(w[l, "k_norm"]), P(cos), P(sin),
+                            pairs, ctypes.byref(desc), P(page_table), committed, P(queries))
+            mixed = np.zeros((rows, QH * D), np.uint16)
+            o.so_attention(P(queries), P(packed), attn_in, rows, QH, cfg["gated_attention"], ctypes.byref(desc), P(page_table),
+                           committed, None, P(mixed), QH * D, None)
+            mixed_w = QH * D
+        else:
+            gdn_in = conv + VH * 128
+            packed = linear(o, cfg["fmt_proj"], w[l, "in_proj"], gdn_in, H, n1, rows)
+            ab = ol.f2bf((ol.bf2f(n1).astype(np.float32) @ w[l, "ssm_ab"].T.astype(np.float32)).astype(np.float32))
+            b, a = np.ascontiguousarray(ab[:, :VH]), np.ascontiguousarray(ab[:, VH:])
+            cur, nxt = parity, parity ^ 1
+            pend, step = s[l, f"tape{nxt}"], s[l, f"tape{cur}"]
+            if not mutate:
+                step = {k: v.copy() for k, v in step.items()}
+            cs_out, st_out = np.zeros_like(s[l, f"conv{cur}"]), np.zeros_like(s[l, f"state{cur}"])
+            mixed = np.zeros((rows, VH * 128), np.uint16)
+            tape = lambda t: ol.SoGdnTape(P(t["inputs"]), P(t["k"]), P(t["v"]), P(t["beta"]), P(t["decay"]))
+            args = ol.SoGdnArgs(P(packed), P(b), P(a), P(w[l, "ssm_conv"]), P(w[l, "ssm_a"]), P(w[l, "ssm_dt_bias"]), P(w[l, "ssm_norm"]),
+                                P(s[l, f"conv{cur}"]), P(cs_out), P(s[l, f"state{cur}"]), P(st_out), tape(pend), tape(step), P(mixed),
+                                rows, s["pending_rows"], KH, VH, gdn_in, VH, VH * 128, cfg["tiled_heads"])
+            o.so_gdn_verify(ctypes.byref(args))
+            new_state[l, f"conv{nxt}"], new_state[l, f"state{nxt}"] = cs_out, st_out
+            mixed_w = VH * 128
+        h = linear(o, cfg["fmt_proj"], w[l, "out_proj"], H, mixed_w, mixed, rows, epilogue=1, aux=h)
+        n2 = np.zeros_like(h)
+        o.so_rmsnorm(P(h), rows, H, H, P(w[l, "ffn_norm"]), P(n2), H)
+        act = linear(o, cfg["fmt_proj"], w[l, "ffn_gate"], I, H, n2, rows, epilogue=3, W2=w[l, "ffn_up"])
+        h = linear(o, cfg["fmt_down"], w[l, "ffn_down"], H, I, act, rows, epilogue=1, aux=h)
+    nf = np.zeros_like(h)
+    o.so_rmsnorm(P(h), rows, H, H, P(w[-1, "output_norm"]), P(nf), H)
+    logits = linear(o, cfg["fmt_head"], w[-1, "output"], V, H, nf, rows, out_f32=True)
+    selected = np.zeros(rows, np.uint32)
+    margin = np.zeros(rows, np.float64)
+    o.so_sample_verify(P(logits), V, V, rows, P(tokens), float(temperature), P(uniforms) if uniforms is not None else None, P(selected),
+                       P(margin))
+    tree = np.zeros((rows, 2), np.uint32)
+    for r in range(rows):
+        tree[r] = ((2 << r) - 1, max(r - 1, 0) | (r << 16))
+    out_tokens = selected.copy()
+    res = np.zeros(3, np.uint32)
+    o.so_accept(P(tokens), P(tree), P(out_tokens), rows, 16, None, 0, P(res[0:1]), P(res[1:2]), P(res[2:3]))
+    if mutate:
+        s.update(new_state)
+        s["step"] += 1
+        if advance:
+            s["committed"] += int(res[0])
+            s["pending_rows"] = int(res[0])
+        else:
+            s["pending_rows"] = 0
+    return dict(logits=logits, selected=selected, retained=int(res[0]), accepted=int(res[1]), mask=int(res[2]),
+                tokens=out_tokens[:res[0]].copy(), margin=margin, hidden=h)
+
+
+def draft_chain(cfg, w, s, first_token, rows=16, p_match=0.7, seed=5):
+    """A draft block for the current state: token r + 1 equals the target's greedy choice after row r with
+    probability p_match, else a uniform token (the benchmark configuration's draft model stand-in)."""
+    rng = np.random.default_rng(seed)
+    tokens = [int(first_token)]
+    for r in range(rows - 1):
+        out = verify_step(cfg, w, s, tokens, mutate=False)
+        target = int(out["selected"][r])
+        tokens.append(target if rng.random() < p_match else int(rng.integers(0, cfg["vocab"])))
+    return np.array(tokens, np.uint32)

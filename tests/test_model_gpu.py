@@ -1,0 +1,95 @@
+"""Whole verify steps of the tiny hybrid configuration (4 layers = 3 Gated-DeltaNet + 1 attention, hidden 1024,
+vocabulary 32000, Q4_K projections, Q6_K embedding and head, INT8 cache of 2048 prefilled tokens, page 256, fp16
+scales): the CUDA path through the C ABI against the CPU oracle, over several steps with acceptance, KV growth
+and GDN state rollback in between."""
+import numpy as np
+import pytest
+
+import model_oracle as mo
+import oracle_lib as ol
+
+pytestmark = pytest.mark.gpu
+
+
+def build(seed=0, committed=2048):
+    from splash_b200 import lib, target
+    lib.init(0)
+    cfg = dict(target.TINY)
+    t = target.Target(**cfg)
+    w = mo.make_weights(cfg, seed)
+    s = mo.make_state(cfg, committed, seed + 1)
+    for (layer, name), arr in w.items():
+        t.upload(layer, name, arr)
+    for key, val in s.items():
+        if isinstance(key, tuple):
+            layer, name = key
+            if name == "kv":
+                t.upload(layer, "kv_k", val.k), t.upload(layer, "kv_v", val.v)
+                t.upload(layer, "kv_ks", val.ks), t.upload(layer, "kv_vs", val.vs)
+            elif name.startswith("tape"):
+                i = name[-1]
+                for f, tn in (("inputs", "tape_inputs"), ("k", "tape_k"), ("v", "tape_v"), ("beta", "tape_beta"), ("decay", "tape_decay")):
+                    t.upload(layer, tn + i, val[f])
+            else:
+                t.upload(layer, name, val)
+    t.reset(committed)
+    return lib, target, t, cfg, w, s
+
+
+@pytest.mark.parametrize("flags_name", ["eager", "graph"])
+def test_tiny_model_steps_match_oracle(flags_name):
+    lib, target, t, cfg, w, s = build()
+    flags = target.ADVANCE | (target.GRAPH if flags_name == "graph" else 0)
+    rng = np.random.default_rng(3)
+    token = 17
+    accept_lengths = []
+    for step in range(4):
+        tokens = mo.draft_chain(cfg, w, s, token, rows=16, seed=step)
+        want = mo.verify_step(cfg, w, s, tokens, advance=True)
+        got_tokens, retained, accepted, mask = t.verify(tokens, flags=flags)
+        assert lib.device_status() == 0
+        logits = t.download(-1, "logits", np.float32, (16, cfg["vocab"]))
+        # logits within 2e-3 of their scale (bf16 activations through 4 layers leave ~1e-3)
+        scale = np.abs(want["logits"]).max()
+        assert np.abs(logits - want["logits"]).max() <= 2e-2 * scale
+        assert np.median(np.abs(logits - want["logits"])) <= 2e-3 * scale
+        # selections and the accept length are exact wherever the top-2 logit gap exceeds 1e-2
+        top2 = np.sort(want["logits"], axis=1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 1e-2
+        sel = t.download(-1, "selected", np.uint32, (16,))
+        # (the device's `selected` holds the retained tokens in its first slots after acceptance)
+        if clear[:want["retained"]].all():
+            assert retained == want["retained"] and accepted == want["accepted"] and mask == want["mask"]
+            assert np.array_equal(got_tokens, want["tokens"])
+            accept_lengths.append(retained)
+        else:
+            s["committed"] += retained - want["retained"]  # follow the device where the oracle's own choice was a near tie
+            s["pending_rows"] = retained
+        token = int(got_tokens[-1])
+    assert len(accept_lengths) >= 3 and max(accept_lengths) > 1
+
+
+def test_tiny_model_stochastic_acceptance_matches_oracle():
+    lib, target, t, cfg, w, s = build(seed=4)
+    rng = np.random.default_rng(11)
+    tokens = mo.draft_chain(cfg, w, s, 99, rows=16, seed=2)
+    uniforms = rng.random(80).astype(np.float32)
+    want = mo.verify_step(cfg, w, s, tokens, temperature=0.7, uniforms=uniforms, advance=True)
+    got_tokens, retained, accepted, mask = t.verify(tokens, uniforms=uniforms, temperature=0.7, flags=target.ADVANCE)
+    # decisions agree unless a test sat within rounding of its threshold (the margin the oracle reports)
+    if (want["margin"][:want["retained"]] > 1e-3).all():
+        assert retained == want["retained"] and accepted == want["accepted"]
+        assert np.array_equal(got_tokens[:accepted], want["tokens"][:accepted])
+
+
+def test_hold_position_steps_are_idempotent():
+    """Without SB_TARGET_ADVANCE a step leaves the lane where it was: repeating it gives the same result."""
+    lib, target, t, cfg, w, s = build(seed=7)
+    tokens = np.arange(16, dtype=np.uint32) + 100
+    a = t.verify(tokens, flags=target.GRAPH)
+    la = t.download(-1, "logits", np.float32, (16, cfg["vocab"]))
+    b = t.verify(tokens, flags=target.GRAPH)
+    lb = t.download(-1, "logits", np.float32, (16, cfg["vocab"]))
+    c = t.verify(tokens, flags=target.GRAPH)
+    lc = t.download(-1, "logits", np.float32, (16, cfg["vocab"]))
+    assert a[1:] == b[1:] == c[1:] and np.array_equal(la, lc)

@@ -125,11 +125,11 @@ def attention_case(lib, l, o, *, q_heads, kv_heads, D, page_tokens, scale_f16, c
     bufs = {n: lib.DeviceBuffer.from_numpy(a) for n, a in dict(qkv=qkv, qn=qn, kn=kn, c=c, s=s, table=table).items()}
     qd = lib.DeviceBuffer(queries.nbytes)
     sa = lib.SbAttnStoreArgs(bufs["qkv"].ptr, bufs["qn"].ptr, bufs["kn"].ptr, bufs["c"].ptr, bufs["s"].ptr, bufs["table"].ptr,
-                             qd.ptr, dev.desc(lib), rows, q_heads, int(gated), pairs, stride, committed)
+                             qd.ptr, dev.desc(lib), None, rows, q_heads, int(gated), pairs, stride, committed)
     lib.check(l.sb_attn_store(None, ctypes.byref(sa)))
     od = lib.DeviceBuffer(want.nbytes)
     od.fill(0xFF)
-    aa = lib.SbAttnArgs(qd.ptr, bufs["qkv"].ptr, bufs["table"].ptr, None, od.ptr, dev.desc(lib), rows, q_heads, int(gated),
+    aa = lib.SbAttnArgs(qd.ptr, bufs["qkv"].ptr, bufs["table"].ptr, None, od.ptr, dev.desc(lib), None, rows, q_heads, int(gated),
                         stride, q_heads * D, committed)
     lib.check(l.sb_attn_verify(None, ctypes.byref(aa)))
     lib.stream_sync()
