@@ -1,0 +1,264 @@
+#!/usr/bin/env python
+"""Benchmark of the DFlash2 verify step on B200: verify tokens/s of a Qwen3.x-27B-shaped hybrid model
+(64 layers at 3:1 Gated-DeltaNet : attention, Q4_K_M mix, batch 1, block 16, 32K-token INT8 paged KV
+context, greedy acceptance) with seeded synthetic weights, cache and state written on the device.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on stdout (rank 0). `value` is device-resident steps; `e2e` goes through the host-facing call
+sb_target_verify with pinned host buffers, copies and the result read-back inside the timed region;
+`roofline` is the dominant kernel (the Q4_K gate/up projection) timed alone over the layers' weights;
+`cpu_baseline` is the CPU oracle's port of the same projections on a bounded sample.
+--impl reference times the reference's arithmetic for this path on the host cores: the oracle port
+(the reference's own GPU kernels are Metal and cannot run here)."""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+ROWS = 16
+CONTEXT = 32768
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel from the ncu capture
+# summarised in profiles/linear_q4k_gate_up_27b.md (bytes); None until a capture exists.
+DOMINANT_TRAFFIC_BYTES = None
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi samples of one GPU's SM clock and throttle reasons while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out = self.proc.communicate(timeout=5)[0]
+        except Exception:
+            self.proc.kill()
+            out = ""
+        clocks, mx, reasons = [], None, set()
+        for line in out.splitlines():
+            p = [x.strip() for x in line.split(",")]
+            if len(p) < 6 or not p[0].isdigit():
+                continue
+            clocks.append(int(p[0]))
+            mx = int(p[1])
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(clocks) if clocks else None, "sm_max_mhz": mx, "reasons": sorted(reasons)}
+
+
+def cpu_baseline(seconds_budget=20.0):
+    """The oracle's port of one FFN (gate/up one pass, then down: the dominant share of a layer's bytes) on the host
+    cores, scaled by weight bytes to a whole step. Returns (tokens/s, cores, sample description)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as ol
+    import quant_fixtures as qf
+    o = ol.load()
+    H, I = 5120, 17408
+    cores = os.cpu_count() or 1
+    # a bounded slice of the FFN: `n` of the 17408 intermediate columns, sized from a quick probe
+    def run(n):
+        wg, wu = qf.realistic(0, n, H, seed=1), qf.realistic(0, n, H, seed=2)
+        wd = qf.realistic(4, H, max(256, n // 256 * 256), seed=3)
+        x = qf.activations(ROWS, H)
+        kd = wd.shape[1] // 210 * 256
+        t0 = time.perf_counter()
+        act = np.zeros((ROWS, n), np.uint16)
+        w2 = np.ascontiguousarray(np.concatenate([wg, wu], axis=0))
+        assert o.so_linear(0, ol.ptr(w2), n, H, ol.ptr(x), ROWS, 3, None, 0, ol.ptr(act), n, 0, 0) == 0
+        xa = np.ascontiguousarray(np.resize(act, (ROWS, kd)))
+        out = np.zeros((ROWS, H), np.uint16)
+        assert o.so_linear(4, ol.ptr(wd), H, kd, ol.ptr(xa), ROWS, 0, None, 0, ol.ptr(out), H, 0, 0) == 0
+        dt = time.perf_counter() - t0
+        return dt, wg.nbytes + wu.nbytes + wd.nbytes
+    dt, nbytes = run(1024)
+    n = int(min(I, max(1024, 1024 * seconds_budget / 3 / max(dt, 1e-3)))) // 256 * 256
+    best, nbytes = min((run(n) for _ in range(3)), key=lambda r: r[0])
+    step_bytes = 15.89e9  # weight bytes of one 27B-shaped step
+    step_seconds = best * step_bytes / nbytes
+    return ROWS / step_seconds, cores, f"oracle port, FFN slice of {n} of {I} columns ({nbytes / 1e6:.0f} MB of weights), best of 3, scaled by weight bytes to a step"
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--tiny", action="store_true", help="the 4-layer configuration (a smoke run, not the benchmark)")
+    args = ap.parse_args()
+    rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    workload = "tiny hybrid verify" if args.tiny else "Qwen3.x-27B-shaped hybrid verify, Q4_K_M mix, batch 1, block 16, 32K INT8 paged KV, greedy"
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        tps, cores, sample = cpu_baseline(30.0)
+        print(json.dumps({"impl": "reference", "metric": "verify_tokens_per_s", "value": tps, "unit": "tokens/s", "n_gpus": args.gpus,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": ROWS / tps * 1e3, "higher_is_better": True,
+                          "scaling": "weak", "vs_baseline": None, "dtype": "f16 operands, f32 accumulate", "data": "synthetic",
+                          "config": {"workload": workload},
+                          "cpu_baseline": {"value": tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+                          "e2e": {"value": tps, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    from splash_b200 import lib, target
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    lib.init(local)
+    cfg = dict(target.TINY if args.tiny else target.QWEN27B)
+    context = 2048 if args.tiny else CONTEXT
+    t = target.Target(**cfg)
+    t.randomize(1234 + rank, context)
+    stream = lib.stream_create()
+    warm = max(args.warmup, 3)
+    flags = target.GRAPH  # hold the lane at 32K: every step does the same work
+    rng = np.random.default_rng(rank)
+    t.upload(-1, "tokens", rng.integers(0, cfg["vocab"], ROWS).astype(np.uint32))
+
+    def barrier():
+        if dist is not None:
+            import torch
+            dist.barrier()
+            torch.cuda.synchronize()
+        lib.stream_sync(stream)
+
+    def reduce_max(ms):
+        if dist is None:
+            return ms
+        import torch
+        v = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        return float(v.item())
+
+    # ---- device-resident steps ----
+    for _ in range(warm):
+        t.step(ROWS, 0.0, flags, stream)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    e0, e1 = lib.Event(), lib.Event()
+    e0.record(stream)
+    for _ in range(args.steps):
+        t.step(ROWS, 0.0, flags, stream)
+    e1.record(stream)
+    e1.sync()
+    barrier()
+    ms = reduce_max(e0.elapsed_ms(e1)) / args.steps
+    clocks = sampler.stop() if sampler else None
+    status = lib.device_status()
+    stats = t.stats(ROWS)
+
+    # ---- end to end through the host-facing call, pinned host buffers ----
+    pinned = ctypes.c_void_p()
+    lib.check(lib.load().sb_host_alloc(4096, ctypes.byref(pinned)))
+    host = np.ctypeslib.as_array((ctypes.c_uint32 * 1024).from_address(pinned.value))
+    host[:ROWS] = rng.integers(0, cfg["vocab"], ROWS)
+    l = target._bind()
+    out_t, out_r = pinned.value + 1024, pinned.value + 2048
+    def verify_once():
+        lib.check(l.sb_target_verify(t.handle, stream, pinned.value, None, ROWS, 0.0, flags, out_t, out_r))
+    for _ in range(2):
+        verify_once()
+    barrier()
+    e2, e3 = lib.Event(), lib.Event()
+    e2.record(stream)
+    for _ in range(args.steps):
+        verify_once()
+    e3.record(stream)
+    e3.sync()
+    barrier()
+    e2e_ms = reduce_max(e2.elapsed_ms(e3)) / args.steps
+
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    # ---- the dominant kernel alone: the one-pass Q4_K gate/up projection over each layer's weights ----
+    peak, peak_kind = measured_peak()
+    roofline = None
+    if not args.tiny:
+        H, I = cfg["hidden"], cfg["intermediate"]
+        x = lib.DeviceBuffer(ROWS * H * 2 + 256)
+        x.upload(rng.standard_normal((ROWS, H)).astype(np.float16).view(np.uint16))  # any finite bf16 bits
+        prep = lib.DeviceBuffer(int(lib.load().sb_linear_prepared_bytes(H)))
+        lib.check(lib.load().sb_linear_prepare(stream, x.ptr, ROWS, H, H, None, lib.FMT_Q4K, prep.ptr, 0))
+        out = lib.DeviceBuffer(ROWS * I * 2 + 256)
+        ptrs = [(t.tensor(layer, "ffn_gate")[0], t.tensor(layer, "ffn_up")[0]) for layer in range(cfg["layers"])]
+        def gate_up(i):
+            g, u = ptrs[i % len(ptrs)]
+            lib.linear(g, None, out.ptr, lib.FMT_Q4K, I, H, ROWS, weights2=u, prepared=prep.ptr, epilogue=lib.EP_GATE_UP, stream=stream)
+        for i in range(8):
+            gate_up(i)
+        lib.stream_sync(stream)
+        n = 64
+        k0, k1 = lib.Event(), lib.Event()
+        k0.record(stream)
+        for i in range(n):
+            gate_up(i + 8)
+        k1.record(stream)
+        k1.sync()
+        launch_ms = k0.elapsed_ms(k1) / n
+        algo = 2 * I * (H // 256) * 144 + ROWS * H * 2 + ROWS * I * 2
+        achieved = algo / launch_ms / 1e6
+        roofline = {"bound": "hbm", "kernel": "linear_kernel<Q4_K> gate/up 2x[17408x5120], M=16", "achieved": achieved, "peak": peak,
+                    "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "algorithmic_bytes": algo,
+                    "launch_us": launch_ms * 1e3, "traffic": DOMINANT_TRAFFIC_BYTES}
+    step_bytes = stats["weight_bytes"] + stats["kv_bytes"] + stats["state_bytes"]
+    step_gbs = step_bytes / ms / 1e6
+    cpu_tps, cores, sample = cpu_baseline(15.0) if not args.tiny else (None, os.cpu_count(), "skipped for the tiny run")
+    result = {
+        "metric": "verify_tokens_per_s", "value": world * ROWS / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16 operands (exact integer codes), f32 accumulate, bf16 activations", "data": "synthetic",
+        "config": {"workload": workload, "context_tokens": context, "block": ROWS, "parallelism": "tp1" if world == 1 else f"{world} independent replicas (lanes); tensor parallel not built",
+                   "l2": "inputs exceed L2: one step streams %.1f GB of weights" % (stats["weight_bytes"] / 1e9), "cuda_graph": True, "pdl": True},
+        "e2e": {"value": world * ROWS / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": ROWS * 4, "d2h_bytes_per_step": 16 + ROWS * 4},
+        "gpu_launches": stats["launches"] * args.steps,
+        "launches_per_step": stats["launches"],
+        "step_roofline": {"bytes_per_step": step_bytes, "weight_bytes": stats["weight_bytes"], "kv_bytes": stats["kv_bytes"],
+                          "state_bytes": stats["state_bytes"], "achieved_gbs": step_gbs, "frac_of_measured_peak": step_gbs / peak},
+        "roofline": roofline,
+        "cpu_baseline": {"value": cpu_tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "clocks": clocks, "device_status": status,
+    }
+    print(json.dumps(result))
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -109,6 +109,8 @@ struct Target {
   std::map<std::tuple<uint32_t, uint32_t, uint32_t, uint32_t, uint32_t>, cudaGraphExec_t> graphs;  // rows, temperature bits, parity, advance, bound
   uint32_t launches = 0;
   uint32_t *results_pinned = nullptr;  // 4 + 16 words
+  cudaStream_t own_stream = nullptr;   // used when the caller passes no stream (the default stream cannot be captured)
+  cudaStream_t pick(void *s) const { return s ? as_stream(s) : own_stream; }
 };
 
 }  // namespace sb
@@ -167,6 +169,7 @@ int sb_target_create(const SbTargetConfig *config, void **out_target) {
     auto t = std::make_unique<Target>();
     t->model = std::make_unique<QwenTarget>(*config);
     SB_CUDA(cudaMallocHost(&t->results_pinned, 20 * sizeof(uint32_t)));
+    SB_CUDA(cudaStreamCreateWithFlags(&t->own_stream, cudaStreamNonBlocking));
     QwenTarget &m = *t->model;
     Buffer table;
     m.find(-1, "page_table", table);
@@ -190,6 +193,7 @@ int sb_target_destroy(void *target) {
   cudaDeviceSynchronize();
   for (auto &g : t->graphs) cudaGraphExecDestroy(g.second);
   if (t->results_pinned) cudaFreeHost(t->results_pinned);
+  if (t->own_stream) cudaStreamDestroy(t->own_stream);
   delete t;
   return SB_OK;
 }
@@ -325,7 +329,7 @@ static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float tempera
 int sb_target_step(void *target, void *stream, uint32_t rows, float temperature, uint32_t flags) {
   SB_NEED_DEVICE();
   SB_REQUIRE(target, "sb_target_step: null target");
-  return run_step(static_cast<Target *>(target), as_stream(stream), rows, temperature, flags);
+  return run_step(static_cast<Target *>(target), static_cast<Target *>(target)->pick(stream), rows, temperature, flags);
 }
 
 int sb_target_verify(void *target, void *stream, const uint32_t *tokens_host, const float *uniforms_host, uint32_t rows, float temperature,
@@ -336,7 +340,7 @@ int sb_target_verify(void *target, void *stream, const uint32_t *tokens_host, co
   SB_REQUIRE(temperature == 0.0f || uniforms_host, "sb_target_verify: a sampled policy needs uniforms");
   Target *t = static_cast<Target *>(target);
   QwenTarget &m = *t->model;
-  cudaStream_t s = as_stream(stream);
+  cudaStream_t s = t->pick(stream);
   const uint32_t before = m.committedHost;
   SB_CUDA(cudaMemcpyAsync(m.tokens.as(), tokens_host, rows * 4, cudaMemcpyHostToDevice, s));
   if (uniforms_host) SB_CUDA(cudaMemcpyAsync(m.uniforms.as(), uniforms_host, 80 * 4, cudaMemcpyHostToDevice, s));
