@@ -215,7 +215,7 @@ def main():
         x = lib.DeviceBuffer(ROWS * H * 2 + 256)
         x.upload(rng.standard_normal((ROWS, H)).astype(np.float16).view(np.uint16))  # any finite bf16 bits
         prep = lib.DeviceBuffer(int(lib.load().sb_linear_prepared_bytes(H)))
-        lib.check(lib.load().sb_linear_prepare(stream, x.ptr, ROWS, H, H, None, lib.FMT_Q4K, prep.ptr, 0))
+        lib.check(lib.load().sb_linear_prepare(stream, x.ptr, ROWS, H, H, None, lib.FMT_Q4K, prep.ptr, None, 0))
         out = lib.DeviceBuffer(ROWS * I * 2 + 256)
         ptrs = [(t.tensor(layer, "ffn_gate")[0], t.tensor(layer, "ffn_up")[0]) for layer in range(cfg["layers"])]
         def gate_up(i):

@@ -136,10 +136,11 @@ enum {
 /* Converts a projection input once into the fragment-ordered fp16 form the product reads
  * (the reference's prepared input: ops::LinearBuffers::prepared / PreparedInput,
  * runtime/ops/Linear.hpp:265-347; kernel decode_linear_gguf_prepare). `format` selects the layout
- * (Q4_K's differs from Q6_K / Q8_0's). An RMSNorm is fused in front when norm_weight is given. */
+ * (Q4_K's differs from Q6_K / Q8_0's). An RMSNorm is fused in front when norm_weight is given; normed_out
+ * (optional, bf16 [rows, k]) also receives the normalised rows for the fp32 side projections. */
 SB_API uint64_t sb_linear_prepared_bytes(uint32_t k);
 SB_API int sb_linear_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride,
-                             const void *norm_weight, uint32_t format, void *prepared_out, uint32_t flags);
+                             const void *norm_weight, uint32_t format, void *prepared_out, void *normed_out, uint32_t flags);
 
 /* Scratch (split-K partials and arrival counters) the context keeps for sb_linear; sized by
  * sb_init for the largest projection of the supported shapes and reused serially within a stream,

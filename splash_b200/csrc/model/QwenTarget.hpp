@@ -67,7 +67,7 @@ class QwenTarget {
   ops::EmbeddingWeights embedding_;
   ops::NormWeights outputNorm_;
   ops::QuantizedSegment output_;
-  Buffer packed_, gates_, mixed_, queries_, act_, prepared_[2], pageTable_, sampleWorkspace_;
+  Buffer packed_, gates_, mixed_, queries_, act_, normed_, prepared_[2], pageTable_, sampleWorkspace_;
   uint32_t packedStride_ = 0;
   uint64_t weightBytes_ = 0;
 };
@@ -136,6 +136,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &c) : cfg_(c) {
   mixed_ = Buffer::allocate(size_t(kVerifyRows) * std::max(gdn_.valueWidth(), c.q_heads * D) * 2);
   queries_ = Buffer::allocate(size_t(kVerifyRows) * c.q_heads * D * 2);
   act_ = Buffer::allocate(size_t(kVerifyRows) * c.intermediate * 2);
+  normed_ = Buffer::allocate(size_t(kVerifyRows) * H * 2);
   const uint32_t widest = std::max(std::max(H, c.intermediate), std::max(gdn_.valueWidth(), c.q_heads * D));
   for (auto &p : prepared_) p = Buffer::allocate(ops::Linear::preparedBytes((widest + 255) / 256 * 256));
   for (auto &h : hidden) h = Buffer::allocate(size_t(kVerifyRows) * H * 2);
@@ -211,7 +212,8 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   uint32_t cur = 0;
   for (LayerWeights &w : layers_) {
     // mixer: h += mixer(norm(h))
-    PreparedInput in = Linear::prepare(graph, hidden[cur], rows, H, H, &w.attnNorm.buffer, w.inProj.format, prepared_[0]);
+    PreparedInput in = Linear::prepare(graph, hidden[cur], rows, H, H, &w.attnNorm.buffer, w.inProj.format, prepared_[0],
+                                       w.attention ? nullptr : &normed_);
     Projection inProj{w.inProj.outputSize, H, Destination::BFloat16, {w.inProj}};
     LinearBuffers inB{Buffer(), packed_, Buffer(), H, packedStride_};
     Linear::add(graph, inB, inProj, Linear::plan(inProj, rows, Epilogue::None), in);
@@ -223,8 +225,8 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
       PagedAttention::addAttention(graph, kv_, w.pages, queries_, packed_, packedStride_, pageTable_, nullptr, mixed_, mixedWidth, rows,
                                    c.q_heads, c.gated_attention != 0, committedHost, &committed);
     } else {
-      Linear::addFloat(graph, w.ssmAb, hidden[cur], H, rows, 2 * gdn_.valueHeads, H, gates_, 2 * gdn_.valueHeads, Destination::BFloat16,
-                       &w.attnNorm.buffer);
+      Linear::addFloat(graph, w.ssmAb, normed_, H, rows, 2 * gdn_.valueHeads, H, gates_, 2 * gdn_.valueHeads, Destination::BFloat16,
+                       nullptr);
       GdnDecodeBuffers g;
       g.packed = packed_, g.gates = gates_, g.convolutionWeights = w.ssmConv, g.decayWeights = w.ssmA, g.timeBias = w.ssmDtBias;
       g.mixerNorm = w.ssmNorm, g.current = w.cells[parity], g.next = w.cells[parity ^ 1];

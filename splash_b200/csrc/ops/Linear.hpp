@@ -62,12 +62,14 @@ class Linear {
 
   // Converts `input` (optionally through an RMSNorm with fp32 weights) for projections of `format`.
   static PreparedInput prepare(CommandGraph &graph, const Buffer &input, uint32_t rows, uint32_t inputSize,
-                               uint32_t inputStride, const Buffer *normWeight, uint32_t format, const Buffer &scratch) {
+                               uint32_t inputStride, const Buffer *normWeight, uint32_t format, const Buffer &scratch,
+                               const Buffer *normedOutput = nullptr) {
     requireBytes(input, size_t(rows - 1) * inputStride * 2 + size_t(inputSize) * 2, "Linear::prepare input");
     requireBytes(scratch, preparedBytes(inputSize), "Linear::prepare scratch");
     if (normWeight) requireBytes(*normWeight, size_t(inputSize) * 4, "Linear::prepare norm weight");
+    if (normedOutput) requireBytes(*normedOutput, size_t(rows) * inputSize * 2, "Linear::prepare normalised output");
     check(sb_linear_prepare(graph.stream, input.as(), rows, inputSize, inputStride, normWeight ? normWeight->as() : nullptr,
-                            format, scratch.as(), graph.pdl ? SB_LINEAR_PDL : 0));
+                            format, scratch.as(), normedOutput ? normedOutput->as() : nullptr, graph.pdl ? SB_LINEAR_PDL : 0));
     ++graph.launches;
     return {scratch, format == SB_FMT_Q4K ? uint32_t(SB_FMT_Q4K) : uint32_t(SB_FMT_Q6K), inputSize};
   }

@@ -71,8 +71,8 @@ int sb_init(int device) {
   SB_CUDA(cudaMemset(c.linear_counters, 0, c.linear_counter_count * sizeof(uint32_t)));
   c.attn_workspace_bytes = size_t(32) << 20;
   SB_CUDA(cudaMalloc(&c.attn_workspace, c.attn_workspace_bytes));
-  SB_CUDA(cudaMalloc(&c.attn_counters, 64 * sizeof(uint32_t)));
-  SB_CUDA(cudaMemset(c.attn_counters, 0, 64 * sizeof(uint32_t)));
+  SB_CUDA(cudaMalloc(&c.attn_counters, 128 * sizeof(uint32_t)));
+  SB_CUDA(cudaMemset(c.attn_counters, 0, 128 * sizeof(uint32_t)));
   SB_CUDA(cudaMalloc(&c.gdn_scratch, size_t(256) * 16 * 128 * 2));
   SB_CUDA(cudaMalloc(&c.gdn_counters, 256 * sizeof(uint32_t)));
   SB_CUDA(cudaMemset(c.gdn_counters, 0, 256 * sizeof(uint32_t)));

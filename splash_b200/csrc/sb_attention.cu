@@ -16,9 +16,10 @@
 //             fp32 accumulators) with ldmatrix fragments; score = S * k_scale[token] / sqrt(D); row r sees
 //             tokens <= committed + r (and, with a tree, only its ancestors inside the block);
 //             P = fp16(p * v_scale[token]) (the reference rounds this product to bf16)
-//   merge     fp32 partial O and (max, sum) per split go to the context's workspace; the last CTA of a KV
-//             head adds the splits in split order with weights exp(max_s - max), divides, rounds to bf16
-//             and multiplies by sigmoid(gate)
+//   merge     fp32 partial O and (max, sum) per split go to the context's workspace; once every split of a KV
+//             head has arrived (cooperative launch, bounded wait) the head's CTAs share its fused rows, each
+//             adding a row's splits in split order with weights exp(max_s - max), dividing, rounding to bf16
+//             and multiplying by sigmoid(gate)
 #include <algorithm>
 
 #include "sb_internal.h"
@@ -38,7 +39,8 @@ struct AttnParams {
   SbKvLayer cache;
   float *partials;     // [kv_head][split][fused][D]
   float *stats;        // [kv_head][split][fused][2]
-  uint32_t *counters;  // [kv_head]
+  uint32_t *counters;  // [kv_head] arrivals, [64 + kv_head] merges done
+  uint32_t *status;
   const uint32_t *committed_dev;
   uint32_t rows, q_heads, group, gated, qkv_stride, out_stride, committed, splits, chunks_per_split, fused;
 };
@@ -293,30 +295,53 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnPa
       }
     }
   }
+  // Every split of this KV head publishes its partials, then all of the head's CTAs (co-resident: the
+  // launch is cooperative and the grid has at most one CTA per SM) share the merge: CTA `split` merges
+  // fused rows split, split + splits, ... A bounded wait: if the other splits never arrive the kernel sets
+  // the status word and leaves.
   __threadfence();
   __syncthreads();
-  if (tid == 0) s_last = atomicAdd(&p.counters[kvh], 1u) == p.splits - 1;
+  if (tid == 0) {
+    atomicAdd(&p.counters[kvh], 1u);
+    uint32_t spins = 0;
+    while (atomicAdd(&p.counters[kvh], 0u) < p.splits && ++spins < (1u << 22)) __nanosleep(100);
+    s_last = spins < (1u << 22);
+    if (!s_last) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
+  }
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  // Merge in split order: thread -> dimension(s) of each fused row.
-  for (uint32_t f = warp; f < F; f += kAttnThreads / 32) {
+  // Merge in split order: a warp per fused row, lane -> dimensions lane + 32 i; loads batched 8 splits deep.
+  for (uint32_t f = split + warp * p.splits; f < F; f += (kAttnThreads / 32) * p.splits) {
+    const float *stats = p.stats + (size_t(kvh) * p.splits * kMaxFused + f) * 2;
+    const float *parts = p.partials + (size_t(kvh) * p.splits * kMaxFused + f) * D;
+    const size_t sstride = size_t(kMaxFused) * 2, pstride = size_t(kMaxFused) * D;
     float mall = -INFINITY;
-    for (uint32_t s = 0; s < p.splits; ++s)
-      mall = fmaxf(mall, __ldcg(p.stats + ((size_t(kvh) * p.splits + s) * kMaxFused + f) * 2));
+    for (uint32_t s = lane; s < p.splits; s += 32) mall = fmaxf(mall, __ldcg(stats + s * sstride));
+#pragma unroll
+    for (int o = 16; o; o >>= 1) mall = fmaxf(mall, __shfl_xor_sync(0xffffffffu, mall, o));
     float num[D / 32];
 #pragma unroll
     for (int i = 0; i < D / 32; ++i) num[i] = 0.0f;
     float den = 0.0f;
-    for (uint32_t s = 0; s < p.splits; ++s) {
-      const float *ps = p.stats + ((size_t(kvh) * p.splits + s) * kMaxFused + f) * 2;
-      const float ms = __ldcg(ps), ls = __ldcg(ps + 1);
-      if (ms == -INFINITY) continue;
-      const float w = exp2f(ms - mall);
-      const float *po = p.partials + ((size_t(kvh) * p.splits + s) * kMaxFused + f) * D;
+    for (uint32_t s0 = 0; s0 < p.splits; s0 += 8) {
+      float ms[8], ls[8], v[8][D / 32];
 #pragma unroll
-      for (int i = 0; i < D / 32; ++i) num[i] += w * __ldcg(po + lane + 32 * i);
-      den += w * ls;
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t s = min(s0 + j, p.splits - 1);
+        ms[j] = __ldcg(stats + s * sstride);
+        ls[j] = __ldcg(stats + s * sstride + 1);
+#pragma unroll
+        for (int i = 0; i < D / 32; ++i) v[j][i] = __ldcg(parts + s * pstride + lane + 32 * i);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (s0 + j >= p.splits || ms[j] == -INFINITY) continue;
+        const float w = exp2f(ms[j] - mall);
+#pragma unroll
+        for (int i = 0; i < D / 32; ++i) num[i] += w * v[j][i];
+        den += w * ls[j];
+      }
     }
     const uint32_t row = f / G, qh = kvh * G + f % G;
 #pragma unroll
@@ -330,7 +355,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnPa
       p.out[size_t(row) * p.out_stride + qh * D + d] = float_to_bf16_bits(o);
     }
   }
-  if (tid == 0) p.counters[kvh] = 0;
+  // The last CTA to finish its share returns both counters to zero for the next launch.
+  __syncthreads();
+  if (tid == 0 && atomicAdd(&p.counters[64 + kvh], 1u) == p.splits - 1) {
+    p.counters[kvh] = 0;
+    p.counters[64 + kvh] = 0;
+  }
 }
 
 }  // namespace sb
@@ -353,7 +383,7 @@ extern "C" int sb_attn_verify(void *stream, const SbAttnArgs *a) {
   Context &cx = ctx();
   const uint32_t D = c.head_dim, visible = a->committed + a->rows, chunks = (visible + kChunk - 1) / kChunk;
   // Splits: about one CTA per SM over all KV heads, at least 4 chunks each.
-  uint32_t splits = std::max(1u, uint32_t(cx.sm_count) / c.kv_heads);
+  uint32_t splits = std::max(1u, uint32_t(cx.sm_count) / c.kv_heads);  // the whole grid is resident at once
   splits = std::min(splits, std::max(1u, chunks / 4));
   const uint32_t cps = (chunks + splits - 1) / splits;
   splits = (chunks + cps - 1) / cps;
@@ -369,6 +399,7 @@ extern "C" int sb_attn_verify(void *stream, const SbAttnArgs *a) {
   p.partials = cx.attn_workspace;
   p.stats = cx.attn_workspace + size_t(c.kv_heads) * splits * kMaxFused * D;
   p.counters = cx.attn_counters;
+  p.status = cx.status_dev;
   p.committed_dev = a->committed_dev;
   p.rows = a->rows, p.q_heads = a->q_heads, p.group = group, p.gated = a->gated, p.qkv_stride = a->qkv_stride;
   p.out_stride = a->out_stride, p.committed = a->committed, p.splits = splits, p.chunks_per_split = cps, p.fused = fused;
@@ -384,11 +415,12 @@ extern "C" int sb_attn_verify(void *stream, const SbAttnArgs *a) {
   cfg.blockDim = dim3(kAttnThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = as_stream(stream);
+  // Cooperative: every CTA is resident before any runs, which the shared merge's wait relies on.
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[0].id = cudaLaunchAttributeCooperative;
+  attr[0].val.cooperative = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = cx.pdl ? 1 : 0;
+  cfg.numAttrs = 1;
   SB_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
   return SB_OK;
 }

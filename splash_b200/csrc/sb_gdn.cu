@@ -47,6 +47,8 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_kernel(const GdnParams p) {
   __shared__ float q_s[kGdnRows][kD], k_s[kGdnRows][kD], pk_s[kGdnRows][kD];
   __shared__ float v_s[kGdnRows][kGdnVd], pv_s[kGdnRows][kGdnVd], o_s[kGdnRows][kGdnVd];
   __shared__ float beta_s[kGdnRows], decay_s[kGdnRows], pbeta_s[kGdnRows], pdecay_s[kGdnRows];
+  __shared__ __align__(16) uint16_t in_s[kGdnRows + 3][2 * kD + kGdnVd];
+  __shared__ uint2 w_s[2 * kD + kGdnVd];
   __shared__ uint32_t s_last;
   pdl_launch_dependents();
   pdl_wait();
@@ -61,20 +63,41 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_kernel(const GdnParams p) {
   const uint16_t *pin = static_cast<const uint16_t *>(a.pending.inputs);
   const bool qk_writer = h % per_key == 0 && vs == 0;
 
-  // Conv input of block row `row` (negative: history) at channel ch. History row i (0..2, oldest first)
-  // is row pending - 3 + i of (carried rows ++ pending rows).
-  auto hist = [&](int i, uint32_t ch) -> uint16_t {
-    const int src = int(pending) - 3 + i;
-    return src >= 0 ? pin[size_t(src) * C + ch] : cs_in[size_t(3 + src) * C + ch];
-  };
-  auto input = [&](int row, uint32_t ch) -> float {
-    return bf16_bits_to_float(row >= 0 ? qkvz[size_t(row) * a.qkvz_stride + ch] : hist(3 + row, ch));
-  };
-  auto conv = [&](uint32_t row, uint32_t ch) -> float {
+  // The state rows of this warp, requested first so their latency hides behind the prologue.
+  float S[4][4];
+  const size_t sbase = (size_t(h) * kD + vd0 + 4 * (tid >> 5)) * kD + 4 * (tid & 31);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const float4 s4 = *reinterpret_cast<const float4 *>(a.state_in + sbase + size_t(r) * kD);
+    S[r][0] = s4.x, S[r][1] = s4.y, S[r][2] = s4.z, S[r][3] = s4.w;
+  }
+  // Conv inputs of this CTA's channels (q and k of the key head, 32 value dimensions) for history rows
+  // -3..-1 and the block's rows, staged with 16-byte loads: in_s[3 + row][local channel]. History row i
+  // (0..2, oldest first) is row pending - 3 + i of (carried rows ++ pending rows).
+  constexpr int kLocal = 2 * kD + kGdnVd;  // 288 local channels
+  const uint32_t chan0[3] = {kh * kD, KW + kh * kD, 2 * KW + h * kD + vd0};
+  auto global_channel = [&](uint32_t lc) { return lc < kD ? chan0[0] + lc : lc < 2 * kD ? chan0[1] + lc - kD : chan0[2] + lc - 2 * kD; };
+  for (uint32_t i = tid; i < (3 + rows) * (kLocal / 8); i += kGdnThreads) {
+    const uint32_t r = i / (kLocal / 8), lc = (i % (kLocal / 8)) * 8, ch = global_channel(lc);
+    const uint16_t *src;
+    if (r >= 3) {
+      src = qkvz + size_t(r - 3) * a.qkvz_stride + ch;
+    } else {
+      const int hsrc = int(pending) - 3 + int(r);
+      src = hsrc >= 0 ? pin + size_t(hsrc) * C + ch : cs_in + size_t(3 + hsrc) * C + ch;
+    }
+    *reinterpret_cast<uint4 *>(&in_s[r][lc]) = *reinterpret_cast<const uint4 *>(src);
+  }
+  for (uint32_t lc = tid; lc < kLocal; lc += kGdnThreads)
+    w_s[lc] = *reinterpret_cast<const uint2 *>(conv_w + size_t(global_channel(lc)) * kTaps);
+  __syncthreads();
+  auto conv = [&](uint32_t row, uint32_t lc) -> float {
+    const uint2 wv = w_s[lc];
+    const float w[4] = {bf16_bits_to_float(wv.x & 0xffffu), bf16_bits_to_float(wv.x >> 16), bf16_bits_to_float(wv.y & 0xffffu),
+                        bf16_bits_to_float(wv.y >> 16)};
     float value = 0.0f;
 #pragma unroll
-    for (int tap = 0; tap < kTaps; ++tap)
-      value = __fadd_rn(value, __fmul_rn(input(int(row) + tap - 3, ch), bf16_bits_to_float(conv_w[size_t(ch) * kTaps + tap])));
+    for (int tap = 0; tap < kTaps; ++tap) value = __fadd_rn(value, __fmul_rn(bf16_bits_to_float(in_s[row + tap][lc]), w[tap]));
     value = round_bf16(value);
     return round_bf16(silu_f(value));
   };
@@ -82,12 +105,12 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_kernel(const GdnParams p) {
   // (2) conv outputs: q, k of the key head (16 x 128 each) and this CTA's 32 value dimensions.
   for (uint32_t i = tid; i < rows * kD; i += kGdnThreads) {
     const uint32_t r = i / kD, d = i % kD;
-    q_s[r][d] = conv(r, kh * kD + d);
-    k_s[r][d] = conv(r, KW + kh * kD + d);
+    q_s[r][d] = conv(r, d);
+    k_s[r][d] = conv(r, kD + d);
   }
   for (uint32_t i = tid; i < rows * kGdnVd; i += kGdnThreads) {
     const uint32_t r = i / kGdnVd, d = i % kGdnVd;
-    v_s[r][d] = conv(r, 2 * KW + h * kD + vd0 + d);
+    v_s[r][d] = conv(r, 2 * kD + d);
   }
   // pending rows' keys, values and gates from their tape
   for (uint32_t i = tid; i < pending * kD; i += kGdnThreads)
@@ -131,40 +154,24 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_kernel(const GdnParams p) {
     for (int g = 0; g < 4; ++g) vec[32 * g + lane] = round_bf16(round_bf16(vec[32 * g + lane] * inv) * post);
   }
   __syncthreads();
-  // (6) tape and carried conv rows.
+  // (6) tape and carried conv rows, from the staged inputs.
   {
     uint16_t *tin = static_cast<uint16_t *>(a.step.inputs), *cs_out = static_cast<uint16_t *>(a.conv_state_out);
-    for (uint32_t i = tid; i < rows * kGdnVd; i += kGdnThreads) {
-      const uint32_t r = i / kGdnVd, d = i % kGdnVd, ch = 2 * KW + h * kD + vd0 + d;
-      tin[size_t(r) * C + ch] = qkvz[size_t(r) * a.qkvz_stride + ch];
-      static_cast<uint16_t *>(a.step.v)[size_t(r) * VW + h * kD + vd0 + d] = float_to_bf16_bits(v_s[r][d]);
+    for (uint32_t i = tid; i < (3 + rows) * kLocal; i += kGdnThreads) {
+      const uint32_t r = i / kLocal, lc = i % kLocal;
+      if (lc < 2 * kD && !qk_writer) continue;
+      const uint32_t ch = global_channel(lc);
+      if (r < 3) cs_out[size_t(r) * C + ch] = in_s[r][lc];
+      else tin[size_t(r - 3) * C + ch] = in_s[r][lc];
     }
-    for (uint32_t i = tid; i < 3 * kGdnVd; i += kGdnThreads) {
-      const uint32_t r = i / kGdnVd, ch = 2 * KW + h * kD + vd0 + i % kGdnVd;
-      cs_out[size_t(r) * C + ch] = hist(int(r), ch);
-    }
-    if (qk_writer) {
-      for (uint32_t i = tid; i < rows * 2 * kD; i += kGdnThreads) {
-        const uint32_t r = i / (2 * kD), d = i % (2 * kD), ch = (d < kD ? 0 : KW) + kh * kD + d % kD;
-        tin[size_t(r) * C + ch] = qkvz[size_t(r) * a.qkvz_stride + ch];
-      }
+    for (uint32_t i = tid; i < rows * kGdnVd; i += kGdnThreads)
+      static_cast<uint16_t *>(a.step.v)[size_t(i / kGdnVd) * VW + h * kD + vd0 + i % kGdnVd] = float_to_bf16_bits(v_s[i / kGdnVd][i % kGdnVd]);
+    if (qk_writer)
       for (uint32_t i = tid; i < rows * kD; i += kGdnThreads)
         static_cast<uint16_t *>(a.step.k)[size_t(i / kD) * KW + kh * kD + i % kD] = float_to_bf16_bits(k_s[i / kD][i % kD]);
-      for (uint32_t i = tid; i < 3 * 2 * kD; i += kGdnThreads) {
-        const uint32_t r = i / (2 * kD), d = i % (2 * kD), ch = (d < kD ? 0 : KW) + kh * kD + d % kD;
-        cs_out[size_t(r) * C + ch] = hist(int(r), ch);
-      }
-    }
   }
 
   // (3) + (4): warp w owns value dimensions vd0 + 4w .. + 3; lane holds key columns 4 lane .. + 3.
-  float S[4][4];
-  const size_t sbase = (size_t(h) * kD + vd0 + 4 * warp) * kD + 4 * lane;
-#pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    const float4 s4 = *reinterpret_cast<const float4 *>(a.state_in + sbase + size_t(r) * kD);
-    S[r][0] = s4.x, S[r][1] = s4.y, S[r][2] = s4.z, S[r][3] = s4.w;
-  }
   auto advance = [&](const float *key, const float *val, float d, float b, const float *query, float *out) {
     const float4 k4 = *reinterpret_cast<const float4 *>(key + 4 * lane);
     const float kk[4] = {k4.x, k4.y, k4.z, k4.w};

@@ -110,6 +110,7 @@ struct PrepareParams {
   const uint16_t *x;
   const float *norm_w;
   uint8_t *out;
+  uint16_t *normed_out;  // optional bf16 [rows][k]: the (normalised) input as the product's fp32 side projections read it
   uint32_t rows, k, x_stride, pair_layout;
 };
 
@@ -166,6 +167,19 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PreparePara
         const float wn[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[i][j] = round_bf16((v[i][j] * inv) * wn[j]);
+      }
+    }
+  }
+  if (p.normed_out && live) {
+#pragma unroll
+    for (int i = 0; i < kPrepMaxChunks; ++i) {
+      const uint32_t c = tid + kPrepThreads * i;
+      if (c < chunks) {
+        uint32_t pk[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          pk[j] = uint32_t(float_to_bf16_bits(v[i][2 * j])) | (uint32_t(float_to_bf16_bits(v[i][2 * j + 1])) << 16);
+        *reinterpret_cast<uint4 *>(p.normed_out + size_t(tok) * p.k + 8 * c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
       }
     }
   }
@@ -856,9 +870,9 @@ static int encode_weight_map(CUtensorMap *map, uintptr_t base, uint32_t stride, 
 }
 
 static int launch_prepare(cudaStream_t stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride,
-                          const void *norm_w, bool pair_layout, void *out, bool pdl) {
+                          const void *norm_w, bool pair_layout, void *out, void *normed_out, bool pdl) {
   PrepareParams pp{static_cast<const uint16_t *>(x), static_cast<const float *>(norm_w), static_cast<uint8_t *>(out),
-                   rows, k, x_stride, pair_layout ? 1u : 0u};
+                   static_cast<uint16_t *>(normed_out), rows, k, x_stride, pair_layout ? 1u : 0u};
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(kTokens);
   cfg.blockDim = dim3(kPrepThreads);
@@ -887,7 +901,8 @@ extern "C" int sb_linear_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t 
 extern "C" uint64_t sb_linear_prepared_bytes(uint32_t k) { return k % 256 ? 0 : kPrepHeader + uint64_t(k / 256) * kPrepSbBytes; }
 
 extern "C" int sb_linear_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride,
-                                 const void *norm_weight, uint32_t format, void *prepared_out, uint32_t flags) {
+                                 const void *norm_weight, uint32_t format, void *prepared_out, void *normed_out,
+                                 uint32_t flags) {
   SB_NEED_DEVICE();
   SB_REQUIRE(x && prepared_out, "sb_linear_prepare: null x or destination");
   SB_REQUIRE(rows >= 1 && rows <= kTokens, "sb_linear_prepare: rows = %u outside 1..%d", rows, kTokens);
@@ -898,7 +913,8 @@ extern "C" int sb_linear_prepare(void *stream, const void *x, uint32_t rows, uin
   SB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(prepared_out) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(norm_weight) & 15) == 0,
              "sb_linear_prepare: x, norm_weight and the destination must be 16-byte aligned");
-  return launch_prepare(as_stream(stream), x, rows, k, x_stride, norm_weight, format == SB_FMT_Q4K, prepared_out,
+  SB_REQUIRE((reinterpret_cast<uintptr_t>(normed_out) & 15) == 0, "sb_linear_prepare: normed_out must be 16-byte aligned");
+  return launch_prepare(as_stream(stream), x, rows, k, x_stride, norm_weight, format == SB_FMT_Q4K, prepared_out, normed_out,
                         (flags & SB_LINEAR_PDL) != 0);
 }
 
@@ -936,7 +952,7 @@ extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
   const void *prepared = a->prepared;
   if (!prepared) {
     SB_REQUIRE(sb_linear_prepared_bytes(a->k) <= c.prepared_bytes, "sb_linear: k = %u exceeds the context's prepared-input scratch", a->k);
-    st = sb_linear_prepare(stream, a->x, a->rows, a->k, a->x_stride, a->norm_weight, a->format, c.prepared, a->flags);
+    st = sb_linear_prepare(stream, a->x, a->rows, a->k, a->x_stride, a->norm_weight, a->format, c.prepared, nullptr, a->flags);
     if (st != SB_OK) return st;
     prepared = c.prepared;
   } else {

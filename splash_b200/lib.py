@@ -64,7 +64,7 @@ def load():
         _lib.sb_graph_destroy.argtypes = [ctypes.c_void_p]
         _lib.sb_linear.argtypes = [ctypes.c_void_p, ctypes.POINTER(SbLinearArgs)]
         _lib.sb_linear_prepare.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32,
-                                           ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32]
+                                           ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32]
         _lib.sb_linear_prepared_bytes.restype = ctypes.c_uint64
         _lib.sb_dequant.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32,
                                     ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32]

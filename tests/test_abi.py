@@ -1,0 +1,62 @@
+"""CPU checks of the drop-in boundary: the shared library loads, exports every entry point that
+include/splash_b200.h declares, refuses compute without a device instead of falling back, and plans
+projections as documented."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "splash_b200.h")).read()
+    return sorted(set(re.findall(r"SB_API\s+[\w\s\*]+?\b(sb_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from splash_b200 import lib
+    l = lib.load()
+    names = declared_symbols()
+    assert len(names) >= 40
+    missing = [n for n in names if not hasattr(l, n)]
+    assert not missing, missing
+
+
+def test_no_cpu_fallback_without_a_device():
+    from splash_b200 import lib
+    if lib.device_count() > 0:
+        pytest.skip("a CUDA device is present")
+    with pytest.raises(lib.SbError):
+        lib.init(0)
+    with pytest.raises(lib.SbError):
+        lib.DeviceBuffer(1024)
+    with pytest.raises(lib.SbError):
+        lib.linear(1 << 20, 1 << 20, 1 << 20, 0, 64, 1024, 16)
+
+
+def test_linear_plans_of_the_27b_projections():
+    from splash_b200 import lib
+    l = lib.load()
+    l.sb_linear_plan.argtypes = [ctypes.c_uint32] * 5 + [ctypes.POINTER(lib.SbLinearPlan)]
+    p = lib.SbLinearPlan()
+    # gate/up: K = 5120 = 20 super-blocks in 2 slices of 10, 544 tiles of 32 columns
+    assert l.sb_linear_plan(lib.FMT_Q4K, 17408, 5120, 16, lib.EP_GATE_UP, ctypes.byref(p)) == 0
+    assert (p.slices, p.tiles, p.slice_blocks_max, p.ctas) == (2, 544, 10, 148) and p.smem_bytes <= 227 * 1024 and p.stages >= 2
+    # down: Q6_K, K = 17408 = 68 super-blocks
+    assert l.sb_linear_plan(lib.FMT_Q6K, 5120, 17408, 16, lib.EP_RESIDUAL, ctypes.byref(p)) == 0
+    assert p.slices * p.slice_blocks_max >= 68 and p.ctas % p.slices == 0 and p.smem_bytes <= 227 * 1024
+    # argument errors are values, not crashes
+    assert l.sb_linear_plan(lib.FMT_Q4K, 17408, 5000, 16, 0, ctypes.byref(p)) == -1
+    assert l.sb_linear_plan(3, 64, 1024, 16, 0, ctypes.byref(p)) == -1
+    assert b"format" in l.sb_last_error()
+
+
+def test_row_bytes():
+    from splash_b200 import lib
+    l = lib.load()
+    assert l.sb_row_bytes(lib.FMT_Q4K, 5120) == 20 * 144
+    assert l.sb_row_bytes(lib.FMT_Q6K, 17408) == 68 * 210
+    assert l.sb_row_bytes(lib.FMT_Q80, 5120) == 160 * 34
+    assert l.sb_row_bytes(lib.FMT_Q4K, 100) == 0
