@@ -132,12 +132,8 @@ def main():
         return
 
     from splash_b200 import lib, target
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from splash_b200.dist import Group
+    group = Group("nccl")
     lib.init(local)
     cfg = dict(target.TINY if args.tiny else target.QWEN27B)
     context = 2048 if args.tiny else CONTEXT
@@ -150,19 +146,10 @@ def main():
     t.upload(-1, "tokens", rng.integers(0, cfg["vocab"], ROWS).astype(np.uint32))
 
     def barrier():
-        if dist is not None:
-            import torch
-            dist.barrier()
-            torch.cuda.synchronize()
         lib.stream_sync(stream)
+        group.barrier()
 
-    def reduce_max(ms):
-        if dist is None:
-            return ms
-        import torch
-        v = torch.tensor([ms], device="cuda", dtype=torch.float64)
-        dist.all_reduce(v, op=dist.ReduceOp.MAX)
-        return float(v.item())
+    reduce_max = group.reduce_max
 
     # ---- device-resident steps ----
     for _ in range(warm):
@@ -203,8 +190,7 @@ def main():
     e2e_ms = reduce_max(e2.elapsed_ms(e3)) / args.steps
 
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+        group.close()
         return
 
     # ---- the dominant kernel alone: the one-pass Q4_K gate/up projection over each layer's weights ----
@@ -256,8 +242,7 @@ def main():
         "clocks": clocks, "device_status": status,
     }
     print(json.dumps(result))
-    if dist is not None:
-        dist.destroy_process_group()
+    group.close()
 
 
 if __name__ == "__main__":

@@ -74,7 +74,7 @@ __global__ void rope_kernel(const uint32_t *positions, uint32_t rows, const floa
   sine[i] = s * scale;
 }
 
-// ---- fp32 projection of plain fp32 rows: one block per output column; warp w takes rows 2w, 2w+1 ----
+// ---- fp32 projection of plain fp32 rows: grid (columns, 2); a warp per (column, row), lanes over k ----
 constexpr int kF32Rows = 16;
 __global__ void __launch_bounds__(256) linear_f32_kernel(const float *w, const uint16_t *x, uint32_t rows, uint32_t n,
                                                          uint32_t k, uint32_t x_stride, void *out, uint32_t out_stride,
@@ -82,45 +82,47 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const float *w, const u
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t col = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t r = blockIdx.y * 8 + warp;
+  if (r >= rows) return;
   const float *wr = w + size_t(col) * k;
-  for (uint32_t r = 2 * warp; r < min(rows, 2 * warp + 2); ++r) {
-    const uint16_t *xr = x + size_t(r) * x_stride;
-    float inv = 1.0f;
-    if (norm_w) {
-      float ss = 0.0f;
-      for (uint32_t c = 8 * lane; c < k; c += 256) {
-        const uint4 v = *reinterpret_cast<const uint4 *>(xr + c);
-        const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float a = bf16_bits_to_float(u[j] & 0xffffu), b = bf16_bits_to_float(u[j] >> 16);
-          ss = fmaf(a, a, fmaf(b, b, ss));
-        }
-      }
-#pragma unroll
-      for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-      inv = rsqrtf(ss / float(k) + 1e-6f);
-    }
-    // Lane-strided groups of 8 inputs, then a butterfly over the lanes.
-    float acc = 0.0f;
+  const uint16_t *xr = x + size_t(r) * x_stride;
+  float inv = 1.0f;
+  if (norm_w) {
+    float ss = 0.0f;
+#pragma unroll 4
     for (uint32_t c = 8 * lane; c < k; c += 256) {
       const uint4 v = *reinterpret_cast<const uint4 *>(xr + c);
-      const float4 w0 = *reinterpret_cast<const float4 *>(wr + c), w1 = *reinterpret_cast<const float4 *>(wr + c + 4);
       const uint32_t u[4] = {v.x, v.y, v.z, v.w};
-      const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float xv = bf16_bits_to_float((j & 1) ? (u[j >> 1] >> 16) : (u[j >> 1] & 0xffffu));
-        if (norm_w) xv = round_bf16((xv * inv) * norm_w[c + j]);
-        acc = fmaf(xv, wv[j], acc);
+      for (int j = 0; j < 4; ++j) {
+        const float a = bf16_bits_to_float(u[j] & 0xffffu), b = bf16_bits_to_float(u[j] >> 16);
+        ss = fmaf(a, a, fmaf(b, b, ss));
       }
     }
 #pragma unroll
-    for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (lane == 0) {
-      if (out_f32) static_cast<float *>(out)[size_t(r) * out_stride + col] = acc;
-      else static_cast<uint16_t *>(out)[size_t(r) * out_stride + col] = float_to_bf16_bits(acc);
+    for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    inv = rsqrtf(ss / float(k) + 1e-6f);
+  }
+  // Lane-strided groups of 8 inputs, then a butterfly over the lanes.
+  float acc = 0.0f;
+#pragma unroll 5
+  for (uint32_t c = 8 * lane; c < k; c += 256) {
+    const uint4 v = *reinterpret_cast<const uint4 *>(xr + c);
+    const float4 w0 = *reinterpret_cast<const float4 *>(wr + c), w1 = *reinterpret_cast<const float4 *>(wr + c + 4);
+    const uint32_t u[4] = {v.x, v.y, v.z, v.w};
+    const float wv[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float xv = bf16_bits_to_float((j & 1) ? (u[j >> 1] >> 16) : (u[j >> 1] & 0xffffu));
+      if (norm_w) xv = round_bf16((xv * inv) * norm_w[c + j]);
+      acc = fmaf(xv, wv[j], acc);
     }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (lane == 0) {
+    if (out_f32) static_cast<float *>(out)[size_t(r) * out_stride + col] = acc;
+    else static_cast<uint16_t *>(out)[size_t(r) * out_stride + col] = float_to_bf16_bits(acc);
   }
 }
 
@@ -440,7 +442,7 @@ int sb_linear_f32(void *stream, const float *w_dev, const void *x, uint32_t rows
   SB_REQUIRE(w_dev && x && out, "sb_linear_f32: null pointer");
   SB_REQUIRE(rows >= 1 && rows <= kF32Rows && n && k, "sb_linear_f32: rows = %u outside 1..%d, or empty shape", rows, kF32Rows);
   SB_REQUIRE(x_stride >= k && out_stride >= n && k % 8 == 0 && x_stride % 8 == 0, "sb_linear_f32: stride below extent, or k not a multiple of 8");
-  return launch(linear_f32_kernel, dim3(n), dim3(256), as_stream(stream), w_dev, static_cast<const uint16_t *>(x), rows, n, k,
+  return launch(linear_f32_kernel, dim3(n, (rows + 7) / 8), dim3(256), as_stream(stream), w_dev, static_cast<const uint16_t *>(x), rows, n, k,
                 x_stride, out, out_stride, out_f32, static_cast<const float *>(norm_weight));
 }
 
