@@ -10,8 +10,8 @@
 //             fused rows (row-major: fused = row * group + head_in_group, at most 128); warp w owns fused
 //             rows 16w..16w+15 as one m16 MMA tile, warps without rows only help loading.
 //   split     a contiguous run of 32-token chunks of the visible tokens [0, committed + rows)
-//   chunk     K and V rows (token-major int8, 32 x D bytes contiguous inside a page) are fetched with
-//             16-byte loads one chunk ahead, converted exactly to fp16 ((q ^ 0x80 | 0x6400) - 1152) and
+//   chunk     K and V rows (token-major int8, 32 x D bytes contiguous inside a page) and their scales arrive
+//             through a ring of bulk async copies three chunks ahead, are converted exactly to fp16 ((q ^ 0x80 | 0x6400) - 1152) and
 //             stored in shared memory; S = Q K^T and O += P V run on mma.sync m16n8k16 (fp16 operands,
 //             fp32 accumulators) with ldmatrix fragments; score = S * k_scale[token] / sqrt(D); row r sees
 //             tokens <= committed + r (and, with a tree, only its ancestors inside the block);
@@ -30,6 +30,7 @@ namespace sb {
 constexpr int kAttnThreads = 256;
 constexpr int kChunk = 32;       // tokens per step of the page loop
 constexpr int kMaxFused = 128;   // rows x query heads of one KV head
+constexpr int kRing = 4;         // raw chunks in flight per CTA
 
 struct AttnParams {
   const uint16_t *queries, *qkv;
@@ -75,11 +76,18 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnPa
   constexpr int KSTEPS = D / 16, NT_O = D / 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __half *q_s = reinterpret_cast<__half *>(smem_raw);              // [128][PITCH]
-  __half *k_s = q_s + kMaxFused * PITCH;                            // [32][PITCH]
-  __half *v_s = k_s + kChunk * PITCH;                               // [32][PITCH]
-  float *ks_s = reinterpret_cast<float *>(v_s + kChunk * PITCH);    // [32] key scales * 1/sqrt(D) * log2(e)
-  float *vs_s = ks_s + kChunk;                                      // [32]
+  // Converted chunks are double-buffered: while the m-tile warps multiply chunk i, every warp has already
+  // converted chunk i + 1 into the other buffer, so one barrier per chunk orders them.
+  __half *kv_s = q_s + kMaxFused * PITCH;                           // [2][K: 32 x PITCH, V: 32 x PITCH]
+  float *sc_s = reinterpret_cast<float *>(kv_s + 4 * kChunk * PITCH);  // [2][ks: 32, vs: 32]; ks holds scale / sqrt(D) * log2(e)
+  uint8_t *ring = reinterpret_cast<uint8_t *>(sc_s + 4 * kChunk);    // [kRing][2 * 32 * D + 256] raw chunks
+  uint64_t *full = reinterpret_cast<uint64_t *>(ring + kRing * (2 * kChunk * D + 256));
   __shared__ uint32_t s_last;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kRing; ++i) mbar_init(&full[i], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
   pdl_launch_dependents();
   pdl_wait();
 
@@ -131,67 +139,76 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnPa
     }
   }
 
-  // Chunk loader: thread -> (token = tid / 8, 32 bytes of the row at (tid % 8) * 32 ...). D bytes per
-  // token = D / 16 uint4; 32 tokens x D / 16 uint4 over 256 threads = D / 128 uint4 each, K and V.
-  constexpr int LD = D / 128;  // uint4 per thread per tensor
-  uint4 kreg[LD], vreg[LD];
-  float ksc = 0.0f, vsc = 0.0f;
-  auto fetch = [&](uint32_t chunk) {
-    const uint32_t tok0 = chunk * kChunk;
-#pragma unroll
-    for (int i = 0; i < LD; ++i) {
-      const uint32_t idx = tid + i * kAttnThreads, tok = idx / (D / 16), part = idx % (D / 16);
-      const uint32_t tk = tok0 + tok;
-      kreg[i] = make_uint4(0x80808080u ^ 0x80808080u, 0, 0, 0);
-      vreg[i] = make_uint4(0, 0, 0, 0);
-      if (tk < visible) {
-        const uint32_t page = p.page_table[tk / p.cache.page_tokens], pt = tk % p.cache.page_tokens;
-        const size_t slot = (size_t(page) * p.cache.kv_heads + kvh) * p.cache.page_tokens + pt;
-        kreg[i] = *reinterpret_cast<const uint4 *>(static_cast<const int8_t *>(p.cache.k) + slot * D + part * 16);
-        vreg[i] = *reinterpret_cast<const uint4 *>(static_cast<const int8_t *>(p.cache.v) + slot * D + part * 16);
-      }
-    }
-    if (tid < kChunk) {
-      const uint32_t tk = tok0 + tid;
-      ksc = 0.0f, vsc = 0.0f;
-      if (tk < visible) {
-        const uint32_t page = p.page_table[tk / p.cache.page_tokens], pt = tk % p.cache.page_tokens;
-        const size_t slot = (size_t(page) * p.cache.kv_heads + kvh) * p.cache.page_tokens + pt;
-        if (p.cache.scale_f16) {
-          ksc = __half2float(static_cast<const __half *>(p.cache.k_scale)[slot]);
-          vsc = __half2float(static_cast<const __half *>(p.cache.v_scale)[slot]);
-        } else {
-          ksc = static_cast<const float *>(p.cache.k_scale)[slot];
-          vsc = static_cast<const float *>(p.cache.v_scale)[slot];
-        }
-      }
-    }
+  // Chunk ring: thread 0 keeps kRing - 1 chunks in flight with bulk async copies (a chunk's 32 tokens are
+  // contiguous inside a page: D x 32 bytes of keys, of values, and their 32 scales each), completing on
+  // one mbarrier per slot. Every thread then converts its share of the landed chunk to fp16.
+  constexpr int LD = D / 128;  // 16-byte pieces per thread per tensor
+  const uint32_t sbytes = p.cache.scale_f16 ? 2u : 4u;
+  const uint32_t slot_bytes = 2 * kChunk * D + 256;
+  auto issue = [&](uint32_t chunk) {
+    const uint32_t s = (chunk - c_begin) % kRing, tk = chunk * kChunk;
+    const uint32_t page = p.page_table[tk / p.cache.page_tokens], pt = tk % p.cache.page_tokens;
+    const size_t slot = (size_t(page) * p.cache.kv_heads + kvh) * p.cache.page_tokens + pt;
+    uint8_t *dst = ring + s * slot_bytes;
+    fence_proxy_async();
+    mbar_arrive_expect_tx(&full[s], 2 * kChunk * D + 2 * kChunk * sbytes);
+    bulk_g2s(dst, static_cast<const int8_t *>(p.cache.k) + slot * D, kChunk * D, &full[s]);
+    bulk_g2s(dst + kChunk * D, static_cast<const int8_t *>(p.cache.v) + slot * D, kChunk * D, &full[s]);
+    bulk_g2s(dst + 2 * kChunk * D, static_cast<const uint8_t *>(p.cache.k_scale) + slot * sbytes, kChunk * sbytes, &full[s]);
+    bulk_g2s(dst + 2 * kChunk * D + 128, static_cast<const uint8_t *>(p.cache.v_scale) + slot * sbytes, kChunk * sbytes, &full[s]);
   };
   const float score_scale = (D == 256 ? 0.0625f : 0.08838834764831845f) * 1.44269504089f;  // 1/sqrt(D) * log2(e)
-  auto stage = [&]() {
+  auto stage = [&](uint32_t chunk) {
+    const uint8_t *src = ring + ((chunk - c_begin) % kRing) * slot_bytes;
+    const uint32_t buf = (chunk - c_begin) & 1;
+    __half *k_s = kv_s + buf * 2 * kChunk * PITCH, *v_s = k_s + kChunk * PITCH;
+    float *ks_s = sc_s + buf * 2 * kChunk, *vs_s = ks_s + kChunk;
 #pragma unroll
     for (int i = 0; i < LD; ++i) {
       const uint32_t idx = tid + i * kAttnThreads, tok = idx / (D / 16), part = idx % (D / 16);
       uint4 lo, hi;
-      int8x16_to_half(kreg[i], lo, hi);
+      int8x16_to_half(*reinterpret_cast<const uint4 *>(src + tok * D + part * 16), lo, hi);
       *reinterpret_cast<uint4 *>(k_s + tok * PITCH + part * 16) = lo;
       *reinterpret_cast<uint4 *>(k_s + tok * PITCH + part * 16 + 8) = hi;
-      int8x16_to_half(vreg[i], lo, hi);
+      int8x16_to_half(*reinterpret_cast<const uint4 *>(src + kChunk * D + tok * D + part * 16), lo, hi);
       *reinterpret_cast<uint4 *>(v_s + tok * PITCH + part * 16) = lo;
       *reinterpret_cast<uint4 *>(v_s + tok * PITCH + part * 16 + 8) = hi;
     }
     if (tid < kChunk) {
-      ks_s[tid] = ksc * score_scale;
-      vs_s[tid] = vsc;
+      // Tokens past the visible ones share the page but hold nothing: their scales read as zero.
+      const bool live = chunk * kChunk + tid < visible;
+      float ksc, vsc;
+      if (p.cache.scale_f16) {
+        ksc = __half2float(reinterpret_cast<const __half *>(src + 2 * kChunk * D)[tid]);
+        vsc = __half2float(reinterpret_cast<const __half *>(src + 2 * kChunk * D + 128)[tid]);
+      } else {
+        ksc = reinterpret_cast<const float *>(src + 2 * kChunk * D)[tid];
+        vsc = reinterpret_cast<const float *>(src + 2 * kChunk * D + 128)[tid];
+      }
+      ks_s[tid] = live ? ksc * score_scale : 0.0f;
+      vs_s[tid] = live ? vsc : 0.0f;
     }
   };
 
-  if (c_begin < c_end) fetch(c_begin);
-  for (uint32_t chunk = c_begin; chunk < c_end; ++chunk) {
-    __syncthreads();  // the previous chunk's readers are done (and q_s is written, first time)
-    stage();
-    __syncthreads();
-    if (chunk + 1 < c_end) fetch(chunk + 1);
+  if (tid == 0)
+    for (uint32_t c = c_begin; c < c_end && c < c_begin + kRing - 1; ++c) issue(c);
+  bool alive = true;
+  auto convert = [&](uint32_t chunk) {  // waits for the raw chunk, then converts this thread's share
+    if (!mbar_wait(&full[(chunk - c_begin) % kRing], ((chunk - c_begin) / kRing) & 1)) {
+      if (tid == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
+      alive = false;
+      return;
+    }
+    stage(chunk);
+  };
+  if (c_begin < c_end) convert(c_begin);
+  for (uint32_t chunk = c_begin; chunk < c_end && alive; ++chunk) {
+    __syncthreads();  // chunk is converted; the buffer chunk + 1 goes to and the raw slot refilled below are free
+    if (tid == 0 && chunk + kRing - 1 < c_end) issue(chunk + kRing - 1);
+    if (chunk + 1 < c_end) convert(chunk + 1);
+    const uint32_t buf = (chunk - c_begin) & 1;
+    const __half *k_s = kv_s + buf * 2 * kChunk * PITCH, *v_s = k_s + kChunk * PITCH;
+    const float *ks_s = sc_s + buf * 2 * kChunk, *vs_s = ks_s + kChunk;
     if (!computes) continue;
     const uint32_t tok0 = chunk * kChunk;
     // S = Q K^T for 16 fused rows x 32 tokens.
@@ -403,7 +420,8 @@ extern "C" int sb_attn_verify(void *stream, const SbAttnArgs *a) {
   p.committed_dev = a->committed_dev;
   p.rows = a->rows, p.q_heads = a->q_heads, p.group = group, p.gated = a->gated, p.qkv_stride = a->qkv_stride;
   p.out_stride = a->out_stride, p.committed = a->committed, p.splits = splits, p.chunks_per_split = cps, p.fused = fused;
-  const size_t smem = size_t(kMaxFused + 2 * kChunk) * (D + 8) * 2 + 2 * kChunk * sizeof(float);
+  const size_t smem = size_t(kMaxFused + 4 * kChunk) * (D + 8) * 2 + 4 * kChunk * sizeof(float) +
+                      size_t(kRing) * (2 * kChunk * D + 256) + kRing * sizeof(uint64_t);
   void (*kernel)(const AttnParams) = D == 256 ? attention_kernel<256> : attention_kernel<128>;
   static bool attr_set[2] = {false, false};
   if (!attr_set[D == 256]) {

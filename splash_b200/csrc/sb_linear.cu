@@ -12,7 +12,7 @@
 // Layout of one launch
 //   prepare   a small kernel converts the 16 x K activations once (optionally through a fused
 //             RMSNorm) to fp16 with a per-row power-of-two scale, in MMA fragment order
-//   grid      one persistent CTA per SM in clusters of S (the k-slice count), 352 threads:
+//   grid      one persistent CTA per SM (a multiple of the k-slice count), 320 threads:
 //             warps 0..7 consume, warp 8 produces, warp 9 finishes tiles
 //   k-slices  K's super-blocks are cut into S contiguous slices; a CTA owns one slice for the whole
 //             launch and keeps its slice of the prepared activations resident in shared memory
@@ -27,11 +27,10 @@
 //   Q6_K      operand = fp16(sc*(q-32)) (one rounding when |.| > 2048); y += d*Aq per super-block
 //   Q8_0      operand = fp16(d*q), the value the reference's staged tile rounds to
 //   reduce    the epilogue warp adds the 4 k-group warps' sums in order from shared memory while the
-//             consumers start the next tile; with S > 1 the S CTAs of a thread-block cluster (one per
-//             slice) reduce-scatter the tile through distributed shared memory and each adds the
-//             slices' sums of its rows in slice order - the fixed-order split sum of
-//             runtime/metal/kernels/common/split_reduce.h:24-55 without a trip through device memory -
-//             then applies the epilogue (runtime/metal/kernels/common/gguf_tile.h:8-14, gguf_linear.metal:38)
+//             consumers start the next tile; with S > 1 the slices publish fp32 partials and the
+//             last arriver adds them in slice order
+//             (runtime/metal/kernels/common/split_reduce.h:24-55), then applies the epilogue
+//             (runtime/metal/kernels/common/gguf_tile.h:8-14, gguf_linear.metal:38)
 #include <algorithm>
 
 #include <cuda.h>
@@ -61,7 +60,8 @@ struct LinearParams {
   const uint8_t *w, *w2, *prepared;
   const uint16_t *aux;
   void *out;
-  uint32_t *status;
+  float *partials;
+  uint32_t *counters, *status;
   uint32_t n, k, rows, aux_stride, out_stride, epilogue, out_f32;
   uint32_t nsb, slices, tiles, stages, row_bytes, pitch, stage_bytes;
   // Tiled-TMA geometry. A tensor's rows are served by `period` maps, map j holding rows = j (mod
@@ -69,8 +69,7 @@ struct LinearParams {
   // pieces of `piece_sb` super-blocks, each piece one box per (tensor, map): box_rows x pitch bytes.
   uint32_t period, period_log2, pieces, piece_sb, box_rows, box_bytes, tensors;
   uint32_t lead[2][8];  // bytes between map j's 16-byte aligned base and its first row's first byte
-  uint32_t x_off, red_off, recv_off, ring_off;  // shared memory offsets
-  uint32_t slices_log2;
+  uint32_t x_off, red_off, ring_off;  // shared memory offsets
   uint32_t debug;
 };
 
@@ -497,7 +496,6 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams 
   uint64_t *xfull = empty + kMaxStages;
   uint64_t *red_full = xfull + 1;   // [2], one per epilogue warp
   uint64_t *red_empty = xfull + 3;  // [2]
-  uint64_t *recv_full = xfull + 5;  // [2], one per tile parity: the cluster's S epilogue warps arrive
   float *scale_back = reinterpret_cast<float *>(smem + 192);  // 16 floats, copied from the prepared header
   constexpr uint32_t kSb = WFmt<FMT>::kSbBytes;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -517,12 +515,10 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams 
     for (int e = 0; e < 2; ++e) {
       mbar_init(&red_full[e], kConsumerWarps);
       mbar_init(&red_empty[e], 1);
-      mbar_init(&recv_full[e], p.slices);
     }
     fence_mbar_init();
   }
   __syncthreads();
-  cluster_sync();  // every CTA of the cluster has its barriers before any peer arrives on them
   pdl_launch_dependents();
 
   if (warp == kConsumerWarps) {
@@ -578,122 +574,129 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams 
   float *red = reinterpret_cast<float *>(smem + p.red_off);
 
   if (warp > kConsumerWarps) {
-    // ---- epilogue warp. It adds the tile's k-group warps' sums in order; with S > 1 slices the S CTAs of
-    // the cluster (one per slice, working on the same tile) then reduce-scatter their partial tiles through
-    // distributed shared memory: rank d finishes 64 / S of the tile's rows (for a gate/up tile 32 / S
-    // columns, their gate and up rows), receiving every rank's sums for them - its own included - into
-    // recv[parity][source rank][token][row] and adding the sources in rank order. Lane l holds token l / 2
-    // and tile rows 32 (l % 2) .. + 31 of this CTA's partial. ----
-    if (warp != kConsumerWarps + 1) return;
-    pdl_wait();  // aux and out belong to the stream's earlier kernels until they finish
-    const uint32_t S = p.slices, lg = p.slices_log2;
+    // ---- epilogue warps: tile i of this CTA belongs to epilogue warp i % 2. Each adds the k-group
+    // warps' sums in order, exchanges split-K partials and stores. Lane l owns token l / 2 and tile
+    // rows 32 (l % 2) .. + 31, so every global access of a lane is 64 or 128 contiguous bytes. ----
+    const uint32_t ew = warp - kConsumerWarps - 1;
+    pdl_wait();  // aux / out / partials belong to the stream's earlier kernels until they finish
+    const uint32_t pcols = gate_up ? 2 * p.n : p.n;
     const uint32_t tok = lane >> 1, half = lane & 1;
     if (!mbar_wait_backoff(xfull, 0)) { if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED); return; }
     const float sback = scale_back[tok];
-    float *recv = reinterpret_cast<float *>(smem + p.recv_off);
-    const uint32_t own = uint32_t(kTileRows) >> lg;  // rows a rank finishes per token
     uint32_t done = 0;
     for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++done) {
-      const uint32_t tile = item / S, pair = done & 1;
-      if (!mbar_wait_backoff(&red_full[pair], (done >> 1) & 1)) { if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED); return; }
+      if ((done & 1) != ew || (p.debug & 8)) continue;
+      const uint32_t tile = item / p.slices;
+      if (!mbar_wait_backoff(&red_full[ew], (done >> 1) & 1)) { if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED); return; }
       float v[32];
 #pragma unroll
       for (int r = 0; r < 32; ++r) {
-        float sum = 0.0f;
+        float s = 0.0f;
 #pragma unroll
-        for (int k = 0; k < kKG; ++k) sum += red[((half * kKG + k) * 32 + r) * kRedPitch + tok];
-        v[r] = sum * sback;
+        for (int k = 0; k < kKG; ++k) s += red[((half * kKG + k) * 32 + r) * kRedPitch + tok];
+        v[r] = s * sback;
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&red_empty[pair]);
-
-      // What this lane finishes: `cnt` values fin[0..cnt) (plain: consecutive columns from col; gate/up:
-      // gate sums in fin[0..cnt), up sums in fup[0..cnt) of columns col..).
-      float fin[32], fup[16];
-      uint32_t cnt, col;
-      if (S == 1) {
-        if (gate_up) {
-          // Lane (tok, 0) holds the gate sums, lane (tok, 1) the up sums of the same 32 columns: swap halves.
-          cnt = 16, col = tile * 32 + 16 * half;
+      if (lane == 0) mbar_arrive(&red_empty[ew]);
+      // First column of the lane's 32 values in the partials; gate/up tiles hold 32 gate rows then the
+      // 32 up rows of the same 32 columns.
+      const uint32_t c0 = gate_up ? tile * 32 : tile * kTileRows + 32 * half;
+      const uint32_t pc0 = gate_up ? c0 + half * p.n : c0;
+      const bool col_ok = c0 < p.n;  // n is a multiple of 32: a 32-column run is inside or outside
+      bool finish = true;
+      if (p.slices > 1) {
+        if (col_ok) {
+          float4 *pp = reinterpret_cast<float4 *>(p.partials + (size_t(slice) * kTokens + tok) * pcols + pc0);
 #pragma unroll
-          for (int r = 0; r < 16; ++r) {
-            const float lo = v[r], hi = v[16 + r];
-            const float got = __shfl_xor_sync(0xffffffffu, half ? lo : hi, 1);
-            fin[r] = half ? got : lo;
-            fup[r] = half ? hi : got;
-          }
-        } else {
-          cnt = 32, col = tile * kTileRows + 32 * half;
-#pragma unroll
-          for (int r = 0; r < 32; ++r) fin[r] = v[r];
+          for (int q = 0; q < 8; ++q) pp[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         }
-      } else {
-        const uint32_t per = 32u >> lg;  // gate/up: columns a rank finishes
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          uint32_t dest, j;
-          if (gate_up) dest = uint32_t(i) >> (5 - lg), j = half * per + (uint32_t(i) & (per - 1));
-          else dest = (32 * half + uint32_t(i)) >> (6 - lg), j = (32 * half + uint32_t(i)) & (own - 1);
-          float *slot = recv + (((pair * S + slice) * kTokens + tok) * own + j);
-          st_cluster_f32x4(map_to_rank(slot, dest), v[i], v[i + 1], v[i + 2], v[i + 3]);
-        }
-        fence_cluster();
+        __threadfence();
         __syncwarp();
-        if (lane < S) mbar_arrive_cluster(map_to_rank(&recv_full[pair], lane));
-        if (!mbar_wait_cluster(&recv_full[pair], (done >> 1) & 1)) { if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED); return; }
-        const float *mine = recv + (pair * S * kTokens + tok) * own;  // + source * kTokens * own
-        if (gate_up) {
-          cnt = per >> 1, col = tile * 32 + slice * per + half * cnt;
+        uint32_t arrived = 0;
+        if (lane == 0) arrived = atomicAdd(&p.counters[tile], 1u);
+        arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        finish = arrived == p.slices - 1;
+        if (finish) {
+          __threadfence();
+          if (col_ok) {
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            if (uint32_t(q) >= cnt) break;
-            float g = 0.0f, u = 0.0f;
-            for (uint32_t src = 0; src < S; ++src) {
-              g += mine[src * kTokens * own + half * cnt + q];
-              u += mine[src * kTokens * own + per + half * cnt + q];
+            for (int r = 0; r < 32; ++r) v[r] = 0.0f;
+            for (uint32_t sl = 0; sl < p.slices; ++sl) {
+              const float4 *pp = reinterpret_cast<const float4 *>(p.partials + (size_t(sl) * kTokens + tok) * pcols + pc0);
+              float4 q[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) q[i] = __ldcg(pp + i);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                v[4 * i] += q[i].x, v[4 * i + 1] += q[i].y, v[4 * i + 2] += q[i].z, v[4 * i + 3] += q[i].w;
+              }
             }
-            fin[q] = g, fup[q] = u;
           }
-        } else {
-          cnt = own >> 1, col = tile * kTileRows + slice * own + half * cnt;
-#pragma unroll
-          for (int q = 0; q < 16; ++q) {
-            if (uint32_t(q) >= cnt) break;
-            float t = 0.0f;
-            for (uint32_t src = 0; src < S; ++src) t += mine[src * kTokens * own + half * cnt + q];
-            fin[q] = t;
-          }
+          if (lane == 0) p.counters[tile] = 0;
         }
       }
-      if (tok >= p.rows || col >= p.n) continue;  // n is a multiple of 32: a lane's run is inside or outside
-      // Epilogue and stores, two values at a time.
+      if (!finish) continue;
       if (gate_up) {
-        uint16_t *op = static_cast<uint16_t *>(p.out) + size_t(tok) * p.out_stride + col;
+        // Lane (tok, 0) holds the gate sums, lane (tok, 1) the up sums of the same 32 columns: swap
+        // halves so each lane finishes 16 columns.
+        float gsum[16], usum[16];
 #pragma unroll
-        for (int q = 0; q < 16; q += 2) {
-          if (uint32_t(q) >= cnt) break;
-          const float o0 = round_bf16(fup[q]) * silu_f(round_bf16(fin[q]));
-          const float o1 = round_bf16(fup[q + 1]) * silu_f(round_bf16(fin[q + 1]));
-          *reinterpret_cast<uint32_t *>(op + q) = uint32_t(float_to_bf16_bits(o0)) | (uint32_t(float_to_bf16_bits(o1)) << 16);
+        for (int r = 0; r < 16; ++r) {
+          const float mine_lo = v[r], mine_hi = v[16 + r];
+          const float send = half ? mine_lo : mine_hi;       // what the partner needs
+          const float got = __shfl_xor_sync(0xffffffffu, send, 1);
+          gsum[r] = half ? got : mine_lo;                      // gate of column 16*half + r
+          usum[r] = half ? mine_hi : got;                      // up of column 16*half + r
+        }
+        if (col_ok && tok < p.rows) {
+          uint32_t pk[8];
+#pragma unroll
+          for (int r = 0; r < 8; ++r) {
+            const float o0 = round_bf16(usum[2 * r]) * silu_f(round_bf16(gsum[2 * r]));
+            const float o1 = round_bf16(usum[2 * r + 1]) * silu_f(round_bf16(gsum[2 * r + 1]));
+            pk[r] = uint32_t(float_to_bf16_bits(o0)) | (uint32_t(float_to_bf16_bits(o1)) << 16);
+          }
+          uint4 *op = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.out) + size_t(tok) * p.out_stride + c0 + 16 * half);
+          op[0] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          op[1] = make_uint4(pk[4], pk[5], pk[6], pk[7]);
         }
         continue;
       }
-      const uint16_t *ap = p.aux ? p.aux + size_t(tok) * p.aux_stride + col : nullptr;
+      if (!col_ok || tok >= p.rows) continue;
+      if (p.epilogue == SB_EPILOGUE_RESIDUAL || p.epilogue == SB_EPILOGUE_UP_WITH_GATE) {
+        const uint4 *ap = reinterpret_cast<const uint4 *>(p.aux + size_t(tok) * p.aux_stride + c0);
 #pragma unroll
-      for (int q = 0; q < 32; q += 2) {
-        if (uint32_t(q) >= cnt) break;
-        float a = fin[q], b = fin[q + 1];
-        if (p.epilogue == SB_EPILOGUE_RESIDUAL || p.epilogue == SB_EPILOGUE_UP_WITH_GATE) {
-          const uint32_t x2 = *reinterpret_cast<const uint32_t *>(ap + q);
-          const float xa = bf16_bits_to_float(x2 & 0xffffu), xb = bf16_bits_to_float(x2 >> 16);
-          if (p.epilogue == SB_EPILOGUE_RESIDUAL) a += xa, b += xb;
-          else a = round_bf16(a) * silu_f(xa), b = round_bf16(b) * silu_f(xb);
+        for (int q = 0; q < 4; ++q) {
+          const uint4 a4 = ap[q];
+          const uint32_t u[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float xa = bf16_bits_to_float(u[i] & 0xffffu), xb = bf16_bits_to_float(u[i] >> 16);
+            float &a = v[8 * q + 2 * i], &b = v[8 * q + 2 * i + 1];
+            if (p.epilogue == SB_EPILOGUE_RESIDUAL) {
+              a += xa;
+              b += xb;
+            } else {
+              a = round_bf16(a) * silu_f(xa);
+              b = round_bf16(b) * silu_f(xb);
+            }
+          }
         }
-        if (p.out_f32)
-          *reinterpret_cast<float2 *>(static_cast<float *>(p.out) + size_t(tok) * p.out_stride + col + q) = make_float2(a, b);
-        else
-          *reinterpret_cast<uint32_t *>(static_cast<uint16_t *>(p.out) + size_t(tok) * p.out_stride + col + q) =
-              uint32_t(float_to_bf16_bits(a)) | (uint32_t(float_to_bf16_bits(b)) << 16);
+      }
+      if (p.out_f32) {
+        float4 *op = reinterpret_cast<float4 *>(static_cast<float *>(p.out) + size_t(tok) * p.out_stride + c0);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) op[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+      } else {
+        uint4 *op = reinterpret_cast<uint4 *>(static_cast<uint16_t *>(p.out) + size_t(tok) * p.out_stride + c0);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            pk[i] = uint32_t(float_to_bf16_bits(v[8 * q + 2 * i])) | (uint32_t(float_to_bf16_bits(v[8 * q + 2 * i + 1])) << 16);
+          op[q] = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
       }
     }
     return;
@@ -783,13 +786,11 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams 
 
 // ---- host side ----
 static uint32_t pick_slices(uint32_t nsb, uint32_t sb_bytes) {
-  // Activations of a slice stay resident: at most kMaxSliceSb super-blocks, fewer where a format's wider
-  // stages need the room. The slices of a tile are the CTAs of one cluster, which reduce-scatter the tile's
-  // 64 rows: a power of two up to 8 (the portable cluster size).
-  const uint32_t cap = sb_bytes > 250 ? 6 : sb_bytes > 160 ? 9 : kMaxSliceSb;
-  uint32_t s = 1;
-  while (s < 8 && (nsb + s - 1) / s > cap) s *= 2;
-  return s;
+  // Activations of a slice stay resident: at most kMaxSliceSb super-blocks, fewer where a format's
+  // wider stages need the room.
+  const uint32_t cap = sb_bytes > 250 ? 6 : sb_bytes > 160 ? 8 : kMaxSliceSb;
+  const uint32_t s = (nsb + cap - 1) / cap;
+  return s < 1 ? 1 : s;
 }
 
 static int make_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t epilogue, LinearParams &p, SbLinearPlan &plan) {
@@ -801,8 +802,6 @@ static int make_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t epilogue,
   const uint32_t sb_bytes = format == SB_FMT_Q4K ? 144 : format == SB_FMT_Q6K ? 210 : 272;
   p.nsb = k / 256;
   p.slices = pick_slices(p.nsb, sb_bytes);
-  p.slices_log2 = p.slices == 1 ? 0 : p.slices == 2 ? 1 : p.slices == 4 ? 2 : 3;
-  SB_REQUIRE((p.nsb + p.slices - 1) / p.slices <= 12, "sb_linear: k = %u needs more than 8 slices", k);
   p.tiles = gate_up ? (n + 31) / 32 : (n + kTileRows - 1) / kTileRows;
   p.row_bytes = uint32_t(sb_row_bytes(format, k));
   // Stage geometry. Q4_K rows are 16-byte multiples: one map, one box of 64 x 144 bytes per
@@ -829,8 +828,7 @@ static int make_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t epilogue,
   const uint32_t slice_max = (p.nsb + p.slices - 1) / p.slices;
   p.x_off = 256;
   p.red_off = p.x_off + slice_max * kPrepSbBytes;
-  p.recv_off = (p.red_off + kConsumerWarps * 32 * kRedPitch * 4 + 15) & ~15u;
-  p.ring_off = (p.recv_off + 2 * kTokens * kTileRows * 4 + 127) & ~127u;
+  p.ring_off = (p.red_off + kConsumerWarps * 32 * kRedPitch * 4 + 127) & ~127u;
   const uint32_t budget = 227 * 1024;
   SB_REQUIRE(p.ring_off + 2 * p.stage_bytes <= budget, "sb_linear: shared memory plan does not fit (k = %u)", k);
   p.stages = std::min(uint32_t(kMaxStages), (budget - p.ring_off) / p.stage_bytes);
@@ -946,6 +944,10 @@ extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
                    (reinterpret_cast<uintptr_t>(a->weights2) & 15) == 0,
                "sb_linear: Q4_K weights must be 16-byte aligned");
   Context &c = ctx();
+  const uint32_t pcols = a->epilogue == SB_EPILOGUE_GATE_UP ? 2 * a->n : a->n;
+  SB_REQUIRE(p.slices == 1 || size_t(p.slices) * kTokens * pcols * 4 <= c.linear_partials_bytes,
+             "sb_linear: split-K scratch too small for n = %u with %u slices", a->n, p.slices);
+  SB_REQUIRE(p.tiles <= c.linear_counter_count, "sb_linear: too many tiles (%u)", p.tiles);
   const bool pdl = (a->flags & SB_LINEAR_PDL) != 0;
   const void *prepared = a->prepared;
   if (!prepared) {
@@ -961,6 +963,8 @@ extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
   p.prepared = static_cast<const uint8_t *>(prepared);
   p.aux = static_cast<const uint16_t *>(a->aux);
   p.out = a->out;
+  p.partials = c.linear_partials;
+  p.counters = c.linear_counters;
   p.status = c.status_dev;
   p.n = a->n, p.k = a->k, p.rows = a->rows;
   p.aux_stride = a->aux_stride, p.out_stride = a->out_stride;
@@ -990,25 +994,11 @@ extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
   cfg.blockDim = dim3(kThreads);
   cfg.dynamicSmemBytes = plan.smem_bytes;
   cfg.stream = as_stream(stream);
-  cudaLaunchAttribute attr[2];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = p.slices, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
-  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 2 : 1;
-  if (p.slices > 1) {
-    // A persistent grid: no more clusters than the device holds at once.
-    static int active[3][4] = {};
-    int &n = active[ki][p.slices_log2];
-    if (n == 0) {
-      cfg.numAttrs = 1;
-      SB_CUDA(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
-      cfg.numAttrs = pdl ? 2 : 1;
-      SB_REQUIRE(n > 0, "sb_linear: no cluster of %u CTAs with %u bytes of shared memory fits this device", p.slices, plan.smem_bytes);
-    }
-    cfg.gridDim = dim3(std::min(plan.ctas, uint32_t(n) * p.slices));
-  }
+  cfg.numAttrs = pdl ? 1 : 0;
   SB_CUDA(cudaLaunchKernelEx(&cfg, kernel, p, maps));
   return SB_OK;
 }

@@ -58,38 +58,6 @@ __device__ __forceinline__ bool mbar_wait_backoff(uint64_t *bar, uint32_t parity
   return false;
 }
 
-// ---- thread-block clusters: distributed shared memory ----
-__device__ __forceinline__ void cluster_sync() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// The shared::cluster address of `p` (an address in this CTA's shared memory) in the CTA of rank `rank`.
-__device__ __forceinline__ uint32_t map_to_rank(const void *p, uint32_t rank) {
-  uint32_t r;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
-  return r;
-}
-__device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, float a, float b, float c, float d) {
-  asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
-__device__ __forceinline__ void fence_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar) : "memory");
-}
-// Bounded wait with cluster-scope acquire: pairs with mbar_arrive_cluster of peers that wrote this CTA's memory.
-__device__ __forceinline__ bool mbar_wait_cluster(uint64_t *bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    uint32_t ok;
-    asm volatile(
-        "{ .reg .pred p; mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    if (ok) return true;
-    __nanosleep(32);
-  }
-  return false;
-}
-
 // Global -> shared bulk copy completing on an mbarrier. Both addresses 16-byte aligned, bytes a
 // multiple of 16. No multicast anywhere in this library.
 __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {
