@@ -266,6 +266,19 @@ typedef struct SbGdnArgs {
 } SbGdnArgs;
 SB_API int sb_gdn_verify(void *stream, const SbGdnArgs *args);
 
+/* sb_gdn_verify for callers that cannot allocate device memory: a process whose GPU memory is already handed out
+ * in full to its own arena, a plugin inside one, code running under a fixed memory budget. It has no counterpart
+ * in the reference. Same arguments and results as sb_gdn_verify; it needs no sb_init and calls no cudaMalloc,
+ * cudaFree or any other allocating routine. Its scratch (the recurrent rows awaiting their gate and one arrival
+ * counter per value head, 256 KiB + 256 bytes) is an array built into the library, so every GPU that loads the
+ * library holds it until the process exits, and the shape is limited to 64 value heads (more fails with
+ * SB_ERR_INVALID).
+ * The first call on each device looks up the array's device address (with that device current); make that first
+ * call outside any stream capture. All calls share the one array: it keeps the previous call's contents (this
+ * call clears the counters it needs at zero on `stream`), and two calls that overlap on the GPU - different
+ * streams, or concurrent processes' threads on one context - race on it. */
+SB_API int sb_gdn_verify_static(void *stream, const SbGdnArgs *args);
+
 /* ---- selection and acceptance ---- */
 
 /* Selection of every row of one lane's chain. temperature 0: greedy (largest finite logit, ties to the

@@ -255,6 +255,37 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_kernel(const GdnParams p) {
   if (tid == 0) p.counters[h] = 0;
 }
 
+
+// ---- the same step with no allocation anywhere ----
+// Some hosts of this library may not allocate device memory at all once they are running: a runtime that
+// reserved the whole GPU for its own arena up front, a plugin loaded into such a process, or code that runs
+// where cudaMalloc would fail or stall (inside a memory-pool callback, under a fixed memory budget). The
+// regular entry point uses two pieces of scratch that sb_init allocated: the recurrent rows awaiting their
+// gate and one arrival counter per value head. This variant keeps both in a fixed array that is part of the
+// library image, so every GPU that loads the library holds kStaticScratchBytes of it until the process exits.
+constexpr uint32_t kStaticMaxValueHeads = 64;  // the 27B shape has 48
+constexpr size_t kStaticRowsBytes = size_t(kStaticMaxValueHeads) * kGdnRows * kD * sizeof(uint16_t);  // 256 KiB
+constexpr size_t kStaticScratchBytes = kStaticRowsBytes + kStaticMaxValueHeads * sizeof(uint32_t);
+static __device__ __align__(256) uint8_t g_gdn_static_scratch[kStaticScratchBytes];
+
+// In host code the array's name only stands for the symbol; the address a kernel can use comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+static int static_scratch_address(uint8_t **out) {
+  constexpr int kMaxDevices = 64;
+  static uint8_t *address[kMaxDevices] = {};
+  int device = -1;
+  SB_CUDA(cudaGetDevice(&device));
+  SB_REQUIRE(device >= 0 && device < kMaxDevices, "sb_gdn_verify_static: device index %d outside 0..%d", device, kMaxDevices - 1);
+  if (!address[device]) {
+    void *p = nullptr;
+    SB_CUDA(cudaGetSymbolAddress(&p, g_gdn_static_scratch));
+    SB_REQUIRE(p != nullptr, "sb_gdn_verify_static: the scratch symbol has no address on device %d", device);
+    address[device] = static_cast<uint8_t *>(p);
+  }
+  *out = address[device];
+  return SB_OK;
+}
+
 }  // namespace sb
 
 using namespace sb;
@@ -275,7 +306,7 @@ extern "C" int sb_gdn_verify(void *stream, const SbGdnArgs *a) {
   SB_REQUIRE(a->rows == 0 || (a->step.inputs && a->step.k && a->step.v && a->step.beta && a->step.decay), "sb_gdn_verify: null tape of this step");
   SB_REQUIRE((a->pending_rows == 0 && !a->pending_rows_dev) || (a->pending.inputs && a->pending.k && a->pending.v && a->pending.beta && a->pending.decay),
              "sb_gdn_verify: null pending tape");
-  SB_REQUIRE(a->state_in != a->state_out, "sb_gdn_verify: the committed state goes to a second cell");
+  SB_REQUIRE(a->state_in != a->state_out && a->conv_state_in != a->conv_state_out, "sb_gdn_verify: the committed cell is a second cell");
   Context &c = ctx();
   GdnParams p{*a, c.gdn_scratch, c.gdn_counters};
   cudaLaunchConfig_t cfg = {};
@@ -288,5 +319,37 @@ extern "C" int sb_gdn_verify(void *stream, const SbGdnArgs *a) {
   cfg.attrs = attr;
   cfg.numAttrs = c.pdl ? 1 : 0;
   SB_CUDA(cudaLaunchKernelEx(&cfg, gdn_kernel, p));
+  return SB_OK;
+}
+
+extern "C" int sb_gdn_verify_static(void *stream, const SbGdnArgs *a) {
+  SB_REQUIRE(a, "sb_gdn_verify_static: null arguments");
+  SB_REQUIRE(a->qkvz && a->b && a->a && a->conv_w && a->a_scale && a->dt_bias && a->norm_w && a->conv_state_in &&
+                 a->conv_state_out && a->state_in && a->state_out && a->hidden,
+             "sb_gdn_verify_static: null pointer");
+  SB_REQUIRE(a->value_heads <= kStaticMaxValueHeads,
+             "sb_gdn_verify_static: %u value heads exceed the %u the built-in scratch holds; use sb_gdn_verify", a->value_heads,
+             kStaticMaxValueHeads);
+  SB_REQUIRE(a->rows <= kGdnRows && a->pending_rows <= kGdnRows, "sb_gdn_verify_static: rows %u or pending rows %u above %d", a->rows,
+             a->pending_rows, kGdnRows);
+  SB_REQUIRE(a->key_heads >= 1 && a->value_heads >= 1 && a->value_heads % a->key_heads == 0, "sb_gdn_verify_static: %u value heads over %u key heads",
+             a->value_heads, a->key_heads);
+  const uint32_t C = (2 * a->key_heads + a->value_heads) * kD;
+  SB_REQUIRE(a->qkvz_stride >= C + a->value_heads * kD && a->ab_stride >= a->value_heads && a->hidden_stride >= a->value_heads * kD,
+             "sb_gdn_verify_static: a stride is below its row");
+  SB_REQUIRE(a->rows == 0 || (a->step.inputs && a->step.k && a->step.v && a->step.beta && a->step.decay), "sb_gdn_verify_static: null tape of this step");
+  SB_REQUIRE((a->pending_rows == 0 && !a->pending_rows_dev) || (a->pending.inputs && a->pending.k && a->pending.v && a->pending.beta && a->pending.decay),
+             "sb_gdn_verify_static: null pending tape");
+  SB_REQUIRE(a->state_in != a->state_out && a->conv_state_in != a->conv_state_out, "sb_gdn_verify_static: the committed cell is a second cell");
+  uint8_t *scratch = nullptr;
+  const int st = static_scratch_address(&scratch);
+  if (st != SB_OK) return st;
+  // The array keeps whatever the last call left. The arrival counters must start at zero; the rows are
+  // written in full before they are read.
+  uint32_t *counters = reinterpret_cast<uint32_t *>(scratch + kStaticRowsBytes);
+  SB_CUDA(cudaMemsetAsync(counters, 0, kStaticMaxValueHeads * sizeof(uint32_t), as_stream(stream)));
+  GdnParams p{*a, reinterpret_cast<uint16_t *>(scratch), counters};
+  gdn_kernel<<<dim3(kGdnSplit, a->value_heads), dim3(kGdnThreads), 0, as_stream(stream)>>>(p);
+  SB_CUDA(cudaGetLastError());
   return SB_OK;
 }

@@ -226,6 +226,7 @@ def _bind_ops():
     l.sb_attn_verify.argtypes = [_P, ctypes.POINTER(SbAttnArgs)]
     l.sb_kv_path_commit.argtypes = [_P, ctypes.POINTER(SbKvLayer), _P, _U, _P]
     l.sb_gdn_verify.argtypes = [_P, ctypes.POINTER(SbGdnArgs)]
+    l.sb_gdn_verify_static.argtypes = [_P, ctypes.POINTER(SbGdnArgs)]
     l.sb_sample_workspace_bytes.restype = ctypes.c_uint64
     l.sb_sample_workspace_bytes.argtypes = [_U, _U]
     l.sb_sample_verify.argtypes = [_P, ctypes.POINTER(SbSampleArgs)]
