@@ -1,0 +1,172 @@
+"""Single-operator cases on seeded synthetic inputs, timed with CUDA events: the small commands the ncu
+summaries under profiles/ were captured from, and a quick way to time one kernel on a shape.
+
+    python -m splash_b200.cases linear --fmt q4k --n 17408 --k 5120 --epilogue gate_up [--iters 20]
+    python -m splash_b200.cases attention --context 32768 [--q-heads 24 --kv-heads 4 --head-dim 256]
+    python -m splash_b200.cases gdn [--key-heads 16 --value-heads 48]
+
+Weights are random native blocks with scale fields in the ranges the tests use (Q4_K / Q8_0 d, dmin in
+U(5e-4, 4e-3); Q6_K d in U(2e-5, 1e-4)); several copies rotate so every launch streams from HBM, not L2."""
+import argparse
+import ctypes
+import sys
+
+import numpy as np
+
+from . import lib
+
+FMT = {"q4k": lib.FMT_Q4K, "q6k": lib.FMT_Q6K, "q80": lib.FMT_Q80}
+EPI = {"none": lib.EP_NONE, "residual": lib.EP_RESIDUAL, "gate_up": lib.EP_GATE_UP}
+
+
+def bf16_bits(x):
+    v = np.ascontiguousarray(x, np.float32).view(np.uint32).astype(np.uint64)
+    return (((v + 0x7FFF + ((v >> 16) & 1)) >> 16) & 0xFFFF).astype(np.uint16)
+
+
+def native_rows(rng, fmt, n, k):
+    """Random native rows with plausible half scales (other bytes uniform)."""
+    if fmt == lib.FMT_Q4K:
+        nb, bb = k // 256, 144
+        blk = rng.integers(0, 256, (n, nb, bb), dtype=np.uint8)
+        blk[..., 0:2] = rng.uniform(5e-4, 4e-3, (n, nb)).astype(np.float16).view(np.uint8).reshape(n, nb, 2)
+        blk[..., 2:4] = rng.uniform(5e-4, 4e-3, (n, nb)).astype(np.float16).view(np.uint8).reshape(n, nb, 2)
+    elif fmt == lib.FMT_Q6K:
+        nb, bb = k // 256, 210
+        blk = rng.integers(0, 256, (n, nb, bb), dtype=np.uint8)
+        blk[..., 208:210] = rng.uniform(2e-5, 1e-4, (n, nb)).astype(np.float16).view(np.uint8).reshape(n, nb, 2)
+    else:
+        nb, bb = k // 32, 34
+        blk = rng.integers(0, 256, (n, nb, bb), dtype=np.uint8)
+        blk[..., 0:2] = rng.uniform(5e-4, 4e-3, (n, nb)).astype(np.float16).view(np.uint8).reshape(n, nb, 2)
+    return blk.reshape(n, nb * bb)
+
+
+def timed(launch, iters, warm=3):
+    for i in range(warm):
+        launch(i)
+    lib.stream_sync()
+    e0, e1 = lib.Event(), lib.Event()
+    e0.record()
+    for i in range(iters):
+        launch(i + warm)
+    e1.record()
+    e1.sync()
+    return e0.elapsed_ms(e1) / iters * 1e3  # microseconds
+
+
+def case_linear(a):
+    rng = np.random.default_rng(0)
+    fmt, n, k, ep = FMT[a.fmt], a.n, a.k, EPI[a.epilogue]
+    rb = int(lib.load().sb_row_bytes(fmt, k))
+    tensors = 2 if ep == lib.EP_GATE_UP else 1
+    base = native_rows(rng, fmt, min(n, 2048), k)
+    rows = np.tile(base, ((n + base.shape[0] - 1) // base.shape[0], 1))[:n]
+    copies = max(2, int(a.resident_mb * 1e6 // (n * rb * tensors)) + 1)
+    bufs = [lib.DeviceBuffer.from_numpy(rows) for _ in range(copies * tensors)]
+    x = lib.DeviceBuffer.from_numpy(bf16_bits(rng.standard_normal((16, k))))
+    prep = lib.DeviceBuffer(int(lib.load().sb_linear_prepared_bytes(k)))
+    lib.check(lib.load().sb_linear_prepare(None, x.ptr, a.rows, k, k, None, fmt, prep.ptr, None, 0))
+    out = lib.DeviceBuffer(16 * n * 4 + 512)
+    aux = lib.DeviceBuffer.from_numpy(np.zeros((16, n), np.uint16))
+
+    def launch(i):
+        kw = {}
+        if ep == lib.EP_GATE_UP:
+            kw = dict(weights2=bufs[(2 * i + 1) % len(bufs)].ptr)
+            w = bufs[(2 * i) % len(bufs)].ptr
+        else:
+            w = bufs[i % len(bufs)].ptr
+            if ep == lib.EP_RESIDUAL:
+                kw = dict(aux=aux.ptr)
+        lib.linear(w, None, out.ptr, fmt, n, k, a.rows, prepared=prep.ptr, epilogue=ep, flags=lib.LINEAR_PDL if a.pdl else 0, **kw)
+
+    us = timed(launch, a.iters)
+    algo = n * rb * tensors + a.rows * k * 2 + a.rows * n * 2
+    print(f"linear {a.fmt} n={n} k={k} rows={a.rows} epilogue={a.epilogue}: {us:.1f} us per launch, {algo / us / 1e3:.0f} GB/s "
+          f"of {algo} algorithmic bytes, device status {lib.device_status()}")
+
+
+def case_attention(a):
+    rng = np.random.default_rng(0)
+    l = lib.ops()
+    QH, KH, D, PT, committed, rows = a.q_heads, a.kv_heads, a.head_dim, a.page_tokens, a.context, a.rows
+    pages = (committed + rows + PT - 1) // PT + 1
+    k = lib.DeviceBuffer.from_numpy(rng.integers(-127, 128, (pages, KH, PT, D), dtype=np.int8))
+    v = lib.DeviceBuffer.from_numpy(rng.integers(-127, 128, (pages, KH, PT, D), dtype=np.int8))
+    ks = lib.DeviceBuffer.from_numpy(rng.uniform(0.005, 0.03, (pages, KH, PT)).astype(np.float16))
+    vs = lib.DeviceBuffer.from_numpy(rng.uniform(0.005, 0.03, (pages, KH, PT)).astype(np.float16))
+    table = lib.DeviceBuffer.from_numpy(np.arange(pages, dtype=np.uint32))
+    stride = QH * 2 * D + 2 * KH * D
+    qkv = lib.DeviceBuffer.from_numpy(bf16_bits(rng.standard_normal((rows, stride))))
+    q = lib.DeviceBuffer.from_numpy(bf16_bits(rng.standard_normal((rows, QH, D))))
+    out = lib.DeviceBuffer(rows * QH * D * 2)
+    cache = lib.SbKvLayer(k.ptr, v.ptr, ks.ptr, vs.ptr, KH, D, PT, 1)
+    args = lib.SbAttnArgs(q.ptr, qkv.ptr, table.ptr, None, out.ptr, cache, None, rows, QH, 1, stride, QH * D, committed)
+    us = timed(lambda i: lib.check(l.sb_attn_verify(None, ctypes.byref(args))), a.iters)
+    algo = 2 * (committed + rows) * KH * (D + 2)
+    print(f"attention q_heads={QH} kv_heads={KH} D={D} context={committed} rows={rows}: {us:.1f} us per launch, "
+          f"{algo / us / 1e3:.0f} GB/s of {algo} algorithmic bytes, device status {lib.device_status()}")
+
+
+def case_gdn(a):
+    rng = np.random.default_rng(0)
+    l = lib.ops()
+    KH, VH, D = a.key_heads, a.value_heads, 128
+    KW, VW = KH * D, VH * D
+    C = 2 * KW + VW
+    up = lambda x: lib.DeviceBuffer.from_numpy(x)
+    bf = lambda shape, s: bf16_bits(rng.standard_normal(shape) * s)
+    d = dict(qkvz=up(bf((16, C + VW), 1.0)), b=up(bf((16, VH), 1.0)), a=up(bf((16, VH), 1.0)), conv_w=up(bf((C, 4), 0.4)),
+             a_scale=up((-np.exp(rng.uniform(-3, 0.5, VH))).astype(np.float32)), dt_bias=up(bf((VH,), 0.5)),
+             norm_w=up(np.ones(D, np.float32)), cs_in=up(bf((3, C), 1.0)), state=up((rng.standard_normal((VH, D, D)) * 0.05).astype(np.float32)))
+    tape = lambda: dict(inputs=lib.DeviceBuffer(16 * C * 2), k=lib.DeviceBuffer(16 * KW * 2), v=lib.DeviceBuffer(16 * VW * 2),
+                        beta=lib.DeviceBuffer(16 * VH * 2), decay=lib.DeviceBuffer(16 * VH * 4))
+    pend, step = tape(), tape()
+    for t in (pend, step):
+        for b in t.values():
+            b.fill(0)
+    cs_out, st_out, hid = lib.DeviceBuffer(3 * C * 2), lib.DeviceBuffer(VH * D * D * 4), lib.DeviceBuffer(16 * VW * 2)
+    T = lambda t: lib.SbGdnTape(t["inputs"].ptr, t["k"].ptr, t["v"].ptr, t["beta"].ptr, t["decay"].ptr)
+    args = lib.SbGdnArgs(d["qkvz"].ptr, d["b"].ptr, d["a"].ptr, d["conv_w"].ptr, d["a_scale"].ptr, d["dt_bias"].ptr, d["norm_w"].ptr,
+                         d["cs_in"].ptr, cs_out.ptr, d["state"].ptr, st_out.ptr, T(pend), T(step), hid.ptr, None,
+                         a.rows, a.pending, KH, VH, C + VW, VH, VW, 0)
+    us = timed(lambda i: lib.check(l.sb_gdn_verify(None, ctypes.byref(args))), a.iters)
+    algo = 2 * VH * D * D * 4
+    print(f"gdn key_heads={KH} value_heads={VH} rows={a.rows} pending={a.pending}: {us:.1f} us per launch, "
+          f"{algo / us / 1e3:.0f} GB/s of {algo} state bytes, device status {lib.device_status()}")
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="python -m splash_b200.cases")
+    sub = ap.add_subparsers(dest="case", required=True)
+    p = sub.add_parser("linear")
+    p.add_argument("--fmt", choices=sorted(FMT), default="q4k")
+    p.add_argument("--n", type=int, default=17408)
+    p.add_argument("--k", type=int, default=5120)
+    p.add_argument("--rows", type=int, default=16)
+    p.add_argument("--epilogue", choices=sorted(EPI), default="none")
+    p.add_argument("--iters", type=int, default=20)
+    p.add_argument("--pdl", action="store_true")
+    p.add_argument("--resident-mb", type=float, default=400.0, help="rotate weight copies over at least this many MB")
+    p = sub.add_parser("attention")
+    p.add_argument("--context", type=int, default=32768)
+    p.add_argument("--q-heads", type=int, default=24)
+    p.add_argument("--kv-heads", type=int, default=4)
+    p.add_argument("--head-dim", type=int, default=256)
+    p.add_argument("--page-tokens", type=int, default=256)
+    p.add_argument("--rows", type=int, default=16)
+    p.add_argument("--iters", type=int, default=10)
+    p = sub.add_parser("gdn")
+    p.add_argument("--key-heads", type=int, default=16)
+    p.add_argument("--value-heads", type=int, default=48)
+    p.add_argument("--rows", type=int, default=16)
+    p.add_argument("--pending", type=int, default=8)
+    p.add_argument("--iters", type=int, default=20)
+    a = ap.parse_args(argv)
+    lib.init(0)
+    {"linear": case_linear, "attention": case_attention, "gdn": case_gdn}[a.case](a)
+
+
+if __name__ == "__main__":
+    main(sys.argv[1:])

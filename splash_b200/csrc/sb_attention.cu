@@ -30,7 +30,8 @@ namespace sb {
 constexpr int kAttnThreads = 256;
 constexpr int kChunk = 32;       // tokens per step of the page loop
 constexpr int kMaxFused = 128;   // rows x query heads of one KV head
-constexpr int kRing = 4;         // raw chunks in flight per CTA
+constexpr int kRing = 3;         // raw chunks in flight per CTA
+constexpr int kConv = 3;         // converted chunks (fp16) buffered for the multiplying warps
 
 struct AttnParams {
   const uint16_t *queries, *qkv;
@@ -76,15 +77,18 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnPa
   constexpr int KSTEPS = D / 16, NT_O = D / 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __half *q_s = reinterpret_cast<__half *>(smem_raw);              // [128][PITCH]
-  // Converted chunks are double-buffered: while the m-tile warps multiply chunk i, every warp has already
-  // converted chunk i + 1 into the other buffer, so one barrier per chunk orders them.
-  __half *kv_s = q_s + kMaxFused * PITCH;                           // [2][K: 32 x PITCH, V: 32 x PITCH]
-  float *sc_s = reinterpret_cast<float *>(kv_s + 4 * kChunk * PITCH);  // [2][ks: 32, vs: 32]; ks holds scale / sqrt(D) * log2(e)
-  uint8_t *ring = reinterpret_cast<uint8_t *>(sc_s + 4 * kChunk);    // [kRing][2 * 32 * D + 256] raw chunks
+  __half *kv_s = q_s + kMaxFused * PITCH;                           // [kConv][K: 32 x PITCH, V: 32 x PITCH]
+  float *sc_s = reinterpret_cast<float *>(kv_s + kConv * 2 * kChunk * PITCH);  // [kConv][ks: 32, vs: 32]; ks = scale / sqrt(D) * log2(e)
+  uint8_t *ring = reinterpret_cast<uint8_t *>(sc_s + kConv * 2 * kChunk);      // [kRing][2 * 32 * D + 256] raw chunks
   uint64_t *full = reinterpret_cast<uint64_t *>(ring + kRing * (2 * kChunk * D + 256));
+  uint64_t *conv_full = full + kRing, *conv_empty = conv_full + kConv;
   __shared__ uint32_t s_last;
   if (threadIdx.x == 0) {
     for (int i = 0; i < kRing; ++i) mbar_init(&full[i], 1);
+    for (int i = 0; i < kConv; ++i) {
+      mbar_init(&conv_full[i], 1);
+      mbar_init(&conv_empty[i], (p.fused + 15) / 16);
+    }
     fence_mbar_init();
   }
   __syncthreads();
@@ -119,6 +123,7 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnPa
     *reinterpret_cast<uint4 *>(q_s + f * PITCH + c8 * 8) = o;
   }
 
+  __syncthreads();  // the queries are staged before any warp multiplies
   const bool computes = warp * 16 < F;
   float o_acc[NT_O][4];
 #pragma unroll
@@ -142,7 +147,6 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnPa
   // Chunk ring: thread 0 keeps kRing - 1 chunks in flight with bulk async copies (a chunk's 32 tokens are
   // contiguous inside a page: D x 32 bytes of keys, of values, and their 32 scales each), completing on
   // one mbarrier per slot. Every thread then converts its share of the landed chunk to fp16.
-  constexpr int LD = D / 128;  // 16-byte pieces per thread per tensor
   const uint32_t sbytes = p.cache.scale_f16 ? 2u : 4u;
   const uint32_t slot_bytes = 2 * kChunk * D + 256;
   auto issue = [&](uint32_t chunk) {
@@ -158,14 +162,12 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnPa
     bulk_g2s(dst + 2 * kChunk * D + 128, static_cast<const uint8_t *>(p.cache.v_scale) + slot * sbytes, kChunk * sbytes, &full[s]);
   };
   const float score_scale = (D == 256 ? 0.0625f : 0.08838834764831845f) * 1.44269504089f;  // 1/sqrt(D) * log2(e)
-  auto stage = [&](uint32_t chunk) {
+  auto stage_into = [&](uint32_t chunk, __half *k_s, float *ks_s, uint32_t wtid, uint32_t wthreads) {
     const uint8_t *src = ring + ((chunk - c_begin) % kRing) * slot_bytes;
-    const uint32_t buf = (chunk - c_begin) & 1;
-    __half *k_s = kv_s + buf * 2 * kChunk * PITCH, *v_s = k_s + kChunk * PITCH;
-    float *ks_s = sc_s + buf * 2 * kChunk, *vs_s = ks_s + kChunk;
-#pragma unroll
-    for (int i = 0; i < LD; ++i) {
-      const uint32_t idx = tid + i * kAttnThreads, tok = idx / (D / 16), part = idx % (D / 16);
+    __half *v_s = k_s + kChunk * PITCH;
+    float *vs_s = ks_s + kChunk;
+    for (uint32_t idx = wtid; idx < kChunk * (D / 16); idx += wthreads) {
+      const uint32_t tok = idx / (D / 16), part = idx % (D / 16);
       uint4 lo, hi;
       int8x16_to_half(*reinterpret_cast<const uint4 *>(src + tok * D + part * 16), lo, hi);
       *reinterpret_cast<uint4 *>(k_s + tok * PITCH + part * 16) = lo;
@@ -174,42 +176,23 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnPa
       *reinterpret_cast<uint4 *>(v_s + tok * PITCH + part * 16) = lo;
       *reinterpret_cast<uint4 *>(v_s + tok * PITCH + part * 16 + 8) = hi;
     }
-    if (tid < kChunk) {
+    if (wtid < kChunk) {
       // Tokens past the visible ones share the page but hold nothing: their scales read as zero.
-      const bool live = chunk * kChunk + tid < visible;
+      const bool live = chunk * kChunk + wtid < visible;
       float ksc, vsc;
       if (p.cache.scale_f16) {
-        ksc = __half2float(reinterpret_cast<const __half *>(src + 2 * kChunk * D)[tid]);
-        vsc = __half2float(reinterpret_cast<const __half *>(src + 2 * kChunk * D + 128)[tid]);
+        ksc = __half2float(reinterpret_cast<const __half *>(src + 2 * kChunk * D)[wtid]);
+        vsc = __half2float(reinterpret_cast<const __half *>(src + 2 * kChunk * D + 128)[wtid]);
       } else {
-        ksc = reinterpret_cast<const float *>(src + 2 * kChunk * D)[tid];
-        vsc = reinterpret_cast<const float *>(src + 2 * kChunk * D + 128)[tid];
+        ksc = reinterpret_cast<const float *>(src + 2 * kChunk * D)[wtid];
+        vsc = reinterpret_cast<const float *>(src + 2 * kChunk * D + 128)[wtid];
       }
-      ks_s[tid] = live ? ksc * score_scale : 0.0f;
-      vs_s[tid] = live ? vsc : 0.0f;
+      ks_s[wtid] = live ? ksc * score_scale : 0.0f;
+      vs_s[wtid] = live ? vsc : 0.0f;
     }
   };
 
-  if (tid == 0)
-    for (uint32_t c = c_begin; c < c_end && c < c_begin + kRing - 1; ++c) issue(c);
-  bool alive = true;
-  auto convert = [&](uint32_t chunk) {  // waits for the raw chunk, then converts this thread's share
-    if (!mbar_wait(&full[(chunk - c_begin) % kRing], ((chunk - c_begin) / kRing) & 1)) {
-      if (tid == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
-      alive = false;
-      return;
-    }
-    stage(chunk);
-  };
-  if (c_begin < c_end) convert(c_begin);
-  for (uint32_t chunk = c_begin; chunk < c_end && alive; ++chunk) {
-    __syncthreads();  // chunk is converted; the buffer chunk + 1 goes to and the raw slot refilled below are free
-    if (tid == 0 && chunk + kRing - 1 < c_end) issue(chunk + kRing - 1);
-    if (chunk + 1 < c_end) convert(chunk + 1);
-    const uint32_t buf = (chunk - c_begin) & 1;
-    const __half *k_s = kv_s + buf * 2 * kChunk * PITCH, *v_s = k_s + kChunk * PITCH;
-    const float *ks_s = sc_s + buf * 2 * kChunk, *vs_s = ks_s + kChunk;
-    if (!computes) continue;
+  auto compute_chunk = [&](uint32_t chunk, const __half *k_s, const __half *v_s, const float *ks_s, const float *vs_s) {
     const uint32_t tok0 = chunk * kChunk;
     // S = Q K^T for 16 fused rows x 32 tokens.
     float s_acc[4][4];
@@ -292,6 +275,69 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnPa
         mma_f16(o_acc[2 * np], pa[kt][0], pa[kt][1], pa[kt][2], pa[kt][3], b[0], b[1]);
         mma_f16(o_acc[2 * np + 1], pa[kt][0], pa[kt][1], pa[kt][2], pa[kt][3], b[2], b[3]);
       }
+  };
+
+  const uint32_t ncw = (F + 15) / 16;  // warps with an m-tile
+  if (ncw + 2 <= kAttnThreads / 32) {
+    // ---- specialised: warps 0..ncw-1 multiply, the last two warps convert chunks into a ring of three
+    // converted buffers and keep the raw ring full. Buffers are handed over through mbarriers, so the
+    // multiplying warps drift apart and keep the tensor pipe busy while others are in their softmax. ----
+    const uint32_t nchunks = c_end > c_begin ? c_end - c_begin : 0;
+    if (warp >= kAttnThreads / 32 - 2) {
+      const uint32_t ctid = tid - (kAttnThreads - 64);
+      if (ctid == 0)
+        for (uint32_t c = c_begin; c < c_end && c < c_begin + kRing; ++c) issue(c);
+      for (uint32_t i = 0; i < nchunks; ++i) {
+        const uint32_t chunk = c_begin + i, buf = i % kConv;
+        bool ok = mbar_wait(&full[i % kRing], (i / kRing) & 1);
+        if (ok && i >= kConv) ok = mbar_wait(&conv_empty[buf], (i / kConv - 1) & 1);
+        if (!ok) {
+          if (ctid == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
+          break;
+        }
+        stage_into(chunk, kv_s + buf * 2 * kChunk * PITCH, sc_s + buf * 2 * kChunk, ctid, 64);
+        named_bar_sync(1, 64);  // both converter warps have written the buffer and read the raw slot
+        if (ctid == 0) {
+          mbar_arrive(&conv_full[buf]);
+          if (chunk + kRing < c_end) issue(chunk + kRing);
+        }
+      }
+    } else if (computes) {
+      for (uint32_t i = 0; i < nchunks; ++i) {
+        const uint32_t buf = i % kConv;
+        if (!mbar_wait(&conv_full[buf], (i / kConv) & 1)) {
+          if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
+          break;
+        }
+        const __half *k_s = kv_s + buf * 2 * kChunk * PITCH;
+        compute_chunk(c_begin + i, k_s, k_s + kChunk * PITCH, sc_s + buf * 2 * kChunk, sc_s + buf * 2 * kChunk + kChunk);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&conv_empty[buf]);
+      }
+    }
+  } else {
+    // ---- every warp has an m-tile: all warps convert chunk i + 1, then multiply chunk i; one barrier a chunk ----
+    if (tid == 0)
+      for (uint32_t c = c_begin; c < c_end && c < c_begin + kRing - 1; ++c) issue(c);
+    bool alive = true;
+    auto convert = [&](uint32_t chunk) {  // waits for the raw chunk, then converts this thread's share
+      if (!mbar_wait(&full[(chunk - c_begin) % kRing], ((chunk - c_begin) / kRing) & 1)) {
+        if (tid == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
+        alive = false;
+        return;
+      }
+      const uint32_t buf = (chunk - c_begin) & 1;
+      stage_into(chunk, kv_s + buf * 2 * kChunk * PITCH, sc_s + buf * 2 * kChunk, tid, kAttnThreads);
+    };
+    if (c_begin < c_end) convert(c_begin);
+    for (uint32_t chunk = c_begin; chunk < c_end && alive; ++chunk) {
+      __syncthreads();  // chunk is converted; the buffer chunk + 1 goes to and the raw slot refilled below are free
+      if (tid == 0 && chunk + kRing - 1 < c_end) issue(chunk + kRing - 1);
+      if (chunk + 1 < c_end) convert(chunk + 1);
+      const uint32_t buf = (chunk - c_begin) & 1;
+      const __half *k_s = kv_s + buf * 2 * kChunk * PITCH;
+      if (computes) compute_chunk(chunk, k_s, k_s + kChunk * PITCH, sc_s + buf * 2 * kChunk, sc_s + buf * 2 * kChunk + kChunk);
+    }
   }
 
   // Partials of this split.
@@ -420,8 +466,8 @@ extern "C" int sb_attn_verify(void *stream, const SbAttnArgs *a) {
   p.committed_dev = a->committed_dev;
   p.rows = a->rows, p.q_heads = a->q_heads, p.group = group, p.gated = a->gated, p.qkv_stride = a->qkv_stride;
   p.out_stride = a->out_stride, p.committed = a->committed, p.splits = splits, p.chunks_per_split = cps, p.fused = fused;
-  const size_t smem = size_t(kMaxFused + 4 * kChunk) * (D + 8) * 2 + 4 * kChunk * sizeof(float) +
-                      size_t(kRing) * (2 * kChunk * D + 256) + kRing * sizeof(uint64_t);
+  const size_t smem = size_t(kMaxFused + kConv * 2 * kChunk) * (D + 8) * 2 + kConv * 2 * kChunk * sizeof(float) +
+                      size_t(kRing) * (2 * kChunk * D + 256) + (kRing + 2 * kConv) * sizeof(uint64_t);
   void (*kernel)(const AttnParams) = D == 256 ? attention_kernel<256> : attention_kernel<128>;
   static bool attr_set[2] = {false, false};
   if (!attr_set[D == 256]) {
