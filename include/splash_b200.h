@@ -129,8 +129,12 @@ typedef struct SbLinearArgs {
 } SbLinearArgs;
 
 enum {
-  SB_LINEAR_PDL = 1 /* launch with programmatic stream serialization: the weight stream starts while the
-                       producer of x drains */
+  SB_LINEAR_PDL = 1, /* launch with programmatic stream serialization: the weight stream starts while the
+                        producer of x drains */
+  SB_LINEAR_TCGEN05 = 2 /* Q4_K only: multiply on the tcgen05 tensor cores (weights expanded straight into tensor
+                           memory, 128-row tiles) instead of warp-level MMA. Give the same flag to
+                           sb_linear_prepare: the kernel reads its activations in another tile order. Same
+                           results contract; at 16 rows the warp-level kernel is the faster one on B200. */
 };
 
 /* Converts a projection input once into the fragment-ordered fp16 form the product reads
@@ -154,6 +158,9 @@ typedef struct SbLinearPlan {
 } SbLinearPlan;
 SB_API int sb_linear_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t rows, uint32_t epilogue,
                           SbLinearPlan *out_plan);
+/* The same for a call that carries `flags` (SB_LINEAR_TCGEN05 selects the 128-row tensor-memory kernel's plan). */
+SB_API int sb_linear_plan_flags(uint32_t format, uint32_t n, uint32_t k, uint32_t rows, uint32_t epilogue, uint32_t flags,
+                                SbLinearPlan *out_plan);
 
 
 /* ---- glue operators ---- */

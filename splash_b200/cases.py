@@ -66,7 +66,7 @@ def case_linear(a):
     bufs = [lib.DeviceBuffer.from_numpy(rows) for _ in range(copies * tensors)]
     x = lib.DeviceBuffer.from_numpy(bf16_bits(rng.standard_normal((16, k))))
     prep = lib.DeviceBuffer(int(lib.load().sb_linear_prepared_bytes(k)))
-    lib.check(lib.load().sb_linear_prepare(None, x.ptr, a.rows, k, k, None, fmt, prep.ptr, None, 0))
+    lib.check(lib.load().sb_linear_prepare(None, x.ptr, a.rows, k, k, None, fmt, prep.ptr, None, (a.diag << 8) | (lib.LINEAR_TCGEN05 if a.tcgen05 else 0)))
     out = lib.DeviceBuffer(16 * n * 4 + 512)
     aux = lib.DeviceBuffer.from_numpy(np.zeros((16, n), np.uint16))
 
@@ -79,7 +79,7 @@ def case_linear(a):
             w = bufs[i % len(bufs)].ptr
             if ep == lib.EP_RESIDUAL:
                 kw = dict(aux=aux.ptr)
-        lib.linear(w, None, out.ptr, fmt, n, k, a.rows, prepared=prep.ptr, epilogue=ep, flags=lib.LINEAR_PDL if a.pdl else 0, **kw)
+        lib.linear(w, None, out.ptr, fmt, n, k, a.rows, prepared=prep.ptr, epilogue=ep, flags=(lib.LINEAR_PDL if a.pdl else 0) | (a.diag << 8) | (lib.LINEAR_TCGEN05 if a.tcgen05 else 0), **kw)
 
     us = timed(launch, a.iters)
     algo = n * rb * tensors + a.rows * k * 2 + a.rows * n * 2
@@ -148,6 +148,8 @@ def main(argv=None):
     p.add_argument("--epilogue", choices=sorted(EPI), default="none")
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--pdl", action="store_true")
+    p.add_argument("--diag", type=int, default=0, help="kernel diagnostics (flags bits 8 and up)")
+    p.add_argument("--tcgen05", action="store_true", help="Q4_K on the tensor-memory kernel (SB_LINEAR_TCGEN05)")
     p.add_argument("--resident-mb", type=float, default=400.0, help="rotate weight copies over at least this many MB")
     p = sub.add_parser("attention")
     p.add_argument("--context", type=int, default=32768)

@@ -36,6 +36,7 @@
 #include <cuda.h>
 
 #include "sb_internal.h"
+#include "sb_linear_internal.h"
 #include "sb_ptx.cuh"
 
 namespace sb {
@@ -101,8 +102,7 @@ __device__ __forceinline__ void slice_range(uint32_t nsb, uint32_t slices, uint3
 // runtime/ops/Linear.hpp:265-347; kernel decode_linear_gguf_prepare of
 // runtime/metal/kernels/decode/linear_gguf_sgmatrix.metal). An optional RMSNorm is fused in front:
 // y = bf16((x * rsqrt(mean x^2 + 1e-6)) * w) (runtime/metal/kernels/shared/normalization.metal:60-94).
-constexpr uint32_t kPrepHeader = 64;
-constexpr uint32_t kPrepSbBytes = kXsbBytes + kSxSbBytes;  // 8704
+static_assert(kPrepSbBytes == kXsbBytes + kSxSbBytes, "prepared super-block size");
 constexpr int kPrepThreads = 256;
 constexpr int kPrepMaxChunks = 9;  // 8-element chunks a thread keeps in registers: k <= 18432
 
@@ -111,7 +111,7 @@ struct PrepareParams {
   const float *norm_w;
   uint8_t *out;
   uint16_t *normed_out;  // optional bf16 [rows][k]: the (normalised) input as the product's fp32 side projections read it
-  uint32_t rows, k, x_stride, pair_layout;
+  uint32_t rows, k, x_stride, pair_layout;  // layout: 0 range, 1 pair, 2 tensor-core tiles
 };
 
 __device__ __forceinline__ float block_reduce(float v, float *scratch, bool is_max) {
@@ -209,9 +209,9 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PreparePara
       hv[jj] = __float2half_rn(v[i][jj] * down);
       sum += __half2float(hv[jj]);
     }
-    uint32_t unit;
-    if (p.pair_layout) unit = (((q * 2 + (j & 1)) * 2 + h) * 8 + g) * 4 + (j >> 1);
-    else unit = ((j * 2 + h) * 8 + g) * 4 + q;
+    uint32_t unit = 0;
+    if (p.pair_layout == 1) unit = (((q * 2 + (j & 1)) * 2 + h) * 8 + g) * 4 + (j >> 1);
+    else if (p.pair_layout == 0) unit = ((j * 2 + h) * 8 + g) * 4 + q;
     const __half2 p0 = __halves2half2(hv[0], hv[2]), p1 = __halves2half2(hv[1], hv[3]);
     const __half2 p2 = __halves2half2(hv[4], hv[6]), p3 = __halves2half2(hv[5], hv[7]);
     uint4 o;
@@ -220,17 +220,35 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PreparePara
     o.z = *reinterpret_cast<const uint32_t *>(&p2);
     o.w = *reinterpret_cast<const uint32_t *>(&p3);
     uint8_t *sbp = p.out + kPrepHeader + size_t(sb) * kPrepSbBytes;
-    *reinterpret_cast<uint4 *>(sbp + size_t(unit) * 16) = o;
+    if (p.pair_layout == 2) {
+      // Tensor-core operand layout: 16 K-major tiles of 16 inputs x 16 tokens, each [token / 8][input / 8]
+      // [token % 8][8 halves]. The inputs of a tile follow the order in which the Q4_K kernel unpacks a
+      // row's nibbles: chunk (pair lane / 8, sub-block parity (lane / 4) % 2, quarter lane % 4) fills
+      // inputs 4 parity .. + 3 of both halves of tile 4 pair + quarter.
+      const uint32_t pair = lane >> 3, parity = (lane >> 2) & 1, quarter = lane & 3;
+      uint8_t *tile = sbp + (4 * pair + quarter) * 512 + h * 256 + g * 16 + 8 * parity;
+      *reinterpret_cast<uint2 *>(tile) = make_uint2(o.x, o.y);
+      *reinterpret_cast<uint2 *>(tile + 128) = make_uint2(o.z, o.w);
+    } else {
+      *reinterpret_cast<uint4 *>(sbp + size_t(unit) * 16) = o;
+    }
     // Sub-block sums: 32 inputs = 4 consecutive lanes.
     sum += __shfl_xor_sync(0xffffffffu, sum, 1);
     sum += __shfl_xor_sync(0xffffffffu, sum, 2);
     if (q == 0) {
       const __half hi = __float2half_rn(sum);
       const __half lo = __float2half_rn(sum - __half2float(hi));
-      const uint32_t at = ((h * 8 + g) * 4 + (j >> 1)) * 4 + (j & 1) * 2;
       __half *sx = reinterpret_cast<__half *>(sbp + kXsbBytes);
-      sx[at] = hi;
-      sx[at + 1] = lo;
+      if (p.pair_layout == 2) {
+        // The 17th tile: input j = high part, input 8 + j = low part of sub-block j's sum.
+        const uint32_t at = h * 128 + g * 8 + j;
+        sx[at] = hi;
+        sx[at + 64] = lo;
+      } else {
+        const uint32_t at = ((h * 8 + g) * 4 + (j >> 1)) * 4 + (j & 1) * 2;
+        sx[at] = hi;
+        sx[at + 1] = lo;
+      }
     }
   }
 }
@@ -845,8 +863,7 @@ static int make_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t epilogue,
 
 // A 2-D map over `rows` rows of `stride` bytes starting at the 16-byte aligned `base`: u32 elements,
 // box = box_rows x box_bytes. Rows past the end and bytes past a row read as zero.
-static int encode_weight_map(CUtensorMap *map, uintptr_t base, uint32_t stride, uint32_t rows, uint32_t box_bytes,
-                             uint32_t box_rows) {
+int encode_weight_map(CUtensorMap *map, uintptr_t base, uint32_t stride, uint32_t rows, uint32_t box_bytes, uint32_t box_rows) {
   using Encode = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                               const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -872,9 +889,9 @@ static int encode_weight_map(CUtensorMap *map, uintptr_t base, uint32_t stride, 
 }
 
 static int launch_prepare(cudaStream_t stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride,
-                          const void *norm_w, bool pair_layout, void *out, void *normed_out, bool pdl) {
+                          const void *norm_w, uint32_t layout, void *out, void *normed_out, bool pdl) {
   PrepareParams pp{static_cast<const uint16_t *>(x), static_cast<const float *>(norm_w), static_cast<uint8_t *>(out),
-                   static_cast<uint16_t *>(normed_out), rows, k, x_stride, pair_layout ? 1u : 0u};
+                   static_cast<uint16_t *>(normed_out), rows, k, x_stride, layout};
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(kTokens);
   cfg.blockDim = dim3(kPrepThreads);
@@ -900,6 +917,14 @@ extern "C" int sb_linear_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t 
   return make_plan(format, n, k, epilogue, p, *out_plan);
 }
 
+extern "C" int sb_linear_plan_flags(uint32_t format, uint32_t n, uint32_t k, uint32_t rows, uint32_t epilogue, uint32_t flags,
+                                    SbLinearPlan *out_plan) {
+  SB_REQUIRE(out_plan, "sb_linear_plan: null plan");
+  SB_REQUIRE(rows >= 1 && rows <= kTokens, "sb_linear_plan: rows = %u outside 1..%d", rows, kTokens);
+  if (format == SB_FMT_Q4K && (flags & SB_LINEAR_TCGEN05)) return tc_plan(n, k, epilogue, *out_plan);
+  return sb_linear_plan(format, n, k, rows, epilogue, out_plan);
+}
+
 extern "C" uint64_t sb_linear_prepared_bytes(uint32_t k) { return k % 256 ? 0 : kPrepHeader + uint64_t(k / 256) * kPrepSbBytes; }
 
 extern "C" int sb_linear_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride,
@@ -916,7 +941,8 @@ extern "C" int sb_linear_prepare(void *stream, const void *x, uint32_t rows, uin
                  (reinterpret_cast<uintptr_t>(norm_weight) & 15) == 0,
              "sb_linear_prepare: x, norm_weight and the destination must be 16-byte aligned");
   SB_REQUIRE((reinterpret_cast<uintptr_t>(normed_out) & 15) == 0, "sb_linear_prepare: normed_out must be 16-byte aligned");
-  return launch_prepare(as_stream(stream), x, rows, k, x_stride, norm_weight, format == SB_FMT_Q4K, prepared_out, normed_out,
+  const uint32_t layout = format != SB_FMT_Q4K ? 0u : (flags & SB_LINEAR_TCGEN05) ? 2u : 1u;
+  return launch_prepare(as_stream(stream), x, rows, k, x_stride, norm_weight, layout, prepared_out, normed_out,
                         (flags & SB_LINEAR_PDL) != 0);
 }
 
@@ -937,15 +963,28 @@ extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
              "sb_linear: out and aux must be 16-byte aligned");
   SB_REQUIRE((reinterpret_cast<uintptr_t>(a->weights) & 1) == 0 && (reinterpret_cast<uintptr_t>(a->weights2) & 1) == 0,
              "sb_linear: weights must be 2-byte aligned");
+  const bool tensor_core = a->format == SB_FMT_Q4K && (a->flags & SB_LINEAR_TCGEN05);
   LinearParams p{};
   SbLinearPlan plan;
-  int st = make_plan(a->format, a->n, a->k, a->epilogue, p, plan);
+  int st = tensor_core ? tc_plan(a->n, a->k, a->epilogue, plan) : make_plan(a->format, a->n, a->k, a->epilogue, p, plan);
   if (st != SB_OK) return st;
   if (a->format == SB_FMT_Q4K)
     SB_REQUIRE((reinterpret_cast<uintptr_t>(a->weights) & 15) == 0 &&
                    (reinterpret_cast<uintptr_t>(a->weights2) & 15) == 0,
                "sb_linear: Q4_K weights must be 16-byte aligned");
   Context &c = ctx();
+  if (tensor_core) {
+    const void *prep = a->prepared;
+    if (!prep) {
+      SB_REQUIRE(sb_linear_prepared_bytes(a->k) <= c.prepared_bytes, "sb_linear: k = %u exceeds the context's prepared-input scratch", a->k);
+      st = sb_linear_prepare(stream, a->x, a->rows, a->k, a->x_stride, a->norm_weight, a->format, c.prepared, nullptr, a->flags);
+      if (st != SB_OK) return st;
+      prep = c.prepared;
+    } else {
+      SB_REQUIRE((reinterpret_cast<uintptr_t>(prep) & 15) == 0, "sb_linear: prepared must be 16-byte aligned");
+    }
+    return launch_linear_tc(as_stream(stream), a, prep, (a->flags & SB_LINEAR_PDL) != 0);
+  }
   const uint32_t pcols = a->epilogue == SB_EPILOGUE_GATE_UP ? 2 * a->n : a->n;
   SB_REQUIRE(p.slices == 1 || size_t(p.slices) * kTokens * pcols * 4 <= c.linear_partials_bytes,
              "sb_linear: split-K scratch too small for n = %u with %u slices", a->n, p.slices);

@@ -48,6 +48,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity) {
   return false;
 }
 
+// A wait for hand-overs whose latency is on the critical path: test_wait never suspends the thread, so the
+// poll sees the phase flip within a few cycles (try_wait may park the thread for a scheduling quantum).
+__device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t *bar, uint32_t parity) {
+  for (uint32_t i = 0; i < (kSpinLimit << 4); ++i)
+    if (mbar_test_wait(bar, parity)) return true;
+  return false;
+}
+
 // The same wait for warps that only coordinate (producer, epilogue): sleeps between polls so the
 // spinning does not take issue slots from the math warps of the same scheduler.
 __device__ __forceinline__ bool mbar_wait_backoff(uint64_t *bar, uint32_t parity) {

@@ -44,6 +44,17 @@ def test_linear_plans_of_the_27b_projections():
     # gate/up: K = 5120 = 20 super-blocks in 2 slices of 10, 544 tiles of 32 columns
     assert l.sb_linear_plan(lib.FMT_Q4K, 17408, 5120, 16, lib.EP_GATE_UP, ctypes.byref(p)) == 0
     assert (p.slices, p.tiles, p.slice_blocks_max, p.ctas) == (2, 544, 10, 148) and p.smem_bytes <= 227 * 1024 and p.stages >= 2
+    # the tensor-memory kernel: 136 tiles of 128 columns (the tensor-memory lanes)
+    l.sb_linear_plan_flags.argtypes = [ctypes.c_uint32] * 6 + [ctypes.POINTER(lib.SbLinearPlan)]
+    T = lib.LINEAR_TCGEN05
+    assert l.sb_linear_plan_flags(lib.FMT_Q4K, 17408, 5120, 16, lib.EP_GATE_UP, T, ctypes.byref(p)) == 0
+    assert (p.slices, p.tiles, p.tile_rows, p.slice_blocks_max, p.ctas) == (2, 136, 128, 10, 148)
+    assert p.smem_bytes <= 227 * 1024 and p.stages >= 3 and p.stages % 3 == 0
+    # every Q4_K projection of the 27B shape gets a plan whose slices cover K and whose grid is whole slice groups
+    for n, k in ((14336, 5120), (16384, 5120), (5120, 6144), (5120, 17408), (248320, 5120)):
+        assert l.sb_linear_plan_flags(lib.FMT_Q4K, n, k, 16, 0, T, ctypes.byref(p)) == 0
+        assert p.slices * p.slice_blocks_max >= k // 256 and p.ctas % p.slices == 0 and p.ctas <= 148
+        assert p.smem_bytes <= 227 * 1024 and p.stages % 3 == 0 and p.tiles == (n + 127) // 128
     # down: Q6_K, K = 17408 = 68 super-blocks
     assert l.sb_linear_plan(lib.FMT_Q6K, 5120, 17408, 16, lib.EP_RESIDUAL, ctypes.byref(p)) == 0
     assert p.slices * p.slice_blocks_max >= 68 and p.ctas % p.slices == 0 and p.smem_bytes <= 227 * 1024

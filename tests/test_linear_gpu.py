@@ -164,3 +164,66 @@ def test_linear_rejects_bad_arguments():
         lib.linear(1 << 20, 1 << 20, 1 << 20, 0, 64, 1024, 17)  # too many rows
     with pytest.raises(lib.SbError):
         lib.linear(1 << 20, 1 << 20, 1 << 20, 3, 64, 1024, 16)  # unsupported format
+
+
+# ---- the same contract on the tcgen05 kernel (SB_LINEAR_TCGEN05: weights expanded into tensor memory) ----
+
+@pytest.mark.parametrize("n,k,rows", [(512, 1024, 16), (320, 5120, 16), (192, 6144, 5), (64, 17408, 16), (96, 2816, 16), (4096, 256, 1)])
+def test_linear_tcgen05_plain(n, k, rows):
+    lib = _setup()
+    W = qf.realistic(0, n, k, seed=n + k)
+    X = qf.activations(rows, k, seed=rows)
+    got = run_linear(lib, 0, W, n, k, X, rows, flags=lib.LINEAR_TCGEN05)
+    v, be, _ = oracle_f64(0, W, n, k, X, rows)
+    check_interval(got, v - be, v + be)
+
+
+def test_linear_tcgen05_config0_and_agreement_with_warp_kernel():
+    """Benchmark configuration 0 on the tensor-memory kernel; both kernels feed the tensor cores the same exact
+    integer operands, so they may differ only by the order of fp32 additions."""
+    lib = _setup()
+    n, k, rows = 17408, 5120, 16
+    W = qf.config0_q4k(n, k, seed=0)
+    X = qf.activations(rows, k, seed=0)
+    got = run_linear(lib, 0, W, n, k, X, rows, flags=lib.LINEAR_TCGEN05, out_f32=True)
+    v, be, _ = oracle_f64(0, W, n, k, X, rows)
+    check_interval(ol.f2bf(got), v - be, v + be)
+    warp = run_linear(lib, 0, W, n, k, X, rows, out_f32=True)
+    assert np.abs(got - warp).max() <= 1e-5 * np.abs(warp).max()
+
+
+def test_linear_tcgen05_epilogues():
+    lib = _setup()
+    n, k, rows = 384, 5120, 16
+    T = lib.LINEAR_TCGEN05
+    Wg = qf.realistic(0, n, k, seed=1)
+    Wu = qf.realistic(0, n, k, seed=2)
+    X = qf.activations(rows, k)
+    rng = np.random.default_rng(3)
+    aux = ol.f2bf(rng.standard_normal((rows, n)).astype(np.float32) * 4)
+    auxd = lib.DeviceBuffer.from_numpy(aux)
+    plain = run_linear(lib, 0, Wg, n, k, X, rows, out_f32=True, flags=T)
+    assert np.array_equal(run_linear(lib, 0, Wg, n, k, X, rows, flags=T), ol.f2bf(plain))
+    res = run_linear(lib, 0, Wg, n, k, X, rows, aux=auxd.ptr, epilogue=lib.EP_RESIDUAL, flags=T)
+    assert np.array_equal(res, ol.f2bf(plain + ol.bf2f(aux)))
+    gate = run_linear(lib, 0, Wg, n, k, X, rows, flags=T)
+    gd = lib.DeviceBuffer.from_numpy(gate)
+    two = run_linear(lib, 0, Wu, n, k, X, rows, aux=gd.ptr, epilogue=lib.EP_UP_WITH_GATE, flags=T)
+    wud = lib.DeviceBuffer.from_numpy(Wu)
+    one = run_linear(lib, 0, Wg, n, k, X, rows, weights2=wud.ptr, epilogue=lib.EP_GATE_UP, flags=T)
+    assert np.array_equal(one, two)
+
+
+def test_linear_tcgen05_rows_independent_of_batch():
+    lib = _setup()
+    n, k = 256, 5120
+    W = qf.realistic(0, n, k)
+    X = qf.activations(16, k)
+    T = lib.LINEAR_TCGEN05
+    full = run_linear(lib, 0, W, n, k, X, 16, flags=T)
+    one = run_linear(lib, 0, W, n, k, X[:1].copy(), 1, flags=T)
+    assert np.array_equal(full[:1], one)
+    Xn = X.copy()
+    Xn[5:] = 0x7FC0
+    part = run_linear(lib, 0, W, n, k, Xn, 16, flags=T)
+    assert np.array_equal(full[:5], part[:5])
