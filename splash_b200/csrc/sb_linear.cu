@@ -39,14 +39,21 @@
 #include "sb_linear_internal.h"
 #include "sb_ptx.cuh"
 
+#ifndef SB_Q4K_I2_UNROLL
+#define SB_Q4K_I2_UNROLL 4
+#endif
+#define SB_PRAGMA_(x) _Pragma(#x)
+#define SB_PRAGMA(x) SB_PRAGMA_(x)
+#define SB_UNROLL_Q4K_I2 SB_PRAGMA(unroll SB_Q4K_I2_UNROLL)
+
 namespace sb {
 
 constexpr int kTokens = 16;         // rows of X one launch multiplies
-constexpr int kConsumerWarps = 8;
+constexpr int kRG = 2, kKG = 6, kMT = 2;  // row groups x k groups of consumer warps; m-tiles per warp
+constexpr int kConsumerWarps = kRG * kKG; // 12: three per scheduler hide the operand expansion's latencies
 constexpr int kThreads = 32 * (kConsumerWarps + 3);  // + producer warp + two epilogue warps
-constexpr int kRG = 2, kKG = 4, kMT = 2;  // row groups x k groups of consumer warps; m-tiles per warp
 constexpr int kTileRows = kRG * kMT * 16; // 64
-constexpr int kStageSb = kKG;             // super-blocks per ring stage
+constexpr int kStageSb = 4;               // super-blocks per ring stage
 constexpr int kMaxStages = 8;
 constexpr int kMaxSliceSb = 10;           // super-blocks of activations a CTA keeps resident (80 KiB)
 constexpr int kRedPitch = 17;
@@ -297,17 +304,15 @@ __device__ __forceinline__ void mul_q4k(const uint8_t *wbase, const uint32_t (*r
       sc[mt][r] = q4_scales(*reinterpret_cast<const uint4 *>(row), t);
       qrow[mt][r] = row + 16 + 32 * t;
     }
-  // Two accumulator sets per (m-tile, token half): the low-nibble and the high-nibble sub-blocks' products.
-  // A set is then touched by every fourth MMA, which leaves room for the MMA's latency.
-  float aq[NMT][2][4], ar[NMT][2][4];
+  float aq[NMT][2][4];
 #pragma unroll
   for (int mt = 0; mt < NMT; ++mt)
 #pragma unroll
     for (int h = 0; h < 2; ++h)
 #pragma unroll
-      for (int c = 0; c < 4; ++c) aq[mt][h][c] = 0.0f, ar[mt][h][c] = 0.0f;
+      for (int c = 0; c < 4; ++c) aq[mt][h][c] = 0.0f;
   const uint32_t kMagic = 0x64006400u;
-#pragma unroll
+  SB_UNROLL_Q4K_I2
   for (int i2 = 0; i2 < 4; ++i2) {
     uint4 bx[2][2];
 #pragma unroll
@@ -342,7 +347,7 @@ __device__ __forceinline__ void mul_q4k(const uint8_t *wbase, const uint32_t (*r
           const uint32_t a3 = hfma2_u32(and_or(w1s, 0x00f000f0u, kMagic), sc[mt][1].mhi, sc[mt][1].bhi);
 #pragma unroll
           for (int h = 0; h < 2; ++h)
-            mma_f16(ar[mt][h], a0, a1, a2, a3, wi ? bx[1][h].z : bx[1][h].x, wi ? bx[1][h].w : bx[1][h].y);
+            mma_f16(aq[mt][h], a0, a1, a2, a3, wi ? bx[1][h].z : bx[1][h].x, wi ? bx[1][h].w : bx[1][h].y);
         }
       }
   }
@@ -354,10 +359,10 @@ __device__ __forceinline__ void mul_q4k(const uint8_t *wbase, const uint32_t (*r
     for (int mt = 0; mt < NMT; ++mt) {
       float am[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       mma_f16(am, sc[mt][0].mn0, sc[mt][1].mn0, sc[mt][0].mn1, sc[mt][1].mn1, s.x, s.y);
-      y[mt][h][0] = fmaf(sc[mt][0].ndmin, am[0], fmaf(sc[mt][0].d, aq[mt][h][0] + ar[mt][h][0], y[mt][h][0]));
-      y[mt][h][1] = fmaf(sc[mt][0].ndmin, am[1], fmaf(sc[mt][0].d, aq[mt][h][1] + ar[mt][h][1], y[mt][h][1]));
-      y[mt][h][2] = fmaf(sc[mt][1].ndmin, am[2], fmaf(sc[mt][1].d, aq[mt][h][2] + ar[mt][h][2], y[mt][h][2]));
-      y[mt][h][3] = fmaf(sc[mt][1].ndmin, am[3], fmaf(sc[mt][1].d, aq[mt][h][3] + ar[mt][h][3], y[mt][h][3]));
+      y[mt][h][0] = fmaf(sc[mt][0].ndmin, am[0], fmaf(sc[mt][0].d, aq[mt][h][0], y[mt][h][0]));
+      y[mt][h][1] = fmaf(sc[mt][0].ndmin, am[1], fmaf(sc[mt][0].d, aq[mt][h][1], y[mt][h][1]));
+      y[mt][h][2] = fmaf(sc[mt][1].ndmin, am[2], fmaf(sc[mt][1].d, aq[mt][h][2], y[mt][h][2]));
+      y[mt][h][3] = fmaf(sc[mt][1].ndmin, am[3], fmaf(sc[mt][1].d, aq[mt][h][3], y[mt][h][3]));
     }
   }
 }
@@ -729,9 +734,10 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams 
     if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
     return;
   }
-  uint32_t drained = 0, done = 0;
+  // Super-blocks are dealt to the k-group warps round-robin over the CTA's whole stream (jmod = count so far
+  // mod kKG), so a stage of 4 keeps 4 of the 6 warps of a row group busy and the next stage the other ones.
+  uint32_t drained = 0, done = 0, jmod = 0;
   for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++done) {
-    const uint32_t tile = item / p.slices;
     float y[kMT][2][4];
 #pragma unroll
     for (int mt = 0; mt < kMT; ++mt)
@@ -741,19 +747,17 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams 
         for (int c = 0; c < 4; ++c) y[mt][h][c] = 0.0f;
     for (uint32_t c = 0; c < chunks; ++c, ++drained) {
       const uint32_t slot = drained % p.stages, round = drained / p.stages;
+      // Every warp follows every stage's barrier, with or without work in it: the parity wait tells only
+      // consecutive phases apart.
       if (!(p.debug & 16) && !mbar_wait(&full[slot], round & 1)) {
         if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
         return;  // the launch has failed; the status word says so
       }
       const uint32_t csb0 = sb0 + c * kStageSb, nsb_c = min(uint32_t(kStageSb), sb1 - csb0);
-      // Which super-block of the stage and which of the warp's m-tiles: a full stage gives each
-      // k-group warp one super-block and both m-tiles; a 2-block tail gives every warp one m-tile
-      // (block kg & 1, m-tile kg >> 1), a 1-block tail gives k-groups 0 and 1 one m-tile each.
-      uint32_t sbi = kg, mt0 = 0, nmt = kMT;
-      if (nsb_c == 2) sbi = kg & 1, mt0 = kg >> 1, nmt = 1;
-      else if (nsb_c == 1) sbi = 0, mt0 = kg & 1, nmt = kg < 2 ? 1 : 0;
-      else if (kg >= nsb_c) nmt = 0;
-      if (nmt && !(p.debug & 1)) {
+      const uint32_t sbi = kg >= jmod ? kg - jmod : kg + kKG - jmod;  // the stage's super-block dealt to this k-group
+      jmod += nsb_c;
+      if (jmod >= kKG) jmod -= kKG;
+      if (sbi < nsb_c && !(p.debug & 1)) {
         const uint8_t *stage = smem + p.ring_off + slot * p.stage_bytes;
         // A row sits in the box of its (piece, tensor, residue) at `lead` bytes past a 16-byte boundary
         // (always 0 for Q4_K, whose rows are 16-byte multiples).
@@ -776,9 +780,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams 
             }
           }
         const uint8_t *xs_sb = smem + p.x_off + lsb * kPrepSbBytes;
-        if (nmt == kMT) multiply_super_block<FMT, kMT>(stage, roff, xs_sb, xs_sb + kXsbBytes, lane, y);
-        else if (mt0 == 0) multiply_super_block<FMT, 1>(stage, roff, xs_sb, xs_sb + kXsbBytes, lane, y);
-        else multiply_super_block<FMT, 1>(stage, roff + 1, xs_sb, xs_sb + kXsbBytes, lane, y + 1);
+        multiply_super_block<FMT, kMT>(stage, roff, xs_sb, xs_sb + kXsbBytes, lane, y);
       }
       __syncwarp();
       if (lane == 0 && !(p.debug & 16)) mbar_arrive(&empty[slot]);
