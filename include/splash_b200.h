@@ -69,6 +69,10 @@ SB_API int sb_sm_count(void);
 /* Programmatic dependent launch (kernel prologues overlap the previous kernel's tail) for the small
  * kernels of this context; on by default. sb_linear takes it per call (SB_LINEAR_PDL). */
 SB_API int sb_set_pdl(int enabled);
+/* Which sb_attn_verify kernel runs: SB_ATTENTION_TCGEN05 (default; S and O in tensor memory) or
+ * SB_ATTENTION_WARP_MMA (mma.sync; also taken when rows x group exceeds 128). Same results contract. */
+enum { SB_ATTENTION_TCGEN05 = 0, SB_ATTENTION_WARP_MMA = 1 };
+SB_API int sb_set_attention_kernel(int kind);
 
 SB_API int sb_alloc(size_t bytes, void **out_dev);
 SB_API int sb_free(void *dev);

@@ -90,6 +90,7 @@ def case_linear(a):
 def case_attention(a):
     rng = np.random.default_rng(0)
     l = lib.ops()
+    lib.check(l.sb_set_attention_kernel(1 if a.warp_mma else 0))
     QH, KH, D, PT, committed, rows = a.q_heads, a.kv_heads, a.head_dim, a.page_tokens, a.context, a.rows
     pages = (committed + rows + PT - 1) // PT + 1
     k = lib.DeviceBuffer.from_numpy(rng.integers(-127, 128, (pages, KH, PT, D), dtype=np.int8))
@@ -105,7 +106,7 @@ def case_attention(a):
     args = lib.SbAttnArgs(q.ptr, qkv.ptr, table.ptr, None, out.ptr, cache, None, rows, QH, 1, stride, QH * D, committed)
     us = timed(lambda i: lib.check(l.sb_attn_verify(None, ctypes.byref(args))), a.iters)
     algo = 2 * (committed + rows) * KH * (D + 2)
-    print(f"attention q_heads={QH} kv_heads={KH} D={D} context={committed} rows={rows}: {us:.1f} us per launch, "
+    print(f"attention ({'warp MMA' if a.warp_mma else 'tcgen05'}) q_heads={QH} kv_heads={KH} D={D} context={committed} rows={rows}: {us:.1f} us per launch, "
           f"{algo / us / 1e3:.0f} GB/s of {algo} algorithmic bytes, device status {lib.device_status()}")
 
 
@@ -159,6 +160,7 @@ def main(argv=None):
     p.add_argument("--page-tokens", type=int, default=256)
     p.add_argument("--rows", type=int, default=16)
     p.add_argument("--iters", type=int, default=10)
+    p.add_argument("--warp-mma", action="store_true", help="the mma.sync kernel instead of the tcgen05 one")
     p = sub.add_parser("gdn")
     p.add_argument("--key-heads", type=int, default=16)
     p.add_argument("--value-heads", type=int, default=48)

@@ -22,30 +22,14 @@
 //             and multiplying by sigmoid(gate)
 #include <algorithm>
 
-#include "sb_internal.h"
-#include "sb_ptx.cuh"
+#include "sb_attention_internal.cuh"
 
 namespace sb {
 
 constexpr int kAttnThreads = 256;
 constexpr int kChunk = 32;       // tokens per step of the page loop
-constexpr int kMaxFused = 128;   // rows x query heads of one KV head
 constexpr int kRing = 3;         // raw chunks in flight per CTA
 constexpr int kConv = 3;         // converted chunks (fp16) buffered for the multiplying warps
-
-struct AttnParams {
-  const uint16_t *queries, *qkv;
-  const uint32_t *page_table;
-  const uint2 *tree;
-  uint16_t *out;
-  SbKvLayer cache;
-  float *partials;     // [kv_head][split][fused][D]
-  float *stats;        // [kv_head][split][fused][2]
-  uint32_t *counters;  // [kv_head] arrivals, [64 + kv_head] merges done
-  uint32_t *status;
-  const uint32_t *committed_dev;
-  uint32_t rows, q_heads, group, gated, qkv_stride, out_stride, committed, splits, chunks_per_split, fused;
-};
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void *p) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
@@ -56,19 +40,6 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
                : "r"(smem_u32(p)));
-}
-
-// 16 int8 (one uint4) -> 16 fp16, exactly: (q ^ 0x80) | 0x6400 is 1024 + q + 128.
-__device__ __forceinline__ void int8x16_to_half(const uint4 v, uint4 &lo, uint4 &hi) {
-  const uint32_t w[4] = {v.x ^ 0x80808080u, v.y ^ 0x80808080u, v.z ^ 0x80808080u, v.w ^ 0x80808080u};
-  uint32_t o[8];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    o[2 * i] = hsub2_u32(__byte_perm(w[i], 0x64646464u, 0x4140), 0x64806480u);      // bytes 0, 1
-    o[2 * i + 1] = hsub2_u32(__byte_perm(w[i], 0x64646464u, 0x4342), 0x64806480u);  // bytes 2, 3
-  }
-  lo = make_uint4(o[0], o[1], o[2], o[3]);
-  hi = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
 template <int D>
@@ -358,77 +329,18 @@ __global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnPa
       }
     }
   }
-  // Every split of this KV head publishes its partials, then all of the head's CTAs (co-resident: the
-  // launch is cooperative and the grid has at most one CTA per SM) share the merge: CTA `split` merges
-  // fused rows split, split + splits, ... A bounded wait: if the other splits never arrive the kernel sets
-  // the status word and leaves.
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    atomicAdd(&p.counters[kvh], 1u);
-    uint32_t spins = 0;
-    while (atomicAdd(&p.counters[kvh], 0u) < p.splits && ++spins < (1u << 22)) __nanosleep(100);
-    s_last = spins < (1u << 22);
-    if (!s_last) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  // Merge in split order: a warp per fused row, lane -> dimensions lane + 32 i; loads batched 8 splits deep.
-  for (uint32_t f = split + warp * p.splits; f < F; f += (kAttnThreads / 32) * p.splits) {
-    const float *stats = p.stats + (size_t(kvh) * p.splits * kMaxFused + f) * 2;
-    const float *parts = p.partials + (size_t(kvh) * p.splits * kMaxFused + f) * D;
-    const size_t sstride = size_t(kMaxFused) * 2, pstride = size_t(kMaxFused) * D;
-    float mall = -INFINITY;
-    for (uint32_t s = lane; s < p.splits; s += 32) mall = fmaxf(mall, __ldcg(stats + s * sstride));
-#pragma unroll
-    for (int o = 16; o; o >>= 1) mall = fmaxf(mall, __shfl_xor_sync(0xffffffffu, mall, o));
-    float num[D / 32];
-#pragma unroll
-    for (int i = 0; i < D / 32; ++i) num[i] = 0.0f;
-    float den = 0.0f;
-    for (uint32_t s0 = 0; s0 < p.splits; s0 += 8) {
-      float ms[8], ls[8], v[8][D / 32];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const uint32_t s = min(s0 + j, p.splits - 1);
-        ms[j] = __ldcg(stats + s * sstride);
-        ls[j] = __ldcg(stats + s * sstride + 1);
-#pragma unroll
-        for (int i = 0; i < D / 32; ++i) v[j][i] = __ldcg(parts + s * pstride + lane + 32 * i);
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (s0 + j >= p.splits || ms[j] == -INFINITY) continue;
-        const float w = exp2f(ms[j] - mall);
-#pragma unroll
-        for (int i = 0; i < D / 32; ++i) num[i] += w * v[j][i];
-        den += w * ls[j];
-      }
-    }
-    const uint32_t row = f / G, qh = kvh * G + f % G;
-#pragma unroll
-    for (int i = 0; i < D / 32; ++i) {
-      const uint32_t d = lane + 32 * i;
-      float o = round_bf16(den > 0.0f ? num[i] / den : 0.0f);
-      if (p.gated) {
-        const float gate = bf16_bits_to_float(p.qkv[size_t(row) * p.qkv_stride + qh * 2 * D + D + d]);
-        o = o * sigmoid_f(gate);
-      }
-      p.out[size_t(row) * p.out_stride + qh * D + d] = float_to_bf16_bits(o);
-    }
-  }
-  // The last CTA to finish its share returns both counters to zero for the next launch.
-  __syncthreads();
-  if (tid == 0 && atomicAdd(&p.counters[64 + kvh], 1u) == p.splits - 1) {
-    p.counters[kvh] = 0;
-    p.counters[64 + kvh] = 0;
-  }
+  attention_merge<D>(p, split, kvh, &s_last);
 }
 
 }  // namespace sb
 
 using namespace sb;
+
+extern "C" int sb_set_attention_kernel(int kind) {
+  SB_REQUIRE(kind == SB_ATTENTION_TCGEN05 || kind == SB_ATTENTION_WARP_MMA, "sb_set_attention_kernel: unknown kernel %d", kind);
+  ctx().attention_kernel = kind;
+  return SB_OK;
+}
 
 extern "C" int sb_attn_verify(void *stream, const SbAttnArgs *a) {
   SB_NEED_DEVICE();
@@ -444,6 +356,22 @@ extern "C" int sb_attn_verify(void *stream, const SbAttnArgs *a) {
   SB_REQUIRE(!a->gated || a->qkv, "sb_attn_verify: a gated layer needs the packed rows");
   SB_REQUIRE(a->out_stride >= a->q_heads * c.head_dim, "sb_attn_verify: out_stride below the row");
   Context &cx = ctx();
+  if (cx.attention_kernel == SB_ATTENTION_TCGEN05) {
+    AttnParams p{};
+    p.queries = static_cast<const uint16_t *>(a->queries);
+    p.qkv = static_cast<const uint16_t *>(a->qkv);
+    p.page_table = a->page_table;
+    p.tree = static_cast<const uint2 *>(a->tree);
+    p.out = static_cast<uint16_t *>(a->out);
+    p.cache = c;
+    p.partials = cx.attn_workspace;
+    p.counters = cx.attn_counters;
+    p.status = cx.status_dev;
+    p.committed_dev = a->committed_dev;
+    p.rows = a->rows, p.q_heads = a->q_heads, p.group = group, p.gated = a->gated, p.qkv_stride = a->qkv_stride;
+    p.out_stride = a->out_stride, p.committed = a->committed, p.fused = fused;
+    return launch_attention_tc(as_stream(stream), p, a->committed + a->rows);
+  }
   const uint32_t D = c.head_dim, visible = a->committed + a->rows, chunks = (visible + kChunk - 1) / kChunk;
   // Splits: about one CTA per SM over all KV heads, at least 4 chunks each.
   uint32_t splits = std::max(1u, uint32_t(cx.sm_count) / c.kv_heads);  // the whole grid is resident at once

@@ -79,9 +79,10 @@ __device__ __forceinline__ uint64_t umma_smem_desc(uint32_t smem_addr, uint32_t 
   return uint64_t((smem_addr >> 4) & 0x3fffu) | (uint64_t((lbo >> 4) & 0x3fffu) << 16) | (uint64_t((sbo >> 4) & 0x3fffu) << 32) |
          (uint64_t(1) << 46);
 }
-// Instruction descriptor of kind::f16: fp16 A and B, both K-major, fp32 accumulator, M x N tile.
-__host__ __device__ constexpr uint32_t umma_idesc_f16(uint32_t m, uint32_t n) {
-  return (1u << 4) | ((n >> 3) << 17) | ((m >> 4) << 24);
+// Instruction descriptor of kind::f16: fp16 A (K-major) and B (K-major, or MN-major = N contiguous), fp32
+// accumulator, M x N tile.
+__host__ __device__ constexpr uint32_t umma_idesc_f16(uint32_t m, uint32_t n, bool b_mn_major = false) {
+  return (1u << 4) | (b_mn_major ? 1u << 16 : 0u) | ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 // D[tmem] (+)= A[tmem] * B[smem]^T for one K = 16 step; issued by one thread.

@@ -225,6 +225,7 @@ def _bind_ops():
     l.sb_linear_f32.argtypes = [_P, _P, _P, _U, _U, _U, _U, _P, _U, _U, _P]
     l.sb_attn_store.argtypes = [_P, ctypes.POINTER(SbAttnStoreArgs)]
     l.sb_attn_verify.argtypes = [_P, ctypes.POINTER(SbAttnArgs)]
+    l.sb_set_attention_kernel.argtypes = [ctypes.c_int]
     l.sb_kv_path_commit.argtypes = [_P, ctypes.POINTER(SbKvLayer), _P, _U, _P]
     l.sb_gdn_verify.argtypes = [_P, ctypes.POINTER(SbGdnArgs)]
     l.sb_gdn_verify_static.argtypes = [_P, ctypes.POINTER(SbGdnArgs)]

@@ -95,7 +95,8 @@ class DevKv:
                 self.ks.to_numpy(h.ks.dtype, h.ks.shape), self.vs.to_numpy(h.vs.dtype, h.vs.shape))
 
 
-def attention_case(lib, l, o, *, q_heads, kv_heads, D, page_tokens, scale_f16, committed, rows, gated, seed):
+def attention_case(lib, l, o, *, q_heads, kv_heads, D, page_tokens, scale_f16, committed, rows, gated, seed, kernel=0):
+    lib.check(l.sb_set_attention_kernel(kernel))  # 0: tcgen05 (S and O in tensor memory), 1: warp-level MMA
     rng = np.random.default_rng(seed)
     pairs = 32 if D == 256 else 16
     pages = (committed + rows + page_tokens - 1) // page_tokens + 1
@@ -146,10 +147,12 @@ def attention_case(lib, l, o, *, q_heads, kv_heads, D, page_tokens, scale_f16, c
     dict(q_heads=24, kv_heads=4, D=256, page_tokens=32, scale_f16=False, committed=1000, rows=5, gated=True, seed=3),
     dict(q_heads=16, kv_heads=2, D=256, page_tokens=64, scale_f16=False, committed=7, rows=16, gated=True, seed=4),
     dict(q_heads=8, kv_heads=2, D=128, page_tokens=32, scale_f16=True, committed=0, rows=1, gated=False, seed=5),
+    dict(q_heads=24, kv_heads=4, D=256, page_tokens=32, scale_f16=True, committed=4999, rows=16, gated=True, seed=6),
 ])
-def test_kv_store_bit_exact_and_attention_within_gates(cfg):
+@pytest.mark.parametrize("kernel", [0, 1])
+def test_kv_store_bit_exact_and_attention_within_gates(cfg, kernel):
     lib, l, o = _setup()
-    r = attention_case(lib, l, o, **cfg)
+    r = attention_case(lib, l, o, kernel=kernel, **cfg)
     # staged queries and the quantized rows: bit-exact
     assert np.array_equal(r["got_q"], r["want_q"])
     h = r["host"]
@@ -165,10 +168,11 @@ def test_kv_store_bit_exact_and_attention_within_gates(cfg):
     assert np.median(rel) < 2e-3 and rel.max() < 2e-2
 
 
-def test_attention_long_context_32k():
+@pytest.mark.parametrize("kernel", [0, 1])
+def test_attention_long_context_32k(kernel):
     lib, l, o = _setup()
     r = attention_case(lib, l, o, q_heads=24, kv_heads=4, D=256, page_tokens=256, scale_f16=True, committed=32768 - 16,
-                       rows=16, gated=True, seed=9)
+                       rows=16, gated=True, seed=9, kernel=kernel)
     got, want64 = ol.bf2f(r["got"]).astype(np.float64), r["want64"]
     cos = (got * want64).sum() / np.sqrt((got * got).sum() * (want64 * want64).sum())
     assert cos > 0.9995 and np.abs(got - want64).max() < 0.02
