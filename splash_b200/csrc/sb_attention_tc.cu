@@ -28,7 +28,10 @@ namespace sb {
 
 constexpr int kAtChunk = 64;                 // tokens per chunk
 constexpr int kAtRaw = 3;                    // raw chunks in flight
-constexpr int kAtThreads = 32 * 9;           // 4 softmax warps, 4 converter warps, 1 MMA warp
+constexpr int kAtConvWarps = 4;               // converter warps
+constexpr int kAtConvThreads = 32 * kAtConvWarps;
+constexpr int kAtMmaWarp = 4 + kAtConvWarps;
+constexpr int kAtThreads = 32 * (kAtMmaWarp + 1);  // 4 softmax warps, the converter warps, 1 MMA warp
 constexpr float kAtLazy = 8.0f;              // the reference maximum moves when exceeded by more than 2^8
 
 template <int D>
@@ -83,7 +86,7 @@ __global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(const AttnP
     mbar_init(q_ready, 4);
     fence_mbar_init();
   }
-  if (warp == 8) tmem_alloc(tmem_slot, 512);
+  if (warp == kAtMmaWarp) tmem_alloc(tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -247,7 +250,7 @@ __global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(const AttnP
         ps[1] = l_run;
       }
     }
-  } else if (warp < 8) {
+  } else if (warp < kAtMmaWarp) {
     // ---- converter warps; their first thread also keeps the raw ring full ----
     const uint32_t ctid = tid - 128;
     uint8_t *ring = smem + L::kRaw;
@@ -282,21 +285,24 @@ __global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(const AttnP
       }
       const uint8_t *src = ring + slot * L::kRawBytes;
       uint8_t *kb = smem + L::kK + b * L::kConvBytes, *vb = smem + L::kV + b * L::kConvBytes;
-      // Unit (token, part = 16 dimensions). Consecutive threads take consecutive tokens and, diagonally,
-      // different parts, so neither the 16-byte reads nor the 16-byte writes of a quarter warp share a bank.
-#pragma unroll 4
-      for (uint32_t idx = ctid; idx < kAtChunk * (D / 16); idx += 128) {
-        const uint32_t tok = idx % kAtChunk, pb = idx / kAtChunk;
+      // Unit (token, part = 16 dimensions). A thread keeps one token (consecutive threads, consecutive tokens)
+      // and walks the parts diagonally, so neither the 16-byte reads nor the 16-byte writes of a quarter warp
+      // share a bank.
+      static_assert(kAtConvThreads % kAtChunk == 0, "a converter thread keeps its token");
+      const uint32_t tok = ctid % kAtChunk, pb0 = ctid / kAtChunk;
+      const uint8_t *ksrc = src + tok * D, *vsrc = ksrc + kAtChunk * D;
+      uint8_t *kdst = kb + (tok >> 3) * 256 + (tok & 7) * 16, *vdst = vb + (tok >> 3) * (D / 8 * 128) + (tok & 7) * 16;
+#pragma unroll
+      for (uint32_t it = 0; it < (D / 16) / (kAtConvThreads / kAtChunk); ++it) {
+        const uint32_t pb = pb0 + it * (kAtConvThreads / kAtChunk);
         const uint32_t part = (pb & ~7u) | ((pb + tok) & 7u);
         uint4 lo, hi;
-        int8x16_to_half(*reinterpret_cast<const uint4 *>(src + tok * D + part * 16), lo, hi);
-        uint8_t *kd = kb + part * (kAtChunk * 32) + (tok >> 3) * 256 + (tok & 7) * 16;
-        *reinterpret_cast<uint4 *>(kd) = lo;
-        *reinterpret_cast<uint4 *>(kd + 128) = hi;
-        int8x16_to_half(*reinterpret_cast<const uint4 *>(src + kAtChunk * D + tok * D + part * 16), lo, hi);
-        uint8_t *vd = vb + (tok >> 3) * (D / 8 * 128) + (2 * part) * 128 + (tok & 7) * 16;
-        *reinterpret_cast<uint4 *>(vd) = lo;
-        *reinterpret_cast<uint4 *>(vd + 128) = hi;
+        int8x16_to_half(*reinterpret_cast<const uint4 *>(ksrc + part * 16), lo, hi);
+        *reinterpret_cast<uint4 *>(kdst + part * (kAtChunk * 32)) = lo;
+        *reinterpret_cast<uint4 *>(kdst + part * (kAtChunk * 32) + 128) = hi;
+        int8x16_to_half(*reinterpret_cast<const uint4 *>(vsrc + part * 16), lo, hi);
+        *reinterpret_cast<uint4 *>(vdst + part * 256) = lo;
+        *reinterpret_cast<uint4 *>(vdst + part * 256 + 128) = hi;
       }
       if (ctid < kAtChunk) {
         // Tokens past the visible ones share the page but hold nothing: their scales read as zero.
@@ -313,7 +319,7 @@ __global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(const AttnP
         scales[b * 2 * kAtChunk + kAtChunk + ctid] = live ? vsc : 0.0f;
       }
       fence_proxy_async();      // the MMAs read these shared-memory writes through the async proxy
-      named_bar_sync(1, 128);   // the four converter warps have written the chunk and read the raw slot
+      named_bar_sync(1, kAtConvThreads);  // every converter warp has written the chunk and read the raw slot
       if (ctid == 0) {
         mbar_arrive(&kv_full[b]);
         if (i + kAtRaw < n) issue(i + kAtRaw);
@@ -361,7 +367,7 @@ __global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(const AttnP
   // Everyone meets here, also after a wait that gave up, so tensor memory is always returned.
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == kAtMmaWarp) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, 512);
   }
