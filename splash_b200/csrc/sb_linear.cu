@@ -121,28 +121,48 @@ struct PrepareParams {
   uint32_t rows, k, x_stride, pair_layout;  // layout: 0 range, 1 pair, 2 tensor-core tiles
 };
 
-__device__ __forceinline__ float block_reduce(float v, float *scratch, bool is_max) {
-  // Fixed order: butterfly within each warp, then the warps' values in index order.
+// Sum of `s` and maximum of `m` over the block, both returned to every thread. Fixed order: butterfly within
+// each warp, then the warps' values in index order.
+__device__ __forceinline__ void block_reduce2(float &s, float &m, float *scratch) {
 #pragma unroll
   for (int o = 16; o; o >>= 1) {
-    const float other = __shfl_xor_sync(0xffffffffu, v, o);
-    v = is_max ? fmaxf(v, other) : v + other;
+    s += __shfl_xor_sync(0xffffffffu, s, o);
+    m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  }
+  if ((threadIdx.x & 31) == 0) {
+    scratch[2 * (threadIdx.x >> 5)] = s;
+    scratch[2 * (threadIdx.x >> 5) + 1] = m;
   }
   __syncthreads();
-  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-  __syncthreads();
-  float r = scratch[0];
-  for (int w = 1; w < kPrepThreads / 32; ++w) r = is_max ? fmaxf(r, scratch[w]) : r + scratch[w];
-  return r;
+  s = scratch[0], m = scratch[1];
+  for (int w = 1; w < kPrepThreads / 32; ++w) {
+    s += scratch[2 * w];
+    m = fmaxf(m, scratch[2 * w + 1]);
+  }
 }
 
 __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PrepareParams p) {
-  __shared__ float scratch[kPrepThreads / 32];
-  pdl_launch_dependents();
-  pdl_wait();
+  __shared__ float scratch[2 * (kPrepThreads / 32)];
   const uint32_t tok = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
   const bool live = tok < p.rows;
   const uint32_t chunks = p.k / 8;
+  pdl_launch_dependents();
+  // The norm weights do not depend on the previous kernel: they are fetched before the dependency wait.
+  float wn[kPrepMaxChunks][8];
+  if (p.norm_w) {
+#pragma unroll
+    for (int i = 0; i < kPrepMaxChunks; ++i) {
+      const uint32_t c = tid + kPrepThreads * i;
+      float4 w0 = make_float4(0, 0, 0, 0), w1 = w0;
+      if (c < chunks) {
+        w0 = *reinterpret_cast<const float4 *>(p.norm_w + 8 * c);
+        w1 = *reinterpret_cast<const float4 *>(p.norm_w + 8 * c + 4);
+      }
+      wn[i][0] = w0.x, wn[i][1] = w0.y, wn[i][2] = w0.z, wn[i][3] = w0.w;
+      wn[i][4] = w1.x, wn[i][5] = w1.y, wn[i][6] = w1.z, wn[i][7] = w1.w;
+    }
+  }
+  pdl_wait();
   float v[kPrepMaxChunks][8];
   const uint16_t *row = p.x + size_t(tok) * p.x_stride;
 #pragma unroll
@@ -157,25 +177,24 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PreparePara
       v[i][2 * j + 1] = bf16_bits_to_float(u[j] >> 16);
     }
   }
+  // One pass of block reductions gives both the sum of squares and the largest |x * w| (or |x| without a
+  // norm): the largest normalised magnitude is then inv * that, up to the bf16 rounding allowed for below.
+  float ss = 0.0f, mx = 0.0f;
+#pragma unroll
+  for (int i = 0; i < kPrepMaxChunks; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      ss = fmaf(v[i][j], v[i][j], ss);
+      mx = fmaxf(mx, fabsf(p.norm_w ? v[i][j] * wn[i][j] : v[i][j]));  // NaN does not win a max; it stays in the values
+    }
+  block_reduce2(ss, mx, scratch);
   if (p.norm_w) {
-    float ss = 0.0f;
+    const float inv = rsqrtf(ss / float(p.k) + 1e-6f);
 #pragma unroll
     for (int i = 0; i < kPrepMaxChunks; ++i)
 #pragma unroll
-      for (int j = 0; j < 8; ++j) ss = fmaf(v[i][j], v[i][j], ss);
-    ss = block_reduce(ss, scratch, false);
-    const float inv = rsqrtf(ss / float(p.k) + 1e-6f);
-#pragma unroll
-    for (int i = 0; i < kPrepMaxChunks; ++i) {
-      const uint32_t c = tid + kPrepThreads * i;
-      if (live && c < chunks) {
-        const float4 w0 = *reinterpret_cast<const float4 *>(p.norm_w + 8 * c);
-        const float4 w1 = *reinterpret_cast<const float4 *>(p.norm_w + 8 * c + 4);
-        const float wn[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[i][j] = round_bf16((v[i][j] * inv) * wn[j]);
-      }
-    }
+      for (int j = 0; j < 8; ++j) v[i][j] = round_bf16((v[i][j] * inv) * wn[i][j]);
+    mx = mx * inv * 1.0625f;  // (x inv) w against x w inv and the rounding to bf16: well inside 6 %
   }
   if (p.normed_out && live) {
 #pragma unroll
@@ -190,12 +209,6 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PreparePara
       }
     }
   }
-  float mx = 0.0f;
-#pragma unroll
-  for (int i = 0; i < kPrepMaxChunks; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) mx = fmaxf(mx, fabsf(v[i][j]));  // NaN does not win a max; it stays in the values
-  mx = block_reduce(mx, scratch, true);
   int e = 0;
   if (mx > 0.0f && mx <= 3.0e38f) {
     (void)frexpf(mx, &e);  // mx = f * 2^e with f in [0.5, 1): scaled values stay below 2^10
