@@ -42,7 +42,8 @@ namespace sb {
 
 constexpr int kTcDequantWarps = 12, kTcEpilogueWarps = 8;  // dequant: 3 groups (one per A buffer) x 4 quadrants
 constexpr int kTcProducerWarp = kTcDequantWarps + kTcEpilogueWarps, kTcMmaWarp = kTcProducerWarp + 1;
-constexpr int kTcThreads = 32 * (kTcMmaWarp + 1);  // 704
+constexpr int kTcMmaWarps = 2;                     // each issues the K-steps of one parity
+constexpr int kTcThreads = 32 * (kTcMmaWarp + kTcMmaWarps);  // 736
 constexpr uint32_t kTcTileRows = 128;
 constexpr uint32_t kTcStageBytes = kTcTileRows * 144;  // one super-block column of a tile
 constexpr uint32_t kTcBoxes = 1, kTcBoxRows = kTcTileRows / kTcBoxes;  // TMA boxes per stage
@@ -138,10 +139,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) linear_tc_kernel(const TcParams
     }
     for (uint32_t i = 0; i < kTcABufs; ++i) {
       mbar_init(&a_full[i], 4);
-      mbar_init(&a_empty[i], 1);
+      mbar_init(&a_empty[i], kTcMmaWarps);
     }
     for (uint32_t i = 0; i < kTcDBufs; ++i) {
-      mbar_init(&d_full[i], 1);
+      mbar_init(&d_full[i], kTcMmaWarps);
       mbar_init(&d_empty[i], 4);
     }
     mbar_init(xfull, 1);
@@ -181,13 +182,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) linear_tc_kernel(const TcParams
     // Do not leave while copies are in flight: the dequant warps release a stage only after its bytes landed.
     for (uint32_t f = u > p.stages ? u - p.stages : 0; f < u; ++f)
       if (!warp_wait_backoff(&raw_empty[f % p.stages], (f / p.stages) & 1)) break;
-  } else if (warp == kTcMmaWarp) {
-    // ---- MMA issuer ----
+  } else if (warp >= kTcMmaWarp) {
+    // ---- MMA issuers: one thread per K-step parity ----
     if (lane == 0) {
-      pdl_wait();  // the prepared activations come from the previous kernel
-      mbar_arrive_expect_tx(xfull, slice_sb * kPrepSbBytes + kPrepHeader);
-      bulk_g2s(scale_back, p.prepared, kPrepHeader, xfull);
-      bulk_g2s(x_s, p.prepared + kPrepHeader + size_t(sb0) * kPrepSbBytes, slice_sb * kPrepSbBytes, xfull);
+      const uint32_t half = warp - kTcMmaWarp;
+      if (half == 0) {
+        pdl_wait();  // the prepared activations come from the previous kernel
+        mbar_arrive_expect_tx(xfull, slice_sb * kPrepSbBytes + kPrepHeader);
+        bulk_g2s(scale_back, p.prepared, kPrepHeader, xfull);
+        bulk_g2s(x_s, p.prepared + kPrepHeader + size_t(sb0) * kPrepSbBytes, slice_sb * kPrepSbBytes, xfull);
+      }
       bool ok = mbar_wait(xfull, 0);
       if (!ok) report_expired(p.status, 2, 0);
       constexpr uint32_t idesc = umma_idesc_f16(128, 16);
@@ -206,7 +210,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) linear_tc_kernel(const TcParams
             tc_fence_after_sync();
             const uint32_t a0 = tmem + ab * kTcACols, d0 = tmem + kTcDCol0 + db * kTcDCols;
             const uint64_t b0 = umma_smem_desc(smem_u32(x_s + c * kPrepSbBytes), 128, 256);
-            if (!(p.debug & 1)) umma_q4k_super_block(d0, a0, b0, idesc);
+            if (!(p.debug & 1)) umma_q4k_super_block_half(d0, a0, b0, idesc, half);
             if (p.debug & 8) {  // only with 1: plain arrivals in place of the commits
               mbar_arrive(&a_empty[ab]);
               mbar_arrive(&d_full[db]);

@@ -163,6 +163,87 @@ __device__ __forceinline__ void umma_q4k_super_block(uint32_t d_tmem, uint32_t a
       ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
       : "memory");
 }
+// The same super-block issued by two threads: thread `half` issues the K-steps of its parity into its own
+// accumulator (D + 16 half); thread 0 also issues the mins' MMA into D + 32. The threads' MMAs are independent,
+// so neither waits for the other's issue slot.
+__device__ __forceinline__ void umma_q4k_super_block_half(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t half) {
+  if (half == 0)
+    asm volatile(
+      "{\n\t"
+      ".reg .pred pf, pt;\n\t"
+      ".reg .b32 a, d;\n\t"
+      ".reg .b64 b;\n\t"
+      "setp.ne.b32 pf, 0, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "add.u32 d, %0, 0;\n\t"
+      "add.u32 a, %1, 0;\n\t"
+      "add.u64 b, %2, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pf;\n\t"
+      "add.u32 a, %1, 16;\n\t"
+      "add.u64 b, %2, 64;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 32;\n\t"
+      "add.u64 b, %2, 128;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 48;\n\t"
+      "add.u64 b, %2, 192;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 64;\n\t"
+      "add.u64 b, %2, 256;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 80;\n\t"
+      "add.u64 b, %2, 320;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 96;\n\t"
+      "add.u64 b, %2, 384;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 112;\n\t"
+      "add.u64 b, %2, 448;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 128;\n\t"
+      "add.u32 d, %0, 32;\n\t"
+      "add.u64 b, %2, 512;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pf;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
+      : "memory");
+  else
+    asm volatile(
+      "{\n\t"
+      ".reg .pred pf, pt;\n\t"
+      ".reg .b32 a, d;\n\t"
+      ".reg .b64 b;\n\t"
+      "setp.ne.b32 pf, 0, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "add.u32 d, %0, 16;\n\t"
+      "add.u32 a, %1, 8;\n\t"
+      "add.u64 b, %2, 32;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pf;\n\t"
+      "add.u32 a, %1, 24;\n\t"
+      "add.u64 b, %2, 96;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 40;\n\t"
+      "add.u64 b, %2, 160;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 56;\n\t"
+      "add.u64 b, %2, 224;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 72;\n\t"
+      "add.u64 b, %2, 288;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 88;\n\t"
+      "add.u64 b, %2, 352;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 104;\n\t"
+      "add.u64 b, %2, 416;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pt;\n\t"
+      "add.u32 a, %1, 120;\n\t"
+      "add.u64 b, %2, 480;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [d], [a], b, %3, pt;\n\t"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc)
+      : "memory");
+}
 // The mbarrier receives one arrival when every MMA this thread has issued so far has completed.
 __device__ __forceinline__ void umma_commit(uint64_t *bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
