@@ -261,7 +261,7 @@ typedef struct SbGdnTape {
  * [value_head][value dim 128][key dim 128]. */
 typedef struct SbGdnArgs {
   const void *qkvz;        /* bf16 [rows, qkvz_stride]: q | k | v | z */
-  const void *b, *a;       /* bf16 [rows, ab_stride] */
+  const void *b, *a;       /* bf16 [rows, ab_stride]; unused (may be null) with gate_weight */
   const void *conv_w;      /* bf16 [conv_dim, 4] */
   const float *a_scale;    /* fp32 [value_heads] */
   const void *dt_bias;     /* bf16 [value_heads] */
@@ -274,6 +274,13 @@ typedef struct SbGdnArgs {
   void *hidden;            /* bf16 [rows, hidden_stride] */
   const uint32_t *pending_rows_dev;
   uint32_t rows, pending_rows, key_heads, value_heads, qkvz_stride, ab_stride, hidden_stride, tiled;
+  /* Optional fused gate projection (ops::addGgufFloat of the alpha / beta rows, runtime/ops/LinearGguf.cpp:559-604,
+   * inside the same kernel): when gate_weight is given, b and a are not read; row r's b for head h is
+   * bf16(gate_input[r] . gate_weight[h]) and its a is bf16(gate_input[r] . gate_weight[value_heads + h]), summed in
+   * sb_linear_f32's order, so both ways give the same bits. */
+  const float *gate_weight; /* fp32 [2 * value_heads, gate_k]: the b rows, then the a rows */
+  const void *gate_input;   /* bf16 [rows, gate_input_stride]: the normalised layer input */
+  uint32_t gate_k, gate_input_stride;
 } SbGdnArgs;
 SB_API int sb_gdn_verify(void *stream, const SbGdnArgs *args);
 

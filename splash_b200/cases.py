@@ -132,6 +132,11 @@ def case_gdn(a):
     args = lib.SbGdnArgs(d["qkvz"].ptr, d["b"].ptr, d["a"].ptr, d["conv_w"].ptr, d["a_scale"].ptr, d["dt_bias"].ptr, d["norm_w"].ptr,
                          d["cs_in"].ptr, cs_out.ptr, d["state"].ptr, st_out.ptr, T(pend), T(step), hid.ptr, None,
                          a.rows, a.pending, KH, VH, C + VW, VH, VW, 0)
+    if a.fused_gates:  # the kernel projects b and a itself from a [16, k] input and fp32 rows [2 * value_heads, k]
+        gk = a.fused_gates
+        gw = up((rng.standard_normal((2 * VH, gk)) / np.sqrt(gk)).astype(np.float32))
+        gx = up(bf(( 16, gk), 1.0))
+        args.gate_weight, args.gate_input, args.gate_k, args.gate_input_stride = gw.ptr, gx.ptr, gk, gk
     us = timed(lambda i: lib.check(l.sb_gdn_verify(None, ctypes.byref(args))), a.iters)
     algo = 2 * VH * D * D * 4
     print(f"gdn key_heads={KH} value_heads={VH} rows={a.rows} pending={a.pending}: {us:.1f} us per launch, "
@@ -166,6 +171,7 @@ def main(argv=None):
     p.add_argument("--value-heads", type=int, default=48)
     p.add_argument("--rows", type=int, default=16)
     p.add_argument("--pending", type=int, default=8)
+    p.add_argument("--fused-gates", type=int, default=0, help="k of the fused alpha / beta projection (0: b and a given)")
     p.add_argument("--iters", type=int, default=20)
     a = ap.parse_args(argv)
     lib.init(0)

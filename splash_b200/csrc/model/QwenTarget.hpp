@@ -225,9 +225,10 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
       PagedAttention::addAttention(graph, kv_, w.pages, queries_, packed_, packedStride_, pageTable_, nullptr, mixed_, mixedWidth, rows,
                                    c.q_heads, c.gated_attention != 0, committedHost, &committed);
     } else {
-      Linear::addFloat(graph, w.ssmAb, normed_, H, rows, 2 * gdn_.valueHeads, H, gates_, 2 * gdn_.valueHeads, Destination::BFloat16,
-                       nullptr);
+      // The alpha / beta projection of the normalised input runs inside the GDN kernel (same sums as
+      // Linear::addFloat would give), which takes one dependent launch per layer off the step.
       GdnDecodeBuffers g;
+      g.gateWeights = &w.ssmAb, g.gateInput = &normed_, g.gateInputSize = H;
       g.packed = packed_, g.gates = gates_, g.convolutionWeights = w.ssmConv, g.decayWeights = w.ssmA, g.timeBias = w.ssmDtBias;
       g.mixerNorm = w.ssmNorm, g.current = w.cells[parity], g.next = w.cells[parity ^ 1];
       g.pendingTape = &w.tapes[parity ^ 1], g.stepTape = &w.tapes[parity];

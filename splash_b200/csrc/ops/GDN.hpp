@@ -37,7 +37,11 @@ struct GdnCell {
 
 struct GdnDecodeBuffers {
   Buffer packed;              // bf16 [rows, packedStride]: q | k | v | z
-  Buffer gates;               // bf16 [rows, 2 * valueHeads]: b then a
+  Buffer gates;               // bf16 [rows, 2 * valueHeads]: b then a; unused when the kernel projects them itself
+  // Fused gate projection (optional): the fp32 alpha / beta rows [2 * valueHeads, gateInputSize], b rows first, and
+  // the layer's normalised input bf16 [rows, gateInputSize]. Takes the place of a separate Linear::addFloat.
+  const Buffer *gateWeights = nullptr, *gateInput = nullptr;
+  uint32_t gateInputSize = 0;
   Buffer convolutionWeights;  // bf16 [convolutionWidth, 4]
   Buffer decayWeights;        // fp32 [valueHeads] (ssm_a)
   Buffer timeBias;            // bf16 [valueHeads]
@@ -54,7 +58,13 @@ class GDN {
  public:
   static void addDecode(CommandGraph &graph, const GdnDecodeBuffers &b, const GdnShape &s, uint32_t rows) {
     requireBytes(b.packed, (size_t(rows ? rows - 1 : 0) * b.packedStride + s.convolutionWidth() + s.valueWidth()) * 2, "GDN::addDecode packed rows");
-    requireBytes(b.gates, size_t(rows) * 2 * s.valueHeads * 2, "GDN::addDecode gates");
+    if (b.gateWeights) {
+      if (!b.gateInput || !b.gateInputSize) throw std::invalid_argument("GDN::addDecode: fused gates without their input");
+      requireBytes(*b.gateWeights, size_t(2) * s.valueHeads * b.gateInputSize * 4, "GDN::addDecode gate weights");
+      requireBytes(*b.gateInput, size_t(rows) * b.gateInputSize * 2, "GDN::addDecode gate input");
+    } else {
+      requireBytes(b.gates, size_t(rows) * 2 * s.valueHeads * 2, "GDN::addDecode gates");
+    }
     requireBytes(b.convolutionWeights, size_t(s.convolutionWidth()) * 4 * 2, "GDN::addDecode convolution weights");
     requireBytes(b.decayWeights, size_t(s.valueHeads) * 4, "GDN::addDecode decay weights");
     requireBytes(b.timeBias, size_t(s.valueHeads) * 2, "GDN::addDecode time bias");
@@ -67,8 +77,13 @@ class GDN {
     if (!b.pendingTape || !b.stepTape) throw std::invalid_argument("GDN::addDecode: a tape is missing");
     SbGdnArgs a{};
     a.qkvz = b.packed.as();
-    a.b = b.gates.as();
-    a.a = b.gates.as<uint16_t>() + s.valueHeads;
+    if (b.gateWeights) {
+      a.gate_weight = b.gateWeights->as<float>(), a.gate_input = b.gateInput->as();
+      a.gate_k = a.gate_input_stride = b.gateInputSize;
+    } else {
+      a.b = b.gates.as();
+      a.a = b.gates.as<uint16_t>() + s.valueHeads;
+    }
     a.conv_w = b.convolutionWeights.as(), a.a_scale = b.decayWeights.as<float>(), a.dt_bias = b.timeBias.as();
     a.norm_w = b.mixerNorm.as<float>();
     a.conv_state_in = b.current.convolution.as(), a.conv_state_out = b.next.convolution.as();

@@ -21,6 +21,7 @@
 
 #include "sb_internal.h"
 #include "sb_ptx.cuh"
+#include "sb_dot.cuh"
 
 namespace sb {
 
@@ -47,6 +48,7 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_kernel(const GdnParams p) {
   __shared__ float q_s[kGdnRows][kD], k_s[kGdnRows][kD], pk_s[kGdnRows][kD];
   __shared__ float v_s[kGdnRows][kGdnVd], pv_s[kGdnRows][kGdnVd], o_s[kGdnRows][kGdnVd];
   __shared__ float beta_s[kGdnRows], decay_s[kGdnRows], pbeta_s[kGdnRows], pdecay_s[kGdnRows];
+  __shared__ float gate_s[2][kGdnRows];  // the head's b and a per row when the kernel projects them itself
   __shared__ __align__(16) uint16_t in_s[kGdnRows + 3][2 * kD + kGdnVd];
   __shared__ uint2 w_s[2 * kD + kGdnVd];
   __shared__ uint32_t s_last;
@@ -70,6 +72,20 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_kernel(const GdnParams p) {
   for (int r = 0; r < 4; ++r) {
     const float4 s4 = *reinterpret_cast<const float4 *>(a.state_in + sbase + size_t(r) * kD);
     S[r][0] = s4.x, S[r][1] = s4.y, S[r][2] = s4.z, S[r][3] = s4.w;
+  }
+  // Fused gate projection: warp w takes rows 2w, 2w + 1 and both gate rows of this head, four dot products at
+  // once over the layer's normalised input (the order of sb_linear_f32, so the bits agree with the unfused way).
+  if (a.gate_weight && rows > 0) {
+    const uint32_t r0 = min(2 * warp, rows ? rows - 1 : 0), r1 = min(2 * warp + 1, rows ? rows - 1 : 0);
+    const float *const wrow[2] = {a.gate_weight + size_t(h) * a.gate_k, a.gate_weight + size_t(VH + h) * a.gate_k};
+    const uint16_t *gx = static_cast<const uint16_t *>(a.gate_input);
+    const uint16_t *const xrow[2] = {gx + size_t(r0) * a.gate_input_stride, gx + size_t(r1) * a.gate_input_stride};
+    float d[2][2];
+    warp_dots_f32_bf16<2, 2>(wrow, xrow, a.gate_k, lane, d);
+    if (lane == 0) {
+      gate_s[0][2 * warp] = round_bf16(d[0][0]), gate_s[1][2 * warp] = round_bf16(d[0][1]);
+      gate_s[0][2 * warp + 1] = round_bf16(d[1][0]), gate_s[1][2 * warp + 1] = round_bf16(d[1][1]);
+    }
   }
   // Conv inputs of this CTA's channels (q and k of the key head, 32 value dimensions) for history rows
   // -3..-1 and the block's rows, staged with 16-byte loads: in_s[3 + row][local channel]. History row i
@@ -123,10 +139,10 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_kernel(const GdnParams p) {
     pdecay_s[tid] = a.pending.decay[size_t(tid) * VH + h];
   }
   if (tid < rows) {
-    const float bb = bf16_bits_to_float(static_cast<const uint16_t *>(a.b)[size_t(tid) * a.ab_stride + h]);
+    const float bb = a.gate_weight ? gate_s[0][tid] : bf16_bits_to_float(static_cast<const uint16_t *>(a.b)[size_t(tid) * a.ab_stride + h]);
+    const float aa = a.gate_weight ? gate_s[1][tid] : bf16_bits_to_float(static_cast<const uint16_t *>(a.a)[size_t(tid) * a.ab_stride + h]);
     const float be = round_bf16(sigmoid_f(bb));
-    const float x = round_bf16(__fadd_rn(bf16_bits_to_float(static_cast<const uint16_t *>(a.a)[size_t(tid) * a.ab_stride + h]),
-                                         bf16_bits_to_float(static_cast<const uint16_t *>(a.dt_bias)[h])));
+    const float x = round_bf16(__fadd_rn(aa, bf16_bits_to_float(static_cast<const uint16_t *>(a.dt_bias)[h])));
     const float sp = round_bf16(fmaxf(x, 0.0f) + log2f(1.0f + exp2f(-1.44269504089f * fabsf(x))) * 0.69314718056f);
     const float de = expf(a.a_scale[h] * sp);
     beta_s[tid] = be;
@@ -293,7 +309,7 @@ using namespace sb;
 extern "C" int sb_gdn_verify(void *stream, const SbGdnArgs *a) {
   SB_NEED_DEVICE();
   SB_REQUIRE(a, "sb_gdn_verify: null arguments");
-  SB_REQUIRE(a->qkvz && a->b && a->a && a->conv_w && a->a_scale && a->dt_bias && a->norm_w && a->conv_state_in &&
+  SB_REQUIRE(a->qkvz && ((a->b && a->a) || a->gate_weight) && a->conv_w && a->a_scale && a->dt_bias && a->norm_w && a->conv_state_in &&
                  a->conv_state_out && a->state_in && a->state_out && a->hidden,
              "sb_gdn_verify: null pointer");
   SB_REQUIRE(a->rows <= kGdnRows && a->pending_rows <= kGdnRows, "sb_gdn_verify: rows %u or pending rows %u above %d", a->rows,
@@ -301,12 +317,15 @@ extern "C" int sb_gdn_verify(void *stream, const SbGdnArgs *a) {
   SB_REQUIRE(a->key_heads >= 1 && a->value_heads % a->key_heads == 0 && a->value_heads <= 256, "sb_gdn_verify: %u value heads over %u key heads",
              a->value_heads, a->key_heads);
   const uint32_t C = (2 * a->key_heads + a->value_heads) * kD;
-  SB_REQUIRE(a->qkvz_stride >= C + a->value_heads * kD && a->ab_stride >= a->value_heads && a->hidden_stride >= a->value_heads * kD,
+  SB_REQUIRE(a->qkvz_stride >= C + a->value_heads * kD && (a->gate_weight || a->ab_stride >= a->value_heads) && a->hidden_stride >= a->value_heads * kD,
              "sb_gdn_verify: a stride is below its row");
   SB_REQUIRE(a->rows == 0 || (a->step.inputs && a->step.k && a->step.v && a->step.beta && a->step.decay), "sb_gdn_verify: null tape of this step");
   SB_REQUIRE((a->pending_rows == 0 && !a->pending_rows_dev) || (a->pending.inputs && a->pending.k && a->pending.v && a->pending.beta && a->pending.decay),
              "sb_gdn_verify: null pending tape");
   SB_REQUIRE(a->state_in != a->state_out && a->conv_state_in != a->conv_state_out, "sb_gdn_verify: the committed cell is a second cell");
+  SB_REQUIRE(!a->gate_weight || (a->gate_input && a->gate_k && a->gate_k % 8 == 0 && a->gate_input_stride >= a->gate_k && a->gate_input_stride % 8 == 0 &&
+                                 (reinterpret_cast<uintptr_t>(a->gate_weight) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->gate_input) & 15) == 0),
+             "sb_gdn_verify: fused gate projection needs a 16-byte aligned input and weight, k a multiple of 8 and stride >= k");
   Context &c = ctx();
   GdnParams p{*a, c.gdn_scratch, c.gdn_counters};
   cudaLaunchConfig_t cfg = {};
@@ -324,7 +343,7 @@ extern "C" int sb_gdn_verify(void *stream, const SbGdnArgs *a) {
 
 extern "C" int sb_gdn_verify_static(void *stream, const SbGdnArgs *a) {
   SB_REQUIRE(a, "sb_gdn_verify_static: null arguments");
-  SB_REQUIRE(a->qkvz && a->b && a->a && a->conv_w && a->a_scale && a->dt_bias && a->norm_w && a->conv_state_in &&
+  SB_REQUIRE(a->qkvz && ((a->b && a->a) || a->gate_weight) && a->conv_w && a->a_scale && a->dt_bias && a->norm_w && a->conv_state_in &&
                  a->conv_state_out && a->state_in && a->state_out && a->hidden,
              "sb_gdn_verify_static: null pointer");
   SB_REQUIRE(a->value_heads <= kStaticMaxValueHeads,
@@ -335,12 +354,15 @@ extern "C" int sb_gdn_verify_static(void *stream, const SbGdnArgs *a) {
   SB_REQUIRE(a->key_heads >= 1 && a->value_heads >= 1 && a->value_heads % a->key_heads == 0, "sb_gdn_verify_static: %u value heads over %u key heads",
              a->value_heads, a->key_heads);
   const uint32_t C = (2 * a->key_heads + a->value_heads) * kD;
-  SB_REQUIRE(a->qkvz_stride >= C + a->value_heads * kD && a->ab_stride >= a->value_heads && a->hidden_stride >= a->value_heads * kD,
+  SB_REQUIRE(a->qkvz_stride >= C + a->value_heads * kD && (a->gate_weight || a->ab_stride >= a->value_heads) && a->hidden_stride >= a->value_heads * kD,
              "sb_gdn_verify_static: a stride is below its row");
   SB_REQUIRE(a->rows == 0 || (a->step.inputs && a->step.k && a->step.v && a->step.beta && a->step.decay), "sb_gdn_verify_static: null tape of this step");
   SB_REQUIRE((a->pending_rows == 0 && !a->pending_rows_dev) || (a->pending.inputs && a->pending.k && a->pending.v && a->pending.beta && a->pending.decay),
              "sb_gdn_verify_static: null pending tape");
   SB_REQUIRE(a->state_in != a->state_out && a->conv_state_in != a->conv_state_out, "sb_gdn_verify_static: the committed cell is a second cell");
+  SB_REQUIRE(!a->gate_weight || (a->gate_input && a->gate_k && a->gate_k % 8 == 0 && a->gate_input_stride >= a->gate_k && a->gate_input_stride % 8 == 0 &&
+                                 (reinterpret_cast<uintptr_t>(a->gate_weight) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->gate_input) & 15) == 0),
+             "sb_gdn_verify_static: fused gate projection needs a 16-byte aligned input and weight, k a multiple of 8 and stride >= k");
   uint8_t *scratch = nullptr;
   const int st = static_scratch_address(&scratch);
   if (st != SB_OK) return st;

@@ -4,6 +4,7 @@
 #include <algorithm>
 
 #include "sb_dequant.cuh"
+#include "sb_dot.cuh"
 
 namespace sb {
 
@@ -105,6 +106,13 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const float *w, const u
   }
   // Lane-strided groups of 8 inputs, then a butterfly over the lanes.
   float acc = 0.0f;
+  if (!norm_w) {
+    const float *const wrow[1] = {wr};
+    const uint16_t *const xrow[1] = {xr};
+    float d[1][1];
+    warp_dots_f32_bf16<1, 1>(wrow, xrow, k, lane, d);
+    acc = d[0][0];
+  } else {
 #pragma unroll 5
   for (uint32_t c = 8 * lane; c < k; c += 256) {
     const uint4 v = *reinterpret_cast<const uint4 *>(xr + c);
@@ -120,6 +128,7 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const float *w, const u
   }
 #pragma unroll
   for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  }
   if (lane == 0) {
     if (out_f32) static_cast<float *>(out)[size_t(r) * out_stride + col] = acc;
     else static_cast<uint16_t *>(out)[size_t(r) * out_stride + col] = float_to_bf16_bits(acc);

@@ -202,7 +202,8 @@ class SbGdnArgs(ctypes.Structure):
                 ("conv_state_in", _P), ("conv_state_out", _P), ("state_in", _P), ("state_out", _P),
                 ("pending", SbGdnTape), ("step", SbGdnTape), ("hidden", _P), ("pending_rows_dev", _P),
                 ("rows", _U), ("pending_rows", _U), ("key_heads", _U), ("value_heads", _U), ("qkvz_stride", _U),
-                ("ab_stride", _U), ("hidden_stride", _U), ("tiled", _U)]
+                ("ab_stride", _U), ("hidden_stride", _U), ("tiled", _U),
+                ("gate_weight", _P), ("gate_input", _P), ("gate_k", _U), ("gate_input_stride", _U)]
 
 
 class SbSampleArgs(ctypes.Structure):

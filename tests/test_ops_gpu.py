@@ -178,7 +178,9 @@ def test_attention_long_context_32k(kernel):
     assert cos > 0.9995 and np.abs(got - want64).max() < 0.02
 
 
-def gdn_case(lib, l, o, *, key_heads, value_heads, rows, pending_rows, tiled, seed):
+def gdn_case(lib, l, o, *, key_heads, value_heads, rows, pending_rows, tiled, seed, fused_gates=0):
+    """fused_gates = k > 0: b and a are projections of a bf16 input [16, k] by fp32 rows [2 * value_heads, k]; the
+    kernel computes them itself (gate_weight / gate_input) and the oracle gets what sb_linear_f32 gives for them."""
     rng = np.random.default_rng(seed)
     D = 128
     KW, VW = key_heads * D, value_heads * D
@@ -187,6 +189,16 @@ def gdn_case(lib, l, o, *, key_heads, value_heads, rows, pending_rows, tiled, se
     qkvz = bf16_randn(rng, (16, stride), 1.0)
     b = bf16_randn(rng, (16, value_heads), 1.0)
     a = bf16_randn(rng, (16, value_heads), 1.0)
+    gate = None
+    if fused_gates:
+        gk = fused_gates
+        gw = (rng.standard_normal((2 * value_heads, gk)) / np.sqrt(gk)).astype(np.float32)
+        gx = bf16_randn(rng, (16, gk), 1.0)
+        gate = dict(w=lib.DeviceBuffer.from_numpy(gw), x=lib.DeviceBuffer.from_numpy(gx), k=gk)
+        gd = lib.DeviceBuffer(16 * 2 * value_heads * 2)
+        lib.check(l.sb_linear_f32(None, gate["w"].ptr, gate["x"].ptr, 16, 2 * value_heads, gk, gk, gd.ptr, 2 * value_heads, 0, None))
+        gates = gd.to_numpy(np.uint16, (16, 2 * value_heads))
+        b, a = np.ascontiguousarray(gates[:, :value_heads]), np.ascontiguousarray(gates[:, value_heads:])
     conv_w = bf16_randn(rng, (C, 4), 0.4)
     a_scale = (-np.exp(rng.uniform(-3, 0.5, value_heads))).astype(np.float32)
     dt_bias = bf16_randn(rng, (value_heads,), 0.5)
@@ -215,6 +227,9 @@ def gdn_case(lib, l, o, *, key_heads, value_heads, rows, pending_rows, tiled, se
     ga = lib.SbGdnArgs(d["qkvz"].ptr, d["b"].ptr, d["a"].ptr, d["conv_w"].ptr, d["a_scale"].ptr, d["dt_bias"].ptr,
                        d["norm_w"].ptr, d["cs_in"].ptr, dcs.ptr, d["state"].ptr, dst.ptr, dtape(dp), dtape(ds), dh.ptr, None,
                        rows, pending_rows, key_heads, value_heads, stride, value_heads, VW, int(tiled))
+    if gate:
+        ga.b = ga.a = None
+        ga.gate_weight, ga.gate_input, ga.gate_k, ga.gate_input_stride = gate["w"].ptr, gate["x"].ptr, gate["k"], gate["k"]
     lib.check(l.sb_gdn_verify(None, ctypes.byref(ga)))
     lib.stream_sync()
     assert lib.device_status() == 0
@@ -245,6 +260,21 @@ def test_gdn_verify_within_reference_gates(cfg):
     g, w = ol.bf2f(got["hidden"][:rows]).astype(np.float64), ol.bf2f(want["hidden"][:rows]).astype(np.float64)
     bad = np.abs(g - w) > 3 * ulp_bf16(w) + 2e-3 * np.abs(w).mean()
     assert bad.mean() <= 0.01
+
+
+def test_gdn_fused_gate_projection_equals_separate_projection():
+    """The kernel's own alpha / beta projection gives the bits of sb_linear_f32 followed by the plain kernel."""
+    lib, l, o = _setup()
+    cfg = dict(key_heads=4, value_heads=12, rows=16, pending_rows=5, tiled=True, seed=21)
+    fused, want, rows = gdn_case(lib, l, o, fused_gates=5120, **cfg)
+    assert np.array_equal(fused["beta"][:rows], want["beta"][:rows]) or \
+        (np.abs(ol.bf2f(fused["beta"][:rows]).astype(np.float64) - ol.bf2f(want["beta"][:rows])) <= 3 * ulp_bf16(ol.bf2f(want["beta"][:rows]))).all()
+    assert np.allclose(fused["decay"][:rows], want["decay"][:rows], rtol=1e-5)
+    assert np.abs(fused["state"] - want["state"]).max() <= 1e-4 * np.abs(want["state"]).max()
+    # and odd shapes: 5 rows, k = 1024
+    fused2, want2, rows2 = gdn_case(lib, l, o, key_heads=2, value_heads=6, rows=5, pending_rows=0, tiled=False, seed=22, fused_gates=1024)
+    assert np.allclose(fused2["decay"][:rows2], want2["decay"][:rows2], rtol=1e-5)
+    assert np.abs(fused2["state"] - want2["state"]).max() <= 1e-4 * np.abs(want2["state"]).max()
 
 
 def test_gdn_fold_then_next_step_is_consistent():
