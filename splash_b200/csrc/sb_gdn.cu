@@ -43,12 +43,12 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-__global__ void __launch_bounds__(kGdnThreads) gdn_kernel(const GdnParams p) {
+__global__ void __launch_bounds__(kGdnThreads, 2) gdn_kernel(const GdnParams p) {
   const SbGdnArgs &a = p.a;
   __shared__ float q_s[kGdnRows][kD], k_s[kGdnRows][kD], pk_s[kGdnRows][kD];
   __shared__ float v_s[kGdnRows][kGdnVd], pv_s[kGdnRows][kGdnVd], o_s[kGdnRows][kGdnVd];
   __shared__ float beta_s[kGdnRows], decay_s[kGdnRows], pbeta_s[kGdnRows], pdecay_s[kGdnRows];
-  __shared__ float gate_s[2][kGdnRows];  // the head's b and a per row when the kernel projects them itself
+  __shared__ float gate_s[kDotGroups][kGdnRows][2];  // group partial sums of the head's b and a per row (fused gate projection)
   __shared__ __align__(16) uint16_t in_s[kGdnRows + 3][2 * kD + kGdnVd];
   __shared__ uint2 w_s[2 * kD + kGdnVd];
   __shared__ uint32_t s_last;
@@ -73,19 +73,21 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_kernel(const GdnParams p) {
     const float4 s4 = *reinterpret_cast<const float4 *>(a.state_in + sbase + size_t(r) * kD);
     S[r][0] = s4.x, S[r][1] = s4.y, S[r][2] = s4.z, S[r][3] = s4.w;
   }
-  // Fused gate projection: warp w takes rows 2w, 2w + 1 and both gate rows of this head, four dot products at
-  // once over the layer's normalised input (the order of sb_linear_f32, so the bits agree with the unfused way).
+  // Fused gate projection: warp w computes group w's partial sums of all 16 rows x {b, a} over the layer's
+  // normalised input; the rows' threads add the 8 groups in order below (the order of sb_linear_f32, so the bits
+  // agree with the unfused way). All of a round's loads are in flight together.
   if (a.gate_weight && rows > 0) {
-    const uint32_t r0 = min(2 * warp, rows ? rows - 1 : 0), r1 = min(2 * warp + 1, rows ? rows - 1 : 0);
+    static_assert(kGdnThreads / 32 == kDotGroups, "one warp per group of the dot product");
     const float *const wrow[2] = {a.gate_weight + size_t(h) * a.gate_k, a.gate_weight + size_t(VH + h) * a.gate_k};
     const uint16_t *gx = static_cast<const uint16_t *>(a.gate_input);
-    const uint16_t *const xrow[2] = {gx + size_t(r0) * a.gate_input_stride, gx + size_t(r1) * a.gate_input_stride};
-    float d[2][2];
-    warp_dots_f32_bf16<2, 2>(wrow, xrow, a.gate_k, lane, d);
-    if (lane == 0) {
-      gate_s[0][2 * warp] = round_bf16(d[0][0]), gate_s[1][2 * warp] = round_bf16(d[0][1]);
-      gate_s[0][2 * warp + 1] = round_bf16(d[1][0]), gate_s[1][2 * warp + 1] = round_bf16(d[1][1]);
-    }
+    const uint16_t *xrow[kGdnRows];
+#pragma unroll
+    for (int r = 0; r < kGdnRows; ++r) xrow[r] = gx + size_t(min(uint32_t(r), rows - 1)) * a.gate_input_stride;
+    float d[kGdnRows][2];
+    warp_dot_group_f32_bf16<2, kGdnRows>(wrow, xrow, a.gate_k, lane, warp, d);
+    if (lane == 0)
+#pragma unroll
+      for (int r = 0; r < kGdnRows; ++r) gate_s[warp][r][0] = d[r][0], gate_s[warp][r][1] = d[r][1];
   }
   // Conv inputs of this CTA's channels (q and k of the key head, 32 value dimensions) for history rows
   // -3..-1 and the block's rows, staged with 16-byte loads: in_s[3 + row][local channel]. History row i
@@ -139,8 +141,16 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_kernel(const GdnParams p) {
     pdecay_s[tid] = a.pending.decay[size_t(tid) * VH + h];
   }
   if (tid < rows) {
-    const float bb = a.gate_weight ? gate_s[0][tid] : bf16_bits_to_float(static_cast<const uint16_t *>(a.b)[size_t(tid) * a.ab_stride + h]);
-    const float aa = a.gate_weight ? gate_s[1][tid] : bf16_bits_to_float(static_cast<const uint16_t *>(a.a)[size_t(tid) * a.ab_stride + h]);
+    float bb, aa;
+    if (a.gate_weight) {
+      bb = gate_s[0][tid][0], aa = gate_s[0][tid][1];
+#pragma unroll
+      for (int g = 1; g < kDotGroups; ++g) bb += gate_s[g][tid][0], aa += gate_s[g][tid][1];
+      bb = round_bf16(bb), aa = round_bf16(aa);
+    } else {
+      bb = bf16_bits_to_float(static_cast<const uint16_t *>(a.b)[size_t(tid) * a.ab_stride + h]);
+      aa = bf16_bits_to_float(static_cast<const uint16_t *>(a.a)[size_t(tid) * a.ab_stride + h]);
+    }
     const float be = round_bf16(sigmoid_f(bb));
     const float x = round_bf16(__fadd_rn(aa, bf16_bits_to_float(static_cast<const uint16_t *>(a.dt_bias)[h])));
     const float sp = round_bf16(fmaxf(x, 0.0f) + log2f(1.0f + exp2f(-1.44269504089f * fabsf(x))) * 0.69314718056f);

@@ -107,11 +107,7 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const float *w, const u
   // Lane-strided groups of 8 inputs, then a butterfly over the lanes.
   float acc = 0.0f;
   if (!norm_w) {
-    const float *const wrow[1] = {wr};
-    const uint16_t *const xrow[1] = {xr};
-    float d[1][1];
-    warp_dots_f32_bf16<1, 1>(wrow, xrow, k, lane, d);
-    acc = d[0][0];
+    acc = warp_dot_f32_bf16(wr, xr, k, lane);
   } else {
 #pragma unroll 5
   for (uint32_t c = 8 * lane; c < k; c += 256) {
