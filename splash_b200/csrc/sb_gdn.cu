@@ -65,13 +65,17 @@ __global__ void __launch_bounds__(kGdnThreads, 2) gdn_kernel(const GdnParams p) 
   const uint16_t *pin = static_cast<const uint16_t *>(a.pending.inputs);
   const bool qk_writer = h % per_key == 0 && vs == 0;
 
-  // The state rows of this warp, requested first so their latency hides behind the prologue.
-  float S[4][4];
-  const size_t sbase = (size_t(h) * kD + vd0 + 4 * (tid >> 5)) * kD + 4 * (tid & 31);
+  // The state of this warp's 4 value dimensions, requested first so the latency hides behind the prologue:
+  // lane l holds row 4 warp + l / 8, key columns 32 c + 4 (l % 8) .. + 3 for c = 0..3 (the 8 lanes of a row read 128
+  // contiguous bytes at a time, from global and from shared memory), so a dot product over the 128 key columns
+  // is 16 multiply-adds in the lane and three butterfly rounds over its 8-lane group.
+  float S[16];
+  const uint32_t srow = 4 * warp + (lane >> 3), scol = 4 * (lane & 7);
+  const size_t sbase = (size_t(h) * kD + vd0 + srow) * kD + scol;
 #pragma unroll
-  for (int r = 0; r < 4; ++r) {
-    const float4 s4 = *reinterpret_cast<const float4 *>(a.state_in + sbase + size_t(r) * kD);
-    S[r][0] = s4.x, S[r][1] = s4.y, S[r][2] = s4.z, S[r][3] = s4.w;
+  for (int c = 0; c < 4; ++c) {
+    const float4 s4 = *reinterpret_cast<const float4 *>(a.state_in + sbase + 32 * c);
+    S[4 * c] = s4.x, S[4 * c + 1] = s4.y, S[4 * c + 2] = s4.z, S[4 * c + 3] = s4.w;
   }
   // Fused gate projection: warp w computes group w's partial sums of all 16 rows x {b, a} over the layer's
   // normalised input; the rows' threads add the 8 groups in order below (the order of sb_linear_f32, so the bits
@@ -121,11 +125,13 @@ __global__ void __launch_bounds__(kGdnThreads, 2) gdn_kernel(const GdnParams p) 
   };
 
   // (2) conv outputs: q, k of the key head (16 x 128 each) and this CTA's 32 value dimensions.
+#pragma unroll 2
   for (uint32_t i = tid; i < rows * kD; i += kGdnThreads) {
     const uint32_t r = i / kD, d = i % kD;
     q_s[r][d] = conv(r, d);
     k_s[r][d] = conv(r, kD + d);
   }
+#pragma unroll 2
   for (uint32_t i = tid; i < rows * kGdnVd; i += kGdnThreads) {
     const uint32_t r = i / kGdnVd, d = i % kGdnVd;
     v_s[r][d] = conv(r, 2 * kD + d);
@@ -197,57 +203,53 @@ __global__ void __launch_bounds__(kGdnThreads, 2) gdn_kernel(const GdnParams p) 
         static_cast<uint16_t *>(a.step.k)[size_t(i / kD) * KW + kh * kD + i % kD] = float_to_bf16_bits(k_s[i / kD][i % kD]);
   }
 
-  // (3) + (4): warp w owns value dimensions vd0 + 4w .. + 3; lane holds key columns 4 lane .. + 3.
+  // (3) + (4): one delta-rule step on the lane's 16 state values (runtime/metal/kernels/common/gdn_primitives.h:63-97):
+  // S *= decay; mem = S k; delta = (v - mem) beta; S += delta k^T; out = S q.
+  auto group_sum = [&](float v) {
+    v += __shfl_xor_sync(0xffffffffu, v, 1);
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    return v;
+  };
   auto advance = [&](const float *key, const float *val, float d, float b, const float *query, float *out) {
-    const float4 k4 = *reinterpret_cast<const float4 *>(key + 4 * lane);
-    const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
-    float mem[4];
+    float kk[16];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      float m = 0.0f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        S[r][i] *= d;
-        m = fmaf(S[r][i], kk[i], m);
-      }
-      mem[r] = m;
+    for (int c = 0; c < 4; ++c) {
+      const float4 k4 = *reinterpret_cast<const float4 *>(key + scol + 32 * c);
+      kk[4 * c] = k4.x, kk[4 * c + 1] = k4.y, kk[4 * c + 2] = k4.z, kk[4 * c + 3] = k4.w;
     }
+    float part[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-    for (int o = 16; o; o >>= 1)
-#pragma unroll
-      for (int r = 0; r < 4; ++r) mem[r] += __shfl_xor_sync(0xffffffffu, mem[r], o);
-    float res[4];
-    float qq[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < 16; ++i) {
+      S[i] *= d;
+      part[i & 3] = fmaf(S[i], kk[i], part[i & 3]);
+    }
+    const float mem = group_sum((part[0] + part[1]) + (part[2] + part[3]));
+    const float delta = (val[srow] - mem) * b;
     if (query) {
-      const float4 q4 = *reinterpret_cast<const float4 *>(query + 4 * lane);
-      qq[0] = q4.x, qq[1] = q4.y, qq[2] = q4.z, qq[3] = q4.w;
-    }
+      float qq[16];
 #pragma unroll
-    for (int r = 0; r < 4; ++r) {
-      const float delta = (val[4 * warp + r] - mem[r]) * b;
-      float acc = 0.0f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        S[r][i] = fmaf(kk[i], delta, S[r][i]);
-        acc = fmaf(S[r][i], qq[i], acc);
+      for (int c = 0; c < 4; ++c) {
+        const float4 q4 = *reinterpret_cast<const float4 *>(query + scol + 32 * c);
+        qq[4 * c] = q4.x, qq[4 * c + 1] = q4.y, qq[4 * c + 2] = q4.z, qq[4 * c + 3] = q4.w;
       }
-      res[r] = acc;
-    }
-    if (query) {
+      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-      for (int o = 16; o; o >>= 1)
-#pragma unroll
-        for (int r = 0; r < 4; ++r) res[r] += __shfl_xor_sync(0xffffffffu, res[r], o);
-      if (lane == 0) {
-#pragma unroll
-        for (int r = 0; r < 4; ++r) out[4 * warp + r] = res[r];
+      for (int i = 0; i < 16; ++i) {
+        S[i] = fmaf(kk[i], delta, S[i]);
+        acc[i & 3] = fmaf(S[i], qq[i], acc[i & 3]);
       }
+      const float res = group_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
+      if ((lane & 7) == 0) out[srow] = res;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) S[i] = fmaf(kk[i], delta, S[i]);
     }
   };
   for (uint32_t t = 0; t < pending; ++t) advance(pk_s[t], pv_s[t], pdecay_s[t], pbeta_s[t], nullptr, nullptr);
 #pragma unroll
-  for (int r = 0; r < 4; ++r)
-    *reinterpret_cast<float4 *>(a.state_out + sbase + size_t(r) * kD) = make_float4(S[r][0], S[r][1], S[r][2], S[r][3]);
+  for (int c = 0; c < 4; ++c)
+    *reinterpret_cast<float4 *>(a.state_out + sbase + 32 * c) = make_float4(S[4 * c], S[4 * c + 1], S[4 * c + 2], S[4 * c + 3]);
   for (uint32_t t = 0; t < rows; ++t) advance(k_s[t], v_s[t], decay_s[t], beta_s[t], q_s[t], o_s[t]);
   __syncthreads();
   // recurrent outputs (bf16) of this CTA's value dimensions -> scratch
