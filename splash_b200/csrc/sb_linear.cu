@@ -49,9 +49,7 @@
 namespace sb {
 
 constexpr int kTokens = 16;         // rows of X one launch multiplies
-constexpr int kRG = 2, kKG = 6, kMT = 2;  // row groups x k groups of consumer warps; m-tiles per warp
-constexpr int kConsumerWarps = kRG * kKG; // 12: three per scheduler hide the operand expansion's latencies
-constexpr int kThreads = 32 * (kConsumerWarps + 3);  // + producer warp + two epilogue warps
+constexpr int kRG = 2, kMT = 2;          // row groups of consumer warps; m-tiles per warp
 constexpr int kTileRows = kRG * kMT * 16; // 64
 constexpr int kStageSb = 4;               // super-blocks per ring stage
 constexpr int kMaxStages = 8;
@@ -82,10 +80,11 @@ struct LinearParams {
 };
 
 template <int FMT> struct WFmt;
-// kSbBytes: bytes of 256 weights; kPieceSb: super-blocks per TMA column piece of a stage.
-template <> struct WFmt<SB_FMT_Q4K> { static constexpr uint32_t kSbBytes = 144, kPieceSb = 1; static constexpr bool kPairLayout = true; };
-template <> struct WFmt<SB_FMT_Q6K> { static constexpr uint32_t kSbBytes = 210, kPieceSb = 4; static constexpr bool kPairLayout = false; };
-template <> struct WFmt<SB_FMT_Q80> { static constexpr uint32_t kSbBytes = 272, kPieceSb = 2; static constexpr bool kPairLayout = false; };
+// kSbBytes: bytes of 256 weights; kPieceSb: super-blocks per TMA column piece of a stage; kKG: k-group warps per
+// row group (consumer warps = kRG * kKG: Q4_K gains from three per scheduler, Q6_K runs best with two).
+template <> struct WFmt<SB_FMT_Q4K> { static constexpr uint32_t kSbBytes = 144, kPieceSb = 1; static constexpr bool kPairLayout = true; static constexpr int kKG = 6; };
+template <> struct WFmt<SB_FMT_Q6K> { static constexpr uint32_t kSbBytes = 210, kPieceSb = 4; static constexpr bool kPairLayout = false; static constexpr int kKG = 4; };
+template <> struct WFmt<SB_FMT_Q80> { static constexpr uint32_t kSbBytes = 272, kPieceSb = 2; static constexpr bool kPairLayout = false; static constexpr int kKG = 4; };
 
 __device__ __forceinline__ void slice_range(uint32_t nsb, uint32_t slices, uint32_t s, uint32_t &b0, uint32_t &b1) {
   b0 = s * nsb / slices;
@@ -527,7 +526,8 @@ __device__ __forceinline__ void multiply_super_block(const uint8_t *wbase, const
 // Barriers in shared memory: full[s] / empty[s] per ring stage, xfull (activations landed),
 // red_full / red_empty (the tile's partial sums handed to the epilogue warp).
 template <int FMT>
-__global__ void __launch_bounds__(kThreads, 1) linear_kernel(const LinearParams p, const __grid_constant__ LinearMaps maps) {
+__global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 3), 1) linear_kernel(const LinearParams p, const __grid_constant__ LinearMaps maps) {
+  constexpr int kKG = WFmt<FMT>::kKG, kConsumerWarps = kRG * kKG;  // + producer warp + two epilogue warps
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
   uint64_t *empty = full + kMaxStages;
@@ -863,7 +863,8 @@ static int make_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t epilogue,
   const uint32_t slice_max = (p.nsb + p.slices - 1) / p.slices;
   p.x_off = 256;
   p.red_off = p.x_off + slice_max * kPrepSbBytes;
-  p.ring_off = (p.red_off + kConsumerWarps * 32 * kRedPitch * 4 + 127) & ~127u;
+  const uint32_t consumer_warps = kRG * (format == SB_FMT_Q4K ? WFmt<SB_FMT_Q4K>::kKG : format == SB_FMT_Q6K ? WFmt<SB_FMT_Q6K>::kKG : WFmt<SB_FMT_Q80>::kKG);
+  p.ring_off = (p.red_off + consumer_warps * 32 * kRedPitch * 4 + 127) & ~127u;
   const uint32_t budget = 227 * 1024;
   SB_REQUIRE(p.ring_off + 2 * p.stage_bytes <= budget, "sb_linear: shared memory plan does not fit (k = %u)", k);
   p.stages = std::min(uint32_t(kMaxStages), (budget - p.ring_off) / p.stage_bytes);
@@ -1047,7 +1048,7 @@ extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
     }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(plan.ctas);
-  cfg.blockDim = dim3(kThreads);
+  cfg.blockDim = dim3(32 * (kRG * (a->format == SB_FMT_Q4K ? WFmt<SB_FMT_Q4K>::kKG : a->format == SB_FMT_Q6K ? WFmt<SB_FMT_Q6K>::kKG : WFmt<SB_FMT_Q80>::kKG) + 3));
   cfg.dynamicSmemBytes = plan.smem_bytes;
   cfg.stream = as_stream(stream);
   cudaLaunchAttribute attr[1];
