@@ -32,6 +32,7 @@
 //             (runtime/metal/kernels/common/split_reduce.h:24-55), then applies the epilogue
 //             (runtime/metal/kernels/common/gguf_tile.h:8-14, gguf_linear.metal:38)
 #include <algorithm>
+#include <cstdlib>
 
 #include <cuda.h>
 
@@ -50,6 +51,7 @@ namespace sb {
 
 constexpr int kTokens = 16;         // rows of X one launch multiplies
 constexpr int kRG = 2, kMT = 2;          // row groups of consumer warps; m-tiles per warp
+constexpr int kEpiWarps = 3;             // tiles of a CTA go to the epilogue warps in turn; a tile's finish takes longer than its sums
 constexpr int kTileRows = kRG * kMT * 16; // 64
 constexpr int kStageSb = 4;               // super-blocks per ring stage
 constexpr int kMaxStages = 8;
@@ -526,15 +528,15 @@ __device__ __forceinline__ void multiply_super_block(const uint8_t *wbase, const
 // Barriers in shared memory: full[s] / empty[s] per ring stage, xfull (activations landed),
 // red_full / red_empty (the tile's partial sums handed to the epilogue warp).
 template <int FMT>
-__global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 3), 1) linear_kernel(const LinearParams p, const __grid_constant__ LinearMaps maps) {
-  constexpr int kKG = WFmt<FMT>::kKG, kConsumerWarps = kRG * kKG;  // + producer warp + two epilogue warps
+__global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1) linear_kernel(const LinearParams p, const __grid_constant__ LinearMaps maps) {
+  constexpr int kKG = WFmt<FMT>::kKG, kConsumerWarps = kRG * kKG;  // + producer warp + the epilogue warps
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *full = reinterpret_cast<uint64_t *>(smem);
   uint64_t *empty = full + kMaxStages;
   uint64_t *xfull = empty + kMaxStages;
-  uint64_t *red_full = xfull + 1;   // [2], one per epilogue warp
-  uint64_t *red_empty = xfull + 3;  // [2]
-  float *scale_back = reinterpret_cast<float *>(smem + 192);  // 16 floats, copied from the prepared header
+  uint64_t *red_full = xfull + 1;               // [kEpiWarps], one per epilogue warp
+  uint64_t *red_empty = red_full + kEpiWarps;   // [kEpiWarps]
+  float *scale_back = reinterpret_cast<float *>(smem + 256);  // 16 floats, copied from the prepared header
   constexpr uint32_t kSb = WFmt<FMT>::kSbBytes;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t slice = blockIdx.x % p.slices;
@@ -550,7 +552,7 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 3), 1) linear_ker
       mbar_init(&empty[s], kConsumerWarps);
     }
     mbar_init(xfull, 1);
-    for (int e = 0; e < 2; ++e) {
+    for (int e = 0; e < kEpiWarps; ++e) {
       mbar_init(&red_full[e], kConsumerWarps);
       mbar_init(&red_empty[e], 1);
     }
@@ -623,9 +625,9 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 3), 1) linear_ker
     const float sback = scale_back[tok];
     uint32_t done = 0;
     for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++done) {
-      if ((done & 1) != ew || (p.debug & 8)) continue;
+      if (done % kEpiWarps != ew || (p.debug & 8)) continue;
       const uint32_t tile = item / p.slices;
-      if (!mbar_wait_backoff(&red_full[ew], (done >> 1) & 1)) { if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED); return; }
+      if (!mbar_wait_backoff(&red_full[ew], (done / kEpiWarps) & 1)) { if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED); return; }
       float v[32];
 #pragma unroll
       for (int r = 0; r < 32; ++r) {
@@ -648,26 +650,31 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 3), 1) linear_ker
 #pragma unroll
           for (int q = 0; q < 8; ++q) pp[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         }
-        __threadfence();
         __syncwarp();
         uint32_t arrived = 0;
-        if (lane == 0) arrived = atomicAdd(&p.counters[tile], 1u);
+        if (lane == 0) arrived = atom_add_acq_rel_gpu(&p.counters[tile], 1u);  // releases the warp's partials, acquires the others'
         arrived = __shfl_sync(0xffffffffu, arrived, 0);
+        __syncwarp();
         finish = arrived == p.slices - 1;
         if (finish) {
-          __threadfence();
           if (col_ok) {
 #pragma unroll
             for (int r = 0; r < 32; ++r) v[r] = 0.0f;
-            for (uint32_t sl = 0; sl < p.slices; ++sl) {
-              const float4 *pp = reinterpret_cast<const float4 *>(p.partials + (size_t(sl) * kTokens + tok) * pcols + pc0);
-              float4 q[8];
+            // Two slices' loads in flight at a time, added in slice order.
+            for (uint32_t sl = 0; sl < p.slices; sl += 2) {
+              const bool two = sl + 1 < p.slices;
+              const float4 *pa = reinterpret_cast<const float4 *>(p.partials + (size_t(sl) * kTokens + tok) * pcols + pc0);
+              const float4 *pb = reinterpret_cast<const float4 *>(p.partials + (size_t(two ? sl + 1 : sl) * kTokens + tok) * pcols + pc0);
+              float4 qa[8], qb[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) q[i] = __ldcg(pp + i);
+              for (int i = 0; i < 8; ++i) qa[i] = __ldcg(pa + i);
 #pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                v[4 * i] += q[i].x, v[4 * i + 1] += q[i].y, v[4 * i + 2] += q[i].z, v[4 * i + 3] += q[i].w;
-              }
+              for (int i = 0; i < 8; ++i) qb[i] = __ldcg(pb + i);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[4 * i] += qa[i].x, v[4 * i + 1] += qa[i].y, v[4 * i + 2] += qa[i].z, v[4 * i + 3] += qa[i].w;
+              if (two)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[4 * i] += qb[i].x, v[4 * i + 1] += qb[i].y, v[4 * i + 2] += qb[i].z, v[4 * i + 3] += qb[i].w;
             }
           }
           if (lane == 0) p.counters[tile] = 0;
@@ -800,7 +807,7 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 3), 1) linear_ker
     }
     if (p.debug & 8) continue;
     // Hand the tile's sums to the epilogue warp once it has read the previous tile's.
-    if (done > 0 && !mbar_wait(&red_empty[(done - 1) & 1], ((done - 1) >> 1) & 1)) {
+    if (done > 0 && !mbar_wait(&red_empty[(done - 1) % kEpiWarps], ((done - 1) / kEpiWarps) & 1)) {
       if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
       return;
     }
@@ -815,7 +822,7 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 3), 1) linear_ker
         mine[(mt * 16 + g + 8) * kRedPitch + h * 8 + 2 * t + 1] = y[mt][h][3];
       }
     __syncwarp();
-    if (lane == 0) mbar_arrive(&red_full[done & 1]);
+    if (lane == 0) mbar_arrive(&red_full[done % kEpiWarps]);
   }
 }
 
@@ -823,7 +830,8 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 3), 1) linear_ker
 static uint32_t pick_slices(uint32_t nsb, uint32_t sb_bytes) {
   // Activations of a slice stay resident: at most kMaxSliceSb super-blocks, fewer where a format's
   // wider stages need the room.
-  const uint32_t cap = sb_bytes > 250 ? 6 : sb_bytes > 160 ? 8 : kMaxSliceSb;
+  uint32_t cap = sb_bytes > 250 ? 6 : sb_bytes > 160 ? 8 : kMaxSliceSb;
+  if (const char *e = getenv("SB_EXPERIMENT_SLICE_CAP")) cap = std::min<uint32_t>(cap, uint32_t(atoi(e)));
   const uint32_t s = (nsb + cap - 1) / cap;
   return s < 1 ? 1 : s;
 }
@@ -861,7 +869,7 @@ static int make_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t epilogue,
   SB_REQUIRE(p.box_bytes % 128 == 0 && p.pitch <= 1024, "sb_linear: unsupported stage geometry (k = %u)", k);
   p.stage_bytes = p.pieces * p.tensors * p.period * p.box_bytes;
   const uint32_t slice_max = (p.nsb + p.slices - 1) / p.slices;
-  p.x_off = 256;
+  p.x_off = 384;  // barriers 0..231, scale_back 256..319
   p.red_off = p.x_off + slice_max * kPrepSbBytes;
   const uint32_t consumer_warps = kRG * (format == SB_FMT_Q4K ? WFmt<SB_FMT_Q4K>::kKG : format == SB_FMT_Q6K ? WFmt<SB_FMT_Q6K>::kKG : WFmt<SB_FMT_Q80>::kKG);
   p.ring_off = (p.red_off + consumer_warps * 32 * kRedPitch * 4 + 127) & ~127u;
@@ -1048,7 +1056,7 @@ extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
     }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(plan.ctas);
-  cfg.blockDim = dim3(32 * (kRG * (a->format == SB_FMT_Q4K ? WFmt<SB_FMT_Q4K>::kKG : a->format == SB_FMT_Q6K ? WFmt<SB_FMT_Q6K>::kKG : WFmt<SB_FMT_Q80>::kKG) + 3));
+  cfg.blockDim = dim3(32 * (kRG * (a->format == SB_FMT_Q4K ? WFmt<SB_FMT_Q4K>::kKG : a->format == SB_FMT_Q6K ? WFmt<SB_FMT_Q6K>::kKG : WFmt<SB_FMT_Q80>::kKG) + 1 + kEpiWarps));
   cfg.dynamicSmemBytes = plan.smem_bytes;
   cfg.stream = as_stream(stream);
   cudaLaunchAttribute attr[1];

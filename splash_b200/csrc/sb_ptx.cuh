@@ -114,6 +114,14 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
   return p;
 }
 
+// Arrival counter of a cross-CTA exchange: one atomic that releases this thread's (and, after a __syncwarp, its
+// warp's) earlier global writes and acquires the other arrivers' at GPU scope, in place of fence + atomic + fence.
+__device__ __forceinline__ uint32_t atom_add_acq_rel_gpu(uint32_t *p, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.acq_rel.gpu.global.add.u32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return old;
+}
+
 // Programmatic dependent launch: wait for the producing grid's memory, and let the dependent
 // grid start launching. Both are no-ops when the launch carries no such dependency.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
