@@ -56,7 +56,10 @@ constexpr int kTileRows = kRG * kMT * 16; // 64
 constexpr int kStageSb = 4;               // super-blocks per ring stage
 constexpr int kMaxStages = 8;
 constexpr int kMaxSliceSb = 10;           // super-blocks of activations a CTA keeps resident (80 KiB)
-constexpr int kRedPitch = 17;
+// A consumer warp's tile sums in shared memory: [token 16][row 32] floats with a token pitch of 36 (the writes of a
+// warp's 8 x 4 lanes hit distinct banks, a lane's 32 rows read as 8 x 16 bytes) and 16 floats of padding per warp so
+// the two row groups' readers do not share banks.
+constexpr int kRedTokPitch = 36, kRedWarpFloats = 16 * kRedTokPitch + 16;
 constexpr uint32_t kXsbBytes = kTokens * 256 * 2;  // fp16 activations of one super-block
 constexpr uint32_t kSxSbBytes = 512;               // hi/lo sub-block sums of one super-block
 
@@ -630,12 +633,18 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
       if (!mbar_wait_backoff(&red_full[ew], (done / kEpiWarps) & 1)) { if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED); return; }
       float v[32];
 #pragma unroll
-      for (int r = 0; r < 32; ++r) {
-        float s = 0.0f;
+      for (int r = 0; r < 32; ++r) v[r] = 0.0f;
 #pragma unroll
-        for (int k = 0; k < kKG; ++k) s += red[((half * kKG + k) * 32 + r) * kRedPitch + tok];
-        v[r] = s * sback;
+      for (int k = 0; k < kKG; ++k) {  // the k-group warps' sums in order
+        const float4 *src = reinterpret_cast<const float4 *>(red + (half * kKG + k) * kRedWarpFloats + tok * kRedTokPitch);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 s4 = src[q];
+          v[4 * q] += s4.x, v[4 * q + 1] += s4.y, v[4 * q + 2] += s4.z, v[4 * q + 3] += s4.w;
+        }
       }
+#pragma unroll
+      for (int r = 0; r < 32; ++r) v[r] *= sback;
       __syncwarp();
       if (lane == 0) mbar_arrive(&red_empty[ew]);
       // First column of the lane's 32 values in the partials; gate/up tiles hold 32 gate rows then the
@@ -811,15 +820,15 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
       if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
       return;
     }
-    float *mine = red + warp * (32 * kRedPitch);
+    float *mine = red + warp * kRedWarpFloats;
 #pragma unroll
     for (int mt = 0; mt < kMT; ++mt)
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        mine[(mt * 16 + g) * kRedPitch + h * 8 + 2 * t] = y[mt][h][0];
-        mine[(mt * 16 + g) * kRedPitch + h * 8 + 2 * t + 1] = y[mt][h][1];
-        mine[(mt * 16 + g + 8) * kRedPitch + h * 8 + 2 * t] = y[mt][h][2];
-        mine[(mt * 16 + g + 8) * kRedPitch + h * 8 + 2 * t + 1] = y[mt][h][3];
+        mine[(h * 8 + 2 * t) * kRedTokPitch + mt * 16 + g] = y[mt][h][0];
+        mine[(h * 8 + 2 * t + 1) * kRedTokPitch + mt * 16 + g] = y[mt][h][1];
+        mine[(h * 8 + 2 * t) * kRedTokPitch + mt * 16 + g + 8] = y[mt][h][2];
+        mine[(h * 8 + 2 * t + 1) * kRedTokPitch + mt * 16 + g + 8] = y[mt][h][3];
       }
     __syncwarp();
     if (lane == 0) mbar_arrive(&red_full[done % kEpiWarps]);
@@ -872,7 +881,7 @@ static int make_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t epilogue,
   p.x_off = 384;  // barriers 0..231, scale_back 256..319
   p.red_off = p.x_off + slice_max * kPrepSbBytes;
   const uint32_t consumer_warps = kRG * (format == SB_FMT_Q4K ? WFmt<SB_FMT_Q4K>::kKG : format == SB_FMT_Q6K ? WFmt<SB_FMT_Q6K>::kKG : WFmt<SB_FMT_Q80>::kKG);
-  p.ring_off = (p.red_off + consumer_warps * 32 * kRedPitch * 4 + 127) & ~127u;
+  p.ring_off = (p.red_off + consumer_warps * kRedWarpFloats * 4 + 127) & ~127u;
   const uint32_t budget = 227 * 1024;
   SB_REQUIRE(p.ring_off + 2 * p.stage_bytes <= budget, "sb_linear: shared memory plan does not fit (k = %u)", k);
   p.stages = std::min(uint32_t(kMaxStages), (budget - p.ring_off) / p.stage_bytes);

@@ -176,7 +176,8 @@ __device__ __forceinline__ uint16_t float_to_bf16_bits(float f) {
 __device__ __forceinline__ float round_bf16(float f) { return __bfloat162float(__float2bfloat16_rn(f)); }
 
 // e^-x as exp2(-x log2 e): the form every activation of the verify step uses.
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + exp2f(-1.44269504089f * x)); }
-__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + exp2f(-1.44269504089f * x)); }
+// The quotient is the approximate one (reciprocal and multiply, 2 ulp): every result is rounded to bf16 next.
+__device__ __forceinline__ float silu_f(float x) { return __fdividef(x, 1.0f + exp2f(-1.44269504089f * x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return __fdividef(1.0f, 1.0f + exp2f(-1.44269504089f * x)); }
 
 }  // namespace sb
