@@ -23,6 +23,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstring>
 #include <vector>
 
 SO_API int so_dequant(uint32_t f, const uint8_t *native, uint32_t rows, uint32_t K, float *out);
@@ -266,21 +267,126 @@ static uint32_t argmax_row(const float *l, uint32_t vocab) {
 // row draws from the residual (w_child removed) with its own uniform: target = u_row * Z', the first id
 // whose running sum exceeds it; the last row always draws from the full
 // distribution. uniforms: [0,16) row draws, 16 + 4 * row child tests.
-SO_API void so_sample_verify(const float *logits, uint32_t logit_stride, uint32_t vocab, uint32_t rows,
-                             const uint32_t *input_tokens, float temperature, const float *uniforms,
-                             uint32_t *selected, double *decision_margin) {
+// Order-preserving key of a selectable logit (larger logit, larger key; -0 counts as +0).
+static uint32_t logit_key(float x) {
+  if (x == 0.0f) x = 0.0f;
+  uint32_t u;
+  memcpy(&u, &x, 4);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// The end of a row's distribution in the order (logit descending, id ascending): a token stays iff its key is
+// above cut_key, or equal to it with an id up to cut_id (sampling.metal:604-668 distribution_end):
+//   min_p  tokens weighing at least min_p of the heaviest: logits >= max + T * log(min_p);
+//   top_k  then the k first of those;
+//   top_p  then the shortest prefix whose mass exceeds top_p of the mass the first two cuts keep; where several
+//          tokens tie at the last logit, 1 + floor((nucleus - mass above) / weight) of them stay, lowest ids first.
+// Masses are sums of exp((l - max) / T) over shards of 256 ids in id order, shards in order; a cut logit is found
+// bit by bit from the top of the key (32 measurements), which is what the CUDA kernel does too.
+struct RowCut {
+  uint32_t key = 0, id = kSentinel;  // keep everything selectable
+};
+static bool cut_keeps(const RowCut &c, float x, uint32_t v) {
+  if (std::isnan(x) || x == -INFINITY) return false;
+  const uint32_t k = logit_key(x);
+  return k > c.key || (k == c.key && v <= c.id);
+}
+struct Measure {
+  uint32_t count;
+  float mass;
+};
+// Count and mass of the tokens the cut keeps whose key is at least `key` (strictly above it when `strict`).
+static Measure measure(const float *l, uint32_t vocab, const RowCut &c, uint32_t key, bool strict, float mx, float inv_t) {
+  Measure m{0, 0.0f};
+  const uint32_t shards = (vocab + kShard - 1) / kShard;
+  for (uint32_t s = 0; s < shards; ++s) {
+    float sum = 0.0f;
+    for (uint32_t v = s * kShard; v < std::min(vocab, (s + 1) * kShard); ++v) {
+      if (!cut_keeps(c, l[v], v)) continue;
+      const uint32_t k = logit_key(l[v]);
+      if (strict ? k > key : k >= key) {
+        ++m.count;
+        sum += expf((l[v] - mx) * inv_t);
+      }
+    }
+    m.mass += sum;
+  }
+  return m;
+}
+// The id of the n-th (1-based) kept token whose key equals `key`, in id order.
+static uint32_t nth_tie(const float *l, uint32_t vocab, const RowCut &c, uint32_t key, uint32_t n) {
+  for (uint32_t v = 0; v < vocab; ++v)
+    if (cut_keeps(c, l[v], v) && logit_key(l[v]) == key && --n == 0) return v;
+  return kSentinel;
+}
+static float key_logit(uint32_t key) {
+  const uint32_t u = (key & 0x80000000u) ? (key & 0x7fffffffu) : ~key;
+  float x;
+  memcpy(&x, &u, 4);
+  return x;
+}
+static RowCut distribution_end(const float *l, uint32_t vocab, float mx, float temperature, float min_p, uint32_t top_k, float top_p) {
+  const float inv_t = 1.0f / temperature;
+  RowCut cut;
+  Measure kept = measure(l, vocab, cut, 0, false, mx, inv_t);
+  if (min_p > 0.0f) {
+    const float t = std::min(mx + temperature * logf(min_p), mx);
+    const Measure m = measure(l, vocab, cut, logit_key(t), false, mx, inv_t);
+    if (m.count < kept.count) cut.key = logit_key(t), cut.id = kSentinel, kept = m;
+  }
+  if (top_k > 0 && top_k < kept.count) {
+    uint32_t key = 0;  // the largest key with at least top_k kept tokens at or above it
+    for (int bit = 31; bit >= 0; --bit) {
+      const uint32_t cand = key | (1u << bit);
+      if (measure(l, vocab, cut, cand, false, mx, inv_t).count >= top_k) key = cand;
+    }
+    const Measure above = measure(l, vocab, cut, key, true, mx, inv_t);
+    const uint32_t need = top_k - above.count;
+    const uint32_t id = nth_tie(l, vocab, cut, key, need);
+    cut.key = key, cut.id = id;
+    kept.count = top_k;
+    kept.mass = above.mass + float(need) * expf((key_logit(key) - mx) * inv_t);
+  }
+  if (top_p > 0.0f && top_p < 1.0f) {
+    const float nucleus = top_p * kept.mass;
+    uint32_t key = 0;  // the largest key whose kept tokens at or above it weigh more than the nucleus
+    bool found = false;
+    for (int bit = 31; bit >= 0; --bit) {
+      const uint32_t cand = key | (1u << bit);
+      if (measure(l, vocab, cut, cand, false, mx, inv_t).mass > nucleus) key = cand, found = true;
+    }
+    if (!found) found = measure(l, vocab, cut, 0, false, mx, inv_t).mass > nucleus;
+    if (found) {  // rounding may leave the nucleus unreached: then everything kept so far stays
+      const Measure above = measure(l, vocab, cut, key, true, mx, inv_t);
+      const Measure at = measure(l, vocab, cut, key, false, mx, inv_t);
+      const uint32_t ties = at.count - above.count;
+      if (ties > 0) {
+        const float w = expf((key_logit(key) - mx) * inv_t);
+        const float q = std::min(std::max((nucleus - above.mass) / w, 0.0f), float(ties - 1));
+        const uint32_t keep = 1u + uint32_t(q);
+        cut.id = nth_tie(l, vocab, cut, key, keep);
+        cut.key = key;
+      }
+    }
+  }
+  return cut;
+}
+
+SO_API void so_sample_verify_filtered(const float *logits, uint32_t logit_stride, uint32_t vocab, uint32_t rows,
+                                      const uint32_t *input_tokens, float temperature, float min_p, uint32_t top_k, float top_p,
+                                      const float *uniforms, uint32_t *selected, double *decision_margin, uint32_t *cut_out) {
   for (uint32_t r = 0; r < rows; ++r) {
     const float *l = logits + size_t(r) * logit_stride;
     if (decision_margin) decision_margin[r] = INFINITY;
     const uint32_t top = argmax_row(l, vocab);
+    if (cut_out) cut_out[2 * r] = 0, cut_out[2 * r + 1] = kSentinel;
     if (temperature == 0.0f || top == kSentinel) { selected[r] = top; continue; }
     const float mx = l[top], inv_t = 1.0f / temperature;
+    const RowCut cut = distribution_end(l, vocab, mx, temperature, min_p, top_k, top_p);
+    if (cut_out) cut_out[2 * r] = cut.key, cut_out[2 * r + 1] = cut.id;
     const uint32_t shards = (vocab + kShard - 1) / kShard;
     std::vector<float> w(vocab), shard(shards, 0.0f);
-    for (uint32_t v = 0; v < vocab; ++v) {
-      const float x = l[v];
-      w[v] = (std::isnan(x) || x == -INFINITY) ? 0.0f : expf((x - mx) * inv_t);
-    }
+    for (uint32_t v = 0; v < vocab; ++v) w[v] = cut_keeps(cut, l[v], v) ? expf((l[v] - mx) * inv_t) : 0.0f;
     const bool has_child = r + 1 < rows;
     const uint32_t child = has_child ? input_tokens[r + 1] : kSentinel;
     auto mass = [&](bool drop_child, std::vector<float> &sh) {
@@ -323,6 +429,13 @@ SO_API void so_sample_verify(const float *logits, uint32_t logit_stride, uint32_
         if (w[v] > 0.0f && !(drop && v == child)) { pick = v; break; }
     selected[r] = pick;
   }
+}
+
+SO_API void so_sample_verify(const float *logits, uint32_t logit_stride, uint32_t vocab, uint32_t rows,
+                             const uint32_t *input_tokens, float temperature, const float *uniforms,
+                             uint32_t *selected, double *decision_margin) {
+  so_sample_verify_filtered(logits, logit_stride, vocab, rows, input_tokens, temperature, 0.0f, 0, 1.0f, uniforms, selected,
+                            decision_margin, nullptr);
 }
 
 // Acceptance of one lane (sampling.metal:2044-2083): from row 0 follow the child whose parent is

@@ -617,7 +617,7 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
   float *red = reinterpret_cast<float *>(smem + p.red_off);
 
   if (warp > kConsumerWarps) {
-    // ---- epilogue warps: tile i of this CTA belongs to epilogue warp i % 2. Each adds the k-group
+    // ---- epilogue warps: tile i of this CTA belongs to epilogue warp i % kEpiWarps. Each adds the k-group
     // warps' sums in order, exchanges split-K partials and stores. Lane l owns token l / 2 and tile
     // rows 32 (l % 2) .. + 31, so every global access of a lane is 64 or 128 contiguous bytes. ----
     const uint32_t ew = warp - kConsumerWarps - 1;
@@ -636,28 +636,34 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
       for (int r = 0; r < 32; ++r) v[r] = 0.0f;
 #pragma unroll
       for (int k = 0; k < kKG; ++k) {  // the k-group warps' sums in order
-        const float4 *src = reinterpret_cast<const float4 *>(red + (half * kKG + k) * kRedWarpFloats + tok * kRedTokPitch);
+        // Plain tiles: rows 32 half .. + 31 of the tile (row group `half`). Gate/up tiles: columns 16 half .. + 15,
+        // their gate sums (row group 0) in v[0..15] and their up sums (row group 1) in v[16..31].
+        const float4 *s0 = reinterpret_cast<const float4 *>(red + ((gate_up ? 0 : half) * kKG + k) * kRedWarpFloats + tok * kRedTokPitch + (gate_up ? 16 * half : 0));
+        const float4 *s1 = gate_up ? reinterpret_cast<const float4 *>(red + (kKG + k) * kRedWarpFloats + tok * kRedTokPitch + 16 * half) : s0 + 4;
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const float4 s4 = src[q];
-          v[4 * q] += s4.x, v[4 * q + 1] += s4.y, v[4 * q + 2] += s4.z, v[4 * q + 3] += s4.w;
+        for (int q = 0; q < 4; ++q) {
+          const float4 a4 = s0[q], b4 = s1[q];
+          v[4 * q] += a4.x, v[4 * q + 1] += a4.y, v[4 * q + 2] += a4.z, v[4 * q + 3] += a4.w;
+          v[16 + 4 * q] += b4.x, v[16 + 4 * q + 1] += b4.y, v[16 + 4 * q + 2] += b4.z, v[16 + 4 * q + 3] += b4.w;
         }
       }
 #pragma unroll
       for (int r = 0; r < 32; ++r) v[r] *= sback;
       __syncwarp();
       if (lane == 0) mbar_arrive(&red_empty[ew]);
-      // First column of the lane's 32 values in the partials; gate/up tiles hold 32 gate rows then the
-      // 32 up rows of the same 32 columns.
+      // The lane's 32 values as two runs of 16 in the partials: columns c0 + 16 half (+ 16) of a plain tile, or
+      // the gate run and, n columns on, the up run of columns c0 + 16 half of a gate/up tile.
       const uint32_t c0 = gate_up ? tile * 32 : tile * kTileRows + 32 * half;
-      const uint32_t pc0 = gate_up ? c0 + half * p.n : c0;
+      const uint32_t run0 = gate_up ? c0 + 16 * half : c0, run1 = gate_up ? run0 + p.n : c0 + 16;
       const bool col_ok = c0 < p.n;  // n is a multiple of 32: a 32-column run is inside or outside
+      auto part = [&](uint32_t sl, uint32_t run) {
+        return reinterpret_cast<float4 *>(p.partials + (size_t(sl) * kTokens + tok) * pcols + (run ? run1 : run0));
+      };
       bool finish = true;
       if (p.slices > 1) {
         if (col_ok) {
-          float4 *pp = reinterpret_cast<float4 *>(p.partials + (size_t(slice) * kTokens + tok) * pcols + pc0);
 #pragma unroll
-          for (int q = 0; q < 8; ++q) pp[q] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          for (int q = 0; q < 8; ++q) part(slice, q >> 2)[q & 3] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
         }
         __syncwarp();
         uint32_t arrived = 0;
@@ -666,19 +672,25 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
         __syncwarp();
         finish = arrived == p.slices - 1;
         if (finish) {
-          if (col_ok) {
+          if (col_ok && p.slices == 2) {
+            // Two slices: a + b is b + a, so this warp keeps its own sums in registers (its stores may still be
+            // on their way) and adds the other slice's from L2.
+            float4 q[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) q[i] = __ldcg(part(slice ^ 1, i >> 2) + (i & 3));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[4 * i] += q[i].x, v[4 * i + 1] += q[i].y, v[4 * i + 2] += q[i].z, v[4 * i + 3] += q[i].w;
+          } else if (col_ok) {
 #pragma unroll
             for (int r = 0; r < 32; ++r) v[r] = 0.0f;
             // Two slices' loads in flight at a time, added in slice order.
             for (uint32_t sl = 0; sl < p.slices; sl += 2) {
               const bool two = sl + 1 < p.slices;
-              const float4 *pa = reinterpret_cast<const float4 *>(p.partials + (size_t(sl) * kTokens + tok) * pcols + pc0);
-              const float4 *pb = reinterpret_cast<const float4 *>(p.partials + (size_t(two ? sl + 1 : sl) * kTokens + tok) * pcols + pc0);
               float4 qa[8], qb[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) qa[i] = __ldcg(pa + i);
+              for (int i = 0; i < 8; ++i) qa[i] = __ldcg(part(sl, i >> 2) + (i & 3));
 #pragma unroll
-              for (int i = 0; i < 8; ++i) qb[i] = __ldcg(pb + i);
+              for (int i = 0; i < 8; ++i) qb[i] = __ldcg(part(two ? sl + 1 : sl, i >> 2) + (i & 3));
 #pragma unroll
               for (int i = 0; i < 8; ++i) v[4 * i] += qa[i].x, v[4 * i + 1] += qa[i].y, v[4 * i + 2] += qa[i].z, v[4 * i + 3] += qa[i].w;
               if (two)
@@ -691,17 +703,8 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
       }
       if (!finish) continue;
       if (gate_up) {
-        // Lane (tok, 0) holds the gate sums, lane (tok, 1) the up sums of the same 32 columns: swap
-        // halves so each lane finishes 16 columns.
-        float gsum[16], usum[16];
-#pragma unroll
-        for (int r = 0; r < 16; ++r) {
-          const float mine_lo = v[r], mine_hi = v[16 + r];
-          const float send = half ? mine_lo : mine_hi;       // what the partner needs
-          const float got = __shfl_xor_sync(0xffffffffu, send, 1);
-          gsum[r] = half ? got : mine_lo;                      // gate of column 16*half + r
-          usum[r] = half ? mine_hi : got;                      // up of column 16*half + r
-        }
+        // v[0..15] are the gate sums and v[16..31] the up sums of columns c0 + 16 half .. + 15.
+        const float *gsum = v, *usum = v + 16;
         if (col_ok && tok < p.rows) {
           uint32_t pk[8];
 #pragma unroll
