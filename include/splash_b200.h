@@ -300,7 +300,8 @@ SB_API int sb_gdn_verify_static(void *stream, const SbGdnArgs *args);
 /* ---- selection and acceptance ---- */
 
 /* Selection of every row of one lane's chain. temperature 0: greedy (largest finite logit, ties to the
- * lowest id, none -> 0xFFFFFFFF). Else weights exp((l - max) / T), shards of 256 ids summed in id order and
+ * lowest id, none -> 0xFFFFFFFF). Else weights exp((l - max) / T) of the tokens before the distribution's end (min_p,
+ * top_k, top_p below), shards of 256 ids summed in id order and
  * the shards in order; the drafted child (input token of row r + 1) is kept iff u_child * Z < w_child, else
  * the row draws from the residual with its own uniform; the last row draws from the full distribution.
  * uniforms (device fp32): [0,16) row draws, 16 + 4 * row child tests (runtime/metal/abi/Sampling.h:12-31).
@@ -314,6 +315,14 @@ typedef struct SbSampleArgs {
   float *workspace;          /* device fp32, rows * (2 * shards + 8) */
   uint32_t rows, vocab, logit_stride;
   float temperature;
+  /* The end of the distribution a sampled row draws from (runtime/metal/kernels/decode/sampling.metal:604-668), in the
+   * order logit descending, id ascending: tokens weighing at least min_p of the heaviest (0: off), then the top_k
+   * first of those (0 or >= vocab: off), then the shortest prefix whose mass exceeds top_p of what those two keep
+   * (0 or >= 1: off; ties at the last logit keep their lowest ids). Vocabulary up to 262144 when any is on. */
+  float min_p;
+  uint32_t top_k;
+  float top_p;
+  uint32_t *cut_out;         /* optional device u32 [rows, 2]: the end as {order key of the last logit, last id} */
 } SbSampleArgs;
 SB_API uint64_t sb_sample_workspace_bytes(uint32_t rows, uint32_t vocab);
 SB_API int sb_sample_verify(void *stream, const SbSampleArgs *args);

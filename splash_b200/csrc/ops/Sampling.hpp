@@ -7,6 +7,10 @@ namespace splash::b200::ops {
 
 struct SamplingPolicy {
   float temperature = 0.0f;  // 0: greedy
+  // The end of a sampled row's distribution (runtime/ops/Sampling.hpp policy; sampling.metal:604-668): off when 0 / 0 / 1.
+  float minP = 0.0f;
+  uint32_t topK = 0;
+  float topP = 1.0f;
 };
 
 struct SamplingBuffers {
@@ -37,7 +41,7 @@ class Sampling {
     }
     SbSampleArgs a{b.logits.as<float>(), b.inputTokens.as<uint32_t>(), policy.temperature > 0.0f ? b.uniforms.as<float>() : nullptr,
                    b.selected.as<uint32_t>(), b.workspace ? b.workspace.as<float>() : nullptr, rows, vocabulary, b.logitStride,
-                   policy.temperature};
+                   policy.temperature, policy.minP, policy.topK, policy.topP, nullptr};
     check(sb_sample_verify(graph.stream, &a));
     ++graph.launches;
   }

@@ -253,7 +253,155 @@ constexpr int kSampleThreads = 1024;
 
 __device__ __forceinline__ bool selectable(float x) { return !(isnan(x) || x == -INFINITY); }
 
+// ---- the end of a row's distribution: min-p, then top-k, then the top-p nucleus (sampling.metal:604-668) ----
+// A token stays iff its key (order-preserving bits of its logit, -0 as +0) is above cut.key, or equal to it with an id
+// up to cut.id. Every search walks the 32 key bits from the top with one block-wide measurement per bit; masses are the
+// shard sums (256 ids in id order) added in shard order by one thread, as everywhere in this kernel.
+constexpr uint32_t kMaxFilterShards = 1024;  // vocabulary up to 262144 with filters
+struct RowCut {
+  uint32_t key, id;
+};
+__device__ __forceinline__ uint32_t logit_key(float x) {
+  if (x == 0.0f) x = 0.0f;
+  const uint32_t u = __float_as_uint(x);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float key_logit(uint32_t key) {
+  return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+}
+__device__ __forceinline__ bool cut_keeps(const RowCut c, float x, uint32_t v) {
+  if (!selectable(x)) return false;
+  const uint32_t k = logit_key(x);
+  return k > c.key || (k == c.key && v <= c.id);
+}
+struct FilterScratch {
+  float shard_mass[kMaxFilterShards];
+  uint32_t counts[kSampleThreads];
+  uint32_t warp_counts[32];
+  uint32_t count, pick_thread, pick_rank, id;
+  float mass;
+};
+// Count and mass of the kept tokens whose key is at least `key` (above it when `strict`); every thread gets both.
+__device__ void block_measure(const float *l, uint32_t vocab, RowCut cut, uint32_t key, bool strict, bool want_mass, float mx, float inv_t,
+                              FilterScratch &fs, uint32_t &count, float &mass) {
+  const uint32_t tid = threadIdx.x, shards = (vocab + kShard - 1) / kShard;
+  uint32_t mine = 0;
+  for (uint32_t s = tid; s < shards; s += kSampleThreads) {
+    float sum = 0.0f;
+    const uint32_t end = min(vocab, (s + 1) * kShard);
+    for (uint32_t v = s * kShard; v < end; ++v) {
+      const float x = l[v];
+      if (!cut_keeps(cut, x, v)) continue;
+      const uint32_t k = logit_key(x);
+      if (strict ? k > key : k >= key) {
+        ++mine;
+        if (want_mass) sum = __fadd_rn(sum, expf(__fmul_rn(__fsub_rn(x, mx), inv_t)));
+      }
+    }
+    fs.shard_mass[s] = sum;
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+  if ((tid & 31) == 0) fs.warp_counts[tid >> 5] = mine;
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t c = 0;
+    for (int w = 0; w < kSampleThreads / 32; ++w) c += fs.warp_counts[w];
+    float m = 0.0f;
+    if (want_mass)
+      for (uint32_t s = 0; s < shards; ++s) m = __fadd_rn(m, fs.shard_mass[s]);
+    fs.count = c, fs.mass = m;
+  }
+  __syncthreads();
+  count = fs.count, mass = fs.mass;
+  __syncthreads();
+}
+// The id of the n-th (1-based) kept token whose key equals `key`, in id order.
+__device__ uint32_t block_nth_tie(const float *l, uint32_t vocab, RowCut cut, uint32_t key, uint32_t n, FilterScratch &fs) {
+  const uint32_t tid = threadIdx.x, chunk = (vocab + kSampleThreads - 1) / kSampleThreads;
+  const uint32_t v0 = min(vocab, tid * chunk), v1 = min(vocab, v0 + chunk);
+  uint32_t mine = 0;
+  for (uint32_t v = v0; v < v1; ++v) mine += cut_keeps(cut, l[v], v) && logit_key(l[v]) == key;
+  fs.counts[tid] = mine;
+  if (tid == 0) fs.id = kSentinel;
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t before = 0, t = 0;
+    for (; t < kSampleThreads && before + fs.counts[t] < n; ++t) before += fs.counts[t];
+    fs.pick_thread = t, fs.pick_rank = n - before;
+  }
+  __syncthreads();
+  if (tid == fs.pick_thread) {
+    uint32_t rank = fs.pick_rank;
+    for (uint32_t v = v0; v < v1; ++v)
+      if (cut_keeps(cut, l[v], v) && logit_key(l[v]) == key && --rank == 0) {
+        fs.id = v;
+        break;
+      }
+  }
+  __syncthreads();
+  const uint32_t id = fs.id;
+  __syncthreads();
+  return id;
+}
+__device__ RowCut distribution_end(const float *l, uint32_t vocab, float mx, float temperature, float inv_t, float min_p, uint32_t top_k,
+                                   float top_p, FilterScratch &fs) {
+  RowCut cut{0u, kSentinel};
+  uint32_t kept_count, count;
+  float kept_mass, mass;
+  block_measure(l, vocab, cut, 0u, false, true, mx, inv_t, fs, kept_count, kept_mass);
+  if (min_p > 0.0f) {
+    const float t = fminf(__fadd_rn(mx, __fmul_rn(temperature, logf(min_p))), mx);
+    block_measure(l, vocab, cut, logit_key(t), false, true, mx, inv_t, fs, count, mass);
+    if (count < kept_count) cut = RowCut{logit_key(t), kSentinel}, kept_count = count, kept_mass = mass;
+  }
+  if (top_k > 0 && top_k < kept_count) {
+    uint32_t key = 0;  // the largest key with at least top_k kept tokens at or above it
+    for (int bit = 31; bit >= 0; --bit) {
+      const uint32_t cand = key | (1u << bit);
+      block_measure(l, vocab, cut, cand, false, false, mx, inv_t, fs, count, mass);
+      if (count >= top_k) key = cand;
+    }
+    block_measure(l, vocab, cut, key, true, true, mx, inv_t, fs, count, mass);
+    const uint32_t need = top_k - count;
+    const uint32_t id = block_nth_tie(l, vocab, cut, key, need, fs);
+    cut = RowCut{key, id};
+    kept_count = top_k;
+    kept_mass = __fadd_rn(mass, __fmul_rn(float(need), expf(__fmul_rn(__fsub_rn(key_logit(key), mx), inv_t))));
+  }
+  if (top_p > 0.0f && top_p < 1.0f) {
+    const float nucleus = __fmul_rn(top_p, kept_mass);
+    uint32_t key = 0;  // the largest key whose kept tokens at or above it weigh more than the nucleus
+    bool found = false;
+    for (int bit = 31; bit >= 0; --bit) {
+      const uint32_t cand = key | (1u << bit);
+      block_measure(l, vocab, cut, cand, false, true, mx, inv_t, fs, count, mass);
+      if (mass > nucleus) key = cand, found = true;
+    }
+    if (!found) {
+      block_measure(l, vocab, cut, 0u, false, true, mx, inv_t, fs, count, mass);
+      found = mass > nucleus;
+    }
+    if (found) {  // rounding may leave the nucleus unreached: then everything kept so far stays
+      uint32_t above_count, at_count;
+      float above_mass, at_mass;
+      block_measure(l, vocab, cut, key, true, true, mx, inv_t, fs, above_count, above_mass);
+      block_measure(l, vocab, cut, key, false, false, mx, inv_t, fs, at_count, at_mass);
+      const uint32_t ties = at_count - above_count;
+      if (ties > 0) {
+        const float w = expf(__fmul_rn(__fsub_rn(key_logit(key), mx), inv_t));
+        const float q = fminf(fmaxf(__fdiv_rn(__fsub_rn(nucleus, above_mass), w), 0.0f), float(ties - 1));
+        const uint32_t keep = 1u + uint32_t(q);
+        const uint32_t id = block_nth_tie(l, vocab, cut, key, keep, fs);
+        cut = RowCut{key, id};
+      }
+    }
+  }
+  return cut;
+}
+
 __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SbSampleArgs a) {
+  __shared__ FilterScratch fs;
   __shared__ float best_v[32];
   __shared__ uint32_t best_i[32];
   __shared__ float s_max;
@@ -301,9 +449,13 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SbSampleAr
   float *shard = a.workspace + size_t(r) * (2 * shards + 8), *shard2 = shard + shards;
   const bool has_child = r + 1 < a.rows;
   const uint32_t child = has_child ? a.input_tokens[r + 1] : kSentinel;
+  RowCut cut{0u, kSentinel};
+  if (a.min_p > 0.0f || (a.top_k > 0 && a.top_k < a.vocab) || (a.top_p > 0.0f && a.top_p < 1.0f))
+    cut = distribution_end(l, a.vocab, mx, a.temperature, inv_t, a.min_p, a.top_k, a.top_p, fs);
+  if (a.cut_out && tid == 0) a.cut_out[2 * r] = cut.key, a.cut_out[2 * r + 1] = cut.id;
   auto weight = [&](uint32_t v) {
     const float x = l[v];
-    return selectable(x) ? expf(__fmul_rn(__fsub_rn(x, mx), inv_t)) : 0.0f;
+    return cut_keeps(cut, x, v) ? expf(__fmul_rn(__fsub_rn(x, mx), inv_t)) : 0.0f;
   };
   for (uint32_t s = tid; s < shards; s += kSampleThreads) {
     float sum = 0.0f, sum2 = 0.0f;
@@ -496,6 +648,9 @@ int sb_sample_verify(void *stream, const SbSampleArgs *a) {
   SB_REQUIRE(a->rows >= 1 && a->rows <= 16 && a->vocab >= 1 && a->logit_stride >= a->vocab, "sb_sample_verify: rows %u outside 1..16 or bad vocabulary extent", a->rows);
   SB_REQUIRE(a->temperature >= 0.0f, "sb_sample_verify: negative temperature");
   SB_REQUIRE(a->temperature == 0.0f || (a->uniforms && a->workspace), "sb_sample_verify: a sampled policy needs uniforms and a workspace");
+  SB_REQUIRE(a->min_p >= 0.0f && a->min_p <= 1.0f && a->top_p >= 0.0f, "sb_sample_verify: min_p %g outside 0..1 or negative top_p", double(a->min_p));
+  const bool filtered = a->min_p > 0.0f || (a->top_k > 0 && a->top_k < a->vocab) || (a->top_p > 0.0f && a->top_p < 1.0f);
+  SB_REQUIRE(!filtered || a->vocab <= kMaxFilterShards * kShard, "sb_sample_verify: min-p / top-k / top-p support vocabularies up to %u", kMaxFilterShards * kShard);
   return launch(sample_kernel, dim3(a->rows), dim3(kSampleThreads), as_stream(stream), *a);
 }
 

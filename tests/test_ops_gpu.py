@@ -344,3 +344,36 @@ def test_stochastic_selection_with_supplied_uniforms():
     clear = margin > 1e-5
     assert clear.sum() >= rows - 2
     assert np.array_equal(got[clear], want[clear])
+
+
+@pytest.mark.parametrize("min_p,top_k,top_p", [(0.05, 0, 1.0), (0.0, 40, 1.0), (0.0, 0, 0.9), (0.02, 50, 0.8), (0.0, 1, 1.0)])
+def test_filtered_selection_matches_the_oracle(min_p, top_k, top_p):
+    """min-p, top-k and top-p ends of the distribution and the selections under them."""
+    lib, l, o = _setup()
+    rng = np.random.default_rng(12)
+    rows, vocab, T = 16, 32000, 0.7
+    logits = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
+    logits[3, 500:520] = logits[3].max()        # ties at the top
+    logits[5, ::5] = np.float32(-np.inf)
+    greedy = logits.argmax(axis=1).astype(np.uint32)
+    inputs = np.zeros(rows, np.uint32)
+    for r in range(1, rows):
+        inputs[r] = greedy[r - 1] if rng.random() < 0.7 else rng.integers(0, vocab)
+    uniforms = rng.random(80).astype(np.float32)
+    want, margin, wcut = np.zeros(rows, np.uint32), np.zeros(rows, np.float64), np.zeros((rows, 2), np.uint32)
+    o.so_sample_verify_filtered(P(logits), vocab, vocab, rows, P(inputs), T, min_p, top_k, top_p, P(uniforms), P(want), P(margin), P(wcut))
+    ld, idd, ud = (lib.DeviceBuffer.from_numpy(x) for x in (logits, inputs, uniforms))
+    sd, cd = lib.DeviceBuffer(rows * 4), lib.DeviceBuffer(rows * 8)
+    wd = lib.DeviceBuffer(int(l.sb_sample_workspace_bytes(rows, vocab)))
+    sa = lib.SbSampleArgs(ld.ptr, idd.ptr, ud.ptr, sd.ptr, wd.ptr, rows, vocab, vocab, T, min_p, top_k, top_p, cd.ptr)
+    lib.check(l.sb_sample_verify(None, ctypes.byref(sa)))
+    got, gcut = sd.to_numpy(np.uint32, (rows,)), cd.to_numpy(np.uint32, (rows, 2))
+    assert lib.device_status() == 0
+    # the ends agree except where a mass sits within rounding of its nucleus (the device's expf is not the host's)
+    same_cut = (gcut == wcut).all(axis=1)
+    assert same_cut.sum() >= rows - 1
+    clear = same_cut & (margin > 1e-5)
+    assert clear.sum() >= rows - 3
+    assert np.array_equal(got[clear], want[clear])
+    if top_k == 1:
+        assert np.array_equal(got, greedy)

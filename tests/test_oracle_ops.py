@@ -111,6 +111,50 @@ def test_rejection_rule_keeps_the_target_distribution():
     assert np.abs(counts / n - p).max() < 0.015
 
 
+def _kept_set_by_sorting(l, T, min_p, top_k, top_p):
+    """The distribution's end stated with a sort (order: logit descending, id ascending) and fp64 masses."""
+    order = np.lexsort((np.arange(l.size), -l.astype(np.float64)))
+    w = np.exp((l.astype(np.float64) - l.max()) / T)
+    keep = order
+    if min_p > 0:
+        keep = keep[l[keep] >= np.float32(l.max() + np.float32(T) * np.float32(np.log(np.float32(min_p))))]
+    if 0 < top_k < keep.size:
+        keep = keep[:top_k]
+    if 0 < top_p < 1:
+        c = np.cumsum(w[keep])
+        over = np.nonzero(c > top_p * c[-1])[0]
+        if over.size:
+            keep = keep[:over[0] + 1]
+    return set(int(v) for v in keep)
+
+
+@pytest.mark.parametrize("min_p,top_k,top_p", [(0.05, 0, 1.0), (0.0, 40, 1.0), (0.0, 0, 0.9), (0.02, 50, 0.8), (0.0, 3, 0.5)])
+def test_distribution_end_equals_a_sorted_statement(min_p, top_k, top_p):
+    o = ol.bind_ops(ol.load())
+    rng = np.random.default_rng(11)
+    rows, vocab, T = 4, 3000, 0.8
+    logits = (rng.standard_normal((rows, vocab)) * 2.5).astype(np.float32)
+    logits[1, 100:110] = logits[1].max()          # ties at the top, resolved by id
+    logits[2, ::7] = np.float32(-np.inf)          # unselectable tokens never stay
+    inputs = np.zeros(rows, np.uint32)
+    u = rng.random(80).astype(np.float32)
+    sel, cut = np.zeros(rows, np.uint32), np.zeros((rows, 2), np.uint32)
+    o.so_sample_verify_filtered(P(logits), vocab, vocab, rows, P(inputs), T, min_p, top_k, top_p, P(u), P(sel), None, P(cut))
+    for r in range(rows):
+        l = logits[r]
+        key = l.copy()
+        key[key == 0] = 0.0
+        bits = key.view(np.uint32).astype(np.uint64)
+        keys = np.where(bits & 0x80000000, (~bits) & 0xFFFFFFFF, bits | 0x80000000)
+        finite = np.isfinite(l) | (l == np.inf)
+        kept = {int(v) for v in np.nonzero(finite & ((keys > cut[r, 0]) | ((keys == cut[r, 0]) & (np.arange(vocab) <= cut[r, 1]))))[0]}
+        want = _kept_set_by_sorting(np.where(finite, l, -np.inf).astype(np.float32), T, min_p, top_k, top_p)
+        want = {v for v in want if finite[v]}
+        # fp32 shard sums against fp64 sums may move a nucleus by a token at most
+        assert len(kept ^ want) <= (1 if 0 < top_p < 1 else 0), (r, len(kept), len(want))
+        assert int(sel[r]) in kept
+
+
 @pytest.mark.parametrize("fmt", [0, 4, 6])
 def test_linear_port_within_projection_bound(fmt):
     o = ol.load()
