@@ -32,7 +32,6 @@
 //             (runtime/metal/kernels/common/split_reduce.h:24-55), then applies the epilogue
 //             (runtime/metal/kernels/common/gguf_tile.h:8-14, gguf_linear.metal:38)
 #include <algorithm>
-#include <cstdlib>
 
 #include <cuda.h>
 
@@ -842,8 +841,7 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
 static uint32_t pick_slices(uint32_t nsb, uint32_t sb_bytes) {
   // Activations of a slice stay resident: at most kMaxSliceSb super-blocks, fewer where a format's
   // wider stages need the room.
-  uint32_t cap = sb_bytes > 250 ? 6 : sb_bytes > 160 ? 8 : kMaxSliceSb;
-  if (const char *e = getenv("SB_EXPERIMENT_SLICE_CAP")) cap = std::min<uint32_t>(cap, uint32_t(atoi(e)));
+  const uint32_t cap = sb_bytes > 250 ? 6 : sb_bytes > 160 ? 8 : kMaxSliceSb;
   const uint32_t s = (nsb + cap - 1) / cap;
   return s < 1 ? 1 : s;
 }
