@@ -55,7 +55,10 @@ enum {
   SB_EPILOGUE_NONE = 0,
   SB_EPILOGUE_RESIDUAL = 1,     /* out = v + aux */
   SB_EPILOGUE_UP_WITH_GATE = 2, /* out = bf16(v) * silu(aux) */
-  SB_EPILOGUE_GATE_UP = 3       /* one pass over gate and up rows: bf16(bf16(up) * silu(bf16(gate))) */
+  SB_EPILOGUE_GATE_UP = 3,      /* one pass over gate and up rows: bf16(bf16(up) * silu(bf16(gate))) */
+  SB_EPILOGUE_PARTIALS = 4      /* no reduction: out is fp32 [slices of sb_linear_plan][16][out_stride] and receives every
+                                   k-slice's sums; sb_linear_prepare_sum adds them (and a residual) where the sum is
+                                   consumed, which takes the split-K exchange off the projection's tail */
 };
 
 /* ---- context, memory, streams, events (replaces MetalBackend's buffer and command API) ---- */
@@ -149,6 +152,13 @@ enum {
 SB_API uint64_t sb_linear_prepared_bytes(uint32_t k);
 SB_API int sb_linear_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride,
                              const void *norm_weight, uint32_t format, void *prepared_out, void *normed_out, uint32_t flags);
+/* The same over x = bf16(residual + sum of `slices` partial sums (fp32 [slices][16][partial_stride], as
+ * SB_EPILOGUE_PARTIALS writes them, added in slice order)): the residual epilogue of the projection that produced the
+ * partials, moved in front of the next projection's input conversion. sum_out (bf16 [rows, sum_stride]) receives x,
+ * the new hidden state. */
+SB_API int sb_linear_prepare_sum(void *stream, const float *partials, uint32_t slices, uint32_t partial_stride, const void *residual,
+                                 uint32_t residual_stride, void *sum_out, uint32_t sum_stride, uint32_t rows, uint32_t k,
+                                 const void *norm_weight, uint32_t format, void *prepared_out, void *normed_out, uint32_t flags);
 
 /* Scratch (split-K partials and arrival counters) the context keeps for sb_linear; sized by
  * sb_init for the largest projection of the supported shapes and reused serially within a stream,

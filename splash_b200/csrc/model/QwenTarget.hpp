@@ -68,6 +68,8 @@ class QwenTarget {
   ops::NormWeights outputNorm_;
   ops::QuantizedSegment output_;
   Buffer packed_, gates_, mixed_, queries_, act_, normed_, prepared_[2], pageTable_, sampleWorkspace_;
+  Buffer partials_;  // fp32 [kMaxPartialSlices][16][hidden]: k-slice sums of out_proj / down awaiting their consumer
+  static constexpr uint32_t kMaxPartialSlices = 16;
   uint32_t packedStride_ = 0;
   uint64_t weightBytes_ = 0;
 };
@@ -137,6 +139,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &c) : cfg_(c) {
   queries_ = Buffer::allocate(size_t(kVerifyRows) * c.q_heads * D * 2);
   act_ = Buffer::allocate(size_t(kVerifyRows) * c.intermediate * 2);
   normed_ = Buffer::allocate(size_t(kVerifyRows) * H * 2);
+  partials_ = Buffer::allocate(size_t(kMaxPartialSlices) * 16 * H * 4);
   const uint32_t widest = std::max(std::max(H, c.intermediate), std::max(gdn_.valueWidth(), c.q_heads * D));
   for (auto &p : prepared_) p = Buffer::allocate(ops::Linear::preparedBytes((widest + 255) / 256 * 256));
   for (auto &h : hidden) h = Buffer::allocate(size_t(kVerifyRows) * H * 2);
@@ -210,10 +213,34 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   if (c.rotary_pairs) RoPE::addTreeTables(graph, positions, invFreq, cosine, sine, rows, 1.0f, c.rotary_pairs);
   Embedding::add(graph, tokens, embedding_, hidden[0], rows, H);
   uint32_t cur = 0;
+  // out_proj and down leave their k-slices' sums unreduced (Epilogue::Partials); the conversion of the next
+  // projection's input adds them and the residual and writes the new hidden state, so no projection ends on a
+  // split-K exchange. `pending` = slices waiting in partials_ whose residual is hidden[cur] and whose sum goes to
+  // hidden[cur ^ 1].
+  uint32_t pending = 0;
+  auto convert = [&](const Buffer *norm, uint32_t format, const Buffer &scratch, const Buffer *normedOutput) {
+    if (!pending) return Linear::prepare(graph, hidden[cur], rows, H, H, norm, format, scratch, normedOutput);
+    PreparedInput in = Linear::prepareSum(graph, partials_, pending, H, hidden[cur], hidden[cur ^ 1], rows, H, H, norm, format, scratch, normedOutput);
+    cur ^= 1;
+    pending = 0;
+    return in;
+  };
+  auto project = [&](const QuantizedSegment &seg, uint32_t inputSize, const PreparedInput &in) {
+    Projection proj{H, inputSize, Destination::BFloat16, {seg}};
+    LinearPlan plan = Linear::plan(proj, rows, Epilogue::Partials);
+    if (plan.kernel.slices > kMaxPartialSlices) {  // a shape with more slices than the scratch holds reduces in the kernel
+      LinearBuffers b{Buffer(), hidden[cur ^ 1], hidden[cur], inputSize, H};
+      Linear::add(graph, b, proj, Linear::plan(proj, rows, Epilogue::Residual), in);
+      cur ^= 1;
+      return;
+    }
+    LinearBuffers b{Buffer(), partials_, Buffer(), inputSize, H};
+    Linear::add(graph, b, proj, plan, in);
+    pending = plan.kernel.slices;
+  };
   for (LayerWeights &w : layers_) {
     // mixer: h += mixer(norm(h))
-    PreparedInput in = Linear::prepare(graph, hidden[cur], rows, H, H, &w.attnNorm.buffer, w.inProj.format, prepared_[0],
-                                       w.attention ? nullptr : &normed_);
+    PreparedInput in = convert(&w.attnNorm.buffer, w.inProj.format, prepared_[0], w.attention ? nullptr : &normed_);
     Projection inProj{w.inProj.outputSize, H, Destination::BFloat16, {w.inProj}};
     LinearBuffers inB{Buffer(), packed_, Buffer(), H, packedStride_};
     Linear::add(graph, inB, inProj, Linear::plan(inProj, rows, Epilogue::None), in);
@@ -238,21 +265,15 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
       GDN::addDecode(graph, g, gdn_, rows);
     }
     PreparedInput mixedIn = Linear::prepare(graph, mixed_, rows, mixedWidth, mixedWidth, nullptr, w.outProj.format, prepared_[1]);
-    Projection outProj{H, mixedWidth, Destination::BFloat16, {w.outProj}};
-    LinearBuffers outB{Buffer(), hidden[cur ^ 1], hidden[cur], mixedWidth, H};
-    Linear::add(graph, outB, outProj, Linear::plan(outProj, rows, Epilogue::Residual), mixedIn);
-    cur ^= 1;
+    project(w.outProj, mixedWidth, mixedIn);
     // FFN: h += down(silu(gate(norm(h))) * up(norm(h)))
-    PreparedInput ffnIn = Linear::prepare(graph, hidden[cur], rows, H, H, &w.ffnNorm.buffer, w.ffnGate.format, prepared_[0]);
+    PreparedInput ffnIn = convert(&w.ffnNorm.buffer, w.ffnGate.format, prepared_[0], nullptr);
     Linear::addGateUp(graph, act_, c.intermediate, w.ffnGate, w.ffnUp, rows, ffnIn);
     PreparedInput actIn = Linear::prepare(graph, act_, rows, c.intermediate, c.intermediate, nullptr, w.ffnDown.format, prepared_[1]);
-    Projection down{H, c.intermediate, Destination::BFloat16, {w.ffnDown}};
-    LinearBuffers downB{Buffer(), hidden[cur ^ 1], hidden[cur], c.intermediate, H};
-    Linear::add(graph, downB, down, Linear::plan(down, rows, Epilogue::Residual), actIn);
-    cur ^= 1;
+    project(w.ffnDown, c.intermediate, actIn);
   }
   // logits of every row
-  PreparedInput headIn = Linear::prepare(graph, hidden[cur], rows, H, H, &outputNorm_.buffer, output_.format, prepared_[0]);
+  PreparedInput headIn = convert(&outputNorm_.buffer, output_.format, prepared_[0], nullptr);
   Projection head{c.vocab, H, Destination::Float32, {output_}};
   LinearBuffers headB{Buffer(), logits, Buffer(), H, c.vocab};
   Linear::add(graph, headB, head, Linear::plan(head, rows, Epilogue::None), headIn);

@@ -10,7 +10,7 @@
 namespace splash::b200::ops {
 
 enum class Epilogue { None = SB_EPILOGUE_NONE, Residual = SB_EPILOGUE_RESIDUAL, UpWithGate = SB_EPILOGUE_UP_WITH_GATE,
-                      GateUp = SB_EPILOGUE_GATE_UP };
+                      GateUp = SB_EPILOGUE_GATE_UP, Partials = SB_EPILOGUE_PARTIALS };
 enum class Destination { BFloat16, Float32 };
 
 // One tensor's rows: `outputSize` rows of `inputSize` weights in `format`, written at `columnOffset`.
@@ -74,11 +74,36 @@ class Linear {
     return {scratch, format == SB_FMT_Q4K ? uint32_t(SB_FMT_Q4K) : uint32_t(SB_FMT_Q6K), inputSize};
   }
 
+  // The same conversion over input = bf16(residual + the k-slices' partial sums a projection left with
+  // Epilogue::Partials): that projection's residual epilogue, done where its result is consumed. `sum` receives the
+  // input, i.e. the new hidden state.
+  static PreparedInput prepareSum(CommandGraph &graph, const Buffer &partials, uint32_t slices, uint32_t partialStride, const Buffer &residual,
+                                  const Buffer &sum, uint32_t rows, uint32_t inputSize, uint32_t inputStride, const Buffer *normWeight,
+                                  uint32_t format, const Buffer &scratch, const Buffer *normedOutput = nullptr) {
+    requireBytes(partials, size_t(slices) * 16 * partialStride * 4, "Linear::prepareSum partial sums");
+    requireBytes(residual, size_t(rows - 1) * inputStride * 2 + size_t(inputSize) * 2, "Linear::prepareSum residual");
+    requireBytes(sum, size_t(rows - 1) * inputStride * 2 + size_t(inputSize) * 2, "Linear::prepareSum sum");
+    requireBytes(scratch, preparedBytes(inputSize), "Linear::prepareSum scratch");
+    if (normWeight) requireBytes(*normWeight, size_t(inputSize) * 4, "Linear::prepareSum norm weight");
+    if (normedOutput) requireBytes(*normedOutput, size_t(rows) * inputSize * 2, "Linear::prepareSum normalised output");
+    check(sb_linear_prepare_sum(graph.stream, partials.as<float>(), slices, partialStride, residual.as(), inputStride, sum.as(), inputStride,
+                                rows, inputSize, normWeight ? normWeight->as() : nullptr, format, scratch.as(),
+                                normedOutput ? normedOutput->as() : nullptr, graph.pdl ? SB_LINEAR_PDL : 0));
+    ++graph.launches;
+    return {scratch, format == SB_FMT_Q4K ? uint32_t(SB_FMT_Q4K) : uint32_t(SB_FMT_Q6K), inputSize};
+  }
+
   // One projection over a prepared input; every segment writes its columns of the output.
   static void add(CommandGraph &graph, const LinearBuffers &b, const Projection &p, const LinearPlan &plan,
                   const PreparedInput &prepared) {
-    const uint32_t esize = p.destination == Destination::Float32 ? 4 : 2;
-    requireBytes(b.output, (size_t(plan.rows - 1) * b.outputStride + p.outputSize) * esize, "Linear::add output");
+    const uint32_t esize = p.destination == Destination::Float32 || plan.epilogue == Epilogue::Partials ? 4 : 2;
+    if (plan.epilogue == Epilogue::Partials) {
+      // Every k-slice's sums, fp32 [slices][16][outputStride]; Linear::prepareSum adds them where they are consumed.
+      if (p.segments.size() != 1) throw std::invalid_argument("Linear::add: partial sums of a single segment only");
+      requireBytes(b.output, size_t(plan.kernel.slices) * 16 * b.outputStride * 4, "Linear::add partial sums");
+    } else {
+      requireBytes(b.output, (size_t(plan.rows - 1) * b.outputStride + p.outputSize) * esize, "Linear::add output");
+    }
     if (plan.epilogue == Epilogue::Residual || plan.epilogue == Epilogue::UpWithGate)
       requireBytes(b.residual, (size_t(plan.rows - 1) * b.outputStride + p.outputSize) * 2, "Linear::add residual");
     if (prepared.inputSize != p.inputSize) throw std::invalid_argument("Linear::add: prepared input of another width");
@@ -95,7 +120,7 @@ class Linear {
       a.out = b.output.as<uint8_t>() + size_t(s.columnOffset) * esize;
       a.format = s.format, a.n = s.outputSize, a.k = s.inputSize, a.rows = plan.rows;
       a.aux_stride = a.aux ? b.outputStride : 0, a.out_stride = b.outputStride;
-      a.epilogue = uint32_t(plan.epilogue), a.out_f32 = p.destination == Destination::Float32;
+      a.epilogue = uint32_t(plan.epilogue), a.out_f32 = p.destination == Destination::Float32 || plan.epilogue == Epilogue::Partials;
       a.flags = graph.pdl ? SB_LINEAR_PDL : 0;
       check(sb_linear(graph.stream, &a));
       ++graph.launches;

@@ -122,6 +122,10 @@ struct PrepareParams {
   uint8_t *out;
   uint16_t *normed_out;  // optional bf16 [rows][k]: the (normalised) input as the product's fp32 side projections read it
   uint32_t rows, k, x_stride, pair_layout;  // layout: 0 range, 1 pair, 2 tensor-core tiles
+  // Optional: x = bf16(residual + the slices' partial sums), also written to sum_out (see sb_linear_prepare_sum).
+  const float *partials;
+  uint16_t *sum_out;
+  uint32_t partial_slices, partial_stride, sum_stride;
 };
 
 // Sum of `s` and maximum of `m` over the block, both returned to every thread. Fixed order: butterfly within
@@ -178,6 +182,21 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PreparePara
     for (int j = 0; j < 4; ++j) {
       v[i][2 * j] = bf16_bits_to_float(u[j] & 0xffffu);
       v[i][2 * j + 1] = bf16_bits_to_float(u[j] >> 16);
+    }
+    if (p.partials && live && c < chunks) {
+      // x = bf16(sum of the slices in order + residual): the projection's residual epilogue, done here.
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (uint32_t sl = 0; sl < p.partial_slices; ++sl) {
+        const float4 *pp = reinterpret_cast<const float4 *>(p.partials + (size_t(sl) * kTokens + tok) * p.partial_stride + 8 * c);
+        const float4 a4 = __ldcg(pp), b4 = __ldcg(pp + 1);
+        acc[0] += a4.x, acc[1] += a4.y, acc[2] += a4.z, acc[3] += a4.w, acc[4] += b4.x, acc[5] += b4.y, acc[6] += b4.z, acc[7] += b4.w;
+      }
+      uint32_t pk[4];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = round_bf16(acc[j] + v[i][j]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pk[j] = uint32_t(float_to_bf16_bits(v[i][2 * j])) | (uint32_t(float_to_bf16_bits(v[i][2 * j + 1])) << 16);
+      *reinterpret_cast<uint4 *>(p.sum_out + size_t(tok) * p.sum_stride + 8 * c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
     }
   }
   // One pass of block reductions gives both the sum of squares and the largest |x * w| (or |x| without a
@@ -658,6 +677,15 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
       auto part = [&](uint32_t sl, uint32_t run) {
         return reinterpret_cast<float4 *>(p.partials + (size_t(sl) * kTokens + tok) * pcols + (run ? run1 : run0));
       };
+      if (p.epilogue == SB_EPILOGUE_PARTIALS) {  // this slice's sums as they are; their consumer adds the slices
+        if (col_ok) {
+          float *dst = static_cast<float *>(p.out) + (size_t(slice) * kTokens + tok) * p.out_stride;
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            reinterpret_cast<float4 *>(dst + (q < 4 ? run0 : run1))[q & 3] = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        }
+        continue;
+      }
       bool finish = true;
       if (p.slices > 1) {
         if (col_ok) {
@@ -923,9 +951,11 @@ int encode_weight_map(CUtensorMap *map, uintptr_t base, uint32_t stride, uint32_
 }
 
 static int launch_prepare(cudaStream_t stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride,
-                          const void *norm_w, uint32_t layout, void *out, void *normed_out, bool pdl) {
+                          const void *norm_w, uint32_t layout, void *out, void *normed_out, bool pdl, const float *partials = nullptr,
+                          uint32_t slices = 0, uint32_t partial_stride = 0, void *sum_out = nullptr, uint32_t sum_stride = 0) {
   PrepareParams pp{static_cast<const uint16_t *>(x), static_cast<const float *>(norm_w), static_cast<uint8_t *>(out),
-                   static_cast<uint16_t *>(normed_out), rows, k, x_stride, layout};
+                   static_cast<uint16_t *>(normed_out), rows, k, x_stride, layout, partials, static_cast<uint16_t *>(sum_out), slices,
+                   partial_stride, sum_stride};
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(kTokens);
   cfg.blockDim = dim3(kPrepThreads);
@@ -980,19 +1010,40 @@ extern "C" int sb_linear_prepare(void *stream, const void *x, uint32_t rows, uin
                         (flags & SB_LINEAR_PDL) != 0);
 }
 
+extern "C" int sb_linear_prepare_sum(void *stream, const float *partials, uint32_t slices, uint32_t partial_stride, const void *residual,
+                                     uint32_t residual_stride, void *sum_out, uint32_t sum_stride, uint32_t rows, uint32_t k,
+                                     const void *norm_weight, uint32_t format, void *prepared_out, void *normed_out, uint32_t flags) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(partials && residual && sum_out && prepared_out, "sb_linear_prepare_sum: null pointer");
+  SB_REQUIRE(slices >= 1 && slices <= 64, "sb_linear_prepare_sum: %u slices outside 1..64", slices);
+  SB_REQUIRE(rows >= 1 && rows <= kTokens, "sb_linear_prepare_sum: rows = %u outside 1..%d", rows, kTokens);
+  SB_REQUIRE(k && k % 256 == 0 && k <= 8 * kPrepThreads * kPrepMaxChunks, "sb_linear_prepare_sum: k = %u is not a multiple of 256 up to %d",
+             k, 8 * kPrepThreads * kPrepMaxChunks);
+  SB_REQUIRE(partial_stride >= k && partial_stride % 4 == 0 && residual_stride >= k && residual_stride % 8 == 0 && sum_stride >= k && sum_stride % 8 == 0,
+             "sb_linear_prepare_sum: a stride is below k or misaligned");
+  SB_REQUIRE(format == SB_FMT_Q4K || format == SB_FMT_Q6K || format == SB_FMT_Q80, "sb_linear_prepare_sum: format %u", format);
+  SB_REQUIRE(((reinterpret_cast<uintptr_t>(partials) | reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(sum_out) |
+               reinterpret_cast<uintptr_t>(prepared_out) | reinterpret_cast<uintptr_t>(norm_weight) | reinterpret_cast<uintptr_t>(normed_out)) & 15) == 0,
+             "sb_linear_prepare_sum: pointers must be 16-byte aligned");
+  const uint32_t layout = format != SB_FMT_Q4K ? 0u : (flags & SB_LINEAR_TCGEN05) ? 2u : 1u;
+  return launch_prepare(as_stream(stream), residual, rows, k, residual_stride, norm_weight, layout, prepared_out, normed_out,
+                        (flags & SB_LINEAR_PDL) != 0, partials, slices, partial_stride, sum_out, sum_stride);
+}
+
 extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
   SB_NEED_DEVICE();
   SB_REQUIRE(a, "sb_linear: null arguments");
   SB_REQUIRE(a->weights && a->out && (a->x || a->prepared), "sb_linear: null weights, out, or neither x nor prepared");
   SB_REQUIRE(a->rows >= 1 && a->rows <= kTokens, "sb_linear: rows = %u outside 1..%d", a->rows, kTokens);
-  SB_REQUIRE(a->epilogue <= SB_EPILOGUE_GATE_UP, "sb_linear: unknown epilogue %u", a->epilogue);
+  SB_REQUIRE(a->epilogue <= SB_EPILOGUE_PARTIALS, "sb_linear: unknown epilogue %u", a->epilogue);
   SB_REQUIRE((a->epilogue == SB_EPILOGUE_GATE_UP) == (a->weights2 != nullptr),
              "sb_linear: weights2 is given exactly with SB_EPILOGUE_GATE_UP");
   SB_REQUIRE((a->epilogue == SB_EPILOGUE_RESIDUAL || a->epilogue == SB_EPILOGUE_UP_WITH_GATE) == (a->aux != nullptr),
              "sb_linear: aux is given exactly with the residual and up-with-gate epilogues");
   SB_REQUIRE(a->out_stride >= a->n && a->out_stride % 8 == 0, "sb_linear: out_stride %u < n or not a multiple of 8", a->out_stride);
   SB_REQUIRE(!a->aux || (a->aux_stride >= a->n && a->aux_stride % 8 == 0), "sb_linear: aux_stride %u < n or not a multiple of 8", a->aux_stride);
-  SB_REQUIRE(!(a->out_f32 && a->epilogue != SB_EPILOGUE_NONE), "sb_linear: an fp32 destination takes no epilogue");
+  SB_REQUIRE(!(a->out_f32 && a->epilogue != SB_EPILOGUE_NONE && a->epilogue != SB_EPILOGUE_PARTIALS), "sb_linear: an fp32 destination takes no epilogue");
+  SB_REQUIRE(a->epilogue != SB_EPILOGUE_PARTIALS || !(a->flags & SB_LINEAR_TCGEN05), "sb_linear: SB_EPILOGUE_PARTIALS is not offered by the tcgen05 kernel");
   SB_REQUIRE((reinterpret_cast<uintptr_t>(a->out) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->aux) & 15) == 0,
              "sb_linear: out and aux must be 16-byte aligned");
   SB_REQUIRE((reinterpret_cast<uintptr_t>(a->weights) & 1) == 0 && (reinterpret_cast<uintptr_t>(a->weights2) & 1) == 0,

@@ -227,3 +227,38 @@ def test_linear_tcgen05_rows_independent_of_batch():
     Xn[5:] = 0x7FC0
     part = run_linear(lib, 0, W, n, k, Xn, 16, flags=T)
     assert np.array_equal(full[:5], part[:5])
+
+
+@pytest.mark.parametrize("fmt,n,k", [(0, 5120, 6144), (4, 1024, 17408), (0, 256, 1024)])
+def test_linear_partial_sums_then_prepare_sum_equal_the_residual_epilogue(fmt, n, k):
+    """SB_EPILOGUE_PARTIALS leaves the k-slices' sums; sb_linear_prepare_sum adds them and the residual in the same
+    order as the in-kernel reduction, so the new hidden state has the same bits, and so has what is prepared from it."""
+    lib = _setup()
+    L = lib.load()
+    rows = 16
+    W = qf.realistic(fmt, n, k, seed=5)
+    X = qf.activations(rows, k, seed=6)
+    rng = np.random.default_rng(7)
+    res = ol.f2bf(rng.standard_normal((rows, n)).astype(np.float32) * 2)
+    resd = lib.DeviceBuffer.from_numpy(res)
+    want = run_linear(lib, fmt, W, n, k, X, rows, aux=resd.ptr, epilogue=lib.EP_RESIDUAL)
+    plan = lib.SbLinearPlan()
+    L.sb_linear_plan.argtypes = [ctypes.c_uint32] * 5 + [ctypes.POINTER(lib.SbLinearPlan)]
+    lib.check(L.sb_linear_plan(fmt, n, k, rows, lib.EP_PARTIALS, ctypes.byref(plan)))
+    wd, xd = lib.DeviceBuffer.from_numpy(W), lib.DeviceBuffer.from_numpy(X)
+    parts = lib.DeviceBuffer(plan.slices * 16 * n * 4)
+    parts.fill(0xFF)
+    lib.linear(wd.ptr, xd.ptr, parts.ptr, fmt, n, k, rows, epilogue=lib.EP_PARTIALS, out_f32=True)
+    # consumer side: a Q4_K projection of the new hidden state (n must be whole super-blocks)
+    prep_a, prep_b = lib.DeviceBuffer(int(L.sb_linear_prepared_bytes(n))), lib.DeviceBuffer(int(L.sb_linear_prepared_bytes(n)))
+    hidden = lib.DeviceBuffer(rows * n * 2)
+    wn = lib.DeviceBuffer.from_numpy((1 + 0.1 * rng.standard_normal(n)).astype(np.float32))
+    lib.check(L.sb_linear_prepare_sum(None, parts.ptr, plan.slices, n, resd.ptr, n, hidden.ptr, n, rows, n, wn.ptr, lib.FMT_Q4K, prep_a.ptr, None, 0))
+    lib.stream_sync()
+    assert lib.device_status() == 0
+    got = hidden.to_numpy(np.uint16, (rows, n))
+    assert np.array_equal(got, want)
+    wantd = lib.DeviceBuffer.from_numpy(want)
+    lib.check(L.sb_linear_prepare(None, wantd.ptr, rows, n, n, wn.ptr, lib.FMT_Q4K, prep_b.ptr, None, 0))
+    lib.stream_sync()
+    assert np.array_equal(prep_a.to_numpy(np.uint8, (int(L.sb_linear_prepared_bytes(n)),)), prep_b.to_numpy(np.uint8, (int(L.sb_linear_prepared_bytes(n)),)))
