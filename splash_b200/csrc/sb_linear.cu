@@ -33,6 +33,7 @@
 //             (runtime/metal/kernels/common/gguf_tile.h:8-14, gguf_linear.metal:38)
 #include <algorithm>
 
+#include <cooperative_groups.h>
 #include <cuda.h>
 
 #include "sb_internal.h"
@@ -114,7 +115,8 @@ __device__ __forceinline__ void slice_range(uint32_t nsb, uint32_t slices, uint3
 // y = bf16((x * rsqrt(mean x^2 + 1e-6)) * w) (runtime/metal/kernels/shared/normalization.metal:60-94).
 static_assert(kPrepSbBytes == kXsbBytes + kSxSbBytes, "prepared super-block size");
 constexpr int kPrepThreads = 256;
-constexpr int kPrepMaxChunks = 9;  // 8-element chunks a thread keeps in registers: k <= 18432
+constexpr int kPrepCluster = 8;    // CTAs per row: a thread-block cluster shares the row's sum of squares and maximum
+constexpr int kPrepMaxChunks = 2;  // 8-element chunks a thread keeps in registers: k <= 8 * 2 * 256 * 8 = 32768
 
 struct PrepareParams {
   const uint16_t *x;
@@ -150,16 +152,19 @@ __device__ __forceinline__ void block_reduce2(float &s, float &m, float *scratch
 
 __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PrepareParams p) {
   __shared__ float scratch[2 * (kPrepThreads / 32)];
-  const uint32_t tok = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
+  __shared__ float cluster_part[2];  // this CTA's sum of squares and maximum, read by the row's other CTAs
+  // A row is shared by the kPrepCluster CTAs of a cluster: CTA `rank` converts whole super-blocks
+  // [rank nsb / C, (rank + 1) nsb / C) and the row's statistics meet through distributed shared memory.
+  const uint32_t tok = blockIdx.x / kPrepCluster, rank = blockIdx.x % kPrepCluster, tid = threadIdx.x, lane = tid & 31;
   const bool live = tok < p.rows;
-  const uint32_t chunks = p.k / 8;
+  const uint32_t nsb = p.k / 256, c0 = rank * nsb / kPrepCluster * 32, chunks = (rank + 1) * nsb / kPrepCluster * 32;
   pdl_launch_dependents();
   // The norm weights do not depend on the previous kernel: they are fetched before the dependency wait.
   float wn[kPrepMaxChunks][8];
   if (p.norm_w) {
 #pragma unroll
     for (int i = 0; i < kPrepMaxChunks; ++i) {
-      const uint32_t c = tid + kPrepThreads * i;
+      const uint32_t c = c0 + tid + kPrepThreads * i;
       float4 w0 = make_float4(0, 0, 0, 0), w1 = w0;
       if (c < chunks) {
         w0 = *reinterpret_cast<const float4 *>(p.norm_w + 8 * c);
@@ -174,7 +179,7 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PreparePara
   const uint16_t *row = p.x + size_t(tok) * p.x_stride;
 #pragma unroll
   for (int i = 0; i < kPrepMaxChunks; ++i) {
-    const uint32_t c = tid + kPrepThreads * i;
+    const uint32_t c = c0 + tid + kPrepThreads * i;
     uint4 raw = make_uint4(0, 0, 0, 0);
     if (live && c < chunks) raw = *reinterpret_cast<const uint4 *>(row + 8 * c);
     const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -186,10 +191,19 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PreparePara
     if (p.partials && live && c < chunks) {
       // x = bf16(sum of the slices in order + residual): the projection's residual epilogue, done here.
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (uint32_t sl = 0; sl < p.partial_slices; ++sl) {
-        const float4 *pp = reinterpret_cast<const float4 *>(p.partials + (size_t(sl) * kTokens + tok) * p.partial_stride + 8 * c);
-        const float4 a4 = __ldcg(pp), b4 = __ldcg(pp + 1);
-        acc[0] += a4.x, acc[1] += a4.y, acc[2] += a4.z, acc[3] += a4.w, acc[4] += b4.x, acc[5] += b4.y, acc[6] += b4.z, acc[7] += b4.w;
+      for (uint32_t s0 = 0; s0 < p.partial_slices; s0 += 8) {  // eight slices' loads in flight, added in slice order
+        float4 a4[8], b4[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t sl = min(s0 + j, p.partial_slices - 1);
+          const float4 *pp = reinterpret_cast<const float4 *>(p.partials + (size_t(sl) * kTokens + tok) * p.partial_stride + 8 * c);
+          a4[j] = __ldcg(pp), b4[j] = __ldcg(pp + 1);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (s0 + j < p.partial_slices)
+            acc[0] += a4[j].x, acc[1] += a4[j].y, acc[2] += a4[j].z, acc[3] += a4[j].w, acc[4] += b4[j].x, acc[5] += b4[j].y,
+                acc[6] += b4[j].z, acc[7] += b4[j].w;
       }
       uint32_t pk[4];
 #pragma unroll
@@ -210,6 +224,22 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PreparePara
       mx = fmaxf(mx, fabsf(p.norm_w ? v[i][j] * wn[i][j] : v[i][j]));  // NaN does not win a max; it stays in the values
     }
   block_reduce2(ss, mx, scratch);
+  {
+    // The row's statistics: every CTA publishes its own and reads the others' in rank order.
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    if (tid == 0) cluster_part[0] = ss, cluster_part[1] = mx;
+    cluster.sync();
+    float ss_all = 0.0f, mx_all = 0.0f;
+#pragma unroll
+    for (int r = 0; r < kPrepCluster; ++r) {
+      const float *remote = cluster.map_shared_rank(cluster_part, r);
+      ss_all += remote[0];
+      mx_all = fmaxf(mx_all, remote[1]);
+    }
+    ss = ss_all, mx = mx_all;
+    cluster.sync();  // nobody leaves (or rewrites its slot) while a peer may still read it
+  }
   if (p.norm_w) {
     const float inv = rsqrtf(ss / float(p.k) + 1e-6f);
 #pragma unroll
@@ -221,7 +251,7 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PreparePara
   if (p.normed_out && live) {
 #pragma unroll
     for (int i = 0; i < kPrepMaxChunks; ++i) {
-      const uint32_t c = tid + kPrepThreads * i;
+      const uint32_t c = c0 + tid + kPrepThreads * i;
       if (c < chunks) {
         uint32_t pk[4];
 #pragma unroll
@@ -237,11 +267,11 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PreparePara
     e -= 10;
   }
   const float down = ldexpf(1.0f, -e);
-  if (tid == 0) reinterpret_cast<float *>(p.out)[tok] = ldexpf(1.0f, e);
+  if (tid == 0 && rank == 0) reinterpret_cast<float *>(p.out)[tok] = ldexpf(1.0f, e);
   const uint32_t h = tok >> 3, g = tok & 7;
 #pragma unroll
   for (int i = 0; i < kPrepMaxChunks; ++i) {
-    const uint32_t c = tid + kPrepThreads * i;  // chunk c = inputs 8c..8c+7; 32 consecutive chunks = one super-block
+    const uint32_t c = c0 + tid + kPrepThreads * i;  // chunk c = inputs 8c..8c+7; 32 consecutive chunks = one super-block
     if (c >= chunks) continue;                  // uniform per warp: chunks is a multiple of 32
     const uint32_t sb = c >> 5, j = lane >> 2, q = lane & 3;
     __half hv[8];
@@ -957,14 +987,16 @@ static int launch_prepare(cudaStream_t stream, const void *x, uint32_t rows, uin
                    static_cast<uint16_t *>(normed_out), rows, k, x_stride, layout, partials, static_cast<uint16_t *>(sum_out), slices,
                    partial_stride, sum_stride};
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(kTokens);
+  cfg.gridDim = dim3(kTokens * kPrepCluster);
   cfg.blockDim = dim3(kPrepThreads);
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kPrepCluster, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = pdl ? 2 : 1;
   SB_CUDA(cudaLaunchKernelEx(&cfg, prepare_kernel, pp));
   return SB_OK;
 }
@@ -997,8 +1029,8 @@ extern "C" int sb_linear_prepare(void *stream, const void *x, uint32_t rows, uin
   SB_NEED_DEVICE();
   SB_REQUIRE(x && prepared_out, "sb_linear_prepare: null x or destination");
   SB_REQUIRE(rows >= 1 && rows <= kTokens, "sb_linear_prepare: rows = %u outside 1..%d", rows, kTokens);
-  SB_REQUIRE(k && k % 256 == 0 && k <= 8 * kPrepThreads * kPrepMaxChunks, "sb_linear_prepare: k = %u is not a multiple of 256 up to %d",
-             k, 8 * kPrepThreads * kPrepMaxChunks);
+  SB_REQUIRE(k && k % 256 == 0 && k <= 8 * kPrepThreads * kPrepMaxChunks * kPrepCluster, "sb_linear_prepare: k = %u is not a multiple of 256 up to %d",
+             k, 8 * kPrepThreads * kPrepMaxChunks * kPrepCluster);
   SB_REQUIRE(x_stride >= k && x_stride % 8 == 0, "sb_linear_prepare: x_stride %u < k or not a multiple of 8", x_stride);
   SB_REQUIRE(format == SB_FMT_Q4K || format == SB_FMT_Q6K || format == SB_FMT_Q80, "sb_linear_prepare: format %u", format);
   SB_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(prepared_out) & 15) == 0 &&
@@ -1017,8 +1049,8 @@ extern "C" int sb_linear_prepare_sum(void *stream, const float *partials, uint32
   SB_REQUIRE(partials && residual && sum_out && prepared_out, "sb_linear_prepare_sum: null pointer");
   SB_REQUIRE(slices >= 1 && slices <= 64, "sb_linear_prepare_sum: %u slices outside 1..64", slices);
   SB_REQUIRE(rows >= 1 && rows <= kTokens, "sb_linear_prepare_sum: rows = %u outside 1..%d", rows, kTokens);
-  SB_REQUIRE(k && k % 256 == 0 && k <= 8 * kPrepThreads * kPrepMaxChunks, "sb_linear_prepare_sum: k = %u is not a multiple of 256 up to %d",
-             k, 8 * kPrepThreads * kPrepMaxChunks);
+  SB_REQUIRE(k && k % 256 == 0 && k <= 8 * kPrepThreads * kPrepMaxChunks * kPrepCluster, "sb_linear_prepare_sum: k = %u is not a multiple of 256 up to %d",
+             k, 8 * kPrepThreads * kPrepMaxChunks * kPrepCluster);
   SB_REQUIRE(partial_stride >= k && partial_stride % 4 == 0 && residual_stride >= k && residual_stride % 8 == 0 && sum_stride >= k && sum_stride % 8 == 0,
              "sb_linear_prepare_sum: a stride is below k or misaligned");
   SB_REQUIRE(format == SB_FMT_Q4K || format == SB_FMT_Q6K || format == SB_FMT_Q80, "sb_linear_prepare_sum: format %u", format);
