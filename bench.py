@@ -3,7 +3,12 @@
 (64 layers at 3:1 Gated-DeltaNet : attention, Q4_K_M mix, batch 1, block 16, 32K-token INT8 paged KV
 context, greedy acceptance) with seeded synthetic weights, cache and state written on the device.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--parallel tp|replicas]
+
+With N > 1 (one process per GPU under torchrun) the N GPUs run ONE lane tensor-parallel: every rank holds its share
+of the model, the shares of out_proj / down meet through peer memory inside the next input conversion, the logits'
+columns are gathered the same way (`scaling: "strong"`, value = the lane's tokens/s). `--parallel replicas` runs N
+independent lanes instead (`scaling: "weak"`).
 
 One JSON line on stdout (rank 0). `value` is device-resident steps; `e2e` goes through the host-facing call
 sb_target_verify with pinned host buffers, copies and the result read-back inside the timed region;
@@ -115,6 +120,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--tiny", action="store_true", help="the 4-layer configuration (a smoke run, not the benchmark)")
+    ap.add_argument("--parallel", default="tp", choices=("tp", "replicas"), help="what N > 1 GPUs do: one lane tensor-parallel, or N lanes")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -138,12 +144,22 @@ def main():
     lib.init(local)
     cfg = dict(target.TINY if args.tiny else target.QWEN27B)
     context = 2048 if args.tiny else CONTEXT
-    t = target.Target(**cfg)
-    t.randomize(1234 + rank, context)
+    tensor_parallel = world > 1 and args.parallel == "tp"
+    if tensor_parallel:
+        # every rank its share of the same model: same seed (tensors held whole must agree), same input tokens
+        from splash_b200 import tp
+        t = target.Target(**cfg, tp_world=world, tp_rank=rank)
+        t.randomize(1234, context)
+        tp.connect(t, group.all_gather_bytes)
+        group.barrier()
+    else:
+        t = target.Target(**cfg)
+        t.randomize(1234 + rank, context)
+    lanes = 1 if tensor_parallel else world
     stream = lib.stream_create()
     warm = max(args.warmup, 3)
     flags = target.GRAPH  # hold the lane at 32K: every step does the same work
-    rng = np.random.default_rng(rank)
+    rng = np.random.default_rng(0 if tensor_parallel else rank)
     t.upload(-1, "tokens", rng.integers(0, cfg["vocab"], ROWS).astype(np.uint32))
 
     def barrier():
@@ -168,6 +184,10 @@ def main():
     clocks = sampler.stop() if sampler else None
     status = lib.device_status()
     stats = t.stats(ROWS)
+    if tensor_parallel:  # the job's bytes are all ranks' shares; a failed exchange on any rank fails the run
+        for key in ("weight_bytes", "kv_bytes", "state_bytes"):
+            stats[key] = int(group.reduce_sum(stats[key]))
+        status = int(reduce_max(status))
 
     # ---- end to end through the host-facing call, pinned host buffers ----
     pinned = ctypes.c_void_p()
@@ -199,6 +219,8 @@ def main():
     roofline = None
     if not args.tiny:
         H, I = cfg["hidden"], cfg["intermediate"]
+        if tensor_parallel:
+            I = tp.share(cfg, world, rank)["intermediate"]  # the launch as this rank runs it
         x = lib.DeviceBuffer(ROWS * H * 2 + 256)
         x.upload(rng.standard_normal((ROWS, H)).astype(np.float16).view(np.uint16))  # any finite bf16 bits
         prep = lib.DeviceBuffer(int(lib.load().sb_linear_prepared_bytes(H)))
@@ -223,11 +245,11 @@ def main():
         launch_ms = k0.elapsed_ms(k1) / n
         algo = 2 * I * (H // 256) * 144 + ROWS * H * 2 + ROWS * I * 2
         achieved = algo / launch_ms / 1e6
-        roofline = {"bound": "hbm", "kernel": "linear_kernel<Q4_K> gate/up 2x[17408x5120], M=16", "achieved": achieved, "peak": peak,
+        roofline = {"bound": "hbm", "kernel": "linear_kernel<Q4_K> gate/up 2x[%dx%d], M=16" % (I, H), "achieved": achieved, "peak": peak,
                     "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind, "algorithmic_bytes": algo,
-                    "launch_us": launch_ms * 1e3, "traffic": DOMINANT_TRAFFIC_BYTES}
+                    "launch_us": launch_ms * 1e3, "traffic": None if tensor_parallel else DOMINANT_TRAFFIC_BYTES}
     step_bytes = stats["weight_bytes"] + stats["kv_bytes"] + stats["state_bytes"]
-    step_gbs = step_bytes / ms / 1e6
+    step_gbs = step_bytes / ms / 1e6 / (world if tensor_parallel else 1)  # per GPU
     if args.tiny:
         cpu_tps, cores, sample = None, os.cpu_count(), "skipped for the tiny run"
     elif world > 1:
@@ -235,12 +257,12 @@ def main():
     else:
         cpu_tps, cores, sample = cpu_baseline(15.0)
     result = {
-        "metric": "verify_tokens_per_s", "value": world * ROWS / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": "verify_tokens_per_s", "value": lanes * ROWS / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if tensor_parallel else "weak", "vs_baseline": None,
         "dtype": "f16 operands (exact integer codes), f32 accumulate, bf16 activations", "data": "synthetic",
-        "config": {"workload": workload, "context_tokens": context, "block": ROWS, "parallelism": "tp1" if world == 1 else f"{world} independent replicas (lanes); tensor parallel not built",
+        "config": {"workload": workload, "context_tokens": context, "block": ROWS, "parallelism": "tp1" if world == 1 else (f"tp{world}: one lane, shares exchanged through peer memory over NVLink in the input conversions" if tensor_parallel else f"{world} independent replicas (lanes)"),
                    "l2": "inputs exceed L2: one step streams %.1f GB of weights" % (stats["weight_bytes"] / 1e9), "cuda_graph": True, "pdl": True},
-        "e2e": {"value": world * ROWS / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": ROWS * 4, "d2h_bytes_per_step": 16 + ROWS * 4},
+        "e2e": {"value": lanes * ROWS / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": ROWS * 4, "d2h_bytes_per_step": 16 + ROWS * 4},
         "gpu_launches": stats["launches"] * args.steps,
         "launches_per_step": stats["launches"],
         "step_roofline": {"bytes_per_step": step_bytes, "weight_bytes": stats["weight_bytes"], "kv_bytes": stats["kv_bytes"],

@@ -369,6 +369,9 @@ typedef struct SbTargetConfig {
   uint32_t page_tokens, kv_scale_f16, max_context;
   uint32_t fmt_proj, fmt_down, fmt_head, fmt_embed; /* SB_FMT_* */
   uint32_t gated_attention, tiled_heads;
+  /* Tensor parallelism: this process is rank tp_rank of tp_world ranks, one per GPU of the node (0 or 1: the whole
+   * model on this GPU). The configuration above stays the whole model's; the rank holds its share (below). */
+  uint32_t tp_world, tp_rank;
 } SbTargetConfig;
 
 enum {
@@ -376,7 +379,51 @@ enum {
   SB_TARGET_GRAPH = 2    /* replay the step as a captured CUDA graph (captured on first use per parity) */
 };
 
+/* ---- tensor parallelism between the GPUs of one node ----
+ * The reference runs on one GPU; its projections admit the usual split, and this is it: rank r of W holds
+ *   q heads [r Q/W, (r+1) Q/W) with their KV heads (KV head r K/W when W > K: a KV head and its pages are then held
+ *   by W/K ranks), GDN key and value heads [r K/W, ..) and [r V/W, ..) with their state, convolution channels and
+ *   tapes, rows of in_proj / ssm_ab / ffn_gate / ffn_up for those heads and for its super-blocks of the intermediate
+ *   width (68 super-blocks over 8 ranks: 9,9,9,9,8,8,8,8), the matching input columns of out_proj and ffn_down, and
+ *   vocabulary columns in units of 64; norms and the embedding table whole.
+ * out_proj and ffn_down then give each rank a share of the sum. The ranks exchange shares through each other's
+ * memory (CUDA IPC mappings over NVLink, plain stores and loads: no TMA, no multicast) inside the kernel that
+ * converts the next projection's input, and add them in rank order, so every rank holds the same hidden state bit
+ * for bit; the logits' columns are gathered the same way and selection, acceptance and the commit run on every rank.
+ * An exchange that waits longer than 2 s for a peer records a wait failure in the device status word
+ * (sb_device_status) and carries on; later exchanges then do not wait.
+ *
+ * A group is one rank's end: create on every rank, pass every rank's exported handle to every rank (any host
+ * transport), connect. `width` = the hidden size; `gather_width` = the vocabulary size. */
+#define SB_TP_HANDLE_BYTES 64
+SB_API int sb_tp_create(uint32_t world, uint32_t rank, uint32_t width, uint32_t gather_width, void **out_group);
+SB_API int sb_tp_destroy(void *group);
+SB_API int sb_tp_export(void *group, void *handle_out /* SB_TP_HANDLE_BYTES */);
+SB_API int sb_tp_connect(void *group, const void *handles /* [world][SB_TP_HANDLE_BYTES], rank order */);
+/* The group's fp32 [16][gather_width] matrix that sb_tp_all_gather completes on every rank. */
+SB_API int sb_tp_gather_matrix(void *group, void **out_dev, uint64_t *out_bytes);
+/* sb_linear_prepare_sum where the slices' sum is this rank's share of the whole: exchange, sum in rank order, residual,
+ * conversion. `index` = the exchange's place among the step's exchanges (the same on every rank). k = the group's width. */
+SB_API int sb_tp_prepare_sum(void *stream, void *group, uint32_t index, const float *partials, uint32_t slices, uint32_t partial_stride,
+                             const void *residual, uint32_t residual_stride, void *sum_out, uint32_t sum_stride, uint32_t rows, uint32_t k,
+                             const void *norm_weight, uint32_t format, void *prepared_out, void *normed_out, uint32_t flags);
+/* This rank's columns [column0, column0 + columns) of the gather matrix go to every peer; returns (on the stream) when
+ * every peer's columns have arrived here. */
+SB_API int sb_tp_all_gather(void *stream, void *group, uint32_t index, uint32_t rows, uint32_t column0, uint32_t columns);
+/* Ends a step of `exchanges` exchanges: the next step's indices start over. (sb_target_* steps do this themselves.) */
+SB_API int sb_tp_advance(void *stream, void *group, uint32_t exchanges);
+
 SB_API int sb_target_create(const SbTargetConfig *config, void **out_target);
+/* With tp_world > 1: the handle of this rank's exchange window, and the connection to all ranks' (sb_tp_export,
+ * sb_tp_connect). A tensor-parallel target steps only after sb_target_tp_connect. */
+SB_API int sb_target_tp_export(void *target, void *handle_out);
+SB_API int sb_target_tp_connect(void *target, const void *handles);
+/* This rank's share of the whole model's dimensions (equal to the configuration's without tensor parallelism). */
+typedef struct SbTargetShare {
+  uint32_t q_heads, q_head0, kv_heads, kv_head0, gdn_key_heads, gdn_key_head0, gdn_value_heads, gdn_value_head0;
+  uint32_t intermediate, intermediate0, vocab, vocab0;
+} SbTargetShare;
+SB_API int sb_target_share(const SbTargetConfig *config, SbTargetShare *out_share);
 SB_API int sb_target_destroy(void *target);
 /* Device pointer and byte size of a tensor or buffer by name. Per layer (layer >= 0): attn_norm, ffn_norm,
  * in_proj, out_proj, ffn_gate, ffn_up, ffn_down, and for GDN layers ssm_ab, ssm_conv, ssm_a, ssm_dt_bias, ssm_norm,

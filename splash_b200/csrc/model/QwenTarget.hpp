@@ -18,6 +18,7 @@
 #include "../ops/Linear.hpp"
 #include "../ops/PagedAttention.hpp"
 #include "../ops/Sampling.hpp"
+#include "../ops/TensorParallel.hpp"
 
 namespace splash::b200::model {
 
@@ -36,14 +37,52 @@ struct LayerWeights {
   ops::kv::LayerPages pages;
 };
 
+// Rank tp_rank's share of the whole model's dimensions (include/splash_b200.h, "tensor parallelism"): heads in
+// contiguous ranges, a KV head shared by tp_world / kv_heads ranks when there are more ranks than KV heads, the
+// intermediate width in super-blocks of 256 and the vocabulary in units of 64, the first ranks taking the remainder.
+inline SbTargetShare shareOf(const SbTargetConfig &c) {
+  const uint32_t W = std::max(1u, c.tp_world), r = c.tp_rank;
+  if (W > 8 || r >= W) throw std::invalid_argument("QwenTarget: rank " + std::to_string(r) + " of " + std::to_string(W) + " ranks (at most 8)");
+  auto even = [&](uint32_t total, const char *what) {
+    if (total % W) throw std::invalid_argument(std::string("QwenTarget: ") + what + " do not divide among the ranks");
+    return total / W;
+  };
+  auto ragged = [&](uint32_t units, uint32_t &first) {
+    const uint32_t base = units / W, extra = units % W;
+    first = r * base + std::min(r, extra);
+    return base + (r < extra ? 1u : 0u);
+  };
+  SbTargetShare s{};
+  s.q_heads = even(c.q_heads, "query heads"), s.q_head0 = r * s.q_heads;
+  if (c.kv_heads >= W) {
+    s.kv_heads = even(c.kv_heads, "KV heads"), s.kv_head0 = r * s.kv_heads;
+  } else {
+    if (!c.kv_heads || W % c.kv_heads) throw std::invalid_argument("QwenTarget: the ranks do not divide among the KV heads");
+    s.kv_heads = 1, s.kv_head0 = r / (W / c.kv_heads);
+  }
+  s.gdn_key_heads = even(c.gdn_key_heads, "GDN key heads"), s.gdn_key_head0 = r * s.gdn_key_heads;
+  s.gdn_value_heads = even(c.gdn_value_heads, "GDN value heads"), s.gdn_value_head0 = r * s.gdn_value_heads;
+  uint32_t first = 0;
+  s.intermediate = 256 * ragged(c.intermediate / 256, first), s.intermediate0 = 256 * first;
+  const uint32_t units = ragged((c.vocab + 63) / 64, first);
+  s.vocab0 = std::min(c.vocab, 64 * first), s.vocab = std::min(c.vocab, 64 * (first + units)) - s.vocab0;
+  if (W > 1 && (!s.intermediate || !s.vocab || c.vocab % 4)) throw std::invalid_argument("QwenTarget: a rank without a share, or a vocabulary that is not a multiple of 4");
+  return s;
+}
+
 class QwenTarget {
  public:
-  explicit QwenTarget(const SbTargetConfig &c);
+  explicit QwenTarget(const SbTargetConfig &whole);
 
   // Appends one verify step of `rows` rows to the graph. `parity` selects which GDN cell is current.
   void encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance);
 
-  const SbTargetConfig &config() const { return cfg_; }
+  const SbTargetConfig &config() const { return cfg_; }   // the whole model
+  const SbTargetConfig &local() const { return loc_; }    // this rank's heads and intermediate width (the vocabulary stays whole)
+  const SbTargetShare &share() const { return share_; }
+  ops::TensorParallel *tensorParallel() { return tp_.get(); }
+  // Exchanges of one step: one after every out_proj and down, one for the logits.
+  uint32_t exchangesPerStep() const { return 2 * cfg_.layers + 1; }
   bool find(int layer, const std::string &name, Buffer &out) const;
   std::vector<LayerWeights> &layers() { return layers_; }
 
@@ -60,7 +99,9 @@ class QwenTarget {
   ops::QuantizedSegment segment(uint32_t n, uint32_t k, uint32_t format);
   Buffer floats(size_t count) { return Buffer::allocate(count * 4); }
 
-  SbTargetConfig cfg_;
+  SbTargetConfig cfg_, loc_;
+  SbTargetShare share_{};
+  std::unique_ptr<ops::TensorParallel> tp_;
   ops::GdnShape gdn_;
   ops::kv::Layout kv_;
   std::vector<LayerWeights> layers_;
@@ -84,7 +125,12 @@ inline ops::QuantizedSegment QwenTarget::segment(uint32_t n, uint32_t k, uint32_
   return s;
 }
 
-inline QwenTarget::QwenTarget(const SbTargetConfig &c) : cfg_(c) {
+inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(whole) {
+  share_ = shareOf(whole);
+  loc_.q_heads = share_.q_heads, loc_.kv_heads = share_.kv_heads, loc_.gdn_key_heads = share_.gdn_key_heads;
+  loc_.gdn_value_heads = share_.gdn_value_heads, loc_.intermediate = share_.intermediate;
+  const SbTargetConfig &c = loc_;
+  if (whole.tp_world > 1) tp_ = std::make_unique<ops::TensorParallel>(whole.tp_world, whole.tp_rank, whole.hidden, whole.vocab);
   if (!c.layers || !c.hidden || !c.vocab || !c.intermediate || !c.attention_interval)
     throw std::invalid_argument("QwenTarget: empty configuration");
   if (c.hidden % 256 || c.intermediate % 256) throw std::invalid_argument("QwenTarget: hidden and intermediate sizes are multiples of 256");
@@ -130,7 +176,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &c) : cfg_(c) {
   embedding_.rows = Buffer::allocate(size_t(c.vocab) * sb_row_bytes(c.fmt_embed, H));
   embedding_.vocabulary = c.vocab, embedding_.width = H, embedding_.format = c.fmt_embed;
   outputNorm_.buffer = floats(H);
-  output_ = segment(c.vocab, H, c.fmt_head);
+  output_ = segment(share_.vocab, H, c.fmt_head);
 
   packedStride_ = std::max(attnIn, gdnIn);
   packed_ = Buffer::allocate(size_t(kVerifyRows) * packedStride_ * 2);
@@ -143,7 +189,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &c) : cfg_(c) {
   const uint32_t widest = std::max(std::max(H, c.intermediate), std::max(gdn_.valueWidth(), c.q_heads * D));
   for (auto &p : prepared_) p = Buffer::allocate(ops::Linear::preparedBytes((widest + 255) / 256 * 256));
   for (auto &h : hidden) h = Buffer::allocate(size_t(kVerifyRows) * H * 2);
-  logits = Buffer::allocate(size_t(kVerifyRows) * c.vocab * 4);
+  logits = tp_ ? tp_->gathered() : Buffer::allocate(size_t(kVerifyRows) * c.vocab * 4);
   tokens = Buffer::allocate(kVerifyRows * 4), selected = Buffer::allocate(kVerifyRows * 4), results = Buffer::allocate(16);
   uniforms = Buffer::allocate(80 * 4), committed = Buffer::allocate(4), pendingRows = Buffer::allocate(4);
   tree = Buffer::allocate(kVerifyRows * 8), positions = Buffer::allocate(kVerifyRows * 4);
@@ -201,14 +247,18 @@ inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) co
 
 // Launched before and after the operator sequence (sb_target.cu).
 void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer &tree, const Buffer &positions, uint32_t rows);
-void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, bool advance);
+// (with a tensor-parallel group the step's end also advances the group's exchange count by `exchanges`)
+void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, bool advance,
+                   void *tpGroup, uint32_t exchanges);
 
 inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance) {
   using namespace ops;
   if (rows < 1 || rows > kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: 1 to 16 rows");
   if (committedHost + rows > cfg_.max_context + kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: past the context bound");
-  const SbTargetConfig &c = cfg_;
+  const SbTargetConfig &c = loc_;
   const uint32_t H = c.hidden, D = c.head_dim;
+  if (tp_ && !tp_->connected()) throw std::invalid_argument("QwenTarget::encodeVerify: the tensor-parallel ranks are not connected");
+  uint32_t exchange = 0;  // the place of the next exchange among the step's
   launchStepBegin(graph, committed, tree, positions, rows);
   if (c.rotary_pairs) RoPE::addTreeTables(graph, positions, invFreq, cosine, sine, rows, 1.0f, c.rotary_pairs);
   Embedding::add(graph, tokens, embedding_, hidden[0], rows, H);
@@ -220,7 +270,8 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   uint32_t pending = 0;
   auto convert = [&](const Buffer *norm, uint32_t format, const Buffer &scratch, const Buffer *normedOutput) {
     if (!pending) return Linear::prepare(graph, hidden[cur], rows, H, H, norm, format, scratch, normedOutput);
-    PreparedInput in = Linear::prepareSum(graph, partials_, pending, H, hidden[cur], hidden[cur ^ 1], rows, H, H, norm, format, scratch, normedOutput);
+    PreparedInput in = tp_ ? tp_->prepareSum(graph, exchange++, partials_, pending, H, hidden[cur], hidden[cur ^ 1], rows, H, H, norm, format, scratch, normedOutput)
+                           : Linear::prepareSum(graph, partials_, pending, H, hidden[cur], hidden[cur ^ 1], rows, H, H, norm, format, scratch, normedOutput);
     cur ^= 1;
     pending = 0;
     return in;
@@ -229,6 +280,7 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
     Projection proj{H, inputSize, Destination::BFloat16, {seg}};
     LinearPlan plan = Linear::plan(proj, rows, Epilogue::Partials);
     if (plan.kernel.slices > kMaxPartialSlices) {  // a shape with more slices than the scratch holds reduces in the kernel
+      if (tp_) throw std::invalid_argument("QwenTarget::encodeVerify: a rank's share of a projection has more k-slices than the exchange takes");
       LinearBuffers b{Buffer(), hidden[cur ^ 1], hidden[cur], inputSize, H};
       Linear::add(graph, b, proj, Linear::plan(proj, rows, Epilogue::Residual), in);
       cur ^= 1;
@@ -274,9 +326,11 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   }
   // logits of every row
   PreparedInput headIn = convert(&outputNorm_.buffer, output_.format, prepared_[0], nullptr);
-  Projection head{c.vocab, H, Destination::Float32, {output_}};
-  LinearBuffers headB{Buffer(), logits, Buffer(), H, c.vocab};
+  // (a rank projects its vocabulary columns into its place of the whole matrix; the ranks then gather the rest)
+  Projection head{share_.vocab, H, Destination::Float32, {output_}};
+  LinearBuffers headB{Buffer(), logits.view(size_t(share_.vocab0) * 4, logits.bytes() - size_t(share_.vocab0) * 4), Buffer(), H, c.vocab};
   Linear::add(graph, headB, head, Linear::plan(head, rows, Epilogue::None), headIn);
+  if (tp_) tp_->allGather(graph, exchange++, rows, share_.vocab0, share_.vocab);
   // selection, acceptance, commit
   SamplingBuffers sb;
   sb.logits = logits, sb.inputTokens = tokens, sb.uniforms = uniforms, sb.selected = selected, sb.workspace = sampleWorkspace_;
@@ -285,7 +339,8 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   AcceptanceBuffers ab;
   ab.inputTokens = tokens, ab.treeRows = tree, ab.outputTokens = selected, ab.results = results;
   Sampling::addAcceptance(graph, ab, rows, kVerifyRows);
-  launchStepEnd(graph, results, committed, pendingRows, advance);
+  if (tp_ && exchange != exchangesPerStep()) throw std::logic_error("QwenTarget::encodeVerify: exchange count");
+  launchStepEnd(graph, results, committed, pendingRows, advance, tp_ ? tp_->group() : nullptr, exchange);
 }
 
 }  // namespace splash::b200::model

@@ -46,6 +46,13 @@ class Buffer {
     b.bytes_ = bytes;
     return b;
   }
+  // Memory owned elsewhere (a tensor-parallel group's window); the owner outlives the buffer.
+  static Buffer wrap(void *p, size_t bytes) {
+    Buffer b;
+    b.data_ = static_cast<uint8_t *>(p);
+    b.bytes_ = bytes;
+    return b;
+  }
   Buffer view(size_t offset, size_t bytes) const {
     if (offset + bytes > bytes_) throw std::invalid_argument("Buffer::view past the allocation");
     Buffer b = *this;

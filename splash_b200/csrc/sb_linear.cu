@@ -38,6 +38,7 @@
 
 #include "sb_internal.h"
 #include "sb_linear_internal.h"
+#include "sb_tp_internal.cuh"
 #include "sb_ptx.cuh"
 
 #ifndef SB_Q4K_I2_UNROLL
@@ -128,6 +129,9 @@ struct PrepareParams {
   const float *partials;
   uint16_t *sum_out;
   uint32_t partial_slices, partial_stride, sum_stride;
+  // Optional (tensor parallelism): the slices' sum is one rank's share; the ranks exchange their shares through each
+  // other's memory and add them in rank order before the residual (sb_tp_internal.cuh).
+  TpExchange tp;
 };
 
 // Sum of `s` and maximum of `m` over the block, both returned to every thread. Fixed order: butterfly within
@@ -150,7 +154,7 @@ __device__ __forceinline__ void block_reduce2(float &s, float &m, float *scratch
   }
 }
 
-__global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PrepareParams p) {
+template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PrepareParams p) {
   __shared__ float scratch[2 * (kPrepThreads / 32)];
   __shared__ float cluster_part[2];  // this CTA's sum of squares and maximum, read by the row's other CTAs
   // A row is shared by the kPrepCluster CTAs of a cluster: CTA `rank` converts whole super-blocks
@@ -176,6 +180,7 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PreparePara
   }
   pdl_wait();
   float v[kPrepMaxChunks][8];
+  float acc[kPrepMaxChunks][8];
   const uint16_t *row = p.x + size_t(tok) * p.x_stride;
 #pragma unroll
   for (int i = 0; i < kPrepMaxChunks; ++i) {
@@ -188,9 +193,10 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PreparePara
       v[i][2 * j] = bf16_bits_to_float(u[j] & 0xffffu);
       v[i][2 * j + 1] = bf16_bits_to_float(u[j] >> 16);
     }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
     if (p.partials && live && c < chunks) {
-      // x = bf16(sum of the slices in order + residual): the projection's residual epilogue, done here.
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      // The sum of the slices in order: with the residual below, the projection's residual epilogue, done here.
       for (uint32_t s0 = 0; s0 < p.partial_slices; s0 += 8) {  // eight slices' loads in flight, added in slice order
         float4 a4[8], b4[8];
 #pragma unroll
@@ -202,12 +208,56 @@ __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PreparePara
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           if (s0 + j < p.partial_slices)
-            acc[0] += a4[j].x, acc[1] += a4[j].y, acc[2] += a4[j].z, acc[3] += a4[j].w, acc[4] += b4[j].x, acc[5] += b4[j].y,
-                acc[6] += b4[j].z, acc[7] += b4[j].w;
+            acc[i][0] += a4[j].x, acc[i][1] += a4[j].y, acc[i][2] += a4[j].z, acc[i][3] += a4[j].w, acc[i][4] += b4[j].x,
+                acc[i][5] += b4[j].y, acc[i][6] += b4[j].z, acc[i][7] += b4[j].w;
       }
+    }
+  }
+  if (TP && live) {
+    // This rank's share goes into every peer's inbox; the peers' shares arrive in this rank's. The sum over the
+    // ranks runs in rank order on every rank, so all ranks hold the same bits afterwards.
+    const TpExchange &x = p.tp;
+    const uint32_t epoch = tp_epoch(x);
+    const bool healthy = tp_healthy(x);
+    const size_t slot = size_t(epoch & 1u) * x.world;
+#pragma unroll
+    for (int i = 0; i < kPrepMaxChunks; ++i) {
+      const uint32_t c = c0 + tid + kPrepThreads * i;
+      if (c >= chunks) continue;
+      const size_t at = ((slot + x.rank) * kTokens + tok) * x.width + 8 * c;
+      const float4 lo = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]), hi = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+      for (uint32_t peer = 0; peer < x.world; ++peer) {
+        if (peer == x.rank) continue;
+        float4 *dst = reinterpret_cast<float4 *>(x.data[peer] + at);
+        dst[0] = lo, dst[1] = hi;
+      }
+    }
+    tp_signal_and_wait(x, epoch, blockIdx.x, gridDim.x, healthy);
+#pragma unroll
+    for (int i = 0; i < kPrepMaxChunks; ++i) {
+      const uint32_t c = c0 + tid + kPrepThreads * i;
+      if (c >= chunks) continue;
+      float total[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (uint32_t src = 0; src < x.world; ++src) {
+        float4 lo = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]), hi = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+        if (src != x.rank) {
+          const float4 *from = reinterpret_cast<const float4 *>(x.data[x.rank] + ((slot + src) * kTokens + tok) * x.width + 8 * c);
+          lo = __ldcg(from), hi = __ldcg(from + 1);
+        }
+        total[0] += lo.x, total[1] += lo.y, total[2] += lo.z, total[3] += lo.w, total[4] += hi.x, total[5] += hi.y, total[6] += hi.z, total[7] += hi.w;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[i][j] = total[j];
+    }
+  }
+  if (p.partials && live) {
+#pragma unroll
+    for (int i = 0; i < kPrepMaxChunks; ++i) {
+      const uint32_t c = c0 + tid + kPrepThreads * i;
+      if (c >= chunks) continue;
       uint32_t pk[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[i][j] = round_bf16(acc[j] + v[i][j]);
+      for (int j = 0; j < 8; ++j) v[i][j] = round_bf16(acc[i][j] + v[i][j]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) pk[j] = uint32_t(float_to_bf16_bits(v[i][2 * j])) | (uint32_t(float_to_bf16_bits(v[i][2 * j + 1])) << 16);
       *reinterpret_cast<uint4 *>(p.sum_out + size_t(tok) * p.sum_stride + 8 * c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
@@ -982,10 +1032,12 @@ int encode_weight_map(CUtensorMap *map, uintptr_t base, uint32_t stride, uint32_
 
 static int launch_prepare(cudaStream_t stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride,
                           const void *norm_w, uint32_t layout, void *out, void *normed_out, bool pdl, const float *partials = nullptr,
-                          uint32_t slices = 0, uint32_t partial_stride = 0, void *sum_out = nullptr, uint32_t sum_stride = 0) {
+                          uint32_t slices = 0, uint32_t partial_stride = 0, void *sum_out = nullptr, uint32_t sum_stride = 0,
+                          const TpExchange *tp = nullptr) {
   PrepareParams pp{static_cast<const uint16_t *>(x), static_cast<const float *>(norm_w), static_cast<uint8_t *>(out),
                    static_cast<uint16_t *>(normed_out), rows, k, x_stride, layout, partials, static_cast<uint16_t *>(sum_out), slices,
-                   partial_stride, sum_stride};
+                   partial_stride, sum_stride, tp ? *tp : TpExchange{}};
+  static_assert(kTokens * kPrepCluster == kTpConvertCtas, "the exchange's flag words are laid out for this grid");
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(kTokens * kPrepCluster);
   cfg.blockDim = dim3(kPrepThreads);
@@ -997,7 +1049,7 @@ static int launch_prepare(cudaStream_t stream, const void *x, uint32_t rows, uin
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 2 : 1;
-  SB_CUDA(cudaLaunchKernelEx(&cfg, prepare_kernel, pp));
+  SB_CUDA(tp ? cudaLaunchKernelEx(&cfg, prepare_kernel<true>, pp) : cudaLaunchKernelEx(&cfg, prepare_kernel<false>, pp));
   return SB_OK;
 }
 
@@ -1060,6 +1112,30 @@ extern "C" int sb_linear_prepare_sum(void *stream, const float *partials, uint32
   const uint32_t layout = format != SB_FMT_Q4K ? 0u : (flags & SB_LINEAR_TCGEN05) ? 2u : 1u;
   return launch_prepare(as_stream(stream), residual, rows, k, residual_stride, norm_weight, layout, prepared_out, normed_out,
                         (flags & SB_LINEAR_PDL) != 0, partials, slices, partial_stride, sum_out, sum_stride);
+}
+
+extern "C" int sb_tp_prepare_sum(void *stream, void *group, uint32_t index, const float *partials, uint32_t slices, uint32_t partial_stride,
+                                 const void *residual, uint32_t residual_stride, void *sum_out, uint32_t sum_stride, uint32_t rows, uint32_t k,
+                                 const void *norm_weight, uint32_t format, void *prepared_out, void *normed_out, uint32_t flags) {
+  SB_NEED_DEVICE();
+  TpExchange x;
+  const int st = tp_exchange(group, index, false, x);
+  if (st != SB_OK) return st;
+  SB_REQUIRE(partials && residual && sum_out && prepared_out, "sb_tp_prepare_sum: null pointer");
+  SB_REQUIRE(slices >= 1 && slices <= 64, "sb_tp_prepare_sum: %u slices outside 1..64", slices);
+  SB_REQUIRE(rows >= 1 && rows <= kTokens, "sb_tp_prepare_sum: rows = %u outside 1..%d", rows, kTokens);
+  SB_REQUIRE(k == x.width, "sb_tp_prepare_sum: k = %u, the group exchanges rows of %u", k, x.width);
+  SB_REQUIRE(k && k % 256 == 0 && k <= 8 * kPrepThreads * kPrepMaxChunks * kPrepCluster, "sb_tp_prepare_sum: k = %u is not a multiple of 256 up to %d",
+             k, 8 * kPrepThreads * kPrepMaxChunks * kPrepCluster);
+  SB_REQUIRE(partial_stride >= k && partial_stride % 4 == 0 && residual_stride >= k && residual_stride % 8 == 0 && sum_stride >= k && sum_stride % 8 == 0,
+             "sb_tp_prepare_sum: a stride is below k or misaligned");
+  SB_REQUIRE(format == SB_FMT_Q4K || format == SB_FMT_Q6K || format == SB_FMT_Q80, "sb_tp_prepare_sum: format %u", format);
+  SB_REQUIRE(((reinterpret_cast<uintptr_t>(partials) | reinterpret_cast<uintptr_t>(residual) | reinterpret_cast<uintptr_t>(sum_out) |
+               reinterpret_cast<uintptr_t>(prepared_out) | reinterpret_cast<uintptr_t>(norm_weight) | reinterpret_cast<uintptr_t>(normed_out)) & 15) == 0,
+             "sb_tp_prepare_sum: pointers must be 16-byte aligned");
+  const uint32_t layout = format != SB_FMT_Q4K ? 0u : (flags & SB_LINEAR_TCGEN05) ? 2u : 1u;
+  return launch_prepare(as_stream(stream), residual, rows, k, residual_stride, norm_weight, layout, prepared_out, normed_out,
+                        (flags & SB_LINEAR_PDL) != 0, partials, slices, partial_stride, sum_out, sum_stride, &x);
 }
 
 extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {

@@ -8,6 +8,7 @@
 #include "model/QwenTarget.hpp"
 #include "sb_internal.h"
 #include "sb_ptx.cuh"
+#include "sb_tp_internal.cuh"
 
 namespace sb {
 
@@ -22,10 +23,12 @@ __global__ void step_begin_kernel(const uint32_t *committed, uint2 *tree, uint32
   positions[r] = *committed + r;
 }
 // The lane's commit: the retained rows become history; the next step folds them into the GDN state.
-__global__ void step_end_kernel(const uint32_t *results, uint32_t *committed, uint32_t *pending_rows, uint32_t advance) {
+__global__ void step_end_kernel(const uint32_t *results, uint32_t *committed, uint32_t *pending_rows, uint32_t advance, uint32_t *tp_epoch,
+                                uint32_t tp_exchanges) {
   pdl_launch_dependents();
   pdl_wait();
   if (threadIdx.x != 0) return;
+  if (tp_epoch) *tp_epoch += tp_exchanges;  // the next step's exchanges are numbered after this step's
   if (advance) {
     *committed += results[0];
     *pending_rows = results[0];
@@ -128,7 +131,8 @@ void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer 
     throw BackendError(SB_ERR_CUDA, "step_begin launch failed");
   ++graph.launches;
 }
-void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, bool advance) {
+void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, bool advance,
+                   void *tpGroup, uint32_t exchanges) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(1), cfg.blockDim = dim3(32), cfg.stream = sb::as_stream(graph.stream);
   cudaLaunchAttribute attr[1];
@@ -136,7 +140,7 @@ void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &com
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = graph.pdl ? 1 : 0;
   if (cudaLaunchKernelEx(&cfg, sb::step_end_kernel, static_cast<const uint32_t *>(results.as<uint32_t>()), committed.as<uint32_t>(),
-                         pendingRows.as<uint32_t>(), advance ? 1u : 0u) != cudaSuccess)
+                         pendingRows.as<uint32_t>(), advance ? 1u : 0u, sb::tp_epoch_word(tpGroup), exchanges) != cudaSuccess)
     throw BackendError(SB_ERR_CUDA, "step_end launch failed");
   ++graph.launches;
 }
@@ -198,6 +202,27 @@ int sb_target_destroy(void *target) {
   return SB_OK;
 }
 
+int sb_target_tp_export(void *target, void *handle_out) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target && handle_out, "sb_target_tp_export: null pointer");
+  auto *tp = static_cast<Target *>(target)->model->tensorParallel();
+  SB_REQUIRE(tp, "sb_target_tp_export: the target was created without tensor parallelism");
+  return guarded([&] { return tp->exportHandle(handle_out), int(SB_OK); });
+}
+
+int sb_target_tp_connect(void *target, const void *handles) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target && handles, "sb_target_tp_connect: null pointer");
+  auto *tp = static_cast<Target *>(target)->model->tensorParallel();
+  SB_REQUIRE(tp, "sb_target_tp_connect: the target was created without tensor parallelism");
+  return guarded([&] { return tp->connect(handles), int(SB_OK); });
+}
+
+int sb_target_share(const SbTargetConfig *config, SbTargetShare *out_share) {
+  SB_REQUIRE(config && out_share, "sb_target_share: null pointer");
+  return guarded([&] { return *out_share = splash::b200::model::shareOf(*config), int(SB_OK); });
+}
+
 int sb_target_tensor(void *target, int layer, const char *name, void **out_dev, uint64_t *out_bytes) {
   SB_NEED_DEVICE();
   SB_REQUIRE(target && name && out_dev && out_bytes, "sb_target_tensor: null pointer");
@@ -225,7 +250,7 @@ int sb_target_randomize(void *target, uint64_t seed, uint32_t committed) {
   SB_NEED_DEVICE();
   SB_REQUIRE(target, "sb_target_randomize: null target");
   QwenTarget &m = *static_cast<Target *>(target)->model;
-  const SbTargetConfig &c = m.config();
+  const SbTargetConfig &c = m.local();  // a rank fills its share; tensors every rank holds whole get the same values on every rank
   return guarded([&] {
     uint64_t s = seed * 1000003ull;
     auto next = [&] { return s += 0x632BE59BD9B4E019ull; };
@@ -267,7 +292,7 @@ int sb_target_randomize(void *target, uint64_t seed, uint32_t committed) {
     seg.outputSize = c.vocab, seg.inputSize = c.hidden, seg.format = c.fmt_embed;
     SB_TRY(fill_rows(seg, next()));
     m.find(-1, "output", seg.rows);
-    seg.format = c.fmt_head;
+    seg.format = c.fmt_head, seg.outputSize = m.share().vocab;
     SB_TRY(fill_rows(seg, next()));
 #undef SB_TRY
     SB_CUDA(cudaDeviceSynchronize());

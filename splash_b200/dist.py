@@ -1,6 +1,7 @@
-"""Rendezvous, barrier and max-over-ranks for multi-GPU runs of independent lanes (one process per GPU).
-The verify step of one lane exchanges nothing between GPUs; ranks only agree on when the timed region starts
-and on its longest duration. torch.distributed is plumbing here (nccl on GPUs, gloo in CPU tests)."""
+"""Rendezvous, barrier and max-over-ranks for multi-GPU runs (one process per GPU). Tensor-parallel ranks exchange
+inside the kernels, through each other's memory (splash_b200.tp); here the ranks only pass each other the handles of
+that memory, agree on when the timed region starts and on its longest duration. Independent replicas exchange
+nothing. torch.distributed is plumbing (nccl on GPUs, gloo in CPU tests)."""
 import os
 
 
@@ -38,6 +39,22 @@ class Group:
         v = torch.tensor([float(value)], device=self.device, dtype=torch.float64)
         self.dist.all_reduce(v, op=self.dist.ReduceOp.MAX)
         return float(v.item())
+
+    def reduce_sum(self, value):
+        if self.dist is None:
+            return float(value)
+        import torch
+        v = torch.tensor([float(value)], device=self.device, dtype=torch.float64)
+        self.dist.all_reduce(v, op=self.dist.ReduceOp.SUM)
+        return float(v.item())
+
+    def all_gather_bytes(self, mine):
+        """Every rank's `mine` (bytes), in rank order: the host transport of splash_b200.tp.connect."""
+        if self.dist is None:
+            return [bytes(mine)]
+        out = [None] * self.world
+        self.dist.all_gather_object(out, bytes(mine))
+        return out
 
     def aggregate_rate(self, units_per_rank, seconds):
         """Whole-job throughput: all ranks' units over the slowest rank's time."""

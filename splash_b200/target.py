@@ -15,7 +15,7 @@ class SbTargetConfig(ctypes.Structure):
                 ("gdn_key_heads", _U), ("gdn_value_heads", _U), ("attention_interval", _U),
                 ("page_tokens", _U), ("kv_scale_f16", _U), ("max_context", _U),
                 ("fmt_proj", _U), ("fmt_down", _U), ("fmt_head", _U), ("fmt_embed", _U),
-                ("gated_attention", _U), ("tiled_heads", _U)]
+                ("gated_attention", _U), ("tiled_heads", _U), ("tp_world", _U), ("tp_rank", _U)]
 
 
 # The benchmark configurations' shapes (weights are synthetic; see quant fixtures and sb_target_randomize).

@@ -67,6 +67,25 @@ def make_state(cfg, committed, seed=1):
     return s
 
 
+def upload(t, w, s, cut=lambda layer, name, array: array):
+    """Uploads weights `w` and state `s` into the device target `t`; `cut` takes a rank's share of each array."""
+    for (layer, name), arr in w.items():
+        t.upload(layer, name, cut(layer, name, arr))
+    for key, val in s.items():
+        if not isinstance(key, tuple):
+            continue
+        layer, name = key
+        if name == "kv":
+            for tn, arr in (("kv_k", val.k), ("kv_v", val.v), ("kv_ks", val.ks), ("kv_vs", val.vs)):
+                t.upload(layer, tn, cut(layer, tn, arr))
+        elif name.startswith("tape"):
+            i = name[-1]
+            for f, tn in (("inputs", "tape_inputs"), ("k", "tape_k"), ("v", "tape_v"), ("beta", "tape_beta"), ("decay", "tape_decay")):
+                t.upload(layer, tn + i, cut(layer, tn + i, val[f]))
+        else:
+            t.upload(layer, name, cut(layer, name, val))
+
+
 def linear(o, fmt, W, n, k, X, rows, epilogue=0, aux=None, out_f32=False, W2=None):
     out = np.zeros((rows, n), np.float32 if out_f32 else np.uint16)
     Wfull = W if W2 is None else np.concatenate([W, W2], axis=0)

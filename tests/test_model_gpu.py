@@ -18,20 +18,7 @@ def build(seed=0, committed=2048):
     t = target.Target(**cfg)
     w = mo.make_weights(cfg, seed)
     s = mo.make_state(cfg, committed, seed + 1)
-    for (layer, name), arr in w.items():
-        t.upload(layer, name, arr)
-    for key, val in s.items():
-        if isinstance(key, tuple):
-            layer, name = key
-            if name == "kv":
-                t.upload(layer, "kv_k", val.k), t.upload(layer, "kv_v", val.v)
-                t.upload(layer, "kv_ks", val.ks), t.upload(layer, "kv_vs", val.vs)
-            elif name.startswith("tape"):
-                i = name[-1]
-                for f, tn in (("inputs", "tape_inputs"), ("k", "tape_k"), ("v", "tape_v"), ("beta", "tape_beta"), ("decay", "tape_decay")):
-                    t.upload(layer, tn + i, val[f])
-            else:
-                t.upload(layer, name, val)
+    mo.upload(t, w, s)
     t.reset(committed)
     return lib, target, t, cfg, w, s
 

@@ -1,0 +1,97 @@
+"""Tensor-parallel verify steps of the tiny hybrid configuration on two GPUs, one process per GPU: each rank holds its
+share of the same seeded model (splash_b200.tp.shard), the ranks exchange through each other's memory, and the
+results are held against the CPU oracle's whole-model step and against each other (every rank must hold the same
+logits bit for bit). Needs two GPUs; skipped otherwise."""
+import ctypes
+import multiprocessing as mp
+
+import numpy as np
+import pytest
+
+import model_oracle as mo
+
+pytestmark = pytest.mark.gpu
+COMMITTED = 2048
+
+
+def _worker(rank, world, barrier, handles, results, step_tokens):
+    try:
+        from splash_b200 import lib, target, tp
+        lib.init(rank)
+        cfg = dict(target.TINY)
+        t = target.Target(**cfg, tp_world=world, tp_rank=rank)
+        sh = tp.share(cfg, world, rank)
+        w, s = mo.make_weights(cfg, 0), mo.make_state(cfg, COMMITTED, 1)
+        mo.upload(t, w, s, cut=lambda layer, name, arr: tp.shard(cfg, sh, layer, name, arr))
+        t.reset(COMMITTED)
+
+        def all_gather(mine):
+            ctypes.memmove(ctypes.addressof(handles) + rank * tp.HANDLE_BYTES, mine, tp.HANDLE_BYTES)
+            barrier.wait(timeout=120)
+            return [bytes(handles[i * tp.HANDLE_BYTES:(i + 1) * tp.HANDLE_BYTES]) for i in range(world)]
+
+        tp.connect(t, all_gather)
+        for step, tokens in enumerate(step_tokens):
+            barrier.wait(timeout=120)
+            got = t.verify(tokens, flags=target.ADVANCE | target.GRAPH)
+            logits = t.download(-1, "logits", np.float32, (16, cfg["vocab"]))
+            results.put((rank, step, got, lib.device_status(), logits))
+        barrier.wait(timeout=120)  # nobody unmaps its window while a peer may still write to it
+        t.close()
+    except Exception as e:  # the parent turns this into a failure instead of waiting for a result
+        results.put((rank, -1, repr(e), 1, None))
+        try:
+            barrier.abort()
+        except Exception:
+            pass
+
+
+def test_two_ranks_match_the_whole_model_oracle():
+    from splash_b200 import lib, target
+    if lib.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world, steps = 2, 3
+    cfg = dict(target.TINY)
+    w, s = mo.make_weights(cfg, 0), mo.make_state(cfg, COMMITTED, 1)
+    step_tokens, wants, token = [], [], 17
+    for step in range(steps):
+        tokens = mo.draft_chain(cfg, w, s, token, rows=16, seed=step)
+        want = mo.verify_step(cfg, w, s, tokens, advance=True)
+        step_tokens.append(tokens), wants.append(want)
+        token = int(want["tokens"][-1])
+    ctx = mp.get_context("spawn")
+    barrier, results = ctx.Barrier(world), ctx.Queue()
+    handles = ctx.RawArray(ctypes.c_ubyte, world * 64)
+    procs = [ctx.Process(target=_worker, args=(r, world, barrier, handles, results, step_tokens)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {}
+    try:
+        for _ in range(world * steps):
+            rank, step, out, status, logits = results.get(timeout=600)
+            assert step >= 0, f"rank {rank} failed: {out}"
+            assert status == 0, f"rank {rank} step {step}: device status {status}"
+            got[rank, step] = (out, logits)
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
+    compared = 0
+    for step in range(steps):
+        (out0, logits0), (out1, logits1) = got[0, step], got[1, step]
+        assert np.array_equal(logits0, logits1), "the ranks hold different logits"
+        assert out0[1:] == out1[1:] and np.array_equal(out0[0], out1[0])
+        want = wants[step]
+        scale = np.abs(want["logits"]).max()
+        assert np.abs(logits0 - want["logits"]).max() <= 2e-2 * scale
+        assert np.median(np.abs(logits0 - want["logits"])) <= 2e-3 * scale
+        top2 = np.sort(want["logits"], axis=1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 1e-2
+        if not clear[:want["retained"]].all():
+            break  # the oracle's own choice was a near tie: later steps start from another position
+        tokens, retained, accepted, mask = out0
+        assert retained == want["retained"] and accepted == want["accepted"] and mask == want["mask"]
+        assert np.array_equal(tokens, want["tokens"])
+        compared += 1
+    assert compared >= 1
