@@ -45,7 +45,7 @@ class TensorParallel {
     check(sb_tp_prepare_sum(graph.stream, group_, index, partials.as<float>(), slices, partialStride, residual.as(), inputStride, sum.as(),
                             inputStride, rows, inputSize, normWeight ? normWeight->as() : nullptr, format, scratch.as(),
                             normedOutput ? normedOutput->as() : nullptr, graph.pdl ? SB_LINEAR_PDL : 0));
-    ++graph.launches;
+    graph.launches += 2;  // the share's push to the peers, and the conversion
     return {scratch, format == SB_FMT_Q4K ? uint32_t(SB_FMT_Q4K) : uint32_t(SB_FMT_Q6K), inputSize};
   }
 

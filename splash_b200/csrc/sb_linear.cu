@@ -154,6 +154,53 @@ __device__ __forceinline__ void block_reduce2(float &s, float &m, float *scratch
   }
 }
 
+// Where chunk c (8 values = 4 units) of a row starts in an inbox matrix: a warp's 32 chunks are 128 units in a row, and
+// unit u of lane l sits at 32 u + l of them, so each of the warp's four stores (and loads) covers 512 consecutive bytes.
+__device__ __forceinline__ size_t tp_unit(size_t matrix, uint32_t tok, uint32_t width, uint32_t c, uint32_t lane) {
+  return ((matrix * kTokens + tok) * width + 8 * (c - lane)) / 2 + lane;
+}
+
+// This rank's share of a sum (its k-slices added in order) into every peer's inbox; the same grid and the same
+// thread-to-element map as prepare_kernel, which adds what arrives (sb_tp_internal.cuh).
+__global__ void __launch_bounds__(kPrepThreads) tp_push_kernel(const PrepareParams p) {
+  const uint32_t tok = blockIdx.x / kPrepCluster, rank = blockIdx.x % kPrepCluster, tid = threadIdx.x, lane = tid & 31;
+  const uint32_t nsb = p.k / 256, c0 = rank * nsb / kPrepCluster * 32, chunks = (rank + 1) * nsb / kPrepCluster * 32;
+  const TpExchange &x = p.tp;
+  pdl_launch_dependents();
+  pdl_wait();  // the projection that wrote the slices has completed
+  const uint32_t epoch = tp_epoch(x);
+  if (blockIdx.x == 0 && tid == 0) st_release_gpu(x.ready, epoch);
+  if (tok >= p.rows) return;
+  const size_t slot = size_t(epoch & 1u) * x.world;
+#pragma unroll
+  for (int i = 0; i < kPrepMaxChunks; ++i) {
+    const uint32_t c = c0 + tid + kPrepThreads * i;
+    if (c >= chunks) continue;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (uint32_t s0 = 0; s0 < p.partial_slices; s0 += 8) {  // the order and grouping of prepare_kernel's own sum
+      float4 a4[8], b4[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t sl = min(s0 + j, p.partial_slices - 1);
+        const float4 *pp = reinterpret_cast<const float4 *>(p.partials + (size_t(sl) * kTokens + tok) * p.partial_stride + 8 * c);
+        a4[j] = __ldcg(pp), b4[j] = __ldcg(pp + 1);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (s0 + j < p.partial_slices)
+          acc[0] += a4[j].x, acc[1] += a4[j].y, acc[2] += a4[j].z, acc[3] += a4[j].w, acc[4] += b4[j].x, acc[5] += b4[j].y, acc[6] += b4[j].z,
+              acc[7] += b4[j].w;
+    }
+    const size_t unit = tp_unit(slot + x.rank, tok, x.width, c, lane);
+    for (uint32_t peer = 0; peer < x.world; ++peer) {
+      if (peer == x.rank) continue;
+      uint4 *dst = reinterpret_cast<uint4 *>(x.data[peer]) + unit;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) tp_store_unit(dst + 32 * u, acc[2 * u], acc[2 * u + 1], epoch);
+    }
+  }
+}
+
 template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PrepareParams p) {
   __shared__ float scratch[2 * (kPrepThreads / 32)];
   __shared__ float cluster_part[2];  // this CTA's sum of squares and maximum, read by the row's other CTAs
@@ -178,7 +225,16 @@ template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kerne
       wn[i][4] = w1.x, wn[i][5] = w1.y, wn[i][6] = w1.z, wn[i][7] = w1.w;
     }
   }
-  pdl_wait();
+  // The conversion of an exchange does not wait for the kernel before it (the push kernel, whose completion includes
+  // the flush of its stores to the peers) but for that kernel's word that the slices' sums are complete.
+  uint32_t epoch = 0;
+  bool healthy = true;
+  if (TP) {
+    epoch = tp_epoch(p.tp), healthy = tp_healthy(p.tp);
+    if (healthy) healthy = tp_wait_ready(p.tp, epoch);
+  } else {
+    pdl_wait();
+  }
   float v[kPrepMaxChunks][8];
   float acc[kPrepMaxChunks][8];
   const uint16_t *row = p.x + size_t(tok) * p.x_stride;
@@ -214,37 +270,40 @@ template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kerne
     }
   }
   if (TP && live) {
-    // This rank's share goes into every peer's inbox; the peers' shares arrive in this rank's. The sum over the
-    // ranks runs in rank order on every rank, so all ranks hold the same bits afterwards.
+    // The peers' shares arrive in this rank's inbox (tp_push_kernel on their side). The sum over the ranks runs in
+    // rank order on every rank, so all ranks hold the same bits afterwards.
     const TpExchange &x = p.tp;
-    const uint32_t epoch = tp_epoch(x);
-    const bool healthy = tp_healthy(x);
     const size_t slot = size_t(epoch & 1u) * x.world;
-#pragma unroll
-    for (int i = 0; i < kPrepMaxChunks; ++i) {
-      const uint32_t c = c0 + tid + kPrepThreads * i;
-      if (c >= chunks) continue;
-      const size_t at = ((slot + x.rank) * kTokens + tok) * x.width + 8 * c;
-      const float4 lo = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]), hi = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
-      for (uint32_t peer = 0; peer < x.world; ++peer) {
-        if (peer == x.rank) continue;
-        float4 *dst = reinterpret_cast<float4 *>(x.data[peer] + at);
-        dst[0] = lo, dst[1] = hi;
-      }
-    }
-    tp_signal_and_wait(x, epoch, blockIdx.x, gridDim.x, healthy);
+    const uint64_t t0 = global_timer_ns();
+    bool expired = !healthy;
 #pragma unroll
     for (int i = 0; i < kPrepMaxChunks; ++i) {
       const uint32_t c = c0 + tid + kPrepThreads * i;
       if (c >= chunks) continue;
       float total[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
       for (uint32_t src = 0; src < x.world; ++src) {
-        float4 lo = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]), hi = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
-        if (src != x.rank) {
-          const float4 *from = reinterpret_cast<const float4 *>(x.data[x.rank] + ((slot + src) * kTokens + tok) * x.width + 8 * c);
-          lo = __ldcg(from), hi = __ldcg(from + 1);
+        if (src == x.rank) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) total[j] += acc[i][j];
+          continue;
         }
-        total[0] += lo.x, total[1] += lo.y, total[2] += lo.z, total[3] += lo.w, total[4] += hi.x, total[5] += hi.y, total[6] += hi.z, total[7] += hi.w;
+        const uint4 *from = reinterpret_cast<const uint4 *>(x.data[x.rank]) + tp_unit(slot + src, tok, x.width, c, lane);
+        uint4 got[4];
+        for (uint32_t polls = 1;; ++polls) {
+          bool all = true;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            got[u] = tp_load_unit(from + 32 * u);
+            all = all && got[u].y == epoch && got[u].w == epoch;
+          }
+          if (all || expired) break;
+          if ((polls & 63u) == 0 && (global_timer_ns() - t0 > kTpWaitNs || polls >= (1u << 30))) {
+            atomicCAS(x.status, uint32_t(SB_DEV_OK), uint32_t(SB_DEV_WAIT_EXPIRED));
+            expired = true;
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) total[2 * u] += __uint_as_float(got[u].x), total[2 * u + 1] += __uint_as_float(got[u].z);
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[i][j] = total[j];
@@ -1037,7 +1096,15 @@ static int launch_prepare(cudaStream_t stream, const void *x, uint32_t rows, uin
   PrepareParams pp{static_cast<const uint16_t *>(x), static_cast<const float *>(norm_w), static_cast<uint8_t *>(out),
                    static_cast<uint16_t *>(normed_out), rows, k, x_stride, layout, partials, static_cast<uint16_t *>(sum_out), slices,
                    partial_stride, sum_stride, tp ? *tp : TpExchange{}};
-  static_assert(kTokens * kPrepCluster == kTpConvertCtas, "the exchange's flag words are laid out for this grid");
+  if (tp) {  // the share's way to the peers, ahead of the conversion and not waited for by it
+    cudaLaunchConfig_t push = {};
+    push.gridDim = dim3(kTokens * kPrepCluster), push.blockDim = dim3(kPrepThreads), push.stream = stream;
+    cudaLaunchAttribute pattr[1];
+    pattr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    pattr[0].val.programmaticStreamSerializationAllowed = 1;
+    push.attrs = pattr, push.numAttrs = pdl ? 1 : 0;
+    SB_CUDA(cudaLaunchKernelEx(&push, tp_push_kernel, pp));
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(kTokens * kPrepCluster);
   cfg.blockDim = dim3(kPrepThreads);

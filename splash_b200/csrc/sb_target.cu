@@ -25,16 +25,21 @@ __global__ void step_begin_kernel(const uint32_t *committed, uint2 *tree, uint32
 // The lane's commit: the retained rows become history; the next step folds them into the GDN state.
 __global__ void step_end_kernel(const uint32_t *results, uint32_t *committed, uint32_t *pending_rows, uint32_t advance, uint32_t *tp_epoch,
                                 uint32_t tp_exchanges) {
-  pdl_launch_dependents();
   pdl_wait();
-  if (threadIdx.x != 0) return;
-  if (tp_epoch) *tp_epoch += tp_exchanges;  // the next step's exchanges are numbered after this step's
-  if (advance) {
-    *committed += results[0];
-    *pending_rows = results[0];
-  } else {
-    *pending_rows = 0;
+  if (threadIdx.x == 0) {
+    // The next step's exchanges are numbered after this step's. Their kernels read the count when they start, and
+    // kernels may start before the ones ahead of them complete: dependents are let go only after the count has moved.
+    if (tp_epoch) *tp_epoch += tp_exchanges;
+    if (advance) {
+      *committed += results[0];
+      *pending_rows = results[0];
+    } else {
+      *pending_rows = 0;
+    }
+    __threadfence();
   }
+  __syncthreads();
+  pdl_launch_dependents();
 }
 
 // ---- seeded synthetic data ----

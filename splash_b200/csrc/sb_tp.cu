@@ -14,9 +14,9 @@ namespace sb {
 struct TpGroup {
   uint32_t world = 0, rank = 0, width = 0, gather_width = 0;
   uint8_t *window = nullptr;  // this rank's
-  size_t window_bytes = 0, inbox_off = 0, flags_a_off = 0, flags_b_off = 0, gather_off = 0;
+  size_t window_bytes = 0, inbox_off = 0, flags_off = 0, gather_off = 0;
   uint8_t *peer[kTpMaxWorld] = {};  // every rank's window as mapped here (peer[rank] == window)
-  uint32_t *epoch = nullptr;
+  uint32_t *epoch = nullptr;  // two words: the exchange count, and `ready`
   bool connected = false;
 };
 
@@ -27,10 +27,10 @@ int tp_exchange(void *group, uint32_t index, bool gather, TpExchange &out) {
   if (!g || !g->connected) return fail(SB_ERR_INVALID, "tensor-parallel group is not connected (sb_tp_connect)");
   out = TpExchange{};
   out.world = g->world, out.rank = g->rank, out.index = index, out.width = gather ? g->gather_width : g->width;
-  out.epoch_base = g->epoch, out.status = ctx().status_dev;
+  out.epoch_base = g->epoch, out.ready = g->epoch + 1, out.status = ctx().status_dev;
   for (uint32_t p = 0; p < g->world; ++p) {
     out.data[p] = reinterpret_cast<float *>(g->peer[p] + (gather ? g->gather_off : g->inbox_off));
-    out.flags[p] = reinterpret_cast<uint32_t *>(g->peer[p] + (gather ? g->flags_b_off : g->flags_a_off));
+    out.flags[p] = reinterpret_cast<uint32_t *>(g->peer[p] + g->flags_off);
   }
   return SB_OK;
 }
@@ -54,10 +54,16 @@ __global__ void __launch_bounds__(256) tp_gather_kernel(const TpExchange x, uint
   tp_signal_and_wait(x, epoch, blockIdx.x, gridDim.x, healthy);
 }
 
+// Later kernels may start before the kernels ahead of them complete, and the exchanges' kernels read the count
+// when they start: so this kernel lets its dependents start only after the count has moved.
 __global__ void tp_advance_kernel(uint32_t *epoch, uint32_t exchanges) {
-  pdl_launch_dependents();
   pdl_wait();
-  if (threadIdx.x == 0) *epoch += exchanges;
+  if (threadIdx.x == 0) {
+    *epoch += exchanges;
+    __threadfence();
+  }
+  __syncthreads();
+  pdl_launch_dependents();
 }
 
 }  // namespace sb
@@ -75,14 +81,13 @@ int sb_tp_create(uint32_t world, uint32_t rank, uint32_t width, uint32_t gather_
   TpGroup *g = new TpGroup;
   g->world = world, g->rank = rank, g->width = width, g->gather_width = gather_width;
   g->inbox_off = 0;
-  g->flags_a_off = align_up(size_t(2) * world * 16 * width * 4, 256);
-  g->flags_b_off = g->flags_a_off + align_up(size_t(world) * kTpConvertCtas * 4, 256);
-  g->gather_off = g->flags_b_off + align_up(size_t(world) * kTpGatherCtas * 4, 256);
+  g->flags_off = align_up(size_t(2) * world * 16 * width * 8, 256);  // units of 16 bytes hold two values
+  g->gather_off = g->flags_off + align_up(size_t(world) * kTpGatherCtas * 4, 256);
   g->window_bytes = g->gather_off + align_up(size_t(16) * gather_width * 4, 256) + 256;
   cudaError_t e = cudaMalloc(&g->window, g->window_bytes);
-  if (e == cudaSuccess) e = cudaMalloc(&g->epoch, 4);
+  if (e == cudaSuccess) e = cudaMalloc(&g->epoch, 8);
   if (e == cudaSuccess) e = cudaMemset(g->window, 0, g->window_bytes);
-  if (e == cudaSuccess) e = cudaMemset(g->epoch, 0, 4);
+  if (e == cudaSuccess) e = cudaMemset(g->epoch, 0, 8);
   if (e == cudaSuccess) e = cudaDeviceSynchronize();
   if (e != cudaSuccess) {
     cudaFree(g->window), cudaFree(g->epoch);

@@ -116,3 +116,43 @@ def connect(t, all_gather):
     assert all(len(h) == HANDLE_BYTES for h in handles)
     blob = b"".join(handles)
     lib.check(l.sb_target_tp_connect(t.handle, blob))
+
+
+class Group:
+    """One rank's end of the node's exchange at operator level (sb_tp_* of include/splash_b200.h)."""
+
+    def __init__(self, world, rank, width, gather_width, all_gather):
+        P, U = ctypes.c_void_p, _U
+        l = self.l = lib.load()
+        l.sb_tp_create.argtypes = [U, U, U, U, ctypes.POINTER(P)]
+        l.sb_tp_destroy.argtypes = [P]
+        l.sb_tp_export.argtypes = [P, P]
+        l.sb_tp_connect.argtypes = [P, P]
+        l.sb_tp_gather_matrix.argtypes = [P, ctypes.POINTER(P), ctypes.POINTER(ctypes.c_uint64)]
+        l.sb_tp_prepare_sum.argtypes = [P, P, U, P, U, U, P, U, P, U, U, U, P, U, P, P, U]
+        l.sb_tp_all_gather.argtypes = [P, P, U, U, U, U]
+        l.sb_tp_advance.argtypes = [P, P, U]
+        h = P()
+        lib.check(l.sb_tp_create(world, rank, width, gather_width, ctypes.byref(h)))
+        self.handle, self.world, self.rank = h.value, world, rank
+        mine = ctypes.create_string_buffer(HANDLE_BYTES)
+        lib.check(l.sb_tp_export(self.handle, mine))
+        lib.check(l.sb_tp_connect(self.handle, b"".join(all_gather(mine.raw))))
+        p, n = P(), ctypes.c_uint64()
+        lib.check(l.sb_tp_gather_matrix(self.handle, ctypes.byref(p), ctypes.byref(n)))
+        self.gather_ptr, self.gather_bytes = p.value, n.value
+
+    def prepare_sum(self, stream, index, partials, slices, partial_stride, residual, sum_out, rows, k, norm_weight, fmt, prepared, flags=0):
+        lib.check(self.l.sb_tp_prepare_sum(stream, self.handle, index, partials, slices, partial_stride, residual, k, sum_out, k, rows, k,
+                                           norm_weight, fmt, prepared, None, flags))
+
+    def all_gather(self, stream, index, rows, column0, columns):
+        lib.check(self.l.sb_tp_all_gather(stream, self.handle, index, rows, column0, columns))
+
+    def advance(self, stream, exchanges):
+        lib.check(self.l.sb_tp_advance(stream, self.handle, exchanges))
+
+    def close(self):
+        if self.handle:
+            self.l.sb_tp_destroy(self.handle)
+            self.handle = None

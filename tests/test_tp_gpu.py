@@ -1,7 +1,7 @@
-"""Tensor-parallel verify steps of the tiny hybrid configuration on two GPUs, one process per GPU: each rank holds its
+"""Tensor-parallel verify steps of the tiny hybrid configuration on two and on four GPUs, one process per GPU: each rank holds its
 share of the same seeded model (splash_b200.tp.shard), the ranks exchange through each other's memory, and the
 results are held against the CPU oracle's whole-model step and against each other (every rank must hold the same
-logits bit for bit). Needs two GPUs; skipped otherwise."""
+logits bit for bit). Skipped where the machine has fewer GPUs."""
 import ctypes
 import multiprocessing as mp
 
@@ -46,11 +46,14 @@ def _worker(rank, world, barrier, handles, results, step_tokens):
             pass
 
 
-def test_two_ranks_match_the_whole_model_oracle():
+@pytest.mark.parametrize("world", [2, 4])
+def test_ranks_match_the_whole_model_oracle(world):
+    """Two ranks: every rank its own KV head. Four ranks: each KV head and its pages are held by two ranks, and the
+    11 super-blocks of the intermediate width fall 3, 3, 3, 2."""
     from splash_b200 import lib, target
-    if lib.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    world, steps = 2, 3
+    if lib.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    steps = 3
     cfg = dict(target.TINY)
     w, s = mo.make_weights(cfg, 0), mo.make_state(cfg, COMMITTED, 1)
     step_tokens, wants, token = [], [], 17
@@ -79,9 +82,11 @@ def test_two_ranks_match_the_whole_model_oracle():
                 p.kill()
     compared = 0
     for step in range(steps):
-        (out0, logits0), (out1, logits1) = got[0, step], got[1, step]
-        assert np.array_equal(logits0, logits1), "the ranks hold different logits"
-        assert out0[1:] == out1[1:] and np.array_equal(out0[0], out1[0])
+        out0, logits0 = got[0, step]
+        for r in range(1, world):
+            out1, logits1 = got[r, step]
+            assert np.array_equal(logits0, logits1), "the ranks hold different logits"
+            assert out0[1:] == out1[1:] and np.array_equal(out0[0], out1[0])
         want = wants[step]
         scale = np.abs(want["logits"]).max()
         assert np.abs(logits0 - want["logits"]).max() <= 2e-2 * scale
