@@ -144,19 +144,40 @@ def main():
     lib.init(local)
     cfg = dict(target.TINY if args.tiny else target.QWEN27B)
     context = 2048 if args.tiny else CONTEXT
+    stream = lib.stream_create()
     tensor_parallel = world > 1 and args.parallel == "tp"
+    fell_back = None
     if tensor_parallel:
         # every rank its share of the same model: same seed (tensors held whole must agree), same input tokens
         from splash_b200 import tp
         t = target.Target(**cfg, tp_world=world, tp_rank=rank)
         t.randomize(1234, context)
-        tp.connect(t, group.all_gather_bytes)
-        group.barrier()
-    else:
+        try:
+            tp.connect(t, group.all_gather_bytes)
+            bad = 0
+        except lib.SbError as e:  # no peer mapping on this machine
+            bad, fell_back = 1, f"tensor-parallel windows could not be mapped ({e}); measured as independent lanes"
+        bad = int(group.reduce_max(bad))
+        if not bad:
+            t.upload(-1, "tokens", np.random.default_rng(0).integers(0, cfg["vocab"], ROWS).astype(np.uint32))
+            group.barrier()
+            # Two steps before anything is timed: an exchange that cannot reach a peer gives up after its bounded wait
+            # and says so in the device status word. The run then measures independent lanes and reports why.
+            for _ in range(2):
+                t.step(ROWS, 0.0, target.GRAPH, stream)
+            lib.stream_sync(stream)
+            bad = int(group.reduce_max(lib.device_status()))
+            if bad:
+                fell_back = f"tensor-parallel exchange failed on this machine (device status {bad}); measured as independent lanes"
+        if bad:
+            fell_back = fell_back or "tensor parallelism failed on another rank; measured as independent lanes"
+            group.barrier()
+            t.close()
+            tensor_parallel = False
+    if not tensor_parallel:
         t = target.Target(**cfg)
         t.randomize(1234 + rank, context)
     lanes = 1 if tensor_parallel else world
-    stream = lib.stream_create()
     warm = max(args.warmup, 3)
     flags = target.GRAPH  # hold the lane at 32K: every step does the same work
     rng = np.random.default_rng(0 if tensor_parallel else rank)
@@ -260,7 +281,7 @@ def main():
         "metric": "verify_tokens_per_s", "value": lanes * ROWS / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if tensor_parallel else "weak", "vs_baseline": None,
         "dtype": "f16 operands (exact integer codes), f32 accumulate, bf16 activations", "data": "synthetic",
-        "config": {"workload": workload, "context_tokens": context, "block": ROWS, "parallelism": "tp1" if world == 1 else (f"tp{world}: one lane, shares exchanged through peer memory over NVLink in the input conversions" if tensor_parallel else f"{world} independent replicas (lanes)"),
+        "config": {"workload": workload, "context_tokens": context, "block": ROWS, "parallelism": "tp1" if world == 1 else (f"tp{world}: one lane, shares exchanged through peer memory over NVLink in the input conversions" if tensor_parallel else f"{world} independent replicas (lanes)" + (f"; {fell_back}" if fell_back else "")),
                    "l2": "inputs exceed L2: one step streams %.1f GB of weights" % (stats["weight_bytes"] / 1e9), "cuda_graph": True, "pdl": True},
         "e2e": {"value": lanes * ROWS / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": ROWS * 4, "d2h_bytes_per_step": 16 + ROWS * 4},
         "gpu_launches": stats["launches"] * args.steps,

@@ -4,6 +4,8 @@ summaries under profiles/ were captured from, and a quick way to time one kernel
     python -m splash_b200.cases linear --fmt q4k --n 17408 --k 5120 --epilogue gate_up [--iters 20]
     python -m splash_b200.cases attention --context 32768 [--q-heads 24 --kv-heads 4 --head-dim 256]
     python -m splash_b200.cases gdn [--key-heads 16 --value-heads 48]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 -m splash_b200.cases exchange
+        (one rank per GPU: the tensor-parallel input conversion against the local one, replayed as CUDA graphs)
 
 Weights are random native blocks with scale fields in the ranges the tests use (Q4_K / Q8_0 d, dmin in
 U(5e-4, 4e-3); Q6_K d in U(2e-5, 1e-4)); several copies rotate so every launch streams from HBM, not L2."""
@@ -143,6 +145,58 @@ def case_gdn(a):
           f"{algo / us / 1e3:.0f} GB/s of {algo} state bytes, device status {lib.device_status()}")
 
 
+def case_exchange(a):
+    """sb_tp_prepare_sum (push + conversion with the peers' shares) against sb_linear_prepare_sum, `launches` calls
+    captured into one CUDA graph and replayed, so the host's launch rate does not enter."""
+    from . import tp
+    from .dist import Group
+    d = Group("nccl")
+    lib.init(d.local)
+    l = lib.load()
+    H, S, N = a.width, a.slices, a.launches
+    g = tp.Group(d.world, d.rank, H, 1024, d.all_gather_bytes)
+    P, U = ctypes.c_void_p, ctypes.c_uint32
+    l.sb_linear_prepare_sum.argtypes = [P, P, U, U, P, U, P, U, U, U, P, U, P, P, U]
+    rng = np.random.default_rng(d.rank)
+    part = lib.DeviceBuffer.from_numpy(rng.standard_normal((S, 16, H)).astype(np.float32))
+    res = lib.DeviceBuffer.from_numpy(np.zeros((16, H), np.uint16))
+    out = lib.DeviceBuffer(16 * H * 2 + 256)
+    norm = lib.DeviceBuffer.from_numpy(np.ones(H, np.float32))
+    prep = lib.DeviceBuffer(int(l.sb_linear_prepared_bytes(H)))
+    st = lib.stream_create()
+    flags = lib.LINEAR_PDL if a.pdl else 0
+    for mode in ("local", "exchange"):
+        lib.check(l.sb_graph_begin(st))
+        for i in range(N):
+            if mode == "exchange":
+                g.prepare_sum(st, i, part.ptr, S, H, res.ptr, out.ptr, 16, H, norm.ptr, lib.FMT_Q4K, prep.ptr, flags)
+            else:
+                lib.check(l.sb_linear_prepare_sum(st, part.ptr, S, H, res.ptr, H, out.ptr, H, 16, H, norm.ptr, lib.FMT_Q4K, prep.ptr, None, flags))
+        if mode == "exchange":
+            g.advance(st, N)
+        graph = P()
+        lib.check(l.sb_graph_end(st, ctypes.byref(graph)))
+        for _ in range(3):
+            lib.check(l.sb_graph_launch(graph, st))
+        lib.stream_sync(st)
+        d.barrier()
+        e0, e1 = lib.Event(), lib.Event()
+        e0.record(st)
+        for _ in range(a.iters):
+            lib.check(l.sb_graph_launch(graph, st))
+        e1.record(st)
+        e1.sync()
+        us = d.reduce_max(e0.elapsed_ms(e1)) / N / a.iters * 1e3
+        status = lib.device_status()
+        d.barrier()
+        if d.rank == 0:
+            print(f"{mode} conversion, width {H}, {S} slices, {d.world} ranks, pdl={int(a.pdl)}: {us:.2f} us per exchange (max over ranks), "
+                  f"device status {status}", flush=True)
+    d.barrier()
+    g.close()
+    d.close()
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="python -m splash_b200.cases")
     sub = ap.add_subparsers(dest="case", required=True)
@@ -173,7 +227,15 @@ def main(argv=None):
     p.add_argument("--pending", type=int, default=8)
     p.add_argument("--fused-gates", type=int, default=0, help="k of the fused alpha / beta projection (0: b and a given)")
     p.add_argument("--iters", type=int, default=20)
+    p = sub.add_parser("exchange")
+    p.add_argument("--width", type=int, default=5120)
+    p.add_argument("--slices", type=int, default=3)
+    p.add_argument("--launches", type=int, default=200)
+    p.add_argument("--iters", type=int, default=5)
+    p.add_argument("--pdl", action="store_true")
     a = ap.parse_args(argv)
+    if a.case == "exchange":
+        return case_exchange(a)
     lib.init(0)
     {"linear": case_linear, "attention": case_attention, "gdn": case_gdn}[a.case](a)
 
