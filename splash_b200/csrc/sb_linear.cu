@@ -203,13 +203,14 @@ __global__ void __launch_bounds__(kPrepThreads) tp_push_kernel(const PreparePara
 
 template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kernel(const PrepareParams p) {
   __shared__ float scratch[2 * (kPrepThreads / 32)];
-  __shared__ float cluster_part[2];  // this CTA's sum of squares and maximum, read by the row's other CTAs
+  __shared__ float cluster_part[kPrepCluster][2];  // every CTA of the row stores its sum of squares and maximum here
   // A row is shared by the kPrepCluster CTAs of a cluster: CTA `rank` converts whole super-blocks
   // [rank nsb / C, (rank + 1) nsb / C) and the row's statistics meet through distributed shared memory.
   const uint32_t tok = blockIdx.x / kPrepCluster, rank = blockIdx.x % kPrepCluster, tid = threadIdx.x, lane = tid & 31;
   const bool live = tok < p.rows;
   const uint32_t nsb = p.k / 256, c0 = rank * nsb / kPrepCluster * 32, chunks = (rank + 1) * nsb / kPrepCluster * 32;
   pdl_launch_dependents();
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");  // "this CTA runs": waited for before the statistics' exchange
   // The norm weights do not depend on the previous kernel: they are fetched before the dependency wait.
   float wn[kPrepMaxChunks][8];
   if (p.norm_w) {
@@ -334,20 +335,24 @@ template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kerne
     }
   block_reduce2(ss, mx, scratch);
   {
-    // The row's statistics: every CTA publishes its own and reads the others' in rank order.
+    // The row's statistics: every CTA stores its own into all eight CTAs' shared memory, one cluster barrier, then
+    // each adds its local copies in rank order. (The barrier that makes sure every CTA of the cluster runs before
+    // anyone writes into it was arrived at when the kernel started, long before this point.)
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
-    if (tid == 0) cluster_part[0] = ss, cluster_part[1] = mx;
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (tid < kPrepCluster) {
+      float *remote = cluster.map_shared_rank(&cluster_part[0][0], tid);
+      remote[2 * rank] = ss, remote[2 * rank + 1] = mx;
+    }
     cluster.sync();
     float ss_all = 0.0f, mx_all = 0.0f;
 #pragma unroll
     for (int r = 0; r < kPrepCluster; ++r) {
-      const float *remote = cluster.map_shared_rank(cluster_part, r);
-      ss_all += remote[0];
-      mx_all = fmaxf(mx_all, remote[1]);
+      ss_all += cluster_part[r][0];
+      mx_all = fmaxf(mx_all, cluster_part[r][1]);
     }
     ss = ss_all, mx = mx_all;
-    cluster.sync();  // nobody leaves (or rewrites its slot) while a peer may still read it
   }
   if (p.norm_w) {
     const float inv = rsqrtf(ss / float(p.k) + 1e-6f);
