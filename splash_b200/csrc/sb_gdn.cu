@@ -18,6 +18,7 @@
 //   rollback the state after the block is never stored: the caller passes how many tape rows were accepted
 //            (pending_rows, or a device word written by sb_accept) to the next step, which folds them
 #include <algorithm>
+#include <cooperative_groups.h>
 
 #include "sb_internal.h"
 #include "sb_ptx.cuh"
@@ -43,7 +44,9 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-__global__ void __launch_bounds__(kGdnThreads, 2) gdn_kernel(const GdnParams p) {
+// The kGdnSplit CTAs of a value head form a cluster: the fused gate projection is divided among them by rows and
+// meets in every CTA's shared memory.
+__global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads, 2) gdn_kernel(const GdnParams p) {
   const SbGdnArgs &a = p.a;
   __shared__ float q_s[kGdnRows][kD], k_s[kGdnRows][kD], pk_s[kGdnRows][kD];
   __shared__ float v_s[kGdnRows][kGdnVd], pv_s[kGdnRows][kGdnVd], o_s[kGdnRows][kGdnVd];
@@ -53,6 +56,8 @@ __global__ void __launch_bounds__(kGdnThreads, 2) gdn_kernel(const GdnParams p) 
   __shared__ uint2 w_s[2 * kD + kGdnVd];
   __shared__ uint32_t s_last;
   pdl_launch_dependents();
+  const bool fused_gates = a.gate_weight && a.rows > 0;
+  if (fused_gates) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");  // "this CTA runs", waited for before the gates' exchange
   pdl_wait();
   const uint32_t vs = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t KH = a.key_heads, VH = a.value_heads, KW = KH * kD, VW = VH * kD, C = 2 * KW + VW;
@@ -77,21 +82,29 @@ __global__ void __launch_bounds__(kGdnThreads, 2) gdn_kernel(const GdnParams p) 
     const float4 s4 = *reinterpret_cast<const float4 *>(a.state_in + sbase + 32 * c);
     S[4 * c] = s4.x, S[4 * c + 1] = s4.y, S[4 * c + 2] = s4.z, S[4 * c + 3] = s4.w;
   }
-  // Fused gate projection: warp w computes group w's partial sums of all 16 rows x {b, a} over the layer's
-  // normalised input; the rows' threads add the 8 groups in order below (the order of sb_linear_f32, so the bits
-  // agree with the unfused way). All of a round's loads are in flight together.
-  if (a.gate_weight && rows > 0) {
+  // Fused gate projection: this CTA takes rows 4 vs .. 4 vs + 3; warp w computes group w's partial sums of those rows x
+  // {b, a} over the layer's normalised input and stores them into all four CTAs of the head; the rows' threads add the
+  // 8 groups in order below (the order of sb_linear_f32, so the bits agree with the unfused way).
+  if (fused_gates) {
     static_assert(kGdnThreads / 32 == kDotGroups, "one warp per group of the dot product");
+    static_assert(kGdnRows == 4 * kGdnSplit, "four rows of the gate projection per CTA of the head");
     const float *const wrow[2] = {a.gate_weight + size_t(h) * a.gate_k, a.gate_weight + size_t(VH + h) * a.gate_k};
     const uint16_t *gx = static_cast<const uint16_t *>(a.gate_input);
-    const uint16_t *xrow[kGdnRows];
+    const uint16_t *xrow[4];
 #pragma unroll
-    for (int r = 0; r < kGdnRows; ++r) xrow[r] = gx + size_t(min(uint32_t(r), rows - 1)) * a.gate_input_stride;
-    float d[kGdnRows][2];
-    warp_dot_group_f32_bf16<2, kGdnRows>(wrow, xrow, a.gate_k, lane, warp, d);
-    if (lane == 0)
+    for (int r = 0; r < 4; ++r) xrow[r] = gx + size_t(min(4 * vs + uint32_t(r), rows - 1)) * a.gate_input_stride;
+    float d[4][2];
+    warp_dot_group_f32_bf16<2, 4>(wrow, xrow, a.gate_k, lane, warp, d);
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (lane < kGdnSplit) {
+      cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
+      float *remote = cluster.map_shared_rank(&gate_s[0][0][0], lane);
 #pragma unroll
-      for (int r = 0; r < kGdnRows; ++r) gate_s[warp][r][0] = d[r][0], gate_s[warp][r][1] = d[r][1];
+      for (int r = 0; r < 4; ++r) {
+        remote[(warp * kGdnRows + 4 * vs + r) * 2] = d[r][0];
+        remote[(warp * kGdnRows + 4 * vs + r) * 2 + 1] = d[r][1];
+      }
+    }
   }
   // Conv inputs of this CTA's channels (q and k of the key head, 32 value dimensions) for history rows
   // -3..-1 and the block's rows, staged with 16-byte loads: in_s[3 + row][local channel]. History row i
@@ -112,7 +125,8 @@ __global__ void __launch_bounds__(kGdnThreads, 2) gdn_kernel(const GdnParams p) 
   }
   for (uint32_t lc = tid; lc < kLocal; lc += kGdnThreads)
     w_s[lc] = *reinterpret_cast<const uint2 *>(conv_w + size_t(global_channel(lc)) * kTaps);
-  __syncthreads();
+  if (fused_gates) cooperative_groups::this_cluster().sync();  // the gates of all rows are here (and the CTA's staging is complete)
+  else __syncthreads();
   auto conv = [&](uint32_t row, uint32_t lc) -> float {
     const uint2 wv = w_s[lc];
     const float w[4] = {bf16_bits_to_float(wv.x & 0xffffu), bf16_bits_to_float(wv.x >> 16), bf16_bits_to_float(wv.y & 0xffffu),
