@@ -57,7 +57,12 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
   __shared__ uint32_t s_last;
   pdl_launch_dependents();
   const bool fused_gates = a.gate_weight && a.rows > 0;
-  if (fused_gates) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");  // "this CTA runs", waited for before the gates' exchange
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");  // "this CTA runs", waited for before the first store into a peer CTA
+  bool peers_run = false;
+  auto wait_peers_run = [&] {
+    if (!peers_run) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    peers_run = true;
+  };
   pdl_wait();
   const uint32_t vs = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t KH = a.key_heads, VH = a.value_heads, KW = KH * kD, VW = VH * kD, C = 2 * KW + VW;
@@ -95,7 +100,7 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
     for (int r = 0; r < 4; ++r) xrow[r] = gx + size_t(min(4 * vs + uint32_t(r), rows - 1)) * a.gate_input_stride;
     float d[4][2];
     warp_dot_group_f32_bf16<2, 4>(wrow, xrow, a.gate_k, lane, warp, d);
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    wait_peers_run();
     if (lane < kGdnSplit) {
       cooperative_groups::cluster_group cluster = cooperative_groups::this_cluster();
       float *remote = cluster.map_shared_rank(&gate_s[0][0][0], lane);
@@ -138,10 +143,12 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
     return round_bf16(silu_f(value));
   };
 
-  // (2) conv outputs: q, k of the key head (16 x 128 each) and this CTA's 32 value dimensions.
+  // (2) conv outputs: this CTA's 32 value dimensions, and q, k of the key head (128 each) for rows 4 vs .. 4 vs + 3 only:
+  // the head's four CTAs divide the rows, normalise their own and store the result into all four (below).
+  const uint32_t qk_row0 = min(4 * vs, rows), qk_rows = min(4 * vs + 4, rows) - qk_row0;
 #pragma unroll 2
-  for (uint32_t i = tid; i < rows * kD; i += kGdnThreads) {
-    const uint32_t r = i / kD, d = i % kD;
+  for (uint32_t i = tid; i < qk_rows * kD; i += kGdnThreads) {
+    const uint32_t r = qk_row0 + i / kD, d = i % kD;
     q_s[r][d] = conv(r, d);
     k_s[r][d] = conv(r, kD + d);
   }
@@ -185,8 +192,10 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
   __syncthreads();
   // q/k RMS norm over the head's 128 dimensions: a warp per (row, q or k); 4 dims per lane in order,
   // then the butterfly.
-  for (uint32_t task = warp; task < 2 * rows; task += kGdnThreads / 32) {
-    const uint32_t r = task >> 1;
+  wait_peers_run();
+  cooperative_groups::cluster_group head_ctas = cooperative_groups::this_cluster();
+  for (uint32_t task = warp; task < 2 * qk_rows; task += kGdnThreads / 32) {
+    const uint32_t r = qk_row0 + (task >> 1);
     float *vec = (task & 1) ? k_s[r] : q_s[r];
     float ss = 0.0f;
 #pragma unroll
@@ -196,10 +205,17 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
     }
     const float inv = rsqrtf(ss / float(kD) + 1e-6f);
     const float post = (task & 1) ? 0.08838834765f : 0.0078125f;
+    float out[4];
 #pragma unroll
-    for (int g = 0; g < 4; ++g) vec[32 * g + lane] = round_bf16(round_bf16(vec[32 * g + lane] * inv) * post);
+    for (int g = 0; g < 4; ++g) out[g] = round_bf16(round_bf16(vec[32 * g + lane] * inv) * post);
+#pragma unroll
+    for (int peer = 0; peer < kGdnSplit; ++peer) {
+      float *remote = head_ctas.map_shared_rank(vec, peer);
+#pragma unroll
+      for (int g = 0; g < 4; ++g) remote[32 * g + lane] = out[g];
+    }
   }
-  __syncthreads();
+  head_ctas.sync();  // every row's q and k are in every CTA of the head
   // (6) tape and carried conv rows, from the staged inputs.
   {
     uint16_t *tin = static_cast<uint16_t *>(a.step.inputs), *cs_out = static_cast<uint16_t *>(a.conv_state_out);
