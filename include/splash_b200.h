@@ -334,6 +334,23 @@ typedef struct SbSampleArgs {
   float top_p;
   uint32_t *cut_out;         /* optional device u32 [rows, 2]: the end as {order key of the last logit, last id} */
 } SbSampleArgs;
+/* The sampling penalties of one lane's rows, in place, before selection: a token the prompt or the output holds has a
+ * positive logit divided and a negative one multiplied by `repetition`; a token the output holds `count` times is
+ * lowered by frequency * count + presence; the result saturates at the largest finite value; NaN and -inf stay.
+ * words (device u32 [vocab]): the output's count of each token in the low 31 bits, bit 31 set when the prompt holds
+ * it; a row's context also counts the draft tokens (input rows 1..) on its path in `tree`, but the anchor. Replaces
+ * ops::Sampling's penalty pass (kernel decode_sample_penalize, runtime/metal/kernels/decode/sampling.metal:985-1048;
+ * SamplingPenaltyParams, runtime/metal/abi/Sampling.h:124-145). */
+typedef struct SbPenaltyArgs {
+  float *logits;                /* device fp32 [rows, logit_stride] */
+  const uint32_t *words;        /* device u32 [vocab] */
+  const uint32_t *input_tokens; /* device u32 [rows] */
+  const void *tree;             /* device SplashTreeRow[rows] */
+  uint32_t rows, vocab, logit_stride;
+  float repetition, presence, frequency;
+} SbPenaltyArgs;
+SB_API int sb_sample_penalize(void *stream, const SbPenaltyArgs *args);
+
 SB_API uint64_t sb_sample_workspace_bytes(uint32_t rows, uint32_t vocab);
 SB_API int sb_sample_verify(void *stream, const SbSampleArgs *args);
 

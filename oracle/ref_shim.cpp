@@ -2,11 +2,12 @@
 //
 // C entry points over the reference's own CPU test references, compiled from the headers where
 // they lie in the reference tree (dev/tests/engine/GgufFormatReference.hpp,
-// dev/tests/engine/Q8PageFormatReference.hpp); no reference source is copied. The result,
+// dev/tests/engine/Q8PageFormatReference.hpp, dev/tests/engine/PenaltyReference.hpp); no reference source is copied. The result,
 // oracle/_ref/libsplash_ref.so, lets the tests compare the oracle's restatement bit for bit
 // with the reference's code and lets the fixture script under tests/golden/ emit vectors.
 #include "GgufFormatReference.hpp"
 #include "Q8PageFormatReference.hpp"
+#include "PenaltyReference.hpp"
 
 #include <cstdint>
 #include <random>
@@ -62,3 +63,10 @@ REF_API void ref_projection(const float *x, const float *w, uint32_t K, double *
 // (Q8PageFormatReference.hpp:107-119).
 REF_API float ref_kv_scale(float maximum) { return splash::kv::reference_detail::storedScale(maximum); }
 REF_API int ref_kv_code(float value, float maximum) { return splash::kv::reference_detail::quantize(value, maximum); }
+
+// The sampling penalties' arithmetic on one logit (PenaltyReference.hpp:28-40).
+REF_API float ref_penalty(float value, uint32_t count, int prompt, float repetition, float presence, float frequency) {
+  splash::ops::SamplingPenalties p;
+  p.repetition = repetition, p.presence = presence, p.frequency = frequency;
+  return splash::test::referencePenalty(value, count, prompt != 0, p);
+}

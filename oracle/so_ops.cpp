@@ -468,3 +468,42 @@ SO_API void so_accept(const uint32_t *input_tokens, const uint32_t *tree, uint32
   *retained = kept;
   *retained_rows = tree[2 * path[kept - 1]];
 }
+
+// ---- sampling penalties (runtime/metal/kernels/decode/sampling.metal:985-1048) ----
+// One logit: repetition divides a positive logit and multiplies a negative one when the prompt or the output holds
+// the token; presence and frequency lower it by the output's count; the result saturates; NaN and -inf stay.
+static bool unselectable_logit(float v) {
+  uint32_t b;
+  memcpy(&b, &v, 4);
+  return (b & 0x7fffffffu) > 0x7f800000u || b == 0xff800000u;
+}
+SO_API float so_penalize_logit(float value, uint32_t count, float repetition, float repetition_inverse, float presence, float frequency) {
+  if (unselectable_logit(value)) return value;
+  value *= value > 0.0f ? repetition_inverse : repetition;
+  if (count) value -= frequency * float(count) + presence;
+  const float mx = 3.402823466e+38f;
+  return value < -mx ? -mx : value > mx ? mx : value;
+}
+// One lane's selected rows rewritten in place. words[token]: the output's count of the token (low 31 bits) and the
+// prompt bit (bit 31); a row's context adds the draft tokens on its path: bit r of `drafted` is set when input row r
+// (r >= 1) holds the token, and row `row` counts the bits of its ancestors but the anchor. tree: 8 bytes a row
+// (ancestors u32 first).
+SO_API void so_sample_penalize(float *logits, uint32_t logit_stride, uint32_t vocab, uint32_t rows, const uint32_t *words,
+                               const uint32_t *input_tokens, const uint32_t *tree, float repetition, float presence, float frequency) {
+  const float mx = 3.402823466e+38f;
+  const float inverse = std::min(1.0f / repetition, mx);
+#pragma omp parallel for
+  for (int64_t token = 0; token < int64_t(vocab); ++token) {
+    uint32_t drafted = 0;
+    for (uint32_t row = 1; row < rows; ++row) drafted |= uint32_t(input_tokens[row] == uint32_t(token)) << row;
+    const uint32_t word = words[token];
+    if (!word && !drafted) continue;
+    for (uint32_t row = 0; row < rows; ++row) {
+      const uint32_t path = tree[2 * row];
+      const uint32_t count = (word & 0x7fffffffu) + uint32_t(__builtin_popcount(drafted & path & ~1u));
+      if (!count && !(word & 0x80000000u)) continue;
+      float &logit = logits[size_t(row) * logit_stride + size_t(token)];
+      logit = so_penalize_logit(logit, count, repetition, inverse, presence, frequency);
+    }
+  }
+}

@@ -13,6 +13,12 @@ struct SamplingPolicy {
   float topP = 1.0f;
 };
 
+// Penalties on the logits of tokens the context holds (runtime/ops/Sampling.hpp:16-29); the defaults change nothing.
+struct SamplingPenalties {
+  float repetition = 1.0f, presence = 0.0f, frequency = 0.0f;
+  bool active() const noexcept { return repetition != 1.0f || presence != 0.0f || frequency != 0.0f; }
+};
+
 struct SamplingBuffers {
   Buffer logits;       // fp32 [rows, logitStride]
   Buffer inputTokens;  // u32 [rows]
@@ -43,6 +49,21 @@ class Sampling {
                    b.selected.as<uint32_t>(), b.workspace ? b.workspace.as<float>() : nullptr, rows, vocabulary, b.logitStride,
                    policy.temperature, policy.minP, policy.topK, policy.topP, nullptr};
     check(sb_sample_verify(graph.stream, &a));
+    ++graph.launches;
+  }
+
+  // The penalty pass over the lane's rows, before addVerify. penaltyWords: u32 [vocabulary], the output's count of each
+  // token with the prompt bit (runtime/metal/abi/Sampling.h:124-125).
+  static void addPenalties(CommandGraph &graph, const SamplingPenalties &penalties, const SamplingBuffers &b, const Buffer &penaltyWords,
+                           const Buffer &treeRows, uint32_t rows, uint32_t vocabulary) {
+    if (!penalties.active()) return;
+    requireBytes(b.logits, (size_t(rows - 1) * b.logitStride + vocabulary) * 4, "Sampling::addPenalties logits");
+    requireBytes(b.inputTokens, size_t(rows) * 4, "Sampling::addPenalties input tokens");
+    requireBytes(penaltyWords, size_t(vocabulary) * 4, "Sampling::addPenalties penalty words");
+    requireBytes(treeRows, size_t(rows) * 8, "Sampling::addPenalties tree rows");
+    SbPenaltyArgs a{b.logits.as<float>(), penaltyWords.as<uint32_t>(), b.inputTokens.as<uint32_t>(), treeRows.as(), rows, vocabulary,
+                    b.logitStride, penalties.repetition, penalties.presence, penalties.frequency};
+    check(sb_sample_penalize(graph.stream, &a));
     ++graph.launches;
   }
 

@@ -544,6 +544,33 @@ __global__ void accept_kernel(const SbAcceptArgs a) {
   a.results[3] = 0;
 }
 
+// One thread per vocabulary token: the token's count in every row's context, then the penalty on the rows that
+// hold it (runtime/metal/kernels/decode/sampling.metal:997-1048). Products and sums are single IEEE operations in
+// the reference's order, so the result equals the CPU statement bit for bit.
+__global__ void penalize_kernel(const SbPenaltyArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t token = blockIdx.x * blockDim.x + threadIdx.x;
+  if (token >= a.vocab) return;
+  uint32_t drafted = 0;
+  for (uint32_t row = 1; row < a.rows; ++row) drafted |= uint32_t(a.input_tokens[row] == token) << row;
+  const uint32_t word = a.words[token];
+  if (!word && !drafted) return;
+  const float inverse = fminf(__fdiv_rn(1.0f, a.repetition), 3.402823466e+38f);
+  const uint2 *tree = static_cast<const uint2 *>(a.tree);
+  for (uint32_t row = 0; row < a.rows; ++row) {
+    const uint32_t count = (word & 0x7fffffffu) + __popc(drafted & tree[row].x & ~1u);
+    if (!count && !(word & 0x80000000u)) continue;
+    float *logit = a.logits + size_t(row) * a.logit_stride + token;
+    float v = *logit;
+    const uint32_t bits = __float_as_uint(v);
+    if ((bits & 0x7fffffffu) > 0x7f800000u || bits == 0xff800000u) continue;  // NaN and -inf stay unselectable
+    v = __fmul_rn(v, v > 0.0f ? inverse : a.repetition);
+    if (count) v = __fsub_rn(v, __fadd_rn(__fmul_rn(a.frequency, float(count)), a.presence));
+    *logit = fminf(fmaxf(v, -3.402823466e+38f), 3.402823466e+38f);
+  }
+}
+
 template <class... Args>
 static int launch(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t cfg = {};
@@ -652,6 +679,15 @@ int sb_sample_verify(void *stream, const SbSampleArgs *a) {
   const bool filtered = a->min_p > 0.0f || (a->top_k > 0 && a->top_k < a->vocab) || (a->top_p > 0.0f && a->top_p < 1.0f);
   SB_REQUIRE(!filtered || a->vocab <= kMaxFilterShards * kShard, "sb_sample_verify: min-p / top-k / top-p support vocabularies up to %u", kMaxFilterShards * kShard);
   return launch(sample_kernel, dim3(a->rows), dim3(kSampleThreads), as_stream(stream), *a);
+}
+
+int sb_sample_penalize(void *stream, const SbPenaltyArgs *a) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(a && a->logits && a->words && a->input_tokens && a->tree, "sb_sample_penalize: null pointer");
+  SB_REQUIRE(a->rows >= 1 && a->rows <= 32 && a->vocab >= 1 && a->logit_stride >= a->vocab, "sb_sample_penalize: rows %u outside 1..32 or bad vocabulary extent",
+             a->rows);
+  SB_REQUIRE(a->repetition > 0.0f, "sb_sample_penalize: repetition %g is not positive", double(a->repetition));
+  return launch(penalize_kernel, dim3((a->vocab + 255) / 256), dim3(256), as_stream(stream), *a);
 }
 
 int sb_accept(void *stream, const SbAcceptArgs *a) {

@@ -215,6 +215,12 @@ class SbSampleArgs(ctypes.Structure):
                 ("min_p", _F), ("top_k", _U), ("top_p", _F), ("cut_out", _P)]
 
 
+class SbPenaltyArgs(ctypes.Structure):
+    _fields_ = [("logits", ctypes.c_void_p), ("words", ctypes.c_void_p), ("input_tokens", ctypes.c_void_p), ("tree", ctypes.c_void_p),
+                ("rows", ctypes.c_uint32), ("vocab", ctypes.c_uint32), ("logit_stride", ctypes.c_uint32),
+                ("repetition", ctypes.c_float), ("presence", ctypes.c_float), ("frequency", ctypes.c_float)]
+
+
 class SbAcceptArgs(ctypes.Structure):
     _fields_ = [("input_tokens", _P), ("tree", _P), ("tokens", _P), ("results", _P), ("stop_tokens", _P),
                 ("rows", _U), ("remaining", _U), ("n_stop", _U)]
@@ -238,6 +244,7 @@ def _bind_ops():
     l.sb_sample_workspace_bytes.argtypes = [_U, _U]
     l.sb_sample_verify.argtypes = [_P, ctypes.POINTER(SbSampleArgs)]
     l.sb_accept.argtypes = [_P, ctypes.POINTER(SbAcceptArgs)]
+    l.sb_sample_penalize.argtypes = [_P, ctypes.POINTER(SbPenaltyArgs)]
     l._ops_bound = True
     return l
 

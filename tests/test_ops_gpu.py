@@ -377,3 +377,46 @@ def test_filtered_selection_matches_the_oracle(min_p, top_k, top_p):
     assert np.array_equal(got[clear], want[clear])
     if top_k == 1:
         assert np.array_equal(got, greedy)
+
+
+@pytest.mark.parametrize("policy", [(1.3, 0.0, 0.0), (1.0, 0.6, 0.2), (0.85, 0.4, 0.1)])
+def test_sampling_penalties_match_oracle_bitwise(policy):
+    """sb_sample_penalize against the oracle's statement of decode_sample_penalize on a branching tree: every logit
+    bit for bit (single IEEE operations in the reference's order), unselectable logits and saturation included."""
+    lib, l, o = _setup()
+    rng = np.random.default_rng(9)
+    rows, vocab = 16, 151936
+    logits = (rng.standard_normal((rows, vocab)) * 6).astype(np.float32)
+    logits[2, 100] = np.nan
+    logits[3, 101] = -np.inf
+    logits[4, 102] = np.inf
+    logits[5, 103] = 3.0e38
+    logits[6, 104] = -3.0e38
+    words = np.zeros(vocab, np.uint32)
+    held = rng.choice(vocab, 4000, replace=False)
+    words[held] = rng.integers(1, 40, 4000).astype(np.uint32)
+    words[rng.choice(vocab, 3000, replace=False)] |= 0x80000000
+    words[100:105] = 7 | 0x80000000
+    inputs = rng.integers(0, vocab, rows).astype(np.uint32)
+    inputs[5] = inputs[2]                 # the same draft token twice on one path
+    inputs[9] = int(held[0])              # a draft token the output already holds
+    # a tree: rows 1..7 a chain, rows 8..15 a second branch under row 3
+    tree = np.zeros((rows, 2), np.uint32)
+    parent = [0, 0, 1, 2, 3, 4, 5, 6, 3, 8, 9, 10, 11, 12, 13, 14]
+    for r in range(rows):
+        tree[r, 0] = (1 << r) | (tree[parent[r], 0] if r else 0)
+        depth = bin(int(tree[r, 0])).count("1") - 1
+        tree[r, 1] = parent[r] | (depth << 16)
+    want = logits.copy()
+    o.so_sample_penalize(P(want), vocab, vocab, rows, P(words), P(inputs), P(tree), *policy)
+    ld, wd = lib.DeviceBuffer.from_numpy(logits), lib.DeviceBuffer.from_numpy(words)
+    idd, td = lib.DeviceBuffer.from_numpy(inputs), lib.DeviceBuffer.from_numpy(tree)
+    pa = lib.SbPenaltyArgs(ld.ptr, wd.ptr, idd.ptr, td.ptr, rows, vocab, vocab, *policy)
+    lib.check(l.sb_sample_penalize(None, ctypes.byref(pa)))
+    got = ld.to_numpy(np.float32, (rows, vocab))
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    assert (got != logits).sum() > 10000 and np.isnan(got[2, 100]) and got[3, 101] == -np.inf
+    assert got[4, 102] == np.float32(3.402823466e38)   # +inf saturates, as in the reference
+    # arguments outside the contract are refused
+    bad = lib.SbPenaltyArgs(ld.ptr, wd.ptr, idd.ptr, td.ptr, rows, vocab, vocab, 0.0, 0.0, 0.0)
+    assert l.sb_sample_penalize(None, ctypes.byref(bad)) == -1

@@ -177,3 +177,49 @@ def test_linear_port_within_projection_bound(fmt):
         val, ex, st = ctypes.c_double(), ctypes.c_double(), ctypes.c_double()
         ref.ref_projection(P(x[1]), P(w[5]), k, ctypes.byref(val), ctypes.byref(ex), ctypes.byref(st))
         assert np.isclose(val.value, v[1, 5]) and np.isclose(ex.value, be[1, 5]) and np.isclose(st.value, bs[1, 5])
+
+
+def test_penalty_arithmetic_matches_the_reference_vectors():
+    """The oracle's penalize_logit against vectors written from the reference's own host statement
+    (tests/golden/make_penalty_goldens.py), bit for bit, and against that code itself where the shim is built."""
+    import json
+    import os
+    import struct
+    o = ol.bind_ops(ol.load())
+    gold = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "penalty_goldens.json")))
+    f = lambda b: struct.unpack("<f", struct.pack("<I", b))[0]
+    bits = lambda v: struct.unpack("<I", struct.pack("<f", v))[0]
+    ref = ol.load_ref()
+    if ref is not None:
+        ref.ref_penalty.restype = ctypes.c_float
+        ref.ref_penalty.argtypes = [ctypes.c_float, ctypes.c_uint32, ctypes.c_int] + [ctypes.c_float] * 3
+    assert len(gold["cases"]) >= 1000
+    for vb, count, prompt, rb, pb, fb, want in gold["cases"]:
+        v, rep, pres, freq = f(vb), f(rb), f(pb), f(fb)
+        with np.errstate(over="ignore"):
+            inverse = float(np.minimum(np.float32(1.0) / np.float32(rep), np.float32(3.402823466e38)))
+        got = v if not count and not prompt else o.so_penalize_logit(v, count, rep, inverse, pres, freq)
+        assert bits(got) == want or (got != got and f(want) != f(want)), (v, count, prompt, rep, pres, freq)
+        if ref is not None:
+            assert bits(ref.ref_penalty(v, count, prompt, rep, pres, freq)) == want or got != got
+
+
+def test_penalty_pass_counts_the_path():
+    """so_sample_penalize on a small tree: a row's count is the table's plus the draft tokens on its own path."""
+    o = ol.bind_ops(ol.load())
+    vocab, rows = 64, 4
+    logits = np.ones((rows, vocab), np.float32)
+    words = np.zeros(vocab, np.uint32)
+    words[5] = 2                      # the output holds token 5 twice
+    words[9] = 0x80000000             # the prompt holds token 9
+    inputs = np.array([1, 7, 7, 5], np.uint32)
+    # rows 1 and 2 are siblings under the anchor, row 3 is a child of row 1
+    tree = np.array([[0b0001, 0], [0b0011, 0 | 1 << 16], [0b0101, 0 | 1 << 16], [0b1011, 1 | 2 << 16]], np.uint32)
+    o.so_sample_penalize(P(logits), vocab, vocab, rows, P(words), P(inputs), P(tree), 2.0, 0.5, 0.25)
+    want = np.ones((rows, vocab), np.float32)
+    want[:, 9] = 0.5                                  # prompt only: repetition
+    want[:, 5] = 0.5 - (0.25 * 2 + 0.5)               # the table's count
+    want[3, 5] = 0.5 - (0.25 * 3 + 0.5)               # row 3 holds token 5 itself
+    want[1, 7] = want[3, 7] = 0.5 - (0.25 * 1 + 0.5)  # row 1 and its child hold the first 7
+    want[2, 7] = 0.5 - (0.25 * 1 + 0.5)               # row 2 holds its own 7 only
+    assert np.array_equal(logits, want)
