@@ -56,9 +56,14 @@ enum {
   SB_EPILOGUE_RESIDUAL = 1,     /* out = v + aux */
   SB_EPILOGUE_UP_WITH_GATE = 2, /* out = bf16(v) * silu(aux) */
   SB_EPILOGUE_GATE_UP = 3,      /* one pass over gate and up rows: bf16(bf16(up) * silu(bf16(gate))) */
-  SB_EPILOGUE_PARTIALS = 4      /* no reduction: out is fp32 [slices of sb_linear_plan][16][out_stride] and receives every
+  SB_EPILOGUE_PARTIALS = 4,     /* no reduction: out is fp32 [slices of sb_linear_plan][16][out_stride] and receives every
                                    k-slice's sums; sb_linear_prepare_sum adds them (and a residual) where the sum is
                                    consumed, which takes the split-K exchange off the projection's tail */
+  SB_EPILOGUE_GATE_UP_PARTIALS = 5 /* SB_EPILOGUE_GATE_UP without the reduction: out is fp32 [slices][16][out_stride] with
+                                   the gate sums of column c at c and the up sums at n + c (out_stride >= 2 n);
+                                   sb_linear_prepare_gate_up adds the slices and applies the activation where the
+                                   result is consumed (same bits; measured no faster than the one-pass epilogue on the
+                                   27B shape, whose two slices exchange cheaply, so the model driver does not use it) */
 };
 
 /* ---- context, memory, streams, events (replaces MetalBackend's buffer and command API) ---- */
@@ -159,6 +164,14 @@ SB_API int sb_linear_prepare(void *stream, const void *x, uint32_t rows, uint32_
 SB_API int sb_linear_prepare_sum(void *stream, const float *partials, uint32_t slices, uint32_t partial_stride, const void *residual,
                                  uint32_t residual_stride, void *sum_out, uint32_t sum_stride, uint32_t rows, uint32_t k,
                                  const void *norm_weight, uint32_t format, void *prepared_out, void *normed_out, uint32_t flags);
+
+/* The conversion for the projection that follows a gate/up pair left as SB_EPILOGUE_GATE_UP_PARTIALS: x = bf16(bf16(up) *
+ * silu(bf16(gate))) with gate and up the slices' sums in slice order, i.e. the one-pass SwiGLU epilogue
+ * (runtime/metal/kernels/shared/gguf_linear.metal:38) done where its result is read. n = the intermediate width (the
+ * conversion's k); act_out (bf16 [rows, act_stride]) receives x. */
+SB_API int sb_linear_prepare_gate_up(void *stream, const float *partials, uint32_t slices, uint32_t partial_stride, uint32_t n,
+                                     void *act_out, uint32_t act_stride, uint32_t rows, uint32_t format, void *prepared_out,
+                                     uint32_t flags);
 
 /* Scratch (split-K partials and arrival counters) the context keeps for sb_linear; sized by
  * sb_init for the largest projection of the supported shapes and reused serially within a stream,

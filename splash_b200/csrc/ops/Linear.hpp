@@ -10,7 +10,7 @@
 namespace splash::b200::ops {
 
 enum class Epilogue { None = SB_EPILOGUE_NONE, Residual = SB_EPILOGUE_RESIDUAL, UpWithGate = SB_EPILOGUE_UP_WITH_GATE,
-                      GateUp = SB_EPILOGUE_GATE_UP, Partials = SB_EPILOGUE_PARTIALS };
+                      GateUp = SB_EPILOGUE_GATE_UP, Partials = SB_EPILOGUE_PARTIALS, GateUpPartials = SB_EPILOGUE_GATE_UP_PARTIALS };
 enum class Destination { BFloat16, Float32 };
 
 // One tensor's rows: `outputSize` rows of `inputSize` weights in `format`, written at `columnOffset`.
@@ -142,6 +142,40 @@ class Linear {
     a.epilogue = SB_EPILOGUE_GATE_UP, a.flags = graph.pdl ? SB_LINEAR_PDL : 0;
     check(sb_linear(graph.stream, &a));
     ++graph.launches;
+  }
+
+  // The same pass leaving every k-slice's gate and up sums unreduced in `partials` (fp32 [slices][16][partialStride],
+  // gate at column c, up at gate.outputSize + c); prepareGateUp adds them and applies the activation. Returns the slices.
+  static uint32_t addGateUpPartials(CommandGraph &graph, const Buffer &partials, uint32_t partialStride, const QuantizedSegment &gate,
+                                    const QuantizedSegment &up, uint32_t rows, const PreparedInput &prepared) {
+    if (gate.format != up.format || gate.outputSize != up.outputSize || gate.inputSize != up.inputSize)
+      throw std::invalid_argument("Linear::addGateUpPartials: gate and up tensors differ in shape or format");
+    SbLinearPlan plan{};
+    check(sb_linear_plan(gate.format, gate.outputSize, gate.inputSize, rows, SB_EPILOGUE_GATE_UP_PARTIALS, &plan));
+    if (partialStride < 2 * gate.outputSize) throw std::invalid_argument("Linear::addGateUpPartials: partial rows hold gate and up columns");
+    requireBytes(partials, size_t(plan.slices) * 16 * partialStride * 4, "Linear::addGateUpPartials partial sums");
+    requireBytes(gate.rows, size_t(gate.outputSize) * sb_row_bytes(gate.format, gate.inputSize), "Linear::addGateUpPartials gate");
+    requireBytes(up.rows, size_t(up.outputSize) * sb_row_bytes(up.format, up.inputSize), "Linear::addGateUpPartials up");
+    SbLinearArgs a{};
+    a.weights = gate.rows.as(), a.weights2 = up.rows.as(), a.prepared = prepared.buffer.as(), a.out = partials.as();
+    a.format = gate.format, a.n = gate.outputSize, a.k = gate.inputSize, a.rows = rows, a.out_stride = partialStride, a.out_f32 = 1;
+    a.epilogue = SB_EPILOGUE_GATE_UP_PARTIALS, a.flags = graph.pdl ? SB_LINEAR_PDL : 0;
+    check(sb_linear(graph.stream, &a));
+    ++graph.launches;
+    return plan.slices;
+  }
+
+  // The conversion of the SwiGLU result for the down projection, from the pair's unreduced sums; `activation` (bf16
+  // [rows, activationStride]) receives the result as Linear::addGateUp would have written it.
+  static PreparedInput prepareGateUp(CommandGraph &graph, const Buffer &partials, uint32_t slices, uint32_t partialStride, uint32_t width,
+                                     const Buffer &activation, uint32_t activationStride, uint32_t rows, uint32_t format, const Buffer &scratch) {
+    requireBytes(partials, size_t(slices) * 16 * partialStride * 4, "Linear::prepareGateUp partial sums");
+    requireBytes(activation, (size_t(rows - 1) * activationStride + width) * 2, "Linear::prepareGateUp activation");
+    requireBytes(scratch, preparedBytes(width), "Linear::prepareGateUp scratch");
+    check(sb_linear_prepare_gate_up(graph.stream, partials.as<float>(), slices, partialStride, width, activation.as(), activationStride, rows,
+                                    format, scratch.as(), graph.pdl ? SB_LINEAR_PDL : 0));
+    ++graph.launches;
+    return {scratch, format == SB_FMT_Q4K ? uint32_t(SB_FMT_Q4K) : uint32_t(SB_FMT_Q6K), width};
   }
 
   // fp32 rows (GDN alpha/beta, MoE router) over the bf16 input, optionally through the same RMSNorm.

@@ -129,6 +129,7 @@ struct PrepareParams {
   const float *partials;
   uint16_t *sum_out;
   uint32_t partial_slices, partial_stride, sum_stride;
+  uint32_t swiglu_n;  // non-zero: x = bf16(bf16(up) * silu(bf16(gate))) of the slices' sums at columns c (gate) and swiglu_n + c (up); no residual
   // Optional (tensor parallelism): the slices' sum is one rank's share; the ranks exchange their shares through each
   // other's memory and add them in rank order before the residual (sb_tp_internal.cuh).
   TpExchange tp;
@@ -243,7 +244,7 @@ template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kerne
   for (int i = 0; i < kPrepMaxChunks; ++i) {
     const uint32_t c = c0 + tid + kPrepThreads * i;
     uint4 raw = make_uint4(0, 0, 0, 0);
-    if (live && c < chunks) raw = *reinterpret_cast<const uint4 *>(row + 8 * c);
+    if (live && c < chunks && !p.swiglu_n) raw = *reinterpret_cast<const uint4 *>(row + 8 * c);
     const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -252,7 +253,31 @@ template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kerne
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
-    if (p.partials && live && c < chunks) {
+    if (p.swiglu_n && live && c < chunks) {
+      // x = bf16(bf16(up) * silu(bf16(gate))) of the slices' gate and up sums (added in slice order): the one-pass
+      // SwiGLU epilogue of the projection pair, done here.
+      float up[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (uint32_t s0 = 0; s0 < p.partial_slices; s0 += 2) {  // two slices' loads in flight
+        float4 g4[2][2], u4[2][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const uint32_t sl = min(s0 + j, p.partial_slices - 1);
+          const float4 *pg = reinterpret_cast<const float4 *>(p.partials + (size_t(sl) * kTokens + tok) * p.partial_stride + 8 * c);
+          const float4 *pu = reinterpret_cast<const float4 *>(p.partials + (size_t(sl) * kTokens + tok) * p.partial_stride + p.swiglu_n + 8 * c);
+          g4[j][0] = __ldcg(pg), g4[j][1] = __ldcg(pg + 1), u4[j][0] = __ldcg(pu), u4[j][1] = __ldcg(pu + 1);
+        }
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+          if (s0 + j < p.partial_slices) {
+            acc[i][0] += g4[j][0].x, acc[i][1] += g4[j][0].y, acc[i][2] += g4[j][0].z, acc[i][3] += g4[j][0].w;
+            acc[i][4] += g4[j][1].x, acc[i][5] += g4[j][1].y, acc[i][6] += g4[j][1].z, acc[i][7] += g4[j][1].w;
+            up[0] += u4[j][0].x, up[1] += u4[j][0].y, up[2] += u4[j][0].z, up[3] += u4[j][0].w;
+            up[4] += u4[j][1].x, up[5] += u4[j][1].y, up[6] += u4[j][1].z, up[7] += u4[j][1].w;
+          }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[i][j] = round_bf16(round_bf16(up[j]) * silu_f(round_bf16(acc[i][j])));
+    } else if (p.partials && live && c < chunks) {
       // The sum of the slices in order: with the residual below, the projection's residual epilogue, done here.
       for (uint32_t s0 = 0; s0 < p.partial_slices; s0 += 8) {  // eight slices' loads in flight, added in slice order
         float4 a4[8], b4[8];
@@ -317,7 +342,7 @@ template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kerne
       if (c >= chunks) continue;
       uint32_t pk[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[i][j] = round_bf16(acc[i][j] + v[i][j]);
+      for (int j = 0; j < 8; ++j) v[i][j] = p.swiglu_n ? acc[i][j] : round_bf16(acc[i][j] + v[i][j]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) pk[j] = uint32_t(float_to_bf16_bits(v[i][2 * j])) | (uint32_t(float_to_bf16_bits(v[i][2 * j + 1])) << 16);
       *reinterpret_cast<uint4 *>(p.sum_out + size_t(tok) * p.sum_stride + 8 * c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
@@ -709,7 +734,7 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
   slice_range(p.nsb, p.slices, slice, sb0, sb1);
   const uint32_t slice_sb = sb1 - sb0, chunks = (slice_sb + kStageSb - 1) / kStageSb;
   const uint32_t items = p.tiles * p.slices;
-  const bool gate_up = p.epilogue == SB_EPILOGUE_GATE_UP;
+  const bool gate_up = p.epilogue == SB_EPILOGUE_GATE_UP || p.epilogue == SB_EPILOGUE_GATE_UP_PARTIALS;
 
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < p.stages; ++s) {
@@ -821,7 +846,7 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
       auto part = [&](uint32_t sl, uint32_t run) {
         return reinterpret_cast<float4 *>(p.partials + (size_t(sl) * kTokens + tok) * pcols + (run ? run1 : run0));
       };
-      if (p.epilogue == SB_EPILOGUE_PARTIALS) {  // this slice's sums as they are; their consumer adds the slices
+      if (p.epilogue == SB_EPILOGUE_PARTIALS || p.epilogue == SB_EPILOGUE_GATE_UP_PARTIALS) {  // this slice's sums as they are; their consumer adds the slices
         if (col_ok) {
           float *dst = static_cast<float *>(p.out) + (size_t(slice) * kTokens + tok) * p.out_stride;
 #pragma unroll
@@ -1023,7 +1048,7 @@ static int make_plan(uint32_t format, uint32_t n, uint32_t k, uint32_t epilogue,
              "sb_linear: format %u is not a quantized block format of this kernel", format);
   SB_REQUIRE(k && k % 256 == 0, "sb_linear: k = %u is not a multiple of 256", k);
   SB_REQUIRE(n && n % 32 == 0, "sb_linear: n = %u is not a multiple of 32", n);
-  const bool gate_up = epilogue == SB_EPILOGUE_GATE_UP;
+  const bool gate_up = epilogue == SB_EPILOGUE_GATE_UP || epilogue == SB_EPILOGUE_GATE_UP_PARTIALS;
   const uint32_t sb_bytes = format == SB_FMT_Q4K ? 144 : format == SB_FMT_Q6K ? 210 : 272;
   p.nsb = k / 256;
   p.slices = pick_slices(p.nsb, sb_bytes);
@@ -1097,10 +1122,10 @@ int encode_weight_map(CUtensorMap *map, uintptr_t base, uint32_t stride, uint32_
 static int launch_prepare(cudaStream_t stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride,
                           const void *norm_w, uint32_t layout, void *out, void *normed_out, bool pdl, const float *partials = nullptr,
                           uint32_t slices = 0, uint32_t partial_stride = 0, void *sum_out = nullptr, uint32_t sum_stride = 0,
-                          const TpExchange *tp = nullptr) {
+                          const TpExchange *tp = nullptr, uint32_t swiglu_n = 0) {
   PrepareParams pp{static_cast<const uint16_t *>(x), static_cast<const float *>(norm_w), static_cast<uint8_t *>(out),
                    static_cast<uint16_t *>(normed_out), rows, k, x_stride, layout, partials, static_cast<uint16_t *>(sum_out), slices,
-                   partial_stride, sum_stride, tp ? *tp : TpExchange{}};
+                   partial_stride, sum_stride, swiglu_n, tp ? *tp : TpExchange{}};
   if (tp) {  // the share's way to the peers, ahead of the conversion and not waited for by it
     cudaLaunchConfig_t push = {};
     push.gridDim = dim3(kTokens * kPrepCluster), push.blockDim = dim3(kPrepThreads), push.stream = stream;
@@ -1186,6 +1211,24 @@ extern "C" int sb_linear_prepare_sum(void *stream, const float *partials, uint32
                         (flags & SB_LINEAR_PDL) != 0, partials, slices, partial_stride, sum_out, sum_stride);
 }
 
+extern "C" int sb_linear_prepare_gate_up(void *stream, const float *partials, uint32_t slices, uint32_t partial_stride, uint32_t n, void *act_out,
+                                         uint32_t act_stride, uint32_t rows, uint32_t format, void *prepared_out, uint32_t flags) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(partials && act_out && prepared_out, "sb_linear_prepare_gate_up: null pointer");
+  SB_REQUIRE(slices >= 1 && slices <= 64, "sb_linear_prepare_gate_up: %u slices outside 1..64", slices);
+  SB_REQUIRE(rows >= 1 && rows <= kTokens, "sb_linear_prepare_gate_up: rows = %u outside 1..%d", rows, kTokens);
+  SB_REQUIRE(n && n % 256 == 0 && n <= 8 * kPrepThreads * kPrepMaxChunks * kPrepCluster, "sb_linear_prepare_gate_up: n = %u is not a multiple of 256 up to %d", n,
+             8 * kPrepThreads * kPrepMaxChunks * kPrepCluster);
+  SB_REQUIRE(partial_stride >= 2 * n && partial_stride % 4 == 0 && act_stride >= n && act_stride % 8 == 0,
+             "sb_linear_prepare_gate_up: the partial rows hold 2 n columns, the output rows n; strides in fours and eights");
+  SB_REQUIRE(format == SB_FMT_Q4K || format == SB_FMT_Q6K || format == SB_FMT_Q80, "sb_linear_prepare_gate_up: format %u", format);
+  SB_REQUIRE(((reinterpret_cast<uintptr_t>(partials) | reinterpret_cast<uintptr_t>(act_out) | reinterpret_cast<uintptr_t>(prepared_out)) & 15) == 0,
+             "sb_linear_prepare_gate_up: pointers must be 16-byte aligned");
+  const uint32_t layout = format != SB_FMT_Q4K ? 0u : (flags & SB_LINEAR_TCGEN05) ? 2u : 1u;
+  return launch_prepare(as_stream(stream), nullptr, rows, n, 0, nullptr, layout, prepared_out, nullptr, (flags & SB_LINEAR_PDL) != 0, partials, slices,
+                        partial_stride, act_out, act_stride, nullptr, n);
+}
+
 extern "C" int sb_tp_prepare_sum(void *stream, void *group, uint32_t index, const float *partials, uint32_t slices, uint32_t partial_stride,
                                  const void *residual, uint32_t residual_stride, void *sum_out, uint32_t sum_stride, uint32_t rows, uint32_t k,
                                  const void *norm_weight, uint32_t format, void *prepared_out, void *normed_out, uint32_t flags) {
@@ -1215,15 +1258,18 @@ extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
   SB_REQUIRE(a, "sb_linear: null arguments");
   SB_REQUIRE(a->weights && a->out && (a->x || a->prepared), "sb_linear: null weights, out, or neither x nor prepared");
   SB_REQUIRE(a->rows >= 1 && a->rows <= kTokens, "sb_linear: rows = %u outside 1..%d", a->rows, kTokens);
-  SB_REQUIRE(a->epilogue <= SB_EPILOGUE_PARTIALS, "sb_linear: unknown epilogue %u", a->epilogue);
-  SB_REQUIRE((a->epilogue == SB_EPILOGUE_GATE_UP) == (a->weights2 != nullptr),
-             "sb_linear: weights2 is given exactly with SB_EPILOGUE_GATE_UP");
+  SB_REQUIRE(a->epilogue <= SB_EPILOGUE_GATE_UP_PARTIALS, "sb_linear: unknown epilogue %u", a->epilogue);
+  const bool unreduced = a->epilogue == SB_EPILOGUE_PARTIALS || a->epilogue == SB_EPILOGUE_GATE_UP_PARTIALS;
+  const bool pair = a->epilogue == SB_EPILOGUE_GATE_UP || a->epilogue == SB_EPILOGUE_GATE_UP_PARTIALS;
+  SB_REQUIRE(pair == (a->weights2 != nullptr), "sb_linear: weights2 is given exactly with the gate/up epilogues");
+  SB_REQUIRE(a->epilogue != SB_EPILOGUE_GATE_UP_PARTIALS || (a->out_f32 && a->out_stride >= 2 * a->n),
+             "sb_linear: SB_EPILOGUE_GATE_UP_PARTIALS writes fp32 rows of at least 2 n columns");
   SB_REQUIRE((a->epilogue == SB_EPILOGUE_RESIDUAL || a->epilogue == SB_EPILOGUE_UP_WITH_GATE) == (a->aux != nullptr),
              "sb_linear: aux is given exactly with the residual and up-with-gate epilogues");
   SB_REQUIRE(a->out_stride >= a->n && a->out_stride % 8 == 0, "sb_linear: out_stride %u < n or not a multiple of 8", a->out_stride);
   SB_REQUIRE(!a->aux || (a->aux_stride >= a->n && a->aux_stride % 8 == 0), "sb_linear: aux_stride %u < n or not a multiple of 8", a->aux_stride);
-  SB_REQUIRE(!(a->out_f32 && a->epilogue != SB_EPILOGUE_NONE && a->epilogue != SB_EPILOGUE_PARTIALS), "sb_linear: an fp32 destination takes no epilogue");
-  SB_REQUIRE(a->epilogue != SB_EPILOGUE_PARTIALS || !(a->flags & SB_LINEAR_TCGEN05), "sb_linear: SB_EPILOGUE_PARTIALS is not offered by the tcgen05 kernel");
+  SB_REQUIRE(!(a->out_f32 && a->epilogue != SB_EPILOGUE_NONE && !unreduced), "sb_linear: an fp32 destination takes no epilogue");
+  SB_REQUIRE(!unreduced || !(a->flags & SB_LINEAR_TCGEN05), "sb_linear: unreduced k-slice sums are not offered by the tcgen05 kernel");
   SB_REQUIRE((reinterpret_cast<uintptr_t>(a->out) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->aux) & 15) == 0,
              "sb_linear: out and aux must be 16-byte aligned");
   SB_REQUIRE((reinterpret_cast<uintptr_t>(a->weights) & 1) == 0 && (reinterpret_cast<uintptr_t>(a->weights2) & 1) == 0,
@@ -1250,8 +1296,8 @@ extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
     }
     return launch_linear_tc(as_stream(stream), a, prep, (a->flags & SB_LINEAR_PDL) != 0);
   }
-  const uint32_t pcols = a->epilogue == SB_EPILOGUE_GATE_UP ? 2 * a->n : a->n;
-  SB_REQUIRE(p.slices == 1 || size_t(p.slices) * kTokens * pcols * 4 <= c.linear_partials_bytes,
+  const uint32_t pcols = pair ? 2 * a->n : a->n;
+  SB_REQUIRE(p.slices == 1 || unreduced || size_t(p.slices) * kTokens * pcols * 4 <= c.linear_partials_bytes,
              "sb_linear: split-K scratch too small for n = %u with %u slices", a->n, p.slices);
   SB_REQUIRE(p.tiles <= c.linear_counter_count, "sb_linear: too many tiles (%u)", p.tiles);
   const bool pdl = (a->flags & SB_LINEAR_PDL) != 0;

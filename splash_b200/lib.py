@@ -9,7 +9,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _PATH = os.path.join(_HERE, "libsplash_b200.so")
 
 FMT_Q4K, FMT_Q6K, FMT_Q80, FMT_NVFP4, FMT_BF16, FMT_F16, FMT_F32 = 0, 4, 6, 37, 41, 42, 64
-EP_NONE, EP_RESIDUAL, EP_UP_WITH_GATE, EP_GATE_UP, EP_PARTIALS = 0, 1, 2, 3, 4
+EP_NONE, EP_RESIDUAL, EP_UP_WITH_GATE, EP_GATE_UP, EP_PARTIALS, EP_GATE_UP_PARTIALS = 0, 1, 2, 3, 4, 5
 LINEAR_PDL = 1
 LINEAR_TCGEN05 = 2
 

@@ -262,3 +262,48 @@ def test_linear_partial_sums_then_prepare_sum_equal_the_residual_epilogue(fmt, n
     lib.check(L.sb_linear_prepare(None, wantd.ptr, rows, n, n, wn.ptr, lib.FMT_Q4K, prep_b.ptr, None, 0))
     lib.stream_sync()
     assert np.array_equal(prep_a.to_numpy(np.uint8, (int(L.sb_linear_prepared_bytes(n)),)), prep_b.to_numpy(np.uint8, (int(L.sb_linear_prepared_bytes(n)),)))
+
+
+@pytest.mark.parametrize("fmt,n,k", [(0, 17408, 5120), (0, 2816, 1024), (4, 512, 2048), (6, 256, 1024)])
+def test_gate_up_partial_sums_then_prepare_equal_the_one_pass_epilogue(fmt, n, k):
+    """SB_EPILOGUE_GATE_UP_PARTIALS leaves the pair's k-slice sums; sb_linear_prepare_gate_up adds them in slice order and
+    applies the activation: the SwiGLU result and what is prepared from it have the bits of the one-pass epilogue."""
+    lib = _setup()
+    L = lib.load()
+    rows = 16
+    Wg, Wu = qf.realistic(fmt, n, k, seed=11), qf.realistic(fmt, n, k, seed=12)
+    X = qf.activations(rows, k, seed=13)
+    gd, ud, xd = lib.DeviceBuffer.from_numpy(Wg), lib.DeviceBuffer.from_numpy(Wu), lib.DeviceBuffer.from_numpy(X)
+    act = lib.DeviceBuffer(rows * n * 2 + 256)
+    lib.linear(gd.ptr, xd.ptr, act.ptr, fmt, n, k, rows, weights2=ud.ptr, epilogue=lib.EP_GATE_UP)
+    lib.stream_sync()
+    want = act.to_numpy(np.uint16, (rows, n))
+    plan = lib.SbLinearPlan()
+    L.sb_linear_plan.argtypes = [ctypes.c_uint32] * 5 + [ctypes.POINTER(lib.SbLinearPlan)]
+    lib.check(L.sb_linear_plan(fmt, n, k, rows, lib.EP_GATE_UP_PARTIALS, ctypes.byref(plan)))
+    parts = lib.DeviceBuffer(plan.slices * 16 * 2 * n * 4)
+    parts.fill(0xFF)
+    lib.linear(gd.ptr, xd.ptr, parts.ptr, fmt, n, k, rows, weights2=ud.ptr, epilogue=lib.EP_GATE_UP_PARTIALS, out_f32=True, out_stride=2 * n)
+    nb = (n + 255) // 256 * 256
+    if nb != n:
+        return  # the conversion takes whole super-blocks; the partial sums above were still written without a fault
+    P, U = ctypes.c_void_p, ctypes.c_uint32
+    L.sb_linear_prepare_gate_up.argtypes = [P, P, U, U, U, P, U, U, U, P, U]
+    size = int(L.sb_linear_prepared_bytes(n))
+    prep_a, prep_b = lib.DeviceBuffer(size), lib.DeviceBuffer(size)
+    got_act = lib.DeviceBuffer(rows * n * 2 + 256)
+    lib.check(L.sb_linear_prepare_gate_up(None, parts.ptr, plan.slices, 2 * n, n, got_act.ptr, n, rows, lib.FMT_Q6K, prep_a.ptr, 0))
+    lib.stream_sync()
+    assert lib.device_status() == 0
+    got = got_act.to_numpy(np.uint16, (rows, n))
+    # -0 and +0 are the same activation; everything else bit for bit
+    same = (got == want) | (((got | want) & 0x7FFF) == 0)
+    assert same.all()
+    lib.check(L.sb_linear_prepare(None, act.ptr, rows, n, n, None, lib.FMT_Q6K, prep_b.ptr, None, 0))
+    lib.stream_sync()
+    a, b = prep_a.to_numpy(np.uint8, (size,)), prep_b.to_numpy(np.uint8, (size,))
+    assert np.array_equal(a.view(np.float16) == 0, b.view(np.float16) == 0)
+    assert np.array_equal(a.view(np.uint16) & 0x7FFF, b.view(np.uint16) & 0x7FFF) or np.array_equal(a, b)
+    # the contract: fp32 rows of 2 n columns
+    bad = lib.SbLinearArgs(gd.ptr, ud.ptr, xd.ptr, None, None, parts.ptr, None, fmt, n, k, rows, k, 0, n, lib.EP_GATE_UP_PARTIALS, 1, 0)
+    assert L.sb_linear(None, ctypes.byref(bad)) == -1
