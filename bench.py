@@ -120,6 +120,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--tiny", action="store_true", help="the 4-layer configuration (a smoke run, not the benchmark)")
+    ap.add_argument("--tp-shots", type=int, default=0, choices=(0, 1, 2), help="how tensor-parallel shares travel (sb_tp_set_exchange); 0: by the number of ranks")
     ap.add_argument("--parallel", default="tp", choices=("tp", "replicas"), help="what N > 1 GPUs do: one lane tensor-parallel, or N lanes")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -142,6 +143,7 @@ def main():
     from splash_b200.dist import Group
     group = Group("nccl")
     lib.init(local)
+    lib.check(lib.load().sb_tp_set_exchange(args.tp_shots))
     cfg = dict(target.TINY if args.tiny else target.QWEN27B)
     context = 2048 if args.tiny else CONTEXT
     stream = lib.stream_create()

@@ -440,6 +440,11 @@ SB_API int sb_tp_prepare_sum(void *stream, void *group, uint32_t index, const fl
 /* This rank's columns [column0, column0 + columns) of the gather matrix go to every peer; returns (on the stream) when
  * every peer's columns have arrived here. */
 SB_API int sb_tp_all_gather(void *stream, void *group, uint32_t index, uint32_t rows, uint32_t column0, uint32_t columns);
+/* How the shares of a sum travel, for exchanges enqueued (or captured) after the call; the same on every rank. 1: every
+ * rank sends its share to every rank and all add (one trip over NVLink, W - 1 copies); 2: shares go to the columns'
+ * owner, which adds them and sends the finished bf16 values to every rank (two trips, 1 / W of the bytes); 0 (default):
+ * one shot with two ranks, two shots with more. Either way every rank ends with the same bits. */
+SB_API int sb_tp_set_exchange(int shots);
 /* Ends a step of `exchanges` exchanges: the next step's indices start over. (sb_target_* steps do this themselves.) */
 SB_API int sb_tp_advance(void *stream, void *group, uint32_t exchanges);
 

@@ -25,6 +25,7 @@ struct Context {
   uint16_t *gdn_scratch = nullptr;       // recurrent outputs before the gate [value_heads][16][128]
   uint32_t *gdn_counters = nullptr;      // one arrival counter per value head
   bool pdl = true;                       // launch glue kernels with programmatic stream serialization
+  int tp_exchange_shots = 0;             // 0: by the number of ranks, 1: one shot, 2: two shots (sb_tp_set_exchange)
   int attention_kernel = 0;              // 0: tcgen05 kernel, 1: warp-level MMA kernel (sb_set_attention_kernel)
 };
 Context &ctx();

@@ -161,8 +161,35 @@ __device__ __forceinline__ size_t tp_unit(size_t matrix, uint32_t tok, uint32_t 
   return ((matrix * kTokens + tok) * width + 8 * (c - lane)) / 2 + lane;
 }
 
-// This rank's share of a sum (its k-slices added in order) into every peer's inbox; the same grid and the same
-// thread-to-element map as prepare_kernel, which adds what arrives (sb_tp_internal.cuh).
+// Where chunk c's two units of finished sums (8 bf16) start in the second inbox, laid out like tp_unit.
+__device__ __forceinline__ size_t tp_sum_unit(uint32_t slot, uint32_t tok, uint32_t width, uint32_t c, uint32_t lane) {
+  return ((size_t(slot) * kTokens + tok) * width + 8 * (c - lane)) / 4 + lane;
+}
+// The rank that owns super-block sb of the row: contiguous ranges.
+__device__ __forceinline__ uint32_t tp_owner(uint32_t sb, uint32_t nsb, uint32_t world) { return sb * world / nsb; }
+
+// Polls `count` units 32 apart until all show `epoch`; gives up after the bounded wait (expired stays set).
+template <int N>
+__device__ __forceinline__ void tp_poll_units(const uint4 *from, uint4 (&got)[N], uint32_t epoch, uint64_t t0, bool &expired, uint32_t *status) {
+  for (uint32_t polls = 1;; ++polls) {
+    bool all = true;
+#pragma unroll
+    for (int u = 0; u < N; ++u) {
+      got[u] = tp_load_unit(from + 32 * u);
+      all = all && got[u].y == epoch && got[u].w == epoch;
+    }
+    if (all || expired) return;
+    if ((polls & 63u) == 0 && (global_timer_ns() - t0 > kTpWaitNs || polls >= (1u << 30))) {
+      atomicCAS(status, uint32_t(SB_DEV_OK), uint32_t(SB_DEV_WAIT_EXPIRED));
+      expired = true;
+    }
+  }
+}
+
+// This rank's share of a sum (its k-slices added in order) on its way to the other ranks; the same grid and the same
+// thread-to-element map as prepare_kernel (sb_tp_internal.cuh). One shot: into every peer's inbox. Two shots: to the
+// columns' owner; the owner's threads add the shares in rank order, add the residual, round, and send the finished
+// values to every rank.
 __global__ void __launch_bounds__(kPrepThreads) tp_push_kernel(const PrepareParams p) {
   const uint32_t tok = blockIdx.x / kPrepCluster, rank = blockIdx.x % kPrepCluster, tid = threadIdx.x, lane = tid & 31;
   const uint32_t nsb = p.k / 256, c0 = rank * nsb / kPrepCluster * 32, chunks = (rank + 1) * nsb / kPrepCluster * 32;
@@ -170,12 +197,16 @@ __global__ void __launch_bounds__(kPrepThreads) tp_push_kernel(const PreparePara
   pdl_launch_dependents();
   pdl_wait();  // the projection that wrote the slices has completed
   const uint32_t epoch = tp_epoch(x);
+  const bool healthy = tp_healthy(x);
   if (blockIdx.x == 0 && tid == 0) st_release_gpu(x.ready, epoch);
   if (tok >= p.rows) return;
   const size_t slot = size_t(epoch & 1u) * x.world;
+  float own[kPrepMaxChunks][8];
+  bool owned[kPrepMaxChunks];
 #pragma unroll
   for (int i = 0; i < kPrepMaxChunks; ++i) {
     const uint32_t c = c0 + tid + kPrepThreads * i;
+    owned[i] = false;
     if (c >= chunks) continue;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     for (uint32_t s0 = 0; s0 < p.partial_slices; s0 += 8) {  // the order and grouping of prepare_kernel's own sum
@@ -193,11 +224,49 @@ __global__ void __launch_bounds__(kPrepThreads) tp_push_kernel(const PreparePara
               acc[7] += b4[j].w;
     }
     const size_t unit = tp_unit(slot + x.rank, tok, x.width, c, lane);
+    const uint32_t owner = tp_owner(c >> 5, nsb, x.world);
     for (uint32_t peer = 0; peer < x.world; ++peer) {
-      if (peer == x.rank) continue;
+      if (peer == x.rank || (x.two_shot && peer != owner)) continue;
       uint4 *dst = reinterpret_cast<uint4 *>(x.data[peer]) + unit;
 #pragma unroll
       for (int u = 0; u < 4; ++u) tp_store_unit(dst + 32 * u, acc[2 * u], acc[2 * u + 1], epoch);
+    }
+    owned[i] = x.two_shot && owner == x.rank;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) own[i][j] = acc[j];
+  }
+  if (!x.two_shot) return;
+  const uint64_t t0 = global_timer_ns();
+  bool expired = !healthy;
+#pragma unroll
+  for (int i = 0; i < kPrepMaxChunks; ++i) {
+    const uint32_t c = c0 + tid + kPrepThreads * i;
+    if (!owned[i]) continue;
+    const uint4 raw = *reinterpret_cast<const uint4 *>(p.x + size_t(tok) * p.x_stride + 8 * c);  // the residual
+    float total[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (uint32_t src = 0; src < x.world; ++src) {
+      if (src == x.rank) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) total[j] += own[i][j];
+        continue;
+      }
+      uint4 got[4];
+      tp_poll_units<4>(reinterpret_cast<const uint4 *>(x.data[x.rank]) + tp_unit(slot + src, tok, x.width, c, lane), got, epoch, t0, expired, x.status);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) total[2 * u] += __uint_as_float(got[u].x), total[2 * u + 1] += __uint_as_float(got[u].z);
+    }
+    const uint32_t r[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t pk[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float lo = round_bf16(total[2 * j] + bf16_bits_to_float(r[j] & 0xffffu)), hi = round_bf16(total[2 * j + 1] + bf16_bits_to_float(r[j] >> 16));
+      pk[j] = uint32_t(float_to_bf16_bits(lo)) | (uint32_t(float_to_bf16_bits(hi)) << 16);
+    }
+    const size_t sunit = tp_sum_unit(epoch & 1u, tok, x.width, c, lane);
+    for (uint32_t peer = 0; peer < x.world; ++peer) {
+      uint4 *dst = x.sums[peer] + sunit;
+      asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(pk[0]), "r"(epoch), "r"(pk[1]), "r"(epoch) : "memory");
+      asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 32), "r"(pk[2]), "r"(epoch), "r"(pk[3]), "r"(epoch) : "memory");
     }
   }
 }
@@ -233,7 +302,7 @@ template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kerne
   bool healthy = true;
   if (TP) {
     epoch = tp_epoch(p.tp), healthy = tp_healthy(p.tp);
-    if (healthy) healthy = tp_wait_ready(p.tp, epoch);
+    if (healthy && !p.tp.two_shot) healthy = tp_wait_ready(p.tp, epoch);  // (two shots: everything arrives as finished sums)
   } else {
     pdl_wait();
   }
@@ -244,7 +313,8 @@ template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kerne
   for (int i = 0; i < kPrepMaxChunks; ++i) {
     const uint32_t c = c0 + tid + kPrepThreads * i;
     uint4 raw = make_uint4(0, 0, 0, 0);
-    if (live && c < chunks && !p.swiglu_n) raw = *reinterpret_cast<const uint4 *>(row + 8 * c);
+    const bool finished = TP && p.tp.two_shot;  // the values arrive whole (below): no residual, no slices to add here
+    if (live && c < chunks && !p.swiglu_n && !finished) raw = *reinterpret_cast<const uint4 *>(row + 8 * c);
     const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -277,7 +347,7 @@ template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kerne
       }
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[i][j] = round_bf16(round_bf16(up[j]) * silu_f(round_bf16(acc[i][j])));
-    } else if (p.partials && live && c < chunks) {
+    } else if (p.partials && live && c < chunks && !finished) {
       // The sum of the slices in order: with the residual below, the projection's residual epilogue, done here.
       for (uint32_t s0 = 0; s0 < p.partial_slices; s0 += 8) {  // eight slices' loads in flight, added in slice order
         float4 a4[8], b4[8];
@@ -295,7 +365,22 @@ template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kerne
       }
     }
   }
-  if (TP && live) {
+  if (TP && live && p.tp.two_shot) {
+    // The finished values of every column arrive from their owners (tp_push_kernel on their side, this rank's included).
+    const TpExchange &x = p.tp;
+    const uint64_t t0 = global_timer_ns();
+    bool expired = !healthy;
+#pragma unroll
+    for (int i = 0; i < kPrepMaxChunks; ++i) {
+      const uint32_t c = c0 + tid + kPrepThreads * i;
+      if (c >= chunks) continue;
+      uint4 got[2];
+      tp_poll_units<2>(x.sums[x.rank] + tp_sum_unit(epoch & 1u, tok, x.width, c, lane), got, epoch, t0, expired, x.status);
+      const uint32_t u[4] = {got[0].x, got[0].z, got[1].x, got[1].z};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][2 * j] = bf16_bits_to_float(u[j] & 0xffffu), acc[i][2 * j + 1] = bf16_bits_to_float(u[j] >> 16);
+    }
+  } else if (TP && live) {
     // The peers' shares arrive in this rank's inbox (tp_push_kernel on their side). The sum over the ranks runs in
     // rank order on every rank, so all ranks hold the same bits afterwards.
     const TpExchange &x = p.tp;
@@ -313,21 +398,8 @@ template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kerne
           for (int j = 0; j < 8; ++j) total[j] += acc[i][j];
           continue;
         }
-        const uint4 *from = reinterpret_cast<const uint4 *>(x.data[x.rank]) + tp_unit(slot + src, tok, x.width, c, lane);
         uint4 got[4];
-        for (uint32_t polls = 1;; ++polls) {
-          bool all = true;
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            got[u] = tp_load_unit(from + 32 * u);
-            all = all && got[u].y == epoch && got[u].w == epoch;
-          }
-          if (all || expired) break;
-          if ((polls & 63u) == 0 && (global_timer_ns() - t0 > kTpWaitNs || polls >= (1u << 30))) {
-            atomicCAS(x.status, uint32_t(SB_DEV_OK), uint32_t(SB_DEV_WAIT_EXPIRED));
-            expired = true;
-          }
-        }
+        tp_poll_units<4>(reinterpret_cast<const uint4 *>(x.data[x.rank]) + tp_unit(slot + src, tok, x.width, c, lane), got, epoch, t0, expired, x.status);
 #pragma unroll
         for (int u = 0; u < 4; ++u) total[2 * u] += __uint_as_float(got[u].x), total[2 * u + 1] += __uint_as_float(got[u].z);
       }
@@ -342,7 +414,7 @@ template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kerne
       if (c >= chunks) continue;
       uint32_t pk[4];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[i][j] = p.swiglu_n ? acc[i][j] : round_bf16(acc[i][j] + v[i][j]);
+      for (int j = 0; j < 8; ++j) v[i][j] = (p.swiglu_n || (TP && p.tp.two_shot)) ? acc[i][j] : round_bf16(acc[i][j] + v[i][j]);
 #pragma unroll
       for (int j = 0; j < 4; ++j) pk[j] = uint32_t(float_to_bf16_bits(v[i][2 * j])) | (uint32_t(float_to_bf16_bits(v[i][2 * j + 1])) << 16);
       *reinterpret_cast<uint4 *>(p.sum_out + size_t(tok) * p.sum_stride + 8 * c) = make_uint4(pk[0], pk[1], pk[2], pk[3]);

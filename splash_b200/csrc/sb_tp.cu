@@ -14,7 +14,7 @@ namespace sb {
 struct TpGroup {
   uint32_t world = 0, rank = 0, width = 0, gather_width = 0;
   uint8_t *window = nullptr;  // this rank's
-  size_t window_bytes = 0, inbox_off = 0, flags_off = 0, gather_off = 0;
+  size_t window_bytes = 0, inbox_off = 0, sums_off = 0, flags_off = 0, gather_off = 0;
   uint8_t *peer[kTpMaxWorld] = {};  // every rank's window as mapped here (peer[rank] == window)
   uint32_t *epoch = nullptr;  // two words: the exchange count, and `ready`
   bool connected = false;
@@ -28,7 +28,9 @@ int tp_exchange(void *group, uint32_t index, bool gather, TpExchange &out) {
   out = TpExchange{};
   out.world = g->world, out.rank = g->rank, out.index = index, out.width = gather ? g->gather_width : g->width;
   out.epoch_base = g->epoch, out.ready = g->epoch + 1, out.status = ctx().status_dev;
+  out.two_shot = ctx().tp_exchange_shots ? ctx().tp_exchange_shots == 2 : g->world > 2;
   for (uint32_t p = 0; p < g->world; ++p) {
+    out.sums[p] = reinterpret_cast<uint4 *>(g->peer[p] + g->sums_off);
     out.data[p] = reinterpret_cast<float *>(g->peer[p] + (gather ? g->gather_off : g->inbox_off));
     out.flags[p] = reinterpret_cast<uint32_t *>(g->peer[p] + g->flags_off);
   }
@@ -81,7 +83,8 @@ int sb_tp_create(uint32_t world, uint32_t rank, uint32_t width, uint32_t gather_
   TpGroup *g = new TpGroup;
   g->world = world, g->rank = rank, g->width = width, g->gather_width = gather_width;
   g->inbox_off = 0;
-  g->flags_off = align_up(size_t(2) * world * 16 * width * 8, 256);  // units of 16 bytes hold two values
+  g->sums_off = align_up(size_t(2) * world * 16 * width * 8, 256);   // (inbox: units of 16 bytes hold two values)
+  g->flags_off = g->sums_off + align_up(size_t(2) * 16 * width * 4, 256);  // (finished sums: units of 16 bytes hold four bf16)
   g->gather_off = g->flags_off + align_up(size_t(world) * kTpGatherCtas * 4, 256);
   g->window_bytes = g->gather_off + align_up(size_t(16) * gather_width * 4, 256) + 256;
   cudaError_t e = cudaMalloc(&g->window, g->window_bytes);
@@ -160,6 +163,12 @@ int sb_tp_all_gather(void *stream, void *group, uint32_t index, uint32_t rows, u
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = ctx().pdl ? 1 : 0;
   SB_CUDA(cudaLaunchKernelEx(&cfg, tp_gather_kernel, x, rows, column0, columns));
+  return SB_OK;
+}
+
+int sb_tp_set_exchange(int shots) {
+  SB_REQUIRE(shots >= 0 && shots <= 2, "sb_tp_set_exchange: %d shots (0: by the number of ranks, 1 or 2)", shots);
+  ctx().tp_exchange_shots = shots;
   return SB_OK;
 }
 

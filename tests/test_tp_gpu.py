@@ -14,10 +14,11 @@ pytestmark = pytest.mark.gpu
 COMMITTED = 2048
 
 
-def _worker(rank, world, barrier, handles, results, step_tokens):
+def _worker(rank, world, shots, barrier, handles, results, step_tokens):
     try:
         from splash_b200 import lib, target, tp
         lib.init(rank)
+        lib.check(lib.load().sb_tp_set_exchange(shots))
         cfg = dict(target.TINY)
         t = target.Target(**cfg, tp_world=world, tp_rank=rank)
         sh = tp.share(cfg, world, rank)
@@ -46,10 +47,11 @@ def _worker(rank, world, barrier, handles, results, step_tokens):
             pass
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_ranks_match_the_whole_model_oracle(world):
+@pytest.mark.parametrize("world,shots", [(2, 0), (2, 2), (4, 0), (4, 1)])
+def test_ranks_match_the_whole_model_oracle(world, shots):
     """Two ranks: every rank its own KV head. Four ranks: each KV head and its pages are held by two ranks, and the
-    11 super-blocks of the intermediate width fall 3, 3, 3, 2."""
+    11 super-blocks of the intermediate width fall 3, 3, 3, 2. shots: how the shares travel (0: one shot with two ranks, two
+    shots with more; 1, 2: forced), so both ways run on two and on four ranks."""
     from splash_b200 import lib, target
     if lib.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
@@ -65,7 +67,7 @@ def test_ranks_match_the_whole_model_oracle(world):
     ctx = mp.get_context("spawn")
     barrier, results = ctx.Barrier(world), ctx.Queue()
     handles = ctx.RawArray(ctypes.c_ubyte, world * 64)
-    procs = [ctx.Process(target=_worker, args=(r, world, barrier, handles, results, step_tokens)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, shots, barrier, handles, results, step_tokens)) for r in range(world)]
     for p in procs:
         p.start()
     got = {}
