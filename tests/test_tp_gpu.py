@@ -102,3 +102,104 @@ def test_ranks_match_the_whole_model_oracle(world, shots):
         assert np.array_equal(tokens, want["tokens"])
         compared += 1
     assert compared >= 1
+
+
+def _op_worker(rank, world, shots, barrier, handles, results):
+    try:
+        import ctypes as C
+        from splash_b200 import lib, tp
+        import oracle_lib as ol
+        lib.init(rank)
+        L = lib.load()
+        lib.check(L.sb_tp_set_exchange(shots))
+        H, S, V, rows = 2048, 3, 4096, 13
+
+        def all_gather(mine):
+            C.memmove(C.addressof(handles) + rank * tp.HANDLE_BYTES, mine, tp.HANDLE_BYTES)
+            barrier.wait(timeout=120)
+            return [bytes(handles[i * tp.HANDLE_BYTES:(i + 1) * tp.HANDLE_BYTES]) for i in range(world)]
+
+        g = tp.Group(world, rank, H, V, all_gather)
+        rng = np.random.default_rng(100 + rank)
+        parts = rng.standard_normal((S, 16, H)).astype(np.float32)
+        res = ol.f2bf(np.random.default_rng(7).standard_normal((16, H)).astype(np.float32))   # the same on every rank
+        pd, rd = lib.DeviceBuffer.from_numpy(parts), lib.DeviceBuffer.from_numpy(res)
+        out = lib.DeviceBuffer(16 * H * 2 + 256)
+        prep = lib.DeviceBuffer(int(L.sb_linear_prepared_bytes(H)))
+        outs = []
+        for index in range(3):       # three exchanges of one step: both inbox slots, then the first again
+            barrier.wait(timeout=120)
+            g.prepare_sum(None, index, pd.ptr, S, H, rd.ptr, out.ptr, rows, H, None, lib.FMT_Q4K, prep.ptr, 0)
+            lib.stream_sync()
+            outs.append(out.to_numpy(np.uint16, (16, H))[:rows].copy())
+        # this rank's columns of the gather matrix, then the gather
+        cols = V // world
+        mine = rng.standard_normal((16, cols)).astype(np.float32)
+        full = np.zeros((16, V), np.float32)
+        full[:, rank * cols:(rank + 1) * cols] = mine
+        lib.check(L.sb_upload(g.gather_ptr, full.ctypes.data_as(C.c_void_p), full.nbytes, None))
+        lib.stream_sync()
+        barrier.wait(timeout=120)
+        g.all_gather(None, 3, rows, rank * cols, cols)
+        g.advance(None, 4)
+        lib.stream_sync()
+        gathered = np.empty((16, V), np.float32)
+        lib.check(L.sb_download(gathered.ctypes.data_as(C.c_void_p), g.gather_ptr, gathered.nbytes, None))
+        lib.stream_sync()
+        results.put((rank, parts, outs, mine, gathered[:rows].copy(), lib.device_status()))
+        barrier.wait(timeout=120)
+        g.close()
+    except Exception as e:
+        results.put((rank, None, repr(e), None, None, 1))
+        try:
+            barrier.abort()
+        except Exception:
+            pass
+
+
+@pytest.mark.parametrize("shots", [1, 2])
+def test_exchange_operators_against_numpy(shots):
+    """sb_tp_prepare_sum and sb_tp_all_gather on two ranks against numpy: the new hidden state is
+    bf16(residual + the ranks' shares added in rank order, each the rank's slices added in slice order), the same bits on
+    both ranks, over three exchanges; the gathered matrix holds every rank's columns."""
+    from splash_b200 import lib
+    import oracle_lib as ol
+    if lib.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    world = 2
+    ctx = mp.get_context("spawn")
+    barrier, results = ctx.Barrier(world), ctx.Queue()
+    handles = ctx.RawArray(ctypes.c_ubyte, world * 64)
+    procs = [ctx.Process(target=_op_worker, args=(r, world, shots, barrier, handles, results)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = {}
+    try:
+        for _ in range(world):
+            rank, parts, outs, mine, gathered, status = results.get(timeout=300)
+            assert parts is not None, f"rank {rank} failed: {outs}"
+            assert status == 0
+            got[rank] = (parts, outs, mine, gathered)
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
+    H, rows = 2048, 13
+    shares = []
+    for r in range(world):
+        s = np.zeros((16, H), np.float32)
+        for sl in range(3):
+            s = s + got[r][0][sl]
+        shares.append(s)
+    total = np.zeros((16, H), np.float32)
+    for s in shares:
+        total = total + s
+    res = ol.bf2f(ol.f2bf(np.random.default_rng(7).standard_normal((16, H)).astype(np.float32)))
+    want = ol.f2bf((total + res).astype(np.float32))[:rows]
+    for r in range(world):
+        for o in got[r][1]:
+            assert np.array_equal(o, want)
+        cols = 4096 // world
+        for src in range(world):
+            assert np.array_equal(got[r][3][:, src * cols:(src + 1) * cols], got[src][2][:rows])
