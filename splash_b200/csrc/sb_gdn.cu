@@ -63,19 +63,19 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
     if (!peers_run) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     peers_run = true;
   };
-  pdl_wait();
   const uint32_t vs = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t KH = a.key_heads, VH = a.value_heads, KW = KH * kD, VW = VH * kD, C = 2 * KW + VW;
   const uint32_t per_key = VH / KH, kh = h / per_key, vd0 = vs * kGdnVd;
   const uint32_t rows = a.rows;
-  const uint32_t pending = a.pending_rows_dev ? min(*a.pending_rows_dev, uint32_t(kGdnRows)) : a.pending_rows;
   const uint16_t *qkvz = static_cast<const uint16_t *>(a.qkvz);
   const uint16_t *conv_w = static_cast<const uint16_t *>(a.conv_w);
   const uint16_t *cs_in = static_cast<const uint16_t *>(a.conv_state_in);
   const uint16_t *pin = static_cast<const uint16_t *>(a.pending.inputs);
   const bool qk_writer = h % per_key == 0 && vs == 0;
 
-  // The state of this warp's 4 value dimensions, requested first so the latency hides behind the prologue:
+  // The state of this warp's 4 value dimensions, requested first so the latency hides behind the prologue, and before
+  // the wait for the kernel ahead: the cell was written a whole step ago, and this CTA may be resident while the
+  // projection before it drains.
   // lane l holds row 4 warp + l / 8, key columns 32 c + 4 (l % 8) .. + 3 for c = 0..3 (the 8 lanes of a row read 128
   // contiguous bytes at a time, from global and from shared memory), so a dot product over the 128 key columns
   // is 16 multiply-adds in the lane and three butterfly rounds over its 8-lane group.
@@ -87,6 +87,8 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
     const float4 s4 = *reinterpret_cast<const float4 *>(a.state_in + sbase + 32 * c);
     S[4 * c] = s4.x, S[4 * c + 1] = s4.y, S[4 * c + 2] = s4.z, S[4 * c + 3] = s4.w;
   }
+  pdl_wait();
+  const uint32_t pending = a.pending_rows_dev ? min(*a.pending_rows_dev, uint32_t(kGdnRows)) : a.pending_rows;
   // Fused gate projection: this CTA takes rows 4 vs .. 4 vs + 3; warp w computes group w's partial sums of those rows x
   // {b, a} over the layer's normalised input and stores them into all four CTAs of the head; the rows' threads add the
   // 8 groups in order below (the order of sb_linear_f32, so the bits agree with the unfused way).
