@@ -304,6 +304,15 @@ typedef struct SbGdnArgs {
   const float *gate_weight; /* fp32 [2 * value_heads, gate_k]: the b rows, then the a rows */
   const void *gate_input;   /* bf16 [rows, gate_input_stride]: the normalised layer input */
   uint32_t gate_k, gate_input_stride;
+  /* Trees (runtime/metal/kernels/decode/gdn.metal:131-137, 198-207, 418-478). tree: device SplashTreeRow[rows] (NULL: the
+   * rows are a chain); a row's convolution taps its path's last tokens and its output is the state after its own path:
+   * S_committed z + sum_j c_j v_j with the query transformed up the path, z_j-1 = d_j (z_j - c_j k_j),
+   * c_j = beta_j (k_j . z_j). pending_path: the row mask, in the pending tape, of the path the previous step accepted
+   * (sb_accept's retained_rows), folded in depth order; pending_path_dev the same as a device word; neither given, the
+   * pending tape's first pending_rows rows. */
+  const void *tree;
+  const uint32_t *pending_path_dev;
+  uint32_t pending_path, reserved;
 } SbGdnArgs;
 SB_API int sb_gdn_verify(void *stream, const SbGdnArgs *args);
 

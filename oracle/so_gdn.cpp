@@ -44,16 +44,30 @@ struct SoGdnArgs {
   SoGdnTape pending, step;
   uint16_t *hidden;            // bf16 [rows][value_heads * 128]
   uint32_t rows, pending_rows, key_heads, value_heads, qkvz_stride, ab_stride, hidden_stride, tiled;
+  // Trees (runtime/metal/kernels/decode/gdn.metal:131-137, 418-478): tree = 8 bytes a row, ancestors u32 first (the row's
+  // path from the anchor, itself included), NULL for a chain; pending_path = the row mask of the previous step's
+  // accepted path in its tape (0: its first pending_rows rows).
+  const uint32_t *tree;
+  uint32_t pending_path;
 };
+
+// Row of the n-th token (from the anchor) of a path mask.
+static uint32_t path_row(uint32_t path, uint32_t n) {
+  for (uint32_t i = 0; i < n; ++i) path &= path - 1;
+  return uint32_t(__builtin_ctz(path));
+}
 
 SO_API void so_gdn_verify(const SoGdnArgs *p) {
   constexpr uint32_t D = 128, Taps = 4;
   const uint32_t KH = p->key_heads, VH = p->value_heads, KW = KH * D, VW = VH * D, C = 2 * KW + VW, per_key = VH / KH;
-  // (1) conv history = last 3 rows of (conv_state_in ++ pending inputs).
+  const uint32_t pending_path = p->pending_path ? p->pending_path : (p->pending_rows >= 32 ? ~0u : (1u << p->pending_rows) - 1u);
+  const uint32_t pending_count = uint32_t(__builtin_popcount(pending_path));
+  auto row_path = [&](uint32_t r) { return (p->tree ? (p->tree[2 * r] & ((2u << r) - 1u)) : ((2u << r) - 1u)) | (1u << r); };
+  // (1) conv history = last 3 rows of (conv_state_in ++ the pending path's inputs).
   std::vector<uint16_t> hist(3 * size_t(C));
   for (int i = 0; i < 3; ++i) {
-    const int src = int(p->pending_rows) - 3 + i;  // index into pending rows; negative -> carried rows
-    const uint16_t *row = src >= 0 ? p->pending.inputs + size_t(src) * C : p->conv_state_in + size_t(3 + src) * C;
+    const int src = int(pending_count) - 3 + i;  // index into the pending path; negative -> carried rows
+    const uint16_t *row = src >= 0 ? p->pending.inputs + size_t(path_row(pending_path, uint32_t(src))) * C : p->conv_state_in + size_t(3 + src) * C;
     std::copy(row, row + C, hist.begin() + size_t(i) * C);
   }
   std::copy(hist.begin(), hist.end(), p->conv_state_out);
@@ -64,10 +78,15 @@ SO_API void so_gdn_verify(const SoGdnArgs *p) {
     if (row >= 0) return bf2f(p->qkvz[size_t(row) * p->qkvz_stride + ch]);
     return bf2f(hist[size_t(3 + row) * C + ch]);
   };
+  // A row's taps are the last four tokens of its path, itself last; tokens before the anchor come from the history.
   auto conv = [&](uint32_t row, uint32_t ch) {
+    const uint32_t path = row_path(row);
+    const int depth = __builtin_popcount(path) - 1;
     float value = 0.0f;
-    for (uint32_t tap = 0; tap < Taps; ++tap)
-      value += input(int(row) + int(tap) - 3, ch) * bf2f(p->conv_w[size_t(ch) * Taps + tap]);
+    for (uint32_t tap = 0; tap < Taps; ++tap) {
+      const int at = depth - 3 + int(tap);  // the tap's token, counted from the anchor
+      value += input(at >= 0 ? int(path_row(path, uint32_t(at))) : at, ch) * bf2f(p->conv_w[size_t(ch) * Taps + tap]);
+    }
     value = rbf(value);
     return rbf(silu(value));
   };
@@ -129,7 +148,8 @@ SO_API void so_gdn_verify(const SoGdnArgs *p) {
       }
     };
     std::vector<float> key(D), val(D);
-    for (uint32_t t = 0; t < p->pending_rows; ++t) {
+    for (uint32_t n = 0; n < pending_count; ++n) {
+      const uint32_t t = path_row(pending_path, n);
       for (uint32_t i = 0; i < D; ++i) {
         key[i] = bf2f(p->pending.k[size_t(t) * KW + kh * D + i]);
         val[i] = bf2f(p->pending.v[size_t(t) * VW + h * D + i]);
@@ -140,9 +160,22 @@ SO_API void so_gdn_verify(const SoGdnArgs *p) {
     std::copy(S.begin(), S.end(), p->state_out + size_t(h) * D * D);
     std::vector<float> o(D);
     const uint32_t out_head = p->tiled ? (uint32_t(h) % per_key) * KH + uint32_t(h) / per_key : uint32_t(h);
+    const std::vector<float> committed = S;
     for (uint32_t r = 0; r < p->rows; ++r) {
-      advance(k.data() + size_t(r) * KW + kh * D, v.data() + size_t(r) * VW + h * D, decay[size_t(r) * VH + h],
-              beta[size_t(r) * VH + h], q.data() + size_t(r) * KW + kh * D, o.data());
+      const uint32_t path = row_path(r);
+      if (path == (2u << r) - 1u && (r == 0 || row_path(r - 1) == (2u << (r - 1)) - 1u)) {
+        // the chain so far: the state carries on from the row before
+        advance(k.data() + size_t(r) * KW + kh * D, v.data() + size_t(r) * VW + h * D, decay[size_t(r) * VH + h],
+                beta[size_t(r) * VH + h], q.data() + size_t(r) * KW + kh * D, o.data());
+      } else {
+        // a tree row: from the committed state along its own path, by definition
+        S = committed;
+        for (uint32_t up = path; up; up &= up - 1) {
+          const uint32_t t = uint32_t(__builtin_ctz(up));
+          advance(k.data() + size_t(t) * KW + kh * D, v.data() + size_t(t) * VW + h * D, decay[size_t(t) * VH + h],
+                  beta[size_t(t) * VH + h], t == r ? q.data() + size_t(r) * KW + kh * D : nullptr, t == r ? o.data() : nullptr);
+        }
+      }
       float total = 0.0f;
       for (uint32_t d = 0; d < D; ++d) {
         o[d] = rbf(o[d]);

@@ -52,6 +52,11 @@ struct GdnDecodeBuffers {
   const Buffer *pendingRowsDevice = nullptr;  // accepted rows of the previous step, written on the device
   uint32_t packedStride = 0, hiddenStride = 0, pendingRows = 0;
   bool tiledHeads = false;
+  // Trees (runtime/ops/GDN.hpp:112-119 GdnTapeLane, runtime/metal/abi/VerifyTree.h:24-45): the block's tree rows (none: a
+  // chain), and the path the previous step accepted as a row mask of its tape, on the host or as a device word (neither:
+  // the tape's first pendingRows rows).
+  const Buffer *treeRows = nullptr, *pendingPathDevice = nullptr;
+  uint32_t pendingPath = 0;
 };
 
 class GDN {
@@ -91,6 +96,15 @@ class GDN {
     a.pending = b.pendingTape->describe(), a.step = b.stepTape->describe();
     a.hidden = b.hidden.as();
     a.pending_rows_dev = b.pendingRowsDevice ? b.pendingRowsDevice->as<uint32_t>() : nullptr;
+    if (b.treeRows) {
+      requireBytes(*b.treeRows, size_t(rows) * 8, "GDN::addDecode tree rows");
+      a.tree = b.treeRows->as();
+    }
+    if (b.pendingPathDevice) {
+      requireBytes(*b.pendingPathDevice, 4, "GDN::addDecode pending path");
+      a.pending_path_dev = b.pendingPathDevice->as<uint32_t>();
+    }
+    a.pending_path = b.pendingPath;
     a.rows = rows, a.pending_rows = b.pendingRows, a.key_heads = s.keyHeads, a.value_heads = s.valueHeads;
     a.qkvz_stride = b.packedStride, a.ab_stride = 2 * s.valueHeads, a.hidden_stride = b.hiddenStride, a.tiled = b.tiledHeads;
     check(sb_gdn_verify(graph.stream, &a));

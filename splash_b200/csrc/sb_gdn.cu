@@ -38,6 +38,12 @@ struct GdnParams {
   uint32_t *counters;   // [value_heads]
 };
 
+// Row of the n-th token (from the anchor) of a path mask.
+__device__ __forceinline__ uint32_t path_row(uint32_t path, uint32_t n) {
+  for (uint32_t i = 0; i < n; ++i) path &= path - 1;
+  return path ? uint32_t(__ffs(int(path))) - 1u : 0u;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -46,6 +52,10 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 // The kGdnSplit CTAs of a value head form a cluster: the fused gate projection is divided among them by rows and
 // meets in every CTA's shared memory.
+// kTree: the rows may form a tree and the pending path may be any row mask (tap tables, transformed queries); without
+// it the rows are a chain and the pending rows the tape's first, which is the verify step's usual case and keeps the
+// indirections out of its kernel.
+template <bool kTree>
 __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads, 2) gdn_kernel(const GdnParams p) {
   const SbGdnArgs &a = p.a;
   __shared__ float q_s[kGdnRows][kD], k_s[kGdnRows][kD], pk_s[kGdnRows][kD];
@@ -55,6 +65,9 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
   __shared__ __align__(16) uint16_t in_s[kGdnRows + 3][2 * kD + kGdnVd];
   __shared__ uint2 w_s[2 * kD + kGdnVd];
   __shared__ uint32_t s_last;
+  __shared__ uint8_t tap_s[kGdnRows][kTaps];   // where in in_s a row's four convolution taps lie (its path's last tokens)
+  __shared__ uint32_t path_s[kGdnRows];         // the row's path from the anchor, itself included
+  __shared__ float coef_s[kGdnRows][kGdnRows];  // tree rows: the coefficient of each row of the path
   pdl_launch_dependents();
   const bool fused_gates = a.gate_weight && a.rows > 0;
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");  // "this CTA runs", waited for before the first store into a peer CTA
@@ -88,7 +101,24 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
     S[4 * c] = s4.x, S[4 * c + 1] = s4.y, S[4 * c + 2] = s4.z, S[4 * c + 3] = s4.w;
   }
   pdl_wait();
-  const uint32_t pending = a.pending_rows_dev ? min(*a.pending_rows_dev, uint32_t(kGdnRows)) : a.pending_rows;
+  // The previous step's accepted path in its tape: a row mask, or the tape's first rows.
+  uint32_t pending_path = a.pending_path_dev ? *a.pending_path_dev : a.pending_path;
+  if (!a.pending_path_dev && !a.pending_path) {
+    const uint32_t n = a.pending_rows_dev ? min(*a.pending_rows_dev, uint32_t(kGdnRows)) : a.pending_rows;
+    pending_path = (1u << n) - 1u;
+  }
+  pending_path &= (1u << kGdnRows) - 1u;
+  const uint32_t pending = uint32_t(__popc(pending_path));
+  auto pending_row = [&](uint32_t n) { return kTree ? path_row(pending_path, n) : n; };
+  if (kTree && tid < rows) {
+    const uint32_t path = (a.tree ? static_cast<const uint2 *>(a.tree)[tid].x & ((2u << tid) - 1u) : (2u << tid) - 1u) | (1u << tid);
+    const int depth = __popc(path) - 1;
+    for (int tap = 0; tap < kTaps; ++tap) {
+      const int at = depth - 3 + tap;  // the tap's token, counted from the anchor; before it: the carried history
+      tap_s[tid][tap] = uint8_t(at < 0 ? 3 + at : 3 + int(path_row(path, uint32_t(at))));
+    }
+    path_s[tid] = path;
+  }
   // Fused gate projection: this CTA takes rows 4 vs .. 4 vs + 3; warp w computes group w's partial sums of those rows x
   // {b, a} over the layer's normalised input and stores them into all four CTAs of the head; the rows' threads add the
   // 8 groups in order below (the order of sb_linear_f32, so the bits agree with the unfused way).
@@ -126,7 +156,7 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
       src = qkvz + size_t(r - 3) * a.qkvz_stride + ch;
     } else {
       const int hsrc = int(pending) - 3 + int(r);
-      src = hsrc >= 0 ? pin + size_t(hsrc) * C + ch : cs_in + size_t(3 + hsrc) * C + ch;
+      src = hsrc >= 0 ? pin + size_t(pending_row(uint32_t(hsrc))) * C + ch : cs_in + size_t(3 + hsrc) * C + ch;
     }
     *reinterpret_cast<uint4 *>(&in_s[r][lc]) = *reinterpret_cast<const uint4 *>(src);
   }
@@ -140,7 +170,7 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
                         bf16_bits_to_float(wv.y >> 16)};
     float value = 0.0f;
 #pragma unroll
-    for (int tap = 0; tap < kTaps; ++tap) value = __fadd_rn(value, __fmul_rn(bf16_bits_to_float(in_s[row + tap][lc]), w[tap]));
+    for (int tap = 0; tap < kTaps; ++tap) value = __fadd_rn(value, __fmul_rn(bf16_bits_to_float(in_s[kTree ? uint32_t(tap_s[row][tap]) : row + tap][lc]), w[tap]));
     value = round_bf16(value);
     return round_bf16(silu_f(value));
   };
@@ -161,13 +191,15 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
   }
   // pending rows' keys, values and gates from their tape
   for (uint32_t i = tid; i < pending * kD; i += kGdnThreads)
-    pk_s[i / kD][i % kD] = bf16_bits_to_float(static_cast<const uint16_t *>(a.pending.k)[size_t(i / kD) * KW + kh * kD + i % kD]);
+    pk_s[i / kD][i % kD] =
+        bf16_bits_to_float(static_cast<const uint16_t *>(a.pending.k)[size_t(pending_row(i / kD)) * KW + kh * kD + i % kD]);
   for (uint32_t i = tid; i < pending * kGdnVd; i += kGdnThreads)
-    pv_s[i / kGdnVd][i % kGdnVd] =
-        bf16_bits_to_float(static_cast<const uint16_t *>(a.pending.v)[size_t(i / kGdnVd) * VW + h * kD + vd0 + i % kGdnVd]);
+    pv_s[i / kGdnVd][i % kGdnVd] = bf16_bits_to_float(
+        static_cast<const uint16_t *>(a.pending.v)[size_t(pending_row(i / kGdnVd)) * VW + h * kD + vd0 + i % kGdnVd]);
   if (tid < pending) {
-    pbeta_s[tid] = bf16_bits_to_float(static_cast<const uint16_t *>(a.pending.beta)[size_t(tid) * VH + h]);
-    pdecay_s[tid] = a.pending.decay[size_t(tid) * VH + h];
+    const uint32_t trow = pending_row(tid);
+    pbeta_s[tid] = bf16_bits_to_float(static_cast<const uint16_t *>(a.pending.beta)[size_t(trow) * VH + h]);
+    pdecay_s[tid] = a.pending.decay[size_t(trow) * VH + h];
   }
   if (tid < rows) {
     float bb, aa;
@@ -282,7 +314,60 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
 #pragma unroll
   for (int c = 0; c < 4; ++c)
     *reinterpret_cast<float4 *>(a.state_out + sbase + 32 * c) = make_float4(S[4 * c], S[4 * c + 1], S[4 * c + 2], S[4 * c + 3]);
-  for (uint32_t t = 0; t < rows; ++t) advance(k_s[t], v_s[t], decay_s[t], beta_s[t], q_s[t], o_s[t]);
+  bool chain = true;
+  if (kTree)
+    for (uint32_t r = 0; r < rows; ++r) chain = chain && path_s[r] == (2u << r) - 1u;
+  if (!kTree || chain) {
+    for (uint32_t t = 0; t < rows; ++t) advance(k_s[t], v_s[t], decay_s[t], beta_s[t], q_s[t], o_s[t]);
+  } else {
+    // Tree rows (runtime/metal/kernels/decode/gdn.metal:418-478): a row's output is the state after its own path,
+    // S_committed z + sum_j c_j v_j, with the query taken up the path: c_j = beta_j (k_j . z_j), z_j-1 = d_j (z_j - c_j k_j).
+    // A warp transforms rows warp and warp + 8 (four dimensions a lane); the transformed queries take the queries' place.
+    float z[2][4], cf[2] = {0.0f, 0.0f};
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const uint32_t r = warp + 8 * pass;
+      if (r >= rows) continue;
+      const float4 q4 = *reinterpret_cast<const float4 *>(&q_s[r][4 * lane]);
+      z[pass][0] = q4.x, z[pass][1] = q4.y, z[pass][2] = q4.z, z[pass][3] = q4.w;
+      for (uint32_t up = path_s[r]; up;) {
+        const uint32_t row = 31u - uint32_t(__clz(int(up)));
+        up &= ~(1u << row);
+        const float4 k4 = *reinterpret_cast<const float4 *>(&k_s[row][4 * lane]);
+        const float c = beta_s[row] * warp_sum(k4.x * z[pass][0] + k4.y * z[pass][1] + k4.z * z[pass][2] + k4.w * z[pass][3]);
+        const float d = decay_s[row];
+        z[pass][0] = d * (z[pass][0] - c * k4.x), z[pass][1] = d * (z[pass][1] - c * k4.y);
+        z[pass][2] = d * (z[pass][2] - c * k4.z), z[pass][3] = d * (z[pass][3] - c * k4.w);
+        if (lane == row) cf[pass] = c;
+      }
+    }
+    __syncthreads();  // every warp has read the queries it needs
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const uint32_t r = warp + 8 * pass;
+      if (r >= rows) continue;
+      *reinterpret_cast<float4 *>(&q_s[r][4 * lane]) = make_float4(z[pass][0], z[pass][1], z[pass][2], z[pass][3]);
+      if (lane < kGdnRows) coef_s[r][lane] = cf[pass];
+    }
+    __syncthreads();
+    for (uint32_t t = 0; t < rows; ++t) {
+      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const float4 q4 = *reinterpret_cast<const float4 *>(&q_s[t][scol + 32 * c]);
+        acc[0] = fmaf(S[4 * c], q4.x, acc[0]), acc[1] = fmaf(S[4 * c + 1], q4.y, acc[1]);
+        acc[2] = fmaf(S[4 * c + 2], q4.z, acc[2]), acc[3] = fmaf(S[4 * c + 3], q4.w, acc[3]);
+      }
+      float res = group_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
+      if ((lane & 7) == 0) {
+        for (uint32_t up = path_s[t]; up; up &= up - 1) {
+          const uint32_t j = uint32_t(__ffs(int(up))) - 1u;
+          res = fmaf(coef_s[t][j], v_s[j][srow], res);
+        }
+        o_s[t][srow] = res;
+      }
+    }
+  }
   __syncthreads();
   // recurrent outputs (bf16) of this CTA's value dimensions -> scratch
   for (uint32_t i = tid; i < rows * kGdnVd; i += kGdnThreads)
@@ -315,6 +400,11 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
   if (tid == 0) p.counters[h] = 0;
 }
 
+
+// Whether the call needs the tree kernel: tree rows, or a pending path that is not known here to be the tape's first rows.
+static bool needs_tree_kernel(const SbGdnArgs &a) {
+  return a.tree || a.pending_path_dev || (a.pending_path & (a.pending_path + 1u)) != 0;
+}
 
 // ---- the same step with no allocation anywhere ----
 // Some hosts of this library may not allocate device memory at all once they are running: a runtime that
@@ -364,8 +454,10 @@ extern "C" int sb_gdn_verify(void *stream, const SbGdnArgs *a) {
   SB_REQUIRE(a->qkvz_stride >= C + a->value_heads * kD && (a->gate_weight || a->ab_stride >= a->value_heads) && a->hidden_stride >= a->value_heads * kD,
              "sb_gdn_verify: a stride is below its row");
   SB_REQUIRE(a->rows == 0 || (a->step.inputs && a->step.k && a->step.v && a->step.beta && a->step.decay), "sb_gdn_verify: null tape of this step");
-  SB_REQUIRE((a->pending_rows == 0 && !a->pending_rows_dev) || (a->pending.inputs && a->pending.k && a->pending.v && a->pending.beta && a->pending.decay),
+  SB_REQUIRE((a->pending_rows == 0 && !a->pending_rows_dev && !a->pending_path && !a->pending_path_dev) ||
+                 (a->pending.inputs && a->pending.k && a->pending.v && a->pending.beta && a->pending.decay),
              "sb_gdn_verify: null pending tape");
+  SB_REQUIRE(a->pending_path < (1u << kGdnRows), "sb_gdn_verify: pending path 0x%x names rows above %d", a->pending_path, kGdnRows);
   SB_REQUIRE(a->state_in != a->state_out && a->conv_state_in != a->conv_state_out, "sb_gdn_verify: the committed cell is a second cell");
   SB_REQUIRE(!a->gate_weight || (a->gate_input && a->gate_k && a->gate_k % 8 == 0 && a->gate_input_stride >= a->gate_k && a->gate_input_stride % 8 == 0 &&
                                  (reinterpret_cast<uintptr_t>(a->gate_weight) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->gate_input) & 15) == 0),
@@ -381,7 +473,7 @@ extern "C" int sb_gdn_verify(void *stream, const SbGdnArgs *a) {
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = c.pdl ? 1 : 0;
-  SB_CUDA(cudaLaunchKernelEx(&cfg, gdn_kernel, p));
+  SB_CUDA(needs_tree_kernel(*a) ? cudaLaunchKernelEx(&cfg, gdn_kernel<true>, p) : cudaLaunchKernelEx(&cfg, gdn_kernel<false>, p));
   return SB_OK;
 }
 
@@ -401,8 +493,10 @@ extern "C" int sb_gdn_verify_static(void *stream, const SbGdnArgs *a) {
   SB_REQUIRE(a->qkvz_stride >= C + a->value_heads * kD && (a->gate_weight || a->ab_stride >= a->value_heads) && a->hidden_stride >= a->value_heads * kD,
              "sb_gdn_verify_static: a stride is below its row");
   SB_REQUIRE(a->rows == 0 || (a->step.inputs && a->step.k && a->step.v && a->step.beta && a->step.decay), "sb_gdn_verify_static: null tape of this step");
-  SB_REQUIRE((a->pending_rows == 0 && !a->pending_rows_dev) || (a->pending.inputs && a->pending.k && a->pending.v && a->pending.beta && a->pending.decay),
+  SB_REQUIRE((a->pending_rows == 0 && !a->pending_rows_dev && !a->pending_path && !a->pending_path_dev) ||
+                 (a->pending.inputs && a->pending.k && a->pending.v && a->pending.beta && a->pending.decay),
              "sb_gdn_verify_static: null pending tape");
+  SB_REQUIRE(a->pending_path < (1u << kGdnRows), "sb_gdn_verify_static: pending path 0x%x names rows above %d", a->pending_path, kGdnRows);
   SB_REQUIRE(a->state_in != a->state_out && a->conv_state_in != a->conv_state_out, "sb_gdn_verify_static: the committed cell is a second cell");
   SB_REQUIRE(!a->gate_weight || (a->gate_input && a->gate_k && a->gate_k % 8 == 0 && a->gate_input_stride >= a->gate_k && a->gate_input_stride % 8 == 0 &&
                                  (reinterpret_cast<uintptr_t>(a->gate_weight) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->gate_input) & 15) == 0),
@@ -415,7 +509,8 @@ extern "C" int sb_gdn_verify_static(void *stream, const SbGdnArgs *a) {
   uint32_t *counters = reinterpret_cast<uint32_t *>(scratch + kStaticRowsBytes);
   SB_CUDA(cudaMemsetAsync(counters, 0, kStaticMaxValueHeads * sizeof(uint32_t), as_stream(stream)));
   GdnParams p{*a, reinterpret_cast<uint16_t *>(scratch), counters};
-  gdn_kernel<<<dim3(kGdnSplit, a->value_heads), dim3(kGdnThreads), 0, as_stream(stream)>>>(p);
+  if (needs_tree_kernel(*a)) gdn_kernel<true><<<dim3(kGdnSplit, a->value_heads), dim3(kGdnThreads), 0, as_stream(stream)>>>(p);
+  else gdn_kernel<false><<<dim3(kGdnSplit, a->value_heads), dim3(kGdnThreads), 0, as_stream(stream)>>>(p);
   SB_CUDA(cudaGetLastError());
   return SB_OK;
 }

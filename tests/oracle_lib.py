@@ -80,7 +80,7 @@ class SoGdnArgs(ctypes.Structure):
                 ("conv_state_in", _P), ("conv_state_out", _P), ("state_in", _P), ("state_out", _P),
                 ("pending", SoGdnTape), ("step", SoGdnTape), ("hidden", _P),
                 ("rows", _U), ("pending_rows", _U), ("key_heads", _U), ("value_heads", _U), ("qkvz_stride", _U),
-                ("ab_stride", _U), ("hidden_stride", _U), ("tiled", _U)]
+                ("ab_stride", _U), ("hidden_stride", _U), ("tiled", _U), ("tree", _P), ("pending_path", _U)]
 
 
 class HostKv:

@@ -178,7 +178,7 @@ def test_attention_long_context_32k(kernel):
     assert cos > 0.9995 and np.abs(got - want64).max() < 0.02
 
 
-def gdn_case(lib, l, o, *, key_heads, value_heads, rows, pending_rows, tiled, seed, fused_gates=0):
+def gdn_case(lib, l, o, *, key_heads, value_heads, rows, pending_rows, tiled, seed, fused_gates=0, tree=None, pending_path=0):
     """fused_gates = k > 0: b and a are projections of a bf16 input [16, k] by fp32 rows [2 * value_heads, k]; the
     kernel computes them itself (gate_weight / gate_input) and the oracle gets what sb_linear_f32 gives for them."""
     rng = np.random.default_rng(seed)
@@ -215,7 +215,7 @@ def gdn_case(lib, l, o, *, key_heads, value_heads, rows, pending_rows, tiled, se
     tape = lambda t: ol.SoGdnTape(P(t["inputs"]), P(t["k"]), P(t["v"]), P(t["beta"]), P(t["decay"]))
     args = ol.SoGdnArgs(P(qkvz), P(b), P(a), P(conv_w), P(a_scale), P(dt_bias), P(norm_w), P(cs_in), P(cs_out), P(state),
                         P(state_out), tape(pend), tape(step), P(hidden), rows, pending_rows, key_heads, value_heads,
-                        stride, value_heads, VW, int(tiled))
+                        stride, value_heads, VW, int(tiled), P(tree) if tree is not None else None, pending_path)
     o.so_gdn_verify(ctypes.byref(args))
     up = lib.DeviceBuffer.from_numpy
     d = {n: up(x) for n, x in dict(qkvz=qkvz, b=b, a=a, conv_w=conv_w, a_scale=a_scale, dt_bias=dt_bias, norm_w=norm_w,
@@ -227,6 +227,10 @@ def gdn_case(lib, l, o, *, key_heads, value_heads, rows, pending_rows, tiled, se
     ga = lib.SbGdnArgs(d["qkvz"].ptr, d["b"].ptr, d["a"].ptr, d["conv_w"].ptr, d["a_scale"].ptr, d["dt_bias"].ptr,
                        d["norm_w"].ptr, d["cs_in"].ptr, dcs.ptr, d["state"].ptr, dst.ptr, dtape(dp), dtape(ds), dh.ptr, None,
                        rows, pending_rows, key_heads, value_heads, stride, value_heads, VW, int(tiled))
+    if tree is not None:
+        tree_dev = up(tree)
+        ga.tree = tree_dev.ptr
+    ga.pending_path = pending_path
     if gate:
         ga.b = ga.a = None
         ga.gate_weight, ga.gate_input, ga.gate_k, ga.gate_input_stride = gate["w"].ptr, gate["x"].ptr, gate["k"], gate["k"]
@@ -260,6 +264,41 @@ def test_gdn_verify_within_reference_gates(cfg):
     g, w = ol.bf2f(got["hidden"][:rows]).astype(np.float64), ol.bf2f(want["hidden"][:rows]).astype(np.float64)
     bad = np.abs(g - w) > 3 * ulp_bf16(w) + 2e-3 * np.abs(w).mean()
     assert bad.mean() <= 0.01
+
+
+def _tree_rows(parent):
+    tree = np.zeros((len(parent), 2), np.uint32)
+    for r in range(len(parent)):
+        tree[r, 0] = (1 << r) | (tree[parent[r], 0] if r else 0)
+        tree[r, 1] = parent[r] | ((bin(int(tree[r, 0])).count("1") - 1) << 16)
+    return tree
+
+
+@pytest.mark.parametrize("cfg", [
+    dict(key_heads=16, value_heads=48, tiled=True, seed=31, parent=[0, 0, 1, 2, 3, 4, 5, 6, 3, 8, 9, 10, 1, 12, 13, 0], pending_path=0b1000100101),
+    dict(key_heads=2, value_heads=6, tiled=False, seed=32, parent=[0, 0, 0, 0, 1, 1, 2, 4, 7], pending_path=0),
+    dict(key_heads=2, value_heads=4, tiled=False, seed=33, parent=[0, 0, 1, 2, 3, 4], pending_path=0b111),   # a chain given as a tree
+])
+def test_gdn_tree_paths_within_reference_gates(cfg):
+    """Tree rows: convolution taps along each row's path, outputs from the committed state along the path (the kernel by
+    the transformed query, the oracle by definition), the previous step's accepted path as a row mask of its tape."""
+    lib, l, o = _setup()
+    parent = cfg.pop("parent")
+    rows = len(parent)
+    got, want, _ = gdn_case(lib, l, o, rows=rows, pending_rows=0, tree=_tree_rows(parent), **cfg)
+    assert np.array_equal(got["cs"], want["cs"])
+    assert np.array_equal(got["inputs"][:rows], want["inputs"][:rows])
+    for n in ("k", "v", "beta"):
+        g, w = ol.bf2f(got[n][:rows]).astype(np.float64), ol.bf2f(want[n][:rows]).astype(np.float64)
+        assert (np.abs(g - w) <= 3 * ulp_bf16(w)).all(), n
+    assert np.abs(got["state"] - want["state"]).max() <= 1e-4 * np.abs(want["state"]).max()
+    g, w = ol.bf2f(got["hidden"][:rows]).astype(np.float64), ol.bf2f(want["hidden"][:rows]).astype(np.float64)
+    bad = np.abs(g - w) > 3 * ulp_bf16(w) + 2e-3 * np.abs(w).mean()
+    assert bad.mean() <= 0.01
+    # every row on its own: a branch's rows differ from what the chain order would give
+    for r in range(rows):
+        gr, wr = g[r], w[r]
+        assert np.abs(gr - wr).max() <= 0.02 * max(1e-6, np.abs(wr).max()), r
 
 
 def test_gdn_fused_gate_projection_equals_separate_projection():

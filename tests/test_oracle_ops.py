@@ -223,3 +223,57 @@ def test_penalty_pass_counts_the_path():
     want[1, 7] = want[3, 7] = 0.5 - (0.25 * 1 + 0.5)  # row 1 and its child hold the first 7
     want[2, 7] = 0.5 - (0.25 * 1 + 0.5)               # row 2 holds its own 7 only
     assert np.array_equal(logits, want)
+
+
+def _gdn_oracle(o, rng_seed, rows, tree=None, pending_rows=0, pending_path=0, order=None, KH=1, VH=2):
+    """so_gdn_verify on seeded inputs; `order` permutes the block's rows (inputs and gates) before the call."""
+    rng = np.random.default_rng(rng_seed)
+    D = 128
+    KW, VW = KH * D, VH * D
+    C = 2 * KW + VW
+    stride = C + VW
+    bf = lambda shape, scale: ol.f2bf((rng.standard_normal(shape) * scale).astype(np.float32))
+    qkvz, b, a = bf((16, stride), 1.0), bf((16, VH), 1.0), bf((16, VH), 1.0)
+    conv_w = bf((C, 4), 0.4)
+    a_scale = (-np.exp(rng.uniform(-3, 0.5, VH))).astype(np.float32)
+    dt_bias, norm_w = bf((VH,), 0.5), (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    cs_in = bf((3, C), 1.0)
+    state = (rng.standard_normal((VH, D, D)) * 0.05).astype(np.float32)
+    pend = dict(inputs=bf((16, C), 1.0), k=bf((16, KW), 0.09), v=bf((16, VW), 0.5),
+                beta=ol.f2bf(rng.uniform(0.1, 0.9, (16, VH)).astype(np.float32)), decay=rng.uniform(0.5, 1.0, (16, VH)).astype(np.float32))
+    if order is not None:
+        qkvz[:len(order)], b[:len(order)], a[:len(order)] = qkvz[order].copy(), b[order].copy(), a[order].copy()
+    step = dict(inputs=np.zeros((16, C), np.uint16), k=np.zeros((16, KW), np.uint16), v=np.zeros((16, VW), np.uint16),
+                beta=np.zeros((16, VH), np.uint16), decay=np.zeros((16, VH), np.float32))
+    cs_out, state_out, hidden = np.zeros_like(cs_in), np.zeros_like(state), np.zeros((16, VW), np.uint16)
+    tape = lambda t: ol.SoGdnTape(P(t["inputs"]), P(t["k"]), P(t["v"]), P(t["beta"]), P(t["decay"]))
+    args = ol.SoGdnArgs(P(qkvz), P(b), P(a), P(conv_w), P(a_scale), P(dt_bias), P(norm_w), P(cs_in), P(cs_out), P(state), P(state_out),
+                        tape(pend), tape(step), P(hidden), rows, pending_rows, KH, VH, stride, VH, VW, 0,
+                        P(tree) if tree is not None else None, pending_path)
+    o.so_gdn_verify(ctypes.byref(args))
+    return dict(hidden=hidden, cs=cs_out, state=state_out, step=step)
+
+
+def test_gdn_tree_rows_equal_their_paths_run_as_chains():
+    """A row of a tree gives what the same row gives at the end of a chain made of its path: anchor 0, a branch
+    1-2-3 and a branch 4-5 under row 1. The pending path in the tape is a row mask, folded in depth order."""
+    o = ol.bind_ops(ol.load())
+    parent = [0, 0, 1, 2, 1, 4]
+    rows = len(parent)
+    tree = np.zeros((rows, 2), np.uint32)
+    for r in range(rows):
+        tree[r, 0] = (1 << r) | (tree[parent[r], 0] if r else 0)
+        tree[r, 1] = parent[r] | ((bin(int(tree[r, 0])).count("1") - 1) << 16)
+    pending_path = 0b101001   # tape rows 0, 3, 5 of the previous step
+    got = _gdn_oracle(o, 3, rows, tree=tree, pending_path=pending_path)
+    for leaf in (3, 5):
+        path = [r for r in range(rows) if tree[leaf, 0] >> r & 1]
+        chain = _gdn_oracle(o, 3, len(path), pending_path=pending_path, order=path)
+        for depth, r in enumerate(path):
+            assert np.array_equal(got["hidden"][r], chain["hidden"][depth]), (leaf, r)
+            assert np.array_equal(got["step"]["k"][r], chain["step"]["k"][depth])
+        assert np.array_equal(got["state"], chain["state"]) and np.array_equal(got["cs"], chain["cs"])
+    # a pending path that is the tape's first rows equals pending_rows
+    a = _gdn_oracle(o, 5, 4, pending_rows=3)
+    b = _gdn_oracle(o, 5, 4, pending_path=0b111)
+    assert np.array_equal(a["hidden"], b["hidden"]) and np.array_equal(a["state"], b["state"])
