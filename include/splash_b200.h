@@ -265,6 +265,9 @@ SB_API int sb_attn_verify(void *stream, const SbAttnArgs *args);
  * path_mask_dev: device u32, the accepted path's row mask (sb_accept's retained_rows). */
 SB_API int sb_kv_path_commit(void *stream, const SbKvLayer *cache, const uint32_t *page_table, uint32_t committed,
                              const uint32_t *path_mask_dev);
+/* The same with the lane's position read from a device word, so a captured graph follows the lane. */
+SB_API int sb_kv_path_commit_at(void *stream, const SbKvLayer *cache, const uint32_t *page_table, const uint32_t *committed_dev,
+                                const uint32_t *path_mask_dev);
 
 /* ---- Gated DeltaNet verify step ---- */
 
@@ -415,7 +418,12 @@ typedef struct SbTargetConfig {
 
 enum {
   SB_TARGET_ADVANCE = 1, /* the step commits: committed += retained, the next step folds the accepted rows */
-  SB_TARGET_GRAPH = 2    /* replay the step as a captured CUDA graph (captured on first use per parity) */
+  SB_TARGET_GRAPH = 2,   /* replay the step as a captured CUDA graph (captured on first use per parity) */
+  SB_TARGET_TREE = 4     /* the block is a tree: the target's `tree` buffer holds its SplashTreeRow rows (row 0 the anchor,
+                            parents before children; runtime/metal/abi/VerifyTree.h:24-45) instead of the chain the step
+                            writes there itself. Positions are the rows' depths, attention and GDN follow each row's path,
+                            the accepted path's KV rows move to their depths, and the next step folds the path's tape
+                            rows. The step after a tree step carries the flag too (a chain can be given as a tree). */
 };
 
 /* ---- tensor parallelism between the GPUs of one node ----
@@ -485,6 +493,10 @@ SB_API int sb_target_step(void *target, void *stream, uint32_t rows, float tempe
  * and waits. */
 SB_API int sb_target_verify(void *target, void *stream, const uint32_t *tokens_host, const float *uniforms_host, uint32_t rows,
                             float temperature, uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host);
+/* sb_target_verify for a tree of draft tokens: tree_host holds `rows` SplashTreeRow entries {ancestors u32, parent u16,
+ * depth u16}; sets SB_TARGET_TREE. out_tokens_host receives the accepted path's tokens. */
+SB_API int sb_target_verify_tree(void *target, void *stream, const uint32_t *tokens_host, const void *tree_host, const float *uniforms_host,
+                                 uint32_t rows, float temperature, uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host);
 /* Kernels one step launches, and the bytes its weights, cache and state stream (the roofline's numerator). */
 SB_API int sb_target_stats(void *target, uint32_t rows, uint32_t *out_launches, uint64_t *out_weight_bytes, uint64_t *out_kv_bytes,
                            uint64_t *out_state_bytes);

@@ -75,7 +75,8 @@ class QwenTarget {
   explicit QwenTarget(const SbTargetConfig &whole);
 
   // Appends one verify step of `rows` rows to the graph. `parity` selects which GDN cell is current.
-  void encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance);
+  // `treeGiven`: the `tree` buffer holds the block's rows (a tree); otherwise the step writes a chain's there.
+  void encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool treeGiven = false);
 
   const SbTargetConfig &config() const { return cfg_; }   // the whole model
   const SbTargetConfig &local() const { return loc_; }    // this rank's heads and intermediate width (the vocabulary stays whole)
@@ -91,6 +92,7 @@ class QwenTarget {
   uint64_t kvBytes(uint32_t visible) const;
   uint64_t stateBytes() const;
 
+  Buffer pendingPath;  // the row mask, in the previous step's tape, of the path it accepted (tree steps)
   Buffer tokens, uniforms, committed, pendingRows, results, selected, logits, hidden[2], tree, positions, invFreq, cosine, sine;
   uint32_t committedHost = 0;  // bound of the device's committed word, for extents and the attention plan
   uint32_t step = 0;
@@ -191,7 +193,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   for (auto &h : hidden) h = Buffer::allocate(size_t(kVerifyRows) * H * 2);
   logits = tp_ ? tp_->gathered() : Buffer::allocate(size_t(kVerifyRows) * c.vocab * 4);
   tokens = Buffer::allocate(kVerifyRows * 4), selected = Buffer::allocate(kVerifyRows * 4), results = Buffer::allocate(16);
-  uniforms = Buffer::allocate(80 * 4), committed = Buffer::allocate(4), pendingRows = Buffer::allocate(4);
+  uniforms = Buffer::allocate(80 * 4), committed = Buffer::allocate(4), pendingRows = Buffer::allocate(4), pendingPath = Buffer::allocate(4);
   tree = Buffer::allocate(kVerifyRows * 8), positions = Buffer::allocate(kVerifyRows * 4);
   invFreq = Buffer::allocate(std::max(1u, c.rotary_pairs) * 4);
   cosine = Buffer::allocate(size_t(kVerifyRows) * std::max(1u, c.rotary_pairs) * 4);
@@ -246,12 +248,12 @@ inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) co
 }
 
 // Launched before and after the operator sequence (sb_target.cu).
-void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer &tree, const Buffer &positions, uint32_t rows);
+void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer &tree, const Buffer &positions, uint32_t rows, bool treeGiven);
 // (with a tensor-parallel group the step's end also advances the group's exchange count by `exchanges`)
-void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, bool advance,
-                   void *tpGroup, uint32_t exchanges);
+void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, const Buffer &pendingPath,
+                   bool advance, void *tpGroup, uint32_t exchanges);
 
-inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance) {
+inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool treeGiven) {
   using namespace ops;
   if (rows < 1 || rows > kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: 1 to 16 rows");
   if (committedHost + rows > cfg_.max_context + kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: past the context bound");
@@ -259,7 +261,7 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   const uint32_t H = c.hidden, D = c.head_dim;
   if (tp_ && !tp_->connected()) throw std::invalid_argument("QwenTarget::encodeVerify: the tensor-parallel ranks are not connected");
   uint32_t exchange = 0;  // the place of the next exchange among the step's
-  launchStepBegin(graph, committed, tree, positions, rows);
+  launchStepBegin(graph, committed, tree, positions, rows, treeGiven);
   if (c.rotary_pairs) RoPE::addTreeTables(graph, positions, invFreq, cosine, sine, rows, 1.0f, c.rotary_pairs);
   Embedding::add(graph, tokens, embedding_, hidden[0], rows, H);
   uint32_t cur = 0;
@@ -301,7 +303,7 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
       PagedAttention::addProjection(graph, kv_, w.pages, packed_, packedStride_, w.qNorm, w.kNorm, cosine, sine, pageTable_, queries_, rows,
                                     c.q_heads, c.gated_attention != 0, c.rotary_pairs, committedHost, &committed);
       mixedWidth = c.q_heads * D;
-      PagedAttention::addAttention(graph, kv_, w.pages, queries_, packed_, packedStride_, pageTable_, nullptr, mixed_, mixedWidth, rows,
+      PagedAttention::addAttention(graph, kv_, w.pages, queries_, packed_, packedStride_, pageTable_, treeGiven ? &tree : nullptr, mixed_, mixedWidth, rows,
                                    c.q_heads, c.gated_attention != 0, committedHost, &committed);
     } else {
       // The alpha / beta projection of the normalised input runs inside the GDN kernel (same sums as
@@ -312,7 +314,9 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
       g.mixerNorm = w.ssmNorm, g.current = w.cells[parity], g.next = w.cells[parity ^ 1];
       g.pendingTape = &w.tapes[parity ^ 1], g.stepTape = &w.tapes[parity];
       mixedWidth = gdn_.valueWidth();
-      g.hidden = mixed_, g.pendingRowsDevice = &pendingRows, g.packedStride = packedStride_, g.hiddenStride = mixedWidth;
+      g.hidden = mixed_, g.packedStride = packedStride_, g.hiddenStride = mixedWidth;
+      if (treeGiven) g.treeRows = &tree, g.pendingPathDevice = &pendingPath;
+      else g.pendingRowsDevice = &pendingRows;
       g.tiledHeads = c.tiled_heads != 0;
       GDN::addDecode(graph, g, gdn_, rows);
     }
@@ -340,7 +344,13 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   ab.inputTokens = tokens, ab.treeRows = tree, ab.outputTokens = selected, ab.results = results;
   Sampling::addAcceptance(graph, ab, rows, kVerifyRows);
   if (tp_ && exchange != exchangesPerStep()) throw std::logic_error("QwenTarget::encodeVerify: exchange count");
-  launchStepEnd(graph, results, committed, pendingRows, advance, tp_ ? tp_->group() : nullptr, exchange);
+  // The accepted path's KV rows move from their rows' slots to their depths' (a chain's are there already).
+  if (treeGiven && advance) {
+    const Buffer pathMask = results.view(8, 4);
+    for (LayerWeights &w : layers_)
+      if (w.attention) PagedAttention::addPathCommit(graph, kv_, w.pages, pageTable_, committedHost, pathMask, &committed);
+  }
+  launchStepEnd(graph, results, committed, pendingRows, pendingPath, advance, tp_ ? tp_->group() : nullptr, exchange);
 }
 
 }  // namespace splash::b200::model

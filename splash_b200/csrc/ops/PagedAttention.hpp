@@ -67,10 +67,11 @@ class PagedAttention {
 
   // Moves an accepted tree path's rows to the slots of their depths; a chain's rows are in place.
   static void addPathCommit(CommandGraph &graph, const kv::Layout &l, const kv::LayerPages &pages, const Buffer &pageTable,
-                            uint32_t committed, const Buffer &pathMask) {
+                            uint32_t committed, const Buffer &pathMask, const Buffer *committedDevice = nullptr) {
     requireBytes(pathMask, 4, "PagedAttention::addPathCommit path");
     const SbKvLayer c = describe(l, pages);
-    check(sb_kv_path_commit(graph.stream, &c, pageTable.as<uint32_t>(), committed, pathMask.as<uint32_t>()));
+    if (committedDevice) check(sb_kv_path_commit_at(graph.stream, &c, pageTable.as<uint32_t>(), committedDevice->as<uint32_t>(), pathMask.as<uint32_t>()));
+    else check(sb_kv_path_commit(graph.stream, &c, pageTable.as<uint32_t>(), committed, pathMask.as<uint32_t>()));
     ++graph.launches;
   }
 };

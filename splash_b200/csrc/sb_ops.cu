@@ -218,9 +218,11 @@ __global__ void __launch_bounds__(D) attn_store_kernel(const StoreParams p) {
 }
 
 // ---- path commit: grid (kv_heads), head_dim threads; rows move in depth order ----
-__global__ void kv_path_commit_kernel(SbKvLayer c, const uint32_t *page_table, uint32_t committed, const uint32_t *path_mask) {
+__global__ void kv_path_commit_kernel(SbKvLayer c, const uint32_t *page_table, uint32_t committed, const uint32_t *committed_dev,
+                                      const uint32_t *path_mask) {
   pdl_launch_dependents();
   pdl_wait();
+  if (committed_dev) committed = *committed_dev;
   const uint32_t mask = *path_mask, h = blockIdx.x, d = threadIdx.x, D = c.head_dim;
   uint32_t depth = 0;
   for (uint32_t row = 0; row < 32; ++row) {
@@ -662,7 +664,17 @@ int sb_kv_path_commit(void *stream, const SbKvLayer *cache, const uint32_t *page
   int st = check_cache(*cache, "sb_kv_path_commit");
   if (st != SB_OK) return st;
   return launch(kv_path_commit_kernel, dim3(cache->kv_heads), dim3(cache->head_dim), as_stream(stream), *cache, page_table,
-                committed, path_mask_dev);
+                committed, static_cast<const uint32_t *>(nullptr), path_mask_dev);
+}
+
+int sb_kv_path_commit_at(void *stream, const SbKvLayer *cache, const uint32_t *page_table, const uint32_t *committed_dev,
+                         const uint32_t *path_mask_dev) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(cache && page_table && committed_dev && path_mask_dev, "sb_kv_path_commit_at: null pointer");
+  int st = check_cache(*cache, "sb_kv_path_commit_at");
+  if (st != SB_OK) return st;
+  return launch(kv_path_commit_kernel, dim3(cache->kv_heads), dim3(cache->head_dim), as_stream(stream), *cache, page_table, 0u, committed_dev,
+                path_mask_dev);
 }
 
 uint64_t sb_sample_workspace_bytes(uint32_t rows, uint32_t vocab) {

@@ -14,17 +14,18 @@ namespace sb {
 
 // ---- step bookkeeping kernels ----
 // positions[row] = committed + depth(row) and the chain's tree rows (parent = row - 1).
-__global__ void step_begin_kernel(const uint32_t *committed, uint2 *tree, uint32_t *positions, uint32_t rows) {
+// With a tree given, the rows stay as the caller wrote them and a row's position is the anchor's plus its depth.
+__global__ void step_begin_kernel(const uint32_t *committed, uint2 *tree, uint32_t *positions, uint32_t rows, uint32_t tree_given) {
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t r = threadIdx.x;
   if (r >= rows) return;
-  tree[r] = make_uint2((2u << r) - 1u, (r ? r - 1 : 0) | (r << 16));
-  positions[r] = *committed + r;
+  if (!tree_given) tree[r] = make_uint2((2u << r) - 1u, (r ? r - 1 : 0) | (r << 16));
+  positions[r] = *committed + (tree_given ? tree[r].y >> 16 : r);
 }
 // The lane's commit: the retained rows become history; the next step folds them into the GDN state.
-__global__ void step_end_kernel(const uint32_t *results, uint32_t *committed, uint32_t *pending_rows, uint32_t advance, uint32_t *tp_epoch,
-                                uint32_t tp_exchanges) {
+__global__ void step_end_kernel(const uint32_t *results, uint32_t *committed, uint32_t *pending_rows, uint32_t *pending_path, uint32_t advance,
+                                uint32_t *tp_epoch, uint32_t tp_exchanges) {
   pdl_wait();
   if (threadIdx.x == 0) {
     // The next step's exchanges are numbered after this step's. Their kernels read the count when they start, and
@@ -33,8 +34,10 @@ __global__ void step_end_kernel(const uint32_t *results, uint32_t *committed, ui
     if (advance) {
       *committed += results[0];
       *pending_rows = results[0];
+      *pending_path = results[2];
     } else {
       *pending_rows = 0;
+      *pending_path = 0;
     }
     __threadfence();
   }
@@ -124,7 +127,7 @@ struct Target {
 }  // namespace sb
 
 namespace splash::b200::model {
-void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer &tree, const Buffer &positions, uint32_t rows) {
+void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer &tree, const Buffer &positions, uint32_t rows, bool treeGiven) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(1), cfg.blockDim = dim3(32), cfg.stream = sb::as_stream(graph.stream);
   cudaLaunchAttribute attr[1];
@@ -132,12 +135,12 @@ void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = graph.pdl ? 1 : 0;
   if (cudaLaunchKernelEx(&cfg, sb::step_begin_kernel, static_cast<const uint32_t *>(committed.as<uint32_t>()), tree.as<uint2>(),
-                         positions.as<uint32_t>(), rows) != cudaSuccess)
+                         positions.as<uint32_t>(), rows, treeGiven ? 1u : 0u) != cudaSuccess)
     throw BackendError(SB_ERR_CUDA, "step_begin launch failed");
   ++graph.launches;
 }
-void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, bool advance,
-                   void *tpGroup, uint32_t exchanges) {
+void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, const Buffer &pendingPath,
+                   bool advance, void *tpGroup, uint32_t exchanges) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(1), cfg.blockDim = dim3(32), cfg.stream = sb::as_stream(graph.stream);
   cudaLaunchAttribute attr[1];
@@ -145,7 +148,7 @@ void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &com
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = graph.pdl ? 1 : 0;
   if (cudaLaunchKernelEx(&cfg, sb::step_end_kernel, static_cast<const uint32_t *>(results.as<uint32_t>()), committed.as<uint32_t>(),
-                         pendingRows.as<uint32_t>(), advance ? 1u : 0u, sb::tp_epoch_word(tpGroup), exchanges) != cudaSuccess)
+                         pendingRows.as<uint32_t>(), pendingPath.as<uint32_t>(), advance ? 1u : 0u, sb::tp_epoch_word(tpGroup), exchanges) != cudaSuccess)
     throw BackendError(SB_ERR_CUDA, "step_end launch failed");
   ++graph.launches;
 }
@@ -187,6 +190,7 @@ int sb_target_create(const SbTargetConfig *config, void **out_target) {
     if (config->rotary_pairs) inv_freq_kernel<<<1, 256>>>(m.invFreq.as<float>(), config->rotary_pairs, config->rope_theta);
     SB_CUDA(cudaMemset(m.committed.as(), 0, 4));
     SB_CUDA(cudaMemset(m.pendingRows.as(), 0, 4));
+    SB_CUDA(cudaMemset(m.pendingPath.as(), 0, 4));
     SB_CUDA(cudaMemset(m.uniforms.as(), 0, 80 * 4));
     SB_CUDA(cudaMemset(m.tokens.as(), 0, 64));
     SB_CUDA(cudaDeviceSynchronize());
@@ -246,6 +250,7 @@ int sb_target_reset(void *target, uint32_t committed) {
   SB_CUDA(cudaDeviceSynchronize());
   SB_CUDA(cudaMemcpy(m.committed.as(), &committed, 4, cudaMemcpyHostToDevice));
   SB_CUDA(cudaMemset(m.pendingRows.as(), 0, 4));
+  SB_CUDA(cudaMemset(m.pendingPath.as(), 0, 4));
   m.committedHost = committed;
   m.step = 0;
   return SB_OK;
@@ -307,7 +312,7 @@ int sb_target_randomize(void *target, uint64_t seed, uint32_t committed) {
 
 static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float temperature, uint32_t flags) {
   QwenTarget &m = *t->model;
-  const bool advance = (flags & SB_TARGET_ADVANCE) != 0;
+  const bool advance = (flags & SB_TARGET_ADVANCE) != 0, tree = (flags & SB_TARGET_TREE) != 0;
   const uint32_t parity = m.step & 1;
   return guarded([&] {
     if (flags & SB_TARGET_GRAPH) {
@@ -316,7 +321,7 @@ static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float tempera
       const uint32_t bound = std::min(m.config().max_context, (m.committedHost / 1024 + 2) * 1024);
       uint32_t tbits;
       memcpy(&tbits, &temperature, 4);
-      const auto key = std::make_tuple(rows, tbits, parity, uint32_t(advance), bound);
+      const auto key = std::make_tuple(rows, tbits, parity, uint32_t(advance) | (uint32_t(tree) << 1), bound);
       auto it = t->graphs.find(key);
       if (it == t->graphs.end()) {
         const uint32_t saved = m.committedHost;
@@ -325,7 +330,7 @@ static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float tempera
         SB_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
         int status = SB_OK;
         try {
-          m.encodeVerify(g, rows, temperature, parity, advance);
+          m.encodeVerify(g, rows, temperature, parity, advance, tree);
         } catch (...) {
           cudaGraph_t dead = nullptr;
           cudaStreamEndCapture(stream, &dead);
@@ -347,7 +352,7 @@ static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float tempera
       SB_CUDA(cudaGraphLaunch(it->second, stream));
     } else {
       CommandGraph g{stream, ctx().pdl, 0};
-      m.encodeVerify(g, rows, temperature, parity, advance);
+      m.encodeVerify(g, rows, temperature, parity, advance, tree);
       t->launches = g.launches;
     }
     ++m.step;
@@ -383,6 +388,24 @@ int sb_target_verify(void *target, void *stream, const uint32_t *tokens_host, co
   memcpy(out_tokens_host, t->results_pinned + 4, rows * 4);
   if (flags & SB_TARGET_ADVANCE) m.committedHost = before + t->results_pinned[0];  // the exact position again
   return SB_OK;
+}
+
+int sb_target_verify_tree(void *target, void *stream, const uint32_t *tokens_host, const void *tree_host, const float *uniforms_host, uint32_t rows,
+                          float temperature, uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target && tree_host, "sb_target_verify_tree: null pointer");
+  SB_REQUIRE(rows >= 1 && rows <= splash::b200::model::kVerifyRows, "sb_target_verify_tree: rows = %u outside 1..16", rows);
+  // Parents come before their children and a row's ancestors are rows before it: what the kernels index by.
+  const uint32_t *t = static_cast<const uint32_t *>(tree_host);
+  for (uint32_t r = 0; r < rows; ++r) {
+    const uint32_t ancestors = t[2 * r], parent = t[2 * r + 1] & 0xffffu, depth = t[2 * r + 1] >> 16;
+    SB_REQUIRE((ancestors >> r & 1u) && (ancestors & 1u) && !(ancestors >> (r + 1)) && parent <= r && depth + 1 == uint32_t(__builtin_popcount(ancestors)) &&
+                   (r == 0 || (parent < r && ancestors == (t[2 * parent] | (1u << r)))),
+               "sb_target_verify_tree: row %u is not a tree row (ancestors 0x%x, parent %u, depth %u)", r, ancestors, parent, depth);
+  }
+  Target *tg = static_cast<Target *>(target);
+  SB_CUDA(cudaMemcpyAsync(tg->model->tree.as(), tree_host, rows * 8, cudaMemcpyHostToDevice, tg->pick(stream)));
+  return sb_target_verify(target, stream, tokens_host, uniforms_host, rows, temperature, flags | SB_TARGET_TREE, out_tokens_host, out_results_host);
 }
 
 int sb_target_stats(void *target, uint32_t rows, uint32_t *out_launches, uint64_t *out_weight_bytes, uint64_t *out_kv_bytes,

@@ -6,7 +6,7 @@ import numpy as np
 from . import lib
 
 _P, _U, _F = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_float
-ADVANCE, GRAPH = 1, 2
+ADVANCE, GRAPH, TREE = 1, 2, 4
 
 
 class SbTargetConfig(ctypes.Structure):
@@ -40,6 +40,7 @@ def _bind():
     l.sb_target_reset.argtypes = [_P, _U]
     l.sb_target_step.argtypes = [_P, _P, _U, _F, _U]
     l.sb_target_verify.argtypes = [_P, _P, _P, _P, _U, _F, _U, _P, _P]
+    l.sb_target_verify_tree.argtypes = [_P, _P, _P, _P, _P, _U, _F, _U, _P, _P]
     l.sb_target_stats.argtypes = [_P, _U, ctypes.POINTER(_U), ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64),
                                   ctypes.POINTER(ctypes.c_uint64)]
     l._target_bound = True
@@ -95,12 +96,20 @@ class Target:
     def step(self, rows=16, temperature=0.0, flags=GRAPH, stream=None):
         lib.check(self.l.sb_target_step(self.handle, stream, rows, temperature, flags))
 
-    def verify(self, tokens, uniforms=None, temperature=0.0, flags=0, stream=None):
-        """One step from host buffers. Returns (retained tokens, retained, accepted, retained_rows mask)."""
+    def verify(self, tokens, uniforms=None, temperature=0.0, flags=0, stream=None, tree=None):
+        """One step from host buffers; `tree` (uint32 [rows, 2]: ancestors, parent | depth << 16) makes the block a tree.
+        Returns (retained tokens, retained, accepted, retained_rows mask)."""
         tokens = np.ascontiguousarray(tokens, np.uint32)
         rows = len(tokens)
         out_t, out_r = np.zeros(16, np.uint32), np.zeros(4, np.uint32)
         u = None if uniforms is None else np.ascontiguousarray(uniforms, np.float32)
+        if tree is not None:
+            tr = np.ascontiguousarray(tree, np.uint32)
+            assert tr.shape == (rows, 2)
+            lib.check(self.l.sb_target_verify_tree(self.handle, stream, tokens.ctypes.data_as(_P), tr.ctypes.data_as(_P),
+                                                   None if u is None else u.ctypes.data_as(_P), rows, temperature, flags,
+                                                   out_t.ctypes.data_as(_P), out_r.ctypes.data_as(_P)))
+            return out_t[:out_r[0]].copy(), int(out_r[0]), int(out_r[1]), int(out_r[2])
         lib.check(self.l.sb_target_verify(self.handle, stream, tokens.ctypes.data_as(_P), None if u is None else u.ctypes.data_as(_P),
                                           rows, temperature, flags, out_t.ctypes.data_as(_P), out_r.ctypes.data_as(_P)))
         return out_t[:out_r[0]].copy(), int(out_r[0]), int(out_r[1]), int(out_r[2])

@@ -94,8 +94,9 @@ def linear(o, fmt, W, n, k, X, rows, epilogue=0, aux=None, out_f32=False, W2=Non
     return out
 
 
-def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True, mutate=True):
-    """One verify step of a chain. Returns dict(logits, selected, retained, accepted, mask, tokens)."""
+def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True, mutate=True, tree=None):
+    """One verify step of a chain, or of the tree whose rows `tree` holds (uint32 [rows, 2]: ancestors, parent | depth << 16).
+    Returns dict(logits, selected, retained, accepted, mask, tokens)."""
     o = ol.bind_ops(ol.load())
     rows = len(tokens)
     H, D, I, V = cfg["hidden"], cfg["head_dim"], cfg["intermediate"], cfg["vocab"]
@@ -104,7 +105,11 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
     pairs = cfg["rotary_pairs"]
     committed, parity = s["committed"], s["step"] & 1
     tokens = np.ascontiguousarray(tokens, np.uint32)
-    pos = (committed + np.arange(rows)).astype(np.uint32)
+    chain_rows = np.zeros((rows, 2), np.uint32)
+    for r in range(rows):
+        chain_rows[r] = ((2 << r) - 1, max(r - 1, 0) | (r << 16))
+    rows_tree = chain_rows if tree is None else np.ascontiguousarray(tree, np.uint32)
+    pos = (committed + (rows_tree[:, 1] >> 16)).astype(np.uint32)
     inv = (np.float32(cfg["rope_theta"]) ** (-np.arange(pairs, dtype=np.float32) / np.float32(pairs))).astype(np.float32)
     cos, sin = np.zeros((rows, pairs), np.float32), np.zeros((rows, pairs), np.float32)
     o.so_rope_tables(P(pos), rows, P(inv), pairs, 1.0, P(cos), P(sin))
@@ -129,7 +134,7 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
                             pairs, ctypes.byref(desc), P(page_table), committed, P(queries))
             mixed = np.zeros((rows, QH * D), np.uint16)
             o.so_attention(P(queries), P(packed), attn_in, rows, QH, cfg["gated_attention"], ctypes.byref(desc), P(page_table),
-                           committed, None, P(mixed), QH * D, None)
+                           committed, P(rows_tree) if tree is not None else None, P(mixed), QH * D, None)
             mixed_w = QH * D
         else:
             gdn_in = conv + VH * 128
@@ -145,7 +150,8 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
             tape = lambda t: ol.SoGdnTape(P(t["inputs"]), P(t["k"]), P(t["v"]), P(t["beta"]), P(t["decay"]))
             args = ol.SoGdnArgs(P(packed), P(b), P(a), P(w[l, "ssm_conv"]), P(w[l, "ssm_a"]), P(w[l, "ssm_dt_bias"]), P(w[l, "ssm_norm"]),
                                 P(s[l, f"conv{cur}"]), P(cs_out), P(s[l, f"state{cur}"]), P(st_out), tape(pend), tape(step), P(mixed),
-                                rows, s["pending_rows"], KH, VH, gdn_in, VH, VH * 128, cfg["tiled_heads"])
+                                rows, s["pending_rows"], KH, VH, gdn_in, VH, VH * 128, cfg["tiled_heads"],
+                                P(rows_tree) if tree is not None else None, s.get("pending_path", 0))
             o.so_gdn_verify(ctypes.byref(args))
             new_state[l, f"conv{nxt}"], new_state[l, f"state{nxt}"] = cs_out, st_out
             mixed_w = VH * 128
@@ -161,20 +167,24 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
     margin = np.zeros(rows, np.float64)
     o.so_sample_verify(P(logits), V, V, rows, P(tokens), float(temperature), P(uniforms) if uniforms is not None else None, P(selected),
                        P(margin))
-    tree = np.zeros((rows, 2), np.uint32)
-    for r in range(rows):
-        tree[r] = ((2 << r) - 1, max(r - 1, 0) | (r << 16))
     out_tokens = selected.copy()
     res = np.zeros(3, np.uint32)
-    o.so_accept(P(tokens), P(tree), P(out_tokens), rows, 16, None, 0, P(res[0:1]), P(res[1:2]), P(res[2:3]))
+    o.so_accept(P(tokens), P(rows_tree), P(out_tokens), rows, 16, None, 0, P(res[0:1]), P(res[1:2]), P(res[2:3]))
     if mutate:
         s.update(new_state)
         s["step"] += 1
         if advance:
+            if tree is not None:  # the accepted path's KV rows move to their depths
+                for l in range(cfg["layers"]):
+                    if (l + 1) % cfg["attention_interval"] == 0:
+                        desc = s[l, "kv"].desc()
+                        o.so_kv_path_commit(ctypes.byref(desc), P(page_table), committed, int(res[2]))
             s["committed"] += int(res[0])
             s["pending_rows"] = int(res[0])
+            s["pending_path"] = int(res[2]) if tree is not None else 0
         else:
             s["pending_rows"] = 0
+            s["pending_path"] = 0
     return dict(logits=logits, selected=selected, retained=int(res[0]), accepted=int(res[1]), mask=int(res[2]),
                 tokens=out_tokens[:res[0]].copy(), margin=margin, hidden=h)
 

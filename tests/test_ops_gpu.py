@@ -459,3 +459,30 @@ def test_sampling_penalties_match_oracle_bitwise(policy):
     # arguments outside the contract are refused
     bad = lib.SbPenaltyArgs(ld.ptr, wd.ptr, idd.ptr, td.ptr, rows, vocab, vocab, 0.0, 0.0, 0.0)
     assert l.sb_sample_penalize(None, ctypes.byref(bad)) == -1
+
+
+def test_kv_path_commit_moves_the_path_rows():
+    """sb_kv_path_commit and sb_kv_path_commit_at against the oracle, bit for bit: the accepted path's rows (codes and
+    scales) move from slot committed + row to slot committed + depth, across a page boundary."""
+    lib, l, o = _setup()
+    rng = np.random.default_rng(12)
+    for scale_f16 in (1, 0):
+        kv = ol.HostKv(6, 2, 128, 32, scale_f16)
+        kv.fill_random(rng)
+        table = rng.permutation(6).astype(np.uint32)
+        committed, mask = 57, 0b1011001000110001   # rows 0, 4, 5, 9, 12, 13, 15 -> depths 0..6, slots 57.. cross into the next page
+        dk, dv, dks, dvs = (lib.DeviceBuffer.from_numpy(x) for x in (kv.k, kv.v, kv.ks, kv.vs))
+        dt, dm, dc = lib.DeviceBuffer.from_numpy(table), lib.DeviceBuffer.from_numpy(np.array([mask], np.uint32)), lib.DeviceBuffer.from_numpy(np.array([committed], np.uint32))
+        cache = lib.SbKvLayer(dk.ptr, dv.ptr, dks.ptr, dvs.ptr, 2, 128, 32, scale_f16)
+        l.sb_kv_path_commit_at.argtypes = [ctypes.c_void_p, ctypes.POINTER(lib.SbKvLayer), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        if scale_f16:
+            lib.check(l.sb_kv_path_commit(None, ctypes.byref(cache), dt.ptr, committed, dm.ptr))
+        else:
+            lib.check(l.sb_kv_path_commit_at(None, ctypes.byref(cache), dt.ptr, dc.ptr, dm.ptr))
+        lib.stream_sync()
+        before = kv.k.copy()
+        desc = kv.desc()
+        o.so_kv_path_commit(ctypes.byref(desc), P(table), committed, mask)
+        assert not np.array_equal(before, kv.k)
+        assert np.array_equal(dk.to_numpy(np.int8, kv.k.shape), kv.k) and np.array_equal(dv.to_numpy(np.int8, kv.v.shape), kv.v)
+        assert np.array_equal(dks.to_numpy(kv.ks.dtype, kv.ks.shape), kv.ks) and np.array_equal(dvs.to_numpy(kv.vs.dtype, kv.vs.shape), kv.vs)
