@@ -480,8 +480,12 @@ SB_API int sb_target_destroy(void *target);
 /* Device pointer and byte size of a tensor or buffer by name. Per layer (layer >= 0): attn_norm, ffn_norm,
  * in_proj, out_proj, ffn_gate, ffn_up, ffn_down, and for GDN layers ssm_ab, ssm_conv, ssm_a, ssm_dt_bias, ssm_norm,
  * state0/1, conv0/1, for attention layers q_norm, k_norm, kv_k, kv_v, kv_ks, kv_vs. Global (layer = -1):
- * token_embd, output_norm, output, logits, selected, results, hidden, tokens, uniforms, committed. */
+ * token_embd, output_norm, output, logits, selected, results, hidden, tokens, uniforms, committed, penalty_words. */
 SB_API int sb_target_tensor(void *target, int layer, const char *name, void **out_dev, uint64_t *out_bytes);
+/* The lane's sampling penalties (ops::SamplingPenalties, runtime/ops/Sampling.hpp:16-29; 1, 0, 0 switches them off): the
+ * step then rewrites the logits in place before selection (sb_sample_penalize) from the table `penalty_words` (u32
+ * [vocab], sb_target_tensor), which the host keeps current: the output's count of each token, bit 31 for the prompt's. */
+SB_API int sb_target_set_penalties(void *target, float repetition, float presence, float frequency);
 /* Seeded synthetic weights, a prefilled INT8 cache of `committed` tokens and random GDN state, written on the device. */
 SB_API int sb_target_randomize(void *target, uint64_t seed, uint32_t committed);
 /* Sets the lane's position and clears the pending GDN rows. */

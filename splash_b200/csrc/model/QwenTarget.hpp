@@ -92,6 +92,10 @@ class QwenTarget {
   uint64_t kvBytes(uint32_t visible) const;
   uint64_t stateBytes() const;
 
+  // Sampling penalties of the lane (off by default): `penaltyWords` holds, per vocabulary token, the output's count and
+  // the prompt bit (runtime/metal/abi/Sampling.h:124-125); the host keeps it current between steps.
+  ops::SamplingPenalties penalties;
+  Buffer penaltyWords;
   Buffer pendingPath;  // the row mask, in the previous step's tape, of the path it accepted (tree steps)
   Buffer tokens, uniforms, committed, pendingRows, results, selected, logits, hidden[2], tree, positions, invFreq, cosine, sine;
   uint32_t committedHost = 0;  // bound of the device's committed word, for extents and the attention plan
@@ -200,6 +204,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   sine = Buffer::allocate(size_t(kVerifyRows) * std::max(1u, c.rotary_pairs) * 4);
   pageTable_ = Buffer::allocate(size_t(pages) * 4);
   sampleWorkspace_ = Buffer::allocate(ops::Sampling::workspace(kVerifyRows, c.vocab));
+  penaltyWords = Buffer::allocate(size_t(c.vocab) * 4);
 }
 
 inline uint64_t QwenTarget::kvBytes(uint32_t visible) const {
@@ -217,7 +222,7 @@ inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) co
                                              {"logits", logits}, {"selected", selected}, {"results", results}, {"hidden", hidden[0]},
                                              {"hidden1", hidden[1]}, {"tokens", tokens}, {"uniforms", uniforms}, {"committed", committed},
                                              {"pending_rows", pendingRows}, {"tree", tree}, {"page_table", pageTable_}, {"inv_freq", invFreq},
-                                             {"positions", positions}, {"packed", packed_}, {"mixed", mixed_}, {"act", act_}};
+                                             {"positions", positions}, {"packed", packed_}, {"mixed", mixed_}, {"act", act_}, {"penalty_words", penaltyWords}};
     auto it = g.find(name);
     if (it == g.end()) return false;
     out = it->second;
@@ -339,6 +344,7 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   SamplingBuffers sb;
   sb.logits = logits, sb.inputTokens = tokens, sb.uniforms = uniforms, sb.selected = selected, sb.workspace = sampleWorkspace_;
   sb.logitStride = c.vocab;
+  Sampling::addPenalties(graph, penalties, sb, penaltyWords, tree, rows, c.vocab);  // (nothing when the penalties are off)
   Sampling::addVerify(graph, SamplingPolicy{temperature}, sb, rows, c.vocab);
   AcceptanceBuffers ab;
   ab.inputTokens = tokens, ab.treeRows = tree, ab.outputTokens = selected, ab.results = results;

@@ -191,6 +191,7 @@ int sb_target_create(const SbTargetConfig *config, void **out_target) {
     SB_CUDA(cudaMemset(m.committed.as(), 0, 4));
     SB_CUDA(cudaMemset(m.pendingRows.as(), 0, 4));
     SB_CUDA(cudaMemset(m.pendingPath.as(), 0, 4));
+    SB_CUDA(cudaMemset(m.penaltyWords.as(), 0, m.penaltyWords.bytes()));
     SB_CUDA(cudaMemset(m.uniforms.as(), 0, 80 * 4));
     SB_CUDA(cudaMemset(m.tokens.as(), 0, 64));
     SB_CUDA(cudaDeviceSynchronize());
@@ -230,6 +231,18 @@ int sb_target_tp_connect(void *target, const void *handles) {
 int sb_target_share(const SbTargetConfig *config, SbTargetShare *out_share) {
   SB_REQUIRE(config && out_share, "sb_target_share: null pointer");
   return guarded([&] { return *out_share = splash::b200::model::shareOf(*config), int(SB_OK); });
+}
+
+int sb_target_set_penalties(void *target, float repetition, float presence, float frequency) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target, "sb_target_set_penalties: null target");
+  SB_REQUIRE(repetition > 0.0f, "sb_target_set_penalties: repetition %g is not positive", double(repetition));
+  Target *t = static_cast<Target *>(target);
+  SB_CUDA(cudaDeviceSynchronize());
+  for (auto &g : t->graphs) cudaGraphExecDestroy(g.second);  // captured steps carry the old policy
+  t->graphs.clear();
+  t->model->penalties = {repetition, presence, frequency};
+  return SB_OK;
 }
 
 int sb_target_tensor(void *target, int layer, const char *name, void **out_dev, uint64_t *out_bytes) {

@@ -38,6 +38,7 @@ def _bind():
     l.sb_target_tensor.argtypes = [_P, ctypes.c_int, ctypes.c_char_p, ctypes.POINTER(_P), ctypes.POINTER(ctypes.c_uint64)]
     l.sb_target_randomize.argtypes = [_P, ctypes.c_uint64, _U]
     l.sb_target_reset.argtypes = [_P, _U]
+    l.sb_target_set_penalties.argtypes = [_P, _F, _F, _F]
     l.sb_target_step.argtypes = [_P, _P, _U, _F, _U]
     l.sb_target_verify.argtypes = [_P, _P, _P, _P, _U, _F, _U, _P, _P]
     l.sb_target_verify_tree.argtypes = [_P, _P, _P, _P, _P, _U, _F, _U, _P, _P]
@@ -89,6 +90,9 @@ class Target:
 
     def randomize(self, seed, committed):
         lib.check(self.l.sb_target_randomize(self.handle, seed, committed))
+
+    def set_penalties(self, repetition=1.0, presence=0.0, frequency=0.0):
+        lib.check(self.l.sb_target_set_penalties(self.handle, repetition, presence, frequency))
 
     def reset(self, committed):
         lib.check(self.l.sb_target_reset(self.handle, committed))

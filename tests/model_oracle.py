@@ -94,7 +94,7 @@ def linear(o, fmt, W, n, k, X, rows, epilogue=0, aux=None, out_f32=False, W2=Non
     return out
 
 
-def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True, mutate=True, tree=None):
+def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True, mutate=True, tree=None, penalties=None, penalty_words=None):
     """One verify step of a chain, or of the tree whose rows `tree` holds (uint32 [rows, 2]: ancestors, parent | depth << 16).
     Returns dict(logits, selected, retained, accepted, mask, tokens)."""
     o = ol.bind_ops(ol.load())
@@ -163,6 +163,8 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
     nf = np.zeros_like(h)
     o.so_rmsnorm(P(h), rows, H, H, P(w[-1, "output_norm"]), P(nf), H)
     logits = linear(o, cfg["fmt_head"], w[-1, "output"], V, H, nf, rows, out_f32=True)
+    if penalties is not None:  # (repetition, presence, frequency) over the table and each row's path
+        o.so_sample_penalize(P(logits), V, V, rows, P(np.ascontiguousarray(penalty_words, np.uint32)), P(tokens), P(rows_tree), *penalties)
     selected = np.zeros(rows, np.uint32)
     margin = np.zeros(rows, np.float64)
     o.so_sample_verify(P(logits), V, V, rows, P(tokens), float(temperature), P(uniforms) if uniforms is not None else None, P(selected),

@@ -130,3 +130,28 @@ def test_tiny_model_tree_steps_match_oracle(flags_name):
         compared += 1
         token = int(got_tokens[-1])
     assert compared >= 2
+
+
+def test_tiny_model_step_with_sampling_penalties_matches_oracle():
+    """The lane's penalties rewrite the step's logits before selection: a strong repetition and frequency penalty on the
+    tokens the target would otherwise choose changes the selections, the same way in the oracle's step."""
+    lib, target, t, cfg, w, s = build(seed=9)
+    tokens = mo.draft_chain(cfg, w, s, 41, rows=16, p_match=1.0, seed=1)
+    plain = mo.verify_step(cfg, w, s, tokens, mutate=False)
+    words = np.zeros(cfg["vocab"], np.uint32)
+    words[plain["selected"]] = 3                 # the output "holds" the target's own choices three times each
+    words[:64] |= 0x80000000                     # and the prompt some others
+    policy = (1.6, 0.5, 0.75)
+    want = mo.verify_step(cfg, w, s, tokens, advance=True, penalties=policy, penalty_words=words)
+    assert not np.array_equal(want["selected"], plain["selected"])
+    t.set_penalties(*policy)
+    t.upload(-1, "penalty_words", words)
+    got_tokens, retained, accepted, mask = t.verify(tokens, flags=target.ADVANCE | target.GRAPH)
+    logits = t.download(-1, "logits", np.float32, (16, cfg["vocab"]))
+    scale = np.abs(want["logits"]).max()
+    assert np.abs(logits - want["logits"]).max() <= 2e-2 * scale
+    top2 = np.sort(want["logits"], axis=1)[:, -2:]
+    if ((top2[:, 1] - top2[:, 0]) > 1e-2)[:want["retained"]].all():
+        assert (retained, accepted, mask) == (want["retained"], want["accepted"], want["mask"])
+        assert np.array_equal(got_tokens, want["tokens"])
+    t.set_penalties()   # off again: the next step's logits are the plain ones
