@@ -59,49 +59,53 @@ __device__ __forceinline__ void attention_merge(const AttnParams &p, uint32_t sp
   __syncthreads();
   if (!*s_last) return;
   __threadfence();
-  // A warp per fused row, lane -> dimensions lane + 32 i; loads batched 8 splits deep.
-  for (uint32_t f = split + warp * p.splits; f < F; f += warps * p.splits) {
+  // A warp per (fused row, 128 dimensions): lane -> dimensions 128 part + 4 lane .. + 3, one 16-byte load a split, 16
+  // splits' loads in flight; the CTA's few rows so spread over all its warps. Every element is summed in split order.
+  constexpr uint32_t kParts = D / 128;
+  static_assert(D % 128 == 0, "merge tasks take 128 dimensions");
+  const uint32_t my_rows = split < F ? (F - split + p.splits - 1) / p.splits : 0;
+  for (uint32_t task = warp; task < my_rows * kParts; task += warps) {
+    const uint32_t f = split + (task / kParts) * p.splits, d0 = 128 * (task % kParts) + 4 * lane;
     const float *stats = p.stats + (size_t(kvh) * p.splits * kMaxFused + f) * 2;
-    const float *parts = p.partials + (size_t(kvh) * p.splits * kMaxFused + f) * D;
+    const float *parts = p.partials + (size_t(kvh) * p.splits * kMaxFused + f) * D + d0;
     const size_t sstride = size_t(kMaxFused) * 2, pstride = size_t(kMaxFused) * D;
     float mall = -INFINITY;
     for (uint32_t s = lane; s < p.splits; s += 32) mall = fmaxf(mall, __ldcg(stats + s * sstride));
 #pragma unroll
     for (int o = 16; o; o >>= 1) mall = fmaxf(mall, __shfl_xor_sync(0xffffffffu, mall, o));
-    float num[D / 32];
-#pragma unroll
-    for (int i = 0; i < D / 32; ++i) num[i] = 0.0f;
+    float num[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     float den = 0.0f;
-    for (uint32_t s0 = 0; s0 < p.splits; s0 += 8) {
-      float ms[8], ls[8], v[8][D / 32];
+    for (uint32_t s0 = 0; s0 < p.splits; s0 += 16) {
+      float ms[16], ls[16];
+      float4 v[16];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 16; ++j) {
         const uint32_t s = min(s0 + j, p.splits - 1);
         ms[j] = __ldcg(stats + s * sstride);
         ls[j] = __ldcg(stats + s * sstride + 1);
-#pragma unroll
-        for (int i = 0; i < D / 32; ++i) v[j][i] = __ldcg(parts + s * pstride + lane + 32 * i);
+        v[j] = __ldcg(reinterpret_cast<const float4 *>(parts + s * pstride));
       }
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < 16; ++j) {
         if (s0 + j >= p.splits || ms[j] == -INFINITY) continue;
         const float w = exp2f(ms[j] - mall);
-#pragma unroll
-        for (int i = 0; i < D / 32; ++i) num[i] += w * v[j][i];
+        num[0] += w * v[j].x, num[1] += w * v[j].y, num[2] += w * v[j].z, num[3] += w * v[j].w;
         den += w * ls[j];
       }
     }
     const uint32_t row = f / G, qh = kvh * G + f % G;
+    float o[4];
 #pragma unroll
-    for (int i = 0; i < D / 32; ++i) {
-      const uint32_t d = lane + 32 * i;
-      float o = round_bf16(den > 0.0f ? num[i] / den : 0.0f);
-      if (p.gated) {
-        const float gate = bf16_bits_to_float(p.qkv[size_t(row) * p.qkv_stride + qh * 2 * D + D + d]);
-        o = o * sigmoid_f(gate);
-      }
-      p.out[size_t(row) * p.out_stride + qh * D + d] = float_to_bf16_bits(o);
+    for (int i = 0; i < 4; ++i) o[i] = round_bf16(den > 0.0f ? num[i] / den : 0.0f);
+    if (p.gated) {
+      const uint2 g2 = *reinterpret_cast<const uint2 *>(p.qkv + size_t(row) * p.qkv_stride + qh * 2 * D + D + d0);
+      o[0] *= sigmoid_f(bf16_bits_to_float(g2.x & 0xffffu)), o[1] *= sigmoid_f(bf16_bits_to_float(g2.x >> 16));
+      o[2] *= sigmoid_f(bf16_bits_to_float(g2.y & 0xffffu)), o[3] *= sigmoid_f(bf16_bits_to_float(g2.y >> 16));
     }
+    uint2 packed;
+    packed.x = uint32_t(float_to_bf16_bits(o[0])) | (uint32_t(float_to_bf16_bits(o[1])) << 16);
+    packed.y = uint32_t(float_to_bf16_bits(o[2])) | (uint32_t(float_to_bf16_bits(o[3])) << 16);
+    *reinterpret_cast<uint2 *>(p.out + size_t(row) * p.out_stride + qh * D + d0) = packed;
   }
   // The last CTA to finish its share returns both counters to zero for the next launch.
   __syncthreads();
