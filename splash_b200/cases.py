@@ -44,7 +44,29 @@ def native_rows(rng, fmt, n, k):
     return blk.reshape(n, nb * bb)
 
 
-def timed(launch, iters, warm=3):
+def timed(launch, iters, warm=3, graph=False):
+    """Microseconds per launch. graph: the launches are captured into one CUDA graph and replayed, which takes the
+    host's launch rate (several microseconds a call from Python) out of the figure."""
+    if graph:
+        l = lib.load()
+        st = lib.stream_create()
+        for i in range(warm):
+            launch(i, st)
+        lib.stream_sync(st)
+        lib.check(l.sb_graph_begin(st))
+        for i in range(iters):
+            launch(i + warm, st)
+        g = ctypes.c_void_p()
+        lib.check(l.sb_graph_end(st, ctypes.byref(g)))
+        lib.check(l.sb_graph_launch(g, st))
+        lib.stream_sync(st)
+        e0, e1 = lib.Event(), lib.Event()
+        e0.record(st)
+        for _ in range(5):
+            lib.check(l.sb_graph_launch(g, st))
+        e1.record(st)
+        e1.sync()
+        return e0.elapsed_ms(e1) / iters / 5 * 1e3
     for i in range(warm):
         launch(i)
     lib.stream_sync()
@@ -72,7 +94,7 @@ def case_linear(a):
     out = lib.DeviceBuffer(16 * n * 4 + 512)
     aux = lib.DeviceBuffer.from_numpy(np.zeros((16, n), np.uint16))
 
-    def launch(i):
+    def launch(i, stream=None):
         kw = {}
         if ep == lib.EP_GATE_UP:
             kw = dict(weights2=bufs[(2 * i + 1) % len(bufs)].ptr)
@@ -81,9 +103,9 @@ def case_linear(a):
             w = bufs[i % len(bufs)].ptr
             if ep == lib.EP_RESIDUAL:
                 kw = dict(aux=aux.ptr)
-        lib.linear(w, None, out.ptr, fmt, n, k, a.rows, prepared=prep.ptr, epilogue=ep, flags=(lib.LINEAR_PDL if a.pdl else 0) | (a.diag << 8) | (lib.LINEAR_TCGEN05 if a.tcgen05 else 0), **kw)
+        lib.linear(w, None, out.ptr, fmt, n, k, a.rows, prepared=prep.ptr, epilogue=ep, flags=(lib.LINEAR_PDL if a.pdl else 0) | (a.diag << 8) | (lib.LINEAR_TCGEN05 if a.tcgen05 else 0), stream=stream, **kw)
 
-    us = timed(launch, a.iters)
+    us = timed(launch, a.iters, graph=a.graph)
     algo = n * rb * tensors + a.rows * k * 2 + a.rows * n * 2
     print(f"linear {a.fmt} n={n} k={k} rows={a.rows} epilogue={a.epilogue}: {us:.1f} us per launch, {algo / us / 1e3:.0f} GB/s "
           f"of {algo} algorithmic bytes, device status {lib.device_status()}")
@@ -208,6 +230,7 @@ def main(argv=None):
     p.add_argument("--epilogue", choices=sorted(EPI), default="none")
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--pdl", action="store_true")
+    p.add_argument("--graph", action="store_true", help="capture the launches into a CUDA graph and time its replay")
     p.add_argument("--diag", type=int, default=0, help="kernel diagnostics (flags bits 8 and up)")
     p.add_argument("--tcgen05", action="store_true", help="Q4_K on the tensor-memory kernel (SB_LINEAR_TCGEN05)")
     p.add_argument("--resident-mb", type=float, default=400.0, help="rotate weight copies over at least this many MB")
