@@ -32,9 +32,9 @@ def _worker(rank, world, shots, barrier, handles, results, step_tokens):
             return [bytes(handles[i * tp.HANDLE_BYTES:(i + 1) * tp.HANDLE_BYTES]) for i in range(world)]
 
         tp.connect(t, all_gather)
-        for step, tokens in enumerate(step_tokens):
+        for step, (tokens, tree) in enumerate(step_tokens):
             barrier.wait(timeout=120)
-            got = t.verify(tokens, flags=target.ADVANCE | target.GRAPH)
+            got = t.verify(tokens, flags=target.ADVANCE | target.GRAPH, tree=tree)
             logits = t.download(-1, "logits", np.float32, (16, cfg["vocab"]))
             results.put((rank, step, got, lib.device_status(), logits))
         barrier.wait(timeout=120)  # nobody unmaps its window while a peer may still write to it
@@ -55,14 +55,26 @@ def test_ranks_match_the_whole_model_oracle(world, shots):
     from splash_b200 import lib, target
     if lib.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
-    steps = 3
+    steps = 4   # three chains, then a tree whose accepted path is not its first rows
     cfg = dict(target.TINY)
     w, s = mo.make_weights(cfg, 0), mo.make_state(cfg, COMMITTED, 1)
     step_tokens, wants, token = [], [], 17
     for step in range(steps):
-        tokens = mo.draft_chain(cfg, w, s, token, rows=16, seed=step)
-        want = mo.verify_step(cfg, w, s, tokens, advance=True)
-        step_tokens.append(tokens), wants.append(want)
+        tree = None
+        if step < 3:
+            tokens = mo.draft_chain(cfg, w, s, token, rows=16, seed=step)
+        else:
+            parent, good = [0, 0, 1, 2, 0, 4, 5, 6, 6, 8, 9, 10, 9, 12, 0, 14], [4, 5, 6, 8, 9, 12, 13]
+            greedy = mo.draft_chain(cfg, w, s, token, rows=len(good) + 1, p_match=1.0, seed=step)
+            tokens = np.random.default_rng(8).integers(0, cfg["vocab"], 16).astype(np.uint32)
+            tokens[0] = token
+            tokens[good] = greedy[1:]
+            tree = np.zeros((16, 2), np.uint32)
+            for r in range(16):
+                tree[r, 0] = (1 << r) | (tree[parent[r], 0] if r else 0)
+                tree[r, 1] = parent[r] | ((bin(int(tree[r, 0])).count("1") - 1) << 16)
+        want = mo.verify_step(cfg, w, s, tokens, advance=True, tree=tree)
+        step_tokens.append((tokens, tree)), wants.append(want)
         token = int(want["tokens"][-1])
     ctx = mp.get_context("spawn")
     barrier, results = ctx.Barrier(world), ctx.Queue()
@@ -95,7 +107,7 @@ def test_ranks_match_the_whole_model_oracle(world, shots):
         assert np.median(np.abs(logits0 - want["logits"])) <= 2e-3 * scale
         top2 = np.sort(want["logits"], axis=1)[:, -2:]
         clear = (top2[:, 1] - top2[:, 0]) > 1e-2
-        if not clear[:want["retained"]].all():
+        if not clear[[r for r in range(16) if want["mask"] >> r & 1]].all():
             break  # the oracle's own choice was a near tie: later steps start from another position
         tokens, retained, accepted, mask = out0
         assert retained == want["retained"] and accepted == want["accepted"] and mask == want["mask"]
