@@ -426,6 +426,23 @@ enum {
                             rows. The step after a tree step carries the flag too (a chain can be given as a tree). */
 };
 
+/* ---- MoE routing ----
+ * Per row: the top_k experts by fp32 router score (descending score, then ascending id) and their weights: the softmax
+ * of their scores, w_r = exp2((s_r - s_0) log2 e) / sum, or with sigmoid_normalized each one's sigmoid over the sum of
+ * theirs; sums in rank order. With shared_gate (fp32 [input_size]) every row gets one more route, the shared expert
+ * (id `experts`), weighted by sigmoid(input . shared_gate). Replaces MoE::addRouting's selection (kernel moe_route_select,
+ * runtime/metal/kernels/shared/moe.metal:22-111); the scores come from sb_linear_f32 over the router's rows. The expert
+ * projections, their grouping by expert and the combine (moe.metal:187-392) are not built. */
+typedef struct SbMoeRouteArgs {
+  const float *scores;      /* device fp32 [rows, slots] */
+  const void *input;        /* bf16 [rows, input_size]; with shared_gate */
+  const float *shared_gate; /* fp32 [input_size] or NULL */
+  uint32_t *selected;       /* device u32 [rows, top_k (+ 1)] */
+  float *weights;           /* device fp32 [rows, top_k (+ 1)] */
+  uint32_t rows, experts, slots, top_k, input_size, sigmoid_normalized;
+} SbMoeRouteArgs;
+SB_API int sb_moe_route(void *stream, const SbMoeRouteArgs *args);
+
 /* ---- tensor parallelism between the GPUs of one node ----
  * The reference runs on one GPU; its projections admit the usual split, and this is it: rank r of W holds
  *   q heads [r Q/W, (r+1) Q/W) with their KV heads (KV head r K/W when W > K: a KV head and its pages are then held

@@ -507,3 +507,51 @@ SO_API void so_sample_penalize(float *logits, uint32_t logit_stride, uint32_t vo
     }
   }
 }
+
+// ---- MoE routing (runtime/metal/kernels/shared/moe.metal:22-111) ----
+// Per row: the top_k experts by fp32 score, descending score then ascending id; their weights the softmax of their
+// scores, w_r = exp2((s_r - s_0) log2 e) / sum (sigmoid_normalized: sigmoid(s_r) / (sum of the top_k's sigmoids + 1e-20)),
+// summed in rank order; with shared_gate, route top_k is the shared expert (id `experts`) weighted by
+// sigmoid(x . shared_gate), the dot product summed as 256 strided partial sums, then lanes, then the 8 groups in order.
+SO_API void so_moe_route(const float *scores, uint32_t rows, uint32_t experts, uint32_t slots, uint32_t top_k, uint32_t sigmoid_normalized,
+                         const uint16_t *input, uint32_t input_size, const float *shared_gate, uint32_t *selected, float *weights) {
+  const uint32_t routes = top_k + (shared_gate ? 1u : 0u);
+  for (uint32_t r = 0; r < rows; ++r) {
+    std::vector<float> sc(scores + size_t(r) * slots, scores + size_t(r) * slots + experts);
+    std::vector<float> ordered(top_k);
+    for (uint32_t rank = 0; rank < top_k; ++rank) {
+      uint32_t best = 0xFFFFFFFFu;
+      float bv = -INFINITY;
+      for (uint32_t e = 0; e < experts; ++e)
+        if (sc[e] > bv) bv = sc[e], best = e;  // ascending scan: the lowest id among equals
+      if (best == 0xFFFFFFFFu) best = 0;  // no score above -inf left: the reference's lane 0 holds the candidate
+      ordered[rank] = bv;
+      selected[size_t(r) * routes + rank] = best;
+      sc[best] = -INFINITY;
+    }
+    float den = 0.0f;
+    for (uint32_t o = 0; o < top_k; ++o)
+      den += sigmoid_normalized ? sigmoid(ordered[o]) : exp2f((ordered[o] - ordered[0]) * 1.44269504089f);
+    for (uint32_t rank = 0; rank < top_k; ++rank)
+      weights[size_t(r) * routes + rank] = sigmoid_normalized ? sigmoid(ordered[rank]) / (den + 1e-20f)
+                                                              : exp2f((ordered[rank] - ordered[0]) * 1.44269504089f) / den;
+    if (shared_gate) {
+      float partial[256];
+      for (uint32_t t = 0; t < 256; ++t) {
+        float a = 0.0f;
+        for (uint32_t d = t; d < input_size; d += 256) a += bf2f(input[size_t(r) * input_size + d]) * shared_gate[d];
+        partial[t] = a;
+      }
+      float total = 0.0f;
+      for (uint32_t g = 0; g < 8; ++g) {
+        float lanes[32];
+        for (uint32_t l = 0; l < 32; ++l) lanes[l] = partial[32 * g + l];
+        for (uint32_t o = 16; o; o >>= 1)
+          for (uint32_t l = 0; l < o; ++l) lanes[l] += lanes[l + o];  // the butterfly's lane 0
+        total += lanes[0];
+      }
+      selected[size_t(r) * routes + top_k] = experts;
+      weights[size_t(r) * routes + top_k] = sigmoid(total);
+    }
+  }
+}

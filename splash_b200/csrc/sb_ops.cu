@@ -573,6 +573,67 @@ __global__ void penalize_kernel(const SbPenaltyArgs a) {
   }
 }
 
+// ---- MoE routing: one block of 256 threads per row (runtime/metal/kernels/shared/moe.metal:22-111) ----
+__global__ void __launch_bounds__(256) moe_route_kernel(const SbMoeRouteArgs a) {
+  __shared__ float row_scores[256], ordered[32], partials[8];
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const uint32_t routes = a.top_k + (a.shared_gate ? 1u : 0u);
+  row_scores[tid] = tid < a.experts ? a.scores[size_t(row) * a.slots + tid] : -INFINITY;
+  if (a.shared_gate) {
+    const uint16_t *x = static_cast<const uint16_t *>(a.input) + size_t(row) * a.input_size;
+    float s = 0.0f;
+    for (uint32_t d = tid; d < a.input_size; d += 256) s = __fadd_rn(s, __fmul_rn(bf16_bits_to_float(x[d]), a.shared_gate[d]));
+#pragma unroll
+    for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0) partials[warp] = s;
+  }
+  __syncthreads();
+  if (a.shared_gate && tid == 0) {
+    float total = 0.0f;
+    for (int g = 0; g < 8; ++g) total += partials[g];
+    a.selected[size_t(row) * routes + a.top_k] = a.experts;
+    a.weights[size_t(row) * routes + a.top_k] = 1.0f / (1.0f + exp2f(-1.44269504089f * total));
+  }
+  if (warp != 0) return;
+  // Lane l holds experts l, l + 32, ...; each rank takes the highest remaining score and the lowest id among ties.
+  float mine[8];
+#pragma unroll
+  for (int s = 0; s < 8; ++s) mine[s] = row_scores[lane + 32 * s];
+  for (uint32_t rank = 0; rank < a.top_k; ++rank) {
+    float best = -INFINITY;
+    uint32_t slot = 0;
+#pragma unroll
+    for (int s = 0; s < 8; ++s)
+      if (mine[s] > best) best = mine[s], slot = s;
+    float row_best = best;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) row_best = fmaxf(row_best, __shfl_xor_sync(0xffffffffu, row_best, o));
+    const uint32_t candidate = best == row_best ? lane + 32 * slot : 0xFFFFFFFFu;
+    uint32_t winner = candidate;
+#pragma unroll
+    for (int o = 16; o; o >>= 1) winner = min(winner, __shfl_xor_sync(0xffffffffu, winner, o));
+    if (candidate == winner) {
+#pragma unroll
+      for (int s = 0; s < 8; ++s)
+        if (uint32_t(s) == slot) mine[s] = -INFINITY;
+    }
+    if (lane == 0) {
+      ordered[rank] = row_best;
+      a.selected[size_t(row) * routes + rank] = winner == 0xFFFFFFFFu ? 0u : winner;
+    }
+  }
+  __syncwarp();
+  if (lane < a.top_k) {
+    float den = 0.0f;
+    for (uint32_t o = 0; o < a.top_k; ++o)
+      den += a.sigmoid_normalized ? 1.0f / (1.0f + exp2f(-1.44269504089f * ordered[o])) : exp2f((ordered[o] - ordered[0]) * 1.44269504089f);
+    a.weights[size_t(row) * routes + lane] = a.sigmoid_normalized ? (1.0f / (1.0f + exp2f(-1.44269504089f * ordered[lane]))) / (den + 1e-20f)
+                                                                   : exp2f((ordered[lane] - ordered[0]) * 1.44269504089f) / den;
+  }
+}
+
 template <class... Args>
 static int launch(void (*kernel)(Args...), dim3 grid, dim3 block, cudaStream_t stream, Args... args) {
   cudaLaunchConfig_t cfg = {};
@@ -700,6 +761,15 @@ int sb_sample_penalize(void *stream, const SbPenaltyArgs *a) {
              a->rows);
   SB_REQUIRE(a->repetition > 0.0f, "sb_sample_penalize: repetition %g is not positive", double(a->repetition));
   return launch(penalize_kernel, dim3((a->vocab + 255) / 256), dim3(256), as_stream(stream), *a);
+}
+
+int sb_moe_route(void *stream, const SbMoeRouteArgs *a) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(a && a->scores && a->selected && a->weights, "sb_moe_route: null pointer");
+  SB_REQUIRE(a->rows >= 1 && a->experts >= 1 && a->experts <= 256 && a->slots >= a->experts, "sb_moe_route: %u experts in %u slots (up to 256)", a->experts, a->slots);
+  SB_REQUIRE(a->top_k >= 1 && a->top_k <= 32 && a->top_k <= a->experts, "sb_moe_route: top_k = %u outside 1..min(32, experts)", a->top_k);
+  SB_REQUIRE(!a->shared_gate || (a->input && a->input_size), "sb_moe_route: a gated shared expert needs the rows' input");
+  return launch(moe_route_kernel, dim3(a->rows), dim3(256), as_stream(stream), *a);
 }
 
 int sb_accept(void *stream, const SbAcceptArgs *a) {

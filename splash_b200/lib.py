@@ -222,6 +222,12 @@ class SbPenaltyArgs(ctypes.Structure):
                 ("repetition", ctypes.c_float), ("presence", ctypes.c_float), ("frequency", ctypes.c_float)]
 
 
+class SbMoeRouteArgs(ctypes.Structure):
+    _fields_ = [("scores", ctypes.c_void_p), ("input", ctypes.c_void_p), ("shared_gate", ctypes.c_void_p), ("selected", ctypes.c_void_p),
+                ("weights", ctypes.c_void_p), ("rows", ctypes.c_uint32), ("experts", ctypes.c_uint32), ("slots", ctypes.c_uint32),
+                ("top_k", ctypes.c_uint32), ("input_size", ctypes.c_uint32), ("sigmoid_normalized", ctypes.c_uint32)]
+
+
 class SbAcceptArgs(ctypes.Structure):
     _fields_ = [("input_tokens", _P), ("tree", _P), ("tokens", _P), ("results", _P), ("stop_tokens", _P),
                 ("rows", _U), ("remaining", _U), ("n_stop", _U)]
@@ -245,6 +251,7 @@ def _bind_ops():
     l.sb_sample_workspace_bytes.argtypes = [_U, _U]
     l.sb_sample_verify.argtypes = [_P, ctypes.POINTER(SbSampleArgs)]
     l.sb_accept.argtypes = [_P, ctypes.POINTER(SbAcceptArgs)]
+    l.sb_moe_route.argtypes = [_P, ctypes.POINTER(SbMoeRouteArgs)]
     l.sb_sample_penalize.argtypes = [_P, ctypes.POINTER(SbPenaltyArgs)]
     l._ops_bound = True
     return l

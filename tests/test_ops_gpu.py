@@ -486,3 +486,29 @@ def test_kv_path_commit_moves_the_path_rows():
         assert not np.array_equal(before, kv.k)
         assert np.array_equal(dk.to_numpy(np.int8, kv.k.shape), kv.k) and np.array_equal(dv.to_numpy(np.int8, kv.v.shape), kv.v)
         assert np.array_equal(dks.to_numpy(kv.ks.dtype, kv.ks.shape), kv.ks) and np.array_equal(dvs.to_numpy(kv.vs.dtype, kv.vs.shape), kv.vs)
+
+
+@pytest.mark.parametrize("mode,shared", [(0, True), (1, False), (0, False)])
+def test_moe_route_matches_oracle(mode, shared):
+    """sb_moe_route against the oracle: the chosen experts exact (ties by id), the weights to rounding of exp2."""
+    lib, l, o = _setup()
+    rng = np.random.default_rng(6)
+    rows, experts, slots, top_k, H = 16, 256, 256, 8, 2048
+    scores = rng.standard_normal((rows, slots)).astype(np.float32)
+    scores[2, 40] = scores[2, 7] = scores[2, 255] = 9.0
+    scores[5, :] = -np.inf
+    scores[6, ::2] = scores[6, 1::2]            # every score twice
+    x = ol.f2bf(rng.standard_normal((rows, H)).astype(np.float32))
+    gate = (rng.standard_normal(H) * 0.05).astype(np.float32)
+    routes = top_k + (1 if shared else 0)
+    want_s, want_w = np.zeros((rows, routes), np.uint32), np.zeros((rows, routes), np.float32)
+    o.so_moe_route(P(scores), rows, experts, slots, top_k, mode, P(x), H, P(gate) if shared else None, P(want_s), P(want_w))
+    sd, xd, gd = lib.DeviceBuffer.from_numpy(scores), lib.DeviceBuffer.from_numpy(x), lib.DeviceBuffer.from_numpy(gate)
+    sel, wts = lib.DeviceBuffer(rows * routes * 4), lib.DeviceBuffer(rows * routes * 4)
+    a = lib.SbMoeRouteArgs(sd.ptr, xd.ptr, gd.ptr if shared else None, sel.ptr, wts.ptr, rows, experts, slots, top_k, H, mode)
+    lib.check(l.sb_moe_route(None, ctypes.byref(a)))
+    lib.stream_sync()
+    assert np.array_equal(sel.to_numpy(np.uint32, (rows, routes)), want_s)
+    assert np.allclose(wts.to_numpy(np.float32, (rows, routes)), want_w, rtol=1e-5, atol=1e-7, equal_nan=True)  # (a row without a finite score has no weights: NaN on both sides)
+    bad = lib.SbMoeRouteArgs(sd.ptr, None, None, sel.ptr, wts.ptr, rows, 300, 300, top_k, 0, 0)
+    assert l.sb_moe_route(None, ctypes.byref(bad)) == -1

@@ -277,3 +277,31 @@ def test_gdn_tree_rows_equal_their_paths_run_as_chains():
     a = _gdn_oracle(o, 5, 4, pending_rows=3)
     b = _gdn_oracle(o, 5, 4, pending_path=0b111)
     assert np.array_equal(a["hidden"], b["hidden"]) and np.array_equal(a["state"], b["state"])
+
+
+def test_moe_route_is_a_stable_top_k_with_softmax_weights():
+    """so_moe_route against a sorted statement: experts by descending score then ascending id, weights the softmax of
+    the top_k scores (or their normalised sigmoids), the shared expert's route last."""
+    o = ol.bind_ops(ol.load())
+    rng = np.random.default_rng(2)
+    rows, experts, slots, top_k, H = 16, 250, 256, 8, 512
+    scores = rng.standard_normal((rows, slots)).astype(np.float32)
+    scores[3, 10] = scores[3, 200] = scores[3, 5] = 7.0          # a three-way tie: ids 5, 10, 200 in that order
+    scores[4, :] = -np.inf                                         # nothing to choose: id 0 every time
+    x = ol.f2bf(rng.standard_normal((rows, H)).astype(np.float32))
+    gate = (rng.standard_normal(H) * 0.1).astype(np.float32)
+    for mode in (0, 1):
+        sel, wts = np.zeros((rows, top_k + 1), np.uint32), np.zeros((rows, top_k + 1), np.float32)
+        o.so_moe_route(P(scores), rows, experts, slots, top_k, mode, P(x), H, P(gate), P(sel), P(wts))
+        for r in range(rows):
+            if r == 4:
+                assert (sel[r, :top_k] == 0).all()
+                continue
+            order = sorted(range(experts), key=lambda e: (-scores[r, e], e))[:top_k]
+            assert sel[r, :top_k].tolist() == order
+            s = scores[r, order].astype(np.float64)
+            want = np.exp(s - s[0]) / np.exp(s - s[0]).sum() if mode == 0 else (1 / (1 + np.exp(-s))) / (1 / (1 + np.exp(-s))).sum()
+            assert np.allclose(wts[r, :top_k], want, rtol=2e-6)
+            assert sel[r, top_k] == experts
+            assert np.isclose(wts[r, top_k], 1 / (1 + np.exp(-float(ol.bf2f(x[r]).astype(np.float64) @ gate))), rtol=1e-5)
+        assert sel[3, :3].tolist() == [5, 10, 200]
