@@ -431,8 +431,7 @@ enum {
  * of their scores, w_r = exp2((s_r - s_0) log2 e) / sum, or with sigmoid_normalized each one's sigmoid over the sum of
  * theirs; sums in rank order. With shared_gate (fp32 [input_size]) every row gets one more route, the shared expert
  * (id `experts`), weighted by sigmoid(input . shared_gate). Replaces MoE::addRouting's selection (kernel moe_route_select,
- * runtime/metal/kernels/shared/moe.metal:22-111); the scores come from sb_linear_f32 over the router's rows. The expert
- * projections, their grouping by expert and the combine (moe.metal:187-392) are not built. */
+ * runtime/metal/kernels/shared/moe.metal:22-111); the scores come from sb_linear_f32 over the router's rows. */
 typedef struct SbMoeRouteArgs {
   const float *scores;      /* device fp32 [rows, slots] */
   const void *input;        /* bf16 [rows, input_size]; with shared_gate */
@@ -442,6 +441,28 @@ typedef struct SbMoeRouteArgs {
   uint32_t rows, experts, slots, top_k, input_size, sigmoid_normalized;
 } SbMoeRouteArgs;
 SB_API int sb_moe_route(void *stream, const SbMoeRouteArgs *args);
+
+/* The routed rows through their experts and back, for the rows of one lane's block (up to 16 rows x 32 routes):
+ *   intermediate = bf16(bf16(up_e . x) * silu(bf16(gate_e . x))), y = bf16(down_e . intermediate) per route (row, expert e),
+ *   out = bf16(residual + sum over the row's routes in slot order of weight * float(y)).
+ * Replaces, in that regime, the expert passes and the combine of MoE::addRouted (runtime/ops/MoE.cpp:122-187,260-270;
+ * runtime/metal/kernels/common/moe_gguf_expert_tile.h:33-84, runtime/metal/kernels/shared/moe_gguf.metal:94-160,
+ * runtime/metal/kernels/shared/moe.metal:367-392). Every route streams its expert's rows by itself (a matrix-vector
+ * product); the reference's grouping of routes into per-expert tiles, which pays from about 64 rows on, is not built.
+ * gate, up: native Q4_K rows [experts_total][inter][hidden]; down: [experts_total][hidden][inter]; the shared expert,
+ * if routed, is expert index `experts` of the same tensors (experts_total counts it). */
+typedef struct SbMoeExpertArgs {
+  const void *input;        /* bf16 [rows, hidden] */
+  const void *residual;     /* bf16 [rows, hidden] or NULL */
+  const uint32_t *selected; /* device u32 [rows, routes] from sb_moe_route */
+  const float *weights;     /* device fp32 [rows, routes] */
+  const void *gate, *up, *down;
+  void *scratch;            /* sb_moe_scratch_bytes */
+  void *out;                /* bf16 [rows, hidden] */
+  uint32_t rows, routes, hidden, inter, format, experts_total;
+} SbMoeExpertArgs;
+SB_API uint64_t sb_moe_scratch_bytes(uint32_t rows, uint32_t routes, uint32_t hidden, uint32_t inter);
+SB_API int sb_moe_experts(void *stream, const SbMoeExpertArgs *args);
 
 /* ---- tensor parallelism between the GPUs of one node ----
  * The reference runs on one GPU; its projections admit the usual split, and this is it: rank r of W holds

@@ -555,3 +555,45 @@ SO_API void so_moe_route(const float *scores, uint32_t rows, uint32_t experts, u
     }
   }
 }
+
+// ---- MoE expert passes and combine (runtime/metal/kernels/shared/moe_gguf.metal:94-160, moe.metal:367-392) ----
+// Per route (row, expert): intermediate = bf16(bf16(up . x) * silu(bf16(gate . x))); y = bf16(down . intermediate);
+// out = bf16(residual + sum over the row's routes in slot order of weight * float(y)). Dot products in fp64 over the
+// effective weights d sc q - dmin m (so_dequant); y64 (optional, [rows * routes][hidden]) receives the down sums before
+// rounding, for tolerance gates.
+SO_API int so_moe_experts(const uint16_t *input, const uint16_t *residual, const uint32_t *selected, const float *weights,
+                          const uint8_t *gate, const uint8_t *up, const uint8_t *down, uint32_t rows, uint32_t routes, uint32_t hidden,
+                          uint32_t inter, uint32_t experts_total, uint16_t *out, double *y64) {
+  const uint64_t gu_row = so_row_bytes(0, hidden), dn_row = so_row_bytes(0, inter);
+  std::vector<float> y(size_t(rows) * routes * hidden);
+  int status = 0;
+#pragma omp parallel for schedule(dynamic)
+  for (int64_t route = 0; route < int64_t(rows) * routes; ++route) {
+    const uint32_t row = uint32_t(route / routes), e = std::min(selected[route], experts_total - 1);
+    std::vector<float> wg(size_t(inter) * hidden), wu(size_t(inter) * hidden), wd(size_t(hidden) * inter), mid(inter);
+    if (so_dequant(0, gate + size_t(e) * inter * gu_row, inter, hidden, wg.data()) || so_dequant(0, up + size_t(e) * inter * gu_row, inter, hidden, wu.data()) ||
+        so_dequant(0, down + size_t(e) * hidden * dn_row, hidden, inter, wd.data()))
+      status = -1;
+    for (uint32_t c = 0; c < inter; ++c) {
+      double g = 0.0, u = 0.0;
+      for (uint32_t k = 0; k < hidden; ++k) {
+        const double x = bf2f(input[size_t(row) * hidden + k]);
+        g += double(wg[size_t(c) * hidden + k]) * x, u += double(wu[size_t(c) * hidden + k]) * x;
+      }
+      mid[c] = rbf(rbf(float(u)) * silu(rbf(float(g))));
+    }
+    for (uint32_t c = 0; c < hidden; ++c) {
+      double v = 0.0;
+      for (uint32_t k = 0; k < inter; ++k) v += double(wd[size_t(c) * inter + k]) * mid[k];
+      if (y64) y64[size_t(route) * hidden + c] = v;
+      y[size_t(route) * hidden + c] = rbf(float(v));
+    }
+  }
+  for (uint32_t row = 0; row < rows; ++row)
+    for (uint32_t c = 0; c < hidden; ++c) {
+      float acc = 0.0f;
+      for (uint32_t s = 0; s < routes; ++s) acc += weights[size_t(row) * routes + s] * y[(size_t(row) * routes + s) * hidden + c];
+      out[size_t(row) * hidden + c] = f2bf((residual ? bf2f(residual[size_t(row) * hidden + c]) : 0.0f) + acc);
+    }
+  return status;
+}

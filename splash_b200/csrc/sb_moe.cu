@@ -1,0 +1,152 @@
+// MoE expert passes for the few rows of one lane's verify block (M <= 16 rows, up to 32 routes a row): every route
+// (row, expert) is a matrix-vector product against the expert's native Q4_K rows. Replaces, for that regime, the
+// expert passes of MoE::addRouted (runtime/ops/MoE.cpp:122-187,260-270; kernels moe_gguf_expert_tile of
+// runtime/metal/kernels/common/moe_gguf_expert_tile.h:33-84, the gate/up pass runtime/metal/kernels/shared/moe_gguf.metal:
+// 94-160 and moe_combine, runtime/metal/kernels/shared/moe.metal:367-392):
+//   intermediate = bf16(bf16(up . x) * silu(bf16(gate . x)))     per route
+//   y            = bf16(down . intermediate)                     per route
+//   out          = bf16(residual + sum over the row's routes, in slot order, of weight * float(y))
+// The reference groups routes by expert into tiles so that an expert's weights stream once for many rows; with at
+// most 16 rows nearly every route has its expert to itself, so a route streams its expert's rows directly: a warp per
+// output column, a lane per 8 consecutive weights of every super-block, effective weights d sc q - dmin m unrounded
+// (as in linear_kernel), fp32 sums. The grouped tile kernel for the M >= 64 regime is not built.
+#include "sb_internal.h"
+#include "sb_ptx.cuh"
+
+namespace sb {
+
+constexpr int kMoeThreads = 256, kMoeWarps = kMoeThreads / 32;
+constexpr int kMoeColsPerWarp = 4;  // output columns a warp computes against the staged row
+
+// scale and min of sub-block j of a Q4_K super-block from its 12 packed bytes (three words).
+__device__ __forceinline__ void q4k_scale_min(const uint32_t (&w)[3], uint32_t j, float &sc, float &mn) {
+  const uint8_t *q = reinterpret_cast<const uint8_t *>(w);
+  if (j < 4) {
+    sc = float(q[j] & 63), mn = float(q[j + 4] & 63);
+  } else {
+    sc = float((q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4)), mn = float((q[j + 4] >> 4) | ((q[j] >> 6) << 4));
+  }
+}
+
+// dot(row, x) for one Q4_K row of k weights; x staged in shared memory as floats; lane l takes weights
+// 32 (l / 4) + 8 (l % 4) .. + 7 of every super-block. All lanes return the sum.
+__device__ __forceinline__ float q4k_row_dot(const uint8_t *row, const float *x, uint32_t k, uint32_t lane) {
+  const uint32_t sub = lane >> 2, t0 = 8 * (lane & 3);
+  float acc = 0.0f;
+  for (uint32_t sb = 0; sb < k / 256; ++sb) {
+    const uint8_t *blk = row + size_t(sb) * 144;
+    const uint32_t dm = *reinterpret_cast<const uint32_t *>(blk);
+    const float d = __half2float(__ushort_as_half(uint16_t(dm & 0xffffu))), dmin = __half2float(__ushort_as_half(uint16_t(dm >> 16)));
+    const uint32_t sw[3] = {*reinterpret_cast<const uint32_t *>(blk + 4), *reinterpret_cast<const uint32_t *>(blk + 8),
+                            *reinterpret_cast<const uint32_t *>(blk + 12)};
+    float sc, mn;
+    q4k_scale_min(sw, sub, sc, mn);
+    const uint2 qs = *reinterpret_cast<const uint2 *>(blk + 16 + 32 * (sub >> 1) + t0);
+    const uint32_t shift = (sub & 1) * 4;
+    const float *xs = x + 256 * sb + 32 * sub + t0;
+    float qx = 0.0f, xsum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const uint32_t word = j < 4 ? qs.x : qs.y;
+      const float q = float((word >> (8 * (j & 3) + shift)) & 15u);
+      qx = fmaf(q, xs[j], qx);
+      xsum += xs[j];
+    }
+    acc = fmaf(d * sc, qx, acc);
+    acc = fmaf(-dmin * mn, xsum, acc);
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  return acc;
+}
+
+struct MoeParams {
+  SbMoeExpertArgs a;
+  uint16_t *intermediate;  // bf16 [rows * routes, inter]
+  uint16_t *y;             // bf16 [rows * routes, hidden]
+};
+
+// PAIR: gate and up of the route's expert over the row's input -> intermediate. Otherwise: down over the route's
+// intermediate -> y. grid (rows * routes, column blocks).
+template <bool PAIR> __global__ void __launch_bounds__(kMoeThreads) moe_expert_kernel(const MoeParams p) {
+  extern __shared__ float xrow[];
+  pdl_launch_dependents();
+  pdl_wait();
+  const SbMoeExpertArgs &a = p.a;
+  const uint32_t route = blockIdx.x, row = route / a.routes, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t k = PAIR ? a.hidden : a.inter, n = PAIR ? a.inter : a.hidden;
+  const uint32_t expert = min(a.selected[route], a.experts_total - 1);
+  const uint16_t *src = PAIR ? static_cast<const uint16_t *>(a.input) + size_t(row) * a.hidden : p.intermediate + size_t(route) * a.inter;
+  for (uint32_t i = tid; i < k; i += kMoeThreads) xrow[i] = bf16_bits_to_float(src[i]);
+  __syncthreads();
+  const size_t row_bytes = size_t(k / 256) * 144;
+  const uint8_t *w0 = static_cast<const uint8_t *>(PAIR ? a.gate : a.down) + size_t(expert) * n * row_bytes;
+  const uint8_t *w1 = PAIR ? static_cast<const uint8_t *>(a.up) + size_t(expert) * n * row_bytes : nullptr;
+  const uint32_t c0 = (blockIdx.y * kMoeWarps + warp) * kMoeColsPerWarp;
+#pragma unroll 1
+  for (uint32_t j = 0; j < kMoeColsPerWarp; ++j) {
+    const uint32_t c = c0 + j;
+    if (c >= n) break;
+    const float s0 = q4k_row_dot(w0 + size_t(c) * row_bytes, xrow, k, lane);
+    if (PAIR) {
+      const float s1 = q4k_row_dot(w1 + size_t(c) * row_bytes, xrow, k, lane);
+      if (lane == 0) p.intermediate[size_t(route) * a.inter + c] = float_to_bf16_bits(round_bf16(s1) * silu_f(round_bf16(s0)));
+    } else if (lane == 0) {
+      p.y[size_t(route) * a.hidden + c] = float_to_bf16_bits(s0);
+    }
+  }
+}
+
+// out = bf16(residual + sum over the row's routes in slot order of weight * float(y)).
+__global__ void __launch_bounds__(256) moe_combine_kernel(const MoeParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const SbMoeExpertArgs &a = p.a;
+  const uint32_t row = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= a.hidden) return;
+  float acc = 0.0f;
+  for (uint32_t s = 0; s < a.routes; ++s)
+    acc += a.weights[size_t(row) * a.routes + s] * bf16_bits_to_float(p.y[(size_t(row) * a.routes + s) * a.hidden + c]);
+  const float res = a.residual ? bf16_bits_to_float(static_cast<const uint16_t *>(a.residual)[size_t(row) * a.hidden + c]) : 0.0f;
+  static_cast<uint16_t *>(a.out)[size_t(row) * a.hidden + c] = float_to_bf16_bits(res + acc);
+}
+
+template <class K> static int launch_moe(K kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const MoeParams &p) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = ctx().pdl ? 1 : 0;
+  SB_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+  return SB_OK;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" uint64_t sb_moe_scratch_bytes(uint32_t rows, uint32_t routes, uint32_t hidden, uint32_t inter) {
+  return uint64_t(rows) * routes * (uint64_t(hidden) + inter) * 2 + 256;
+}
+
+extern "C" int sb_moe_experts(void *stream, const SbMoeExpertArgs *a) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(a && a->input && a->selected && a->weights && a->gate && a->up && a->down && a->scratch && a->out, "sb_moe_experts: null pointer");
+  SB_REQUIRE(a->format == SB_FMT_Q4K, "sb_moe_experts: experts in format %u (Q4_K only)", a->format);
+  SB_REQUIRE(a->rows >= 1 && a->rows <= 16 && a->routes >= 1 && a->routes <= 32, "sb_moe_experts: %u rows (1..16) x %u routes (1..32)", a->rows, a->routes);
+  SB_REQUIRE(a->hidden && a->hidden % 256 == 0 && a->inter && a->inter % 256 == 0 && a->hidden <= 8192 && a->inter <= 8192,
+             "sb_moe_experts: hidden %u and intermediate %u are multiples of 256 up to 8192", a->hidden, a->inter);
+  SB_REQUIRE(a->experts_total >= 1, "sb_moe_experts: no experts");
+  SB_REQUIRE(((reinterpret_cast<uintptr_t>(a->gate) | reinterpret_cast<uintptr_t>(a->up) | reinterpret_cast<uintptr_t>(a->down) |
+               reinterpret_cast<uintptr_t>(a->scratch)) & 15) == 0,
+             "sb_moe_experts: expert tensors and scratch must be 16-byte aligned");
+  MoeParams p{*a, static_cast<uint16_t *>(a->scratch), static_cast<uint16_t *>(a->scratch) + size_t(a->rows) * a->routes * a->inter};
+  const uint32_t routes = a->rows * a->routes, per_block = kMoeWarps * kMoeColsPerWarp;
+  cudaStream_t s = as_stream(stream);
+  int st = launch_moe(moe_expert_kernel<true>, dim3(routes, (a->inter + per_block - 1) / per_block), dim3(kMoeThreads), size_t(a->hidden) * 4, s, p);
+  if (st != SB_OK) return st;
+  st = launch_moe(moe_expert_kernel<false>, dim3(routes, (a->hidden + per_block - 1) / per_block), dim3(kMoeThreads), size_t(a->inter) * 4, s, p);
+  if (st != SB_OK) return st;
+  return launch_moe(moe_combine_kernel, dim3((a->hidden + 255) / 256, a->rows), dim3(256), 0, s, p);
+}

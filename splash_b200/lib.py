@@ -228,6 +228,13 @@ class SbMoeRouteArgs(ctypes.Structure):
                 ("top_k", ctypes.c_uint32), ("input_size", ctypes.c_uint32), ("sigmoid_normalized", ctypes.c_uint32)]
 
 
+class SbMoeExpertArgs(ctypes.Structure):
+    _fields_ = [("input", ctypes.c_void_p), ("residual", ctypes.c_void_p), ("selected", ctypes.c_void_p), ("weights", ctypes.c_void_p),
+                ("gate", ctypes.c_void_p), ("up", ctypes.c_void_p), ("down", ctypes.c_void_p), ("scratch", ctypes.c_void_p), ("out", ctypes.c_void_p),
+                ("rows", ctypes.c_uint32), ("routes", ctypes.c_uint32), ("hidden", ctypes.c_uint32), ("inter", ctypes.c_uint32),
+                ("format", ctypes.c_uint32), ("experts_total", ctypes.c_uint32)]
+
+
 class SbAcceptArgs(ctypes.Structure):
     _fields_ = [("input_tokens", _P), ("tree", _P), ("tokens", _P), ("results", _P), ("stop_tokens", _P),
                 ("rows", _U), ("remaining", _U), ("n_stop", _U)]
@@ -252,6 +259,9 @@ def _bind_ops():
     l.sb_sample_verify.argtypes = [_P, ctypes.POINTER(SbSampleArgs)]
     l.sb_accept.argtypes = [_P, ctypes.POINTER(SbAcceptArgs)]
     l.sb_moe_route.argtypes = [_P, ctypes.POINTER(SbMoeRouteArgs)]
+    l.sb_moe_experts.argtypes = [_P, ctypes.POINTER(SbMoeExpertArgs)]
+    l.sb_moe_scratch_bytes.restype = ctypes.c_uint64
+    l.sb_moe_scratch_bytes.argtypes = [_U, _U, _U, _U]
     l.sb_sample_penalize.argtypes = [_P, ctypes.POINTER(SbPenaltyArgs)]
     l._ops_bound = True
     return l

@@ -112,6 +112,7 @@ def bind_ops(lib):
     lib.so_rope_tables.argtypes = [_P, _U, _P, _U, F, _P, _P]
     lib.so_kv_path_commit.argtypes = [_P, _P, _U, _U]
     lib.so_moe_route.argtypes = [_P, _U, _U, _U, _U, _U, _P, _U, _P, _P, _P]
+    lib.so_moe_experts.argtypes = [_P, _P, _P, _P, _P, _P, _P, _U, _U, _U, _U, _U, _P, _P]
     lib.so_penalize_logit.restype = F
     lib.so_penalize_logit.argtypes = [F, _U, F, F, F, F]
     lib.so_sample_penalize.argtypes = [_P, _U, _U, _U, _P, _P, _P, F, F, F]

@@ -512,3 +512,47 @@ def test_moe_route_matches_oracle(mode, shared):
     assert np.allclose(wts.to_numpy(np.float32, (rows, routes)), want_w, rtol=1e-5, atol=1e-7, equal_nan=True)  # (a row without a finite score has no weights: NaN on both sides)
     bad = lib.SbMoeRouteArgs(sd.ptr, None, None, sel.ptr, wts.ptr, rows, 300, 300, top_k, 0, 0)
     assert l.sb_moe_route(None, ctypes.byref(bad)) == -1
+
+
+def test_moe_experts_match_oracle():
+    """sb_moe_route + sb_moe_experts on a small MoE block (24 experts + the shared one, 8 + 1 routes a row, hidden 1024,
+    intermediate 512) against the oracle's fp64 statement: the per-route sums within 2e-3 of their scale, the combined
+    rows within bf16 rounding of the oracle's."""
+    lib, l, o = _setup()
+    rng = np.random.default_rng(17)
+    rows, experts, top_k, H, I = 13, 24, 8, 1024, 512
+    total, routes = experts + 1, top_k + 1
+    gate = np.concatenate([qf.realistic(0, I, H, seed=100 + e) for e in range(total)])
+    up = np.concatenate([qf.realistic(0, I, H, seed=200 + e) for e in range(total)])
+    down = np.concatenate([qf.realistic(0, H, I, seed=300 + e) for e in range(total)])
+    x = ol.f2bf(rng.standard_normal((rows, H)).astype(np.float32))
+    res = ol.f2bf(rng.standard_normal((rows, H)).astype(np.float32))
+    scores = rng.standard_normal((rows, 32)).astype(np.float32)
+    sgate = (rng.standard_normal(H) * 0.05).astype(np.float32)
+    up_dev = lib.DeviceBuffer.from_numpy
+    sd, xd, rd, gd = up_dev(scores), up_dev(x), up_dev(res), up_dev(sgate)
+    sel, wts = lib.DeviceBuffer(rows * routes * 4), lib.DeviceBuffer(rows * routes * 4)
+    ra = lib.SbMoeRouteArgs(sd.ptr, xd.ptr, gd.ptr, sel.ptr, wts.ptr, rows, experts, 32, top_k, H, 0)
+    lib.check(l.sb_moe_route(None, ctypes.byref(ra)))
+    wg, wu, wd = up_dev(gate), up_dev(up), up_dev(down)
+    scratch = lib.DeviceBuffer(int(l.sb_moe_scratch_bytes(rows, routes, H, I)))
+    out = lib.DeviceBuffer(rows * H * 2 + 256)
+    ea = lib.SbMoeExpertArgs(xd.ptr, rd.ptr, sel.ptr, wts.ptr, wg.ptr, wu.ptr, wd.ptr, scratch.ptr, out.ptr, rows, routes, H, I, lib.FMT_Q4K, total)
+    lib.check(l.sb_moe_experts(None, ctypes.byref(ea)))
+    lib.stream_sync()
+    assert lib.device_status() == 0
+    selected, weights = sel.to_numpy(np.uint32, (rows, routes)), wts.to_numpy(np.float32, (rows, routes))
+    assert (selected[:, top_k] == experts).all() and len(np.unique(selected[:, :top_k])) > 8
+    want = np.zeros((rows, H), np.uint16)
+    y64 = np.zeros((rows * routes, H), np.float64)
+    assert o.so_moe_experts(P(x), P(res), P(selected), P(weights), P(gate), P(up), P(down), rows, routes, H, I, total, P(want), P(y64)) == 0
+    y = ol.bf2f(scratch.to_numpy(np.uint16, (rows * routes * (I + H),))[rows * routes * I:].reshape(rows * routes, H)).astype(np.float64)
+    # y is bf16: its rounding, and 2e-3 of the route's scale (a sum that cancels is judged against its row, not itself)
+    ratio = np.abs(y - y64) / (ulp_bf16(y64) + 2e-3 * np.abs(y64).mean(axis=1, keepdims=True))
+    # (an intermediate value that rounds to the neighbouring bf16 on one side moves a few sums a little further)
+    assert (ratio > 1.0).mean() <= 1e-3 and ratio.max() <= 4.0, (float(ratio.max()), float((ratio > 1).mean()))
+    g, w = ol.bf2f(out.to_numpy(np.uint16, (rows, H))).astype(np.float64), ol.bf2f(want).astype(np.float64)
+    assert (np.abs(g - w) <= 2 * ulp_bf16(w) + 2e-3 * np.abs(w).mean()).all()
+    assert np.abs(g - ol.bf2f(res)).max() > 1e-3     # the experts did contribute
+    bad = lib.SbMoeExpertArgs(xd.ptr, rd.ptr, sel.ptr, wts.ptr, wg.ptr, wu.ptr, wd.ptr, scratch.ptr, out.ptr, 17, routes, H, I, lib.FMT_Q4K, total)
+    assert l.sb_moe_experts(None, ctypes.byref(bad)) == -1
