@@ -167,6 +167,36 @@ def case_gdn(a):
           f"{algo / us / 1e3:.0f} GB/s of {algo} state bytes, device status {lib.device_status()}")
 
 
+def case_moe(a):
+    """Routing and expert passes of one MoE layer for a lane's rows (35B-A3B shape by default: 256 experts + the shared one,
+    top 8, hidden 2048, intermediate 512), random router scores so the routes spread over the experts."""
+    rng = np.random.default_rng(0)
+    l = lib.ops()
+    rows, E, K, H, I = a.rows, a.experts, a.top_k, a.hidden, a.inter
+    total, routes = E + 1, K + 1
+    one = native_rows(rng, lib.FMT_Q4K, I, H)
+    gate = lib.DeviceBuffer.from_numpy(np.tile(one, (total, 1)))
+    up = lib.DeviceBuffer.from_numpy(np.tile(one[::-1], (total, 1)))
+    down = lib.DeviceBuffer.from_numpy(np.tile(native_rows(rng, lib.FMT_Q4K, H, I), (total, 1)))
+    x = lib.DeviceBuffer.from_numpy(bf16_bits(rng.standard_normal((rows, H))))
+    scores = lib.DeviceBuffer.from_numpy(rng.standard_normal((rows, E)).astype(np.float32))
+    sgate = lib.DeviceBuffer.from_numpy((rng.standard_normal(H) * 0.05).astype(np.float32))
+    sel, wts = lib.DeviceBuffer(rows * routes * 4), lib.DeviceBuffer(rows * routes * 4)
+    scratch = lib.DeviceBuffer(int(l.sb_moe_scratch_bytes(rows, routes, H, I)))
+    out = lib.DeviceBuffer(rows * H * 2 + 256)
+    ra = lib.SbMoeRouteArgs(scores.ptr, x.ptr, sgate.ptr, sel.ptr, wts.ptr, rows, E, E, K, H, 0)
+    ea = lib.SbMoeExpertArgs(x.ptr, x.ptr, sel.ptr, wts.ptr, gate.ptr, up.ptr, down.ptr, scratch.ptr, out.ptr, rows, routes, H, I, lib.FMT_Q4K, total)
+
+    def launch(i, stream=None):
+        lib.check(l.sb_moe_route(stream, ctypes.byref(ra)))
+        lib.check(l.sb_moe_experts(stream, ctypes.byref(ea)))
+
+    us = timed(launch, a.iters, graph=a.graph)
+    algo = rows * routes * 3 * I * (H // 256) * 144
+    print(f"moe rows={rows} experts={E}+1 top_k={K} hidden={H} intermediate={I}: {us:.1f} us per layer (routing + 3 expert launches), "
+          f"{algo / us / 1e3:.0f} GB/s of {algo} expert bytes (every route its own), device status {lib.device_status()}")
+
+
 def case_exchange(a):
     """sb_tp_prepare_sum (push + conversion with the peers' shares) against sb_linear_prepare_sum, `launches` calls
     captured into one CUDA graph and replayed, so the host's launch rate does not enter."""
@@ -250,6 +280,14 @@ def main(argv=None):
     p.add_argument("--pending", type=int, default=8)
     p.add_argument("--fused-gates", type=int, default=0, help="k of the fused alpha / beta projection (0: b and a given)")
     p.add_argument("--iters", type=int, default=20)
+    p = sub.add_parser("moe")
+    p.add_argument("--rows", type=int, default=16)
+    p.add_argument("--experts", type=int, default=256)
+    p.add_argument("--top-k", type=int, default=8)
+    p.add_argument("--hidden", type=int, default=2048)
+    p.add_argument("--inter", type=int, default=512)
+    p.add_argument("--iters", type=int, default=20)
+    p.add_argument("--graph", action="store_true")
     p = sub.add_parser("exchange")
     p.add_argument("--width", type=int, default=5120)
     p.add_argument("--slices", type=int, default=3)
@@ -260,7 +298,7 @@ def main(argv=None):
     if a.case == "exchange":
         return case_exchange(a)
     lib.init(0)
-    {"linear": case_linear, "attention": case_attention, "gdn": case_gdn}[a.case](a)
+    {"linear": case_linear, "attention": case_attention, "gdn": case_gdn, "moe": case_moe}[a.case](a)
 
 
 if __name__ == "__main__":
