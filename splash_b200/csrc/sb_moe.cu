@@ -28,36 +28,46 @@ __device__ __forceinline__ void q4k_scale_min(const uint32_t (&w)[3], uint32_t j
   }
 }
 
-// dot(row, x) for one Q4_K row of k weights; x staged in shared memory as floats; lane l takes weights
-// 32 (l / 4) + 8 (l % 4) .. + 7 of every super-block. All lanes return the sum.
-__device__ __forceinline__ float q4k_row_dot(const uint8_t *row, const float *x, uint32_t k, uint32_t lane) {
-  const uint32_t sub = lane >> 2, t0 = 8 * (lane & 3);
-  float acc = 0.0f;
-  for (uint32_t sb = 0; sb < k / 256; ++sb) {
-    const uint8_t *blk = row + size_t(sb) * 144;
-    const uint32_t dm = *reinterpret_cast<const uint32_t *>(blk);
-    const float d = __half2float(__ushort_as_half(uint16_t(dm & 0xffffu))), dmin = __half2float(__ushort_as_half(uint16_t(dm >> 16)));
-    const uint32_t sw[3] = {*reinterpret_cast<const uint32_t *>(blk + 4), *reinterpret_cast<const uint32_t *>(blk + 8),
-                            *reinterpret_cast<const uint32_t *>(blk + 12)};
-    float sc, mn;
-    q4k_scale_min(sw, sub, sc, mn);
-    const uint2 qs = *reinterpret_cast<const uint2 *>(blk + 16 + 32 * (sub >> 1) + t0);
-    const uint32_t shift = (sub & 1) * 4;
-    const float *xs = x + 256 * sb + 32 * sub + t0;
-    float qx = 0.0f, xsum = 0.0f;
+// acc[m][c] += lane's share of dot(row c of matrix m, x) for NC consecutive Q4_K rows of each of NM matrices; x staged in
+// shared memory as floats; lane l takes weights 32 (l / 4) + 8 (l % 4) .. + 7 of every super-block, so the lane's x values
+// and their sum are fetched once per super-block for all the rows.
+template <int NM, int NC>
+__device__ __forceinline__ void q4k_rows_dot(const uint8_t *const (&rows)[NM], size_t row_bytes, const float *x, uint32_t k, uint32_t lane,
+                                             float (&acc)[NM][NC]) {
+  const uint32_t sub = lane >> 2, t0 = 8 * (lane & 3), shift = (sub & 1) * 4;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const uint32_t word = j < 4 ? qs.x : qs.y;
-      const float q = float((word >> (8 * (j & 3) + shift)) & 15u);
-      qx = fmaf(q, xs[j], qx);
-      xsum += xs[j];
-    }
-    acc = fmaf(d * sc, qx, acc);
-    acc = fmaf(-dmin * mn, xsum, acc);
+  for (int m = 0; m < NM; ++m)
+#pragma unroll
+    for (int c = 0; c < NC; ++c) acc[m][c] = 0.0f;
+  for (uint32_t sb = 0; sb < k / 256; ++sb) {
+    const float4 x0 = *reinterpret_cast<const float4 *>(x + 256 * sb + 32 * sub + t0), x1 = *reinterpret_cast<const float4 *>(x + 256 * sb + 32 * sub + t0 + 4);
+    const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+    const float xsum = ((xs[0] + xs[1]) + (xs[2] + xs[3])) + ((xs[4] + xs[5]) + (xs[6] + xs[7]));
+#pragma unroll
+    for (int m = 0; m < NM; ++m)
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        const uint8_t *blk = rows[m] + size_t(c) * row_bytes + size_t(sb) * 144;
+        const uint32_t dm = *reinterpret_cast<const uint32_t *>(blk);
+        const float d = __half2float(__ushort_as_half(uint16_t(dm & 0xffffu))), dmin = __half2float(__ushort_as_half(uint16_t(dm >> 16)));
+        const uint32_t sw[3] = {*reinterpret_cast<const uint32_t *>(blk + 4), *reinterpret_cast<const uint32_t *>(blk + 8),
+                                *reinterpret_cast<const uint32_t *>(blk + 12)};
+        float sc, mn;
+        q4k_scale_min(sw, sub, sc, mn);
+        const uint2 qs = *reinterpret_cast<const uint2 *>(blk + 16 + 32 * (sub >> 1) + t0);
+        float qx = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) qx = fmaf(float(((j < 4 ? qs.x : qs.y) >> (8 * (j & 3) + shift)) & 15u), xs[j], qx);
+        acc[m][c] = fmaf(d * sc, qx, acc[m][c]);
+        acc[m][c] = fmaf(-dmin * mn, xsum, acc[m][c]);
+      }
   }
 #pragma unroll
-  for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  return acc;
+  for (int m = 0; m < NM; ++m)
+#pragma unroll
+    for (int c = 0; c < NC; ++c)
+#pragma unroll
+      for (int o = 16; o; o >>= 1) acc[m][c] += __shfl_xor_sync(0xffffffffu, acc[m][c], o);
 }
 
 struct MoeParams {
@@ -83,16 +93,28 @@ template <bool PAIR> __global__ void __launch_bounds__(kMoeThreads) moe_expert_k
   const uint8_t *w0 = static_cast<const uint8_t *>(PAIR ? a.gate : a.down) + size_t(expert) * n * row_bytes;
   const uint8_t *w1 = PAIR ? static_cast<const uint8_t *>(a.up) + size_t(expert) * n * row_bytes : nullptr;
   const uint32_t c0 = (blockIdx.y * kMoeWarps + warp) * kMoeColsPerWarp;
-#pragma unroll 1
-  for (uint32_t j = 0; j < kMoeColsPerWarp; ++j) {
-    const uint32_t c = c0 + j;
-    if (c >= n) break;
-    const float s0 = q4k_row_dot(w0 + size_t(c) * row_bytes, xrow, k, lane);
-    if (PAIR) {
-      const float s1 = q4k_row_dot(w1 + size_t(c) * row_bytes, xrow, k, lane);
-      if (lane == 0) p.intermediate[size_t(route) * a.inter + c] = float_to_bf16_bits(round_bf16(s1) * silu_f(round_bf16(s0)));
-    } else if (lane == 0) {
-      p.y[size_t(route) * a.hidden + c] = float_to_bf16_bits(s0);
+  if (c0 >= n) return;  // n is a multiple of 256, so a warp's columns are inside or outside together
+  if (PAIR) {
+    const uint8_t *const rows[2] = {w0 + size_t(c0) * row_bytes, w1 + size_t(c0) * row_bytes};
+    float acc[2][kMoeColsPerWarp];
+    q4k_rows_dot<2, kMoeColsPerWarp>(rows, row_bytes, xrow, k, lane, acc);
+    if (lane < kMoeColsPerWarp) {
+      float g = 0.0f, u = 0.0f;
+#pragma unroll
+      for (int c = 0; c < kMoeColsPerWarp; ++c)
+        if (lane == uint32_t(c)) g = acc[0][c], u = acc[1][c];
+      p.intermediate[size_t(route) * a.inter + c0 + lane] = float_to_bf16_bits(round_bf16(u) * silu_f(round_bf16(g)));
+    }
+  } else {
+    const uint8_t *const rows[1] = {w0 + size_t(c0) * row_bytes};
+    float acc[1][kMoeColsPerWarp];
+    q4k_rows_dot<1, kMoeColsPerWarp>(rows, row_bytes, xrow, k, lane, acc);
+    if (lane < kMoeColsPerWarp) {
+      float v = 0.0f;
+#pragma unroll
+      for (int c = 0; c < kMoeColsPerWarp; ++c)
+        if (lane == uint32_t(c)) v = acc[0][c];
+      p.y[size_t(route) * a.hidden + c0 + lane] = float_to_bf16_bits(v);
     }
   }
 }
