@@ -125,12 +125,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--tiny", action="store_true", help="the 4-layer configuration (a smoke run, not the benchmark)")
+    ap.add_argument("--moe", action="store_true", help="the 35B-A3B-shaped MoE model, one lane of 16 rows at an 8K context (an extra measurement, not the benchmark)")
     ap.add_argument("--tp-shots", type=int, default=0, choices=(0, 1, 2), help="how tensor-parallel shares travel (sb_tp_set_exchange); 0: by the number of ranks")
     ap.add_argument("--parallel", default="tp", choices=("tp", "replicas"), help="what N > 1 GPUs do: one lane tensor-parallel, or N lanes")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     workload = "tiny hybrid verify" if args.tiny else "Qwen3.x-27B-shaped hybrid verify, Q4_K_M mix, batch 1, block 16, 32K INT8 paged KV, greedy"
+    if args.moe:
+        workload = "35B-A3B-shaped MoE verify (256 experts + shared, top 8), Q4_K, ONE lane of 16 rows (not the configuration's 32 lanes), 8K INT8 paged KV, greedy"
+        args.tiny, args.parallel = True, "replicas"  # (the extra legs of the benchmark are for the 27B workload only)
 
     if args.impl == "reference":
         if rank != 0:
@@ -149,8 +153,8 @@ def main():
     group = Group("nccl")
     lib.init(local)
     lib.check(lib.load().sb_tp_set_exchange(args.tp_shots))
-    cfg = dict(target.TINY if args.tiny else target.QWEN27B)
-    context = 2048 if args.tiny else CONTEXT
+    cfg = dict(target.QWEN35B_A3B if args.moe else target.TINY if args.tiny else target.QWEN27B)
+    context = 8192 if args.moe else 2048 if args.tiny else CONTEXT
     stream = lib.stream_create()
     tensor_parallel = world > 1 and args.parallel == "tp"
     fell_back = None

@@ -414,6 +414,12 @@ typedef struct SbTargetConfig {
   /* Tensor parallelism: this process is rank tp_rank of tp_world ranks, one per GPU of the node (0 or 1: the whole
    * model on this GPU). The configuration above stays the whole model's; the rank holds its share (below). */
   uint32_t tp_world, tp_rank;
+  /* MoE feed-forward blocks (runtime/model/Qwen3_6Moe.hpp:27-52) instead of dense ones when moe_experts > 0: a router over
+   * moe_experts experts, the moe_top_k best per row, expert intermediate width moe_intermediate, and one shared expert
+   * gated by a scalar per row; tensors ffn_router (fp32 [experts, hidden]), ffn_shared_gate (fp32 [hidden]),
+   * ffn_gate_exps / ffn_up_exps ([experts + 1][moe_intermediate][hidden] rows of fmt_proj, the shared expert last),
+   * ffn_down_exps ([experts + 1][hidden][moe_intermediate]). `intermediate` is then unused. Not with tensor parallelism. */
+  uint32_t moe_experts, moe_top_k, moe_intermediate, reserved;
 } SbTargetConfig;
 
 enum {

@@ -16,6 +16,7 @@
 #include "../ops/GDN.hpp"
 #include "../ops/Glue.hpp"
 #include "../ops/Linear.hpp"
+#include "../ops/MoE.hpp"
 #include "../ops/PagedAttention.hpp"
 #include "../ops/Sampling.hpp"
 #include "../ops/TensorParallel.hpp"
@@ -28,6 +29,7 @@ struct LayerWeights {
   bool attention = false;
   ops::NormWeights attnNorm, ffnNorm;
   ops::QuantizedSegment inProj, outProj, ffnGate, ffnUp, ffnDown;
+  ops::MoeWeights moe;  // MoE feed-forward block (then ffnGate / ffnUp / ffnDown are empty)
   // GDN
   Buffer ssmAb, ssmConv, ssmA, ssmDtBias, ssmNorm;
   std::array<ops::GdnCell, 2> cells;
@@ -88,7 +90,8 @@ class QwenTarget {
   std::vector<LayerWeights> &layers() { return layers_; }
 
   // Bytes one step streams: weights once, the visible INT8 cache, the GDN state in and out.
-  uint64_t weightBytes() const { return weightBytes_; }
+  // (MoE blocks: a step reads the routed experts only, every route its own expert's three matrices)
+  uint64_t weightBytes(uint32_t rows = kVerifyRows) const { return weightBytes_ + uint64_t(moeLayers_) * rows * moe_.routes() * moeExpertBytes_; }
   uint64_t kvBytes(uint32_t visible) const;
   uint64_t stateBytes() const;
 
@@ -105,6 +108,8 @@ class QwenTarget {
   ops::QuantizedSegment segment(uint32_t n, uint32_t k, uint32_t format);
   Buffer floats(size_t count) { return Buffer::allocate(count * 4); }
 
+  ops::MoeShape moe_;
+  Buffer moeScores_, moeSelected_, moeWeights_, moeScratch_;
   SbTargetConfig cfg_, loc_;
   SbTargetShare share_{};
   std::unique_ptr<ops::TensorParallel> tp_;
@@ -118,7 +123,8 @@ class QwenTarget {
   Buffer partials_;  // fp32 [kMaxPartialSlices][16][hidden]: k-slice sums of out_proj / down awaiting their consumer
   static constexpr uint32_t kMaxPartialSlices = 16;
   uint32_t packedStride_ = 0;
-  uint64_t weightBytes_ = 0;
+  uint64_t weightBytes_ = 0, moeExpertBytes_ = 0;
+  uint32_t moeLayers_ = 0;
 };
 
 inline ops::QuantizedSegment QwenTarget::segment(uint32_t n, uint32_t k, uint32_t format) {
@@ -140,6 +146,14 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   if (!c.layers || !c.hidden || !c.vocab || !c.intermediate || !c.attention_interval)
     throw std::invalid_argument("QwenTarget: empty configuration");
   if (c.hidden % 256 || c.intermediate % 256) throw std::invalid_argument("QwenTarget: hidden and intermediate sizes are multiples of 256");
+  if (c.moe_experts) {
+    if (tp_) throw std::invalid_argument("QwenTarget: MoE blocks are not offered with tensor parallelism");
+    if (c.fmt_proj != SB_FMT_Q4K) throw std::invalid_argument("QwenTarget: MoE experts are Q4_K");
+    moe_.experts = moe_.slots = c.moe_experts, moe_.topK = c.moe_top_k, moe_.hidden = c.hidden, moe_.intermediate = c.moe_intermediate;
+    moe_.sharedExpert = moe_.sharedGate = true;
+    if (!c.moe_top_k || c.moe_top_k > c.moe_experts || c.moe_experts > 256 || !c.moe_intermediate || c.moe_intermediate % 256)
+      throw std::invalid_argument("QwenTarget: MoE shape (up to 256 experts, top_k of them, intermediate a multiple of 256)");
+  }
   gdn_.keyHeads = c.gdn_key_heads, gdn_.valueHeads = c.gdn_value_heads;
   kv_.kvHeads = c.kv_heads, kv_.headDimension = c.head_dim, kv_.pageTokens = c.page_tokens, kv_.halfScales = c.kv_scale_f16 != 0;
   const uint32_t H = c.hidden, D = c.head_dim;
@@ -175,9 +189,19 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
         w.tapes[i] = ops::GdnTape::allocate(gdn_, kVerifyRows);
       }
     }
-    w.ffnGate = segment(c.intermediate, H, c.fmt_proj);
-    w.ffnUp = segment(c.intermediate, H, c.fmt_proj);
-    w.ffnDown = segment(H, c.intermediate, c.fmt_down);
+    if (c.moe_experts) {
+      const uint32_t total = moe_.expertsTotal();
+      w.moe.router = floats(size_t(moe_.slots) * H), w.moe.sharedGate = floats(H);
+      const size_t pair = size_t(total) * moe_.intermediate * sb_row_bytes(c.fmt_proj, H), down = size_t(total) * H * sb_row_bytes(c.fmt_proj, moe_.intermediate);
+      w.moe.gate = Buffer::allocate(pair), w.moe.up = Buffer::allocate(pair), w.moe.down = Buffer::allocate(down);
+      weightBytes_ += size_t(moe_.slots + 1) * H * 4;
+      moeExpertBytes_ = (2 * pair + down) / total;
+      ++moeLayers_;
+    } else {
+      w.ffnGate = segment(c.intermediate, H, c.fmt_proj);
+      w.ffnUp = segment(c.intermediate, H, c.fmt_proj);
+      w.ffnDown = segment(H, c.intermediate, c.fmt_down);
+    }
   }
   embedding_.rows = Buffer::allocate(size_t(c.vocab) * sb_row_bytes(c.fmt_embed, H));
   embedding_.vocabulary = c.vocab, embedding_.width = H, embedding_.format = c.fmt_embed;
@@ -205,6 +229,11 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   pageTable_ = Buffer::allocate(size_t(pages) * 4);
   sampleWorkspace_ = Buffer::allocate(ops::Sampling::workspace(kVerifyRows, c.vocab));
   penaltyWords = Buffer::allocate(size_t(c.vocab) * 4);
+  if (c.moe_experts) {
+    moeScores_ = Buffer::allocate(size_t(kVerifyRows) * moe_.slots * 4);
+    moeSelected_ = Buffer::allocate(size_t(kVerifyRows) * moe_.routes() * 4), moeWeights_ = Buffer::allocate(size_t(kVerifyRows) * moe_.routes() * 4);
+    moeScratch_ = Buffer::allocate(ops::MoE::scratchBytes(moe_, kVerifyRows));
+  }
 }
 
 inline uint64_t QwenTarget::kvBytes(uint32_t visible) const {
@@ -233,6 +262,9 @@ inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) co
   std::map<std::string, Buffer> m = {{"attn_norm", w.attnNorm.buffer}, {"ffn_norm", w.ffnNorm.buffer}, {"in_proj", w.inProj.rows},
                                      {"out_proj", w.outProj.rows}, {"ffn_gate", w.ffnGate.rows}, {"ffn_up", w.ffnUp.rows},
                                      {"ffn_down", w.ffnDown.rows}};
+  if (cfg_.moe_experts)
+    m.insert({{"ffn_router", w.moe.router}, {"ffn_shared_gate", w.moe.sharedGate}, {"ffn_gate_exps", w.moe.gate}, {"ffn_up_exps", w.moe.up},
+              {"ffn_down_exps", w.moe.down}});
   if (w.attention) {
     m.insert({{"q_norm", w.qNorm}, {"k_norm", w.kNorm}, {"kv_k", w.pages.keys}, {"kv_v", w.pages.values},
               {"kv_ks", w.pages.keyScales}, {"kv_vs", w.pages.valueScales}});
@@ -327,6 +359,16 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
     }
     PreparedInput mixedIn = Linear::prepare(graph, mixed_, rows, mixedWidth, mixedWidth, nullptr, w.outProj.format, prepared_[1]);
     project(w.outProj, mixedWidth, mixedIn);
+    if (c.moe_experts) {
+      // MoE block: h += sum over the row's routes of weight * expert(norm(h)) (runtime/model/Qwen3_6Moe.hpp:27-52). The
+      // conversion is run for its side products: the new hidden state and the normalised rows.
+      convert(&w.ffnNorm.buffer, c.fmt_proj, prepared_[0], &normed_);
+      MoeBuffers mb{normed_, hidden[cur], moeScores_, moeSelected_, moeWeights_, moeScratch_, hidden[cur ^ 1]};
+      MoE::addRouting(graph, moe_, w.moe, mb, rows);
+      MoE::addRouted(graph, moe_, w.moe, mb, rows);
+      cur ^= 1;
+      continue;
+    }
     // FFN: h += down(silu(gate(norm(h))) * up(norm(h)))
     PreparedInput ffnIn = convert(&w.ffnNorm.buffer, w.ffnGate.format, prepared_[0], nullptr);
     Linear::addGateUp(graph, act_, c.intermediate, w.ffnGate, w.ffnUp, rows, ffnIn);

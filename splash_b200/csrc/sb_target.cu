@@ -284,9 +284,23 @@ int sb_target_randomize(void *target, uint64_t seed, uint32_t committed) {
       SB_TRY(fill(kF32Normal, w.ffnNorm.buffer, c.hidden, next(), 1.0f, 0.1f));
       SB_TRY(fill_rows(w.inProj, next()));
       SB_TRY(fill_rows(w.outProj, next()));
-      SB_TRY(fill_rows(w.ffnGate, next()));
-      SB_TRY(fill_rows(w.ffnUp, next()));
-      SB_TRY(fill_rows(w.ffnDown, next()));
+      if (c.moe_experts) {
+        const uint32_t total = c.moe_experts + 1;
+        splash::b200::ops::QuantizedSegment e;
+        e.format = c.fmt_proj;
+        e.rows = w.moe.gate, e.outputSize = total * c.moe_intermediate, e.inputSize = c.hidden;
+        SB_TRY(fill_rows(e, next()));
+        e.rows = w.moe.up;
+        SB_TRY(fill_rows(e, next()));
+        e.rows = w.moe.down, e.outputSize = total * c.hidden, e.inputSize = c.moe_intermediate;
+        SB_TRY(fill_rows(e, next()));
+        SB_TRY(fill(kF32Normal, w.moe.router, w.moe.router.bytes() / 4, next(), 0.0f, 0.05f));
+        SB_TRY(fill(kF32Normal, w.moe.sharedGate, c.hidden, next(), 0.0f, 0.02f));
+      } else {
+        SB_TRY(fill_rows(w.ffnGate, next()));
+        SB_TRY(fill_rows(w.ffnUp, next()));
+        SB_TRY(fill_rows(w.ffnDown, next()));
+      }
       if (w.attention) {
         SB_TRY(fill(kF32Normal, w.qNorm, c.head_dim, next(), 1.0f, 0.1f));
         SB_TRY(fill(kF32Normal, w.kNorm, c.head_dim, next(), 1.0f, 0.1f));
@@ -427,7 +441,7 @@ int sb_target_stats(void *target, uint32_t rows, uint32_t *out_launches, uint64_
   SB_REQUIRE(target, "sb_target_stats: null target");
   Target *t = static_cast<Target *>(target);
   if (out_launches) *out_launches = t->launches;
-  if (out_weight_bytes) *out_weight_bytes = t->model->weightBytes();
+  if (out_weight_bytes) *out_weight_bytes = t->model->weightBytes(rows);
   if (out_kv_bytes) *out_kv_bytes = t->model->kvBytes(t->model->committedHost + rows);
   if (out_state_bytes) *out_state_bytes = t->model->stateBytes();
   return SB_OK;

@@ -15,7 +15,8 @@ class SbTargetConfig(ctypes.Structure):
                 ("gdn_key_heads", _U), ("gdn_value_heads", _U), ("attention_interval", _U),
                 ("page_tokens", _U), ("kv_scale_f16", _U), ("max_context", _U),
                 ("fmt_proj", _U), ("fmt_down", _U), ("fmt_head", _U), ("fmt_embed", _U),
-                ("gated_attention", _U), ("tiled_heads", _U), ("tp_world", _U), ("tp_rank", _U)]
+                ("gated_attention", _U), ("tiled_heads", _U), ("tp_world", _U), ("tp_rank", _U),
+                ("moe_experts", _U), ("moe_top_k", _U), ("moe_intermediate", _U), ("reserved", _U)]
 
 
 # The benchmark configurations' shapes (weights are synthetic; see quant fixtures and sb_target_randomize).
@@ -27,6 +28,14 @@ QWEN27B = dict(layers=64, hidden=5120, vocab=151936, intermediate=17408, q_heads
                rotary_pairs=32, rope_theta=1e7, gdn_key_heads=16, gdn_value_heads=48, attention_interval=4, page_tokens=256,
                kv_scale_f16=1, max_context=32768 + 1024, fmt_proj=lib.FMT_Q4K, fmt_down=lib.FMT_Q6K, fmt_head=lib.FMT_Q6K,
                fmt_embed=lib.FMT_Q6K, gated_attention=1, tiled_heads=1)
+
+
+# The MoE configuration's shape (35B-A3B: 40 layers at 3:1, hidden 2048, 16 query / 2 KV heads of 256, 256 experts of
+# width 512 plus a shared one, top 8); the GDN head counts are this harness's choice (the configuration names none).
+QWEN35B_A3B = dict(layers=40, hidden=2048, vocab=151936, intermediate=512, q_heads=16, kv_heads=2, head_dim=256, rotary_pairs=32,
+                   rope_theta=1e7, gdn_key_heads=16, gdn_value_heads=32, attention_interval=4, page_tokens=256, kv_scale_f16=1,
+                   max_context=8192 + 1024, fmt_proj=lib.FMT_Q4K, fmt_down=lib.FMT_Q4K, fmt_head=lib.FMT_Q6K, fmt_embed=lib.FMT_Q6K,
+                   gated_attention=1, tiled_heads=1, moe_experts=256, moe_top_k=8, moe_intermediate=512)
 
 
 def _bind():

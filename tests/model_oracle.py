@@ -36,6 +36,14 @@ def make_weights(cfg, seed=0):
             w[l, "ssm_a"] = (-np.exp(rng.uniform(-3, 0.5, VH))).astype(np.float32)
             w[l, "ssm_dt_bias"] = ol.f2bf((rng.standard_normal(VH) * 0.5).astype(np.float32))
             w[l, "ssm_norm"] = norm(128)
+        if cfg.get("moe_experts"):
+            E, Ie = cfg["moe_experts"] + 1, cfg["moe_intermediate"]
+            w[l, "ffn_router"] = (rng.standard_normal((cfg["moe_experts"], H)) * 0.05).astype(np.float32)
+            w[l, "ffn_shared_gate"] = (rng.standard_normal(H) * 0.02).astype(np.float32)
+            w[l, "ffn_gate_exps"] = np.concatenate([rows(cfg["fmt_proj"], Ie, H) for _ in range(E)])
+            w[l, "ffn_up_exps"] = np.concatenate([rows(cfg["fmt_proj"], Ie, H) for _ in range(E)])
+            w[l, "ffn_down_exps"] = np.concatenate([rows(cfg["fmt_proj"], H, Ie) for _ in range(E)])
+            continue
         w[l, "ffn_gate"] = rows(cfg["fmt_proj"], I, H)
         w[l, "ffn_up"] = rows(cfg["fmt_proj"], I, H)
         w[l, "ffn_down"] = rows(cfg["fmt_down"], H, I)
@@ -158,6 +166,16 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
         h = linear(o, cfg["fmt_proj"], w[l, "out_proj"], H, mixed_w, mixed, rows, epilogue=1, aux=h)
         n2 = np.zeros_like(h)
         o.so_rmsnorm(P(h), rows, H, H, P(w[l, "ffn_norm"]), P(n2), H)
+        if cfg.get("moe_experts"):
+            E, K, Ie = cfg["moe_experts"], cfg["moe_top_k"], cfg["moe_intermediate"]
+            scores = np.ascontiguousarray((ol.bf2f(n2).astype(np.float32) @ w[l, "ffn_router"].T).astype(np.float32))
+            sel, wts = np.zeros((rows, K + 1), np.uint32), np.zeros((rows, K + 1), np.float32)
+            o.so_moe_route(P(scores), rows, E, E, K, 0, P(n2), H, P(w[l, "ffn_shared_gate"]), P(sel), P(wts))
+            out = np.zeros_like(h)
+            assert o.so_moe_experts(P(n2), P(h), P(sel), P(wts), P(w[l, "ffn_gate_exps"]), P(w[l, "ffn_up_exps"]), P(w[l, "ffn_down_exps"]),
+                                    rows, K + 1, H, Ie, E + 1, P(out), None) == 0
+            h = out
+            continue
         act = linear(o, cfg["fmt_proj"], w[l, "ffn_gate"], I, H, n2, rows, epilogue=3, W2=w[l, "ffn_up"])
         h = linear(o, cfg["fmt_down"], w[l, "ffn_down"], H, I, act, rows, epilogue=1, aux=h)
     nf = np.zeros_like(h)

@@ -155,3 +155,33 @@ def test_tiny_model_step_with_sampling_penalties_matches_oracle():
         assert (retained, accepted, mask) == (want["retained"], want["accepted"], want["mask"])
         assert np.array_equal(got_tokens, want["tokens"])
     t.set_penalties()   # off again: the next step's logits are the plain ones
+
+
+def test_tiny_moe_model_steps_match_oracle():
+    """The tiny hybrid configuration with MoE feed-forward blocks (16 experts + the shared one, top 4, expert width 256):
+    router, routes, expert passes and combine inside whole verify steps against the oracle's."""
+    from splash_b200 import lib, target
+    lib.init(0)
+    cfg = dict(target.TINY, moe_experts=16, moe_top_k=4, moe_intermediate=256)
+    t = target.Target(**cfg)
+    w, s = mo.make_weights(cfg, 3), mo.make_state(cfg, 2048, 4)
+    mo.upload(t, w, s)
+    t.reset(2048)
+    token, compared = 31, 0
+    for step in range(2):
+        tokens = mo.draft_chain(cfg, w, s, token, rows=16, seed=step)
+        want = mo.verify_step(cfg, w, s, tokens, advance=True)
+        got_tokens, retained, accepted, mask = t.verify(tokens, flags=target.ADVANCE | target.GRAPH)
+        assert lib.device_status() == 0
+        logits = t.download(-1, "logits", np.float32, (16, cfg["vocab"]))
+        scale = np.abs(want["logits"]).max()
+        assert np.abs(logits - want["logits"]).max() <= 2e-2 * scale
+        assert np.median(np.abs(logits - want["logits"])) <= 2e-3 * scale
+        top2 = np.sort(want["logits"], axis=1)[:, -2:]
+        if not ((top2[:, 1] - top2[:, 0]) > 1e-2)[:want["retained"]].all():
+            break
+        assert (retained, accepted, mask) == (want["retained"], want["accepted"], want["mask"])
+        assert np.array_equal(got_tokens, want["tokens"])
+        compared += 1
+        token = int(got_tokens[-1])
+    assert compared >= 1
