@@ -57,7 +57,11 @@ __device__ __forceinline__ void q4k_rows_dot(const uint8_t *const (&rows)[NM], s
         const uint2 qs = *reinterpret_cast<const uint2 *>(blk + 16 + 32 * (sub >> 1) + t0);
         float qx = 0.0f;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) qx = fmaf(float(((j < 4 ? qs.x : qs.y) >> (8 * (j & 3) + shift)) & 15u), xs[j], qx);
+        for (int j = 0; j < 8; ++j) {
+          // the code as a float without a conversion instruction (quarter rate): 2^23 + q in the mantissa, minus 2^23
+          const float q = __uint_as_float(0x4B000000u | (((j < 4 ? qs.x : qs.y) >> (8 * (j & 3) + shift)) & 15u)) - 8388608.0f;
+          qx = fmaf(q, xs[j], qx);
+        }
         acc[m][c] = fmaf(d * sc, qx, acc[m][c]);
         acc[m][c] = fmaf(-dmin * mn, xsum, acc[m][c]);
       }
