@@ -18,14 +18,19 @@ namespace sb {
 constexpr int kMoeThreads = 256, kMoeWarps = kMoeThreads / 32;
 constexpr int kMoeColsPerWarp = 4;  // output columns a warp computes against the staged row
 
-// scale and min of sub-block j of a Q4_K super-block from its 12 packed bytes (three words).
+// scale and min of sub-block j of a Q4_K super-block from its 12 packed bytes (three words), in registers: bytes 0-3
+// hold the low 6 bits of scales 0-3 (and in their top 2 bits the high bits of scales 4-7), bytes 4-7 the same for the mins,
+// bytes 8-11 the low nibbles of scales 4-7 (low half) and mins 4-7 (high half).
 __device__ __forceinline__ void q4k_scale_min(const uint32_t (&w)[3], uint32_t j, float &sc, float &mn) {
-  const uint8_t *q = reinterpret_cast<const uint8_t *>(w);
+  const uint32_t s8 = 8 * (j & 3);
+  uint32_t isc, imn;
   if (j < 4) {
-    sc = float(q[j] & 63), mn = float(q[j + 4] & 63);
+    isc = (w[0] >> s8) & 63u, imn = (w[1] >> s8) & 63u;
   } else {
-    sc = float((q[j + 4] & 0xF) | ((q[j - 4] >> 6) << 4)), mn = float((q[j + 4] >> 4) | ((q[j] >> 6) << 4));
+    isc = ((w[2] >> s8) & 0xFu) | (((w[0] >> (s8 + 6)) & 3u) << 4);
+    imn = ((w[2] >> (s8 + 4)) & 0xFu) | (((w[1] >> (s8 + 6)) & 3u) << 4);
   }
+  sc = float(isc), mn = float(imn);
 }
 
 // acc[m][c] += lane's share of dot(row c of matrix m, x) for NC consecutive Q4_K rows of each of NM matrices; x staged in
@@ -39,6 +44,7 @@ __device__ __forceinline__ void q4k_rows_dot(const uint8_t *const (&rows)[NM], s
   for (int m = 0; m < NM; ++m)
 #pragma unroll
     for (int c = 0; c < NC; ++c) acc[m][c] = 0.0f;
+#pragma unroll 2
   for (uint32_t sb = 0; sb < k / 256; ++sb) {
     const float4 x0 = *reinterpret_cast<const float4 *>(x + 256 * sb + 32 * sub + t0), x1 = *reinterpret_cast<const float4 *>(x + 256 * sb + 32 * sub + t0 + 4);
     const float xs[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
@@ -56,10 +62,11 @@ __device__ __forceinline__ void q4k_rows_dot(const uint8_t *const (&rows)[NM], s
         q4k_scale_min(sw, sub, sc, mn);
         const uint2 qs = *reinterpret_cast<const uint2 *>(blk + 16 + 32 * (sub >> 1) + t0);
         float qx = 0.0f;
+        const uint32_t n0 = (qs.x >> shift) & 0x0F0F0F0Fu, n1 = (qs.y >> shift) & 0x0F0F0F0Fu;  // the lane's eight codes, a byte each
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           // the code as a float without a conversion instruction (quarter rate): 2^23 + q in the mantissa, minus 2^23
-          const float q = __uint_as_float(0x4B000000u | (((j < 4 ? qs.x : qs.y) >> (8 * (j & 3) + shift)) & 15u)) - 8388608.0f;
+          const float q = __uint_as_float(0x4B000000u | __byte_perm(j < 4 ? n0 : n1, 0, 0x4440 + (j & 3))) - 8388608.0f;
           qx = fmaf(q, xs[j], qx);
         }
         acc[m][c] = fmaf(d * sc, qx, acc[m][c]);
