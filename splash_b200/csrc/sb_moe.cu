@@ -16,7 +16,7 @@
 namespace sb {
 
 constexpr int kMoeThreads = 256, kMoeWarps = kMoeThreads / 32;
-constexpr int kMoeColsPerWarp = 4;  // output columns a warp computes against the staged row
+constexpr int kMoeColsPair = 8, kMoeColsDown = 8;  // output columns a warp computes against the staged row (gate/up pass, down pass)
 
 // scale and min of sub-block j of a Q4_K super-block from its 12 packed bytes (three words), in registers: bytes 0-3
 // hold the low 6 bits of scales 0-3 (and in their top 2 bits the high bits of scales 4-7), bytes 4-7 the same for the mins,
@@ -90,6 +90,7 @@ struct MoeParams {
 // PAIR: gate and up of the route's expert over the row's input -> intermediate. Otherwise: down over the route's
 // intermediate -> y. grid (rows * routes, column blocks).
 template <bool PAIR> __global__ void __launch_bounds__(kMoeThreads) moe_expert_kernel(const MoeParams p) {
+  constexpr int kMoeColsPerWarp = PAIR ? kMoeColsPair : kMoeColsDown;
   extern __shared__ float xrow[];
   pdl_launch_dependents();
   pdl_wait();
@@ -175,11 +176,11 @@ extern "C" int sb_moe_experts(void *stream, const SbMoeExpertArgs *a) {
                reinterpret_cast<uintptr_t>(a->scratch)) & 15) == 0,
              "sb_moe_experts: expert tensors and scratch must be 16-byte aligned");
   MoeParams p{*a, static_cast<uint16_t *>(a->scratch), static_cast<uint16_t *>(a->scratch) + size_t(a->rows) * a->routes * a->inter};
-  const uint32_t routes = a->rows * a->routes, per_block = kMoeWarps * kMoeColsPerWarp;
+  const uint32_t routes = a->rows * a->routes, pair_block = kMoeWarps * kMoeColsPair, down_block = kMoeWarps * kMoeColsDown;
   cudaStream_t s = as_stream(stream);
-  int st = launch_moe(moe_expert_kernel<true>, dim3(routes, (a->inter + per_block - 1) / per_block), dim3(kMoeThreads), size_t(a->hidden) * 4, s, p);
+  int st = launch_moe(moe_expert_kernel<true>, dim3(routes, (a->inter + pair_block - 1) / pair_block), dim3(kMoeThreads), size_t(a->hidden) * 4, s, p);
   if (st != SB_OK) return st;
-  st = launch_moe(moe_expert_kernel<false>, dim3(routes, (a->hidden + per_block - 1) / per_block), dim3(kMoeThreads), size_t(a->inter) * 4, s, p);
+  st = launch_moe(moe_expert_kernel<false>, dim3(routes, (a->hidden + down_block - 1) / down_block), dim3(kMoeThreads), size_t(a->inter) * 4, s, p);
   if (st != SB_OK) return st;
   return launch_moe(moe_combine_kernel, dim3((a->hidden + 255) / 256, a->rows), dim3(256), 0, s, p);
 }
