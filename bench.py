@@ -4,6 +4,7 @@
 context, greedy acceptance) with seeded synthetic weights, cache and state written on the device.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--parallel tp|replicas]
+    python bench.py --case linear|attention|gdn|moe|exchange ...   (one operator on one shape: bench_cases.py)
 
 With N > 1 (one process per GPU under torchrun) the N GPUs run ONE lane tensor-parallel: every rank holds its share
 of the model, the shares of out_proj / down meet through peer memory inside the next input conversion, the logits'
@@ -13,7 +14,8 @@ independent lanes instead (`scaling: "weak"`).
 One JSON line on stdout (rank 0). `value` is device-resident steps; `e2e` goes through the host-facing call
 sb_target_verify with pinned host buffers, copies and the result read-back inside the timed region;
 `roofline` is the dominant kernel (the Q4_K gate/up projection) timed alone over the layers' weights;
-`cpu_baseline` is the CPU oracle's port of the same projections on a bounded sample.
+`cpu_baseline` is the CPU oracle's port of the step's projections, attention and Gated-DeltaNet work on bounded samples;
+`parity_check` is one checked step after the timed loops (finite logits, a sane accept length, equal logits on all ranks).
 --impl reference times the reference's arithmetic for this path on the host cores: the oracle port
 (the reference's own GPU kernels are Metal and cannot run here)."""
 import argparse
@@ -32,9 +34,13 @@ sys.path.insert(0, ROOT)
 
 ROWS = 16
 CONTEXT = 32768
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel from the ncu capture
-# summarised in profiles/linear_q4k_gate_up_27b.md (bytes): 100,532,736 read + 3,923,200 written, captured at this
-# bench's own shape, so no scaling.
+# Rows of the previous step's tape that every timed step folds into the Gated-DeltaNet state: the lane is held at its
+# position (every step does the same work) but keeps this many pending rows, a typical accept length, so the fold a
+# committing cycle performs stays inside the timed region.
+FOLD_ROWS = 6
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from one ncu capture of that kernel
+# at this bench's own shape (100,532,736 bytes read + 3,923,200 written), so no scaling. ncu cannot run inside a timed
+# run; the figure is carried here and re-taken whenever the kernel changes.
 DOMINANT_TRAFFIC_BYTES = 104455936
 
 
@@ -82,43 +88,99 @@ class ClockSampler:
 
 
 def cpu_baseline(seconds_budget=20.0):
-    """The oracle's port of one FFN (gate/up one pass, then down: the dominant share of a layer's bytes) on the host
-    cores, scaled by weight bytes to a whole step. Returns (tokens/s, cores, sample description)."""
+    """The oracle's port of the verify step's three kinds of work on the host cores, each on a bounded sample and scaled
+    to a whole 27B-shaped step: the quantized projections (one FFN: gate/up in one pass, then down; scaled by weight
+    bytes), INT8 paged attention (one KV head with its 6 query heads over the 32K context; scaled to 4 heads x 16 layers)
+    and the Gated-DeltaNet step (one layer of 48 heads, folding 6 rows; x 48 layers). OpenMP over all host cores, the
+    thread count set here (a launcher may export OMP_NUM_THREADS=1). Returns (tokens/s, threads, sample description)."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as ol
     import quant_fixtures as qf
-    o = ol.load()
+    o = ol.bind_ops(ol.load())
+    o.so_threads.argtypes = [ctypes.c_int]
+    threads = int(o.so_threads(os.cpu_count() or 1))
     H, I = 5120, 17408
-    cores = os.cpu_count() or 1
-    # a bounded slice of the FFN: `n` of the 17408 intermediate columns, sized from a quick probe
-    def run(n):
+    P = ol.ptr
+
+    def best_of(run, budget, least=2, most=200):
+        runs, spent = [], 0.0
+        while len(runs) < least or (spent < budget and len(runs) < most):
+            t0 = time.perf_counter()
+            run()
+            runs.append(time.perf_counter() - t0)
+            spent += runs[-1]
+        return min(runs), len(runs), spent
+
+    # ---- projections: a slice of `n` of the FFN's 17408 intermediate columns, sized from a quick probe ----
+    def ffn(n):
         wg, wu = qf.realistic(0, n, H, seed=1), qf.realistic(0, n, H, seed=2)
-        wd = qf.realistic(4, H, max(256, n // 256 * 256), seed=3)
-        x = qf.activations(ROWS, H)
-        kd = wd.shape[1] // 210 * 256
-        t0 = time.perf_counter()
-        act = np.zeros((ROWS, n), np.uint16)
         w2 = np.ascontiguousarray(np.concatenate([wg, wu], axis=0))
-        assert o.so_linear(0, ol.ptr(w2), n, H, ol.ptr(x), ROWS, 3, None, 0, ol.ptr(act), n, 0, 0) == 0
-        xa = np.ascontiguousarray(np.resize(act, (ROWS, kd)))
-        out = np.zeros((ROWS, H), np.uint16)
-        assert o.so_linear(4, ol.ptr(wd), H, kd, ol.ptr(xa), ROWS, 0, None, 0, ol.ptr(out), H, 0, 0) == 0
-        dt = time.perf_counter() - t0
-        return dt, wg.nbytes + wu.nbytes + wd.nbytes
-    dt, nbytes = run(1024)
-    n = int(min(I, max(1024, 1024 * seconds_budget / 3 / max(dt, 1e-3)))) // 256 * 256
-    # repeated until about half the budget is spent (at least 3 times); the best run counts
-    runs, spent = [], 0.0
-    while len(runs) < 3 or (spent < seconds_budget / 2 and len(runs) < 200):
-        runs.append(run(n))
-        spent += runs[-1][0]
-    best, nbytes = min(runs, key=lambda r: r[0])
-    step_bytes = 15.89e9  # weight bytes of one 27B-shaped step
-    step_seconds = best * step_bytes / nbytes
-    return ROWS / step_seconds, cores, f"oracle port, FFN slice of {n} of {I} columns ({nbytes / 1e6:.0f} MB of weights), best of {len(runs)} runs ({spent:.0f} s of CPU work), scaled by weight bytes to a step"
+        kd = max(256, n // 256 * 256)
+        wd = qf.realistic(4, H, kd, seed=3)
+        x, xa = qf.activations(ROWS, H), qf.activations(ROWS, kd, seed=1)
+        act, out = np.zeros((ROWS, n), np.uint16), np.zeros((ROWS, H), np.uint16)
+
+        def run():
+            assert o.so_linear(0, P(w2), n, H, P(x), ROWS, 3, None, 0, P(act), n, 0, 0) == 0
+            assert o.so_linear(4, P(wd), H, kd, P(xa), ROWS, 0, None, 0, P(out), H, 0, 0) == 0
+        return run, w2.nbytes + wd.nbytes
+    probe, _ = ffn(1024)
+    dt, _, _ = best_of(probe, 0.0, least=1)
+    n = int(min(I, max(1024, 1024 * seconds_budget / 6 / max(dt, 1e-3)))) // 256 * 256
+    run, nbytes = ffn(n)
+    ffn_s, ffn_runs, ffn_spent = best_of(run, seconds_budget / 3, least=3)
+    proj_s = ffn_s * 15.89e9 / nbytes  # weight bytes of one 27B-shaped step
+
+    # ---- attention: one KV head (6 query heads, D = 256) over 32K tokens of INT8 pages, 16 rows ----
+    rng = np.random.default_rng(5)
+    D, G, page = 256, 6, 256
+    pages = (CONTEXT + page - 1) // page + 1
+    kv = ol.HostKv(pages, 1, D, page, True)
+    kv.fill_random(rng)
+    table = np.arange(pages, dtype=np.uint32)
+    queries = ol.f2bf(rng.standard_normal((ROWS, G, D)).astype(np.float32))
+    qkv = ol.f2bf(rng.standard_normal((ROWS, G * 2 * D + 2 * D)).astype(np.float32))
+    attn_out = np.zeros((ROWS, G * D), np.uint16)
+    desc = kv.desc()
+    o.so_attention.argtypes = [ctypes.c_void_p] * 2 + [ctypes.c_uint32] * 4 + [ctypes.c_void_p] * 2 + [ctypes.c_uint32] + [ctypes.c_void_p] * 2 + [ctypes.c_uint32, ctypes.c_void_p]
+    attn_s, attn_runs, attn_spent = best_of(
+        lambda: o.so_attention(P(queries), P(qkv), qkv.shape[1], ROWS, G, 1, ctypes.byref(desc), P(table), CONTEXT - ROWS, None, P(attn_out), G * D, None),
+        seconds_budget / 3, least=1)
+    attn_step_s = attn_s * 4 * 16
+
+    # ---- Gated DeltaNet: one layer (16 key / 48 value heads), 16 rows, folding 6 pending rows ----
+    KH, VH = 16, 48
+    KW, VW = KH * 128, VH * 128
+    C = 2 * KW + VW
+    bf = lambda shape, sc: ol.f2bf((rng.standard_normal(shape) * sc).astype(np.float32))
+    g = dict(qkvz=bf((ROWS, C + VW), 1.0), b=bf((ROWS, VH), 1.0), a=bf((ROWS, VH), 1.0), conv_w=bf((C, 4), 0.4),
+             a_scale=(-np.exp(rng.uniform(-3, 0.5, VH))).astype(np.float32), dt_bias=bf((VH,), 0.5), norm_w=np.ones(128, np.float32),
+             cs_in=bf((3, C), 1.0), cs_out=np.zeros((3, C), np.uint16), state=(rng.standard_normal((VH, 128, 128)) * 0.05).astype(np.float32),
+             state_out=np.zeros((VH, 128, 128), np.float32), hidden=np.zeros((ROWS, VW), np.uint16))
+    pend = dict(inputs=bf((ROWS, C), 1.0), k=bf((ROWS, KW), 0.09), v=bf((ROWS, VW), 0.5), beta=ol.f2bf(rng.uniform(0.1, 0.9, (ROWS, VH)).astype(np.float32)),
+                decay=rng.uniform(0.5, 1.0, (ROWS, VH)).astype(np.float32))
+    step = dict(inputs=np.zeros((ROWS, C), np.uint16), k=np.zeros((ROWS, KW), np.uint16), v=np.zeros((ROWS, VW), np.uint16),
+                beta=np.zeros((ROWS, VH), np.uint16), decay=np.zeros((ROWS, VH), np.float32))
+    tape = lambda t: ol.SoGdnTape(P(t["inputs"]), P(t["k"]), P(t["v"]), P(t["beta"]), P(t["decay"]))
+    ga = ol.SoGdnArgs(P(g["qkvz"]), P(g["b"]), P(g["a"]), P(g["conv_w"]), P(g["a_scale"]), P(g["dt_bias"]), P(g["norm_w"]), P(g["cs_in"]), P(g["cs_out"]),
+                      P(g["state"]), P(g["state_out"]), tape(pend), tape(step), P(g["hidden"]), ROWS, FOLD_ROWS, KH, VH, C + VW, VH, VW, 1, None, 0)
+    gdn_s, gdn_runs, gdn_spent = best_of(lambda: o.so_gdn_verify(ctypes.byref(ga)), seconds_budget / 6, least=3)
+    gdn_step_s = gdn_s * 48
+
+    step_seconds = proj_s + attn_step_s + gdn_step_s
+    sample = (f"oracle port on {threads} OpenMP threads: projections from an FFN slice of {n} of {I} columns ({nbytes / 1e6:.0f} MB of weights, best of "
+              f"{ffn_runs} runs) scaled by weight bytes = {proj_s:.2f} s; attention of one KV head x 6 query heads over {CONTEXT} tokens (best of {attn_runs}) "
+              f"x 4 heads x 16 layers = {attn_step_s:.2f} s; one Gated-DeltaNet layer of {VH} heads folding {FOLD_ROWS} rows (best of {gdn_runs}) x 48 layers = "
+              f"{gdn_step_s:.2f} s; {ffn_spent + attn_spent + gdn_spent:.0f} s of CPU work in all")
+    return ROWS / step_seconds, threads, sample
 
 
 def main():
+    if "--case" in sys.argv[1:]:  # one operator on one shape (bench_cases.py), not the benchmark
+        import bench_cases
+        argv = sys.argv[1:]
+        argv.remove("--case")
+        return bench_cases.main(argv)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
@@ -166,7 +228,7 @@ def main():
         try:
             tp.connect(t, group.all_gather_bytes)
             bad = 0
-        except lib.SbError as e:  # no peer mapping on this machine
+        except lib.SbError as e:  # the peers' memory could not be mapped
             bad, fell_back = 1, f"tensor-parallel windows could not be mapped ({e}); measured as independent lanes"
         bad = int(group.reduce_max(bad))
         if not bad:
@@ -179,7 +241,7 @@ def main():
             lib.stream_sync(stream)
             bad = int(group.reduce_max(lib.device_status()))
             if bad:
-                fell_back = f"tensor-parallel exchange failed on this machine (device status {bad}); measured as independent lanes"
+                fell_back = f"tensor-parallel exchange failed (device status {bad}); measured as independent lanes"
         if bad:
             fell_back = fell_back or "tensor parallelism failed on another rank; measured as independent lanes"
             group.barrier()
@@ -190,9 +252,13 @@ def main():
         t.randomize(1234 + rank, context)
     lanes = 1 if tensor_parallel else world
     warm = max(args.warmup, 3)
-    flags = target.GRAPH  # hold the lane at 32K: every step does the same work
+    # The lane is held at its context length, so every step does the same work, and keeps FOLD_ROWS pending rows, so
+    # every step also folds that many rows of the previous step's tape into the Gated-DeltaNet state, as a committing
+    # cycle with that accept length would.
+    flags = target.GRAPH | target.KEEP_PENDING
     rng = np.random.default_rng(0 if tensor_parallel else rank)
     t.upload(-1, "tokens", rng.integers(0, cfg["vocab"], ROWS).astype(np.uint32))
+    t.upload(-1, "pending_rows", np.array([FOLD_ROWS], np.uint32))
 
     def barrier():
         lib.stream_sync(stream)
@@ -241,6 +307,22 @@ def main():
     e3.sync()
     barrier()
     e2e_ms = reduce_max(e2.elapsed_ms(e3)) / args.steps
+
+    # ---- one checked step after the timed loops: the step computed something sane, and the same thing on every rank ----
+    _, retained, _, _ = t.verify(host[:ROWS].copy(), flags=flags, stream=stream)
+    logits = t.download(-1, "logits", np.float32, (ROWS, cfg["vocab"]))
+    finite = bool(np.isfinite(logits).all())
+    bits = logits.view(np.uint32).astype(np.uint64)
+    checksum = float(int((bits * (np.arange(bits.size, dtype=np.uint64).reshape(bits.shape) % 65521 + 1)).sum() % (1 << 52)))
+    spread = 0.0
+    if tensor_parallel:  # every rank selected from the same gathered logits: the ranks' checksums must be one value
+        spread = reduce_max(checksum) + reduce_max(-checksum)
+    finite = int(reduce_max(0 if finite else 1)) == 0  # on every rank
+    parity_check = {"finite_logits": finite, "retained": int(retained),
+                    "retained_ok": 1 <= int(retained) <= ROWS, "device_status": int(reduce_max(lib.device_status())),
+                    "ranks_agree": (spread == 0.0) if tensor_parallel else None,
+                    "what": "one verify step after the timed loops: logits finite, 1 <= retained <= 16, device status 0" +
+                            ("; a position-weighted checksum of the logits' bits is equal on all ranks (max - min = 0)" if tensor_parallel else "")}
 
     if rank != 0:
         group.close()
@@ -292,7 +374,9 @@ def main():
         "metric": "verify_tokens_per_s", "value": lanes * ROWS / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if tensor_parallel else "weak", "vs_baseline": None,
         "dtype": "f16 operands (exact integer codes), f32 accumulate, bf16 activations", "data": "synthetic",
-        "config": {"workload": workload, "context_tokens": context, "block": ROWS, "parallelism": "tp1" if world == 1 else (f"tp{world}: one lane, shares exchanged through peer memory over NVLink in the input conversions" if tensor_parallel else f"{world} independent replicas (lanes)" + (f"; {fell_back}" if fell_back else "")),
+        "config": {"workload": workload, "context_tokens": context, "block": ROWS,
+                   "fold": f"held lane that keeps {FOLD_ROWS} pending rows: every timed step folds {FOLD_ROWS} tape rows into the GDN state",
+                   "parallelism": "tp1" if world == 1 else (f"tp{world}: one lane, shares exchanged through peer memory over NVLink in the input conversions" if tensor_parallel else f"{world} independent replicas (lanes)" + (f"; {fell_back}" if fell_back else "")),
                    "l2": "inputs exceed L2: one step streams %.1f GB of weights" % (stats["weight_bytes"] / 1e9), "cuda_graph": True, "pdl": True},
         "e2e": {"value": lanes * ROWS / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": ROWS * 4, "d2h_bytes_per_step": 16 + ROWS * 4},
         "gpu_launches": stats["launches"] * args.steps,
@@ -301,7 +385,7 @@ def main():
                           "state_bytes": stats["state_bytes"], "achieved_gbs": step_gbs, "frac_of_measured_peak": step_gbs / peak},
         "roofline": roofline,
         "cpu_baseline": {"value": cpu_tps, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
-        "clocks": clocks, "device_status": status,
+        "clocks": clocks, "device_status": status, "parity_check": parity_check,
     }
     print(json.dumps(result))
     group.close()

@@ -1,10 +1,11 @@
-"""Single-operator cases on seeded synthetic inputs, timed with CUDA events: the small commands the ncu
-summaries under profiles/ were captured from, and a quick way to time one kernel on a shape.
+"""Single-operator cases of bench.py on seeded synthetic inputs, timed with CUDA events: the small commands that
+single-kernel ncu captures are taken from, and a quick way to time one kernel on a shape.
 
-    python -m splash_b200.cases linear --fmt q4k --n 17408 --k 5120 --epilogue gate_up [--iters 20]
-    python -m splash_b200.cases attention --context 32768 [--q-heads 24 --kv-heads 4 --head-dim 256]
-    python -m splash_b200.cases gdn [--key-heads 16 --value-heads 48]
-    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 -m splash_b200.cases exchange
+    python bench.py --case linear --fmt q4k --n 17408 --k 5120 --epilogue gate_up [--iters 20]
+    python bench.py --case attention --context 32768 [--q-heads 24 --kv-heads 4 --head-dim 256]
+    python bench.py --case gdn [--key-heads 16 --value-heads 48]
+    python bench.py --case moe
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 2 --master-addr 127.0.0.1 bench.py --case exchange
         (one rank per GPU: the tensor-parallel input conversion against the local one, replayed as CUDA graphs)
 
 Weights are random native blocks with scale fields in the ranges the tests use (Q4_K / Q8_0 d, dmin in
@@ -15,7 +16,7 @@ import sys
 
 import numpy as np
 
-from . import lib
+from splash_b200 import lib
 
 FMT = {"q4k": lib.FMT_Q4K, "q6k": lib.FMT_Q6K, "q80": lib.FMT_Q80}
 EPI = {"none": lib.EP_NONE, "residual": lib.EP_RESIDUAL, "gate_up": lib.EP_GATE_UP}
@@ -90,7 +91,7 @@ def case_linear(a):
     bufs = [lib.DeviceBuffer.from_numpy(rows) for _ in range(copies * tensors)]
     x = lib.DeviceBuffer.from_numpy(bf16_bits(rng.standard_normal((16, k))))
     prep = lib.DeviceBuffer(int(lib.load().sb_linear_prepared_bytes(k)))
-    lib.check(lib.load().sb_linear_prepare(None, x.ptr, a.rows, k, k, None, fmt, prep.ptr, None, (a.diag << 8) | (lib.LINEAR_TCGEN05 if a.tcgen05 else 0)))
+    lib.check(lib.load().sb_linear_prepare(None, x.ptr, a.rows, k, k, None, fmt, prep.ptr, None, (lib.LINEAR_TCGEN05 if a.tcgen05 else 0)))
     out = lib.DeviceBuffer(16 * n * 4 + 512)
     aux = lib.DeviceBuffer.from_numpy(np.zeros((16, n), np.uint16))
 
@@ -103,7 +104,7 @@ def case_linear(a):
             w = bufs[i % len(bufs)].ptr
             if ep == lib.EP_RESIDUAL:
                 kw = dict(aux=aux.ptr)
-        lib.linear(w, None, out.ptr, fmt, n, k, a.rows, prepared=prep.ptr, epilogue=ep, flags=(lib.LINEAR_PDL if a.pdl else 0) | (a.diag << 8) | (lib.LINEAR_TCGEN05 if a.tcgen05 else 0), stream=stream, **kw)
+        lib.linear(w, None, out.ptr, fmt, n, k, a.rows, prepared=prep.ptr, epilogue=ep, flags=(lib.LINEAR_PDL if a.pdl else 0) | (lib.LINEAR_TCGEN05 if a.tcgen05 else 0), stream=stream, **kw)
 
     us = timed(launch, a.iters, graph=a.graph)
     algo = n * rb * tensors + a.rows * k * 2 + a.rows * n * 2
@@ -200,8 +201,8 @@ def case_moe(a):
 def case_exchange(a):
     """sb_tp_prepare_sum (push + conversion with the peers' shares) against sb_linear_prepare_sum, `launches` calls
     captured into one CUDA graph and replayed, so the host's launch rate does not enter."""
-    from . import tp
-    from .dist import Group
+    from splash_b200 import tp
+    from splash_b200.dist import Group
     d = Group("nccl")
     lib.init(d.local)
     l = lib.load()
@@ -250,7 +251,7 @@ def case_exchange(a):
 
 
 def main(argv=None):
-    ap = argparse.ArgumentParser(prog="python -m splash_b200.cases")
+    ap = argparse.ArgumentParser(prog="python bench.py --case")
     sub = ap.add_subparsers(dest="case", required=True)
     p = sub.add_parser("linear")
     p.add_argument("--fmt", choices=sorted(FMT), default="q4k")
@@ -261,7 +262,6 @@ def main(argv=None):
     p.add_argument("--iters", type=int, default=20)
     p.add_argument("--pdl", action="store_true")
     p.add_argument("--graph", action="store_true", help="capture the launches into a CUDA graph and time its replay")
-    p.add_argument("--diag", type=int, default=0, help="kernel diagnostics (flags bits 8 and up)")
     p.add_argument("--tcgen05", action="store_true", help="Q4_K on the tensor-memory kernel (SB_LINEAR_TCGEN05)")
     p.add_argument("--resident-mb", type=float, default=400.0, help="rotate weight copies over at least this many MB")
     p = sub.add_parser("attention")

@@ -82,7 +82,13 @@ SB_API int sb_set_pdl(int enabled);
 enum { SB_ATTENTION_TCGEN05 = 0, SB_ATTENTION_WARP_MMA = 1 };
 SB_API int sb_set_attention_kernel(int kind);
 
+/* Device buffers. An allocation is held by whoever allocated it and by every live view of it; sb_free lets one holder
+ * go (an allocation's own, given its base address; a view's, given the view's address) and the memory returns to the
+ * driver with the last one, so a view keeps its base alive (the reference's ref-counted buffer handles,
+ * runtime/metal/MetalBackend.hpp:42-78). sb_view checks [offset, offset + bytes) against the allocation that holds
+ * base_dev (itself a base or a view) and fails with SB_ERR_INVALID when it runs past it. */
 SB_API int sb_alloc(size_t bytes, void **out_dev);
+SB_API int sb_view(void *base_dev, size_t offset, size_t bytes, void **out_view);
 SB_API int sb_free(void *dev);
 SB_API int sb_memset(void *dev, int value, size_t bytes, void *stream);
 SB_API int sb_upload(void *dst_dev, const void *src_host, size_t bytes, void *stream);
@@ -97,6 +103,10 @@ SB_API int sb_event_create(void **out_event);
 SB_API int sb_event_destroy(void *event);
 SB_API int sb_event_record(void *event, void *stream);
 SB_API int sb_event_sync(void *event);
+/* Completion without blocking (*out_done 1 or 0), and a wait that gives up: SB_ERR_BUSY after timeout_ms with the event
+ * still pending (the reference's bounded wait on a ticket, runtime/metal/MetalBackend.hpp:468-478). */
+SB_API int sb_event_query(void *event, int *out_done);
+SB_API int sb_event_wait_bounded(void *event, uint32_t timeout_ms);
 SB_API int sb_event_elapsed_ms(void *start, void *stop, float *out_ms);
 
 /* CUDA-graph capture of a sequence of launches on `stream` (replaces CommandGraph). */
@@ -104,6 +114,13 @@ SB_API int sb_graph_begin(void *stream);
 SB_API int sb_graph_end(void *stream, void **out_graph);
 SB_API int sb_graph_launch(void *graph, void *stream);
 SB_API int sb_graph_destroy(void *graph);
+/* The reference's submission rule on top of sb_graph_launch: exactly one command in flight
+ * (runtime/metal/MetalBackend.hpp:371-375). sb_submit launches the graph and hands out a ticket; a second sb_submit
+ * before that ticket is consumed fails with SB_ERR_BUSY and enqueues nothing. sb_ticket_wait consumes the ticket once the
+ * command has completed, or returns SB_ERR_BUSY after timeout_ms and leaves the ticket out. sb_graph_launch itself
+ * stays unguarded for callers that order their work by streams and events. */
+SB_API int sb_submit(void *graph, void *stream, uint64_t *out_ticket);
+SB_API int sb_ticket_wait(uint64_t ticket, uint32_t timeout_ms);
 
 /* ---- weights ---- */
 
@@ -315,8 +332,15 @@ typedef struct SbGdnArgs {
    * pending tape's first pending_rows rows. */
   const void *tree;
   const uint32_t *pending_path_dev;
-  uint32_t pending_path, reserved;
+  uint32_t pending_path;
+  uint32_t flags;           /* SB_GDN_* */
 } SbGdnArgs;
+enum {
+  SB_GDN_STATE_SETTLED = 1 /* the caller vouches that no launch still running on the stream writes state_in, so the kernel
+                              may fetch the cell before it waits for the launch ahead (the model's step: the cell was written
+                              a whole step earlier). Without the flag every read waits, which is what a fold followed at
+                              once by a step on the swapped cells needs (ops::GDN::addFold then addDecode). */
+};
 SB_API int sb_gdn_verify(void *stream, const SbGdnArgs *args);
 
 /* sb_gdn_verify for callers that cannot allocate device memory: a process whose GPU memory is already handed out
@@ -425,11 +449,14 @@ typedef struct SbTargetConfig {
 enum {
   SB_TARGET_ADVANCE = 1, /* the step commits: committed += retained, the next step folds the accepted rows */
   SB_TARGET_GRAPH = 2,   /* replay the step as a captured CUDA graph (captured on first use per parity) */
-  SB_TARGET_TREE = 4     /* the block is a tree: the target's `tree` buffer holds its SplashTreeRow rows (row 0 the anchor,
+  SB_TARGET_TREE = 4,    /* the block is a tree: the target's `tree` buffer holds its SplashTreeRow rows (row 0 the anchor,
                             parents before children; runtime/metal/abi/VerifyTree.h:24-45) instead of the chain the step
                             writes there itself. Positions are the rows' depths, attention and GDN follow each row's path,
                             the accepted path's KV rows move to their depths, and the next step folds the path's tape
                             rows. The step after a tree step carries the flag too (a chain can be given as a tree). */
+  SB_TARGET_KEEP_PENDING = 8 /* without SB_TARGET_ADVANCE: the lane's pending GDN rows (`pending_rows`, sb_target_tensor) stay
+                            as they are instead of being cleared, so every such step folds the same rows again: a held
+                            lane that still does a committing cycle's fold work (steady-state timing). */
 };
 
 /* ---- MoE routing ----

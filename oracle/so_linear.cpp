@@ -14,6 +14,8 @@
 //                  OpenMP over output columns; this is the timed host-CPU baseline
 #include "so_common.h"
 
+#include <omp.h>
+
 #include <algorithm>
 #include <vector>
 
@@ -21,6 +23,13 @@ SO_API uint64_t so_row_bytes(uint32_t f, uint32_t K);
 SO_API int so_dequant(uint32_t f, const uint8_t *native, uint32_t rows, uint32_t K, float *out);
 
 using namespace so;
+
+// Sets the OpenMP thread count of every oracle routine (n > 0) and returns the count in force. A launcher may have
+// exported OMP_NUM_THREADS=1 (torchrun does); the timed CPU baseline asks for the host's cores itself.
+SO_API int so_threads(int n) {
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+}
 
 // value[m*N+n] = sum_k x[m][k] w[n][k] in fp64 over the fp32 weight values;
 // bound_exact = 2^-16 sum|x| max|w| (weights used unrounded), bound_staged adds 2^-11 sum|x w| +

@@ -78,7 +78,10 @@ class QwenTarget {
 
   // Appends one verify step of `rows` rows to the graph. `parity` selects which GDN cell is current.
   // `treeGiven`: the `tree` buffer holds the block's rows (a tree); otherwise the step writes a chain's there.
-  void encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool treeGiven = false);
+  // `keepPending` (only without `advance`): the lane's pending GDN rows stay as they are instead of being cleared, so
+  // a held lane folds the same rows in every step (a steady-state timing loop).
+  void encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool treeGiven = false,
+                    bool keepPending = false);
 
   const SbTargetConfig &config() const { return cfg_; }   // the whole model
   const SbTargetConfig &local() const { return loc_; }    // this rank's heads and intermediate width (the vocabulary stays whole)
@@ -287,10 +290,11 @@ inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) co
 // Launched before and after the operator sequence (sb_target.cu).
 void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer &tree, const Buffer &positions, uint32_t rows, bool treeGiven);
 // (with a tensor-parallel group the step's end also advances the group's exchange count by `exchanges`)
+// advance: 0 the lane holds its position and its pending rows are cleared, 1 it commits, 2 it holds and keeps them
 void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, const Buffer &pendingPath,
-                   bool advance, void *tpGroup, uint32_t exchanges);
+                   uint32_t advance, void *tpGroup, uint32_t exchanges);
 
-inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool treeGiven) {
+inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool treeGiven, bool keepPending) {
   using namespace ops;
   if (rows < 1 || rows > kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: 1 to 16 rows");
   if (committedHost + rows > cfg_.max_context + kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: past the context bound");
@@ -355,6 +359,7 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
       if (treeGiven) g.treeRows = &tree, g.pendingPathDevice = &pendingPath;
       else g.pendingRowsDevice = &pendingRows;
       g.tiledHeads = c.tiled_heads != 0;
+      g.stateSettled = true;  // the current cell was written by the previous step's launch of this layer
       GDN::addDecode(graph, g, gdn_, rows);
     }
     PreparedInput mixedIn = Linear::prepare(graph, mixed_, rows, mixedWidth, mixedWidth, nullptr, w.outProj.format, prepared_[1]);
@@ -398,7 +403,7 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
     for (LayerWeights &w : layers_)
       if (w.attention) PagedAttention::addPathCommit(graph, kv_, w.pages, pageTable_, committedHost, pathMask, &committed);
   }
-  launchStepEnd(graph, results, committed, pendingRows, pendingPath, advance, tp_ ? tp_->group() : nullptr, exchange);
+  launchStepEnd(graph, results, committed, pendingRows, pendingPath, advance ? 1u : keepPending ? 2u : 0u, tp_ ? tp_->group() : nullptr, exchange);
 }
 
 }  // namespace splash::b200::model

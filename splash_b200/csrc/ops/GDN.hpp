@@ -57,6 +57,10 @@ struct GdnDecodeBuffers {
   // the tape's first pendingRows rows).
   const Buffer *treeRows = nullptr, *pendingPathDevice = nullptr;
   uint32_t pendingPath = 0;
+  // The caller vouches that nothing still running on the stream writes `current.state` (the model's step: the cell
+  // was written a whole step earlier), so the kernel may fetch it before waiting for the launch ahead
+  // (SB_GDN_STATE_SETTLED). Leave it off for addFold followed at once by addDecode on the swapped cells.
+  bool stateSettled = false;
 };
 
 class GDN {
@@ -105,6 +109,7 @@ class GDN {
       a.pending_path_dev = b.pendingPathDevice->as<uint32_t>();
     }
     a.pending_path = b.pendingPath;
+    a.flags = b.stateSettled ? SB_GDN_STATE_SETTLED : 0;
     a.rows = rows, a.pending_rows = b.pendingRows, a.key_heads = s.keyHeads, a.value_heads = s.valueHeads;
     a.qkvz_stride = b.packedStride, a.ab_stride = 2 * s.valueHeads, a.hidden_stride = b.hiddenStride, a.tiled = b.tiledHeads;
     check(sb_gdn_verify(graph.stream, &a));

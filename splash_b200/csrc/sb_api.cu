@@ -4,6 +4,12 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <atomic>
+#include <chrono>
+#include <map>
+#include <mutex>
+#include <thread>
+
 #include "sb_internal.h"
 
 namespace sb {
@@ -29,6 +35,31 @@ int cuda_fail(cudaError_t e, const char *what) {
                                                                                    : SB_ERR_CUDA;
   return fail(status, "%s: %s", what, cudaGetErrorString(e));
 }
+
+// Allocations by base address with a holder count: the allocation itself holds one, every live view one more, and the
+// memory goes back to the driver when the last holder lets go (the reference's buffers are ref-counted handles whose
+// views keep the base alive, runtime/metal/MetalBackend.hpp:42-78).
+struct Allocation {
+  size_t bytes = 0;
+  uint32_t holders = 0;
+};
+static std::mutex g_alloc_mutex;
+static std::map<uintptr_t, Allocation> g_allocs;       // base -> allocation
+static std::map<uintptr_t, std::pair<uintptr_t, uint32_t>> g_views;  // view address (not a base) -> {base, live views there}
+
+// The allocation that holds `p`, or end().
+static std::map<uintptr_t, Allocation>::iterator owner_of(uintptr_t p) {
+  auto it = g_allocs.upper_bound(p);
+  if (it == g_allocs.begin()) return g_allocs.end();
+  --it;
+  return p < it->first + it->second.bytes ? it : g_allocs.end();
+}
+
+// The one command the boundary lets be in flight (sb_submit): its completion event and whether a ticket is out.
+static std::mutex g_ticket_mutex;
+static cudaEvent_t g_ticket_event = nullptr;
+static uint64_t g_ticket_serial = 0;
+static bool g_ticket_out = false;
 
 }  // namespace sb
 
@@ -87,7 +118,15 @@ int sb_device_status(uint32_t *status) {
   SB_REQUIRE(status, "status is null");
   SB_CUDA(cudaDeviceSynchronize());
   SB_CUDA(cudaMemcpy(status, ctx().status_dev, sizeof(uint32_t), cudaMemcpyDeviceToHost));
-  if (*status) SB_CUDA(cudaMemset(ctx().status_dev, 0, sizeof(uint32_t)));
+  if (*status) {
+    // A kernel that gave up may have left its arrival counters part-way: the next launch must find them at zero, or its
+    // own wait would pass early on a stale count.
+    Context &c = ctx();
+    SB_CUDA(cudaMemset(c.status_dev, 0, sizeof(uint32_t)));
+    SB_CUDA(cudaMemset(c.linear_counters, 0, c.linear_counter_count * sizeof(uint32_t)));
+    SB_CUDA(cudaMemset(c.attn_counters, 0, 128 * sizeof(uint32_t)));
+    SB_CUDA(cudaMemset(c.gdn_counters, 0, 256 * sizeof(uint32_t)));
+  }
   return SB_OK;
 }
 
@@ -96,11 +135,48 @@ int sb_alloc(size_t bytes, void **out_dev) {
   SB_REQUIRE(out_dev && bytes, "sb_alloc: null result or zero bytes");
   *out_dev = nullptr;
   SB_CUDA(cudaMalloc(out_dev, bytes));
+  std::lock_guard<std::mutex> lock(g_alloc_mutex);
+  g_allocs[reinterpret_cast<uintptr_t>(*out_dev)] = Allocation{bytes, 1};
+  return SB_OK;
+}
+int sb_view(void *base_dev, size_t offset, size_t bytes, void **out_view) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(base_dev && out_view && bytes, "sb_view: null pointer or zero bytes");
+  std::lock_guard<std::mutex> lock(g_alloc_mutex);
+  const uintptr_t from = reinterpret_cast<uintptr_t>(base_dev);
+  auto it = owner_of(from);
+  SB_REQUIRE(it != g_allocs.end(), "sb_view: %p is not inside a live sb_alloc allocation", base_dev);
+  const size_t at = from - it->first;
+  SB_REQUIRE(offset <= it->second.bytes - at && bytes <= it->second.bytes - at - offset,
+             "sb_view: [%zu, %zu) runs past the allocation's %zu bytes", at + offset, at + offset + bytes, it->second.bytes);
+  const uintptr_t view = from + offset;
+  ++it->second.holders;
+  if (view != it->first) {
+    auto &v = g_views[view];
+    v.first = it->first;
+    ++v.second;
+  }
+  *out_view = reinterpret_cast<void *>(view);
   return SB_OK;
 }
 int sb_free(void *dev) {
   SB_NEED_DEVICE();
-  SB_CUDA(cudaFree(dev));
+  if (!dev) return SB_OK;
+  uintptr_t base = reinterpret_cast<uintptr_t>(dev);
+  {
+    std::lock_guard<std::mutex> lock(g_alloc_mutex);
+    auto v = g_views.find(base);
+    if (v != g_views.end()) {  // a view: its base loses a holder
+      const uintptr_t of = v->second.first;
+      if (--v->second.second == 0) g_views.erase(v);
+      base = of;
+    }
+    auto it = g_allocs.find(base);
+    SB_REQUIRE(it != g_allocs.end(), "sb_free: %p is neither a live allocation nor a live view", dev);
+    if (--it->second.holders > 0) return SB_OK;
+    g_allocs.erase(it);
+  }
+  SB_CUDA(cudaFree(reinterpret_cast<void *>(base)));
   return SB_OK;
 }
 int sb_memset(void *dev, int value, size_t bytes, void *stream) {
@@ -171,6 +247,27 @@ int sb_event_sync(void *event) {
   SB_CUDA(cudaEventSynchronize(reinterpret_cast<cudaEvent_t>(event)));
   return SB_OK;
 }
+int sb_event_query(void *event, int *out_done) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(event && out_done, "sb_event_query: null pointer");
+  const cudaError_t e = cudaEventQuery(reinterpret_cast<cudaEvent_t>(event));
+  if (e != cudaSuccess && e != cudaErrorNotReady) return cuda_fail(e, "cudaEventQuery");
+  *out_done = e == cudaSuccess;
+  return SB_OK;
+}
+int sb_event_wait_bounded(void *event, uint32_t timeout_ms) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(event, "sb_event_wait_bounded: null event");
+  const auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  for (uint32_t polls = 0;; ++polls) {
+    const cudaError_t e = cudaEventQuery(reinterpret_cast<cudaEvent_t>(event));
+    if (e == cudaSuccess) return SB_OK;
+    if (e != cudaErrorNotReady) return cuda_fail(e, "cudaEventQuery");
+    if (std::chrono::steady_clock::now() >= deadline) return fail(SB_ERR_BUSY, "sb_event_wait_bounded: not complete after %u ms", timeout_ms);
+    if (polls < 64) std::this_thread::yield();
+    else std::this_thread::sleep_for(std::chrono::microseconds(50));
+  }
+}
 int sb_event_elapsed_ms(void *start, void *stop, float *out_ms) {
   SB_NEED_DEVICE();
   SB_CUDA(cudaEventElapsedTime(out_ms, reinterpret_cast<cudaEvent_t>(start), reinterpret_cast<cudaEvent_t>(stop)));
@@ -196,6 +293,30 @@ int sb_graph_end(void *stream, void **out_graph) {
 int sb_graph_launch(void *graph, void *stream) {
   SB_NEED_DEVICE();
   SB_CUDA(cudaGraphLaunch(reinterpret_cast<cudaGraphExec_t>(graph), as_stream(stream)));
+  return SB_OK;
+}
+int sb_submit(void *graph, void *stream, uint64_t *out_ticket) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(graph && out_ticket, "sb_submit: null graph or ticket");
+  std::lock_guard<std::mutex> lock(g_ticket_mutex);
+  if (g_ticket_out) return fail(SB_ERR_BUSY, "sb_submit: command %llu is still in flight; consume its ticket first", (unsigned long long)g_ticket_serial);
+  if (!g_ticket_event) SB_CUDA(cudaEventCreateWithFlags(&g_ticket_event, cudaEventDisableTiming));
+  SB_CUDA(cudaGraphLaunch(reinterpret_cast<cudaGraphExec_t>(graph), as_stream(stream)));
+  SB_CUDA(cudaEventRecord(g_ticket_event, as_stream(stream)));
+  g_ticket_out = true;
+  *out_ticket = ++g_ticket_serial;
+  return SB_OK;
+}
+int sb_ticket_wait(uint64_t ticket, uint32_t timeout_ms) {
+  SB_NEED_DEVICE();
+  {
+    std::lock_guard<std::mutex> lock(g_ticket_mutex);
+    SB_REQUIRE(g_ticket_out && ticket == g_ticket_serial, "sb_ticket_wait: ticket %llu is not the command in flight", (unsigned long long)ticket);
+  }
+  const int st = sb_event_wait_bounded(g_ticket_event, timeout_ms);
+  if (st != SB_OK) return st;  // still in flight: the ticket stays out
+  std::lock_guard<std::mutex> lock(g_ticket_mutex);
+  g_ticket_out = false;
   return SB_OK;
 }
 int sb_graph_destroy(void *graph) {

@@ -397,10 +397,11 @@ extern "C" int sb_attn_verify(void *stream, const SbAttnArgs *a) {
   const size_t smem = size_t(kMaxFused + kConv * 2 * kChunk) * (D + 8) * 2 + kConv * 2 * kChunk * sizeof(float) +
                       size_t(kRing) * (2 * kChunk * D + 256) + (kRing + 2 * kConv) * sizeof(uint64_t);
   void (*kernel)(const AttnParams) = D == 256 ? attention_kernel<256> : attention_kernel<128>;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[D == 256]) {
+  static bool attr_set[64][2] = {};  // a function attribute is per device
+  const int dev = ctx().device >= 0 && ctx().device < 64 ? ctx().device : 0;
+  if (!attr_set[dev][D == 256]) {
     SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    attr_set[D == 256] = true;
+    attr_set[dev][D == 256] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(splits, c.kv_heads);

@@ -388,10 +388,11 @@ int launch_attention_tc(cudaStream_t stream, AttnParams &p, uint32_t visible) {
   p.splits = splits, p.chunks_per_split = cps;
   const size_t smem = D == 256 ? AtLayout<256>::kBytes : AtLayout<128>::kBytes;
   void (*kernel)(const AttnParams) = D == 256 ? attention_tc_kernel<256> : attention_tc_kernel<128>;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[D == 256]) {
+  static bool attr_set[64][2] = {};  // a function attribute is per device
+  const int dev = ctx().device >= 0 && ctx().device < 64 ? ctx().device : 0;
+  if (!attr_set[dev][D == 256]) {
     SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)));
-    attr_set[D == 256] = true;
+    attr_set[dev][D == 256] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(splits, p.cache.kv_heads);

@@ -18,6 +18,7 @@
 //   rollback the state after the block is never stored: the caller passes how many tape rows were accepted
 //            (pending_rows, or a device word written by sb_accept) to the next step, which folds them
 #include <algorithm>
+#include <atomic>
 #include <cooperative_groups.h>
 
 #include "sb_internal.h"
@@ -86,21 +87,29 @@ __global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads,
   const uint16_t *pin = static_cast<const uint16_t *>(a.pending.inputs);
   const bool qk_writer = h % per_key == 0 && vs == 0;
 
-  // The state of this warp's 4 value dimensions, requested first so the latency hides behind the prologue, and before
-  // the wait for the kernel ahead: the cell was written a whole step ago, and this CTA may be resident while the
-  // projection before it drains.
+  // The state of this warp's 4 value dimensions, requested first so the latency hides behind the prologue and, where
+  // the caller allows it (below), before the wait for the kernel ahead: in the model's step the cell was written a
+  // whole step ago, and this CTA may be resident while the projection before it drains.
   // lane l holds row 4 warp + l / 8, key columns 32 c + 4 (l % 8) .. + 3 for c = 0..3 (the 8 lanes of a row read 128
   // contiguous bytes at a time, from global and from shared memory), so a dot product over the 128 key columns
   // is 16 multiply-adds in the lane and three butterfly rounds over its 8-lane group.
   float S[16];
   const uint32_t srow = 4 * warp + (lane >> 3), scol = 4 * (lane & 7);
   const size_t sbase = (size_t(h) * kD + vd0 + srow) * kD + scol;
+  auto load_state = [&] {
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    const float4 s4 = *reinterpret_cast<const float4 *>(a.state_in + sbase + 32 * c);
-    S[4 * c] = s4.x, S[4 * c + 1] = s4.y, S[4 * c + 2] = s4.z, S[4 * c + 3] = s4.w;
-  }
+    for (int c = 0; c < 4; ++c) {
+      const float4 s4 = *reinterpret_cast<const float4 *>(a.state_in + sbase + 32 * c);
+      S[4 * c] = s4.x, S[4 * c + 1] = s4.y, S[4 * c + 2] = s4.z, S[4 * c + 3] = s4.w;
+    }
+  };
+  // Only a caller that vouches for the cell (SB_GDN_STATE_SETTLED: nothing still running on the stream writes
+  // state_in) gets the early load; otherwise the launch ahead may be the one that produced the cell (a fold
+  // followed at once by a step on the swapped cells), and the load waits for it like every other read.
+  const bool settled = (a.flags & SB_GDN_STATE_SETTLED) != 0;
+  if (settled) load_state();
   pdl_wait();
+  if (!settled) load_state();
   // The previous step's accepted path in its tape: a row mask, or the tape's first rows.
   uint32_t pending_path = a.pending_path_dev ? *a.pending_path_dev : a.pending_path;
   if (!a.pending_path_dev && !a.pending_path) {
@@ -422,17 +431,17 @@ static __device__ __align__(256) uint8_t g_gdn_static_scratch[kStaticScratchByte
 // cudaGetSymbolAddress, asked once per device with that device current.
 static int static_scratch_address(uint8_t **out) {
   constexpr int kMaxDevices = 64;
-  static uint8_t *address[kMaxDevices] = {};
+  static std::atomic<uint8_t *> address[kMaxDevices];  // (two threads racing here store the same value)
   int device = -1;
   SB_CUDA(cudaGetDevice(&device));
   SB_REQUIRE(device >= 0 && device < kMaxDevices, "sb_gdn_verify_static: device index %d outside 0..%d", device, kMaxDevices - 1);
-  if (!address[device]) {
+  if (!address[device].load(std::memory_order_acquire)) {
     void *p = nullptr;
     SB_CUDA(cudaGetSymbolAddress(&p, g_gdn_static_scratch));
     SB_REQUIRE(p != nullptr, "sb_gdn_verify_static: the scratch symbol has no address on device %d", device);
-    address[device] = static_cast<uint8_t *>(p);
+    address[device].store(static_cast<uint8_t *>(p), std::memory_order_release);
   }
-  *out = address[device];
+  *out = address[device].load(std::memory_order_acquire);
   return SB_OK;
 }
 
@@ -440,28 +449,37 @@ static int static_scratch_address(uint8_t **out) {
 
 using namespace sb;
 
-extern "C" int sb_gdn_verify(void *stream, const SbGdnArgs *a) {
-  SB_NEED_DEVICE();
-  SB_REQUIRE(a, "sb_gdn_verify: null arguments");
+namespace sb {
+// The argument checks both entry points share; `who` names the caller in the message.
+static int gdn_validate(const SbGdnArgs *a, const char *who) {
+  SB_REQUIRE(a, "%s: null arguments", who);
   SB_REQUIRE(a->qkvz && ((a->b && a->a) || a->gate_weight) && a->conv_w && a->a_scale && a->dt_bias && a->norm_w && a->conv_state_in &&
                  a->conv_state_out && a->state_in && a->state_out && a->hidden,
-             "sb_gdn_verify: null pointer");
-  SB_REQUIRE(a->rows <= kGdnRows && a->pending_rows <= kGdnRows, "sb_gdn_verify: rows %u or pending rows %u above %d", a->rows,
-             a->pending_rows, kGdnRows);
-  SB_REQUIRE(a->key_heads >= 1 && a->value_heads % a->key_heads == 0 && a->value_heads <= 256, "sb_gdn_verify: %u value heads over %u key heads",
-             a->value_heads, a->key_heads);
+             "%s: null pointer", who);
+  SB_REQUIRE(a->rows <= kGdnRows && a->pending_rows <= kGdnRows, "%s: rows %u or pending rows %u above %d", who, a->rows, a->pending_rows, kGdnRows);
+  SB_REQUIRE(a->key_heads >= 1 && a->value_heads >= 1 && a->value_heads % a->key_heads == 0 && a->value_heads <= 256,
+             "%s: %u value heads over %u key heads", who, a->value_heads, a->key_heads);
   const uint32_t C = (2 * a->key_heads + a->value_heads) * kD;
   SB_REQUIRE(a->qkvz_stride >= C + a->value_heads * kD && (a->gate_weight || a->ab_stride >= a->value_heads) && a->hidden_stride >= a->value_heads * kD,
-             "sb_gdn_verify: a stride is below its row");
-  SB_REQUIRE(a->rows == 0 || (a->step.inputs && a->step.k && a->step.v && a->step.beta && a->step.decay), "sb_gdn_verify: null tape of this step");
+             "%s: a stride is below its row", who);
+  SB_REQUIRE(a->rows == 0 || (a->step.inputs && a->step.k && a->step.v && a->step.beta && a->step.decay), "%s: null tape of this step", who);
   SB_REQUIRE((a->pending_rows == 0 && !a->pending_rows_dev && !a->pending_path && !a->pending_path_dev) ||
                  (a->pending.inputs && a->pending.k && a->pending.v && a->pending.beta && a->pending.decay),
-             "sb_gdn_verify: null pending tape");
-  SB_REQUIRE(a->pending_path < (1u << kGdnRows), "sb_gdn_verify: pending path 0x%x names rows above %d", a->pending_path, kGdnRows);
-  SB_REQUIRE(a->state_in != a->state_out && a->conv_state_in != a->conv_state_out, "sb_gdn_verify: the committed cell is a second cell");
+             "%s: null pending tape", who);
+  SB_REQUIRE(a->pending_path < (1u << kGdnRows), "%s: pending path 0x%x names rows above %d", who, a->pending_path, kGdnRows);
+  SB_REQUIRE(a->state_in != a->state_out && a->conv_state_in != a->conv_state_out, "%s: the committed cell is a second cell", who);
   SB_REQUIRE(!a->gate_weight || (a->gate_input && a->gate_k && a->gate_k % 8 == 0 && a->gate_input_stride >= a->gate_k && a->gate_input_stride % 8 == 0 &&
                                  (reinterpret_cast<uintptr_t>(a->gate_weight) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->gate_input) & 15) == 0),
-             "sb_gdn_verify: fused gate projection needs a 16-byte aligned input and weight, k a multiple of 8 and stride >= k");
+             "%s: fused gate projection needs a 16-byte aligned input and weight, k a multiple of 8 and stride >= k", who);
+  SB_REQUIRE((a->flags & ~uint32_t(SB_GDN_STATE_SETTLED)) == 0, "%s: unknown flags 0x%x", who, a->flags);
+  return SB_OK;
+}
+}  // namespace sb
+
+extern "C" int sb_gdn_verify(void *stream, const SbGdnArgs *a) {
+  SB_NEED_DEVICE();
+  const int valid = gdn_validate(a, "sb_gdn_verify");
+  if (valid != SB_OK) return valid;
   Context &c = ctx();
   GdnParams p{*a, c.gdn_scratch, c.gdn_counters};
   cudaLaunchConfig_t cfg = {};
@@ -478,29 +496,11 @@ extern "C" int sb_gdn_verify(void *stream, const SbGdnArgs *a) {
 }
 
 extern "C" int sb_gdn_verify_static(void *stream, const SbGdnArgs *a) {
-  SB_REQUIRE(a, "sb_gdn_verify_static: null arguments");
-  SB_REQUIRE(a->qkvz && ((a->b && a->a) || a->gate_weight) && a->conv_w && a->a_scale && a->dt_bias && a->norm_w && a->conv_state_in &&
-                 a->conv_state_out && a->state_in && a->state_out && a->hidden,
-             "sb_gdn_verify_static: null pointer");
+  const int valid = gdn_validate(a, "sb_gdn_verify_static");
+  if (valid != SB_OK) return valid;
   SB_REQUIRE(a->value_heads <= kStaticMaxValueHeads,
              "sb_gdn_verify_static: %u value heads exceed the %u the built-in scratch holds; use sb_gdn_verify", a->value_heads,
              kStaticMaxValueHeads);
-  SB_REQUIRE(a->rows <= kGdnRows && a->pending_rows <= kGdnRows, "sb_gdn_verify_static: rows %u or pending rows %u above %d", a->rows,
-             a->pending_rows, kGdnRows);
-  SB_REQUIRE(a->key_heads >= 1 && a->value_heads >= 1 && a->value_heads % a->key_heads == 0, "sb_gdn_verify_static: %u value heads over %u key heads",
-             a->value_heads, a->key_heads);
-  const uint32_t C = (2 * a->key_heads + a->value_heads) * kD;
-  SB_REQUIRE(a->qkvz_stride >= C + a->value_heads * kD && (a->gate_weight || a->ab_stride >= a->value_heads) && a->hidden_stride >= a->value_heads * kD,
-             "sb_gdn_verify_static: a stride is below its row");
-  SB_REQUIRE(a->rows == 0 || (a->step.inputs && a->step.k && a->step.v && a->step.beta && a->step.decay), "sb_gdn_verify_static: null tape of this step");
-  SB_REQUIRE((a->pending_rows == 0 && !a->pending_rows_dev && !a->pending_path && !a->pending_path_dev) ||
-                 (a->pending.inputs && a->pending.k && a->pending.v && a->pending.beta && a->pending.decay),
-             "sb_gdn_verify_static: null pending tape");
-  SB_REQUIRE(a->pending_path < (1u << kGdnRows), "sb_gdn_verify_static: pending path 0x%x names rows above %d", a->pending_path, kGdnRows);
-  SB_REQUIRE(a->state_in != a->state_out && a->conv_state_in != a->conv_state_out, "sb_gdn_verify_static: the committed cell is a second cell");
-  SB_REQUIRE(!a->gate_weight || (a->gate_input && a->gate_k && a->gate_k % 8 == 0 && a->gate_input_stride >= a->gate_k && a->gate_input_stride % 8 == 0 &&
-                                 (reinterpret_cast<uintptr_t>(a->gate_weight) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->gate_input) & 15) == 0),
-             "sb_gdn_verify_static: fused gate projection needs a 16-byte aligned input and weight, k a multiple of 8 and stride >= k");
   uint8_t *scratch = nullptr;
   const int st = static_scratch_address(&scratch);
   if (st != SB_OK) return st;

@@ -44,6 +44,13 @@
 #ifndef SB_Q4K_I2_UNROLL
 #define SB_Q4K_I2_UNROLL 4
 #endif
+// Diagnostic switches (parts of the kernel turned off to time the rest) exist only in a build with -DSB_DIAG, where the
+// flags word's bits 8.. carry them; the shipped library ignores nothing: it refuses unknown flag bits.
+#ifdef SB_DIAG
+#define SB_DBG(bit) ((p.debug & (bit)) != 0)
+#else
+#define SB_DBG(bit) false
+#endif
 #define SB_PRAGMA_(x) _Pragma(#x)
 #define SB_PRAGMA(x) SB_PRAGMA_(x)
 #define SB_UNROLL_Q4K_I2 SB_PRAGMA(unroll SB_Q4K_I2_UNROLL)
@@ -840,13 +847,13 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
       }
       x_issued = true;
     };
-    for (uint32_t item = blockIdx.x; item < items && ok && !(p.debug & 16); item += gridDim.x) {
+    for (uint32_t item = blockIdx.x; item < items && ok && !SB_DBG(16); item += gridDim.x) {
       const uint32_t tile = item / p.slices;
       for (uint32_t c = 0; c < chunks && ok; ++c, ++fill) {
         const uint32_t slot = fill % p.stages, round = fill / p.stages;
         if (round > 0) {
           if (!x_issued) issue_x();
-          ok = (p.debug & 4) ? mbar_wait(&empty[slot], (round - 1) & 1) : mbar_wait_backoff(&empty[slot], (round - 1) & 1);
+          ok = SB_DBG(4) ? mbar_wait(&empty[slot], (round - 1) & 1) : mbar_wait_backoff(&empty[slot], (round - 1) & 1);
         }
         if (!ok) break;
         const uint32_t csb0 = sb0 + c * kStageSb, nsb_c = min(uint32_t(kStageSb), sb1 - csb0);
@@ -860,7 +867,7 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
           const uint32_t row0 = gate_up ? tile * 32 : tile * kTileRows;
           const uint32_t byte0 = p.lead[tn][j] + (csb0 + piece * p.piece_sb) * kSb;
           uint8_t *dst = smem + p.ring_off + slot * p.stage_bytes + lane * p.box_bytes;
-          tma_load_2d(dst, &maps.m[tn][j], int(byte0 >> 4) * 4, int(row0 >> p.period_log2), &full[slot], policy, (p.debug & 2) == 0);
+          tma_load_2d(dst, &maps.m[tn][j], int(byte0 >> 4) * 4, int(row0 >> p.period_log2), &full[slot], policy, SB_DBG(2) == 0);
         }
       }
     }
@@ -887,7 +894,7 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
     const float sback = scale_back[tok];
     uint32_t done = 0;
     for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++done) {
-      if (done % kEpiWarps != ew || (p.debug & 8)) continue;
+      if (done % kEpiWarps != ew || SB_DBG(8)) continue;
       const uint32_t tile = item / p.slices;
       if (!mbar_wait_backoff(&red_full[ew], (done / kEpiWarps) & 1)) { if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED); return; }
       float v[32];
@@ -1049,7 +1056,7 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
       const uint32_t slot = drained % p.stages, round = drained / p.stages;
       // Every warp follows every stage's barrier, with or without work in it: the parity wait tells only
       // consecutive phases apart.
-      if (!(p.debug & 16) && !mbar_wait(&full[slot], round & 1)) {
+      if (!SB_DBG(16) && !mbar_wait(&full[slot], round & 1)) {
         if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
         return;  // the launch has failed; the status word says so
       }
@@ -1057,7 +1064,7 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
       const uint32_t sbi = kg >= jmod ? kg - jmod : kg + kKG - jmod;  // the stage's super-block dealt to this k-group
       jmod += nsb_c;
       if (jmod >= kKG) jmod -= kKG;
-      if (sbi < nsb_c && !(p.debug & 1)) {
+      if (sbi < nsb_c && !SB_DBG(1)) {
         const uint8_t *stage = smem + p.ring_off + slot * p.stage_bytes;
         // A row sits in the box of its (piece, tensor, residue) at `lead` bytes past a 16-byte boundary
         // (always 0 for Q4_K, whose rows are 16-byte multiples).
@@ -1083,9 +1090,9 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
         multiply_super_block<FMT, kMT>(stage, roff, xs_sb, xs_sb + kXsbBytes, lane, y);
       }
       __syncwarp();
-      if (lane == 0 && !(p.debug & 16)) mbar_arrive(&empty[slot]);
+      if (lane == 0 && !SB_DBG(16)) mbar_arrive(&empty[slot]);
     }
-    if (p.debug & 8) continue;
+    if (SB_DBG(8)) continue;
     // Hand the tile's sums to the epilogue warp once it has read the previous tile's.
     if (done > 0 && !mbar_wait(&red_empty[(done - 1) % kEpiWarps], ((done - 1) / kEpiWarps) & 1)) {
       if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
@@ -1393,16 +1400,22 @@ extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
   p.n = a->n, p.k = a->k, p.rows = a->rows;
   p.aux_stride = a->aux_stride, p.out_stride = a->out_stride;
   p.epilogue = a->epilogue, p.out_f32 = a->out_f32;
+#ifdef SB_DIAG
   p.debug = a->flags >> 8;
+#else
+  SB_REQUIRE((a->flags & ~uint32_t(SB_LINEAR_PDL | SB_LINEAR_TCGEN05)) == 0, "sb_linear: unknown flags 0x%x", a->flags);
+#endif
 
   void (*kernel)(const LinearParams, const LinearMaps) = a->format == SB_FMT_Q4K   ? linear_kernel<SB_FMT_Q4K>
                                        : a->format == SB_FMT_Q6K ? linear_kernel<SB_FMT_Q6K>
                                                                  : linear_kernel<SB_FMT_Q80>;
-  static bool attr_set[3] = {false, false, false};
+  // The shared-memory cap is a per-device attribute of the function: remembered per (device, format).
+  static bool attr_set[64][3] = {};
   const int ki = a->format == SB_FMT_Q4K ? 0 : a->format == SB_FMT_Q6K ? 1 : 2;
-  if (!attr_set[ki]) {
+  const int dev = c.device >= 0 && c.device < 64 ? c.device : 0;
+  if (!attr_set[dev][ki]) {
     SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    attr_set[ki] = true;
+    attr_set[dev][ki] = true;
   }
   LinearMaps maps;
   for (uint32_t tn = 0; tn < p.tensors; ++tn)

@@ -478,10 +478,11 @@ int launch_linear_tc(cudaStream_t stream, const SbLinearArgs *a, const void *pre
   }
   if (!gate_up) maps.m[1] = maps.m[0];
   void (*kernel)(const TcParams, const TcMaps) = gate_up ? linear_tc_kernel<true> : linear_tc_kernel<false>;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[gate_up]) {
+  static bool attr_set[64][2] = {};  // a function attribute is per device
+  const int dev = ctx().device >= 0 && ctx().device < 64 ? ctx().device : 0;
+  if (!attr_set[dev][gate_up]) {
     SB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    attr_set[gate_up] = true;
+    attr_set[dev][gate_up] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(g.ctas);

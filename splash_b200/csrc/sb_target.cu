@@ -31,14 +31,14 @@ __global__ void step_end_kernel(const uint32_t *results, uint32_t *committed, ui
     // The next step's exchanges are numbered after this step's. Their kernels read the count when they start, and
     // kernels may start before the ones ahead of them complete: dependents are let go only after the count has moved.
     if (tp_epoch) *tp_epoch += tp_exchanges;
-    if (advance) {
+    if (advance == 1) {
       *committed += results[0];
       *pending_rows = results[0];
       *pending_path = results[2];
-    } else {
+    } else if (advance == 0) {
       *pending_rows = 0;
       *pending_path = 0;
-    }
+    }  // (2: the lane stays where it is and keeps its pending rows: every such step folds the same rows again)
     __threadfence();
   }
   __syncthreads();
@@ -140,7 +140,7 @@ void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer 
   ++graph.launches;
 }
 void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, const Buffer &pendingPath,
-                   bool advance, void *tpGroup, uint32_t exchanges) {
+                   uint32_t advance, void *tpGroup, uint32_t exchanges) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(1), cfg.blockDim = dim3(32), cfg.stream = sb::as_stream(graph.stream);
   cudaLaunchAttribute attr[1];
@@ -148,7 +148,7 @@ void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &com
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = graph.pdl ? 1 : 0;
   if (cudaLaunchKernelEx(&cfg, sb::step_end_kernel, static_cast<const uint32_t *>(results.as<uint32_t>()), committed.as<uint32_t>(),
-                         pendingRows.as<uint32_t>(), pendingPath.as<uint32_t>(), advance ? 1u : 0u, sb::tp_epoch_word(tpGroup), exchanges) != cudaSuccess)
+                         pendingRows.as<uint32_t>(), pendingPath.as<uint32_t>(), advance, sb::tp_epoch_word(tpGroup), exchanges) != cudaSuccess)
     throw BackendError(SB_ERR_CUDA, "step_end launch failed");
   ++graph.launches;
 }
@@ -340,6 +340,7 @@ int sb_target_randomize(void *target, uint64_t seed, uint32_t committed) {
 static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float temperature, uint32_t flags) {
   QwenTarget &m = *t->model;
   const bool advance = (flags & SB_TARGET_ADVANCE) != 0, tree = (flags & SB_TARGET_TREE) != 0;
+  const bool keep = !advance && (flags & SB_TARGET_KEEP_PENDING) != 0;
   const uint32_t parity = m.step & 1;
   return guarded([&] {
     if (flags & SB_TARGET_GRAPH) {
@@ -348,7 +349,7 @@ static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float tempera
       const uint32_t bound = std::min(m.config().max_context, (m.committedHost / 1024 + 2) * 1024);
       uint32_t tbits;
       memcpy(&tbits, &temperature, 4);
-      const auto key = std::make_tuple(rows, tbits, parity, uint32_t(advance) | (uint32_t(tree) << 1), bound);
+      const auto key = std::make_tuple(rows, tbits, parity, uint32_t(advance) | (uint32_t(tree) << 1) | (uint32_t(keep) << 2), bound);
       auto it = t->graphs.find(key);
       if (it == t->graphs.end()) {
         const uint32_t saved = m.committedHost;
@@ -357,7 +358,7 @@ static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float tempera
         SB_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
         int status = SB_OK;
         try {
-          m.encodeVerify(g, rows, temperature, parity, advance, tree);
+          m.encodeVerify(g, rows, temperature, parity, advance, tree, keep);
         } catch (...) {
           cudaGraph_t dead = nullptr;
           cudaStreamEndCapture(stream, &dead);
@@ -379,7 +380,7 @@ static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float tempera
       SB_CUDA(cudaGraphLaunch(it->second, stream));
     } else {
       CommandGraph g{stream, ctx().pdl, 0};
-      m.encodeVerify(g, rows, temperature, parity, advance, tree);
+      m.encodeVerify(g, rows, temperature, parity, advance, tree, keep);
       t->launches = g.launches;
     }
     ++m.step;

@@ -207,7 +207,7 @@ class SbGdnArgs(ctypes.Structure):
                 ("rows", _U), ("pending_rows", _U), ("key_heads", _U), ("value_heads", _U), ("qkvz_stride", _U),
                 ("ab_stride", _U), ("hidden_stride", _U), ("tiled", _U),
                 ("gate_weight", _P), ("gate_input", _P), ("gate_k", _U), ("gate_input_stride", _U),
-                ("tree", _P), ("pending_path_dev", _P), ("pending_path", _U), ("reserved", _U)]
+                ("tree", _P), ("pending_path_dev", _P), ("pending_path", _U), ("flags", _U)]
 
 
 class SbSampleArgs(ctypes.Structure):

@@ -316,13 +316,93 @@ def test_gdn_fused_gate_projection_equals_separate_projection():
     assert np.abs(fused2["state"] - want2["state"]).max() <= 1e-4 * np.abs(want2["state"]).max()
 
 
-def test_gdn_fold_then_next_step_is_consistent():
-    """Folding r accepted rows in the next step equals scanning them now: the output of row r of one block
-    equals the output of row 0 of a block that starts after folding the first r rows (same inputs)."""
+def _gdn_inputs(rng, key_heads, value_heads):
+    D = 128
+    KW, VW = key_heads * D, value_heads * D
+    C = 2 * KW + VW
+    return dict(
+        C=C, KW=KW, VW=VW, stride=C + VW, key_heads=key_heads, value_heads=value_heads,
+        qkvz=bf16_randn(rng, (16, C + VW), 1.0), b=bf16_randn(rng, (16, value_heads), 1.0), a=bf16_randn(rng, (16, value_heads), 1.0),
+        conv_w=bf16_randn(rng, (C, 4), 0.4), a_scale=(-np.exp(rng.uniform(-3, 0.5, value_heads))).astype(np.float32),
+        dt_bias=bf16_randn(rng, (value_heads,), 0.5), norm_w=(1 + 0.1 * rng.standard_normal(D)).astype(np.float32),
+        cs=bf16_randn(rng, (3, C), 1.0), state=(rng.standard_normal((value_heads, D, D)) * 0.05).astype(np.float32),
+        pend=dict(inputs=bf16_randn(rng, (16, C), 1.0), k=bf16_randn(rng, (16, KW), 0.09), v=bf16_randn(rng, (16, VW), 0.5),
+                  beta=ol.f2bf(rng.uniform(0.1, 0.9, (16, value_heads)).astype(np.float32)),
+                  decay=rng.uniform(0.5, 1.0, (16, value_heads)).astype(np.float32)))
+
+
+def _gdn_oracle(o, x, cs, state, rows, pending_rows):
+    """One oracle call from the cell (cs, state): returns (cs_out, state_out, hidden, step tape)."""
+    VH, VW, C, KW = x["value_heads"], x["VW"], x["C"], x["KW"]
+    step = dict(inputs=np.zeros((16, C), np.uint16), k=np.zeros((16, KW), np.uint16), v=np.zeros((16, VW), np.uint16),
+                beta=np.zeros((16, VH), np.uint16), decay=np.zeros((16, VH), np.float32))
+    cs_out, state_out, hidden = np.zeros_like(cs), np.zeros_like(state), np.zeros((16, VW), np.uint16)
+    tape = lambda t: ol.SoGdnTape(P(t["inputs"]), P(t["k"]), P(t["v"]), P(t["beta"]), P(t["decay"]))
+    args = ol.SoGdnArgs(P(x["qkvz"]), P(x["b"]), P(x["a"]), P(x["conv_w"]), P(x["a_scale"]), P(x["dt_bias"]), P(x["norm_w"]), P(cs), P(cs_out),
+                        P(state), P(state_out), tape(x["pend"]), tape(step), P(hidden), rows, pending_rows, x["key_heads"], VH, x["stride"], VH,
+                        VW, 0, None, 0)
+    o.so_gdn_verify(ctypes.byref(args))
+    return cs_out, state_out, hidden, step
+
+
+def test_gdn_fold_call_then_step_on_the_swapped_cells():
+    """ops::GDN::addFold (the step with no rows of its own) followed at once by a step whose current cell is the fold's
+    next cell, both launched with programmatic dependent launch and nothing between them: the step must read the cell
+    the fold has just written (it does not carry SB_GDN_STATE_SETTLED). Checked against the oracle making the same two
+    calls, and against one call that folds and steps at once: folding r accepted rows first and then stepping gives the
+    bits of doing both in one launch (the reference tests the same: fold(first r rows) == the state the next step
+    commits, dev/tests/engine/gdn_decode_metal_test.mm:12-20)."""
     lib, l, o = _setup()
-    got_a, want_a, _ = gdn_case(lib, l, o, key_heads=2, value_heads=4, rows=16, pending_rows=3, tiled=False, seed=11)
-    got_b, want_b, _ = gdn_case(lib, l, o, key_heads=2, value_heads=4, rows=16, pending_rows=3, tiled=False, seed=11)
-    assert np.array_equal(got_a["hidden"], got_b["hidden"]) and np.array_equal(got_a["state"], got_b["state"])
+    rng = np.random.default_rng(11)
+    x = _gdn_inputs(rng, 2, 4)
+    VH, VW, C, KW, pending = 4, x["VW"], x["C"], x["KW"], 5
+    # oracle: fold, then step from the folded cell
+    cs1, st1, _, _ = _gdn_oracle(o, x, x["cs"], x["state"], 0, pending)
+    cs2, st2, hid2, tape2 = _gdn_oracle(o, x, cs1, st1, 16, 0)
+    # device: the same two calls back to back on one stream, then the fused call
+    up = lib.DeviceBuffer.from_numpy
+    d = {n: up(x[n]) for n in ("qkvz", "b", "a", "conv_w", "a_scale", "dt_bias", "norm_w", "cs", "state")}
+    dp = {n: up(v) for n, v in x["pend"].items()}
+    sizes = dict(inputs=16 * C * 2, k=16 * KW * 2, v=16 * VW * 2, beta=16 * VH * 2, decay=16 * VH * 4)
+    dtape = lambda t: lib.SbGdnTape(t["inputs"].ptr, t["k"].ptr, t["v"].ptr, t["beta"].ptr, t["decay"].ptr)
+
+    def cell():
+        return lib.DeviceBuffer(x["cs"].nbytes), lib.DeviceBuffer(x["state"].nbytes)
+
+    def call(cs_in, st_in, cs_out, st_out, step, hidden, rows, pend_rows):
+        ga = lib.SbGdnArgs(d["qkvz"].ptr, d["b"].ptr, d["a"].ptr, d["conv_w"].ptr, d["a_scale"].ptr, d["dt_bias"].ptr, d["norm_w"].ptr,
+                           cs_in.ptr, cs_out.ptr, st_in.ptr, st_out.ptr, dtape(dp), dtape(step), hidden.ptr, None,
+                           rows, pend_rows, 2, VH, x["stride"], VH, VW, 0)
+        lib.check(l.sb_gdn_verify(None, ctypes.byref(ga)))
+
+    results = {}
+    for name in ("two calls", "one call"):
+        (csa, sta), (csb, stb) = cell(), cell()
+        step = {n: lib.DeviceBuffer(b) for n, b in sizes.items()}
+        hidden = lib.DeviceBuffer(16 * VW * 2)
+        for b in (csa, sta, csb, stb, hidden, *step.values()):
+            b.fill(0)
+        if name == "two calls":
+            call(d["cs"], d["state"], csa, sta, step, hidden, 0, pending)   # addFold: the folded cell
+            call(csa, sta, csb, stb, step, hidden, 16, 0)                  # addDecode on the swapped cells
+        else:
+            call(d["cs"], d["state"], csb, stb, step, hidden, 16, pending)
+        lib.stream_sync()
+        assert lib.device_status() == 0
+        results[name] = dict(cs=csb.to_numpy(np.uint16, x["cs"].shape), state=stb.to_numpy(np.float32, x["state"].shape),
+                             hidden=hidden.to_numpy(np.uint16, (16, VW)), k=step["k"].to_numpy(np.uint16, (16, KW)),
+                             folded=sta.to_numpy(np.float32, x["state"].shape) if name == "two calls" else None)
+    two, one = results["two calls"], results["one call"]
+    # the fold alone, against the oracle's
+    assert np.abs(two["folded"] - st1).max() <= 1e-4 * np.abs(st1).max()
+    assert np.array_equal(two["cs"], cs2)
+    assert np.abs(two["state"] - st2).max() <= 1e-4 * np.abs(st2).max()
+    g, w = ol.bf2f(two["hidden"]).astype(np.float64), ol.bf2f(hid2).astype(np.float64)
+    assert (np.abs(g - w) > 3 * ulp_bf16(w) + 2e-3 * np.abs(w).mean()).mean() <= 0.01
+    assert np.abs(g).max() > 0
+    # and fold-then-step is the one-launch step, bit for bit
+    for n in ("cs", "state", "hidden", "k"):
+        assert np.array_equal(two[n], one[n]), n
 
 
 def test_greedy_selection_and_acceptance():
@@ -514,25 +594,29 @@ def test_moe_route_matches_oracle(mode, shared):
     assert l.sb_moe_route(None, ctypes.byref(bad)) == -1
 
 
-def test_moe_experts_match_oracle():
-    """sb_moe_route + sb_moe_experts on a small MoE block (24 experts + the shared one, 8 + 1 routes a row, hidden 1024,
-    intermediate 512) against the oracle's fp64 statement: the per-route sums within 2e-3 of their scale, the combined
-    rows within bf16 rounding of the oracle's."""
+@pytest.mark.parametrize("shape", [
+    dict(rows=13, experts=24, slots=32, top_k=8, H=1024, I=512),       # a small block, a ragged row count
+    dict(rows=16, experts=256, slots=256, top_k=8, H=2048, I=512),     # the 35B-A3B block: 256 experts + the shared one
+])
+def test_moe_experts_match_oracle(shape):
+    """sb_moe_route + sb_moe_experts on a MoE block (the experts + the shared one, 8 + 1 routes a row) against the oracle's
+    fp64 statement: the per-route sums within 2e-3 of their scale, the combined rows within bf16 rounding of the
+    oracle's."""
     lib, l, o = _setup()
     rng = np.random.default_rng(17)
-    rows, experts, top_k, H, I = 13, 24, 8, 1024, 512
+    rows, experts, slots, top_k, H, I = (shape[n] for n in ("rows", "experts", "slots", "top_k", "H", "I"))
     total, routes = experts + 1, top_k + 1
     gate = np.concatenate([qf.realistic(0, I, H, seed=100 + e) for e in range(total)])
     up = np.concatenate([qf.realistic(0, I, H, seed=200 + e) for e in range(total)])
     down = np.concatenate([qf.realistic(0, H, I, seed=300 + e) for e in range(total)])
     x = ol.f2bf(rng.standard_normal((rows, H)).astype(np.float32))
     res = ol.f2bf(rng.standard_normal((rows, H)).astype(np.float32))
-    scores = rng.standard_normal((rows, 32)).astype(np.float32)
+    scores = rng.standard_normal((rows, slots)).astype(np.float32)
     sgate = (rng.standard_normal(H) * 0.05).astype(np.float32)
     up_dev = lib.DeviceBuffer.from_numpy
     sd, xd, rd, gd = up_dev(scores), up_dev(x), up_dev(res), up_dev(sgate)
     sel, wts = lib.DeviceBuffer(rows * routes * 4), lib.DeviceBuffer(rows * routes * 4)
-    ra = lib.SbMoeRouteArgs(sd.ptr, xd.ptr, gd.ptr, sel.ptr, wts.ptr, rows, experts, 32, top_k, H, 0)
+    ra = lib.SbMoeRouteArgs(sd.ptr, xd.ptr, gd.ptr, sel.ptr, wts.ptr, rows, experts, slots, top_k, H, 0)
     lib.check(l.sb_moe_route(None, ctypes.byref(ra)))
     wg, wu, wd = up_dev(gate), up_dev(up), up_dev(down)
     scratch = lib.DeviceBuffer(int(l.sb_moe_scratch_bytes(rows, routes, H, I)))
