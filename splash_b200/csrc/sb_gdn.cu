@@ -496,11 +496,12 @@ extern "C" int sb_gdn_verify(void *stream, const SbGdnArgs *a) {
 }
 
 extern "C" int sb_gdn_verify_static(void *stream, const SbGdnArgs *a) {
-  const int valid = gdn_validate(a, "sb_gdn_verify_static");
-  if (valid != SB_OK) return valid;
+  SB_REQUIRE(a, "sb_gdn_verify_static: null arguments");
   SB_REQUIRE(a->value_heads <= kStaticMaxValueHeads,
              "sb_gdn_verify_static: %u value heads exceed the %u the built-in scratch holds; use sb_gdn_verify", a->value_heads,
              kStaticMaxValueHeads);
+  const int valid = gdn_validate(a, "sb_gdn_verify_static");
+  if (valid != SB_OK) return valid;
   uint8_t *scratch = nullptr;
   const int st = static_scratch_address(&scratch);
   if (st != SB_OK) return st;
