@@ -847,10 +847,13 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
       }
       x_issued = true;
     };
+    // (Asking the L2 for later stages ahead of the ring, with TMA prefetches of the same boxes, was measured and
+    // dropped: the gate/up launch went from 36 to 44 us at every distance tried. The 3-stage ring alone streams 6.6
+    // TB/s when its stages are released at once; what it lacks is early release, not bytes in flight.)
+    uint32_t slot = 0, round = 0;
     for (uint32_t item = blockIdx.x; item < items && ok && !SB_DBG(16); item += gridDim.x) {
       const uint32_t tile = item / p.slices;
       for (uint32_t c = 0; c < chunks && ok; ++c, ++fill) {
-        const uint32_t slot = fill % p.stages, round = fill / p.stages;
         if (round > 0) {
           if (!x_issued) issue_x();
           ok = SB_DBG(4) ? mbar_wait(&empty[slot], (round - 1) & 1) : mbar_wait_backoff(&empty[slot], (round - 1) & 1);
@@ -869,6 +872,7 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
           uint8_t *dst = smem + p.ring_off + slot * p.stage_bytes + lane * p.box_bytes;
           tma_load_2d(dst, &maps.m[tn][j], int(byte0 >> 4) * 4, int(row0 >> p.period_log2), &full[slot], policy, SB_DBG(2) == 0);
         }
+        if (++slot == p.stages) slot = 0, ++round;
       }
     }
     if (!x_issued) issue_x();
@@ -1043,7 +1047,30 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
   }
   // Super-blocks are dealt to the k-group warps round-robin over the CTA's whole stream (jmod = count so far
   // mod kKG), so a stage of 4 keeps 4 of the 6 warps of a row group busy and the next stage the other ones.
-  uint32_t drained = 0, done = 0, jmod = 0;
+  uint32_t done = 0, jmod = 0;
+  // The ring position is carried along (slot, phase) and each lane's row offsets inside a stage are formed once:
+  // per stage a warp then spends a handful of instructions besides its multiply.
+  uint32_t slot = 0, phase = 0;
+  uint32_t row_at[kMT][2];  // where the lane's rows lie inside a piece: (tensor, row) -> bytes
+  uint32_t row_lead[kMT][2];
+#pragma unroll
+  for (int mt = 0; mt < kMT; ++mt)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const uint32_t tr = rg * 32 + mt * 16 + r * 8 + g;          // tile row
+      const uint32_t tn = gate_up ? tr >> 5 : 0, rl = gate_up ? tr & 31 : tr;
+      if (FMT == SB_FMT_Q4K) {
+        row_at[mt][r] = tn * p.box_bytes + rl * 144;
+        row_lead[mt][r] = 0;
+      } else {
+        // A row sits in the box of its (piece, tensor, residue) at `lead` bytes past a 16-byte boundary.
+        const uint32_t j = rl & (p.period - 1), i = rl >> p.period_log2;  // map and row within its box
+        row_at[mt][r] = ((tn << p.period_log2) + j) * p.box_bytes + i * p.pitch;
+        row_lead[mt][r] = p.lead[tn][j];
+      }
+    }
+  const uint32_t piece_bytes = (p.tensors << p.period_log2) * p.box_bytes;
+  const uint8_t *ring = smem + p.ring_off;
   for (uint32_t item = blockIdx.x; item < items; item += gridDim.x, ++done) {
     float y[kMT][2][4];
 #pragma unroll
@@ -1052,22 +1079,20 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
       for (int h = 0; h < 2; ++h)
 #pragma unroll
         for (int c = 0; c < 4; ++c) y[mt][h][c] = 0.0f;
-    for (uint32_t c = 0; c < chunks; ++c, ++drained) {
-      const uint32_t slot = drained % p.stages, round = drained / p.stages;
+    uint32_t csb0 = sb0;
+    for (uint32_t c = 0; c < chunks; ++c, csb0 += kStageSb) {
       // Every warp follows every stage's barrier, with or without work in it: the parity wait tells only
       // consecutive phases apart.
-      if (!SB_DBG(16) && !mbar_wait(&full[slot], round & 1)) {
+      if (!SB_DBG(16) && !mbar_wait(&full[slot], phase)) {
         if (lane == 0) atomicExch(p.status, SB_DEV_WAIT_EXPIRED);
         return;  // the launch has failed; the status word says so
       }
-      const uint32_t csb0 = sb0 + c * kStageSb, nsb_c = min(uint32_t(kStageSb), sb1 - csb0);
+      const uint32_t nsb_c = min(uint32_t(kStageSb), sb1 - csb0);
       const uint32_t sbi = kg >= jmod ? kg - jmod : kg + kKG - jmod;  // the stage's super-block dealt to this k-group
       jmod += nsb_c;
       if (jmod >= kKG) jmod -= kKG;
       if (sbi < nsb_c && !SB_DBG(1)) {
-        const uint8_t *stage = smem + p.ring_off + slot * p.stage_bytes;
-        // A row sits in the box of its (piece, tensor, residue) at `lead` bytes past a 16-byte boundary
-        // (always 0 for Q4_K, whose rows are 16-byte multiples).
+        const uint8_t *stage = ring + slot * p.stage_bytes;
         constexpr uint32_t kPieceSb = WFmt<FMT>::kPieceSb;
         const uint32_t lsb = csb0 + sbi - sb0;
         const uint32_t piece = sbi / kPieceSb, within = sbi % kPieceSb;
@@ -1076,14 +1101,11 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
         for (int mt = 0; mt < kMT; ++mt)
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
-            const uint32_t tr = rg * 32 + mt * 16 + r * 8 + g;          // tile row
-            const uint32_t tn = gate_up ? tr >> 5 : 0, rl = gate_up ? tr & 31 : tr;
             if (FMT == SB_FMT_Q4K) {
-              roff[mt][r] = (piece * p.tensors + tn) * p.box_bytes + rl * 144;
+              roff[mt][r] = piece * piece_bytes + row_at[mt][r];
             } else {
-              const uint32_t j = rl & (p.period - 1), i = rl >> p.period_log2;  // map and row within its box
-              const uint32_t lead = (p.lead[tn][j] + (csb0 + piece * kPieceSb) * kSb) & 15u;
-              roff[mt][r] = (((piece * p.tensors + tn) << p.period_log2) + j) * p.box_bytes + i * p.pitch + lead + within * kSb;
+              const uint32_t lead = (row_lead[mt][r] + (csb0 + piece * kPieceSb) * kSb) & 15u;
+              roff[mt][r] = piece * piece_bytes + row_at[mt][r] + lead + within * kSb;
             }
           }
         const uint8_t *xs_sb = smem + p.x_off + lsb * kPrepSbBytes;
@@ -1091,6 +1113,7 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
       }
       __syncwarp();
       if (lane == 0 && !SB_DBG(16)) mbar_arrive(&empty[slot]);
+      if (++slot == p.stages) slot = 0, phase ^= 1;
     }
     if (SB_DBG(8)) continue;
     // Hand the tile's sums to the epilogue warp once it has read the previous tile's.

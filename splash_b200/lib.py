@@ -6,7 +6,8 @@ import os
 import numpy as np
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-_PATH = os.path.join(_HERE, "libsplash_b200.so")
+# The library built in-tree; SPLASH_B200_LIBRARY names another build of it (a diagnostic build, say).
+_PATH = os.environ.get("SPLASH_B200_LIBRARY") or os.path.join(_HERE, "libsplash_b200.so")
 
 FMT_Q4K, FMT_Q6K, FMT_Q80, FMT_NVFP4, FMT_BF16, FMT_F16, FMT_F32 = 0, 4, 6, 37, 41, 42, 64
 EP_NONE, EP_RESIDUAL, EP_UP_WITH_GATE, EP_GATE_UP, EP_PARTIALS, EP_GATE_UP_PARTIALS = 0, 1, 2, 3, 4, 5
