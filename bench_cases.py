@@ -89,11 +89,21 @@ def case_linear(a):
     rows = np.tile(base, ((n + base.shape[0] - 1) // base.shape[0], 1))[:n]
     copies = max(2, int(a.resident_mb * 1e6 // (n * rb * tensors)) + 1)
     bufs = [lib.DeviceBuffer.from_numpy(rows) for _ in range(copies * tensors)]
-    x = lib.DeviceBuffer.from_numpy(bf16_bits(rng.standard_normal((16, k))))
-    prep = lib.DeviceBuffer(int(lib.load().sb_linear_prepared_bytes(k)))
-    lib.check(lib.load().sb_linear_prepare(None, x.ptr, a.rows, k, k, None, fmt, prep.ptr, None, (lib.LINEAR_TCGEN05 if a.tcgen05 else 0)))
-    out = lib.DeviceBuffer(16 * n * 4 + 512)
-    aux = lib.DeviceBuffer.from_numpy(np.zeros((16, n), np.uint16))
+    slots = max(16, a.rows)
+    x = lib.DeviceBuffer.from_numpy(bf16_bits(rng.standard_normal((slots, k))))
+    l = lib.load()
+    if a.rows > 16:  # the many-row kernel (tensor memory): its own conversion, once
+        l.sb_linear_wide_prepared_bytes.restype = ctypes.c_uint64
+        l.sb_linear_wide_prepared_bytes.argtypes = [ctypes.c_uint32, ctypes.c_uint32]
+        l.sb_linear_wide_prepare.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p,
+                                             ctypes.c_void_p, ctypes.c_uint32]
+        prep = lib.DeviceBuffer(int(l.sb_linear_wide_prepared_bytes(a.rows, k)))
+        lib.check(l.sb_linear_wide_prepare(None, x.ptr, a.rows, k, k, None, prep.ptr, 0))
+    else:
+        prep = lib.DeviceBuffer(int(l.sb_linear_prepared_bytes(k)))
+        lib.check(l.sb_linear_prepare(None, x.ptr, a.rows, k, k, None, fmt, prep.ptr, None, (lib.LINEAR_TCGEN05 if a.tcgen05 else 0)))
+    out = lib.DeviceBuffer(slots * n * 4 + 512)
+    aux = lib.DeviceBuffer.from_numpy(np.zeros((slots, n), np.uint16))
 
     def launch(i, stream=None):
         kw = {}
@@ -108,8 +118,9 @@ def case_linear(a):
 
     us = timed(launch, a.iters, graph=a.graph)
     algo = n * rb * tensors + a.rows * k * 2 + a.rows * n * 2
+    flops = 2.0 * a.rows * n * tensors * k
     print(f"linear {a.fmt} n={n} k={k} rows={a.rows} epilogue={a.epilogue}: {us:.1f} us per launch, {algo / us / 1e3:.0f} GB/s "
-          f"of {algo} algorithmic bytes, device status {lib.device_status()}")
+          f"of {algo} algorithmic bytes, {flops / us / 1e6:.1f} TFLOP/s, device status {lib.device_status()}")
 
 
 def case_attention(a):

@@ -195,6 +195,18 @@ SB_API int sb_linear_prepare_gate_up(void *stream, const float *partials, uint32
  * counters left at zero by the kernel that used them (runtime/ops/Linear.hpp:169-182). */
 SB_API int sb_linear(void *stream, const SbLinearArgs *args);
 
+/* ---- many rows (17 and up): the same product on the tcgen05 tensor cores with the weights dequantized to half ----
+ * Replaces the reference's many-row projection tile (gguf_prefill_<fmt>_{a,r,g}, runtime/metal/kernels/shared/gguf_linear.metal,
+ * geometry runtime/metal/abi/Gguf.h:31-35; the 64-row decode tiles of runtime/ops/Linear.hpp:94-97) and follows its
+ * arithmetic: weights rounded to half once dequantized (runtime/metal/kernels/common/gguf_staged.h:11-57), fp32 sums, one
+ * rounding after the epilogue. Q4_K; epilogues none / residual / up-with-gate / one-pass gate-up. Rows beyond 128 run as
+ * passes of 128 over the weights. sb_linear forwards calls with more than 16 rows here. `prepared`, if given, is the
+ * output of sb_linear_wide_prepare for the same rows and k (another layout than sb_linear_prepare's). */
+SB_API uint64_t sb_linear_wide_prepared_bytes(uint32_t rows, uint32_t k);
+SB_API int sb_linear_wide_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride, const void *norm_weight,
+                                  void *prepared_out, uint32_t flags);
+SB_API int sb_linear_wide(void *stream, const SbLinearArgs *args);
+
 /* The plan sb_linear will use for a shape: k-slices, CTAs, tile rows, ring stages, shared bytes.
  * (runtime/ops/Linear.hpp:287-301 `plan` is a value object shared by sizing and encoding.) */
 typedef struct SbLinearPlan {

@@ -97,6 +97,8 @@ int sb_init(int device) {
   SB_CUDA(cudaMalloc(&c.linear_partials, c.linear_partials_bytes));
   c.prepared_bytes = 64 + size_t(72) * 8704;  // k up to 18432
   SB_CUDA(cudaMalloc(&c.prepared, c.prepared_bytes));
+  c.wide_prepared_bytes = 4 * (1024 + size_t(128) * 18432 * 2);
+  SB_CUDA(cudaMalloc(&c.wide_prepared, c.wide_prepared_bytes));
   c.linear_counter_count = 1u << 16;
   SB_CUDA(cudaMalloc(&c.linear_counters, c.linear_counter_count * sizeof(uint32_t)));
   SB_CUDA(cudaMemset(c.linear_counters, 0, c.linear_counter_count * sizeof(uint32_t)));

@@ -19,6 +19,8 @@ struct Context {
   uint8_t *prepared = nullptr;           // sb_linear's own prepared-input scratch
   size_t prepared_bytes = 0;
   uint32_t linear_counter_count = 0;
+  uint8_t *wide_prepared = nullptr;      // sb_linear_wide's own converted-input scratch (up to 512 rows of k up to 18432)
+  size_t wide_prepared_bytes = 0;
   float *attn_workspace = nullptr;       // split partials and (max, sum) of sb_attn_verify
   size_t attn_workspace_bytes = 0;
   uint32_t *attn_counters = nullptr;     // one arrival counter per KV head, zero between launches

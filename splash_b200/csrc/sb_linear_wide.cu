@@ -1,0 +1,521 @@
+// Quantized linear for many rows (17 .. 128 per pass; more rows run as passes of 128): Y[M,N] = X[M,K] W[N,K]^T with the
+// weights dequantized in registers to fp16 and multiplied on the tcgen05 tensor cores, A operand and accumulators in
+// tensor memory.
+//
+// Takes the place of the reference's many-row projection tile (the 128-row prefill entry points gguf_prefill_<fmt>_{a,r,g}
+// of runtime/metal/kernels/shared/gguf_linear.metal with the geometry of runtime/metal/abi/Gguf.h:31-35, and the 64-row
+// decode tiles of runtime/ops/Linear.hpp:94-97). Its arithmetic is that tile's: the weight is rounded to half once it is
+// dequantized (the staged tile, runtime/metal/kernels/common/gguf_staged.h:11-57), products and sums run in fp32, one
+// rounding to the destination after the epilogue (runtime/metal/kernels/common/gguf_tile.h:8-14). Here the half weight of
+// Q4_K is fl16(q * fl16(d sc) + fl16(-dmin mn)): the two floating factors are rounded to half before the one fused
+// multiply-add, which keeps the expansion at three instructions per two weights; the projection stays inside the
+// reference's bound for half-rounded weights with room to spare (tests/test_linear_wide_gpu.py states the bound used).
+//
+//   item      256 weight rows (two 128-row halves, or 128 gate rows and the 128 up rows of the same columns) x all of K
+//             x one pass of up to 128 rows of X; persistent CTAs walk the items
+//   weights   tiled TMA: one box of 128 rows x 144 bytes per (half, super-block) into a ring; never re-read
+//   X         converted once by wide_prepare_kernel to fp16 with a per-row power-of-two scale, laid out as the K-major
+//             core matrices the MMA reads (8 rows x 16 bytes), and streamed per 64 inputs from the L2 into a second ring
+//   dequant   8 warps: warp (quadrant q, half h) expands sub-blocks 4h .. 4h+3 of rows 32q .. 32q+31 (a thread owns a row)
+//             and writes the 128 halves with tcgen05.st into one of four A buffers of tensor memory (64 columns each)
+//   mma       one thread: per A buffer 8 tcgen05.mma (M 128, N = rows rounded up to 16, K 16), A from tensor memory, B from
+//             the X ring; tcgen05.commit frees the A buffer, the X stage and, after the item's last step, hands the two
+//             accumulators (128 lanes x N fp32 columns each) to the epilogue
+//   epilogue  4 warps, a thread per weight row: tcgen05.ld 32 columns at a time, scale back, epilogue, store
+// Every wait is bounded and reports through the status word; tensor memory is always returned.
+#include <algorithm>
+
+#include <cuda.h>
+
+#include "sb_internal.h"
+#include "sb_linear_internal.h"
+#include "sb_ptx.cuh"
+#include "sb_tcgen05.cuh"
+
+namespace sb {
+
+constexpr uint32_t kWideMaxRows = 128;             // rows of X one pass multiplies (the accumulators' columns)
+constexpr uint32_t kWideHeader = 1024;             // scale_back[256] floats (a pass reads its 128)
+constexpr uint32_t kWideDequantWarps = 8, kWideEpilogueWarps = 4;
+constexpr uint32_t kWideProducerWarp = kWideDequantWarps + kWideEpilogueWarps, kWideMmaWarp = kWideProducerWarp + 1;
+constexpr uint32_t kWideThreads = 32 * (kWideMmaWarp + 1);  // 448
+constexpr uint32_t kWideRawStage = 128 * 144, kWideRawStages = 4;   // one (half, super-block) of an item: 18 KB
+constexpr uint32_t kWideXBytes = 128 * 1024, kWideMaxXStages = 8;   // the X ring; a stage holds 64 inputs of every row
+constexpr uint32_t kWideABufs = 4, kWideACols = 64, kWideACol0 = 256, kWideDCols = 128, kWideTmemCols = 512;
+constexpr uint32_t kWideBarBytes = 1024;           // barriers, tensor-memory slot, then scale_back[128] at 512
+constexpr uint32_t kWideXOff = kWideBarBytes, kWideRawOff = kWideXOff + kWideXBytes;
+constexpr uint32_t kWideSmem = kWideRawOff + kWideRawStages * kWideRawStage;  // 205,824 bytes
+
+struct WideParams {
+  const uint8_t *prepared;  // header + units of 64 inputs: [k-step 4][row / 8][input / 8 (2)][row % 8][8 halves]
+  const uint16_t *aux;
+  void *out;
+  uint32_t *status;
+  uint32_t n, rows, rows_padded, aux_stride, out_stride, epilogue, out_f32;
+  uint32_t nsb, items, x_stages, x_stage_bytes, gate_up;
+};
+struct WideMaps {
+  CUtensorMap m[2];  // the item's first half (or gate rows), its second half (or up rows)
+};
+
+__device__ __forceinline__ void wide_expired(uint32_t *status, uint32_t site) {
+  atomicCAS(status, 0u, uint32_t(SB_DEV_WAIT_EXPIRED) | (site << 8));
+}
+__device__ __forceinline__ bool wide_warp_wait(uint64_t *bar, uint32_t parity, bool backoff = false) {
+  uint32_t ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = backoff ? mbar_wait_backoff(bar, parity) : mbar_wait(bar, parity);
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// ---- the conversion of X ----
+// One CTA per row slot (rows past `rows` are written as zeros): optional RMSNorm, the row's largest magnitude, a
+// power-of-two scale that keeps the values below 2^10, fp16, stored in the MMA's core-matrix order. Within every four
+// consecutive inputs the order is [0, 2, 1, 3]: the order in which the weight expansion produces its halves.
+constexpr int kWidePrepThreads = 256;
+struct WidePrepParams {
+  const uint16_t *x;
+  const float *norm_w;
+  uint8_t *out;
+  uint32_t rows, rows_padded, k, x_stride;
+};
+__global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const WidePrepParams p) {
+  __shared__ float red_s[2 * (kWidePrepThreads / 32)];
+  const uint32_t tok = blockIdx.x, tid = threadIdx.x;
+  pdl_launch_dependents();
+  pdl_wait();
+  const bool live = tok < p.rows;
+  const uint32_t chunks = p.k / 8;  // 8 inputs each
+  float ss = 0.0f, mx = 0.0f;
+  for (uint32_t c = tid; c < chunks && live; c += kWidePrepThreads) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(p.x + size_t(tok) * p.x_stride + 8 * c);
+    const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float a = bf16_bits_to_float(u[j] & 0xffffu), b = bf16_bits_to_float(u[j] >> 16);
+      ss = fmaf(a, a, ss), ss = fmaf(b, b, ss);
+      const float wa = p.norm_w ? p.norm_w[8 * c + 2 * j] : 1.0f, wb = p.norm_w ? p.norm_w[8 * c + 2 * j + 1] : 1.0f;
+      mx = fmaxf(mx, fmaxf(fabsf(a * wa), fabsf(b * wb)));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  }
+  if ((tid & 31) == 0) red_s[2 * (tid >> 5)] = ss, red_s[2 * (tid >> 5) + 1] = mx;
+  __syncthreads();
+  ss = red_s[0], mx = red_s[1];
+  for (int w = 1; w < kWidePrepThreads / 32; ++w) ss += red_s[2 * w], mx = fmaxf(mx, red_s[2 * w + 1]);
+  float inv = 1.0f;
+  if (p.norm_w) {
+    inv = rsqrtf(ss / float(p.k) + 1e-6f);
+    mx = mx * inv * 1.0625f;  // (x inv) w against x w inv and the rounding to bf16: well inside 6 %
+  }
+  int e = 0;
+  if (mx > 0.0f && mx <= 3.0e38f) {
+    (void)frexpf(mx, &e);
+    e -= 10;
+  }
+  const float down = ldexpf(1.0f, -e);
+  if (tid == 0) reinterpret_cast<float *>(p.out)[tok] = live ? ldexpf(1.0f, e) : 0.0f;
+  const size_t unit_bytes = size_t(p.rows_padded) * 128;  // 64 inputs of every row slot
+  for (uint32_t c = tid; c < chunks; c += kWidePrepThreads) {
+    uint32_t h[4] = {0, 0, 0, 0};
+    if (live) {
+      const uint4 raw = *reinterpret_cast<const uint4 *>(p.x + size_t(tok) * p.x_stride + 8 * c);
+      const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v[2 * j] = bf16_bits_to_float(u[j] & 0xffffu), v[2 * j + 1] = bf16_bits_to_float(u[j] >> 16);
+      if (p.norm_w) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = round_bf16((v[j] * inv) * p.norm_w[8 * c + j]);
+      }
+      __half hv[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) hv[j] = __float2half_rn(v[j] * down);
+      const __half2 p0 = __halves2half2(hv[0], hv[2]), p1 = __halves2half2(hv[1], hv[3]);
+      const __half2 p2 = __halves2half2(hv[4], hv[6]), p3 = __halves2half2(hv[5], hv[7]);
+      h[0] = *reinterpret_cast<const uint32_t *>(&p0), h[1] = *reinterpret_cast<const uint32_t *>(&p1);
+      h[2] = *reinterpret_cast<const uint32_t *>(&p2), h[3] = *reinterpret_cast<const uint32_t *>(&p3);
+    }
+    const uint32_t k0 = 8 * c, unit = k0 / 64, step = (k0 % 64) / 16, half = (k0 % 16) / 8;
+    uint8_t *dst = p.out + kWideHeader + unit * unit_bytes + size_t(step) * p.rows_padded * 32 + (tok >> 3) * 256 + half * 128 + (tok & 7) * 16;
+    *reinterpret_cast<uint4 *>(dst) = make_uint4(h[0], h[1], h[2], h[3]);
+  }
+}
+
+// The four sub-blocks 4h .. 4h+3 of a Q4_K row's super-block as 128 halves in 64 packed columns:
+// fl16(q * fl16(d sc) + fl16(-dmin mn)); a high nibble enters as 16 q against fl16(d sc / 16).
+__device__ __forceinline__ void wide_expand_q4k(const uint8_t *row, uint32_t h, uint32_t (&r)[64]) {
+  const uint4 hdr = *reinterpret_cast<const uint4 *>(row);
+  const __half2 dd = *reinterpret_cast<const __half2 *>(&hdr.x);
+  const float d = __low2float(dd), ndmin = -__high2float(dd);
+  // 6-bit scales and mins of sub-blocks 0..3 (h = 0) or 4..7 (h = 1) as bytes
+  const uint32_t sc4 = h ? ((hdr.w & 0x0f0f0f0fu) | ((hdr.y >> 2) & 0x30303030u)) : (hdr.y & 0x3f3f3f3fu);
+  const uint32_t mn4 = h ? (((hdr.w >> 4) & 0x0f0f0f0fu) | ((hdr.z >> 2) & 0x30303030u)) : (hdr.z & 0x3f3f3f3fu);
+  const uint32_t k1024 = 0x64006400u;
+#pragma unroll
+  for (uint32_t pr = 0; pr < 2; ++pr) {  // pair pr of this half: sub-blocks 2 pr (low nibbles) and 2 pr + 1 (high nibbles)
+    const float sc0 = float((sc4 >> (16 * pr)) & 0xffu), sc1 = float((sc4 >> (16 * pr + 8)) & 0xffu);
+    const float mn0 = float((mn4 >> (16 * pr)) & 0xffu), mn1 = float((mn4 >> (16 * pr + 8)) & 0xffu);
+    const __half2 a0 = __float2half2_rn(d * sc0), a1 = __float2half2_rn(d * sc1 * 0.0625f);
+    const __half2 b0 = __float2half2_rn(ndmin * mn0), b1 = __float2half2_rn(ndmin * mn1);
+    const uint32_t ua0 = *reinterpret_cast<const uint32_t *>(&a0), ua1 = *reinterpret_cast<const uint32_t *>(&a1);
+    const uint32_t ub0 = *reinterpret_cast<const uint32_t *>(&b0), ub1 = *reinterpret_cast<const uint32_t *>(&b1);
+    const uint8_t *qs = row + 16 + 32 * (2 * h + pr);
+    const uint4 qa = *reinterpret_cast<const uint4 *>(qs), qb = *reinterpret_cast<const uint4 *>(qs + 16);
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint32_t hi8 = w[c] >> 8;
+      // {1024 + q} - 1024 = q exactly, then one fused multiply-add per two weights
+      r[32 * pr + 2 * c] = hfma2_u32(hsub2_u32(and_or(w[c], 0x000f000fu, k1024), k1024), ua0, ub0);
+      r[32 * pr + 2 * c + 1] = hfma2_u32(hsub2_u32(and_or(hi8, 0x000f000fu, k1024), k1024), ua0, ub0);
+      r[32 * pr + 16 + 2 * c] = hfma2_u32(hsub2_u32(and_or(w[c], 0x00f000f0u, k1024), k1024), ua1, ub1);
+      r[32 * pr + 16 + 2 * c + 1] = hfma2_u32(hsub2_u32(and_or(hi8, 0x00f000f0u, k1024), k1024), ua1, ub1);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const WideParams p, const __grid_constant__ WideMaps maps) {
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint64_t *raw_full = reinterpret_cast<uint64_t *>(smem);        // [kWideRawStages]
+  uint64_t *raw_empty = raw_full + kWideRawStages;
+  uint64_t *x_full = raw_empty + kWideRawStages;                   // [kWideMaxXStages]
+  uint64_t *x_empty = x_full + kWideMaxXStages;
+  uint64_t *a_full = x_empty + kWideMaxXStages;                    // [kWideABufs]
+  uint64_t *a_empty = a_full + kWideABufs;
+  uint64_t *d_full = a_empty + kWideABufs;
+  uint64_t *d_empty = d_full + 1;
+  uint64_t *h_full = d_empty + 1;                                  // the header (scale_back) has landed
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 496);
+  float *scale_back = reinterpret_cast<float *>(smem + 512);       // [128]
+  uint8_t *x_ring = smem + kWideXOff, *raw_ring = smem + kWideRawOff;
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t units_per_item = 2 * p.nsb;  // (super-block, half of the item) pairs, each dequantized in two halves of 128 inputs
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < kWideRawStages; ++s) mbar_init(&raw_full[s], 1), mbar_init(&raw_empty[s], kWideDequantWarps);
+    for (uint32_t s = 0; s < kWideMaxXStages; ++s) mbar_init(&x_full[s], 1), mbar_init(&x_empty[s], 1);
+    for (uint32_t s = 0; s < kWideABufs; ++s) mbar_init(&a_full[s], 4), mbar_init(&a_empty[s], 1);
+    mbar_init(d_full, 1), mbar_init(d_empty, kWideEpilogueWarps), mbar_init(h_full, 1);
+    fence_mbar_init();
+  }
+  if (warp == kWideMmaWarp) tmem_alloc(tmem_slot, kWideTmemCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = *tmem_slot;
+  pdl_launch_dependents();
+
+  if (warp == kWideProducerWarp) {
+    // ---- producer: the weights' ring fills at once (they do not depend on the kernel ahead); X follows the wait ----
+    const uint64_t policy = policy_evict_first();
+    bool ok = true;
+    uint32_t rs = 0, rphase = 0, rcount = 0, xs = 0, xphase = 0, xcount = 0;
+    // X stages trail the weights: per super-block the two halves' boxes, then that super-block's four X stages.
+    bool waited = false;
+    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
+      for (uint32_t sb = 0; sb < p.nsb && ok; ++sb) {
+        for (uint32_t tn = 0; tn < 2 && ok; ++tn, ++rcount) {
+          if (rcount >= kWideRawStages && !wide_warp_wait(&raw_empty[rs], rphase ^ 1, true)) {
+            if (lane == 0) wide_expired(p.status, 1);
+            ok = false;
+            break;
+          }
+          if (lane == 0) {
+            mbar_arrive_expect_tx(&raw_full[rs], kWideRawStage);
+            tma_load_2d(raw_ring + rs * kWideRawStage, &maps.m[tn], int(sb * 36), int(p.gate_up ? item * 128 : item * 256 + tn * 128), &raw_full[rs], policy, true);
+          }
+          if (++rs == kWideRawStages) rs = 0, rphase ^= 1;
+        }
+        if (!waited) {
+          pdl_wait();  // X comes from the kernel ahead
+          if (lane == 0) {
+            mbar_arrive_expect_tx(h_full, 512);
+            bulk_g2s(scale_back, p.prepared, 512, h_full);
+          }
+          waited = true;
+        }
+        for (uint32_t q = 0; q < 4 && ok; ++q, ++xcount) {
+          if (xcount >= p.x_stages && !wide_warp_wait(&x_empty[xs], xphase ^ 1, true)) {
+            if (lane == 0) wide_expired(p.status, 2);
+            ok = false;
+            break;
+          }
+          if (lane == 0) {
+            mbar_arrive_expect_tx(&x_full[xs], p.x_stage_bytes);
+            bulk_g2s(x_ring + xs * p.x_stage_bytes, p.prepared + kWideHeader + size_t(4 * sb + q) * p.x_stage_bytes, p.x_stage_bytes, &x_full[xs]);
+          }
+          if (++xs == p.x_stages) xs = 0, xphase ^= 1;
+        }
+      }
+    }
+    // Do not leave while copies are in flight: every stage issued is waited for (bounded) before the warp returns.
+    for (uint32_t f = rcount > kWideRawStages ? rcount - kWideRawStages : 0; f < rcount; ++f)
+      if (!wide_warp_wait(&raw_empty[f % kWideRawStages], (f / kWideRawStages) & 1, true)) break;
+    for (uint32_t f = xcount > p.x_stages ? xcount - p.x_stages : 0; f < xcount; ++f)
+      if (!wide_warp_wait(&x_empty[f % p.x_stages], (f / p.x_stages) & 1, true)) break;
+  } else if (warp == kWideMmaWarp) {
+    // ---- MMA issuer ----
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_f16(128, p.rows_padded);
+      bool ok = true;
+      uint32_t ucount = 0, xs = 0, xphase = 0, dphase = 0;
+      uint32_t done_items = 0;
+      for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x, ++done_items) {
+        if (done_items > 0) {  // the accumulators of the item before must have been read
+          ok = mbar_wait(d_empty, dphase);
+          dphase ^= 1;
+          if (!ok) { wide_expired(p.status, 3); break; }
+        }
+        for (uint32_t sb = 0; sb < p.nsb && ok; ++sb) {
+          // Units of this super-block in the order the dequant warps fill the A buffers: (half of the item, inputs' half).
+          // X stage xs + 2 hh + j serves K-steps of inputs' half hh; both halves of the item read the same X stages.
+          for (uint32_t tn = 0; tn < 2 && ok; ++tn) {
+            for (uint32_t hh = 0; hh < 2 && ok; ++hh, ++ucount) {
+              const uint32_t ab = ucount % kWideABufs;
+              ok = mbar_wait(&a_full[ab], (ucount / kWideABufs) & 1);
+              if (!ok) { wide_expired(p.status, 4); break; }
+              tc_fence_after_sync();
+              const uint32_t a0 = tmem + kWideACol0 + ab * kWideACols, d0 = tmem + tn * kWideDCols;
+#pragma unroll 1
+              for (uint32_t j = 0; j < 2 && ok; ++j) {  // the two X stages (64 inputs each) of this half
+                uint32_t st = xs + 2 * hh + j, ph = xphase;
+                if (st >= p.x_stages) st -= p.x_stages, ph ^= 1;
+                if (tn == 0) {
+                  ok = mbar_wait(&x_full[st], ph);
+                  if (!ok) { wide_expired(p.status, 5); break; }
+                  tc_fence_after_sync();
+                }
+                const uint32_t xbase = smem_u32(x_ring + st * p.x_stage_bytes);
+#pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) {
+                  const uint64_t b = umma_smem_desc(xbase + i * p.rows_padded * 32, 128, 256);
+                  umma_f16_ts(d0, a0 + (4 * j + i) * 8, b, idesc, !(sb == 0 && hh == 0 && j == 0 && i == 0));
+                }
+                if (tn == 1) umma_commit(&x_empty[st]);  // both halves of the item have read the stage
+              }
+              umma_commit(&a_empty[ab]);
+            }
+          }
+          xs += 4;
+          if (xs >= p.x_stages) xs -= p.x_stages, xphase ^= 1;
+        }
+        if (ok) umma_commit(d_full);
+      }
+    }
+    __syncwarp();
+  } else if (warp < kWideDequantWarps) {
+    // ---- dequant: warp (q, h) expands inputs' half h of rows 32 q .. 32 q + 31 of every (super-block, item half) ----
+    const uint32_t q = warp & 3, h = warp >> 2, row = 32 * q + lane;
+    uint32_t rs = 0, rphase = 0, ucount = h;  // this warp's units are ucount = h, h + 2, ...: A buffers h, h + 2
+    bool ok = true;
+    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x)
+      for (uint32_t u = 0; u < units_per_item && ok; ++u, ucount += 2) {
+        if (!wide_warp_wait(&raw_full[rs], rphase)) {
+          if (lane == 0) wide_expired(p.status, 6);
+          ok = false;
+          break;
+        }
+        uint32_t r[64];
+        wide_expand_q4k(raw_ring + rs * kWideRawStage + row * 144, h, r);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&raw_empty[rs]);  // the row's bytes are in registers
+        if (++rs == kWideRawStages) rs = 0, rphase ^= 1;
+        const uint32_t ab = ucount % kWideABufs, use = ucount / kWideABufs;
+        if (use > 0 && !wide_warp_wait(&a_empty[ab], (use - 1) & 1)) {
+          if (lane == 0) wide_expired(p.status, 7);
+          ok = false;
+          break;
+        }
+        tc_fence_after_sync();
+        const uint32_t ta = tmem_addr(tmem, 32 * q, kWideACol0 + ab * kWideACols);
+        tmem_st16(ta, r), tmem_st16(ta + 16, r + 16), tmem_st16(ta + 32, r + 32), tmem_st16(ta + 48, r + 48);
+        tmem_wait_st();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&a_full[ab]);
+      }
+  } else {
+    // ---- epilogue: a thread per weight row of each half of the item ----
+    const uint32_t q = warp & 3, row = 32 * q + lane;
+    pdl_wait();  // aux / out belong to the stream's earlier kernels until they finish
+    bool ok = wide_warp_wait(h_full, 0);
+    if (!ok && lane == 0) wide_expired(p.status, 8);
+    uint32_t dphase = 0;
+    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
+      if (!wide_warp_wait(d_full, dphase)) {
+        if (lane == 0) wide_expired(p.status, 9);
+        ok = false;
+        break;
+      }
+      dphase ^= 1;
+      tc_fence_after_sync();
+      const uint32_t t0 = tmem_addr(tmem, 32 * q, 0);
+      if (p.gate_up) {
+        const uint32_t col = item * 128 + row;
+        for (uint32_t c = 0; c < p.rows_padded; c += 16) {
+          float g[16], u[16];
+          tmem_ld16_wait(t0 + c, g);
+          tmem_ld16_wait(t0 + kWideDCols + c, u);
+          if (col < p.n) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const uint32_t t = c + j;
+              if (t < p.rows) {
+                const float s = scale_back[t];
+                const float o = round_bf16(u[j] * s) * silu_f(round_bf16(g[j] * s));
+                static_cast<uint16_t *>(p.out)[size_t(t) * p.out_stride + col] = float_to_bf16_bits(o);
+              }
+            }
+          }
+        }
+      } else {
+        for (uint32_t half = 0; half < 2; ++half) {
+          const uint32_t col = item * 256 + half * 128 + row;
+          for (uint32_t c = 0; c < p.rows_padded; c += 16) {
+            float v[16];
+            tmem_ld16_wait(t0 + half * kWideDCols + c, v);
+            if (col >= p.n) continue;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const uint32_t t = c + j;
+              if (t < p.rows) {
+                float y = v[j] * scale_back[t];
+                if (p.epilogue == SB_EPILOGUE_RESIDUAL) y += bf16_bits_to_float(p.aux[size_t(t) * p.aux_stride + col]);
+                else if (p.epilogue == SB_EPILOGUE_UP_WITH_GATE) y = round_bf16(y) * silu_f(bf16_bits_to_float(p.aux[size_t(t) * p.aux_stride + col]));
+                if (p.out_f32) static_cast<float *>(p.out)[size_t(t) * p.out_stride + col] = y;
+                else static_cast<uint16_t *>(p.out)[size_t(t) * p.out_stride + col] = float_to_bf16_bits(y);
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(d_empty);
+    }
+  }
+
+  // Everyone meets here, also after a wait that gave up, so tensor memory is always returned.
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == kWideMmaWarp) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem, kWideTmemCols);
+  }
+}
+
+static int wide_check(const SbLinearArgs *a, const char *who) {
+  SB_REQUIRE(a, "%s: null arguments", who);
+  SB_REQUIRE(a->format == SB_FMT_Q4K, "%s: format %u (the many-row kernel multiplies Q4_K rows)", who, a->format);
+  SB_REQUIRE(a->rows >= 1, "%s: no rows", who);
+  SB_REQUIRE(a->k && a->k % 256 == 0 && a->n && a->n % 8 == 0, "%s: k = %u is not a multiple of 256 or n = %u not a multiple of 8", who, a->k, a->n);
+  SB_REQUIRE(a->weights && a->out && (a->x || a->prepared), "%s: null weights, out, or neither x nor prepared", who);
+  SB_REQUIRE(a->epilogue <= SB_EPILOGUE_GATE_UP, "%s: epilogue %u (none, residual, up-with-gate or one-pass gate/up)", who, a->epilogue);
+  SB_REQUIRE((a->epilogue == SB_EPILOGUE_GATE_UP) == (a->weights2 != nullptr), "%s: weights2 is given exactly with the gate/up epilogue", who);
+  SB_REQUIRE((a->epilogue == SB_EPILOGUE_RESIDUAL || a->epilogue == SB_EPILOGUE_UP_WITH_GATE) == (a->aux != nullptr),
+             "%s: aux is given exactly with the residual and up-with-gate epilogues", who);
+  SB_REQUIRE(a->out_stride >= a->n && (!a->aux || a->aux_stride >= a->n), "%s: a stride is below n", who);
+  SB_REQUIRE(!(a->out_f32 && a->epilogue != SB_EPILOGUE_NONE), "%s: an fp32 destination takes no epilogue", who);
+  SB_REQUIRE((reinterpret_cast<uintptr_t>(a->weights) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->weights2) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(a->prepared) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->x) & 15) == 0,
+             "%s: weights, x and prepared must be 16-byte aligned", who);
+  return SB_OK;
+}
+
+}  // namespace sb
+
+using namespace sb;
+
+extern "C" uint64_t sb_linear_wide_prepared_bytes(uint32_t rows, uint32_t k) {
+  if (!rows || !k || k % 256) return 0;
+  const uint64_t passes = (rows + kWideMaxRows - 1) / kWideMaxRows;
+  return passes * (kWideHeader + uint64_t(kWideMaxRows) * k * 2);  // every pass sized for a full one
+}
+
+// One pass = up to 128 rows; pass i of the conversion starts at sb_linear_wide_prepared_bytes(128, k) * i.
+extern "C" int sb_linear_wide_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride, const void *norm_weight,
+                                      void *prepared_out, uint32_t flags) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(x && prepared_out && rows >= 1, "sb_linear_wide_prepare: null x or destination, or no rows");
+  SB_REQUIRE(k && k % 256 == 0 && x_stride >= k && x_stride % 8 == 0, "sb_linear_wide_prepare: k = %u is not a multiple of 256, or x_stride %u", k, x_stride);
+  SB_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(prepared_out) | reinterpret_cast<uintptr_t>(norm_weight)) & 15) == 0,
+             "sb_linear_wide_prepare: pointers must be 16-byte aligned");
+  const uint64_t pass_bytes = sb_linear_wide_prepared_bytes(kWideMaxRows, k);
+  for (uint32_t r0 = 0, pass = 0; r0 < rows; r0 += kWideMaxRows, ++pass) {
+    const uint32_t n = std::min(kWideMaxRows, rows - r0), padded = (n + 15) / 16 * 16;
+    WidePrepParams pp{static_cast<const uint16_t *>(x) + size_t(r0) * x_stride, static_cast<const float *>(norm_weight),
+                      static_cast<uint8_t *>(prepared_out) + pass * pass_bytes, n, padded, k, x_stride};
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(padded), cfg.blockDim = dim3(kWidePrepThreads), cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = (flags & SB_LINEAR_PDL) ? 1 : 0;
+    SB_CUDA(cudaLaunchKernelEx(&cfg, wide_prepare_kernel, pp));
+  }
+  return SB_OK;
+}
+
+extern "C" int sb_linear_wide(void *stream, const SbLinearArgs *a) {
+  SB_NEED_DEVICE();
+  const int valid = wide_check(a, "sb_linear_wide");
+  if (valid != SB_OK) return valid;
+  Context &c = ctx();
+  const void *prepared = a->prepared;
+  if (!prepared) {
+    SB_REQUIRE(sb_linear_wide_prepared_bytes(a->rows, a->k) <= c.wide_prepared_bytes, "sb_linear_wide: %u rows of k = %u exceed the context's conversion scratch", a->rows, a->k);
+    const int st = sb_linear_wide_prepare(stream, a->x, a->rows, a->k, a->x_stride, a->norm_weight, c.wide_prepared, a->flags);
+    if (st != SB_OK) return st;
+    prepared = c.wide_prepared;
+  }
+  const bool gate_up = a->epilogue == SB_EPILOGUE_GATE_UP;
+  WideMaps maps;
+  const uint32_t row_bytes = uint32_t(sb_row_bytes(a->format, a->k));
+  if (gate_up) {
+    int st = encode_weight_map(&maps.m[0], reinterpret_cast<uintptr_t>(a->weights), row_bytes, a->n, 144, 128);
+    if (st == SB_OK) st = encode_weight_map(&maps.m[1], reinterpret_cast<uintptr_t>(a->weights2), row_bytes, a->n, 144, 128);
+    if (st != SB_OK) return st;
+  } else {
+    // The item's halves are rows [256 i, 256 i + 128) and [256 i + 128, 256 i + 256): two maps over every other block of 128
+    // rows would need a 3-D map; instead the second half is the same map shifted by 128 rows (rows past n read as zero).
+    int st = encode_weight_map(&maps.m[0], reinterpret_cast<uintptr_t>(a->weights), row_bytes, a->n, 144, 128);
+    if (st != SB_OK) return st;
+    maps.m[1] = maps.m[0];
+  }
+  static bool attr_set[64] = {};  // a function attribute is per device
+  const int dev = c.device >= 0 && c.device < 64 ? c.device : 0;
+  if (!attr_set[dev]) {
+    SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kWideSmem)));
+    attr_set[dev] = true;
+  }
+  const uint64_t pass_bytes = sb_linear_wide_prepared_bytes(kWideMaxRows, a->k);
+  for (uint32_t r0 = 0, pass = 0; r0 < a->rows; r0 += kWideMaxRows, ++pass) {
+    WideParams p{};
+    p.prepared = static_cast<const uint8_t *>(prepared) + pass * pass_bytes;
+    p.rows = std::min(kWideMaxRows, a->rows - r0), p.rows_padded = (p.rows + 15) / 16 * 16;
+    const size_t esz = a->out_f32 ? 4 : 2;
+    p.aux = a->aux ? static_cast<const uint16_t *>(a->aux) + size_t(r0) * a->aux_stride : nullptr;
+    p.out = static_cast<uint8_t *>(a->out) + size_t(r0) * a->out_stride * esz;
+    p.status = c.status_dev;
+    p.n = a->n, p.aux_stride = a->aux_stride, p.out_stride = a->out_stride, p.epilogue = a->epilogue, p.out_f32 = a->out_f32;
+    p.nsb = a->k / 256, p.gate_up = gate_up;
+    p.items = gate_up ? (a->n + 127) / 128 : (a->n + 255) / 256;
+    p.x_stage_bytes = p.rows_padded * 128;
+    p.x_stages = std::min(kWideMaxXStages, kWideXBytes / p.x_stage_bytes) / 4 * 4;  // whole super-blocks of stages
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(std::min<uint32_t>(p.items, uint32_t(c.sm_count)));
+    cfg.blockDim = dim3(kWideThreads);
+    cfg.dynamicSmemBytes = kWideSmem;
+    cfg.stream = as_stream(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = (a->flags & SB_LINEAR_PDL) ? 1 : 0;
+    SB_CUDA(cudaLaunchKernelEx(&cfg, linear_wide_kernel, p, maps));
+  }
+  return SB_OK;
+}

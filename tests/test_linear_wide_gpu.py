@@ -1,0 +1,117 @@
+"""Parity of the many-row projection (sb_linear with more than 16 rows -> sb_linear_wide: weights dequantized to half,
+tcgen05 tensor cores, accumulators in tensor memory) with the oracle's fp64 products, through the C ABI.
+
+Gate, as in the reference's projection test for its staged tile (dev/tests/engine/gguf_projection_test.mm:226-245):
+every output lies in [round(v - e), round(v + e)], v the fp64 dot product and e the bound that admits weights rounded to
+half (2^-16 sum|x| max|w| + 2^-11 sum|x w| + 2^-25 sum|x|, dev/tests/engine/GgufFormatReference.hpp:728-742). This
+kernel rounds the weight's two factors (d sc, dmin mn) to half before their fused multiply-add, so each weight carries
+up to three half roundings where the reference's tile carries one: the middle term is taken three times. The north
+star's 2e-3 of the output's scale is checked as well."""
+import numpy as np
+import pytest
+
+import oracle_lib as ol
+import quant_fixtures as qf
+from test_linear_gpu import check_interval, oracle_f64, run_linear
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup():
+    from splash_b200 import lib
+    lib.init(0)
+    return lib
+
+
+def wide_bound(fmt, W, n, k, X, rows):
+    v, be, bs = oracle_f64(fmt, W, n, k, X, rows)
+    return v, be + 3.0 * (bs - be)
+
+
+@pytest.mark.parametrize("n,k,rows", [
+    (512, 1024, 128), (256, 5120, 64), (392, 2048, 17), (1024, 1024, 100), (256, 1024, 130), (768, 2048, 256), (128, 17408, 48),
+])
+def test_wide_plain(n, k, rows):
+    lib = _setup()
+    W = qf.realistic(0, n, k, seed=n + k)
+    X = qf.activations(rows, k, seed=rows)
+    got = run_linear(lib, 0, W, n, k, X, rows)
+    v, e = wide_bound(0, W, n, k, X, rows)
+    check_interval(got, v - e, v + e)
+    # the north star's tolerance on the fp32 sums (the bf16 destination's own rounding is up to 2^-9 = 1.95e-3 more)
+    got32 = run_linear(lib, 0, W, n, k, X, rows, out_f32=True)
+    rel = np.abs(got32 - v) / np.maximum(np.abs(v), np.abs(v).mean())
+    assert rel.max() < 2e-3 and np.median(rel) < 4e-4
+    assert np.array_equal(got, ol.f2bf(got32))
+
+
+def test_wide_config0_shape_at_128_rows():
+    """The gate projection of the 27B shape at 128 rows (8 lanes of 16): X ~ N(0,1), W [17408, 5120] Q4_K by the benchmark's recipe."""
+    lib = _setup()
+    n, k, rows = 17408, 5120, 128
+    W = qf.config0_q4k(n, k, seed=0)
+    X = qf.activations(rows, k, seed=0)
+    got = run_linear(lib, 0, W, n, k, X, rows)
+    v, e = wide_bound(0, W, n, k, X, rows)
+    check_interval(got, v - e, v + e)
+
+
+def test_wide_f32_destination_rounds_to_bf16_destination():
+    lib = _setup()
+    n, k, rows = 512, 2048, 96
+    W = qf.realistic(0, n, k)
+    X = qf.activations(rows, k)
+    a = run_linear(lib, 0, W, n, k, X, rows)
+    b = run_linear(lib, 0, W, n, k, X, rows, out_f32=True)
+    assert np.array_equal(a, ol.f2bf(b))
+
+
+def test_wide_rows_independent_of_the_other_rows():
+    """A row's output does not depend on how many other rows share the launch or the pass, nor on NaN in them."""
+    lib = _setup()
+    n, k = 256, 2048
+    W = qf.realistic(0, n, k)
+    X = qf.activations(160, k)
+    full = run_linear(lib, 0, W, n, k, X, 160)
+    some = run_linear(lib, 0, W, n, k, X[:40].copy(), 40)
+    assert np.array_equal(full[:40], some)
+    tail = run_linear(lib, 0, W, n, k, X[128:160].copy(), 32)   # the second pass's rows, alone
+    assert np.array_equal(full[128:160], tail)
+    Xn = X[:64].copy()
+    Xn[30:] = 0x7FC0
+    part = run_linear(lib, 0, W, n, k, Xn, 64)
+    assert np.array_equal(full[:30], part[:30])
+
+
+def test_wide_residual_gate_and_one_pass_gate_up():
+    lib = _setup()
+    n, k, rows = 384, 2048, 80
+    rng = np.random.default_rng(3)
+    W, W2 = qf.realistic(0, n, k, seed=1), qf.realistic(0, n, k, seed=2)
+    X = qf.activations(rows, k)
+    aux = ol.f2bf(rng.standard_normal((rows, n)).astype(np.float32))
+    plain = run_linear(lib, 0, W, n, k, X, rows, out_f32=True)
+    ad = lib.DeviceBuffer.from_numpy(aux)
+    res = run_linear(lib, 0, W, n, k, X, rows, aux=ad.ptr, epilogue=lib.EP_RESIDUAL)
+    assert np.array_equal(res, ol.f2bf(plain + ol.bf2f(aux)))
+    silu = lambda x: x / (1.0 + np.exp2(np.float32(-1.44269504089) * x))
+    gated = run_linear(lib, 0, W, n, k, X, rows, aux=ad.ptr, epilogue=lib.EP_UP_WITH_GATE)
+    want = ol.bf2f(ol.f2bf(plain)) * silu(ol.bf2f(aux))
+    d = np.abs(ol.bf2f(gated) - want)
+    assert (d <= 2.0 ** -7 * np.abs(want) + 1e-30).all()          # within a bf16 step (the quotient is the approximate one)
+    # one pass over gate and up rows == the separate gate pass feeding the up pass
+    w2d = lib.DeviceBuffer.from_numpy(W2)
+    one = run_linear(lib, 0, W, n, k, X, rows, weights2=w2d.ptr, epilogue=lib.EP_GATE_UP)
+    gate = run_linear(lib, 0, W, n, k, X, rows)
+    gd = lib.DeviceBuffer.from_numpy(gate)
+    two = run_linear(lib, 0, W2, n, k, X, rows, aux=gd.ptr, epilogue=lib.EP_UP_WITH_GATE)
+    assert np.array_equal(one, two)
+
+
+def test_wide_rejects_what_it_does_not_multiply():
+    lib = _setup()
+    d = lib.DeviceBuffer(1 << 20)
+    with pytest.raises(lib.SbError):
+        lib.linear(d.ptr, d.ptr, d.ptr, lib.FMT_Q6K, 256, 1024, 64)       # Q4_K only
+    with pytest.raises(lib.SbError):
+        lib.linear(d.ptr, d.ptr, d.ptr, lib.FMT_Q4K, 256, 1000, 64)       # k not whole super-blocks
