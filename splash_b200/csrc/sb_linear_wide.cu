@@ -11,17 +11,23 @@
 // multiply-add, which keeps the expansion at three instructions per two weights; the projection stays inside the
 // reference's bound for half-rounded weights with room to spare (tests/test_linear_wide_gpu.py states the bound used).
 //
-//   item      256 weight rows (two 128-row halves, or 128 gate rows and the 128 up rows of the same columns) x all of K
-//             x one pass of up to 128 rows of X; persistent CTAs walk the items
-//   weights   tiled TMA: one box of 128 rows x 144 bytes per (half, super-block) into a ring; never re-read
+//   item      256 weight rows (two 128-row halves, or 128 gate rows and the 128 up rows of the same columns; one half where
+//             whole items would leave SMs idle) x all of K x one pass of up to 128 rows of X; persistent CTAs walk the items
+//   weights   tiled TMA: one box of 128 rows x 144 bytes per (half, super-block) into a ring of four; never re-read
 //   X         converted once by wide_prepare_kernel to fp16 with a per-row power-of-two scale, laid out as the K-major
-//             core matrices the MMA reads (8 rows x 16 bytes), and streamed per 64 inputs from the L2 into a second ring
-//   dequant   8 warps: warp (quadrant q, half h) expands sub-blocks 4h .. 4h+3 of rows 32q .. 32q+31 (a thread owns a row)
-//             and writes the 128 halves with tcgen05.st into one of four A buffers of tensor memory (64 columns each)
-//   mma       one thread: per A buffer 8 tcgen05.mma (M 128, N = rows rounded up to 16, K 16), A from tensor memory, B from
-//             the X ring; tcgen05.commit frees the A buffer, the X stage and, after the item's last step, hands the two
-//             accumulators (128 lanes x N fp32 columns each) to the epilogue
-//   epilogue  4 warps, a thread per weight row: tcgen05.ld 32 columns at a time, scale back, epilogue, store
+//             core matrices the MMA reads (8 rows x 16 bytes), and streamed super-block by super-block from the L2 into a
+//             second ring (128 KB) by a warp of its own
+//   dequant   16 warps: warp (half of the item, inputs' half h, quadrant q) expands sub-blocks 4h .. 4h+3 of rows
+//             32q .. 32q+31 (a thread owns a row) and writes the 128 halves with tcgen05.st into its A buffer of tensor
+//             memory (64 columns; four buffers, one per (half of the item, inputs' half))
+//   mma       two threads in two warps, one per half of the item, each with its own accumulator (128 lanes x N fp32
+//             columns), so the order of a sum is fixed. Measured here: one thread issues a tcgen05.mma of this shape every
+//             100 to 125 cycles whatever N <= 128 is, two threads together one per 62 to 70, four one per 31 to 36; the
+//             tensor pipe needs 64 at N = 128. Per A buffer 8 MMAs (M 128, N = rows rounded up to 16, K 16), A from tensor
+//             memory, B from the X ring; tcgen05.commit frees the A buffer, the X group and, after the item's last step,
+//             hands the accumulators to the epilogue
+//   epilogue  4 warps, a thread per weight row: tcgen05.ld 16 columns at a time, scale back, the epilogue on all 16
+//             without a branch, then the stores
 // Every wait is bounded and reports through the status word; tensor memory is always returned.
 #include <algorithm>
 
@@ -36,9 +42,9 @@ namespace sb {
 
 constexpr uint32_t kWideMaxRows = 128;             // rows of X one pass multiplies (the accumulators' columns)
 constexpr uint32_t kWideHeader = 1024;             // scale_back[256] floats (a pass reads its 128)
-constexpr uint32_t kWideDequantWarps = 8, kWideEpilogueWarps = 4;
-constexpr uint32_t kWideProducerWarp = kWideDequantWarps + kWideEpilogueWarps, kWideMmaWarp = kWideProducerWarp + 1;
-constexpr uint32_t kWideThreads = 32 * (kWideMmaWarp + 1);  // 448
+constexpr uint32_t kWideDequantWarps = 16, kWideEpilogueWarps = 4;  // dequant: (half of the item, inputs' half, quadrant)
+constexpr uint32_t kWideRawWarp = kWideDequantWarps + kWideEpilogueWarps, kWideXWarp = kWideRawWarp + 1, kWideMmaWarp0 = kWideXWarp + 1;
+constexpr uint32_t kWideThreads = 32 * (kWideMmaWarp0 + 2);  // 768
 constexpr uint32_t kWideRawStage = 128 * 144, kWideRawStages = 4;   // one (half, super-block) of an item: 18 KB
 constexpr uint32_t kWideXBytes = 128 * 1024, kWideMaxXStages = 8;   // the X ring; a stage holds 64 inputs of every row
 constexpr uint32_t kWideABufs = 4, kWideACols = 64, kWideACol0 = 256, kWideDCols = 128, kWideTmemCols = 512;
@@ -52,8 +58,24 @@ struct WideParams {
   void *out;
   uint32_t *status;
   uint32_t n, rows, rows_padded, aux_stride, out_stride, epilogue, out_f32;
-  uint32_t nsb, items, x_stages, x_stage_bytes, gate_up;
+  uint32_t nsb, items, x_groups, x_stage_bytes, gate_up;
+  uint32_t halves;  // 128-row halves per item: 2, or 1 when whole items would leave SMs idle  // x_groups: super-blocks of X the ring holds
 };
+#ifdef SB_DIAG
+// Cycle counters of the roles of CTA 0 (diagnostic builds only): [role][what], read back through sb_linear_wide_timing.
+__device__ unsigned long long g_wide_timing[8][8];
+#define WIDE_T0() const long long t_begin_ = clock64()
+#define WIDE_TADD(role, what) do { wt_[what] += (unsigned long long)(clock64() - t_begin_); wt_role_ = role; } while (0)
+#define WIDE_EVENT(i) do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0) g_wide_timing[7][i] = (unsigned long long)(clock64() - t_kernel_); } while (0)
+#define WIDE_KERNEL_T0() const long long t_kernel_ = clock64(); unsigned long long wt_[4] = {0, 0, 0, 0}; int wt_role_ = -1
+#define WIDE_FLUSH() do { if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && wt_role_ >= 0) for (int i_ = 0; i_ < 4; ++i_) g_wide_timing[wt_role_][i_] = wt_[i_]; } while (0)
+#else
+#define WIDE_FLUSH() do {} while (0)
+#define WIDE_T0() do {} while (0)
+#define WIDE_TADD(role, what) do {} while (0)
+#define WIDE_EVENT(i) do {} while (0)
+#define WIDE_KERNEL_T0() do {} while (0)
+#endif
 struct WideMaps {
   CUtensorMap m[2];  // the item's first half (or gate rows), its second half (or up rows)
 };
@@ -180,6 +202,7 @@ __device__ __forceinline__ void wide_expand_q4k(const uint8_t *row, uint32_t h, 
 
 __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const WideParams p, const __grid_constant__ WideMaps maps) {
   extern __shared__ __align__(128) uint8_t smem[];
+  WIDE_KERNEL_T0();
   uint64_t *raw_full = reinterpret_cast<uint64_t *>(smem);        // [kWideRawStages]
   uint64_t *raw_empty = raw_full + kWideRawStages;
   uint64_t *x_full = raw_empty + kWideRawStages;                   // [kWideMaxXStages]
@@ -193,32 +216,30 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
   float *scale_back = reinterpret_cast<float *>(smem + 512);       // [128]
   uint8_t *x_ring = smem + kWideXOff, *raw_ring = smem + kWideRawOff;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t units_per_item = 2 * p.nsb;  // (super-block, half of the item) pairs, each dequantized in two halves of 128 inputs
 
   if (threadIdx.x == 0) {
-    for (uint32_t s = 0; s < kWideRawStages; ++s) mbar_init(&raw_full[s], 1), mbar_init(&raw_empty[s], kWideDequantWarps);
-    for (uint32_t s = 0; s < kWideMaxXStages; ++s) mbar_init(&x_full[s], 1), mbar_init(&x_empty[s], 1);
+    for (uint32_t s = 0; s < kWideRawStages; ++s) mbar_init(&raw_full[s], 1), mbar_init(&raw_empty[s], 8);
+    for (uint32_t s = 0; s < kWideMaxXStages; ++s) mbar_init(&x_full[s], 1), mbar_init(&x_empty[s], p.halves);
     for (uint32_t s = 0; s < kWideABufs; ++s) mbar_init(&a_full[s], 4), mbar_init(&a_empty[s], 1);
-    mbar_init(d_full, 1), mbar_init(d_empty, kWideEpilogueWarps), mbar_init(h_full, 1);
+    mbar_init(d_full, p.halves), mbar_init(d_empty, kWideEpilogueWarps), mbar_init(h_full, 1);
     fence_mbar_init();
   }
-  if (warp == kWideMmaWarp) tmem_alloc(tmem_slot, kWideTmemCols);
+  if (warp == kWideMmaWarp0) tmem_alloc(tmem_slot, kWideTmemCols);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
   pdl_launch_dependents();
+  if (warp == 0) WIDE_EVENT(0);  // set-up done
 
-  if (warp == kWideProducerWarp) {
-    // ---- producer: the weights' ring fills at once (they do not depend on the kernel ahead); X follows the wait ----
+  if (warp == kWideRawWarp) {
+    // ---- weights: they do not depend on the kernel ahead, so the ring fills at once ----
     const uint64_t policy = policy_evict_first();
+    uint32_t rs = 0, rphase = 0, rcount = 0;
     bool ok = true;
-    uint32_t rs = 0, rphase = 0, rcount = 0, xs = 0, xphase = 0, xcount = 0;
-    // X stages trail the weights: per super-block the two halves' boxes, then that super-block's four X stages.
-    bool waited = false;
-    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
-      for (uint32_t sb = 0; sb < p.nsb && ok; ++sb) {
-        for (uint32_t tn = 0; tn < 2 && ok; ++tn, ++rcount) {
+    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x)
+      for (uint32_t sb = 0; sb < p.nsb && ok; ++sb)
+        for (uint32_t tn = 0; tn < p.halves && ok; ++tn, ++rcount) {
           if (rcount >= kWideRawStages && !wide_warp_wait(&raw_empty[rs], rphase ^ 1, true)) {
             if (lane == 0) wide_expired(p.status, 1);
             ok = false;
@@ -226,44 +247,48 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
           }
           if (lane == 0) {
             mbar_arrive_expect_tx(&raw_full[rs], kWideRawStage);
-            tma_load_2d(raw_ring + rs * kWideRawStage, &maps.m[tn], int(sb * 36), int(p.gate_up ? item * 128 : item * 256 + tn * 128), &raw_full[rs], policy, true);
+            tma_load_2d(raw_ring + rs * kWideRawStage, &maps.m[tn], int(sb * 36), int(p.gate_up ? item * 128 : item * 128 * p.halves + tn * 128), &raw_full[rs], policy, true);
           }
           if (++rs == kWideRawStages) rs = 0, rphase ^= 1;
         }
-        if (!waited) {
-          pdl_wait();  // X comes from the kernel ahead
-          if (lane == 0) {
-            mbar_arrive_expect_tx(h_full, 512);
-            bulk_g2s(scale_back, p.prepared, 512, h_full);
-          }
-          waited = true;
-        }
-        for (uint32_t q = 0; q < 4 && ok; ++q, ++xcount) {
-          if (xcount >= p.x_stages && !wide_warp_wait(&x_empty[xs], xphase ^ 1, true)) {
-            if (lane == 0) wide_expired(p.status, 2);
-            ok = false;
-            break;
-          }
-          if (lane == 0) {
-            mbar_arrive_expect_tx(&x_full[xs], p.x_stage_bytes);
-            bulk_g2s(x_ring + xs * p.x_stage_bytes, p.prepared + kWideHeader + size_t(4 * sb + q) * p.x_stage_bytes, p.x_stage_bytes, &x_full[xs]);
-          }
-          if (++xs == p.x_stages) xs = 0, xphase ^= 1;
-        }
-      }
-    }
     // Do not leave while copies are in flight: every stage issued is waited for (bounded) before the warp returns.
     for (uint32_t f = rcount > kWideRawStages ? rcount - kWideRawStages : 0; f < rcount; ++f)
       if (!wide_warp_wait(&raw_empty[f % kWideRawStages], (f / kWideRawStages) & 1, true)) break;
-    for (uint32_t f = xcount > p.x_stages ? xcount - p.x_stages : 0; f < xcount; ++f)
-      if (!wide_warp_wait(&x_empty[f % p.x_stages], (f / p.x_stages) & 1, true)) break;
-  } else if (warp == kWideMmaWarp) {
-    // ---- MMA issuer ----
+  } else if (warp == kWideXWarp) {
+    // ---- X: a group is the four stages (64 inputs each) of one super-block; the ring holds x_groups of them ----
+    pdl_wait();  // X comes from the kernel ahead
     if (lane == 0) {
+      mbar_arrive_expect_tx(h_full, 512);
+      bulk_g2s(scale_back, p.prepared, 512, h_full);
+    }
+    uint32_t xg = 0, xphase = 0, xcount = 0;
+    bool ok = true;
+    const uint32_t group_bytes = 4 * p.x_stage_bytes;
+    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x)
+      for (uint32_t sb = 0; sb < p.nsb && ok; ++sb, ++xcount) {
+        if (xcount >= p.x_groups && !wide_warp_wait(&x_empty[xg], xphase ^ 1, true)) {
+          if (lane == 0) wide_expired(p.status, 2);
+          ok = false;
+          break;
+        }
+        if (lane == 0) {
+          mbar_arrive_expect_tx(&x_full[xg], group_bytes);
+          bulk_g2s(x_ring + xg * group_bytes, p.prepared + kWideHeader + size_t(sb) * group_bytes, group_bytes, &x_full[xg]);
+        }
+        if (++xg == p.x_groups) xg = 0, xphase ^= 1;
+      }
+    for (uint32_t f = xcount > p.x_groups ? xcount - p.x_groups : 0; f < xcount; ++f)
+      if (!wide_warp_wait(&x_empty[f % p.x_groups], (f / p.x_groups) & 1, true)) break;
+  } else if (warp >= kWideMmaWarp0) {
+    // ---- MMA issuers: one thread per half of the item (its own accumulator, so the sums' order is fixed). A single
+    // thread issues one tcgen05.mma of this shape per 100 to 125 cycles whatever N is; two threads keep the tensor pipe
+    // busy at N = 128 (measured: 62 to 70 cycles per MMA overall). ----
+    if (lane == 0 && warp - kWideMmaWarp0 < p.halves) {
+      const uint32_t tn = warp - kWideMmaWarp0;
       const uint32_t idesc = umma_idesc_f16(128, p.rows_padded);
+      const uint32_t d0 = tmem + tn * kWideDCols;
       bool ok = true;
-      uint32_t ucount = 0, xs = 0, xphase = 0, dphase = 0;
-      uint32_t done_items = 0;
+      uint32_t ucount = 0, xg = 0, xphase = 0, dphase = 0, done_items = 0;
       for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x, ++done_items) {
         if (done_items > 0) {  // the accumulators of the item before must have been read
           ok = mbar_wait(d_empty, dphase);
@@ -271,72 +296,90 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
           if (!ok) { wide_expired(p.status, 3); break; }
         }
         for (uint32_t sb = 0; sb < p.nsb && ok; ++sb) {
-          // Units of this super-block in the order the dequant warps fill the A buffers: (half of the item, inputs' half).
-          // X stage xs + 2 hh + j serves K-steps of inputs' half hh; both halves of the item read the same X stages.
-          for (uint32_t tn = 0; tn < 2 && ok; ++tn) {
-            for (uint32_t hh = 0; hh < 2 && ok; ++hh, ++ucount) {
-              const uint32_t ab = ucount % kWideABufs;
-              ok = mbar_wait(&a_full[ab], (ucount / kWideABufs) & 1);
-              if (!ok) { wide_expired(p.status, 4); break; }
-              tc_fence_after_sync();
-              const uint32_t a0 = tmem + kWideACol0 + ab * kWideACols, d0 = tmem + tn * kWideDCols;
-#pragma unroll 1
-              for (uint32_t j = 0; j < 2 && ok; ++j) {  // the two X stages (64 inputs each) of this half
-                uint32_t st = xs + 2 * hh + j, ph = xphase;
-                if (st >= p.x_stages) st -= p.x_stages, ph ^= 1;
-                if (tn == 0) {
-                  ok = mbar_wait(&x_full[st], ph);
-                  if (!ok) { wide_expired(p.status, 5); break; }
-                  tc_fence_after_sync();
-                }
-                const uint32_t xbase = smem_u32(x_ring + st * p.x_stage_bytes);
-#pragma unroll
-                for (uint32_t i = 0; i < 4; ++i) {
-                  const uint64_t b = umma_smem_desc(xbase + i * p.rows_padded * 32, 128, 256);
-                  umma_f16_ts(d0, a0 + (4 * j + i) * 8, b, idesc, !(sb == 0 && hh == 0 && j == 0 && i == 0));
-                }
-                if (tn == 1) umma_commit(&x_empty[st]);  // both halves of the item have read the stage
-              }
-              umma_commit(&a_empty[ab]);
-            }
+          {
+            WIDE_T0();
+            ok = mbar_wait(&x_full[xg], xphase);
+            if (tn == 0) WIDE_TADD(1, 2);
           }
-          xs += 4;
-          if (xs >= p.x_stages) xs -= p.x_stages, xphase ^= 1;
+          if (!ok) { wide_expired(p.status, 5); break; }
+          const uint32_t xbase = smem_u32(x_ring + xg * 4 * p.x_stage_bytes);
+          for (uint32_t hh = 0; hh < 2 && ok; ++hh, ++ucount) {
+            const uint32_t ab = 2 * tn + hh;  // this half's A buffer for inputs' half hh
+            {
+              WIDE_T0();
+              ok = mbar_wait(&a_full[ab], ucount >> 1 & 1);
+              if (tn == 0) WIDE_TADD(1, 0);
+            }
+            if (!ok) { wide_expired(p.status, 4); break; }
+            if (tn == 0 && ucount == 0) WIDE_EVENT(2);  // first MMA
+            WIDE_T0();
+            tc_fence_after_sync();
+            const uint32_t a0 = tmem + kWideACol0 + ab * kWideACols;
+#pragma unroll
+            for (uint32_t i = 0; i < 8; ++i) {  // K-step i of this half of the super-block
+              const uint64_t b = umma_smem_desc(xbase + (8 * hh + i) * p.rows_padded * 32, 128, 256);
+              umma_f16_ts(d0, a0 + i * 8, b, idesc, !(sb == 0 && hh == 0 && i == 0));
+            }
+            umma_commit(&a_empty[ab]);
+            if (tn == 0) WIDE_TADD(1, 1);
+          }
+          if (ok) umma_commit(&x_empty[xg]);  // this half of the item has read the group (the barrier counts both halves)
+          if (++xg == p.x_groups) xg = 0, xphase ^= 1;
         }
         if (ok) umma_commit(d_full);
+        if (tn == 0) WIDE_EVENT(3);  // last MMA issued
       }
     }
     __syncwarp();
   } else if (warp < kWideDequantWarps) {
-    // ---- dequant: warp (q, h) expands inputs' half h of rows 32 q .. 32 q + 31 of every (super-block, item half) ----
-    const uint32_t q = warp & 3, h = warp >> 2, row = 32 * q + lane;
-    uint32_t rs = 0, rphase = 0, ucount = h;  // this warp's units are ucount = h, h + 2, ...: A buffers h, h + 2
-    bool ok = true;
+    // ---- dequant: warp (tn, h, q) expands inputs' half h of rows 32 q .. 32 q + 31 of half tn of the item, super-block by
+    // super-block: its raw stages are every other one of the ring, its A buffer is 2 tn + h ----
+    const uint32_t q = warp & 3, h = (warp >> 2) & 1, tn = warp >> 3, row = 32 * q + lane;
+    const uint32_t ab = 2 * tn + h;
+    uint32_t rs = tn, rphase = 0, scount = 0;  // super-blocks this warp has expanded
+    bool ok = tn < p.halves;
     for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x)
-      for (uint32_t u = 0; u < units_per_item && ok; ++u, ucount += 2) {
-        if (!wide_warp_wait(&raw_full[rs], rphase)) {
-          if (lane == 0) wide_expired(p.status, 6);
-          ok = false;
-          break;
+      for (uint32_t sb = 0; sb < p.nsb && ok; ++sb, ++scount) {
+        {
+          WIDE_T0();
+          if (!wide_warp_wait(&raw_full[rs], rphase)) {
+            if (lane == 0) wide_expired(p.status, 6);
+            ok = false;
+            break;
+          }
+          if (warp == 0) WIDE_TADD(0, 0);
+          if (warp == 0 && scount == 0) WIDE_EVENT(1);  // first weights landed
         }
         uint32_t r[64];
-        wide_expand_q4k(raw_ring + rs * kWideRawStage + row * 144, h, r);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&raw_empty[rs]);  // the row's bytes are in registers
-        if (++rs == kWideRawStages) rs = 0, rphase ^= 1;
-        const uint32_t ab = ucount % kWideABufs, use = ucount / kWideABufs;
-        if (use > 0 && !wide_warp_wait(&a_empty[ab], (use - 1) & 1)) {
-          if (lane == 0) wide_expired(p.status, 7);
-          ok = false;
-          break;
+        {
+          WIDE_T0();
+          wide_expand_q4k(raw_ring + rs * kWideRawStage + row * 144, h, r);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&raw_empty[rs]);  // the row's bytes are in registers
+          if (warp == 0) WIDE_TADD(0, 1);
         }
-        tc_fence_after_sync();
-        const uint32_t ta = tmem_addr(tmem, 32 * q, kWideACol0 + ab * kWideACols);
-        tmem_st16(ta, r), tmem_st16(ta + 16, r + 16), tmem_st16(ta + 32, r + 32), tmem_st16(ta + 48, r + 48);
-        tmem_wait_st();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&a_full[ab]);
+        rs += p.halves;
+        if (rs >= kWideRawStages) rs -= kWideRawStages, rphase ^= 1;
+        {
+          WIDE_T0();
+          if (scount > 0 && !wide_warp_wait(&a_empty[ab], (scount - 1) & 1)) {
+            if (lane == 0) wide_expired(p.status, 7);
+            ok = false;
+            break;
+          }
+          if (warp == 0) WIDE_TADD(0, 2);
+        }
+        {
+          WIDE_T0();
+          tc_fence_after_sync();
+          const uint32_t ta = tmem_addr(tmem, 32 * q, kWideACol0 + ab * kWideACols);
+          tmem_st16(ta, r), tmem_st16(ta + 16, r + 16), tmem_st16(ta + 32, r + 32), tmem_st16(ta + 48, r + 48);
+          tmem_wait_st();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&a_full[ab]);
+          if (warp == 0) WIDE_TADD(0, 3);
+        }
       }
   } else {
     // ---- epilogue: a thread per weight row of each half of the item ----
@@ -346,49 +389,71 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
     if (!ok && lane == 0) wide_expired(p.status, 8);
     uint32_t dphase = 0;
     for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
-      if (!wide_warp_wait(d_full, dphase)) {
-        if (lane == 0) wide_expired(p.status, 9);
-        ok = false;
-        break;
+      {
+        WIDE_T0();
+        if (!wide_warp_wait(d_full, dphase)) {
+          if (lane == 0) wide_expired(p.status, 9);
+          ok = false;
+          break;
+        }
+        if (q == 0) WIDE_TADD(2, 0);
       }
       dphase ^= 1;
       tc_fence_after_sync();
+      if (q == 0) WIDE_EVENT(4);  // sums complete
+      WIDE_T0();
       const uint32_t t0 = tmem_addr(tmem, 32 * q, 0);
+      // Per 16 rows of X: the sums out of tensor memory, the epilogue on all 16 without a branch (the chains of the
+      // activation overlap), then the stores of the rows that exist.
       if (p.gate_up) {
         const uint32_t col = item * 128 + row;
+        uint16_t *dst = static_cast<uint16_t *>(p.out) + col;
         for (uint32_t c = 0; c < p.rows_padded; c += 16) {
           float g[16], u[16];
           tmem_ld16_wait(t0 + c, g);
           tmem_ld16_wait(t0 + kWideDCols + c, u);
+          uint16_t o[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float s = scale_back[c + j];
+            o[j] = float_to_bf16_bits(round_bf16(u[j] * s) * silu_f(round_bf16(g[j] * s)));
+          }
           if (col < p.n) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const uint32_t t = c + j;
-              if (t < p.rows) {
-                const float s = scale_back[t];
-                const float o = round_bf16(u[j] * s) * silu_f(round_bf16(g[j] * s));
-                static_cast<uint16_t *>(p.out)[size_t(t) * p.out_stride + col] = float_to_bf16_bits(o);
-              }
-            }
+            for (int j = 0; j < 16; ++j)
+              if (c + j < p.rows) dst[size_t(c + j) * p.out_stride] = o[j];
           }
         }
       } else {
-        for (uint32_t half = 0; half < 2; ++half) {
-          const uint32_t col = item * 256 + half * 128 + row;
+        for (uint32_t half = 0; half < p.halves; ++half) {
+          const uint32_t col = item * 128 * p.halves + half * 128 + row;
+          const bool live = col < p.n;
           for (uint32_t c = 0; c < p.rows_padded; c += 16) {
             float v[16];
             tmem_ld16_wait(t0 + half * kWideDCols + c, v);
-            if (col >= p.n) continue;
+            float a[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) a[j] = 0.0f;
+            if (p.aux && live) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (c + j < p.rows) a[j] = bf16_bits_to_float(p.aux[size_t(c + j) * p.aux_stride + col]);
+            }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              const uint32_t t = c + j;
-              if (t < p.rows) {
-                float y = v[j] * scale_back[t];
-                if (p.epilogue == SB_EPILOGUE_RESIDUAL) y += bf16_bits_to_float(p.aux[size_t(t) * p.aux_stride + col]);
-                else if (p.epilogue == SB_EPILOGUE_UP_WITH_GATE) y = round_bf16(y) * silu_f(bf16_bits_to_float(p.aux[size_t(t) * p.aux_stride + col]));
-                if (p.out_f32) static_cast<float *>(p.out)[size_t(t) * p.out_stride + col] = y;
-                else static_cast<uint16_t *>(p.out)[size_t(t) * p.out_stride + col] = float_to_bf16_bits(y);
-              }
+              v[j] *= scale_back[c + j];
+              if (p.epilogue == SB_EPILOGUE_RESIDUAL) v[j] += a[j];
+              else if (p.epilogue == SB_EPILOGUE_UP_WITH_GATE) v[j] = round_bf16(v[j]) * silu_f(a[j]);
+            }
+            if (!live) continue;
+            if (p.out_f32) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (c + j < p.rows) static_cast<float *>(p.out)[size_t(c + j) * p.out_stride + col] = v[j];
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (c + j < p.rows) static_cast<uint16_t *>(p.out)[size_t(c + j) * p.out_stride + col] = float_to_bf16_bits(v[j]);
             }
           }
         }
@@ -396,13 +461,16 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
       tc_fence_before_sync();
       __syncwarp();
       if (lane == 0) mbar_arrive(d_empty);
+      if (q == 0) WIDE_TADD(2, 1);
+      if (q == 0) WIDE_EVENT(5);  // stored
     }
   }
 
+  WIDE_FLUSH();
   // Everyone meets here, also after a wait that gave up, so tensor memory is always returned.
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == kWideMmaWarp) {
+  if (warp == kWideMmaWarp0) {
     tc_fence_after_sync();
     tmem_dealloc(tmem, kWideTmemCols);
   }
@@ -429,6 +497,17 @@ static int wide_check(const SbLinearArgs *a, const char *who) {
 }  // namespace sb
 
 using namespace sb;
+
+#ifdef SB_DIAG
+extern "C" __attribute__((visibility("default"))) int sb_linear_wide_timing(unsigned long long *out64, int reset) {
+  if (out64) cudaMemcpyFromSymbol(out64, g_wide_timing, sizeof(g_wide_timing));
+  if (reset) {
+    static unsigned long long zero[64] = {};
+    cudaMemcpyToSymbol(g_wide_timing, zero, sizeof(zero));
+  }
+  return 0;
+}
+#endif
 
 extern "C" uint64_t sb_linear_wide_prepared_bytes(uint32_t rows, uint32_t k) {
   if (!rows || !k || k % 256) return 0;
@@ -503,9 +582,11 @@ extern "C" int sb_linear_wide(void *stream, const SbLinearArgs *a) {
     p.status = c.status_dev;
     p.n = a->n, p.aux_stride = a->aux_stride, p.out_stride = a->out_stride, p.epilogue = a->epilogue, p.out_f32 = a->out_f32;
     p.nsb = a->k / 256, p.gate_up = gate_up;
-    p.items = gate_up ? (a->n + 127) / 128 : (a->n + 255) / 256;
+    // Items of two halves read X once for 256 weight rows; where they would leave SMs idle, items of one half fill more.
+    p.halves = gate_up || (a->n + 255) / 256 >= uint32_t(c.sm_count) ? 2 : 1;
+    p.items = gate_up ? (a->n + 127) / 128 : (a->n + 128 * p.halves - 1) / (128 * p.halves);
     p.x_stage_bytes = p.rows_padded * 128;
-    p.x_stages = std::min(kWideMaxXStages, kWideXBytes / p.x_stage_bytes) / 4 * 4;  // whole super-blocks of stages
+    p.x_groups = std::min(kWideMaxXStages, kWideXBytes / (4 * p.x_stage_bytes));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(std::min<uint32_t>(p.items, uint32_t(c.sm_count)));
     cfg.blockDim = dim3(kWideThreads);
