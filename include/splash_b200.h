@@ -394,6 +394,17 @@ typedef struct SbSampleArgs {
   uint32_t top_k;
   float top_p;
   uint32_t *cut_out;         /* optional device u32 [rows, 2]: the end as {order key of the last logit, last id} */
+  /* Optional: the children each row's draft drew, for recursive rejection sampling without replacement
+   * (runtime/metal/kernels/decode/sampling.metal:693-885; uniforms runtime/metal/abi/Sampling.h:12-31). Per row its 16
+   * draft candidates (token ids, 0xFFFFFFFF past the draft's list), the draft's probabilities q of them, and the candidate
+   * indices of up to 4 drawn children in the order drawn (0xff past them). Child c of row r is kept iff
+   * u[16 + 4 r + c] q < p (p its probability under the target); after a rejection the target becomes max(p - q, 0)
+   * renormalised and the draft loses the child; a row that keeps none draws with u[r] from the last residual, its
+   * candidates first, then the tokens outside them by the target's own weights. Without these the drafted child is the
+   * input token of row r + 1 with q = 1 (a chain from a deterministic draft), which is the same rule. */
+  const uint32_t *candidate_ids; /* device u32 [rows, 16] or NULL */
+  const float *candidate_q;      /* device fp32 [rows, 16] */
+  const uint8_t *draws;          /* device u8 [rows, 4] */
 } SbSampleArgs;
 /* The sampling penalties of one lane's rows, in place, before selection: a token the prompt or the output holds has a
  * positive logit divided and a negative one multiplied by `repetition`; a token the output holds `count` times is
@@ -466,9 +477,14 @@ enum {
                             writes there itself. Positions are the rows' depths, attention and GDN follow each row's path,
                             the accepted path's KV rows move to their depths, and the next step folds the path's tape
                             rows. The step after a tree step carries the flag too (a chain can be given as a tree). */
-  SB_TARGET_KEEP_PENDING = 8 /* without SB_TARGET_ADVANCE: the lane's pending GDN rows (`pending_rows`, sb_target_tensor) stay
+  SB_TARGET_KEEP_PENDING = 8, /* without SB_TARGET_ADVANCE: the lane's pending GDN rows (`pending_rows`, sb_target_tensor) stay
                             as they are instead of being cleared, so every such step folds the same rows again: a held
                             lane that still does a committing cycle's fold work (steady-state timing). */
+  SB_TARGET_DRAWS = 16   /* sampled rows (temperature > 0) take their children from the target's `candidates` (u32 [16][16]),
+                            `candidate_q` (fp32 [16][16]) and `draws` (u8 [16][4]) buffers, which the host (the draft side)
+                            fills before the step: recursive rejection sampling over up to 4 drawn children a row
+                            (SbSampleArgs). A sampled tree block requires it; a sampled chain without it tests the next row's
+                            input token with q = 1. */
 };
 
 /* ---- MoE routing ----
@@ -563,7 +579,8 @@ SB_API int sb_target_destroy(void *target);
 /* Device pointer and byte size of a tensor or buffer by name. Per layer (layer >= 0): attn_norm, ffn_norm,
  * in_proj, out_proj, ffn_gate, ffn_up, ffn_down, and for GDN layers ssm_ab, ssm_conv, ssm_a, ssm_dt_bias, ssm_norm,
  * state0/1, conv0/1, for attention layers q_norm, k_norm, kv_k, kv_v, kv_ks, kv_vs. Global (layer = -1):
- * token_embd, output_norm, output, logits, selected, results, hidden, tokens, uniforms, committed, penalty_words. */
+ * token_embd, output_norm, output, logits, selected, results, hidden, tokens, uniforms, committed, penalty_words,
+ * candidates, candidate_q, draws. */
 SB_API int sb_target_tensor(void *target, int layer, const char *name, void **out_dev, uint64_t *out_bytes);
 /* The lane's sampling penalties (ops::SamplingPenalties, runtime/ops/Sampling.hpp:16-29; 1, 0, 0 switches them off): the
  * step then rewrites the logits in place before selection (sb_sample_penalize) from the table `penalty_words` (u32

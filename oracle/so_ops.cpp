@@ -431,6 +431,119 @@ SO_API void so_sample_verify_filtered(const float *logits, uint32_t logit_stride
   }
 }
 
+// Sampled rows whose children are the draws of a draft (runtime/metal/kernels/decode/sampling.metal:693-885, uniforms
+// runtime/metal/abi/Sampling.h:12-31): per row 16 candidate ids with the draft's probabilities q and the candidate indices
+// of up to 4 drawn children in the order drawn (0xff past them). Recursive rejection sampling without replacement: child c
+// is taken iff u[16 + 4 r + c] q < p; after a rejection p <- max(p - q, 0) / sum and the mass outside the candidates is
+// renormalised with it, q loses the child and is renormalised; a row that takes none draws with u[r] from the last
+// residual, its candidates first (cumulative in candidate order), else a token outside them by the target's own weights:
+// the shard (256 ids, weights summed in id order, the candidates' taken out) the point falls in, then its ids in order.
+// decision_margin[r]: the smallest relative distance of a test or of the final point from its threshold.
+SO_API void so_sample_verify_draws(const float *logits, uint32_t logit_stride, uint32_t vocab, uint32_t rows, float temperature,
+                                   float min_p, uint32_t top_k, float top_p, const float *uniforms, const uint32_t *candidate_ids,
+                                   const float *candidate_q, const uint8_t *draws, uint32_t *selected, double *decision_margin) {
+  constexpr uint32_t C = 16;
+  for (uint32_t r = 0; r < rows; ++r) {
+    const float *l = logits + size_t(r) * logit_stride;
+    double margin = INFINITY;
+    auto near = [&](double a, double b, double scale) { margin = std::min(margin, std::fabs(a - b) / std::max(scale, 1e-30)); };
+    const uint32_t top = argmax_row(l, vocab);
+    if (decision_margin) decision_margin[r] = INFINITY;
+    if (temperature == 0.0f || top == kSentinel) { selected[r] = top; continue; }
+    const float mx = l[top], inv_t = 1.0f / temperature;
+    const RowCut cut = distribution_end(l, vocab, mx, temperature, min_p, top_k, top_p);
+    const uint32_t shards = (vocab + kShard - 1) / kShard;
+    std::vector<float> w(vocab), shard(shards, 0.0f);
+    for (uint32_t v = 0; v < vocab; ++v) w[v] = cut_keeps(cut, l[v], v) ? expf((l[v] - mx) * inv_t) : 0.0f;
+    float z = 0.0f;
+    for (uint32_t s = 0; s < shards; ++s) {
+      float sum = 0.0f;
+      for (uint32_t v = s * kShard; v < std::min(vocab, (s + 1) * kShard); ++v) sum += w[v];
+      shard[s] = sum;
+      z += sum;
+    }
+    const uint32_t *ids = candidate_ids + C * r;
+    const uint8_t *dr = draws + 4 * r;
+    uint32_t pick = kSentinel;
+    bool done = false;
+    float p[C], q[C];
+    float outside_weight = z, outside = 1.0f;
+    const bool children = dr[0] != 0xff && z > 0.0f;
+    if (children) {
+      for (uint32_t i = 0; i < C; ++i) {
+        const float wi = ids[i] < vocab ? w[ids[i]] : 0.0f;
+        if (ids[i] < vocab) shard[ids[i] / kShard] = std::max(shard[ids[i] / kShard] - wi, 0.0f);
+        p[i] = wi / z;
+        q[i] = candidate_q[C * r + i];
+      }
+      outside_weight = 0.0f;
+      for (uint32_t s = 0; s < shards; ++s) outside_weight += shard[s];
+      outside = outside_weight / z;
+      for (uint32_t c = 0; c < 4 && !done; ++c) {
+        const uint32_t dc = dr[c];
+        if (dc >= C) break;
+        const float lhs = uniforms[16 + 4 * r + c] * q[dc];
+        near(lhs, p[dc], std::max(p[dc], q[dc]));
+        if (lhs < p[dc]) { pick = ids[dc], done = true; break; }
+        float residual = outside;
+        for (uint32_t i = 0; i < C; ++i) residual += std::max(p[i] - q[i], 0.0f);
+        if (!(residual > 0.0f)) break;
+        for (uint32_t i = 0; i < C; ++i) p[i] = std::max(p[i] - q[i], 0.0f) / residual;
+        outside /= residual;
+        q[dc] = 0.0f;
+        float rest = 0.0f;
+        for (uint32_t i = 0; i < C; ++i) rest += q[i];
+        for (uint32_t i = 0; rest > 0.0f && i < C; ++i) q[i] /= rest;
+      }
+    }
+    float target = uniforms[r] * z;
+    bool excluding = false;
+    if (children && !done) {
+      float inside = 0.0f;
+      for (uint32_t i = 0; i < C; ++i) inside += p[i];
+      const float point = uniforms[r] * (inside + outside);
+      float cumulative = 0.0f;
+      uint32_t last = C;
+      for (uint32_t i = 0; i < C && !(point < cumulative); ++i)
+        if (p[i] > 0.0f) {
+          last = i, cumulative += p[i];
+          near(point, cumulative, inside + outside);
+        }
+      if (last < C && (point < cumulative || !(outside > 0.0f))) pick = ids[last], done = true;
+      else excluding = true, target = (point - inside) / outside * outside_weight;
+    }
+    if (!done) {
+      auto excluded = [&](uint32_t v) {
+        if (!excluding) return false;
+        for (uint32_t i = 0; i < C; ++i)
+          if (ids[i] == v) return true;
+        return false;
+      };
+      float run = 0.0f, shard_target = 0.0f;
+      uint32_t at = kSentinel;
+      for (uint32_t s = 0; s < shards; ++s) {
+        if (!(shard[s] > 0.0f)) continue;
+        at = s, shard_target = target - run;
+        run += shard[s];
+        near(run, target, outside_weight);
+        if (run > target) break;
+      }
+      if (at != kSentinel) {
+        float loc = 0.0f;
+        for (uint32_t v = at * kShard; v < std::min(vocab, (at + 1) * kShard); ++v) {
+          const float wv = excluded(v) ? 0.0f : w[v];
+          if (wv > 0.0f) pick = v;
+          loc += wv;
+          if (wv > 0.0f) near(loc, shard_target, outside_weight);
+          if (wv > 0.0f && loc > shard_target) break;
+        }
+      }
+    }
+    selected[r] = pick;
+    if (decision_margin) decision_margin[r] = margin;
+  }
+}
+
 SO_API void so_sample_verify(const float *logits, uint32_t logit_stride, uint32_t vocab, uint32_t rows,
                              const uint32_t *input_tokens, float temperature, const float *uniforms,
                              uint32_t *selected, double *decision_margin) {

@@ -80,8 +80,10 @@ class QwenTarget {
   // `treeGiven`: the `tree` buffer holds the block's rows (a tree); otherwise the step writes a chain's there.
   // `keepPending` (only without `advance`): the lane's pending GDN rows stay as they are instead of being cleared, so
   // a held lane folds the same rows in every step (a steady-state timing loop).
+  // `draws`: sampled rows take their children from the `candidates` / `candidateQ` / `draws` buffers (the draft's
+  // candidates per row, their probabilities and the children it drew) instead of the next row's input token.
   void encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool treeGiven = false,
-                    bool keepPending = false);
+                    bool keepPending = false, bool draws = false);
 
   const SbTargetConfig &config() const { return cfg_; }   // the whole model
   const SbTargetConfig &local() const { return loc_; }    // this rank's heads and intermediate width (the vocabulary stays whole)
@@ -103,6 +105,7 @@ class QwenTarget {
   ops::SamplingPenalties penalties;
   Buffer penaltyWords;
   Buffer pendingPath;  // the row mask, in the previous step's tape, of the path it accepted (tree steps)
+  Buffer candidates, candidateQ, draws;  // per row: 16 draft candidates (u32), their draft probabilities (fp32), 4 drawn children (u8)
   Buffer tokens, uniforms, committed, pendingRows, results, selected, logits, hidden[2], tree, positions, invFreq, cosine, sine;
   uint32_t committedHost = 0;  // bound of the device's committed word, for extents and the attention plan
   uint32_t step = 0;
@@ -232,6 +235,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   pageTable_ = Buffer::allocate(size_t(pages) * 4);
   sampleWorkspace_ = Buffer::allocate(ops::Sampling::workspace(kVerifyRows, c.vocab));
   penaltyWords = Buffer::allocate(size_t(c.vocab) * 4);
+  candidates = Buffer::allocate(kVerifyRows * 16 * 4), candidateQ = Buffer::allocate(kVerifyRows * 16 * 4), draws = Buffer::allocate(kVerifyRows * 4);
   if (c.moe_experts) {
     moeScores_ = Buffer::allocate(size_t(kVerifyRows) * moe_.slots * 4);
     moeSelected_ = Buffer::allocate(size_t(kVerifyRows) * moe_.routes() * 4), moeWeights_ = Buffer::allocate(size_t(kVerifyRows) * moe_.routes() * 4);
@@ -254,7 +258,8 @@ inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) co
                                              {"logits", logits}, {"selected", selected}, {"results", results}, {"hidden", hidden[0]},
                                              {"hidden1", hidden[1]}, {"tokens", tokens}, {"uniforms", uniforms}, {"committed", committed},
                                              {"pending_rows", pendingRows}, {"tree", tree}, {"page_table", pageTable_}, {"inv_freq", invFreq},
-                                             {"positions", positions}, {"packed", packed_}, {"mixed", mixed_}, {"act", act_}, {"penalty_words", penaltyWords}};
+                                             {"positions", positions}, {"packed", packed_}, {"mixed", mixed_}, {"act", act_}, {"penalty_words", penaltyWords},
+                                             {"candidates", candidates}, {"candidate_q", candidateQ}, {"draws", draws}, {"pending_path", pendingPath}};
     auto it = g.find(name);
     if (it == g.end()) return false;
     out = it->second;
@@ -294,7 +299,7 @@ void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer 
 void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, const Buffer &pendingPath,
                    uint32_t advance, void *tpGroup, uint32_t exchanges);
 
-inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool treeGiven, bool keepPending) {
+inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool treeGiven, bool keepPending, bool drawsGiven) {
   using namespace ops;
   if (rows < 1 || rows > kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: 1 to 16 rows");
   if (committedHost + rows > cfg_.max_context + kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: past the context bound");
@@ -391,6 +396,9 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   SamplingBuffers sb;
   sb.logits = logits, sb.inputTokens = tokens, sb.uniforms = uniforms, sb.selected = selected, sb.workspace = sampleWorkspace_;
   sb.logitStride = c.vocab;
+  if (drawsGiven) sb.candidateIds = &candidates, sb.candidateQ = &candidateQ, sb.draws = &draws;
+  else if (treeGiven && temperature > 0.0f)
+    throw std::invalid_argument("QwenTarget::encodeVerify: a sampled tree block needs the draft's candidates and draws (SB_TARGET_DRAWS)");
   Sampling::addPenalties(graph, penalties, sb, penaltyWords, tree, rows, c.vocab);  // (nothing when the penalties are off)
   Sampling::addVerify(graph, SamplingPolicy{temperature}, sb, rows, c.vocab);
   AcceptanceBuffers ab;

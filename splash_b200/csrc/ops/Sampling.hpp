@@ -26,6 +26,10 @@ struct SamplingBuffers {
   Buffer selected;     // u32 [rows]
   Buffer workspace;
   uint32_t logitStride = 0;
+  // The children each row's draft drew (optional; runtime/metal/kernels/decode/sampling.metal:680-690 DrawChildren): per
+  // row 16 candidate ids (u32), the draft's probabilities of them (fp32) and up to 4 drawn candidate indices (u8, 0xff
+  // past them). Given, sampled rows select by recursive rejection sampling over these children.
+  const Buffer *candidateIds = nullptr, *candidateQ = nullptr, *draws = nullptr;
 };
 
 struct AcceptanceBuffers {
@@ -47,7 +51,14 @@ class Sampling {
     }
     SbSampleArgs a{b.logits.as<float>(), b.inputTokens.as<uint32_t>(), policy.temperature > 0.0f ? b.uniforms.as<float>() : nullptr,
                    b.selected.as<uint32_t>(), b.workspace ? b.workspace.as<float>() : nullptr, rows, vocabulary, b.logitStride,
-                   policy.temperature, policy.minP, policy.topK, policy.topP, nullptr};
+                   policy.temperature, policy.minP, policy.topK, policy.topP, nullptr, nullptr, nullptr, nullptr};
+    if (b.candidateIds && policy.temperature > 0.0f) {
+      if (!b.candidateQ || !b.draws) throw std::invalid_argument("Sampling::addVerify: candidates without their probabilities or draws");
+      requireBytes(*b.candidateIds, size_t(rows) * 16 * 4, "Sampling::addVerify candidate ids");
+      requireBytes(*b.candidateQ, size_t(rows) * 16 * 4, "Sampling::addVerify candidate probabilities");
+      requireBytes(*b.draws, size_t(rows) * 4, "Sampling::addVerify draws");
+      a.candidate_ids = b.candidateIds->as<uint32_t>(), a.candidate_q = b.candidateQ->as<float>(), a.draws = b.draws->as<uint8_t>();
+    }
     check(sb_sample_verify(graph.stream, &a));
     ++graph.launches;
   }

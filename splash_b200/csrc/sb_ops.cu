@@ -251,6 +251,7 @@ __global__ void kv_path_commit_kernel(SbKvLayer c, const uint32_t *page_table, u
 // ---- selection: one block of 1024 threads per row ----
 constexpr uint32_t kSentinel = 0xFFFFFFFFu;
 constexpr uint32_t kShard = 256;
+constexpr uint32_t kDrawCandidates = 16, kNoDraw = 0xff;  // a row's draft candidates; "no child drawn" (runtime/metal/abi/ExecutionGeometry.h:63)
 constexpr int kSampleThreads = 1024;
 
 __device__ __forceinline__ bool selectable(float x) { return !(isnan(x) || x == -INFINITY); }
@@ -449,7 +450,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SbSampleAr
   const float mx = s_max, inv_t = __fdiv_rn(1.0f, a.temperature);
   const uint32_t shards = (a.vocab + kShard - 1) / kShard;
   float *shard = a.workspace + size_t(r) * (2 * shards + 8), *shard2 = shard + shards;
-  const bool has_child = r + 1 < a.rows;
+  const bool has_child = !a.candidate_ids && r + 1 < a.rows;  // (with the draft's candidates given, the children are the rows' draws)
   const uint32_t child = has_child ? a.input_tokens[r + 1] : kSentinel;
   RowCut cut{0u, kSentinel};
   if (a.min_p > 0.0f || (a.top_k > 0 && a.top_k < a.vocab) || (a.top_p > 0.0f && a.top_p < 1.0f))
@@ -474,6 +475,90 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SbSampleAr
   if (tid != 0) return;
   float z = 0.0f;
   for (uint32_t s = 0; s < shards; ++s) z = __fadd_rn(z, shard[s]);
+  if (a.candidate_ids) {
+    // Recursive rejection sampling without replacement over the children the draft drew for this row
+    // (runtime/metal/kernels/decode/sampling.metal:693-885): child i of the row's kDrawCandidates candidates, of
+    // probability p_i under the target and q_i under the draft, is taken when u_i q_i < p_i; after a rejection the
+    // target becomes its residual max(p - q, 0), renormalised, and the draft loses the rejected child, renormalised; a
+    // row that takes none draws from the last residual, its candidates first, then the tokens outside them. A row
+    // without drawn children draws from its whole distribution.
+    const uint32_t *ids = a.candidate_ids + kDrawCandidates * r;
+    const float *cq = a.candidate_q + kDrawCandidates * r;
+    const uint8_t *draws = a.draws + 4 * r;
+    float target = __fmul_rn(a.uniforms[r], z);
+    bool excluding = false;
+    if (draws[0] != kNoDraw && z > 0.0f) {
+      float pc[kDrawCandidates], qc[kDrawCandidates];
+      for (uint32_t i = 0; i < kDrawCandidates; ++i) {
+        const uint32_t id = ids[i];
+        const float w = id < a.vocab ? weight(id) : 0.0f;
+        if (id < a.vocab) shard[id / kShard] = fmaxf(__fsub_rn(shard[id / kShard], w), 0.0f);  // the shards without the candidates
+        pc[i] = __fdiv_rn(w, z);
+        qc[i] = cq[i];
+      }
+      float outside_weight = 0.0f;
+      for (uint32_t s = 0; s < shards; ++s) outside_weight = __fadd_rn(outside_weight, shard[s]);
+      float outside = __fdiv_rn(outside_weight, z);
+      for (uint32_t c = 0; c < 4; ++c) {
+        const uint32_t dc = draws[c];
+        if (dc >= kDrawCandidates) break;
+        if (__fmul_rn(a.uniforms[16 + 4 * r + c], qc[dc]) < pc[dc]) {
+          a.selected[r] = ids[dc];
+          return;
+        }
+        float residual = outside;
+        for (uint32_t i = 0; i < kDrawCandidates; ++i) residual = __fadd_rn(residual, fmaxf(__fsub_rn(pc[i], qc[i]), 0.0f));
+        if (!(residual > 0.0f)) break;
+        for (uint32_t i = 0; i < kDrawCandidates; ++i) pc[i] = __fdiv_rn(fmaxf(__fsub_rn(pc[i], qc[i]), 0.0f), residual);
+        outside = __fdiv_rn(outside, residual);
+        qc[dc] = 0.0f;
+        float rest = 0.0f;
+        for (uint32_t i = 0; i < kDrawCandidates; ++i) rest = __fadd_rn(rest, qc[i]);
+        for (uint32_t i = 0; rest > 0.0f && i < kDrawCandidates; ++i) qc[i] = __fdiv_rn(qc[i], rest);
+      }
+      float inside = 0.0f;
+      for (uint32_t i = 0; i < kDrawCandidates; ++i) inside = __fadd_rn(inside, pc[i]);
+      const float point = __fmul_rn(a.uniforms[r], __fadd_rn(inside, outside));
+      float cumulative = 0.0f;
+      uint32_t last = kDrawCandidates;
+      for (uint32_t i = 0; i < kDrawCandidates && !(point < cumulative); ++i)
+        if (pc[i] > 0.0f) last = i, cumulative = __fadd_rn(cumulative, pc[i]);
+      if (last < kDrawCandidates && (point < cumulative || !(outside > 0.0f))) {
+        a.selected[r] = ids[last];
+        return;
+      }
+      excluding = true;
+      target = __fmul_rn(__fdiv_rn(__fsub_rn(point, inside), outside), outside_weight);
+    }
+    // By the target's own weights (outside the candidates after rejections): the shard the point falls in (the last one
+    // with weight if rounding leaves it unreached), then its ids in order.
+    auto excluded = [&](uint32_t v) {
+      bool e = false;
+      for (uint32_t i = 0; excluding && i < kDrawCandidates; ++i) e = e || ids[i] == v;
+      return e;
+    };
+    float run = 0.0f, shard_target = 0.0f;
+    uint32_t at = kSentinel;
+    for (uint32_t s = 0; s < shards; ++s) {
+      if (!(shard[s] > 0.0f)) continue;
+      at = s, shard_target = __fsub_rn(target, run);
+      run = __fadd_rn(run, shard[s]);
+      if (run > target) break;
+    }
+    uint32_t pick = kSentinel;
+    if (at != kSentinel) {
+      float loc = 0.0f;
+      const uint32_t end = min(a.vocab, (at + 1) * kShard);
+      for (uint32_t v = at * kShard; v < end; ++v) {
+        const float w = excluded(v) ? 0.0f : weight(v);
+        if (w > 0.0f) pick = v;  // the last id weighed so far: where the walk ends if rounding leaves the target unreached
+        loc = __fadd_rn(loc, w);
+        if (w > 0.0f && loc > shard_target) break;
+      }
+    }
+    a.selected[r] = pick;
+    return;
+  }
   bool drop = false;
   if (has_child && child < a.vocab) {
     const float u = a.uniforms[16 + 4 * r];
@@ -751,6 +836,7 @@ int sb_sample_verify(void *stream, const SbSampleArgs *a) {
   SB_REQUIRE(a->min_p >= 0.0f && a->min_p <= 1.0f && a->top_p >= 0.0f, "sb_sample_verify: min_p %g outside 0..1 or negative top_p", double(a->min_p));
   const bool filtered = a->min_p > 0.0f || (a->top_k > 0 && a->top_k < a->vocab) || (a->top_p > 0.0f && a->top_p < 1.0f);
   SB_REQUIRE(!filtered || a->vocab <= kMaxFilterShards * kShard, "sb_sample_verify: min-p / top-k / top-p support vocabularies up to %u", kMaxFilterShards * kShard);
+  SB_REQUIRE(!a->candidate_ids || (a->candidate_q && a->draws), "sb_sample_verify: candidates come with their draft probabilities and the rows' draws");
   return launch(sample_kernel, dim3(a->rows), dim3(kSampleThreads), as_stream(stream), *a);
 }
 

@@ -340,7 +340,7 @@ int sb_target_randomize(void *target, uint64_t seed, uint32_t committed) {
 static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float temperature, uint32_t flags) {
   QwenTarget &m = *t->model;
   const bool advance = (flags & SB_TARGET_ADVANCE) != 0, tree = (flags & SB_TARGET_TREE) != 0;
-  const bool keep = !advance && (flags & SB_TARGET_KEEP_PENDING) != 0;
+  const bool keep = !advance && (flags & SB_TARGET_KEEP_PENDING) != 0, draws = (flags & SB_TARGET_DRAWS) != 0;
   const uint32_t parity = m.step & 1;
   return guarded([&] {
     if (flags & SB_TARGET_GRAPH) {
@@ -349,7 +349,7 @@ static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float tempera
       const uint32_t bound = std::min(m.config().max_context, (m.committedHost / 1024 + 2) * 1024);
       uint32_t tbits;
       memcpy(&tbits, &temperature, 4);
-      const auto key = std::make_tuple(rows, tbits, parity, uint32_t(advance) | (uint32_t(tree) << 1) | (uint32_t(keep) << 2), bound);
+      const auto key = std::make_tuple(rows, tbits, parity, uint32_t(advance) | (uint32_t(tree) << 1) | (uint32_t(keep) << 2) | (uint32_t(draws) << 3), bound);
       auto it = t->graphs.find(key);
       if (it == t->graphs.end()) {
         const uint32_t saved = m.committedHost;
@@ -358,7 +358,7 @@ static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float tempera
         SB_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
         int status = SB_OK;
         try {
-          m.encodeVerify(g, rows, temperature, parity, advance, tree, keep);
+          m.encodeVerify(g, rows, temperature, parity, advance, tree, keep, draws);
         } catch (...) {
           cudaGraph_t dead = nullptr;
           cudaStreamEndCapture(stream, &dead);
@@ -380,7 +380,7 @@ static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float tempera
       SB_CUDA(cudaGraphLaunch(it->second, stream));
     } else {
       CommandGraph g{stream, ctx().pdl, 0};
-      m.encodeVerify(g, rows, temperature, parity, advance, tree, keep);
+      m.encodeVerify(g, rows, temperature, parity, advance, tree, keep, draws);
       t->launches = g.launches;
     }
     ++m.step;

@@ -214,7 +214,8 @@ class SbGdnArgs(ctypes.Structure):
 class SbSampleArgs(ctypes.Structure):
     _fields_ = [("logits", _P), ("input_tokens", _P), ("uniforms", _P), ("selected", _P), ("workspace", _P),
                 ("rows", _U), ("vocab", _U), ("logit_stride", _U), ("temperature", _F),
-                ("min_p", _F), ("top_k", _U), ("top_p", _F), ("cut_out", _P)]
+                ("min_p", _F), ("top_k", _U), ("top_p", _F), ("cut_out", _P),
+                ("candidate_ids", _P), ("candidate_q", _P), ("draws", _P)]
 
 
 class SbPenaltyArgs(ctypes.Structure):

@@ -161,7 +161,9 @@ def test_linear_rejects_bad_arguments():
     with pytest.raises(lib.SbError):
         lib.linear(1 << 20, 1 << 20, 1 << 20, 0, 64, 1000, 16)  # k not whole super-blocks
     with pytest.raises(lib.SbError):
-        lib.linear(1 << 20, 1 << 20, 1 << 20, 0, 64, 1024, 17)  # too many rows
+        lib.linear(1 << 20, 1 << 20, 1 << 20, 0, 64, 1024, 0)  # no rows
+    with pytest.raises(lib.SbError):
+        lib.linear(1 << 20, 1 << 20, 1 << 20, 4, 64, 1024, 17)  # more than 16 rows go to the many-row kernel, which multiplies Q4_K only
     with pytest.raises(lib.SbError):
         lib.linear(1 << 20, 1 << 20, 1 << 20, 3, 64, 1024, 16)  # unsupported format
 

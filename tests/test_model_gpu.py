@@ -145,6 +145,58 @@ def test_tiny_model_tree_steps_match_oracle(flags_name):
     assert compared >= 2
 
 
+def test_tiny_model_sampled_tree_steps_with_drafted_children_match_oracle():
+    """Sampled acceptance on tree blocks: every row's children are draws of a (synthetic) draft over its 16 candidates, with
+    the draft's probabilities; the step selects by recursive rejection sampling over those children (SB_TARGET_DRAWS) and
+    acceptance follows the child that was selected. Whole steps against the oracle's, over several seeds; a sampled tree
+    block without the draws is refused."""
+    lib, target, t, cfg, w, s = build(seed=6)
+    parent = [0, 0, 0, 1, 1, 2, 3, 3, 5, 6, 6, 8, 9, 11, 12, 13]
+    tree = _tree(parent)
+    rows, V = 16, cfg["vocab"]
+    compared = accepted_total = 0
+    for seed in range(8):
+        t.reset(2048)
+        s["committed"], s["pending_rows"], s["pending_path"] = 2048, 0, 0
+        rng = np.random.default_rng(200 + seed)
+        ids = np.stack([rng.choice(V, 16, replace=False) for _ in range(rows)]).astype(np.uint32)
+        q = rng.dirichlet(np.ones(16) * 0.5, size=rows).astype(np.float32)
+        draws = np.full((rows, 4), 255, np.uint8)
+        tokens = np.zeros(rows, np.uint32)
+        tokens[0] = 50 + seed
+        # a first pass with placeholder children gives the target's own favourites, which the draft then lists first
+        for r in range(rows):
+            children = [c for c in range(1, rows) if parent[c] == r]
+            order = rng.choice(16, size=len(children), replace=False, p=q[r].astype(np.float64) / q[r].astype(np.float64).sum())
+            draws[r, :len(children)] = order
+            for c, d in zip(children, order):
+                tokens[c] = ids[r, d]
+        plain = mo.verify_step(cfg, w, s, tokens, mutate=False, tree=tree)
+        for r in range(rows):                                  # make the draft good: its first-drawn child is the target's argmax
+            children = [c for c in range(1, rows) if parent[c] == r]
+            if children and rng.random() < 0.8:
+                ids[r, draws[r, 0]] = plain["selected"][r]
+                tokens[children[0]] = plain["selected"][r]
+                q[r, draws[r, 0]] = 0.3
+        uniforms = rng.random(80).astype(np.float32)
+        want = mo.verify_step(cfg, w, s, tokens, temperature=0.7, uniforms=uniforms, mutate=False, tree=tree, draws=(ids, q, draws))
+        t.upload(-1, "candidates", ids)
+        t.upload(-1, "candidate_q", q)
+        t.upload(-1, "draws", draws)
+        got_tokens, retained, accepted, mask = t.verify(tokens, uniforms=uniforms, temperature=0.7, flags=target.DRAWS, tree=tree)
+        assert lib.device_status() == 0
+        path_rows = [r for r in range(rows) if want["mask"] >> r & 1]
+        if not (want["margin"][path_rows] > 1e-3).all():
+            continue
+        compared += 1
+        accepted_total += want["accepted"]
+        assert (retained, accepted, mask) == (want["retained"], want["accepted"], want["mask"]), seed
+        assert np.array_equal(got_tokens, want["tokens"]), seed
+    assert compared >= 5 and accepted_total >= 2
+    with pytest.raises(lib.SbError):
+        t.verify(tokens, uniforms=uniforms, temperature=0.7, tree=tree)     # a sampled tree block needs the draws
+
+
 def test_tiny_model_step_with_sampling_penalties_matches_oracle():
     """The lane's penalties rewrite the step's logits before selection: a strong repetition and frequency penalty on the
     tokens the target would otherwise choose changes the selections, the same way in the oracle's step."""

@@ -465,6 +465,51 @@ def test_stochastic_selection_with_supplied_uniforms():
     assert np.array_equal(got[clear], want[clear])
 
 
+def test_recursive_rejection_over_drafted_children_matches_the_oracle():
+    """Sampled rows with the draft's candidates, probabilities and up to four drawn children a row: the kernel's recursive
+    rejection sampling against the oracle's, exact wherever no test sat within rounding of its threshold; with and without
+    an end of the distribution (top-k / top-p)."""
+    import ctypes as ct
+    lib, l, o = _setup()
+    o.so_sample_verify_draws.argtypes = ([ct.c_void_p, ct.c_uint32, ct.c_uint32, ct.c_uint32, ct.c_float, ct.c_float, ct.c_uint32, ct.c_float] +
+                                         [ct.c_void_p] * 6)
+    rows, vocab, T = 16, 32000, 0.7
+    total_clear = taken = 0
+    for seed, (min_p, top_k, top_p) in enumerate([(0.0, 0, 1.0), (0.0, 50, 0.9), (0.02, 0, 1.0)]):
+        rng = np.random.default_rng(40 + seed)
+        logits = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
+        draft = logits + (rng.standard_normal((rows, vocab)) * 1.5).astype(np.float32)
+        ids = np.argsort(-draft, axis=1)[:, :16].astype(np.uint32).copy()
+        dq = np.exp((np.take_along_axis(draft, ids.astype(np.int64), 1) - draft.max(axis=1, keepdims=True)) / T)
+        q = (dq / dq.sum(axis=1, keepdims=True)).astype(np.float32)
+        draws = np.full((rows, 4), 255, np.uint8)
+        for r in range(rows):
+            n = int(rng.integers(0, 5))                      # 0 .. 4 children, drawn without replacement from q
+            if n:
+                draws[r, :n] = rng.choice(16, size=n, replace=False, p=q[r].astype(np.float64) / q[r].astype(np.float64).sum())
+        ids[3, 12:] = 0xFFFFFFFF                              # a draft that listed fewer candidates
+        q[3, 12:] = 0
+        draws[3] = [1, 0, 255, 255]
+        uniforms = rng.random(80).astype(np.float32)
+        want, margin = np.zeros(rows, np.uint32), np.zeros(rows, np.float64)
+        o.so_sample_verify_draws(P(logits), vocab, vocab, rows, T, min_p, top_k, top_p, P(uniforms), P(ids), P(q), P(draws), P(want), P(margin))
+        up = lib.DeviceBuffer.from_numpy
+        ld, ud, cd, qd, dd = up(logits), up(uniforms), up(ids), up(q), up(draws)
+        inp = up(np.zeros(rows, np.uint32))
+        sd = lib.DeviceBuffer(rows * 4)
+        wd = lib.DeviceBuffer(int(l.sb_sample_workspace_bytes(rows, vocab)))
+        sa = lib.SbSampleArgs(ld.ptr, inp.ptr, ud.ptr, sd.ptr, wd.ptr, rows, vocab, vocab, T, min_p, top_k, top_p, None, cd.ptr, qd.ptr, dd.ptr)
+        lib.check(l.sb_sample_verify(None, ctypes.byref(sa)))
+        got = sd.to_numpy(np.uint32, (rows,))
+        assert lib.device_status() == 0
+        clear = margin > 1e-5
+        assert clear.sum() >= rows - 3
+        assert np.array_equal(got[clear], want[clear]), (seed, got, want)
+        total_clear += int(clear.sum())
+        taken += sum(int(want[r]) in ids[r, draws[r][draws[r] < 16]].tolist() for r in range(rows))
+    assert total_clear >= 40 and taken >= 5    # children were taken in a fair share of the rows
+
+
 @pytest.mark.parametrize("min_p,top_k,top_p", [(0.05, 0, 1.0), (0.0, 40, 1.0), (0.0, 0, 0.9), (0.02, 50, 0.8), (0.0, 1, 1.0)])
 def test_filtered_selection_matches_the_oracle(min_p, top_k, top_p):
     """min-p, top-k and top-p ends of the distribution and the selections under them."""

@@ -305,3 +305,63 @@ def test_moe_route_is_a_stable_top_k_with_softmax_weights():
             assert sel[r, top_k] == experts
             assert np.isclose(wts[r, top_k], 1 / (1 + np.exp(-float(ol.bf2f(x[r]).astype(np.float64) @ gate))), rtol=1e-5)
         assert sel[3, :3].tolist() == [5, 10, 200]
+
+
+def _draws_setup(o):
+    import ctypes
+    o.so_sample_verify_draws.argtypes = ([ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_float, ctypes.c_float,
+                                          ctypes.c_uint32, ctypes.c_float] + [ctypes.c_void_p] * 6)
+    return o
+
+
+def test_recursive_rejection_sampling_draws_from_the_target_distribution():
+    """The property the reference states for its sampled verify rows (runtime/metal/abi/Sampling.h:17-28): whatever the
+    children the draft drew and whatever its probabilities q, a row's selection is a draw from the target's distribution.
+    60,000 rows with fresh uniforms and fresh draws (up to 3 children drawn without replacement from q over the 16
+    candidates): the selections' frequencies match softmax(logits / T) within five standard deviations."""
+    o = _draws_setup(ol.bind_ops(ol.load()))
+    rng = np.random.default_rng(0)
+    vocab, T, N = 600, 0.7, 60000
+    logits = (rng.standard_normal((1, vocab)) * 2).astype(np.float32)
+    w = np.exp((logits[0].astype(np.float64) - logits[0].max()) / T)
+    p = w / w.sum()
+    draft = logits[0] + rng.standard_normal(vocab).astype(np.float32)          # a draft that disagrees with the target
+    ids = np.argsort(-draft)[:16].astype(np.uint32)[None, :].copy()
+    q = rng.dirichlet(np.ones(16)).astype(np.float32)[None, :]
+    counts = np.zeros(vocab)
+    sel = np.zeros(1, np.uint32)
+    taken_child = 0
+    for t in range(N):
+        u = rng.random(80).astype(np.float32)
+        order = rng.choice(16, size=3, replace=False, p=q[0].astype(np.float64) / q[0].astype(np.float64).sum())
+        draws = np.full((1, 4), 255, np.uint8)
+        draws[0, :3] = order
+        o.so_sample_verify_draws(P(logits), vocab, vocab, 1, T, 0.0, 0, 1.0, P(u), P(ids), P(q), P(draws), P(sel), None)
+        counts[sel[0]] += 1
+        taken_child += int(sel[0]) in ids[0, order].tolist()
+    emp = counts / N
+    sigma = np.sqrt(np.maximum(p * (1 - p), 1e-12) / N)
+    assert (np.abs(emp - p) <= 5 * sigma + 1e-4).all()
+    assert 0.1 * N < taken_child < 0.95 * N        # children were taken often, and rejected often
+
+
+def test_rejection_sampling_with_one_certain_child_is_the_chain_rule():
+    """One candidate drawn with q = 1 is the chain from a deterministic draft: the row keeps the child iff u < p(child) and
+    otherwise draws from the distribution without it, which is what so_sample_verify does with the next row's token."""
+    o = _draws_setup(ol.bind_ops(ol.load()))
+    rng = np.random.default_rng(3)
+    rows, vocab, T = 16, 3000, 0.7
+    logits = (rng.standard_normal((rows, vocab)) * 3).astype(np.float32)
+    inputs = np.zeros(rows, np.uint32)
+    inputs[1:] = [int(logits[r].argmax()) if rng.random() < 0.7 else int(rng.integers(0, vocab)) for r in range(rows - 1)]
+    uniforms = rng.random(80).astype(np.float32)
+    chain, m1 = np.zeros(rows, np.uint32), np.zeros(rows, np.float64)
+    o.so_sample_verify(P(logits), vocab, vocab, rows, P(inputs), T, P(uniforms), P(chain), P(m1))
+    ids = np.full((rows, 16), 0xFFFFFFFF, np.uint32)
+    q = np.zeros((rows, 16), np.float32)
+    draws = np.full((rows, 4), 255, np.uint8)
+    ids[:-1, 0], q[:-1, 0], draws[:-1, 0] = inputs[1:], 1.0, 0
+    got, m2 = np.zeros(rows, np.uint32), np.zeros(rows, np.float64)
+    o.so_sample_verify_draws(P(logits), vocab, vocab, rows, T, 0.0, 0, 1.0, P(uniforms), P(ids), P(q), P(draws), P(got), P(m2))
+    clear = (m1 > 1e-5) & (m2 > 1e-5)
+    assert clear.sum() >= rows - 3 and np.array_equal(got[clear], chain[clear])
