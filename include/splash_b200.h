@@ -243,6 +243,15 @@ SB_API int sb_rope_tables(void *stream, const uint32_t *positions_dev, uint32_t 
 SB_API int sb_linear_f32(void *stream, const float *w_dev, const void *x, uint32_t rows, uint32_t n, uint32_t k,
                          uint32_t x_stride, void *out, uint32_t out_stride, uint32_t out_f32, const void *norm_weight);
 
+/* ---- steps of several lanes ----
+ * A step may carry several lanes (concurrent requests), each with its own block of rows (the reference's StepRows /
+ * SplashLaneRows, runtime/ops/LaneRows.hpp:36-62, runtime/metal/abi/VerifyTree.h:38-45). Here a lane has 16 row slots: lane l's
+ * rows are rows 16 l .. 16 l + rows - 1 of every row-indexed buffer (packed rows, queries, tokens, tree rows, logits, outputs),
+ * its uniforms the 80 from 80 l on, its results the 4 words from 4 l on, and every per-lane state buffer (positions, page
+ * tables, GDN cells and tapes, penalty tables) is an array over the lanes of the one-lane buffer. The operators below take
+ * `lanes` (0 or 1: one lane, the layout above with l = 0) and spread the lanes over their grids; `rows` stays the rows of
+ * one lane. The projections see the step's rows as one matrix of 16 x lanes rows (sb_linear / sb_linear_wide). */
+
 /* ---- INT8 paged KV attention ---- */
 
 /* One attention layer's cache: pages of page_tokens tokens; keys and values token-major
@@ -265,8 +274,11 @@ typedef struct SbAttnStoreArgs {
   const uint32_t *page_table; /* device u32 physical page per logical page */
   void *queries;            /* bf16 [rows, q_heads, head_dim] */
   SbKvLayer cache;
-  const uint32_t *committed_dev; /* optional device word overriding `committed`, so a captured graph follows the lane */
+  const uint32_t *committed_dev; /* optional device word overriding `committed`, so a captured graph follows the lane;
+                                    with lanes: one word per lane (required) */
   uint32_t rows, q_heads, gated, pairs, qkv_stride, committed;
+  uint32_t lanes;             /* 0 or 1: one lane */
+  uint32_t page_table_stride; /* entries between consecutive lanes' page tables */
 } SbAttnStoreArgs;
 SB_API int sb_attn_store(void *stream, const SbAttnStoreArgs *args);
 
@@ -283,8 +295,11 @@ typedef struct SbAttnArgs {
   const void *tree;         /* optional device SplashTreeRow[rows] */
   void *out;                /* bf16 [rows, out_stride] = [row][q_head][dim] */
   SbKvLayer cache;
-  const uint32_t *committed_dev; /* optional device word; `committed` is then the bound the split plan is made for */
+  const uint32_t *committed_dev; /* optional device word; `committed` is then the bound the split plan is made for; with lanes:
+                                    one word per lane (required), `committed` the largest */
   uint32_t rows, q_heads, gated, qkv_stride, out_stride, committed;
+  uint32_t lanes;             /* 0 or 1: one lane; else the lanes share the launch (fewer splits a lane) */
+  uint32_t page_table_stride; /* entries between consecutive lanes' page tables */
 } SbAttnArgs;
 SB_API int sb_attn_verify(void *stream, const SbAttnArgs *args);
 
@@ -346,6 +361,10 @@ typedef struct SbGdnArgs {
   const uint32_t *pending_path_dev;
   uint32_t pending_path;
   uint32_t flags;           /* SB_GDN_* */
+  uint32_t lanes;           /* 0 or 1: one lane. Else state_in / state_out, the carried convolution rows and both tapes are arrays
+                               over the lanes, pending_rows_dev / pending_path_dev one word per lane (the host values
+                               pending_rows / pending_path then apply to every lane), the rows of lane l at 16 l */
+  uint32_t reserved;
 } SbGdnArgs;
 enum {
   SB_GDN_STATE_SETTLED = 1 /* the caller vouches that no launch still running on the stream writes state_in, so the kernel
@@ -405,6 +424,8 @@ typedef struct SbSampleArgs {
   const uint32_t *candidate_ids; /* device u32 [rows, 16] or NULL */
   const float *candidate_q;      /* device fp32 [rows, 16] */
   const uint8_t *draws;          /* device u8 [rows, 4] */
+  uint32_t lanes;                /* 0 or 1: one lane */
+  uint32_t reserved;
 } SbSampleArgs;
 /* The sampling penalties of one lane's rows, in place, before selection: a token the prompt or the output holds has a
  * positive logit divided and a negative one multiplied by `repetition`; a token the output holds `count` times is
@@ -420,6 +441,8 @@ typedef struct SbPenaltyArgs {
   const void *tree;             /* device SplashTreeRow[rows] */
   uint32_t rows, vocab, logit_stride;
   float repetition, presence, frequency;
+  uint32_t lanes;               /* 0 or 1: one lane; else `words` is [lanes][vocab] */
+  uint32_t reserved;
 } SbPenaltyArgs;
 SB_API int sb_sample_penalize(void *stream, const SbPenaltyArgs *args);
 
@@ -438,6 +461,7 @@ typedef struct SbAcceptArgs {
   uint32_t *results;            /* device u32 [4] */
   const uint32_t *stop_tokens;  /* device u32 [n_stop] or NULL */
   uint32_t rows, remaining, n_stop;
+  uint32_t lanes;               /* 0 or 1: one lane; else results is [lanes][4] */
 } SbAcceptArgs;
 SB_API int sb_accept(void *stream, const SbAcceptArgs *args);
 
@@ -448,7 +472,7 @@ SB_API int sb_accept(void *stream, const SbAcceptArgs *args);
  * layer l a full-attention layer iff (l + 1) % attention_interval == 0 (runtime/model/QwenHybridLayout.hpp:132-135),
  * else Gated DeltaNet; dense SwiGLU FFN; final norm and the vocabulary projection into fp32 logits of every row;
  * selection, acceptance, and the lane's commit (committed tokens and the GDN tape's accepted rows stay on the device).
- * One lane (batch 1) per target. */
+ * One lane (batch 1) per target, or SbTargetConfig.lanes of them stepped together. */
 typedef struct SbTargetConfig {
   uint32_t layers, hidden, vocab, intermediate;
   uint32_t q_heads, kv_heads, head_dim, rotary_pairs;
@@ -466,7 +490,12 @@ typedef struct SbTargetConfig {
    * gated by a scalar per row; tensors ffn_router (fp32 [experts, hidden]), ffn_shared_gate (fp32 [hidden]),
    * ffn_gate_exps / ffn_up_exps ([experts + 1][moe_intermediate][hidden] rows of fmt_proj, the shared expert last),
    * ffn_down_exps ([experts + 1][hidden][moe_intermediate]). `intermediate` is then unused. Not with tensor parallelism. */
-  uint32_t moe_experts, moe_top_k, moe_intermediate, reserved;
+  uint32_t moe_experts, moe_top_k, moe_intermediate;
+  /* Concurrent requests stepped together (0 or 1: one lane; up to 32): every per-lane buffer of the target becomes an array
+   * over the lanes ("steps of several lanes" above), a layer's KV pool holds the lanes' pages one lane after the other, and
+   * a step multiplies 16 x lanes rows on the many-row projection kernel, which needs Q4_K projections (fmt_proj, fmt_down,
+   * fmt_head). Dense models on one GPU; chain blocks. */
+  uint32_t lanes;
 } SbTargetConfig;
 
 enum {
@@ -588,8 +617,10 @@ SB_API int sb_target_tensor(void *target, int layer, const char *name, void **ou
 SB_API int sb_target_set_penalties(void *target, float repetition, float presence, float frequency);
 /* Seeded synthetic weights, a prefilled INT8 cache of `committed` tokens and random GDN state, written on the device. */
 SB_API int sb_target_randomize(void *target, uint64_t seed, uint32_t committed);
-/* Sets the lane's position and clears the pending GDN rows. */
+/* Sets the lane's position (every lane's, with several) and clears the pending GDN rows. */
 SB_API int sb_target_reset(void *target, uint32_t committed);
+/* The same with a position per lane: committed_host holds SbTargetConfig.lanes words. */
+SB_API int sb_target_reset_lanes(void *target, const uint32_t *committed_host);
 /* One verify step over inputs already on the device (`tokens`, `uniforms` buffers of the target). */
 SB_API int sb_target_step(void *target, void *stream, uint32_t rows, float temperature, uint32_t flags);
 /* One verify step from host buffers: uploads the block's input tokens (row 0 the last accepted token, rows 1.. the
@@ -597,6 +628,11 @@ SB_API int sb_target_step(void *target, void *stream, uint32_t rows, float tempe
  * and waits. */
 SB_API int sb_target_verify(void *target, void *stream, const uint32_t *tokens_host, const float *uniforms_host, uint32_t rows,
                             float temperature, uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host);
+/* sb_target_verify for a target of several lanes: tokens_host u32 [lanes][16] (a lane's block in its 16 slots, rows of them used),
+ * uniforms_host fp32 [lanes][80] or NULL, out_tokens_host u32 [lanes][16] (a lane's retained tokens first), out_results_host
+ * u32 [lanes][4] = {retained, accepted, retained_rows, 0} per lane. Chain blocks. */
+SB_API int sb_target_verify_lanes(void *target, void *stream, const uint32_t *tokens_host, const float *uniforms_host, uint32_t rows,
+                                  float temperature, uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host);
 /* sb_target_verify for a tree of draft tokens: tree_host holds `rows` SplashTreeRow entries {ancestors u32, parent u16,
  * depth u16}; sets SB_TARGET_TREE. out_tokens_host receives the accepted path's tokens. */
 SB_API int sb_target_verify_tree(void *target, void *stream, const uint32_t *tokens_host, const void *tree_host, const float *uniforms_host,

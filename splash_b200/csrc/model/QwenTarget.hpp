@@ -107,8 +107,10 @@ class QwenTarget {
   Buffer pendingPath;  // the row mask, in the previous step's tape, of the path it accepted (tree steps)
   Buffer candidates, candidateQ, draws;  // per row: 16 draft candidates (u32), their draft probabilities (fp32), 4 drawn children (u8)
   Buffer tokens, uniforms, committed, pendingRows, results, selected, logits, hidden[2], tree, positions, invFreq, cosine, sine;
-  uint32_t committedHost = 0;  // bound of the device's committed word, for extents and the attention plan
+  uint32_t committedHost = 0;  // bound of the device's committed word(s), for extents and the attention plan
   uint32_t step = 0;
+  uint32_t lanes() const { return lanes_; }
+  uint32_t pagesPerLane() const { return pagesPerLane_; }
 
  private:
   ops::QuantizedSegment segment(uint32_t n, uint32_t k, uint32_t format);
@@ -129,6 +131,9 @@ class QwenTarget {
   Buffer partials_;  // fp32 [kMaxPartialSlices][16][hidden]: k-slice sums of out_proj / down awaiting their consumer
   static constexpr uint32_t kMaxPartialSlices = 16;
   uint32_t packedStride_ = 0;
+  uint32_t lanes_ = 1, pagesPerLane_ = 0;
+  Buffer widePrepared_[2];  // conversions for the many-row projection kernel (steps of several lanes)
+  void encodeVerifyLanes(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool keepPending, bool drawsGiven);
   uint64_t weightBytes_ = 0, moeExpertBytes_ = 0;
   uint32_t moeLayers_ = 0;
 };
@@ -148,6 +153,15 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   loc_.q_heads = share_.q_heads, loc_.kv_heads = share_.kv_heads, loc_.gdn_key_heads = share_.gdn_key_heads;
   loc_.gdn_value_heads = share_.gdn_value_heads, loc_.intermediate = share_.intermediate;
   const SbTargetConfig &c = loc_;
+  lanes_ = std::max(1u, whole.lanes);
+  const uint32_t L = lanes_;
+  if (L > 32) throw std::invalid_argument("QwenTarget: " + std::to_string(L) + " lanes (up to 32)");
+  if (L > 1) {
+    // A step of several lanes multiplies 16 x lanes rows: the many-row projection kernel, which takes Q4_K rows.
+    if (whole.tp_world > 1 || whole.moe_experts) throw std::invalid_argument("QwenTarget: several lanes are offered for dense models on one GPU");
+    if (whole.fmt_proj != SB_FMT_Q4K || whole.fmt_down != SB_FMT_Q4K || whole.fmt_head != SB_FMT_Q4K)
+      throw std::invalid_argument("QwenTarget: several lanes need Q4_K projections (fmt_proj, fmt_down, fmt_head)");
+  }
   if (whole.tp_world > 1) tp_ = std::make_unique<ops::TensorParallel>(whole.tp_world, whole.tp_rank, whole.hidden, whole.vocab);
   if (!c.layers || !c.hidden || !c.vocab || !c.intermediate || !c.attention_interval)
     throw std::invalid_argument("QwenTarget: empty configuration");
@@ -165,7 +179,8 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   const uint32_t H = c.hidden, D = c.head_dim;
   const uint32_t attnIn = c.q_heads * (c.gated_attention ? 2 * D : D) + 2 * c.kv_heads * D;
   const uint32_t gdnIn = gdn_.convolutionWidth() + gdn_.valueWidth();
-  const uint32_t pages = (c.max_context + kVerifyRows + c.page_tokens - 1) / c.page_tokens;
+  pagesPerLane_ = (c.max_context + kVerifyRows + c.page_tokens - 1) / c.page_tokens;
+  const uint32_t pages = pagesPerLane_ * L;  // a layer's pool: the lanes' pages one lane after the other
   layers_.resize(c.layers);
   for (uint32_t l = 0; l < c.layers; ++l) {
     LayerWeights &w = layers_[l];
@@ -189,10 +204,10 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
       weightBytes_ += size_t(2) * gdn_.valueHeads * H * 4;
       w.ssmConv = Buffer::allocate(size_t(gdn_.convolutionWidth()) * 4 * 2);
       w.ssmA = floats(gdn_.valueHeads), w.ssmDtBias = Buffer::allocate(gdn_.valueHeads * 2), w.ssmNorm = floats(128);
-      for (int i = 0; i < 2; ++i) {
-        w.cells[i].state = Buffer::allocate(gdn_.stateBytes());
-        w.cells[i].convolution = Buffer::allocate(gdn_.convolutionStateBytes());
-        w.tapes[i] = ops::GdnTape::allocate(gdn_, kVerifyRows);
+      for (int i = 0; i < 2; ++i) {  // (arrays over the lanes)
+        w.cells[i].state = Buffer::allocate(gdn_.stateBytes() * L);
+        w.cells[i].convolution = Buffer::allocate(gdn_.convolutionStateBytes() * L);
+        w.tapes[i] = ops::GdnTape::allocate(gdn_, kVerifyRows * L);
       }
     }
     if (c.moe_experts) {
@@ -215,27 +230,30 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   output_ = segment(share_.vocab, H, c.fmt_head);
 
   packedStride_ = std::max(attnIn, gdnIn);
-  packed_ = Buffer::allocate(size_t(kVerifyRows) * packedStride_ * 2);
-  gates_ = Buffer::allocate(size_t(kVerifyRows) * 2 * std::max(1u, gdn_.valueHeads) * 2);
-  mixed_ = Buffer::allocate(size_t(kVerifyRows) * std::max(gdn_.valueWidth(), c.q_heads * D) * 2);
-  queries_ = Buffer::allocate(size_t(kVerifyRows) * c.q_heads * D * 2);
-  act_ = Buffer::allocate(size_t(kVerifyRows) * c.intermediate * 2);
-  normed_ = Buffer::allocate(size_t(kVerifyRows) * H * 2);
+  const size_t R = size_t(kVerifyRows) * L;  // row slots of a step
+  packed_ = Buffer::allocate(R * packedStride_ * 2);
+  gates_ = Buffer::allocate(R * 2 * std::max(1u, gdn_.valueHeads) * 2);
+  mixed_ = Buffer::allocate(R * std::max(gdn_.valueWidth(), c.q_heads * D) * 2);
+  queries_ = Buffer::allocate(R * c.q_heads * D * 2);
+  act_ = Buffer::allocate(R * c.intermediate * 2);
+  normed_ = Buffer::allocate(R * H * 2);
   partials_ = Buffer::allocate(size_t(kMaxPartialSlices) * 16 * H * 4);
   const uint32_t widest = std::max(std::max(H, c.intermediate), std::max(gdn_.valueWidth(), c.q_heads * D));
   for (auto &p : prepared_) p = Buffer::allocate(ops::Linear::preparedBytes((widest + 255) / 256 * 256));
-  for (auto &h : hidden) h = Buffer::allocate(size_t(kVerifyRows) * H * 2);
-  logits = tp_ ? tp_->gathered() : Buffer::allocate(size_t(kVerifyRows) * c.vocab * 4);
-  tokens = Buffer::allocate(kVerifyRows * 4), selected = Buffer::allocate(kVerifyRows * 4), results = Buffer::allocate(16);
-  uniforms = Buffer::allocate(80 * 4), committed = Buffer::allocate(4), pendingRows = Buffer::allocate(4), pendingPath = Buffer::allocate(4);
-  tree = Buffer::allocate(kVerifyRows * 8), positions = Buffer::allocate(kVerifyRows * 4);
+  if (L > 1)
+    for (auto &p : widePrepared_) p = Buffer::allocate(ops::Linear::wideBytes(uint32_t(R), (widest + 255) / 256 * 256));
+  for (auto &h : hidden) h = Buffer::allocate(R * H * 2);
+  logits = tp_ ? tp_->gathered() : Buffer::allocate(R * c.vocab * 4);
+  tokens = Buffer::allocate(R * 4), selected = Buffer::allocate(R * 4), results = Buffer::allocate(16 * L);
+  uniforms = Buffer::allocate(80 * 4 * L), committed = Buffer::allocate(4 * L), pendingRows = Buffer::allocate(4 * L), pendingPath = Buffer::allocate(4 * L);
+  tree = Buffer::allocate(R * 8), positions = Buffer::allocate(R * 4);
   invFreq = Buffer::allocate(std::max(1u, c.rotary_pairs) * 4);
-  cosine = Buffer::allocate(size_t(kVerifyRows) * std::max(1u, c.rotary_pairs) * 4);
-  sine = Buffer::allocate(size_t(kVerifyRows) * std::max(1u, c.rotary_pairs) * 4);
+  cosine = Buffer::allocate(R * std::max(1u, c.rotary_pairs) * 4);
+  sine = Buffer::allocate(R * std::max(1u, c.rotary_pairs) * 4);
   pageTable_ = Buffer::allocate(size_t(pages) * 4);
-  sampleWorkspace_ = Buffer::allocate(ops::Sampling::workspace(kVerifyRows, c.vocab));
-  penaltyWords = Buffer::allocate(size_t(c.vocab) * 4);
-  candidates = Buffer::allocate(kVerifyRows * 16 * 4), candidateQ = Buffer::allocate(kVerifyRows * 16 * 4), draws = Buffer::allocate(kVerifyRows * 4);
+  sampleWorkspace_ = Buffer::allocate(ops::Sampling::workspace(uint32_t(R), c.vocab));
+  penaltyWords = Buffer::allocate(size_t(c.vocab) * 4 * L);
+  candidates = Buffer::allocate(R * 16 * 4), candidateQ = Buffer::allocate(R * 16 * 4), draws = Buffer::allocate(R * 4);
   if (c.moe_experts) {
     moeScores_ = Buffer::allocate(size_t(kVerifyRows) * moe_.slots * 4);
     moeSelected_ = Buffer::allocate(size_t(kVerifyRows) * moe_.routes() * 4), moeWeights_ = Buffer::allocate(size_t(kVerifyRows) * moe_.routes() * 4);
@@ -243,13 +261,13 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   }
 }
 
-inline uint64_t QwenTarget::kvBytes(uint32_t visible) const {
-  return uint64_t(kv_.attentionLayers) * 2 * visible * kv_.kvHeads * (kv_.headDimension + (kv_.halfScales ? 2 : 4));
+inline uint64_t QwenTarget::kvBytes(uint32_t visible) const {  // (every lane at `visible` tokens)
+  return uint64_t(lanes_) * kv_.attentionLayers * 2 * visible * kv_.kvHeads * (kv_.headDimension + (kv_.halfScales ? 2 : 4));
 }
 inline uint64_t QwenTarget::stateBytes() const {
   uint64_t gdnLayers = 0;
   for (const LayerWeights &w : layers_) gdnLayers += !w.attention;
-  return gdnLayers * 2 * gdn_.stateBytes();
+  return gdnLayers * 2 * gdn_.stateBytes() * lanes_;
 }
 
 inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) const {
@@ -293,16 +311,21 @@ inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) co
 }
 
 // Launched before and after the operator sequence (sb_target.cu).
-void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer &tree, const Buffer &positions, uint32_t rows, bool treeGiven);
+void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer &tree, const Buffer &positions, uint32_t rows, bool treeGiven,
+                     uint32_t lanes = 1);
 // (with a tensor-parallel group the step's end also advances the group's exchange count by `exchanges`)
 // advance: 0 the lane holds its position and its pending rows are cleared, 1 it commits, 2 it holds and keeps them
 void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, const Buffer &pendingPath,
-                   uint32_t advance, void *tpGroup, uint32_t exchanges);
+                   uint32_t advance, void *tpGroup, uint32_t exchanges, uint32_t lanes = 1);
 
 inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool treeGiven, bool keepPending, bool drawsGiven) {
   using namespace ops;
   if (rows < 1 || rows > kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: 1 to 16 rows");
   if (committedHost + rows > cfg_.max_context + kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: past the context bound");
+  if (lanes_ > 1) {
+    if (treeGiven) throw std::invalid_argument("QwenTarget::encodeVerify: tree blocks are offered for one lane");
+    return encodeVerifyLanes(graph, rows, temperature, parity, advance, keepPending, drawsGiven);
+  }
   const SbTargetConfig &c = loc_;
   const uint32_t H = c.hidden, D = c.head_dim;
   if (tp_ && !tp_->connected()) throw std::invalid_argument("QwenTarget::encodeVerify: the tensor-parallel ranks are not connected");
@@ -412,6 +435,79 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
       if (w.attention) PagedAttention::addPathCommit(graph, kv_, w.pages, pageTable_, committedHost, pathMask, &committed);
   }
   launchStepEnd(graph, results, committed, pendingRows, pendingPath, advance ? 1u : keepPending ? 2u : 0u, tp_ ? tp_->group() : nullptr, exchange);
+}
+
+// A step of several lanes (SbTargetConfig.lanes): every lane a chain of `rows` rows in its 16 row slots, the projections
+// over all 16 x lanes slots at once on the many-row kernel (RMSNorm inside its conversion, the residual in its epilogue),
+// attention, GDN, selection and acceptance gridded over the lanes with each lane's own position, pages, cell and tapes.
+inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool keepPending,
+                                          bool drawsGiven) {
+  using namespace ops;
+  const SbTargetConfig &c = loc_;
+  const uint32_t H = c.hidden, D = c.head_dim, L = lanes_, R = kVerifyRows * L;
+  launchStepBegin(graph, committed, tree, positions, rows, false, L);
+  if (c.rotary_pairs) RoPE::addTreeTables(graph, positions, invFreq, cosine, sine, R, 1.0f, c.rotary_pairs);
+  Embedding::add(graph, tokens, embedding_, hidden[0], R, H);
+  uint32_t cur = 0;
+  for (LayerWeights &w : layers_) {
+    // mixer: h += mixer(norm(h))
+    PreparedInput in = Linear::prepareWide(graph, hidden[cur], R, H, H, &w.attnNorm.buffer, widePrepared_[0]);
+    Linear::addWide(graph, w.inProj, nullptr, in, R, Epilogue::None, nullptr, packed_, packedStride_);
+    uint32_t mixedWidth;
+    if (w.attention) {
+      mixedWidth = c.q_heads * D;
+      SbAttnStoreArgs sa{packed_.as(), w.qNorm.as<float>(), w.kNorm.as<float>(), cosine.as<float>(), sine.as<float>(), pageTable_.as<uint32_t>(),
+                         queries_.as(), PagedAttention::describe(kv_, w.pages), committed.as<uint32_t>(), rows, c.q_heads,
+                         c.gated_attention ? 1u : 0u, c.rotary_pairs, packedStride_, committedHost, L, pagesPerLane_};
+      check(sb_attn_store(graph.stream, &sa));
+      SbAttnArgs aa{queries_.as(), c.gated_attention ? packed_.as() : nullptr, pageTable_.as<uint32_t>(), nullptr, mixed_.as(),
+                    PagedAttention::describe(kv_, w.pages), committed.as<uint32_t>(), rows, c.q_heads, c.gated_attention ? 1u : 0u,
+                    packedStride_, mixedWidth, committedHost, L, pagesPerLane_};
+      check(sb_attn_verify(graph.stream, &aa));
+      graph.launches += 2;
+    } else {
+      // The layer's normalised rows for the kernel's own alpha / beta projection.
+      Normalization::addRms(graph, hidden[cur], w.attnNorm, normed_, H, R, H, H);
+      mixedWidth = gdn_.valueWidth();
+      SbGdnArgs a{};
+      a.qkvz = packed_.as(), a.gate_weight = w.ssmAb.as<float>(), a.gate_input = normed_.as(), a.gate_k = a.gate_input_stride = H;
+      a.conv_w = w.ssmConv.as(), a.a_scale = w.ssmA.as<float>(), a.dt_bias = w.ssmDtBias.as(), a.norm_w = w.ssmNorm.as<float>();
+      a.conv_state_in = w.cells[parity].convolution.as(), a.conv_state_out = w.cells[parity ^ 1].convolution.as();
+      a.state_in = w.cells[parity].state.as<float>(), a.state_out = w.cells[parity ^ 1].state.as<float>();
+      a.pending = w.tapes[parity ^ 1].describe(), a.step = w.tapes[parity].describe();
+      a.hidden = mixed_.as(), a.pending_rows_dev = pendingRows.as<uint32_t>();
+      a.rows = rows, a.key_heads = gdn_.keyHeads, a.value_heads = gdn_.valueHeads, a.qkvz_stride = packedStride_, a.ab_stride = 2 * gdn_.valueHeads;
+      a.hidden_stride = mixedWidth, a.tiled = c.tiled_heads != 0, a.flags = SB_GDN_STATE_SETTLED, a.lanes = L;
+      check(sb_gdn_verify(graph.stream, &a));
+      ++graph.launches;
+    }
+    PreparedInput mixedIn = Linear::prepareWide(graph, mixed_, R, mixedWidth, mixedWidth, nullptr, widePrepared_[1]);
+    Linear::addWide(graph, w.outProj, nullptr, mixedIn, R, Epilogue::Residual, &hidden[cur], hidden[cur ^ 1], H);
+    cur ^= 1;
+    // FFN: h += down(silu(gate(norm(h))) * up(norm(h)))
+    PreparedInput ffnIn = Linear::prepareWide(graph, hidden[cur], R, H, H, &w.ffnNorm.buffer, widePrepared_[0]);
+    Linear::addWide(graph, w.ffnGate, &w.ffnUp, ffnIn, R, Epilogue::GateUp, nullptr, act_, c.intermediate);
+    PreparedInput actIn = Linear::prepareWide(graph, act_, R, c.intermediate, c.intermediate, nullptr, widePrepared_[1]);
+    Linear::addWide(graph, w.ffnDown, nullptr, actIn, R, Epilogue::Residual, &hidden[cur], hidden[cur ^ 1], H);
+    cur ^= 1;
+  }
+  PreparedInput headIn = Linear::prepareWide(graph, hidden[cur], R, H, H, &outputNorm_.buffer, widePrepared_[0]);
+  Linear::addWide(graph, output_, nullptr, headIn, R, Epilogue::None, nullptr, logits, c.vocab, true);
+  // selection, acceptance, commit: every lane its own rows, uniforms and results
+  if (penalties.active()) {
+    SbPenaltyArgs pa{logits.as<float>(), penaltyWords.as<uint32_t>(), tokens.as<uint32_t>(), tree.as(), rows, c.vocab, c.vocab,
+                     penalties.repetition, penalties.presence, penalties.frequency, L, 0};
+    check(sb_sample_penalize(graph.stream, &pa));
+    ++graph.launches;
+  }
+  SbSampleArgs sa{logits.as<float>(), tokens.as<uint32_t>(), temperature > 0.0f ? uniforms.as<float>() : nullptr, selected.as<uint32_t>(),
+                  sampleWorkspace_.as<float>(), rows, c.vocab, c.vocab, temperature, 0.0f, 0, 1.0f, nullptr, nullptr, nullptr, nullptr, L, 0};
+  if (drawsGiven && temperature > 0.0f) sa.candidate_ids = candidates.as<uint32_t>(), sa.candidate_q = candidateQ.as<float>(), sa.draws = draws.as<uint8_t>();
+  check(sb_sample_verify(graph.stream, &sa));
+  SbAcceptArgs ac{tokens.as<uint32_t>(), tree.as(), selected.as<uint32_t>(), results.as<uint32_t>(), nullptr, rows, kVerifyRows, 0, L};
+  check(sb_accept(graph.stream, &ac));
+  graph.launches += 2;
+  launchStepEnd(graph, results, committed, pendingRows, pendingPath, advance ? 1u : keepPending ? 2u : 0u, nullptr, 0, L);
 }
 
 }  // namespace splash::b200::model

@@ -93,6 +93,38 @@ class Linear {
     return {scratch, format == SB_FMT_Q4K ? uint32_t(SB_FMT_Q4K) : uint32_t(SB_FMT_Q6K), inputSize};
   }
 
+  // ---- many rows (a step of several lanes, or a chunk): the tensor-memory kernel (sb_linear_wide) ----
+  // The conversion for it (another layout than prepare's); `scratch` holds wideBytes(rows, inputSize).
+  static uint64_t wideBytes(uint32_t rows, uint32_t inputSize) { return sb_linear_wide_prepared_bytes(rows, inputSize); }
+  static PreparedInput prepareWide(CommandGraph &graph, const Buffer &input, uint32_t rows, uint32_t inputSize, uint32_t inputStride,
+                                   const Buffer *normWeight, const Buffer &scratch) {
+    requireBytes(input, size_t(rows - 1) * inputStride * 2 + size_t(inputSize) * 2, "Linear::prepareWide input");
+    requireBytes(scratch, wideBytes(rows, inputSize), "Linear::prepareWide scratch");
+    if (normWeight) requireBytes(*normWeight, size_t(inputSize) * 4, "Linear::prepareWide norm weight");
+    check(sb_linear_wide_prepare(graph.stream, input.as(), rows, inputSize, inputStride, normWeight ? normWeight->as() : nullptr, scratch.as(),
+                                 graph.pdl ? SB_LINEAR_PDL : 0));
+    graph.launches += (rows + 127) / 128;
+    return {scratch, 0xFFFFu, inputSize};  // (format tag of the wide layout)
+  }
+  // One Q4_K segment over `rows` rows: epilogues None / Residual / UpWithGate, or GateUp with `up` given.
+  static void addWide(CommandGraph &graph, const QuantizedSegment &s, const QuantizedSegment *up, const PreparedInput &prepared, uint32_t rows,
+                      Epilogue epilogue, const Buffer *aux, const Buffer &output, uint32_t outputStride, bool float32 = false) {
+    if (prepared.format != 0xFFFFu || prepared.inputSize != s.inputSize) throw std::invalid_argument("Linear::addWide: not a wide conversion of this width");
+    if ((epilogue == Epilogue::GateUp) != (up != nullptr)) throw std::invalid_argument("Linear::addWide: the up tensor comes with GateUp");
+    requireBytes(s.rows, size_t(s.outputSize) * sb_row_bytes(s.format, s.inputSize), "Linear::addWide segment rows");
+    if (up) requireBytes(up->rows, size_t(up->outputSize) * sb_row_bytes(up->format, up->inputSize), "Linear::addWide up rows");
+    requireBytes(output, (size_t(rows - 1) * outputStride + s.outputSize) * (float32 ? 4 : 2), "Linear::addWide output");
+    if (aux) requireBytes(*aux, (size_t(rows - 1) * outputStride + s.outputSize) * 2, "Linear::addWide residual or gate");
+    SbLinearArgs a{};
+    a.weights = s.rows.as(), a.weights2 = up ? up->rows.as() : nullptr, a.prepared = prepared.buffer.as();
+    a.aux = aux ? aux->as() : nullptr, a.out = output.as();
+    a.format = s.format, a.n = s.outputSize, a.k = s.inputSize, a.rows = rows;
+    a.aux_stride = aux ? outputStride : 0, a.out_stride = outputStride, a.epilogue = uint32_t(epilogue), a.out_f32 = float32;
+    a.flags = graph.pdl ? SB_LINEAR_PDL : 0;
+    check(sb_linear_wide(graph.stream, &a));
+    graph.launches += (rows + 127) / 128;
+  }
+
   // One projection over a prepared input; every segment writes its columns of the output.
   static void add(CommandGraph &graph, const LinearBuffers &b, const Projection &p, const LinearPlan &plan,
                   const PreparedInput &prepared) {

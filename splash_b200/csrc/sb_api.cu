@@ -104,11 +104,12 @@ int sb_init(int device) {
   SB_CUDA(cudaMemset(c.linear_counters, 0, c.linear_counter_count * sizeof(uint32_t)));
   c.attn_workspace_bytes = size_t(32) << 20;
   SB_CUDA(cudaMalloc(&c.attn_workspace, c.attn_workspace_bytes));
-  SB_CUDA(cudaMalloc(&c.attn_counters, 128 * sizeof(uint32_t)));
-  SB_CUDA(cudaMemset(c.attn_counters, 0, 128 * sizeof(uint32_t)));
-  SB_CUDA(cudaMalloc(&c.gdn_scratch, size_t(256) * 16 * 128 * 2));
-  SB_CUDA(cudaMalloc(&c.gdn_counters, 256 * sizeof(uint32_t)));
-  SB_CUDA(cudaMemset(c.gdn_counters, 0, 256 * sizeof(uint32_t)));
+  // (per lane of a step of several lanes: 128 attention counters; the GDN scratch and counters hold kGdnScratchHeads heads over all lanes)
+  SB_CUDA(cudaMalloc(&c.attn_counters, kAttnCounterWords * sizeof(uint32_t)));
+  SB_CUDA(cudaMemset(c.attn_counters, 0, kAttnCounterWords * sizeof(uint32_t)));
+  SB_CUDA(cudaMalloc(&c.gdn_scratch, size_t(kGdnScratchHeads) * 16 * 128 * 2));
+  SB_CUDA(cudaMalloc(&c.gdn_counters, kGdnScratchHeads * sizeof(uint32_t)));
+  SB_CUDA(cudaMemset(c.gdn_counters, 0, kGdnScratchHeads * sizeof(uint32_t)));
   c.ready = true;
   return SB_OK;
 }
@@ -126,8 +127,8 @@ int sb_device_status(uint32_t *status) {
     Context &c = ctx();
     SB_CUDA(cudaMemset(c.status_dev, 0, sizeof(uint32_t)));
     SB_CUDA(cudaMemset(c.linear_counters, 0, c.linear_counter_count * sizeof(uint32_t)));
-    SB_CUDA(cudaMemset(c.attn_counters, 0, 128 * sizeof(uint32_t)));
-    SB_CUDA(cudaMemset(c.gdn_counters, 0, 256 * sizeof(uint32_t)));
+    SB_CUDA(cudaMemset(c.attn_counters, 0, kAttnCounterWords * sizeof(uint32_t)));
+    SB_CUDA(cudaMemset(c.gdn_counters, 0, kGdnScratchHeads * sizeof(uint32_t)));
   }
   return SB_OK;
 }

@@ -43,7 +43,8 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void *
 }
 
 template <int D>
-__global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kAttnThreads, 1) attention_kernel(const AttnParams p_in) {
+  const AttnParams p = attn_lane_view(p_in);  // (one lane: p_in itself)
   constexpr int PITCH = D + 8;             // halves per shared row: 16-byte rows shifted by 4 banks
   constexpr int KSTEPS = D / 16, NT_O = D / 8;
   extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -356,6 +357,8 @@ extern "C" int sb_attn_verify(void *stream, const SbAttnArgs *a) {
   SB_REQUIRE(!a->gated || a->qkv, "sb_attn_verify: a gated layer needs the packed rows");
   SB_REQUIRE(a->out_stride >= a->q_heads * c.head_dim, "sb_attn_verify: out_stride below the row");
   Context &cx = ctx();
+  const uint32_t lanes = std::max(1u, a->lanes);
+  SB_REQUIRE(lanes == 1 || (a->rows <= 16 && a->committed_dev && lanes <= 64), "sb_attn_verify: %u lanes need rows <= 16 and the lanes' positions on the device", lanes);
   if (cx.attention_kernel == SB_ATTENTION_TCGEN05) {
     AttnParams p{};
     p.queries = static_cast<const uint16_t *>(a->queries);
@@ -369,16 +372,18 @@ extern "C" int sb_attn_verify(void *stream, const SbAttnArgs *a) {
     p.status = cx.status_dev;
     p.committed_dev = a->committed_dev;
     p.rows = a->rows, p.q_heads = a->q_heads, p.group = group, p.gated = a->gated, p.qkv_stride = a->qkv_stride;
-    p.out_stride = a->out_stride, p.committed = a->committed, p.fused = fused;
-    return launch_attention_tc(as_stream(stream), p, a->committed + a->rows);
+    p.out_stride = a->out_stride, p.committed = a->committed, p.fused = fused, p.page_table_stride = a->page_table_stride;
+    return launch_attention_tc(as_stream(stream), p, a->committed + a->rows, lanes);
   }
   const uint32_t D = c.head_dim, visible = a->committed + a->rows, chunks = (visible + kChunk - 1) / kChunk;
   // Splits: about one CTA per SM over all KV heads, at least 4 chunks each.
-  uint32_t splits = std::max(1u, uint32_t(cx.sm_count) / c.kv_heads);  // the whole grid is resident at once
+  uint32_t splits = std::max(1u, uint32_t(cx.sm_count) / (c.kv_heads * lanes));  // the whole grid is resident at once
   splits = std::min(splits, std::max(1u, chunks / 4));
   const uint32_t cps = (chunks + splits - 1) / splits;
   splits = (chunks + cps - 1) / cps;
-  const size_t need = size_t(c.kv_heads) * splits * kMaxFused * (D + 2) * sizeof(float);
+  SB_REQUIRE(size_t(lanes) * c.kv_heads * splits <= size_t(cx.sm_count), "sb_attn_verify: %u lanes x %u KV heads exceed the %d SMs one launch fills", lanes,
+             c.kv_heads, cx.sm_count);
+  const size_t need = size_t(lanes) * c.kv_heads * splits * kMaxFused * (D + 2) * sizeof(float);
   SB_REQUIRE(need <= cx.attn_workspace_bytes && c.kv_heads <= 64, "sb_attn_verify: workspace too small (%zu bytes needed)", need);
   AttnParams p{};
   p.queries = static_cast<const uint16_t *>(a->queries);
@@ -388,7 +393,8 @@ extern "C" int sb_attn_verify(void *stream, const SbAttnArgs *a) {
   p.out = static_cast<uint16_t *>(a->out);
   p.cache = c;
   p.partials = cx.attn_workspace;
-  p.stats = cx.attn_workspace + size_t(c.kv_heads) * splits * kMaxFused * D;
+  p.stats = cx.attn_workspace + size_t(lanes) * c.kv_heads * splits * kMaxFused * D;
+  p.page_table_stride = a->page_table_stride;
   p.counters = cx.attn_counters;
   p.status = cx.status_dev;
   p.committed_dev = a->committed_dev;
@@ -404,7 +410,7 @@ extern "C" int sb_attn_verify(void *stream, const SbAttnArgs *a) {
     attr_set[dev][D == 256] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(splits, c.kv_heads);
+  cfg.gridDim = dim3(splits, c.kv_heads, lanes);
   cfg.blockDim = dim3(kAttnThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = as_stream(stream);

@@ -21,7 +21,27 @@ struct AttnParams {
   uint32_t *status;
   const uint32_t *committed_dev;
   uint32_t rows, q_heads, group, gated, qkv_stride, out_stride, committed, splits, chunks_per_split, fused;
+  uint32_t page_table_stride;  // lanes (blockIdx.z): page-table entries between consecutive lanes' tables
 };
+
+// Lane blockIdx.z's view of a launch over several lanes: its 16 row slots of the row-indexed buffers, its page table and
+// position, its share of the workspace and counters.
+__device__ __forceinline__ AttnParams attn_lane_view(AttnParams p) {
+  const uint32_t z = blockIdx.z;
+  if (z == 0 && gridDim.z == 1) return p;
+  const size_t D = p.cache.head_dim;
+  p.queries += size_t(16) * z * p.q_heads * D;
+  if (p.qkv) p.qkv += size_t(16) * z * p.qkv_stride;
+  p.page_table += size_t(z) * p.page_table_stride;
+  if (p.tree) p.tree += 16 * z;
+  p.out += size_t(16) * z * p.out_stride;
+  const size_t per_lane = size_t(p.cache.kv_heads) * p.splits * kMaxFused;
+  p.partials += size_t(z) * per_lane * D;
+  p.stats += size_t(z) * per_lane * 2;
+  p.counters += 128 * z;
+  if (p.committed_dev) p.committed_dev += z;
+  return p;
+}
 
 // 16 int8 (one uint4) -> 16 fp16, exactly: (q ^ 0x80) | 0x6400 is 1024 + q + 128.
 __device__ __forceinline__ void int8x16_to_half(const uint4 v, uint4 &lo, uint4 &hi) {
@@ -116,6 +136,6 @@ __device__ __forceinline__ void attention_merge(const AttnParams &p, uint32_t sp
 }
 
 // The tcgen05 kernel's launcher (sb_attention_tc.cu); `p` comes filled except for the split geometry.
-int launch_attention_tc(cudaStream_t stream, AttnParams &p, uint32_t visible);
+int launch_attention_tc(cudaStream_t stream, AttnParams &p, uint32_t visible, uint32_t lanes);
 
 }  // namespace sb

@@ -58,7 +58,8 @@ __device__ __forceinline__ bool at_wait(uint64_t *bar, uint32_t parity) {  // sa
 }
 
 template <int D>
-__global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(const AttnParams p_in) {
+  const AttnParams p = attn_lane_view(p_in);  // (one lane: p_in itself)
   using L = AtLayout<D>;
   extern __shared__ __align__(128) uint8_t smem[];
   uint64_t *raw_full = reinterpret_cast<uint64_t *>(smem + L::kBars);  // [kAtRaw]
@@ -374,17 +375,19 @@ __global__ void __launch_bounds__(kAtThreads, 1) attention_tc_kernel(const AttnP
   attention_merge<D>(p, split, kvh, s_last);
 }
 
-int launch_attention_tc(cudaStream_t stream, AttnParams &p, uint32_t visible) {
+int launch_attention_tc(cudaStream_t stream, AttnParams &p, uint32_t visible, uint32_t lanes) {
   Context &cx = ctx();
   const uint32_t D = p.cache.head_dim, chunks = (visible + kAtChunk - 1) / kAtChunk;
-  // Splits: about one CTA per SM over all KV heads (the whole grid is resident at once), at least 2 chunks each.
-  uint32_t splits = std::max(1u, uint32_t(cx.sm_count) / p.cache.kv_heads);
+  // Splits: about one CTA per SM over all KV heads and lanes (the whole grid is resident at once), at least 2 chunks each.
+  uint32_t splits = std::max(1u, uint32_t(cx.sm_count) / (p.cache.kv_heads * lanes));
   splits = std::min(splits, std::max(1u, chunks / 2));
   const uint32_t cps = (chunks + splits - 1) / splits;
   splits = (chunks + cps - 1) / cps;
-  const size_t need = size_t(p.cache.kv_heads) * splits * kMaxFused * (D + 2) * sizeof(float);
+  SB_REQUIRE(size_t(lanes) * p.cache.kv_heads * splits <= size_t(cx.sm_count), "sb_attn_verify: %u lanes x %u KV heads exceed the %d SMs one launch fills",
+             lanes, p.cache.kv_heads, cx.sm_count);
+  const size_t need = size_t(lanes) * p.cache.kv_heads * splits * kMaxFused * (D + 2) * sizeof(float);
   SB_REQUIRE(need <= cx.attn_workspace_bytes && p.cache.kv_heads <= 64, "sb_attn_verify: workspace too small (%zu bytes needed)", need);
-  p.stats = cx.attn_workspace + size_t(p.cache.kv_heads) * splits * kMaxFused * D;
+  p.stats = cx.attn_workspace + size_t(lanes) * p.cache.kv_heads * splits * kMaxFused * D;
   p.splits = splits, p.chunks_per_split = cps;
   const size_t smem = D == 256 ? AtLayout<256>::kBytes : AtLayout<128>::kBytes;
   void (*kernel)(const AttnParams) = D == 256 ? attention_tc_kernel<256> : attention_tc_kernel<128>;
@@ -395,7 +398,7 @@ int launch_attention_tc(cudaStream_t stream, AttnParams &p, uint32_t visible) {
     attr_set[dev][D == 256] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(splits, p.cache.kv_heads);
+  cfg.gridDim = dim3(splits, p.cache.kv_heads, lanes);
   cfg.blockDim = dim3(kAtThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;

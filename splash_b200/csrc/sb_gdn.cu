@@ -39,6 +39,36 @@ struct GdnParams {
   uint32_t *counters;   // [value_heads]
 };
 
+// Lane blockIdx.z's view of a launch over several lanes: its 16 row slots of the row-indexed buffers, its cell, tapes and
+// pending words, its share of the scratch and the counters.
+__device__ __forceinline__ GdnParams gdn_lane_view(GdnParams p) {
+  const uint32_t z = blockIdx.z;
+  if (z == 0 && gridDim.z == 1) return p;
+  SbGdnArgs &a = p.a;
+  const size_t KW = size_t(a.key_heads) * 128, VW = size_t(a.value_heads) * 128, C = 2 * KW + VW, R = 16 * size_t(z);
+  auto rows16 = [&](const void *q, size_t stride) { return q ? static_cast<const void *>(static_cast<const uint16_t *>(q) + R * stride) : q; };
+  a.qkvz = rows16(a.qkvz, a.qkvz_stride), a.b = rows16(a.b, a.ab_stride), a.a = rows16(a.a, a.ab_stride);
+  a.gate_input = rows16(a.gate_input, a.gate_input_stride);
+  a.hidden = const_cast<void *>(rows16(a.hidden, a.hidden_stride));
+  if (a.tree) a.tree = static_cast<const uint2 *>(a.tree) + R;
+  a.conv_state_in = static_cast<const uint16_t *>(a.conv_state_in) + size_t(z) * 3 * C;
+  a.conv_state_out = static_cast<uint16_t *>(a.conv_state_out) + size_t(z) * 3 * C;
+  a.state_in += size_t(z) * a.value_heads * 128 * 128, a.state_out += size_t(z) * a.value_heads * 128 * 128;
+  auto tape = [&](SbGdnTape &t) {
+    if (t.inputs) t.inputs = static_cast<uint16_t *>(t.inputs) + R * C;
+    if (t.k) t.k = static_cast<uint16_t *>(t.k) + R * KW;
+    if (t.v) t.v = static_cast<uint16_t *>(t.v) + R * VW;
+    if (t.beta) t.beta = static_cast<uint16_t *>(t.beta) + R * a.value_heads;
+    if (t.decay) t.decay += R * a.value_heads;
+  };
+  tape(a.pending), tape(a.step);
+  if (a.pending_rows_dev) a.pending_rows_dev += z;
+  if (a.pending_path_dev) a.pending_path_dev += z;
+  p.scratch += size_t(z) * a.value_heads * 16 * 128;
+  p.counters += size_t(z) * a.value_heads;
+  return p;
+}
+
 // Row of the n-th token (from the anchor) of a path mask.
 __device__ __forceinline__ uint32_t path_row(uint32_t path, uint32_t n) {
   for (uint32_t i = 0; i < n; ++i) path &= path - 1;
@@ -57,7 +87,8 @@ __device__ __forceinline__ float warp_sum(float v) {
 // it the rows are a chain and the pending rows the tape's first, which is the verify step's usual case and keeps the
 // indirections out of its kernel.
 template <bool kTree>
-__global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads, 2) gdn_kernel(const GdnParams p) {
+__global__ void __cluster_dims__(kGdnSplit, 1, 1) __launch_bounds__(kGdnThreads, 2) gdn_kernel(const GdnParams p_in) {
+  const GdnParams p = gdn_lane_view(p_in);  // (one lane: p_in itself)
   const SbGdnArgs &a = p.a;
   __shared__ float q_s[kGdnRows][kD], k_s[kGdnRows][kD], pk_s[kGdnRows][kD];
   __shared__ float v_s[kGdnRows][kGdnVd], pv_s[kGdnRows][kGdnVd], o_s[kGdnRows][kGdnVd];
@@ -472,6 +503,8 @@ static int gdn_validate(const SbGdnArgs *a, const char *who) {
                                  (reinterpret_cast<uintptr_t>(a->gate_weight) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->gate_input) & 15) == 0),
              "%s: fused gate projection needs a 16-byte aligned input and weight, k a multiple of 8 and stride >= k", who);
   SB_REQUIRE((a->flags & ~uint32_t(SB_GDN_STATE_SETTLED)) == 0, "%s: unknown flags 0x%x", who, a->flags);
+  SB_REQUIRE(a->lanes <= 64 && size_t(std::max(1u, a->lanes)) * a->value_heads <= kGdnScratchHeads, "%s: %u lanes of %u value heads exceed the scratch", who,
+             a->lanes, a->value_heads);
   return SB_OK;
 }
 }  // namespace sb
@@ -483,7 +516,7 @@ extern "C" int sb_gdn_verify(void *stream, const SbGdnArgs *a) {
   Context &c = ctx();
   GdnParams p{*a, c.gdn_scratch, c.gdn_counters};
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(kGdnSplit, a->value_heads);
+  cfg.gridDim = dim3(kGdnSplit, a->value_heads, std::max(1u, a->lanes));
   cfg.blockDim = dim3(kGdnThreads);
   cfg.stream = as_stream(stream);
   cudaLaunchAttribute attr[1];
@@ -500,6 +533,7 @@ extern "C" int sb_gdn_verify_static(void *stream, const SbGdnArgs *a) {
   SB_REQUIRE(a->value_heads <= kStaticMaxValueHeads,
              "sb_gdn_verify_static: %u value heads exceed the %u the built-in scratch holds; use sb_gdn_verify", a->value_heads,
              kStaticMaxValueHeads);
+  SB_REQUIRE(a->lanes <= 1, "sb_gdn_verify_static: one lane a call (the built-in scratch holds one lane's rows)");
   const int valid = gdn_validate(a, "sb_gdn_verify_static");
   if (valid != SB_OK) return valid;
   uint8_t *scratch = nullptr;

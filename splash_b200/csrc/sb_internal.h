@@ -51,6 +51,9 @@ int cuda_fail(cudaError_t e, const char *what);
     if (!::sb::ctx().ready) return ::sb::fail(SB_ERR_NO_DEVICE, "sb_init has not succeeded: no CUDA device"); \
   } while (0)
 
+constexpr uint32_t kAttnCounterWords = 64 * 128;  // 128 arrival / merge counters per lane, up to 64 lanes
+constexpr uint32_t kGdnScratchHeads = 2048;       // value heads x lanes of one sb_gdn_verify launch
+
 // Device status word values.
 enum : uint32_t {
   SB_DEV_OK = 0,

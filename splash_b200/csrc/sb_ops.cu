@@ -131,7 +131,9 @@ __global__ void __launch_bounds__(256) linear_f32_kernel(const float *w, const u
   }
 }
 
-// ---- q/k norm + RoPE + INT8 KV store: grid (q_heads + kv_heads, rows), head_dim threads ----
+constexpr uint32_t kLaneRows = 16;  // row slots of a lane in a step of several lanes (the verify block's most rows)
+
+// ---- q/k norm + RoPE + INT8 KV store: grid (q_heads + kv_heads, rows, lanes), head_dim threads ----
 struct StoreParams {
   const uint16_t *qkv;
   const float *q_norm, *k_norm, *cos_tab, *sin_tab;
@@ -140,6 +142,7 @@ struct StoreParams {
   SbKvLayer cache;
   const uint32_t *committed_dev;
   uint32_t rows, q_heads, gated, pairs, qkv_stride, committed;
+  uint32_t page_table_stride;  // lanes (blockIdx.z): page-table entries between consecutive lanes' tables
 };
 
 __device__ __forceinline__ int8_t kv_code(float v, float m) {
@@ -155,7 +158,9 @@ __global__ void __launch_bounds__(D) attn_store_kernel(const StoreParams p) {
   __shared__ float normed[D];
   pdl_launch_dependents();
   pdl_wait();
-  const uint32_t head = blockIdx.x, row = blockIdx.y, d = threadIdx.x, lane = d & 31, warp = d >> 5;
+  // Lanes (blockIdx.z): a lane's rows are rows 16 z .. of the row-indexed buffers; its position and page table are its own.
+  const uint32_t lane_index = blockIdx.z;
+  const uint32_t head = blockIdx.x, row = kLaneRows * lane_index + blockIdx.y, d = threadIdx.x, lane = d & 31, warp = d >> 5;
   const bool query = head < p.q_heads;
   const uint32_t kvh = query ? 0 : head - p.q_heads, qs = p.gated ? 2 * D : D;
   const uint16_t *prow = p.qkv + size_t(row) * p.qkv_stride;
@@ -201,7 +206,8 @@ __global__ void __launch_bounds__(D) attn_store_kernel(const StoreParams p) {
   km = 0.0f, vm = 0.0f;
 #pragma unroll
   for (int w = 0; w < W; ++w) km = fmaxf(km, part[w]), vm = fmaxf(vm, part2[w]);
-  const uint32_t tok = (p.committed_dev ? *p.committed_dev : p.committed) + row, page = p.page_table[tok / p.cache.page_tokens], pt = tok % p.cache.page_tokens;
+  const uint32_t tok = (p.committed_dev ? p.committed_dev[lane_index] : p.committed) + blockIdx.y;
+  const uint32_t page = p.page_table[size_t(lane_index) * p.page_table_stride + tok / p.cache.page_tokens], pt = tok % p.cache.page_tokens;
   const size_t slot = (size_t(page) * p.cache.kv_heads + kvh) * p.cache.page_tokens + pt;
   static_cast<int8_t *>(p.cache.k)[slot * D + d] = kv_code(r, km);
   static_cast<int8_t *>(p.cache.v)[slot * D + d] = kv_code(v, vm);
@@ -403,7 +409,7 @@ __device__ RowCut distribution_end(const float *l, uint32_t vocab, float mx, flo
   return cut;
 }
 
-__global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SbSampleArgs a) {
+__global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SbSampleArgs a_in) {
   __shared__ FilterScratch fs;
   __shared__ float best_v[32];
   __shared__ uint32_t best_i[32];
@@ -411,6 +417,16 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SbSampleAr
   __shared__ uint32_t s_top;
   pdl_launch_dependents();
   pdl_wait();
+  // Lanes (blockIdx.y): lane z's rows are rows 16 z .. of every row-indexed buffer, its uniforms the 80 from 80 z on.
+  SbSampleArgs a = a_in;
+  {
+    const uint32_t z = blockIdx.y, r0 = kLaneRows * z;
+    a.logits += size_t(r0) * a.logit_stride, a.input_tokens += r0, a.selected += r0;
+    if (a.uniforms) a.uniforms += 80 * z;
+    if (a.workspace) a.workspace += size_t(r0) * (2 * ((a.vocab + kShard - 1) / kShard) + 8);
+    if (a.cut_out) a.cut_out += 2 * r0;
+    if (a.candidate_ids) a.candidate_ids += kDrawCandidates * r0, a.candidate_q += kDrawCandidates * r0, a.draws += 4 * r0;
+  }
   const uint32_t r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float *l = a.logits + size_t(r) * a.logit_stride;
   // Greedy: value descending, id ascending.
@@ -601,10 +617,13 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SbSampleAr
 }
 
 // ---- acceptance: one thread ----
-__global__ void accept_kernel(const SbAcceptArgs a) {
+__global__ void accept_kernel(const SbAcceptArgs a_in) {
   pdl_launch_dependents();
   pdl_wait();
-  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  if (threadIdx.x != 0) return;
+  SbAcceptArgs a = a_in;  // lane blockIdx.x: rows 16 z .., results 4 z ..
+  a.input_tokens += kLaneRows * blockIdx.x, a.tokens += kLaneRows * blockIdx.x, a.results += 4 * blockIdx.x;
+  a.tree = static_cast<const uint2 *>(a.tree) + kLaneRows * blockIdx.x;
   const uint2 *tree = static_cast<const uint2 *>(a.tree);  // {ancestors, parent | depth << 16}
   uint32_t path[32];
   path[0] = 0;
@@ -634,9 +653,12 @@ __global__ void accept_kernel(const SbAcceptArgs a) {
 // One thread per vocabulary token: the token's count in every row's context, then the penalty on the rows that
 // hold it (runtime/metal/kernels/decode/sampling.metal:997-1048). Products and sums are single IEEE operations in
 // the reference's order, so the result equals the CPU statement bit for bit.
-__global__ void penalize_kernel(const SbPenaltyArgs a) {
+__global__ void penalize_kernel(const SbPenaltyArgs a_in) {
   pdl_launch_dependents();
   pdl_wait();
+  SbPenaltyArgs a = a_in;  // lane blockIdx.y: rows 16 z .., its own table of the vocabulary
+  a.logits += size_t(kLaneRows) * blockIdx.y * a.logit_stride, a.input_tokens += kLaneRows * blockIdx.y;
+  a.words += size_t(blockIdx.y) * a.vocab, a.tree = static_cast<const uint2 *>(a.tree) + kLaneRows * blockIdx.y;
   const uint32_t token = blockIdx.x * blockDim.x + threadIdx.x;
   if (token >= a.vocab) return;
   uint32_t drafted = 0;
@@ -796,9 +818,12 @@ int sb_attn_store(void *stream, const SbAttnStoreArgs *a) {
              "sb_attn_store: rows %u outside 1..32 or q_heads %u not a multiple of kv_heads", a->rows, a->q_heads);
   SB_REQUIRE(a->qkv_stride >= a->q_heads * qs + 2 * a->cache.kv_heads * D, "sb_attn_store: qkv_stride %u below the packed row", a->qkv_stride);
   SB_REQUIRE(2 * a->pairs <= D && (a->pairs == 0 || (a->cos_tab && a->sin_tab)), "sb_attn_store: %u rotary pairs exceed the head, or no tables", a->pairs);
+  const uint32_t lanes = std::max(1u, a->lanes);
+  SB_REQUIRE(lanes == 1 || (a->rows <= kLaneRows && a->committed_dev && lanes <= 64), "sb_attn_store: %u lanes need rows <= 16 and the lanes' positions on the device", lanes);
   StoreParams p{static_cast<const uint16_t *>(a->qkv), a->q_norm, a->k_norm, a->cos_tab, a->sin_tab, a->page_table,
-                static_cast<uint16_t *>(a->queries), a->cache, a->committed_dev, a->rows, a->q_heads, a->gated, a->pairs, a->qkv_stride, a->committed};
-  const dim3 grid(a->q_heads + a->cache.kv_heads, a->rows);
+                static_cast<uint16_t *>(a->queries), a->cache, a->committed_dev, a->rows, a->q_heads, a->gated, a->pairs, a->qkv_stride, a->committed,
+                a->page_table_stride};
+  const dim3 grid(a->q_heads + a->cache.kv_heads, a->rows, lanes);
   if (D == 256) return launch(attn_store_kernel<256>, grid, dim3(256), as_stream(stream), p);
   return launch(attn_store_kernel<128>, grid, dim3(128), as_stream(stream), p);
 }
@@ -837,7 +862,8 @@ int sb_sample_verify(void *stream, const SbSampleArgs *a) {
   const bool filtered = a->min_p > 0.0f || (a->top_k > 0 && a->top_k < a->vocab) || (a->top_p > 0.0f && a->top_p < 1.0f);
   SB_REQUIRE(!filtered || a->vocab <= kMaxFilterShards * kShard, "sb_sample_verify: min-p / top-k / top-p support vocabularies up to %u", kMaxFilterShards * kShard);
   SB_REQUIRE(!a->candidate_ids || (a->candidate_q && a->draws), "sb_sample_verify: candidates come with their draft probabilities and the rows' draws");
-  return launch(sample_kernel, dim3(a->rows), dim3(kSampleThreads), as_stream(stream), *a);
+  SB_REQUIRE(a->lanes <= 64, "sb_sample_verify: %u lanes (up to 64)", a->lanes);
+  return launch(sample_kernel, dim3(a->rows, std::max(1u, a->lanes)), dim3(kSampleThreads), as_stream(stream), *a);
 }
 
 int sb_sample_penalize(void *stream, const SbPenaltyArgs *a) {
@@ -846,7 +872,8 @@ int sb_sample_penalize(void *stream, const SbPenaltyArgs *a) {
   SB_REQUIRE(a->rows >= 1 && a->rows <= 32 && a->vocab >= 1 && a->logit_stride >= a->vocab, "sb_sample_penalize: rows %u outside 1..32 or bad vocabulary extent",
              a->rows);
   SB_REQUIRE(a->repetition > 0.0f, "sb_sample_penalize: repetition %g is not positive", double(a->repetition));
-  return launch(penalize_kernel, dim3((a->vocab + 255) / 256), dim3(256), as_stream(stream), *a);
+  SB_REQUIRE(a->lanes <= 64 && (a->lanes <= 1 || a->rows <= kLaneRows), "sb_sample_penalize: %u lanes (up to 64, of up to 16 rows)", a->lanes);
+  return launch(penalize_kernel, dim3((a->vocab + 255) / 256, std::max(1u, a->lanes)), dim3(256), as_stream(stream), *a);
 }
 
 int sb_moe_route(void *stream, const SbMoeRouteArgs *a) {
@@ -863,7 +890,8 @@ int sb_accept(void *stream, const SbAcceptArgs *a) {
   SB_REQUIRE(a && a->input_tokens && a->tree && a->tokens && a->results, "sb_accept: null pointer");
   SB_REQUIRE(a->rows >= 1 && a->rows <= 32 && a->remaining >= 1, "sb_accept: rows %u outside 1..32 or nothing remaining", a->rows);
   SB_REQUIRE(a->n_stop == 0 || a->stop_tokens, "sb_accept: stop tokens missing");
-  return launch(accept_kernel, dim3(1), dim3(32), as_stream(stream), *a);
+  SB_REQUIRE(a->lanes <= 64 && (a->lanes <= 1 || a->rows <= kLaneRows), "sb_accept: %u lanes (up to 64, of up to 16 rows)", a->lanes);
+  return launch(accept_kernel, dim3(std::max(1u, a->lanes)), dim3(32), as_stream(stream), *a);
 }
 
 /* Programmatic dependent launch for the glue kernels of this context (on by default). */

@@ -4,6 +4,7 @@
 #include <map>
 #include <memory>
 #include <tuple>
+#include <vector>
 
 #include "model/QwenTarget.hpp"
 #include "sb_internal.h"
@@ -18,26 +19,28 @@ namespace sb {
 __global__ void step_begin_kernel(const uint32_t *committed, uint2 *tree, uint32_t *positions, uint32_t rows, uint32_t tree_given) {
   pdl_launch_dependents();
   pdl_wait();
-  const uint32_t r = threadIdx.x;
+  const uint32_t r = threadIdx.x, lane = blockIdx.x;  // (a block per lane: its 16 row slots, its own position)
   if (r >= rows) return;
+  tree += 16 * lane, positions += 16 * lane;
   if (!tree_given) tree[r] = make_uint2((2u << r) - 1u, (r ? r - 1 : 0) | (r << 16));
-  positions[r] = *committed + (tree_given ? tree[r].y >> 16 : r);
+  positions[r] = committed[lane] + (tree_given ? tree[r].y >> 16 : r);
 }
 // The lane's commit: the retained rows become history; the next step folds them into the GDN state.
 __global__ void step_end_kernel(const uint32_t *results, uint32_t *committed, uint32_t *pending_rows, uint32_t *pending_path, uint32_t advance,
-                                uint32_t *tp_epoch, uint32_t tp_exchanges) {
+                                uint32_t *tp_epoch, uint32_t tp_exchanges, uint32_t lanes) {
   pdl_wait();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x < lanes) {  // (a thread per lane)
+    const uint32_t lane = threadIdx.x;
     // The next step's exchanges are numbered after this step's. Their kernels read the count when they start, and
     // kernels may start before the ones ahead of them complete: dependents are let go only after the count has moved.
-    if (tp_epoch) *tp_epoch += tp_exchanges;
+    if (tp_epoch && lane == 0) *tp_epoch += tp_exchanges;
     if (advance == 1) {
-      *committed += results[0];
-      *pending_rows = results[0];
-      *pending_path = results[2];
+      committed[lane] += results[4 * lane];
+      pending_rows[lane] = results[4 * lane];
+      pending_path[lane] = results[4 * lane + 2];
     } else if (advance == 0) {
-      *pending_rows = 0;
-      *pending_path = 0;
+      pending_rows[lane] = 0;
+      pending_path[lane] = 0;
     }  // (2: the lane stays where it is and keeps its pending rows: every such step folds the same rows again)
     __threadfence();
   }
@@ -127,9 +130,10 @@ struct Target {
 }  // namespace sb
 
 namespace splash::b200::model {
-void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer &tree, const Buffer &positions, uint32_t rows, bool treeGiven) {
+void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer &tree, const Buffer &positions, uint32_t rows, bool treeGiven,
+                     uint32_t lanes) {
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(1), cfg.blockDim = dim3(32), cfg.stream = sb::as_stream(graph.stream);
+  cfg.gridDim = dim3(lanes), cfg.blockDim = dim3(32), cfg.stream = sb::as_stream(graph.stream);
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
@@ -140,7 +144,7 @@ void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer 
   ++graph.launches;
 }
 void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, const Buffer &pendingPath,
-                   uint32_t advance, void *tpGroup, uint32_t exchanges) {
+                   uint32_t advance, void *tpGroup, uint32_t exchanges, uint32_t lanes) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(1), cfg.blockDim = dim3(32), cfg.stream = sb::as_stream(graph.stream);
   cudaLaunchAttribute attr[1];
@@ -148,7 +152,7 @@ void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &com
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = graph.pdl ? 1 : 0;
   if (cudaLaunchKernelEx(&cfg, sb::step_end_kernel, static_cast<const uint32_t *>(results.as<uint32_t>()), committed.as<uint32_t>(),
-                         pendingRows.as<uint32_t>(), pendingPath.as<uint32_t>(), advance, sb::tp_epoch_word(tpGroup), exchanges) != cudaSuccess)
+                         pendingRows.as<uint32_t>(), pendingPath.as<uint32_t>(), advance, sb::tp_epoch_word(tpGroup), exchanges, lanes) != cudaSuccess)
     throw BackendError(SB_ERR_CUDA, "step_end launch failed");
   ++graph.launches;
 }
@@ -180,7 +184,8 @@ int sb_target_create(const SbTargetConfig *config, void **out_target) {
   return guarded([&] {
     auto t = std::make_unique<Target>();
     t->model = std::make_unique<QwenTarget>(*config);
-    SB_CUDA(cudaMallocHost(&t->results_pinned, 20 * sizeof(uint32_t)));
+    const uint32_t L = std::max(1u, config->lanes);
+    SB_CUDA(cudaMallocHost(&t->results_pinned, size_t(20) * L * sizeof(uint32_t)));
     SB_CUDA(cudaStreamCreateWithFlags(&t->own_stream, cudaStreamNonBlocking));
     QwenTarget &m = *t->model;
     Buffer table;
@@ -188,12 +193,13 @@ int sb_target_create(const SbTargetConfig *config, void **out_target) {
     const uint32_t pages = uint32_t(table.bytes() / 4);
     iota_kernel<<<(pages + 255) / 256, 256>>>(table.as<uint32_t>(), pages);
     if (config->rotary_pairs) inv_freq_kernel<<<1, 256>>>(m.invFreq.as<float>(), config->rotary_pairs, config->rope_theta);
-    SB_CUDA(cudaMemset(m.committed.as(), 0, 4));
-    SB_CUDA(cudaMemset(m.pendingRows.as(), 0, 4));
-    SB_CUDA(cudaMemset(m.pendingPath.as(), 0, 4));
+    SB_CUDA(cudaMemset(m.committed.as(), 0, 4 * L));
+    SB_CUDA(cudaMemset(m.pendingRows.as(), 0, 4 * L));
+    SB_CUDA(cudaMemset(m.pendingPath.as(), 0, 4 * L));
     SB_CUDA(cudaMemset(m.penaltyWords.as(), 0, m.penaltyWords.bytes()));
-    SB_CUDA(cudaMemset(m.uniforms.as(), 0, 80 * 4));
-    SB_CUDA(cudaMemset(m.tokens.as(), 0, 64));
+    SB_CUDA(cudaMemset(m.uniforms.as(), 0, 80 * 4 * L));
+    SB_CUDA(cudaMemset(m.tokens.as(), 0, 64 * L));
+    SB_CUDA(cudaMemset(m.tree.as(), 0, 128 * L));
     SB_CUDA(cudaDeviceSynchronize());
     *out_target = t.release();
     return int(SB_OK);
@@ -261,10 +267,30 @@ int sb_target_reset(void *target, uint32_t committed) {
   QwenTarget &m = *static_cast<Target *>(target)->model;
   SB_REQUIRE(committed <= m.config().max_context, "sb_target_reset: %u tokens exceed the context bound %u", committed, m.config().max_context);
   SB_CUDA(cudaDeviceSynchronize());
-  SB_CUDA(cudaMemcpy(m.committed.as(), &committed, 4, cudaMemcpyHostToDevice));
-  SB_CUDA(cudaMemset(m.pendingRows.as(), 0, 4));
-  SB_CUDA(cudaMemset(m.pendingPath.as(), 0, 4));
+  const std::vector<uint32_t> all(m.lanes(), committed);  // every lane at the same position
+  SB_CUDA(cudaMemcpy(m.committed.as(), all.data(), 4 * all.size(), cudaMemcpyHostToDevice));
+  SB_CUDA(cudaMemset(m.pendingRows.as(), 0, 4 * all.size()));
+  SB_CUDA(cudaMemset(m.pendingPath.as(), 0, 4 * all.size()));
   m.committedHost = committed;
+  m.step = 0;
+  return SB_OK;
+}
+
+int sb_target_reset_lanes(void *target, const uint32_t *committed_host) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target && committed_host, "sb_target_reset_lanes: null pointer");
+  QwenTarget &m = *static_cast<Target *>(target)->model;
+  uint32_t most = 0;
+  for (uint32_t l = 0; l < m.lanes(); ++l) {
+    SB_REQUIRE(committed_host[l] <= m.config().max_context, "sb_target_reset_lanes: lane %u at %u tokens exceeds the context bound %u", l, committed_host[l],
+               m.config().max_context);
+    most = std::max(most, committed_host[l]);
+  }
+  SB_CUDA(cudaDeviceSynchronize());
+  SB_CUDA(cudaMemcpy(m.committed.as(), committed_host, 4 * m.lanes(), cudaMemcpyHostToDevice));
+  SB_CUDA(cudaMemset(m.pendingRows.as(), 0, 4 * m.lanes()));
+  SB_CUDA(cudaMemset(m.pendingPath.as(), 0, 4 * m.lanes()));
+  m.committedHost = most;
   m.step = 0;
   return SB_OK;
 }
@@ -403,6 +429,7 @@ int sb_target_verify(void *target, void *stream, const uint32_t *tokens_host, co
   SB_REQUIRE(temperature == 0.0f || uniforms_host, "sb_target_verify: a sampled policy needs uniforms");
   Target *t = static_cast<Target *>(target);
   QwenTarget &m = *t->model;
+  SB_REQUIRE(m.lanes() == 1, "sb_target_verify: the target steps %u lanes; use sb_target_verify_lanes", m.lanes());
   cudaStream_t s = t->pick(stream);
   const uint32_t before = m.committedHost;
   SB_CUDA(cudaMemcpyAsync(m.tokens.as(), tokens_host, rows * 4, cudaMemcpyHostToDevice, s));
@@ -415,6 +442,35 @@ int sb_target_verify(void *target, void *stream, const uint32_t *tokens_host, co
   memcpy(out_results_host, t->results_pinned, 16);
   memcpy(out_tokens_host, t->results_pinned + 4, rows * 4);
   if (flags & SB_TARGET_ADVANCE) m.committedHost = before + t->results_pinned[0];  // the exact position again
+  return SB_OK;
+}
+
+int sb_target_verify_lanes(void *target, void *stream, const uint32_t *tokens_host, const float *uniforms_host, uint32_t rows, float temperature,
+                           uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target && tokens_host && out_tokens_host && out_results_host, "sb_target_verify_lanes: null pointer");
+  SB_REQUIRE(rows >= 1 && rows <= splash::b200::model::kVerifyRows, "sb_target_verify_lanes: rows = %u outside 1..16", rows);
+  SB_REQUIRE(temperature == 0.0f || uniforms_host, "sb_target_verify_lanes: a sampled policy needs uniforms");
+  SB_REQUIRE(!(flags & SB_TARGET_TREE), "sb_target_verify_lanes: chain blocks");
+  Target *t = static_cast<Target *>(target);
+  QwenTarget &m = *t->model;
+  const uint32_t L = m.lanes();
+  cudaStream_t s = t->pick(stream);
+  const uint32_t before = m.committedHost;
+  SB_CUDA(cudaMemcpyAsync(m.tokens.as(), tokens_host, size_t(16) * L * 4, cudaMemcpyHostToDevice, s));
+  if (uniforms_host) SB_CUDA(cudaMemcpyAsync(m.uniforms.as(), uniforms_host, size_t(80) * L * 4, cudaMemcpyHostToDevice, s));
+  const int st = run_step(t, s, rows, temperature, flags);
+  if (st != SB_OK) return st;
+  SB_CUDA(cudaMemcpyAsync(t->results_pinned, m.results.as(), size_t(16) * L, cudaMemcpyDeviceToHost, s));
+  SB_CUDA(cudaMemcpyAsync(t->results_pinned + 4 * L, m.selected.as(), size_t(16) * L * 4, cudaMemcpyDeviceToHost, s));
+  SB_CUDA(cudaStreamSynchronize(s));
+  memcpy(out_results_host, t->results_pinned, size_t(16) * L);
+  memcpy(out_tokens_host, t->results_pinned + 4 * L, size_t(16) * L * 4);
+  if (flags & SB_TARGET_ADVANCE) {  // the exact bound again: the furthest lane
+    uint32_t most = 0;
+    for (uint32_t l = 0; l < L; ++l) most = std::max(most, t->results_pinned[4 * l]);
+    m.committedHost = std::min(m.config().max_context, before + most);
+  }
   return SB_OK;
 }
 

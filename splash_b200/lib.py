@@ -189,12 +189,14 @@ class SbKvLayer(ctypes.Structure):
 class SbAttnStoreArgs(ctypes.Structure):
     _fields_ = [("qkv", _P), ("q_norm", _P), ("k_norm", _P), ("cos_tab", _P), ("sin_tab", _P), ("page_table", _P),
                 ("queries", _P), ("cache", SbKvLayer), ("committed_dev", _P),
-                ("rows", _U), ("q_heads", _U), ("gated", _U), ("pairs", _U), ("qkv_stride", _U), ("committed", _U)]
+                ("rows", _U), ("q_heads", _U), ("gated", _U), ("pairs", _U), ("qkv_stride", _U), ("committed", _U),
+                ("lanes", _U), ("page_table_stride", _U)]
 
 
 class SbAttnArgs(ctypes.Structure):
     _fields_ = [("queries", _P), ("qkv", _P), ("page_table", _P), ("tree", _P), ("out", _P), ("cache", SbKvLayer), ("committed_dev", _P),
-                ("rows", _U), ("q_heads", _U), ("gated", _U), ("qkv_stride", _U), ("out_stride", _U), ("committed", _U)]
+                ("rows", _U), ("q_heads", _U), ("gated", _U), ("qkv_stride", _U), ("out_stride", _U), ("committed", _U),
+                ("lanes", _U), ("page_table_stride", _U)]
 
 
 class SbGdnTape(ctypes.Structure):
@@ -208,20 +210,21 @@ class SbGdnArgs(ctypes.Structure):
                 ("rows", _U), ("pending_rows", _U), ("key_heads", _U), ("value_heads", _U), ("qkvz_stride", _U),
                 ("ab_stride", _U), ("hidden_stride", _U), ("tiled", _U),
                 ("gate_weight", _P), ("gate_input", _P), ("gate_k", _U), ("gate_input_stride", _U),
-                ("tree", _P), ("pending_path_dev", _P), ("pending_path", _U), ("flags", _U)]
+                ("tree", _P), ("pending_path_dev", _P), ("pending_path", _U), ("flags", _U), ("lanes", _U), ("reserved", _U)]
 
 
 class SbSampleArgs(ctypes.Structure):
     _fields_ = [("logits", _P), ("input_tokens", _P), ("uniforms", _P), ("selected", _P), ("workspace", _P),
                 ("rows", _U), ("vocab", _U), ("logit_stride", _U), ("temperature", _F),
                 ("min_p", _F), ("top_k", _U), ("top_p", _F), ("cut_out", _P),
-                ("candidate_ids", _P), ("candidate_q", _P), ("draws", _P)]
+                ("candidate_ids", _P), ("candidate_q", _P), ("draws", _P), ("lanes", _U), ("reserved", _U)]
 
 
 class SbPenaltyArgs(ctypes.Structure):
     _fields_ = [("logits", ctypes.c_void_p), ("words", ctypes.c_void_p), ("input_tokens", ctypes.c_void_p), ("tree", ctypes.c_void_p),
                 ("rows", ctypes.c_uint32), ("vocab", ctypes.c_uint32), ("logit_stride", ctypes.c_uint32),
-                ("repetition", ctypes.c_float), ("presence", ctypes.c_float), ("frequency", ctypes.c_float)]
+                ("repetition", ctypes.c_float), ("presence", ctypes.c_float), ("frequency", ctypes.c_float),
+                ("lanes", ctypes.c_uint32), ("reserved", ctypes.c_uint32)]
 
 
 class SbMoeRouteArgs(ctypes.Structure):
@@ -239,7 +242,7 @@ class SbMoeExpertArgs(ctypes.Structure):
 
 class SbAcceptArgs(ctypes.Structure):
     _fields_ = [("input_tokens", _P), ("tree", _P), ("tokens", _P), ("results", _P), ("stop_tokens", _P),
-                ("rows", _U), ("remaining", _U), ("n_stop", _U)]
+                ("rows", _U), ("remaining", _U), ("n_stop", _U), ("lanes", _U)]
 
 
 def _bind_ops():

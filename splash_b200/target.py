@@ -16,7 +16,7 @@ class SbTargetConfig(ctypes.Structure):
                 ("page_tokens", _U), ("kv_scale_f16", _U), ("max_context", _U),
                 ("fmt_proj", _U), ("fmt_down", _U), ("fmt_head", _U), ("fmt_embed", _U),
                 ("gated_attention", _U), ("tiled_heads", _U), ("tp_world", _U), ("tp_rank", _U),
-                ("moe_experts", _U), ("moe_top_k", _U), ("moe_intermediate", _U), ("reserved", _U)]
+                ("moe_experts", _U), ("moe_top_k", _U), ("moe_intermediate", _U), ("lanes", _U)]
 
 
 # The benchmark configurations' shapes (weights are synthetic; see quant fixtures and sb_target_randomize).
@@ -51,6 +51,8 @@ def _bind():
     l.sb_target_step.argtypes = [_P, _P, _U, _F, _U]
     l.sb_target_verify.argtypes = [_P, _P, _P, _P, _U, _F, _U, _P, _P]
     l.sb_target_verify_tree.argtypes = [_P, _P, _P, _P, _P, _U, _F, _U, _P, _P]
+    l.sb_target_reset_lanes.argtypes = [_P, _P]
+    l.sb_target_verify_lanes.argtypes = [_P, _P, _P, _P, _U, _F, _U, _P, _P]
     l.sb_target_stats.argtypes = [_P, _U, ctypes.POINTER(_U), ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64),
                                   ctypes.POINTER(ctypes.c_uint64)]
     l._target_bound = True
@@ -82,18 +84,21 @@ class Target:
         lib.check(self.l.sb_target_tensor(self.handle, layer, name.encode(), ctypes.byref(p), ctypes.byref(n)))
         return p.value, n.value
 
-    def upload(self, layer, name, array):
+    def upload(self, layer, name, array, lane=0):
+        """`lane`: the lane's share of a per-lane tensor (the tensor is an array over the lanes)."""
         a = np.ascontiguousarray(array)
         p, n = self.tensor(layer, name)
-        assert a.nbytes <= n, (name, a.nbytes, n)
-        lib.check(self.l.sb_upload(p, a.ctypes.data_as(_P), a.nbytes, None))
+        share = n // max(1, self.cfg.lanes) if lane else n
+        assert a.nbytes <= share, (name, a.nbytes, share)
+        lib.check(self.l.sb_upload(p + lane * share, a.ctypes.data_as(_P), a.nbytes, None))
         lib.stream_sync()
 
-    def download(self, layer, name, dtype, shape):
+    def download(self, layer, name, dtype, shape, lane=0):
         out = np.empty(shape, dtype)
         p, n = self.tensor(layer, name)
-        assert out.nbytes <= n, (name, out.nbytes, n)
-        lib.check(self.l.sb_download(out.ctypes.data_as(_P), p, out.nbytes, None))
+        share = n // max(1, self.cfg.lanes) if lane else n
+        assert out.nbytes <= share, (name, out.nbytes, share)
+        lib.check(self.l.sb_download(out.ctypes.data_as(_P), p + lane * share, out.nbytes, None))
         lib.stream_sync()
         return out
 
@@ -105,6 +110,26 @@ class Target:
 
     def reset(self, committed):
         lib.check(self.l.sb_target_reset(self.handle, committed))
+
+    def reset_lanes(self, committed):
+        c = np.ascontiguousarray(committed, np.uint32)
+        assert len(c) == max(1, self.cfg.lanes)
+        lib.check(self.l.sb_target_reset_lanes(self.handle, c.ctypes.data_as(_P)))
+
+    def verify_lanes(self, tokens, uniforms=None, temperature=0.0, flags=0, stream=None):
+        """One step of every lane from host buffers: tokens [lanes, rows]; uniforms [lanes, 80] for a sampled policy.
+        Returns per lane (retained tokens, retained, accepted, retained_rows mask)."""
+        tokens = np.ascontiguousarray(tokens, np.uint32)
+        lanes, rows = tokens.shape
+        assert lanes == max(1, self.cfg.lanes)
+        slots = np.zeros((lanes, 16), np.uint32)
+        slots[:, :rows] = tokens
+        u = None if uniforms is None else np.ascontiguousarray(uniforms, np.float32)
+        assert u is None or u.shape == (lanes, 80)
+        out_t, out_r = np.zeros((lanes, 16), np.uint32), np.zeros((lanes, 4), np.uint32)
+        lib.check(self.l.sb_target_verify_lanes(self.handle, stream, slots.ctypes.data_as(_P), None if u is None else u.ctypes.data_as(_P),
+                                                rows, temperature, flags, out_t.ctypes.data_as(_P), out_r.ctypes.data_as(_P)))
+        return [(out_t[l, :out_r[l, 0]].copy(), int(out_r[l, 0]), int(out_r[l, 1]), int(out_r[l, 2])) for l in range(lanes)]
 
     def step(self, rows=16, temperature=0.0, flags=GRAPH, stream=None):
         lib.check(self.l.sb_target_step(self.handle, stream, rows, temperature, flags))

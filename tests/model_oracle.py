@@ -75,10 +75,18 @@ def make_state(cfg, committed, seed=1):
     return s
 
 
-def upload(t, w, s, cut=lambda layer, name, array: array):
-    """Uploads weights `w` and state `s` into the device target `t`; `cut` takes a rank's share of each array."""
+def upload(t, w, s, cut=lambda layer, name, array: array, lane=0):
+    """Uploads weights `w` and state `s` into the device target `t`; `cut` takes a rank's share of each array. With `lane`
+    the state goes into that lane's share of every state tensor (w may be empty for the lanes after the first)."""
     for (layer, name), arr in w.items():
         t.upload(layer, name, cut(layer, name, arr))
+    _up = t.upload
+    if lane:
+        class _Lane:
+            @staticmethod
+            def upload(layer, name, array):
+                _up(layer, name, array, lane=lane)
+        t = _Lane
     for key, val in s.items():
         if not isinstance(key, tuple):
             continue

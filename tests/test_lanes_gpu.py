@@ -1,0 +1,268 @@
+"""Steps of several lanes (concurrent requests stepped together, the reference's StepRows / SplashLaneRows:
+runtime/ops/LaneRows.hpp:36-62, runtime/metal/abi/VerifyTree.h:38-45): lane l's rows at 16 l of every row-indexed buffer,
+per-lane state buffers arrays over the lanes. The operators with `lanes` against the same operator called a lane at a
+time, and whole steps of a 4-lane target against 4 independent oracle lanes."""
+import ctypes
+
+import numpy as np
+import pytest
+
+import model_oracle as mo
+import oracle_lib as ol
+from test_ops_gpu import DevKv, bf16_randn
+
+pytestmark = pytest.mark.gpu
+P = ol.ptr
+
+
+def _setup():
+    from splash_b200 import lib
+    lib.init(0)
+    return lib, lib.ops(), ol.bind_ops(ol.load())
+
+
+def test_gdn_lanes_equal_the_lanes_one_at_a_time():
+    """3 lanes with their own cells, tapes, pending rows and row counts' worth of inputs: bit-equal to three one-lane calls."""
+    lib, l, o = _setup()
+    rng = np.random.default_rng(11)
+    L, KH, VH, D, rows = 3, 4, 8, 128, 13
+    KW, VW = KH * D, VH * D
+    C = 2 * KW + VW
+    stride = C + VW
+    up = lib.DeviceBuffer.from_numpy
+    qkvz, b, a = bf16_randn(rng, (16 * L, stride)), bf16_randn(rng, (16 * L, VH)), bf16_randn(rng, (16 * L, VH))
+    conv_w, dt_bias = bf16_randn(rng, (C, 4), 0.4), bf16_randn(rng, (VH,), 0.5)
+    a_scale = (-np.exp(rng.uniform(-3, 0.5, VH))).astype(np.float32)
+    norm_w = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    cs_in = bf16_randn(rng, (L, 3, C))
+    state = (rng.standard_normal((L, VH, D, D)) * 0.05).astype(np.float32)
+    pend = dict(inputs=bf16_randn(rng, (16 * L, C)), k=bf16_randn(rng, (16 * L, KW), 0.09), v=bf16_randn(rng, (16 * L, VW), 0.5),
+                beta=ol.f2bf(rng.uniform(0.1, 0.9, (16 * L, VH)).astype(np.float32)),
+                decay=rng.uniform(0.5, 1.0, (16 * L, VH)).astype(np.float32))
+    pending_rows = np.array([5, 0, 16], np.uint32)
+    pending_path = np.zeros(L, np.uint32)
+    d = {n: up(x) for n, x in dict(qkvz=qkvz, b=b, a=a, conv_w=conv_w, a_scale=a_scale, dt_bias=dt_bias, norm_w=norm_w, cs_in=cs_in,
+                                   state=state, pr=pending_rows, pp=pending_path).items()}
+    dp = {n: up(x) for n, x in pend.items()}
+    step_shapes = dict(inputs=((16 * L, C), np.uint16), k=((16 * L, KW), np.uint16), v=((16 * L, VW), np.uint16),
+                       beta=((16 * L, VH), np.uint16), decay=((16 * L, VH), np.float32))
+
+    def run(lanes):
+        ds = {n: lib.DeviceBuffer(int(np.prod(s)) * np.dtype(t).itemsize) for n, (s, t) in step_shapes.items()}
+        dcs, dst, dh = lib.DeviceBuffer(cs_in.nbytes), lib.DeviceBuffer(state.nbytes), lib.DeviceBuffer(16 * L * VW * 2)
+        for x in (dcs, dst, dh, *ds.values()):
+            x.fill(0)
+
+        def call(lane, n):
+            off = lambda buf, per: buf.ptr + lane * per
+            row = lambda buf, w, size: buf.ptr + lane * 16 * w * size
+            tape = lambda t: lib.SbGdnTape(row(t["inputs"], C, 2), row(t["k"], KW, 2), row(t["v"], VW, 2), row(t["beta"], VH, 2),
+                                           row(t["decay"], VH, 4))
+            ga = lib.SbGdnArgs(row(d["qkvz"], stride, 2), row(d["b"], VH, 2), row(d["a"], VH, 2), d["conv_w"].ptr, d["a_scale"].ptr,
+                               d["dt_bias"].ptr, d["norm_w"].ptr, off(d["cs_in"], 3 * C * 2), off(dcs, 3 * C * 2),
+                               off(d["state"], VH * D * D * 4), off(dst, VH * D * D * 4), tape(dp), tape(ds), row(dh, VW, 2),
+                               d["pr"].ptr + 4 * lane, rows, 0, KH, VH, stride, VH, VW, 0)
+            ga.pending_path_dev = d["pp"].ptr + 4 * lane
+            ga.lanes = n
+            lib.check(l.sb_gdn_verify(None, ctypes.byref(ga)))
+
+        if lanes:
+            call(0, L)
+        else:
+            for lane in range(L):
+                call(lane, 1)
+        lib.stream_sync()
+        assert lib.device_status() == 0
+        out = dict(cs=dcs.to_numpy(np.uint16, cs_in.shape), state=dst.to_numpy(np.float32, state.shape),
+                   hidden=dh.to_numpy(np.uint16, (16 * L, VW)))
+        out.update({n: ds[n].to_numpy(t, s) for n, (s, t) in step_shapes.items()})
+        return out
+
+    one, many = run(False), run(True)
+    for n in one:
+        assert np.array_equal(one[n].view(np.uint8), many[n].view(np.uint8)), n
+    assert np.abs(many["state"][1]).max() > 0 and many["hidden"][16 * 2: 16 * 2 + rows].any()
+
+
+@pytest.mark.parametrize("kernel", [0, 1])
+def test_attention_lanes_match_the_oracle_lane_by_lane(kernel):
+    """4 lanes at positions 3000 / 17 / 1024 / 0 with their own page tables over one pool: the store bit-exact, the outputs
+    within the one-lane gates, for each lane against the oracle run on that lane alone."""
+    lib, l, o = _setup()
+    lib.check(l.sb_set_attention_kernel(kernel))
+    rng = np.random.default_rng(21)
+    L, QH, KVH, D, PT, rows, pairs = 4, 8, 2, 128, 64, 16, 16
+    committed = np.array([3000, 17, 1024, 0], np.uint32)
+    per_lane = (int(committed.max()) + rows + PT - 1) // PT + 1
+    pages = per_lane * L
+    host = ol.HostKv(pages, KVH, D, PT, True)
+    host.fill_random(rng)
+    table = rng.permutation(pages).astype(np.uint32).reshape(L, per_lane)   # lanes' pages interleaved in the pool
+    stride = QH * 2 * D + 2 * KVH * D
+    qkv = bf16_randn(rng, (16 * L, stride), 1.5)
+    qn, kn = (1 + 0.1 * rng.standard_normal(D)).astype(np.float32), (1 + 0.1 * rng.standard_normal(D)).astype(np.float32)
+    inv = (1e6 ** (-np.arange(pairs) / pairs)).astype(np.float32)
+    pos = (committed[:, None] + np.arange(16)[None, :]).astype(np.uint32).reshape(-1)
+    c, s = np.zeros((16 * L, pairs), np.float32), np.zeros((16 * L, pairs), np.float32)
+    o.so_rope_tables(P(pos), 16 * L, P(inv), pairs, 1.0, P(c), P(s))
+    dev = DevKv(lib, host)
+    want_q = np.zeros((16 * L, QH, D), np.uint16)
+    want = np.zeros((16 * L, QH * D), np.float64)
+    desc = host.desc()
+    for lane in range(L):
+        r0 = 16 * lane
+        q1 = np.zeros((rows, QH, D), np.uint16)
+        o.so_attn_store(P(qkv[r0:]), stride, rows, QH, 1, P(qn), P(kn), P(c[r0:]), P(s[r0:]), pairs, ctypes.byref(desc),
+                        P(table[lane]), int(committed[lane]), P(q1))
+        w16, w64 = np.zeros((rows, QH * D), np.uint16), np.zeros((rows, QH, D), np.float64)
+        o.so_attention(P(q1), P(qkv[r0:]), stride, rows, QH, 1, ctypes.byref(desc), P(table[lane]), int(committed[lane]), None,
+                       P(w16), QH * D, P(w64))
+        want_q[r0:r0 + rows], want[r0:r0 + rows] = q1, w64.reshape(rows, -1)
+    b = {n: lib.DeviceBuffer.from_numpy(x) for n, x in dict(qkv=qkv, qn=qn, kn=kn, c=c, s=s, table=table, committed=committed).items()}
+    qd, od = lib.DeviceBuffer(want_q.nbytes), lib.DeviceBuffer(16 * L * QH * D * 2)
+    sa = lib.SbAttnStoreArgs(b["qkv"].ptr, b["qn"].ptr, b["kn"].ptr, b["c"].ptr, b["s"].ptr, b["table"].ptr, qd.ptr, dev.desc(lib),
+                             b["committed"].ptr, rows, QH, 1, pairs, stride, int(committed.max()), L, per_lane)
+    lib.check(l.sb_attn_store(None, ctypes.byref(sa)))
+    aa = lib.SbAttnArgs(qd.ptr, b["qkv"].ptr, b["table"].ptr, None, od.ptr, dev.desc(lib), b["committed"].ptr, rows, QH, 1, stride,
+                        QH * D, int(committed.max()), L, per_lane)
+    lib.check(l.sb_attn_verify(None, ctypes.byref(aa)))
+    lib.stream_sync()
+    assert lib.device_status() == 0
+    lib.check(l.sb_set_attention_kernel(0))
+    assert np.array_equal(qd.to_numpy(np.uint16, want_q.shape), want_q)
+    k, v, ks, vs = dev.download()
+    assert np.array_equal(k, host.k) and np.array_equal(v, host.v) and np.array_equal(ks, host.ks) and np.array_equal(vs, host.vs)
+    got = ol.bf2f(od.to_numpy(np.uint16, (16 * L, QH * D))).astype(np.float64)
+    for lane in range(L):
+        g, w = got[16 * lane:16 * lane + rows], want[16 * lane:16 * lane + rows]
+        cos = (g * w).sum() / np.sqrt((g * g).sum() * (w * w).sum())
+        assert cos > 0.9995 and np.abs(g - w).max() < max(0.02, 4e-3 * np.abs(w).max()), lane
+
+
+def test_selection_penalties_and_acceptance_of_lanes_equal_the_lanes_one_at_a_time():
+    lib, l, o = _setup()
+    rng = np.random.default_rng(31)
+    L, rows, V = 5, 9, 6000
+    logits = (rng.standard_normal((16 * L, V)) * 3).astype(np.float32)
+    tokens = rng.integers(0, V, 16 * L).astype(np.uint32)
+    for lane in range(L):                      # lane `lane` accepts `lane` draft tokens when greedy
+        for r in range(min(lane, rows - 1)):
+            tokens[16 * lane + r + 1] = np.argmax(logits[16 * lane + r])
+    uniforms = rng.random(80 * L).astype(np.float32)
+    words = rng.integers(0, 3, (L, V)).astype(np.uint32) * (rng.random((L, V)) < 0.05)
+    tree = np.tile(lib.chain_tree(16), (L, 1))
+    up = lib.DeviceBuffer.from_numpy
+
+    def run(lanes, temperature):
+        dl, dt, du, dw, dtree = up(logits), up(tokens), up(uniforms), up(words), up(tree)
+        sel, res = lib.DeviceBuffer(16 * L * 4), lib.DeviceBuffer(16 * L)
+        ws = lib.DeviceBuffer(int(l.sb_sample_workspace_bytes(16 * L, V)))
+        sel.fill(0), res.fill(0)
+
+        def call(lane, n):
+            r4 = 16 * lane * 4
+            pa = lib.SbPenaltyArgs(dl.ptr + r4 * V, dw.ptr + lane * V * 4, dt.ptr + r4, dtree.ptr + 16 * lane * 8, rows, V, V, 1.2, 0.3, 0.1)
+            pa.lanes = n
+            lib.check(l.sb_sample_penalize(None, ctypes.byref(pa)))
+            sa = lib.SbSampleArgs(dl.ptr + r4 * V, dt.ptr + r4, du.ptr + 80 * lane * 4 if temperature else None, sel.ptr + r4, ws.ptr,
+                                  rows, V, V, temperature, 0.0, 0, 1.0)
+            sa.lanes = n
+            lib.check(l.sb_sample_verify(None, ctypes.byref(sa)))
+            aa = lib.SbAcceptArgs(dt.ptr + r4, dtree.ptr + 16 * lane * 8, sel.ptr + r4, res.ptr + 16 * lane, None, rows, 16, 0)
+            aa.lanes = n
+            lib.check(l.sb_accept(None, ctypes.byref(aa)))
+
+        if lanes:
+            call(0, L)
+        else:
+            for lane in range(L):
+                call(lane, 1)
+        lib.stream_sync()
+        assert lib.device_status() == 0
+        return dl.to_numpy(np.float32, logits.shape), sel.to_numpy(np.uint32, (L, 16)), res.to_numpy(np.uint32, (L, 4))
+
+    for temperature in (0.0, 0.8):
+        one, many = run(False, temperature), run(True, temperature)
+        for x, y in zip(one, many):
+            assert np.array_equal(x.view(np.uint32), y.view(np.uint32))
+    greedy = run(True, 0.0)[2]
+    assert len(set(greedy[:, 0].tolist())) >= 3          # the lanes did accept different lengths
+
+
+def build_lanes(lanes, positions, seed=0):
+    from splash_b200 import lib, target
+    lib.init(0)
+    cfg = dict(target.TINY, fmt_head=lib.FMT_Q4K, lanes=lanes)     # the many-row projections take Q4_K rows
+    t = target.Target(**cfg)
+    w = mo.make_weights(cfg, seed)
+    states = [mo.make_state(cfg, int(positions[i]), seed + 1 + i) for i in range(lanes)]
+    for i, s in enumerate(states):
+        mo.upload(t, w if i == 0 else {}, s, lane=i)
+    t.reset_lanes(positions)
+    return lib, target, t, cfg, w, states
+
+
+@pytest.mark.parametrize("flags_name", ["eager", "graph"])
+def test_tiny_model_of_four_lanes_matches_four_oracle_lanes(flags_name):
+    """4 lanes at different positions, drafts of different quality (so unequal accept lengths), 3 committed steps. Per
+    lane: logits within the many-row kernel's distance of the oracle's (weights and inputs rounded to half there), and the
+    retained tokens, accept length and path equal wherever the top-2 gap of the retained rows exceeds that distance."""
+    positions = np.array([2048, 300, 1537, 1000], np.uint32)
+    lib, target, t, cfg, w, states = build_lanes(4, positions)
+    flags = target.ADVANCE | (target.GRAPH if flags_name == "graph" else 0)
+    match = [0.95, 0.3, 0.7, 0.0]
+    first = [17, 400, 9000, 31999]
+    compared, lengths = 0, []
+    for step in range(3):
+        blocks = np.stack([mo.draft_chain(cfg, w, states[i], first[i], rows=16, p_match=match[i], seed=10 * step + i) for i in range(4)])
+        wants = [mo.verify_step(cfg, w, states[i], blocks[i], advance=True) for i in range(4)]
+        got = t.verify_lanes(blocks, flags=flags)
+        assert lib.device_status() == 0
+        logits = t.download(-1, "logits", np.float32, (64, cfg["vocab"]))
+        for i in range(4):
+            want, (tokens, retained, accepted, mask) = wants[i], got[i]
+            mine = logits[16 * i:16 * i + 16]
+            scale = np.abs(want["logits"]).max()
+            err = np.abs(mine - want["logits"])
+            assert err.max() <= 2e-2 * scale and np.median(err) <= 2e-3 * scale, (step, i)
+            top2 = np.sort(want["logits"], axis=1)[:, -2:]
+            clear = (top2[:, 1] - top2[:, 0]) > 2.5 * err.max(axis=1)
+            if clear[:want["retained"]].all():
+                assert (retained, accepted, mask) == (want["retained"], want["accepted"], want["mask"]), (step, i)
+                assert np.array_equal(tokens, want["tokens"]), (step, i)
+                compared += 1
+                lengths.append(retained)
+            else:  # follow the device where the oracle's own choice was a near tie
+                states[i]["committed"] += retained - want["retained"]
+                states[i]["pending_rows"] = retained
+            first[i] = int(tokens[-1])
+    assert compared >= 9 and len(set(lengths)) >= 3, (compared, lengths)
+
+
+def test_lane_of_a_four_lane_step_does_not_depend_on_the_other_lanes():
+    """The same lane 2 next to different neighbours: its logits and results are bit-equal."""
+    positions = np.array([2048, 300, 1537, 1000], np.uint32)
+    lib, target, t, cfg, w, states = build_lanes(4, positions, seed=3)
+    rng = np.random.default_rng(5)
+    blocks = rng.integers(0, cfg["vocab"], (4, 16)).astype(np.uint32)
+    a = t.verify_lanes(blocks)
+    la = t.download(-1, "logits", np.float32, (64, cfg["vocab"]))[32:48].copy()
+    blocks2 = rng.integers(0, cfg["vocab"], (4, 16)).astype(np.uint32)
+    blocks2[2] = blocks[2]
+    t.reset_lanes(np.array([100, 2048, 1537, 5], np.uint32))   # (the furthest lane as before: the same split plan)
+    b = t.verify_lanes(blocks2)
+    lb = t.download(-1, "logits", np.float32, (64, cfg["vocab"]))[32:48]
+    assert np.array_equal(la.view(np.uint32), lb.view(np.uint32))
+    assert a[2][1:] == b[2][1:] and np.array_equal(a[2][0], b[2][0])
+
+
+def test_lanes_reject_what_they_do_not_step():
+    from splash_b200 import lib, target
+    lib.init(0)
+    with pytest.raises(lib.SbError):
+        target.Target(**dict(target.TINY, lanes=4))                          # Q6_K head
+    with pytest.raises(lib.SbError):
+        target.Target(**dict(target.TINY, fmt_head=lib.FMT_Q4K, lanes=33))
+    t = target.Target(**dict(target.TINY, fmt_head=lib.FMT_Q4K, lanes=2))
+    with pytest.raises(lib.SbError):
+        t.verify(np.arange(16, dtype=np.uint32))                             # the one-lane entry
