@@ -52,6 +52,15 @@ def measured_peak():
         return 6650.0, "fallback"
 
 
+def measured_peak_tensor():
+    """Dense bf16 TFLOP/s of a library GEMM timed alone (the burst figure: the projection launch is timed alone too)."""
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["bf16_tflops"]), "measured"
+    except Exception:
+        return 1590.0, "fallback"
+
+
 class ClockSampler:
     """nvidia-smi samples of one GPU's SM clock and throttle reasons while the timed region runs."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
@@ -190,6 +199,7 @@ def main():
     ap.add_argument("--moe", action="store_true", help="the 35B-A3B-shaped MoE model, one lane of 16 rows at an 8K context (an extra measurement, not the benchmark)")
     ap.add_argument("--tp-shots", type=int, default=0, choices=(0, 1, 2), help="how tensor-parallel shares travel (sb_tp_set_exchange); 0: by the number of ranks")
     ap.add_argument("--parallel", default="tp", choices=("tp", "replicas"), help="what N > 1 GPUs do: one lane tensor-parallel, or N lanes")
+    ap.add_argument("--lanes", type=int, default=1, help="concurrent requests stepped together on each GPU, 16 rows each (an extra measurement, not the benchmark)")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -197,6 +207,10 @@ def main():
     if args.moe:
         workload = "35B-A3B-shaped MoE verify (256 experts + shared, top 8), Q4_K, ONE lane of 16 rows (not the configuration's 32 lanes), 8K INT8 paged KV, greedy"
         args.tiny, args.parallel = True, "replicas"  # (the extra legs of the benchmark are for the 27B workload only)
+    L = max(1, args.lanes)
+    if L > 1:
+        workload = f"{L} lanes stepped together: " + workload.replace("batch 1", f"batch {L}").replace("Q4_K_M mix", "all projections Q4_K")
+        args.parallel = "replicas"
 
     if args.impl == "reference":
         if rank != 0:
@@ -248,17 +262,19 @@ def main():
             t.close()
             tensor_parallel = False
     if not tensor_parallel:
+        if L > 1:  # (the many-row projection kernel takes Q4_K rows: the whole model Q4_K, not the Q4_K_M mix)
+            cfg.update(lanes=L, fmt_down=lib.FMT_Q4K, fmt_head=lib.FMT_Q4K)
         t = target.Target(**cfg)
         t.randomize(1234 + rank, context)
-    lanes = 1 if tensor_parallel else world
+    lanes = 1 if tensor_parallel else world * L
     warm = max(args.warmup, 3)
     # The lane is held at its context length, so every step does the same work, and keeps FOLD_ROWS pending rows, so
     # every step also folds that many rows of the previous step's tape into the Gated-DeltaNet state, as a committing
     # cycle with that accept length would.
     flags = target.GRAPH | target.KEEP_PENDING
     rng = np.random.default_rng(0 if tensor_parallel else rank)
-    t.upload(-1, "tokens", rng.integers(0, cfg["vocab"], ROWS).astype(np.uint32))
-    t.upload(-1, "pending_rows", np.array([FOLD_ROWS], np.uint32))
+    t.upload(-1, "tokens", rng.integers(0, cfg["vocab"], ROWS * L).astype(np.uint32))
+    t.upload(-1, "pending_rows", np.full(L, FOLD_ROWS, np.uint32))
 
     def barrier():
         lib.stream_sync(stream)
@@ -289,13 +305,16 @@ def main():
 
     # ---- end to end through the host-facing call, pinned host buffers ----
     pinned = ctypes.c_void_p()
-    lib.check(lib.load().sb_host_alloc(4096, ctypes.byref(pinned)))
+    lib.check(lib.load().sb_host_alloc(3 * 4096, ctypes.byref(pinned)))
     host = np.ctypeslib.as_array((ctypes.c_uint32 * 1024).from_address(pinned.value))
-    host[:ROWS] = rng.integers(0, cfg["vocab"], ROWS)
+    host[:ROWS * L] = rng.integers(0, cfg["vocab"], ROWS * L)
     l = target._bind()
-    out_t, out_r = pinned.value + 1024, pinned.value + 2048
+    out_t, out_r = pinned.value + 4096, pinned.value + 2 * 4096
     def verify_once():
-        lib.check(l.sb_target_verify(t.handle, stream, pinned.value, None, ROWS, 0.0, flags, out_t, out_r))
+        if L > 1:
+            lib.check(l.sb_target_verify_lanes(t.handle, stream, pinned.value, None, ROWS, 0.0, flags, out_t, out_r))
+        else:
+            lib.check(l.sb_target_verify(t.handle, stream, pinned.value, None, ROWS, 0.0, flags, out_t, out_r))
     for _ in range(2):
         verify_once()
     barrier()
@@ -309,8 +328,14 @@ def main():
     e2e_ms = reduce_max(e2.elapsed_ms(e3)) / args.steps
 
     # ---- one checked step after the timed loops: the step computed something sane, and the same thing on every rank ----
-    _, retained, _, _ = t.verify(host[:ROWS].copy(), flags=flags, stream=stream)
-    logits = t.download(-1, "logits", np.float32, (ROWS, cfg["vocab"]))
+    if L > 1:
+        per_lane = t.verify_lanes(host[:ROWS * L].copy().reshape(L, ROWS), flags=flags, stream=stream)
+        retained = min(r[1] for r in per_lane)  # (the bounds below then hold for every lane)
+        if max(r[1] for r in per_lane) > ROWS:
+            retained = 0
+    else:
+        _, retained, _, _ = t.verify(host[:ROWS].copy(), flags=flags, stream=stream)
+    logits = t.download(-1, "logits", np.float32, (ROWS * L, cfg["vocab"]))
     finite = bool(np.isfinite(logits).all())
     bits = logits.view(np.uint32).astype(np.uint64)
     checksum = float(int((bits * (np.arange(bits.size, dtype=np.uint64).reshape(bits.shape) % 65521 + 1)).sum() % (1 << 52)))
@@ -331,7 +356,38 @@ def main():
     # ---- the dominant kernel alone: the one-pass Q4_K gate/up projection over each layer's weights ----
     peak, peak_kind = measured_peak()
     roofline = None
-    if not args.tiny:
+    if not args.tiny and L > 1:
+        # the many-row projection on the tensor cores: the one-pass gate/up launch over 16 x lanes rows
+        H, I, M = cfg["hidden"], cfg["intermediate"], ROWS * L
+        x = lib.DeviceBuffer(M * H * 2 + 256)
+        x.upload(rng.standard_normal((M, H)).astype(np.float16).view(np.uint16))
+        prep = lib.DeviceBuffer(int(lib.load().sb_linear_wide_prepared_bytes(M, H)))
+        lib.check(lib.load().sb_linear_wide_prepare(stream, x.ptr, M, H, H, None, prep.ptr, 0))
+        out = lib.DeviceBuffer(M * I * 2 + 256)
+        ptrs = [(t.tensor(layer, "ffn_gate")[0], t.tensor(layer, "ffn_up")[0]) for layer in range(cfg["layers"])]
+        def gate_up(i):
+            g, u = ptrs[i % len(ptrs)]
+            lib.linear(g, None, out.ptr, lib.FMT_Q4K, I, H, M, weights2=u, prepared=prep.ptr, epilogue=lib.EP_GATE_UP, stream=stream,
+                       flags=lib.LINEAR_PDL)
+        for i in range(8):
+            gate_up(i)
+        lib.stream_sync(stream)
+        n = 64
+        k0, k1 = lib.Event(), lib.Event()
+        k0.record(stream)
+        for i in range(n):
+            gate_up(i + 8)
+        k1.record(stream)
+        k1.sync()
+        launch_ms = k0.elapsed_ms(k1) / n
+        flops = 2.0 * M * 2 * I * H
+        algo = 2 * I * (H // 256) * 144 + M * H * 2 + M * I * 2
+        tensor_peak = measured_peak_tensor()
+        achieved = flops / launch_ms / 1e9
+        roofline = {"bound": "tensor", "kernel": "linear_wide_kernel<Q4_K> gate/up 2x[%dx%d], M=%d (Q4_K dequantized to half, tcgen05, accumulators in tensor memory)" % (I, H, M),
+                    "achieved": achieved, "peak": tensor_peak[0], "unit": "TFLOP/s", "frac": achieved / tensor_peak[0], "peak_kind": tensor_peak[1],
+                    "algorithmic_bytes": algo, "hbm_gbs": algo / launch_ms / 1e6, "launch_us": launch_ms * 1e3, "traffic": None}
+    elif not args.tiny:
         H, I = cfg["hidden"], cfg["intermediate"]
         if tensor_parallel:
             I = tp.share(cfg, world, rank)["intermediate"]  # the launch as this rank runs it
@@ -378,7 +434,7 @@ def main():
                    "fold": f"held lane that keeps {FOLD_ROWS} pending rows: every timed step folds {FOLD_ROWS} tape rows into the GDN state",
                    "parallelism": "tp1" if world == 1 else (f"tp{world}: one lane, shares exchanged through peer memory over NVLink in the input conversions" if tensor_parallel else f"{world} independent replicas (lanes)" + (f"; {fell_back}" if fell_back else "")),
                    "l2": "inputs exceed L2: one step streams %.1f GB of weights" % (stats["weight_bytes"] / 1e9), "cuda_graph": True, "pdl": True},
-        "e2e": {"value": lanes * ROWS / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": ROWS * 4, "d2h_bytes_per_step": 16 + ROWS * 4},
+        "e2e": {"value": lanes * ROWS / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": ROWS * 4 * L, "d2h_bytes_per_step": (16 + ROWS * 4) * L},
         "gpu_launches": stats["launches"] * args.steps,
         "launches_per_step": stats["launches"],
         "step_roofline": {"bytes_per_step": step_bytes, "weight_bytes": stats["weight_bytes"], "kv_bytes": stats["kv_bytes"],

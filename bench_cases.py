@@ -93,10 +93,6 @@ def case_linear(a):
     x = lib.DeviceBuffer.from_numpy(bf16_bits(rng.standard_normal((slots, k))))
     l = lib.load()
     if a.rows > 16:  # the many-row kernel (tensor memory): its own conversion, once
-        l.sb_linear_wide_prepared_bytes.restype = ctypes.c_uint64
-        l.sb_linear_wide_prepared_bytes.argtypes = [ctypes.c_uint32, ctypes.c_uint32]
-        l.sb_linear_wide_prepare.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p,
-                                             ctypes.c_void_p, ctypes.c_uint32]
         prep = lib.DeviceBuffer(int(l.sb_linear_wide_prepared_bytes(a.rows, k)))
         lib.check(l.sb_linear_wide_prepare(None, x.ptr, a.rows, k, k, None, prep.ptr, 0))
     else:

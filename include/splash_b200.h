@@ -205,6 +205,15 @@ SB_API int sb_linear(void *stream, const SbLinearArgs *args);
 SB_API uint64_t sb_linear_wide_prepared_bytes(uint32_t rows, uint32_t k);
 SB_API int sb_linear_wide_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride, const void *norm_weight,
                                   void *prepared_out, uint32_t flags);
+/* Split K for narrow projections (n below what fills the SMs): with SB_EPILOGUE_PARTIALS the launch divides k into
+ * sb_linear_wide_splits(n, k) ranges and out receives every range's sums, fp32 [splits][rows][out_stride];
+ * sb_linear_wide_prepare_sum is then the next projection's conversion over x = bf16(residual + the splits' sums in split
+ * order), x also written to sum_out (bf16 [rows, sum_stride]): the residual epilogue moved in front of its consumer, as
+ * sb_linear_prepare_sum does for 16 rows. */
+SB_API uint32_t sb_linear_wide_splits(uint32_t n, uint32_t k);
+SB_API int sb_linear_wide_prepare_sum(void *stream, const float *partials, uint32_t splits, uint32_t partial_stride, const void *residual,
+                                      uint32_t residual_stride, void *sum_out, uint32_t sum_stride, uint32_t rows, uint32_t k,
+                                      const void *norm_weight, void *prepared_out, uint32_t flags);
 SB_API int sb_linear_wide(void *stream, const SbLinearArgs *args);
 
 /* The plan sb_linear will use for a shape: k-slices, CTAs, tile rows, ring stages, shared bytes.

@@ -132,7 +132,7 @@ class QwenTarget {
   static constexpr uint32_t kMaxPartialSlices = 16;
   uint32_t packedStride_ = 0;
   uint32_t lanes_ = 1, pagesPerLane_ = 0;
-  Buffer widePrepared_[2];  // conversions for the many-row projection kernel (steps of several lanes)
+  Buffer widePrepared_[2], widePartials_;  // conversions for the many-row projection kernel (steps of several lanes)
   void encodeVerifyLanes(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool keepPending, bool drawsGiven);
   uint64_t weightBytes_ = 0, moeExpertBytes_ = 0;
   uint32_t moeLayers_ = 0;
@@ -240,8 +240,11 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   partials_ = Buffer::allocate(size_t(kMaxPartialSlices) * 16 * H * 4);
   const uint32_t widest = std::max(std::max(H, c.intermediate), std::max(gdn_.valueWidth(), c.q_heads * D));
   for (auto &p : prepared_) p = Buffer::allocate(ops::Linear::preparedBytes((widest + 255) / 256 * 256));
-  if (L > 1)
+  if (L > 1) {
     for (auto &p : widePrepared_) p = Buffer::allocate(ops::Linear::wideBytes(uint32_t(R), (widest + 255) / 256 * 256));
+    const uint32_t splits = std::max(ops::Linear::wideSplits(H, c.intermediate), std::max(ops::Linear::wideSplits(H, gdn_.valueWidth()), ops::Linear::wideSplits(H, c.q_heads * D)));
+    widePartials_ = Buffer::allocate(size_t(splits) * R * H * 4);
+  }
   for (auto &h : hidden) h = Buffer::allocate(R * H * 2);
   logits = tp_ ? tp_->gathered() : Buffer::allocate(R * c.vocab * 4);
   tokens = Buffer::allocate(R * 4), selected = Buffer::allocate(R * 4), results = Buffer::allocate(16 * L);
@@ -449,9 +452,19 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
   if (c.rotary_pairs) RoPE::addTreeTables(graph, positions, invFreq, cosine, sine, R, 1.0f, c.rotary_pairs);
   Embedding::add(graph, tokens, embedding_, hidden[0], R, H);
   uint32_t cur = 0;
+  // The projections back into the hidden width (out_proj, down) are narrow: they divide k over the SMs and leave their
+  // splits' sums in widePartials_; the conversion in front of the next projection adds them onto the residual and writes
+  // the new hidden rows. `owed`: splits the rows of hidden[cur] still lack.
+  uint32_t owed = 0;
+  auto convert = [&](const Buffer *norm) {
+    if (!owed) return Linear::prepareWide(graph, hidden[cur], R, H, H, norm, widePrepared_[0]);
+    PreparedInput in = Linear::prepareWideSum(graph, widePartials_, owed, hidden[cur], hidden[cur ^ 1], R, H, norm, widePrepared_[0]);
+    cur ^= 1, owed = 0;
+    return in;
+  };
   for (LayerWeights &w : layers_) {
     // mixer: h += mixer(norm(h))
-    PreparedInput in = Linear::prepareWide(graph, hidden[cur], R, H, H, &w.attnNorm.buffer, widePrepared_[0]);
+    PreparedInput in = convert(&w.attnNorm.buffer);
     Linear::addWide(graph, w.inProj, nullptr, in, R, Epilogue::None, nullptr, packed_, packedStride_);
     uint32_t mixedWidth;
     if (w.attention) {
@@ -482,16 +495,16 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
       ++graph.launches;
     }
     PreparedInput mixedIn = Linear::prepareWide(graph, mixed_, R, mixedWidth, mixedWidth, nullptr, widePrepared_[1]);
-    Linear::addWide(graph, w.outProj, nullptr, mixedIn, R, Epilogue::Residual, &hidden[cur], hidden[cur ^ 1], H);
-    cur ^= 1;
+    Linear::addWide(graph, w.outProj, nullptr, mixedIn, R, Epilogue::Partials, nullptr, widePartials_, H);
+    owed = Linear::wideSplits(H, mixedWidth);
     // FFN: h += down(silu(gate(norm(h))) * up(norm(h)))
-    PreparedInput ffnIn = Linear::prepareWide(graph, hidden[cur], R, H, H, &w.ffnNorm.buffer, widePrepared_[0]);
+    PreparedInput ffnIn = convert(&w.ffnNorm.buffer);
     Linear::addWide(graph, w.ffnGate, &w.ffnUp, ffnIn, R, Epilogue::GateUp, nullptr, act_, c.intermediate);
     PreparedInput actIn = Linear::prepareWide(graph, act_, R, c.intermediate, c.intermediate, nullptr, widePrepared_[1]);
-    Linear::addWide(graph, w.ffnDown, nullptr, actIn, R, Epilogue::Residual, &hidden[cur], hidden[cur ^ 1], H);
-    cur ^= 1;
+    Linear::addWide(graph, w.ffnDown, nullptr, actIn, R, Epilogue::Partials, nullptr, widePartials_, H);
+    owed = Linear::wideSplits(H, c.intermediate);
   }
-  PreparedInput headIn = Linear::prepareWide(graph, hidden[cur], R, H, H, &outputNorm_.buffer, widePrepared_[0]);
+  PreparedInput headIn = convert(&outputNorm_.buffer);
   Linear::addWide(graph, output_, nullptr, headIn, R, Epilogue::None, nullptr, logits, c.vocab, true);
   // selection, acceptance, commit: every lane its own rows, uniforms and results
   if (penalties.active()) {

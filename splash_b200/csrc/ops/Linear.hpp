@@ -106,14 +106,35 @@ class Linear {
     graph.launches += (rows + 127) / 128;
     return {scratch, 0xFFFFu, inputSize};  // (format tag of the wide layout)
   }
-  // One Q4_K segment over `rows` rows: epilogues None / Residual / UpWithGate, or GateUp with `up` given.
+  // k-splits of a projection left as Epilogue::Partials, and the conversion that adds them: x = bf16(residual + the
+  // splits' sums in split order) goes to `sumOut` (the new hidden rows), then the conversion of x as prepareWide does it.
+  static uint32_t wideSplits(uint32_t outputSize, uint32_t inputSize) { return sb_linear_wide_splits(outputSize, inputSize); }
+  static PreparedInput prepareWideSum(CommandGraph &graph, const Buffer &partials, uint32_t splits, const Buffer &residual, const Buffer &sumOut,
+                                      uint32_t rows, uint32_t inputSize, const Buffer *normWeight, const Buffer &scratch) {
+    requireBytes(partials, size_t(splits) * rows * inputSize * 4, "Linear::prepareWideSum partial sums");
+    requireBytes(residual, size_t(rows) * inputSize * 2, "Linear::prepareWideSum residual");
+    requireBytes(sumOut, size_t(rows) * inputSize * 2, "Linear::prepareWideSum sum");
+    requireBytes(scratch, wideBytes(rows, inputSize), "Linear::prepareWideSum scratch");
+    if (normWeight) requireBytes(*normWeight, size_t(inputSize) * 4, "Linear::prepareWideSum norm weight");
+    check(sb_linear_wide_prepare_sum(graph.stream, partials.as<float>(), splits, inputSize, residual.as(), inputSize, sumOut.as(), inputSize, rows,
+                                     inputSize, normWeight ? normWeight->as() : nullptr, scratch.as(), graph.pdl ? SB_LINEAR_PDL : 0));
+    graph.launches += (rows + 127) / 128;
+    return {scratch, 0xFFFFu, inputSize};
+  }
+  // One Q4_K segment over `rows` rows: epilogues None / Residual / UpWithGate, GateUp with `up` given, or Partials (output:
+  // fp32 [wideSplits][rows][outputStride]).
   static void addWide(CommandGraph &graph, const QuantizedSegment &s, const QuantizedSegment *up, const PreparedInput &prepared, uint32_t rows,
                       Epilogue epilogue, const Buffer *aux, const Buffer &output, uint32_t outputStride, bool float32 = false) {
     if (prepared.format != 0xFFFFu || prepared.inputSize != s.inputSize) throw std::invalid_argument("Linear::addWide: not a wide conversion of this width");
     if ((epilogue == Epilogue::GateUp) != (up != nullptr)) throw std::invalid_argument("Linear::addWide: the up tensor comes with GateUp");
     requireBytes(s.rows, size_t(s.outputSize) * sb_row_bytes(s.format, s.inputSize), "Linear::addWide segment rows");
     if (up) requireBytes(up->rows, size_t(up->outputSize) * sb_row_bytes(up->format, up->inputSize), "Linear::addWide up rows");
-    requireBytes(output, (size_t(rows - 1) * outputStride + s.outputSize) * (float32 ? 4 : 2), "Linear::addWide output");
+    if (epilogue == Epilogue::Partials) {
+      float32 = true;
+      requireBytes(output, size_t(wideSplits(s.outputSize, s.inputSize)) * rows * outputStride * 4, "Linear::addWide partial sums");
+    } else {
+      requireBytes(output, (size_t(rows - 1) * outputStride + s.outputSize) * (float32 ? 4 : 2), "Linear::addWide output");
+    }
     if (aux) requireBytes(*aux, (size_t(rows - 1) * outputStride + s.outputSize) * 2, "Linear::addWide residual or gate");
     SbLinearArgs a{};
     a.weights = s.rows.as(), a.weights2 = up ? up->rows.as() : nullptr, a.prepared = prepared.buffer.as();

@@ -60,7 +60,20 @@ struct WideParams {
   uint32_t n, rows, rows_padded, aux_stride, out_stride, epilogue, out_f32;
   uint32_t nsb, items, x_groups, x_stage_bytes, gate_up;
   uint32_t halves;  // 128-row halves per item: 2, or 1 when whole items would leave SMs idle  // x_groups: super-blocks of X the ring holds
+  // Split K (SB_EPILOGUE_PARTIALS): an item is (tile, split), items = tiles x splits; a split's sums over its range of
+  // super-blocks go to out as fp32 [split][rows_total][out_stride], for the next input conversion to add in split order.
+  uint32_t splits, rows_total, row0;
 };
+// An item's tile and its range of super-blocks.
+struct WideItem {
+  uint32_t tile, split, sb0, sb1;
+};
+__device__ __forceinline__ WideItem wide_item(const WideParams &p, uint32_t item) {
+  WideItem w;
+  w.tile = item / p.splits, w.split = item - w.tile * p.splits;
+  w.sb0 = w.split * p.nsb / p.splits, w.sb1 = (w.split + 1) * p.nsb / p.splits;
+  return w;
+}
 #ifdef SB_DIAG
 // Cycle counters of the roles of CTA 0 (diagnostic builds only): [role][what], read back through sb_linear_wide_timing.
 __device__ unsigned long long g_wide_timing[8][8];
@@ -99,6 +112,10 @@ struct WidePrepParams {
   const float *norm_w;
   uint8_t *out;
   uint32_t rows, rows_padded, k, x_stride;
+  // With `partials`: x = bf16(residual + the splits' sums added in split order), written to x (the new hidden rows) first.
+  const float *partials;  // fp32 [splits][rows_total][partial_stride], this pass's first row at row0
+  const uint16_t *residual;
+  uint32_t splits, rows_total, row0, partial_stride, residual_stride;
 };
 __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const WidePrepParams p) {
   __shared__ float red_s[2 * (kWidePrepThreads / 32)];
@@ -107,6 +124,29 @@ __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const Wi
   pdl_wait();
   const bool live = tok < p.rows;
   const uint32_t chunks = p.k / 8;  // 8 inputs each
+  if (p.partials && live) {
+    // The projection ahead left its k-splits' sums: add them in split order onto the residual, round once, and keep the
+    // rows (the new hidden state). A thread reads back below only what it wrote itself.
+    uint16_t *xw = const_cast<uint16_t *>(p.x);
+    for (uint32_t c = tid; c < chunks; c += kWidePrepThreads) {
+      const uint4 raw = *reinterpret_cast<const uint4 *>(p.residual + size_t(tok) * p.residual_stride + 8 * c);
+      const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (uint32_t sp = 0; sp < p.splits; ++sp) {
+        const float4 *src = reinterpret_cast<const float4 *>(p.partials + (size_t(sp) * p.rows_total + p.row0 + tok) * p.partial_stride + 8 * c);
+        const float4 a = __ldcg(src), b = __ldcg(src + 1);
+        acc[0] += a.x, acc[1] += a.y, acc[2] += a.z, acc[3] += a.w, acc[4] += b.x, acc[5] += b.y, acc[6] += b.z, acc[7] += b.w;
+      }
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t lo = float_to_bf16_bits(acc[2 * j] + bf16_bits_to_float(u[j] & 0xffffu));
+        const uint32_t hi = float_to_bf16_bits(acc[2 * j + 1] + bf16_bits_to_float(u[j] >> 16));
+        o[j] = lo | (hi << 16);
+      }
+      *reinterpret_cast<uint4 *>(xw + size_t(tok) * p.x_stride + 8 * c) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
   float ss = 0.0f, mx = 0.0f;
   for (uint32_t c = tid; c < chunks && live; c += kWidePrepThreads) {
     const uint4 raw = *reinterpret_cast<const uint4 *>(p.x + size_t(tok) * p.x_stride + 8 * c);
@@ -237,8 +277,9 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
     const uint64_t policy = policy_evict_first();
     uint32_t rs = 0, rphase = 0, rcount = 0;
     bool ok = true;
-    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x)
-      for (uint32_t sb = 0; sb < p.nsb && ok; ++sb)
+    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
+      const WideItem w = wide_item(p, item);
+      for (uint32_t sb = w.sb0; sb < w.sb1 && ok; ++sb)
         for (uint32_t tn = 0; tn < p.halves && ok; ++tn, ++rcount) {
           if (rcount >= kWideRawStages && !wide_warp_wait(&raw_empty[rs], rphase ^ 1, true)) {
             if (lane == 0) wide_expired(p.status, 1);
@@ -247,10 +288,11 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
           }
           if (lane == 0) {
             mbar_arrive_expect_tx(&raw_full[rs], kWideRawStage);
-            tma_load_2d(raw_ring + rs * kWideRawStage, &maps.m[tn], int(sb * 36), int(p.gate_up ? item * 128 : item * 128 * p.halves + tn * 128), &raw_full[rs], policy, true);
+            tma_load_2d(raw_ring + rs * kWideRawStage, &maps.m[tn], int(sb * 36), int(p.gate_up ? w.tile * 128 : w.tile * 128 * p.halves + tn * 128), &raw_full[rs], policy, true);
           }
           if (++rs == kWideRawStages) rs = 0, rphase ^= 1;
         }
+    }
     // Do not leave while copies are in flight: every stage issued is waited for (bounded) before the warp returns.
     for (uint32_t f = rcount > kWideRawStages ? rcount - kWideRawStages : 0; f < rcount; ++f)
       if (!wide_warp_wait(&raw_empty[f % kWideRawStages], (f / kWideRawStages) & 1, true)) break;
@@ -264,8 +306,9 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
     uint32_t xg = 0, xphase = 0, xcount = 0;
     bool ok = true;
     const uint32_t group_bytes = 4 * p.x_stage_bytes;
-    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x)
-      for (uint32_t sb = 0; sb < p.nsb && ok; ++sb, ++xcount) {
+    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
+      const WideItem w = wide_item(p, item);
+      for (uint32_t sb = w.sb0; sb < w.sb1 && ok; ++sb, ++xcount) {
         if (xcount >= p.x_groups && !wide_warp_wait(&x_empty[xg], xphase ^ 1, true)) {
           if (lane == 0) wide_expired(p.status, 2);
           ok = false;
@@ -277,6 +320,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
         }
         if (++xg == p.x_groups) xg = 0, xphase ^= 1;
       }
+    }
     for (uint32_t f = xcount > p.x_groups ? xcount - p.x_groups : 0; f < xcount; ++f)
       if (!wide_warp_wait(&x_empty[f % p.x_groups], (f / p.x_groups) & 1, true)) break;
   } else if (warp >= kWideMmaWarp0) {
@@ -295,7 +339,8 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
           dphase ^= 1;
           if (!ok) { wide_expired(p.status, 3); break; }
         }
-        for (uint32_t sb = 0; sb < p.nsb && ok; ++sb) {
+        const WideItem w = wide_item(p, item);
+        for (uint32_t sb = w.sb0; sb < w.sb1 && ok; ++sb) {
           {
             WIDE_T0();
             ok = mbar_wait(&x_full[xg], xphase);
@@ -318,7 +363,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
 #pragma unroll
             for (uint32_t i = 0; i < 8; ++i) {  // K-step i of this half of the super-block
               const uint64_t b = umma_smem_desc(xbase + (8 * hh + i) * p.rows_padded * 32, 128, 256);
-              umma_f16_ts(d0, a0 + i * 8, b, idesc, !(sb == 0 && hh == 0 && i == 0));
+              umma_f16_ts(d0, a0 + i * 8, b, idesc, !(sb == w.sb0 && hh == 0 && i == 0));
             }
             umma_commit(&a_empty[ab]);
             if (tn == 0) WIDE_TADD(1, 1);
@@ -338,8 +383,9 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
     const uint32_t ab = 2 * tn + h;
     uint32_t rs = tn, rphase = 0, scount = 0;  // super-blocks this warp has expanded
     bool ok = tn < p.halves;
-    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x)
-      for (uint32_t sb = 0; sb < p.nsb && ok; ++sb, ++scount) {
+    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
+      const WideItem w = wide_item(p, item);
+      for (uint32_t sb = w.sb0; sb < w.sb1 && ok; ++sb, ++scount) {
         {
           WIDE_T0();
           if (!wide_warp_wait(&raw_full[rs], rphase)) {
@@ -381,6 +427,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
           if (warp == 0) WIDE_TADD(0, 3);
         }
       }
+    }
   } else {
     // ---- epilogue: a thread per weight row of each half of the item ----
     const uint32_t q = warp & 3, row = 32 * q + lane;
@@ -422,6 +469,21 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
 #pragma unroll
             for (int j = 0; j < 16; ++j)
               if (c + j < p.rows) dst[size_t(c + j) * p.out_stride] = o[j];
+          }
+        }
+      } else if (p.epilogue == SB_EPILOGUE_PARTIALS) {
+        const WideItem w = wide_item(p, item);
+        for (uint32_t half = 0; half < p.halves; ++half) {
+          const uint32_t col = w.tile * 128 * p.halves + half * 128 + row;
+          float *dst = static_cast<float *>(p.out) + (size_t(w.split) * p.rows_total + p.row0) * p.out_stride + col;
+          for (uint32_t c = 0; c < p.rows_padded; c += 16) {
+            float v[16];
+            tmem_ld16_wait(t0 + half * kWideDCols + c, v);
+            if (col < p.n) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (c + j < p.rows) dst[size_t(c + j) * p.out_stride] = v[j] * scale_back[c + j];
+            }
           }
         }
       } else {
@@ -482,12 +544,13 @@ static int wide_check(const SbLinearArgs *a, const char *who) {
   SB_REQUIRE(a->rows >= 1, "%s: no rows", who);
   SB_REQUIRE(a->k && a->k % 256 == 0 && a->n && a->n % 8 == 0, "%s: k = %u is not a multiple of 256 or n = %u not a multiple of 8", who, a->k, a->n);
   SB_REQUIRE(a->weights && a->out && (a->x || a->prepared), "%s: null weights, out, or neither x nor prepared", who);
-  SB_REQUIRE(a->epilogue <= SB_EPILOGUE_GATE_UP, "%s: epilogue %u (none, residual, up-with-gate or one-pass gate/up)", who, a->epilogue);
+  SB_REQUIRE(a->epilogue <= SB_EPILOGUE_PARTIALS, "%s: epilogue %u (none, residual, up-with-gate, one-pass gate/up or k-split sums)", who, a->epilogue);
+  SB_REQUIRE(a->epilogue != SB_EPILOGUE_PARTIALS || a->out_f32, "%s: k-split sums are fp32", who);
   SB_REQUIRE((a->epilogue == SB_EPILOGUE_GATE_UP) == (a->weights2 != nullptr), "%s: weights2 is given exactly with the gate/up epilogue", who);
   SB_REQUIRE((a->epilogue == SB_EPILOGUE_RESIDUAL || a->epilogue == SB_EPILOGUE_UP_WITH_GATE) == (a->aux != nullptr),
              "%s: aux is given exactly with the residual and up-with-gate epilogues", who);
   SB_REQUIRE(a->out_stride >= a->n && (!a->aux || a->aux_stride >= a->n), "%s: a stride is below n", who);
-  SB_REQUIRE(!(a->out_f32 && a->epilogue != SB_EPILOGUE_NONE), "%s: an fp32 destination takes no epilogue", who);
+  SB_REQUIRE(!(a->out_f32 && a->epilogue != SB_EPILOGUE_NONE && a->epilogue != SB_EPILOGUE_PARTIALS), "%s: an fp32 destination takes no epilogue", who);
   SB_REQUIRE((reinterpret_cast<uintptr_t>(a->weights) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->weights2) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(a->prepared) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->x) & 15) == 0,
              "%s: weights, x and prepared must be 16-byte aligned", who);
@@ -509,6 +572,15 @@ extern "C" __attribute__((visibility("default"))) int sb_linear_wide_timing(unsi
 }
 #endif
 
+// k-splits of a projection left as SB_EPILOGUE_PARTIALS: as many as fill the SMs with two-half items, three super-blocks
+// each at least.
+static uint32_t wide_splits(uint32_t n, uint32_t k, int sm_count) {
+  const uint32_t tiles = (n + 255) / 256, nsb = k / 256;
+  if (!tiles || !nsb) return 1;
+  return std::max(1u, std::min(uint32_t(sm_count) / tiles, nsb / 3));
+}
+extern "C" uint32_t sb_linear_wide_splits(uint32_t n, uint32_t k) { return ctx().ready ? wide_splits(n, k, ctx().sm_count) : 0; }
+
 extern "C" uint64_t sb_linear_wide_prepared_bytes(uint32_t rows, uint32_t k) {
   if (!rows || !k || k % 256) return 0;
   const uint64_t passes = (rows + kWideMaxRows - 1) / kWideMaxRows;
@@ -516,8 +588,26 @@ extern "C" uint64_t sb_linear_wide_prepared_bytes(uint32_t rows, uint32_t k) {
 }
 
 // One pass = up to 128 rows; pass i of the conversion starts at sb_linear_wide_prepared_bytes(128, k) * i.
+static int wide_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride, const void *norm_weight, void *prepared_out,
+                        uint32_t flags, const float *partials, uint32_t splits, uint32_t partial_stride, const void *residual, uint32_t residual_stride);
+
 extern "C" int sb_linear_wide_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride, const void *norm_weight,
                                       void *prepared_out, uint32_t flags) {
+  return wide_prepare(stream, x, rows, k, x_stride, norm_weight, prepared_out, flags, nullptr, 0, 0, nullptr, 0);
+}
+
+extern "C" int sb_linear_wide_prepare_sum(void *stream, const float *partials, uint32_t splits, uint32_t partial_stride, const void *residual,
+                                          uint32_t residual_stride, void *sum_out, uint32_t sum_stride, uint32_t rows, uint32_t k,
+                                          const void *norm_weight, void *prepared_out, uint32_t flags) {
+  SB_REQUIRE(partials && residual && sum_out && splits >= 1 && splits <= 64, "sb_linear_wide_prepare_sum: null partials, residual or destination, or %u splits", splits);
+  SB_REQUIRE(partial_stride >= k && partial_stride % 4 == 0 && residual_stride >= k && residual_stride % 8 == 0,
+             "sb_linear_wide_prepare_sum: partial_stride %u or residual_stride %u", partial_stride, residual_stride);
+  SB_REQUIRE(((reinterpret_cast<uintptr_t>(partials) | reinterpret_cast<uintptr_t>(residual)) & 15) == 0, "sb_linear_wide_prepare_sum: pointers must be 16-byte aligned");
+  return wide_prepare(stream, sum_out, rows, k, sum_stride, norm_weight, prepared_out, flags, partials, splits, partial_stride, residual, residual_stride);
+}
+
+static int wide_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride, const void *norm_weight, void *prepared_out,
+                        uint32_t flags, const float *partials, uint32_t splits, uint32_t partial_stride, const void *residual, uint32_t residual_stride) {
   SB_NEED_DEVICE();
   SB_REQUIRE(x && prepared_out && rows >= 1, "sb_linear_wide_prepare: null x or destination, or no rows");
   SB_REQUIRE(k && k % 256 == 0 && x_stride >= k && x_stride % 8 == 0, "sb_linear_wide_prepare: k = %u is not a multiple of 256, or x_stride %u", k, x_stride);
@@ -527,7 +617,9 @@ extern "C" int sb_linear_wide_prepare(void *stream, const void *x, uint32_t rows
   for (uint32_t r0 = 0, pass = 0; r0 < rows; r0 += kWideMaxRows, ++pass) {
     const uint32_t n = std::min(kWideMaxRows, rows - r0), padded = (n + 15) / 16 * 16;
     WidePrepParams pp{static_cast<const uint16_t *>(x) + size_t(r0) * x_stride, static_cast<const float *>(norm_weight),
-                      static_cast<uint8_t *>(prepared_out) + pass * pass_bytes, n, padded, k, x_stride};
+                      static_cast<uint8_t *>(prepared_out) + pass * pass_bytes, n, padded, k, x_stride,
+                      partials, residual ? static_cast<const uint16_t *>(residual) + size_t(r0) * residual_stride : nullptr,
+                      splits, rows, r0, partial_stride, residual_stride};
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(padded), cfg.blockDim = dim3(kWidePrepThreads), cfg.stream = as_stream(stream);
     cudaLaunchAttribute attr[1];
@@ -551,7 +643,7 @@ extern "C" int sb_linear_wide(void *stream, const SbLinearArgs *a) {
     if (st != SB_OK) return st;
     prepared = c.wide_prepared;
   }
-  const bool gate_up = a->epilogue == SB_EPILOGUE_GATE_UP;
+  const bool gate_up = a->epilogue == SB_EPILOGUE_GATE_UP, split_k = a->epilogue == SB_EPILOGUE_PARTIALS;
   WideMaps maps;
   const uint32_t row_bytes = uint32_t(sb_row_bytes(a->format, a->k));
   if (gate_up) {
@@ -578,13 +670,15 @@ extern "C" int sb_linear_wide(void *stream, const SbLinearArgs *a) {
     p.rows = std::min(kWideMaxRows, a->rows - r0), p.rows_padded = (p.rows + 15) / 16 * 16;
     const size_t esz = a->out_f32 ? 4 : 2;
     p.aux = a->aux ? static_cast<const uint16_t *>(a->aux) + size_t(r0) * a->aux_stride : nullptr;
-    p.out = static_cast<uint8_t *>(a->out) + size_t(r0) * a->out_stride * esz;
+    p.out = split_k ? static_cast<uint8_t *>(a->out) : static_cast<uint8_t *>(a->out) + size_t(r0) * a->out_stride * esz;
     p.status = c.status_dev;
     p.n = a->n, p.aux_stride = a->aux_stride, p.out_stride = a->out_stride, p.epilogue = a->epilogue, p.out_f32 = a->out_f32;
     p.nsb = a->k / 256, p.gate_up = gate_up;
     // Items of two halves read X once for 256 weight rows; where they would leave SMs idle, items of one half fill more.
-    p.halves = gate_up || (a->n + 255) / 256 >= uint32_t(c.sm_count) ? 2 : 1;
-    p.items = gate_up ? (a->n + 127) / 128 : (a->n + 128 * p.halves - 1) / (128 * p.halves);
+    p.halves = gate_up || split_k || (a->n + 255) / 256 >= uint32_t(c.sm_count) ? 2 : 1;
+    p.splits = split_k ? wide_splits(a->n, a->k, c.sm_count) : 1;
+    p.rows_total = a->rows, p.row0 = r0;
+    p.items = (gate_up ? (a->n + 127) / 128 : (a->n + 128 * p.halves - 1) / (128 * p.halves)) * p.splits;
     p.x_stage_bytes = p.rows_padded * 128;
     p.x_groups = std::min(kWideMaxXStages, kWideXBytes / (4 * p.x_stage_bytes));
     cudaLaunchConfig_t cfg = {};

@@ -68,6 +68,10 @@ def load():
         _lib.sb_linear_prepare.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32,
                                            ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32]
         _lib.sb_linear_prepared_bytes.restype = ctypes.c_uint64
+        _lib.sb_linear_wide_prepared_bytes.restype = ctypes.c_uint64
+        _lib.sb_linear_wide_prepared_bytes.argtypes = [ctypes.c_uint32, ctypes.c_uint32]
+        _lib.sb_linear_wide_prepare.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p,
+                                                ctypes.c_void_p, ctypes.c_uint32]
         _lib.sb_linear_prepare_sum.argtypes = ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32,
                                                 ctypes.c_void_p] + [ctypes.c_uint32] * 3 + [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p,
                                                                                             ctypes.c_uint32])

@@ -108,6 +108,48 @@ def test_wide_residual_gate_and_one_pass_gate_up():
     assert np.array_equal(one, two)
 
 
+@pytest.mark.parametrize("n,k,rows", [(512, 6144, 128), (1024, 17408, 80), (256, 1024, 40), (1280, 2816, 200)])
+def test_wide_k_split_sums_then_the_conversion_that_adds_them(n, k, rows):
+    """SB_EPILOGUE_PARTIALS leaves every k-range's sums; sb_linear_wide_prepare_sum adds them onto the residual in split order,
+    writes the new hidden rows and converts them. The hidden rows against the oracle's bound, and the conversion equal to a
+    plain conversion of those rows."""
+    import ctypes
+    lib = _setup()
+    l = lib.load()
+    l.sb_linear_wide_splits.argtypes = [ctypes.c_uint32] * 2
+    l.sb_linear_wide_prepare_sum.argtypes = ([ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32,
+                                              ctypes.c_void_p] + [ctypes.c_uint32] * 3 + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32])
+    rng = np.random.default_rng(n + rows)
+    W = qf.realistic(0, n, k, seed=k)
+    X = qf.activations(rows, k, seed=3)
+    res = ol.f2bf(rng.standard_normal((rows, n)).astype(np.float32))
+    splits = int(l.sb_linear_wide_splits(n, k))
+    assert 1 <= splits <= 64 and (splits > 1 or k < 1536 or n >= 148 * 256)
+    wd, xd, rd = lib.DeviceBuffer.from_numpy(W), lib.DeviceBuffer.from_numpy(X), lib.DeviceBuffer.from_numpy(res)
+    parts = lib.DeviceBuffer(splits * rows * n * 4)
+    parts.fill(0xFF)
+    lib.linear(wd.ptr, xd.ptr, parts.ptr, 0, n, k, rows, epilogue=lib.EP_PARTIALS, out_f32=True)
+    summed, norm_w = lib.DeviceBuffer(rows * n * 2), lib.DeviceBuffer.from_numpy((1 + 0.1 * rng.standard_normal(n)).astype(np.float32))
+    nbytes = int(l.sb_linear_wide_prepared_bytes(rows, n))
+    conv, conv2 = lib.DeviceBuffer(nbytes), lib.DeviceBuffer(nbytes)
+    conv.fill(0), conv2.fill(0)
+    lib.check(l.sb_linear_wide_prepare_sum(None, parts.ptr, splits, n, rd.ptr, n, summed.ptr, n, rows, n, norm_w.ptr, conv.ptr, 0))
+    lib.stream_sync()
+    assert lib.device_status() == 0
+    p = parts.to_numpy(np.float32, (splits, rows, n))
+    got = summed.to_numpy(np.uint16, (rows, n))
+    total = np.zeros((rows, n), np.float32)
+    for sp in range(splits):
+        total += p[sp]
+    assert np.array_equal(got, ol.f2bf(total + ol.bf2f(res)))              # the sum as stated: split order, then the residual
+    v, e = wide_bound(0, W, n, k, X, rows)
+    e = e + 2.0 ** -22 * splits * np.abs(v).max()                          # (fp32 additions of the splits)
+    assert (total >= v - e).all() and (total <= v + e).all()
+    lib.check(l.sb_linear_wide_prepare(None, summed.ptr, rows, n, n, norm_w.ptr, conv2.ptr, 0))
+    lib.stream_sync()
+    assert np.array_equal(conv.to_numpy(np.uint8, (nbytes,)), conv2.to_numpy(np.uint8, (nbytes,)))
+
+
 def test_wide_rejects_what_it_does_not_multiply():
     lib = _setup()
     d = lib.DeviceBuffer(1 << 20)
