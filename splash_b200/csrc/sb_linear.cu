@@ -1358,7 +1358,8 @@ extern "C" int sb_tp_prepare_sum(void *stream, void *group, uint32_t index, cons
 extern "C" int sb_linear(void *stream, const SbLinearArgs *a) {
   SB_NEED_DEVICE();
   SB_REQUIRE(a, "sb_linear: null arguments");
-  if (a->rows > uint32_t(kTokens)) return sb_linear_wide(stream, a);  // the many-row kernel (tensor memory, fp16 weights)
+  // The many-row kernel (tensor memory, fp16 weights): more than 16 rows, and every NVFP4 projection (given as its image).
+  if (a->rows > uint32_t(kTokens) || (a->flags & SB_LINEAR_WIDE_IMAGE) || a->format == SB_FMT_NVFP4) return sb_linear_wide(stream, a);
   SB_REQUIRE(a->weights && a->out && (a->x || a->prepared), "sb_linear: null weights, out, or neither x nor prepared");
   SB_REQUIRE(a->rows >= 1 && a->rows <= kTokens, "sb_linear: rows = %u outside 1..%d", a->rows, kTokens);
   SB_REQUIRE(a->epilogue <= SB_EPILOGUE_GATE_UP_PARTIALS, "sb_linear: unknown epilogue %u", a->epilogue);

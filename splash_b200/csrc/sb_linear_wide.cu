@@ -45,12 +45,22 @@ constexpr uint32_t kWideHeader = 1024;             // scale_back[256] floats (a 
 constexpr uint32_t kWideDequantWarps = 16, kWideEpilogueWarps = 4;  // dequant: (half of the item, inputs' half, quadrant)
 constexpr uint32_t kWideRawWarp = kWideDequantWarps + kWideEpilogueWarps, kWideXWarp = kWideRawWarp + 1, kWideMmaWarp0 = kWideXWarp + 1;
 constexpr uint32_t kWideThreads = 32 * (kWideMmaWarp0 + 2);  // 768
-constexpr uint32_t kWideRawStage = 128 * 144, kWideRawStages = 4;   // one (half, super-block) of an item: 18 KB
+// A super-block of a weight row as the kernel reads it, and the ring of 128-row stages it fits in shared memory.
+//   Q4_K   the native 144 bytes (4 stages of 18 KB)
+//   Q6_K   the image of sb_linear_wide_image, 224 bytes: low nibbles paired as Q4_K pairs them, the two high bits in a plane
+//          of their own, the sixteen scales as halves d * sc / row scale (3 stages of 28 KB)
+//   NVFP4  the image, 160 bytes: the nibbles in expansion order, the sixteen scales as halves e4m3 * g * 2^14 / row scale
+//          (4 stages of 20 KB)
+template <uint32_t FMT> struct WideFmt;
+template <> struct WideFmt<SB_FMT_Q4K> { static constexpr uint32_t kSb = 144, kStages = 4; };
+template <> struct WideFmt<SB_FMT_Q6K> { static constexpr uint32_t kSb = 224, kStages = 3; };
+template <> struct WideFmt<SB_FMT_NVFP4> { static constexpr uint32_t kSb = 160, kStages = 4; };
+constexpr uint32_t kWideMaxRawStages = 4;
 constexpr uint32_t kWideXBytes = 128 * 1024, kWideMaxXStages = 8;   // the X ring; a stage holds 64 inputs of every row
 constexpr uint32_t kWideABufs = 4, kWideACols = 64, kWideACol0 = 256, kWideDCols = 128, kWideTmemCols = 512;
 constexpr uint32_t kWideBarBytes = 1024;           // barriers, tensor-memory slot, then scale_back[128] at 512
 constexpr uint32_t kWideXOff = kWideBarBytes, kWideRawOff = kWideXOff + kWideXBytes;
-constexpr uint32_t kWideSmem = kWideRawOff + kWideRawStages * kWideRawStage;  // 205,824 bytes
+template <uint32_t FMT> constexpr uint32_t wide_smem() { return kWideRawOff + WideFmt<FMT>::kStages * 128 * WideFmt<FMT>::kSb; }  // 205,824 bytes for Q4_K
 
 struct WideParams {
   const uint8_t *prepared;  // header + units of 64 inputs: [k-step 4][row / 8][input / 8 (2)][row % 8][8 halves]
@@ -63,6 +73,7 @@ struct WideParams {
   // Split K (SB_EPILOGUE_PARTIALS): an item is (tile, split), items = tiles x splits; a split's sums over its range of
   // super-blocks go to out as fp32 [split][rows_total][out_stride], for the next input conversion to add in split order.
   uint32_t splits, rows_total, row0;
+  const float *row_scale[2];  // images: a power of two per weight row taken out of its scales (NULL for native Q4_K rows)
 };
 // An item's tile and its range of super-blocks.
 struct WideItem {
@@ -240,12 +251,81 @@ __device__ __forceinline__ void wide_expand_q4k(const uint8_t *row, uint32_t h, 
   }
 }
 
+__device__ __forceinline__ uint32_t wide_shift(uint32_t q, int from, int to) { return to >= from ? q << (to - from) : q >> (from - to); }
+
+// Inputs' half h of a Q6_K image row's super-block: half = fl16((u - 32) * s), u - 32 exact. The low nibbles of a pair of
+// 32-element groups share bytes as in Q4_K; a group in the high nibbles enters as 16 (u - 32) against s / 16.
+__device__ __forceinline__ void wide_expand_q6k(const uint8_t *row, uint32_t h, uint32_t (&r)[64]) {
+  const uint4 sc = *reinterpret_cast<const uint4 *>(row + 192 + 16 * h);  // 8 halves: the scales of elements 128 h ..
+  const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w};
+  const uint32_t k1024 = 0x64006400u;
+#pragma unroll
+  for (uint32_t pr = 0; pr < 2; ++pr) {
+    const uint8_t *ql = row + 32 * (2 * h + pr);
+    const uint4 qa = *reinterpret_cast<const uint4 *>(ql), qb = *reinterpret_cast<const uint4 *>(ql + 16);
+    const uint4 qh = *reinterpret_cast<const uint4 *>(row + 128 + 16 * (2 * h + pr));
+    const uint32_t w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w}, hw[4] = {qh.x, qh.y, qh.z, qh.w};
+    // the pair's four scales: low group's elements 0..15, 16..31, high group's 0..15, 16..31
+    const uint32_t sa = scw[2 * pr], sb = scw[2 * pr + 1];
+    const uint32_t s_lo[2] = {__byte_perm(sa, sa, 0x1010), __byte_perm(sa, sa, 0x3232)};
+    const uint32_t t0 = __byte_perm(sb, sb, 0x1010), t1 = __byte_perm(sb, sb, 0x3232);
+    const uint32_t s_hi[2] = {hmul2_u32(t0, 0x2c002c00u), hmul2_u32(t1, 0x2c002c00u)};  // / 16
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint32_t hi8 = w[c] >> 8, q = hw[c >> 1];
+      // Output j's two high bits sit at bits b + 2 j (and 16 higher) of the plane's word, b = 8 (c & 1). They go to
+      // [5:4] of each half beside a low nibble, to [9:8] beside a high nibble (16 u).
+      const int b = 8 * (c & 1);
+      const uint32_t f0 = wide_shift(q, b, 4), f1 = wide_shift(q, b + 2, 4), f2 = wide_shift(q, b + 4, 8), f3 = wide_shift(q, b + 6, 8);
+      const uint32_t v0 = and_or(f0, 0x00300030u, and_or(w[c], 0x000f000fu, k1024));
+      const uint32_t v1 = and_or(f1, 0x00300030u, and_or(hi8, 0x000f000fu, k1024));
+      const uint32_t v2 = and_or(f2, 0x03000300u, and_or(w[c], 0x00f000f0u, k1024));
+      const uint32_t v3 = and_or(f3, 0x03000300u, and_or(hi8, 0x00f000f0u, k1024));
+      r[32 * pr + 2 * c] = hmul2_u32(hsub2_u32(v0, 0x64206420u), s_lo[c >> 2]);           // 1024 + 32
+      r[32 * pr + 2 * c + 1] = hmul2_u32(hsub2_u32(v1, 0x64206420u), s_lo[c >> 2]);
+      r[32 * pr + 16 + 2 * c] = hmul2_u32(hsub2_u32(v2, 0x66006600u), s_hi[c >> 2]);      // 1024 + 512
+      r[32 * pr + 16 + 2 * c + 1] = hmul2_u32(hsub2_u32(v3, 0x66006600u), s_hi[c >> 2]);
+    }
+  }
+}
+
+// Inputs' half h of an NVFP4 image row's super-block. An e2m1 code's three magnitude bits at bits 11..9 of a half are
+// |value| * 2^-14 exactly (the subnormal 0.5 included), the sign goes to bit 15; the 2^14 is in the image's scales.
+__device__ __forceinline__ void wide_expand_nvfp4(const uint8_t *row, uint32_t h, uint32_t (&r)[64]) {
+  const uint4 sc = *reinterpret_cast<const uint4 *>(row + 128 + 16 * h);
+  const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w};
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const uint4 qv = *reinterpret_cast<const uint4 *>(row + 64 * h + 16 * g);
+    const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = 4 * g + i;  // word c of this half: elements 8 c .. 8 c + 7, scale c / 2
+      const uint32_t s2 = (c >> 1) & 1 ? __byte_perm(scw[c >> 2], 0, 0x3232) : __byte_perm(scw[c >> 2], 0, 0x1010);
+      const uint32_t x = w[i];
+      r[4 * c] = hmul2_u32(and_or(x << 9, 0x0e000e00u, (x << 12) & 0x80008000u), s2);
+      r[4 * c + 1] = hmul2_u32(and_or(x << 5, 0x0e000e00u, (x << 8) & 0x80008000u), s2);
+      r[4 * c + 2] = hmul2_u32(and_or(x << 1, 0x0e000e00u, (x << 4) & 0x80008000u), s2);
+      r[4 * c + 3] = hmul2_u32(and_or(x >> 3, 0x0e000e00u, x & 0x80008000u), s2);
+    }
+  }
+}
+
+template <uint32_t FMT>
+__device__ __forceinline__ void wide_expand(const uint8_t *row, uint32_t h, uint32_t (&r)[64]) {
+  if (FMT == SB_FMT_Q4K) wide_expand_q4k(row, h, r);
+  else if (FMT == SB_FMT_Q6K) wide_expand_q6k(row, h, r);
+  else wide_expand_nvfp4(row, h, r);
+}
+
+template <uint32_t FMT>
 __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const WideParams p, const __grid_constant__ WideMaps maps) {
+  constexpr uint32_t kWideRawStages = WideFmt<FMT>::kStages, kWideRawStage = 128 * WideFmt<FMT>::kSb;
   extern __shared__ __align__(128) uint8_t smem[];
   WIDE_KERNEL_T0();
   uint64_t *raw_full = reinterpret_cast<uint64_t *>(smem);        // [kWideRawStages]
-  uint64_t *raw_empty = raw_full + kWideRawStages;
-  uint64_t *x_full = raw_empty + kWideRawStages;                   // [kWideMaxXStages]
+  uint64_t *raw_empty = raw_full + kWideMaxRawStages;
+  uint64_t *x_full = raw_empty + kWideMaxRawStages;                   // [kWideMaxXStages]
   uint64_t *x_empty = x_full + kWideMaxXStages;
   uint64_t *a_full = x_empty + kWideMaxXStages;                    // [kWideABufs]
   uint64_t *a_empty = a_full + kWideABufs;
@@ -288,7 +368,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
           }
           if (lane == 0) {
             mbar_arrive_expect_tx(&raw_full[rs], kWideRawStage);
-            tma_load_2d(raw_ring + rs * kWideRawStage, &maps.m[tn], int(sb * 36), int(p.gate_up ? w.tile * 128 : w.tile * 128 * p.halves + tn * 128), &raw_full[rs], policy, true);
+            tma_load_2d(raw_ring + rs * kWideRawStage, &maps.m[tn], int(sb * (WideFmt<FMT>::kSb / 4)), int(p.gate_up ? w.tile * 128 : w.tile * 128 * p.halves + tn * 128), &raw_full[rs], policy, true);
           }
           if (++rs == kWideRawStages) rs = 0, rphase ^= 1;
         }
@@ -399,7 +479,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
         uint32_t r[64];
         {
           WIDE_T0();
-          wide_expand_q4k(raw_ring + rs * kWideRawStage + row * 144, h, r);
+          wide_expand<FMT>(raw_ring + rs * kWideRawStage + row * WideFmt<FMT>::kSb, h, r);
           __syncwarp();
           if (lane == 0) mbar_arrive(&raw_empty[rs]);  // the row's bytes are in registers
           if (warp == 0) WIDE_TADD(0, 1);
@@ -454,6 +534,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
       // activation overlap), then the stores of the rows that exist.
       if (p.gate_up) {
         const uint32_t col = item * 128 + row;
+        const float rg = p.row_scale[0] && col < p.n ? p.row_scale[0][col] : 1.0f, ru = p.row_scale[1] && col < p.n ? p.row_scale[1][col] : 1.0f;
         uint16_t *dst = static_cast<uint16_t *>(p.out) + col;
         for (uint32_t c = 0; c < p.rows_padded; c += 16) {
           float g[16], u[16];
@@ -463,7 +544,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const float s = scale_back[c + j];
-            o[j] = float_to_bf16_bits(round_bf16(u[j] * s) * silu_f(round_bf16(g[j] * s)));
+            o[j] = float_to_bf16_bits(round_bf16(u[j] * (s * ru)) * silu_f(round_bf16(g[j] * (s * rg))));
           }
           if (col < p.n) {
 #pragma unroll
@@ -475,6 +556,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
         const WideItem w = wide_item(p, item);
         for (uint32_t half = 0; half < p.halves; ++half) {
           const uint32_t col = w.tile * 128 * p.halves + half * 128 + row;
+          const float rw = p.row_scale[0] && col < p.n ? p.row_scale[0][col] : 1.0f;
           float *dst = static_cast<float *>(p.out) + (size_t(w.split) * p.rows_total + p.row0) * p.out_stride + col;
           for (uint32_t c = 0; c < p.rows_padded; c += 16) {
             float v[16];
@@ -482,7 +564,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
             if (col < p.n) {
 #pragma unroll
               for (int j = 0; j < 16; ++j)
-                if (c + j < p.rows) dst[size_t(c + j) * p.out_stride] = v[j] * scale_back[c + j];
+                if (c + j < p.rows) dst[size_t(c + j) * p.out_stride] = v[j] * (scale_back[c + j] * rw);
             }
           }
         }
@@ -490,6 +572,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
         for (uint32_t half = 0; half < p.halves; ++half) {
           const uint32_t col = item * 128 * p.halves + half * 128 + row;
           const bool live = col < p.n;
+          const float rw = p.row_scale[0] && live ? p.row_scale[0][col] : 1.0f;
           for (uint32_t c = 0; c < p.rows_padded; c += 16) {
             float v[16];
             tmem_ld16_wait(t0 + half * kWideDCols + c, v);
@@ -503,7 +586,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
             }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-              v[j] *= scale_back[c + j];
+              v[j] *= scale_back[c + j] * rw;
               if (p.epilogue == SB_EPILOGUE_RESIDUAL) v[j] += a[j];
               else if (p.epilogue == SB_EPILOGUE_UP_WITH_GATE) v[j] = round_bf16(v[j]) * silu_f(a[j]);
             }
@@ -540,7 +623,10 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
 
 static int wide_check(const SbLinearArgs *a, const char *who) {
   SB_REQUIRE(a, "%s: null arguments", who);
-  SB_REQUIRE(a->format == SB_FMT_Q4K, "%s: format %u (the many-row kernel multiplies Q4_K rows)", who, a->format);
+  SB_REQUIRE(a->format == SB_FMT_Q4K || a->format == SB_FMT_Q6K || a->format == SB_FMT_NVFP4,
+             "%s: format %u (the many-row kernel multiplies Q4_K rows, and Q6_K and NVFP4 images)", who, a->format);
+  SB_REQUIRE((a->format == SB_FMT_Q4K) != ((a->flags & SB_LINEAR_WIDE_IMAGE) != 0),
+             "%s: Q6_K and NVFP4 weights are given as their image (sb_linear_wide_image, SB_LINEAR_WIDE_IMAGE); Q4_K rows as they are", who);
   SB_REQUIRE(a->rows >= 1, "%s: no rows", who);
   SB_REQUIRE(a->k && a->k % 256 == 0 && a->n && a->n % 8 == 0, "%s: k = %u is not a multiple of 256 or n = %u not a multiple of 8", who, a->k, a->n);
   SB_REQUIRE(a->weights && a->out && (a->x || a->prepared), "%s: null weights, out, or neither x nor prepared", who);
@@ -572,6 +658,92 @@ extern "C" __attribute__((visibility("default"))) int sb_linear_wide_timing(unsi
 }
 #endif
 
+// ---- the images of Q6_K and NVFP4 rows ----
+// One CTA per weight row: the row's largest scale magnitude, the power of two that brings it to [256, 512) (Q6_K) or
+// [2^13, 2^14) (NVFP4, whose halves carry 2^-14), then every super-block rewritten (layouts at WideFmt).
+__device__ __forceinline__ float wide_e4m3(uint32_t b) {  // bias 7, subnormals below exponent 1
+  const int e = (b >> 3) & 15, m = b & 7;
+  const float mag = e ? ldexpf(1.0f + float(m) * 0.125f, e - 7) : ldexpf(float(m) * 0.125f, -6);
+  return (b & 0x80) ? -mag : mag;
+}
+__device__ __forceinline__ uint32_t wide_q6k_code(const uint8_t *blk, uint32_t e) {  // element e of a native super-block
+  const uint32_t j = e >> 5, k = e & 31, n = j >> 2, r = j & 3;
+  const uint8_t *ql = blk + 64 * n, *qh = blk + 128 + 32 * n;
+  return ((ql[k + 32 * (r & 1)] >> (4 * (r >> 1))) & 15u) | (((qh[k] >> (2 * r)) & 3u) << 4);
+}
+template <uint32_t FMT>
+__global__ void __launch_bounds__(128) wide_image_kernel(const uint8_t *native, uint32_t n, uint32_t nsb, uint8_t *image, float *row_scale) {
+  constexpr uint32_t kNative = FMT == SB_FMT_Q6K ? 210 : 148, kSb = WideFmt<FMT>::kSb;
+  __shared__ float red_s[4];
+  const uint32_t row = blockIdx.x, tid = threadIdx.x;
+  const uint8_t *src = native + size_t(row) * nsb * kNative;
+  auto scale_of = [&](const uint8_t *blk, uint32_t i) -> float {  // scale of elements 16 i .. 16 i + 15, fp32 as the format defines it
+    if (FMT == SB_FMT_Q6K) {
+      const __half d = *reinterpret_cast<const __half *>(blk + 208);
+      return __half2float(d) * float(reinterpret_cast<const int8_t *>(blk + 192)[i]);
+    }
+    float g;
+    memcpy(&g, blk + 16, 4);
+    return wide_e4m3(blk[i]) * g;
+  };
+  float mx = 0.0f;
+  for (uint32_t u = tid; u < nsb * 16; u += 128) {
+    const float v = fabsf(scale_of(src + (u >> 4) * kNative, u & 15));
+    if (v <= 3.0e38f) mx = fmaxf(mx, v);
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  if ((tid & 31) == 0) red_s[tid >> 5] = mx;
+  __syncthreads();
+  mx = fmaxf(fmaxf(red_s[0], red_s[1]), fmaxf(red_s[2], red_s[3]));
+  int e = 0;
+  if (mx > 0.0f) {
+    (void)frexpf(mx, &e);  // mx = m 2^e, m in [0.5, 1)
+    e -= FMT == SB_FMT_Q6K ? 9 : 0;
+  }
+  if (tid == 0) row_scale[row] = ldexpf(1.0f, e);
+  const float down = ldexpf(1.0f, (FMT == SB_FMT_Q6K ? 0 : 14) - e);
+  uint8_t *dst_row = image + size_t(row) * nsb * kSb;
+  for (uint32_t sb = 0; sb < nsb; ++sb) {
+    const uint8_t *blk = src + sb * kNative;
+    uint8_t *dst = dst_row + sb * kSb;
+    if (FMT == SB_FMT_Q6K) {
+      // ql': byte i of pair-block pb (64 elements from 64 pb) = low nibbles of its first 32 elements | of its next 32 << 4
+      {
+        const uint32_t pb = tid >> 5, i = tid & 31;
+        const uint32_t a = wide_q6k_code(blk, 64 * pb + i), bb = wide_q6k_code(blk, 64 * pb + 32 + i);
+        dst[32 * pb + i] = uint8_t((a & 15u) | ((bb & 15u) << 4));
+      }
+      // qh': word w of pair-block pb serves ql' words c = 2 w, 2 w + 1; output j of word c at bits 8 (c & 1) + 2 j (+16)
+      if (tid < 16) {
+        const uint32_t pb = tid >> 2, w = tid & 3;
+        uint32_t word = 0;
+        for (uint32_t cc = 0; cc < 2; ++cc)
+          for (uint32_t j = 0; j < 4; ++j) {
+            const uint32_t c = 2 * w + cc, base = 64 * pb + (j >= 2 ? 32 : 0) + 4 * c + (j & 1);
+            const uint32_t lo = wide_q6k_code(blk, base) >> 4, hi = wide_q6k_code(blk, base + 2) >> 4;
+            word |= (lo << (8 * cc + 2 * j)) | (hi << (8 * cc + 2 * j + 16));
+          }
+        reinterpret_cast<uint32_t *>(dst + 128)[4 * pb + w] = word;
+      }
+      if (tid >= 32 && tid < 48) reinterpret_cast<__half *>(dst + 192)[tid - 32] = __float2half_rn(scale_of(blk, tid - 32) * down);
+    } else {
+      // nibbles of every 8 elements in the order [0, 1, 4, 5, 2, 3, 6, 7]: nibbles k and k + 4 of a word are neighbours in
+      // the order the inputs are laid out in ([0, 2, 1, 3] within every four)
+      if (tid < 32) {
+        const uint32_t order[8] = {0, 1, 4, 5, 2, 3, 6, 7};
+        uint32_t word = 0;
+        for (uint32_t k = 0; k < 8; ++k) {
+          const uint32_t el = 8 * tid + order[k];
+          word |= uint32_t((blk[20 + el / 2] >> (4 * (el & 1))) & 15u) << (4 * k);
+        }
+        reinterpret_cast<uint32_t *>(dst)[tid] = word;
+      }
+      if (tid >= 32 && tid < 48) reinterpret_cast<__half *>(dst + 128)[tid - 32] = __float2half_rn(scale_of(blk, tid - 32) * down);
+    }
+  }
+}
+
 // k-splits of a projection left as SB_EPILOGUE_PARTIALS: as many as fill the SMs with two-half items, three super-blocks
 // each at least.
 static uint32_t wide_splits(uint32_t n, uint32_t k, int sm_count) {
@@ -580,6 +752,27 @@ static uint32_t wide_splits(uint32_t n, uint32_t k, int sm_count) {
   return std::max(1u, std::min(uint32_t(sm_count) / tiles, nsb / 3));
 }
 extern "C" uint32_t sb_linear_wide_splits(uint32_t n, uint32_t k) { return ctx().ready ? wide_splits(n, k, ctx().sm_count) : 0; }
+
+static uint32_t wide_sb_bytes(uint32_t format) {
+  return format == SB_FMT_Q4K ? WideFmt<SB_FMT_Q4K>::kSb : format == SB_FMT_Q6K ? WideFmt<SB_FMT_Q6K>::kSb : format == SB_FMT_NVFP4 ? WideFmt<SB_FMT_NVFP4>::kSb : 0;
+}
+extern "C" uint64_t sb_linear_wide_image_bytes(uint32_t format, uint32_t n, uint32_t k) {
+  if ((format != SB_FMT_Q6K && format != SB_FMT_NVFP4) || !n || !k || k % 256) return 0;
+  return uint64_t(n) * (k / 256) * wide_sb_bytes(format) + uint64_t(n) * 4;  // the rows, then a scale per row
+}
+extern "C" int sb_linear_wide_image(void *stream, uint32_t format, const void *weights, uint32_t n, uint32_t k, void *image_out) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(format == SB_FMT_Q6K || format == SB_FMT_NVFP4, "sb_linear_wide_image: format %u (Q6_K and NVFP4 rows have images; Q4_K rows are read as they are)", format);
+  SB_REQUIRE(weights && image_out && n && k && k % 256 == 0, "sb_linear_wide_image: null pointer, no rows or k = %u not a multiple of 256", k);
+  SB_REQUIRE((reinterpret_cast<uintptr_t>(image_out) & 15) == 0 && (reinterpret_cast<uintptr_t>(weights) & 3) == 0, "sb_linear_wide_image: the image must be 16-byte aligned, the rows 4-byte");
+  const uint32_t nsb = k / 256;
+  uint8_t *image = static_cast<uint8_t *>(image_out);
+  float *row_scale = reinterpret_cast<float *>(image + size_t(n) * nsb * wide_sb_bytes(format));
+  if (format == SB_FMT_Q6K) wide_image_kernel<SB_FMT_Q6K><<<n, 128, 0, as_stream(stream)>>>(static_cast<const uint8_t *>(weights), n, nsb, image, row_scale);
+  else wide_image_kernel<SB_FMT_NVFP4><<<n, 128, 0, as_stream(stream)>>>(static_cast<const uint8_t *>(weights), n, nsb, image, row_scale);
+  SB_CUDA(cudaGetLastError());
+  return SB_OK;
+}
 
 extern "C" uint64_t sb_linear_wide_prepared_bytes(uint32_t rows, uint32_t k) {
   if (!rows || !k || k % 256) return 0;
@@ -645,22 +838,27 @@ extern "C" int sb_linear_wide(void *stream, const SbLinearArgs *a) {
   }
   const bool gate_up = a->epilogue == SB_EPILOGUE_GATE_UP, split_k = a->epilogue == SB_EPILOGUE_PARTIALS;
   WideMaps maps;
-  const uint32_t row_bytes = uint32_t(sb_row_bytes(a->format, a->k));
+  const uint32_t sb_bytes = wide_sb_bytes(a->format), row_bytes = (a->k / 256) * sb_bytes;
+  const bool image = a->format != SB_FMT_Q4K;
+  const float *row_scale[2] = {image ? reinterpret_cast<const float *>(static_cast<const uint8_t *>(a->weights) + size_t(a->n) * row_bytes) : nullptr,
+                               image && a->weights2 ? reinterpret_cast<const float *>(static_cast<const uint8_t *>(a->weights2) + size_t(a->n) * row_bytes) : nullptr};
   if (gate_up) {
-    int st = encode_weight_map(&maps.m[0], reinterpret_cast<uintptr_t>(a->weights), row_bytes, a->n, 144, 128);
-    if (st == SB_OK) st = encode_weight_map(&maps.m[1], reinterpret_cast<uintptr_t>(a->weights2), row_bytes, a->n, 144, 128);
+    int st = encode_weight_map(&maps.m[0], reinterpret_cast<uintptr_t>(a->weights), row_bytes, a->n, sb_bytes, 128);
+    if (st == SB_OK) st = encode_weight_map(&maps.m[1], reinterpret_cast<uintptr_t>(a->weights2), row_bytes, a->n, sb_bytes, 128);
     if (st != SB_OK) return st;
   } else {
     // The item's halves are rows [256 i, 256 i + 128) and [256 i + 128, 256 i + 256): two maps over every other block of 128
     // rows would need a 3-D map; instead the second half is the same map shifted by 128 rows (rows past n read as zero).
-    int st = encode_weight_map(&maps.m[0], reinterpret_cast<uintptr_t>(a->weights), row_bytes, a->n, 144, 128);
+    int st = encode_weight_map(&maps.m[0], reinterpret_cast<uintptr_t>(a->weights), row_bytes, a->n, sb_bytes, 128);
     if (st != SB_OK) return st;
     maps.m[1] = maps.m[0];
   }
   static bool attr_set[64] = {};  // a function attribute is per device
   const int dev = c.device >= 0 && c.device < 64 ? c.device : 0;
   if (!attr_set[dev]) {
-    SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(kWideSmem)));
+    SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel<SB_FMT_Q4K>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(wide_smem<SB_FMT_Q4K>())));
+    SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel<SB_FMT_Q6K>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(wide_smem<SB_FMT_Q6K>())));
+    SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel<SB_FMT_NVFP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(wide_smem<SB_FMT_NVFP4>())));
     attr_set[dev] = true;
   }
   const uint64_t pass_bytes = sb_linear_wide_prepared_bytes(kWideMaxRows, a->k);
@@ -684,13 +882,16 @@ extern "C" int sb_linear_wide(void *stream, const SbLinearArgs *a) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(std::min<uint32_t>(p.items, uint32_t(c.sm_count)));
     cfg.blockDim = dim3(kWideThreads);
-    cfg.dynamicSmemBytes = kWideSmem;
+    cfg.dynamicSmemBytes = a->format == SB_FMT_Q4K ? wide_smem<SB_FMT_Q4K>() : a->format == SB_FMT_Q6K ? wide_smem<SB_FMT_Q6K>() : wide_smem<SB_FMT_NVFP4>();
+    p.row_scale[0] = row_scale[0], p.row_scale[1] = row_scale[1];
     cfg.stream = as_stream(stream);
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr, cfg.numAttrs = (a->flags & SB_LINEAR_PDL) ? 1 : 0;
-    SB_CUDA(cudaLaunchKernelEx(&cfg, linear_wide_kernel, p, maps));
+    if (a->format == SB_FMT_Q4K) SB_CUDA(cudaLaunchKernelEx(&cfg, linear_wide_kernel<SB_FMT_Q4K>, p, maps));
+    else if (a->format == SB_FMT_Q6K) SB_CUDA(cudaLaunchKernelEx(&cfg, linear_wide_kernel<SB_FMT_Q6K>, p, maps));
+    else SB_CUDA(cudaLaunchKernelEx(&cfg, linear_wide_kernel<SB_FMT_NVFP4>, p, maps));
   }
   return SB_OK;
 }

@@ -13,6 +13,7 @@ FMT_Q4K, FMT_Q6K, FMT_Q80, FMT_NVFP4, FMT_BF16, FMT_F16, FMT_F32 = 0, 4, 6, 37, 
 EP_NONE, EP_RESIDUAL, EP_UP_WITH_GATE, EP_GATE_UP, EP_PARTIALS, EP_GATE_UP_PARTIALS = 0, 1, 2, 3, 4, 5
 LINEAR_PDL = 1
 LINEAR_TCGEN05 = 2
+LINEAR_WIDE_IMAGE = 4
 
 
 class SbError(RuntimeError):
@@ -69,6 +70,9 @@ def load():
                                            ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32]
         _lib.sb_linear_prepared_bytes.restype = ctypes.c_uint64
         _lib.sb_linear_wide_prepared_bytes.restype = ctypes.c_uint64
+        _lib.sb_linear_wide_image_bytes.restype = ctypes.c_uint64
+        _lib.sb_linear_wide_image_bytes.argtypes = [ctypes.c_uint32] * 3
+        _lib.sb_linear_wide_image.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p]
         _lib.sb_linear_wide_prepared_bytes.argtypes = [ctypes.c_uint32, ctypes.c_uint32]
         _lib.sb_linear_wide_prepare.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p,
                                                 ctypes.c_void_p, ctypes.c_uint32]

@@ -150,10 +150,106 @@ def test_wide_k_split_sums_then_the_conversion_that_adds_them(n, k, rows):
     assert np.array_equal(conv.to_numpy(np.uint8, (nbytes,)), conv2.to_numpy(np.uint8, (nbytes,)))
 
 
+def image_of(lib, fmt, W, n, k):
+    wd = lib.DeviceBuffer.from_numpy(W)
+    img = lib.DeviceBuffer(int(lib.load().sb_linear_wide_image_bytes(fmt, n, k)))
+    lib.check(lib.load().sb_linear_wide_image(None, fmt, wd.ptr, n, k, img.ptr))
+    lib.stream_sync()
+    return img
+
+
+def run_image(lib, fmt, img, n, k, X, rows, img2=None, **kw):
+    xd = lib.DeviceBuffer.from_numpy(X)
+    f32 = kw.get("out_f32", False)
+    od = lib.DeviceBuffer(rows * n * (4 if f32 else 2) + 512)
+    od.fill(0xFF)
+    lib.linear(img.ptr, xd.ptr, od.ptr, fmt, n, k, rows, weights2=img2.ptr if img2 else None, flags=lib.LINEAR_WIDE_IMAGE, **kw)
+    lib.stream_sync()
+    assert lib.device_status() == 0
+    return od.to_numpy(np.float32 if f32 else np.uint16, (rows, n))
+
+
+@pytest.mark.parametrize("fmt", [4, 37])
+@pytest.mark.parametrize("n,k,rows", [(512, 1024, 128), (392, 2816, 17), (256, 5120, 64), (128, 17408, 48), (640, 2048, 200)])
+def test_wide_q6k_and_nvfp4_images(fmt, n, k, rows):
+    """Q6_K and NVFP4 rows through their images: the weight's half is fl16(code * fl16(scale)), two roundings, so the
+    middle term of the reference's bound for half-rounded weights is taken twice."""
+    lib = _setup()
+    W = qf.realistic(fmt, n, k, seed=n + k + fmt)
+    X = qf.activations(rows, k, seed=rows)
+    img = image_of(lib, fmt, W, n, k)
+    v, be, bs = oracle_f64(fmt, W, n, k, X, rows)
+    e = be + 2.0 * (bs - be)
+    got = run_image(lib, fmt, img, n, k, X, rows)
+    check_interval(got, v - e, v + e)
+    got32 = run_image(lib, fmt, img, n, k, X, rows, out_f32=True)
+    rel = np.abs(got32 - v) / np.maximum(np.abs(v), np.abs(v).mean())
+    # (the NVFP4 fixture's scales span 2^7 inside a row, so a few of its sums are small against their terms)
+    assert rel.max() < (2e-3 if fmt == 4 else 5e-3) and np.median(rel) < 4e-4
+    assert np.array_equal(got, ol.f2bf(got32))
+
+
+@pytest.mark.parametrize("fmt", [4, 37])
+def test_wide_image_rows_with_scales_far_apart(fmt):
+    """Rows whose scales differ by 2^40 from row to row, and by 2^12 inside a row: the power of two taken out of each row
+    keeps every row's halves in range."""
+    lib = _setup()
+    n, k, rows = 256, 2048, 32
+    rng = np.random.default_rng(9)
+    W = qf.realistic(fmt, n, k, seed=3).reshape(n, k // 256, -1).copy()
+    for r in range(n):
+        row_pow = float(2.0 ** rng.integers(-20, 21))
+        for sb in range(k // 256):
+            inner = float(2.0 ** -rng.integers(0, 13))
+            if fmt == 4:
+                d = np.float16(min(6e4, max(6.2e-5, 1e-3 * row_pow * inner)))
+                W[r, sb, 208:210] = np.frombuffer(d.tobytes(), np.uint8)
+            else:
+                W[r, sb, 16:20] = np.frombuffer(np.float32(1e-3 * row_pow * inner).tobytes(), np.uint8)
+    W = W.reshape(n, -1)
+    X = qf.activations(rows, k, seed=1)
+    img = image_of(lib, fmt, W, n, k)
+    v, be, bs = oracle_f64(fmt, W, n, k, X, rows)
+    e = be + 2.0 * (bs - be)
+    got32 = run_image(lib, fmt, img, n, k, X, rows, out_f32=True)
+    assert np.isfinite(got32).all()
+    assert (got32 >= v - e - 1e-30).all() and (got32 <= v + e + 1e-30).all()
+
+
+def test_wide_image_gate_up_and_k_split_sums():
+    lib = _setup()
+    n, k, rows = 384, 2048, 80
+    W, W2 = qf.realistic(37, n, k, seed=1), qf.realistic(37, n, k, seed=2)
+    X = qf.activations(rows, k)
+    g, u = image_of(lib, 37, W, n, k), image_of(lib, 37, W2, n, k)
+    one = run_image(lib, 37, g, n, k, X, rows, img2=u, epilogue=lib.EP_GATE_UP)
+    gate = run_image(lib, 37, g, n, k, X, rows)
+    gd = lib.DeviceBuffer.from_numpy(gate)
+    two = run_image(lib, 37, u, n, k, X, rows, aux=gd.ptr, epilogue=lib.EP_UP_WITH_GATE)
+    assert np.array_equal(one, two)
+    # the k-split sums of a Q6_K image add up to the plain product (fp32, up to the order of the additions)
+    W6 = qf.realistic(4, 512, 6144, seed=5)
+    X6 = qf.activations(rows, 6144)
+    i6 = image_of(lib, 4, W6, 512, 6144)
+    plain = run_image(lib, 4, i6, 512, 6144, X6, rows, out_f32=True)
+    import ctypes
+    lib.load().sb_linear_wide_splits.argtypes = [ctypes.c_uint32] * 2
+    splits = int(lib.load().sb_linear_wide_splits(512, 6144))
+    xd, parts = lib.DeviceBuffer.from_numpy(X6), lib.DeviceBuffer(splits * rows * 512 * 4)
+    lib.linear(i6.ptr, xd.ptr, parts.ptr, 4, 512, 6144, rows, epilogue=lib.EP_PARTIALS, out_f32=True, flags=lib.LINEAR_WIDE_IMAGE)
+    lib.stream_sync()
+    total = parts.to_numpy(np.float32, (splits, rows, 512)).astype(np.float64).sum(axis=0)
+    assert splits > 1 and np.abs(total - plain).max() <= 1e-5 * np.abs(plain).max()
+
+
 def test_wide_rejects_what_it_does_not_multiply():
     lib = _setup()
     d = lib.DeviceBuffer(1 << 20)
     with pytest.raises(lib.SbError):
-        lib.linear(d.ptr, d.ptr, d.ptr, lib.FMT_Q6K, 256, 1024, 64)       # Q4_K only
+        lib.linear(d.ptr, d.ptr, d.ptr, lib.FMT_Q6K, 256, 1024, 64)       # Q6_K rows as they are: the kernel reads their image
+    with pytest.raises(lib.SbError):
+        lib.linear(d.ptr, d.ptr, d.ptr, lib.FMT_Q4K, 256, 1024, 64, flags=lib.LINEAR_WIDE_IMAGE)   # Q4_K has no image
+    with pytest.raises(lib.SbError):
+        lib.linear(d.ptr, d.ptr, d.ptr, lib.FMT_Q80, 256, 1024, 64)
     with pytest.raises(lib.SbError):
         lib.linear(d.ptr, d.ptr, d.ptr, lib.FMT_Q4K, 256, 1000, 64)       # k not whole super-blocks
