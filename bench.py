@@ -200,6 +200,8 @@ def main():
     ap.add_argument("--tp-shots", type=int, default=0, choices=(0, 1, 2), help="how tensor-parallel shares travel (sb_tp_set_exchange); 0: by the number of ranks")
     ap.add_argument("--parallel", default="tp", choices=("tp", "replicas"), help="what N > 1 GPUs do: one lane tensor-parallel, or N lanes")
     ap.add_argument("--lanes", type=int, default=1, help="concurrent requests stepped together on each GPU, 16 rows each (an extra measurement, not the benchmark)")
+    ap.add_argument("--nvfp4", action="store_true", help="NVFP4 projections (e2m1 codes, e4m3 scale per 16, fp32 scale) instead of the Q4_K_M mix (an extra measurement)")
+    ap.add_argument("--context", type=int, default=0, help="tokens of context each lane holds (default: the workload's)")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
@@ -208,8 +210,13 @@ def main():
         workload = "35B-A3B-shaped MoE verify (256 experts + shared, top 8), Q4_K, ONE lane of 16 rows (not the configuration's 32 lanes), 8K INT8 paged KV, greedy"
         args.tiny, args.parallel = True, "replicas"  # (the extra legs of the benchmark are for the 27B workload only)
     L = max(1, args.lanes)
+    if args.nvfp4:
+        workload = workload.replace("Q4_K_M mix", "NVFP4 projections")
+        args.parallel = "replicas"
+    if args.context:
+        workload = workload.replace("32K", f"{args.context // 1024}K")
     if L > 1:
-        workload = f"{L} lanes stepped together: " + workload.replace("batch 1", f"batch {L}").replace("Q4_K_M mix", "all projections Q4_K")
+        workload = f"{L} lanes stepped together: " + workload.replace("batch 1", f"batch {L}")
         args.parallel = "replicas"
 
     if args.impl == "reference":
@@ -230,7 +237,10 @@ def main():
     lib.init(local)
     lib.check(lib.load().sb_tp_set_exchange(args.tp_shots))
     cfg = dict(target.QWEN35B_A3B if args.moe else target.TINY if args.tiny else target.QWEN27B)
-    context = 8192 if args.moe else 2048 if args.tiny else CONTEXT
+    context = args.context or (8192 if args.moe else 2048 if args.tiny else CONTEXT)
+    cfg["max_context"] = max(cfg["max_context"], context + 1024)
+    if args.nvfp4:
+        cfg.update(fmt_proj=lib.FMT_NVFP4, fmt_down=lib.FMT_NVFP4, fmt_head=lib.FMT_NVFP4)
     stream = lib.stream_create()
     tensor_parallel = world > 1 and args.parallel == "tp"
     fell_back = None
@@ -262,8 +272,8 @@ def main():
             t.close()
             tensor_parallel = False
     if not tensor_parallel:
-        if L > 1:  # (the many-row projection kernel takes Q4_K rows: the whole model Q4_K, not the Q4_K_M mix)
-            cfg.update(lanes=L, fmt_down=lib.FMT_Q4K, fmt_head=lib.FMT_Q4K)
+        if L > 1:
+            cfg.update(lanes=L)
         t = target.Target(**cfg)
         t.randomize(1234 + rank, context)
     lanes = 1 if tensor_parallel else world * L
@@ -356,7 +366,9 @@ def main():
     # ---- the dominant kernel alone: the one-pass Q4_K gate/up projection over each layer's weights ----
     peak, peak_kind = measured_peak()
     roofline = None
-    if not args.tiny and L > 1:
+    extra = L > 1 or args.nvfp4 or bool(args.context)
+    fmt = lib.FMT_NVFP4 if args.nvfp4 else lib.FMT_Q4K
+    if not args.tiny and (L > 1 or args.nvfp4):
         # the many-row projection on the tensor cores: the one-pass gate/up launch over 16 x lanes rows
         H, I, M = cfg["hidden"], cfg["intermediate"], ROWS * L
         x = lib.DeviceBuffer(M * H * 2 + 256)
@@ -364,11 +376,12 @@ def main():
         prep = lib.DeviceBuffer(int(lib.load().sb_linear_wide_prepared_bytes(M, H)))
         lib.check(lib.load().sb_linear_wide_prepare(stream, x.ptr, M, H, H, None, prep.ptr, 0))
         out = lib.DeviceBuffer(M * I * 2 + 256)
-        ptrs = [(t.tensor(layer, "ffn_gate")[0], t.tensor(layer, "ffn_up")[0]) for layer in range(cfg["layers"])]
+        names = ("ffn_gate_image", "ffn_up_image") if args.nvfp4 else ("ffn_gate", "ffn_up")
+        ptrs = [(t.tensor(layer, names[0])[0], t.tensor(layer, names[1])[0]) for layer in range(cfg["layers"])]
         def gate_up(i):
             g, u = ptrs[i % len(ptrs)]
-            lib.linear(g, None, out.ptr, lib.FMT_Q4K, I, H, M, weights2=u, prepared=prep.ptr, epilogue=lib.EP_GATE_UP, stream=stream,
-                       flags=lib.LINEAR_PDL)
+            lib.linear(g, None, out.ptr, fmt, I, H, M, weights2=u, prepared=prep.ptr, epilogue=lib.EP_GATE_UP, stream=stream,
+                       flags=lib.LINEAR_PDL | (lib.LINEAR_WIDE_IMAGE if args.nvfp4 else 0))
         for i in range(8):
             gate_up(i)
         lib.stream_sync(stream)
@@ -381,10 +394,10 @@ def main():
         k1.sync()
         launch_ms = k0.elapsed_ms(k1) / n
         flops = 2.0 * M * 2 * I * H
-        algo = 2 * I * (H // 256) * 144 + M * H * 2 + M * I * 2
+        algo = 2 * I * (H // 256) * (160 if args.nvfp4 else 144) + M * H * 2 + M * I * 2
         tensor_peak = measured_peak_tensor()
         achieved = flops / launch_ms / 1e9
-        roofline = {"bound": "tensor", "kernel": "linear_wide_kernel<Q4_K> gate/up 2x[%dx%d], M=%d (Q4_K dequantized to half, tcgen05, accumulators in tensor memory)" % (I, H, M),
+        roofline = {"bound": "tensor", "kernel": "linear_wide_kernel<%s> gate/up 2x[%dx%d], M=%d (weights dequantized to half, tcgen05, accumulators in tensor memory)" % ("NVFP4 image" if args.nvfp4 else "Q4_K", I, H, M),
                     "achieved": achieved, "peak": tensor_peak[0], "unit": "TFLOP/s", "frac": achieved / tensor_peak[0], "peak_kind": tensor_peak[1],
                     "algorithmic_bytes": algo, "hbm_gbs": algo / launch_ms / 1e6, "launch_us": launch_ms * 1e3, "traffic": None}
     elif not args.tiny:
@@ -420,8 +433,8 @@ def main():
                     "launch_us": launch_ms * 1e3, "traffic": None if tensor_parallel else DOMINANT_TRAFFIC_BYTES}
     step_bytes = stats["weight_bytes"] + stats["kv_bytes"] + stats["state_bytes"]
     step_gbs = step_bytes / ms / 1e6 / (world if tensor_parallel else 1)  # per GPU
-    if args.tiny:
-        cpu_tps, cores, sample = None, os.cpu_count(), "skipped for the tiny run"
+    if args.tiny or extra:
+        cpu_tps, cores, sample = None, os.cpu_count(), "skipped: not the benchmark's workload"
     elif world > 1:
         cpu_tps, cores, sample = None, os.cpu_count(), "timed at N = 1 only"
     else:

@@ -110,6 +110,16 @@ class QwenTarget {
   uint32_t committedHost = 0;  // bound of the device's committed word(s), for extents and the attention plan
   uint32_t step = 0;
   uint32_t lanes() const { return lanes_; }
+  // The images of the Q6_K / NVFP4 projections are out of date: set when a weight tensor's address is handed out or the
+  // weights are filled, cleared by buildImages, which the next step runs first.
+  bool imagesStale = true;
+  void buildImages(void *stream) {
+    if (wide_)
+      for (LayerWeights &w : layers_)
+        for (const ops::QuantizedSegment *s : {&w.inProj, &w.outProj, &w.ffnGate, &w.ffnUp, &w.ffnDown}) ops::Linear::buildImage(stream, *s);
+    if (wide_) ops::Linear::buildImage(stream, output_);
+    imagesStale = false;
+  }
   uint32_t pagesPerLane() const { return pagesPerLane_; }
 
  private:
@@ -132,6 +142,7 @@ class QwenTarget {
   static constexpr uint32_t kMaxPartialSlices = 16;
   uint32_t packedStride_ = 0;
   uint32_t lanes_ = 1, pagesPerLane_ = 0;
+  bool wide_ = false;  // the step runs on the many-row projection kernel (several lanes, or NVFP4 projections)
   Buffer widePrepared_[2], widePartials_;  // conversions for the many-row projection kernel (steps of several lanes)
   void encodeVerifyLanes(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool keepPending, bool drawsGiven);
   uint64_t weightBytes_ = 0, moeExpertBytes_ = 0;
@@ -144,7 +155,12 @@ inline ops::QuantizedSegment QwenTarget::segment(uint32_t n, uint32_t k, uint32_
   const size_t bytes = size_t(n) * sb_row_bytes(format, k);
   if (!bytes) throw std::invalid_argument("QwenTarget: a projection's width is not whole blocks of its format");
   s.rows = Buffer::allocate(bytes);
-  weightBytes_ += bytes;
+  if (wide_ && format != SB_FMT_Q4K) {
+    s.image = Buffer::allocate(ops::Linear::imageBytes(s));
+    weightBytes_ += s.image.bytes();  // (what a step streams)
+  } else {
+    weightBytes_ += bytes;
+  }
   return s;
 }
 
@@ -156,11 +172,16 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   lanes_ = std::max(1u, whole.lanes);
   const uint32_t L = lanes_;
   if (L > 32) throw std::invalid_argument("QwenTarget: " + std::to_string(L) + " lanes (up to 32)");
-  if (L > 1) {
-    // A step of several lanes multiplies 16 x lanes rows: the many-row projection kernel, which takes Q4_K rows.
-    if (whole.tp_world > 1 || whole.moe_experts) throw std::invalid_argument("QwenTarget: several lanes are offered for dense models on one GPU");
-    if (whole.fmt_proj != SB_FMT_Q4K || whole.fmt_down != SB_FMT_Q4K || whole.fmt_head != SB_FMT_Q4K)
-      throw std::invalid_argument("QwenTarget: several lanes need Q4_K projections (fmt_proj, fmt_down, fmt_head)");
+  // The many-row projection kernel carries steps of several lanes (16 x lanes rows) and every NVFP4 projection; it takes
+  // Q4_K rows as they are and Q6_K / NVFP4 rows as images made when the weights change (buildImages).
+  const bool fp4 = whole.fmt_proj == SB_FMT_NVFP4 || whole.fmt_down == SB_FMT_NVFP4 || whole.fmt_head == SB_FMT_NVFP4;
+  wide_ = L > 1 || fp4;
+  if (wide_) {
+    if (whole.tp_world > 1 || whole.moe_experts)
+      throw std::invalid_argument("QwenTarget: several lanes and NVFP4 projections are offered for dense models on one GPU");
+    for (uint32_t f : {whole.fmt_proj, whole.fmt_down, whole.fmt_head})
+      if (f != SB_FMT_Q4K && f != SB_FMT_Q6K && f != SB_FMT_NVFP4)
+        throw std::invalid_argument("QwenTarget: several lanes and NVFP4 models take Q4_K, Q6_K and NVFP4 projections (fmt_proj, fmt_down, fmt_head)");
   }
   if (whole.tp_world > 1) tp_ = std::make_unique<ops::TensorParallel>(whole.tp_world, whole.tp_rank, whole.hidden, whole.vocab);
   if (!c.layers || !c.hidden || !c.vocab || !c.intermediate || !c.attention_interval)
@@ -240,7 +261,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   partials_ = Buffer::allocate(size_t(kMaxPartialSlices) * 16 * H * 4);
   const uint32_t widest = std::max(std::max(H, c.intermediate), std::max(gdn_.valueWidth(), c.q_heads * D));
   for (auto &p : prepared_) p = Buffer::allocate(ops::Linear::preparedBytes((widest + 255) / 256 * 256));
-  if (L > 1) {
+  if (wide_) {
     for (auto &p : widePrepared_) p = Buffer::allocate(ops::Linear::wideBytes(uint32_t(R), (widest + 255) / 256 * 256));
     const uint32_t splits = std::max(ops::Linear::wideSplits(H, c.intermediate), std::max(ops::Linear::wideSplits(H, gdn_.valueWidth()), ops::Linear::wideSplits(H, c.q_heads * D)));
     widePartials_ = Buffer::allocate(size_t(splits) * R * H * 4);
@@ -291,6 +312,9 @@ inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) co
   std::map<std::string, Buffer> m = {{"attn_norm", w.attnNorm.buffer}, {"ffn_norm", w.ffnNorm.buffer}, {"in_proj", w.inProj.rows},
                                      {"out_proj", w.outProj.rows}, {"ffn_gate", w.ffnGate.rows}, {"ffn_up", w.ffnUp.rows},
                                      {"ffn_down", w.ffnDown.rows}};
+  // (the images the many-row kernel reads, where a projection has one: for measurements of that kernel by itself)
+  for (auto &[tensor, seg] : {std::pair<const char *, const ops::QuantizedSegment &>{"ffn_gate_image", w.ffnGate}, {"ffn_up_image", w.ffnUp}, {"ffn_down_image", w.ffnDown}})
+    if (seg.image) m.insert({tensor, seg.image});
   if (cfg_.moe_experts)
     m.insert({{"ffn_router", w.moe.router}, {"ffn_shared_gate", w.moe.sharedGate}, {"ffn_gate_exps", w.moe.gate}, {"ffn_up_exps", w.moe.up},
               {"ffn_down_exps", w.moe.down}});
@@ -325,8 +349,8 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   using namespace ops;
   if (rows < 1 || rows > kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: 1 to 16 rows");
   if (committedHost + rows > cfg_.max_context + kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: past the context bound");
-  if (lanes_ > 1) {
-    if (treeGiven) throw std::invalid_argument("QwenTarget::encodeVerify: tree blocks are offered for one lane");
+  if (wide_) {
+    if (treeGiven) throw std::invalid_argument("QwenTarget::encodeVerify: tree blocks are offered for one lane of Q4_K / Q6_K / Q8_0 projections");
     return encodeVerifyLanes(graph, rows, temperature, parity, advance, keepPending, drawsGiven);
   }
   const SbTargetConfig &c = loc_;

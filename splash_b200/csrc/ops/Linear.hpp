@@ -17,6 +17,7 @@ enum class Destination { BFloat16, Float32 };
 struct QuantizedSegment {
   Buffer rows;
   uint32_t outputSize = 0, inputSize = 0, columnOffset = 0, format = SB_FMT_Q4K;
+  Buffer image;  // Q6_K / NVFP4 rows as the many-row kernel reads them (Linear::buildImage); empty otherwise
 };
 
 struct Projection {
@@ -121,8 +122,15 @@ class Linear {
     graph.launches += (rows + 127) / 128;
     return {scratch, 0xFFFFu, inputSize};
   }
-  // One Q4_K segment over `rows` rows: epilogues None / Residual / UpWithGate, GateUp with `up` given, or Partials (output:
-  // fp32 [wideSplits][rows][outputStride]).
+  // The image of a Q6_K / NVFP4 segment's rows for addWide (made when the weights are loaded or changed; Q4_K has none).
+  static uint64_t imageBytes(const QuantizedSegment &s) { return sb_linear_wide_image_bytes(s.format, s.outputSize, s.inputSize); }
+  static void buildImage(void *stream, const QuantizedSegment &s) {
+    if (!s.image) return;
+    requireBytes(s.image, imageBytes(s), "Linear::buildImage image");
+    check(sb_linear_wide_image(stream, s.format, s.rows.as(), s.outputSize, s.inputSize, s.image.as()));
+  }
+  // One segment over `rows` rows (Q4_K rows, or the image of Q6_K / NVFP4 rows): epilogues None / Residual / UpWithGate,
+  // GateUp with `up` given, or Partials (output: fp32 [wideSplits][rows][outputStride]).
   static void addWide(CommandGraph &graph, const QuantizedSegment &s, const QuantizedSegment *up, const PreparedInput &prepared, uint32_t rows,
                       Epilogue epilogue, const Buffer *aux, const Buffer &output, uint32_t outputStride, bool float32 = false) {
     if (prepared.format != 0xFFFFu || prepared.inputSize != s.inputSize) throw std::invalid_argument("Linear::addWide: not a wide conversion of this width");
@@ -137,11 +145,13 @@ class Linear {
     }
     if (aux) requireBytes(*aux, (size_t(rows - 1) * outputStride + s.outputSize) * 2, "Linear::addWide residual or gate");
     SbLinearArgs a{};
-    a.weights = s.rows.as(), a.weights2 = up ? up->rows.as() : nullptr, a.prepared = prepared.buffer.as();
+    const bool image = s.format != SB_FMT_Q4K;
+    if (image && (!s.image || (up && !up->image))) throw std::invalid_argument("Linear::addWide: the segment's image has not been made");
+    a.weights = image ? s.image.as() : s.rows.as(), a.weights2 = up ? (image ? up->image.as() : up->rows.as()) : nullptr, a.prepared = prepared.buffer.as();
     a.aux = aux ? aux->as() : nullptr, a.out = output.as();
     a.format = s.format, a.n = s.outputSize, a.k = s.inputSize, a.rows = rows;
     a.aux_stride = aux ? outputStride : 0, a.out_stride = outputStride, a.epilogue = uint32_t(epilogue), a.out_f32 = float32;
-    a.flags = graph.pdl ? SB_LINEAR_PDL : 0;
+    a.flags = (graph.pdl ? SB_LINEAR_PDL : 0) | (image ? SB_LINEAR_WIDE_IMAGE : 0);
     check(sb_linear_wide(graph.stream, &a));
     graph.launches += (rows + 127) / 128;
   }

@@ -87,6 +87,11 @@ __global__ void scale_fields_kernel(uint32_t format, uint8_t *p, uint64_t blocks
       *reinterpret_cast<__half *>(p + i * 210 + 208) = __float2half_rn(2e-5f + 8e-5f * uniform01(seed, i));
     } else if (format == SB_FMT_Q80) {
       *reinterpret_cast<__half *>(p + i * 34) = __float2half_rn(5e-4f + 3.5e-3f * uniform01(seed, i));
+    } else if (format == SB_FMT_NVFP4) {  // e4m3 scales of exponents 3..10 (the codes stay as filled), one fp32 scale for the tensor
+      uint8_t *b = p + i * 148;
+      for (int j = 0; j < 16; ++j) b[j] = uint8_t((b[j] & 0x87u) | ((3u + (b[j] >> 3) % 8u) << 3));
+      const float g = 2e-4f + 1.8e-3f * uniform01(seed, 0);
+      memcpy(b + 16, &g, 4);
     }
   }
 }
@@ -258,6 +263,10 @@ int sb_target_tensor(void *target, int layer, const char *name, void **out_dev, 
   SB_REQUIRE(static_cast<Target *>(target)->model->find(layer, name, b), "sb_target_tensor: no tensor '%s' in layer %d", name, layer);
   *out_dev = b.as();
   *out_bytes = b.bytes();
+  // The caller may write a projection's rows through this address: their image (Q6_K / NVFP4 on the many-row kernel) is
+  // made again before the next step.
+  for (const char *w : {"in_proj", "out_proj", "ffn_gate", "ffn_up", "ffn_down", "output"})
+    if (!strcmp(name, w)) static_cast<Target *>(target)->model->imagesStale = true;
   return SB_OK;
 }
 
@@ -357,6 +366,7 @@ int sb_target_randomize(void *target, uint64_t seed, uint32_t committed) {
     m.find(-1, "output", seg.rows);
     seg.format = c.fmt_head, seg.outputSize = m.share().vocab;
     SB_TRY(fill_rows(seg, next()));
+    m.imagesStale = true;
 #undef SB_TRY
     SB_CUDA(cudaDeviceSynchronize());
     return sb_target_reset(target, committed);
@@ -369,6 +379,7 @@ static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float tempera
   const bool keep = !advance && (flags & SB_TARGET_KEEP_PENDING) != 0, draws = (flags & SB_TARGET_DRAWS) != 0;
   const uint32_t parity = m.step & 1;
   return guarded([&] {
+    if (m.imagesStale) m.buildImages(stream);
     if (flags & SB_TARGET_GRAPH) {
       // The attention plan and the page-table extents are made for a bound of the lane's position; a graph
       // serves until the lane passes its bound.

@@ -59,7 +59,7 @@ def realistic(fmt, n, k, seed=42):
     if fmt == 37:  # NVFP4: 16 e4m3 scales, an fp32 scale, 128 bytes of e2m1 codes
         nb = k // 256
         blk = rng.integers(0, 256, (n, nb, 148), dtype=np.uint8)
-        blk[..., 0:16] = (rng.integers(0, 2, (n, nb, 16)) << 7) | (rng.integers(3, 11, (n, nb, 16)) << 3) | rng.integers(0, 8, (n, nb, 16))
+        blk[..., 0:16] = (rng.integers(0, 2, (n, nb, 16)) << 7) | (rng.integers(6, 9, (n, nb, 16)) << 3) | rng.integers(0, 8, (n, nb, 16))
         g = rng.uniform(2e-4, 2e-3, (n, 1)).astype(np.float32) * np.ones((1, nb), np.float32)  # one scale a tensor row here
         blk[..., 16:20] = g.view(np.uint8).reshape(n, nb, 4)
         return blk.reshape(n, nb * 148)

@@ -192,7 +192,7 @@ def test_selection_penalties_and_acceptance_of_lanes_equal_the_lanes_one_at_a_ti
 def build_lanes(lanes, positions, seed=0):
     from splash_b200 import lib, target
     lib.init(0)
-    cfg = dict(target.TINY, fmt_head=lib.FMT_Q4K, lanes=lanes)     # the many-row projections take Q4_K rows
+    cfg = dict(target.TINY, lanes=lanes)     # (Q4_K projections, Q6_K head: the head runs from its image)
     t = target.Target(**cfg)
     w = mo.make_weights(cfg, seed)
     states = [mo.make_state(cfg, int(positions[i]), seed + 1 + i) for i in range(lanes)]
@@ -256,13 +256,46 @@ def test_lane_of_a_four_lane_step_does_not_depend_on_the_other_lanes():
     assert a[2][1:] == b[2][1:] and np.array_equal(a[2][0], b[2][0])
 
 
+def test_tiny_nvfp4_model_steps_match_oracle():
+    """One lane with NVFP4 projections (Q6_K embedding): every projection runs on the many-row kernel from its image."""
+    from splash_b200 import lib, target
+    lib.init(0)
+    cfg = dict(target.TINY, fmt_proj=lib.FMT_NVFP4, fmt_down=lib.FMT_NVFP4, fmt_head=lib.FMT_NVFP4)
+    t = target.Target(**cfg)
+    w = mo.make_weights(cfg, 2)
+    s = mo.make_state(cfg, 2048, 3)
+    mo.upload(t, w, s)
+    t.reset(2048)
+    token, compared = 5, 0
+    for step in range(3):
+        tokens = mo.draft_chain(cfg, w, s, token, rows=16, seed=step)
+        want = mo.verify_step(cfg, w, s, tokens, advance=True)
+        got_tokens, retained, accepted, mask = t.verify(tokens, flags=target.ADVANCE | target.GRAPH)
+        assert lib.device_status() == 0
+        logits = t.download(-1, "logits", np.float32, (16, cfg["vocab"]))
+        scale = np.abs(want["logits"]).max()
+        err = np.abs(logits - want["logits"])
+        assert err.max() <= 3e-2 * scale and np.median(err) <= 2e-3 * scale, step
+        top2 = np.sort(want["logits"], axis=1)[:, -2:]
+        clear = (top2[:, 1] - top2[:, 0]) > 2.5 * err.max(axis=1)
+        if clear[:want["retained"]].all():
+            assert (retained, accepted, mask) == (want["retained"], want["accepted"], want["mask"]), step
+            assert np.array_equal(got_tokens, want["tokens"]), step
+            compared += 1
+        else:
+            s["committed"] += retained - want["retained"]
+            s["pending_rows"] = retained
+        token = int(got_tokens[-1])
+    assert compared >= 2
+
+
 def test_lanes_reject_what_they_do_not_step():
     from splash_b200 import lib, target
     lib.init(0)
     with pytest.raises(lib.SbError):
-        target.Target(**dict(target.TINY, lanes=4))                          # Q6_K head
+        target.Target(**dict(target.TINY, fmt_down=lib.FMT_Q80, lanes=4))     # Q8_0 rows have no many-row kernel
     with pytest.raises(lib.SbError):
-        target.Target(**dict(target.TINY, fmt_head=lib.FMT_Q4K, lanes=33))
-    t = target.Target(**dict(target.TINY, fmt_head=lib.FMT_Q4K, lanes=2))
+        target.Target(**dict(target.TINY, lanes=33))
+    t = target.Target(**dict(target.TINY, lanes=2))
     with pytest.raises(lib.SbError):
         t.verify(np.arange(16, dtype=np.uint32))                             # the one-lane entry

@@ -184,8 +184,7 @@ def test_wide_q6k_and_nvfp4_images(fmt, n, k, rows):
     check_interval(got, v - e, v + e)
     got32 = run_image(lib, fmt, img, n, k, X, rows, out_f32=True)
     rel = np.abs(got32 - v) / np.maximum(np.abs(v), np.abs(v).mean())
-    # (the NVFP4 fixture's scales span 2^7 inside a row, so a few of its sums are small against their terms)
-    assert rel.max() < (2e-3 if fmt == 4 else 5e-3) and np.median(rel) < 4e-4
+    assert rel.max() < (2e-3 if fmt == 4 else 4e-3) and np.median(rel) < 4e-4    # (e2m1 codes: heavier tails than the 6-bit codes)
     assert np.array_equal(got, ol.f2bf(got32))
 
 
