@@ -21,4 +21,34 @@ int encode_weight_map(CUtensorMap *map, uintptr_t base, uint32_t stride, uint32_
 int tc_plan(uint32_t n, uint32_t k, uint32_t epilogue, SbLinearPlan &plan);
 int launch_linear_tc(cudaStream_t stream, const SbLinearArgs *a, const void *prepared, bool pdl);
 
+// ---- the many-row kernel over groups of rows with their own weights (the experts of an MoE block) ----
+// groups: device uint4 {expert, first row slot, rows (up to 128), rows padded to 16}; group_count: device word. A group's
+// inputs are converted into a block of their own (launch_wide_prepare_grouped), its outputs are rows [slot0, slot0 + rows)
+// of `out`.
+struct WideGroupedArgs {
+  const void *weights, *weights2;  // stacked native Q4_K rows [experts][expert_rows][k]; weights2: the up tensor (one-pass gate/up)
+  uint32_t experts, expert_rows, k;
+  const void *prepared;            // the groups' converted inputs
+  const float *scales;             // a scale per row slot
+  const uint4 *groups;
+  const uint32_t *group_count;
+  uint32_t max_groups;             // bounds the grid
+  void *out;                       // bf16 [row slots][out_stride]
+  uint32_t out_stride;
+  bool pdl;
+};
+int launch_linear_wide_grouped(cudaStream_t stream, const WideGroupedArgs &a);
+// Converts row slot s of every group from row slot_src[s] of x (bf16 [.., x_stride]; ~0: zeros) into the groups' blocks.
+struct WidePrepareGroupedArgs {
+  const void *x;
+  uint32_t x_stride, k;
+  const uint32_t *slot_src, *slot_group, *slot_count;
+  uint32_t max_slots;  // the grid
+  const uint4 *groups;
+  void *prepared;
+  float *scales;
+  bool pdl;
+};
+int launch_wide_prepare_grouped(cudaStream_t stream, const WidePrepareGroupedArgs &a);
+
 }  // namespace sb

@@ -58,7 +58,7 @@ template <> struct WideFmt<SB_FMT_NVFP4> { static constexpr uint32_t kSb = 160, 
 constexpr uint32_t kWideMaxRawStages = 4;
 constexpr uint32_t kWideXBytes = 128 * 1024, kWideMaxXStages = 8;   // the X ring; a stage holds 64 inputs of every row
 constexpr uint32_t kWideABufs = 4, kWideACols = 64, kWideACol0 = 256, kWideDCols = 128, kWideTmemCols = 512;
-constexpr uint32_t kWideBarBytes = 1024;           // barriers, tensor-memory slot, then scale_back[128] at 512
+constexpr uint32_t kWideBarBytes = 3072;           // barriers, tensor-memory slot, scale_back[128] at 512, then an epilogue warp's own [128] x 4
 constexpr uint32_t kWideXOff = kWideBarBytes, kWideRawOff = kWideXOff + kWideXBytes;
 template <uint32_t FMT> constexpr uint32_t wide_smem() { return kWideRawOff + WideFmt<FMT>::kStages * 128 * WideFmt<FMT>::kSb; }  // 205,824 bytes for Q4_K
 
@@ -74,15 +74,35 @@ struct WideParams {
   // super-blocks go to out as fp32 [split][rows_total][out_stride], for the next input conversion to add in split order.
   uint32_t splits, rows_total, row0;
   const float *row_scale[2];  // images: a power of two per weight row taken out of its scales (NULL for native Q4_K rows)
+  // Grouped (the experts of an MoE block): the launch's items are (group, tile) pairs over a device table of groups, each
+  // group the rows routed to one expert (up to 128 of them, padded to 16), its inputs a block of `prepared` of its own at
+  // row slot `slot0`, its weights the expert's rows of the stacked tensor, its outputs rows slot0 .. of `out`.
+  const uint4 *groups;         // {expert, slot0, rows, rows padded to 16}
+  const uint32_t *group_count;
+  const float *group_scales;   // scale_back of every row slot
+  uint32_t tiles_per_group, expert_rows;  // weight rows per expert in the stacked tensor
 };
-// An item's tile and its range of super-blocks.
+// An item's tile, its range of super-blocks, its rows of X and where its weights, inputs and outputs are.
 struct WideItem {
   uint32_t tile, split, sb0, sb1;
+  uint32_t rows, rows_padded, slot0, wrow0;
+  const uint8_t *x;  // the item's converted inputs: super-block sb at x + sb * 512 * rows_padded
 };
+__device__ __forceinline__ uint32_t wide_items(const WideParams &p) { return p.groups ? __ldg(p.group_count) * p.tiles_per_group : p.items; }
 __device__ __forceinline__ WideItem wide_item(const WideParams &p, uint32_t item) {
   WideItem w;
+  if (p.groups) {
+    const uint32_t g = item / p.tiles_per_group;
+    const uint4 rec = __ldg(p.groups + g);
+    w.tile = item - g * p.tiles_per_group, w.split = 0, w.sb0 = 0, w.sb1 = p.nsb;
+    w.rows = rec.z, w.rows_padded = rec.w, w.slot0 = rec.y, w.wrow0 = rec.x * p.expert_rows;
+    w.x = p.prepared + size_t(rec.y) * p.nsb * 512;
+    return w;
+  }
   w.tile = item / p.splits, w.split = item - w.tile * p.splits;
   w.sb0 = w.split * p.nsb / p.splits, w.sb1 = (w.split + 1) * p.nsb / p.splits;
+  w.rows = p.rows, w.rows_padded = p.rows_padded, w.slot0 = 0, w.wrow0 = 0;
+  w.x = p.prepared + kWideHeader;
   return w;
 }
 #ifdef SB_DIAG
@@ -127,18 +147,40 @@ struct WidePrepParams {
   const float *partials;  // fp32 [splits][rows_total][partial_stride], this pass's first row at row0
   const uint16_t *residual;
   uint32_t splits, rows_total, row0, partial_stride, residual_stride;
+  // Grouped (an MoE block's routed rows): CTA s converts row slot s of the groups' blocks. slot_src[s] is the row of x it
+  // holds (~0: a padding slot, zeros), slot_group[s] = group << 8 | its row inside the group, groups as WideParams has them;
+  // the blocks start at out (a group's at slot0 * k * 2), the slots' scales go to `scales`.
+  const uint32_t *slot_src, *slot_group, *slot_count;
+  const uint4 *groups;
+  float *scales;
 };
 __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const WidePrepParams p) {
   __shared__ float red_s[2 * (kWidePrepThreads / 32)];
-  const uint32_t tok = blockIdx.x, tid = threadIdx.x;
+  uint32_t tok = blockIdx.x;  // the row slot inside its block
+  const uint32_t tid = threadIdx.x;
   pdl_launch_dependents();
   pdl_wait();
-  const bool live = tok < p.rows;
+  bool live = tok < p.rows;
+  uint32_t rows_padded = p.rows_padded;
+  const uint16_t *xrow = p.x + size_t(tok) * p.x_stride;
+  uint8_t *block = p.out + kWideHeader;
+  float *scale_dst = reinterpret_cast<float *>(p.out) + tok;
+  if (p.slot_src) {
+    const uint32_t slot = blockIdx.x;
+    if (slot >= __ldg(p.slot_count)) return;
+    const uint32_t src = __ldg(p.slot_src + slot), sg = __ldg(p.slot_group + slot);
+    const uint4 rec = __ldg(p.groups + (sg >> 8));
+    live = src != 0xffffffffu;
+    tok = sg & 0xffu, rows_padded = rec.w;
+    xrow = p.x + size_t(live ? src : 0) * p.x_stride;
+    block = p.out + size_t(rec.y) * p.k * 2;
+    scale_dst = p.scales + slot;
+  }
   const uint32_t chunks = p.k / 8;  // 8 inputs each
   if (p.partials && live) {
     // The projection ahead left its k-splits' sums: add them in split order onto the residual, round once, and keep the
     // rows (the new hidden state). A thread reads back below only what it wrote itself.
-    uint16_t *xw = const_cast<uint16_t *>(p.x);
+    uint16_t *xw = const_cast<uint16_t *>(xrow);
     for (uint32_t c = tid; c < chunks; c += kWidePrepThreads) {
       const uint4 raw = *reinterpret_cast<const uint4 *>(p.residual + size_t(tok) * p.residual_stride + 8 * c);
       const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
@@ -155,12 +197,12 @@ __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const Wi
         const uint32_t hi = float_to_bf16_bits(acc[2 * j + 1] + bf16_bits_to_float(u[j] >> 16));
         o[j] = lo | (hi << 16);
       }
-      *reinterpret_cast<uint4 *>(xw + size_t(tok) * p.x_stride + 8 * c) = make_uint4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<uint4 *>(xw + 8 * c) = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
   float ss = 0.0f, mx = 0.0f;
   for (uint32_t c = tid; c < chunks && live; c += kWidePrepThreads) {
-    const uint4 raw = *reinterpret_cast<const uint4 *>(p.x + size_t(tok) * p.x_stride + 8 * c);
+    const uint4 raw = *reinterpret_cast<const uint4 *>(xrow + 8 * c);
     const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -190,12 +232,12 @@ __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const Wi
     e -= 10;
   }
   const float down = ldexpf(1.0f, -e);
-  if (tid == 0) reinterpret_cast<float *>(p.out)[tok] = live ? ldexpf(1.0f, e) : 0.0f;
-  const size_t unit_bytes = size_t(p.rows_padded) * 128;  // 64 inputs of every row slot
+  if (tid == 0) *scale_dst = live ? ldexpf(1.0f, e) : 0.0f;
+  const size_t unit_bytes = size_t(rows_padded) * 128;  // 64 inputs of every row slot
   for (uint32_t c = tid; c < chunks; c += kWidePrepThreads) {
     uint32_t h[4] = {0, 0, 0, 0};
     if (live) {
-      const uint4 raw = *reinterpret_cast<const uint4 *>(p.x + size_t(tok) * p.x_stride + 8 * c);
+      const uint4 raw = *reinterpret_cast<const uint4 *>(xrow + 8 * c);
       const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
       float v[8];
 #pragma unroll
@@ -213,7 +255,7 @@ __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const Wi
       h[2] = *reinterpret_cast<const uint32_t *>(&p2), h[3] = *reinterpret_cast<const uint32_t *>(&p3);
     }
     const uint32_t k0 = 8 * c, unit = k0 / 64, step = (k0 % 64) / 16, half = (k0 % 16) / 8;
-    uint8_t *dst = p.out + kWideHeader + unit * unit_bytes + size_t(step) * p.rows_padded * 32 + (tok >> 3) * 256 + half * 128 + (tok & 7) * 16;
+    uint8_t *dst = block + unit * unit_bytes + size_t(step) * rows_padded * 32 + (tok >> 3) * 256 + half * 128 + (tok & 7) * 16;
     *reinterpret_cast<uint4 *>(dst) = make_uint4(h[0], h[1], h[2], h[3]);
   }
 }
@@ -333,7 +375,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
   uint64_t *d_empty = d_full + 1;
   uint64_t *h_full = d_empty + 1;                                  // the header (scale_back) has landed
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 496);
-  float *scale_back = reinterpret_cast<float *>(smem + 512);       // [128]
+  float *scale_back_all = reinterpret_cast<float *>(smem + 512);   // [128], the launch's rows (not grouped)
   uint8_t *x_ring = smem + kWideXOff, *raw_ring = smem + kWideRawOff;
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -350,6 +392,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
   tc_fence_after_sync();
   const uint32_t tmem = *tmem_slot;
   pdl_launch_dependents();
+  const bool grouped = p.groups != nullptr;
   if (warp == 0) WIDE_EVENT(0);  // set-up done
 
   if (warp == kWideRawWarp) {
@@ -357,7 +400,9 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
     const uint64_t policy = policy_evict_first();
     uint32_t rs = 0, rphase = 0, rcount = 0;
     bool ok = true;
-    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
+    if (grouped) pdl_wait();  // the table of groups comes from the kernels ahead
+    const uint32_t n_items = wide_items(p);
+    for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       const WideItem w = wide_item(p, item);
       for (uint32_t sb = w.sb0; sb < w.sb1 && ok; ++sb)
         for (uint32_t tn = 0; tn < p.halves && ok; ++tn, ++rcount) {
@@ -368,7 +413,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
           }
           if (lane == 0) {
             mbar_arrive_expect_tx(&raw_full[rs], kWideRawStage);
-            tma_load_2d(raw_ring + rs * kWideRawStage, &maps.m[tn], int(sb * (WideFmt<FMT>::kSb / 4)), int(p.gate_up ? w.tile * 128 : w.tile * 128 * p.halves + tn * 128), &raw_full[rs], policy, true);
+            tma_load_2d(raw_ring + rs * kWideRawStage, &maps.m[tn], int(sb * (WideFmt<FMT>::kSb / 4)), int(w.wrow0 + (p.gate_up ? w.tile * 128 : w.tile * 128 * p.halves + tn * 128)), &raw_full[rs], policy, true);
           }
           if (++rs == kWideRawStages) rs = 0, rphase ^= 1;
         }
@@ -379,14 +424,15 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
   } else if (warp == kWideXWarp) {
     // ---- X: a group is the four stages (64 inputs each) of one super-block; the ring holds x_groups of them ----
     pdl_wait();  // X comes from the kernel ahead
-    if (lane == 0) {
+    if (lane == 0 && !grouped) {
       mbar_arrive_expect_tx(h_full, 512);
-      bulk_g2s(scale_back, p.prepared, 512, h_full);
+      bulk_g2s(scale_back_all, p.prepared, 512, h_full);
     }
     uint32_t xg = 0, xphase = 0, xcount = 0;
     bool ok = true;
-    const uint32_t group_bytes = 4 * p.x_stage_bytes;
-    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
+    const uint32_t group_bytes = 4 * p.x_stage_bytes;  // a ring slot (sized for the launch's most rows)
+    const uint32_t n_items = wide_items(p);
+    for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       const WideItem w = wide_item(p, item);
       for (uint32_t sb = w.sb0; sb < w.sb1 && ok; ++sb, ++xcount) {
         if (xcount >= p.x_groups && !wide_warp_wait(&x_empty[xg], xphase ^ 1, true)) {
@@ -395,8 +441,9 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
           break;
         }
         if (lane == 0) {
-          mbar_arrive_expect_tx(&x_full[xg], group_bytes);
-          bulk_g2s(x_ring + xg * group_bytes, p.prepared + kWideHeader + size_t(sb) * group_bytes, group_bytes, &x_full[xg]);
+          const uint32_t bytes = 512 * w.rows_padded;  // a super-block of the item's rows
+          mbar_arrive_expect_tx(&x_full[xg], bytes);
+          bulk_g2s(x_ring + xg * group_bytes, w.x + size_t(sb) * bytes, bytes, &x_full[xg]);
         }
         if (++xg == p.x_groups) xg = 0, xphase ^= 1;
       }
@@ -409,17 +456,19 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
     // busy at N = 128 (measured: 62 to 70 cycles per MMA overall). ----
     if (lane == 0 && warp - kWideMmaWarp0 < p.halves) {
       const uint32_t tn = warp - kWideMmaWarp0;
-      const uint32_t idesc = umma_idesc_f16(128, p.rows_padded);
       const uint32_t d0 = tmem + tn * kWideDCols;
+      if (grouped) pdl_wait();
+      const uint32_t n_items = wide_items(p);
       bool ok = true;
       uint32_t ucount = 0, xg = 0, xphase = 0, dphase = 0, done_items = 0;
-      for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x, ++done_items) {
+      for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++done_items) {
         if (done_items > 0) {  // the accumulators of the item before must have been read
           ok = mbar_wait(d_empty, dphase);
           dphase ^= 1;
           if (!ok) { wide_expired(p.status, 3); break; }
         }
         const WideItem w = wide_item(p, item);
+        const uint32_t idesc = umma_idesc_f16(128, w.rows_padded);
         for (uint32_t sb = w.sb0; sb < w.sb1 && ok; ++sb) {
           {
             WIDE_T0();
@@ -442,7 +491,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
             const uint32_t a0 = tmem + kWideACol0 + ab * kWideACols;
 #pragma unroll
             for (uint32_t i = 0; i < 8; ++i) {  // K-step i of this half of the super-block
-              const uint64_t b = umma_smem_desc(xbase + (8 * hh + i) * p.rows_padded * 32, 128, 256);
+              const uint64_t b = umma_smem_desc(xbase + (8 * hh + i) * w.rows_padded * 32, 128, 256);
               umma_f16_ts(d0, a0 + i * 8, b, idesc, !(sb == w.sb0 && hh == 0 && i == 0));
             }
             umma_commit(&a_empty[ab]);
@@ -463,7 +512,9 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
     const uint32_t ab = 2 * tn + h;
     uint32_t rs = tn, rphase = 0, scount = 0;  // super-blocks this warp has expanded
     bool ok = tn < p.halves;
-    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
+    if (grouped) pdl_wait();
+    const uint32_t n_items = wide_items(p);
+    for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
       const WideItem w = wide_item(p, item);
       for (uint32_t sb = w.sb0; sb < w.sb1 && ok; ++sb, ++scount) {
         {
@@ -512,10 +563,19 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
     // ---- epilogue: a thread per weight row of each half of the item ----
     const uint32_t q = warp & 3, row = 32 * q + lane;
     pdl_wait();  // aux / out belong to the stream's earlier kernels until they finish
-    bool ok = wide_warp_wait(h_full, 0);
+    bool ok = grouped || wide_warp_wait(h_full, 0);
     if (!ok && lane == 0) wide_expired(p.status, 8);
     uint32_t dphase = 0;
-    for (uint32_t item = blockIdx.x; item < p.items && ok; item += gridDim.x) {
+    const uint32_t n_items = wide_items(p);
+    float *own_scales = reinterpret_cast<float *>(smem + 1024 + 512 * q);
+    for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      const WideItem w = wide_item(p, item);
+      const float *scale_back = grouped ? own_scales : reinterpret_cast<const float *>(smem + 512);
+      if (grouped) {  // the rows' scales, a copy per warp
+        __syncwarp();
+        for (uint32_t i = lane; i < w.rows_padded; i += 32) own_scales[i] = __ldg(p.group_scales + w.slot0 + i);
+        __syncwarp();
+      }
       {
         WIDE_T0();
         if (!wide_warp_wait(d_full, dphase)) {
@@ -533,10 +593,10 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
       // Per 16 rows of X: the sums out of tensor memory, the epilogue on all 16 without a branch (the chains of the
       // activation overlap), then the stores of the rows that exist.
       if (p.gate_up) {
-        const uint32_t col = item * 128 + row;
+        const uint32_t col = w.tile * 128 + row;
         const float rg = p.row_scale[0] && col < p.n ? p.row_scale[0][col] : 1.0f, ru = p.row_scale[1] && col < p.n ? p.row_scale[1][col] : 1.0f;
-        uint16_t *dst = static_cast<uint16_t *>(p.out) + col;
-        for (uint32_t c = 0; c < p.rows_padded; c += 16) {
+        uint16_t *dst = static_cast<uint16_t *>(p.out) + size_t(w.slot0) * p.out_stride + col;
+        for (uint32_t c = 0; c < w.rows_padded; c += 16) {
           float g[16], u[16];
           tmem_ld16_wait(t0 + c, g);
           tmem_ld16_wait(t0 + kWideDCols + c, u);
@@ -549,31 +609,30 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
           if (col < p.n) {
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-              if (c + j < p.rows) dst[size_t(c + j) * p.out_stride] = o[j];
+              if (c + j < w.rows) dst[size_t(c + j) * p.out_stride] = o[j];
           }
         }
       } else if (p.epilogue == SB_EPILOGUE_PARTIALS) {
-        const WideItem w = wide_item(p, item);
         for (uint32_t half = 0; half < p.halves; ++half) {
           const uint32_t col = w.tile * 128 * p.halves + half * 128 + row;
           const float rw = p.row_scale[0] && col < p.n ? p.row_scale[0][col] : 1.0f;
           float *dst = static_cast<float *>(p.out) + (size_t(w.split) * p.rows_total + p.row0) * p.out_stride + col;
-          for (uint32_t c = 0; c < p.rows_padded; c += 16) {
+          for (uint32_t c = 0; c < w.rows_padded; c += 16) {
             float v[16];
             tmem_ld16_wait(t0 + half * kWideDCols + c, v);
             if (col < p.n) {
 #pragma unroll
               for (int j = 0; j < 16; ++j)
-                if (c + j < p.rows) dst[size_t(c + j) * p.out_stride] = v[j] * (scale_back[c + j] * rw);
+                if (c + j < w.rows) dst[size_t(c + j) * p.out_stride] = v[j] * (scale_back[c + j] * rw);
             }
           }
         }
       } else {
         for (uint32_t half = 0; half < p.halves; ++half) {
-          const uint32_t col = item * 128 * p.halves + half * 128 + row;
+          const uint32_t col = w.tile * 128 * p.halves + half * 128 + row;
           const bool live = col < p.n;
           const float rw = p.row_scale[0] && live ? p.row_scale[0][col] : 1.0f;
-          for (uint32_t c = 0; c < p.rows_padded; c += 16) {
+          for (uint32_t c = 0; c < w.rows_padded; c += 16) {
             float v[16];
             tmem_ld16_wait(t0 + half * kWideDCols + c, v);
             float a[16];
@@ -582,7 +641,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
             if (p.aux && live) {
 #pragma unroll
               for (int j = 0; j < 16; ++j)
-                if (c + j < p.rows) a[j] = bf16_bits_to_float(p.aux[size_t(c + j) * p.aux_stride + col]);
+                if (c + j < w.rows) a[j] = bf16_bits_to_float(p.aux[size_t(w.slot0 + c + j) * p.aux_stride + col]);
             }
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -594,11 +653,11 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
             if (p.out_f32) {
 #pragma unroll
               for (int j = 0; j < 16; ++j)
-                if (c + j < p.rows) static_cast<float *>(p.out)[size_t(c + j) * p.out_stride + col] = v[j];
+                if (c + j < w.rows) static_cast<float *>(p.out)[size_t(w.slot0 + c + j) * p.out_stride + col] = v[j];
             } else {
 #pragma unroll
               for (int j = 0; j < 16; ++j)
-                if (c + j < p.rows) static_cast<uint16_t *>(p.out)[size_t(c + j) * p.out_stride + col] = float_to_bf16_bits(v[j]);
+                if (c + j < w.rows) static_cast<uint16_t *>(p.out)[size_t(w.slot0 + c + j) * p.out_stride + col] = float_to_bf16_bits(v[j]);
             }
           }
         }
@@ -640,6 +699,69 @@ static int wide_check(const SbLinearArgs *a, const char *who) {
   SB_REQUIRE((reinterpret_cast<uintptr_t>(a->weights) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->weights2) & 15) == 0 &&
                  (reinterpret_cast<uintptr_t>(a->prepared) & 15) == 0 && (reinterpret_cast<uintptr_t>(a->x) & 15) == 0,
              "%s: weights, x and prepared must be 16-byte aligned", who);
+  return SB_OK;
+}
+
+static int wide_set_attributes() {
+  static bool attr_set[64] = {};  // a function attribute is per device
+  Context &c = ctx();
+  const int dev = c.device >= 0 && c.device < 64 ? c.device : 0;
+  if (!attr_set[dev]) {
+    SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel<SB_FMT_Q4K>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(wide_smem<SB_FMT_Q4K>())));
+    SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel<SB_FMT_Q6K>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(wide_smem<SB_FMT_Q6K>())));
+    SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel<SB_FMT_NVFP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(wide_smem<SB_FMT_NVFP4>())));
+    attr_set[dev] = true;
+  }
+  return SB_OK;
+}
+
+int launch_wide_prepare_grouped(cudaStream_t stream, const WidePrepareGroupedArgs &a) {
+  SB_REQUIRE(a.x && a.prepared && a.scales && a.slot_src && a.slot_group && a.slot_count && a.groups && a.max_slots,
+             "grouped conversion: null pointer or no slots");
+  SB_REQUIRE(a.k && a.k % 256 == 0 && a.x_stride >= a.k && a.x_stride % 8 == 0, "grouped conversion: k = %u is not a multiple of 256, or x_stride %u", a.k, a.x_stride);
+  WidePrepParams pp{};
+  pp.x = static_cast<const uint16_t *>(a.x), pp.out = static_cast<uint8_t *>(a.prepared), pp.k = a.k, pp.x_stride = a.x_stride;
+  pp.slot_src = a.slot_src, pp.slot_group = a.slot_group, pp.slot_count = a.slot_count, pp.groups = a.groups, pp.scales = a.scales;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(a.max_slots), cfg.blockDim = dim3(kWidePrepThreads), cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = a.pdl ? 1 : 0;
+  SB_CUDA(cudaLaunchKernelEx(&cfg, wide_prepare_kernel, pp));
+  return SB_OK;
+}
+
+int launch_linear_wide_grouped(cudaStream_t stream, const WideGroupedArgs &a) {
+  SB_REQUIRE(a.weights && a.prepared && a.scales && a.groups && a.group_count && a.out && a.max_groups, "grouped projection: null pointer or no groups");
+  SB_REQUIRE(a.k && a.k % 256 == 0, "grouped projection: k = %u is not a multiple of 256", a.k);
+  const bool gate_up = a.weights2 != nullptr;
+  SB_REQUIRE(a.expert_rows % (gate_up ? 128 : 256) == 0, "grouped projection: %u rows an expert (whole tiles of %u)", a.expert_rows, gate_up ? 128 : 256);
+  Context &c = ctx();
+  int st = wide_set_attributes();
+  if (st != SB_OK) return st;
+  WideMaps maps;
+  const uint32_t row_bytes = (a.k / 256) * 144, total_rows = a.experts * a.expert_rows;
+  st = encode_weight_map(&maps.m[0], reinterpret_cast<uintptr_t>(a.weights), row_bytes, total_rows, 144, 128);
+  if (st == SB_OK && gate_up) st = encode_weight_map(&maps.m[1], reinterpret_cast<uintptr_t>(a.weights2), row_bytes, total_rows, 144, 128);
+  if (st != SB_OK) return st;
+  if (!gate_up) maps.m[1] = maps.m[0];
+  WideParams p{};
+  p.prepared = static_cast<const uint8_t *>(a.prepared), p.out = a.out, p.status = c.status_dev;
+  p.n = a.expert_rows, p.out_stride = a.out_stride, p.epilogue = gate_up ? SB_EPILOGUE_GATE_UP : SB_EPILOGUE_NONE;
+  p.nsb = a.k / 256, p.gate_up = gate_up, p.halves = 2, p.splits = 1;
+  p.rows = p.rows_padded = kWideMaxRows;  // (a group's own rows come from the table)
+  p.x_stage_bytes = kWideMaxRows * 128, p.x_groups = kWideXBytes / (4 * p.x_stage_bytes);
+  p.groups = a.groups, p.group_count = a.group_count, p.group_scales = a.scales;
+  p.tiles_per_group = gate_up ? a.expert_rows / 128 : a.expert_rows / 256, p.expert_rows = a.expert_rows;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(std::min<uint32_t>(a.max_groups * p.tiles_per_group, uint32_t(c.sm_count)));
+  cfg.blockDim = dim3(kWideThreads), cfg.dynamicSmemBytes = wide_smem<SB_FMT_Q4K>(), cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = a.pdl ? 1 : 0;
+  SB_CUDA(cudaLaunchKernelEx(&cfg, linear_wide_kernel<SB_FMT_Q4K>, p, maps));
   return SB_OK;
 }
 
@@ -853,13 +975,9 @@ extern "C" int sb_linear_wide(void *stream, const SbLinearArgs *a) {
     if (st != SB_OK) return st;
     maps.m[1] = maps.m[0];
   }
-  static bool attr_set[64] = {};  // a function attribute is per device
-  const int dev = c.device >= 0 && c.device < 64 ? c.device : 0;
-  if (!attr_set[dev]) {
-    SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel<SB_FMT_Q4K>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(wide_smem<SB_FMT_Q4K>())));
-    SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel<SB_FMT_Q6K>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(wide_smem<SB_FMT_Q6K>())));
-    SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel<SB_FMT_NVFP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(wide_smem<SB_FMT_NVFP4>())));
-    attr_set[dev] = true;
+  {
+    const int st = wide_set_attributes();
+    if (st != SB_OK) return st;
   }
   const uint64_t pass_bytes = sb_linear_wide_prepared_bytes(kWideMaxRows, a->k);
   for (uint32_t r0 = 0, pass = 0; r0 < a->rows; r0 += kWideMaxRows, ++pass) {

@@ -10,7 +10,10 @@
 // most 16 rows nearly every route has its expert to itself, so a route streams its expert's rows directly: a warp per
 // output column, a lane per 8 consecutive weights of every super-block, effective weights d sc q - dmin m unrounded
 // (as in linear_kernel), fp32 sums. The grouped tile kernel for the M >= 64 regime is not built.
+#include <algorithm>
+
 #include "sb_internal.h"
+#include "sb_linear_internal.h"
 #include "sb_ptx.cuh"
 
 namespace sb {
@@ -145,6 +148,131 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeParams p) {
   static_cast<uint16_t *>(a.out)[size_t(row) * a.hidden + c] = float_to_bf16_bits(res + acc);
 }
 
+// ---- many rows (the rows of several lanes): routes grouped by expert, the experts' passes on the many-row kernel ----
+// (MoE::addRouted's grouping: runtime/metal/kernels/shared/moe.metal:187-287, the row gather :347-365, the expert tiles
+// runtime/metal/kernels/common/moe_gguf_expert_tile.h:33-84, the combine moe.metal:367-392.)
+constexpr uint32_t kMoeMaxExperts = 512, kMoeMaxRoutes = 16384, kMoeGroupRows = 128, kMoeGroupThreads = 512;
+struct MoeGrouping {
+  uint32_t *counts;         // [0] groups, [1] row slots
+  uint4 *groups;            // {expert, first slot, rows, rows padded to 16}
+  uint32_t *slot_of_route;  // [rows * routes]
+  uint32_t *slot_src;       // [slots] the input row a slot holds, ~0 for padding
+  uint32_t *slot_self;      // [slots] the slot itself, ~0 for padding
+  uint32_t *slot_group;     // [slots] group << 8 | row inside the group
+};
+struct MoeGroupLayout {
+  uint64_t counts, groups, slot_of_route, slot_src, slot_self, slot_group, scales1, scales2, prepared1, prepared2, act, y, bytes;
+  uint32_t max_groups, max_slots;
+};
+static MoeGroupLayout moe_group_layout(uint32_t rows, uint32_t routes, uint32_t hidden, uint32_t inter) {
+  MoeGroupLayout l{};
+  const uint64_t n = uint64_t(rows) * routes;
+  l.max_groups = uint32_t(kMoeMaxExperts + n / kMoeGroupRows + 1);
+  l.max_slots = uint32_t((n + 15ull * l.max_groups + 15) / 16 * 16);  // every group ends with fewer than 16 padding slots
+  uint64_t at = 0;
+  auto take = [&](uint64_t bytes) { const uint64_t here = at; at += (bytes + 255) / 256 * 256; return here; };
+  l.counts = take(16), l.groups = take(uint64_t(l.max_groups) * 16), l.slot_of_route = take(n * 4);
+  l.slot_src = take(uint64_t(l.max_slots) * 4), l.slot_self = take(uint64_t(l.max_slots) * 4), l.slot_group = take(uint64_t(l.max_slots) * 4);
+  l.scales1 = take(uint64_t(l.max_slots) * 4), l.scales2 = take(uint64_t(l.max_slots) * 4);
+  l.prepared1 = take(uint64_t(l.max_slots) * hidden * 2), l.prepared2 = take(uint64_t(l.max_slots) * inter * 2);
+  l.act = take(uint64_t(l.max_slots) * inter * 2), l.y = take(uint64_t(l.max_slots) * hidden * 2);
+  l.bytes = at;
+  return l;
+}
+
+// One CTA: a stable counting sort of the routes by expert. Thread e counts expert e's routes, one thread lays the experts'
+// groups out one after the other (an expert's routes in groups of 128, the last padded to 16 row slots), thread e then
+// numbers its routes in their order (row, then slot of the row).
+__global__ void __launch_bounds__(kMoeGroupThreads) moe_group_kernel(const uint32_t *selected, uint32_t n, uint32_t routes, uint32_t experts, MoeGrouping g,
+                                                                     uint32_t *status) {
+  extern __shared__ __align__(16) uint16_t ids[];  // [n rounded up to 8]
+  __shared__ uint32_t count_s[kMoeMaxExperts], slot0_s[kMoeMaxExperts], group0_s[kMoeMaxExperts];
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t tid = threadIdx.x, n8 = (n + 7) / 8 * 8;
+  for (uint32_t i = tid; i < n8; i += kMoeGroupThreads) {
+    uint32_t e = i < n ? selected[i] : 0xffffu;
+    if (i < n && e >= experts) {  // outside the contract: the route is dropped and the launch says so
+      atomicCAS(status, 0u, uint32_t(SB_DEV_CONTRACT));
+      e = 0xffffu;
+    }
+    ids[i] = uint16_t(e);
+  }
+  __syncthreads();
+  auto walk = [&](uint32_t e, auto &&found) {
+    const uint32_t pat = e | (e << 16);
+    for (uint32_t i = 0; i < n8; i += 8) {
+      const uint4 v = *reinterpret_cast<const uint4 *>(ids + i);
+      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t x = w[j] ^ pat;
+        if (!(x & 0xffffu)) found(i + 2 * j);
+        if (!(x >> 16)) found(i + 2 * j + 1);
+      }
+    }
+  };
+  for (uint32_t e = tid; e < experts; e += kMoeGroupThreads) {
+    uint32_t c = 0;
+    walk(e, [&](uint32_t) { ++c; });
+    count_s[e] = c;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t slot = 0, group = 0;
+    for (uint32_t e = 0; e < experts; ++e) {
+      slot0_s[e] = slot, group0_s[e] = group;
+      for (uint32_t left = count_s[e]; left > 0;) {
+        const uint32_t rows = min(left, kMoeGroupRows), padded = (rows + 15) / 16 * 16;
+        g.groups[group++] = make_uint4(e, slot, rows, padded);
+        slot += padded, left -= rows;
+      }
+    }
+    g.counts[0] = group, g.counts[1] = slot;
+  }
+  __syncthreads();
+  for (uint32_t e = tid; e < experts; e += kMoeGroupThreads) {
+    const uint32_t slot0 = slot0_s[e], group0 = group0_s[e];
+    uint32_t j = 0;
+    walk(e, [&](uint32_t i) {  // (full groups carry no padding, so the expert's j-th route sits at slot0 + j)
+      g.slot_of_route[i] = slot0 + j;
+      g.slot_src[slot0 + j] = i / routes, g.slot_self[slot0 + j] = slot0 + j;
+      g.slot_group[slot0 + j] = ((group0 + j / kMoeGroupRows) << 8) | (j % kMoeGroupRows);
+      ++j;
+    });
+    if (j) {
+      const uint32_t last = group0 + (j - 1) / kMoeGroupRows;
+      for (uint32_t r = j; r < (j + 15) / 16 * 16; ++r) {
+        g.slot_src[slot0 + r] = 0xffffffffu, g.slot_self[slot0 + r] = 0xffffffffu;
+        g.slot_group[slot0 + r] = (last << 8) | (r - (last - group0) * kMoeGroupRows);
+      }
+    }
+  }
+}
+
+// out = bf16(residual + sum over the row's routes in slot order of weight * float(y)), y at the routes' row slots.
+__global__ void __launch_bounds__(256) moe_combine_grouped_kernel(const SbMoeExpertArgs a, const uint32_t *slot_of_route, const uint16_t *y) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t row = blockIdx.y, c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+  if (c >= a.hidden) return;
+  float acc0 = 0.0f, acc1 = 0.0f;
+  for (uint32_t s = 0; s < a.routes; ++s) {
+    const uint32_t route = row * a.routes + s, slot = slot_of_route[route];
+    if (a.selected[route] >= a.experts_total) continue;  // (dropped by the grouping, which has flagged it)
+    const float w = a.weights[route];
+    const uint32_t pair = *reinterpret_cast<const uint32_t *>(y + size_t(slot) * a.hidden + c);
+    acc0 += w * bf16_bits_to_float(pair & 0xffffu), acc1 += w * bf16_bits_to_float(pair >> 16);
+  }
+  float r0 = 0.0f, r1 = 0.0f;
+  if (a.residual) {
+    const uint32_t pair = *reinterpret_cast<const uint32_t *>(static_cast<const uint16_t *>(a.residual) + size_t(row) * a.hidden + c);
+    r0 = bf16_bits_to_float(pair & 0xffffu), r1 = bf16_bits_to_float(pair >> 16);
+  }
+  *reinterpret_cast<uint32_t *>(static_cast<uint16_t *>(a.out) + size_t(row) * a.hidden + c) =
+      uint32_t(float_to_bf16_bits(r0 + acc0)) | (uint32_t(float_to_bf16_bits(r1 + acc1)) << 16);
+}
+
 template <class K> static int launch_moe(K kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const MoeParams &p) {
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = stream;
@@ -161,20 +289,70 @@ template <class K> static int launch_moe(K kernel, dim3 grid, dim3 block, size_t
 using namespace sb;
 
 extern "C" uint64_t sb_moe_scratch_bytes(uint32_t rows, uint32_t routes, uint32_t hidden, uint32_t inter) {
+  if (rows > 16) return moe_group_layout(rows, routes, hidden, inter).bytes;
   return uint64_t(rows) * routes * (uint64_t(hidden) + inter) * 2 + 256;
+}
+
+// More than 16 rows: group the routes by expert, gather and convert each group's rows, the experts' one-pass gate/up and
+// down on the many-row kernel over the groups, and the combine.
+static int moe_experts_grouped(cudaStream_t s, const SbMoeExpertArgs *a) {
+  const uint64_t n = uint64_t(a->rows) * a->routes;
+  SB_REQUIRE(n <= kMoeMaxRoutes && a->experts_total <= kMoeMaxExperts, "sb_moe_experts: %u rows x %u routes over %u experts (up to %u routes, %u experts)",
+             a->rows, a->routes, a->experts_total, kMoeMaxRoutes, kMoeMaxExperts);
+  SB_REQUIRE(a->inter % 128 == 0 && a->hidden % 256 == 0, "sb_moe_experts: many rows need an intermediate width in 128s and a hidden width in 256s");
+  const MoeGroupLayout l = moe_group_layout(a->rows, a->routes, a->hidden, a->inter);
+  uint8_t *base = static_cast<uint8_t *>(a->scratch);
+  auto at = [&](uint64_t off) { return base + off; };
+  MoeGrouping g{reinterpret_cast<uint32_t *>(at(l.counts)), reinterpret_cast<uint4 *>(at(l.groups)), reinterpret_cast<uint32_t *>(at(l.slot_of_route)),
+                reinterpret_cast<uint32_t *>(at(l.slot_src)), reinterpret_cast<uint32_t *>(at(l.slot_self)), reinterpret_cast<uint32_t *>(at(l.slot_group))};
+  const bool pdl = ctx().pdl;
+  {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1), cfg.blockDim = dim3(kMoeGroupThreads), cfg.dynamicSmemBytes = size_t((n + 7) / 8 * 8) * 2, cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = pdl ? 1 : 0;
+    SB_CUDA(cudaLaunchKernelEx(&cfg, moe_group_kernel, a->selected, uint32_t(n), a->routes, a->experts_total, g, ctx().status_dev));
+  }
+  WidePrepareGroupedArgs c1{a->input, a->hidden, a->hidden, g.slot_src, g.slot_group, g.counts + 1, l.max_slots, g.groups, at(l.prepared1),
+                            reinterpret_cast<float *>(at(l.scales1)), pdl};
+  int st = launch_wide_prepare_grouped(s, c1);
+  if (st != SB_OK) return st;
+  WideGroupedArgs pair{a->gate, a->up, a->experts_total, a->inter, a->hidden, at(l.prepared1), reinterpret_cast<const float *>(at(l.scales1)), g.groups,
+                       g.counts, l.max_groups, at(l.act), a->inter, pdl};
+  st = launch_linear_wide_grouped(s, pair);
+  if (st != SB_OK) return st;
+  WidePrepareGroupedArgs c2{at(l.act), a->inter, a->inter, g.slot_self, g.slot_group, g.counts + 1, l.max_slots, g.groups, at(l.prepared2),
+                            reinterpret_cast<float *>(at(l.scales2)), pdl};
+  st = launch_wide_prepare_grouped(s, c2);
+  if (st != SB_OK) return st;
+  WideGroupedArgs down{a->down, nullptr, a->experts_total, a->hidden, a->inter, at(l.prepared2), reinterpret_cast<const float *>(at(l.scales2)), g.groups,
+                       g.counts, l.max_groups, at(l.y), a->hidden, pdl};
+  st = launch_linear_wide_grouped(s, down);
+  if (st != SB_OK) return st;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((a->hidden / 2 + 255) / 256, a->rows), cfg.blockDim = dim3(256), cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = pdl ? 1 : 0;
+  SB_CUDA(cudaLaunchKernelEx(&cfg, moe_combine_grouped_kernel, *a, static_cast<const uint32_t *>(g.slot_of_route), reinterpret_cast<const uint16_t *>(at(l.y))));
+  return SB_OK;
 }
 
 extern "C" int sb_moe_experts(void *stream, const SbMoeExpertArgs *a) {
   SB_NEED_DEVICE();
   SB_REQUIRE(a && a->input && a->selected && a->weights && a->gate && a->up && a->down && a->scratch && a->out, "sb_moe_experts: null pointer");
   SB_REQUIRE(a->format == SB_FMT_Q4K, "sb_moe_experts: experts in format %u (Q4_K only)", a->format);
-  SB_REQUIRE(a->rows >= 1 && a->rows <= 16 && a->routes >= 1 && a->routes <= 32, "sb_moe_experts: %u rows (1..16) x %u routes (1..32)", a->rows, a->routes);
+  SB_REQUIRE(a->rows >= 1 && a->routes >= 1 && a->routes <= 32, "sb_moe_experts: %u rows x %u routes (1..32)", a->rows, a->routes);
   SB_REQUIRE(a->hidden && a->hidden % 256 == 0 && a->inter && a->inter % 256 == 0 && a->hidden <= 8192 && a->inter <= 8192,
              "sb_moe_experts: hidden %u and intermediate %u are multiples of 256 up to 8192", a->hidden, a->inter);
   SB_REQUIRE(a->experts_total >= 1, "sb_moe_experts: no experts");
   SB_REQUIRE(((reinterpret_cast<uintptr_t>(a->gate) | reinterpret_cast<uintptr_t>(a->up) | reinterpret_cast<uintptr_t>(a->down) |
                reinterpret_cast<uintptr_t>(a->scratch)) & 15) == 0,
              "sb_moe_experts: expert tensors and scratch must be 16-byte aligned");
+  if (a->rows > 16) return moe_experts_grouped(as_stream(stream), a);
   MoeParams p{*a, static_cast<uint16_t *>(a->scratch), static_cast<uint16_t *>(a->scratch) + size_t(a->rows) * a->routes * a->inter};
   const uint32_t routes = a->rows * a->routes, pair_block = kMoeWarps * kMoeColsPair, down_block = kMoeWarps * kMoeColsDown;
   cudaStream_t s = as_stream(stream);

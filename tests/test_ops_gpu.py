@@ -683,5 +683,5 @@ def test_moe_experts_match_oracle(shape):
     g, w = ol.bf2f(out.to_numpy(np.uint16, (rows, H))).astype(np.float64), ol.bf2f(want).astype(np.float64)
     assert (np.abs(g - w) <= 2 * ulp_bf16(w) + 2e-3 * np.abs(w).mean()).all()
     assert np.abs(g - ol.bf2f(res)).max() > 1e-3     # the experts did contribute
-    bad = lib.SbMoeExpertArgs(xd.ptr, rd.ptr, sel.ptr, wts.ptr, wg.ptr, wu.ptr, wd.ptr, scratch.ptr, out.ptr, 17, routes, H, I, lib.FMT_Q4K, total)
+    bad = lib.SbMoeExpertArgs(xd.ptr, rd.ptr, sel.ptr, wts.ptr, wg.ptr, wu.ptr, wd.ptr, scratch.ptr, out.ptr, rows, 33, H, I, lib.FMT_Q4K, total)
     assert l.sb_moe_experts(None, ctypes.byref(bad)) == -1
