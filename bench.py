@@ -207,7 +207,7 @@ def main():
     local = int(os.environ.get("LOCAL_RANK", 0))
     workload = "tiny hybrid verify" if args.tiny else "Qwen3.x-27B-shaped hybrid verify, Q4_K_M mix, batch 1, block 16, 32K INT8 paged KV, greedy"
     if args.moe:
-        workload = "35B-A3B-shaped MoE verify (256 experts + shared, top 8), Q4_K, ONE lane of 16 rows (not the configuration's 32 lanes), 8K INT8 paged KV, greedy"
+        workload = "35B-A3B-shaped MoE verify (256 experts + shared, top 8), Q4_K, batch 1, block 16, 8K INT8 paged KV, greedy"
         args.tiny, args.parallel = True, "replicas"  # (the extra legs of the benchmark are for the 27B workload only)
     L = max(1, args.lanes)
     if args.nvfp4:

@@ -177,8 +177,8 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   const bool fp4 = whole.fmt_proj == SB_FMT_NVFP4 || whole.fmt_down == SB_FMT_NVFP4 || whole.fmt_head == SB_FMT_NVFP4;
   wide_ = L > 1 || fp4;
   if (wide_) {
-    if (whole.tp_world > 1 || whole.moe_experts)
-      throw std::invalid_argument("QwenTarget: several lanes and NVFP4 projections are offered for dense models on one GPU");
+    if (whole.tp_world > 1) throw std::invalid_argument("QwenTarget: several lanes and NVFP4 projections are offered on one GPU");
+    if (whole.moe_experts && fp4) throw std::invalid_argument("QwenTarget: MoE experts are Q4_K");
     for (uint32_t f : {whole.fmt_proj, whole.fmt_down, whole.fmt_head})
       if (f != SB_FMT_Q4K && f != SB_FMT_Q6K && f != SB_FMT_NVFP4)
         throw std::invalid_argument("QwenTarget: several lanes and NVFP4 models take Q4_K, Q6_K and NVFP4 projections (fmt_proj, fmt_down, fmt_head)");
@@ -279,9 +279,9 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   penaltyWords = Buffer::allocate(size_t(c.vocab) * 4 * L);
   candidates = Buffer::allocate(R * 16 * 4), candidateQ = Buffer::allocate(R * 16 * 4), draws = Buffer::allocate(R * 4);
   if (c.moe_experts) {
-    moeScores_ = Buffer::allocate(size_t(kVerifyRows) * moe_.slots * 4);
-    moeSelected_ = Buffer::allocate(size_t(kVerifyRows) * moe_.routes() * 4), moeWeights_ = Buffer::allocate(size_t(kVerifyRows) * moe_.routes() * 4);
-    moeScratch_ = Buffer::allocate(ops::MoE::scratchBytes(moe_, kVerifyRows));
+    moeScores_ = Buffer::allocate(R * moe_.slots * 4);
+    moeSelected_ = Buffer::allocate(R * moe_.routes() * 4), moeWeights_ = Buffer::allocate(R * moe_.routes() * 4);
+    moeScratch_ = Buffer::allocate(ops::MoE::scratchBytes(moe_, uint32_t(R)));
   }
 }
 
@@ -521,6 +521,17 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
     PreparedInput mixedIn = Linear::prepareWide(graph, mixed_, R, mixedWidth, mixedWidth, nullptr, widePrepared_[1]);
     Linear::addWide(graph, w.outProj, nullptr, mixedIn, R, Epilogue::Partials, nullptr, widePartials_, H);
     owed = Linear::wideSplits(H, mixedWidth);
+    if (c.moe_experts) {
+      // MoE block: h += sum over the row's routes of weight * expert(norm(h)). The conversion is run for the hidden rows it
+      // leaves (residual + out_proj's splits); the routes of all lanes' rows are grouped by expert (MoE::addRouted).
+      convert(nullptr);
+      Normalization::addRms(graph, hidden[cur], w.ffnNorm, normed_, H, R, H, H);
+      MoeBuffers mb{normed_, hidden[cur], moeScores_, moeSelected_, moeWeights_, moeScratch_, hidden[cur ^ 1]};
+      MoE::addRouting(graph, moe_, w.moe, mb, R);
+      MoE::addRouted(graph, moe_, w.moe, mb, R);
+      cur ^= 1;
+      continue;
+    }
     // FFN: h += down(silu(gate(norm(h))) * up(norm(h)))
     PreparedInput ffnIn = convert(&w.ffnNorm.buffer);
     Linear::addWide(graph, w.ffnGate, &w.ffnUp, ffnIn, R, Epilogue::GateUp, nullptr, act_, c.intermediate);

@@ -1,5 +1,6 @@
 // ops::MoE of the reference (runtime/ops/MoE.hpp, runtime/ops/MoE.cpp:211-247 addRouting, :260-270 addRouted) on the
-// B200 kernels, for the rows of one lane's verify block (up to 16 rows): the router's fp32 scores
+// B200 kernels, for the rows of one lane's verify block (up to 16 rows: a route streams its expert by itself) or of several
+// lanes' blocks (routes grouped by expert on the many-row kernel): the router's fp32 scores
 // (Linear::addFloat over the router's rows), the routes and their weights, the expert passes and the combine.
 #pragma once
 #include "Linear.hpp"
@@ -60,7 +61,7 @@ class MoE {
     SbMoeExpertArgs a{b.input.as(), b.residual ? b.residual.as() : nullptr, b.selected.as<uint32_t>(), b.weights.as<float>(), w.gate.as(), w.up.as(),
                       w.down.as(), b.scratch.as(), b.output.as(), rows, s.routes(), s.hidden, s.intermediate, SB_FMT_Q4K, s.expertsTotal()};
     check(sb_moe_experts(graph.stream, &a));
-    graph.launches += 3;
+    graph.launches += rows > 16 ? 6 : 3;  // (grouping, two conversions, two grouped passes, combine)
   }
 };
 

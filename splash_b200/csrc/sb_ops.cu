@@ -76,7 +76,7 @@ __global__ void rope_kernel(const uint32_t *positions, uint32_t rows, const floa
 }
 
 // ---- fp32 projection of plain fp32 rows: grid (columns, 2); a warp per (column, row), lanes over k ----
-constexpr int kF32Rows = 16;
+constexpr int kF32Rows = 1024;  // (a warp per (column, row): the rows of several lanes too)
 __global__ void __launch_bounds__(256) linear_f32_kernel(const float *w, const uint16_t *x, uint32_t rows, uint32_t n,
                                                          uint32_t k, uint32_t x_stride, void *out, uint32_t out_stride,
                                                          uint32_t out_f32, const float *norm_w) {

@@ -232,10 +232,10 @@ def test_moe_experts_of_many_rows_grouped_by_expert_match_oracle(shape):
     assert np.abs(g - ol.bf2f(res)).max() > 1e-3     # the experts did contribute
 
 
-def build_lanes(lanes, positions, seed=0):
+def build_lanes(lanes, positions, seed=0, **more):
     from splash_b200 import lib, target
     lib.init(0)
-    cfg = dict(target.TINY, lanes=lanes)     # (Q4_K projections, Q6_K head: the head runs from its image)
+    cfg = dict(target.TINY, lanes=lanes, **more)     # (Q4_K projections, Q6_K head: the head runs from its image)
     t = target.Target(**cfg)
     w = mo.make_weights(cfg, seed)
     states = [mo.make_state(cfg, int(positions[i]), seed + 1 + i) for i in range(lanes)]
@@ -280,6 +280,35 @@ def test_tiny_model_of_four_lanes_matches_four_oracle_lanes(flags_name):
                 states[i]["pending_rows"] = retained
             first[i] = int(tokens[-1])
     assert compared >= 9 and len(set(lengths)) >= 3, (compared, lengths)
+
+
+def test_tiny_moe_model_of_three_lanes_matches_three_oracle_lanes():
+    """MoE feed-forward blocks (16 experts + the shared one, top 4, expert width 256) under several lanes: the 48 rows' routes
+    grouped by expert inside whole steps."""
+    positions = np.array([2048, 700, 1300], np.uint32)
+    lib, target, t, cfg, w, states = build_lanes(3, positions, seed=5, moe_experts=16, moe_top_k=4, moe_intermediate=256)
+    first, compared = [31, 77, 4000], 0
+    for step in range(2):
+        blocks = np.stack([mo.draft_chain(cfg, w, states[i], first[i], rows=16, p_match=0.6, seed=10 * step + i) for i in range(3)])
+        wants = [mo.verify_step(cfg, w, states[i], blocks[i], advance=True) for i in range(3)]
+        got = t.verify_lanes(blocks, flags=target.ADVANCE | target.GRAPH)
+        assert lib.device_status() == 0
+        logits = t.download(-1, "logits", np.float32, (48, cfg["vocab"]))
+        for i in range(3):
+            want, (tokens, retained, accepted, mask) = wants[i], got[i]
+            err = np.abs(logits[16 * i:16 * i + 16] - want["logits"])
+            scale = np.abs(want["logits"]).max()
+            assert err.max() <= 3e-2 * scale and np.median(err) <= 2e-3 * scale, (step, i)
+            top2 = np.sort(want["logits"], axis=1)[:, -2:]
+            if ((top2[:, 1] - top2[:, 0]) > 2.5 * err.max(axis=1))[:want["retained"]].all():
+                assert (retained, accepted, mask) == (want["retained"], want["accepted"], want["mask"]), (step, i)
+                assert np.array_equal(tokens, want["tokens"]), (step, i)
+                compared += 1
+            else:
+                states[i]["committed"] += retained - want["retained"]
+                states[i]["pending_rows"] = retained
+            first[i] = int(tokens[-1])
+    assert compared >= 4, compared
 
 
 def test_lane_of_a_four_lane_step_does_not_depend_on_the_other_lanes():
