@@ -180,73 +180,92 @@ static MoeGroupLayout moe_group_layout(uint32_t rows, uint32_t routes, uint32_t 
   return l;
 }
 
-// One CTA: a stable counting sort of the routes by expert. Thread e counts expert e's routes, one thread lays the experts'
-// groups out one after the other (an expert's routes in groups of 128, the last padded to 16 row slots), thread e then
-// numbers its routes in their order (row, then slot of the row).
+// One CTA of 16 warps: a stable counting sort of the routes by expert. Warp w owns a run of consecutive routes; it counts
+// them by expert (a step of 32 routes at a time, equal experts found with a warp match), a thread per expert then adds the
+// warps' counts in warp order, one warp lays the experts' groups out one after the other (an expert's routes in groups of
+// 128, the last padded to 16 row slots), and the warps walk their runs again to number the routes: a route's place among
+// its expert's routes is the earlier warps' count, plus this warp's count so far, plus its rank inside the step.
+constexpr uint32_t kMoeGroupWarps = kMoeGroupThreads / 32;
 __global__ void __launch_bounds__(kMoeGroupThreads) moe_group_kernel(const uint32_t *selected, uint32_t n, uint32_t routes, uint32_t experts, MoeGrouping g,
                                                                      uint32_t *status) {
-  extern __shared__ __align__(16) uint16_t ids[];  // [n rounded up to 8]
+  __shared__ uint16_t warp_count[kMoeGroupWarps][kMoeMaxExperts];  // then: the place of the warp's next route of the expert
   __shared__ uint32_t count_s[kMoeMaxExperts], slot0_s[kMoeMaxExperts], group0_s[kMoeMaxExperts];
   pdl_launch_dependents();
   pdl_wait();
-  const uint32_t tid = threadIdx.x, n8 = (n + 7) / 8 * 8;
-  for (uint32_t i = tid; i < n8; i += kMoeGroupThreads) {
-    uint32_t e = i < n ? selected[i] : 0xffffu;
-    if (i < n && e >= experts) {  // outside the contract: the route is dropped and the launch says so
+  const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  for (uint32_t i = tid; i < kMoeGroupWarps * kMoeMaxExperts; i += kMoeGroupThreads) (&warp_count[0][0])[i] = 0;
+  __syncthreads();
+  const uint32_t run = ((n + kMoeGroupWarps - 1) / kMoeGroupWarps + 31) / 32 * 32, first = warp * run, last = min(n, first + run);
+  const uint32_t lt = (1u << lane) - 1u;
+  auto expert_at = [&](uint32_t i) -> uint32_t {
+    if (i >= last) return 0xffffffffu;
+    const uint32_t e = selected[i];
+    if (e >= experts) {  // outside the contract: the route is dropped and the launch says so
       atomicCAS(status, 0u, uint32_t(SB_DEV_CONTRACT));
-      e = 0xffffu;
+      return 0xffffffffu;
     }
-    ids[i] = uint16_t(e);
-  }
-  __syncthreads();
-  auto walk = [&](uint32_t e, auto &&found) {
-    const uint32_t pat = e | (e << 16);
-    for (uint32_t i = 0; i < n8; i += 8) {
-      const uint4 v = *reinterpret_cast<const uint4 *>(ids + i);
-      const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t x = w[j] ^ pat;
-        if (!(x & 0xffffu)) found(i + 2 * j);
-        if (!(x >> 16)) found(i + 2 * j + 1);
-      }
-    }
+    return e;
   };
-  for (uint32_t e = tid; e < experts; e += kMoeGroupThreads) {
-    uint32_t c = 0;
-    walk(e, [&](uint32_t) { ++c; });
-    count_s[e] = c;
+  for (uint32_t i0 = first; i0 < last; i0 += 32) {
+    const uint32_t e = expert_at(i0 + lane);
+    const uint32_t same = __match_any_sync(0xffffffffu, e);
+    if (e != 0xffffffffu && !(same & lt)) warp_count[warp][e] += uint16_t(__popc(same));
+    __syncwarp();
   }
   __syncthreads();
-  if (tid == 0) {
+  for (uint32_t e = tid; e < experts; e += kMoeGroupThreads) {
+    uint32_t total = 0;
+    for (uint32_t w = 0; w < kMoeGroupWarps; ++w) {
+      const uint32_t c = warp_count[w][e];
+      warp_count[w][e] = uint16_t(total);
+      total += c;
+    }
+    count_s[e] = total;
+  }
+  __syncthreads();
+  if (warp == 0) {
+    // 32 experts a round: their group counts and padded slots scanned over the lanes
     uint32_t slot = 0, group = 0;
-    for (uint32_t e = 0; e < experts; ++e) {
-      slot0_s[e] = slot, group0_s[e] = group;
-      for (uint32_t left = count_s[e]; left > 0;) {
-        const uint32_t rows = min(left, kMoeGroupRows), padded = (rows + 15) / 16 * 16;
-        g.groups[group++] = make_uint4(e, slot, rows, padded);
-        slot += padded, left -= rows;
+    for (uint32_t e0 = 0; e0 < experts; e0 += 32) {
+      const uint32_t e = e0 + lane, c = e < experts ? count_s[e] : 0;
+      const uint32_t groups = (c + kMoeGroupRows - 1) / kMoeGroupRows, slots = (c + 15) / 16 * 16;
+      uint32_t gs = groups, ss = slots;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t a = __shfl_up_sync(0xffffffffu, gs, o), b = __shfl_up_sync(0xffffffffu, ss, o);
+        if (lane >= uint32_t(o)) gs += a, ss += b;
       }
+      const uint32_t my_group = group + gs - groups, my_slot = slot + ss - slots;
+      if (e < experts) {
+        slot0_s[e] = my_slot, group0_s[e] = my_group;
+        for (uint32_t k = 0; k < groups; ++k) {
+          const uint32_t rows = min(c - k * kMoeGroupRows, kMoeGroupRows);
+          g.groups[my_group + k] = make_uint4(e, my_slot + k * kMoeGroupRows, rows, (rows + 15) / 16 * 16);
+        }
+        // the padding slots behind the expert's last route
+        const uint32_t lastg = my_group + (groups ? groups - 1 : 0);
+        for (uint32_t r = c; r < slots; ++r) {
+          g.slot_src[my_slot + r] = 0xffffffffu, g.slot_self[my_slot + r] = 0xffffffffu;
+          g.slot_group[my_slot + r] = (lastg << 8) | (r - (lastg - my_group) * kMoeGroupRows);
+        }
+      }
+      group += __shfl_sync(0xffffffffu, gs, 31), slot += __shfl_sync(0xffffffffu, ss, 31);
     }
-    g.counts[0] = group, g.counts[1] = slot;
+    if (lane == 0) g.counts[0] = group, g.counts[1] = slot;
   }
   __syncthreads();
-  for (uint32_t e = tid; e < experts; e += kMoeGroupThreads) {
-    const uint32_t slot0 = slot0_s[e], group0 = group0_s[e];
-    uint32_t j = 0;
-    walk(e, [&](uint32_t i) {  // (full groups carry no padding, so the expert's j-th route sits at slot0 + j)
-      g.slot_of_route[i] = slot0 + j;
-      g.slot_src[slot0 + j] = i / routes, g.slot_self[slot0 + j] = slot0 + j;
-      g.slot_group[slot0 + j] = ((group0 + j / kMoeGroupRows) << 8) | (j % kMoeGroupRows);
-      ++j;
-    });
-    if (j) {
-      const uint32_t last = group0 + (j - 1) / kMoeGroupRows;
-      for (uint32_t r = j; r < (j + 15) / 16 * 16; ++r) {
-        g.slot_src[slot0 + r] = 0xffffffffu, g.slot_self[slot0 + r] = 0xffffffffu;
-        g.slot_group[slot0 + r] = (last << 8) | (r - (last - group0) * kMoeGroupRows);
-      }
+  for (uint32_t i0 = first; i0 < last; i0 += 32) {
+    const uint32_t i = i0 + lane, e = expert_at(i);
+    const uint32_t same = __match_any_sync(0xffffffffu, e);
+    if (e != 0xffffffffu) {
+      const uint32_t j = warp_count[warp][e] + __popc(same & lt), slot = slot0_s[e] + j;  // (full groups carry no padding)
+      g.slot_of_route[i] = slot;
+      g.slot_src[slot] = i / routes, g.slot_self[slot] = slot;
+      g.slot_group[slot] = ((group0_s[e] + j / kMoeGroupRows) << 8) | (j % kMoeGroupRows);
     }
+    __syncwarp();
+    if (e != 0xffffffffu && !(same & lt)) warp_count[warp][e] += uint16_t(__popc(same));
+    __syncwarp();
   }
 }
 
@@ -308,7 +327,7 @@ static int moe_experts_grouped(cudaStream_t s, const SbMoeExpertArgs *a) {
   const bool pdl = ctx().pdl;
   {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(1), cfg.blockDim = dim3(kMoeGroupThreads), cfg.dynamicSmemBytes = size_t((n + 7) / 8 * 8) * 2, cfg.stream = s;
+    cfg.gridDim = dim3(1), cfg.blockDim = dim3(kMoeGroupThreads), cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;

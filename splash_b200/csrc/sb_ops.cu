@@ -61,6 +61,61 @@ __global__ void __launch_bounds__(256) embed_kernel(uint32_t format, const uint8
   out[size_t(r) * out_stride + c] = float_to_bf16_bits(v);
 }
 
+// ---- the same projection for many rows (the rows of several lanes): warp-level MMA with the fp32 weights split into three
+// bf16 terms (hi + mid + lo carry the 24 bits of an fp32 significand), so every product with a bf16 input is exact and the
+// sums run in fp32. grid (n / 16, rows / 128); a warp takes 16 rows x 16 columns over all of k. ----
+__device__ __forceinline__ void split3_bf16(float a, float b, uint32_t &hi, uint32_t &mid, uint32_t &lo) {
+  const uint32_t ah = float_to_bf16_bits(a), bh = float_to_bf16_bits(b);
+  const float ar = a - bf16_bits_to_float(ah), br = b - bf16_bits_to_float(bh);
+  const uint32_t am = float_to_bf16_bits(ar), bm = float_to_bf16_bits(br);
+  const uint32_t al = float_to_bf16_bits(ar - bf16_bits_to_float(am)), bl = float_to_bf16_bits(br - bf16_bits_to_float(bm));
+  hi = ah | (bh << 16), mid = am | (bm << 16), lo = al | (bl << 16);
+}
+__global__ void __launch_bounds__(256) linear_f32_rows_kernel(const float *w, const uint16_t *x, uint32_t rows, uint32_t n, uint32_t k,
+                                                              uint32_t x_stride, void *out, uint32_t out_stride, uint32_t out_f32) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+  const uint32_t r0 = blockIdx.y * 128 + 16 * warp, c0 = blockIdx.x * 16;
+  if (r0 >= rows) return;
+  const uint16_t *xa = x + size_t(min(r0 + g, rows - 1)) * x_stride + 2 * t, *xb = x + size_t(min(r0 + g + 8, rows - 1)) * x_stride + 2 * t;
+  const float *w0 = w + size_t(c0 + g) * k + 2 * t, *w1 = w + size_t(c0 + 8 + g) * k + 2 * t;
+  // The tensor cores' fp32 additions truncate; sums of 64 inputs are kept short and added up with rounded additions.
+  float acc[2][4] = {}, total[2][4] = {};
+#pragma unroll 4
+  for (uint32_t k0 = 0; k0 < k; k0 += 16) {
+    if (k0 && k0 % 64 == 0) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) total[j][i] += acc[j][i], acc[j][i] = 0.0f;
+    }
+    const uint32_t a0 = *reinterpret_cast<const uint32_t *>(xa + k0), a1 = *reinterpret_cast<const uint32_t *>(xb + k0);
+    const uint32_t a2 = *reinterpret_cast<const uint32_t *>(xa + k0 + 8), a3 = *reinterpret_cast<const uint32_t *>(xb + k0 + 8);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const float *wr = j ? w1 : w0;
+      const float2 p = *reinterpret_cast<const float2 *>(wr + k0), q = *reinterpret_cast<const float2 *>(wr + k0 + 8);
+      uint32_t h0, m0, l0, h1, m1, l1;
+      split3_bf16(p.x, p.y, h0, m0, l0);
+      split3_bf16(q.x, q.y, h1, m1, l1);
+      mma_bf16(acc[j], a0, a1, a2, a3, l0, l1);  // the small terms first
+      mma_bf16(acc[j], a0, a1, a2, a3, m0, m1);
+      mma_bf16(acc[j], a0, a1, a2, a3, h0, h1);
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t r = r0 + g + (i >> 1) * 8, c = c0 + 8 * j + 2 * t + (i & 1);
+      if (r >= rows) continue;
+      const float v = total[j][i] + acc[j][i];
+      if (out_f32) static_cast<float *>(out)[size_t(r) * out_stride + c] = v;
+      else static_cast<uint16_t *>(out)[size_t(r) * out_stride + c] = float_to_bf16_bits(v);
+    }
+}
+
 // ---- RoPE tables ----
 __global__ void rope_kernel(const uint32_t *positions, uint32_t rows, const float *inv_freq, uint32_t pairs, float scale,
                             float *cosine, float *sine) {
@@ -796,6 +851,9 @@ int sb_linear_f32(void *stream, const float *w_dev, const void *x, uint32_t rows
   SB_REQUIRE(w_dev && x && out, "sb_linear_f32: null pointer");
   SB_REQUIRE(rows >= 1 && rows <= kF32Rows && n && k, "sb_linear_f32: rows = %u outside 1..%d, or empty shape", rows, kF32Rows);
   SB_REQUIRE(x_stride >= k && out_stride >= n && k % 8 == 0 && x_stride % 8 == 0, "sb_linear_f32: stride below extent, or k not a multiple of 8");
+  if (rows > 16 && !norm_weight && n % 16 == 0 && k % 16 == 0)  // many rows: on the tensor cores
+    return launch(linear_f32_rows_kernel, dim3(n / 16, (rows + 127) / 128), dim3(256), as_stream(stream), w_dev, static_cast<const uint16_t *>(x), rows, n, k,
+                  x_stride, out, out_stride, out_f32);
   return launch(linear_f32_kernel, dim3(n, (rows + 7) / 8), dim3(256), as_stream(stream), w_dev, static_cast<const uint16_t *>(x), rows, n, k,
                 x_stride, out, out_stride, out_f32, static_cast<const float *>(norm_weight));
 }

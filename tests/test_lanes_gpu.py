@@ -189,6 +189,24 @@ def test_selection_penalties_and_acceptance_of_lanes_equal_the_lanes_one_at_a_ti
     assert len(set(greedy[:, 0].tolist())) >= 3          # the lanes did accept different lengths
 
 
+@pytest.mark.parametrize("rows,n,k", [(200, 256, 2048), (512, 64, 1024), (17, 48, 512)])
+def test_float_projection_of_many_rows_keeps_fp32_accuracy(rows, n, k):
+    """sb_linear_f32 over more than 16 rows runs on the tensor cores with the fp32 weights split into three bf16 terms:
+    against fp64 it stays at fp32 accuracy (the router's scores decide routes)."""
+    lib, l, o = _setup()
+    rng = np.random.default_rng(rows)
+    w = (rng.standard_normal((n, k)) * 0.05).astype(np.float32)
+    x = bf16_randn(rng, (rows, k), 2.0)
+    wd, xd, od = lib.DeviceBuffer.from_numpy(w), lib.DeviceBuffer.from_numpy(x), lib.DeviceBuffer(rows * n * 4)
+    lib.check(l.sb_linear_f32(None, wd.ptr, xd.ptr, rows, n, k, k, od.ptr, n, 1, None))
+    lib.stream_sync()
+    got = od.to_numpy(np.float32, (rows, n)).astype(np.float64)
+    xf = ol.bf2f(x).astype(np.float64)
+    want = xf @ w.astype(np.float64).T
+    bound = 2.0 ** -20 * (np.abs(xf) @ np.abs(w.astype(np.float64)).T)      # fp32 sums of exact products (the tensor cores' additions truncate)
+    assert (np.abs(got - want) <= bound + 1e-30).all(), float((np.abs(got - want) / bound).max())
+
+
 @pytest.mark.parametrize("shape", [
     dict(rows=200, experts=24, slots=32, top_k=8, H=1024, I=512),     # about 67 routes an expert; the shared expert's 200 rows are two groups
     dict(rows=128, experts=256, slots=256, top_k=8, H=2048, I=512),   # the 35B-A3B block at 8 lanes: about 4 routes an expert
