@@ -514,6 +514,11 @@ typedef struct SbTargetConfig {
    * a step multiplies 16 x lanes rows on the many-row projection kernel, which needs Q4_K projections (fmt_proj, fmt_down,
    * fmt_head). Dense models on one GPU; chain blocks. */
   uint32_t lanes;
+  /* Expert parallelism: this process is rank ep_rank of ep_world ranks (0 or 1: none), one per GPU of the node. Every rank
+   * steps its own `lanes` lanes and holds the routed experts [ep_rank E / ep_world, ..) of every MoE block in its
+   * ffn_*_exps tensors, then the shared expert ([E / ep_world + 1] experts); everything else whole. MoE models with
+   * several lanes. The ranks' windows are connected with sb_target_tp_export / sb_target_tp_connect. */
+  uint32_t ep_world, ep_rank;
 } SbTargetConfig;
 
 enum {
@@ -571,6 +576,14 @@ typedef struct SbMoeExpertArgs {
 } SbMoeExpertArgs;
 SB_API uint64_t sb_moe_scratch_bytes(uint32_t rows, uint32_t routes, uint32_t hidden, uint32_t inter);
 SB_API int sb_moe_experts(void *stream, const SbMoeExpertArgs *args);
+/* A rank's share of an MoE block under expert parallelism: of the routes in `selected` (expert ids of the whole block) those
+ * whose expert is one of [expert0, expert0 + experts_local), and those of the shared expert (id shared_id, if below
+ * 0xffffffff) for rows [own_row0, own_row0 + own_rows). gate / up / down hold the rank's experts in order, then the shared
+ * expert: experts_total = experts_local (+ 1). out: fp32 [rows, hidden], the weighted sums in slot order (no residual; rows
+ * without a route here get zeros). Any number of rows (the grouped kernels); scratch as sb_moe_scratch_bytes with at
+ * least 17 rows. */
+SB_API int sb_moe_experts_partial(void *stream, const SbMoeExpertArgs *args, uint32_t expert0, uint32_t experts_local, uint32_t shared_id,
+                                  uint32_t own_row0, uint32_t own_rows);
 
 /* ---- tensor parallelism between the GPUs of one node ----
  * The reference runs on one GPU; its projections admit the usual split, and this is it: rank r of W holds
@@ -610,6 +623,25 @@ SB_API int sb_tp_all_gather(void *stream, void *group, uint32_t index, uint32_t 
 SB_API int sb_tp_set_exchange(int shots);
 /* Ends a step of `exchanges` exchanges: the next step's indices start over. (sb_target_* steps do this themselves.) */
 SB_API int sb_tp_advance(void *stream, void *group, uint32_t exchanges);
+
+/* ---- expert parallelism between the GPUs of one node ----
+ * Rank r of W holds the routed experts [r E / W, (r + 1) E / W) of every MoE block (and a copy of the shared expert, which
+ * it applies to its own rows) and steps its own lanes; the reference runs on one GPU (MoE::addRouted,
+ * runtime/ops/MoE.cpp:122-187,260-270). A block's rows meet their experts in two exchanges through peer-mapped memory
+ * (CUDA IPC windows over NVLink, plain stores and loads, bounded waits):
+ *   sb_ep_dispatch  every rank's normalised rows (bf16 [rows, hidden]), routes and route weights ([rows, routes]) into
+ *                   every rank's gathered arrays [world][rows][..] (sb_ep_gathered)
+ *   sb_moe_experts_partial over the gathered rows: the routes that name this rank's experts, weighted sums per row
+ *   sb_ep_combine   partial: this rank's sums for every rank's rows (fp32 [world][rows][hidden]); out = bf16(residual + the
+ *                   ranks' sums for this rank's rows, added in rank order)
+ * Windows are exchanged as CUDA IPC handles (SB_TP_HANDLE_BYTES each, rank order), as for sb_tp_connect. */
+SB_API int sb_ep_create(uint32_t world, uint32_t rank, uint32_t rows, uint32_t hidden, uint32_t routes, void **out_group);
+SB_API int sb_ep_destroy(void *group);
+SB_API int sb_ep_export(void *group, void *handle_out /* SB_TP_HANDLE_BYTES */);
+SB_API int sb_ep_connect(void *group, const void *handles /* [world][SB_TP_HANDLE_BYTES] */);
+SB_API int sb_ep_gathered(void *group, void **out_rows, uint32_t **out_selected, float **out_weights);
+SB_API int sb_ep_dispatch(void *stream, void *group, const void *rows, const uint32_t *selected, const float *weights);
+SB_API int sb_ep_combine(void *stream, void *group, const float *partial, const void *residual, void *out);
 
 SB_API int sb_target_create(const SbTargetConfig *config, void **out_target);
 /* With tp_world > 1: the handle of this rank's exchange window, and the connection to all ranks' (sb_tp_export,

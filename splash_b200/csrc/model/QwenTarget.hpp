@@ -19,6 +19,7 @@
 #include "../ops/MoE.hpp"
 #include "../ops/PagedAttention.hpp"
 #include "../ops/Sampling.hpp"
+#include "../ops/ExpertParallel.hpp"
 #include "../ops/TensorParallel.hpp"
 
 namespace splash::b200::model {
@@ -89,6 +90,7 @@ class QwenTarget {
   const SbTargetConfig &local() const { return loc_; }    // this rank's heads and intermediate width (the vocabulary stays whole)
   const SbTargetShare &share() const { return share_; }
   ops::TensorParallel *tensorParallel() { return tp_.get(); }
+  ops::ExpertParallel *expertParallel() { return ep_.get(); }
   // Exchanges of one step: one after every out_proj and down, one for the logits.
   uint32_t exchangesPerStep() const { return 2 * cfg_.layers + 1; }
   bool find(int layer, const std::string &name, Buffer &out) const;
@@ -96,7 +98,11 @@ class QwenTarget {
 
   // Bytes one step streams: weights once, the visible INT8 cache, the GDN state in and out.
   // (MoE blocks: a step reads the routed experts only, every route its own expert's three matrices)
-  uint64_t weightBytes(uint32_t rows = kVerifyRows) const { return weightBytes_ + uint64_t(moeLayers_) * rows * moe_.routes() * moeExpertBytes_; }
+  // (the rows of several lanes are grouped by expert: every expert the rank holds streams once)
+  uint64_t weightBytes(uint32_t rows = kVerifyRows) const {
+    const uint64_t experts = wide_ ? (ep_ ? ep_->local().expertsTotal() : moe_.expertsTotal()) : uint64_t(rows) * moe_.routes();
+    return weightBytes_ + uint64_t(moeLayers_) * experts * moeExpertBytes_;
+  }
   uint64_t kvBytes(uint32_t visible) const;
   uint64_t stateBytes() const;
 
@@ -127,6 +133,7 @@ class QwenTarget {
   Buffer floats(size_t count) { return Buffer::allocate(count * 4); }
 
   ops::MoeShape moe_;
+  std::unique_ptr<ops::ExpertParallel> ep_;
   Buffer moeScores_, moeSelected_, moeWeights_, moeScratch_;
   SbTargetConfig cfg_, loc_;
   SbTargetShare share_{};
@@ -195,6 +202,12 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
     if (!c.moe_top_k || c.moe_top_k > c.moe_experts || c.moe_experts > 256 || !c.moe_intermediate || c.moe_intermediate % 256)
       throw std::invalid_argument("QwenTarget: MoE shape (up to 256 experts, top_k of them, intermediate a multiple of 256)");
   }
+  if (whole.ep_world > 1) {
+    // Expert parallelism: this rank's lanes, its share of every block's experts; the blocks' rows meet their experts
+    // through the ranks' exchange windows (ops::ExpertParallel).
+    if (!c.moe_experts || !wide_) throw std::invalid_argument("QwenTarget: expert parallelism is offered for MoE models stepping several lanes");
+    ep_ = std::make_unique<ops::ExpertParallel>(whole.ep_world, whole.ep_rank, kVerifyRows * L, moe_);
+  }
   gdn_.keyHeads = c.gdn_key_heads, gdn_.valueHeads = c.gdn_value_heads;
   kv_.kvHeads = c.kv_heads, kv_.headDimension = c.head_dim, kv_.pageTokens = c.page_tokens, kv_.halfScales = c.kv_scale_f16 != 0;
   const uint32_t H = c.hidden, D = c.head_dim;
@@ -232,7 +245,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
       }
     }
     if (c.moe_experts) {
-      const uint32_t total = moe_.expertsTotal();
+      const uint32_t total = ep_ ? ep_->local().expertsTotal() : moe_.expertsTotal();  // (the router stays whole)
       w.moe.router = floats(size_t(moe_.slots) * H), w.moe.sharedGate = floats(H);
       const size_t pair = size_t(total) * moe_.intermediate * sb_row_bytes(c.fmt_proj, H), down = size_t(total) * H * sb_row_bytes(c.fmt_proj, moe_.intermediate);
       w.moe.gate = Buffer::allocate(pair), w.moe.up = Buffer::allocate(pair), w.moe.down = Buffer::allocate(down);
@@ -528,7 +541,8 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
       Normalization::addRms(graph, hidden[cur], w.ffnNorm, normed_, H, R, H, H);
       MoeBuffers mb{normed_, hidden[cur], moeScores_, moeSelected_, moeWeights_, moeScratch_, hidden[cur ^ 1]};
       MoE::addRouting(graph, moe_, w.moe, mb, R);
-      MoE::addRouted(graph, moe_, w.moe, mb, R);
+      if (ep_) ep_->addRouted(graph, w.moe, mb);
+      else MoE::addRouted(graph, moe_, w.moe, mb, R);
       cur ^= 1;
       continue;
     }

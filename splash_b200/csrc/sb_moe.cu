@@ -186,8 +186,14 @@ static MoeGroupLayout moe_group_layout(uint32_t rows, uint32_t routes, uint32_t 
 // 128, the last padded to 16 row slots), and the warps walk their runs again to number the routes: a route's place among
 // its expert's routes is the earlier warps' count, plus this warp's count so far, plus its rank inside the step.
 constexpr uint32_t kMoeGroupWarps = kMoeGroupThreads / 32;
+// Which routes a launch takes, and the expert's place in its tensors: all of them (experts0 = 0, local = experts), or a
+// rank's share under expert parallelism: experts [expert0, expert0 + local) at 0 .., the shared expert (shared_id) for rows
+// [own_row0, own_row0 + own_rows) at `local`.
+struct MoeShare {
+  uint32_t expert0, local, shared_id, own_row0, own_rows;
+};
 __global__ void __launch_bounds__(kMoeGroupThreads) moe_group_kernel(const uint32_t *selected, uint32_t n, uint32_t routes, uint32_t experts, MoeGrouping g,
-                                                                     uint32_t *status) {
+                                                                     uint32_t *status, MoeShare share) {
   __shared__ uint16_t warp_count[kMoeGroupWarps][kMoeMaxExperts];  // then: the place of the warp's next route of the expert
   __shared__ uint32_t count_s[kMoeMaxExperts], slot0_s[kMoeMaxExperts], group0_s[kMoeMaxExperts];
   pdl_launch_dependents();
@@ -200,11 +206,15 @@ __global__ void __launch_bounds__(kMoeGroupThreads) moe_group_kernel(const uint3
   auto expert_at = [&](uint32_t i) -> uint32_t {
     if (i >= last) return 0xffffffffu;
     const uint32_t e = selected[i];
-    if (e >= experts) {  // outside the contract: the route is dropped and the launch says so
-      atomicCAS(status, 0u, uint32_t(SB_DEV_CONTRACT));
-      return 0xffffffffu;
+    if (e == share.shared_id) {
+      const uint32_t row = i / routes;
+      return row >= share.own_row0 && row - share.own_row0 < share.own_rows ? share.local : 0xffffffffu;
     }
-    return e;
+    if (e - share.expert0 < share.local) return e - share.expert0;
+    if (share.expert0 == 0 && share.shared_id == 0xffffffffu && share.local == experts) {  // a whole block: an id outside it breaks the contract
+      atomicCAS(status, 0u, uint32_t(SB_DEV_CONTRACT));
+    }
+    return 0xffffffffu;  // another rank's expert (or a dropped route)
   };
   for (uint32_t i0 = first; i0 < last; i0 += 32) {
     const uint32_t e = expert_at(i0 + lane);
@@ -262,6 +272,8 @@ __global__ void __launch_bounds__(kMoeGroupThreads) moe_group_kernel(const uint3
       g.slot_of_route[i] = slot;
       g.slot_src[slot] = i / routes, g.slot_self[slot] = slot;
       g.slot_group[slot] = ((group0_s[e] + j / kMoeGroupRows) << 8) | (j % kMoeGroupRows);
+    } else if (i < last) {
+      g.slot_of_route[i] = 0xffffffffu;
     }
     __syncwarp();
     if (e != 0xffffffffu && !(same & lt)) warp_count[warp][e] += uint16_t(__popc(same));
@@ -270,7 +282,8 @@ __global__ void __launch_bounds__(kMoeGroupThreads) moe_group_kernel(const uint3
 }
 
 // out = bf16(residual + sum over the row's routes in slot order of weight * float(y)), y at the routes' row slots.
-__global__ void __launch_bounds__(256) moe_combine_grouped_kernel(const SbMoeExpertArgs a, const uint32_t *slot_of_route, const uint16_t *y) {
+// partial != 0: the routes the launch took only (slot_of_route says which: the others hold ~0), fp32 sums without the residual.
+__global__ void __launch_bounds__(256) moe_combine_grouped_kernel(const SbMoeExpertArgs a, const uint32_t *slot_of_route, const uint16_t *y, uint32_t partial) {
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t row = blockIdx.y, c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
@@ -278,10 +291,14 @@ __global__ void __launch_bounds__(256) moe_combine_grouped_kernel(const SbMoeExp
   float acc0 = 0.0f, acc1 = 0.0f;
   for (uint32_t s = 0; s < a.routes; ++s) {
     const uint32_t route = row * a.routes + s, slot = slot_of_route[route];
-    if (a.selected[route] >= a.experts_total) continue;  // (dropped by the grouping, which has flagged it)
+    if (slot == 0xffffffffu) continue;  // (not taken by the grouping)
     const float w = a.weights[route];
     const uint32_t pair = *reinterpret_cast<const uint32_t *>(y + size_t(slot) * a.hidden + c);
     acc0 += w * bf16_bits_to_float(pair & 0xffffu), acc1 += w * bf16_bits_to_float(pair >> 16);
+  }
+  if (partial) {
+    *reinterpret_cast<float2 *>(static_cast<float *>(a.out) + size_t(row) * a.hidden + c) = make_float2(acc0, acc1);
+    return;
   }
   float r0 = 0.0f, r1 = 0.0f;
   if (a.residual) {
@@ -314,7 +331,7 @@ extern "C" uint64_t sb_moe_scratch_bytes(uint32_t rows, uint32_t routes, uint32_
 
 // More than 16 rows: group the routes by expert, gather and convert each group's rows, the experts' one-pass gate/up and
 // down on the many-row kernel over the groups, and the combine.
-static int moe_experts_grouped(cudaStream_t s, const SbMoeExpertArgs *a) {
+static int moe_experts_grouped(cudaStream_t s, const SbMoeExpertArgs *a, const MoeShare *part = nullptr) {
   const uint64_t n = uint64_t(a->rows) * a->routes;
   SB_REQUIRE(n <= kMoeMaxRoutes && a->experts_total <= kMoeMaxExperts, "sb_moe_experts: %u rows x %u routes over %u experts (up to %u routes, %u experts)",
              a->rows, a->routes, a->experts_total, kMoeMaxRoutes, kMoeMaxExperts);
@@ -332,7 +349,8 @@ static int moe_experts_grouped(cudaStream_t s, const SbMoeExpertArgs *a) {
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr, cfg.numAttrs = pdl ? 1 : 0;
-    SB_CUDA(cudaLaunchKernelEx(&cfg, moe_group_kernel, a->selected, uint32_t(n), a->routes, a->experts_total, g, ctx().status_dev));
+    const MoeShare share = part ? *part : MoeShare{0, a->experts_total, 0xffffffffu, 0, 0};
+    SB_CUDA(cudaLaunchKernelEx(&cfg, moe_group_kernel, a->selected, uint32_t(n), a->routes, a->experts_total, g, ctx().status_dev, share));
   }
   WidePrepareGroupedArgs c1{a->input, a->hidden, a->hidden, g.slot_src, g.slot_group, g.counts + 1, l.max_slots, g.groups, at(l.prepared1),
                             reinterpret_cast<float *>(at(l.scales1)), pdl};
@@ -356,21 +374,31 @@ static int moe_experts_grouped(cudaStream_t s, const SbMoeExpertArgs *a) {
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = pdl ? 1 : 0;
-  SB_CUDA(cudaLaunchKernelEx(&cfg, moe_combine_grouped_kernel, *a, static_cast<const uint32_t *>(g.slot_of_route), reinterpret_cast<const uint16_t *>(at(l.y))));
+  SB_CUDA(cudaLaunchKernelEx(&cfg, moe_combine_grouped_kernel, *a, static_cast<const uint32_t *>(g.slot_of_route), reinterpret_cast<const uint16_t *>(at(l.y)),
+                             part ? 1u : 0u));
   return SB_OK;
+}
+
+static int moe_check(const SbMoeExpertArgs *a, const char *who);
+
+extern "C" int sb_moe_experts_partial(void *stream, const SbMoeExpertArgs *a, uint32_t expert0, uint32_t experts_local, uint32_t shared_id,
+                                      uint32_t own_row0, uint32_t own_rows) {
+  SB_NEED_DEVICE();
+  const int st = moe_check(a, "sb_moe_experts_partial");
+  if (st != SB_OK) return st;
+  const bool shared = shared_id != 0xffffffffu;
+  SB_REQUIRE(experts_local >= 1 && a->experts_total == experts_local + (shared ? 1u : 0u), "sb_moe_experts_partial: %u experts here (+ the shared one) against %u in the tensors",
+             experts_local, a->experts_total);
+  SB_REQUIRE(!shared || (shared_id >= expert0 + experts_local || shared_id < expert0), "sb_moe_experts_partial: the shared expert's id lies inside the rank's range");
+  SB_REQUIRE(own_row0 + own_rows <= a->rows, "sb_moe_experts_partial: own rows [%u, %u) of %u", own_row0, own_row0 + own_rows, a->rows);
+  const MoeShare share{expert0, experts_local, shared_id, own_row0, own_rows};
+  return moe_experts_grouped(as_stream(stream), a, &share);
 }
 
 extern "C" int sb_moe_experts(void *stream, const SbMoeExpertArgs *a) {
   SB_NEED_DEVICE();
-  SB_REQUIRE(a && a->input && a->selected && a->weights && a->gate && a->up && a->down && a->scratch && a->out, "sb_moe_experts: null pointer");
-  SB_REQUIRE(a->format == SB_FMT_Q4K, "sb_moe_experts: experts in format %u (Q4_K only)", a->format);
-  SB_REQUIRE(a->rows >= 1 && a->routes >= 1 && a->routes <= 32, "sb_moe_experts: %u rows x %u routes (1..32)", a->rows, a->routes);
-  SB_REQUIRE(a->hidden && a->hidden % 256 == 0 && a->inter && a->inter % 256 == 0 && a->hidden <= 8192 && a->inter <= 8192,
-             "sb_moe_experts: hidden %u and intermediate %u are multiples of 256 up to 8192", a->hidden, a->inter);
-  SB_REQUIRE(a->experts_total >= 1, "sb_moe_experts: no experts");
-  SB_REQUIRE(((reinterpret_cast<uintptr_t>(a->gate) | reinterpret_cast<uintptr_t>(a->up) | reinterpret_cast<uintptr_t>(a->down) |
-               reinterpret_cast<uintptr_t>(a->scratch)) & 15) == 0,
-             "sb_moe_experts: expert tensors and scratch must be 16-byte aligned");
+  const int valid = moe_check(a, "sb_moe_experts");
+  if (valid != SB_OK) return valid;
   if (a->rows > 16) return moe_experts_grouped(as_stream(stream), a);
   MoeParams p{*a, static_cast<uint16_t *>(a->scratch), static_cast<uint16_t *>(a->scratch) + size_t(a->rows) * a->routes * a->inter};
   const uint32_t routes = a->rows * a->routes, pair_block = kMoeWarps * kMoeColsPair, down_block = kMoeWarps * kMoeColsDown;
@@ -380,4 +408,17 @@ extern "C" int sb_moe_experts(void *stream, const SbMoeExpertArgs *a) {
   st = launch_moe(moe_expert_kernel<false>, dim3(routes, (a->hidden + down_block - 1) / down_block), dim3(kMoeThreads), size_t(a->inter) * 4, s, p);
   if (st != SB_OK) return st;
   return launch_moe(moe_combine_kernel, dim3((a->hidden + 255) / 256, a->rows), dim3(256), 0, s, p);
+}
+
+static int moe_check(const SbMoeExpertArgs *a, const char *who) {
+  SB_REQUIRE(a && a->input && a->selected && a->weights && a->gate && a->up && a->down && a->scratch && a->out, "%s: null pointer", who);
+  SB_REQUIRE(a->format == SB_FMT_Q4K, "%s: experts in format %u (Q4_K only)", who, a->format);
+  SB_REQUIRE(a->rows >= 1 && a->routes >= 1 && a->routes <= 32, "%s: %u rows x %u routes (1..32)", who, a->rows, a->routes);
+  SB_REQUIRE(a->hidden && a->hidden % 256 == 0 && a->inter && a->inter % 256 == 0 && a->hidden <= 8192 && a->inter <= 8192,
+             "%s: hidden %u and intermediate %u are multiples of 256 up to 8192", who, a->hidden, a->inter);
+  SB_REQUIRE(a->experts_total >= 1, "%s: no experts", who);
+  SB_REQUIRE(((reinterpret_cast<uintptr_t>(a->gate) | reinterpret_cast<uintptr_t>(a->up) | reinterpret_cast<uintptr_t>(a->down) |
+               reinterpret_cast<uintptr_t>(a->scratch)) & 15) == 0,
+             "%s: expert tensors and scratch must be 16-byte aligned", who);
+  return SB_OK;
 }

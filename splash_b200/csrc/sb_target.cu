@@ -227,7 +227,9 @@ int sb_target_tp_export(void *target, void *handle_out) {
   SB_NEED_DEVICE();
   SB_REQUIRE(target && handle_out, "sb_target_tp_export: null pointer");
   auto *tp = static_cast<Target *>(target)->model->tensorParallel();
-  SB_REQUIRE(tp, "sb_target_tp_export: the target was created without tensor parallelism");
+  auto *ep = static_cast<Target *>(target)->model->expertParallel();
+  SB_REQUIRE(tp || ep, "sb_target_tp_export: the target was created without tensor or expert parallelism");
+  if (ep) return guarded([&] { return ep->exportHandle(handle_out), int(SB_OK); });
   return guarded([&] { return tp->exportHandle(handle_out), int(SB_OK); });
 }
 
@@ -235,7 +237,9 @@ int sb_target_tp_connect(void *target, const void *handles) {
   SB_NEED_DEVICE();
   SB_REQUIRE(target && handles, "sb_target_tp_connect: null pointer");
   auto *tp = static_cast<Target *>(target)->model->tensorParallel();
-  SB_REQUIRE(tp, "sb_target_tp_connect: the target was created without tensor parallelism");
+  auto *ep = static_cast<Target *>(target)->model->expertParallel();
+  SB_REQUIRE(tp || ep, "sb_target_tp_connect: the target was created without tensor or expert parallelism");
+  if (ep) return guarded([&] { return ep->connect(handles), int(SB_OK); });
   return guarded([&] { return tp->connect(handles), int(SB_OK); });
 }
 
@@ -320,7 +324,7 @@ int sb_target_randomize(void *target, uint64_t seed, uint32_t committed) {
       SB_TRY(fill_rows(w.inProj, next()));
       SB_TRY(fill_rows(w.outProj, next()));
       if (c.moe_experts) {
-        const uint32_t total = c.moe_experts + 1;
+        const uint32_t total = m.expertParallel() ? m.expertParallel()->local().expertsTotal() : c.moe_experts + 1;  // (a rank's experts)
         splash::b200::ops::QuantizedSegment e;
         e.format = c.fmt_proj;
         e.rows = w.moe.gate, e.outputSize = total * c.moe_intermediate, e.inputSize = c.hidden;

@@ -16,7 +16,8 @@ class SbTargetConfig(ctypes.Structure):
                 ("page_tokens", _U), ("kv_scale_f16", _U), ("max_context", _U),
                 ("fmt_proj", _U), ("fmt_down", _U), ("fmt_head", _U), ("fmt_embed", _U),
                 ("gated_attention", _U), ("tiled_heads", _U), ("tp_world", _U), ("tp_rank", _U),
-                ("moe_experts", _U), ("moe_top_k", _U), ("moe_intermediate", _U), ("lanes", _U)]
+                ("moe_experts", _U), ("moe_top_k", _U), ("moe_intermediate", _U), ("lanes", _U),
+                ("ep_world", _U), ("ep_rank", _U)]
 
 
 # The benchmark configurations' shapes (weights are synthetic; see quant fixtures and sb_target_randomize).
