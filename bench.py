@@ -198,7 +198,7 @@ def main():
     ap.add_argument("--tiny", action="store_true", help="the 4-layer configuration (a smoke run, not the benchmark)")
     ap.add_argument("--moe", action="store_true", help="the 35B-A3B-shaped MoE model, one lane of 16 rows at an 8K context (an extra measurement, not the benchmark)")
     ap.add_argument("--tp-shots", type=int, default=0, choices=(0, 1, 2), help="how tensor-parallel shares travel (sb_tp_set_exchange); 0: by the number of ranks")
-    ap.add_argument("--parallel", default="tp", choices=("tp", "replicas"), help="what N > 1 GPUs do: one lane tensor-parallel, or N lanes")
+    ap.add_argument("--parallel", default="tp", choices=("tp", "replicas", "ep"), help="what N > 1 GPUs do: one lane tensor-parallel, N independent lanes, or (--moe --lanes L) the L lanes dealt to the ranks with the experts divided among them")
     ap.add_argument("--lanes", type=int, default=1, help="concurrent requests stepped together on each GPU, 16 rows each (an extra measurement, not the benchmark)")
     ap.add_argument("--nvfp4", action="store_true", help="NVFP4 projections (e2m1 codes, e4m3 scale per 16, fp32 scale) instead of the Q4_K_M mix (an extra measurement)")
     ap.add_argument("--context", type=int, default=0, help="tokens of context each lane holds (default: the workload's)")
@@ -206,18 +206,27 @@ def main():
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     workload = "tiny hybrid verify" if args.tiny else "Qwen3.x-27B-shaped hybrid verify, Q4_K_M mix, batch 1, block 16, 32K INT8 paged KV, greedy"
+    expert_parallel = args.parallel == "ep" and world > 1
+    if expert_parallel and not (args.moe and args.lanes % world == 0 and args.lanes // world >= 2):
+        raise SystemExit("--parallel ep needs --moe and --lanes a multiple of the ranks, two lanes a rank at least")
     if args.moe:
         workload = "35B-A3B-shaped MoE verify (256 experts + shared, top 8), Q4_K, batch 1, block 16, 8K INT8 paged KV, greedy"
-        args.tiny, args.parallel = True, "replicas"  # (the extra legs of the benchmark are for the 27B workload only)
+        args.tiny = True  # (the extra legs of the benchmark are for the 27B workload only)
+        if not expert_parallel:
+            args.parallel = "replicas"
     L = max(1, args.lanes)
+    total_lanes = L
+    if expert_parallel:
+        L //= world  # a rank's lanes
     if args.nvfp4:
         workload = workload.replace("Q4_K_M mix", "NVFP4 projections")
         args.parallel = "replicas"
     if args.context:
         workload = workload.replace("32K", f"{args.context // 1024}K")
-    if L > 1:
-        workload = f"{L} lanes stepped together: " + workload.replace("batch 1", f"batch {L}")
-        args.parallel = "replicas"
+    if total_lanes > 1:
+        workload = f"{total_lanes} lanes stepped together: " + workload.replace("batch 1", f"batch {total_lanes}")
+        if not expert_parallel:
+            args.parallel = "replicas"
 
     if args.impl == "reference":
         if rank != 0:
@@ -274,8 +283,14 @@ def main():
     if not tensor_parallel:
         if L > 1:
             cfg.update(lanes=L)
+        if expert_parallel:
+            from splash_b200 import tp
+            cfg.update(ep_world=world, ep_rank=rank)
         t = target.Target(**cfg)
         t.randomize(1234 + rank, context)
+        if expert_parallel:
+            tp.connect(t, group.all_gather_bytes)
+            group.barrier()
     lanes = 1 if tensor_parallel else world * L
     warm = max(args.warmup, 3)
     # The lane is held at its context length, so every step does the same work, and keeps FOLD_ROWS pending rows, so
@@ -311,6 +326,8 @@ def main():
     if tensor_parallel:  # the job's bytes are all ranks' shares; a failed exchange on any rank fails the run
         for key in ("weight_bytes", "kv_bytes", "state_bytes"):
             stats[key] = int(group.reduce_sum(stats[key]))
+        status = int(reduce_max(status))
+    if expert_parallel:
         status = int(reduce_max(status))
 
     # ---- end to end through the host-facing call, pinned host buffers ----
@@ -441,11 +458,11 @@ def main():
         cpu_tps, cores, sample = cpu_baseline(15.0)
     result = {
         "metric": "verify_tokens_per_s", "value": lanes * ROWS / (ms / 1e3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if tensor_parallel else "weak", "vs_baseline": None,
+        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong" if tensor_parallel or expert_parallel else "weak", "vs_baseline": None,
         "dtype": "f16 operands (exact integer codes), f32 accumulate, bf16 activations", "data": "synthetic",
         "config": {"workload": workload, "context_tokens": context, "block": ROWS,
                    "fold": f"held lane that keeps {FOLD_ROWS} pending rows: every timed step folds {FOLD_ROWS} tape rows into the GDN state",
-                   "parallelism": "tp1" if world == 1 else (f"tp{world}: one lane, shares exchanged through peer memory over NVLink in the input conversions" if tensor_parallel else f"{world} independent replicas (lanes)" + (f"; {fell_back}" if fell_back else "")),
+                   "parallelism": "tp1" if world == 1 else (f"tp{world}: one lane, shares exchanged through peer memory over NVLink in the input conversions" if tensor_parallel else f"ep{world}: {L} lanes and {cfg.get('moe_experts', 0) // world} of the routed experts a rank, rows dispatched and sums combined through peer memory over NVLink" if expert_parallel else f"{world} independent replicas (lanes)" + (f"; {fell_back}" if fell_back else "")),
                    "l2": "inputs exceed L2: one step streams %.1f GB of weights" % (stats["weight_bytes"] / 1e9), "cuda_graph": True, "pdl": True},
         "e2e": {"value": lanes * ROWS / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": ROWS * 4 * L, "d2h_bytes_per_step": (16 + ROWS * 4) * L},
         "gpu_launches": stats["launches"] * args.steps,
