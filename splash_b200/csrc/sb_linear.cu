@@ -1140,7 +1140,10 @@ __global__ void __launch_bounds__(32 * (kRG * WFmt<FMT>::kKG + 1 + kEpiWarps), 1
 static uint32_t pick_slices(uint32_t nsb, uint32_t sb_bytes) {
   // Activations of a slice stay resident: at most kMaxSliceSb super-blocks, fewer where a format's
   // wider stages need the room.
-  const uint32_t cap = sb_bytes > 250 ? 6 : sb_bytes > 160 ? 8 : kMaxSliceSb;
+  uint32_t cap = sb_bytes > 250 ? 6 : sb_bytes > 160 ? 8 : kMaxSliceSb;
+#ifdef SB_DIAG
+  if (const char *e = getenv("SB_SLICE_CAP")) cap = std::min<uint32_t>(cap, std::max(1, atoi(e)));  // (diagnostic builds: shorter slices, more items)
+#endif
   const uint32_t s = (nsb + cap - 1) / cap;
   return s < 1 ? 1 : s;
 }

@@ -63,7 +63,7 @@ __global__ void __launch_bounds__(256) embed_kernel(uint32_t format, const uint8
 
 // ---- the same projection for many rows (the rows of several lanes): warp-level MMA with the fp32 weights split into three
 // bf16 terms (hi + mid + lo carry the 24 bits of an fp32 significand), so every product with a bf16 input is exact and the
-// sums run in fp32. grid (n / 16, rows / 128); a warp takes 16 rows x 16 columns over all of k. ----
+// sums run in fp32. ----
 __device__ __forceinline__ void split3_bf16(float a, float b, uint32_t &hi, uint32_t &mid, uint32_t &lo) {
   const uint32_t ah = float_to_bf16_bits(a), bh = float_to_bf16_bits(b);
   const float ar = a - bf16_bits_to_float(ah), br = b - bf16_bits_to_float(bh);
@@ -71,19 +71,22 @@ __device__ __forceinline__ void split3_bf16(float a, float b, uint32_t &hi, uint
   const uint32_t al = float_to_bf16_bits(ar - bf16_bits_to_float(am)), bl = float_to_bf16_bits(br - bf16_bits_to_float(bm));
   hi = ah | (bh << 16), mid = am | (bm << 16), lo = al | (bl << 16);
 }
+// grid (n / 16, rows / 16): a CTA takes 16 rows x 16 columns; its 8 warps divide k (every warp's loads are in flight at once)
+// and their sums are added in warp order.
 __global__ void __launch_bounds__(256) linear_f32_rows_kernel(const float *w, const uint16_t *x, uint32_t rows, uint32_t n, uint32_t k,
                                                               uint32_t x_stride, void *out, uint32_t out_stride, uint32_t out_f32) {
+  __shared__ float part_s[8][16][17];
   pdl_launch_dependents();
   pdl_wait();
   const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-  const uint32_t r0 = blockIdx.y * 128 + 16 * warp, c0 = blockIdx.x * 16;
-  if (r0 >= rows) return;
-  const uint16_t *xa = x + size_t(min(r0 + g, rows - 1)) * x_stride + 2 * t, *xb = x + size_t(min(r0 + g + 8, rows - 1)) * x_stride + 2 * t;
-  const float *w0 = w + size_t(c0 + g) * k + 2 * t, *w1 = w + size_t(c0 + 8 + g) * k + 2 * t;
+  const uint32_t r0 = blockIdx.y * 16, c0 = blockIdx.x * 16;
+  const uint32_t kw = k / 8, kb = warp * kw;  // this warp's inputs
+  const uint16_t *xa = x + size_t(min(r0 + g, rows - 1)) * x_stride + kb + 2 * t, *xb = x + size_t(min(r0 + g + 8, rows - 1)) * x_stride + kb + 2 * t;
+  const float *w0 = w + size_t(c0 + g) * k + kb + 2 * t, *w1 = w + size_t(c0 + 8 + g) * k + kb + 2 * t;
   // The tensor cores' fp32 additions truncate; sums of 64 inputs are kept short and added up with rounded additions.
   float acc[2][4] = {}, total[2][4] = {};
 #pragma unroll 4
-  for (uint32_t k0 = 0; k0 < k; k0 += 16) {
+  for (uint32_t k0 = 0; k0 < kw; k0 += 16) {
     if (k0 && k0 % 64 == 0) {
 #pragma unroll
       for (int j = 0; j < 2; ++j)
@@ -107,13 +110,15 @@ __global__ void __launch_bounds__(256) linear_f32_rows_kernel(const float *w, co
 #pragma unroll
   for (int j = 0; j < 2; ++j)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t r = r0 + g + (i >> 1) * 8, c = c0 + 8 * j + 2 * t + (i & 1);
-      if (r >= rows) continue;
-      const float v = total[j][i] + acc[j][i];
-      if (out_f32) static_cast<float *>(out)[size_t(r) * out_stride + c] = v;
-      else static_cast<uint16_t *>(out)[size_t(r) * out_stride + c] = float_to_bf16_bits(v);
-    }
+    for (int i = 0; i < 4; ++i) part_s[warp][g + (i >> 1) * 8][8 * j + 2 * t + (i & 1)] = total[j][i] + acc[j][i];
+  __syncthreads();
+  const uint32_t r = threadIdx.x >> 4, c = threadIdx.x & 15;
+  float v = 0.0f;
+#pragma unroll
+  for (int wv = 0; wv < 8; ++wv) v += part_s[wv][r][c];
+  if (r0 + r >= rows) return;
+  if (out_f32) static_cast<float *>(out)[size_t(r0 + r) * out_stride + c0 + c] = v;
+  else static_cast<uint16_t *>(out)[size_t(r0 + r) * out_stride + c0 + c] = float_to_bf16_bits(v);
 }
 
 // ---- RoPE tables ----
@@ -851,8 +856,8 @@ int sb_linear_f32(void *stream, const float *w_dev, const void *x, uint32_t rows
   SB_REQUIRE(w_dev && x && out, "sb_linear_f32: null pointer");
   SB_REQUIRE(rows >= 1 && rows <= kF32Rows && n && k, "sb_linear_f32: rows = %u outside 1..%d, or empty shape", rows, kF32Rows);
   SB_REQUIRE(x_stride >= k && out_stride >= n && k % 8 == 0 && x_stride % 8 == 0, "sb_linear_f32: stride below extent, or k not a multiple of 8");
-  if (rows > 16 && !norm_weight && n % 16 == 0 && k % 16 == 0)  // many rows: on the tensor cores
-    return launch(linear_f32_rows_kernel, dim3(n / 16, (rows + 127) / 128), dim3(256), as_stream(stream), w_dev, static_cast<const uint16_t *>(x), rows, n, k,
+  if (rows > 16 && !norm_weight && n % 16 == 0 && k % 128 == 0)  // many rows: on the tensor cores
+    return launch(linear_f32_rows_kernel, dim3(n / 16, (rows + 15) / 16), dim3(256), as_stream(stream), w_dev, static_cast<const uint16_t *>(x), rows, n, k,
                   x_stride, out, out_stride, out_f32);
   return launch(linear_f32_kernel, dim3(n, (rows + 7) / 8), dim3(256), as_stream(stream), w_dev, static_cast<const uint16_t *>(x), rows, n, k,
                 x_stride, out, out_stride, out_f32, static_cast<const float *>(norm_weight));

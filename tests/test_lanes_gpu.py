@@ -189,7 +189,7 @@ def test_selection_penalties_and_acceptance_of_lanes_equal_the_lanes_one_at_a_ti
     assert len(set(greedy[:, 0].tolist())) >= 3          # the lanes did accept different lengths
 
 
-@pytest.mark.parametrize("rows,n,k", [(200, 256, 2048), (512, 64, 1024), (17, 48, 512)])
+@pytest.mark.parametrize("rows,n,k", [(200, 256, 2048), (512, 64, 1024), (17, 48, 512), (40, 32, 384)])
 def test_float_projection_of_many_rows_keeps_fp32_accuracy(rows, n, k):
     """sb_linear_f32 over more than 16 rows runs on the tensor cores with the fp32 weights split into three bf16 terms:
     against fp64 it stays at fp32 accuracy (the router's scores decide routes)."""
