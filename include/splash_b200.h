@@ -122,6 +122,10 @@ SB_API int sb_graph_destroy(void *graph);
 SB_API int sb_submit(void *graph, void *stream, uint64_t *out_ticket);
 SB_API int sb_ticket_wait(uint64_t ticket, uint32_t timeout_ms);
 
+/* Bytes of an argument structure of this header by its name ("SbLinearArgs", "SbGdnArgs", ...), 0 for an unknown name: lets a
+ * binding in another language check its mirror of the structure against the library it loaded. */
+SB_API uint64_t sb_struct_bytes(const char *name);
+
 /* ---- weights ---- */
 
 /* Bytes of one row of `k` weights in `format` as a GGUF stores it; 0 if k is not whole blocks. */

@@ -114,6 +114,27 @@ int sb_init(int device) {
   return SB_OK;
 }
 
+uint64_t sb_struct_bytes(const char *name) {
+  if (!name) return 0;
+#define SB_SIZE_OF(T) if (!strcmp(name, #T)) return sizeof(T)
+  SB_SIZE_OF(SbLinearArgs);
+  SB_SIZE_OF(SbLinearPlan);
+  SB_SIZE_OF(SbKvLayer);
+  SB_SIZE_OF(SbAttnStoreArgs);
+  SB_SIZE_OF(SbAttnArgs);
+  SB_SIZE_OF(SbGdnTape);
+  SB_SIZE_OF(SbGdnArgs);
+  SB_SIZE_OF(SbSampleArgs);
+  SB_SIZE_OF(SbPenaltyArgs);
+  SB_SIZE_OF(SbAcceptArgs);
+  SB_SIZE_OF(SbMoeRouteArgs);
+  SB_SIZE_OF(SbMoeExpertArgs);
+  SB_SIZE_OF(SbTargetConfig);
+  SB_SIZE_OF(SbTargetShare);
+#undef SB_SIZE_OF
+  return 0;
+}
+
 int sb_sm_count(void) { return ctx().ready ? ctx().sm_count : 0; }
 
 int sb_device_status(uint32_t *status) {

@@ -12,23 +12,23 @@
 // Layout of one launch
 //   prepare   a small kernel converts the 16 x K activations once (optionally through a fused
 //             RMSNorm) to fp16 with a per-row power-of-two scale, in MMA fragment order
-//   grid      one persistent CTA per SM (a multiple of the k-slice count), 320 threads:
-//             warps 0..7 consume, warp 8 produces, warp 9 finishes tiles
+//   grid      one persistent CTA per SM (a multiple of the k-slice count): 12 (Q4_K) or 8 (Q6_K, Q8_0) consumer
+//             warps (2 row groups x 6 or 4 k-groups), 1 producer warp, 3 epilogue warps that take tiles in turn
 //   k-slices  K's super-blocks are cut into S contiguous slices; a CTA owns one slice for the whole
 //             launch and keeps its slice of the prepared activations resident in shared memory
 //             (one bulk copy)
 //   tiles     64 weight rows x slice; the producer warp streams each tile's rows into a ring of
-//             stages (64 rows x 4 super-blocks) with 1-D bulk async copies completing on
-//             mbarriers; consumer warp (rg, kg) multiplies rows 32 rg..32 rg+31 of super-block kg
-//             of each stage: mma.sync m16n8k16 (A = 16 weight rows, B = 8 tokens) into fp32
+//             stages (64 rows x 4 super-blocks) with tiled 2-D TMA copies (cp.async.bulk.tensor, no multicast)
+//             completing on mbarriers; consumer warp (rg, kg) multiplies rows 32 rg..32 rg+31 of the stage's
+//             super-blocks dealt to k-group kg: mma.sync m16n8k16 (A = 16 weight rows, B = 8 tokens) into fp32
 //   Q4_K      operand = sc*q (exact integer <= 945 in fp16, built as (1024+q)*sc - 1024*sc with one
 //             LOP3 and one HFMA2 per two weights); per super-block y += d*Aq - dmin*Am, where Am is
 //             one more MMA of the 6-bit mins against the sub-block sums of x (split hi + lo fp16)
 //   Q6_K      operand = fp16(sc*(q-32)) (one rounding when |.| > 2048); y += d*Aq per super-block
 //   Q8_0      operand = fp16(d*q), the value the reference's staged tile rounds to
-//   reduce    the epilogue warp adds the 4 k-group warps' sums in order from shared memory while the
+//   reduce    an epilogue warp adds the k-group warps' sums in order from shared memory while the
 //             consumers start the next tile; with S > 1 the slices publish fp32 partials and the
-//             last arriver adds them in slice order
+//             last arriver adds them in slice order (or, SB_EPILOGUE_PARTIALS, leaves them to the next input conversion)
 //             (runtime/metal/kernels/common/split_reduce.h:24-55), then applies the epilogue
 //             (runtime/metal/kernels/common/gguf_tile.h:8-14, gguf_linear.metal:38)
 #include <algorithm>

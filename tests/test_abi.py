@@ -71,3 +71,19 @@ def test_row_bytes():
     assert l.sb_row_bytes(lib.FMT_Q6K, 17408) == 68 * 210
     assert l.sb_row_bytes(lib.FMT_Q80, 5120) == 160 * 34
     assert l.sb_row_bytes(lib.FMT_Q4K, 100) == 0
+
+
+def test_ctypes_mirrors_have_the_headers_structure_sizes():
+    """Every argument structure the harness mirrors in ctypes has the size the library was compiled with."""
+    import ctypes
+    from splash_b200 import lib, target, tp
+    l = lib.load()
+    l.sb_struct_bytes.restype = ctypes.c_uint64
+    l.sb_struct_bytes.argtypes = [ctypes.c_char_p]
+    mirrors = dict(SbLinearArgs=lib.SbLinearArgs, SbLinearPlan=lib.SbLinearPlan, SbKvLayer=lib.SbKvLayer, SbAttnStoreArgs=lib.SbAttnStoreArgs,
+                   SbAttnArgs=lib.SbAttnArgs, SbGdnTape=lib.SbGdnTape, SbGdnArgs=lib.SbGdnArgs, SbSampleArgs=lib.SbSampleArgs,
+                   SbPenaltyArgs=lib.SbPenaltyArgs, SbAcceptArgs=lib.SbAcceptArgs, SbMoeRouteArgs=lib.SbMoeRouteArgs,
+                   SbMoeExpertArgs=lib.SbMoeExpertArgs, SbTargetConfig=target.SbTargetConfig, SbTargetShare=tp.SbTargetShare)
+    for name, mirror in mirrors.items():
+        assert int(l.sb_struct_bytes(name.encode())) == ctypes.sizeof(mirror), name
+    assert int(l.sb_struct_bytes(b"NoSuchStruct")) == 0
