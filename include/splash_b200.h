@@ -625,6 +625,10 @@ SB_API int sb_tp_all_gather(void *stream, void *group, uint32_t index, uint32_t 
  * owner, which adds them and sends the finished bf16 values to every rank (two trips, 1 / W of the bytes); 0 (default):
  * one shot with two ranks, two shots with more. Either way every rank ends with the same bits. */
 SB_API int sb_tp_set_exchange(int shots);
+/* How long a kernel waits for another GPU's data (the tensor- and expert-parallel exchanges) before it records
+ * SB_DEV_WAIT_EXPIRED in the device status word and carries on; 0 restores the default of 2 s. Kernels that find the status
+ * word set do not wait at all, so a lost peer costs one limit, not one per exchange. */
+SB_API int sb_set_wait_limit_ns(uint64_t ns);
 /* Ends a step of `exchanges` exchanges: the next step's indices start over. (sb_target_* steps do this themselves.) */
 SB_API int sb_tp_advance(void *stream, void *group, uint32_t exchanges);
 

@@ -40,6 +40,7 @@ struct EpGroup {
 struct EpParams {
   uint32_t world, rank, rows, hidden, routes;
   uint32_t *words, *status;
+  uint64_t wait_ns;
   uint8_t *peer[kTpMaxWorld];
   size_t rows_off, selected_off, weights_off, inbox_off, flags_off;
 };
@@ -50,7 +51,7 @@ __device__ __forceinline__ void ep_signal_and_wait(const EpParams &p, uint32_t e
   if (t < p.world && t != p.rank) {
     __threadfence_system();
     st_release_sys(reinterpret_cast<uint32_t *>(p.peer[t] + p.flags_off) + p.rank * kEpCtas + blockIdx.x, epoch);
-    if (healthy) tp_wait_flag(reinterpret_cast<const uint32_t *>(p.peer[p.rank] + p.flags_off) + t * kEpCtas + blockIdx.x, epoch, p.status);
+    if (healthy) tp_wait_flag(reinterpret_cast<const uint32_t *>(p.peer[p.rank] + p.flags_off) + t * kEpCtas + blockIdx.x, epoch, p.status, p.wait_ns);
   }
   __syncthreads();
 }
@@ -126,7 +127,7 @@ static int ep_params(void *group, EpParams &p) {
   if (!g || !g->connected) return fail(SB_ERR_INVALID, "expert-parallel group is not connected (sb_ep_connect)");
   p = EpParams{};
   p.world = g->world, p.rank = g->rank, p.rows = g->rows, p.hidden = g->hidden, p.routes = g->routes;
-  p.words = g->words, p.status = ctx().status_dev;
+  p.words = g->words, p.status = ctx().status_dev, p.wait_ns = ctx().wait_ns;
   for (uint32_t r = 0; r < g->world; ++r) p.peer[r] = g->peer[r];
   p.rows_off = g->rows_off, p.selected_off = g->selected_off, p.weights_off = g->weights_off, p.inbox_off = g->inbox_off, p.flags_off = g->flags_off;
   return SB_OK;

@@ -28,6 +28,7 @@ struct Context {
   uint32_t *gdn_counters = nullptr;      // one arrival counter per value head
   bool pdl = true;                       // launch glue kernels with programmatic stream serialization
   int tp_exchange_shots = 0;             // 0: by the number of ranks, 1: one shot, 2: two shots (sb_tp_set_exchange)
+  uint64_t wait_ns = 2000000000ull;      // how long a kernel waits for a peer GPU before it gives up (sb_set_wait_limit_ns)
   int attention_kernel = 0;              // 0: tcgen05 kernel, 1: warp-level MMA kernel (sb_set_attention_kernel)
 };
 Context &ctx();

@@ -177,7 +177,7 @@ __device__ __forceinline__ uint32_t tp_owner(uint32_t sb, uint32_t nsb, uint32_t
 
 // Polls `count` units 32 apart until all show `epoch`; gives up after the bounded wait (expired stays set).
 template <int N>
-__device__ __forceinline__ void tp_poll_units(const uint4 *from, uint4 (&got)[N], uint32_t epoch, uint64_t t0, bool &expired, uint32_t *status) {
+__device__ __forceinline__ void tp_poll_units(const uint4 *from, uint4 (&got)[N], uint32_t epoch, uint64_t t0, bool &expired, uint32_t *status, uint64_t wait_ns) {
   for (uint32_t polls = 1;; ++polls) {
     bool all = true;
 #pragma unroll
@@ -186,7 +186,7 @@ __device__ __forceinline__ void tp_poll_units(const uint4 *from, uint4 (&got)[N]
       all = all && got[u].y == epoch && got[u].w == epoch;
     }
     if (all || expired) return;
-    if ((polls & 63u) == 0 && (global_timer_ns() - t0 > kTpWaitNs || polls >= (1u << 30))) {
+    if ((polls & 63u) == 0 && (global_timer_ns() - t0 > wait_ns || polls >= (1u << 30))) {
       atomicCAS(status, uint32_t(SB_DEV_OK), uint32_t(SB_DEV_WAIT_EXPIRED));
       expired = true;
     }
@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(kPrepThreads) tp_push_kernel(const PreparePara
         continue;
       }
       uint4 got[4];
-      tp_poll_units<4>(reinterpret_cast<const uint4 *>(x.data[x.rank]) + tp_unit(slot + src, tok, x.width, c, lane), got, epoch, t0, expired, x.status);
+      tp_poll_units<4>(reinterpret_cast<const uint4 *>(x.data[x.rank]) + tp_unit(slot + src, tok, x.width, c, lane), got, epoch, t0, expired, x.status, x.wait_ns);
 #pragma unroll
       for (int u = 0; u < 4; ++u) total[2 * u] += __uint_as_float(got[u].x), total[2 * u + 1] += __uint_as_float(got[u].z);
     }
@@ -382,7 +382,7 @@ template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kerne
       const uint32_t c = c0 + tid + kPrepThreads * i;
       if (c >= chunks) continue;
       uint4 got[2];
-      tp_poll_units<2>(x.sums[x.rank] + tp_sum_unit(epoch & 1u, tok, x.width, c, lane), got, epoch, t0, expired, x.status);
+      tp_poll_units<2>(x.sums[x.rank] + tp_sum_unit(epoch & 1u, tok, x.width, c, lane), got, epoch, t0, expired, x.status, x.wait_ns);
       const uint32_t u[4] = {got[0].x, got[0].z, got[1].x, got[1].z};
 #pragma unroll
       for (int j = 0; j < 4; ++j) acc[i][2 * j] = bf16_bits_to_float(u[j] & 0xffffu), acc[i][2 * j + 1] = bf16_bits_to_float(u[j] >> 16);
@@ -406,7 +406,7 @@ template <bool TP> __global__ void __launch_bounds__(kPrepThreads) prepare_kerne
           continue;
         }
         uint4 got[4];
-        tp_poll_units<4>(reinterpret_cast<const uint4 *>(x.data[x.rank]) + tp_unit(slot + src, tok, x.width, c, lane), got, epoch, t0, expired, x.status);
+        tp_poll_units<4>(reinterpret_cast<const uint4 *>(x.data[x.rank]) + tp_unit(slot + src, tok, x.width, c, lane), got, epoch, t0, expired, x.status, x.wait_ns);
 #pragma unroll
         for (int u = 0; u < 4; ++u) total[2 * u] += __uint_as_float(got[u].x), total[2 * u + 1] += __uint_as_float(got[u].z);
       }

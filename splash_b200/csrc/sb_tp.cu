@@ -29,6 +29,7 @@ int tp_exchange(void *group, uint32_t index, bool gather, TpExchange &out) {
   out.world = g->world, out.rank = g->rank, out.index = index, out.width = gather ? g->gather_width : g->width;
   out.epoch_base = g->epoch, out.ready = g->epoch + 1, out.status = ctx().status_dev;
   out.two_shot = ctx().tp_exchange_shots ? ctx().tp_exchange_shots == 2 : g->world > 2;
+  out.wait_ns = ctx().wait_ns;
   for (uint32_t p = 0; p < g->world; ++p) {
     out.sums[p] = reinterpret_cast<uint4 *>(g->peer[p] + g->sums_off);
     out.data[p] = reinterpret_cast<float *>(g->peer[p] + (gather ? g->gather_off : g->inbox_off));
@@ -169,6 +170,11 @@ int sb_tp_all_gather(void *stream, void *group, uint32_t index, uint32_t rows, u
 int sb_tp_set_exchange(int shots) {
   SB_REQUIRE(shots >= 0 && shots <= 2, "sb_tp_set_exchange: %d shots (0: by the number of ranks, 1 or 2)", shots);
   ctx().tp_exchange_shots = shots;
+  return SB_OK;
+}
+
+int sb_set_wait_limit_ns(uint64_t ns) {
+  ctx().wait_ns = ns ? ns : kTpWaitNs;
   return SB_OK;
 }
 

@@ -46,7 +46,7 @@ namespace sb {
 
 constexpr int kTpMaxWorld = 8;
 constexpr int kTpGatherCtas = 64;
-constexpr uint64_t kTpWaitNs = 2000000000ull;  // 2 s
+constexpr uint64_t kTpWaitNs = 2000000000ull;  // 2 s: the default of the context's limit (sb_set_wait_limit_ns)
 
 // By value in kernel parameters; world == 0: no exchange.
 struct TpExchange {
@@ -55,6 +55,7 @@ struct TpExchange {
   uint32_t *status;
   uint32_t *ready;               // this rank's word: the number of the last exchange whose slices' sums are complete
   uint32_t two_shot;             // shares go to the columns' owner only, which adds them and sends the sum to everybody
+  uint64_t wait_ns;              // how long a wait for a peer may last
   uint4 *sums[kTpMaxWorld];      // rank p's inbox of finished sums (two_shot), as mapped here
   float *data[kTpMaxWorld];      // rank p's inbox (or gather matrix) as mapped here; data[rank] is this rank's own
   uint32_t *flags[kTpMaxWorld];  // rank p's flag words (the gather kernel's)
@@ -109,7 +110,7 @@ __device__ __forceinline__ bool tp_healthy(const TpExchange &x) { return *reinte
 
 // Waits until the flag has reached `epoch`. Gives up after kTpWaitNs (or 2^30 polls, should the clock stand
 // still), records the failure and returns false.
-__device__ __forceinline__ bool tp_wait_flag(const uint32_t *flag, uint32_t epoch, uint32_t *status) {
+__device__ __forceinline__ bool tp_wait_flag(const uint32_t *flag, uint32_t epoch, uint32_t *status, uint64_t wait_ns) {
   const uint64_t t0 = global_timer_ns();
   for (uint32_t polls = 1;; ++polls) {
     if (int32_t(ld_relaxed_sys(flag) - epoch) >= 0) {
@@ -117,7 +118,7 @@ __device__ __forceinline__ bool tp_wait_flag(const uint32_t *flag, uint32_t epoc
       return true;
     }
     if ((polls & 63u) == 0) {
-      if (global_timer_ns() - t0 > kTpWaitNs || polls >= (1u << 30)) {
+      if (global_timer_ns() - t0 > wait_ns || polls >= (1u << 30)) {
         atomicCAS(status, uint32_t(SB_DEV_OK), uint32_t(SB_DEV_WAIT_EXPIRED));
         return false;
       }
@@ -131,7 +132,7 @@ __device__ __forceinline__ bool tp_wait_ready(const TpExchange &x, uint32_t epoc
   const uint64_t t0 = global_timer_ns();
   for (uint32_t polls = 1;; ++polls) {
     if (int32_t(ld_acquire_gpu(x.ready) - epoch) >= 0) return true;
-    if ((polls & 63u) == 0 && (global_timer_ns() - t0 > kTpWaitNs || polls >= (1u << 30))) {
+    if ((polls & 63u) == 0 && (global_timer_ns() - t0 > x.wait_ns || polls >= (1u << 30))) {
       atomicCAS(x.status, uint32_t(SB_DEV_OK), uint32_t(SB_DEV_WAIT_EXPIRED));
       return false;
     }
@@ -146,7 +147,7 @@ __device__ __forceinline__ void tp_signal_and_wait(const TpExchange &x, uint32_t
   if (t < x.world && t != x.rank) {
     __threadfence_system();
     st_release_sys(x.flags[t] + x.rank * ctas + cta, epoch);
-    if (healthy) tp_wait_flag(x.flags[x.rank] + t * ctas + cta, epoch, x.status);
+    if (healthy) tp_wait_flag(x.flags[x.rank] + t * ctas + cta, epoch, x.status, x.wait_ns);
   }
   __syncthreads();
 }

@@ -118,3 +118,88 @@ def test_two_ranks_of_two_lanes_match_four_oracle_lanes():
             else:
                 diverged.add(lane)   # the oracle's own choice was a near tie: the lane's later steps start elsewhere
     assert compared >= 4, compared
+
+
+def _expiry_worker(rank, barrier, handles, results):
+    try:
+        import time
+        from splash_b200 import lib, tp
+        lib.init(rank)
+        l = lib.load()
+        P, U = ctypes.c_void_p, ctypes.c_uint32
+        l.sb_ep_create.argtypes = [U, U, U, U, U, ctypes.POINTER(P)]
+        l.sb_ep_export.argtypes = [P, P]
+        l.sb_ep_connect.argtypes = [P, P]
+        l.sb_ep_destroy.argtypes = [P]
+        l.sb_ep_dispatch.argtypes = [P, P, P, P, P]
+        l.sb_set_wait_limit_ns.argtypes = [ctypes.c_uint64]
+        rows, hidden, routes = 16, 256, 3
+        g = P()
+        lib.check(l.sb_ep_create(WORLD, rank, rows, hidden, routes, ctypes.byref(g)))
+        mine = ctypes.create_string_buffer(tp.HANDLE_BYTES)
+        lib.check(l.sb_ep_export(g, mine))
+        ctypes.memmove(ctypes.addressof(handles) + rank * tp.HANDLE_BYTES, mine.raw, tp.HANDLE_BYTES)
+        barrier.wait(timeout=120)
+        lib.check(l.sb_ep_connect(g, bytes(handles[:WORLD * tp.HANDLE_BYTES])))
+        out = None
+        if rank == 0:   # the only rank that dispatches: its peer's flag never comes
+            lib.check(l.sb_set_wait_limit_ns(5_000_000))   # 5 ms
+            x = lib.DeviceBuffer(rows * hidden * 2)
+            sel, wts = lib.DeviceBuffer(rows * routes * 4), lib.DeviceBuffer(rows * routes * 4)
+            for b in (x, sel, wts):
+                b.fill(0)
+            t0 = time.time()
+            lib.check(l.sb_ep_dispatch(None, g, x.ptr, sel.ptr, wts.ptr))
+            lib.stream_sync()
+            first = time.time() - t0
+            status = lib.device_status()            # reads and clears the word
+            # a kernel that finds the status word set does not wait: leave it set by a second expiry, then time a third call
+            lib.check(l.sb_ep_dispatch(None, g, x.ptr, sel.ptr, wts.ptr))
+            lib.stream_sync()
+            again = lib.device_status()
+            # the context is usable: a local operator runs and the status word stays clear
+            y, w = lib.DeviceBuffer(rows * hidden * 2), lib.DeviceBuffer.from_numpy(np.ones(hidden, np.float32))
+            lib.check(lib.ops().sb_rmsnorm(None, x.ptr, rows, hidden, hidden, w.ptr, y.ptr, hidden))   # (lib.ops() declares the argument types)
+            lib.stream_sync()
+            out = (first, status, again, lib.device_status())
+            lib.check(l.sb_set_wait_limit_ns(0))
+        barrier.wait(timeout=120)   # rank 1 keeps its window mapped until rank 0 is done
+        results.put((rank, out, None))
+        barrier.wait(timeout=120)
+        l.sb_ep_destroy(g)
+    except Exception as e:
+        results.put((rank, None, repr(e)))
+        try:
+            barrier.abort()
+        except Exception:
+            pass
+
+
+def test_a_wait_for_a_rank_that_never_joins_runs_out_and_says_so():
+    """Failure made on the host: rank 1 connects its window and then never takes part. Rank 0's exchange waits for the flag
+    that nothing sets, gives up after the limit set with sb_set_wait_limit_ns, records SB_DEV_WAIT_EXPIRED and returns; the
+    context stays usable. No GPU faults or hangs: the wait is bounded by the clock."""
+    from splash_b200 import lib
+    if lib.device_count() < WORLD:
+        pytest.skip(f"needs {WORLD} GPUs")
+    ctx = mp.get_context("spawn")
+    barrier, results = ctx.Barrier(WORLD), ctx.Queue()
+    handles = ctx.RawArray(ctypes.c_ubyte, WORLD * 64)
+    procs = [ctx.Process(target=_expiry_worker, args=(r, barrier, handles, results)) for r in range(WORLD)]
+    for p in procs:
+        p.start()
+    got = {}
+    try:
+        for _ in range(WORLD):
+            rank, out, err = results.get(timeout=300)
+            assert err is None, f"rank {rank} failed: {err}"
+            got[rank] = out
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
+    first, status, again, after = got[0]
+    assert status == 1 and again == 1          # SB_DEV_WAIT_EXPIRED, both times
+    assert 0.004 < first < 2.0                 # it waited for the limit, not for the default 2 s
+    assert after == 0                          # and the context carried on
