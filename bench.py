@@ -210,7 +210,7 @@ def main():
     if expert_parallel and not (args.moe and args.lanes % world == 0 and args.lanes // world >= 2):
         raise SystemExit("--parallel ep needs --moe and --lanes a multiple of the ranks, two lanes a rank at least")
     if args.moe:
-        workload = "35B-A3B-shaped MoE verify (256 experts + shared, top 8), Q4_K, batch 1, block 16, 8K INT8 paged KV, greedy"
+        workload = "35B-A3B-shaped MoE verify (256 experts + shared, top 8, router logits ~ N(0,1) given), Q4_K, batch 1, block 16, 8K INT8 paged KV, greedy"
         args.tiny = True  # (the extra legs of the benchmark are for the 27B workload only)
         if not expert_parallel:
             args.parallel = "replicas"
@@ -291,6 +291,10 @@ def main():
         if expert_parallel:
             tp.connect(t, group.all_gather_bytes)
             group.barrier()
+    if args.moe:
+        # Router logits ~ N(0, 1), as the benchmark's configuration states them: random weights do not make a router whose
+        # routes spread over the experts as a trained one's do (its rows collapse onto a few experts, which flatters the step).
+        t.set_router_scores(np.random.default_rng(77 + rank).standard_normal((ROWS * L, cfg["moe_experts"])).astype(np.float32))
     lanes = 1 if tensor_parallel else world * L
     warm = max(args.warmup, 3)
     # The lane is held at its context length, so every step does the same work, and keeps FOLD_ROWS pending rows, so

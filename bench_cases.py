@@ -18,8 +18,8 @@ import numpy as np
 
 from splash_b200 import lib
 
-FMT = {"q4k": lib.FMT_Q4K, "q6k": lib.FMT_Q6K, "q80": lib.FMT_Q80}
-EPI = {"none": lib.EP_NONE, "residual": lib.EP_RESIDUAL, "gate_up": lib.EP_GATE_UP}
+FMT = {"q4k": lib.FMT_Q4K, "q6k": lib.FMT_Q6K, "q80": lib.FMT_Q80, "nvfp4": lib.FMT_NVFP4}
+EPI = {"none": lib.EP_NONE, "residual": lib.EP_RESIDUAL, "gate_up": lib.EP_GATE_UP, "partials": lib.EP_PARTIALS}
 
 
 def bf16_bits(x):
@@ -38,6 +38,11 @@ def native_rows(rng, fmt, n, k):
         nb, bb = k // 256, 210
         blk = rng.integers(0, 256, (n, nb, bb), dtype=np.uint8)
         blk[..., 208:210] = rng.uniform(2e-5, 1e-4, (n, nb)).astype(np.float16).view(np.uint8).reshape(n, nb, 2)
+    elif fmt == lib.FMT_NVFP4:
+        nb, bb = k // 256, 148
+        blk = rng.integers(0, 256, (n, nb, bb), dtype=np.uint8)
+        blk[..., 0:16] = (rng.integers(0, 2, (n, nb, 16)) << 7) | (rng.integers(6, 9, (n, nb, 16)) << 3) | rng.integers(0, 8, (n, nb, 16))
+        blk[..., 16:20] = np.full((n, nb), 1e-3, np.float32).view(np.uint8).reshape(n, nb, 4)
     else:
         nb, bb = k // 32, 34
         blk = rng.integers(0, 256, (n, nb, bb), dtype=np.uint8)
@@ -89,16 +94,30 @@ def case_linear(a):
     rows = np.tile(base, ((n + base.shape[0] - 1) // base.shape[0], 1))[:n]
     copies = max(2, int(a.resident_mb * 1e6 // (n * rb * tensors)) + 1)
     bufs = [lib.DeviceBuffer.from_numpy(rows) for _ in range(copies * tensors)]
+    wide = a.rows > 16 or fmt == lib.FMT_NVFP4   # the many-row kernel
+    image = wide and fmt in (lib.FMT_Q6K, lib.FMT_NVFP4)
+    if image:  # it reads Q6_K and NVFP4 rows as images made once
+        natives, bufs = bufs, []
+        for b in natives:
+            img = lib.DeviceBuffer(int(lib.load().sb_linear_wide_image_bytes(fmt, n, k)))
+            lib.check(lib.load().sb_linear_wide_image(None, fmt, b.ptr, n, k, img.ptr))
+            bufs.append(img)
+        lib.stream_sync()
+        rb = int(lib.load().sb_linear_wide_image_bytes(fmt, n, k)) // n
     slots = max(16, a.rows)
     x = lib.DeviceBuffer.from_numpy(bf16_bits(rng.standard_normal((slots, k))))
     l = lib.load()
-    if a.rows > 16:  # the many-row kernel (tensor memory): its own conversion, once
+    if wide:  # its own conversion, once
         prep = lib.DeviceBuffer(int(l.sb_linear_wide_prepared_bytes(a.rows, k)))
         lib.check(l.sb_linear_wide_prepare(None, x.ptr, a.rows, k, k, None, prep.ptr, 0))
     else:
         prep = lib.DeviceBuffer(int(l.sb_linear_prepared_bytes(k)))
         lib.check(l.sb_linear_prepare(None, x.ptr, a.rows, k, k, None, fmt, prep.ptr, None, (lib.LINEAR_TCGEN05 if a.tcgen05 else 0)))
-    out = lib.DeviceBuffer(slots * n * 4 + 512)
+    splits = 1
+    if ep == lib.EP_PARTIALS:
+        l.sb_linear_wide_splits.argtypes = [ctypes.c_uint32] * 2
+        splits = int(l.sb_linear_wide_splits(n, k)) if wide else 16
+    out = lib.DeviceBuffer(splits * slots * n * 4 + 512)
     aux = lib.DeviceBuffer.from_numpy(np.zeros((slots, n), np.uint16))
 
     def launch(i, stream=None):
@@ -110,7 +129,8 @@ def case_linear(a):
             w = bufs[i % len(bufs)].ptr
             if ep == lib.EP_RESIDUAL:
                 kw = dict(aux=aux.ptr)
-        lib.linear(w, None, out.ptr, fmt, n, k, a.rows, prepared=prep.ptr, epilogue=ep, flags=(lib.LINEAR_PDL if a.pdl else 0) | (lib.LINEAR_TCGEN05 if a.tcgen05 else 0), stream=stream, **kw)
+        flags = (lib.LINEAR_PDL if a.pdl else 0) | (lib.LINEAR_TCGEN05 if a.tcgen05 else 0) | (lib.LINEAR_WIDE_IMAGE if image else 0)
+        lib.linear(w, None, out.ptr, fmt, n, k, a.rows, prepared=prep.ptr, epilogue=ep, out_f32=ep == lib.EP_PARTIALS, flags=flags, stream=stream, **kw)
 
     us = timed(launch, a.iters, graph=a.graph)
     algo = n * rb * tensors + a.rows * k * 2 + a.rows * n * 2
@@ -200,6 +220,13 @@ def case_moe(a):
         lib.check(l.sb_moe_experts(stream, ctypes.byref(ea)))
 
     us = timed(launch, a.iters, graph=a.graph)
+    if rows > 16:  # grouped by expert: every expert that has a route streams once
+        hit = len(np.unique(sel.to_numpy(np.uint32, (rows, routes))))
+        algo = hit * 3 * I * (H // 256) * 144
+        print(f"moe rows={rows} experts={E}+1 top_k={K} hidden={H} intermediate={I}: {us:.1f} us per layer (routing, grouping, 2 conversions, 2 grouped "
+              f"expert launches, combine), {algo / us / 1e3:.0f} GB/s of {algo} bytes of the {hit} experts hit, "
+              f"{2.0 * rows * routes * 3 * I * H / us / 1e6:.1f} TFLOP/s, device status {lib.device_status()}")
+        return
     algo = rows * routes * 3 * I * (H // 256) * 144
     print(f"moe rows={rows} experts={E}+1 top_k={K} hidden={H} intermediate={I}: {us:.1f} us per layer (routing + 3 expert launches), "
           f"{algo / us / 1e3:.0f} GB/s of {algo} expert bytes (every route its own), device status {lib.device_status()}")

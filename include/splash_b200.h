@@ -675,6 +675,11 @@ SB_API int sb_target_tensor(void *target, int layer, const char *name, void **ou
 SB_API int sb_target_set_penalties(void *target, float repetition, float presence, float frequency);
 /* Seeded synthetic weights, a prefilled INT8 cache of `committed` tokens and random GDN state, written on the device. */
 SB_API int sb_target_randomize(void *target, uint64_t seed, uint32_t committed);
+/* Synthetic routing for measurements: with `given` != 0 every MoE block routes by the scores in the target's `moe_scores`
+ * tensor (fp32 [rows of all lanes][experts], filled by the host, e.g. N(0, 1) as the benchmark's configuration states its
+ * router logits) instead of its own router's; the router's projection still runs, into a buffer nothing reads. Random
+ * weights do not make a router whose routes spread over the experts as a trained one's do. */
+SB_API int sb_target_set_router_scores(void *target, int given);
 /* Sets the lane's position (every lane's, with several) and clears the pending GDN rows. */
 SB_API int sb_target_reset(void *target, uint32_t committed);
 /* The same with a position per lane: committed_host holds SbTargetConfig.lanes words. */

@@ -119,6 +119,8 @@ class QwenTarget {
   // The images of the Q6_K / NVFP4 projections are out of date: set when a weight tensor's address is handed out or the
   // weights are filled, cleared by buildImages, which the next step runs first.
   bool imagesStale = true;
+  // Measurements with synthetic routing: the blocks route by the host's `moe_scores` instead of their router's scores.
+  bool routerScoresGiven = false;
   void buildImages(void *stream) {
     if (wide_)
       for (LayerWeights &w : layers_)
@@ -134,7 +136,7 @@ class QwenTarget {
 
   ops::MoeShape moe_;
   std::unique_ptr<ops::ExpertParallel> ep_;
-  Buffer moeScores_, moeSelected_, moeWeights_, moeScratch_;
+  Buffer moeScores_, moeScoresGiven_, moeSelected_, moeWeights_, moeScratch_;
   SbTargetConfig cfg_, loc_;
   SbTargetShare share_{};
   std::unique_ptr<ops::TensorParallel> tp_;
@@ -292,7 +294,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   penaltyWords = Buffer::allocate(size_t(c.vocab) * 4 * L);
   candidates = Buffer::allocate(R * 16 * 4), candidateQ = Buffer::allocate(R * 16 * 4), draws = Buffer::allocate(R * 4);
   if (c.moe_experts) {
-    moeScores_ = Buffer::allocate(R * moe_.slots * 4);
+    moeScores_ = Buffer::allocate(R * moe_.slots * 4), moeScoresGiven_ = Buffer::allocate(R * moe_.slots * 4);
     moeSelected_ = Buffer::allocate(R * moe_.routes() * 4), moeWeights_ = Buffer::allocate(R * moe_.routes() * 4);
     moeScratch_ = Buffer::allocate(ops::MoE::scratchBytes(moe_, uint32_t(R)));
   }
@@ -314,7 +316,8 @@ inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) co
                                              {"hidden1", hidden[1]}, {"tokens", tokens}, {"uniforms", uniforms}, {"committed", committed},
                                              {"pending_rows", pendingRows}, {"tree", tree}, {"page_table", pageTable_}, {"inv_freq", invFreq},
                                              {"positions", positions}, {"packed", packed_}, {"mixed", mixed_}, {"act", act_}, {"penalty_words", penaltyWords},
-                                             {"candidates", candidates}, {"candidate_q", candidateQ}, {"draws", draws}, {"pending_path", pendingPath}};
+                                             {"candidates", candidates}, {"candidate_q", candidateQ}, {"draws", draws}, {"pending_path", pendingPath},
+                                             {"moe_scores", moeScoresGiven_}};
     auto it = g.find(name);
     if (it == g.end()) return false;
     out = it->second;
@@ -437,7 +440,7 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
       // conversion is run for its side products: the new hidden state and the normalised rows.
       convert(&w.ffnNorm.buffer, c.fmt_proj, prepared_[0], &normed_);
       MoeBuffers mb{normed_, hidden[cur], moeScores_, moeSelected_, moeWeights_, moeScratch_, hidden[cur ^ 1]};
-      MoE::addRouting(graph, moe_, w.moe, mb, rows);
+      MoE::addRouting(graph, moe_, w.moe, mb, rows, routerScoresGiven ? &moeScoresGiven_ : nullptr);
       MoE::addRouted(graph, moe_, w.moe, mb, rows);
       cur ^= 1;
       continue;
@@ -540,7 +543,7 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
       convert(nullptr);
       Normalization::addRms(graph, hidden[cur], w.ffnNorm, normed_, H, R, H, H);
       MoeBuffers mb{normed_, hidden[cur], moeScores_, moeSelected_, moeWeights_, moeScratch_, hidden[cur ^ 1]};
-      MoE::addRouting(graph, moe_, w.moe, mb, R);
+      MoE::addRouting(graph, moe_, w.moe, mb, R, routerScoresGiven ? &moeScoresGiven_ : nullptr);
       if (ep_) ep_->addRouted(graph, w.moe, mb);
       else MoE::addRouted(graph, moe_, w.moe, mb, R);
       cur ^= 1;

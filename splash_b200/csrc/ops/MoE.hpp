@@ -35,15 +35,17 @@ class MoE {
  public:
   static size_t scratchBytes(const MoeShape &s, uint32_t rows) { return sb_moe_scratch_bytes(rows, s.routes(), s.hidden, s.intermediate); }
 
-  // Router scores, then each row's routes and weights.
-  static void addRouting(CommandGraph &graph, const MoeShape &s, const MoeWeights &w, const MoeBuffers &b, uint32_t rows) {
+  // Router scores, then each row's routes and weights. `given` (measurements with synthetic routing): the routes come from
+  // these scores (fp32 [rows, slots]) instead; the router's projection still runs.
+  static void addRouting(CommandGraph &graph, const MoeShape &s, const MoeWeights &w, const MoeBuffers &b, uint32_t rows, const Buffer *given = nullptr) {
     if (s.sharedGate && !s.sharedExpert) throw std::invalid_argument("MoE::addRouting: a shared gate without a shared expert");
     if (s.sharedExpert && !s.sharedGate) throw std::invalid_argument("MoE::addRouting: an ungated shared expert is not offered (weight 1 routes)");
     Linear::addFloat(graph, w.router, b.input, s.hidden, rows, s.slots, s.hidden, b.scores, s.slots, Destination::Float32, nullptr);
     requireBytes(b.selected, size_t(rows) * s.routes() * 4, "MoE::addRouting selected");
     requireBytes(b.weights, size_t(rows) * s.routes() * 4, "MoE::addRouting weights");
     if (s.sharedGate) requireBytes(w.sharedGate, size_t(s.hidden) * 4, "MoE::addRouting shared gate");
-    SbMoeRouteArgs a{b.scores.as<float>(), b.input.as(), s.sharedGate ? w.sharedGate.as<float>() : nullptr, b.selected.as<uint32_t>(),
+    if (given) requireBytes(*given, size_t(rows) * s.slots * 4, "MoE::addRouting given scores");
+    SbMoeRouteArgs a{given ? given->as<float>() : b.scores.as<float>(), b.input.as(), s.sharedGate ? w.sharedGate.as<float>() : nullptr, b.selected.as<uint32_t>(),
                      b.weights.as<float>(), rows, s.experts, s.slots, s.topK, s.hidden, s.sigmoidNormalized ? 1u : 0u};
     check(sb_moe_route(graph.stream, &a));
     ++graph.launches;

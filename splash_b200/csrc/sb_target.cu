@@ -260,6 +260,18 @@ int sb_target_set_penalties(void *target, float repetition, float presence, floa
   return SB_OK;
 }
 
+int sb_target_set_router_scores(void *target, int given) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target, "sb_target_set_router_scores: null target");
+  Target *t = static_cast<Target *>(target);
+  SB_REQUIRE(t->model->config().moe_experts, "sb_target_set_router_scores: the model has no MoE blocks");
+  SB_CUDA(cudaDeviceSynchronize());
+  for (auto &g : t->graphs) cudaGraphExecDestroy(g.second);  // captured steps carry the old choice
+  t->graphs.clear();
+  t->model->routerScoresGiven = given != 0;
+  return SB_OK;
+}
+
 int sb_target_tensor(void *target, int layer, const char *name, void **out_dev, uint64_t *out_bytes) {
   SB_NEED_DEVICE();
   SB_REQUIRE(target && name && out_dev && out_bytes, "sb_target_tensor: null pointer");

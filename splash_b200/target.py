@@ -49,6 +49,7 @@ def _bind():
     l.sb_target_randomize.argtypes = [_P, ctypes.c_uint64, _U]
     l.sb_target_reset.argtypes = [_P, _U]
     l.sb_target_set_penalties.argtypes = [_P, _F, _F, _F]
+    l.sb_target_set_router_scores.argtypes = [_P, ctypes.c_int]
     l.sb_target_step.argtypes = [_P, _P, _U, _F, _U]
     l.sb_target_verify.argtypes = [_P, _P, _P, _P, _U, _F, _U, _P, _P]
     l.sb_target_verify_tree.argtypes = [_P, _P, _P, _P, _P, _U, _F, _U, _P, _P]
@@ -108,6 +109,14 @@ class Target:
 
     def set_penalties(self, repetition=1.0, presence=0.0, frequency=0.0):
         lib.check(self.l.sb_target_set_penalties(self.handle, repetition, presence, frequency))
+
+    def set_router_scores(self, scores):
+        """Synthetic routing for measurements: every MoE block routes by `scores` (fp32 [rows of all lanes, experts]); None: by its own router."""
+        if scores is None:
+            lib.check(self.l.sb_target_set_router_scores(self.handle, 0))
+            return
+        self.upload(-1, "moe_scores", np.ascontiguousarray(scores, np.float32))
+        lib.check(self.l.sb_target_set_router_scores(self.handle, 1))
 
     def reset(self, committed):
         lib.check(self.l.sb_target_reset(self.handle, committed))
