@@ -22,7 +22,7 @@ int tc_plan(uint32_t n, uint32_t k, uint32_t epilogue, SbLinearPlan &plan);
 int launch_linear_tc(cudaStream_t stream, const SbLinearArgs *a, const void *prepared, bool pdl);
 
 // ---- the many-row kernel over groups of rows with their own weights (the experts of an MoE block) ----
-// groups: device uint4 {expert, first row slot, rows (up to 128), rows padded to 16}; group_count: device word. A group's
+// groups: device uint4 {expert, first row slot, rows (up to max_rows), rows padded to 16}; group_count: device word. A group's
 // inputs are converted into a block of their own (launch_wide_prepare_grouped), its outputs are rows [slot0, slot0 + rows)
 // of `out`.
 struct WideGroupedArgs {
@@ -33,6 +33,7 @@ struct WideGroupedArgs {
   const uint4 *groups;
   const uint32_t *group_count;
   uint32_t max_groups;             // bounds the grid
+  uint32_t max_rows;               // the most rows a group holds (a multiple of 16 up to 128; up to 64: double-buffered sums)
   void *out;                       // bf16 [row slots][out_stride]
   uint32_t out_stride;
   bool pdl;

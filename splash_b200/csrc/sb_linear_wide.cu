@@ -81,6 +81,9 @@ struct WideParams {
   const uint32_t *group_count;
   const float *group_scales;   // scale_back of every row slot
   uint32_t tiles_per_group, expert_rows;  // weight rows per expert in the stacked tensor
+  // Up to 64 rows of X in every item: the accumulators are double-buffered inside their 128 columns (an item's sums at
+  // columns 64 (i & 1) .., i the CTA's count of items), so the epilogue of an item overlaps the next item's MMAs.
+  uint32_t dbuf;
 };
 // An item's tile, its range of super-blocks, its rows of X and where its weights, inputs and outputs are.
 struct WideItem {
@@ -371,9 +374,9 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
   uint64_t *x_empty = x_full + kWideMaxXStages;
   uint64_t *a_full = x_empty + kWideMaxXStages;                    // [kWideABufs]
   uint64_t *a_empty = a_full + kWideABufs;
-  uint64_t *d_full = a_empty + kWideABufs;
-  uint64_t *d_empty = d_full + 1;
-  uint64_t *h_full = d_empty + 1;                                  // the header (scale_back) has landed
+  uint64_t *d_full = a_empty + kWideABufs;                         // [2]: per accumulator buffer (the second with p.dbuf)
+  uint64_t *d_empty = d_full + 2;                                  // [2]
+  uint64_t *h_full = d_empty + 2;                                  // the header (scale_back) has landed
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(smem + 496);
   float *scale_back_all = reinterpret_cast<float *>(smem + 512);   // [128], the launch's rows (not grouped)
   uint8_t *x_ring = smem + kWideXOff, *raw_ring = smem + kWideRawOff;
@@ -383,7 +386,8 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
     for (uint32_t s = 0; s < kWideRawStages; ++s) mbar_init(&raw_full[s], 1), mbar_init(&raw_empty[s], 8);
     for (uint32_t s = 0; s < kWideMaxXStages; ++s) mbar_init(&x_full[s], 1), mbar_init(&x_empty[s], p.halves);
     for (uint32_t s = 0; s < kWideABufs; ++s) mbar_init(&a_full[s], 4), mbar_init(&a_empty[s], 1);
-    mbar_init(d_full, p.halves), mbar_init(d_empty, kWideEpilogueWarps), mbar_init(h_full, 1);
+    for (uint32_t s = 0; s < 2; ++s) mbar_init(&d_full[s], p.halves), mbar_init(&d_empty[s], kWideEpilogueWarps);
+    mbar_init(h_full, 1);
     fence_mbar_init();
   }
   if (warp == kWideMmaWarp0) tmem_alloc(tmem_slot, kWideTmemCols);
@@ -456,15 +460,15 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
     // busy at N = 128 (measured: 62 to 70 cycles per MMA overall). ----
     if (lane == 0 && warp - kWideMmaWarp0 < p.halves) {
       const uint32_t tn = warp - kWideMmaWarp0;
-      const uint32_t d0 = tmem + tn * kWideDCols;
       if (grouped) pdl_wait();
       const uint32_t n_items = wide_items(p);
       bool ok = true;
-      uint32_t ucount = 0, xg = 0, xphase = 0, dphase = 0, done_items = 0;
+      uint32_t ucount = 0, xg = 0, xphase = 0, done_items = 0;
       for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++done_items) {
-        if (done_items > 0) {  // the accumulators of the item before must have been read
-          ok = mbar_wait(d_empty, dphase);
-          dphase ^= 1;
+        const uint32_t buf = p.dbuf ? done_items & 1 : 0, uses = p.dbuf ? done_items >> 1 : done_items;  // uses of this buffer so far
+        const uint32_t d0 = tmem + tn * kWideDCols + buf * (kWideDCols / 2);
+        if (uses > 0) {  // the buffer's sums of its item before must have been read
+          ok = mbar_wait(&d_empty[buf], (uses - 1) & 1);
           if (!ok) { wide_expired(p.status, 3); break; }
         }
         const WideItem w = wide_item(p, item);
@@ -500,7 +504,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
           if (ok) umma_commit(&x_empty[xg]);  // this half of the item has read the group (the barrier counts both halves)
           if (++xg == p.x_groups) xg = 0, xphase ^= 1;
         }
-        if (ok) umma_commit(d_full);
+        if (ok) umma_commit(&d_full[buf]);
         if (tn == 0) WIDE_EVENT(3);  // last MMA issued
       }
     }
@@ -565,11 +569,12 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
     pdl_wait();  // aux / out belong to the stream's earlier kernels until they finish
     bool ok = grouped || wide_warp_wait(h_full, 0);
     if (!ok && lane == 0) wide_expired(p.status, 8);
-    uint32_t dphase = 0;
+    uint32_t done_items = 0;
     const uint32_t n_items = wide_items(p);
     float *own_scales = reinterpret_cast<float *>(smem + 1024 + 512 * q);
-    for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (uint32_t item = blockIdx.x; item < n_items && ok; item += gridDim.x, ++done_items) {
       const WideItem w = wide_item(p, item);
+      const uint32_t buf = p.dbuf ? done_items & 1 : 0, uses = p.dbuf ? done_items >> 1 : done_items;
       const float *scale_back = grouped ? own_scales : reinterpret_cast<const float *>(smem + 512);
       if (grouped) {  // the rows' scales, a copy per warp
         __syncwarp();
@@ -578,18 +583,17 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
       }
       {
         WIDE_T0();
-        if (!wide_warp_wait(d_full, dphase)) {
+        if (!wide_warp_wait(&d_full[buf], uses & 1)) {
           if (lane == 0) wide_expired(p.status, 9);
           ok = false;
           break;
         }
         if (q == 0) WIDE_TADD(2, 0);
       }
-      dphase ^= 1;
       tc_fence_after_sync();
       if (q == 0) WIDE_EVENT(4);  // sums complete
       WIDE_T0();
-      const uint32_t t0 = tmem_addr(tmem, 32 * q, 0);
+      const uint32_t t0 = tmem_addr(tmem, 32 * q, buf * (kWideDCols / 2));
       // Per 16 rows of X: the sums out of tensor memory, the epilogue on all 16 without a branch (the chains of the
       // activation overlap), then the stores of the rows that exist.
       if (p.gate_up) {
@@ -664,7 +668,7 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
       }
       tc_fence_before_sync();
       __syncwarp();
-      if (lane == 0) mbar_arrive(d_empty);
+      if (lane == 0) mbar_arrive(&d_empty[buf]);
       if (q == 0) WIDE_TADD(2, 1);
       if (q == 0) WIDE_EVENT(5);  // stored
     }
@@ -735,6 +739,7 @@ int launch_wide_prepare_grouped(cudaStream_t stream, const WidePrepareGroupedArg
 int launch_linear_wide_grouped(cudaStream_t stream, const WideGroupedArgs &a) {
   SB_REQUIRE(a.weights && a.prepared && a.scales && a.groups && a.group_count && a.out && a.max_groups, "grouped projection: null pointer or no groups");
   SB_REQUIRE(a.k && a.k % 256 == 0, "grouped projection: k = %u is not a multiple of 256", a.k);
+  SB_REQUIRE(a.max_rows >= 16 && a.max_rows <= kWideMaxRows && a.max_rows % 16 == 0, "grouped projection: groups of up to %u rows (16 .. 128 in sixteens)", a.max_rows);
   const bool gate_up = a.weights2 != nullptr;
   SB_REQUIRE(a.expert_rows % (gate_up ? 128 : 256) == 0, "grouped projection: %u rows an expert (whole tiles of %u)", a.expert_rows, gate_up ? 128 : 256);
   Context &c = ctx();
@@ -750,8 +755,9 @@ int launch_linear_wide_grouped(cudaStream_t stream, const WideGroupedArgs &a) {
   p.prepared = static_cast<const uint8_t *>(a.prepared), p.out = a.out, p.status = c.status_dev;
   p.n = a.expert_rows, p.out_stride = a.out_stride, p.epilogue = gate_up ? SB_EPILOGUE_GATE_UP : SB_EPILOGUE_NONE;
   p.nsb = a.k / 256, p.gate_up = gate_up, p.halves = 2, p.splits = 1;
-  p.rows = p.rows_padded = kWideMaxRows;  // (a group's own rows come from the table)
-  p.x_stage_bytes = kWideMaxRows * 128, p.x_groups = kWideXBytes / (4 * p.x_stage_bytes);
+  p.rows = p.rows_padded = a.max_rows;  // (a group's own rows come from the table)
+  p.x_stage_bytes = a.max_rows * 128, p.x_groups = std::min(kWideMaxXStages, kWideXBytes / (4 * p.x_stage_bytes));
+  p.dbuf = a.max_rows <= kWideDCols / 2 ? 1 : 0;
   p.groups = a.groups, p.group_count = a.group_count, p.group_scales = a.scales;
   p.tiles_per_group = gate_up ? a.expert_rows / 128 : a.expert_rows / 256, p.expert_rows = a.expert_rows;
   cudaLaunchConfig_t cfg = {};
@@ -997,6 +1003,7 @@ extern "C" int sb_linear_wide(void *stream, const SbLinearArgs *a) {
     p.items = (gate_up ? (a->n + 127) / 128 : (a->n + 128 * p.halves - 1) / (128 * p.halves)) * p.splits;
     p.x_stage_bytes = p.rows_padded * 128;
     p.x_groups = std::min(kWideMaxXStages, kWideXBytes / (4 * p.x_stage_bytes));
+    p.dbuf = p.rows_padded <= kWideDCols / 2 ? 1 : 0;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(std::min<uint32_t>(p.items, uint32_t(c.sm_count)));
     cfg.blockDim = dim3(kWideThreads);

@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeParams p) {
 // ---- many rows (the rows of several lanes): routes grouped by expert, the experts' passes on the many-row kernel ----
 // (MoE::addRouted's grouping: runtime/metal/kernels/shared/moe.metal:187-287, the row gather :347-365, the expert tiles
 // runtime/metal/kernels/common/moe_gguf_expert_tile.h:33-84, the combine moe.metal:367-392.)
-constexpr uint32_t kMoeMaxExperts = 512, kMoeMaxRoutes = 16384, kMoeGroupRows = 128, kMoeGroupThreads = 512;
+constexpr uint32_t kMoeMaxExperts = 512, kMoeMaxRoutes = 16384, kMoeGroupRows = 64, kMoeGroupThreads = 512;
 struct MoeGrouping {
   uint32_t *counts;         // [0] groups, [1] row slots
   uint4 *groups;            // {expert, first slot, rows, rows padded to 16}
@@ -183,7 +183,7 @@ static MoeGroupLayout moe_group_layout(uint32_t rows, uint32_t routes, uint32_t 
 // One CTA of 16 warps: a stable counting sort of the routes by expert. Warp w owns a run of consecutive routes; it counts
 // them by expert (a step of 32 routes at a time, equal experts found with a warp match), a thread per expert then adds the
 // warps' counts in warp order, one warp lays the experts' groups out one after the other (an expert's routes in groups of
-// 128, the last padded to 16 row slots), and the warps walk their runs again to number the routes: a route's place among
+// 64, the last padded to 16 row slots), and the warps walk their runs again to number the routes: a route's place among
 // its expert's routes is the earlier warps' count, plus this warp's count so far, plus its rank inside the step.
 constexpr uint32_t kMoeGroupWarps = kMoeGroupThreads / 32;
 // Which routes a launch takes, and the expert's place in its tensors: all of them (experts0 = 0, local = experts), or a
@@ -357,7 +357,7 @@ static int moe_experts_grouped(cudaStream_t s, const SbMoeExpertArgs *a, const M
   int st = launch_wide_prepare_grouped(s, c1);
   if (st != SB_OK) return st;
   WideGroupedArgs pair{a->gate, a->up, a->experts_total, a->inter, a->hidden, at(l.prepared1), reinterpret_cast<const float *>(at(l.scales1)), g.groups,
-                       g.counts, l.max_groups, at(l.act), a->inter, pdl};
+                       g.counts, l.max_groups, kMoeGroupRows, at(l.act), a->inter, pdl};
   st = launch_linear_wide_grouped(s, pair);
   if (st != SB_OK) return st;
   WidePrepareGroupedArgs c2{at(l.act), a->inter, a->inter, g.slot_self, g.slot_group, g.counts + 1, l.max_slots, g.groups, at(l.prepared2),
@@ -365,7 +365,7 @@ static int moe_experts_grouped(cudaStream_t s, const SbMoeExpertArgs *a, const M
   st = launch_wide_prepare_grouped(s, c2);
   if (st != SB_OK) return st;
   WideGroupedArgs down{a->down, nullptr, a->experts_total, a->hidden, a->inter, at(l.prepared2), reinterpret_cast<const float *>(at(l.scales2)), g.groups,
-                       g.counts, l.max_groups, at(l.y), a->hidden, pdl};
+                       g.counts, l.max_groups, kMoeGroupRows, at(l.y), a->hidden, pdl};
   st = launch_linear_wide_grouped(s, down);
   if (st != SB_OK) return st;
   cudaLaunchConfig_t cfg = {};
