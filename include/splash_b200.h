@@ -331,6 +331,10 @@ SB_API int sb_attn_verify(void *stream, const SbAttnArgs *args);
  * path_mask_dev: device u32, the accepted path's row mask (sb_accept's retained_rows). */
 SB_API int sb_kv_path_commit(void *stream, const SbKvLayer *cache, const uint32_t *page_table, uint32_t committed,
                              const uint32_t *path_mask_dev);
+/* The same for the lanes of a step: lane l's position committed_dev[l], its page table page_table_stride entries after lane
+ * l - 1's, its path mask mask_stride words after lane l - 1's (4 for the results of sb_accept). */
+SB_API int sb_kv_path_commit_lanes(void *stream, const SbKvLayer *cache, const uint32_t *page_table, uint32_t page_table_stride,
+                                   const uint32_t *committed_dev, const uint32_t *path_mask_dev, uint32_t mask_stride, uint32_t lanes);
 /* The same with the lane's position read from a device word, so a captured graph follows the lane. */
 SB_API int sb_kv_path_commit_at(void *stream, const SbKvLayer *cache, const uint32_t *page_table, const uint32_t *committed_dev,
                                 const uint32_t *path_mask_dev);
@@ -516,7 +520,7 @@ typedef struct SbTargetConfig {
   /* Concurrent requests stepped together (0 or 1: one lane; up to 32): every per-lane buffer of the target becomes an array
    * over the lanes ("steps of several lanes" above), a layer's KV pool holds the lanes' pages one lane after the other, and
    * a step multiplies 16 x lanes rows on the many-row projection kernel, which needs Q4_K projections (fmt_proj, fmt_down,
-   * fmt_head). Dense models on one GPU; chain blocks. */
+   * fmt_head). One GPU (or expert-parallel ranks). */
   uint32_t lanes;
   /* Expert parallelism: this process is rank ep_rank of ep_world ranks (0 or 1: none), one per GPU of the node. Every rank
    * steps its own `lanes` lanes and holds the routed experts [ep_rank E / ep_world, ..) of every MoE block in its
@@ -693,7 +697,8 @@ SB_API int sb_target_verify(void *target, void *stream, const uint32_t *tokens_h
                             float temperature, uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host);
 /* sb_target_verify for a target of several lanes: tokens_host u32 [lanes][16] (a lane's block in its 16 slots, rows of them used),
  * uniforms_host fp32 [lanes][80] or NULL, out_tokens_host u32 [lanes][16] (a lane's retained tokens first), out_results_host
- * u32 [lanes][4] = {retained, accepted, retained_rows, 0} per lane. Chain blocks. */
+ * u32 [lanes][4] = {retained, accepted, retained_rows, 0} per lane. With SB_TARGET_TREE every lane's block is a tree: the
+ * host has written the lanes' SplashTreeRow rows into the target's `tree` tensor ([lanes][16] rows) beforehand. */
 SB_API int sb_target_verify_lanes(void *target, void *stream, const uint32_t *tokens_host, const float *uniforms_host, uint32_t rows,
                                   float temperature, uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host);
 /* sb_target_verify for a tree of draft tokens: tree_host holds `rows` SplashTreeRow entries {ancestors u32, parent u16,

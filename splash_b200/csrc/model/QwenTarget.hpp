@@ -153,7 +153,8 @@ class QwenTarget {
   uint32_t lanes_ = 1, pagesPerLane_ = 0;
   bool wide_ = false;  // the step runs on the many-row projection kernel (several lanes, or NVFP4 projections)
   Buffer widePrepared_[2], widePartials_;  // conversions for the many-row projection kernel (steps of several lanes)
-  void encodeVerifyLanes(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool keepPending, bool drawsGiven);
+  void encodeVerifyLanes(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool treeGiven, bool keepPending,
+                         bool drawsGiven);
   uint64_t weightBytes_ = 0, moeExpertBytes_ = 0;
   uint32_t moeLayers_ = 0;
 };
@@ -366,8 +367,7 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   if (rows < 1 || rows > kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: 1 to 16 rows");
   if (committedHost + rows > cfg_.max_context + kVerifyRows) throw std::invalid_argument("QwenTarget::encodeVerify: past the context bound");
   if (wide_) {
-    if (treeGiven) throw std::invalid_argument("QwenTarget::encodeVerify: tree blocks are offered for one lane of Q4_K / Q6_K / Q8_0 projections");
-    return encodeVerifyLanes(graph, rows, temperature, parity, advance, keepPending, drawsGiven);
+    return encodeVerifyLanes(graph, rows, temperature, parity, advance, treeGiven, keepPending, drawsGiven);
   }
   const SbTargetConfig &c = loc_;
   const uint32_t H = c.hidden, D = c.head_dim;
@@ -483,12 +483,14 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
 // A step of several lanes (SbTargetConfig.lanes): every lane a chain of `rows` rows in its 16 row slots, the projections
 // over all 16 x lanes slots at once on the many-row kernel (RMSNorm inside its conversion, the residual in its epilogue),
 // attention, GDN, selection and acceptance gridded over the lanes with each lane's own position, pages, cell and tapes.
-inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool keepPending,
-                                          bool drawsGiven) {
+inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool treeGiven,
+                                          bool keepPending, bool drawsGiven) {
   using namespace ops;
   const SbTargetConfig &c = loc_;
   const uint32_t H = c.hidden, D = c.head_dim, L = lanes_, R = kVerifyRows * L;
-  launchStepBegin(graph, committed, tree, positions, rows, false, L);
+  if (treeGiven && temperature > 0.0f && !drawsGiven)
+    throw std::invalid_argument("QwenTarget::encodeVerify: a sampled tree block needs the draft's candidates and draws (SB_TARGET_DRAWS)");
+  launchStepBegin(graph, committed, tree, positions, rows, treeGiven, L);
   if (c.rotary_pairs) RoPE::addTreeTables(graph, positions, invFreq, cosine, sine, R, 1.0f, c.rotary_pairs);
   Embedding::add(graph, tokens, embedding_, hidden[0], R, H);
   uint32_t cur = 0;
@@ -513,7 +515,7 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
                          queries_.as(), PagedAttention::describe(kv_, w.pages), committed.as<uint32_t>(), rows, c.q_heads,
                          c.gated_attention ? 1u : 0u, c.rotary_pairs, packedStride_, committedHost, L, pagesPerLane_};
       check(sb_attn_store(graph.stream, &sa));
-      SbAttnArgs aa{queries_.as(), c.gated_attention ? packed_.as() : nullptr, pageTable_.as<uint32_t>(), nullptr, mixed_.as(),
+      SbAttnArgs aa{queries_.as(), c.gated_attention ? packed_.as() : nullptr, pageTable_.as<uint32_t>(), treeGiven ? tree.as() : nullptr, mixed_.as(),
                     PagedAttention::describe(kv_, w.pages), committed.as<uint32_t>(), rows, c.q_heads, c.gated_attention ? 1u : 0u,
                     packedStride_, mixedWidth, committedHost, L, pagesPerLane_};
       check(sb_attn_verify(graph.stream, &aa));
@@ -529,6 +531,7 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
       a.state_in = w.cells[parity].state.as<float>(), a.state_out = w.cells[parity ^ 1].state.as<float>();
       a.pending = w.tapes[parity ^ 1].describe(), a.step = w.tapes[parity].describe();
       a.hidden = mixed_.as(), a.pending_rows_dev = pendingRows.as<uint32_t>();
+      if (treeGiven) a.tree = tree.as(), a.pending_path_dev = pendingPath.as<uint32_t>();  // (a tree step's pending rows are a path of the tape)
       a.rows = rows, a.key_heads = gdn_.keyHeads, a.value_heads = gdn_.valueHeads, a.qkvz_stride = packedStride_, a.ab_stride = 2 * gdn_.valueHeads;
       a.hidden_stride = mixedWidth, a.tiled = c.tiled_heads != 0, a.flags = SB_GDN_STATE_SETTLED, a.lanes = L;
       check(sb_gdn_verify(graph.stream, &a));
@@ -572,6 +575,14 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
   SbAcceptArgs ac{tokens.as<uint32_t>(), tree.as(), selected.as<uint32_t>(), results.as<uint32_t>(), nullptr, rows, kVerifyRows, 0, L};
   check(sb_accept(graph.stream, &ac));
   graph.launches += 2;
+  // The accepted paths' KV rows move from their rows' slots to their depths' (a chain's are there already).
+  if (treeGiven && advance)
+    for (LayerWeights &w : layers_)
+      if (w.attention) {
+        const SbKvLayer cache = PagedAttention::describe(kv_, w.pages);
+        check(sb_kv_path_commit_lanes(graph.stream, &cache, pageTable_.as<uint32_t>(), pagesPerLane_, committed.as<uint32_t>(), results.as<uint32_t>() + 2, 4, L));
+        ++graph.launches;
+      }
   launchStepEnd(graph, results, committed, pendingRows, pendingPath, advance ? 1u : keepPending ? 2u : 0u, nullptr, 0, L);
 }
 

@@ -284,11 +284,15 @@ __global__ void __launch_bounds__(D) attn_store_kernel(const StoreParams p) {
 }
 
 // ---- path commit: grid (kv_heads), head_dim threads; rows move in depth order ----
+// Several lanes: grid (kv_heads, lanes); lane l's position at committed_dev[l], its page table page_table_stride entries
+// further on, its path mask mask_stride words further on.
 __global__ void kv_path_commit_kernel(SbKvLayer c, const uint32_t *page_table, uint32_t committed, const uint32_t *committed_dev,
-                                      const uint32_t *path_mask) {
+                                      const uint32_t *path_mask, uint32_t page_table_stride, uint32_t mask_stride) {
   pdl_launch_dependents();
   pdl_wait();
-  if (committed_dev) committed = *committed_dev;
+  const uint32_t lane_of_step = blockIdx.y;
+  page_table += size_t(lane_of_step) * page_table_stride, path_mask += size_t(lane_of_step) * mask_stride;
+  if (committed_dev) committed = committed_dev[lane_of_step];
   const uint32_t mask = *path_mask, h = blockIdx.x, d = threadIdx.x, D = c.head_dim;
   uint32_t depth = 0;
   for (uint32_t row = 0; row < 32; ++row) {
@@ -898,7 +902,17 @@ int sb_kv_path_commit(void *stream, const SbKvLayer *cache, const uint32_t *page
   int st = check_cache(*cache, "sb_kv_path_commit");
   if (st != SB_OK) return st;
   return launch(kv_path_commit_kernel, dim3(cache->kv_heads), dim3(cache->head_dim), as_stream(stream), *cache, page_table,
-                committed, static_cast<const uint32_t *>(nullptr), path_mask_dev);
+                committed, static_cast<const uint32_t *>(nullptr), path_mask_dev, 0u, 0u);
+}
+
+int sb_kv_path_commit_lanes(void *stream, const SbKvLayer *cache, const uint32_t *page_table, uint32_t page_table_stride,
+                            const uint32_t *committed_dev, const uint32_t *path_mask_dev, uint32_t mask_stride, uint32_t lanes) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(cache && page_table && committed_dev && path_mask_dev && lanes >= 1 && lanes <= 64, "sb_kv_path_commit_lanes: null pointer, or %u lanes (1..64)", lanes);
+  int st = check_cache(*cache, "sb_kv_path_commit_lanes");
+  if (st != SB_OK) return st;
+  return launch(kv_path_commit_kernel, dim3(cache->kv_heads, lanes), dim3(cache->head_dim), as_stream(stream), *cache, page_table, 0u, committed_dev,
+                path_mask_dev, page_table_stride, mask_stride);
 }
 
 int sb_kv_path_commit_at(void *stream, const SbKvLayer *cache, const uint32_t *page_table, const uint32_t *committed_dev,
@@ -908,7 +922,7 @@ int sb_kv_path_commit_at(void *stream, const SbKvLayer *cache, const uint32_t *p
   int st = check_cache(*cache, "sb_kv_path_commit_at");
   if (st != SB_OK) return st;
   return launch(kv_path_commit_kernel, dim3(cache->kv_heads), dim3(cache->head_dim), as_stream(stream), *cache, page_table, 0u, committed_dev,
-                path_mask_dev);
+                path_mask_dev, 0u, 0u);
 }
 
 uint64_t sb_sample_workspace_bytes(uint32_t rows, uint32_t vocab) {

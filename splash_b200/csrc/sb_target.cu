@@ -478,7 +478,6 @@ int sb_target_verify_lanes(void *target, void *stream, const uint32_t *tokens_ho
   SB_REQUIRE(target && tokens_host && out_tokens_host && out_results_host, "sb_target_verify_lanes: null pointer");
   SB_REQUIRE(rows >= 1 && rows <= splash::b200::model::kVerifyRows, "sb_target_verify_lanes: rows = %u outside 1..16", rows);
   SB_REQUIRE(temperature == 0.0f || uniforms_host, "sb_target_verify_lanes: a sampled policy needs uniforms");
-  SB_REQUIRE(!(flags & SB_TARGET_TREE), "sb_target_verify_lanes: chain blocks");
   Target *t = static_cast<Target *>(target);
   QwenTarget &m = *t->model;
   const uint32_t L = m.lanes();

@@ -126,8 +126,9 @@ class Target:
         assert len(c) == max(1, self.cfg.lanes)
         lib.check(self.l.sb_target_reset_lanes(self.handle, c.ctypes.data_as(_P)))
 
-    def verify_lanes(self, tokens, uniforms=None, temperature=0.0, flags=0, stream=None):
-        """One step of every lane from host buffers: tokens [lanes, rows]; uniforms [lanes, 80] for a sampled policy.
+    def verify_lanes(self, tokens, uniforms=None, temperature=0.0, flags=0, stream=None, trees=None):
+        """One step of every lane from host buffers: tokens [lanes, rows]; uniforms [lanes, 80] for a sampled policy; trees
+        (uint32 [lanes, rows, 2]: ancestors, parent | depth << 16) makes every lane's block a tree.
         Returns per lane (retained tokens, retained, accepted, retained_rows mask)."""
         tokens = np.ascontiguousarray(tokens, np.uint32)
         lanes, rows = tokens.shape
@@ -137,6 +138,11 @@ class Target:
         u = None if uniforms is None else np.ascontiguousarray(uniforms, np.float32)
         assert u is None or u.shape == (lanes, 80)
         out_t, out_r = np.zeros((lanes, 16), np.uint32), np.zeros((lanes, 4), np.uint32)
+        if trees is not None:
+            tr = np.zeros((lanes, 16, 2), np.uint32)
+            tr[:, :rows] = np.asarray(trees, np.uint32)
+            self.upload(-1, "tree", tr)
+            flags |= TREE
         lib.check(self.l.sb_target_verify_lanes(self.handle, stream, slots.ctypes.data_as(_P), None if u is None else u.ctypes.data_as(_P),
                                                 rows, temperature, flags, out_t.ctypes.data_as(_P), out_r.ctypes.data_as(_P)))
         return [(out_t[l, :out_r[l, 0]].copy(), int(out_r[l, 0]), int(out_r[l, 1]), int(out_r[l, 2])) for l in range(lanes)]

@@ -329,6 +329,50 @@ def test_tiny_moe_model_of_three_lanes_matches_three_oracle_lanes():
     assert compared >= 4, compared
 
 
+def _tree_rows(parent):
+    t = np.zeros((len(parent), 2), np.uint32)
+    for r in range(len(parent)):
+        t[r, 0] = (1 << r) | (t[parent[r], 0] if r else 0)
+        t[r, 1] = parent[r] | ((bin(int(t[r, 0])).count("1") - 1) << 16)
+    return t
+
+
+def test_tiny_model_tree_blocks_of_two_lanes_match_two_oracle_lanes():
+    """Every lane its own tree of draft tokens, two committed steps: positions by depth, attention and GDN along each row's
+    path, the accepted path's KV rows moved to their depths per lane, the next step folding each lane's accepted path."""
+    positions = np.array([2048, 900], np.uint32)
+    lib, target, t, cfg, w, states = build_lanes(2, positions, seed=9)
+    parents = [[0, 0, 1, 2, 0, 4, 5, 6, 6, 8, 9, 10, 9, 12, 0, 14], [0, 0, 0, 1, 1, 2, 3, 3, 5, 5, 8, 8, 10, 11, 12, 13]]
+    goods = [[4, 5, 6, 8, 9, 12, 13], [2, 5, 9]]      # rows along which the draft matches the target (a path of each tree)
+    first, compared = [17, 4000], 0
+    for step in range(2):
+        blocks, trees = [], []
+        for i in range(2):
+            good = goods[i]
+            greedy = mo.draft_chain(cfg, w, states[i], first[i], rows=len(good) + 1, p_match=1.0, seed=step)
+            tokens = np.random.default_rng(8 + i + 2 * step).integers(0, cfg["vocab"], 16).astype(np.uint32)
+            tokens[0] = first[i]
+            tokens[good] = greedy[1:]
+            blocks.append(tokens), trees.append(_tree_rows(parents[i]))
+        wants = [mo.verify_step(cfg, w, states[i], blocks[i], advance=True, tree=trees[i]) for i in range(2)]
+        got = t.verify_lanes(np.stack(blocks), flags=target.ADVANCE | target.GRAPH, trees=np.stack(trees))
+        assert lib.device_status() == 0
+        logits = t.download(-1, "logits", np.float32, (32, cfg["vocab"]))
+        for i in range(2):
+            want, (tokens, retained, accepted, mask) = wants[i], got[i]
+            err = np.abs(logits[16 * i:16 * i + 16] - want["logits"])
+            scale = np.abs(want["logits"]).max()
+            assert err.max() <= 3e-2 * scale and np.median(err) <= 2e-3 * scale, (step, i)
+            top2 = np.sort(want["logits"], axis=1)[:, -2:]
+            on_path = [r for r in range(16) if want["mask"] >> r & 1]
+            assert ((top2[:, 1] - top2[:, 0]) > 2.5 * err.max(axis=1))[on_path].all(), "a near tie on the accepted path: pick another seed"
+            assert (retained, accepted, mask) == (want["retained"], want["accepted"], want["mask"]), (step, i)
+            assert np.array_equal(tokens, want["tokens"]), (step, i)
+            compared += 1
+            first[i] = int(tokens[-1])
+    assert compared == 4 and wants[0]["accepted"] >= 3
+
+
 def test_lane_of_a_four_lane_step_does_not_depend_on_the_other_lanes():
     """The same lane 2 next to different neighbours: its logits and results are bit-equal."""
     positions = np.array([2048, 300, 1537, 1000], np.uint32)
