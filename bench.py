@@ -210,7 +210,7 @@ def main():
     if expert_parallel and not (args.moe and args.lanes % world == 0 and args.lanes // world >= 2):
         raise SystemExit("--parallel ep needs --moe and --lanes a multiple of the ranks, two lanes a rank at least")
     if args.moe:
-        workload = "35B-A3B-shaped MoE verify (256 experts + shared, top 8, router logits ~ N(0,1) given), Q4_K, batch 1, block 16, 8K INT8 paged KV, greedy"
+        workload = "35B-A3B-shaped MoE verify (256 experts + shared, top 8, router logits ~ N(0,1) given), Q4_K, batch 1, block 16, 8K INT8 paged KV, rejection sampling at temperature 0.7 with supplied uniforms"
         args.tiny = True  # (the extra legs of the benchmark are for the 27B workload only)
         if not expert_parallel:
             args.parallel = "replicas"
@@ -304,6 +304,12 @@ def main():
     rng = np.random.default_rng(0 if tensor_parallel else rank)
     t.upload(-1, "tokens", rng.integers(0, cfg["vocab"], ROWS * L).astype(np.uint32))
     t.upload(-1, "pending_rows", np.full(L, FOLD_ROWS, np.uint32))
+    # The MoE configuration verifies by rejection sampling at temperature 0.7 with supplied uniforms (80 a lane and step);
+    # the others greedily.
+    temperature = 0.7 if args.moe else 0.0
+    uniforms = rng.random(80 * L).astype(np.float32)
+    if temperature:
+        t.upload(-1, "uniforms", uniforms)
 
     def barrier():
         lib.stream_sync(stream)
@@ -313,13 +319,13 @@ def main():
 
     # ---- device-resident steps ----
     for _ in range(warm):
-        t.step(ROWS, 0.0, flags, stream)
+        t.step(ROWS, temperature, flags, stream)
     barrier()
     sampler = ClockSampler(local) if rank == 0 else None
     e0, e1 = lib.Event(), lib.Event()
     e0.record(stream)
     for _ in range(args.steps):
-        t.step(ROWS, 0.0, flags, stream)
+        t.step(ROWS, temperature, flags, stream)
     e1.record(stream)
     e1.sync()
     barrier()
@@ -336,16 +342,19 @@ def main():
 
     # ---- end to end through the host-facing call, pinned host buffers ----
     pinned = ctypes.c_void_p()
-    lib.check(lib.load().sb_host_alloc(3 * 4096, ctypes.byref(pinned)))
+    lib.check(lib.load().sb_host_alloc(8 * 4096, ctypes.byref(pinned)))
     host = np.ctypeslib.as_array((ctypes.c_uint32 * 1024).from_address(pinned.value))
     host[:ROWS * L] = rng.integers(0, cfg["vocab"], ROWS * L)
+    host_u = np.ctypeslib.as_array((ctypes.c_float * (80 * L)).from_address(pinned.value + 3 * 4096))
+    host_u[:] = uniforms
+    u_ptr = pinned.value + 3 * 4096 if temperature else None
     l = target._bind()
     out_t, out_r = pinned.value + 4096, pinned.value + 2 * 4096
     def verify_once():
         if L > 1:
-            lib.check(l.sb_target_verify_lanes(t.handle, stream, pinned.value, None, ROWS, 0.0, flags, out_t, out_r))
+            lib.check(l.sb_target_verify_lanes(t.handle, stream, pinned.value, u_ptr, ROWS, temperature, flags, out_t, out_r))
         else:
-            lib.check(l.sb_target_verify(t.handle, stream, pinned.value, None, ROWS, 0.0, flags, out_t, out_r))
+            lib.check(l.sb_target_verify(t.handle, stream, pinned.value, u_ptr, ROWS, temperature, flags, out_t, out_r))
     for _ in range(2):
         verify_once()
     barrier()
@@ -360,12 +369,13 @@ def main():
 
     # ---- one checked step after the timed loops: the step computed something sane, and the same thing on every rank ----
     if L > 1:
-        per_lane = t.verify_lanes(host[:ROWS * L].copy().reshape(L, ROWS), flags=flags, stream=stream)
+        per_lane = t.verify_lanes(host[:ROWS * L].copy().reshape(L, ROWS), uniforms=uniforms.reshape(L, 80) if temperature else None,
+                                  temperature=temperature, flags=flags, stream=stream)
         retained = min(r[1] for r in per_lane)  # (the bounds below then hold for every lane)
         if max(r[1] for r in per_lane) > ROWS:
             retained = 0
     else:
-        _, retained, _, _ = t.verify(host[:ROWS].copy(), flags=flags, stream=stream)
+        _, retained, _, _ = t.verify(host[:ROWS].copy(), uniforms=uniforms if temperature else None, temperature=temperature, flags=flags, stream=stream)
     logits = t.download(-1, "logits", np.float32, (ROWS * L, cfg["vocab"]))
     finite = bool(np.isfinite(logits).all())
     bits = logits.view(np.uint32).astype(np.uint64)
@@ -468,7 +478,7 @@ def main():
                    "fold": f"held lane that keeps {FOLD_ROWS} pending rows: every timed step folds {FOLD_ROWS} tape rows into the GDN state",
                    "parallelism": "tp1" if world == 1 else (f"tp{world}: one lane, shares exchanged through peer memory over NVLink in the input conversions" if tensor_parallel else f"ep{world}: {L} lanes and {cfg.get('moe_experts', 0) // world} of the routed experts a rank, rows dispatched and sums combined through peer memory over NVLink" if expert_parallel else f"{world} independent replicas (lanes)" + (f"; {fell_back}" if fell_back else "")),
                    "l2": "inputs exceed L2: one step streams %.1f GB of weights" % (stats["weight_bytes"] / 1e9), "cuda_graph": True, "pdl": True},
-        "e2e": {"value": lanes * ROWS / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": ROWS * 4 * L, "d2h_bytes_per_step": (16 + ROWS * 4) * L},
+        "e2e": {"value": lanes * ROWS / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": (ROWS * 4 + (320 if temperature else 0)) * L, "d2h_bytes_per_step": (16 + ROWS * 4) * L},
         "gpu_launches": stats["launches"] * args.steps,
         "launches_per_step": stats["launches"],
         "step_roofline": {"bytes_per_step": step_bytes, "weight_bytes": stats["weight_bytes"], "kv_bytes": stats["kv_bytes"],
