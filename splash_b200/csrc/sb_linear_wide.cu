@@ -150,35 +150,23 @@ struct WidePrepParams {
   const float *partials;  // fp32 [splits][rows_total][partial_stride], this pass's first row at row0
   const uint16_t *residual;
   uint32_t splits, rows_total, row0, partial_stride, residual_stride;
-  // Grouped (an MoE block's routed rows): CTA s converts row slot s of the groups' blocks. slot_src[s] is the row of x it
-  // holds (~0: a padding slot, zeros), slot_group[s] = group << 8 | its row inside the group, groups as WideParams has them;
-  // the blocks start at out (a group's at slot0 * k * 2), the slots' scales go to `scales`.
+  // Grouped (an MoE block's routed rows; wide_prepare_slots_kernel): slot_src[s] is the row of x that row slot s of the
+  // groups' blocks holds (~0: a padding slot, zeros), slot_group[s] = group << 8 | its row inside the group, groups as
+  // WideParams has them; the blocks start at out (a group's at slot0 * k * 2), the slots' scales go to `scales`.
   const uint32_t *slot_src, *slot_group, *slot_count;
   const uint4 *groups;
   float *scales;
 };
 __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const WidePrepParams p) {
   __shared__ float red_s[2 * (kWidePrepThreads / 32)];
-  uint32_t tok = blockIdx.x;  // the row slot inside its block
-  const uint32_t tid = threadIdx.x;
+  const uint32_t tok = blockIdx.x, tid = threadIdx.x;  // the row slot inside its block
   pdl_launch_dependents();
   pdl_wait();
-  bool live = tok < p.rows;
-  uint32_t rows_padded = p.rows_padded;
+  const bool live = tok < p.rows;
+  const uint32_t rows_padded = p.rows_padded;
   const uint16_t *xrow = p.x + size_t(tok) * p.x_stride;
   uint8_t *block = p.out + kWideHeader;
   float *scale_dst = reinterpret_cast<float *>(p.out) + tok;
-  if (p.slot_src) {
-    const uint32_t slot = blockIdx.x;
-    if (slot >= __ldg(p.slot_count)) return;
-    const uint32_t src = __ldg(p.slot_src + slot), sg = __ldg(p.slot_group + slot);
-    const uint4 rec = __ldg(p.groups + (sg >> 8));
-    live = src != 0xffffffffu;
-    tok = sg & 0xffu, rows_padded = rec.w;
-    xrow = p.x + size_t(live ? src : 0) * p.x_stride;
-    block = p.out + size_t(rec.y) * p.k * 2;
-    scale_dst = p.scales + slot;
-  }
   const uint32_t chunks = p.k / 8;  // 8 inputs each
   if (p.partials && live) {
     // The projection ahead left its k-splits' sums: add them in split order onto the residual, round once, and keep the
@@ -252,6 +240,59 @@ __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const Wi
       __half hv[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) hv[j] = __float2half_rn(v[j] * down);
+      const __half2 p0 = __halves2half2(hv[0], hv[2]), p1 = __halves2half2(hv[1], hv[3]);
+      const __half2 p2 = __halves2half2(hv[4], hv[6]), p3 = __halves2half2(hv[5], hv[7]);
+      h[0] = *reinterpret_cast<const uint32_t *>(&p0), h[1] = *reinterpret_cast<const uint32_t *>(&p1);
+      h[2] = *reinterpret_cast<const uint32_t *>(&p2), h[3] = *reinterpret_cast<const uint32_t *>(&p3);
+    }
+    const uint32_t k0 = 8 * c, unit = k0 / 64, step = (k0 % 64) / 16, half = (k0 % 16) / 8;
+    uint8_t *dst = block + unit * unit_bytes + size_t(step) * rows_padded * 32 + (tok >> 3) * 256 + half * 128 + (tok & 7) * 16;
+    *reinterpret_cast<uint4 *>(dst) = make_uint4(h[0], h[1], h[2], h[3]);
+  }
+}
+
+// The conversion of the groups' row slots with a warp per slot (no norm, no sums to add): a slot's table look-ups and its row
+// are a short chain, so many slots a CTA and few CTAs beat a CTA per slot (an MoE block's 6700 slots were 27 us as a CTA each).
+constexpr int kWideSlotWarps = 8;
+__global__ void __launch_bounds__(32 * kWideSlotWarps) wide_prepare_slots_kernel(const WidePrepParams p) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const uint32_t slot = blockIdx.x * kWideSlotWarps + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (slot >= __ldg(p.slot_count)) return;
+  const uint32_t src = __ldg(p.slot_src + slot), sg = __ldg(p.slot_group + slot);
+  const uint4 rec = __ldg(p.groups + (sg >> 8));
+  const bool live = src != 0xffffffffu;
+  const uint32_t tok = sg & 0xffu, rows_padded = rec.w, chunks = p.k / 8;
+  const uint16_t *xrow = p.x + size_t(live ? src : 0) * p.x_stride;
+  uint8_t *block = p.out + size_t(rec.y) * p.k * 2;
+  float mx = 0.0f;
+  for (uint32_t c = lane; c < chunks && live; c += 32) {
+    const uint4 raw = *reinterpret_cast<const uint4 *>(xrow + 8 * c);
+    const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) mx = fmaxf(mx, fmaxf(fabsf(bf16_bits_to_float(u[j] & 0xffffu)), fabsf(bf16_bits_to_float(u[j] >> 16))));
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  int e = 0;
+  if (mx > 0.0f && mx <= 3.0e38f) {
+    (void)frexpf(mx, &e);
+    e -= 10;
+  }
+  const float down = ldexpf(1.0f, -e);
+  if (lane == 0) p.scales[slot] = live ? ldexpf(1.0f, e) : 0.0f;
+  const size_t unit_bytes = size_t(rows_padded) * 128;
+  for (uint32_t c = lane; c < chunks; c += 32) {
+    uint32_t h[4] = {0, 0, 0, 0};
+    if (live) {
+      const uint4 raw = *reinterpret_cast<const uint4 *>(xrow + 8 * c);
+      const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
+      __half hv[8];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        hv[2 * j] = __float2half_rn(bf16_bits_to_float(u[j] & 0xffffu) * down);
+        hv[2 * j + 1] = __float2half_rn(bf16_bits_to_float(u[j] >> 16) * down);
+      }
       const __half2 p0 = __halves2half2(hv[0], hv[2]), p1 = __halves2half2(hv[1], hv[3]);
       const __half2 p2 = __halves2half2(hv[4], hv[6]), p3 = __halves2half2(hv[5], hv[7]);
       h[0] = *reinterpret_cast<const uint32_t *>(&p0), h[1] = *reinterpret_cast<const uint32_t *>(&p1);
@@ -727,12 +768,12 @@ int launch_wide_prepare_grouped(cudaStream_t stream, const WidePrepareGroupedArg
   pp.x = static_cast<const uint16_t *>(a.x), pp.out = static_cast<uint8_t *>(a.prepared), pp.k = a.k, pp.x_stride = a.x_stride;
   pp.slot_src = a.slot_src, pp.slot_group = a.slot_group, pp.slot_count = a.slot_count, pp.groups = a.groups, pp.scales = a.scales;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(a.max_slots), cfg.blockDim = dim3(kWidePrepThreads), cfg.stream = stream;
+  cfg.gridDim = dim3((a.max_slots + kWideSlotWarps - 1) / kWideSlotWarps), cfg.blockDim = dim3(32 * kWideSlotWarps), cfg.stream = stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = a.pdl ? 1 : 0;
-  SB_CUDA(cudaLaunchKernelEx(&cfg, wide_prepare_kernel, pp));
+  SB_CUDA(cudaLaunchKernelEx(&cfg, wide_prepare_slots_kernel, pp));
   return SB_OK;
 }
 
