@@ -95,7 +95,7 @@ def case_linear(a):
     copies = max(2, int(a.resident_mb * 1e6 // (n * rb * tensors)) + 1)
     bufs = [lib.DeviceBuffer.from_numpy(rows) for _ in range(copies * tensors)]
     wide = a.rows > 16 or fmt == lib.FMT_NVFP4   # the many-row kernel
-    image = wide and fmt in (lib.FMT_Q6K, lib.FMT_NVFP4)
+    image = wide and fmt in (lib.FMT_Q6K, lib.FMT_Q80, lib.FMT_NVFP4)
     if image:  # it reads Q6_K and NVFP4 rows as images made once
         natives, bufs = bufs, []
         for b in natives:

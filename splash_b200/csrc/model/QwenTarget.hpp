@@ -190,8 +190,8 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
     if (whole.tp_world > 1) throw std::invalid_argument("QwenTarget: several lanes and NVFP4 projections are offered on one GPU");
     if (whole.moe_experts && fp4) throw std::invalid_argument("QwenTarget: MoE experts are Q4_K");
     for (uint32_t f : {whole.fmt_proj, whole.fmt_down, whole.fmt_head})
-      if (f != SB_FMT_Q4K && f != SB_FMT_Q6K && f != SB_FMT_NVFP4)
-        throw std::invalid_argument("QwenTarget: several lanes and NVFP4 models take Q4_K, Q6_K and NVFP4 projections (fmt_proj, fmt_down, fmt_head)");
+      if (f != SB_FMT_Q4K && f != SB_FMT_Q6K && f != SB_FMT_Q80 && f != SB_FMT_NVFP4)
+        throw std::invalid_argument("QwenTarget: several lanes and NVFP4 models take Q4_K, Q6_K, Q8_0 and NVFP4 projections (fmt_proj, fmt_down, fmt_head)");
   }
   if (whole.tp_world > 1) tp_ = std::make_unique<ops::TensorParallel>(whole.tp_world, whole.tp_rank, whole.hidden, whole.vocab);
   if (!c.layers || !c.hidden || !c.vocab || !c.intermediate || !c.attention_interval)

@@ -51,10 +51,13 @@ constexpr uint32_t kWideThreads = 32 * (kWideMmaWarp0 + 2);  // 768
 //          of their own, the sixteen scales as halves d * sc / row scale (3 stages of 28 KB)
 //   NVFP4  the image, 160 bytes: the nibbles in expansion order, the sixteen scales as halves e4m3 * g * 2^14 / row scale
 //          (4 stages of 20 KB)
+//   Q8_0   the image, 272 bytes for eight blocks of 32: the codes + 128 as bytes, the eight scales as halves d / row scale
+//          (2 stages of 34 KB: a stream of the item has one stage to itself)
 template <uint32_t FMT> struct WideFmt;
 template <> struct WideFmt<SB_FMT_Q4K> { static constexpr uint32_t kSb = 144, kStages = 4; };
 template <> struct WideFmt<SB_FMT_Q6K> { static constexpr uint32_t kSb = 224, kStages = 3; };
 template <> struct WideFmt<SB_FMT_NVFP4> { static constexpr uint32_t kSb = 160, kStages = 4; };
+template <> struct WideFmt<SB_FMT_Q80> { static constexpr uint32_t kSb = 272, kStages = 2; };
 constexpr uint32_t kWideMaxRawStages = 4;
 constexpr uint32_t kWideXBytes = 128 * 1024, kWideMaxXStages = 8;   // the X ring; a stage holds 64 inputs of every row
 constexpr uint32_t kWideABufs = 4, kWideACols = 64, kWideACol0 = 256, kWideDCols = 128, kWideTmemCols = 512;
@@ -397,10 +400,29 @@ __device__ __forceinline__ void wide_expand_nvfp4(const uint8_t *row, uint32_t h
   }
 }
 
+// Inputs' half h of a Q8_0 image row's super-block (four blocks of 32): half = fl16(c * s), c exact: the image's byte is c + 128,
+// beside 0x64 it reads 1024 + 128 + c.
+__device__ __forceinline__ void wide_expand_q80(const uint8_t *row, uint32_t h, uint32_t (&r)[64]) {
+  const uint2 sc = *reinterpret_cast<const uint2 *>(row + 256 + 8 * h);  // 4 halves: the scales of blocks 4 h ..
+  const uint32_t scw[2] = {sc.x, sc.y};
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {  // 16 codes a load; two loads a block
+    const uint4 qv = *reinterpret_cast<const uint4 *>(row + 128 * h + 16 * g);
+    const uint32_t w[4] = {qv.x, qv.y, qv.z, qv.w};
+    const uint32_t s2 = (g >> 1) & 1 ? __byte_perm(scw[g >> 2], 0, 0x3232) : __byte_perm(scw[g >> 2], 0, 0x1010);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {  // elements 4 i .. 4 i + 3 of the load: halves (e0, e2) and (e1, e3)
+      r[8 * g + 2 * i] = hmul2_u32(hsub2_u32(__byte_perm(w[i], 0x64646464u, 0x4240), 0x64806480u), s2);
+      r[8 * g + 2 * i + 1] = hmul2_u32(hsub2_u32(__byte_perm(w[i], 0x64646464u, 0x4341), 0x64806480u), s2);
+    }
+  }
+}
+
 template <uint32_t FMT>
 __device__ __forceinline__ void wide_expand(const uint8_t *row, uint32_t h, uint32_t (&r)[64]) {
   if (FMT == SB_FMT_Q4K) wide_expand_q4k(row, h, r);
   else if (FMT == SB_FMT_Q6K) wide_expand_q6k(row, h, r);
+  else if (FMT == SB_FMT_Q80) wide_expand_q80(row, h, r);
   else wide_expand_nvfp4(row, h, r);
 }
 
@@ -727,10 +749,10 @@ __global__ void __launch_bounds__(kWideThreads, 1) linear_wide_kernel(const Wide
 
 static int wide_check(const SbLinearArgs *a, const char *who) {
   SB_REQUIRE(a, "%s: null arguments", who);
-  SB_REQUIRE(a->format == SB_FMT_Q4K || a->format == SB_FMT_Q6K || a->format == SB_FMT_NVFP4,
-             "%s: format %u (the many-row kernel multiplies Q4_K rows, and Q6_K and NVFP4 images)", who, a->format);
+  SB_REQUIRE(a->format == SB_FMT_Q4K || a->format == SB_FMT_Q6K || a->format == SB_FMT_NVFP4 || a->format == SB_FMT_Q80,
+             "%s: format %u (the many-row kernel multiplies Q4_K rows, and Q6_K, Q8_0 and NVFP4 images)", who, a->format);
   SB_REQUIRE((a->format == SB_FMT_Q4K) != ((a->flags & SB_LINEAR_WIDE_IMAGE) != 0),
-             "%s: Q6_K and NVFP4 weights are given as their image (sb_linear_wide_image, SB_LINEAR_WIDE_IMAGE); Q4_K rows as they are", who);
+             "%s: Q6_K, Q8_0 and NVFP4 weights are given as their image (sb_linear_wide_image, SB_LINEAR_WIDE_IMAGE); Q4_K rows as they are", who);
   SB_REQUIRE(a->rows >= 1, "%s: no rows", who);
   SB_REQUIRE(a->k && a->k % 256 == 0 && a->n && a->n % 8 == 0, "%s: k = %u is not a multiple of 256 or n = %u not a multiple of 8", who, a->k, a->n);
   SB_REQUIRE(a->weights && a->out && (a->x || a->prepared), "%s: null weights, out, or neither x nor prepared", who);
@@ -755,6 +777,7 @@ static int wide_set_attributes() {
     SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel<SB_FMT_Q4K>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(wide_smem<SB_FMT_Q4K>())));
     SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel<SB_FMT_Q6K>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(wide_smem<SB_FMT_Q6K>())));
     SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel<SB_FMT_NVFP4>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(wide_smem<SB_FMT_NVFP4>())));
+    SB_CUDA(cudaFuncSetAttribute(linear_wide_kernel<SB_FMT_Q80>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(wide_smem<SB_FMT_Q80>())));
     attr_set[dev] = true;
   }
   return SB_OK;
@@ -842,11 +865,13 @@ __device__ __forceinline__ uint32_t wide_q6k_code(const uint8_t *blk, uint32_t e
 }
 template <uint32_t FMT>
 __global__ void __launch_bounds__(128) wide_image_kernel(const uint8_t *native, uint32_t n, uint32_t nsb, uint8_t *image, float *row_scale) {
-  constexpr uint32_t kNative = FMT == SB_FMT_Q6K ? 210 : 148, kSb = WideFmt<FMT>::kSb;
+  constexpr uint32_t kNative = FMT == SB_FMT_Q6K ? 210 : FMT == SB_FMT_Q80 ? 272 : 148, kSb = WideFmt<FMT>::kSb;  // (Q8_0: eight blocks of 34)
+  constexpr uint32_t kScales = FMT == SB_FMT_Q80 ? 8 : 16;  // scales a super-block
   __shared__ float red_s[4];
   const uint32_t row = blockIdx.x, tid = threadIdx.x;
   const uint8_t *src = native + size_t(row) * nsb * kNative;
-  auto scale_of = [&](const uint8_t *blk, uint32_t i) -> float {  // scale of elements 16 i .. 16 i + 15, fp32 as the format defines it
+  auto scale_of = [&](const uint8_t *blk, uint32_t i) -> float {  // scale i of the super-block, fp32 as the format defines it
+    if (FMT == SB_FMT_Q80) return __half2float(*reinterpret_cast<const __half *>(blk + 34 * i));
     if (FMT == SB_FMT_Q6K) {
       const __half d = *reinterpret_cast<const __half *>(blk + 208);
       return __half2float(d) * float(reinterpret_cast<const int8_t *>(blk + 192)[i]);
@@ -856,8 +881,8 @@ __global__ void __launch_bounds__(128) wide_image_kernel(const uint8_t *native, 
     return wide_e4m3(blk[i]) * g;
   };
   float mx = 0.0f;
-  for (uint32_t u = tid; u < nsb * 16; u += 128) {
-    const float v = fabsf(scale_of(src + (u >> 4) * kNative, u & 15));
+  for (uint32_t u = tid; u < nsb * kScales; u += 128) {
+    const float v = fabsf(scale_of(src + (u / kScales) * kNative, u % kScales));
     if (v <= 3.0e38f) mx = fmaxf(mx, v);
   }
 #pragma unroll
@@ -868,15 +893,19 @@ __global__ void __launch_bounds__(128) wide_image_kernel(const uint8_t *native, 
   int e = 0;
   if (mx > 0.0f) {
     (void)frexpf(mx, &e);  // mx = m 2^e, m in [0.5, 1)
-    e -= FMT == SB_FMT_Q6K ? 9 : 0;
+    e -= FMT == SB_FMT_Q6K ? 9 : FMT == SB_FMT_Q80 ? 7 : 0;  // largest scale to [256, 512) / [64, 128) / [2^13, 2^14) after the 2^14 below
   }
   if (tid == 0) row_scale[row] = ldexpf(1.0f, e);
-  const float down = ldexpf(1.0f, (FMT == SB_FMT_Q6K ? 0 : 14) - e);
+  const float down = ldexpf(1.0f, (FMT == SB_FMT_NVFP4 ? 14 : 0) - e);
   uint8_t *dst_row = image + size_t(row) * nsb * kSb;
   for (uint32_t sb = 0; sb < nsb; ++sb) {
     const uint8_t *blk = src + sb * kNative;
     uint8_t *dst = dst_row + sb * kSb;
-    if (FMT == SB_FMT_Q6K) {
+    if (FMT == SB_FMT_Q80) {
+      // codes + 128 in element order, then the eight blocks' scales
+      for (uint32_t el = tid; el < 256; el += 128) dst[el] = uint8_t(reinterpret_cast<const int8_t *>(blk + 34 * (el >> 5) + 2)[el & 31] + 128);
+      if (tid < 8) reinterpret_cast<__half *>(dst + 256)[tid] = __float2half_rn(scale_of(blk, tid) * down);
+    } else if (FMT == SB_FMT_Q6K) {
       // ql': byte i of pair-block pb (64 elements from 64 pb) = low nibbles of its first 32 elements | of its next 32 << 4
       {
         const uint32_t pb = tid >> 5, i = tid & 31;
@@ -923,21 +952,23 @@ static uint32_t wide_splits(uint32_t n, uint32_t k, int sm_count) {
 extern "C" uint32_t sb_linear_wide_splits(uint32_t n, uint32_t k) { return ctx().ready ? wide_splits(n, k, ctx().sm_count) : 0; }
 
 static uint32_t wide_sb_bytes(uint32_t format) {
-  return format == SB_FMT_Q4K ? WideFmt<SB_FMT_Q4K>::kSb : format == SB_FMT_Q6K ? WideFmt<SB_FMT_Q6K>::kSb : format == SB_FMT_NVFP4 ? WideFmt<SB_FMT_NVFP4>::kSb : 0;
+  return format == SB_FMT_Q4K ? WideFmt<SB_FMT_Q4K>::kSb : format == SB_FMT_Q6K ? WideFmt<SB_FMT_Q6K>::kSb : format == SB_FMT_NVFP4 ? WideFmt<SB_FMT_NVFP4>::kSb
+       : format == SB_FMT_Q80 ? WideFmt<SB_FMT_Q80>::kSb : 0;
 }
 extern "C" uint64_t sb_linear_wide_image_bytes(uint32_t format, uint32_t n, uint32_t k) {
-  if ((format != SB_FMT_Q6K && format != SB_FMT_NVFP4) || !n || !k || k % 256) return 0;
+  if ((format != SB_FMT_Q6K && format != SB_FMT_NVFP4 && format != SB_FMT_Q80) || !n || !k || k % 256) return 0;
   return uint64_t(n) * (k / 256) * wide_sb_bytes(format) + uint64_t(n) * 4;  // the rows, then a scale per row
 }
 extern "C" int sb_linear_wide_image(void *stream, uint32_t format, const void *weights, uint32_t n, uint32_t k, void *image_out) {
   SB_NEED_DEVICE();
-  SB_REQUIRE(format == SB_FMT_Q6K || format == SB_FMT_NVFP4, "sb_linear_wide_image: format %u (Q6_K and NVFP4 rows have images; Q4_K rows are read as they are)", format);
+  SB_REQUIRE(format == SB_FMT_Q6K || format == SB_FMT_NVFP4 || format == SB_FMT_Q80, "sb_linear_wide_image: format %u (Q6_K, Q8_0 and NVFP4 rows have images; Q4_K rows are read as they are)", format);
   SB_REQUIRE(weights && image_out && n && k && k % 256 == 0, "sb_linear_wide_image: null pointer, no rows or k = %u not a multiple of 256", k);
-  SB_REQUIRE((reinterpret_cast<uintptr_t>(image_out) & 15) == 0 && (reinterpret_cast<uintptr_t>(weights) & 3) == 0, "sb_linear_wide_image: the image must be 16-byte aligned, the rows 4-byte");
+  SB_REQUIRE((reinterpret_cast<uintptr_t>(image_out) & 15) == 0 && (reinterpret_cast<uintptr_t>(weights) & 1) == 0, "sb_linear_wide_image: the image must be 16-byte aligned, the rows 2-byte");
   const uint32_t nsb = k / 256;
   uint8_t *image = static_cast<uint8_t *>(image_out);
   float *row_scale = reinterpret_cast<float *>(image + size_t(n) * nsb * wide_sb_bytes(format));
   if (format == SB_FMT_Q6K) wide_image_kernel<SB_FMT_Q6K><<<n, 128, 0, as_stream(stream)>>>(static_cast<const uint8_t *>(weights), n, nsb, image, row_scale);
+  else if (format == SB_FMT_Q80) wide_image_kernel<SB_FMT_Q80><<<n, 128, 0, as_stream(stream)>>>(static_cast<const uint8_t *>(weights), n, nsb, image, row_scale);
   else wide_image_kernel<SB_FMT_NVFP4><<<n, 128, 0, as_stream(stream)>>>(static_cast<const uint8_t *>(weights), n, nsb, image, row_scale);
   SB_CUDA(cudaGetLastError());
   return SB_OK;
@@ -1048,7 +1079,8 @@ extern "C" int sb_linear_wide(void *stream, const SbLinearArgs *a) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(std::min<uint32_t>(p.items, uint32_t(c.sm_count)));
     cfg.blockDim = dim3(kWideThreads);
-    cfg.dynamicSmemBytes = a->format == SB_FMT_Q4K ? wide_smem<SB_FMT_Q4K>() : a->format == SB_FMT_Q6K ? wide_smem<SB_FMT_Q6K>() : wide_smem<SB_FMT_NVFP4>();
+    cfg.dynamicSmemBytes = a->format == SB_FMT_Q4K ? wide_smem<SB_FMT_Q4K>() : a->format == SB_FMT_Q6K ? wide_smem<SB_FMT_Q6K>()
+                         : a->format == SB_FMT_Q80 ? wide_smem<SB_FMT_Q80>() : wide_smem<SB_FMT_NVFP4>();
     p.row_scale[0] = row_scale[0], p.row_scale[1] = row_scale[1];
     cfg.stream = as_stream(stream);
     cudaLaunchAttribute attr[1];
@@ -1057,6 +1089,7 @@ extern "C" int sb_linear_wide(void *stream, const SbLinearArgs *a) {
     cfg.attrs = attr, cfg.numAttrs = (a->flags & SB_LINEAR_PDL) ? 1 : 0;
     if (a->format == SB_FMT_Q4K) SB_CUDA(cudaLaunchKernelEx(&cfg, linear_wide_kernel<SB_FMT_Q4K>, p, maps));
     else if (a->format == SB_FMT_Q6K) SB_CUDA(cudaLaunchKernelEx(&cfg, linear_wide_kernel<SB_FMT_Q6K>, p, maps));
+    else if (a->format == SB_FMT_Q80) SB_CUDA(cudaLaunchKernelEx(&cfg, linear_wide_kernel<SB_FMT_Q80>, p, maps));
     else SB_CUDA(cudaLaunchKernelEx(&cfg, linear_wide_kernel<SB_FMT_NVFP4>, p, maps));
   }
   return SB_OK;

@@ -427,7 +427,7 @@ def test_lanes_reject_what_they_do_not_step():
     from splash_b200 import lib, target
     lib.init(0)
     with pytest.raises(lib.SbError):
-        target.Target(**dict(target.TINY, fmt_down=lib.FMT_Q80, lanes=4))     # Q8_0 rows have no many-row kernel
+        target.Target(**dict(target.TINY, fmt_down=lib.FMT_BF16, lanes=4))    # plain rows are not a projection format
     with pytest.raises(lib.SbError):
         target.Target(**dict(target.TINY, lanes=33))
     t = target.Target(**dict(target.TINY, lanes=2))

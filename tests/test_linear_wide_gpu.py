@@ -169,10 +169,10 @@ def run_image(lib, fmt, img, n, k, X, rows, img2=None, **kw):
     return od.to_numpy(np.float32 if f32 else np.uint16, (rows, n))
 
 
-@pytest.mark.parametrize("fmt", [4, 37])
+@pytest.mark.parametrize("fmt", [4, 6, 37])
 @pytest.mark.parametrize("n,k,rows", [(512, 1024, 128), (392, 2816, 17), (256, 5120, 64), (128, 17408, 48), (640, 2048, 200)])
 def test_wide_q6k_and_nvfp4_images(fmt, n, k, rows):
-    """Q6_K and NVFP4 rows through their images: the weight's half is fl16(code * fl16(scale)), two roundings, so the
+    """Q6_K, Q8_0 and NVFP4 rows through their images: the weight's half is fl16(code * fl16(scale)), two roundings, so the
     middle term of the reference's bound for half-rounded weights is taken twice."""
     lib = _setup()
     W = qf.realistic(fmt, n, k, seed=n + k + fmt)
@@ -184,7 +184,7 @@ def test_wide_q6k_and_nvfp4_images(fmt, n, k, rows):
     check_interval(got, v - e, v + e)
     got32 = run_image(lib, fmt, img, n, k, X, rows, out_f32=True)
     rel = np.abs(got32 - v) / np.maximum(np.abs(v), np.abs(v).mean())
-    assert rel.max() < (2e-3 if fmt == 4 else 4e-3) and np.median(rel) < 4e-4    # (e2m1 codes: heavier tails than the 6-bit codes)
+    assert rel.max() < (4e-3 if fmt == 37 else 2e-3) and np.median(rel) < 4e-4    # (e2m1 codes: heavier tails than the 6- and 8-bit codes)
     assert np.array_equal(got, ol.f2bf(got32))
 
 
@@ -249,6 +249,6 @@ def test_wide_rejects_what_it_does_not_multiply():
     with pytest.raises(lib.SbError):
         lib.linear(d.ptr, d.ptr, d.ptr, lib.FMT_Q4K, 256, 1024, 64, flags=lib.LINEAR_WIDE_IMAGE)   # Q4_K has no image
     with pytest.raises(lib.SbError):
-        lib.linear(d.ptr, d.ptr, d.ptr, lib.FMT_Q80, 256, 1024, 64)
+        lib.linear(d.ptr, d.ptr, d.ptr, lib.FMT_Q80, 256, 1024, 64)       # Q8_0 rows as they are: likewise
     with pytest.raises(lib.SbError):
         lib.linear(d.ptr, d.ptr, d.ptr, lib.FMT_Q4K, 256, 1000, 64)       # k not whole super-blocks
