@@ -164,7 +164,7 @@ typedef struct SbLinearArgs {
 enum {
   SB_LINEAR_PDL = 1, /* launch with programmatic stream serialization: the weight stream starts while the
                         producer of x drains */
-  SB_LINEAR_WIDE_IMAGE = 4, /* sb_linear_wide: weights / weights2 point to images made by sb_linear_wide_image (Q6_K, NVFP4) */
+  SB_LINEAR_WIDE_IMAGE = 4, /* sb_linear_wide: weights / weights2 point to images made by sb_linear_wide_image (Q6_K, Q8_0, NVFP4) */
   SB_LINEAR_TCGEN05 = 2 /* Q4_K only: multiply on the tcgen05 tensor cores (weights expanded straight into tensor
                            memory, 128-row tiles) instead of warp-level MMA. Give the same flag to
                            sb_linear_prepare: the kernel reads its activations in another tile order. Same
@@ -210,11 +210,11 @@ SB_API int sb_linear(void *stream, const SbLinearArgs *args);
 SB_API uint64_t sb_linear_wide_prepared_bytes(uint32_t rows, uint32_t k);
 SB_API int sb_linear_wide_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride, const void *norm_weight,
                                   void *prepared_out, uint32_t flags);
-/* Q6_K and NVFP4 rows are not 16-byte multiples and their codes are spread over bit planes, so the many-row kernel reads an
+/* Q6_K, Q8_0 and NVFP4 rows are not 16-byte multiples (and Q6_K's codes are spread over bit planes), so the many-row kernel reads an
  * image of them, made once when the weights are loaded (as the reference prepares its GGUF tensors when it loads them,
  * runtime/model/GgufPreparation.hpp): per super-block the same codes re-ordered for the expansion and the block's scales
  * already multiplied out and rounded to half with a power of two per row taken out (Q6_K 224 bytes: d * sc; NVFP4 160
- * bytes: e4m3 * g), then one fp32 power of two per row. The weight's half is fl16(code * fl16(scale)): two roundings.
+ * bytes: e4m3 * g; Q8_0 272 bytes: eight blocks' codes + 128 and their d), then one fp32 power of two per row. The weight's half is fl16(code * fl16(scale)): two roundings.
  * sb_linear_wide takes the image as `weights` with SB_LINEAR_WIDE_IMAGE. */
 SB_API uint64_t sb_linear_wide_image_bytes(uint32_t format, uint32_t n, uint32_t k);
 SB_API int sb_linear_wide_image(void *stream, uint32_t format, const void *weights, uint32_t n, uint32_t k, void *image_out);
