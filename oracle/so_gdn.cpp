@@ -13,7 +13,10 @@
 // step's tape. The state after the block is not stored: the next step folds what was accepted.
 // Rounding points follow the kernel (bf16 where it rounds, fp32 sums); sums run in index order, so
 // tests compare with the reference's gates (state 1e-4 relative, hidden 3 bf16 ulp), not bitwise.
-// No vectors of this kernel are stored in the reference: "parity unpinned".
+// No vectors of this kernel are stored in the reference; parity is pinned against the fp64 models of the
+// reference's kernel test (dev/tests/engine/gdn_decode_metal_test.mm:371-407, 474-522) compiled into
+// oracle/_ref (oracle/ref_models_shim.cpp, tests/test_oracle_ref_models.py); trees are held to chains of
+// their paths (tests/test_oracle_ops.py).
 #include "so_common.h"
 
 #include <algorithm>

@@ -17,8 +17,11 @@
 //   acceptance         runtime/metal/kernels/decode/sampling.metal:2044-2083
 //   path commit        runtime/metal/kernels/shared/kv_path_commit.metal:21-46
 // Parity of the INT8 quantizer is pinned against the reference's own CPU code through oracle/_ref
-// (tests/test_oracle_ops.py); attention, selection and acceptance have no stored vectors in the
-// reference ("parity unpinned" for those: tolerance gates and invariants only).
+// (tests/test_oracle_ops.py), and attention against the reference's fp64 model compiled from its
+// test file, as is the sampled selection (distribution cuts, child tests, residual draw) against the
+// fp64 recursion of the reference's sampling test (oracle/ref_models_shim.cpp,
+// tests/test_oracle_ref_models.py). Greedy selection and acceptance have neither stored vectors nor a
+// host model in the reference ("parity unpinned" for those: tolerance gates and invariants only).
 #include "so_common.h"
 
 #include <algorithm>
