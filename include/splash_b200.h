@@ -540,11 +540,17 @@ enum {
   SB_TARGET_KEEP_PENDING = 8, /* without SB_TARGET_ADVANCE: the lane's pending GDN rows (`pending_rows`, sb_target_tensor) stay
                             as they are instead of being cleared, so every such step folds the same rows again: a held
                             lane that still does a committing cycle's fold work (steady-state timing). */
-  SB_TARGET_DRAWS = 16   /* sampled rows (temperature > 0) take their children from the target's `candidates` (u32 [16][16]),
+  SB_TARGET_DRAWS = 16,  /* sampled rows (temperature > 0) take their children from the target's `candidates` (u32 [16][16]),
                             `candidate_q` (fp32 [16][16]) and `draws` (u8 [16][4]) buffers, which the host (the draft side)
                             fills before the step: recursive rejection sampling over up to 4 drawn children a row
                             (SbSampleArgs). A sampled tree block requires it; a sampled chain without it tests the next row's
                             input token with q = 1. */
+  SB_TARGET_PROMPT = 32  /* with SB_TARGET_ADVANCE, chains only: the block's rows are tokens of the prompt (row 0 the first of them
+                            that the target has not seen), and every row is committed whatever the target selected: results =
+                            {rows, rows - 1, all rows}, the cache keeps the rows' K/V, the next step folds all of them into the
+                            GDN state. `selected` row rows - 1 is the target's token after the block. A prompt enters the cache
+                            this way, 16 tokens a step and lane, through the verify step's own kernels (the reference's prefill
+                            path with its 128-row tiles, runtime/metal/kernels/prefill/, is a separate one). */
 };
 
 /* ---- MoE routing ----

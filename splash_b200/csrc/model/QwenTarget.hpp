@@ -121,6 +121,7 @@ class QwenTarget {
   bool imagesStale = true;
   // Measurements with synthetic routing: the blocks route by the host's `moe_scores` instead of their router's scores.
   bool routerScoresGiven = false;
+  bool promptBlock = false;  // the step being encoded commits every row of its block (a block of prompt tokens)
   void buildImages(void *stream) {
     if (wide_)
       for (LayerWeights &w : layers_)
@@ -358,7 +359,8 @@ inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) co
 void launchStepBegin(CommandGraph &graph, const Buffer &committed, const Buffer &tree, const Buffer &positions, uint32_t rows, bool treeGiven,
                      uint32_t lanes = 1);
 // (with a tensor-parallel group the step's end also advances the group's exchange count by `exchanges`)
-// advance: 0 the lane holds its position and its pending rows are cleared, 1 it commits, 2 it holds and keeps them
+// advance: 0 the lane holds its position and its pending rows are cleared, 1 it commits, 2 it holds and keeps them,
+// 3 | rows << 8 it commits all `rows` rows of its block
 void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &committed, const Buffer &pendingRows, const Buffer &pendingPath,
                    uint32_t advance, void *tpGroup, uint32_t exchanges, uint32_t lanes = 1);
 
@@ -477,7 +479,7 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
     for (LayerWeights &w : layers_)
       if (w.attention) PagedAttention::addPathCommit(graph, kv_, w.pages, pageTable_, committedHost, pathMask, &committed);
   }
-  launchStepEnd(graph, results, committed, pendingRows, pendingPath, advance ? 1u : keepPending ? 2u : 0u, tp_ ? tp_->group() : nullptr, exchange);
+  launchStepEnd(graph, results, committed, pendingRows, pendingPath, promptBlock ? 3u | rows << 8 : advance ? 1u : keepPending ? 2u : 0u, tp_ ? tp_->group() : nullptr, exchange);
 }
 
 // A step of several lanes (SbTargetConfig.lanes): every lane a chain of `rows` rows in its 16 row slots, the projections
@@ -583,7 +585,7 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
         check(sb_kv_path_commit_lanes(graph.stream, &cache, pageTable_.as<uint32_t>(), pagesPerLane_, committed.as<uint32_t>(), results.as<uint32_t>() + 2, 4, L));
         ++graph.launches;
       }
-  launchStepEnd(graph, results, committed, pendingRows, pendingPath, advance ? 1u : keepPending ? 2u : 0u, nullptr, 0, L);
+  launchStepEnd(graph, results, committed, pendingRows, pendingPath, promptBlock ? 3u | rows << 8 : advance ? 1u : keepPending ? 2u : 0u, nullptr, 0, L);
 }
 
 }  // namespace splash::b200::model

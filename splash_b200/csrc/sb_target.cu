@@ -26,19 +26,26 @@ __global__ void step_begin_kernel(const uint32_t *committed, uint2 *tree, uint32
   positions[r] = committed[lane] + (tree_given ? tree[r].y >> 16 : r);
 }
 // The lane's commit: the retained rows become history; the next step folds them into the GDN state.
-__global__ void step_end_kernel(const uint32_t *results, uint32_t *committed, uint32_t *pending_rows, uint32_t *pending_path, uint32_t advance,
+// advance: 0 hold and clear the pending rows, 1 commit what acceptance retained, 2 hold and keep the pending rows,
+// 3 | rows << 8 commit every row of the block whatever was selected (a block of prompt tokens).
+__global__ void step_end_kernel(uint32_t *results, uint32_t *committed, uint32_t *pending_rows, uint32_t *pending_path, uint32_t advance,
                                 uint32_t *tp_epoch, uint32_t tp_exchanges, uint32_t lanes) {
   pdl_wait();
   if (threadIdx.x < lanes) {  // (a thread per lane)
-    const uint32_t lane = threadIdx.x;
+    const uint32_t lane = threadIdx.x, mode = advance & 0xffu, rows = advance >> 8;
     // The next step's exchanges are numbered after this step's. Their kernels read the count when they start, and
     // kernels may start before the ones ahead of them complete: dependents are let go only after the count has moved.
     if (tp_epoch && lane == 0) *tp_epoch += tp_exchanges;
-    if (advance == 1) {
+    if (mode == 3) {
+      results[4 * lane] = rows, results[4 * lane + 1] = rows - 1, results[4 * lane + 2] = (2u << (rows - 1)) - 1u;
+      committed[lane] += rows;
+      pending_rows[lane] = rows;
+      pending_path[lane] = 0;  // (the tape's first `rows` rows)
+    } else if (mode == 1) {
       committed[lane] += results[4 * lane];
       pending_rows[lane] = results[4 * lane];
       pending_path[lane] = results[4 * lane + 2];
-    } else if (advance == 0) {
+    } else if (mode == 0) {
       pending_rows[lane] = 0;
       pending_path[lane] = 0;
     }  // (2: the lane stays where it is and keeps its pending rows: every such step folds the same rows again)
@@ -156,7 +163,7 @@ void launchStepEnd(CommandGraph &graph, const Buffer &results, const Buffer &com
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = graph.pdl ? 1 : 0;
-  if (cudaLaunchKernelEx(&cfg, sb::step_end_kernel, static_cast<const uint32_t *>(results.as<uint32_t>()), committed.as<uint32_t>(),
+  if (cudaLaunchKernelEx(&cfg, sb::step_end_kernel, results.as<uint32_t>(), committed.as<uint32_t>(),
                          pendingRows.as<uint32_t>(), pendingPath.as<uint32_t>(), advance, sb::tp_epoch_word(tpGroup), exchanges, lanes) != cudaSuccess)
     throw BackendError(SB_ERR_CUDA, "step_end launch failed");
   ++graph.launches;
@@ -393,7 +400,10 @@ static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float tempera
   QwenTarget &m = *t->model;
   const bool advance = (flags & SB_TARGET_ADVANCE) != 0, tree = (flags & SB_TARGET_TREE) != 0;
   const bool keep = !advance && (flags & SB_TARGET_KEEP_PENDING) != 0, draws = (flags & SB_TARGET_DRAWS) != 0;
+  const bool prompt = (flags & SB_TARGET_PROMPT) != 0;
+  SB_REQUIRE(!prompt || (advance && !tree), "sb_target_step: SB_TARGET_PROMPT commits a chain: it needs SB_TARGET_ADVANCE and excludes SB_TARGET_TREE");
   const uint32_t parity = m.step & 1;
+  m.promptBlock = prompt;
   return guarded([&] {
     if (m.imagesStale) m.buildImages(stream);
     if (flags & SB_TARGET_GRAPH) {
@@ -402,7 +412,7 @@ static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float tempera
       const uint32_t bound = std::min(m.config().max_context, (m.committedHost / 1024 + 2) * 1024);
       uint32_t tbits;
       memcpy(&tbits, &temperature, 4);
-      const auto key = std::make_tuple(rows, tbits, parity, uint32_t(advance) | (uint32_t(tree) << 1) | (uint32_t(keep) << 2) | (uint32_t(draws) << 3), bound);
+      const auto key = std::make_tuple(rows, tbits, parity, uint32_t(advance) | (uint32_t(tree) << 1) | (uint32_t(keep) << 2) | (uint32_t(draws) << 3) | (uint32_t(prompt) << 4), bound);
       auto it = t->graphs.find(key);
       if (it == t->graphs.end()) {
         const uint32_t saved = m.committedHost;

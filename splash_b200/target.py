@@ -6,7 +6,7 @@ import numpy as np
 from . import lib
 
 _P, _U, _F = ctypes.c_void_p, ctypes.c_uint32, ctypes.c_float
-ADVANCE, GRAPH, TREE, KEEP_PENDING, DRAWS = 1, 2, 4, 8, 16
+ADVANCE, GRAPH, TREE, KEEP_PENDING, DRAWS, PROMPT = 1, 2, 4, 8, 16, 32
 
 
 class SbTargetConfig(ctypes.Structure):

@@ -111,10 +111,11 @@ def linear(o, fmt, W, n, k, X, rows, epilogue=0, aux=None, out_f32=False, W2=Non
 
 
 def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True, mutate=True, tree=None, penalties=None, penalty_words=None,
-                draws=None):
+                draws=None, prompt=False):
     """One verify step of a chain, or of the tree whose rows `tree` holds (uint32 [rows, 2]: ancestors, parent | depth << 16).
     draws = (candidate ids u32 [rows, 16], draft probabilities f32 [rows, 16], drawn children u8 [rows, 4]): sampled rows
-    select by recursive rejection sampling over these children. Returns dict(logits, selected, retained, accepted, mask, tokens)."""
+    select by recursive rejection sampling over these children. prompt: the rows are prompt tokens, all committed whatever
+    was selected. Returns dict(logits, selected, retained, accepted, mask, tokens)."""
     o = ol.bind_ops(ol.load())
     rows = len(tokens)
     H, D, I, V = cfg["hidden"], cfg["head_dim"], cfg["intermediate"], cfg["vocab"]
@@ -206,6 +207,10 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
     out_tokens = selected.copy()
     res = np.zeros(3, np.uint32)
     o.so_accept(P(tokens), P(rows_tree), P(out_tokens), rows, 16, None, 0, P(res[0:1]), P(res[1:2]), P(res[2:3]))
+    if prompt:
+        assert advance and tree is None
+        res[:] = (rows, rows - 1, (2 << (rows - 1)) - 1)
+        out_tokens = selected.copy()
     if mutate:
         s.update(new_state)
         s["step"] += 1
@@ -218,6 +223,8 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
             s["committed"] += int(res[0])
             s["pending_rows"] = int(res[0])
             s["pending_path"] = int(res[2]) if tree is not None else 0
+            if prompt:
+                s["pending_path"] = 0
         else:
             s["pending_rows"] = 0
             s["pending_path"] = 0

@@ -329,6 +329,38 @@ def test_tiny_moe_model_of_three_lanes_matches_three_oracle_lanes():
     assert compared >= 4, compared
 
 
+def test_prompt_blocks_of_two_lanes_match_two_oracle_lanes():
+    """Two lanes take prompt blocks (every row committed) from different positions, then one verify step."""
+    positions = np.array([0, 700], np.uint32)
+    lib, target, t, cfg, w, states = build_lanes(2, positions, seed=6)
+    rng = np.random.default_rng(12)
+
+    def close(i, want, logits):
+        mine = logits[16 * i:16 * i + len(want["logits"])]
+        scale = np.abs(want["logits"]).max()
+        err = np.abs(mine - want["logits"])
+        assert err.max() <= 2e-2 * scale and np.median(err) <= 2e-3 * scale, i
+
+    last = [0, 0]
+    for rows in (16, 16, 5):
+        blocks = rng.integers(0, cfg["vocab"], (2, rows)).astype(np.uint32)
+        wants = [mo.verify_step(cfg, w, states[i], blocks[i], advance=True, prompt=True) for i in range(2)]
+        got = t.verify_lanes(blocks, flags=target.ADVANCE | target.PROMPT)
+        assert lib.device_status() == 0
+        logits = t.download(-1, "logits", np.float32, (32, cfg["vocab"]))
+        for i in range(2):
+            assert got[i][1:] == (rows, rows - 1, (1 << rows) - 1)
+            close(i, wants[i], logits)
+            last[i] = int(got[i][0][rows - 1])
+    assert np.array_equal(t.download(-1, "committed", np.uint32, (2,)), positions + 37)
+    blocks = np.stack([mo.draft_chain(cfg, w, states[i], last[i], rows=16, p_match=0.6, seed=i) for i in range(2)])
+    wants = [mo.verify_step(cfg, w, states[i], blocks[i], advance=True) for i in range(2)]
+    t.verify_lanes(blocks, flags=target.ADVANCE)
+    logits = t.download(-1, "logits", np.float32, (32, cfg["vocab"]))
+    for i in range(2):
+        close(i, wants[i], logits)
+
+
 def _tree_rows(parent):
     t = np.zeros((len(parent), 2), np.uint32)
     for r in range(len(parent)):

@@ -250,3 +250,49 @@ def test_tiny_moe_model_steps_match_oracle():
         compared += 1
         token = int(got_tokens[-1])
     assert compared >= 1
+
+
+@pytest.mark.parametrize("flags_name", ["eager", "graph"])
+def test_tiny_model_prompt_blocks_then_verify_steps_match_oracle(flags_name):
+    """A prompt enters an empty cache as blocks whose rows are all committed (SB_TARGET_PROMPT), the last one ragged;
+    verify steps follow from the state the blocks left. Every step's logits against the oracle's."""
+    lib, target, t, cfg, w, s = build(seed=4, committed=0)
+    extra = target.GRAPH if flags_name == "graph" else 0
+    rng = np.random.default_rng(8)
+    prompt = rng.integers(0, cfg["vocab"], 16 * 3 + 7).astype(np.uint32)
+
+    def close(want):
+        logits = t.download(-1, "logits", np.float32, (16, cfg["vocab"]))[:len(want["logits"])]
+        scale = np.abs(want["logits"]).max()
+        assert np.abs(logits - want["logits"]).max() <= 2e-2 * scale
+        assert np.median(np.abs(logits - want["logits"])) <= 2e-3 * scale
+
+    token = None
+    for at in range(0, len(prompt), 16):
+        block = prompt[at:at + 16]
+        want = mo.verify_step(cfg, w, s, block, advance=True, prompt=True)
+        got_tokens, retained, accepted, mask = t.verify(block, flags=target.ADVANCE | target.PROMPT | extra)
+        assert lib.device_status() == 0
+        assert (retained, accepted, mask) == (len(block), len(block) - 1, (1 << len(block)) - 1)
+        close(want)
+        top2 = np.sort(want["logits"][len(block) - 1])[-2:]
+        token = int(got_tokens[len(block) - 1])
+        if top2[1] - top2[0] > 1e-2:
+            assert token == int(want["selected"][len(block) - 1])
+    assert s["committed"] == len(prompt)
+    assert int(t.download(-1, "committed", np.uint32, (1,))[0]) == len(prompt)
+    for step in range(2):
+        tokens = mo.draft_chain(cfg, w, s, token, rows=16, seed=step)
+        want = mo.verify_step(cfg, w, s, tokens, advance=True)
+        got_tokens, retained, accepted, mask = t.verify(tokens, flags=target.ADVANCE | extra)
+        close(want)
+        top2 = np.sort(want["logits"], axis=1)[:, -2:]
+        if ((top2[:, 1] - top2[:, 0]) > 1e-2)[:want["retained"]].all():
+            assert retained == want["retained"] and np.array_equal(got_tokens, want["tokens"])
+        else:
+            s["committed"] += retained - want["retained"]
+            s["pending_rows"] = retained
+        token = int(got_tokens[-1])
+    # a tree block cannot be a prompt block
+    with pytest.raises(Exception):
+        t.verify(prompt[:4], flags=target.ADVANCE | target.PROMPT | target.TREE)
