@@ -491,6 +491,25 @@ typedef struct SbAcceptArgs {
 } SbAcceptArgs;
 SB_API int sb_accept(void *stream, const SbAcceptArgs *args);
 
+/* Selection and acceptance in one launch (the reference's verify selection ends in its acceptance the same way,
+ * runtime/metal/kernels/decode/sampling.metal:1896-2083: the rows select, then the lane's path is walked): a block per
+ * row selects as sb_sample_verify does; the block of a lane that finishes last walks the accepted path as sb_accept does
+ * and, with `committed` given, commits the lane: advance 0 clears the lane's pending rows, 1 adds the retained rows to
+ * committed[lane] and leaves them (and the path's row mask) pending for the next step's GDN fold, 2 leaves everything,
+ * 3 | rows << 8 commits every row (SB_TARGET_PROMPT). accept.input_tokens = sample.input_tokens, accept.tokens =
+ * sample.selected, same rows and lanes. tickets: device u32 [lanes], zero before the first call; the kernel returns
+ * them to zero. Results equal those of the two separate calls bit for bit. */
+typedef struct SbSelectAcceptArgs {
+  SbSampleArgs sample;
+  SbAcceptArgs accept;
+  uint32_t *tickets;      /* device u32 [lanes] */
+  uint32_t *committed;    /* device u32 [lanes] or NULL: no commit */
+  uint32_t *pending_rows; /* device u32 [lanes] */
+  uint32_t *pending_path; /* device u32 [lanes] */
+  uint32_t advance, reserved;
+} SbSelectAcceptArgs;
+SB_API int sb_select_accept(void *stream, const SbSelectAcceptArgs *args);
+
 /* ---- the target model's verify step ----
  * The layer loop and the step's commit, as the reference's QwenTarget::addPrefillLayers /
  * encodeTargetDecodeForward / encodeVerifyCommit build them (runtime/model/QwenTarget.hpp:618-652,

@@ -121,6 +121,7 @@ class QwenTarget {
   bool imagesStale = true;
   // Measurements with synthetic routing: the blocks route by the host's `moe_scores` instead of their router's scores.
   bool routerScoresGiven = false;
+  Buffer tickets;  // u32 [64]: the selection launch's count of finished rows a lane (zero between launches; zeroed at creation)
   bool promptBlock = false;  // the step being encoded commits every row of its block (a block of prompt tokens)
   void buildImages(void *stream) {
     if (wide_)
@@ -293,6 +294,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   sine = Buffer::allocate(R * std::max(1u, c.rotary_pairs) * 4);
   pageTable_ = Buffer::allocate(size_t(pages) * 4);
   sampleWorkspace_ = Buffer::allocate(ops::Sampling::workspace(uint32_t(R), c.vocab));
+  tickets = Buffer::allocate(64 * 4);
   penaltyWords = Buffer::allocate(size_t(c.vocab) * 4 * L);
   candidates = Buffer::allocate(R * 16 * 4), candidateQ = Buffer::allocate(R * 16 * 4), draws = Buffer::allocate(R * 4);
   if (c.moe_experts) {
@@ -468,10 +470,14 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   else if (treeGiven && temperature > 0.0f)
     throw std::invalid_argument("QwenTarget::encodeVerify: a sampled tree block needs the draft's candidates and draws (SB_TARGET_DRAWS)");
   Sampling::addPenalties(graph, penalties, sb, penaltyWords, tree, rows, c.vocab);  // (nothing when the penalties are off)
-  Sampling::addVerify(graph, SamplingPolicy{temperature}, sb, rows, c.vocab);
   AcceptanceBuffers ab;
   ab.inputTokens = tokens, ab.treeRows = tree, ab.outputTokens = selected, ab.results = results;
-  Sampling::addAcceptance(graph, ab, rows, kVerifyRows);
+  // One launch selects, accepts and, where nothing has to come between (a tree's path commit reads the lane's position
+  // before it moves; a tensor-parallel step's end also numbers the next step's exchanges), ends the step.
+  const uint32_t stepAdvance = promptBlock ? 3u | rows << 8 : advance ? 1u : keepPending ? 2u : 0u;
+  const bool endsHere = !tp_ && !(treeGiven && advance);
+  const Sampling::LaneCommit lc{committed, pendingRows, pendingPath, stepAdvance};
+  Sampling::addVerifyAndAcceptance(graph, SamplingPolicy{temperature}, sb, ab, rows, c.vocab, kVerifyRows, 1, tickets, endsHere ? &lc : nullptr);
   if (tp_ && exchange != exchangesPerStep()) throw std::logic_error("QwenTarget::encodeVerify: exchange count");
   // The accepted path's KV rows move from their rows' slots to their depths' (a chain's are there already).
   if (treeGiven && advance) {
@@ -479,7 +485,7 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
     for (LayerWeights &w : layers_)
       if (w.attention) PagedAttention::addPathCommit(graph, kv_, w.pages, pageTable_, committedHost, pathMask, &committed);
   }
-  launchStepEnd(graph, results, committed, pendingRows, pendingPath, promptBlock ? 3u | rows << 8 : advance ? 1u : keepPending ? 2u : 0u, tp_ ? tp_->group() : nullptr, exchange);
+  if (!endsHere) launchStepEnd(graph, results, committed, pendingRows, pendingPath, stepAdvance, tp_ ? tp_->group() : nullptr, exchange);
 }
 
 // A step of several lanes (SbTargetConfig.lanes): every lane a chain of `rows` rows in its 16 row slots, the projections
@@ -573,10 +579,18 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
   SbSampleArgs sa{logits.as<float>(), tokens.as<uint32_t>(), temperature > 0.0f ? uniforms.as<float>() : nullptr, selected.as<uint32_t>(),
                   sampleWorkspace_.as<float>(), rows, c.vocab, c.vocab, temperature, 0.0f, 0, 1.0f, nullptr, nullptr, nullptr, nullptr, L, 0};
   if (drawsGiven && temperature > 0.0f) sa.candidate_ids = candidates.as<uint32_t>(), sa.candidate_q = candidateQ.as<float>(), sa.draws = draws.as<uint8_t>();
-  check(sb_sample_verify(graph.stream, &sa));
-  SbAcceptArgs ac{tokens.as<uint32_t>(), tree.as(), selected.as<uint32_t>(), results.as<uint32_t>(), nullptr, rows, kVerifyRows, 0, L};
-  check(sb_accept(graph.stream, &ac));
-  graph.launches += 2;
+  const uint32_t stepAdvance = promptBlock ? 3u | rows << 8 : advance ? 1u : keepPending ? 2u : 0u;
+  const bool endsHere = !(treeGiven && advance);  // (a tree's path commit reads the lanes' positions before they move)
+  SbSelectAcceptArgs fused{};
+  fused.sample = sa;
+  fused.accept = SbAcceptArgs{tokens.as<uint32_t>(), tree.as(), selected.as<uint32_t>(), results.as<uint32_t>(), nullptr, rows, kVerifyRows, 0, L};
+  fused.tickets = tickets.as<uint32_t>();
+  if (endsHere) {
+    fused.committed = committed.as<uint32_t>(), fused.pending_rows = pendingRows.as<uint32_t>(), fused.pending_path = pendingPath.as<uint32_t>();
+    fused.advance = stepAdvance;
+  }
+  check(sb_select_accept(graph.stream, &fused));
+  ++graph.launches;
   // The accepted paths' KV rows move from their rows' slots to their depths' (a chain's are there already).
   if (treeGiven && advance)
     for (LayerWeights &w : layers_)
@@ -585,7 +599,7 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
         check(sb_kv_path_commit_lanes(graph.stream, &cache, pageTable_.as<uint32_t>(), pagesPerLane_, committed.as<uint32_t>(), results.as<uint32_t>() + 2, 4, L));
         ++graph.launches;
       }
-  launchStepEnd(graph, results, committed, pendingRows, pendingPath, promptBlock ? 3u | rows << 8 : advance ? 1u : keepPending ? 2u : 0u, nullptr, 0, L);
+  if (!endsHere) launchStepEnd(graph, results, committed, pendingRows, pendingPath, stepAdvance, nullptr, 0, L);
 }
 
 }  // namespace splash::b200::model

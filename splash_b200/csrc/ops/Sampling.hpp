@@ -78,6 +78,52 @@ class Sampling {
     ++graph.launches;
   }
 
+  // addVerify and addAcceptance as one launch (sb_select_accept), for `lanes` lanes whose rows, uniforms and results
+  // lie lane after lane in the same buffers; with `commit` the launch also ends the lanes' step (LaneCommit::advance as
+  // the step's end takes it). tickets: u32 [lanes], zeroed once.
+  struct LaneCommit {
+    Buffer committed, pendingRows, pendingPath;
+    uint32_t advance = 0;
+  };
+  static void addVerifyAndAcceptance(CommandGraph &graph, const SamplingPolicy &policy, const SamplingBuffers &b, const AcceptanceBuffers &ab,
+                                     uint32_t rows, uint32_t vocabulary, uint32_t maximumRetained, uint32_t lanes, const Buffer &tickets,
+                                     const LaneCommit *commit) {
+    const size_t slots = lanes > 1 ? size_t(lanes) * 16 : rows;  // (a lane's block lies in its 16 row slots)
+    requireBytes(b.logits, ((slots - 1) * b.logitStride + vocabulary) * 4, "Sampling::addVerifyAndAcceptance logits");
+    requireBytes(b.inputTokens, slots * 4, "Sampling::addVerifyAndAcceptance input tokens");
+    requireBytes(b.selected, slots * 4, "Sampling::addVerifyAndAcceptance selected");
+    requireBytes(ab.treeRows, slots * 8, "Sampling::addVerifyAndAcceptance tree rows");
+    requireBytes(ab.results, size_t(16) * std::max(1u, lanes), "Sampling::addVerifyAndAcceptance results");
+    requireBytes(tickets, size_t(4) * std::max(1u, lanes), "Sampling::addVerifyAndAcceptance tickets");
+    if (policy.temperature > 0.0f) {
+      requireBytes(b.uniforms, size_t(80) * 4 * std::max(1u, lanes), "Sampling::addVerifyAndAcceptance uniforms");
+      requireBytes(b.workspace, workspace(uint32_t(slots), vocabulary), "Sampling::addVerifyAndAcceptance workspace");
+    }
+    SbSelectAcceptArgs c{};
+    c.sample = SbSampleArgs{b.logits.as<float>(), b.inputTokens.as<uint32_t>(), policy.temperature > 0.0f ? b.uniforms.as<float>() : nullptr,
+                            b.selected.as<uint32_t>(), b.workspace ? b.workspace.as<float>() : nullptr, rows, vocabulary, b.logitStride,
+                            policy.temperature, policy.minP, policy.topK, policy.topP, nullptr, nullptr, nullptr, nullptr, lanes, 0};
+    if (b.candidateIds && policy.temperature > 0.0f) {
+      if (!b.candidateQ || !b.draws) throw std::invalid_argument("Sampling::addVerifyAndAcceptance: candidates without their probabilities or draws");
+      requireBytes(*b.candidateIds, slots * 16 * 4, "Sampling::addVerifyAndAcceptance candidate ids");
+      requireBytes(*b.candidateQ, slots * 16 * 4, "Sampling::addVerifyAndAcceptance candidate probabilities");
+      requireBytes(*b.draws, slots * 4, "Sampling::addVerifyAndAcceptance draws");
+      c.sample.candidate_ids = b.candidateIds->as<uint32_t>(), c.sample.candidate_q = b.candidateQ->as<float>(), c.sample.draws = b.draws->as<uint8_t>();
+    }
+    c.accept = SbAcceptArgs{b.inputTokens.as<uint32_t>(), ab.treeRows.as(), b.selected.as<uint32_t>(), ab.results.as<uint32_t>(),
+                            ab.stopTokenCount ? ab.stopTokens.as<uint32_t>() : nullptr, rows, maximumRetained, ab.stopTokenCount, lanes};
+    c.tickets = tickets.as<uint32_t>();
+    if (commit) {
+      requireBytes(commit->committed, size_t(4) * std::max(1u, lanes), "Sampling::addVerifyAndAcceptance committed");
+      requireBytes(commit->pendingRows, size_t(4) * std::max(1u, lanes), "Sampling::addVerifyAndAcceptance pending rows");
+      requireBytes(commit->pendingPath, size_t(4) * std::max(1u, lanes), "Sampling::addVerifyAndAcceptance pending path");
+      c.committed = commit->committed.as<uint32_t>(), c.pending_rows = commit->pendingRows.as<uint32_t>(), c.pending_path = commit->pendingPath.as<uint32_t>();
+      c.advance = commit->advance;
+    }
+    check(sb_select_accept(graph.stream, &c));
+    ++graph.launches;
+  }
+
   static void addAcceptance(CommandGraph &graph, const AcceptanceBuffers &b, uint32_t rows, uint32_t maximumRetained) {
     requireBytes(b.inputTokens, size_t(rows) * 4, "Sampling::addAcceptance input tokens");
     requireBytes(b.treeRows, size_t(rows) * 8, "Sampling::addAcceptance tree rows");

@@ -473,14 +473,13 @@ __device__ RowCut distribution_end(const float *l, uint32_t vocab, float mx, flo
   return cut;
 }
 
-__global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SbSampleArgs a_in) {
+// One row's selection by one block (row blockIdx.x of lane blockIdx.y).
+__device__ __forceinline__ void sample_row(const SbSampleArgs &a_in) {
   __shared__ FilterScratch fs;
   __shared__ float best_v[32];
   __shared__ uint32_t best_i[32];
   __shared__ float s_max;
   __shared__ uint32_t s_top;
-  pdl_launch_dependents();
-  pdl_wait();
   // Lanes (blockIdx.y): lane z's rows are rows 16 z .. of every row-indexed buffer, its uniforms the 80 from 80 z on.
   SbSampleArgs a = a_in;
   {
@@ -680,20 +679,25 @@ __global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SbSampleAr
   a.selected[r] = pick;
 }
 
-// ---- acceptance: one thread ----
-__global__ void accept_kernel(const SbAcceptArgs a_in) {
+__global__ void __launch_bounds__(kSampleThreads) sample_kernel(const SbSampleArgs a) {
   pdl_launch_dependents();
   pdl_wait();
-  if (threadIdx.x != 0) return;
-  SbAcceptArgs a = a_in;  // lane blockIdx.x: rows 16 z .., results 4 z ..
-  a.input_tokens += kLaneRows * blockIdx.x, a.tokens += kLaneRows * blockIdx.x, a.results += 4 * blockIdx.x;
-  a.tree = static_cast<const uint2 *>(a.tree) + kLaneRows * blockIdx.x;
-  const uint2 *tree = static_cast<const uint2 *>(a.tree);  // {ancestors, parent | depth << 16}
+  sample_row(a);
+}
+
+// ---- acceptance: one thread ----
+// Lane z: rows 16 z .., results 4 z ... The selections are read as other blocks of the same launch may have
+// written them (volatile: from L2).
+__device__ __forceinline__ void accept_lane(const SbAcceptArgs &a_in, uint32_t z) {
+  SbAcceptArgs a = a_in;
+  a.input_tokens += kLaneRows * z, a.tokens += kLaneRows * z, a.results += 4 * z;
+  const uint2 *tree = static_cast<const uint2 *>(a.tree) + kLaneRows * z;  // {ancestors, parent | depth << 16}
+  volatile uint32_t *tokens = a.tokens;
   uint32_t path[32];
   path[0] = 0;
   uint32_t accepted = 0;
   for (uint32_t row = 0;;) {
-    const uint32_t token = a.tokens[row];
+    const uint32_t token = tokens[row];
     uint32_t next = 0;
     for (uint32_t child = row + 1; child < a.rows && !next; ++child)
       next = ((tree[child].y & 0xffffu) == row && a.input_tokens[child] == token) ? child : 0;
@@ -703,8 +707,8 @@ __global__ void accept_kernel(const SbAcceptArgs a_in) {
   }
   uint32_t kept = min(accepted + 1, a.remaining);
   for (uint32_t i = 0; i < kept; ++i) {
-    const uint32_t token = a.tokens[path[i]];
-    a.tokens[i] = token;
+    const uint32_t token = tokens[path[i]];
+    tokens[i] = token;
     for (uint32_t s = 0; s < a.n_stop; ++s)
       if (a.stop_tokens[s] == token) kept = i + 1;
   }
@@ -712,6 +716,48 @@ __global__ void accept_kernel(const SbAcceptArgs a_in) {
   a.results[1] = min(accepted, kept);
   a.results[2] = tree[path[kept - 1]].x;
   a.results[3] = 0;
+}
+__global__ void accept_kernel(const SbAcceptArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  if (threadIdx.x == 0) accept_lane(a, blockIdx.x);
+}
+
+// The lane's commit after acceptance (mode as the step's end takes it: 0 hold and clear the pending rows, 1 commit the
+// retained rows, 2 hold and keep the pending rows, 3 | rows << 8 commit every row).
+__device__ __forceinline__ void commit_lane(const SbSelectAcceptArgs &c, uint32_t lane) {
+  uint32_t *results = c.accept.results + 4 * lane;
+  const uint32_t mode = c.advance & 0xffu, rows = c.advance >> 8;
+  if (mode == 3) {
+    results[0] = rows, results[1] = rows - 1, results[2] = (2u << (rows - 1)) - 1u;
+    c.committed[lane] += rows;
+    c.pending_rows[lane] = rows;
+    c.pending_path[lane] = 0;
+  } else if (mode == 1) {
+    c.committed[lane] += results[0];
+    c.pending_rows[lane] = results[0];
+    c.pending_path[lane] = results[2];
+  } else if (mode == 0) {
+    c.pending_rows[lane] = 0;
+    c.pending_path[lane] = 0;
+  }
+}
+
+// Selection, acceptance and the lane's commit in one launch: a block per row selects (sample_row), and the block of a
+// lane that finishes last (a ticket per lane, drawn after the block's selection is visible) walks the accepted path
+// and commits the lane. The ticket word returns to zero for the next launch.
+__global__ void __launch_bounds__(kSampleThreads) select_accept_kernel(const SbSelectAcceptArgs c) {
+  pdl_launch_dependents();
+  pdl_wait();
+  sample_row(c.sample);
+  if (threadIdx.x != 0) return;
+  const uint32_t lane = blockIdx.y;
+  __threadfence();
+  if (atomicAdd(c.tickets + lane, 1u) != c.sample.rows - 1) return;
+  __threadfence();
+  c.tickets[lane] = 0;
+  accept_lane(c.accept, lane);
+  if (c.committed) commit_lane(c, lane);
 }
 
 // One thread per vocabulary token: the token's count in every row's context, then the penalty on the rows that
@@ -960,6 +1006,28 @@ int sb_moe_route(void *stream, const SbMoeRouteArgs *a) {
   SB_REQUIRE(a->top_k >= 1 && a->top_k <= 32 && a->top_k <= a->experts, "sb_moe_route: top_k = %u outside 1..min(32, experts)", a->top_k);
   SB_REQUIRE(!a->shared_gate || (a->input && a->input_size), "sb_moe_route: a gated shared expert needs the rows' input");
   return launch(moe_route_kernel, dim3(a->rows), dim3(256), as_stream(stream), *a);
+}
+
+int sb_select_accept(void *stream, const SbSelectAcceptArgs *c) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(c && c->tickets, "sb_select_accept: null pointer");
+  const SbSampleArgs *a = &c->sample;
+  const SbAcceptArgs *b = &c->accept;
+  SB_REQUIRE(a->logits && a->selected && a->input_tokens, "sb_select_accept: null pointer");
+  SB_REQUIRE(a->rows >= 1 && a->rows <= 16 && a->vocab >= 1 && a->logit_stride >= a->vocab, "sb_select_accept: rows %u outside 1..16 or bad vocabulary extent", a->rows);
+  SB_REQUIRE(a->temperature >= 0.0f, "sb_select_accept: negative temperature");
+  SB_REQUIRE(a->temperature == 0.0f || (a->uniforms && a->workspace), "sb_select_accept: a sampled policy needs uniforms and a workspace");
+  SB_REQUIRE(a->min_p >= 0.0f && a->min_p <= 1.0f && a->top_p >= 0.0f, "sb_select_accept: min_p %g outside 0..1 or negative top_p", double(a->min_p));
+  const bool filtered = a->min_p > 0.0f || (a->top_k > 0 && a->top_k < a->vocab) || (a->top_p > 0.0f && a->top_p < 1.0f);
+  SB_REQUIRE(!filtered || a->vocab <= kMaxFilterShards * kShard, "sb_select_accept: min-p / top-k / top-p support vocabularies up to %u", kMaxFilterShards * kShard);
+  SB_REQUIRE(!a->candidate_ids || (a->candidate_q && a->draws), "sb_select_accept: candidates come with their draft probabilities and the rows' draws");
+  SB_REQUIRE(a->lanes <= 64, "sb_select_accept: %u lanes (up to 64)", a->lanes);
+  SB_REQUIRE(b->input_tokens == a->input_tokens && b->tokens == a->selected && b->tree && b->results, "sb_select_accept: acceptance reads the selection's rows: same input tokens, tokens = selected");
+  SB_REQUIRE(b->rows == a->rows && b->remaining >= 1 && std::max(1u, b->lanes) == std::max(1u, a->lanes), "sb_select_accept: selection and acceptance disagree on rows or lanes");
+  SB_REQUIRE(b->n_stop == 0 || b->stop_tokens, "sb_select_accept: stop tokens missing");
+  SB_REQUIRE(!c->committed || (c->pending_rows && c->pending_path), "sb_select_accept: the commit needs the lanes' pending words");
+  SB_REQUIRE((c->advance & 0xffu) <= 3 && ((c->advance & 0xffu) != 3 || c->advance >> 8 == a->rows), "sb_select_accept: advance = 0x%x", c->advance);
+  return launch(select_accept_kernel, dim3(a->rows, std::max(1u, a->lanes)), dim3(kSampleThreads), as_stream(stream), *c);
 }
 
 int sb_accept(void *stream, const SbAcceptArgs *a) {

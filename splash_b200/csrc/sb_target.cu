@@ -206,6 +206,7 @@ int sb_target_create(const SbTargetConfig *config, void **out_target) {
     iota_kernel<<<(pages + 255) / 256, 256>>>(table.as<uint32_t>(), pages);
     if (config->rotary_pairs) inv_freq_kernel<<<1, 256>>>(m.invFreq.as<float>(), config->rotary_pairs, config->rope_theta);
     SB_CUDA(cudaMemset(m.committed.as(), 0, 4 * L));
+    SB_CUDA(cudaMemset(m.tickets.as(), 0, m.tickets.bytes()));
     SB_CUDA(cudaMemset(m.pendingRows.as(), 0, 4 * L));
     SB_CUDA(cudaMemset(m.pendingPath.as(), 0, 4 * L));
     SB_CUDA(cudaMemset(m.penaltyWords.as(), 0, m.penaltyWords.bytes()));

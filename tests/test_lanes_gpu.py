@@ -189,6 +189,80 @@ def test_selection_penalties_and_acceptance_of_lanes_equal_the_lanes_one_at_a_ti
     assert len(set(greedy[:, 0].tolist())) >= 3          # the lanes did accept different lengths
 
 
+@pytest.mark.parametrize("temperature", [0.0, 0.8])
+def test_selection_and_acceptance_in_one_launch_equal_the_two_calls(temperature):
+    """sb_select_accept against sb_sample_verify followed by sb_accept on the same lanes, bit for bit, over repeated launches
+    (the ticket words return to zero), and the lanes' commit in each of its modes."""
+    lib, l, o = _setup()
+    rng = np.random.default_rng(41)
+    L, rows, V = 5, 9, 6000
+    logits = (rng.standard_normal((16 * L, V)) * 3).astype(np.float32)
+    tokens = rng.integers(0, V, 16 * L).astype(np.uint32)
+    for lane in range(L):
+        for r in range(min(lane, rows - 1)):
+            tokens[16 * lane + r + 1] = np.argmax(logits[16 * lane + r])
+    uniforms = rng.random(80 * L).astype(np.float32)
+    tree = np.tile(lib.chain_tree(16), (L, 1))
+    up = lib.DeviceBuffer.from_numpy
+    dl, dt, du, dtree = up(logits), up(tokens), up(uniforms), up(tree)
+    ws = lib.DeviceBuffer(int(l.sb_sample_workspace_bytes(16 * L, V)))
+
+    def args(sel, res):
+        sa = lib.SbSampleArgs(dl.ptr, dt.ptr, du.ptr if temperature else None, sel.ptr, ws.ptr, rows, V, V, temperature, 0.0, 0, 1.0)
+        sa.lanes = L
+        aa = lib.SbAcceptArgs(dt.ptr, dtree.ptr, sel.ptr, res.ptr, None, rows, 16, 0)
+        aa.lanes = L
+        return sa, aa
+
+    sel, res = lib.DeviceBuffer(16 * L * 4), lib.DeviceBuffer(16 * L)
+    sel.fill(0), res.fill(0)
+    sa, aa = args(sel, res)
+    lib.check(l.sb_sample_verify(None, ctypes.byref(sa)))
+    lib.check(l.sb_accept(None, ctypes.byref(aa)))
+    lib.stream_sync()
+    want_sel, want_res = sel.to_numpy(np.uint32, (L, 16)), res.to_numpy(np.uint32, (L, 4))
+
+    tickets = lib.DeviceBuffer(4 * L)
+    tickets.fill(0)
+    committed0 = np.array([100, 200, 300, 400, 500], np.uint32)
+    for advance in (None, 1, 0, 2, 3 | rows << 8):
+        sel2, res2 = lib.DeviceBuffer(16 * L * 4), lib.DeviceBuffer(16 * L)
+        sel2.fill(0), res2.fill(0)
+        committed, pending_rows, pending_path = up(committed0), up(np.full(L, 7, np.uint32)), up(np.full(L, 0x55, np.uint32))
+        c = lib.SbSelectAcceptArgs()
+        c.sample, c.accept = args(sel2, res2)
+        c.tickets = tickets.ptr
+        if advance is not None:
+            c.committed, c.pending_rows, c.pending_path, c.advance = committed.ptr, pending_rows.ptr, pending_path.ptr, advance
+        for repeat in range(3):
+            if repeat and advance is not None:
+                break                                         # (a commit moves the lane: once)
+            lib.check(l.sb_select_accept(None, ctypes.byref(c)))
+        lib.stream_sync()
+        assert lib.device_status() == 0
+        assert not tickets.to_numpy(np.uint32, (L,)).any()
+        got_sel, got_res = sel2.to_numpy(np.uint32, (L, 16)), res2.to_numpy(np.uint32, (L, 4))
+        got = committed.to_numpy(np.uint32, (L,)), pending_rows.to_numpy(np.uint32, (L,)), pending_path.to_numpy(np.uint32, (L,))
+        if advance == (3 | rows << 8):
+            assert np.array_equal(got_res, np.tile(np.array([rows, rows - 1, (1 << rows) - 1, 0], np.uint32), (L, 1)))
+            assert np.array_equal(got[0], committed0 + rows) and (got[1] == rows).all() and (got[2] == 0).all()
+            continue
+        assert np.array_equal(got_sel, want_sel) and np.array_equal(got_res, want_res)
+        if advance is None or advance == 2:
+            assert np.array_equal(got[0], committed0) and (got[1] == 7).all() and (got[2] == 0x55).all()
+        elif advance == 1:
+            assert np.array_equal(got[0], committed0 + want_res[:, 0]) and np.array_equal(got[1], want_res[:, 0]) and np.array_equal(got[2], want_res[:, 2])
+        else:
+            assert np.array_equal(got[0], committed0) and not got[1].any() and not got[2].any()
+    # what the call refuses: acceptance over other rows than the selection's, no tickets
+    c = lib.SbSelectAcceptArgs()
+    c.sample, c.accept = args(sel, res)
+    assert l.sb_select_accept(None, ctypes.byref(c)) == -1
+    c.tickets = tickets.ptr
+    c.accept.rows = rows - 1
+    assert l.sb_select_accept(None, ctypes.byref(c)) == -1
+
+
 @pytest.mark.parametrize("rows,n,k", [(200, 256, 2048), (512, 64, 1024), (17, 48, 512), (40, 32, 384)])
 def test_float_projection_of_many_rows_keeps_fp32_accuracy(rows, n, k):
     """sb_linear_f32 over more than 16 rows runs on the tensor cores with the fp32 weights split into three bf16 terms:
