@@ -731,6 +731,45 @@ SB_API int sb_target_verify_lanes(void *target, void *stream, const uint32_t *to
 SB_API int sb_target_verify_tree(void *target, void *stream, const uint32_t *tokens_host, const void *tree_host, const float *uniforms_host,
                                  uint32_t rows, float temperature, uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host);
 /* Kernels one step launches, and the bytes its weights, cache and state stream (the roofline's numerator). */
+/* The configuration the target was created with. */
+SB_API int sb_target_config(void *target, SbTargetConfig *out_config);
+
+/* ---- GGUF files ----
+ * A reader of llama.cpp's GGUF container (version 3; the reference's runtime/model/GgufFile.hpp:23-141) over a read-only
+ * mapping of the file, and the loader of a Qwen3.5 hybrid model (general.architecture qwen35 or qwen35moe) from it into a
+ * target. The reader is host code: it works without a device. Tensor types are ggml's ids (0 F32, 1 F16, 8 Q8_0, 12 Q4_K,
+ * 14 Q6_K, 30 BF16, ...); dims[0] is a row's length. Pointers handed out stay valid until sb_gguf_close. */
+typedef struct SbGgufTensor {
+  const char *name;
+  uint32_t type, n_dims;
+  uint64_t dims[4];  /* 1 past n_dims */
+  const void *data;  /* host address of the tensor's bytes in the mapping */
+  uint64_t bytes;
+} SbGgufTensor;
+SB_API int sb_gguf_open(const char *path, void **out_file);
+SB_API int sb_gguf_close(void *file);
+SB_API int sb_gguf_tensor_count(void *file, uint64_t *out_count);
+SB_API int sb_gguf_tensor(void *file, uint64_t index, SbGgufTensor *out);
+SB_API int sb_gguf_find(void *file, const char *name, SbGgufTensor *out); /* SB_ERR_INVALID without such a tensor */
+/* Scalar metadata by key: integers and booleans as unsigned (a negative one as its two's complement), floats (and
+ * integers) as double, strings. SB_ERR_INVALID without such a key. */
+SB_API int sb_gguf_meta_u64(void *file, const char *key, uint64_t *out);
+SB_API int sb_gguf_meta_f64(void *file, const char *key, double *out);
+SB_API int sb_gguf_meta_str(void *file, const char *key, const char **out);
+/* Fills the model's fields of *config from the file's metadata and tensors (the keys runtime/model/GgufImage.cpp:902-933
+ * checks: block_count, embedding_length, attention.*, rope.*, full_attention_interval, ssm.*, expert_*,
+ * feed_forward_length; the vocabulary from token_embd; fmt_* from the tensors' types; gated_attention from attn_q's rows;
+ * tiled_heads = 1) and leaves the rest (page_tokens, kv_scale_f16, max_context, lanes, tp_*, ep_*) as the caller set them. */
+SB_API int sb_gguf_target_config(void *file, SbTargetConfig *config);
+/* Copies the file's tensors into the target's (whole model on one GPU): names, shapes and conversions as
+ * runtime/model/GgufImage.cpp:477-556 - attn_q / attn_k / attn_v (or attn_qkv and attn_gate) into the fused input
+ * projection, ssm_beta / ssm_alpha into the fp32 gate rows, ssm_conv1d and ssm_dt.bias narrowed to bf16, the rows that
+ * carry a value head gathered from llama.cpp's tiled head order into grouped order, stacked experts with the shared
+ * expert last. A target has one weight format for its projections, one for the down projections, one for the head and
+ * one for the embedding: a tensor of another type is refused by name (so are types no kernel here reads, e.g. Q5_K),
+ * and so is a file whose metadata differs from the target's configuration. Synchronous. */
+SB_API int sb_target_load_gguf(void *target, void *file);
+
 SB_API int sb_target_stats(void *target, uint32_t rows, uint32_t *out_launches, uint64_t *out_weight_bytes, uint64_t *out_kv_bytes,
                            uint64_t *out_state_bytes);
 

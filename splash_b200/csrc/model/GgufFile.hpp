@@ -1,0 +1,263 @@
+// GGUF (version 3) header reader over a read-only mapping of the file: scalar and string metadata, small numeric
+// arrays, the tensor table, and where each tensor's bytes lie. Host code only; nothing is copied out of the mapping
+// but the header's own strings.
+//
+// Mirrors the reference's header parser (runtime/model/GgufFile.hpp:23-141: GgufTensor, GgufMetadata, GgufFile::find /
+// require / numericArray; type table :38-57) for one file; split files and the rotation keys are not read.
+// File layout as llama.cpp's gguf.h documents it: magic "GGUF", u32 version, u64 tensor count, u64 key count; per key a
+// string, a u32 value type and the value; per tensor a string, u32 dimensions, u64 extents (fastest first), u32 ggml
+// type, u64 offset into the data section, which starts at the next multiple of general.alignment (32 by default).
+#pragma once
+
+#include <fcntl.h>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <cstdint>
+#include <cstring>
+#include <map>
+#include <optional>
+#include <stdexcept>
+#include <string>
+#include <string_view>
+#include <vector>
+
+namespace splash::b200::model {
+
+class GgufError : public std::runtime_error {
+ public:
+  using std::runtime_error::runtime_error;
+};
+
+namespace ggml {
+constexpr uint32_t kF32 = 0, kF16 = 1, kQ8_0 = 8, kQ4_K = 12, kQ6_K = 14, kBF16 = 30;
+}
+
+struct GgmlType {
+  uint32_t id;
+  const char *name;
+  uint32_t blockElements, blockBytes;
+};
+// The ggml tensor types this reader can size (ggml's own ids and block shapes): a tensor of another type is refused,
+// since its extent in the file could not be checked.
+inline const GgmlType *ggmlType(uint32_t id) {
+  static const GgmlType table[] = {
+      {0, "F32", 1, 4},        {1, "F16", 1, 2},        {2, "Q4_0", 32, 18},     {3, "Q4_1", 32, 20},     {6, "Q5_0", 32, 22},
+      {7, "Q5_1", 32, 24},     {8, "Q8_0", 32, 34},     {9, "Q8_1", 32, 36},     {10, "Q2_K", 256, 84},   {11, "Q3_K", 256, 110},
+      {12, "Q4_K", 256, 144},  {13, "Q5_K", 256, 176},  {14, "Q6_K", 256, 210},  {15, "Q8_K", 256, 292},  {16, "IQ2_XXS", 256, 66},
+      {17, "IQ2_XS", 256, 74}, {18, "IQ3_XXS", 256, 98}, {19, "IQ1_S", 256, 50}, {20, "IQ4_NL", 32, 18},  {21, "IQ3_S", 256, 110},
+      {22, "IQ2_S", 256, 82},  {23, "IQ4_XS", 256, 136}, {24, "I8", 1, 1},       {25, "I16", 1, 2},       {26, "I32", 1, 4},
+      {27, "I64", 1, 8},       {28, "F64", 1, 8},       {29, "IQ1_M", 256, 56},  {30, "BF16", 1, 2},      {39, "MXFP4", 32, 17},
+      {40, "NVFP4", 64, 36},
+  };
+  for (const GgmlType &t : table)
+    if (t.id == id) return &t;
+  return nullptr;
+}
+inline std::string ggmlTypeName(uint32_t id) {
+  const GgmlType *t = ggmlType(id);
+  return t ? t->name : "type " + std::to_string(id);
+}
+
+struct GgufTensor {
+  std::string name;
+  uint32_t type = 0;
+  std::vector<uint64_t> dims;  // dims[0] is the fastest (a row's length)
+  uint64_t offset = 0;         // in the file's data section
+  uint64_t bytes = 0;
+  const uint8_t *data = nullptr;  // in the mapping
+  uint64_t columns() const { return dims.empty() ? 0 : dims[0]; }
+  uint64_t rows() const { return elements() / (columns() ? columns() : 1); }
+  uint64_t elements() const {
+    uint64_t n = dims.empty() ? 0 : 1;
+    for (uint64_t d : dims) n *= d;
+    return n;
+  }
+};
+
+// Scalar metadata by key: integers and booleans as unsigned (a negative one as its two's complement), floats as double.
+struct GgufMetadata {
+  std::map<std::string, uint64_t, std::less<>> unsigneds;
+  std::map<std::string, double, std::less<>> floats;
+  std::map<std::string, std::string, std::less<>> strings;
+  std::optional<uint64_t> unsignedValue(std::string_view key) const {
+    auto it = unsigneds.find(key);
+    return it == unsigneds.end() ? std::nullopt : std::optional<uint64_t>(it->second);
+  }
+  std::optional<double> floatValue(std::string_view key) const {
+    auto it = floats.find(key);
+    if (it != floats.end()) return it->second;
+    if (auto u = unsignedValue(key)) return double(*u);
+    return std::nullopt;
+  }
+  std::optional<std::string> stringValue(std::string_view key) const {
+    auto it = strings.find(key);
+    return it == strings.end() ? std::nullopt : std::optional<std::string>(it->second);
+  }
+  std::string architecture() const { return stringValue("general.architecture").value_or(""); }
+};
+
+class GgufFile {
+ public:
+  explicit GgufFile(const std::string &path) : path_(path) {
+    const int fd = ::open(path.c_str(), O_RDONLY);
+    if (fd < 0) throw GgufError("cannot open " + path);
+    struct stat st {};
+    if (::fstat(fd, &st) != 0 || st.st_size < 24) {
+      ::close(fd);
+      throw GgufError(path + " is not a GGUF file (too short)");
+    }
+    size_ = uint64_t(st.st_size);
+    void *m = ::mmap(nullptr, size_, PROT_READ, MAP_PRIVATE, fd, 0);
+    ::close(fd);
+    if (m == MAP_FAILED) throw GgufError("cannot map " + path);
+    base_ = static_cast<const uint8_t *>(m);
+    try {
+      parse();
+    } catch (...) {
+      ::munmap(const_cast<uint8_t *>(base_), size_);
+      throw;
+    }
+  }
+  ~GgufFile() {
+    if (base_) ::munmap(const_cast<uint8_t *>(base_), size_);
+  }
+  GgufFile(const GgufFile &) = delete;
+  GgufFile &operator=(const GgufFile &) = delete;
+
+  const GgufMetadata &metadata() const { return metadata_; }
+  const std::vector<GgufTensor> &tensors() const { return tensors_; }
+  const GgufTensor *find(std::string_view name) const {
+    auto it = index_.find(name);
+    return it == index_.end() ? nullptr : &tensors_[it->second];
+  }
+  const GgufTensor &require(std::string_view name) const {
+    const GgufTensor *t = find(name);
+    if (!t) throw GgufError("the GGUF has no tensor " + std::string(name));
+    return *t;
+  }
+  // A numeric array's values, nullptr for a key that holds none (arrays of up to 65536 numbers are kept).
+  const std::vector<double> *numericArray(std::string_view key) const {
+    auto it = arrays_.find(key);
+    return it == arrays_.end() ? nullptr : &it->second;
+  }
+  uint64_t dataStart() const { return dataStart_; }
+  uint32_t alignment() const { return alignment_; }
+  const std::string &path() const { return path_; }
+
+ private:
+  // GGUF value types.
+  enum : uint32_t { kU8, kI8, kU16, kI16, kU32, kI32, kF32, kBool, kString, kArray, kU64, kI64, kF64 };
+
+  template <class T> T take() {
+    if (at_ + sizeof(T) > size_) throw GgufError(path_ + ": the header runs past the end of the file");
+    T v;
+    std::memcpy(&v, base_ + at_, sizeof(T));
+    at_ += sizeof(T);
+    return v;
+  }
+  std::string takeString() {
+    const uint64_t n = take<uint64_t>();
+    if (n > size_ - at_) throw GgufError(path_ + ": a string runs past the end of the file");
+    std::string s(reinterpret_cast<const char *>(base_ + at_), size_t(n));
+    at_ += n;
+    return s;
+  }
+  // One scalar of `type` as (is it a float, unsigned bits, double).
+  bool takeScalar(uint32_t type, uint64_t &u, double &f) {
+    switch (type) {
+      case kU8: u = take<uint8_t>(); return false;
+      case kI8: u = uint64_t(int64_t(take<int8_t>())); return false;
+      case kU16: u = take<uint16_t>(); return false;
+      case kI16: u = uint64_t(int64_t(take<int16_t>())); return false;
+      case kU32: u = take<uint32_t>(); return false;
+      case kI32: u = uint64_t(int64_t(take<int32_t>())); return false;
+      case kBool: u = take<uint8_t>() != 0; return false;
+      case kU64: u = take<uint64_t>(); return false;
+      case kI64: u = uint64_t(take<int64_t>()); return false;
+      case kF32: f = take<float>(); return true;
+      case kF64: f = take<double>(); return true;
+      default: throw GgufError(path_ + ": metadata value type " + std::to_string(type) + " is not one of GGUF's");
+    }
+  }
+  void parse() {
+    if (std::memcmp(base_, "GGUF", 4) != 0) throw GgufError(path_ + " is not a GGUF file (magic)");
+    at_ = 4;
+    const uint32_t version = take<uint32_t>();
+    if (version != 3) throw GgufError(path_ + ": GGUF version " + std::to_string(version) + " (version 3 is read)");
+    const uint64_t tensorCount = take<uint64_t>(), keyCount = take<uint64_t>();
+    if (tensorCount > size_ / 24 || keyCount > size_ / 12) throw GgufError(path_ + ": counts exceed what the file can hold");
+    for (uint64_t k = 0; k < keyCount; ++k) {
+      const std::string key = takeString();
+      const uint32_t type = take<uint32_t>();
+      if (type == kString) {
+        metadata_.strings[key] = takeString();
+      } else if (type == kArray) {
+        const uint32_t inner = take<uint32_t>();
+        const uint64_t n = take<uint64_t>();
+        if (inner == kArray) throw GgufError(path_ + ": nested arrays (" + key + ")");
+        std::vector<double> kept;
+        const bool keep = inner != kString && n <= 65536;
+        for (uint64_t i = 0; i < n; ++i) {
+          if (inner == kString) {
+            (void)takeString();
+            continue;
+          }
+          uint64_t u = 0;
+          double f = 0;
+          const bool isFloat = takeScalar(inner, u, f);
+          if (keep) kept.push_back(isFloat ? f : (inner == kI8 || inner == kI16 || inner == kI32 || inner == kI64 ? double(int64_t(u)) : double(u)));
+        }
+        if (keep) arrays_[key] = std::move(kept);
+      } else {
+        uint64_t u = 0;
+        double f = 0;
+        if (takeScalar(type, u, f)) metadata_.floats[key] = f;
+        else metadata_.unsigneds[key] = u;
+      }
+    }
+    alignment_ = uint32_t(metadata_.unsignedValue("general.alignment").value_or(32));
+    if (!alignment_ || (alignment_ & (alignment_ - 1))) throw GgufError(path_ + ": general.alignment is not a power of two");
+    tensors_.reserve(size_t(tensorCount));
+    for (uint64_t t = 0; t < tensorCount; ++t) {
+      GgufTensor tensor;
+      tensor.name = takeString();
+      const uint32_t nd = take<uint32_t>();
+      if (nd < 1 || nd > 4) throw GgufError(path_ + ": " + tensor.name + " has " + std::to_string(nd) + " dimensions");
+      uint64_t elements = 1;
+      for (uint32_t d = 0; d < nd; ++d) {
+        const uint64_t e = take<uint64_t>();
+        if (!e || elements > UINT64_MAX / e) throw GgufError(path_ + ": " + tensor.name + " has an empty or overflowing extent");
+        elements *= e;
+        tensor.dims.push_back(e);
+      }
+      tensor.type = take<uint32_t>();
+      tensor.offset = take<uint64_t>();
+      const GgmlType *type = ggmlType(tensor.type);
+      if (!type) throw GgufError(path_ + ": " + tensor.name + " is of ggml type " + std::to_string(tensor.type) + ", which this reader cannot size");
+      if (tensor.dims[0] % type->blockElements) throw GgufError(path_ + ": " + tensor.name + " rows are not whole " + type->name + " blocks");
+      tensor.bytes = elements / type->blockElements * type->blockBytes;
+      if (tensor.offset % alignment_) throw GgufError(path_ + ": " + tensor.name + " does not start on the file's alignment");
+      if (!index_.emplace(tensor.name, tensors_.size()).second) throw GgufError(path_ + ": two tensors named " + tensor.name);
+      tensors_.push_back(std::move(tensor));
+    }
+    dataStart_ = (at_ + alignment_ - 1) / alignment_ * alignment_;
+    for (GgufTensor &tensor : tensors_) {
+      if (dataStart_ > size_ || tensor.offset > size_ - dataStart_ || tensor.bytes > size_ - dataStart_ - tensor.offset)
+        throw GgufError(path_ + ": " + tensor.name + " lies past the end of the file");
+      tensor.data = base_ + dataStart_ + tensor.offset;
+    }
+  }
+
+  std::string path_;
+  const uint8_t *base_ = nullptr;
+  uint64_t size_ = 0, at_ = 0, dataStart_ = 0;
+  uint32_t alignment_ = 32;
+  GgufMetadata metadata_;
+  std::map<std::string, std::vector<double>, std::less<>> arrays_;
+  std::vector<GgufTensor> tensors_;
+  std::map<std::string, size_t, std::less<>> index_;
+};
+
+}  // namespace splash::b200::model

@@ -294,6 +294,12 @@ int sb_target_tensor(void *target, int layer, const char *name, void **out_dev, 
   return SB_OK;
 }
 
+int sb_target_config(void *target, SbTargetConfig *out_config) {
+  SB_REQUIRE(target && out_config, "sb_target_config: null pointer");
+  *out_config = static_cast<Target *>(target)->model->config();
+  return SB_OK;
+}
+
 int sb_target_reset(void *target, uint32_t committed) {
   SB_NEED_DEVICE();
   SB_REQUIRE(target, "sb_target_reset: null target");

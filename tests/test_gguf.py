@@ -1,0 +1,217 @@
+"""The GGUF reader (host code: runs without a GPU) and the loader that fills a target from a GGUF of the Qwen3.5 hybrid
+family. The files are written by tests/gguf_writer.py from the tiny model's synthetic tensors, with the names, shapes and
+llama.cpp's tiled value-head order the reference's loader expects (runtime/model/GgufImage.cpp:477-556)."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+
+import gguf_writer as gw
+import model_oracle as mo
+import oracle_lib as ol
+
+FMT_TO_GGML = {0: gw.GGML["Q4_K"], 4: gw.GGML["Q6_K"], 6: gw.GGML["Q8_0"]}
+
+
+def tiny_config():
+    from splash_b200 import target
+    return dict(target.TINY, gdn_key_heads=4, gdn_value_heads=8, tiled_heads=1)   # (two value heads a key head: the head order matters)
+
+
+def ungroup(rows, start, head_rows, key_heads, per_key):
+    """Rows in grouped head order (as the target holds them) back into llama.cpp's tiled order from row `start` on."""
+    out = rows.copy()
+    heads = (len(rows) - start) // head_rows
+    for h in range(heads):
+        src = (h % per_key) * key_heads + h // per_key
+        out[start + src * head_rows:start + (src + 1) * head_rows] = rows[start + h * head_rows:start + (h + 1) * head_rows]
+    return out
+
+
+def model_to_gguf(path, cfg, w, arch="qwen35", drop=(), replace=None):
+    """Writes the model's tensors `w` (keyed as sb_target_tensor names them) as a GGUF of architecture `arch`."""
+    H, D = cfg["hidden"], cfg["head_dim"]
+    KH, VH = cfg["gdn_key_heads"], cfg["gdn_value_heads"]
+    per_key, KW, VW = VH // KH, KH * 128, VH * 128
+    conv = 2 * KW + VW
+    a = arch + "."
+    meta = [("general.architecture", gw.STRING, arch), ("general.name", gw.STRING, "tiny synthetic"), ("general.alignment", gw.U32, 32),
+            (a + "block_count", gw.U32, cfg["layers"]), (a + "embedding_length", gw.U32, H), (a + "feed_forward_length", gw.U32, cfg["intermediate"]),
+            (a + "attention.head_count", gw.U32, cfg["q_heads"]), (a + "attention.head_count_kv", gw.U32, cfg["kv_heads"]),
+            (a + "attention.key_length", gw.U32, D), (a + "attention.value_length", gw.U32, D),
+            (a + "rope.dimension_count", gw.U32, 2 * cfg["rotary_pairs"]), (a + "rope.freq_base", gw.F32, cfg["rope_theta"]),
+            (a + "attention.layer_norm_rms_epsilon", gw.F32, 1e-6), (a + "full_attention_interval", gw.U32, cfg["attention_interval"]),
+            (a + "ssm.conv_kernel", gw.U32, 4), (a + "ssm.group_count", gw.U32, KH), (a + "ssm.time_step_rank", gw.U32, VH),
+            (a + "ssm.state_size", gw.U32, 128), (a + "ssm.inner_size", gw.U32, VW),
+            ("tokenizer.ggml.tokens", gw.ARRAY, (gw.STRING, ["<a>", "<b>", "<c>"])), ("tokenizer.ggml.scores", gw.ARRAY, (gw.F32, [0.5, -1.0, 2.0])),
+            ("some.negative", gw.I32, -7), ("some.flag", gw.BOOL, 1)]
+    tensors = []
+
+    def quantized(name, fmt, rows, k):
+        tensors.append((name, FMT_TO_GGML[fmt], [k, len(rows)], rows))
+
+    def floats(name, values, dims=None):
+        values = np.ascontiguousarray(values, np.float32)
+        tensors.append((name, gw.GGML["F32"], dims or [values.size], values))
+
+    quantized("token_embd.weight", cfg["fmt_embed"], w[-1, "token_embd"], H)
+    floats("output_norm.weight", w[-1, "output_norm"])
+    quantized("output.weight", cfg["fmt_head"], w[-1, "output"], H)
+    for l in range(cfg["layers"]):
+        p = f"blk.{l}."
+        floats(p + "attn_norm.weight", w[l, "attn_norm"])
+        floats(p + "post_attention_norm.weight", w[l, "ffn_norm"])
+        if (l + 1) % cfg["attention_interval"] == 0:
+            q, kv = cfg["q_heads"] * D * (2 if cfg["gated_attention"] else 1), cfg["kv_heads"] * D
+            rows = w[l, "in_proj"]
+            quantized(p + "attn_q.weight", cfg["fmt_proj"], rows[:q], H)
+            quantized(p + "attn_k.weight", cfg["fmt_proj"], rows[q:q + kv], H)
+            quantized(p + "attn_v.weight", cfg["fmt_proj"], rows[q + kv:], H)
+            floats(p + "attn_q_norm.weight", w[l, "q_norm"])
+            floats(p + "attn_k_norm.weight", w[l, "k_norm"])
+            quantized(p + "attn_output.weight", cfg["fmt_proj"], w[l, "out_proj"], cfg["q_heads"] * D)
+        else:
+            rows = w[l, "in_proj"]
+            quantized(p + "attn_qkv.weight", cfg["fmt_proj"], ungroup(rows[:conv], 2 * KW, 128, KH, per_key), H)
+            quantized(p + "attn_gate.weight", cfg["fmt_proj"], ungroup(rows[conv:], 0, 128, KH, per_key), H)
+            ab = w[l, "ssm_ab"]
+            floats(p + "ssm_beta.weight", ungroup(ab[:VH], 0, 1, KH, per_key), [H, VH])
+            floats(p + "ssm_alpha.weight", ungroup(ab[VH:], 0, 1, KH, per_key), [H, VH])
+            floats(p + "ssm_conv1d.weight", ungroup(ol.bf2f(w[l, "ssm_conv"]), 2 * KW, 128, KH, per_key), [4, conv])
+            floats(p + "ssm_a", ungroup(w[l, "ssm_a"], 0, 1, KH, per_key))
+            floats(p + "ssm_dt.bias", ungroup(ol.bf2f(w[l, "ssm_dt_bias"]), 0, 1, KH, per_key))
+            floats(p + "ssm_norm.weight", w[l, "ssm_norm"])
+            quantized(p + "ssm_out.weight", cfg["fmt_proj"], w[l, "out_proj"], VW)
+        quantized(p + "ffn_gate.weight", cfg["fmt_proj"], w[l, "ffn_gate"], H)
+        quantized(p + "ffn_up.weight", cfg["fmt_proj"], w[l, "ffn_up"], H)
+        quantized(p + "ffn_down.weight", cfg["fmt_down"], w[l, "ffn_down"], cfg["intermediate"])
+    tensors = [t for t in tensors if t[0] not in drop]
+    if replace:                                  # name -> (ggml type, dims, data)
+        tensors = [(n,) + tuple(replace[n]) if n in replace else (n, k, d, x) for n, k, d, x in tensors]
+    return gw.write(path, meta, tensors)
+
+
+@pytest.fixture(scope="module")
+def tiny_file(tmp_path_factory):
+    cfg = tiny_config()
+    w = mo.make_weights(cfg, 3)
+    path = str(tmp_path_factory.mktemp("gguf") / "tiny.gguf")
+    start = model_to_gguf(path, cfg, w)
+    return path, cfg, w, start
+
+
+def test_reader_lists_the_files_tensors_and_metadata(tiny_file):
+    from splash_b200 import gguf
+    path, cfg, w, start = tiny_file
+    f = gguf.GgufFile(path)
+    tensors = {t["name"]: t for t in f.tensors()}
+    assert len(tensors) == 3 + sum(11 if (l + 1) % 4 == 0 else 14 for l in range(cfg["layers"]))
+    t = tensors["blk.3.attn_k.weight"]
+    q = cfg["q_heads"] * cfg["head_dim"] * 2
+    assert t["type"] == 12 and t["dims"] == [cfg["hidden"], cfg["kv_heads"] * cfg["head_dim"]]
+    assert np.array_equal(t["data"].reshape(-1), w[3, "in_proj"][q:q + cfg["kv_heads"] * cfg["head_dim"]].reshape(-1))
+    t = f.find("blk.0.ssm_conv1d.weight")
+    assert t["type"] == 0 and t["dims"] == [4, (2 * 4 + 8) * 128] and len(t["data"]) == 4 * 4 * 2048
+    assert f.find("blk.0.nothing") is None
+    # every tensor starts on the file's alignment, inside the file
+    raw = open(path, "rb").read()
+    for t in tensors.values():
+        at = t["data"].ctypes.data - tensors["token_embd.weight"]["data"].ctypes.data
+        assert at % 32 == 0 and raw[start + at:start + at + 16] == bytes(t["data"][:16])
+    assert f.meta("general.architecture") == "qwen35" and f.meta("qwen35.block_count") == 4
+    assert f.meta("qwen35.rope.freq_base") == 1e6 and f.meta("general.alignment") == 32
+    assert f.meta("some.negative") == 2 ** 64 - 7 and f.meta("some.flag") == 1 and f.meta("no.such.key") is None
+    f.close()
+
+
+def test_reader_makes_the_targets_configuration(tiny_file):
+    from splash_b200 import gguf
+    path, cfg, w, _ = tiny_file
+    got = gguf.GgufFile(path).target_config(page_tokens=cfg["page_tokens"], kv_scale_f16=cfg["kv_scale_f16"], max_context=cfg["max_context"])
+    for key, value in cfg.items():
+        assert got[key] == value, key
+    assert got["moe_experts"] == 0 and got["lanes"] == 0
+
+
+def test_reader_refuses_what_is_not_a_readable_gguf(tmp_path):
+    from splash_b200 import gguf, lib
+    one = [("t", 0, [4], np.arange(4, dtype=np.float32))]
+    meta = [("general.architecture", gw.STRING, "llama")]
+    cases = {}
+    gw.write(tmp_path / "magic.gguf", meta, one, magic=b"GGML")
+    cases["magic.gguf"] = "magic"
+    gw.write(tmp_path / "version.gguf", meta, one, version=2)
+    cases["version.gguf"] = "version 2"
+    gw.write(tmp_path / "type.gguf", meta, [("t", 99, [4], np.arange(4, dtype=np.float32))])
+    cases["type.gguf"] = "cannot size"
+    gw.write(tmp_path / "blocks.gguf", meta, [("t", 12, [100, 2], np.zeros(288, np.uint8))])
+    cases["blocks.gguf"] = "whole Q4_K blocks"
+    gw.write(tmp_path / "twice.gguf", meta, one + one)
+    cases["twice.gguf"] = "two tensors named t"
+    gw.write(tmp_path / "whole.gguf", meta, [("t", 0, [1024], np.zeros(1024, np.float32))])
+    raw = open(tmp_path / "whole.gguf", "rb").read()
+    open(tmp_path / "cut.gguf", "wb").write(raw[:-64])
+    cases["cut.gguf"] = "past the end"
+    open(tmp_path / "header.gguf", "wb").write(raw[:40])
+    cases["header.gguf"] = "past the end"
+    open(tmp_path / "short.gguf", "wb").write(b"GGUF")
+    cases["short.gguf"] = "too short"
+    for name, words in cases.items():
+        with pytest.raises(lib.SbError, match=words):
+            gguf.GgufFile(tmp_path / name)
+    with pytest.raises(lib.SbError, match="cannot open"):
+        gguf.GgufFile(tmp_path / "absent.gguf")
+    # a readable file of another architecture gives no target configuration
+    with pytest.raises(lib.SbError, match="architecture is 'llama'"):
+        gguf.GgufFile(tmp_path / "whole.gguf").target_config()
+
+
+@pytest.mark.gpu
+def test_loader_fills_a_target_that_steps_like_the_oracle(tiny_file):
+    from splash_b200 import gguf, lib
+    lib.init(0)
+    path, cfg, w, _ = tiny_file
+    t, f = gguf.load_target(path, page_tokens=cfg["page_tokens"], kv_scale_f16=cfg["kv_scale_f16"], max_context=cfg["max_context"])
+    for (layer, name), want in w.items():
+        got = t.download(layer, name, want.dtype, want.shape)
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (layer, name)
+    s = mo.make_state(cfg, 1000, 5)
+    mo.upload(t, {}, s)
+    t.reset(1000)
+    tokens = mo.draft_chain(cfg, w, s, 17, rows=16, seed=0)
+    want = mo.verify_step(cfg, w, s, tokens, advance=True)
+    t.verify(tokens, flags=1)
+    assert lib.device_status() == 0
+    logits = t.download(-1, "logits", np.float32, (16, cfg["vocab"]))
+    scale = np.abs(want["logits"]).max()
+    assert np.abs(logits - want["logits"]).max() <= 2e-2 * scale and np.median(np.abs(logits - want["logits"])) <= 2e-3 * scale
+
+
+@pytest.mark.gpu
+def test_loader_refuses_files_that_do_not_fit_the_target(tiny_file, tmp_path):
+    from splash_b200 import gguf, lib, target
+    lib.init(0)
+    path, cfg, w, _ = tiny_file
+    runtime = dict(page_tokens=cfg["page_tokens"], kv_scale_f16=cfg["kv_scale_f16"], max_context=cfg["max_context"])
+    f = gguf.GgufFile(path)
+    # another model's target
+    other = target.Target(**dict(cfg, q_heads=4))
+    assert f.l.sb_target_load_gguf(other.handle, f.handle) == -1 and b"query heads" in f.l.sb_last_error()
+    other.close()
+    # a tensor missing; a tensor of another format than the target's projections (Q4_K_M files mix Q4_K and Q6_K)
+    missing = str(tmp_path / "missing.gguf")
+    model_to_gguf(missing, cfg, w, drop=("blk.1.ssm_a",))
+    with pytest.raises(lib.SbError, match="no tensor blk.1.ssm_a"):
+        gguf.load_target(missing, **runtime)
+    import quant_fixtures as qf
+    mixed = str(tmp_path / "mixed.gguf")
+    v_rows = cfg["kv_heads"] * cfg["head_dim"]
+    model_to_gguf(mixed, cfg, w, replace={"blk.3.attn_v.weight": (gw.GGML["Q6_K"], [cfg["hidden"], v_rows], qf.realistic(4, v_rows, cfg["hidden"], seed=1))})
+    with pytest.raises(lib.SbError, match="blk.3.attn_v.weight is Q6_K"):
+        gguf.load_target(mixed, **runtime)
+    # a type that no kernel here reads
+    q5 = str(tmp_path / "q5.gguf")
+    model_to_gguf(q5, cfg, w, replace={"blk.0.attn_qkv.weight": (gw.GGML["Q5_K"], [cfg["hidden"], 2048], np.zeros(2048 * 4 * 176, np.uint8))})
+    with pytest.raises(lib.SbError, match="Q5_K, which no kernel"):
+        gguf.load_target(q5, **runtime)
