@@ -338,7 +338,7 @@ int sb_gguf_target_config(void *file, SbTargetConfig *config) {
     c.fmt_proj = format(proj);
     if (arch == "qwen35moe") {
       c.moe_experts = u("expert_count"), c.moe_top_k = u("expert_used_count"), c.moe_intermediate = u("expert_feed_forward_length");
-      c.intermediate = 0;
+      c.intermediate = c.moe_intermediate;  // (a MoE target does not use it, but a target's configuration holds a width)
       c.fmt_down = c.fmt_proj;
     } else {
       c.moe_experts = c.moe_top_k = c.moe_intermediate = 0;
@@ -371,7 +371,8 @@ int sb_target_load_gguf(void *target, void *file) {
       if (a != b) throw GgufError(std::string("the GGUF's ") + what + " is " + std::to_string(b) + ", the target's " + std::to_string(a));
     };
     same("layers", c.layers, g.layers), same("hidden size", c.hidden, g.hidden), same("vocabulary", c.vocab, g.vocab);
-    same("intermediate size", c.moe_experts ? 0 : c.intermediate, g.intermediate), same("query heads", c.q_heads, g.q_heads), same("KV heads", c.kv_heads, g.kv_heads);
+    if (!c.moe_experts) same("intermediate size", c.intermediate, g.intermediate);
+    same("query heads", c.q_heads, g.q_heads), same("KV heads", c.kv_heads, g.kv_heads);
     same("head dimension", c.head_dim, g.head_dim), same("rotary pairs", c.rotary_pairs, g.rotary_pairs), same("GDN key heads", c.gdn_key_heads, g.gdn_key_heads);
     same("GDN value heads", c.gdn_value_heads, g.gdn_value_heads), same("attention interval", c.attention_interval, g.attention_interval);
     same("experts", c.moe_experts, g.moe_experts), same("experts per token", c.moe_top_k, g.moe_top_k), same("expert width", c.moe_intermediate, g.moe_intermediate);

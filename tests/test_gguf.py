@@ -46,6 +46,9 @@ def model_to_gguf(path, cfg, w, arch="qwen35", drop=(), replace=None):
             (a + "ssm.state_size", gw.U32, 128), (a + "ssm.inner_size", gw.U32, VW),
             ("tokenizer.ggml.tokens", gw.ARRAY, (gw.STRING, ["<a>", "<b>", "<c>"])), ("tokenizer.ggml.scores", gw.ARRAY, (gw.F32, [0.5, -1.0, 2.0])),
             ("some.negative", gw.I32, -7), ("some.flag", gw.BOOL, 1)]
+    if cfg.get("moe_experts"):
+        meta += [(a + "expert_count", gw.U32, cfg["moe_experts"]), (a + "expert_used_count", gw.U32, cfg["moe_top_k"]),
+                 (a + "expert_feed_forward_length", gw.U32, cfg["moe_intermediate"])]
     tensors = []
 
     def quantized(name, fmt, rows, k):
@@ -83,6 +86,16 @@ def model_to_gguf(path, cfg, w, arch="qwen35", drop=(), replace=None):
             floats(p + "ssm_dt.bias", ungroup(ol.bf2f(w[l, "ssm_dt_bias"]), 0, 1, KH, per_key))
             floats(p + "ssm_norm.weight", w[l, "ssm_norm"])
             quantized(p + "ssm_out.weight", cfg["fmt_proj"], w[l, "out_proj"], VW)
+        if cfg.get("moe_experts"):
+            E, I = cfg["moe_experts"], cfg["moe_intermediate"]
+            floats(p + "ffn_gate_inp.weight", w[l, "ffn_router"], [H, E])
+            floats(p + "ffn_gate_inp_shexp.weight", w[l, "ffn_shared_gate"])
+            kind = FMT_TO_GGML[cfg["fmt_proj"]]
+            for part, rows_, k in (("gate", I, H), ("up", I, H), ("down", H, I)):
+                stacked = w[l, f"ffn_{part}_exps"]
+                tensors.append((p + f"ffn_{part}_exps.weight", kind, [k, rows_, E], stacked[:E * rows_]))
+                quantized(p + f"ffn_{part}_shexp.weight", cfg["fmt_proj"], stacked[E * rows_:], k)
+            continue
         quantized(p + "ffn_gate.weight", cfg["fmt_proj"], w[l, "ffn_gate"], H)
         quantized(p + "ffn_up.weight", cfg["fmt_proj"], w[l, "ffn_up"], H)
         quantized(p + "ffn_down.weight", cfg["fmt_down"], w[l, "ffn_down"], cfg["intermediate"])
@@ -215,3 +228,29 @@ def test_loader_refuses_files_that_do_not_fit_the_target(tiny_file, tmp_path):
     model_to_gguf(q5, cfg, w, replace={"blk.0.attn_qkv.weight": (gw.GGML["Q5_K"], [cfg["hidden"], 2048], np.zeros(2048 * 4 * 176, np.uint8))})
     with pytest.raises(lib.SbError, match="Q5_K, which no kernel"):
         gguf.load_target(q5, **runtime)
+
+
+@pytest.mark.gpu
+def test_loader_fills_a_moe_target_that_steps_like_the_oracle(tmp_path):
+    """A qwen35moe file: router, stacked routed experts (one tensor of three extents each) and the shared expert."""
+    from splash_b200 import gguf, lib
+    lib.init(0)
+    cfg = dict(tiny_config(), moe_experts=16, moe_top_k=4, moe_intermediate=256)
+    w = mo.make_weights(cfg, 6)
+    path = str(tmp_path / "moe.gguf")
+    model_to_gguf(path, cfg, w, arch="qwen35moe")
+    t, f = gguf.load_target(path, page_tokens=cfg["page_tokens"], kv_scale_f16=cfg["kv_scale_f16"], max_context=cfg["max_context"])
+    assert t.config["moe_experts"] == 16 and t.config["moe_top_k"] == 4 and t.config["moe_intermediate"] == 256
+    for (layer, name), want in w.items():
+        got = t.download(layer, name, want.dtype, want.shape)
+        assert np.array_equal(got.view(np.uint8), want.view(np.uint8)), (layer, name)
+    s = mo.make_state(cfg, 500, 5)
+    mo.upload(t, {}, s)
+    t.reset(500)
+    tokens = mo.draft_chain(cfg, w, s, 17, rows=16, seed=0)
+    want = mo.verify_step(cfg, w, s, tokens, advance=True)
+    t.verify(tokens, flags=1)
+    assert lib.device_status() == 0
+    logits = t.download(-1, "logits", np.float32, (16, cfg["vocab"]))
+    scale = np.abs(want["logits"]).max()
+    assert np.abs(logits - want["logits"]).max() <= 2e-2 * scale and np.median(np.abs(logits - want["logits"])) <= 2e-3 * scale
