@@ -696,7 +696,9 @@ SB_API int sb_target_destroy(void *target);
  * in_proj, out_proj, ffn_gate, ffn_up, ffn_down, and for GDN layers ssm_ab, ssm_conv, ssm_a, ssm_dt_bias, ssm_norm,
  * state0/1, conv0/1, for attention layers q_norm, k_norm, kv_k, kv_v, kv_ks, kv_vs. Global (layer = -1):
  * token_embd, output_norm, output, logits, selected, results, hidden, tokens, uniforms, committed, penalty_words,
- * candidates, candidate_q, draws. */
+ * candidates, candidate_q, draws. The tensors a checkpoint fuses into in_proj are also reached one by one under their
+ * GGUF stems, in the order of in_proj's rows: attn_q, attn_k, attn_v (attention layers), attn_qkv, attn_gate (GDN layers);
+ * a target whose parts differ in format (sb_target_create_from_gguf) has only those, no in_proj. */
 SB_API int sb_target_tensor(void *target, int layer, const char *name, void **out_dev, uint64_t *out_bytes);
 /* The lane's sampling penalties (ops::SamplingPenalties, runtime/ops/Sampling.hpp:16-29; 1, 0, 0 switches them off): the
  * step then rewrites the logits in place before selection (sb_sample_penalize) from the table `penalty_words` (u32
@@ -761,13 +763,23 @@ SB_API int sb_gguf_meta_str(void *file, const char *key, const char **out);
  * feed_forward_length; the vocabulary from token_embd; fmt_* from the tensors' types; gated_attention from attn_q's rows;
  * tiled_heads = 1) and leaves the rest (page_tokens, kv_scale_f16, max_context, lanes, tp_*, ep_*) as the caller set them. */
 SB_API int sb_gguf_target_config(void *file, SbTargetConfig *config);
+/* The weight format (SB_FMT_*) of the rows behind a weight tensor's name of sb_target_tensor. */
+SB_API int sb_target_tensor_format(void *target, int layer, const char *name, uint32_t *out_format);
+/* A target made for the file and filled from it: the configuration of sb_gguf_target_config over *runtime (whose model
+ * fields are ignored), and every projection tensor in the format the file stores it in, layer by layer - so a file that
+ * mixes formats loads (llama.cpp's Q4_K_M keeps attn_v and half of the ffn_down tensors in Q6_K). Where the tensors fused
+ * into a layer's input projection differ in format, the projection runs as one launch a tensor, each writing its columns
+ * (the reference's fused column segments, runtime/ops/LinearGguf.cpp:25,78-86). ffn_gate and ffn_up of a layer share one
+ * format; every type must be one a kernel reads (Q4_K, Q6_K, Q8_0). Not with tensor parallelism. */
+SB_API int sb_target_create_from_gguf(void *file, const SbTargetConfig *runtime, void **out_target);
 /* Copies the file's tensors into the target's (whole model on one GPU): names, shapes and conversions as
  * runtime/model/GgufImage.cpp:477-556 - attn_q / attn_k / attn_v (or attn_qkv and attn_gate) into the fused input
  * projection, ssm_beta / ssm_alpha into the fp32 gate rows, ssm_conv1d and ssm_dt.bias narrowed to bf16, the rows that
  * carry a value head gathered from llama.cpp's tiled head order into grouped order, stacked experts with the shared
- * expert last. A target has one weight format for its projections, one for the down projections, one for the head and
- * one for the embedding: a tensor of another type is refused by name (so are types no kernel here reads, e.g. Q5_K),
- * and so is a file whose metadata differs from the target's configuration. Synchronous. */
+ * expert last. A tensor whose type is not the format the target holds it in is refused by name (a target of sb_target_create
+ * has one format for its projections, one for the down projections, one for the head and one for the embedding), so are
+ * types no kernel here reads (e.g. Q5_K), and so is a file whose metadata differs from the target's configuration.
+ * Synchronous. */
 SB_API int sb_target_load_gguf(void *target, void *file);
 
 SB_API int sb_target_stats(void *target, uint32_t rows, uint32_t *out_launches, uint64_t *out_weight_bytes, uint64_t *out_kv_bytes,

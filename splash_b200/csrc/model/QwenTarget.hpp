@@ -17,6 +17,8 @@
 #include "../ops/Glue.hpp"
 #include "../ops/Linear.hpp"
 #include "../ops/MoE.hpp"
+#include <functional>
+
 #include "../ops/PagedAttention.hpp"
 #include "../ops/Sampling.hpp"
 #include "../ops/ExpertParallel.hpp"
@@ -30,6 +32,17 @@ struct LayerWeights {
   bool attention = false;
   ops::NormWeights attnNorm, ffnNorm;
   ops::QuantizedSegment inProj, outProj, ffnGate, ffnUp, ffnDown;
+  // The input projection fuses several tensors of a checkpoint (attn_q | attn_k | attn_v, or attn_qkv | attn_gate). Where
+  // their formats differ (a Q4_K_M file keeps attn_v in Q6_K) it is held as one segment per tensor, each writing its
+  // columns of the fused output in a launch of its own, and inProj stays empty (the reference's fused column segments,
+  // runtime/ops/LinearGguf.cpp:25,78-86).
+  std::vector<ops::QuantizedSegment> inParts;
+  std::vector<const ops::QuantizedSegment *> inSegments() const {
+    std::vector<const ops::QuantizedSegment *> v;
+    if (inParts.empty()) v.push_back(&inProj);
+    for (const ops::QuantizedSegment &part : inParts) v.push_back(&part);
+    return v;
+  }
   ops::MoeWeights moe;  // MoE feed-forward block (then ffnGate / ffnUp / ffnDown are empty)
   // GDN
   Buffer ssmAb, ssmConv, ssmA, ssmDtBias, ssmNorm;
@@ -75,7 +88,13 @@ inline SbTargetShare shareOf(const SbTargetConfig &c) {
 
 class QwenTarget {
  public:
-  explicit QwenTarget(const SbTargetConfig &whole);
+  // formatOf (optional): the weight format of a checkpoint tensor of a layer by its GGUF stem ("attn_q", "attn_k", "attn_v",
+  // "attn_qkv", "attn_gate", "attn_output", "ssm_out", "ffn_gate", "ffn_up", "ffn_down"), given the configuration's format
+  // for its kind; without it every tensor takes the configuration's.
+  using FormatOf = std::function<uint32_t(uint32_t layer, const char *stem, uint32_t configured)>;
+  explicit QwenTarget(const SbTargetConfig &whole, const FormatOf &formatOf = {});
+  // The format of the rows behind a weight tensor's name (find), SB_FMT_F32 for the fp32 tensors; false for no such tensor.
+  bool formatOfTensor(int layer, const std::string &name, uint32_t &format) const;
 
   // Appends one verify step of `rows` rows to the graph. `parity` selects which GDN cell is current.
   // `treeGiven`: the `tree` buffer holds the block's rows (a tree); otherwise the step writes a chain's there.
@@ -94,6 +113,7 @@ class QwenTarget {
   // Exchanges of one step: one after every out_proj and down, one for the logits.
   uint32_t exchangesPerStep() const { return 2 * cfg_.layers + 1; }
   bool find(int layer, const std::string &name, Buffer &out) const;
+  std::vector<struct InputPart> inputParts(const LayerWeights &w) const;
   std::vector<LayerWeights> &layers() { return layers_; }
 
   // Bytes one step streams: weights once, the visible INT8 cache, the GDN state in and out.
@@ -126,7 +146,10 @@ class QwenTarget {
   void buildImages(void *stream) {
     if (wide_)
       for (LayerWeights &w : layers_)
-        for (const ops::QuantizedSegment *s : {&w.inProj, &w.outProj, &w.ffnGate, &w.ffnUp, &w.ffnDown}) ops::Linear::buildImage(stream, *s);
+      {
+        for (const ops::QuantizedSegment *s : {&w.outProj, &w.ffnGate, &w.ffnUp, &w.ffnDown}) ops::Linear::buildImage(stream, *s);
+        for (const ops::QuantizedSegment *s : w.inSegments()) ops::Linear::buildImage(stream, *s);
+      }
     if (wide_) ops::Linear::buildImage(stream, output_);
     imagesStale = false;
   }
@@ -154,6 +177,8 @@ class QwenTarget {
   uint32_t packedStride_ = 0;
   uint32_t lanes_ = 1, pagesPerLane_ = 0;
   bool wide_ = false;  // the step runs on the many-row projection kernel (several lanes, or NVFP4 projections)
+  bool mixedInputs_ = false;  // some layer's input projection is held as segments of several formats (LayerWeights::inParts)
+  Buffer preparedOther_;      // then: the layer's input converted for the other fragment layout
   Buffer widePrepared_[2], widePartials_;  // conversions for the many-row projection kernel (steps of several lanes)
   void encodeVerifyLanes(CommandGraph &graph, uint32_t rows, float temperature, uint32_t parity, bool advance, bool treeGiven, bool keepPending,
                          bool drawsGiven);
@@ -176,7 +201,7 @@ inline ops::QuantizedSegment QwenTarget::segment(uint32_t n, uint32_t k, uint32_
   return s;
 }
 
-inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(whole) {
+inline QwenTarget::QwenTarget(const SbTargetConfig &whole, const FormatOf &formatOf) : cfg_(whole), loc_(whole) {
   share_ = shareOf(whole);
   loc_.q_heads = share_.q_heads, loc_.kv_heads = share_.kv_heads, loc_.gdn_key_heads = share_.gdn_key_heads;
   loc_.gdn_value_heads = share_.gdn_value_heads, loc_.intermediate = share_.intermediate;
@@ -226,10 +251,29 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
     w.attention = (l + 1) % c.attention_interval == 0;
     w.attnNorm.buffer = floats(H), w.ffnNorm.buffer = floats(H);
     weightBytes_ += 2 * size_t(H) * 4;
+    auto fmt = [&](const char *stem, uint32_t configured) { return formatOf ? formatOf(l, stem, configured) : configured; };
+    // The fused input projection of `parts` (stem, rows): one segment when the tensors share a format, else one a tensor.
+    auto fused = [&](std::initializer_list<std::pair<const char *, uint32_t>> parts) {
+      bool same = true;
+      uint32_t total = 0;
+      for (const auto &[stem, n] : parts) same = same && fmt(stem, c.fmt_proj) == fmt(parts.begin()->first, c.fmt_proj), total += n;
+      if (same) {
+        w.inProj = segment(total, H, fmt(parts.begin()->first, c.fmt_proj));
+        return;
+      }
+      if (whole.tp_world > 1) throw std::invalid_argument("QwenTarget: an input projection of several formats is not divided over tensor-parallel ranks");
+      uint32_t at = 0;
+      for (const auto &[stem, n] : parts) {
+        w.inParts.push_back(segment(n, H, fmt(stem, c.fmt_proj)));
+        w.inParts.back().columnOffset = at;
+        at += n;
+      }
+      mixedInputs_ = true;
+    };
     if (w.attention) {
       ++kv_.attentionLayers;
-      w.inProj = segment(attnIn, H, c.fmt_proj);
-      w.outProj = segment(H, c.q_heads * D, c.fmt_proj);
+      fused({{"attn_q", c.q_heads * (c.gated_attention ? 2 * D : D)}, {"attn_k", c.kv_heads * D}, {"attn_v", c.kv_heads * D}});
+      w.outProj = segment(H, c.q_heads * D, fmt("attn_output", c.fmt_proj));
       w.qNorm = floats(D), w.kNorm = floats(D);
       w.pages.pages = pages;
       w.pages.keys = Buffer::allocate(pages * kv_.dataBytesPerLayerPage());
@@ -237,8 +281,8 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
       w.pages.keyScales = Buffer::allocate(pages * kv_.scaleBytesPerLayerPage());
       w.pages.valueScales = Buffer::allocate(pages * kv_.scaleBytesPerLayerPage());
     } else {
-      w.inProj = segment(gdnIn, H, c.fmt_proj);
-      w.outProj = segment(H, gdn_.valueWidth(), c.fmt_proj);
+      fused({{"attn_qkv", gdn_.convolutionWidth()}, {"attn_gate", gdn_.valueWidth()}});
+      w.outProj = segment(H, gdn_.valueWidth(), fmt("ssm_out", c.fmt_proj));
       w.ssmAb = floats(size_t(2) * gdn_.valueHeads * H);
       weightBytes_ += size_t(2) * gdn_.valueHeads * H * 4;
       w.ssmConv = Buffer::allocate(size_t(gdn_.convolutionWidth()) * 4 * 2);
@@ -258,9 +302,11 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
       moeExpertBytes_ = (2 * pair + down) / total;
       ++moeLayers_;
     } else {
-      w.ffnGate = segment(c.intermediate, H, c.fmt_proj);
-      w.ffnUp = segment(c.intermediate, H, c.fmt_proj);
-      w.ffnDown = segment(H, c.intermediate, c.fmt_down);
+      if (fmt("ffn_gate", c.fmt_proj) != fmt("ffn_up", c.fmt_proj))
+        throw std::invalid_argument("QwenTarget: a layer's ffn_gate and ffn_up tensors share one format (they run as one launch)");
+      w.ffnGate = segment(c.intermediate, H, fmt("ffn_gate", c.fmt_proj));
+      w.ffnUp = segment(c.intermediate, H, fmt("ffn_up", c.fmt_proj));
+      w.ffnDown = segment(H, c.intermediate, fmt("ffn_down", c.fmt_down));
     }
   }
   embedding_.rows = Buffer::allocate(size_t(c.vocab) * sb_row_bytes(c.fmt_embed, H));
@@ -279,6 +325,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole) : cfg_(whole), loc_(w
   partials_ = Buffer::allocate(size_t(kMaxPartialSlices) * 16 * H * 4);
   const uint32_t widest = std::max(std::max(H, c.intermediate), std::max(gdn_.valueWidth(), c.q_heads * D));
   for (auto &p : prepared_) p = Buffer::allocate(ops::Linear::preparedBytes((widest + 255) / 256 * 256));
+  if (mixedInputs_) preparedOther_ = Buffer::allocate(ops::Linear::preparedBytes(H));
   if (wide_) {
     for (auto &p : widePrepared_) p = Buffer::allocate(ops::Linear::wideBytes(uint32_t(R), (widest + 255) / 256 * 256));
     const uint32_t splits = std::max(ops::Linear::wideSplits(H, c.intermediate), std::max(ops::Linear::wideSplits(H, gdn_.valueWidth()), ops::Linear::wideSplits(H, c.q_heads * D)));
@@ -313,6 +360,55 @@ inline uint64_t QwenTarget::stateBytes() const {
   return gdnLayers * 2 * gdn_.stateBytes() * lanes_;
 }
 
+// The checkpoint tensors behind a layer's input projection: their stems, rows (a view of the fused segment, or the
+// tensor's own segment) and formats, in the order of the fused output's columns.
+struct InputPart {
+  const char *stem;
+  Buffer rows;
+  uint32_t format;
+};
+inline std::vector<InputPart> QwenTarget::inputParts(const LayerWeights &w) const {
+  const SbTargetConfig &c = loc_;
+  const uint32_t D = c.head_dim;
+  std::vector<std::pair<const char *, uint32_t>> parts;
+  if (w.attention) parts = {{"attn_q", c.q_heads * (c.gated_attention ? 2 * D : D)}, {"attn_k", c.kv_heads * D}, {"attn_v", c.kv_heads * D}};
+  else parts = {{"attn_qkv", gdn_.convolutionWidth()}, {"attn_gate", gdn_.valueWidth()}};
+  std::vector<InputPart> out;
+  size_t at = 0;
+  for (size_t i = 0; i < parts.size(); ++i) {
+    if (!w.inParts.empty()) {
+      out.push_back({parts[i].first, w.inParts[i].rows, w.inParts[i].format});
+      continue;
+    }
+    const size_t bytes = size_t(parts[i].second) * sb_row_bytes(w.inProj.format, c.hidden);
+    out.push_back({parts[i].first, w.inProj.rows.view(at, bytes), w.inProj.format});
+    at += bytes;
+  }
+  return out;
+}
+inline bool QwenTarget::formatOfTensor(int layer, const std::string &name, uint32_t &format) const {
+  if (layer < 0) {
+    if (name == "token_embd") format = cfg_.fmt_embed;
+    else if (name == "output") format = output_.format;
+    else return false;
+    return true;
+  }
+  if (size_t(layer) >= layers_.size()) return false;
+  const LayerWeights &w = layers_[layer];
+  for (const InputPart &part : inputParts(w))
+    if (name == part.stem) return format = part.format, true;
+  if (name == "in_proj" && w.inParts.empty()) return format = w.inProj.format, true;
+  if (name == "out_proj") return format = w.outProj.format, true;
+  if (cfg_.moe_experts) {
+    if (name == "ffn_gate_exps" || name == "ffn_up_exps" || name == "ffn_down_exps") return format = cfg_.fmt_proj, true;
+    return false;
+  }
+  if (name == "ffn_gate") return format = w.ffnGate.format, true;
+  if (name == "ffn_up") return format = w.ffnUp.format, true;
+  if (name == "ffn_down") return format = w.ffnDown.format, true;
+  return false;
+}
+
 inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) const {
   if (layer < 0) {
     const std::map<std::string, Buffer> g = {{"token_embd", embedding_.rows}, {"output_norm", outputNorm_.buffer}, {"output", output_.rows},
@@ -329,9 +425,12 @@ inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) co
   }
   if (size_t(layer) >= layers_.size()) return false;
   const LayerWeights &w = layers_[layer];
-  std::map<std::string, Buffer> m = {{"attn_norm", w.attnNorm.buffer}, {"ffn_norm", w.ffnNorm.buffer}, {"in_proj", w.inProj.rows},
+  std::map<std::string, Buffer> m = {{"attn_norm", w.attnNorm.buffer}, {"ffn_norm", w.ffnNorm.buffer},
                                      {"out_proj", w.outProj.rows}, {"ffn_gate", w.ffnGate.rows}, {"ffn_up", w.ffnUp.rows},
                                      {"ffn_down", w.ffnDown.rows}};
+  // The fused input projection whole (when it is one segment) and tensor by tensor under the checkpoint's stems.
+  for (const InputPart &part : inputParts(w)) m.insert({part.stem, part.rows});
+  if (w.inParts.empty()) m.insert({"in_proj", w.inProj.rows});
   // (the images the many-row kernel reads, where a projection has one: for measurements of that kernel by itself)
   for (auto &[tensor, seg] : {std::pair<const char *, const ops::QuantizedSegment &>{"ffn_gate_image", w.ffnGate}, {"ffn_up_image", w.ffnUp}, {"ffn_down_image", w.ffnDown}})
     if (seg.image) m.insert({tensor, seg.image});
@@ -410,10 +509,26 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   };
   for (LayerWeights &w : layers_) {
     // mixer: h += mixer(norm(h))
-    PreparedInput in = convert(&w.attnNorm.buffer, w.inProj.format, prepared_[0], w.attention ? nullptr : &normed_);
-    Projection inProj{w.inProj.outputSize, H, Destination::BFloat16, {w.inProj}};
     LinearBuffers inB{Buffer(), packed_, Buffer(), H, packedStride_};
-    Linear::add(graph, inB, inProj, Linear::plan(inProj, rows, Epilogue::None), in);
+    if (w.inParts.empty()) {
+      PreparedInput in = convert(&w.attnNorm.buffer, w.inProj.format, prepared_[0], w.attention ? nullptr : &normed_);
+      Projection inProj{w.inProj.outputSize, H, Destination::BFloat16, {w.inProj}};
+      Linear::add(graph, inB, inProj, Linear::plan(inProj, rows, Epilogue::None), in);
+    } else {
+      // Segments of several formats: the input is converted once per fragment layout among them (Q4_K's, or the one
+      // Q6_K and Q8_0 share), and every segment writes its columns in a launch of its own.
+      const uint32_t first = w.inParts.front().format;
+      PreparedInput in = convert(&w.attnNorm.buffer, first, prepared_[0], w.attention ? nullptr : &normed_);
+      PreparedInput other;
+      uint32_t total = 0;
+      for (const QuantizedSegment &part : w.inParts) total += part.outputSize;
+      for (const QuantizedSegment &part : w.inParts) {
+        const bool same = (part.format == SB_FMT_Q4K) == (first == SB_FMT_Q4K);
+        if (!same && !other.buffer) other = Linear::prepare(graph, hidden[cur], rows, H, H, &w.attnNorm.buffer, part.format, preparedOther_);
+        Projection one{total, H, Destination::BFloat16, {part}};
+        Linear::add(graph, inB, one, Linear::plan(one, rows, Epilogue::None), same ? in : other);
+      }
+    }
     uint32_t mixedWidth;
     if (w.attention) {
       PagedAttention::addProjection(graph, kv_, w.pages, packed_, packedStride_, w.qNorm, w.kNorm, cosine, sine, pageTable_, queries_, rows,
@@ -515,7 +630,9 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
   for (LayerWeights &w : layers_) {
     // mixer: h += mixer(norm(h))
     PreparedInput in = convert(&w.attnNorm.buffer);
-    Linear::addWide(graph, w.inProj, nullptr, in, R, Epilogue::None, nullptr, packed_, packedStride_);
+    for (const QuantizedSegment *part : w.inSegments())  // (one segment, or one a checkpoint tensor where their formats differ)
+      Linear::addWide(graph, *part, nullptr, in, R, Epilogue::None, nullptr,
+                      part->columnOffset ? packed_.view(size_t(part->columnOffset) * 2, packed_.bytes() - size_t(part->columnOffset) * 2) : packed_, packedStride_);
     uint32_t mixedWidth;
     if (w.attention) {
       mixedWidth = c.q_heads * D;

@@ -139,12 +139,15 @@ struct Loader {
     if (cudaMemcpy(dst + offset, src, bytes, cudaMemcpyHostToDevice) != cudaSuccess) throw GgufError("copy of " + what + " to the device failed");
   }
   // Quantized rows [rows, columns] of GGUF tensor `name` into rows [row0, row0 + rows) of the target's `tensor`.
-  void rows(int layer, const char *tensor, uint64_t row0, const std::string &name, uint64_t rows_, uint64_t columns, uint32_t format, RowOrder order = {}) {
+  void rows(int layer, const char *tensor, uint64_t row0, const std::string &name, uint64_t rows_, uint64_t columns, RowOrder order = {}) {
     const GgufTensor &t = need(name);
     shape(t, rows_, columns);
+    uint32_t format = 0;
+    if (sb_target_tensor_format(target, layer, tensor, &format) != SB_OK) throw GgufError(sb_last_error());
     if (format_of(t.type) != int(format))
-      throw GgufError(name + " is " + splash::b200::model::ggmlTypeName(t.type) + " but the target holds this projection in format " + std::to_string(format) +
-                      ": a target has one format for its projections, one for its down projections, one for its head and one for its embedding");
+      throw GgufError(name + " is " + splash::b200::model::ggmlTypeName(t.type) + " but the target holds it in format " + std::to_string(format) +
+                      " (a target made by sb_target_create has one format for its projections, one for the down projections, one for the head and one for the "
+                      "embedding; sb_target_create_from_gguf takes every tensor's from the file)");
     const uint64_t rb = sb_row_bytes(format, uint32_t(columns));
     if (!rb || rb * rows_ != t.bytes) throw GgufError(name + ": rows of " + std::to_string(columns) + " inputs are not whole blocks");
     uint64_t capacity = 0;
@@ -181,17 +184,17 @@ struct Loader {
     values(int(l), "ffn_norm", 0, p + "post_attention_norm.weight", H);
     if ((l + 1) % c.attention_interval == 0) {
       const uint64_t q = uint64_t(c.q_heads) * D * (c.gated_attention ? 2 : 1), kv = uint64_t(c.kv_heads) * D;
-      rows(int(l), "in_proj", 0, p + "attn_q.weight", q, H, c.fmt_proj);
-      rows(int(l), "in_proj", q, p + "attn_k.weight", kv, H, c.fmt_proj);
-      rows(int(l), "in_proj", q + kv, p + "attn_v.weight", kv, H, c.fmt_proj);
+      rows(int(l), "attn_q", 0, p + "attn_q.weight", q, H);   // (the parts of the fused input projection, in its column order)
+      rows(int(l), "attn_k", 0, p + "attn_k.weight", kv, H);
+      rows(int(l), "attn_v", 0, p + "attn_v.weight", kv, H);
       values(int(l), "q_norm", 0, p + "attn_q_norm.weight", D);
       values(int(l), "k_norm", 0, p + "attn_k_norm.weight", D);
-      rows(int(l), "out_proj", 0, p + "attn_output.weight", H, uint64_t(c.q_heads) * D, c.fmt_proj);
+      rows(int(l), "out_proj", 0, p + "attn_output.weight", H, uint64_t(c.q_heads) * D);
     } else {
       const uint32_t KH = c.gdn_key_heads, VH = c.gdn_value_heads, per_key = VH / KH;
       const uint64_t KW = uint64_t(KH) * 128, VW = uint64_t(VH) * 128, conv = 2 * KW + VW;
-      rows(int(l), "in_proj", 0, p + "attn_qkv.weight", conv, H, c.fmt_proj, RowOrder{2 * KW, 128, KH, per_key});
-      rows(int(l), "in_proj", conv, p + "attn_gate.weight", VW, H, c.fmt_proj, RowOrder{0, 128, KH, per_key});
+      rows(int(l), "attn_qkv", 0, p + "attn_qkv.weight", conv, H, RowOrder{2 * KW, 128, KH, per_key});
+      rows(int(l), "attn_gate", 0, p + "attn_gate.weight", VW, H, RowOrder{0, 128, KH, per_key});
       const RowOrder heads{0, 1, KH, per_key};
       values(int(l), "ssm_ab", 0, p + "ssm_beta.weight", uint64_t(VH) * H, false, H, heads);
       values(int(l), "ssm_ab", uint64_t(VH) * H, p + "ssm_alpha.weight", uint64_t(VH) * H, false, H, heads);
@@ -199,7 +202,7 @@ struct Loader {
       values(int(l), "ssm_a", 0, p + "ssm_a", VH, false, 1, heads);
       values(int(l), "ssm_dt_bias", 0, p + "ssm_dt.bias", VH, true, 1, heads);
       values(int(l), "ssm_norm", 0, p + "ssm_norm.weight", 128);
-      rows(int(l), "out_proj", 0, p + "ssm_out.weight", H, VW, c.fmt_proj);
+      rows(int(l), "out_proj", 0, p + "ssm_out.weight", H, VW);
     }
     if (c.moe_experts) {
       const uint64_t E = c.moe_experts, I = c.moe_intermediate;
@@ -217,20 +220,20 @@ struct Loader {
       stacked("ffn_gate_exps", p + "ffn_gate_exps.weight", I, H);
       stacked("ffn_up_exps", p + "ffn_up_exps.weight", I, H);
       stacked("ffn_down_exps", p + "ffn_down_exps.weight", H, I);
-      rows(int(l), "ffn_gate_exps", E * I, p + "ffn_gate_shexp.weight", I, H, c.fmt_proj);   // the shared expert last
-      rows(int(l), "ffn_up_exps", E * I, p + "ffn_up_shexp.weight", I, H, c.fmt_proj);
-      rows(int(l), "ffn_down_exps", E * H, p + "ffn_down_shexp.weight", H, I, c.fmt_proj);
+      rows(int(l), "ffn_gate_exps", E * I, p + "ffn_gate_shexp.weight", I, H);   // the shared expert last
+      rows(int(l), "ffn_up_exps", E * I, p + "ffn_up_shexp.weight", I, H);
+      rows(int(l), "ffn_down_exps", E * H, p + "ffn_down_shexp.weight", H, I);
     } else {
-      rows(int(l), "ffn_gate", 0, p + "ffn_gate.weight", c.intermediate, H, c.fmt_proj);
-      rows(int(l), "ffn_up", 0, p + "ffn_up.weight", c.intermediate, H, c.fmt_proj);
-      rows(int(l), "ffn_down", 0, p + "ffn_down.weight", H, c.intermediate, c.fmt_down);
+      rows(int(l), "ffn_gate", 0, p + "ffn_gate.weight", c.intermediate, H);
+      rows(int(l), "ffn_up", 0, p + "ffn_up.weight", c.intermediate, H);
+      rows(int(l), "ffn_down", 0, p + "ffn_down.weight", H, c.intermediate);
     }
   }
   void all() {
-    rows(-1, "token_embd", 0, "token_embd.weight", c.vocab, c.hidden, c.fmt_embed);
+    rows(-1, "token_embd", 0, "token_embd.weight", c.vocab, c.hidden);
     values(-1, "output_norm", 0, "output_norm.weight", c.hidden);
     // A GGUF without an output tensor ties the head to the embedding.
-    rows(-1, "output", 0, file.find("output.weight") ? "output.weight" : "token_embd.weight", c.vocab, c.hidden, c.fmt_head);
+    rows(-1, "output", 0, file.find("output.weight") ? "output.weight" : "token_embd.weight", c.vocab, c.hidden);
     for (uint32_t l = 0; l < c.layers; ++l) layer(l);
   }
 };
@@ -352,6 +355,42 @@ int sb_gguf_target_config(void *file, SbTargetConfig *config) {
       if (q_rows != uint64_t(c.q_heads) * c.head_dim && q_rows != 2ull * c.q_heads * c.head_dim) throw GgufError("attn_q holds neither the heads' queries nor queries and gates");
       c.gated_attention = q_rows == 2ull * c.q_heads * c.head_dim;
     }
+    return int(SB_OK);
+  });
+}
+
+int sb_target_create_with_formats(const SbTargetConfig *config, uint32_t (*format_of)(void *, uint32_t, const char *, uint32_t), void *context, void **out_target);
+
+int sb_target_create_from_gguf(void *file, const SbTargetConfig *runtime, void **out_target) {
+  SB_NEED_DEVICE();
+  if (!file || !runtime || !out_target) return sb::fail(SB_ERR_INVALID, "sb_target_create_from_gguf: null pointer");
+  return host_guarded([&] {
+    SbTargetConfig c = *runtime;
+    int st = sb_gguf_target_config(file, &c);
+    if (st != SB_OK) return st;
+    const GgufFile &f = *static_cast<OpenFile *>(file)->file;
+    // Every projection tensor's type is one a kernel reads: checked here, so that the formats' lookup below cannot fail.
+    for (const GgufTensor &t : f.tensors())
+      if (t.dims.size() >= 2 && t.name.rfind("blk.", 0) == 0 && t.name.size() > 7 && t.name.compare(t.name.size() - 7, 7, ".weight") == 0 &&
+          t.name.find("ssm_conv1d") == std::string::npos && t.name.find("ssm_alpha") == std::string::npos && t.name.find("ssm_beta") == std::string::npos &&
+          t.name.find("ffn_gate_inp") == std::string::npos && format_of(t.type) < 0)
+        throw GgufError(t.name + " is " + splash::b200::model::ggmlTypeName(t.type) + ", which no kernel of this library reads");
+    auto lookup = [](void *context, uint32_t layer, const char *stem, uint32_t configured) -> uint32_t {
+      const GgufFile &file_ = *static_cast<const GgufFile *>(context);
+      const GgufTensor *t = file_.find("blk." + std::to_string(layer) + "." + stem + ".weight");
+      const int fmt = t ? format_of(t->type) : -1;
+      return fmt < 0 ? configured : uint32_t(fmt);  // (a missing tensor is reported by name when the file is loaded)
+    };
+    void *target = nullptr;
+    st = sb_target_create_with_formats(&c, lookup, const_cast<GgufFile *>(&f), &target);
+    if (st != SB_OK) return st;
+    st = sb_target_load_gguf(target, file);
+    if (st != SB_OK) {
+      const std::string message = sb_last_error();
+      sb_target_destroy(target);
+      return sb::fail(st, "%s", message.c_str());
+    }
+    *out_target = target;
     return int(SB_OK);
   });
 }

@@ -190,12 +190,20 @@ template <class F> static int guarded(F body) {
 
 extern "C" {
 
-int sb_target_create(const SbTargetConfig *config, void **out_target) {
+// The format of a checkpoint tensor, for a target whose tensors take their formats from a checkpoint (sb_gguf.cu).
+using TensorFormat = uint32_t (*)(void *context, uint32_t layer, const char *stem, uint32_t configured);
+int sb_target_create_with_formats(const SbTargetConfig *config, TensorFormat format_of, void *context, void **out_target);
+
+int sb_target_create(const SbTargetConfig *config, void **out_target) { return sb_target_create_with_formats(config, nullptr, nullptr, out_target); }
+
+int sb_target_create_with_formats(const SbTargetConfig *config, TensorFormat format_of, void *context, void **out_target) {
   SB_NEED_DEVICE();
   SB_REQUIRE(config && out_target, "sb_target_create: null pointer");
   return guarded([&] {
     auto t = std::make_unique<Target>();
-    t->model = std::make_unique<QwenTarget>(*config);
+    QwenTarget::FormatOf by_tensor;
+    if (format_of) by_tensor = [=](uint32_t layer, const char *stem, uint32_t configured) { return format_of(context, layer, stem, configured); };
+    t->model = std::make_unique<QwenTarget>(*config, by_tensor);
     const uint32_t L = std::max(1u, config->lanes);
     SB_CUDA(cudaMallocHost(&t->results_pinned, size_t(20) * L * sizeof(uint32_t)));
     SB_CUDA(cudaStreamCreateWithFlags(&t->own_stream, cudaStreamNonBlocking));
@@ -289,8 +297,14 @@ int sb_target_tensor(void *target, int layer, const char *name, void **out_dev, 
   *out_bytes = b.bytes();
   // The caller may write a projection's rows through this address: their image (Q6_K / NVFP4 on the many-row kernel) is
   // made again before the next step.
-  for (const char *w : {"in_proj", "out_proj", "ffn_gate", "ffn_up", "ffn_down", "output"})
+  for (const char *w : {"in_proj", "attn_q", "attn_k", "attn_v", "attn_qkv", "attn_gate", "out_proj", "ffn_gate", "ffn_up", "ffn_down", "output"})
     if (!strcmp(name, w)) static_cast<Target *>(target)->model->imagesStale = true;
+  return SB_OK;
+}
+
+int sb_target_tensor_format(void *target, int layer, const char *name, uint32_t *out_format) {
+  SB_REQUIRE(target && name && out_format, "sb_target_tensor_format: null pointer");
+  SB_REQUIRE(static_cast<Target *>(target)->model->formatOfTensor(layer, name, *out_format), "sb_target_tensor_format: no weight tensor '%s' in layer %d", name, layer);
   return SB_OK;
 }
 
@@ -347,7 +361,7 @@ int sb_target_randomize(void *target, uint64_t seed, uint32_t committed) {
     for (auto &w : m.layers()) {
       SB_TRY(fill(kF32Normal, w.attnNorm.buffer, c.hidden, next(), 1.0f, 0.1f));
       SB_TRY(fill(kF32Normal, w.ffnNorm.buffer, c.hidden, next(), 1.0f, 0.1f));
-      SB_TRY(fill_rows(w.inProj, next()));
+      for (const splash::b200::ops::QuantizedSegment *part : w.inSegments()) SB_TRY(fill_rows(*part, next()));
       SB_TRY(fill_rows(w.outProj, next()));
       if (c.moe_experts) {
         const uint32_t total = m.expertParallel() ? m.expertParallel()->local().expertsTotal() : c.moe_experts + 1;  // (a rank's experts)

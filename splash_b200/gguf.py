@@ -91,8 +91,17 @@ class GgufFile:
 
 
 def load_target(path, **runtime):
-    """A target created from the GGUF's configuration and filled with its tensors. Returns (target, file)."""
+    """A target created for the GGUF (its configuration, every projection tensor in the file's format) and filled with its
+    tensors; `runtime` gives the fields a file does not hold (page_tokens, kv_scale_f16, max_context, lanes). Returns
+    (target, file)."""
     f = GgufFile(path)
-    t = Target(**f.target_config(**runtime))
-    lib.check(f.l.sb_target_load_gguf(t.handle, f.handle))
-    return t, f
+    cfg = SbTargetConfig(**runtime)
+    h = _P()
+    f.l.sb_target_create_from_gguf.argtypes = [_P, ctypes.POINTER(SbTargetConfig), ctypes.POINTER(_P)]
+    lib.check(f.l.sb_target_create_from_gguf(f.handle, ctypes.byref(cfg), ctypes.byref(h)))
+    return Target.from_handle(h.value), f
+
+
+def load_into(target, f):
+    """Fills an existing target from an open GgufFile (sb_target_load_gguf)."""
+    lib.check(f.l.sb_target_load_gguf(target.handle, f.handle))

@@ -70,6 +70,24 @@ class Target:
         lib.check(self.l.sb_target_create(ctypes.byref(self.cfg), ctypes.byref(h)))
         self.handle = h.value
 
+    @classmethod
+    def from_handle(cls, handle):
+        """Wraps a target created by the library (sb_target_create_from_gguf)."""
+        self = cls.__new__(cls)
+        self.l = _bind()
+        self.handle = handle
+        self.cfg = SbTargetConfig()
+        self.l.sb_target_config.argtypes = [_P, ctypes.POINTER(SbTargetConfig)]
+        lib.check(self.l.sb_target_config(handle, ctypes.byref(self.cfg)))
+        self.config = {name: getattr(self.cfg, name) for name, _ in SbTargetConfig._fields_}
+        return self
+
+    def tensor_format(self, layer, name):
+        f = _U()
+        self.l.sb_target_tensor_format.argtypes = [_P, ctypes.c_int, ctypes.c_char_p, ctypes.POINTER(_U)]
+        lib.check(self.l.sb_target_tensor_format(self.handle, layer, name.encode(), ctypes.byref(f)))
+        return int(f.value)
+
     def close(self):
         if self.handle:
             self.l.sb_target_destroy(self.handle)

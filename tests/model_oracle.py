@@ -102,6 +102,17 @@ def upload(t, w, s, cut=lambda layer, name, array: array, lane=0):
             t.upload(layer, name, cut(layer, name, val))
 
 
+def input_projection(o, cfg, w, l, n, k, X, rows):
+    """A layer's fused input projection: one tensor `in_proj` of the configuration's format, or `in_parts`, a list of
+    (format, rows array) tensors of different formats whose outputs lie side by side."""
+    if (l, "in_parts") not in w:
+        return linear(o, cfg["fmt_proj"], w[l, "in_proj"], n, k, X, rows)
+    outs = [linear(o, fmt, part, len(part), k, X, rows) for fmt, part in w[l, "in_parts"]]
+    out = np.concatenate(outs, axis=1)
+    assert out.shape[1] == n
+    return np.ascontiguousarray(out)
+
+
 def linear(o, fmt, W, n, k, X, rows, epilogue=0, aux=None, out_f32=False, W2=None):
     out = np.zeros((rows, n), np.float32 if out_f32 else np.uint16)
     Wfull = W if W2 is None else np.concatenate([W, W2], axis=0)
@@ -142,7 +153,7 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
         o.so_rmsnorm(P(h), rows, H, H, P(w[l, "attn_norm"]), P(n1), H)
         if attention:
             attn_in = QH * (2 * D if cfg["gated_attention"] else D) + 2 * KVH * D
-            packed = linear(o, cfg["fmt_proj"], w[l, "in_proj"], attn_in, H, n1, rows)
+            packed = input_projection(o, cfg, w, l, attn_in, H, n1, rows)
             kv = s[l, "kv"]
             if not mutate:
                 import copy
@@ -157,7 +168,7 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
             mixed_w = QH * D
         else:
             gdn_in = conv + VH * 128
-            packed = linear(o, cfg["fmt_proj"], w[l, "in_proj"], gdn_in, H, n1, rows)
+            packed = input_projection(o, cfg, w, l, gdn_in, H, n1, rows)
             ab = ol.f2bf((ol.bf2f(n1).astype(np.float32) @ w[l, "ssm_ab"].T.astype(np.float32)).astype(np.float32))
             b, a = np.ascontiguousarray(ab[:, :VH]), np.ascontiguousarray(ab[:, VH:])
             cur, nxt = parity, parity ^ 1
@@ -174,7 +185,7 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
             o.so_gdn_verify(ctypes.byref(args))
             new_state[l, f"conv{nxt}"], new_state[l, f"state{nxt}"] = cs_out, st_out
             mixed_w = VH * 128
-        h = linear(o, cfg["fmt_proj"], w[l, "out_proj"], H, mixed_w, mixed, rows, epilogue=1, aux=h)
+        h = linear(o, w.get((l, "out_proj_fmt"), cfg["fmt_proj"]), w[l, "out_proj"], H, mixed_w, mixed, rows, epilogue=1, aux=h)
         n2 = np.zeros_like(h)
         o.so_rmsnorm(P(h), rows, H, H, P(w[l, "ffn_norm"]), P(n2), H)
         if cfg.get("moe_experts"):
@@ -188,7 +199,7 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
             h = out
             continue
         act = linear(o, cfg["fmt_proj"], w[l, "ffn_gate"], I, H, n2, rows, epilogue=3, W2=w[l, "ffn_up"])
-        h = linear(o, cfg["fmt_down"], w[l, "ffn_down"], H, I, act, rows, epilogue=1, aux=h)
+        h = linear(o, w.get((l, "ffn_down_fmt"), cfg["fmt_down"]), w[l, "ffn_down"], H, I, act, rows, epilogue=1, aux=h)
     nf = np.zeros_like(h)
     o.so_rmsnorm(P(h), rows, H, H, P(w[-1, "output_norm"]), P(nf), H)
     logits = linear(o, cfg["fmt_head"], w[-1, "output"], V, H, nf, rows, out_f32=True)

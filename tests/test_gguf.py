@@ -67,17 +67,24 @@ def model_to_gguf(path, cfg, w, arch="qwen35", drop=(), replace=None):
         floats(p + "post_attention_norm.weight", w[l, "ffn_norm"])
         if (l + 1) % cfg["attention_interval"] == 0:
             q, kv = cfg["q_heads"] * D * (2 if cfg["gated_attention"] else 1), cfg["kv_heads"] * D
-            rows = w[l, "in_proj"]
-            quantized(p + "attn_q.weight", cfg["fmt_proj"], rows[:q], H)
-            quantized(p + "attn_k.weight", cfg["fmt_proj"], rows[q:q + kv], H)
-            quantized(p + "attn_v.weight", cfg["fmt_proj"], rows[q + kv:], H)
+            if (l, "in_parts") in w:
+                for stem, (fmt, part) in zip(("attn_q", "attn_k", "attn_v"), w[l, "in_parts"]):
+                    quantized(p + stem + ".weight", fmt, part, H)
+            else:
+                rows = w[l, "in_proj"]
+                quantized(p + "attn_q.weight", cfg["fmt_proj"], rows[:q], H)
+                quantized(p + "attn_k.weight", cfg["fmt_proj"], rows[q:q + kv], H)
+                quantized(p + "attn_v.weight", cfg["fmt_proj"], rows[q + kv:], H)
             floats(p + "attn_q_norm.weight", w[l, "q_norm"])
             floats(p + "attn_k_norm.weight", w[l, "k_norm"])
-            quantized(p + "attn_output.weight", cfg["fmt_proj"], w[l, "out_proj"], cfg["q_heads"] * D)
+            quantized(p + "attn_output.weight", w.get((l, "out_proj_fmt"), cfg["fmt_proj"]), w[l, "out_proj"], cfg["q_heads"] * D)
         else:
-            rows = w[l, "in_proj"]
-            quantized(p + "attn_qkv.weight", cfg["fmt_proj"], ungroup(rows[:conv], 2 * KW, 128, KH, per_key), H)
-            quantized(p + "attn_gate.weight", cfg["fmt_proj"], ungroup(rows[conv:], 0, 128, KH, per_key), H)
+            if (l, "in_parts") in w:
+                (f0, qkv), (f1, gate) = w[l, "in_parts"]
+            else:
+                (f0, qkv), (f1, gate) = (cfg["fmt_proj"], w[l, "in_proj"][:conv]), (cfg["fmt_proj"], w[l, "in_proj"][conv:])
+            quantized(p + "attn_qkv.weight", f0, ungroup(qkv, 2 * KW, 128, KH, per_key), H)
+            quantized(p + "attn_gate.weight", f1, ungroup(gate, 0, 128, KH, per_key), H)
             ab = w[l, "ssm_ab"]
             floats(p + "ssm_beta.weight", ungroup(ab[:VH], 0, 1, KH, per_key), [H, VH])
             floats(p + "ssm_alpha.weight", ungroup(ab[VH:], 0, 1, KH, per_key), [H, VH])
@@ -85,7 +92,7 @@ def model_to_gguf(path, cfg, w, arch="qwen35", drop=(), replace=None):
             floats(p + "ssm_a", ungroup(w[l, "ssm_a"], 0, 1, KH, per_key))
             floats(p + "ssm_dt.bias", ungroup(ol.bf2f(w[l, "ssm_dt_bias"]), 0, 1, KH, per_key))
             floats(p + "ssm_norm.weight", w[l, "ssm_norm"])
-            quantized(p + "ssm_out.weight", cfg["fmt_proj"], w[l, "out_proj"], VW)
+            quantized(p + "ssm_out.weight", w.get((l, "out_proj_fmt"), cfg["fmt_proj"]), w[l, "out_proj"], VW)
         if cfg.get("moe_experts"):
             E, I = cfg["moe_experts"], cfg["moe_intermediate"]
             floats(p + "ffn_gate_inp.weight", w[l, "ffn_router"], [H, E])
@@ -98,7 +105,7 @@ def model_to_gguf(path, cfg, w, arch="qwen35", drop=(), replace=None):
             continue
         quantized(p + "ffn_gate.weight", cfg["fmt_proj"], w[l, "ffn_gate"], H)
         quantized(p + "ffn_up.weight", cfg["fmt_proj"], w[l, "ffn_up"], H)
-        quantized(p + "ffn_down.weight", cfg["fmt_down"], w[l, "ffn_down"], cfg["intermediate"])
+        quantized(p + "ffn_down.weight", w.get((l, "ffn_down_fmt"), cfg["fmt_down"]), w[l, "ffn_down"], cfg["intermediate"])
     tensors = [t for t in tensors if t[0] not in drop]
     if replace:                                  # name -> (ggml type, dims, data)
         tensors = [(n,) + tuple(replace[n]) if n in replace else (n, k, d, x) for n, k, d, x in tensors]
@@ -212,17 +219,20 @@ def test_loader_refuses_files_that_do_not_fit_the_target(tiny_file, tmp_path):
     other = target.Target(**dict(cfg, q_heads=4))
     assert f.l.sb_target_load_gguf(other.handle, f.handle) == -1 and b"query heads" in f.l.sb_last_error()
     other.close()
-    # a tensor missing; a tensor of another format than the target's projections (Q4_K_M files mix Q4_K and Q6_K)
+    # a tensor missing
     missing = str(tmp_path / "missing.gguf")
     model_to_gguf(missing, cfg, w, drop=("blk.1.ssm_a",))
     with pytest.raises(lib.SbError, match="no tensor blk.1.ssm_a"):
         gguf.load_target(missing, **runtime)
+    # a tensor of another format than a target of one format a kind holds (the target made for the file takes it: below)
     import quant_fixtures as qf
     mixed = str(tmp_path / "mixed.gguf")
     v_rows = cfg["kv_heads"] * cfg["head_dim"]
     model_to_gguf(mixed, cfg, w, replace={"blk.3.attn_v.weight": (gw.GGML["Q6_K"], [cfg["hidden"], v_rows], qf.realistic(4, v_rows, cfg["hidden"], seed=1))})
+    uniform = target.Target(**cfg)
     with pytest.raises(lib.SbError, match="blk.3.attn_v.weight is Q6_K"):
-        gguf.load_target(mixed, **runtime)
+        gguf.load_into(uniform, gguf.GgufFile(mixed))
+    uniform.close()
     # a type that no kernel here reads
     q5 = str(tmp_path / "q5.gguf")
     model_to_gguf(q5, cfg, w, replace={"blk.0.attn_qkv.weight": (gw.GGML["Q5_K"], [cfg["hidden"], 2048], np.zeros(2048 * 4 * 176, np.uint8))})
@@ -254,3 +264,58 @@ def test_loader_fills_a_moe_target_that_steps_like_the_oracle(tmp_path):
     logits = t.download(-1, "logits", np.float32, (16, cfg["vocab"]))
     scale = np.abs(want["logits"]).max()
     assert np.abs(logits - want["logits"]).max() <= 2e-2 * scale and np.median(np.abs(logits - want["logits"])) <= 2e-3 * scale
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("lanes", [1, 2])
+def test_a_file_of_mixed_formats_loads_and_steps_like_the_oracle(tmp_path, lanes):
+    """The mix of llama.cpp's Q4_K_M: attn_v, a GDN layer's attn_gate, an out projection and some ffn_down tensors in Q6_K
+    (one more in Q8_0) among Q4_K ones. The target made for the file holds each tensor in its format; the layers' fused input
+    projections run as one launch a tensor. One lane (the 16-row kernel, two fragment layouts of the input) and two lanes
+    (the many-row kernel from images)."""
+    import quant_fixtures as qf
+    from splash_b200 import gguf, lib
+    lib.init(0)
+    cfg = tiny_config()
+    w = mo.make_weights(cfg, 9)
+    H, D = cfg["hidden"], cfg["head_dim"]
+    q, kv = cfg["q_heads"] * D * 2, cfg["kv_heads"] * D
+    conv, VW = (2 * 4 + 8) * 128, 8 * 128
+    rows = w.pop((3, "in_proj"))
+    w[3, "in_parts"] = [(0, rows[:q]), (0, rows[q:q + kv]), (4, qf.realistic(4, kv, H, seed=21))]
+    rows = w.pop((1, "in_proj"))
+    w[1, "in_parts"] = [(0, rows[:conv]), (4, qf.realistic(4, VW, H, seed=22))]
+    rows = w.pop((2, "in_proj"))
+    w[2, "in_parts"] = [(6, qf.realistic(6, conv, H, seed=23)), (0, rows[conv:])]
+    w[0, "ffn_down"], w[0, "ffn_down_fmt"] = qf.realistic(4, H, cfg["intermediate"], seed=24), 4
+    w[2, "ffn_down"], w[2, "ffn_down_fmt"] = qf.realistic(6, H, cfg["intermediate"], seed=25), 6
+    w[1, "out_proj"], w[1, "out_proj_fmt"] = qf.realistic(4, H, VW, seed=26), 4
+    path = str(tmp_path / "mixed.gguf")
+    model_to_gguf(path, cfg, w)
+    t, f = gguf.load_target(path, page_tokens=cfg["page_tokens"], kv_scale_f16=cfg["kv_scale_f16"], max_context=cfg["max_context"], lanes=lanes)
+    assert [t.tensor_format(3, n) for n in ("attn_q", "attn_k", "attn_v")] == [0, 0, 4]
+    assert [t.tensor_format(2, n) for n in ("attn_qkv", "attn_gate", "ffn_down")] == [6, 0, 6] and t.tensor_format(1, "out_proj") == 4
+    assert t.tensor_format(0, "in_proj") == 0
+    with pytest.raises(lib.SbError):
+        t.tensor(3, "in_proj")                            # (held tensor by tensor)
+    for layer, stems in ((3, ("attn_q", "attn_k", "attn_v")), (1, ("attn_qkv", "attn_gate")), (2, ("attn_qkv", "attn_gate"))):
+        for stem, (fmt, part) in zip(stems, w[layer, "in_parts"]):
+            assert np.array_equal(t.download(layer, stem, np.uint8, part.shape), part), (layer, stem)
+    positions = [700, 33][:lanes]
+    states = [mo.make_state(cfg, positions[i], 5 + i) for i in range(lanes)]
+    for i, s in enumerate(states):
+        mo.upload(t, {}, s, lane=i)
+    t.reset_lanes(np.array(positions, np.uint32)) if lanes > 1 else t.reset(positions[0])
+    for step in range(2):
+        blocks = np.stack([mo.draft_chain(cfg, w, states[i], 17 + i, rows=16, seed=step) for i in range(lanes)])
+        wants = [mo.verify_step(cfg, w, states[i], blocks[i], advance=True) for i in range(lanes)]
+        got = t.verify_lanes(blocks, flags=1) if lanes > 1 else [t.verify(blocks[0], flags=1)]
+        assert lib.device_status() == 0
+        logits = t.download(-1, "logits", np.float32, (16 * lanes, cfg["vocab"]))
+        for i in range(lanes):
+            want = wants[i]
+            scale = np.abs(want["logits"]).max()
+            err = np.abs(logits[16 * i:16 * i + 16] - want["logits"])
+            assert err.max() <= 2e-2 * scale and np.median(err) <= 2e-3 * scale, (step, i)
+            states[i]["committed"] += got[i][1] - want["retained"]     # follow the device's own choice at near ties
+            states[i]["pending_rows"] = got[i][1]
