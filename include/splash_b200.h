@@ -736,6 +736,25 @@ SB_API int sb_target_verify_tree(void *target, void *stream, const uint32_t *tok
 /* The configuration the target was created with. */
 SB_API int sb_target_config(void *target, SbTargetConfig *out_config);
 
+/* ---- prompt lookup ----
+ * Proposals a request's own tokens make (the reference's LookupIndex, runtime/model/LookupProposals.hpp:17-66; step 1 of a
+ * decode cycle, where the host proposes a lane's lookup chain): the index holds the request's tokens, its prompt and then
+ * every token its steps retain, and after each append knows the match of the latest tokens - the earlier occurrence of
+ * their longest suffix, its length counted up to 64 tokens, the most recent among those of that length, none shorter than
+ * 3 tokens. sb_lookup_match gives the match's length (0: none) and the index of the earlier occurrence's last token;
+ * sb_lookup_proposals copies up to `count` tokens that followed it (at most as far as the latest token): a verify block's
+ * chain after its anchor. Host code: works without a device. */
+SB_API int sb_lookup_create(void **out_index);
+SB_API int sb_lookup_destroy(void *index);
+SB_API int sb_lookup_append(void *index, const uint32_t *tokens, uint64_t count);
+SB_API int sb_lookup_match(void *index, uint32_t *out_length, uint32_t *out_end);
+SB_API int sb_lookup_proposals(void *index, uint32_t count, uint32_t *out_tokens, uint32_t *out_count);
+SB_API int sb_lookup_size(void *index, uint64_t *out_tokens);
+/* How a lookup token at `depth` (0: the first proposal after the anchor) compares with the draft's candidates (16 a proposal
+ * position, the most likely first; `count` ids in all): 0 the most likely, 1 another candidate, 2 none of them, 3 unknown
+ * (lookupAgreement, runtime/model/LookupProposals.cpp:170-178). */
+SB_API int sb_lookup_agreement(uint32_t token, uint32_t depth, const uint32_t *candidates, uint64_t count, uint32_t *out_agreement);
+
 /* ---- GGUF files ----
  * A reader of llama.cpp's GGUF container (version 3; the reference's runtime/model/GgufFile.hpp:23-141) over a read-only
  * mapping of the file, and the loader of a Qwen3.5 hybrid model (general.architecture qwen35 or qwen35moe) from it into a
