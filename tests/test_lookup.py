@@ -105,7 +105,8 @@ def test_index_equals_the_compiled_reference_after_every_token():
 def test_index_follows_the_references_replay_fixture():
     """The decode traces the reference's own test replays (dev/tests/engine/lookup_replay_fixture.txt, read where it lies):
     at every cycle's anchor the match and the chain of up to 31 tokens are the offline replay's."""
-    root = os.environ.get("SPLASH_REFERENCE", "/root/reference")
+    # (the reference tree: SPLASH_REFERENCE, else a `reference` folder beside the repository)
+    root = os.environ.get("SPLASH_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(ol.ORACLE_DIR)), "reference")
     path = os.path.join(root, "dev", "tests", "engine", "lookup_replay_fixture.txt")
     if not os.path.exists(path):
         pytest.skip("the reference tree is not here")
