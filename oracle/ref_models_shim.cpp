@@ -7,7 +7,8 @@
 //               recurrence
 //   selection   referenceDistribution (min_p, top_k,  dev/tests/engine/target_sampling_metal_test.mm
 //               top_p), startOf, reject,
-//               referenceSelection (child tests and the residual draw)
+//               referenceSelection (child tests and the residual draw),
+//               referenceBest / referenceArgmax (the greedy order)
 // Those functions are plain C++ inside Objective-C++ test files. The build recipe (Makefile, target
 // `ref`) cuts their text out of the files where they lie in the reference tree into a scratch folder that
 // it deletes after the compile, and this file includes the cuts between stand-ins for the tests'
@@ -242,6 +243,15 @@ constexpr StopTokens kStopTokens{};
 }  // namespace sampling_model
 
 REF_API uint32_t ref_sampling_candidates() { return sampling_model::kCandidates; }
+
+// The greedy selection of one row: the model's order (value descending, id ascending), its first token.
+REF_API uint32_t ref_argmax(const float *logits, uint32_t vocab) { return sampling_model::referenceArgmax(logits, vocab); }
+// The row's best `count` tokens in that order.
+REF_API uint32_t ref_best(const float *logits, uint32_t vocab, uint32_t count, uint32_t *out) {
+  const std::vector<uint32_t> best = sampling_model::referenceBest(logits, vocab, count);
+  std::copy(best.begin(), best.end(), out);
+  return uint32_t(best.size());
+}
 
 // One sampled row. logits: f32 [vocab]; ids, q: the row's 16 candidates and the draft's probabilities of them;
 // draws: up to 4 candidate indices in the order drawn, 0xff past them (all 0xff: no children); tests: the 4

@@ -20,8 +20,8 @@
 // (tests/test_oracle_ops.py), and attention against the reference's fp64 model compiled from its
 // test file, as is the sampled selection (distribution cuts, child tests, residual draw) against the
 // fp64 recursion of the reference's sampling test (oracle/ref_models_shim.cpp,
-// tests/test_oracle_ref_models.py). Greedy selection and acceptance have neither stored vectors nor a
-// host model in the reference ("parity unpinned" for those: tolerance gates and invariants only).
+// tests/test_oracle_ref_models.py), and the greedy order against its referenceBest. Acceptance has neither
+// stored vectors nor a host model in the reference ("parity unpinned" for it: invariants only).
 #include "so_common.h"
 
 #include <algorithm>

@@ -210,3 +210,31 @@ def test_sampled_selection_matches_the_reference_model(policy):
             checked += 1
             assert got[r] == token.value, (round_, r, int(got[r]), token.value)
     assert checked * 10 >= drawn * 9, (checked, drawn)
+
+
+def test_greedy_selection_matches_the_reference_order():
+    """Temperature 0: the oracle's selection is the first token of the reference's order (value descending, id ascending),
+    ties and all; the order itself is what numpy's stable sort gives."""
+    ref = _models()
+    ref.ref_argmax.argtypes = [_V, _U]
+    ref.ref_best.argtypes = [_V, _U, _U, _V]
+    o = ol.bind_ops(ol.load())
+    rng = np.random.default_rng(17)
+    rows, vocab = 16, 5003
+    logits = rng.standard_normal((rows, vocab)).astype(np.float32)
+    logits[1, [7, 4000, 300]] = 9.0                      # a three-way tie for the maximum: the lowest id
+    logits[2, :] = 0.25                                  # every token ties
+    logits[3, vocab - 1] = 11.0                          # the last id
+    logits[4, 100] = np.nextafter(np.float32(30.0), np.float32(31.0))   # one unit in the last place apart
+    logits[4, 50] = np.float32(30.0)
+    logits[5, :] = -np.inf                               # no comparable logit ...
+    logits[5, 4321] = -1e30                              # ... but one
+    tokens = np.zeros(rows, np.uint32)
+    selected = np.zeros(rows, np.uint32)
+    o.so_sample_verify(P(logits), vocab, vocab, rows, P(tokens), 0.0, None, P(selected), None)
+    for r in range(rows):
+        assert selected[r] == ref.ref_argmax(P(logits[r]), vocab), r
+        best = np.zeros(8, np.uint32)
+        assert ref.ref_best(P(logits[r]), vocab, 8, P(best)) == 8
+        assert np.array_equal(best, np.lexsort((np.arange(vocab), -logits[r]))[:8])
+    assert selected[1] == 7 and selected[2] == 0 and selected[3] == vocab - 1 and selected[4] == 100 and selected[5] == 4321
