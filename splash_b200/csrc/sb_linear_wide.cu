@@ -171,11 +171,16 @@ __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const Wi
   uint8_t *block = p.out + kWideHeader;
   float *scale_dst = reinterpret_cast<float *>(p.out) + tok;
   const uint32_t chunks = p.k / 8;  // 8 inputs each
+  // A thread's chunks (tid, tid + 256, ...) stay in its registers from the pass that forms or first reads them to the
+  // conversion (up to kKeep of them: k <= 18432); a longer row is read again from memory, where this thread wrote it.
+  constexpr int kKeep = 9;
+  uint4 keep[kKeep];
+  const bool kept = chunks <= uint32_t(kKeep) * kWidePrepThreads;
   if (p.partials && live) {
     // The projection ahead left its k-splits' sums: add them in split order onto the residual, round once, and keep the
-    // rows (the new hidden state). A thread reads back below only what it wrote itself.
+    // rows (the new hidden state).
     uint16_t *xw = const_cast<uint16_t *>(xrow);
-    for (uint32_t c = tid; c < chunks; c += kWidePrepThreads) {
+    auto sum_chunk = [&](uint32_t c) {
       const uint4 raw = *reinterpret_cast<const uint4 *>(p.residual + size_t(tok) * p.residual_stride + 8 * c);
       const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
@@ -191,12 +196,28 @@ __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const Wi
         const uint32_t hi = float_to_bf16_bits(acc[2 * j + 1] + bf16_bits_to_float(u[j] >> 16));
         o[j] = lo | (hi << 16);
       }
-      *reinterpret_cast<uint4 *>(xw + 8 * c) = make_uint4(o[0], o[1], o[2], o[3]);
+      const uint4 out = make_uint4(o[0], o[1], o[2], o[3]);
+      *reinterpret_cast<uint4 *>(xw + 8 * c) = out;
+      return out;
+    };
+    if (kept) {
+#pragma unroll
+      for (int i = 0; i < kKeep; ++i) {
+        const uint32_t c = tid + uint32_t(i) * kWidePrepThreads;
+        if (c < chunks) keep[i] = sum_chunk(c);
+      }
+    } else {
+      for (uint32_t c = tid; c < chunks; c += kWidePrepThreads) (void)sum_chunk(c);
+    }
+  } else if (kept && live) {
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {
+      const uint32_t c = tid + uint32_t(i) * kWidePrepThreads;
+      if (c < chunks) keep[i] = *reinterpret_cast<const uint4 *>(xrow + 8 * c);
     }
   }
   float ss = 0.0f, mx = 0.0f;
-  for (uint32_t c = tid; c < chunks && live; c += kWidePrepThreads) {
-    const uint4 raw = *reinterpret_cast<const uint4 *>(xrow + 8 * c);
+  auto measure = [&](uint32_t c, const uint4 raw) {
     const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
@@ -205,6 +226,15 @@ __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const Wi
       const float wa = p.norm_w ? p.norm_w[8 * c + 2 * j] : 1.0f, wb = p.norm_w ? p.norm_w[8 * c + 2 * j + 1] : 1.0f;
       mx = fmaxf(mx, fmaxf(fabsf(a * wa), fabsf(b * wb)));
     }
+  };
+  if (kept) {
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {
+      const uint32_t c = tid + uint32_t(i) * kWidePrepThreads;
+      if (c < chunks && live) measure(c, keep[i]);
+    }
+  } else {
+    for (uint32_t c = tid; c < chunks && live; c += kWidePrepThreads) measure(c, *reinterpret_cast<const uint4 *>(xrow + 8 * c));
   }
 #pragma unroll
   for (int o = 16; o; o >>= 1) {
@@ -228,10 +258,9 @@ __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const Wi
   const float down = ldexpf(1.0f, -e);
   if (tid == 0) *scale_dst = live ? ldexpf(1.0f, e) : 0.0f;
   const size_t unit_bytes = size_t(rows_padded) * 128;  // 64 inputs of every row slot
-  for (uint32_t c = tid; c < chunks; c += kWidePrepThreads) {
+  auto convert = [&](uint32_t c, const uint4 raw) {
     uint32_t h[4] = {0, 0, 0, 0};
     if (live) {
-      const uint4 raw = *reinterpret_cast<const uint4 *>(xrow + 8 * c);
       const uint32_t u[4] = {raw.x, raw.y, raw.z, raw.w};
       float v[8];
 #pragma unroll
@@ -251,6 +280,15 @@ __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const Wi
     const uint32_t k0 = 8 * c, unit = k0 / 64, step = (k0 % 64) / 16, half = (k0 % 16) / 8;
     uint8_t *dst = block + unit * unit_bytes + size_t(step) * rows_padded * 32 + (tok >> 3) * 256 + half * 128 + (tok & 7) * 16;
     *reinterpret_cast<uint4 *>(dst) = make_uint4(h[0], h[1], h[2], h[3]);
+  };
+  if (kept) {
+#pragma unroll
+    for (int i = 0; i < kKeep; ++i) {
+      const uint32_t c = tid + uint32_t(i) * kWidePrepThreads;
+      if (c < chunks) convert(c, live ? keep[i] : make_uint4(0, 0, 0, 0));
+    }
+  } else {
+    for (uint32_t c = tid; c < chunks; c += kWidePrepThreads) convert(c, live ? *reinterpret_cast<const uint4 *>(xrow + 8 * c) : make_uint4(0, 0, 0, 0));
   }
 }
 
