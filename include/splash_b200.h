@@ -227,6 +227,13 @@ SB_API uint32_t sb_linear_wide_splits(uint32_t n, uint32_t k);
 SB_API int sb_linear_wide_prepare_sum(void *stream, const float *partials, uint32_t splits, uint32_t partial_stride, const void *residual,
                                       uint32_t residual_stride, void *sum_out, uint32_t sum_stride, uint32_t rows, uint32_t k,
                                       const void *norm_weight, void *prepared_out, uint32_t flags);
+/* Either of the two conversions above (partials NULL: sb_linear_wide_prepare of x_or_sum_out; else sb_linear_wide_prepare_sum
+ * into it) that also stores the normalised rows, bf16 [rows][k], as the fp32 side projections of the same input read them
+ * (the GDN alpha / beta rows, the MoE router): what a separate sb_rmsnorm over the same rows would give, from the
+ * conversion's own row statistics. Needs norm_weight. */
+SB_API int sb_linear_wide_prepare_normed(void *stream, const float *partials, uint32_t splits, uint32_t partial_stride, const void *residual,
+                                         uint32_t residual_stride, void *x_or_sum_out, uint32_t x_stride, uint32_t rows, uint32_t k,
+                                         const void *norm_weight, void *prepared_out, void *normed_out, uint32_t flags);
 SB_API int sb_linear_wide(void *stream, const SbLinearArgs *args);
 
 /* The plan sb_linear will use for a shape: k-slices, CTAs, tile rows, ring stages, shared bytes.

@@ -621,15 +621,16 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
   // splits' sums in widePartials_; the conversion in front of the next projection adds them onto the residual and writes
   // the new hidden rows. `owed`: splits the rows of hidden[cur] still lack.
   uint32_t owed = 0;
-  auto convert = [&](const Buffer *norm) {
-    if (!owed) return Linear::prepareWide(graph, hidden[cur], R, H, H, norm, widePrepared_[0]);
-    PreparedInput in = Linear::prepareWideSum(graph, widePartials_, owed, hidden[cur], hidden[cur ^ 1], R, H, norm, widePrepared_[0]);
+  // (normedOutput: the conversion also leaves the normalised rows, for the fp32 projections that read the same input)
+  auto convert = [&](const Buffer *norm, const Buffer *normedOutput = nullptr) {
+    if (!owed) return Linear::prepareWide(graph, hidden[cur], R, H, H, norm, widePrepared_[0], normedOutput);
+    PreparedInput in = Linear::prepareWideSum(graph, widePartials_, owed, hidden[cur], hidden[cur ^ 1], R, H, norm, widePrepared_[0], normedOutput);
     cur ^= 1, owed = 0;
     return in;
   };
   for (LayerWeights &w : layers_) {
     // mixer: h += mixer(norm(h))
-    PreparedInput in = convert(&w.attnNorm.buffer);
+    PreparedInput in = convert(&w.attnNorm.buffer, w.attention ? nullptr : &normed_);  // (a GDN layer's own alpha / beta projection reads the normalised rows)
     for (const QuantizedSegment *part : w.inSegments())  // (one segment, or one a checkpoint tensor where their formats differ)
       Linear::addWide(graph, *part, nullptr, in, R, Epilogue::None, nullptr,
                       part->columnOffset ? packed_.view(size_t(part->columnOffset) * 2, packed_.bytes() - size_t(part->columnOffset) * 2) : packed_, packedStride_);
@@ -646,8 +647,6 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
       check(sb_attn_verify(graph.stream, &aa));
       graph.launches += 2;
     } else {
-      // The layer's normalised rows for the kernel's own alpha / beta projection.
-      Normalization::addRms(graph, hidden[cur], w.attnNorm, normed_, H, R, H, H);
       mixedWidth = gdn_.valueWidth();
       SbGdnArgs a{};
       a.qkvz = packed_.as(), a.gate_weight = w.ssmAb.as<float>(), a.gate_input = normed_.as(), a.gate_k = a.gate_input_stride = H;
@@ -668,8 +667,7 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
     if (c.moe_experts) {
       // MoE block: h += sum over the row's routes of weight * expert(norm(h)). The conversion is run for the hidden rows it
       // leaves (residual + out_proj's splits); the routes of all lanes' rows are grouped by expert (MoE::addRouted).
-      convert(nullptr);
-      Normalization::addRms(graph, hidden[cur], w.ffnNorm, normed_, H, R, H, H);
+      convert(&w.ffnNorm.buffer, &normed_);  // (its normalised rows are the block's input)
       MoeBuffers mb{normed_, hidden[cur], moeScores_, moeSelected_, moeWeights_, moeScratch_, hidden[cur ^ 1]};
       MoE::addRouting(graph, moe_, w.moe, mb, R, routerScoresGiven ? &moeScoresGiven_ : nullptr);
       if (ep_) ep_->addRouted(graph, w.moe, mb);

@@ -98,12 +98,14 @@ class Linear {
   // The conversion for it (another layout than prepare's); `scratch` holds wideBytes(rows, inputSize).
   static uint64_t wideBytes(uint32_t rows, uint32_t inputSize) { return sb_linear_wide_prepared_bytes(rows, inputSize); }
   static PreparedInput prepareWide(CommandGraph &graph, const Buffer &input, uint32_t rows, uint32_t inputSize, uint32_t inputStride,
-                                   const Buffer *normWeight, const Buffer &scratch) {
+                                   const Buffer *normWeight, const Buffer &scratch, const Buffer *normedOutput = nullptr) {
     requireBytes(input, size_t(rows - 1) * inputStride * 2 + size_t(inputSize) * 2, "Linear::prepareWide input");
     requireBytes(scratch, wideBytes(rows, inputSize), "Linear::prepareWide scratch");
     if (normWeight) requireBytes(*normWeight, size_t(inputSize) * 4, "Linear::prepareWide norm weight");
-    check(sb_linear_wide_prepare(graph.stream, input.as(), rows, inputSize, inputStride, normWeight ? normWeight->as() : nullptr, scratch.as(),
-                                 graph.pdl ? SB_LINEAR_PDL : 0));
+    if (normedOutput) requireBytes(*normedOutput, size_t(rows) * inputSize * 2, "Linear::prepareWide normalised output");
+    check(sb_linear_wide_prepare_normed(graph.stream, nullptr, 0, 0, nullptr, 0, input.as(), inputStride, rows, inputSize,
+                                        normWeight ? normWeight->as() : nullptr, scratch.as(), normedOutput ? normedOutput->as() : nullptr,
+                                        graph.pdl ? SB_LINEAR_PDL : 0));
     graph.launches += (rows + 127) / 128;
     return {scratch, 0xFFFFu, inputSize};  // (format tag of the wide layout)
   }
@@ -111,14 +113,17 @@ class Linear {
   // splits' sums in split order) goes to `sumOut` (the new hidden rows), then the conversion of x as prepareWide does it.
   static uint32_t wideSplits(uint32_t outputSize, uint32_t inputSize) { return sb_linear_wide_splits(outputSize, inputSize); }
   static PreparedInput prepareWideSum(CommandGraph &graph, const Buffer &partials, uint32_t splits, const Buffer &residual, const Buffer &sumOut,
-                                      uint32_t rows, uint32_t inputSize, const Buffer *normWeight, const Buffer &scratch) {
+                                      uint32_t rows, uint32_t inputSize, const Buffer *normWeight, const Buffer &scratch,
+                                      const Buffer *normedOutput = nullptr) {
+    if (normedOutput) requireBytes(*normedOutput, size_t(rows) * inputSize * 2, "Linear::prepareWideSum normalised output");
     requireBytes(partials, size_t(splits) * rows * inputSize * 4, "Linear::prepareWideSum partial sums");
     requireBytes(residual, size_t(rows) * inputSize * 2, "Linear::prepareWideSum residual");
     requireBytes(sumOut, size_t(rows) * inputSize * 2, "Linear::prepareWideSum sum");
     requireBytes(scratch, wideBytes(rows, inputSize), "Linear::prepareWideSum scratch");
     if (normWeight) requireBytes(*normWeight, size_t(inputSize) * 4, "Linear::prepareWideSum norm weight");
-    check(sb_linear_wide_prepare_sum(graph.stream, partials.as<float>(), splits, inputSize, residual.as(), inputSize, sumOut.as(), inputSize, rows,
-                                     inputSize, normWeight ? normWeight->as() : nullptr, scratch.as(), graph.pdl ? SB_LINEAR_PDL : 0));
+    check(sb_linear_wide_prepare_normed(graph.stream, partials.as<float>(), splits, inputSize, residual.as(), inputSize, sumOut.as(), inputSize, rows,
+                                        inputSize, normWeight ? normWeight->as() : nullptr, scratch.as(), normedOutput ? normedOutput->as() : nullptr,
+                                        graph.pdl ? SB_LINEAR_PDL : 0));
     graph.launches += (rows + 127) / 128;
     return {scratch, 0xFFFFu, inputSize};
   }

@@ -159,6 +159,7 @@ struct WidePrepParams {
   const uint32_t *slot_src, *slot_group, *slot_count;
   const uint4 *groups;
   float *scales;
+  uint16_t *normed_out;  // optional bf16 [rows][k]: the normalised rows (with norm_w), for the fp32 side projections of the same input
 };
 __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const WidePrepParams p) {
   __shared__ float red_s[2 * (kWidePrepThreads / 32)];
@@ -268,6 +269,12 @@ __global__ void __launch_bounds__(kWidePrepThreads) wide_prepare_kernel(const Wi
       if (p.norm_w) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) v[j] = round_bf16((v[j] * inv) * p.norm_w[8 * c + j]);
+        if (p.normed_out) {
+          uint32_t n[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) n[j] = float_to_bf16_bits(v[2 * j]) | (float_to_bf16_bits(v[2 * j + 1]) << 16);
+          *reinterpret_cast<uint4 *>(p.normed_out + size_t(tok) * p.k + 8 * c) = make_uint4(n[0], n[1], n[2], n[3]);
+        }
       }
       __half hv[8];
 #pragma unroll
@@ -1020,11 +1027,23 @@ extern "C" uint64_t sb_linear_wide_prepared_bytes(uint32_t rows, uint32_t k) {
 
 // One pass = up to 128 rows; pass i of the conversion starts at sb_linear_wide_prepared_bytes(128, k) * i.
 static int wide_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride, const void *norm_weight, void *prepared_out,
-                        uint32_t flags, const float *partials, uint32_t splits, uint32_t partial_stride, const void *residual, uint32_t residual_stride);
+                        uint32_t flags, const float *partials, uint32_t splits, uint32_t partial_stride, const void *residual, uint32_t residual_stride,
+                        void *normed_out = nullptr);
 
 extern "C" int sb_linear_wide_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride, const void *norm_weight,
                                       void *prepared_out, uint32_t flags) {
   return wide_prepare(stream, x, rows, k, x_stride, norm_weight, prepared_out, flags, nullptr, 0, 0, nullptr, 0);
+}
+
+extern "C" int sb_linear_wide_prepare_normed(void *stream, const float *partials, uint32_t splits, uint32_t partial_stride, const void *residual,
+                                             uint32_t residual_stride, void *x_or_sum_out, uint32_t x_stride, uint32_t rows, uint32_t k,
+                                             const void *norm_weight, void *prepared_out, void *normed_out, uint32_t flags) {
+  if (!partials) return wide_prepare(stream, x_or_sum_out, rows, k, x_stride, norm_weight, prepared_out, flags, nullptr, 0, 0, nullptr, 0, normed_out);
+  SB_REQUIRE(residual && x_or_sum_out && splits >= 1 && splits <= 64, "sb_linear_wide_prepare_normed: null residual or destination, or %u splits", splits);
+  SB_REQUIRE(partial_stride >= k && partial_stride % 4 == 0 && residual_stride >= k && residual_stride % 8 == 0,
+             "sb_linear_wide_prepare_normed: partial_stride %u or residual_stride %u", partial_stride, residual_stride);
+  SB_REQUIRE(((reinterpret_cast<uintptr_t>(partials) | reinterpret_cast<uintptr_t>(residual)) & 15) == 0, "sb_linear_wide_prepare_normed: pointers must be 16-byte aligned");
+  return wide_prepare(stream, x_or_sum_out, rows, k, x_stride, norm_weight, prepared_out, flags, partials, splits, partial_stride, residual, residual_stride, normed_out);
 }
 
 extern "C" int sb_linear_wide_prepare_sum(void *stream, const float *partials, uint32_t splits, uint32_t partial_stride, const void *residual,
@@ -1038,8 +1057,10 @@ extern "C" int sb_linear_wide_prepare_sum(void *stream, const float *partials, u
 }
 
 static int wide_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, uint32_t x_stride, const void *norm_weight, void *prepared_out,
-                        uint32_t flags, const float *partials, uint32_t splits, uint32_t partial_stride, const void *residual, uint32_t residual_stride) {
+                        uint32_t flags, const float *partials, uint32_t splits, uint32_t partial_stride, const void *residual, uint32_t residual_stride,
+                        void *normed_out) {
   SB_NEED_DEVICE();
+  SB_REQUIRE(!normed_out || (norm_weight && (reinterpret_cast<uintptr_t>(normed_out) & 15) == 0), "sb_linear_wide_prepare: normalised rows come with a norm weight, 16-byte aligned");
   SB_REQUIRE(x && prepared_out && rows >= 1, "sb_linear_wide_prepare: null x or destination, or no rows");
   SB_REQUIRE(k && k % 256 == 0 && x_stride >= k && x_stride % 8 == 0, "sb_linear_wide_prepare: k = %u is not a multiple of 256, or x_stride %u", k, x_stride);
   SB_REQUIRE(((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(prepared_out) | reinterpret_cast<uintptr_t>(norm_weight)) & 15) == 0,
@@ -1051,6 +1072,7 @@ static int wide_prepare(void *stream, const void *x, uint32_t rows, uint32_t k, 
                       static_cast<uint8_t *>(prepared_out) + pass * pass_bytes, n, padded, k, x_stride,
                       partials, residual ? static_cast<const uint16_t *>(residual) + size_t(r0) * residual_stride : nullptr,
                       splits, rows, r0, partial_stride, residual_stride};
+    pp.normed_out = normed_out ? static_cast<uint16_t *>(normed_out) + size_t(r0) * k : nullptr;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(padded), cfg.blockDim = dim3(kWidePrepThreads), cfg.stream = as_stream(stream);
     cudaLaunchAttribute attr[1];
