@@ -2,8 +2,8 @@
 // arrays, the tensor table, and where each tensor's bytes lie. Host code only; nothing is copied out of the mapping
 // but the header's own strings.
 //
-// Mirrors the reference's header parser (runtime/model/GgufFile.hpp:23-141: GgufTensor, GgufMetadata, GgufFile::find /
-// require / numericArray; type table :38-57) for one file; split files and the rotation keys are not read.
+// Stands where the reference has its header parser (runtime/model/GgufFile.hpp:23-141: tensors, metadata by key, find /
+// require, numeric arrays; ggml's type table :38-57) for one file; split files and the rotation keys are not read.
 // File layout as llama.cpp's gguf.h documents it: magic "GGUF", u32 version, u64 tensor count, u64 key count; per key a
 // string, a u32 value type and the value; per tensor a string, u32 dimensions, u64 extents (fastest first), u32 ggml
 // type, u64 offset into the data section, which starts at the next multiple of general.alignment (32 by default).
@@ -35,29 +35,53 @@ constexpr uint32_t kF32 = 0, kF16 = 1, kQ8_0 = 8, kQ4_K = 12, kQ6_K = 14, kBF16 
 }
 
 struct GgmlType {
-  uint32_t id;
   const char *name;
   uint32_t blockElements, blockBytes;
 };
-// The ggml tensor types this reader can size (ggml's own ids and block shapes): a tensor of another type is refused,
-// since its extent in the file could not be checked.
-inline const GgmlType *ggmlType(uint32_t id) {
-  static const GgmlType table[] = {
-      {0, "F32", 1, 4},        {1, "F16", 1, 2},        {2, "Q4_0", 32, 18},     {3, "Q4_1", 32, 20},     {6, "Q5_0", 32, 22},
-      {7, "Q5_1", 32, 24},     {8, "Q8_0", 32, 34},     {9, "Q8_1", 32, 36},     {10, "Q2_K", 256, 84},   {11, "Q3_K", 256, 110},
-      {12, "Q4_K", 256, 144},  {13, "Q5_K", 256, 176},  {14, "Q6_K", 256, 210},  {15, "Q8_K", 256, 292},  {16, "IQ2_XXS", 256, 66},
-      {17, "IQ2_XS", 256, 74}, {18, "IQ3_XXS", 256, 98}, {19, "IQ1_S", 256, 50}, {20, "IQ4_NL", 32, 18},  {21, "IQ3_S", 256, 110},
-      {22, "IQ2_S", 256, 82},  {23, "IQ4_XS", 256, 136}, {24, "I8", 1, 1},       {25, "I16", 1, 2},       {26, "I32", 1, 4},
-      {27, "I64", 1, 8},       {28, "F64", 1, 8},       {29, "IQ1_M", 256, 56},  {30, "BF16", 1, 2},      {39, "MXFP4", 32, 17},
-      {40, "NVFP4", 64, 36},
-  };
-  for (const GgmlType &t : table)
-    if (t.id == id) return &t;
-  return nullptr;
+// Name and block shape of a ggml tensor type by its id (ggml's own numbers), for the types this reader can size; a tensor
+// of another type is refused, since its extent in the file could not be checked.
+inline bool ggmlTypeOf(uint32_t id, GgmlType &t) {
+  switch (id) {
+    // plain element types
+    case 0: t = {"F32", 1, 4}; return true;
+    case 1: t = {"F16", 1, 2}; return true;
+    case 30: t = {"BF16", 1, 2}; return true;
+    case 28: t = {"F64", 1, 8}; return true;
+    case 24: t = {"I8", 1, 1}; return true;
+    case 25: t = {"I16", 1, 2}; return true;
+    case 26: t = {"I32", 1, 4}; return true;
+    case 27: t = {"I64", 1, 8}; return true;
+    // blocks of 32 weights
+    case 2: t = {"Q4_0", 32, 18}; return true;
+    case 3: t = {"Q4_1", 32, 20}; return true;
+    case 6: t = {"Q5_0", 32, 22}; return true;
+    case 7: t = {"Q5_1", 32, 24}; return true;
+    case 8: t = {"Q8_0", 32, 34}; return true;
+    case 9: t = {"Q8_1", 32, 36}; return true;
+    case 20: t = {"IQ4_NL", 32, 18}; return true;
+    case 39: t = {"MXFP4", 32, 17}; return true;
+    case 40: t = {"NVFP4", 64, 36}; return true;  // (64 weights)
+    // super-blocks of 256 weights
+    case 10: t = {"Q2_K", 256, 84}; return true;
+    case 11: t = {"Q3_K", 256, 110}; return true;
+    case 12: t = {"Q4_K", 256, 144}; return true;
+    case 13: t = {"Q5_K", 256, 176}; return true;
+    case 14: t = {"Q6_K", 256, 210}; return true;
+    case 15: t = {"Q8_K", 256, 292}; return true;
+    case 16: t = {"IQ2_XXS", 256, 66}; return true;
+    case 17: t = {"IQ2_XS", 256, 74}; return true;
+    case 22: t = {"IQ2_S", 256, 82}; return true;
+    case 18: t = {"IQ3_XXS", 256, 98}; return true;
+    case 21: t = {"IQ3_S", 256, 110}; return true;
+    case 19: t = {"IQ1_S", 256, 50}; return true;
+    case 29: t = {"IQ1_M", 256, 56}; return true;
+    case 23: t = {"IQ4_XS", 256, 136}; return true;
+    default: return false;
+  }
 }
 inline std::string ggmlTypeName(uint32_t id) {
-  const GgmlType *t = ggmlType(id);
-  return t ? t->name : "type " + std::to_string(id);
+  GgmlType t;
+  return ggmlTypeOf(id, t) ? std::string(t.name) : "type " + std::to_string(id);
 }
 
 struct GgufTensor {
@@ -81,26 +105,26 @@ struct GgufMetadata {
   std::map<std::string, uint64_t, std::less<>> unsigneds;
   std::map<std::string, double, std::less<>> floats;
   std::map<std::string, std::string, std::less<>> strings;
-  std::optional<uint64_t> unsignedValue(std::string_view key) const {
+  std::optional<uint64_t> integer(std::string_view key) const {
     auto it = unsigneds.find(key);
     return it == unsigneds.end() ? std::nullopt : std::optional<uint64_t>(it->second);
   }
-  std::optional<double> floatValue(std::string_view key) const {
+  std::optional<double> number(std::string_view key) const {
     auto it = floats.find(key);
     if (it != floats.end()) return it->second;
-    if (auto u = unsignedValue(key)) return double(*u);
+    if (auto u = integer(key)) return double(*u);
     return std::nullopt;
   }
-  std::optional<std::string> stringValue(std::string_view key) const {
+  std::optional<std::string> text(std::string_view key) const {
     auto it = strings.find(key);
     return it == strings.end() ? std::nullopt : std::optional<std::string>(it->second);
   }
-  std::string architecture() const { return stringValue("general.architecture").value_or(""); }
+  std::string architecture() const { return text("general.architecture").value_or(""); }
 };
 
-class GgufFile {
+class GgufReader {
  public:
-  explicit GgufFile(const std::string &path) : path_(path) {
+  explicit GgufReader(const std::string &path) : path_(path) {
     const int fd = ::open(path.c_str(), O_RDONLY);
     if (fd < 0) throw GgufError("cannot open " + path);
     struct stat st {};
@@ -120,11 +144,11 @@ class GgufFile {
       throw;
     }
   }
-  ~GgufFile() {
+  ~GgufReader() {
     if (base_) ::munmap(const_cast<uint8_t *>(base_), size_);
   }
-  GgufFile(const GgufFile &) = delete;
-  GgufFile &operator=(const GgufFile &) = delete;
+  GgufReader(const GgufReader &) = delete;
+  GgufReader &operator=(const GgufReader &) = delete;
 
   const GgufMetadata &metadata() const { return metadata_; }
   const std::vector<GgufTensor> &tensors() const { return tensors_; }
@@ -217,7 +241,7 @@ class GgufFile {
         else metadata_.unsigneds[key] = u;
       }
     }
-    alignment_ = uint32_t(metadata_.unsignedValue("general.alignment").value_or(32));
+    alignment_ = uint32_t(metadata_.integer("general.alignment").value_or(32));
     if (!alignment_ || (alignment_ & (alignment_ - 1))) throw GgufError(path_ + ": general.alignment is not a power of two");
     tensors_.reserve(size_t(tensorCount));
     for (uint64_t t = 0; t < tensorCount; ++t) {
@@ -234,10 +258,10 @@ class GgufFile {
       }
       tensor.type = take<uint32_t>();
       tensor.offset = take<uint64_t>();
-      const GgmlType *type = ggmlType(tensor.type);
-      if (!type) throw GgufError(path_ + ": " + tensor.name + " is of ggml type " + std::to_string(tensor.type) + ", which this reader cannot size");
-      if (tensor.dims[0] % type->blockElements) throw GgufError(path_ + ": " + tensor.name + " rows are not whole " + type->name + " blocks");
-      tensor.bytes = elements / type->blockElements * type->blockBytes;
+      GgmlType type;
+      if (!ggmlTypeOf(tensor.type, type)) throw GgufError(path_ + ": " + tensor.name + " is of ggml type " + std::to_string(tensor.type) + ", which this reader cannot size");
+      if (tensor.dims[0] % type.blockElements) throw GgufError(path_ + ": " + tensor.name + " rows are not whole " + type.name + " blocks");
+      tensor.bytes = elements / type.blockElements * type.blockBytes;
       if (tensor.offset % alignment_) throw GgufError(path_ + ": " + tensor.name + " does not start on the file's alignment");
       if (!index_.emplace(tensor.name, tensors_.size()).second) throw GgufError(path_ + ": two tensors named " + tensor.name);
       tensors_.push_back(std::move(tensor));

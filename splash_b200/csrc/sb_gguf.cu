@@ -1,5 +1,5 @@
 // C ABI of the GGUF reader and of the loader that fills a target model from a GGUF of the Qwen3.5 hybrid family
-// (include/splash_b200.h, "GGUF files"). The reader is host code (model/GgufFile.hpp) and needs no device; the loader
+// (include/splash_b200.h, "GGUF files"). The reader is host code (model/GgufReader.hpp) and needs no device; the loader
 // goes through the same tensor addresses sb_target_tensor hands out.
 //
 // Tensor names, shapes and conversions follow the reference's image builder (runtime/model/GgufImage.cpp:477-520 mixers
@@ -12,18 +12,18 @@
 #include <string>
 #include <vector>
 
-#include "model/GgufFile.hpp"
+#include "model/GgufReader.hpp"
 #include "sb_internal.h"
 
 using splash::b200::model::GgufError;
-using splash::b200::model::GgufFile;
+using splash::b200::model::GgufReader;
 using splash::b200::model::GgufTensor;
 namespace ggml = splash::b200::model::ggml;
 
 namespace {
 
 struct OpenFile {
-  std::unique_ptr<GgufFile> file;
+  std::unique_ptr<GgufReader> file;
 };
 
 // Host-only entry points report failures like the rest of the ABI: a status and the thread's message.
@@ -118,7 +118,7 @@ struct RowOrder {
 
 struct Loader {
   void *target;
-  const GgufFile &file;
+  const GgufReader &file;
   SbTargetConfig c;
   std::vector<uint8_t> staging;
 
@@ -246,7 +246,7 @@ int sb_gguf_open(const char *path, void **out_file) {
   if (!path || !out_file) return sb::fail(SB_ERR_INVALID, "sb_gguf_open: null pointer");
   return host_guarded([&] {
     auto f = std::make_unique<OpenFile>();
-    f->file = std::make_unique<GgufFile>(path);
+    f->file = std::make_unique<GgufReader>(path);
     *out_file = f.release();
     return int(SB_OK);
   });
@@ -276,14 +276,14 @@ int sb_gguf_find(void *file, const char *name, SbGgufTensor *out) {
 }
 int sb_gguf_meta_u64(void *file, const char *key, uint64_t *out) {
   if (!file || !key || !out) return sb::fail(SB_ERR_INVALID, "sb_gguf_meta_u64: null pointer");
-  const auto v = static_cast<OpenFile *>(file)->file->metadata().unsignedValue(key);
+  const auto v = static_cast<OpenFile *>(file)->file->metadata().integer(key);
   if (!v) return sb::fail(SB_ERR_INVALID, "sb_gguf_meta_u64: no integer key %s", key);
   *out = *v;
   return SB_OK;
 }
 int sb_gguf_meta_f64(void *file, const char *key, double *out) {
   if (!file || !key || !out) return sb::fail(SB_ERR_INVALID, "sb_gguf_meta_f64: null pointer");
-  const auto v = static_cast<OpenFile *>(file)->file->metadata().floatValue(key);
+  const auto v = static_cast<OpenFile *>(file)->file->metadata().number(key);
   if (!v) return sb::fail(SB_ERR_INVALID, "sb_gguf_meta_f64: no numeric key %s", key);
   *out = *v;
   return SB_OK;
@@ -300,26 +300,26 @@ int sb_gguf_meta_str(void *file, const char *key, const char **out) {
 int sb_gguf_target_config(void *file, SbTargetConfig *config) {
   if (!file || !config) return sb::fail(SB_ERR_INVALID, "sb_gguf_target_config: null pointer");
   return host_guarded([&] {
-    const GgufFile &f = *static_cast<OpenFile *>(file)->file;
+    const GgufReader &f = *static_cast<OpenFile *>(file)->file;
     const std::string arch = f.metadata().architecture();
     if (arch != "qwen35" && arch != "qwen35moe") throw GgufError("GGUF architecture is '" + arch + "'; qwen35 or qwen35moe is loaded");
     auto u = [&](const char *key) {
-      const auto v = f.metadata().unsignedValue(arch + "." + key);
+      const auto v = f.metadata().integer(arch + "." + key);
       if (!v) throw GgufError("the GGUF's metadata has no " + arch + "." + key);
       return uint32_t(*v);
     };
     SbTargetConfig &c = *config;
-    c.layers = u("block_count") - uint32_t(f.metadata().unsignedValue(arch + ".nextn_predict_layers").value_or(0));
+    c.layers = u("block_count") - uint32_t(f.metadata().integer(arch + ".nextn_predict_layers").value_or(0));
     c.hidden = u("embedding_length");
     c.q_heads = u("attention.head_count"), c.kv_heads = u("attention.head_count_kv"), c.head_dim = u("attention.key_length");
     if (u("attention.value_length") != c.head_dim) throw GgufError("attention.value_length differs from attention.key_length");
     c.rotary_pairs = u("rope.dimension_count") / 2;
-    const auto theta = f.metadata().floatValue(arch + ".rope.freq_base");
+    const auto theta = f.metadata().number(arch + ".rope.freq_base");
     if (!theta) throw GgufError("the GGUF's metadata has no " + arch + ".rope.freq_base");
     c.rope_theta = float(*theta);
-    if (const auto scaling = f.metadata().stringValue(arch + ".rope.scaling.type"); scaling && *scaling != "none")
+    if (const auto scaling = f.metadata().text(arch + ".rope.scaling.type"); scaling && *scaling != "none")
       throw GgufError("rope.scaling.type " + *scaling + " (none is run)");
-    if (const auto eps = f.metadata().floatValue(arch + ".attention.layer_norm_rms_epsilon"); eps && std::abs(*eps - 1e-6) > 1e-12)
+    if (const auto eps = f.metadata().number(arch + ".attention.layer_norm_rms_epsilon"); eps && std::abs(*eps - 1e-6) > 1e-12)
       throw GgufError("attention.layer_norm_rms_epsilon is not 1e-6");
     c.attention_interval = u("full_attention_interval");
     if (u("ssm.conv_kernel") != 4 || u("ssm.state_size") != 128) throw GgufError("ssm.conv_kernel / ssm.state_size other than 4 / 128");
@@ -368,7 +368,7 @@ int sb_target_create_from_gguf(void *file, const SbTargetConfig *runtime, void *
     SbTargetConfig c = *runtime;
     int st = sb_gguf_target_config(file, &c);
     if (st != SB_OK) return st;
-    const GgufFile &f = *static_cast<OpenFile *>(file)->file;
+    const GgufReader &f = *static_cast<OpenFile *>(file)->file;
     // Every projection tensor's type is one a kernel reads: checked here, so that the formats' lookup below cannot fail.
     for (const GgufTensor &t : f.tensors())
       if (t.dims.size() >= 2 && t.name.rfind("blk.", 0) == 0 && t.name.size() > 7 && t.name.compare(t.name.size() - 7, 7, ".weight") == 0 &&
@@ -376,13 +376,13 @@ int sb_target_create_from_gguf(void *file, const SbTargetConfig *runtime, void *
           t.name.find("ffn_gate_inp") == std::string::npos && format_of(t.type) < 0)
         throw GgufError(t.name + " is " + splash::b200::model::ggmlTypeName(t.type) + ", which no kernel of this library reads");
     auto lookup = [](void *context, uint32_t layer, const char *stem, uint32_t configured) -> uint32_t {
-      const GgufFile &file_ = *static_cast<const GgufFile *>(context);
+      const GgufReader &file_ = *static_cast<const GgufReader *>(context);
       const GgufTensor *t = file_.find("blk." + std::to_string(layer) + "." + stem + ".weight");
       const int fmt = t ? format_of(t->type) : -1;
       return fmt < 0 ? configured : uint32_t(fmt);  // (a missing tensor is reported by name when the file is loaded)
     };
     void *target = nullptr;
-    st = sb_target_create_with_formats(&c, lookup, const_cast<GgufFile *>(&f), &target);
+    st = sb_target_create_with_formats(&c, lookup, const_cast<GgufReader *>(&f), &target);
     if (st != SB_OK) return st;
     st = sb_target_load_gguf(target, file);
     if (st != SB_OK) {

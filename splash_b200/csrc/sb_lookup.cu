@@ -2,7 +2,7 @@
 #include <memory>
 #include <new>
 
-#include "model/LookupProposals.hpp"
+#include "model/PromptLookup.hpp"
 #include "sb_internal.h"
 
 using splash::b200::model::LookupIndex;
