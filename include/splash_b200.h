@@ -479,6 +479,22 @@ typedef struct SbPenaltyArgs {
 } SbPenaltyArgs;
 SB_API int sb_sample_penalize(void *stream, const SbPenaltyArgs *args);
 
+/* The tokens a lane's rows may select, in place, before selection (the admission of the reference's selection kernels,
+ * TargetRow::admits, runtime/metal/kernels/decode/sampling.metal:33-46; ops::SamplingBuffers::constraintMasks and
+ * SamplingPolicy::constrained / excludesStopTokens, runtime/ops/Sampling.hpp:58-70,112): a token whose bit in the row's
+ * constraint mask is clear, or that is one of `excluded` (the stop tokens of a lane that ignores end-of-sequence), gets the
+ * logit -inf, which selection reads as not selectable; a row that admits nothing selects 0xFFFFFFFF. masks: device u32
+ * [rows][mask_words], bit t % 32 of word t / 32 for token t, or NULL (unconstrained); excluded: device u32 [n_excluded]
+ * (up to 16) or NULL. */
+typedef struct SbAdmitArgs {
+  float *logits;             /* device fp32 [rows, logit_stride] */
+  const uint32_t *masks;     /* device u32 [rows, mask_words] or NULL */
+  const uint32_t *excluded;  /* device u32 [n_excluded] or NULL */
+  uint32_t rows, vocab, logit_stride, mask_words, n_excluded;
+  uint32_t lanes;            /* 0 or 1: one lane; else rows 16 z .. of lane z */
+} SbAdmitArgs;
+SB_API int sb_sample_admit(void *stream, const SbAdmitArgs *args);
+
 SB_API uint64_t sb_sample_workspace_bytes(uint32_t rows, uint32_t vocab);
 SB_API int sb_sample_verify(void *stream, const SbSampleArgs *args);
 
@@ -711,6 +727,11 @@ SB_API int sb_target_tensor(void *target, int layer, const char *name, void **ou
  * step then rewrites the logits in place before selection (sb_sample_penalize) from the table `penalty_words` (u32
  * [vocab], sb_target_tensor), which the host keeps current: the output's count of each token, bit 31 for the prompt's. */
 SB_API int sb_target_set_penalties(void *target, float repetition, float presence, float frequency);
+/* The lane's admission (every lane's, with several): with `constrained` the step reads a constraint mask for every row from
+ * the target's `constraint_masks` tensor (u32 [16 x lanes][ceil(vocab / 32)], sb_target_tensor), which the host (its grammar
+ * or schema engine) fills before the step; excluded_host: up to 16 token ids no row selects (NULL, 0: none). The step then
+ * runs sb_sample_admit on the logits before the penalties and the selection. */
+SB_API int sb_target_set_admission(void *target, int constrained, const uint32_t *excluded_host, uint32_t n_excluded);
 /* Seeded synthetic weights, a prefilled INT8 cache of `committed` tokens and random GDN state, written on the device. */
 SB_API int sb_target_randomize(void *target, uint64_t seed, uint32_t committed);
 /* Synthetic routing for measurements: with `given` != 0 every MoE block routes by the scores in the target's `moe_scores`

@@ -233,16 +233,43 @@ struct SamplingPolicy {
   uint32_t topK;
   float temperature, topP, minP;
 };
-// No lane of these calls ignores end-of-sequence.
+// The tokens a lane that ignores end-of-sequence never selects: set by the entry points below before they call the model.
 struct StopTokens {
-  bool contains(uint32_t) const { return false; }
+  std::vector<uint32_t> ids;
+  bool contains(uint32_t token) const { return std::find(ids.begin(), ids.end(), token) != ids.end(); }
 };
-constexpr StopTokens kStopTokens{};
+static StopTokens kStopTokens;
 
 #include "sampling_model.inc"
 }  // namespace sampling_model
 
 REF_API uint32_t ref_sampling_candidates() { return sampling_model::kCandidates; }
+
+// The same selections under an admission: mask (u32 words, a bit a token; NULL: unconstrained) and excluded tokens.
+// greedy: the first token of the model's order among the admitted; sampled: referenceDistribution with the admission, then
+// the draw of a row without children. token 0xFFFFFFFF: nothing admitted.
+REF_API int ref_select_admitted(const float *logits, uint32_t vocab, const uint32_t *mask, const uint32_t *excluded, uint32_t n_excluded,
+                                float temperature, float min_p, uint32_t top_k, float top_p, float uniform, uint32_t *token, uint32_t *close,
+                                double *ambiguous) {
+  using namespace sampling_model;
+  kStopTokens.ids.assign(excluded, excluded + n_excluded);
+  const Admission admits{mask, n_excluded != 0};
+  bool any = false;
+  for (uint32_t t = 0; t < vocab && !any; ++t) any = admits(t);
+  *close = 0, *ambiguous = 0.0;
+  if (!any) {
+    *token = 0xffffffffu;
+  } else if (!(temperature > 0.0f)) {
+    *token = referenceArgmax(logits, vocab, admits);
+  } else {
+    const Distribution target = referenceDistribution(logits, vocab, SamplingPolicy{top_k, temperature, top_p, min_p}, admits);
+    const float none[kChildren] = {};
+    const Selection s = referenceSelection(target.probabilities, Children{}, std::span<const float>(none, kChildren), uniform);
+    *token = s.token, *close = s.close, *ambiguous = target.ambiguousMass;
+  }
+  kStopTokens.ids.clear();
+  return 0;
+}
 
 // The greedy selection of one row: the model's order (value descending, id ascending), its first token.
 REF_API uint32_t ref_argmax(const float *logits, uint32_t vocab) { return sampling_model::referenceArgmax(logits, vocab); }

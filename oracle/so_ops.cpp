@@ -604,6 +604,18 @@ SO_API float so_penalize_logit(float value, uint32_t count, float repetition, fl
 // prompt bit (bit 31); a row's context adds the draft tokens on its path: bit r of `drafted` is set when input row r
 // (r >= 1) holds the token, and row `row` counts the bits of its ancestors but the anchor. tree: 8 bytes a row
 // (ancestors u32 first).
+// Admission (TargetRow::admits, runtime/metal/kernels/decode/sampling.metal:33-46): a token whose bit in the row's mask is
+// clear, or that is excluded, is not selectable: its logit becomes -inf.
+SO_API void so_sample_admit(float *logits, uint32_t logit_stride, uint32_t vocab, uint32_t rows, const uint32_t *masks, uint32_t mask_words,
+                            const uint32_t *excluded, uint32_t n_excluded) {
+  for (uint32_t row = 0; row < rows; ++row)
+    for (uint32_t token = 0; token < vocab; ++token) {
+      bool out = masks && !((masks[size_t(row) * mask_words + token / 32] >> (token % 32)) & 1u);
+      for (uint32_t i = 0; i < n_excluded; ++i) out = out || excluded[i] == token;
+      if (out) logits[size_t(row) * logit_stride + token] = -INFINITY;
+    }
+}
+
 SO_API void so_sample_penalize(float *logits, uint32_t logit_stride, uint32_t vocab, uint32_t rows, const uint32_t *words,
                                const uint32_t *input_tokens, const uint32_t *tree, float repetition, float presence, float frequency) {
   const float mx = 3.402823466e+38f;

@@ -141,6 +141,12 @@ class QwenTarget {
   bool imagesStale = true;
   // Measurements with synthetic routing: the blocks route by the host's `moe_scores` instead of their router's scores.
   bool routerScoresGiven = false;
+  // Admission (sb_target_set_admission): the rows' constraint masks, filled by the host when `constrained`; the tokens no row
+  // selects.
+  Buffer constraintMasks, excludedTokens;  // u32 [16 x lanes][maskWords()]; u32 [16]
+  bool constrained = false;
+  uint32_t excludedCount = 0;
+  uint32_t maskWords() const { return (cfg_.vocab + 31) / 32; }
   Buffer tickets;  // u32 [64]: the selection launch's count of finished rows a lane (zero between launches; zeroed at creation)
   bool promptBlock = false;  // the step being encoded commits every row of its block (a block of prompt tokens)
   void buildImages(void *stream) {
@@ -343,6 +349,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole, const FormatOf &forma
   sampleWorkspace_ = Buffer::allocate(ops::Sampling::workspace(uint32_t(R), c.vocab));
   tickets = Buffer::allocate(64 * 4);
   penaltyWords = Buffer::allocate(size_t(c.vocab) * 4 * L);
+  constraintMasks = Buffer::allocate(size_t(kVerifyRows) * L * ((c.vocab + 31) / 32) * 4), excludedTokens = Buffer::allocate(16 * 4);
   candidates = Buffer::allocate(R * 16 * 4), candidateQ = Buffer::allocate(R * 16 * 4), draws = Buffer::allocate(R * 4);
   if (c.moe_experts) {
     moeScores_ = Buffer::allocate(R * moe_.slots * 4), moeScoresGiven_ = Buffer::allocate(R * moe_.slots * 4);
@@ -415,7 +422,7 @@ inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) co
                                              {"logits", logits}, {"selected", selected}, {"results", results}, {"hidden", hidden[0]},
                                              {"hidden1", hidden[1]}, {"tokens", tokens}, {"uniforms", uniforms}, {"committed", committed},
                                              {"pending_rows", pendingRows}, {"tree", tree}, {"page_table", pageTable_}, {"inv_freq", invFreq},
-                                             {"positions", positions}, {"packed", packed_}, {"mixed", mixed_}, {"act", act_}, {"penalty_words", penaltyWords},
+                                             {"positions", positions}, {"packed", packed_}, {"mixed", mixed_}, {"act", act_}, {"penalty_words", penaltyWords}, {"constraint_masks", constraintMasks},
                                              {"candidates", candidates}, {"candidate_q", candidateQ}, {"draws", draws}, {"pending_path", pendingPath},
                                              {"moe_scores", moeScoresGiven_}};
     auto it = g.find(name);
@@ -584,6 +591,12 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   if (drawsGiven) sb.candidateIds = &candidates, sb.candidateQ = &candidateQ, sb.draws = &draws;
   else if (treeGiven && temperature > 0.0f)
     throw std::invalid_argument("QwenTarget::encodeVerify: a sampled tree block needs the draft's candidates and draws (SB_TARGET_DRAWS)");
+  if (constrained || excludedCount) {  // the rows' admission first: what a row does not admit is not selectable
+    SbAdmitArgs ad{logits.as<float>(), constrained ? constraintMasks.as<uint32_t>() : nullptr, excludedCount ? excludedTokens.as<uint32_t>() : nullptr,
+                   rows, c.vocab, c.vocab, maskWords(), excludedCount, 1};
+    check(sb_sample_admit(graph.stream, &ad));
+    ++graph.launches;
+  }
   Sampling::addPenalties(graph, penalties, sb, penaltyWords, tree, rows, c.vocab);  // (nothing when the penalties are off)
   AcceptanceBuffers ab;
   ab.inputTokens = tokens, ab.treeRows = tree, ab.outputTokens = selected, ab.results = results;
@@ -685,6 +698,12 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
   PreparedInput headIn = convert(&outputNorm_.buffer);
   Linear::addWide(graph, output_, nullptr, headIn, R, Epilogue::None, nullptr, logits, c.vocab, true);
   // selection, acceptance, commit: every lane its own rows, uniforms and results
+  if (constrained || excludedCount) {
+    SbAdmitArgs ad{logits.as<float>(), constrained ? constraintMasks.as<uint32_t>() : nullptr, excludedCount ? excludedTokens.as<uint32_t>() : nullptr,
+                   rows, c.vocab, c.vocab, maskWords(), excludedCount, L};
+    check(sb_sample_admit(graph.stream, &ad));
+    ++graph.launches;
+  }
   if (penalties.active()) {
     SbPenaltyArgs pa{logits.as<float>(), penaltyWords.as<uint32_t>(), tokens.as<uint32_t>(), tree.as(), rows, c.vocab, c.vocab,
                      penalties.repetition, penalties.presence, penalties.frequency, L, 0};

@@ -760,6 +760,26 @@ __global__ void __launch_bounds__(kSampleThreads) select_accept_kernel(const SbS
   if (c.committed) commit_lane(c, lane);
 }
 
+// The tokens a lane's rows may select (TargetRow::admits, runtime/metal/kernels/decode/sampling.metal:33-46): a row's
+// constraint mask, a bit a token, and the tokens the lane never selects (the stop tokens of a lane that ignores
+// end-of-sequence). A token a row does not admit gets the logit -inf in place, which every selection reads as not
+// selectable; a row that admits nothing selects the sentinel. One thread per vocabulary token.
+__global__ void admit_kernel(const SbAdmitArgs a_in) {
+  pdl_launch_dependents();
+  pdl_wait();
+  SbAdmitArgs a = a_in;  // lane blockIdx.y: rows 16 z ..
+  a.logits += size_t(kLaneRows) * blockIdx.y * a.logit_stride;
+  if (a.masks) a.masks += size_t(kLaneRows) * blockIdx.y * a.mask_words;
+  const uint32_t token = blockIdx.x * blockDim.x + threadIdx.x;
+  if (token >= a.vocab) return;
+  bool excluded = false;
+  for (uint32_t i = 0; i < a.n_excluded; ++i) excluded |= a.excluded[i] == token;
+  for (uint32_t row = 0; row < a.rows; ++row) {
+    const bool masked = a.masks && !((a.masks[size_t(row) * a.mask_words + token / 32] >> (token % 32)) & 1u);
+    if (excluded || masked) a.logits[size_t(row) * a.logit_stride + token] = -INFINITY;
+  }
+}
+
 // One thread per vocabulary token: the token's count in every row's context, then the penalty on the rows that
 // hold it (runtime/metal/kernels/decode/sampling.metal:997-1048). Products and sums are single IEEE operations in
 // the reference's order, so the result equals the CPU statement bit for bit.
@@ -987,6 +1007,16 @@ int sb_sample_verify(void *stream, const SbSampleArgs *a) {
   SB_REQUIRE(!a->candidate_ids || (a->candidate_q && a->draws), "sb_sample_verify: candidates come with their draft probabilities and the rows' draws");
   SB_REQUIRE(a->lanes <= 64, "sb_sample_verify: %u lanes (up to 64)", a->lanes);
   return launch(sample_kernel, dim3(a->rows, std::max(1u, a->lanes)), dim3(kSampleThreads), as_stream(stream), *a);
+}
+
+int sb_sample_admit(void *stream, const SbAdmitArgs *a) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(a && a->logits && (a->masks || a->n_excluded), "sb_sample_admit: null logits, or neither masks nor excluded tokens");
+  SB_REQUIRE(a->rows >= 1 && a->rows <= 32 && a->vocab >= 1 && a->logit_stride >= a->vocab, "sb_sample_admit: rows %u outside 1..32 or bad vocabulary extent", a->rows);
+  SB_REQUIRE(!a->masks || a->mask_words >= (a->vocab + 31) / 32, "sb_sample_admit: %u mask words a row do not cover %u tokens", a->mask_words, a->vocab);
+  SB_REQUIRE(a->n_excluded <= 16 && (!a->n_excluded || a->excluded), "sb_sample_admit: up to 16 excluded tokens, with their ids");
+  SB_REQUIRE(a->lanes <= 64 && (a->lanes <= 1 || a->rows <= kLaneRows), "sb_sample_admit: %u lanes (up to 64, of up to 16 rows)", a->lanes);
+  return launch(admit_kernel, dim3((a->vocab + 255) / 256, std::max(1u, a->lanes)), dim3(256), as_stream(stream), *a);
 }
 
 int sb_sample_penalize(void *stream, const SbPenaltyArgs *a) {

@@ -264,6 +264,19 @@ int sb_target_share(const SbTargetConfig *config, SbTargetShare *out_share) {
   return guarded([&] { return *out_share = splash::b200::model::shareOf(*config), int(SB_OK); });
 }
 
+int sb_target_set_admission(void *target, int constrained, const uint32_t *excluded_host, uint32_t n_excluded) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target, "sb_target_set_admission: null target");
+  SB_REQUIRE(n_excluded <= 16 && (!n_excluded || excluded_host), "sb_target_set_admission: up to 16 excluded tokens, with their ids");
+  Target *t = static_cast<Target *>(target);
+  SB_CUDA(cudaDeviceSynchronize());
+  for (auto &g : t->graphs) cudaGraphExecDestroy(g.second);  // captured steps carry the old admission
+  t->graphs.clear();
+  if (n_excluded) SB_CUDA(cudaMemcpy(t->model->excludedTokens.as(), excluded_host, n_excluded * 4, cudaMemcpyHostToDevice));
+  t->model->constrained = constrained != 0, t->model->excludedCount = n_excluded;
+  return SB_OK;
+}
+
 int sb_target_set_penalties(void *target, float repetition, float presence, float frequency) {
   SB_NEED_DEVICE();
   SB_REQUIRE(target, "sb_target_set_penalties: null target");

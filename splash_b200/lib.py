@@ -253,6 +253,11 @@ class SbAcceptArgs(ctypes.Structure):
                 ("rows", _U), ("remaining", _U), ("n_stop", _U), ("lanes", _U)]
 
 
+class SbAdmitArgs(ctypes.Structure):
+    _fields_ = [("logits", _P), ("masks", _P), ("excluded", _P), ("rows", _U), ("vocab", _U), ("logit_stride", _U), ("mask_words", _U),
+                ("n_excluded", _U), ("lanes", _U)]
+
+
 class SbSelectAcceptArgs(ctypes.Structure):
     _fields_ = [("sample", SbSampleArgs), ("accept", SbAcceptArgs), ("tickets", _P), ("committed", _P), ("pending_rows", _P),
                 ("pending_path", _P), ("advance", _U), ("reserved", _U)]
@@ -277,6 +282,7 @@ def _bind_ops():
     l.sb_sample_verify.argtypes = [_P, ctypes.POINTER(SbSampleArgs)]
     l.sb_accept.argtypes = [_P, ctypes.POINTER(SbAcceptArgs)]
     l.sb_select_accept.argtypes = [_P, ctypes.POINTER(SbSelectAcceptArgs)]
+    l.sb_sample_admit.argtypes = [_P, ctypes.POINTER(SbAdmitArgs)]
     l.sb_moe_route.argtypes = [_P, ctypes.POINTER(SbMoeRouteArgs)]
     l.sb_moe_experts.argtypes = [_P, ctypes.POINTER(SbMoeExpertArgs)]
     l.sb_moe_scratch_bytes.restype = ctypes.c_uint64

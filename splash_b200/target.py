@@ -125,6 +125,13 @@ class Target:
     def randomize(self, seed, committed):
         lib.check(self.l.sb_target_randomize(self.handle, seed, committed))
 
+    def set_admission(self, constrained=False, excluded=()):
+        """The rows' admission: with `constrained` the step reads every row's constraint mask from the `constraint_masks` tensor;
+        `excluded` are token ids no row selects."""
+        e = np.ascontiguousarray(excluded, np.uint32)
+        self.l.sb_target_set_admission.argtypes = [_P, ctypes.c_int, _P, _U]
+        lib.check(self.l.sb_target_set_admission(self.handle, int(bool(constrained)), e.ctypes.data_as(_P) if e.size else None, e.size))
+
     def set_penalties(self, repetition=1.0, presence=0.0, frequency=0.0):
         lib.check(self.l.sb_target_set_penalties(self.handle, repetition, presence, frequency))
 

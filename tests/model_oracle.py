@@ -122,11 +122,11 @@ def linear(o, fmt, W, n, k, X, rows, epilogue=0, aux=None, out_f32=False, W2=Non
 
 
 def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True, mutate=True, tree=None, penalties=None, penalty_words=None,
-                draws=None, prompt=False):
+                draws=None, prompt=False, admission=None):
     """One verify step of a chain, or of the tree whose rows `tree` holds (uint32 [rows, 2]: ancestors, parent | depth << 16).
     draws = (candidate ids u32 [rows, 16], draft probabilities f32 [rows, 16], drawn children u8 [rows, 4]): sampled rows
     select by recursive rejection sampling over these children. prompt: the rows are prompt tokens, all committed whatever
-    was selected. Returns dict(logits, selected, retained, accepted, mask, tokens)."""
+    was selected. admission = (masks u32 [rows, words] or None, excluded token ids): what the rows may select. Returns dict(logits, selected, retained, accepted, mask, tokens)."""
     o = ol.bind_ops(ol.load())
     rows = len(tokens)
     H, D, I, V = cfg["hidden"], cfg["head_dim"], cfg["intermediate"], cfg["vocab"]
@@ -203,6 +203,13 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
     nf = np.zeros_like(h)
     o.so_rmsnorm(P(h), rows, H, H, P(w[-1, "output_norm"]), P(nf), H)
     logits = linear(o, cfg["fmt_head"], w[-1, "output"], V, H, nf, rows, out_f32=True)
+    if admission is not None:
+        masks, excluded = admission
+        excluded = np.ascontiguousarray(excluded, np.uint32)
+        o.so_sample_admit.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32,
+                                      ctypes.c_void_p, ctypes.c_uint32]
+        o.so_sample_admit(P(logits), V, V, rows, P(np.ascontiguousarray(masks[:rows], np.uint32)) if masks is not None else None,
+                          (V + 31) // 32, P(excluded) if len(excluded) else None, len(excluded))
     if penalties is not None:  # (repetition, presence, frequency) over the table and each row's path
         o.so_sample_penalize(P(logits), V, V, rows, P(np.ascontiguousarray(penalty_words, np.uint32)), P(tokens), P(rows_tree), *penalties)
     selected = np.zeros(rows, np.uint32)

@@ -539,3 +539,51 @@ def test_lanes_reject_what_they_do_not_step():
     t = target.Target(**dict(target.TINY, lanes=2))
     with pytest.raises(lib.SbError):
         t.verify(np.arange(16, dtype=np.uint32))                             # the one-lane entry
+
+
+def test_admission_of_lanes_equals_the_oracles():
+    """sb_sample_admit on the rows of several lanes in one launch: the logits bit for bit what the oracle's pass leaves lane by lane
+    (constraint masks with and without excluded tokens), then greedy selections that respect them."""
+    lib, l, o = _setup()
+    o.so_sample_admit.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_uint32,
+                                  ctypes.c_void_p, ctypes.c_uint32]
+    rng = np.random.default_rng(51)
+    L, rows, V = 3, 11, 5003
+    words = (V + 31) // 32
+    logits = rng.standard_normal((16 * L, V)).astype(np.float32)
+    masks = rng.integers(0, 2 ** 32, (16 * L, words), dtype=np.uint64).astype(np.uint32)
+    masks[16 + 2] = 0                                     # a row of lane 1 that admits nothing
+    excluded = np.array([7, int(np.argmax(logits[0])), V - 1], np.uint32)
+    up = lib.DeviceBuffer.from_numpy
+    for use_masks, use_excluded in ((True, True), (True, False), (False, True)):
+        dl, dm, de = up(logits), up(masks), up(excluded)
+        a = lib.SbAdmitArgs(dl.ptr, dm.ptr if use_masks else None, de.ptr if use_excluded else None, rows, V, V, words, 3 if use_excluded else 0, L)
+        lib.check(l.sb_sample_admit(None, ctypes.byref(a)))
+        lib.stream_sync()
+        got = dl.to_numpy(np.float32, logits.shape)
+        want = logits.copy()
+        for lane in range(L):
+            block = want[16 * lane:16 * lane + rows]
+            o.so_sample_admit(P(block), V, V, rows, P(np.ascontiguousarray(masks[16 * lane:16 * lane + rows])) if use_masks else None, words,
+                              P(excluded) if use_excluded else None, 3 if use_excluded else 0)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+        assert np.array_equal(got[rows:16], logits[rows:16])          # the slots past the lane's rows stay as they were
+        sel = lib.DeviceBuffer(16 * L * 4)
+        sel.fill(0)
+        sa = lib.SbSampleArgs(dl.ptr, up(np.zeros(16 * L, np.uint32)).ptr, None, sel.ptr, None, rows, V, V, 0.0, 0.0, 0, 1.0)
+        sa.lanes = L
+        lib.check(l.sb_sample_verify(None, ctypes.byref(sa)))
+        lib.stream_sync()
+        chosen = sel.to_numpy(np.uint32, (L, 16))
+        for lane in range(L):
+            for r in range(rows):
+                t = int(chosen[lane, r])
+                if use_masks and lane == 1 and r == 2:
+                    assert t == 0xffffffff
+                    continue
+                assert not use_masks or (masks[16 * lane + r, t // 32] >> (t % 32)) & 1
+                assert not use_excluded or t not in excluded
+    bad = lib.SbAdmitArgs(dl.ptr, None, None, rows, V, V, words, 0, L)
+    assert l.sb_sample_admit(None, ctypes.byref(bad)) == -1               # neither masks nor excluded tokens
+    bad = lib.SbAdmitArgs(dl.ptr, dm.ptr, None, rows, V, V, words - 1, 0, L)
+    assert l.sb_sample_admit(None, ctypes.byref(bad)) == -1               # mask rows too short for the vocabulary

@@ -296,3 +296,42 @@ def test_tiny_model_prompt_blocks_then_verify_steps_match_oracle(flags_name):
     # a tree block cannot be a prompt block
     with pytest.raises(Exception):
         t.verify(prompt[:4], flags=target.ADVANCE | target.PROMPT | target.TREE)
+
+
+@pytest.mark.parametrize("flags_name", ["eager", "graph"])
+def test_tiny_model_step_under_an_admission_matches_oracle(flags_name):
+    """Constraint masks a row and excluded tokens: the step's selections come from the admitted tokens only, as the oracle's
+    step with the same admission selects; switched off again the step is the plain one."""
+    lib, target, t, cfg, w, s = build(seed=12)
+    V = cfg["vocab"]
+    rng = np.random.default_rng(4)
+    tokens = mo.draft_chain(cfg, w, s, 23, rows=16, p_match=1.0, seed=2)
+    plain = mo.verify_step(cfg, w, s, tokens, mutate=False)
+    masks = rng.integers(0, 2 ** 32, (16, (V + 31) // 32), dtype=np.uint64).astype(np.uint32)
+    for r in range(0, 16, 2):                             # every other row loses the token it would have selected
+        masks[r, plain["selected"][r] // 32] &= ~np.uint32(1 << (plain["selected"][r] % 32))
+    excluded = np.array([plain["selected"][1], plain["selected"][3], 11], np.uint32)
+    want = mo.verify_step(cfg, w, s, tokens, mutate=False, admission=(masks, excluded))
+    assert not np.array_equal(want["selected"], plain["selected"])
+    t.upload(-1, "constraint_masks", masks)
+    t.set_admission(True, excluded)
+    flags = target.GRAPH if flags_name == "graph" else 0
+    got_tokens, retained, accepted, mask = t.verify(tokens, flags=flags)
+    assert lib.device_status() == 0
+    logits = t.download(-1, "logits", np.float32, (16, V))
+    assert np.array_equal(np.isneginf(logits), np.isneginf(want["logits"]))
+    finite = np.isfinite(want["logits"])
+    scale = np.abs(want["logits"][finite]).max()
+    assert np.abs(logits[finite] - want["logits"][finite]).max() <= 2e-2 * scale
+    masked = np.where(finite, want["logits"], -np.inf)
+    top2 = np.sort(masked, axis=1)[:, -2:]
+    if ((top2[:, 1] - top2[:, 0]) > 1e-2)[:want["retained"]].all():
+        assert (retained, accepted, mask) == (want["retained"], want["accepted"], want["mask"])
+        assert np.array_equal(got_tokens, want["tokens"])
+    for tok in got_tokens:
+        assert int(tok) not in excluded
+    t.set_admission(False, ())
+    got_tokens, retained, accepted, mask = t.verify(tokens, flags=flags)
+    top2 = np.sort(plain["logits"], axis=1)[:, -2:]
+    if ((top2[:, 1] - top2[:, 0]) > 1e-2)[:plain["retained"]].all():
+        assert np.array_equal(got_tokens, plain["tokens"])

@@ -238,3 +238,52 @@ def test_greedy_selection_matches_the_reference_order():
         assert ref.ref_best(P(logits[r]), vocab, 8, P(best)) == 8
         assert np.array_equal(best, np.lexsort((np.arange(vocab), -logits[r]))[:8])
     assert selected[1] == 7 and selected[2] == 0 and selected[3] == vocab - 1 and selected[4] == 100 and selected[5] == 4321
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.8])
+def test_admission_matches_the_reference_model(temperature):
+    """Rows that admit only the tokens of a constraint mask, less the excluded ones: the oracle's in-place -inf followed by its
+    selection against the reference's selections under the same admission (referenceArgmax / referenceDistribution with an
+    Admission, dev/tests/engine/target_sampling_metal_test.mm:269-300,333-403)."""
+    ref = _models()
+    F = ctypes.c_float
+    ref.ref_select_admitted.argtypes = [_V, _U, _V, _V, _U, F, F, _U, F, F, _V, _V, _V]
+    o = ol.bind_ops(ol.load())
+    o.so_sample_admit.argtypes = [_V, _U, _U, _U, _V, _U, _V, _U]
+    rng = np.random.default_rng(23)
+    rows, vocab = 16, 3001
+    words = (vocab + 31) // 32
+    logits = (rng.standard_normal((rows, vocab)) * 2).astype(np.float32)
+    masks = rng.integers(0, 2 ** 32, (rows, words), dtype=np.uint64).astype(np.uint32)
+    masks[3] = 0                                          # a row that admits nothing
+    masks[4] = 0
+    masks[4, 40] = 1 << 7                                 # a row that admits one token, 40 * 32 + 7
+    excluded = np.array([int(np.argmax(logits[0])), int(np.argmax(logits[1])), 5], np.uint32)
+    masks[0, excluded[0] // 32] |= np.uint32(1 << (excluded[0] % 32))   # admitted by the mask, excluded all the same
+    uniforms = rng.uniform(0, 1, 80).astype(np.float32)
+    for use_mask, use_excluded in ((True, True), (True, False), (False, True)):
+        mine = logits.copy()
+        ex = excluded if use_excluded else np.zeros(0, np.uint32)
+        o.so_sample_admit(P(mine), vocab, vocab, rows, P(masks) if use_mask else None, words, P(ex) if len(ex) else None, len(ex))
+        selected = np.zeros(rows, np.uint32)
+        o.so_sample_verify(P(mine), vocab, vocab, 1, P(np.zeros(rows, np.uint32)), temperature, P(uniforms), P(selected), None)
+        for r in range(rows):
+            # one row at a time: a row alone has no drafted child to test
+            one = np.zeros(1, np.uint32)
+            u = uniforms.copy()
+            u[0] = uniforms[r]
+            o.so_sample_verify(P(mine[r]), vocab, vocab, 1, P(np.zeros(1, np.uint32)), temperature, P(u), P(one), None)
+            token, close, amb = ctypes.c_uint32(), ctypes.c_uint32(), ctypes.c_double()
+            ref.ref_select_admitted(P(logits[r]), vocab, P(masks[r]) if use_mask else None, P(ex) if len(ex) else None, len(ex), temperature,
+                                    0.0, 0, 1.0, float(uniforms[r]), ctypes.byref(token), ctypes.byref(close), ctypes.byref(amb))
+            if close.value or amb.value > 0:
+                continue
+            assert one[0] == token.value, (use_mask, use_excluded, r)
+            if token.value != 0xffffffff:
+                assert not use_mask or (masks[r, token.value // 32] >> (token.value % 32)) & 1
+                assert not use_excluded or token.value not in excluded
+        if use_mask:
+            o.so_sample_verify(P(mine[3]), vocab, vocab, 1, P(np.zeros(1, np.uint32)), temperature, P(uniforms), P(one), None)
+            assert one[0] == 0xffffffff
+            o.so_sample_verify(P(mine[4]), vocab, vocab, 1, P(np.zeros(1, np.uint32)), temperature, P(uniforms), P(one), None)
+            assert one[0] == 40 * 32 + 7
