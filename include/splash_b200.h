@@ -727,6 +727,10 @@ SB_API int sb_target_tensor(void *target, int layer, const char *name, void **ou
  * step then rewrites the logits in place before selection (sb_sample_penalize) from the table `penalty_words` (u32
  * [vocab], sb_target_tensor), which the host keeps current: the output's count of each token, bit 31 for the prompt's. */
 SB_API int sb_target_set_penalties(void *target, float repetition, float presence, float frequency);
+/* The end of the sampled rows' distribution (SamplingPolicy::minP / topK / topP, runtime/ops/Sampling.hpp:58-85: the tokens
+ * min_p leaves, then the top_k most likely of those, then their top_p nucleus; 0 / 0 / 1 keep everything, the default).
+ * Greedy steps (temperature 0) read none of the three. Vocabularies up to the limit of sb_sample_verify's filters. */
+SB_API int sb_target_set_policy(void *target, float min_p, uint32_t top_k, float top_p);
 /* The lane's admission (every lane's, with several): with `constrained` the step reads a constraint mask for every row from
  * the target's `constraint_masks` tensor (u32 [16 x lanes][ceil(vocab / 32)], sb_target_tensor), which the host (its grammar
  * or schema engine) fills before the step; excluded_host: up to 16 token ids no row selects (NULL, 0: none). The step then

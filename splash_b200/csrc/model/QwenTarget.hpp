@@ -146,6 +146,9 @@ class QwenTarget {
   Buffer constraintMasks, excludedTokens;  // u32 [16 x lanes][maskWords()]; u32 [16]
   bool constrained = false;
   uint32_t excludedCount = 0;
+  // The end of a sampled row's distribution (sb_target_set_policy): min-p, then top-k, then the top-p nucleus; off at 0 / 0 / 1.
+  float minP = 0.0f, topP = 1.0f;
+  uint32_t topK = 0;
   uint32_t maskWords() const { return (cfg_.vocab + 31) / 32; }
   Buffer tickets;  // u32 [64]: the selection launch's count of finished rows a lane (zero between launches; zeroed at creation)
   bool promptBlock = false;  // the step being encoded commits every row of its block (a block of prompt tokens)
@@ -605,7 +608,7 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   const uint32_t stepAdvance = promptBlock ? 3u | rows << 8 : advance ? 1u : keepPending ? 2u : 0u;
   const bool endsHere = !tp_ && !(treeGiven && advance);
   const Sampling::LaneCommit lc{committed, pendingRows, pendingPath, stepAdvance};
-  Sampling::addVerifyAndAcceptance(graph, SamplingPolicy{temperature}, sb, ab, rows, c.vocab, kVerifyRows, 1, tickets, endsHere ? &lc : nullptr);
+  Sampling::addVerifyAndAcceptance(graph, SamplingPolicy{temperature, minP, topK, topP}, sb, ab, rows, c.vocab, kVerifyRows, 1, tickets, endsHere ? &lc : nullptr);
   if (tp_ && exchange != exchangesPerStep()) throw std::logic_error("QwenTarget::encodeVerify: exchange count");
   // The accepted path's KV rows move from their rows' slots to their depths' (a chain's are there already).
   if (treeGiven && advance) {
@@ -711,7 +714,7 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
     ++graph.launches;
   }
   SbSampleArgs sa{logits.as<float>(), tokens.as<uint32_t>(), temperature > 0.0f ? uniforms.as<float>() : nullptr, selected.as<uint32_t>(),
-                  sampleWorkspace_.as<float>(), rows, c.vocab, c.vocab, temperature, 0.0f, 0, 1.0f, nullptr, nullptr, nullptr, nullptr, L, 0};
+                  sampleWorkspace_.as<float>(), rows, c.vocab, c.vocab, temperature, minP, topK, topP, nullptr, nullptr, nullptr, nullptr, L, 0};
   if (drawsGiven && temperature > 0.0f) sa.candidate_ids = candidates.as<uint32_t>(), sa.candidate_q = candidateQ.as<float>(), sa.draws = draws.as<uint8_t>();
   const uint32_t stepAdvance = promptBlock ? 3u | rows << 8 : advance ? 1u : keepPending ? 2u : 0u;
   const bool endsHere = !(treeGiven && advance);  // (a tree's path commit reads the lanes' positions before they move)

@@ -264,6 +264,18 @@ int sb_target_share(const SbTargetConfig *config, SbTargetShare *out_share) {
   return guarded([&] { return *out_share = splash::b200::model::shareOf(*config), int(SB_OK); });
 }
 
+int sb_target_set_policy(void *target, float min_p, uint32_t top_k, float top_p) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target, "sb_target_set_policy: null target");
+  SB_REQUIRE(min_p >= 0.0f && min_p <= 1.0f && top_p > 0.0f && top_p <= 1.0f, "sb_target_set_policy: min_p %g outside 0..1 or top_p %g outside (0, 1]", double(min_p), double(top_p));
+  Target *t = static_cast<Target *>(target);
+  SB_CUDA(cudaDeviceSynchronize());
+  for (auto &g : t->graphs) cudaGraphExecDestroy(g.second);  // captured steps carry the old policy
+  t->graphs.clear();
+  t->model->minP = min_p, t->model->topK = top_k, t->model->topP = top_p;
+  return SB_OK;
+}
+
 int sb_target_set_admission(void *target, int constrained, const uint32_t *excluded_host, uint32_t n_excluded) {
   SB_NEED_DEVICE();
   SB_REQUIRE(target, "sb_target_set_admission: null target");

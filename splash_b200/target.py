@@ -125,6 +125,10 @@ class Target:
     def randomize(self, seed, committed):
         lib.check(self.l.sb_target_randomize(self.handle, seed, committed))
 
+    def set_policy(self, min_p=0.0, top_k=0, top_p=1.0):
+        self.l.sb_target_set_policy.argtypes = [_P, _F, _U, _F]
+        lib.check(self.l.sb_target_set_policy(self.handle, min_p, top_k, top_p))
+
     def set_admission(self, constrained=False, excluded=()):
         """The rows' admission: with `constrained` the step reads every row's constraint mask from the `constraint_masks` tensor;
         `excluded` are token ids no row selects."""

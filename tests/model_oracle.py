@@ -122,11 +122,12 @@ def linear(o, fmt, W, n, k, X, rows, epilogue=0, aux=None, out_f32=False, W2=Non
 
 
 def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True, mutate=True, tree=None, penalties=None, penalty_words=None,
-                draws=None, prompt=False, admission=None):
+                draws=None, prompt=False, admission=None, policy=(0.0, 0, 1.0)):
     """One verify step of a chain, or of the tree whose rows `tree` holds (uint32 [rows, 2]: ancestors, parent | depth << 16).
     draws = (candidate ids u32 [rows, 16], draft probabilities f32 [rows, 16], drawn children u8 [rows, 4]): sampled rows
     select by recursive rejection sampling over these children. prompt: the rows are prompt tokens, all committed whatever
-    was selected. admission = (masks u32 [rows, words] or None, excluded token ids): what the rows may select. Returns dict(logits, selected, retained, accepted, mask, tokens)."""
+    was selected. admission = (masks u32 [rows, words] or None, excluded token ids): what the rows may select. policy = (min_p,
+    top_k, top_p): the end of a sampled row's distribution. Returns dict(logits, selected, retained, accepted, mask, tokens)."""
     o = ol.bind_ops(ol.load())
     rows = len(tokens)
     H, D, I, V = cfg["hidden"], cfg["head_dim"], cfg["intermediate"], cfg["vocab"]
@@ -218,10 +219,13 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
         o.so_sample_verify_draws.argtypes = ([ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_float, ctypes.c_float,
                                               ctypes.c_uint32, ctypes.c_float] + [ctypes.c_void_p] * 6)
         ids, q, dr = (np.ascontiguousarray(a) for a in draws)
-        o.so_sample_verify_draws(P(logits), V, V, rows, float(temperature), 0.0, 0, 1.0, P(uniforms), P(ids), P(q), P(dr), P(selected), P(margin))
+        o.so_sample_verify_draws(P(logits), V, V, rows, float(temperature), float(policy[0]), int(policy[1]), float(policy[2]), P(uniforms), P(ids), P(q), P(dr),
+                                 P(selected), P(margin))
     else:
-        o.so_sample_verify(P(logits), V, V, rows, P(tokens), float(temperature), P(uniforms) if uniforms is not None else None, P(selected),
-                           P(margin))
+        o.so_sample_verify_filtered.argtypes = [ctypes.c_void_p, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_uint32, ctypes.c_void_p, ctypes.c_float,
+                                                ctypes.c_float, ctypes.c_uint32, ctypes.c_float, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        o.so_sample_verify_filtered(P(logits), V, V, rows, P(tokens), float(temperature), float(policy[0]), int(policy[1]), float(policy[2]),
+                                    P(uniforms) if uniforms is not None else None, P(selected), P(margin), None)
     out_tokens = selected.copy()
     res = np.zeros(3, np.uint32)
     o.so_accept(P(tokens), P(rows_tree), P(out_tokens), rows, 16, None, 0, P(res[0:1]), P(res[1:2]), P(res[2:3]))

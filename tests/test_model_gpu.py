@@ -335,3 +335,33 @@ def test_tiny_model_step_under_an_admission_matches_oracle(flags_name):
     top2 = np.sort(plain["logits"], axis=1)[:, -2:]
     if ((top2[:, 1] - top2[:, 0]) > 1e-2)[:plain["retained"]].all():
         assert np.array_equal(got_tokens, plain["tokens"])
+
+
+def test_tiny_model_sampled_steps_under_a_policy_match_oracle():
+    """The production policy's end of the distribution (top 20, nucleus 0.95) and a min-p one, set on the target: whole sampled
+    steps select as the oracle's step with the same policy, wherever no test or cut sat within rounding of its threshold."""
+    lib, target, t, cfg, w, s = build(seed=14)
+    compared, differs = 0, 0
+    for policy in ((0.0, 20, 0.95), (0.05, 0, 1.0), (0.0, 5, 1.0)):
+        t.set_policy(*policy)
+        for seed in range(5):
+            t.reset(2048)
+            s["committed"], s["pending_rows"] = 2048, 0
+            rng = np.random.default_rng(300 + seed)
+            tokens = mo.draft_chain(cfg, w, s, 7 + seed, rows=16, seed=seed)
+            uniforms = rng.random(80).astype(np.float32)
+            want = mo.verify_step(cfg, w, s, tokens, temperature=1.0, uniforms=uniforms, mutate=False, policy=policy)
+            loose = mo.verify_step(cfg, w, s, tokens, temperature=1.0, uniforms=uniforms, mutate=False)
+            got_tokens, retained, accepted, mask = t.verify(tokens, uniforms=uniforms, temperature=1.0)
+            assert lib.device_status() == 0
+            if not (want["margin"][:want["retained"]] > 1e-3).all():
+                continue
+            compared += 1
+            differs += not np.array_equal(want["selected"], loose["selected"])
+            assert retained == want["retained"] and accepted == want["accepted"], (policy, seed)
+            assert np.array_equal(got_tokens[:retained], want["tokens"][:retained]), (policy, seed)
+    t.set_policy()
+    assert compared >= 9, compared
+    assert differs >= 3, differs              # the policies did change what the rows select
+    with pytest.raises(lib.SbError):
+        t.set_policy(min_p=1.5)
