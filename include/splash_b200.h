@@ -430,6 +430,12 @@ SB_API int sb_gdn_verify_static(void *stream, const SbGdnArgs *args);
  * uniforms (device fp32): [0,16) row draws, 16 + 4 * row child tests (runtime/metal/abi/Sampling.h:12-31).
  * Replaces ops::Sampling::addVerify (runtime/ops/Sampling.cpp:198-328; runtime/metal/kernels/decode/sampling.metal
  * :1896-1991 greedy, :713-885 draw). */
+typedef struct SbLanePolicy {
+  float temperature; /* 0: greedy */
+  float min_p;       /* 0: off */
+  uint32_t top_k;    /* 0: off */
+  float top_p;       /* 1: off */
+} SbLanePolicy;
 typedef struct SbSampleArgs {
   const float *logits;       /* fp32 [rows, logit_stride] */
   const uint32_t *input_tokens; /* device u32 [rows] */
@@ -459,6 +465,11 @@ typedef struct SbSampleArgs {
   const uint8_t *draws;          /* device u8 [rows, 4] */
   uint32_t lanes;                /* 0 or 1: one lane */
   uint32_t reserved;
+  /* Optional: a policy a lane (device SbLanePolicy [lanes]), read by the kernel in place of temperature / min_p / top_k /
+   * top_p above, so the lanes of one step may be greedy and sampled side by side (the reference's policies a lane,
+   * Sampling::addVerify's `policies`, runtime/ops/Sampling.hpp:58-85) and may change between replays of a captured step.
+   * Needs uniforms and the workspace. */
+  const struct SbLanePolicy *lane_policies;
 } SbSampleArgs;
 /* The sampling penalties of one lane's rows, in place, before selection: a token the prompt or the output holds has a
  * positive logit divided and a negative one multiplied by `repetition`; a token the output holds `count` times is
@@ -731,6 +742,11 @@ SB_API int sb_target_set_penalties(void *target, float repetition, float presenc
  * min_p leaves, then the top_k most likely of those, then their top_p nucleus; 0 / 0 / 1 keep everything, the default).
  * Greedy steps (temperature 0) read none of the three. Vocabularies up to the limit of sb_sample_verify's filters. */
 SB_API int sb_target_set_policy(void *target, float min_p, uint32_t top_k, float top_p);
+/* A policy a lane (host array of SbTargetConfig.lanes entries; NULL: back to the step's temperature and sb_target_set_policy's
+ * end for every lane): the lanes' steps then select each by its own temperature and end of the distribution, greedy and
+ * sampled lanes side by side. The values live on the device and are read by the selection when it runs, so they can change
+ * between steps without a new capture. Steps need uniforms while policies are set. */
+SB_API int sb_target_set_lane_policies(void *target, const SbLanePolicy *policies_host);
 /* The lane's admission (every lane's, with several): with `constrained` the step reads a constraint mask for every row from
  * the target's `constraint_masks` tensor (u32 [16 x lanes][ceil(vocab / 32)], sb_target_tensor), which the host (its grammar
  * or schema engine) fills before the step; excluded_host: up to 16 token ids no row selects (NULL, 0: none). The step then

@@ -146,6 +146,10 @@ class QwenTarget {
   Buffer constraintMasks, excludedTokens;  // u32 [16 x lanes][maskWords()]; u32 [16]
   bool constrained = false;
   uint32_t excludedCount = 0;
+  // A policy a lane (sb_target_set_lane_policies): SbLanePolicy [lanes] on the device, read by the selection when it runs.
+  Buffer lanePolicies;
+  bool lanePoliciesSet = false;
+  bool manyRowStep() const { return wide_; }
   // The end of a sampled row's distribution (sb_target_set_policy): min-p, then top-k, then the top-p nucleus; off at 0 / 0 / 1.
   float minP = 0.0f, topP = 1.0f;
   uint32_t topK = 0;
@@ -352,6 +356,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole, const FormatOf &forma
   sampleWorkspace_ = Buffer::allocate(ops::Sampling::workspace(uint32_t(R), c.vocab));
   tickets = Buffer::allocate(64 * 4);
   penaltyWords = Buffer::allocate(size_t(c.vocab) * 4 * L);
+  lanePolicies = Buffer::allocate(sizeof(SbLanePolicy) * 64);
   constraintMasks = Buffer::allocate(size_t(kVerifyRows) * L * ((c.vocab + 31) / 32) * 4), excludedTokens = Buffer::allocate(16 * 4);
   candidates = Buffer::allocate(R * 16 * 4), candidateQ = Buffer::allocate(R * 16 * 4), draws = Buffer::allocate(R * 4);
   if (c.moe_experts) {
@@ -713,9 +718,12 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
     check(sb_sample_penalize(graph.stream, &pa));
     ++graph.launches;
   }
-  SbSampleArgs sa{logits.as<float>(), tokens.as<uint32_t>(), temperature > 0.0f ? uniforms.as<float>() : nullptr, selected.as<uint32_t>(),
+  // (with policies a lane, the kernel reads each lane's temperature and end of the distribution from lanePolicies)
+  const bool sampled = temperature > 0.0f || lanePoliciesSet;
+  SbSampleArgs sa{logits.as<float>(), tokens.as<uint32_t>(), sampled ? uniforms.as<float>() : nullptr, selected.as<uint32_t>(),
                   sampleWorkspace_.as<float>(), rows, c.vocab, c.vocab, temperature, minP, topK, topP, nullptr, nullptr, nullptr, nullptr, L, 0};
-  if (drawsGiven && temperature > 0.0f) sa.candidate_ids = candidates.as<uint32_t>(), sa.candidate_q = candidateQ.as<float>(), sa.draws = draws.as<uint8_t>();
+  if (lanePoliciesSet) sa.lane_policies = lanePolicies.as<SbLanePolicy>();
+  if (drawsGiven && sampled) sa.candidate_ids = candidates.as<uint32_t>(), sa.candidate_q = candidateQ.as<float>(), sa.draws = draws.as<uint8_t>();
   const uint32_t stepAdvance = promptBlock ? 3u | rows << 8 : advance ? 1u : keepPending ? 2u : 0u;
   const bool endsHere = !(treeGiven && advance);  // (a tree's path commit reads the lanes' positions before they move)
   SbSelectAcceptArgs fused{};

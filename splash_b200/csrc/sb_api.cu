@@ -129,6 +129,7 @@ uint64_t sb_struct_bytes(const char *name) {
   SB_SIZE_OF(SbAcceptArgs);
   SB_SIZE_OF(SbSelectAcceptArgs);
   SB_SIZE_OF(SbAdmitArgs);
+  SB_SIZE_OF(SbLanePolicy);
   SB_SIZE_OF(SbGgufTensor);
   SB_SIZE_OF(SbMoeRouteArgs);
   SB_SIZE_OF(SbMoeExpertArgs);

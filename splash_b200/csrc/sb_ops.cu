@@ -489,6 +489,10 @@ __device__ __forceinline__ void sample_row(const SbSampleArgs &a_in) {
     if (a.workspace) a.workspace += size_t(r0) * (2 * ((a.vocab + kShard - 1) / kShard) + 8);
     if (a.cut_out) a.cut_out += 2 * r0;
     if (a.candidate_ids) a.candidate_ids += kDrawCandidates * r0, a.candidate_q += kDrawCandidates * r0, a.draws += 4 * r0;
+    if (a.lane_policies) {  // the lane's own policy
+      const SbLanePolicy q = a.lane_policies[z];
+      a.temperature = q.temperature, a.min_p = q.min_p, a.top_k = q.top_k, a.top_p = q.top_p;
+    }
   }
   const uint32_t r = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const float *l = a.logits + size_t(r) * a.logit_stride;
@@ -1006,6 +1010,7 @@ int sb_sample_verify(void *stream, const SbSampleArgs *a) {
   SB_REQUIRE(!filtered || a->vocab <= kMaxFilterShards * kShard, "sb_sample_verify: min-p / top-k / top-p support vocabularies up to %u", kMaxFilterShards * kShard);
   SB_REQUIRE(!a->candidate_ids || (a->candidate_q && a->draws), "sb_sample_verify: candidates come with their draft probabilities and the rows' draws");
   SB_REQUIRE(a->lanes <= 64, "sb_sample_verify: %u lanes (up to 64)", a->lanes);
+  SB_REQUIRE(!a->lane_policies || (a->uniforms && a->workspace && a->vocab <= kMaxFilterShards * kShard), "sb_sample_verify: policies a lane need uniforms, the workspace and a vocabulary the filters take");
   return launch(sample_kernel, dim3(a->rows, std::max(1u, a->lanes)), dim3(kSampleThreads), as_stream(stream), *a);
 }
 
@@ -1052,6 +1057,7 @@ int sb_select_accept(void *stream, const SbSelectAcceptArgs *c) {
   SB_REQUIRE(!filtered || a->vocab <= kMaxFilterShards * kShard, "sb_select_accept: min-p / top-k / top-p support vocabularies up to %u", kMaxFilterShards * kShard);
   SB_REQUIRE(!a->candidate_ids || (a->candidate_q && a->draws), "sb_select_accept: candidates come with their draft probabilities and the rows' draws");
   SB_REQUIRE(a->lanes <= 64, "sb_select_accept: %u lanes (up to 64)", a->lanes);
+  SB_REQUIRE(!a->lane_policies || (a->uniforms && a->workspace && a->vocab <= kMaxFilterShards * kShard), "sb_select_accept: policies a lane need uniforms, the workspace and a vocabulary the filters take");
   SB_REQUIRE(b->input_tokens == a->input_tokens && b->tokens == a->selected && b->tree && b->results, "sb_select_accept: acceptance reads the selection's rows: same input tokens, tokens = selected");
   SB_REQUIRE(b->rows == a->rows && b->remaining >= 1 && std::max(1u, b->lanes) == std::max(1u, a->lanes), "sb_select_accept: selection and acceptance disagree on rows or lanes");
   SB_REQUIRE(b->n_stop == 0 || b->stop_tokens, "sb_select_accept: stop tokens missing");

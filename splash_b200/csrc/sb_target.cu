@@ -276,6 +276,28 @@ int sb_target_set_policy(void *target, float min_p, uint32_t top_k, float top_p)
   return SB_OK;
 }
 
+int sb_target_set_lane_policies(void *target, const SbLanePolicy *policies_host) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target, "sb_target_set_lane_policies: null target");
+  Target *t = static_cast<Target *>(target);
+  QwenTarget &m = *t->model;
+  SB_REQUIRE(m.manyRowStep(), "sb_target_set_lane_policies: a target of one lane takes the step's temperature and sb_target_set_policy");
+  if (policies_host)
+    for (uint32_t l = 0; l < m.lanes(); ++l) {
+      const SbLanePolicy &q = policies_host[l];
+      SB_REQUIRE(q.temperature >= 0.0f && q.min_p >= 0.0f && q.min_p <= 1.0f && q.top_p > 0.0f && q.top_p <= 1.0f,
+                 "sb_target_set_lane_policies: lane %u: temperature %g, min_p %g, top_p %g", l, double(q.temperature), double(q.min_p), double(q.top_p));
+    }
+  SB_CUDA(cudaDeviceSynchronize());
+  if (m.lanePoliciesSet != (policies_host != nullptr)) {  // (only switching them on or off changes the captured step: the values are read on the device)
+    for (auto &g : t->graphs) cudaGraphExecDestroy(g.second);
+    t->graphs.clear();
+  }
+  if (policies_host) SB_CUDA(cudaMemcpy(m.lanePolicies.as(), policies_host, sizeof(SbLanePolicy) * m.lanes(), cudaMemcpyHostToDevice));
+  m.lanePoliciesSet = policies_host != nullptr;
+  return SB_OK;
+}
+
 int sb_target_set_admission(void *target, int constrained, const uint32_t *excluded_host, uint32_t n_excluded) {
   SB_NEED_DEVICE();
   SB_REQUIRE(target, "sb_target_set_admission: null target");
@@ -533,7 +555,7 @@ int sb_target_verify_lanes(void *target, void *stream, const uint32_t *tokens_ho
   SB_NEED_DEVICE();
   SB_REQUIRE(target && tokens_host && out_tokens_host && out_results_host, "sb_target_verify_lanes: null pointer");
   SB_REQUIRE(rows >= 1 && rows <= splash::b200::model::kVerifyRows, "sb_target_verify_lanes: rows = %u outside 1..16", rows);
-  SB_REQUIRE(temperature == 0.0f || uniforms_host, "sb_target_verify_lanes: a sampled policy needs uniforms");
+  SB_REQUIRE((temperature == 0.0f && !static_cast<Target *>(target)->model->lanePoliciesSet) || uniforms_host, "sb_target_verify_lanes: a sampled policy (or policies a lane) needs uniforms");
   Target *t = static_cast<Target *>(target);
   QwenTarget &m = *t->model;
   const uint32_t L = m.lanes();

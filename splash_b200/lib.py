@@ -225,7 +225,11 @@ class SbSampleArgs(ctypes.Structure):
     _fields_ = [("logits", _P), ("input_tokens", _P), ("uniforms", _P), ("selected", _P), ("workspace", _P),
                 ("rows", _U), ("vocab", _U), ("logit_stride", _U), ("temperature", _F),
                 ("min_p", _F), ("top_k", _U), ("top_p", _F), ("cut_out", _P),
-                ("candidate_ids", _P), ("candidate_q", _P), ("draws", _P), ("lanes", _U), ("reserved", _U)]
+                ("candidate_ids", _P), ("candidate_q", _P), ("draws", _P), ("lanes", _U), ("reserved", _U), ("lane_policies", _P)]
+
+
+class SbLanePolicy(ctypes.Structure):
+    _fields_ = [("temperature", _F), ("min_p", _F), ("top_k", _U), ("top_p", _F)]
 
 
 class SbPenaltyArgs(ctypes.Structure):

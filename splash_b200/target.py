@@ -129,6 +129,15 @@ class Target:
         self.l.sb_target_set_policy.argtypes = [_P, _F, _U, _F]
         lib.check(self.l.sb_target_set_policy(self.handle, min_p, top_k, top_p))
 
+    def set_lane_policies(self, policies=None):
+        """policies: a (temperature, min_p, top_k, top_p) per lane, or None to go back to the step's temperature."""
+        self.l.sb_target_set_lane_policies.argtypes = [_P, _P]
+        if policies is None:
+            return lib.check(self.l.sb_target_set_lane_policies(self.handle, None))
+        arr = (lib.SbLanePolicy * len(policies))(*[lib.SbLanePolicy(*p) for p in policies])
+        assert len(policies) == max(1, self.cfg.lanes)
+        lib.check(self.l.sb_target_set_lane_policies(self.handle, ctypes.cast(arr, _P)))
+
     def set_admission(self, constrained=False, excluded=()):
         """The rows' admission: with `constrained` the step reads every row's constraint mask from the `constraint_masks` tensor;
         `excluded` are token ids no row selects."""

@@ -82,7 +82,7 @@ def test_ctypes_mirrors_have_the_headers_structure_sizes():
     l.sb_struct_bytes.argtypes = [ctypes.c_char_p]
     mirrors = dict(SbLinearArgs=lib.SbLinearArgs, SbLinearPlan=lib.SbLinearPlan, SbKvLayer=lib.SbKvLayer, SbAttnStoreArgs=lib.SbAttnStoreArgs,
                    SbAttnArgs=lib.SbAttnArgs, SbGdnTape=lib.SbGdnTape, SbGdnArgs=lib.SbGdnArgs, SbSampleArgs=lib.SbSampleArgs,
-                   SbPenaltyArgs=lib.SbPenaltyArgs, SbAcceptArgs=lib.SbAcceptArgs, SbSelectAcceptArgs=lib.SbSelectAcceptArgs, SbAdmitArgs=lib.SbAdmitArgs, SbMoeRouteArgs=lib.SbMoeRouteArgs,
+                   SbPenaltyArgs=lib.SbPenaltyArgs, SbAcceptArgs=lib.SbAcceptArgs, SbSelectAcceptArgs=lib.SbSelectAcceptArgs, SbAdmitArgs=lib.SbAdmitArgs, SbLanePolicy=lib.SbLanePolicy, SbMoeRouteArgs=lib.SbMoeRouteArgs,
                    SbMoeExpertArgs=lib.SbMoeExpertArgs, SbTargetConfig=target.SbTargetConfig, SbTargetShare=tp.SbTargetShare)
     for name, mirror in mirrors.items():
         assert int(l.sb_struct_bytes(name.encode())) == ctypes.sizeof(mirror), name

@@ -587,3 +587,42 @@ def test_admission_of_lanes_equals_the_oracles():
     assert l.sb_sample_admit(None, ctypes.byref(bad)) == -1               # neither masks nor excluded tokens
     bad = lib.SbAdmitArgs(dl.ptr, dm.ptr, None, rows, V, V, words - 1, 0, L)
     assert l.sb_sample_admit(None, ctypes.byref(bad)) == -1               # mask rows too short for the vocabulary
+
+
+@pytest.mark.parametrize("flags_name", ["eager", "graph"])
+def test_lanes_select_each_by_its_own_policy(flags_name):
+    """A greedy lane beside two sampled ones with different temperatures and ends of the distribution, in one step; then other
+    policies without a new capture (the values are read on the device). Each lane against the oracle's lane with its policy,
+    wherever no test or cut sat within rounding of its threshold."""
+    positions = np.array([900, 40, 1500], np.uint32)
+    lib, target, t, cfg, w, states = build_lanes(3, positions, seed=8)
+    flags = target.GRAPH if flags_name == "graph" else 0
+    rng = np.random.default_rng(77)
+    compared = 0
+    for policies in ([(0.0, 0.0, 0, 1.0), (0.8, 0.0, 10, 1.0), (1.2, 0.05, 0, 1.0)], [(1.0, 0.0, 20, 0.95), (0.0, 0.0, 0, 1.0), (0.6, 0.0, 0, 0.9)]):
+        t.set_lane_policies(policies)
+        for trial in range(3):
+            blocks = np.stack([mo.draft_chain(cfg, w, states[i], 5 + i, rows=16, p_match=0.8, seed=10 * trial + i) for i in range(3)])
+            uniforms = rng.random((3, 80)).astype(np.float32)
+            wants = [mo.verify_step(cfg, w, states[i], blocks[i], temperature=policies[i][0], uniforms=uniforms[i], mutate=False,
+                                    policy=policies[i][1:]) for i in range(3)]
+            got = t.verify_lanes(blocks, uniforms=uniforms, flags=flags)
+            assert lib.device_status() == 0
+            logits = t.download(-1, "logits", np.float32, (48, cfg["vocab"]))
+            for i in range(3):
+                want, (tokens, retained, accepted, mask) = wants[i], got[i]
+                if policies[i][0] == 0.0:
+                    err = np.abs(logits[16 * i:16 * i + 16] - want["logits"]).max(axis=1)
+                    top2 = np.sort(want["logits"], axis=1)[:, -2:]
+                    clear = ((top2[:, 1] - top2[:, 0]) > 2.5 * err)[:want["retained"]].all()
+                else:
+                    clear = (want["margin"][:want["retained"]] > 1e-3).all()
+                if not clear:
+                    continue
+                compared += 1
+                assert (retained, accepted) == (want["retained"], want["accepted"]), (policies[i], trial, i)
+                assert np.array_equal(tokens, want["tokens"]), (policies[i], trial, i)
+    assert compared >= 12, compared
+    t.set_lane_policies(None)
+    with pytest.raises(lib.SbError):
+        t.set_lane_policies([(1.0, 0.0, 0, 1.0), (1.0, 2.0, 0, 1.0), (1.0, 0.0, 0, 1.0)])     # min_p above 1
