@@ -541,6 +541,11 @@ typedef struct SbSelectAcceptArgs {
   uint32_t *pending_rows; /* device u32 [lanes] */
   uint32_t *pending_path; /* device u32 [lanes] */
   uint32_t advance, reserved;
+  /* Optional: the rows each lane's block really holds (device u32 [lanes], each 0..sample.rows; the reference's SplashLaneRows,
+   * runtime/ops/LaneRows.hpp:36-62): lanes step together with blocks of different lengths. A lane selects and accepts among
+   * its own rows only (the slots past them hold whatever the caller left there and are never accepted), a prompt block
+   * commits its own rows, and a lane of no rows keeps its position and gets results {0, 0, 0, 0}. NULL: sample.rows for all. */
+  const uint32_t *lane_rows;
 } SbSelectAcceptArgs;
 SB_API int sb_select_accept(void *stream, const SbSelectAcceptArgs *args);
 
@@ -778,6 +783,12 @@ SB_API int sb_target_verify_lanes(void *target, void *stream, const uint32_t *to
                                   float temperature, uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host);
 /* sb_target_verify for a tree of draft tokens: tree_host holds `rows` SplashTreeRow entries {ancestors u32, parent u16,
  * depth u16}; sets SB_TARGET_TREE. out_tokens_host receives the accepted path's tokens. */
+/* sb_target_verify_lanes for blocks of different lengths: lane_rows_host u32 [lanes], each 0..16, the rows of the lane's block
+ * (the slots past them in tokens_host are ignored; a lane of 0 rows sits the step out: its position, cache and state stay).
+ * The step runs max(lane_rows) row slots for every lane and selects, accepts and commits each lane by its own rows. */
+SB_API int sb_target_verify_lanes_ragged(void *target, void *stream, const uint32_t *tokens_host, const float *uniforms_host,
+                                         const uint32_t *lane_rows_host, float temperature, uint32_t flags, uint32_t *out_tokens_host,
+                                         uint32_t *out_results_host);
 SB_API int sb_target_verify_tree(void *target, void *stream, const uint32_t *tokens_host, const void *tree_host, const float *uniforms_host,
                                  uint32_t rows, float temperature, uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host);
 /* Kernels one step launches, and the bytes its weights, cache and state stream (the roofline's numerator). */

@@ -156,6 +156,8 @@ class QwenTarget {
   uint32_t maskWords() const { return (cfg_.vocab + 31) / 32; }
   Buffer tickets;  // u32 [64]: the selection launch's count of finished rows a lane (zero between launches; zeroed at creation)
   bool promptBlock = false;  // the step being encoded commits every row of its block (a block of prompt tokens)
+  Buffer laneRows;           // u32 [64]: the rows of each lane's block, for steps whose lanes' blocks differ in length
+  bool raggedStep = false;   // the step being encoded reads laneRows
   void buildImages(void *stream) {
     if (wide_)
       for (LayerWeights &w : layers_)
@@ -355,6 +357,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole, const FormatOf &forma
   pageTable_ = Buffer::allocate(size_t(pages) * 4);
   sampleWorkspace_ = Buffer::allocate(ops::Sampling::workspace(uint32_t(R), c.vocab));
   tickets = Buffer::allocate(64 * 4);
+  laneRows = Buffer::allocate(64 * 4);
   penaltyWords = Buffer::allocate(size_t(c.vocab) * 4 * L);
   lanePolicies = Buffer::allocate(sizeof(SbLanePolicy) * 64);
   constraintMasks = Buffer::allocate(size_t(kVerifyRows) * L * ((c.vocab + 31) / 32) * 4), excludedTokens = Buffer::allocate(16 * 4);
@@ -730,6 +733,7 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
   fused.sample = sa;
   fused.accept = SbAcceptArgs{tokens.as<uint32_t>(), tree.as(), selected.as<uint32_t>(), results.as<uint32_t>(), nullptr, rows, kVerifyRows, 0, L};
   fused.tickets = tickets.as<uint32_t>();
+  if (raggedStep) fused.lane_rows = laneRows.as<uint32_t>();
   if (endsHere) {
     fused.committed = committed.as<uint32_t>(), fused.pending_rows = pendingRows.as<uint32_t>(), fused.pending_path = pendingPath.as<uint32_t>();
     fused.advance = stepAdvance;

@@ -750,16 +750,31 @@ __device__ __forceinline__ void commit_lane(const SbSelectAcceptArgs &c, uint32_
 // Selection, acceptance and the lane's commit in one launch: a block per row selects (sample_row), and the block of a
 // lane that finishes last (a ticket per lane, drawn after the block's selection is visible) walks the accepted path
 // and commits the lane. The ticket word returns to zero for the next launch.
-__global__ void __launch_bounds__(kSampleThreads) select_accept_kernel(const SbSelectAcceptArgs c) {
+__global__ void __launch_bounds__(kSampleThreads) select_accept_kernel(const SbSelectAcceptArgs c_in) {
   pdl_launch_dependents();
   pdl_wait();
-  sample_row(c.sample);
-  if (threadIdx.x != 0) return;
   const uint32_t lane = blockIdx.y;
+  // The lane's own rows (blocks of different lengths step together): the blocks of the slots past them select nothing.
+  const uint32_t lane_rows = c_in.lane_rows ? min(c_in.lane_rows[lane], c_in.sample.rows) : c_in.sample.rows;
+  if (blockIdx.x < lane_rows) {
+    SbSampleArgs s = c_in.sample;
+    s.rows = lane_rows;
+    sample_row(s);
+  }
+  if (threadIdx.x != 0) return;
   __threadfence();
-  if (atomicAdd(c.tickets + lane, 1u) != c.sample.rows - 1) return;
+  if (atomicAdd(c_in.tickets + lane, 1u) != c_in.sample.rows - 1) return;
   __threadfence();
-  c.tickets[lane] = 0;
+  c_in.tickets[lane] = 0;
+  SbSelectAcceptArgs c = c_in;
+  c.accept.rows = lane_rows;
+  if ((c.advance & 0xffu) == 3) c.advance = 3u | lane_rows << 8;
+  if (!lane_rows) {  // the lane sits the step out
+    uint32_t *results = c.accept.results + 4 * lane;
+    results[0] = results[1] = results[2] = results[3] = 0;
+    if (c.committed && (c.advance & 0xffu) != 2) c.pending_rows[lane] = 0, c.pending_path[lane] = 0;
+    return;
+  }
   accept_lane(c.accept, lane);
   if (c.committed) commit_lane(c, lane);
 }

@@ -464,14 +464,19 @@ int sb_target_randomize(void *target, uint64_t seed, uint32_t committed) {
   });
 }
 
+constexpr uint32_t kRaggedStep = 1u << 30;  // (internal: the step reads the lanes' own row counts)
+
 static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float temperature, uint32_t flags) {
   QwenTarget &m = *t->model;
   const bool advance = (flags & SB_TARGET_ADVANCE) != 0, tree = (flags & SB_TARGET_TREE) != 0;
   const bool keep = !advance && (flags & SB_TARGET_KEEP_PENDING) != 0, draws = (flags & SB_TARGET_DRAWS) != 0;
   const bool prompt = (flags & SB_TARGET_PROMPT) != 0;
   SB_REQUIRE(!prompt || (advance && !tree), "sb_target_step: SB_TARGET_PROMPT commits a chain: it needs SB_TARGET_ADVANCE and excludes SB_TARGET_TREE");
+  const bool ragged = (flags & kRaggedStep) != 0;
+  SB_REQUIRE(!ragged || (m.manyRowStep() && !tree), "sb_target_verify_lanes_ragged: blocks of different lengths are chains of a target of several lanes");
   const uint32_t parity = m.step & 1;
   m.promptBlock = prompt;
+  m.raggedStep = ragged;
   return guarded([&] {
     if (m.imagesStale) m.buildImages(stream);
     if (flags & SB_TARGET_GRAPH) {
@@ -480,7 +485,7 @@ static int run_step(Target *t, cudaStream_t stream, uint32_t rows, float tempera
       const uint32_t bound = std::min(m.config().max_context, (m.committedHost / 1024 + 2) * 1024);
       uint32_t tbits;
       memcpy(&tbits, &temperature, 4);
-      const auto key = std::make_tuple(rows, tbits, parity, uint32_t(advance) | (uint32_t(tree) << 1) | (uint32_t(keep) << 2) | (uint32_t(draws) << 3) | (uint32_t(prompt) << 4), bound);
+      const auto key = std::make_tuple(rows, tbits, parity, uint32_t(advance) | (uint32_t(tree) << 1) | (uint32_t(keep) << 2) | (uint32_t(draws) << 3) | (uint32_t(prompt) << 4) | (uint32_t(ragged) << 5), bound);
       auto it = t->graphs.find(key);
       if (it == t->graphs.end()) {
         const uint32_t saved = m.committedHost;
@@ -576,6 +581,23 @@ int sb_target_verify_lanes(void *target, void *stream, const uint32_t *tokens_ho
     m.committedHost = std::min(m.config().max_context, before + most);
   }
   return SB_OK;
+}
+
+int sb_target_verify_lanes_ragged(void *target, void *stream, const uint32_t *tokens_host, const float *uniforms_host, const uint32_t *lane_rows_host,
+                                  float temperature, uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target && lane_rows_host, "sb_target_verify_lanes_ragged: null pointer");
+  SB_REQUIRE(!(flags & (SB_TARGET_TREE | kRaggedStep)), "sb_target_verify_lanes_ragged: chains only");
+  Target *t = static_cast<Target *>(target);
+  QwenTarget &m = *t->model;
+  uint32_t most = 0;
+  for (uint32_t l = 0; l < m.lanes(); ++l) {
+    SB_REQUIRE(lane_rows_host[l] <= splash::b200::model::kVerifyRows, "sb_target_verify_lanes_ragged: lane %u has %u rows (up to 16)", l, lane_rows_host[l]);
+    most = std::max(most, lane_rows_host[l]);
+  }
+  SB_REQUIRE(most >= 1, "sb_target_verify_lanes_ragged: no lane has a row");
+  SB_CUDA(cudaMemcpyAsync(m.laneRows.as(), lane_rows_host, size_t(4) * m.lanes(), cudaMemcpyHostToDevice, t->pick(stream)));
+  return sb_target_verify_lanes(target, stream, tokens_host, uniforms_host, most, temperature, flags | kRaggedStep, out_tokens_host, out_results_host);
 }
 
 int sb_target_verify_tree(void *target, void *stream, const uint32_t *tokens_host, const void *tree_host, const float *uniforms_host, uint32_t rows,

@@ -185,6 +185,22 @@ class Target:
                                                 rows, temperature, flags, out_t.ctypes.data_as(_P), out_r.ctypes.data_as(_P)))
         return [(out_t[l, :out_r[l, 0]].copy(), int(out_r[l, 0]), int(out_r[l, 1]), int(out_r[l, 2])) for l in range(lanes)]
 
+    def verify_lanes_ragged(self, blocks, uniforms=None, temperature=0.0, flags=0, stream=None):
+        """One step of lanes whose blocks differ in length: blocks is a list of token arrays (0..16 tokens each, an empty one
+        for a lane that sits the step out). Returns per lane (retained tokens, retained, accepted, retained_rows mask)."""
+        lanes = max(1, self.cfg.lanes)
+        assert len(blocks) == lanes
+        slots, rows = np.zeros((lanes, 16), np.uint32), np.zeros(lanes, np.uint32)
+        for i, b in enumerate(blocks):
+            b = np.asarray(b, np.uint32)
+            slots[i, :len(b)], rows[i] = b, len(b)
+        u = None if uniforms is None else np.ascontiguousarray(uniforms, np.float32)
+        out_t, out_r = np.zeros((lanes, 16), np.uint32), np.zeros((lanes, 4), np.uint32)
+        self.l.sb_target_verify_lanes_ragged.argtypes = [_P, _P, _P, _P, _P, _F, _U, _P, _P]
+        lib.check(self.l.sb_target_verify_lanes_ragged(self.handle, stream, slots.ctypes.data_as(_P), None if u is None else u.ctypes.data_as(_P),
+                                                       rows.ctypes.data_as(_P), temperature, flags, out_t.ctypes.data_as(_P), out_r.ctypes.data_as(_P)))
+        return [(out_t[l, :out_r[l, 0]].copy(), int(out_r[l, 0]), int(out_r[l, 1]), int(out_r[l, 2])) for l in range(lanes)]
+
     def step(self, rows=16, temperature=0.0, flags=GRAPH, stream=None):
         lib.check(self.l.sb_target_step(self.handle, stream, rows, temperature, flags))
 

@@ -626,3 +626,60 @@ def test_lanes_select_each_by_its_own_policy(flags_name):
     t.set_lane_policies(None)
     with pytest.raises(lib.SbError):
         t.set_lane_policies([(1.0, 0.0, 0, 1.0), (1.0, 2.0, 0, 1.0), (1.0, 0.0, 0, 1.0)])     # min_p above 1
+
+
+@pytest.mark.parametrize("flags_name", ["eager", "graph"])
+def test_lanes_step_together_with_blocks_of_different_lengths(flags_name):
+    """Blocks of 16, 5 and 0 rows in one step, then of 3, 16 and 9: every lane selects, accepts and commits among its own rows
+    (the slots past them hold tokens that would have been accepted had they counted), a lane without rows sits the step out
+    with its position and state intact. Each lane against the oracle's lane stepped with its own block."""
+    positions = np.array([1200, 64, 500], np.uint32)
+    lib, target, t, cfg, w, states = build_lanes(3, positions, seed=10)
+    flags = target.ADVANCE | (target.GRAPH if flags_name == "graph" else 0)
+    first = [17, 400, 9000]
+    compared = 0
+    for step, lengths in enumerate(([16, 5, 0], [3, 16, 9], [16, 16, 16])):
+        full = [mo.draft_chain(cfg, w, states[i], first[i], rows=16, p_match=1.0, seed=7 * step + i) for i in range(3)]   # all would be accepted
+        blocks = [full[i][:lengths[i]] for i in range(3)]
+        wants = []
+        for i in range(3):
+            if lengths[i]:
+                wants.append(mo.verify_step(cfg, w, states[i], blocks[i], advance=True))
+            else:   # a lane that sits out: its pending rows are folded, nothing is committed (a held step in the oracle)
+                wants.append(mo.verify_step(cfg, w, states[i], full[i], advance=False))
+        # the device's slots past a lane's rows hold the rest of the chain: tokens that match the target's own selections
+        slots = np.stack(full)
+        got = t.verify_lanes_ragged([slots[i][:lengths[i]] for i in range(3)], flags=flags) if step != 1 else None
+        if got is None:   # (the same through explicit slots: the tokens past the lanes' rows are there, and ignored)
+            out_t, out_r = np.zeros((3, 16), np.uint32), np.zeros((3, 4), np.uint32)
+            rows = np.array(lengths, np.uint32)
+            P_ = ctypes.c_void_p
+            t.l.sb_target_verify_lanes_ragged.argtypes = [P_, P_, P_, P_, P_, ctypes.c_float, ctypes.c_uint32, P_, P_]
+            lib.check(t.l.sb_target_verify_lanes_ragged(t.handle, None, slots.ctypes.data_as(P_), None, rows.ctypes.data_as(P_), 0.0, flags,
+                                                        out_t.ctypes.data_as(P_), out_r.ctypes.data_as(P_)))
+            got = [(out_t[l, :out_r[l, 0]].copy(), int(out_r[l, 0]), int(out_r[l, 1]), int(out_r[l, 2])) for l in range(3)]
+        assert lib.device_status() == 0
+        logits = t.download(-1, "logits", np.float32, (48, cfg["vocab"]))
+        for i in range(3):
+            tokens, retained, accepted, mask = got[i]
+            if not lengths[i]:
+                assert (retained, accepted, mask) == (0, 0, 0) and len(tokens) == 0
+                continue
+            want = wants[i]
+            assert retained <= lengths[i]
+            mine = logits[16 * i:16 * i + lengths[i]]
+            scale = np.abs(want["logits"]).max()
+            err = np.abs(mine - want["logits"])
+            assert err.max() <= 2e-2 * scale and np.median(err) <= 2e-3 * scale, (step, i)
+            top2 = np.sort(want["logits"], axis=1)[:, -2:]
+            if ((top2[:, 1] - top2[:, 0]) > 2.5 * err.max(axis=1))[:want["retained"]].all():
+                assert (retained, accepted, mask) == (want["retained"], want["accepted"], want["mask"]), (step, i)
+                assert np.array_equal(tokens, want["tokens"]), (step, i)
+                compared += 1
+            else:
+                states[i]["committed"] += retained - want["retained"]
+                states[i]["pending_rows"] = retained
+            first[i] = int(tokens[-1])
+        committed = t.download(-1, "committed", np.uint32, (3,))
+        assert [int(c) for c in committed] == [states[i]["committed"] for i in range(3)], step
+    assert compared >= 6, compared
