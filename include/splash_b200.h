@@ -752,6 +752,9 @@ SB_API int sb_target_set_policy(void *target, float min_p, uint32_t top_k, float
  * sampled lanes side by side. The values live on the device and are read by the selection when it runs, so they can change
  * between steps without a new capture. Steps need uniforms while policies are set. */
 SB_API int sb_target_set_lane_policies(void *target, const SbLanePolicy *policies_host);
+/* The tokens that end a request (up to 16; NULL, 0: none): a retained stop token is the last token the step retains
+ * (sb_accept's stop_tokens; the reference's StopTokens of Sampling::addAcceptance, runtime/ops/Sampling.hpp). */
+SB_API int sb_target_set_stop_tokens(void *target, const uint32_t *stop_tokens_host, uint32_t n_stop);
 /* The lane's admission (every lane's, with several): with `constrained` the step reads a constraint mask for every row from
  * the target's `constraint_masks` tensor (u32 [16 x lanes][ceil(vocab / 32)], sb_target_tensor), which the host (its grammar
  * or schema engine) fills before the step; excluded_host: up to 16 token ids no row selects (NULL, 0: none). The step then

@@ -156,6 +156,8 @@ class QwenTarget {
   uint32_t maskWords() const { return (cfg_.vocab + 31) / 32; }
   Buffer tickets;  // u32 [64]: the selection launch's count of finished rows a lane (zero between launches; zeroed at creation)
   bool promptBlock = false;  // the step being encoded commits every row of its block (a block of prompt tokens)
+  Buffer stopTokens;         // u32 [16]: tokens that end a lane's retained path (sb_target_set_stop_tokens)
+  uint32_t stopCount = 0;
   Buffer laneRows;           // u32 [64]: the rows of each lane's block, for steps whose lanes' blocks differ in length
   bool raggedStep = false;   // the step being encoded reads laneRows
   void buildImages(void *stream) {
@@ -358,6 +360,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole, const FormatOf &forma
   sampleWorkspace_ = Buffer::allocate(ops::Sampling::workspace(uint32_t(R), c.vocab));
   tickets = Buffer::allocate(64 * 4);
   laneRows = Buffer::allocate(64 * 4);
+  stopTokens = Buffer::allocate(16 * 4);
   penaltyWords = Buffer::allocate(size_t(c.vocab) * 4 * L);
   lanePolicies = Buffer::allocate(sizeof(SbLanePolicy) * 64);
   constraintMasks = Buffer::allocate(size_t(kVerifyRows) * L * ((c.vocab + 31) / 32) * 4), excludedTokens = Buffer::allocate(16 * 4);
@@ -611,6 +614,7 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   Sampling::addPenalties(graph, penalties, sb, penaltyWords, tree, rows, c.vocab);  // (nothing when the penalties are off)
   AcceptanceBuffers ab;
   ab.inputTokens = tokens, ab.treeRows = tree, ab.outputTokens = selected, ab.results = results;
+  ab.stopTokens = stopTokens, ab.stopTokenCount = stopCount;  // (a retained stop token ends the retained path)
   // One launch selects, accepts and, where nothing has to come between (a tree's path commit reads the lane's position
   // before it moves; a tensor-parallel step's end also numbers the next step's exchanges), ends the step.
   const uint32_t stepAdvance = promptBlock ? 3u | rows << 8 : advance ? 1u : keepPending ? 2u : 0u;
@@ -731,7 +735,8 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
   const bool endsHere = !(treeGiven && advance);  // (a tree's path commit reads the lanes' positions before they move)
   SbSelectAcceptArgs fused{};
   fused.sample = sa;
-  fused.accept = SbAcceptArgs{tokens.as<uint32_t>(), tree.as(), selected.as<uint32_t>(), results.as<uint32_t>(), nullptr, rows, kVerifyRows, 0, L};
+  fused.accept = SbAcceptArgs{tokens.as<uint32_t>(), tree.as(), selected.as<uint32_t>(), results.as<uint32_t>(), stopCount ? stopTokens.as<uint32_t>() : nullptr, rows,
+                              kVerifyRows, stopCount, L};
   fused.tickets = tickets.as<uint32_t>();
   if (raggedStep) fused.lane_rows = laneRows.as<uint32_t>();
   if (endsHere) {

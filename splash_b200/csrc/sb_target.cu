@@ -298,6 +298,19 @@ int sb_target_set_lane_policies(void *target, const SbLanePolicy *policies_host)
   return SB_OK;
 }
 
+int sb_target_set_stop_tokens(void *target, const uint32_t *stop_tokens_host, uint32_t n_stop) {
+  SB_NEED_DEVICE();
+  SB_REQUIRE(target, "sb_target_set_stop_tokens: null target");
+  SB_REQUIRE(n_stop <= 16 && (!n_stop || stop_tokens_host), "sb_target_set_stop_tokens: up to 16 stop tokens, with their ids");
+  Target *t = static_cast<Target *>(target);
+  SB_CUDA(cudaDeviceSynchronize());
+  for (auto &g : t->graphs) cudaGraphExecDestroy(g.second);  // captured steps carry the old count
+  t->graphs.clear();
+  if (n_stop) SB_CUDA(cudaMemcpy(t->model->stopTokens.as(), stop_tokens_host, n_stop * 4, cudaMemcpyHostToDevice));
+  t->model->stopCount = n_stop;
+  return SB_OK;
+}
+
 int sb_target_set_admission(void *target, int constrained, const uint32_t *excluded_host, uint32_t n_excluded) {
   SB_NEED_DEVICE();
   SB_REQUIRE(target, "sb_target_set_admission: null target");

@@ -138,6 +138,11 @@ class Target:
         assert len(policies) == max(1, self.cfg.lanes)
         lib.check(self.l.sb_target_set_lane_policies(self.handle, ctypes.cast(arr, _P)))
 
+    def set_stop_tokens(self, tokens=()):
+        e = np.ascontiguousarray(tokens, np.uint32)
+        self.l.sb_target_set_stop_tokens.argtypes = [_P, _P, _U]
+        lib.check(self.l.sb_target_set_stop_tokens(self.handle, e.ctypes.data_as(_P) if e.size else None, e.size))
+
     def set_admission(self, constrained=False, excluded=()):
         """The rows' admission: with `constrained` the step reads every row's constraint mask from the `constraint_masks` tensor;
         `excluded` are token ids no row selects."""

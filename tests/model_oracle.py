@@ -122,7 +122,7 @@ def linear(o, fmt, W, n, k, X, rows, epilogue=0, aux=None, out_f32=False, W2=Non
 
 
 def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True, mutate=True, tree=None, penalties=None, penalty_words=None,
-                draws=None, prompt=False, admission=None, policy=(0.0, 0, 1.0)):
+                draws=None, prompt=False, admission=None, policy=(0.0, 0, 1.0), stop_tokens=()):
     """One verify step of a chain, or of the tree whose rows `tree` holds (uint32 [rows, 2]: ancestors, parent | depth << 16).
     draws = (candidate ids u32 [rows, 16], draft probabilities f32 [rows, 16], drawn children u8 [rows, 4]): sampled rows
     select by recursive rejection sampling over these children. prompt: the rows are prompt tokens, all committed whatever
@@ -228,7 +228,8 @@ def verify_step(cfg, w, s, tokens, temperature=0.0, uniforms=None, advance=True,
                                     P(uniforms) if uniforms is not None else None, P(selected), P(margin), None)
     out_tokens = selected.copy()
     res = np.zeros(3, np.uint32)
-    o.so_accept(P(tokens), P(rows_tree), P(out_tokens), rows, 16, None, 0, P(res[0:1]), P(res[1:2]), P(res[2:3]))
+    stops = np.ascontiguousarray(stop_tokens, np.uint32)
+    o.so_accept(P(tokens), P(rows_tree), P(out_tokens), rows, 16, P(stops) if len(stops) else None, len(stops), P(res[0:1]), P(res[1:2]), P(res[2:3]))
     if prompt:
         assert advance and tree is None
         res[:] = (rows, rows - 1, (2 << (rows - 1)) - 1)

@@ -365,3 +365,25 @@ def test_tiny_model_sampled_steps_under_a_policy_match_oracle():
     assert differs >= 3, differs              # the policies did change what the rows select
     with pytest.raises(lib.SbError):
         t.set_policy(min_p=1.5)
+
+
+def test_tiny_model_stop_token_ends_the_retained_path():
+    """With the token the target selects at the third accepted row set as a stop token, the step retains three tokens where it
+    retained more; the oracle's acceptance with the same stop tokens agrees. One lane, then the same in a lane of several."""
+    lib, target, t, cfg, w, s = build(seed=16)
+    tokens = mo.draft_chain(cfg, w, s, 5, rows=16, p_match=1.0, seed=3)
+    plain = mo.verify_step(cfg, w, s, tokens, mutate=False)
+    assert plain["retained"] >= 6
+    stop = [int(plain["tokens"][2]), 31999]
+    want = mo.verify_step(cfg, w, s, tokens, mutate=False, stop_tokens=stop)
+    assert want["retained"] == 3 and want["tokens"][-1] == stop[0]
+    t.set_stop_tokens(stop)
+    got_tokens, retained, accepted, mask = t.verify(tokens, flags=target.GRAPH)
+    top2 = np.sort(plain["logits"], axis=1)[:, -2:]
+    if ((top2[:, 1] - top2[:, 0]) > 1e-2)[:plain["retained"]].all():
+        assert (retained, accepted, mask) == (want["retained"], want["accepted"], want["mask"])
+        assert np.array_equal(got_tokens, want["tokens"])
+    t.set_stop_tokens(())
+    got_tokens, retained, _, _ = t.verify(tokens, flags=target.GRAPH)
+    if ((top2[:, 1] - top2[:, 0]) > 1e-2)[:plain["retained"]].all():
+        assert retained == plain["retained"]
