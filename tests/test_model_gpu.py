@@ -368,22 +368,33 @@ def test_tiny_model_sampled_steps_under_a_policy_match_oracle():
 
 
 def test_tiny_model_stop_token_ends_the_retained_path():
-    """With the token the target selects at the third accepted row set as a stop token, the step retains three tokens where it
-    retained more; the oracle's acceptance with the same stop tokens agrees. One lane, then the same in a lane of several."""
+    """With the token the target selects at the third row set as a stop token, the step retains three tokens where it retained
+    six; the oracle's acceptance with the same stop tokens agrees. (Penalties over the rows' paths keep the tiny model's
+    selections from collapsing onto one token, so that the stop token is not also the first.)"""
     lib, target, t, cfg, w, s = build(seed=16)
-    tokens = mo.draft_chain(cfg, w, s, 5, rows=16, p_match=1.0, seed=3)
-    plain = mo.verify_step(cfg, w, s, tokens, mutate=False)
-    assert plain["retained"] >= 6
+    policy, words = (1.4, 0.5, 0.7), np.zeros(cfg["vocab"], np.uint32)
+    chain = [5]
+    for _ in range(5):    # a chain of the target's own selections under the penalties: every draft token is right
+        step = mo.verify_step(cfg, w, s, np.array(chain, np.uint32), mutate=False, penalties=policy, penalty_words=words)
+        chain.append(int(step["selected"][-1]))
+    tokens = np.array(chain, np.uint32)
+    plain = mo.verify_step(cfg, w, s, tokens, mutate=False, penalties=policy, penalty_words=words)
+    assert plain["retained"] == 6 and len(set(plain["tokens"].tolist())) >= 4
     stop = [int(plain["tokens"][2]), 31999]
-    want = mo.verify_step(cfg, w, s, tokens, mutate=False, stop_tokens=stop)
+    assert stop[0] not in plain["tokens"][:2]
+    want = mo.verify_step(cfg, w, s, tokens, mutate=False, penalties=policy, penalty_words=words, stop_tokens=stop)
     assert want["retained"] == 3 and want["tokens"][-1] == stop[0]
+    t.set_penalties(*policy)
+    t.upload(-1, "penalty_words", words)
     t.set_stop_tokens(stop)
     got_tokens, retained, accepted, mask = t.verify(tokens, flags=target.GRAPH)
     top2 = np.sort(plain["logits"], axis=1)[:, -2:]
-    if ((top2[:, 1] - top2[:, 0]) > 1e-2)[:plain["retained"]].all():
+    clear = ((top2[:, 1] - top2[:, 0]) > 1e-2)[:plain["retained"]].all()
+    if clear:
         assert (retained, accepted, mask) == (want["retained"], want["accepted"], want["mask"])
         assert np.array_equal(got_tokens, want["tokens"])
     t.set_stop_tokens(())
     got_tokens, retained, _, _ = t.verify(tokens, flags=target.GRAPH)
-    if ((top2[:, 1] - top2[:, 0]) > 1e-2)[:plain["retained"]].all():
+    if clear:
         assert retained == plain["retained"]
+    t.set_penalties()
