@@ -546,6 +546,10 @@ typedef struct SbSelectAcceptArgs {
    * its own rows only (the slots past them hold whatever the caller left there and are never accepted), a prompt block
    * commits its own rows, and a lane of no rows keeps its position and gets results {0, 0, 0, 0}. NULL: sample.rows for all. */
   const uint32_t *lane_rows;
+  /* Optional: how many more tokens each lane's request may take (device u32 [lanes], each at least 1; the `remaining` of the
+   * reference's acceptance a lane, AcceptBatchParams, runtime/metal/abi/Sampling.h:314-317): a lane retains at most that
+   * many tokens. NULL: accept.remaining for all. */
+  const uint32_t *lane_remaining;
 } SbSelectAcceptArgs;
 SB_API int sb_select_accept(void *stream, const SbSelectAcceptArgs *args);
 
@@ -735,7 +739,8 @@ SB_API int sb_target_destroy(void *target);
  * in_proj, out_proj, ffn_gate, ffn_up, ffn_down, and for GDN layers ssm_ab, ssm_conv, ssm_a, ssm_dt_bias, ssm_norm,
  * state0/1, conv0/1, for attention layers q_norm, k_norm, kv_k, kv_v, kv_ks, kv_vs. Global (layer = -1):
  * token_embd, output_norm, output, logits, selected, results, hidden, tokens, uniforms, committed, penalty_words,
- * candidates, candidate_q, draws. The tensors a checkpoint fuses into in_proj are also reached one by one under their
+ * candidates, candidate_q, draws, constraint_masks, remaining (u32 [lanes]: the tokens each lane's request may still take,
+ * 0xFFFFFFFF at creation; the step retains no more). The tensors a checkpoint fuses into in_proj are also reached one by one under their
  * GGUF stems, in the order of in_proj's rows: attn_q, attn_k, attn_v (attention layers), attn_qkv, attn_gate (GDN layers);
  * a target whose parts differ in format (sb_target_create_from_gguf) has only those, no in_proj. */
 SB_API int sb_target_tensor(void *target, int layer, const char *name, void **out_dev, uint64_t *out_bytes);

@@ -158,6 +158,7 @@ class QwenTarget {
   bool promptBlock = false;  // the step being encoded commits every row of its block (a block of prompt tokens)
   Buffer stopTokens;         // u32 [16]: tokens that end a lane's retained path (sb_target_set_stop_tokens)
   uint32_t stopCount = 0;
+  Buffer remaining;          // u32 [64]: the tokens each lane's request may still take (0xFFFFFFFF: no bound)
   Buffer laneRows;           // u32 [64]: the rows of each lane's block, for steps whose lanes' blocks differ in length
   bool raggedStep = false;   // the step being encoded reads laneRows
   void buildImages(void *stream) {
@@ -360,6 +361,7 @@ inline QwenTarget::QwenTarget(const SbTargetConfig &whole, const FormatOf &forma
   sampleWorkspace_ = Buffer::allocate(ops::Sampling::workspace(uint32_t(R), c.vocab));
   tickets = Buffer::allocate(64 * 4);
   laneRows = Buffer::allocate(64 * 4);
+  remaining = Buffer::allocate(64 * 4);
   stopTokens = Buffer::allocate(16 * 4);
   penaltyWords = Buffer::allocate(size_t(c.vocab) * 4 * L);
   lanePolicies = Buffer::allocate(sizeof(SbLanePolicy) * 64);
@@ -436,7 +438,7 @@ inline bool QwenTarget::find(int layer, const std::string &name, Buffer &out) co
                                              {"logits", logits}, {"selected", selected}, {"results", results}, {"hidden", hidden[0]},
                                              {"hidden1", hidden[1]}, {"tokens", tokens}, {"uniforms", uniforms}, {"committed", committed},
                                              {"pending_rows", pendingRows}, {"tree", tree}, {"page_table", pageTable_}, {"inv_freq", invFreq},
-                                             {"positions", positions}, {"packed", packed_}, {"mixed", mixed_}, {"act", act_}, {"penalty_words", penaltyWords}, {"constraint_masks", constraintMasks},
+                                             {"positions", positions}, {"packed", packed_}, {"mixed", mixed_}, {"act", act_}, {"penalty_words", penaltyWords}, {"constraint_masks", constraintMasks}, {"remaining", remaining},
                                              {"candidates", candidates}, {"candidate_q", candidateQ}, {"draws", draws}, {"pending_path", pendingPath},
                                              {"moe_scores", moeScoresGiven_}};
     auto it = g.find(name);
@@ -620,7 +622,7 @@ inline void QwenTarget::encodeVerify(CommandGraph &graph, uint32_t rows, float t
   const uint32_t stepAdvance = promptBlock ? 3u | rows << 8 : advance ? 1u : keepPending ? 2u : 0u;
   const bool endsHere = !tp_ && !(treeGiven && advance);
   const Sampling::LaneCommit lc{committed, pendingRows, pendingPath, stepAdvance};
-  Sampling::addVerifyAndAcceptance(graph, SamplingPolicy{temperature, minP, topK, topP}, sb, ab, rows, c.vocab, kVerifyRows, 1, tickets, endsHere ? &lc : nullptr);
+  Sampling::addVerifyAndAcceptance(graph, SamplingPolicy{temperature, minP, topK, topP}, sb, ab, rows, c.vocab, kVerifyRows, 1, tickets, endsHere ? &lc : nullptr, &remaining);
   if (tp_ && exchange != exchangesPerStep()) throw std::logic_error("QwenTarget::encodeVerify: exchange count");
   // The accepted path's KV rows move from their rows' slots to their depths' (a chain's are there already).
   if (treeGiven && advance) {
@@ -739,6 +741,7 @@ inline void QwenTarget::encodeVerifyLanes(CommandGraph &graph, uint32_t rows, fl
                               kVerifyRows, stopCount, L};
   fused.tickets = tickets.as<uint32_t>();
   if (raggedStep) fused.lane_rows = laneRows.as<uint32_t>();
+  fused.lane_remaining = remaining.as<uint32_t>();
   if (endsHere) {
     fused.committed = committed.as<uint32_t>(), fused.pending_rows = pendingRows.as<uint32_t>(), fused.pending_path = pendingPath.as<uint32_t>();
     fused.advance = stepAdvance;

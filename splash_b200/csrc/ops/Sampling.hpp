@@ -87,7 +87,7 @@ class Sampling {
   };
   static void addVerifyAndAcceptance(CommandGraph &graph, const SamplingPolicy &policy, const SamplingBuffers &b, const AcceptanceBuffers &ab,
                                      uint32_t rows, uint32_t vocabulary, uint32_t maximumRetained, uint32_t lanes, const Buffer &tickets,
-                                     const LaneCommit *commit) {
+                                     const LaneCommit *commit, const Buffer *remaining = nullptr) {
     const size_t slots = lanes > 1 ? size_t(lanes) * 16 : rows;  // (a lane's block lies in its 16 row slots)
     requireBytes(b.logits, ((slots - 1) * b.logitStride + vocabulary) * 4, "Sampling::addVerifyAndAcceptance logits");
     requireBytes(b.inputTokens, slots * 4, "Sampling::addVerifyAndAcceptance input tokens");
@@ -113,6 +113,10 @@ class Sampling {
     c.accept = SbAcceptArgs{b.inputTokens.as<uint32_t>(), ab.treeRows.as(), b.selected.as<uint32_t>(), ab.results.as<uint32_t>(),
                             ab.stopTokenCount ? ab.stopTokens.as<uint32_t>() : nullptr, rows, maximumRetained, ab.stopTokenCount, lanes};
     c.tickets = tickets.as<uint32_t>();
+    if (remaining) {
+      requireBytes(*remaining, size_t(4) * std::max(1u, lanes), "Sampling::addVerifyAndAcceptance remaining");
+      c.lane_remaining = remaining->as<uint32_t>();
+    }
     if (commit) {
       requireBytes(commit->committed, size_t(4) * std::max(1u, lanes), "Sampling::addVerifyAndAcceptance committed");
       requireBytes(commit->pendingRows, size_t(4) * std::max(1u, lanes), "Sampling::addVerifyAndAcceptance pending rows");

@@ -768,6 +768,7 @@ __global__ void __launch_bounds__(kSampleThreads) select_accept_kernel(const SbS
   c_in.tickets[lane] = 0;
   SbSelectAcceptArgs c = c_in;
   c.accept.rows = lane_rows;
+  if (c.lane_remaining) c.accept.remaining = min(c.accept.remaining, max(c.lane_remaining[lane], 1u));
   if ((c.advance & 0xffu) == 3) c.advance = 3u | lane_rows << 8;
   if (!lane_rows) {  // the lane sits the step out
     uint32_t *results = c.accept.results + 4 * lane;

@@ -215,6 +215,7 @@ int sb_target_create_with_formats(const SbTargetConfig *config, TensorFormat for
     if (config->rotary_pairs) inv_freq_kernel<<<1, 256>>>(m.invFreq.as<float>(), config->rotary_pairs, config->rope_theta);
     SB_CUDA(cudaMemset(m.committed.as(), 0, 4 * L));
     SB_CUDA(cudaMemset(m.tickets.as(), 0, m.tickets.bytes()));
+    SB_CUDA(cudaMemset(m.remaining.as(), 0xff, m.remaining.bytes()));  // no bound on what a request may still take
     SB_CUDA(cudaMemset(m.pendingRows.as(), 0, 4 * L));
     SB_CUDA(cudaMemset(m.pendingPath.as(), 0, 4 * L));
     SB_CUDA(cudaMemset(m.penaltyWords.as(), 0, m.penaltyWords.bytes()));

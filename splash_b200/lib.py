@@ -264,7 +264,7 @@ class SbAdmitArgs(ctypes.Structure):
 
 class SbSelectAcceptArgs(ctypes.Structure):
     _fields_ = [("sample", SbSampleArgs), ("accept", SbAcceptArgs), ("tickets", _P), ("committed", _P), ("pending_rows", _P),
-                ("pending_path", _P), ("advance", _U), ("reserved", _U)]
+                ("pending_path", _P), ("advance", _U), ("reserved", _U), ("lane_rows", _P), ("lane_remaining", _P)]
 
 
 def _bind_ops():

@@ -683,3 +683,9 @@ def test_lanes_step_together_with_blocks_of_different_lengths(flags_name):
         committed = t.download(-1, "committed", np.uint32, (3,))
         assert [int(c) for c in committed] == [states[i]["committed"] for i in range(3)], step
     assert compared >= 6, compared
+    # a request that may take two more tokens retains two, however many its block would give
+    t.upload(-1, "remaining", np.array([2, 0xffffffff, 1], np.uint32))
+    full = [mo.draft_chain(cfg, w, states[i], first[i], rows=16, p_match=1.0, seed=90 + i) for i in range(3)]
+    got = t.verify_lanes(np.stack(full), flags=flags)
+    assert got[0][1] <= 2 and got[2][1] == 1 and got[1][1] >= got[0][1]
+    t.upload(-1, "remaining", np.full(3, 0xffffffff, np.uint32))
