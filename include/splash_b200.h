@@ -835,6 +835,10 @@ typedef struct SbGgufTensor {
   uint64_t bytes;
 } SbGgufTensor;
 SB_API int sb_gguf_open(const char *path, void **out_file);
+/* The parts of a split GGUF in split order (gguf-split's parts: the keys split.no, split.count, split.tensors.count; the
+ * first part holds the model's metadata) as one file: every part's tensors, the first part's metadata. A part given
+ * alone, out of order or with parts missing is refused. */
+SB_API int sb_gguf_open_parts(const char *const *paths, uint32_t count, void **out_file);
 SB_API int sb_gguf_close(void *file);
 SB_API int sb_gguf_tensor_count(void *file, uint64_t *out_count);
 SB_API int sb_gguf_tensor(void *file, uint64_t index, SbGgufTensor *out);
@@ -844,6 +848,8 @@ SB_API int sb_gguf_find(void *file, const char *name, SbGgufTensor *out); /* SB_
 SB_API int sb_gguf_meta_u64(void *file, const char *key, uint64_t *out);
 SB_API int sb_gguf_meta_f64(void *file, const char *key, double *out);
 SB_API int sb_gguf_meta_str(void *file, const char *key, const char **out);
+/* A numeric array's values as doubles (arrays of up to 65536 numbers are kept; string arrays, e.g. the tokenizer's, are not). */
+SB_API int sb_gguf_meta_array(void *file, const char *key, const double **out_values, uint64_t *out_count);
 /* Fills the model's fields of *config from the file's metadata and tensors (the keys runtime/model/GgufImage.cpp:902-933
  * checks: block_count, embedding_length, attention.*, rope.*, full_attention_interval, ssm.*, expert_*,
  * feed_forward_length; the vocabulary from token_embd; fmt_* from the tensors' types; gated_attention from attn_q's rows;

@@ -3,7 +3,7 @@
 // but the header's own strings.
 //
 // Stands where the reference has its header parser (runtime/model/GgufFile.hpp:23-141: tensors, metadata by key, find /
-// require, numeric arrays; ggml's type table :38-57) for one file; split files and the rotation keys are not read.
+// require, numeric arrays; ggml's type table :38-57) for one file or the parts of a split one; the rotation keys are not read.
 // File layout as llama.cpp's gguf.h documents it: magic "GGUF", u32 version, u64 tensor count, u64 key count; per key a
 // string, a u32 value type and the value; per tensor a string, u32 dimensions, u64 extents (fastest first), u32 ggml
 // type, u64 offset into the data section, which starts at the next multiple of general.alignment (32 by default).
@@ -88,7 +88,8 @@ struct GgufTensor {
   std::string name;
   uint32_t type = 0;
   std::vector<uint64_t> dims;  // dims[0] is the fastest (a row's length)
-  uint64_t offset = 0;         // in the file's data section
+  uint64_t offset = 0;         // in its part's data section
+  uint32_t part = 0;           // which file of a split GGUF holds it
   uint64_t bytes = 0;
   const uint8_t *data = nullptr;  // in the mapping
   uint64_t columns() const { return dims.empty() ? 0 : dims[0]; }
@@ -124,29 +125,32 @@ struct GgufMetadata {
 
 class GgufReader {
  public:
-  explicit GgufReader(const std::string &path) : path_(path) {
-    const int fd = ::open(path.c_str(), O_RDONLY);
-    if (fd < 0) throw GgufError("cannot open " + path);
-    struct stat st {};
-    if (::fstat(fd, &st) != 0 || st.st_size < 24) {
-      ::close(fd);
-      throw GgufError(path + " is not a GGUF file (too short)");
-    }
-    size_ = uint64_t(st.st_size);
-    void *m = ::mmap(nullptr, size_, PROT_READ, MAP_PRIVATE, fd, 0);
-    ::close(fd);
-    if (m == MAP_FAILED) throw GgufError("cannot map " + path);
-    base_ = static_cast<const uint8_t *>(m);
+  explicit GgufReader(const std::string &path) : GgufReader(std::vector<std::string>{path}) {}
+  // The parts of a split GGUF in split order (llama.cpp's gguf-split: every part a GGUF of its own with the keys split.no,
+  // split.count and split.tensors.count; the first holds the model's metadata), or one whole file. A part read alone, parts
+  // out of order or of another split are refused (the reference's GgufFile over several sources,
+  // runtime/model/GgufFile.hpp:104-111).
+  explicit GgufReader(const std::vector<std::string> &paths) {
+    if (paths.empty()) throw GgufError("no GGUF file given");
     try {
-      parse();
+      for (const std::string &path : paths) {
+        open(path);
+        GgufMetadata own;
+        parse(parts_.size() - 1, parts_.size() == 1 ? metadata_ : own);
+        const GgufMetadata &meta = parts_.size() == 1 ? metadata_ : own;
+        const uint64_t count = meta.integer("split.count").value_or(1), number = meta.integer("split.no").value_or(0);
+        if (count != paths.size() || number != parts_.size() - 1)
+          throw GgufError(path + " is part " + std::to_string(number + 1) + " of " + std::to_string(count) + " of a split GGUF, given as part " +
+                          std::to_string(parts_.size()) + " of " + std::to_string(paths.size()));
+      }
+      if (const auto total = metadata_.integer("split.tensors.count"); total && *total != tensors_.size())
+        throw GgufError(paths.front() + ": the parts hold " + std::to_string(tensors_.size()) + " tensors, the split " + std::to_string(*total));
     } catch (...) {
-      ::munmap(const_cast<uint8_t *>(base_), size_);
+      close();
       throw;
     }
   }
-  ~GgufReader() {
-    if (base_) ::munmap(const_cast<uint8_t *>(base_), size_);
-  }
+  ~GgufReader() { close(); }
   GgufReader(const GgufReader &) = delete;
   GgufReader &operator=(const GgufReader &) = delete;
 
@@ -161,123 +165,153 @@ class GgufReader {
     if (!t) throw GgufError("the GGUF has no tensor " + std::string(name));
     return *t;
   }
-  // A numeric array's values, nullptr for a key that holds none (arrays of up to 65536 numbers are kept).
+  // A numeric array's values (of the first part's metadata), nullptr for a key that holds none (arrays of up to 65536
+  // numbers are kept).
   const std::vector<double> *numericArray(std::string_view key) const {
     auto it = arrays_.find(key);
     return it == arrays_.end() ? nullptr : &it->second;
   }
-  uint64_t dataStart() const { return dataStart_; }
-  uint32_t alignment() const { return alignment_; }
-  const std::string &path() const { return path_; }
+  size_t parts() const { return parts_.size(); }
+  uint64_t dataStart(size_t part = 0) const { return parts_[part].dataStart; }
+  uint32_t alignment(size_t part = 0) const { return parts_[part].alignment; }
+  const std::string &path(size_t part = 0) const { return parts_[part].path; }
 
  private:
   // GGUF value types.
   enum : uint32_t { kU8, kI8, kU16, kI16, kU32, kI32, kF32, kBool, kString, kArray, kU64, kI64, kF64 };
+  struct Part {
+    std::string path;
+    const uint8_t *base = nullptr;
+    uint64_t size = 0, at = 0, dataStart = 0;
+    uint32_t alignment = 32;
+  };
 
-  template <class T> T take() {
-    if (at_ + sizeof(T) > size_) throw GgufError(path_ + ": the header runs past the end of the file");
+  void open(const std::string &path) {
+    const int fd = ::open(path.c_str(), O_RDONLY);
+    if (fd < 0) throw GgufError("cannot open " + path);
+    struct stat st {};
+    if (::fstat(fd, &st) != 0 || st.st_size < 24) {
+      ::close(fd);
+      throw GgufError(path + " is not a GGUF file (too short)");
+    }
+    void *m = ::mmap(nullptr, size_t(st.st_size), PROT_READ, MAP_PRIVATE, fd, 0);
+    ::close(fd);
+    if (m == MAP_FAILED) throw GgufError("cannot map " + path);
+    Part part;
+    part.path = path, part.base = static_cast<const uint8_t *>(m), part.size = uint64_t(st.st_size);
+    parts_.push_back(part);
+  }
+  void close() {
+    for (Part &part : parts_)
+      if (part.base) ::munmap(const_cast<uint8_t *>(part.base), part.size);
+    parts_.clear();
+  }
+  template <class T> T take(Part &f) {
+    if (f.at + sizeof(T) > f.size) throw GgufError(f.path + ": the header runs past the end of the file");
     T v;
-    std::memcpy(&v, base_ + at_, sizeof(T));
-    at_ += sizeof(T);
+    std::memcpy(&v, f.base + f.at, sizeof(T));
+    f.at += sizeof(T);
     return v;
   }
-  std::string takeString() {
-    const uint64_t n = take<uint64_t>();
-    if (n > size_ - at_) throw GgufError(path_ + ": a string runs past the end of the file");
-    std::string s(reinterpret_cast<const char *>(base_ + at_), size_t(n));
-    at_ += n;
+  std::string takeString(Part &f) {
+    const uint64_t n = take<uint64_t>(f);
+    if (n > f.size - f.at) throw GgufError(f.path + ": a string runs past the end of the file");
+    std::string s(reinterpret_cast<const char *>(f.base + f.at), size_t(n));
+    f.at += n;
     return s;
   }
   // One scalar of `type` as (is it a float, unsigned bits, double).
-  bool takeScalar(uint32_t type, uint64_t &u, double &f) {
+  bool takeScalar(Part &f, uint32_t type, uint64_t &u, double &d) {
     switch (type) {
-      case kU8: u = take<uint8_t>(); return false;
-      case kI8: u = uint64_t(int64_t(take<int8_t>())); return false;
-      case kU16: u = take<uint16_t>(); return false;
-      case kI16: u = uint64_t(int64_t(take<int16_t>())); return false;
-      case kU32: u = take<uint32_t>(); return false;
-      case kI32: u = uint64_t(int64_t(take<int32_t>())); return false;
-      case kBool: u = take<uint8_t>() != 0; return false;
-      case kU64: u = take<uint64_t>(); return false;
-      case kI64: u = uint64_t(take<int64_t>()); return false;
-      case kF32: f = take<float>(); return true;
-      case kF64: f = take<double>(); return true;
-      default: throw GgufError(path_ + ": metadata value type " + std::to_string(type) + " is not one of GGUF's");
+      case kU8: u = take<uint8_t>(f); return false;
+      case kI8: u = uint64_t(int64_t(take<int8_t>(f))); return false;
+      case kU16: u = take<uint16_t>(f); return false;
+      case kI16: u = uint64_t(int64_t(take<int16_t>(f))); return false;
+      case kU32: u = take<uint32_t>(f); return false;
+      case kI32: u = uint64_t(int64_t(take<int32_t>(f))); return false;
+      case kBool: u = take<uint8_t>(f) != 0; return false;
+      case kU64: u = take<uint64_t>(f); return false;
+      case kI64: u = uint64_t(take<int64_t>(f)); return false;
+      case kF32: d = take<float>(f); return true;
+      case kF64: d = take<double>(f); return true;
+      default: throw GgufError(f.path + ": metadata value type " + std::to_string(type) + " is not one of GGUF's");
     }
   }
-  void parse() {
-    if (std::memcmp(base_, "GGUF", 4) != 0) throw GgufError(path_ + " is not a GGUF file (magic)");
-    at_ = 4;
-    const uint32_t version = take<uint32_t>();
-    if (version != 3) throw GgufError(path_ + ": GGUF version " + std::to_string(version) + " (version 3 is read)");
-    const uint64_t tensorCount = take<uint64_t>(), keyCount = take<uint64_t>();
-    if (tensorCount > size_ / 24 || keyCount > size_ / 12) throw GgufError(path_ + ": counts exceed what the file can hold");
+  // Part `index`: its metadata into `meta` (the first part's numeric arrays are kept), its tensors appended.
+  void parse(size_t index, GgufMetadata &meta) {
+    Part &f = parts_[index];
+    if (std::memcmp(f.base, "GGUF", 4) != 0) throw GgufError(f.path + " is not a GGUF file (magic)");
+    f.at = 4;
+    const uint32_t version = take<uint32_t>(f);
+    if (version != 3) throw GgufError(f.path + ": GGUF version " + std::to_string(version) + " (version 3 is read)");
+    const uint64_t tensorCount = take<uint64_t>(f), keyCount = take<uint64_t>(f);
+    if (tensorCount > f.size / 24 || keyCount > f.size / 12) throw GgufError(f.path + ": counts exceed what the file can hold");
     for (uint64_t k = 0; k < keyCount; ++k) {
-      const std::string key = takeString();
-      const uint32_t type = take<uint32_t>();
+      const std::string key = takeString(f);
+      const uint32_t type = take<uint32_t>(f);
       if (type == kString) {
-        metadata_.strings[key] = takeString();
+        meta.strings[key] = takeString(f);
       } else if (type == kArray) {
-        const uint32_t inner = take<uint32_t>();
-        const uint64_t n = take<uint64_t>();
-        if (inner == kArray) throw GgufError(path_ + ": nested arrays (" + key + ")");
+        const uint32_t inner = take<uint32_t>(f);
+        const uint64_t n = take<uint64_t>(f);
+        if (inner == kArray) throw GgufError(f.path + ": nested arrays (" + key + ")");
         std::vector<double> kept;
-        const bool keep = inner != kString && n <= 65536;
+        const bool keep = inner != kString && n <= 65536 && index == 0;
         for (uint64_t i = 0; i < n; ++i) {
           if (inner == kString) {
-            (void)takeString();
+            (void)takeString(f);
             continue;
           }
           uint64_t u = 0;
-          double f = 0;
-          const bool isFloat = takeScalar(inner, u, f);
-          if (keep) kept.push_back(isFloat ? f : (inner == kI8 || inner == kI16 || inner == kI32 || inner == kI64 ? double(int64_t(u)) : double(u)));
+          double d = 0;
+          const bool isFloat = takeScalar(f, inner, u, d);
+          if (keep) kept.push_back(isFloat ? d : (inner == kI8 || inner == kI16 || inner == kI32 || inner == kI64 ? double(int64_t(u)) : double(u)));
         }
         if (keep) arrays_[key] = std::move(kept);
       } else {
         uint64_t u = 0;
-        double f = 0;
-        if (takeScalar(type, u, f)) metadata_.floats[key] = f;
-        else metadata_.unsigneds[key] = u;
+        double d = 0;
+        if (takeScalar(f, type, u, d)) meta.floats[key] = d;
+        else meta.unsigneds[key] = u;
       }
     }
-    alignment_ = uint32_t(metadata_.integer("general.alignment").value_or(32));
-    if (!alignment_ || (alignment_ & (alignment_ - 1))) throw GgufError(path_ + ": general.alignment is not a power of two");
-    tensors_.reserve(size_t(tensorCount));
+    f.alignment = uint32_t(meta.integer("general.alignment").value_or(32));
+    if (!f.alignment || (f.alignment & (f.alignment - 1))) throw GgufError(f.path + ": general.alignment is not a power of two");
+    const size_t first = tensors_.size();
+    tensors_.reserve(first + size_t(tensorCount));
     for (uint64_t t = 0; t < tensorCount; ++t) {
       GgufTensor tensor;
-      tensor.name = takeString();
-      const uint32_t nd = take<uint32_t>();
-      if (nd < 1 || nd > 4) throw GgufError(path_ + ": " + tensor.name + " has " + std::to_string(nd) + " dimensions");
+      tensor.name = takeString(f);
+      const uint32_t nd = take<uint32_t>(f);
+      if (nd < 1 || nd > 4) throw GgufError(f.path + ": " + tensor.name + " has " + std::to_string(nd) + " dimensions");
       uint64_t elements = 1;
       for (uint32_t d = 0; d < nd; ++d) {
-        const uint64_t e = take<uint64_t>();
-        if (!e || elements > UINT64_MAX / e) throw GgufError(path_ + ": " + tensor.name + " has an empty or overflowing extent");
+        const uint64_t e = take<uint64_t>(f);
+        if (!e || elements > UINT64_MAX / e) throw GgufError(f.path + ": " + tensor.name + " has an empty or overflowing extent");
         elements *= e;
         tensor.dims.push_back(e);
       }
-      tensor.type = take<uint32_t>();
-      tensor.offset = take<uint64_t>();
+      tensor.type = take<uint32_t>(f);
+      tensor.offset = take<uint64_t>(f);
+      tensor.part = uint32_t(index);
       GgmlType type;
-      if (!ggmlTypeOf(tensor.type, type)) throw GgufError(path_ + ": " + tensor.name + " is of ggml type " + std::to_string(tensor.type) + ", which this reader cannot size");
-      if (tensor.dims[0] % type.blockElements) throw GgufError(path_ + ": " + tensor.name + " rows are not whole " + type.name + " blocks");
+      if (!ggmlTypeOf(tensor.type, type)) throw GgufError(f.path + ": " + tensor.name + " is of ggml type " + std::to_string(tensor.type) + ", which this reader cannot size");
+      if (tensor.dims[0] % type.blockElements) throw GgufError(f.path + ": " + tensor.name + " rows are not whole " + type.name + " blocks");
       tensor.bytes = elements / type.blockElements * type.blockBytes;
-      if (tensor.offset % alignment_) throw GgufError(path_ + ": " + tensor.name + " does not start on the file's alignment");
-      if (!index_.emplace(tensor.name, tensors_.size()).second) throw GgufError(path_ + ": two tensors named " + tensor.name);
+      if (tensor.offset % f.alignment) throw GgufError(f.path + ": " + tensor.name + " does not start on the file's alignment");
+      if (!index_.emplace(tensor.name, tensors_.size()).second) throw GgufError(f.path + ": two tensors named " + tensor.name);
       tensors_.push_back(std::move(tensor));
     }
-    dataStart_ = (at_ + alignment_ - 1) / alignment_ * alignment_;
-    for (GgufTensor &tensor : tensors_) {
-      if (dataStart_ > size_ || tensor.offset > size_ - dataStart_ || tensor.bytes > size_ - dataStart_ - tensor.offset)
-        throw GgufError(path_ + ": " + tensor.name + " lies past the end of the file");
-      tensor.data = base_ + dataStart_ + tensor.offset;
+    f.dataStart = (f.at + f.alignment - 1) / f.alignment * f.alignment;
+    for (size_t t = first; t < tensors_.size(); ++t) {
+      GgufTensor &tensor = tensors_[t];
+      if (f.dataStart > f.size || tensor.offset > f.size - f.dataStart || tensor.bytes > f.size - f.dataStart - tensor.offset)
+        throw GgufError(f.path + ": " + tensor.name + " lies past the end of the file");
+      tensor.data = f.base + f.dataStart + tensor.offset;
     }
   }
 
-  std::string path_;
-  const uint8_t *base_ = nullptr;
-  uint64_t size_ = 0, at_ = 0, dataStart_ = 0;
-  uint32_t alignment_ = 32;
+  std::vector<Part> parts_;
   GgufMetadata metadata_;
   std::map<std::string, std::vector<double>, std::less<>> arrays_;
   std::vector<GgufTensor> tensors_;

@@ -251,6 +251,27 @@ int sb_gguf_open(const char *path, void **out_file) {
     return int(SB_OK);
   });
 }
+int sb_gguf_open_parts(const char *const *paths, uint32_t count, void **out_file) {
+  if (!paths || !count || !out_file) return sb::fail(SB_ERR_INVALID, "sb_gguf_open_parts: null pointer or no part");
+  return host_guarded([&] {
+    std::vector<std::string> all;
+    for (uint32_t i = 0; i < count; ++i) {
+      if (!paths[i]) throw GgufError("sb_gguf_open_parts: null path");
+      all.emplace_back(paths[i]);
+    }
+    auto f = std::make_unique<OpenFile>();
+    f->file = std::make_unique<GgufReader>(all);
+    *out_file = f.release();
+    return int(SB_OK);
+  });
+}
+int sb_gguf_meta_array(void *file, const char *key, const double **out_values, uint64_t *out_count) {
+  if (!file || !key || !out_values || !out_count) return sb::fail(SB_ERR_INVALID, "sb_gguf_meta_array: null pointer");
+  const std::vector<double> *v = static_cast<OpenFile *>(file)->file->numericArray(key);
+  if (!v) return sb::fail(SB_ERR_INVALID, "sb_gguf_meta_array: no numeric array %s", key);
+  *out_values = v->data(), *out_count = v->size();
+  return SB_OK;
+}
 int sb_gguf_close(void *file) {
   delete static_cast<OpenFile *>(file);
   return SB_OK;

@@ -35,11 +35,25 @@ def _bind():
 
 class GgufFile:
     def __init__(self, path):
+        """path: one file, or the parts of a split GGUF in split order (a list)."""
         self.handle = None
         self.l = _bind()
         h = _P()
-        lib.check(self.l.sb_gguf_open(str(path).encode(), ctypes.byref(h)))
+        if isinstance(path, (list, tuple)):
+            paths = (ctypes.c_char_p * len(path))(*[str(p).encode() for p in path])
+            self.l.sb_gguf_open_parts.argtypes = [ctypes.POINTER(ctypes.c_char_p), _U, ctypes.POINTER(_P)]
+            lib.check(self.l.sb_gguf_open_parts(paths, len(path), ctypes.byref(h)))
+        else:
+            lib.check(self.l.sb_gguf_open(str(path).encode(), ctypes.byref(h)))
         self.handle = h.value
+
+    def array(self, key):
+        """A numeric metadata array as float64 values; None without such a key."""
+        values, n = ctypes.POINTER(ctypes.c_double)(), ctypes.c_uint64()
+        self.l.sb_gguf_meta_array.argtypes = [_P, ctypes.c_char_p, ctypes.POINTER(ctypes.POINTER(ctypes.c_double)), ctypes.POINTER(ctypes.c_uint64)]
+        if self.l.sb_gguf_meta_array(self.handle, key.encode(), ctypes.byref(values), ctypes.byref(n)) != 0:
+            return None
+        return np.array([values[i] for i in range(n.value)], np.float64)
 
     def close(self):
         if self.handle:

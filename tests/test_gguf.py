@@ -187,6 +187,36 @@ def test_reader_refuses_what_is_not_a_readable_gguf(tmp_path):
         gguf.GgufFile(tmp_path / "whole.gguf").target_config()
 
 
+def test_reader_takes_the_parts_of_a_split_file(tiny_file, tmp_path):
+    """The tiny model's tensors dealt over three parts as gguf-split writes them (every part a GGUF with split.no, split.count
+    and split.tensors.count; the model's metadata in the first): read together they are the whole file; alone, out of order or
+    short of a part they are refused."""
+    from splash_b200 import gguf, lib
+    path, cfg, w, _ = tiny_file
+    whole = gguf.GgufFile(path)
+    tensors = whole.tensors()
+    model_meta = [("general.architecture", gw.STRING, "qwen35"), ("qwen35.block_count", gw.U32, 4), ("some.array", gw.ARRAY, (gw.I32, [3, -1, 4]))]
+    cuts = [0, 20, 41, len(tensors)]
+    parts = []
+    for i in range(3):
+        meta = (model_meta if i == 0 else []) + [("split.no", gw.U16, i), ("split.count", gw.U16, 3), ("split.tensors.count", gw.I32, len(tensors))]
+        part = str(tmp_path / f"tiny-{i + 1:05d}-of-00003.gguf")
+        gw.write(part, meta, [(t["name"], t["type"], t["dims"], t["data"]) for t in tensors[cuts[i]:cuts[i + 1]]])
+        parts.append(part)
+    split = gguf.GgufFile(parts)
+    got = split.tensors()
+    assert [t["name"] for t in got] == [t["name"] for t in tensors]
+    for a, b in zip(got, tensors):
+        assert a["type"] == b["type"] and a["dims"] == b["dims"] and np.array_equal(a["data"], b["data"])
+    assert split.meta("qwen35.block_count") == 4 and split.meta("split.count") == 3
+    assert np.array_equal(split.array("some.array"), [3.0, -1.0, 4.0]) and split.array("no.such") is None
+    assert split.find("blk.3.attn_v.weight") is not None
+    for wrong, words in (([parts[1]], "part 2 of 3"), ([parts[0], parts[2], parts[1]], "given as part 2"), (parts[:2], "of 3 of a split"),
+                         ([parts[0], parts[1], parts[1]], "two tensors named")):
+        with pytest.raises(lib.SbError, match=words):
+            gguf.GgufFile(wrong)
+
+
 @pytest.mark.gpu
 def test_loader_fills_a_target_that_steps_like_the_oracle(tiny_file):
     from splash_b200 import gguf, lib
