@@ -780,7 +780,10 @@ SB_API int sb_target_reset_lanes(void *target, const uint32_t *committed_host);
 SB_API int sb_target_step(void *target, void *stream, uint32_t rows, float temperature, uint32_t flags);
 /* One verify step from host buffers: uploads the block's input tokens (row 0 the last accepted token, rows 1.. the
  * draft) and the uniforms, runs the step, downloads {retained, accepted, retained_rows, 0} and the retained tokens,
- * and waits. */
+ * and waits. The results are checked before they are handed back (the reference's finalizeDecode,
+ * runtime/model/Runtime.cpp:2943-2977): 1 <= retained <= rows, the retained rows a mask of that many rows with the anchor, accepted
+ * below rows and at most retained, every retained token one of the vocabulary; SB_ERR_DEVICE otherwise (e.g. a row whose
+ * admission left it no token selects 0xFFFFFFFF), with the outputs filled in for inspection. */
 SB_API int sb_target_verify(void *target, void *stream, const uint32_t *tokens_host, const float *uniforms_host, uint32_t rows,
                             float temperature, uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host);
 /* sb_target_verify for a target of several lanes: tokens_host u32 [lanes][16] (a lane's block in its 16 slots, rows of them used),

@@ -135,6 +135,7 @@ struct Target {
   std::map<std::tuple<uint32_t, uint32_t, uint32_t, uint32_t, uint32_t>, cudaGraphExec_t> graphs;  // rows, temperature bits, parity, advance, bound
   uint32_t launches = 0;
   uint32_t *results_pinned = nullptr;  // 4 + 16 words
+  uint32_t lane_rows_host[64] = {};    // the lanes' row counts of the ragged step in flight
   cudaStream_t own_stream = nullptr;   // used when the caller passes no stream (the default stream cannot be captured)
   cudaStream_t pick(void *s) const { return s ? as_stream(s) : own_stream; }
 };
@@ -545,6 +546,21 @@ int sb_target_step(void *target, void *stream, uint32_t rows, float temperature,
   return run_step(static_cast<Target *>(target), static_cast<Target *>(target)->pick(stream), rows, temperature, flags);
 }
 
+// What a step's results must satisfy before a host acts on them (the reference's finalizeDecode,
+// runtime/model/Runtime.cpp:2943-2977): 1 <= retained <= rows, the retained rows a mask of that many rows with the anchor among
+// them and none past the block, accepted < rows and <= retained, and every retained token one of the vocabulary (a row without
+// a selectable logit selects the sentinel 0xFFFFFFFF, which must not be retained as a token).
+static int check_lane_results(const uint32_t *results, const uint32_t *tokens, uint32_t rows, uint32_t vocab, uint32_t lane) {
+  const uint32_t retained = results[0], accepted = results[1], mask = results[2];
+  if (!rows) return retained || accepted || mask ? fail(SB_ERR_DEVICE, "lane %u: a lane without rows retained %u tokens", lane, retained) : int(SB_OK);
+  if (!retained || retained > rows || uint32_t(__builtin_popcount(mask)) != retained || !(mask & 1u) || (mask >> (rows - 1)) > 1u)
+    return fail(SB_ERR_DEVICE, "lane %u: invalid retention (retained %u of %u rows, rows 0x%x)", lane, retained, rows, mask);
+  if (accepted >= rows || accepted > retained) return fail(SB_ERR_DEVICE, "lane %u: accepted %u of %u rows, retained %u", lane, accepted, rows, retained);
+  for (uint32_t i = 0; i < retained; ++i)
+    if (tokens[i] >= vocab) return fail(SB_ERR_DEVICE, "lane %u: retained token %u is 0x%x, not one of the vocabulary's %u (a row without a selectable logit)", lane, i, tokens[i], vocab);
+  return SB_OK;
+}
+
 int sb_target_verify(void *target, void *stream, const uint32_t *tokens_host, const float *uniforms_host, uint32_t rows, float temperature,
                      uint32_t flags, uint32_t *out_tokens_host, uint32_t *out_results_host) {
   SB_NEED_DEVICE();
@@ -565,8 +581,8 @@ int sb_target_verify(void *target, void *stream, const uint32_t *tokens_host, co
   SB_CUDA(cudaStreamSynchronize(s));
   memcpy(out_results_host, t->results_pinned, 16);
   memcpy(out_tokens_host, t->results_pinned + 4, rows * 4);
-  if (flags & SB_TARGET_ADVANCE) m.committedHost = before + t->results_pinned[0];  // the exact position again
-  return SB_OK;
+  if (flags & SB_TARGET_ADVANCE) m.committedHost = before + std::min(t->results_pinned[0], rows);  // the exact position again
+  return check_lane_results(t->results_pinned, t->results_pinned + 4, rows, m.config().vocab, 0);
 }
 
 int sb_target_verify_lanes(void *target, void *stream, const uint32_t *tokens_host, const float *uniforms_host, uint32_t rows, float temperature,
@@ -591,8 +607,13 @@ int sb_target_verify_lanes(void *target, void *stream, const uint32_t *tokens_ho
   memcpy(out_tokens_host, t->results_pinned + 4 * L, size_t(16) * L * 4);
   if (flags & SB_TARGET_ADVANCE) {  // the exact bound again: the furthest lane
     uint32_t most = 0;
-    for (uint32_t l = 0; l < L; ++l) most = std::max(most, t->results_pinned[4 * l]);
+    for (uint32_t l = 0; l < L; ++l) most = std::max(most, std::min(t->results_pinned[4 * l], rows));
     m.committedHost = std::min(m.config().max_context, before + most);
+  }
+  for (uint32_t l = 0; l < L; ++l) {
+    const uint32_t lane_rows = (flags & kRaggedStep) ? std::min(t->lane_rows_host[l], rows) : rows;
+    const int st = check_lane_results(t->results_pinned + 4 * l, t->results_pinned + 4 * L + 16 * l, lane_rows, m.config().vocab, l);
+    if (st != SB_OK) return st;
   }
   return SB_OK;
 }
@@ -610,7 +631,8 @@ int sb_target_verify_lanes_ragged(void *target, void *stream, const uint32_t *to
     most = std::max(most, lane_rows_host[l]);
   }
   SB_REQUIRE(most >= 1, "sb_target_verify_lanes_ragged: no lane has a row");
-  SB_CUDA(cudaMemcpyAsync(m.laneRows.as(), lane_rows_host, size_t(4) * m.lanes(), cudaMemcpyHostToDevice, t->pick(stream)));
+  memcpy(t->lane_rows_host, lane_rows_host, size_t(4) * m.lanes());
+  SB_CUDA(cudaMemcpyAsync(m.laneRows.as(), t->lane_rows_host, size_t(4) * m.lanes(), cudaMemcpyHostToDevice, t->pick(stream)));
   return sb_target_verify_lanes(target, stream, tokens_host, uniforms_host, most, temperature, flags | kRaggedStep, out_tokens_host, out_results_host);
 }
 

@@ -330,6 +330,12 @@ def test_tiny_model_step_under_an_admission_matches_oracle(flags_name):
         assert np.array_equal(got_tokens, want["tokens"])
     for tok in got_tokens:
         assert int(tok) not in excluded
+    # a row whose mask admits nothing selects the sentinel; the step's results are refused when such a token is retained
+    none = masks.copy()
+    none[0] = 0
+    t.upload(-1, "constraint_masks", none)
+    with pytest.raises(lib.SbError, match="not one of the vocabulary"):
+        t.verify(tokens, flags=flags)
     t.set_admission(False, ())
     got_tokens, retained, accepted, mask = t.verify(tokens, flags=flags)
     top2 = np.sort(plain["logits"], axis=1)[:, -2:]
