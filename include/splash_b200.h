@@ -806,6 +806,23 @@ SB_API int sb_target_verify_tree(void *target, void *stream, const uint32_t *tok
 /* The configuration the target was created with. */
 SB_API int sb_target_config(void *target, SbTargetConfig *out_config);
 
+/* ---- KV page pool ----
+ * The pages of a target's INT8 cache as a pool its lanes draw from (the acquire / release of the reference's
+ * engine::KvPool, runtime/engine/KvPool.hpp, for a fixed set of pages: no extents, no compaction, no shared prefixes). A lane
+ * acquires the pages of the tokens it is about to hold (its position plus the step's rows) and releases them when its request
+ * ends; SB_ERR_OOM, with nothing taken, when the pool cannot give them (the reference's KvPageAcquisition::failure).
+ * sb_kv_pool_write_tables copies the lanes' page ids into the target's `page_table` (synchronous; between steps). A target
+ * starts with every lane holding its own equal share of the pages; a pool made by sb_kv_pool_for_target takes all of them
+ * over, with a lane's most pages the share it had. Host bookkeeping: everything but write_tables works without a device. */
+SB_API int sb_kv_pool_create(uint32_t pages, uint32_t lanes, uint32_t lane_cap_pages, uint32_t page_tokens, void **out_pool);
+SB_API int sb_kv_pool_for_target(void *target, void **out_pool);
+SB_API int sb_kv_pool_destroy(void *pool);
+SB_API int sb_kv_pool_acquire(void *pool, uint32_t lane, uint64_t tokens);
+SB_API int sb_kv_pool_release(void *pool, uint32_t lane);
+SB_API int sb_kv_pool_table(void *pool, uint32_t lane, const uint32_t **out_pages, uint32_t *out_count);
+SB_API int sb_kv_pool_counts(void *pool, uint32_t *out_free, uint32_t *out_held);
+SB_API int sb_kv_pool_write_tables(void *pool, void *target);
+
 /* ---- prompt lookup ----
  * Proposals a request's own tokens make (the reference's LookupIndex, runtime/model/LookupProposals.hpp:17-66; step 1 of a
  * decode cycle, where the host proposes a lane's lookup chain): the index holds the request's tokens, its prompt and then
