@@ -9,6 +9,7 @@
 //               top_p), startOf, reject,
 //               referenceSelection (child tests and the residual draw),
 //               referenceBest / referenceArgmax (the greedy order)
+//   RMSNorm     normWeight, rmsNorm, roundedOnceToBf16   dev/tests/engine/NormReference.hpp
 // Those functions are plain C++ inside Objective-C++ test files. The build recipe (Makefile, target
 // `ref`) cuts their text out of the files where they lie in the reference tree into a scratch folder that
 // it deletes after the compile, and this file includes the cuts between stand-ins for the tests'
@@ -304,4 +305,36 @@ REF_API int ref_sample_row(const float *logits, uint32_t vocab, float temperatur
   *ambiguous = target.ambiguousMass;
   if (probabilities) std::copy(target.probabilities.begin(), target.probabilities.end(), probabilities);
   return 0;
+}
+
+// ---- RMSNorm ---------------------------------------------------------------------------------------
+// The header's functions are inline in namespace splash::test behind includes of the Metal backend; their text is cut
+// like the models above, between a stand-in for the weights' buffer.
+namespace norm_model {
+namespace ops {
+struct Contents {
+  const void *p;
+  const void *contents() const { return p; }
+};
+struct NormWeights {
+  Contents buffer;
+  bool float32;
+};
+}  // namespace ops
+using splash::test::bf16ToFloat;
+using splash::test::ulpBf16;
+#include "norm_model.inc"
+}  // namespace norm_model
+
+// The fp64 norm of `rows` bf16 rows of `size` values with fp32 weights; `once` (optional, u8 a value) says whether the bf16
+// value `got` holds there is the exact one rounded once, by the reference's own test.
+REF_API void ref_rmsnorm(const uint16_t *x, uint32_t rows, uint32_t size, const float *weights, double *out, const uint16_t *got, uint8_t *once) {
+  const norm_model::ops::NormWeights norm{{weights}, true};
+  for (uint32_t r = 0; r < rows; ++r) {
+    const std::vector<double> exact = norm_model::rmsNorm(x + size_t(r) * size, norm, size);
+    for (uint32_t i = 0; i < size; ++i) {
+      out[size_t(r) * size + i] = exact[i];
+      if (got && once) once[size_t(r) * size + i] = norm_model::roundedOnceToBf16(got[size_t(r) * size + i], exact[i]);
+    }
+  }
 }

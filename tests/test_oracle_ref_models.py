@@ -287,3 +287,24 @@ def test_admission_matches_the_reference_model(temperature):
             assert one[0] == 0xffffffff
             o.so_sample_verify(P(mine[4]), vocab, vocab, 1, P(np.zeros(1, np.uint32)), temperature, P(uniforms), P(one), None)
             assert one[0] == 40 * 32 + 7
+
+
+def test_rmsnorm_matches_the_reference_model():
+    """so_rmsnorm against the reference's fp64 norm (dev/tests/engine/NormReference.hpp rmsNorm): every value the exact one
+    rounded once to bf16 by the reference's own criterion (roundedOnceToBf16), rows of small and large magnitudes."""
+    ref = _models()
+    ref.ref_rmsnorm.argtypes = [_V, _U, _U, _V, _V, _V, _V]
+    o = ol.bind_ops(ol.load())
+    o.so_rmsnorm.argtypes = [_V, _U, _U, _U, _V, _V, _U]
+    rng = np.random.default_rng(29)
+    rows, size = 16, 5120
+    x = (rng.standard_normal((rows, size)) * np.exp(rng.uniform(-6, 6, (rows, 1)))).astype(np.float32)
+    x[3] = 0.0                                            # a row of zeros: the epsilon alone
+    xb = ol.f2bf(x)
+    w = (1 + 0.1 * rng.standard_normal(size)).astype(np.float32)
+    got = np.zeros((rows, size), np.uint16)
+    o.so_rmsnorm(P(xb), rows, size, size, P(w), P(got), size)
+    exact, once = np.zeros((rows, size)), np.zeros((rows, size), np.uint8)
+    ref.ref_rmsnorm(P(xb), rows, size, P(w), P(exact), P(got), P(once))
+    assert once.all(), int((once == 0).sum())
+    assert np.mean(ol.bf2f(got) != ol.bf2f(ol.f2bf(exact.astype(np.float32)))) < 2e-3   # (fp32 sums move a value on a rounding boundary)
