@@ -67,7 +67,7 @@ class GgufFile:
     def _view(t):
         dims = [int(t.dims[d]) for d in range(t.n_dims)]
         data = np.ctypeslib.as_array(ctypes.cast(t.data, ctypes.POINTER(ctypes.c_uint8)), (int(t.bytes),)) if t.bytes else np.zeros(0, np.uint8)
-        return dict(name=t.name.decode(), type=int(t.type), dims=dims, data=data)
+        return dict(name=t.name.decode(errors="replace"), type=int(t.type), dims=dims, data=data)
 
     def tensors(self):
         n = ctypes.c_uint64()

@@ -86,7 +86,7 @@ def load():
 
 def check(status):
     if status != 0:
-        raise SbError(f"splash_b200 status {status}: {load().sb_last_error().decode()}")
+        raise SbError(f"splash_b200 status {status}: {load().sb_last_error().decode(errors='replace')}")
 
 
 def device_count():

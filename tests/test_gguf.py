@@ -349,3 +349,44 @@ def test_a_file_of_mixed_formats_loads_and_steps_like_the_oracle(tmp_path, lanes
             assert err.max() <= 2e-2 * scale and np.median(err) <= 2e-3 * scale, (step, i)
             states[i]["committed"] += got[i][1] - want["retained"]     # follow the device's own choice at near ties
             states[i]["pending_rows"] = got[i][1]
+
+
+def test_reader_survives_damaged_files(tmp_path):
+    """Truncations and flipped bytes of a small valid file: the reader opens what is still a GGUF and refuses the rest with an
+    error; it never reads outside the mapping (a fault would end the test run)."""
+    from splash_b200 import gguf, lib
+    meta = [("general.architecture", gw.STRING, "qwen35"), ("a.count", gw.U32, 7), ("a.list", gw.ARRAY, (gw.F32, [1.0, 2.0, 3.0])),
+            ("a.names", gw.ARRAY, (gw.STRING, ["x", "yy", "zzz"])), ("a.flag", gw.BOOL, 1), ("a.big", gw.U64, 2 ** 40)]
+    tensors = [("t0", 0, [8, 4], np.arange(32, dtype=np.float32)), ("t1", 12, [256, 2], np.zeros(288, np.uint8)),
+               ("t2", 30, [16], np.zeros(16, np.uint16))]
+    good = tmp_path / "good.gguf"
+    gw.write(good, meta, tensors)
+    raw = bytearray(open(good, "rb").read())
+    rng = np.random.default_rng(1)
+    opened = refused = 0
+    for trial in range(400):
+        data = bytearray(raw)
+        kind = trial % 4
+        if kind == 0:
+            data = data[:int(rng.integers(0, len(data)))]
+        elif kind == 1:
+            for _ in range(int(rng.integers(1, 4))):
+                data[int(rng.integers(0, min(len(data), 400)))] = int(rng.integers(0, 256))      # in the header
+        elif kind == 2:
+            at = int(rng.integers(0, min(len(data), 400) - 8))
+            data[at:at + 8] = (2 ** 64 - 1 - int(rng.integers(0, 1000))).to_bytes(8, "little")    # a huge count, length or offset
+        else:
+            at = int(rng.integers(0, min(len(data), 400) - 4))
+            data[at:at + 4] = int(rng.integers(0, 2 ** 32)).to_bytes(4, "little")
+        path = tmp_path / "damaged.gguf"
+        open(path, "wb").write(bytes(data))
+        try:
+            f = gguf.GgufFile(path)
+            for t in f.tensors():
+                assert len(t["data"]) == 0 or int(t["data"][0]) >= 0 and int(t["data"][-1]) >= 0   # the tensor's bytes are inside the mapping
+            f.meta("a.count"), f.array("a.list")
+            f.close()
+            opened += 1
+        except lib.SbError:
+            refused += 1
+    assert opened + refused == 400 and refused >= 150 and opened >= 20, (opened, refused)
